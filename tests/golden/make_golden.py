@@ -1,0 +1,501 @@
+"""Generates the golden fixtures of this folder from the reference implementation itself.
+
+Run where the reference checkout is available (it is NOT needed to run the tests):
+
+    python tests/golden/make_golden.py --reference /path/to/hsn
+
+It imports the reference's own CPU code (``python/hsn``) and dumps, for small seeded cases, the
+inputs and outputs of every function on the window path as ``.npz`` files:
+
+* ``select_*.npz``      ``Router.select`` (``python/hsn/model/router.py:1263``): tie-heavy logits, stale
+                        ages, budget cuts, cost penalties, reserved slots.
+* ``update_*.npz``      ``PDGCell.step_sparse`` + ``CellGraphState.tick``
+                        (``python/hsn/model/cell.py:349``, ``python/hsn/model/state.py:316``) on the
+                        products of ``PDGCell.sparse_products`` (``cell.py:507``).
+* ``recurrence_*.npz``  ``recurrence_backward`` (``python/hsn/train/split.py:128``).
+* ``window_*.npz``      a whole split window: the prologue's inputs, every weight, the eager sweep's
+                        tape (``python/hsn/train/compile.py:1234``), the replay's record, the arguments
+                        and results of ``state_gradient_backward``
+                        (``python/hsn/train/state_gradient.py:357``) with its ``A``/``R`` trace.
+* ``chain_*.npz``       two chained windows against the unsplit window of twice the length: the
+                        carried state forward, the state cotangent ``(A, R)`` backward.
+
+Nothing here is read at test time except the ``.npz`` files it wrote.
+"""
+
+from __future__ import annotations
+
+import argparse
+import sys
+import tempfile
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+
+
+def _import_reference(root: Path) -> None:
+    stub = Path(tempfile.mkdtemp()) / "hsn-0.1.0.dist-info"
+    stub.mkdir(parents=True)
+    (stub / "METADATA").write_text("Metadata-Version: 2.1\nName: hsn\nVersion: 0.1.0\n")
+    sys.path[:0] = [str(stub.parent), str(root / "python"), str(root / "tests")]
+
+
+def _np(x):
+    import torch
+
+    if isinstance(x, torch.Tensor):
+        x = x.detach().cpu()
+        if x.dtype == torch.bool:
+            return x.numpy().astype(np.uint8)
+        if x.dtype == torch.bfloat16:
+            return x.float().numpy()
+        return x.numpy()
+    return np.asarray(x)
+
+
+def _cfg(root: Path, *, B, T, N, d, K, H, M, D, fd, extra=(), precision="fp32"):
+    from hsn.config import load_config
+
+    return load_config(
+        root / "configs" / "ref_a1.yaml",
+        overrides=[
+            "profile=cpu",
+            f"model.d={d}",
+            f"model.context_dim={d}",
+            f"model.n_cells={N}",
+            f"model.in_degree={D}",
+            f"model.n_units={M}",
+            f"model.k_select={K}",
+            f"model.hidden={H}",
+            "model.routing=topk",
+            "train.gate_mode=ste",
+            "model.key_address=true",
+            "model.selected_readout=true",
+            "model.cand_norm=rms",
+            "model.budget=1.0",
+            "model.lambda_cost=0",
+            "model.init=trunc_normal_0.02",
+            "model.state_init=trunc_normal_0.02",
+            f"train.unroll={T}",
+            f"train.batch={B}",
+            f"train.micro_batch={B}",
+            f"train.precision={precision}",
+            f"train.feedback_detach={fd}",
+            *extra,
+        ],
+    )
+
+
+def _model(cfg, dtype, perturb: float):
+    import torch
+    from hsn.device import seed_everything
+    from hsn.model.hsn import HSN
+
+    seed_everything(0)
+    model = HSN.from_config(cfg).to(dtype)
+    if perturb:
+        with torch.no_grad():
+            for p in model.parameters():
+                p.add_(perturb * torch.randn_like(p))
+    return model.train()
+
+
+def _weights(model) -> dict[str, np.ndarray]:
+    """Every weight the window reads, in torch's own layouts (``nn.Linear``: ``[out, in]``)."""
+    from hsn.model.router import BUDGET_SLACK
+
+    cell, router = model.cell, model.router
+    scorer = model.scorer
+    with cell.window():
+        edge_w = cell.graph._padded_weights().detach().clone()
+    out = {
+        "s_w1": model.shared.fc1.weight, "s_b1": model.shared.fc1.bias,
+        "s_w2": model.shared.fc2.weight, "s_b2": model.shared.fc2.bias,
+        "p_w1": model.predictor.fc1.weight, "p_b1": model.predictor.fc1.bias,
+        "p_w2": model.predictor.fc2.weight, "p_b2": model.predictor.fc2.bias,
+        "score_w": scorer.net.weight, "score_b": scorer.net.bias,
+        "v_w": cell.V.weight, "wout_w": cell.W_out.weight,
+        "gate_w": cell.gate.weight, "gate_b": cell.gate.bias,
+        "norm_w": cell.norm.weight, "cand_w": cell.cand_norm.weight,
+        "w1": cell.units.W1, "b1": cell.units.b1, "w2": cell.units.W2, "b2": cell.units.b2,
+        "pad_src": cell.graph._pad_src, "edge_w": edge_w, "cost": router.cost_table,
+    }  # fmt: skip
+    out = {k: _np(v) for k, v in out.items()}
+    out["scalars_f"] = np.array(
+        [
+            float(router.age_max),
+            float(router.lambda_cost),
+            float(router.cell_overhead),
+            float(router.shared_cost),
+            float(model.cfg.budget) * (1.0 + BUDGET_SLACK),
+            float(cell.norm.eps),
+            float(cell.cand_norm.eps),
+        ],
+        dtype=np.float64,
+    )
+    return out
+
+
+# --------------------------------------------------------------------------------------------------
+
+
+def make_select(root: Path) -> None:
+    import torch
+    from hsn.model.router import BUDGET_SLACK
+    from test_a6_feedback_detach import A5, ALL, _cfg as ref_cfg, _model as ref_model
+
+    sets = {
+        "plain": (),
+        "probes": ("model.age_max=2",),
+        "budget": ("model.budget=0.1",),
+        "probes_budget": ("model.age_max=2", "model.budget=0.1"),
+        "cost": ("model.lambda_cost=0.05", "model.age_max=3"),
+    }
+    for name, overrides in sets.items():
+        cfg = ref_cfg(*A5, ALL, "model.cand_norm=rms", *overrides)
+        router = ref_model(cfg).router.to(dtype=torch.float32)
+        N, M, K = cfg.model.n_cells, cfg.model.n_units, cfg.model.k_select
+        g = torch.Generator().manual_seed(7)
+        out: dict[str, np.ndarray] = {}
+        n = 0
+        for trial in range(40):
+            B = 1 + trial % 5
+            logits = torch.randn(B, N, M, generator=g)
+            if trial % 2:
+                logits = (logits * 2).round() / 2
+            age = torch.randint(0, 2 * int(router.age_max) + 2, (B, N), generator=g)
+            if trial % 3 == 0:
+                age = (age // 3) * 3
+            for probes in (True, False):
+                want = router.select(
+                    logits, cfg.model.budget, K, cfg.model.k_min, "topk", gate=None,
+                    age=age if probes else None,
+                )  # fmt: skip
+                pre = f"t{n}_"
+                out[pre + "logits"] = _np(logits)
+                out[pre + "age"] = _np(age)
+                out[pre + "probes"] = np.array(int(probes))
+                out[pre + "cells"] = _np(want.cell_idx)
+                out[pre + "units"] = _np(want.unit_idx)
+                out[pre + "valid"] = _np(want.valid)
+                out[pre + "theta"] = _np(want.threshold)
+                out[pre + "refreshed"] = _np(want.refreshed)
+                n += 1
+        out["n"] = np.array(n)
+        out["cost"] = _np(router.cost_table)
+        out["params"] = np.array(
+            [
+                K,
+                int(router.age_max),
+                float(router.lambda_cost),
+                float(router.cell_overhead),
+                float(router.shared_cost),
+                float(cfg.model.budget) * (1.0 + BUDGET_SLACK),
+            ],
+            dtype=np.float64,
+        )
+        np.savez_compressed(HERE / f"select_{name}.npz", **out)
+    # amendment A8's reserved slots (router.py:1640-1648): a larger router, fixed and free units
+    cfg = _cfg(root, B=2, T=4, N=12, d=8, K=5, H=8, M=4, D=2, fd="[summary,eps,state,router]",
+               extra=("model.age_max=2",))  # fmt: skip
+    router = _model(cfg, torch.float32, 0.3).router
+    g = torch.Generator().manual_seed(9)
+    out = {}
+    n = 0
+    for trial in range(16):
+        logits = (torch.randn(3, 12, 4, generator=g) * 2).round() / 2
+        age = torch.randint(0, 6, (3, 12), generator=g)
+        for fixed_units in (False, True):
+            want = router.select(
+                logits, cfg.model.budget, 5, cfg.model.k_min, "topk", gate=None, age=age,
+                reserved=2, reserved_units=fixed_units,
+            )  # fmt: skip
+            pre = f"t{n}_"
+            out[pre + "logits"] = _np(logits)
+            out[pre + "age"] = _np(age)
+            out[pre + "probes"] = np.array(1)
+            out[pre + "fixed_units"] = np.array(int(fixed_units))
+            out[pre + "cells"] = _np(want.cell_idx)
+            out[pre + "units"] = _np(want.unit_idx)
+            out[pre + "valid"] = _np(want.valid)
+            out[pre + "theta"] = _np(want.threshold)
+            out[pre + "refreshed"] = _np(want.refreshed)
+            n += 1
+    out["n"] = np.array(n)
+    out["cost"] = _np(router.cost_table)
+    out["params"] = np.array(
+        [5, int(router.age_max), float(router.lambda_cost), float(router.cell_overhead),
+         float(router.shared_cost), float(cfg.model.budget) * (1.0 + BUDGET_SLACK), 2],
+        dtype=np.float64,
+    )  # fmt: skip
+    np.savez_compressed(HERE / "select_reserved.npz", **out)
+
+
+def make_update(root: Path) -> None:
+    import torch
+    from test_a6_feedback_detach import A5, ALL, _cfg as ref_cfg, _model as ref_model
+
+    sets = {
+        "rms": ("model.cand_norm=rms",),
+        "none": ("model.cand_norm=none",),
+        "budget": ("model.cand_norm=rms", "model.budget=0.1"),
+    }
+    for name, extra in sets.items():
+        cfg = ref_cfg(*A5, ALL, *extra)
+        model = ref_model(cfg).to(dtype=torch.float32)
+        cell, router = model.cell, model.router
+        N, d, K = cfg.model.n_cells, cfg.model.d, cfg.model.k_select
+        g = torch.Generator().manual_seed(11)
+        B = 5
+        state = model.init_state(B)
+        out: dict[str, np.ndarray] = {}
+        with torch.no_grad(), cell.window():
+            consts = cell.window_consts()
+            for step in range(12):
+                u = torch.randn(B, d, generator=g)
+                eps = torch.randn(B, d, generator=g)
+                logits = torch.randn(B, N, cfg.model.n_units, generator=g)
+                sel = router.select(logits, cfg.model.budget, K, cfg.model.k_min, "topk", gate=None)
+                _, info = cell.step_sparse(u, eps, state, sel, static=True, consts=consts)
+                want = info["state"].tick(info["selected"])
+                gate, y = cell.sparse_products(
+                    u, eps, state, sel.cell_idx, sel.unit_idx, sel.valid, consts
+                )
+                pre = f"s{step}_"
+                for key, value in (
+                    ("y", y), ("gate", gate), ("h", state.h), ("q", state.q), ("age", state.age),
+                    ("pos", state.pos), ("cells", sel.cell_idx), ("valid", sel.valid),
+                    ("h_next", want.h), ("q_next", want.q), ("age_next", want.age),
+                    ("pos_next", want.pos),
+                ):  # fmt: skip
+                    out[pre + key] = _np(value)
+                state = want
+        out["n"] = np.array(12)
+        out["cand_w"] = _np(cell.cand_norm.weight if name != "none" else cell.norm.weight)
+        out["cand_norm"] = np.array(int(name != "none"))
+        out["cand_eps"] = np.array(float(cell.cand_norm.eps) if name != "none" else 0.0)
+        np.savez_compressed(HERE / f"update_{name}.npz", **out)
+
+
+def make_recurrence(root: Path) -> None:
+    import torch
+    from hsn.train.split import dense_recurrence_backward, recurrence_backward
+
+    shapes = {"a": (3, 7, 5, 3, 4), "b": (1, 1, 2, 1, 1), "c": (3, 9, 9, 9, 37), "d": (2, 6, 40, 6, 20)}
+    for name, (B, T, N, K, d) in shapes.items():
+        g = torch.Generator().manual_seed(B + T + N + K + d)
+        cells = torch.stack(
+            [torch.stack([torch.randperm(N, generator=g)[:K] for _ in range(T)]) for _ in range(B)]
+        )
+        valid = torch.rand(B, T, K, generator=g) > 0.25
+        reset = torch.rand(B, T, generator=g) < 0.05
+        case = {
+            "c": torch.rand(B, T, K, d, generator=g, dtype=torch.float64) * 2 - 1,
+            "b": torch.rand(B, T, K, d, generator=g, dtype=torch.float64),
+            "h_old": torch.rand(B, T, K, d, generator=g, dtype=torch.float64) * 2 - 1,
+            "cells": torch.where(valid, cells, torch.zeros_like(cells)),
+            "valid": valid,
+            "reset": reset,
+            "pre": torch.randn(B, T, d, generator=g, dtype=torch.float64),
+            "post": torch.randn(B, T, d, generator=g, dtype=torch.float64),
+            "sel": torch.randn(B, T, K, d, generator=g, dtype=torch.float64),
+        }
+        out = {k: _np(v) for k, v in case.items()}
+        out["N"] = np.array(N)
+        for tag, present in (("111", (1, 1, 1)), ("010", (0, 1, 0)), ("101", (1, 0, 1))):
+            cots = [case[k] if on else None for k, on in zip(("pre", "post", "sel"), present)]
+            dc, db = recurrence_backward(
+                case["c"], case["b"], case["h_old"], case["cells"], valid, reset, N, *cots
+            )
+            out[f"dc_{tag}"], out[f"db_{tag}"] = _np(dc), _np(db)
+        # the dense-fallback rows' recurrence (split.py:177): every cell is a slot
+        cN = torch.rand(B, T, N, d, generator=g, dtype=torch.float64) * 2 - 1
+        bN = torch.rand(B, T, N, d, generator=g, dtype=torch.float64)
+        hN = torch.rand(B, T, N, d, generator=g, dtype=torch.float64) * 2 - 1
+        dcN, dbN = dense_recurrence_backward(cN, bN, hN, reset, N, case["pre"], case["post"])
+        out.update(dense_c=_np(cN), dense_b=_np(bN), dense_h=_np(hN), dense_dc=_np(dcN), dense_db=_np(dbN))
+        np.savez_compressed(HERE / f"recurrence_{name}.npz", **out)
+
+
+def _run_window(root, cfg, model, dtype, tokens, ctx, reset, state, *, initial=None, cot_seed=5):
+    """One split window of the reference on the CPU, every intermediate captured."""
+    import torch
+    import hsn.train.split as split
+    import hsn.train.state_gradient as sg
+    from hsn.train.split import SplitWindow
+
+    captured: dict[str, object] = {}
+    real_tape, real_sweep, real_rec = split.run_tape, sg.state_gradient_backward, split.recurrence_backward
+    real_prologue = model._window_prologue
+
+    def tape_spy(*args, **kwargs):
+        tape = real_tape(*args, **kwargs)
+        captured["tape"] = {k: v.clone() for k, v in tape.items()}
+        return tape
+
+    def prologue_spy(*args, **kwargs):
+        pro = real_prologue(*args, **kwargs)
+        captured["pro"] = pro
+        return pro
+
+    def sweep_spy(*args, **kwargs):
+        trace: dict[str, torch.Tensor] = {}
+        kwargs = dict(kwargs, trace=trace, initial=initial)
+        result = real_sweep(*args, **kwargs)
+        captured["sweep_args"] = args
+        captured["sweep_out"] = result
+        captured["trace"] = trace
+        return result
+
+    def rec_spy(*args):
+        result = real_rec(*args)
+        captured["rec_args"] = args
+        captured["rec_out"] = result
+        return result
+
+    split.run_tape, sg.state_gradient_backward, split.recurrence_backward = tape_spy, sweep_spy, rec_spy
+    model._window_prologue = prologue_spy
+    try:
+        win = SplitWindow(model, cfg, None)
+        logits, final, info = win(tokens, ctx, state, reset)
+        g = torch.Generator().manual_seed(cot_seed)
+        weight = torch.randn(logits.shape, generator=g, dtype=torch.float64).to(logits.dtype)
+        loss = (logits * weight).sum() / logits.shape[0]
+        model.zero_grad(set_to_none=True)
+        loss.backward()
+    finally:
+        split.run_tape, sg.state_gradient_backward, split.recurrence_backward = real_tape, real_sweep, real_rec
+        model._window_prologue = real_prologue
+    captured["final"] = final
+    captured["logits"] = logits.detach()
+    return captured
+
+
+def _dump_window(path: Path, model, cap, reset, state) -> None:
+    pro = cap["pro"]
+    out = {f"w_{k}": v for k, v in _weights(model).items()}
+    out.update(
+        z=_np(pro.z), ctx=_np(pro.context), scalars=_np(pro.scalars), reset=_np(reset),
+        h0=_np(state.h), q0=_np(state.q), age0=_np(state.age), pos0=_np(state.pos),
+    )  # fmt: skip
+    for key, value in cap["tape"].items():
+        out[f"tape_{key}"] = _np(value)
+    if "sweep_args" in cap:
+        (c, b, h_old, cells, units, valid, rst, n_cells, d_q_pre, d_q_post, d_h_sel, d_h_fast,
+         record, consts) = cap["sweep_args"]  # fmt: skip
+        out.update(
+            bw_c=_np(c), bw_b=_np(b), bw_h_old=_np(h_old), bw_cells=_np(cells), bw_units=_np(units),
+            bw_valid=_np(valid), bw_dc=_np(cap["sweep_out"][0]), bw_db=_np(cap["sweep_out"][1]),
+            bw_A=_np(cap["trace"]["A"]), bw_R=_np(cap["trace"]["R"]),
+            bw_dh=_np(cap["trace"]["dh"]), bw_dvm=_np(cap["trace"]["dvm"]),
+        )  # fmt: skip
+        for name, cot in (("d_q_pre", d_q_pre), ("d_q_post", d_q_post), ("d_h_sel", d_h_sel)):
+            if cot is not None:
+                out[f"bw_{name}"] = _np(cot)
+        for key, value in record.items():
+            out[f"rec_{key}"] = _np(value)
+    if "rec_args" in cap:
+        c, b, h_old, cells, valid, rst, n_cells, d_q_pre, d_q_post, d_h_sel = cap["rec_args"]
+        out.update(
+            bw_c=_np(c), bw_b=_np(b), bw_h_old=_np(h_old), bw_cells=_np(cells), bw_valid=_np(valid),
+            bw_dc=_np(cap["rec_out"][0]), bw_db=_np(cap["rec_out"][1]),
+        )  # fmt: skip
+        for name, cot in (("d_q_pre", d_q_pre), ("d_q_post", d_q_post), ("d_h_sel", d_h_sel)):
+            if cot is not None:
+                out[f"bw_{name}"] = _np(cot)
+    np.savez_compressed(path, **out)
+
+
+def _inputs(cfg, B, T, p_reset, seed=1):
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+    tokens = torch.randint(0, cfg.model.vocab_size, (B, T), generator=g)
+    ctx = torch.randint(0, cfg.model.n_context, (B, T), generator=g)
+    reset = torch.rand(B, T, generator=g) < p_reset
+    reset[:, 0] = True
+    return tokens, ctx, reset
+
+
+def make_windows(root: Path) -> None:
+    import torch
+
+    SG, FULL = "[summary,eps,router]", "[summary,eps,state,router]"
+    cases = {
+        # config 1 of the benchmark contract: B2 T8 N16 d32 K2 H32, M2 D2, resets p=0.1
+        "c1_f32": dict(shape=dict(B=2, T=8, N=16, d=32, K=2, H=32, M=2, D=2), fd=SG, dtype="f32", perturb=0.0, p=0.1),
+        "c1_f64": dict(shape=dict(B=2, T=8, N=16, d=32, K=2, H=32, M=2, D=2), fd=SG, dtype="f64", perturb=0.0, p=0.1),
+        # the same with every path live (weights away from their init), fp64 and fp32
+        "c1p_f64": dict(shape=dict(B=2, T=8, N=16, d=32, K=2, H=32, M=2, D=2), fd=SG, dtype="f64", perturb=0.3, p=0.1),
+        "c1p_f32": dict(shape=dict(B=2, T=8, N=16, d=32, K=2, H=32, M=2, D=2), fd=SG, dtype="f32", perturb=0.3, p=0.1),
+        # the refresh probes fire (age_max 2) and the budget pads slots
+        "probes_f64": dict(shape=dict(B=3, T=12, N=12, d=16, K=3, H=24, M=3, D=2), fd=SG, dtype="f64", perturb=0.3, p=0.15,
+                           extra=("model.age_max=2",)),
+        "budget_f64": dict(shape=dict(B=3, T=10, N=12, d=16, K=4, H=24, M=3, D=3), fd=SG, dtype="f64", perturb=0.3, p=0.1,
+                           extra=("model.budget=0.06",)),
+        # odd sizes: nothing a power of two
+        "odd_f64": dict(shape=dict(B=3, T=7, N=11, d=12, K=3, H=20, M=3, D=2), fd=SG, dtype="f64", perturb=0.3, p=0.2),
+        # the full feedback cut (the plain recurrence of split.py:128)
+        "cut_f64": dict(shape=dict(B=2, T=8, N=16, d=32, K=2, H=32, M=2, D=2), fd=FULL, dtype="f64", perturb=0.3, p=0.1),
+        # a mid-sized fp32 case closer to the reference shape's proportions
+        "mid_f32": dict(shape=dict(B=2, T=12, N=64, d=32, K=8, H=64, M=8, D=4), fd=SG, dtype="f32", perturb=0.0, p=0.05,
+                        extra=("model.age_max=1000000",)),
+    }  # fmt: skip
+    for name, case in cases.items():
+        shape = case["shape"]
+        dtype = torch.float64 if case["dtype"] == "f64" else torch.float32
+        cfg = _cfg(root, **shape, fd=case["fd"], extra=case.get("extra", ()),
+                   precision="fp64" if dtype == torch.float64 else "fp32")  # fmt: skip
+        model = _model(cfg, dtype, case["perturb"])
+        tokens, ctx, reset = _inputs(cfg, shape["B"], shape["T"], case["p"])
+        state = model.init_state(shape["B"])
+        cap = _run_window(root, cfg, model, dtype, tokens, ctx, reset, state)
+        _dump_window(HERE / f"window_{name}.npz", model, cap, reset, state)
+        print(name, "ok")
+
+
+def make_chain(root: Path) -> None:
+    """Two chained windows of T positions against one window of 2T: the forward carry is the
+    final state; the backward carry is the unsplit sweep's (A, R) at position T (what the second
+    window's sweep ends with), given to the first window's sweep as ``initial``."""
+    import torch
+    from hsn.model.state import CellGraphState
+
+    shape = dict(B=2, N=12, d=16, K=3, H=24, M=3, D=2)
+    T = 6
+    for name, dtype in (("f64", torch.float64),):
+        cfg2 = _cfg(root, **shape, T=2 * T, fd="[summary,eps,router]", precision="fp64")
+        model = _model(cfg2, dtype, 0.3)
+        tokens, ctx, reset = _inputs(cfg2, shape["B"], 2 * T, 0.1)
+        g = torch.Generator().manual_seed(2)
+        zero = model.init_state(shape["B"])
+        h = (0.5 * torch.rand(zero.h.shape, generator=g, dtype=torch.float64) - 0.25).to(dtype)
+        reset[:, 0] = False  # a carried, non-zero start state
+        start = CellGraphState._make(h=h, q=h.mean(dim=1), age=zero.age, pos=zero.pos)
+        whole = _run_window(root, cfg2, model, dtype, tokens, ctx, reset, start)
+        _dump_window(HERE / f"chain_{name}.npz", model, whole, reset, start)
+        print("chain", name, "ok")
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--reference", type=Path, required=True)
+    parser.add_argument("--only", default="")
+    args = parser.parse_args()
+    _import_reference(args.reference)
+    import torch
+
+    torch.set_num_threads(1)
+    steps = {
+        "select": make_select, "update": make_update, "recurrence": make_recurrence,
+        "windows": make_windows, "chain": make_chain,
+    }  # fmt: skip
+    for key, fn in steps.items():
+        if not args.only or key in args.only.split(","):
+            fn(args.reference)
+
+
+if __name__ == "__main__":
+    main()

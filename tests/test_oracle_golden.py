@@ -1,0 +1,231 @@
+"""The oracle against the fixtures the reference itself produced (tests/golden/make_golden.py)."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+from conftest import load_golden
+
+from oracle import window_oracle as O
+
+SELECT_SETS = ["plain", "probes", "budget", "probes_budget", "cost", "reserved"]
+
+
+@pytest.mark.parametrize("name", SELECT_SETS)
+def test_select_takes_the_routers_decision(name: str) -> None:
+    z = load_golden(f"select_{name}")
+    p = z["params"]
+    reserved = int(p[6]) if len(p) > 6 else 0
+    fired = 0
+    for i in range(int(z["n"])):
+        pre = f"t{i}_"
+        cells, units, valid, theta, refreshed = O.select(
+            z[pre + "logits"], z[pre + "age"], z["cost"], k=int(p[0]), age_max=int(p[1]),
+            probes=bool(z[pre + "probes"]), lambda_cost=float(p[2]), cell_overhead=float(p[3]),
+            shared_cost=float(p[4]), limit=float(p[5]), reserved=reserved,
+            reserved_units=bool(z[pre + "fixed_units"]) if reserved else False,
+        )  # fmt: skip
+        assert np.array_equal(valid, z[pre + "valid"].astype(bool))
+        assert np.array_equal(cells, z[pre + "cells"])
+        assert np.array_equal(units, z[pre + "units"])
+        assert np.array_equal(refreshed, z[pre + "refreshed"].astype(bool))
+        assert np.array_equal(theta, z[pre + "theta"])
+        fired += int(refreshed.sum())
+    if "probes" in name or name in ("cost", "reserved"):
+        assert fired > 0
+
+
+@pytest.mark.parametrize("name", ["rms", "none", "budget"])
+def test_cell_update_equals_the_native_round(name: str) -> None:
+    z = load_golden(f"update_{name}")
+    padded = 0
+    for i in range(int(z["n"])):
+        s = f"s{i}_"
+        valid = z[s + "valid"].astype(bool)
+        h, q, age, pos, h_sel, h_max, _, _ = O.cell_update(
+            z[s + "y"], z[s + "gate"], z[s + "h"], z[s + "q"], z[s + "age"], z[s + "pos"],
+            z[s + "cells"], valid, z["cand_w"], cand_norm=bool(z["cand_norm"]),
+            cand_eps=float(z["cand_eps"]),
+        )  # fmt: skip
+        assert np.abs(h - z[s + "h_next"]).max() <= 2e-6
+        assert np.abs(q - z[s + "q_next"]).max() <= 2e-6
+        assert np.array_equal(age, z[s + "age_next"]) and np.array_equal(pos, z[s + "pos_next"])
+        assert np.array_equal(h_max, np.abs(h).reshape(h.shape[0], -1).max(axis=1))
+        padded += int((~valid).sum())
+    if name == "budget":
+        assert padded > 0
+
+
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
+def test_recurrence_equals_the_reference(name: str) -> None:
+    z = load_golden(f"recurrence_{name}")
+    N = int(z["N"])
+    base = (z["c"], z["b"], z["h_old"], z["cells"], z["valid"], z["reset"], N)
+    for tag in ("111", "010", "101"):
+        cots = [z[k] if on == "1" else None for k, on in zip(("pre", "post", "sel"), tag)]
+        dc, db = O.recurrence_backward(*base, *cots)
+        np.testing.assert_allclose(dc, z[f"dc_{tag}"], rtol=1e-12, atol=1e-13)
+        np.testing.assert_allclose(db, z[f"db_{tag}"], rtol=1e-12, atol=1e-13)
+        assert (dc[~z["valid"].astype(bool)] == 0).all()
+    dc, db = O.dense_recurrence_backward(
+        z["dense_c"], z["dense_b"], z["dense_h"], z["reset"], N, z["pre"], z["post"]
+    )
+    np.testing.assert_allclose(dc, z["dense_dc"], rtol=1e-12, atol=1e-13)
+    np.testing.assert_allclose(db, z["dense_db"], rtol=1e-12, atol=1e-13)
+
+
+WINDOWS = ["c1_f32", "c1_f64", "c1p_f64", "c1p_f32", "probes_f64", "budget_f64", "odd_f64",
+           "cut_f64", "mid_f32", ]  # fmt: skip
+
+
+def _forward(z, dtype):
+    K = z["tape_sel_cell_idx"].shape[-1]
+    W = O.WindowWeights.from_npz(z, K, dtype)
+    cast = lambda a: np.asarray(a, dtype=dtype)  # noqa: E731
+    tape = O.window_forward(
+        W, cast(z["z"]), cast(z["ctx"]), cast(z["scalars"]), z["reset"], cast(z["h0"]),
+        cast(z["q0"]), z["age0"], z["pos0"],
+    )  # fmt: skip
+    return W, tape
+
+
+@pytest.mark.parametrize("name", WINDOWS + ["chain_f64"])
+def test_forward_sweep_reproduces_the_reference_tape(name: str) -> None:
+    z = load_golden(name if name.startswith("chain") else f"window_{name}")
+    f64 = z["h0"].dtype == np.float64
+    dtype = np.float64 if f64 else np.float32
+    _, tape = _forward(z, np.dtype(dtype))
+    tol = 1e-9 if f64 else 2e-5
+    # routing: bit-exact
+    assert np.array_equal(tape["sel_valid"], z["tape_sel_valid"].astype(bool))
+    assert np.array_equal(tape["sel_cell_idx"], z["tape_sel_cell_idx"])
+    assert np.array_equal(tape["sel_unit_idx"], z["tape_sel_unit_idx"])
+    assert np.array_equal(tape["tape_age"], z["tape_tape_age"])
+    assert np.array_equal(tape["age"], z["tape_age"]) and np.array_equal(tape["pos"], z["tape_pos"])
+    for mine, ref in (
+        ("tape_h", "tape_tape_h"), ("tape_q", "tape_tape_q"), ("tape_hsel", "tape_tape_hsel"),
+        ("qs", "tape_qs"), ("h", "tape_h"), ("q", "tape_q"), ("state_abs_max", "tape_state_abs_max"),
+        ("refreshed", "tape_refreshed"),
+    ):  # fmt: skip
+        np.testing.assert_allclose(tape[mine], z[ref], rtol=tol, atol=tol, err_msg=mine)
+    np.testing.assert_allclose(tape["tape_theta"], z["tape_tape_theta"], rtol=1e-5, atol=1e-6)
+    if name.startswith("probes"):
+        assert tape["sel_refreshed"].sum() > 0
+    if name.startswith("budget"):
+        assert (~tape["sel_valid"]).sum() > 0
+    if "rec_y" in z.files:
+        # the sweep's own values of the round against the replay's record (batched matmuls)
+        for key in ("y", "gate_pre", "m", "rms", "hidden"):
+            got, want = tape["rec_" + key], z["rec_" + key]
+            mask = tape["sel_valid"]
+            np.testing.assert_allclose(got[mask], want[mask], rtol=10 * tol, atol=10 * tol, err_msg=key)
+        mask = tape["sel_valid"]
+        np.testing.assert_allclose(tape["rec_c"][mask], z["bw_c"][mask], rtol=10 * tol, atol=10 * tol)
+        np.testing.assert_allclose(tape["rec_b"][mask], z["bw_b"][mask], rtol=10 * tol, atol=10 * tol)
+
+
+@pytest.mark.parametrize("name", [w for w in WINDOWS if w != "cut_f64"] + ["chain_f64"])
+def test_state_gradient_sweep_equals_the_reference(name: str) -> None:
+    z = load_golden(name if name.startswith("chain") else f"window_{name}")
+    f64 = z["h0"].dtype == np.float64
+    dtype = np.dtype(np.float64 if f64 else np.float32)
+    K = z["bw_cells"].shape[-1]
+    W = O.WindowWeights.from_npz(z, K, dtype)
+    N = z["h0"].shape[1]
+    record = {k: z["rec_" + k] for k in ("y", "hidden", "gate_pre", "m", "rms")}
+    cot = lambda k: z[k] if k in z.files else None  # noqa: E731
+    trace: dict = {}
+    dc, db = O.state_gradient_backward(
+        W, z["bw_c"], z["bw_b"], z["bw_h_old"], z["bw_cells"], z["bw_units"], z["bw_valid"],
+        z["reset"], N, cot("bw_d_q_pre"), cot("bw_d_q_post"), cot("bw_d_h_sel"), record, trace=trace,
+    )  # fmt: skip
+    tol = 1e-10 if f64 else 2e-5
+    scale = max(1.0, float(np.abs(z["bw_dc"]).max()))
+    np.testing.assert_allclose(dc, z["bw_dc"], rtol=tol, atol=tol * scale)
+    np.testing.assert_allclose(db, z["bw_db"], rtol=tol, atol=tol * scale)
+    np.testing.assert_allclose(trace["A"], z["bw_A"], rtol=tol, atol=tol * scale)
+    np.testing.assert_allclose(trace["R"], z["bw_R"], rtol=tol, atol=tol * scale)
+    np.testing.assert_allclose(trace["dh"], z["bw_dh"], rtol=tol, atol=tol * scale)
+    np.testing.assert_allclose(trace["dvm"], z["bw_dvm"], rtol=tol, atol=tol * scale)
+
+
+def test_full_cut_window_equals_the_reference() -> None:
+    z = load_golden("window_cut_f64")
+    N = z["h0"].shape[1]
+    cot = lambda k: z[k] if k in z.files else None  # noqa: E731
+    dc, db = O.recurrence_backward(
+        z["bw_c"], z["bw_b"], z["bw_h_old"], z["bw_cells"], z["bw_valid"], z["reset"], N,
+        cot("bw_d_q_pre"), cot("bw_d_q_post"), cot("bw_d_h_sel"),
+    )  # fmt: skip
+    np.testing.assert_allclose(dc, z["bw_dc"], rtol=1e-12, atol=1e-14)
+    np.testing.assert_allclose(db, z["bw_db"], rtol=1e-12, atol=1e-14)
+
+
+def test_chained_windows_equal_the_unsplit_window() -> None:
+    """Two windows of T positions with the state carried forward and (A, R) carried back are the
+    window of 2T positions (fixture: the reference's unsplit window and its sweep's trace)."""
+    z = load_golden("chain_f64")
+    dtype = np.dtype(np.float64)
+    K = z["bw_cells"].shape[-1]
+    W = O.WindowWeights.from_npz(z, K, dtype)
+    N = z["h0"].shape[1]
+    T2 = z["reset"].shape[1]
+    T = T2 // 2
+    # forward: window 1, then window 2 from its final state
+    first = O.window_forward(W, z["z"][:, :T], z["ctx"][:, :T], z["scalars"][:, :T], z["reset"][:, :T],
+                             z["h0"], z["q0"], z["age0"], z["pos0"])  # fmt: skip
+    second = O.window_forward(W, z["z"][:, T:], z["ctx"][:, T:], z["scalars"][:, T:], z["reset"][:, T:],
+                              first["h"], first["q"], first["age"], first["pos"])  # fmt: skip
+    for key in ("tape_h", "tape_q", "qs", "tape_hsel"):
+        joined = np.concatenate([first[key], second[key]], axis=1)
+        np.testing.assert_allclose(joined, z["tape_" + key], rtol=1e-9, atol=1e-10)
+    assert np.array_equal(np.concatenate([first["sel_cell_idx"], second["sel_cell_idx"]], 1), z["tape_sel_cell_idx"])
+    np.testing.assert_allclose(second["h"], z["tape_h"], rtol=1e-9, atol=1e-10)
+    assert np.array_equal(second["pos"], z["tape_pos"])
+    # backward: window 2's sweep, its (A, R) into window 1's sweep
+    record = {k: z["rec_" + k] for k in ("y", "hidden", "gate_pre", "m", "rms")}
+    part = lambda a, s: None if a is None else a[:, s]  # noqa: E731
+    cot = lambda k: z[k] if k in z.files else None  # noqa: E731
+    halves = {}
+    carry = None
+    for s in (slice(T, T2), slice(0, T)):
+        trace: dict = {}
+        dc, db = O.state_gradient_backward(
+            W, z["bw_c"][:, s], z["bw_b"][:, s], z["bw_h_old"][:, s], z["bw_cells"][:, s],
+            z["bw_units"][:, s], z["bw_valid"][:, s], z["reset"][:, s], N,
+            part(cot("bw_d_q_pre"), s), part(cot("bw_d_q_post"), s), part(cot("bw_d_h_sel"), s),
+            {k: v[:, s] for k, v in record.items()}, initial=carry, trace=trace,
+        )  # fmt: skip
+        halves[s.start] = (dc, db)
+        reset0 = z["reset"][:, s.start].astype(bool)
+        carry = (np.where(reset0[:, None, None], 0, trace["A"][:, 0]),
+                 np.where(reset0[:, None], 0, trace["R"][:, 0]))  # fmt: skip
+    dc = np.concatenate([halves[0][0], halves[T][0]], axis=1)
+    db = np.concatenate([halves[0][1], halves[T][1]], axis=1)
+    np.testing.assert_allclose(dc, z["bw_dc"], rtol=1e-10, atol=1e-12)
+    np.testing.assert_allclose(db, z["bw_db"], rtol=1e-10, atol=1e-12)
+
+
+def test_out_adjacency_lists_every_edge_by_source() -> None:
+    rng = np.random.default_rng(0)
+    N, D = 9, 3
+    pad_src = rng.integers(0, N, (N, D))
+    mask = rng.random((N, D)) > 0.2
+    tgt, edge = O.out_adjacency(pad_src, mask)
+    seen = set()
+    for n in range(N):
+        for j in range(tgt.shape[1]):
+            if tgt[n, j] >= 0:
+                t, s = divmod(int(edge[n, j]), D)
+                assert t == tgt[n, j] and pad_src[t, s] == n and mask[t, s]
+                seen.add((t, s))
+    assert len(seen) == int(mask.sum())
+
+
+def test_bf16_rounding_is_nearest_even() -> None:
+    import torch
+
+    x = torch.randn(4096, generator=torch.Generator().manual_seed(0)) * 3
+    x[:4] = torch.tensor([1.00390625, 1.01171875, float("inf"), -0.0])
+    want = x.to(torch.bfloat16).float().numpy()
+    assert np.array_equal(O.bf16_round(x.numpy()), want)
