@@ -1,0 +1,13 @@
+"""hsn_b200: the HSN TBPTT window path (router top-K, sparse state gather, gated cell update,
+reset masking, reverse state recurrence, carried state) as hand-written sm_100a CUDA behind a
+C ABI, with the reference's Python interface on top.
+
+* :mod:`hsn_b200.kernels.window` mirrors the reference's ``hsn.kernels.window`` (custom ops kept).
+* :mod:`hsn_b200.window` holds the whole-window entry points (forward sweep, reverse sweep,
+  streaming step).
+* :mod:`hsn_b200.build` compiles ``csrc`` into ``lib/libhsn_window_b200.so``.
+
+Importing the package neither initialises CUDA nor loads the library.
+"""
+
+__version__ = "0.1.0"

@@ -1,0 +1,131 @@
+"""ctypes binding of ``libhsn_window_b200.so`` (``include/hsn_window_b200.h``).
+
+Import never initialises CUDA and never builds anything; :func:`library` loads the shared object
+on first use and raises if it is missing: there is no CPU or PyTorch fallback on this path.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
+from functools import lru_cache
+from pathlib import Path
+
+PACKAGE = Path(__file__).resolve().parent
+LIBRARY = PACKAGE / "lib" / "libhsn_window_b200.so"
+
+HSN_WIN_POINTERS, HSN_WIN_INTS, HSN_WIN_FLOATS = 48, 32, 8
+OK, E_ARG, E_UNSUPPORTED, E_CUDA, E_NAME, E_STATE = 0, -1, -2, -3, -4, -5
+
+
+class HsnWinArgs(Structure):
+    """The launch descriptor of the kernels launched by name (544 bytes, the reference's)."""
+
+    _fields_ = [
+        ("p", c_void_p * HSN_WIN_POINTERS),
+        ("i", c_int32 * HSN_WIN_INTS),
+        ("f", c_float * HSN_WIN_FLOATS),
+    ]
+
+
+MODEL_INTS = ("N", "d", "K", "H", "M", "D", "S", "dc", "prod_bf16", "probes", "age_max", "reserved_")
+MODEL_FLOATS = ("lambda_cost", "cell_overhead", "shared_cost", "limit", "norm_eps", "cand_eps")
+MODEL_POINTERS = (
+    "s_w1zc_t", "f_w1q_t", "f_b1", "f_w2_t", "f_b2", "score_w_t", "score_b", "v_t", "wout_t", "gate_t",
+    "gate_b", "norm_w", "cand_w", "w1", "b1", "w2", "b2", "pad_src", "edge_w", "cost",
+)  # fmt: skip
+
+
+class HsnwModel(Structure):
+    _fields_ = (
+        [(n, c_int32) for n in MODEL_INTS]
+        + [(n, c_float) for n in MODEL_FLOATS]
+        + [(n, c_void_p) for n in MODEL_POINTERS]
+    )
+
+
+FORWARD_POINTERS = (
+    "z", "ctx", "scalars", "reset", "h0", "q0", "age0", "pos", "tape_h", "tape_q", "tape_age", "cells",
+    "units", "valid", "refreshed", "theta", "h_sel", "qs", "h_max", "rec_c", "rec_b", "rec_h_old", "rec_y",
+    "rec_gate_pre", "rec_m", "rec_rms", "rec_hidden", "logits", "scratch",
+)  # fmt: skip
+
+
+class HsnwForward(Structure):
+    _fields_ = (
+        [(n, c_int32) for n in ("B", "T", "tape_state", "forced")]
+        + [(n, c_void_p) for n in FORWARD_POINTERS]
+        + [("scratch_bytes", c_int64)]
+    )
+
+
+BACKWARD_POINTERS = (
+    "c", "b", "h_old", "y", "gate_pre", "m", "rms", "hidden", "cells", "units", "valid", "reset",
+    "d_q_pre", "d_q_post", "d_h_sel", "dc", "db", "A", "R", "scratch",
+)  # fmt: skip
+
+
+class HsnwBackward(Structure):
+    _fields_ = (
+        [(n, c_int32) for n in ("B", "T", "full_cut", "pad_")]
+        + [(n, c_void_p) for n in BACKWARD_POINTERS]
+        + [("scratch_bytes", c_int64)]
+    )
+
+
+#: Every symbol ``include/hsn_window_b200.h`` declares: (restype, argtypes).
+SYMBOLS: dict[str, tuple[object, list[object]]] = {
+    "hsnw_version": (c_int, []),
+    "hsnw_last_error": (c_char_p, []),
+    "hsnw_prepare": (c_int, [c_int]),
+    "hsnw_prepared": (c_int, [c_int]),
+    "hsnw_sm_count": (c_int, [c_int]),
+    "hsnw_launch": (c_int, [c_char_p, POINTER(HsnWinArgs), c_int64, c_int, c_int, c_void_p]),
+    "hsnw_loop": (
+        c_int,
+        [POINTER(c_char_p), c_int, POINTER(c_int64), POINTER(c_int), POINTER(c_int), POINTER(HsnWinArgs),
+         c_int64, c_int, c_void_p],
+    ),  # fmt: skip
+    "hsnw_launch_shape": (
+        c_int, [c_char_p, POINTER(HsnWinArgs), POINTER(c_int64), POINTER(c_int), POINTER(c_int)]
+    ),
+    "hsnw_forward_scratch_bytes": (c_int64, [POINTER(HsnwModel), c_int32, c_int32]),
+    "hsnw_window_forward": (c_int, [POINTER(HsnwModel), POINTER(HsnwForward), c_void_p]),
+    "hsnw_stream_step": (c_int, [POINTER(HsnwModel), POINTER(HsnwForward), c_void_p]),
+    "hsnw_backward_scratch_bytes": (c_int64, [POINTER(HsnwModel), c_int32, c_int32]),
+    "hsnw_window_backward": (c_int, [POINTER(HsnwModel), POINTER(HsnwBackward), c_void_p]),
+    "hsnw_front_projection": (c_int, [POINTER(HsnwModel), c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+}
+
+
+class WindowKernelError(RuntimeError):
+    """An entry point of the library returned an error code."""
+
+    def __init__(self, code: int, message: str) -> None:
+        super().__init__(f"hsn_window_b200: {message} (code {code})")
+        self.code = code
+
+
+def available() -> bool:
+    """Artifact presence only: never initialises CUDA or loads the library."""
+    return LIBRARY.is_file()
+
+
+@lru_cache(maxsize=1)
+def library() -> ctypes.CDLL:
+    if not available():
+        raise RuntimeError(
+            f"{LIBRARY} is missing: build it with `python -m hsn_b200.build`. The window path has no "
+            "CPU or PyTorch fallback."
+        )
+    lib = ctypes.CDLL(str(LIBRARY))
+    for name, (restype, argtypes) in SYMBOLS.items():
+        fn = getattr(lib, name)
+        fn.restype = restype
+        fn.argtypes = argtypes
+    return lib
+
+
+def check(code: int) -> None:
+    if code != OK:
+        raise WindowKernelError(code, library().hsnw_last_error().decode())

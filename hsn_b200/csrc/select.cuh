@@ -1,0 +1,150 @@
+// The router's hard decision for one batch row, by the whole thread block that owns the row.
+//
+// Follows Router.select with mode "topk" (reference python/hsn/model/router.py:1263-1417):
+//   _topk       :1640-1648  descending by score, equal scores in index order (a stable sort);
+//                           the unit of a cell is the first maximiser of its scores
+//   _truncate   :1650-1657  the longest prefix of the slots whose cumulative cost fits the limit
+//   _ste_threshold :1771-1786, the refresh probes of _post_process :1788-1850
+// and keeps the contract of the reference kernel hsn_win_select (kernels/cuda/hsn_window.cu:533-562).
+//
+// Method: a cell's (score, index) pair is packed into one 64-bit key whose unsigned order is
+// "higher score first, then lower index", so all keys differ. Slot r takes the largest key below
+// slot r-1's: K rounds of a warp-shuffle maximum (lanes fold 64-bit keys with shuffles, the
+// warps' maxima are folded by the first warp). No rank counting, no sort, no atomics: the result
+// does not depend on thread scheduling. The probes use the same rounds on (age, index) keys.
+#pragma once
+#include "common.cuh"
+
+namespace hsnw {
+
+constexpr int kMaxSlots = 64;   // K of a row
+constexpr int kMaxUnits = 64;   // M
+
+struct SelectParams {
+    int N, M, K;
+    int age_max;
+    int probes;
+    int reserved;      // amendment A8: cells 0..reserved-1 hold the first slots
+    int fixed_units;   // and slot k < reserved runs unit k mod M
+    float overhead, shared_cost, limit;
+};
+
+// Shared-memory working set of a decision (the [N]-sized arrays are the caller's).
+struct SelectShared {
+    uint64_t red[33];
+    float cost[kMaxUnits];
+    int order[kMaxSlots];      // the scored decision's cells, slot by slot
+    int out_cell[kMaxSlots];
+    int out_unit[kMaxSlots];
+    int out_flag[kMaxSlots];   // bit 0 valid, bit 1 refreshed
+    int n_valid;
+    float theta;
+};
+
+// score[N], unit[N]: shared memory, filled by the caller (score_i = max_j(logit_ij - lambda c_j),
+// unit_i its first maximiser); age_row: the row's ages (global or shared; read only with probes).
+// Every thread of the block calls this; the results are in S.out_* / S.theta after the trailing
+// barrier.
+__device__ __forceinline__ void select_row(const SelectParams& P, const float* score, const int* unit,
+                                           const int64_t* age_row, SelectShared& S) {
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const int N = P.N, K = P.K, F = P.reserved;
+    uint64_t prev = ~0ull;
+    for (int r = 0; r < K; ++r) {
+        if (r < F) {
+            if (tid == 0) S.order[r] = r;
+            continue;
+        }
+        uint64_t best = 0ull;
+        for (int i = F + tid; i < N; i += nt) {
+            const uint64_t key = pack_key(score[i], i);
+            if (key < prev && key > best) best = key;
+        }
+        best = block_max_u64(best, S.red);
+        if (tid == 0) S.order[r] = best ? key_cell(best) : 0;
+        prev = best;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        // the budget: the longest prefix that fits, the costs summed in slot order
+        float cumulative = 0.0f;
+        int n_valid = 0;
+        for (int k = 0; k < K; ++k) {
+            const int c = S.order[k];
+            const int u = (P.fixed_units && k < F) ? k % P.M : unit[c];
+            cumulative += P.overhead + S.cost[u];
+            const bool ok = P.shared_cost + cumulative <= P.limit;
+            S.out_cell[k] = ok ? c : 0;
+            S.out_unit[k] = ok ? u : 0;
+            S.out_flag[k] = ok ? 1 : 0;
+            n_valid += ok ? 1 : 0;
+        }
+        S.n_valid = n_valid;
+    }
+    __syncthreads();
+    const int n_valid = S.n_valid;
+    const bool any_scored = n_valid > F;
+    const int last = any_scored ? S.order[n_valid - 1] : 0;
+    const float lowest_in = any_scored ? score[last] : INFINITY;
+    const uint64_t in_key = any_scored ? pack_key(score[last], last) : ~0ull;
+    // the straight-through threshold: midway between the lowest selected (scored slots only) and
+    // the highest unselected score
+    float high = -INFINITY;
+    int stale = 0;
+    for (int i = tid; i < N; i += nt) {
+        const bool chosen = i < F ? i < n_valid : (any_scored && pack_key(score[i], i) >= in_key);
+        if (!chosen) {
+            high = fmaxf(high, score[i]);
+            if (P.probes && age_row[i] > static_cast<int64_t>(P.age_max)) ++stale;
+        }
+    }
+    high = block_max_float(high, S.red);
+    if (tid == 0) S.theta = 0.5f * (lowest_in + high);
+    if (P.probes) {
+        // the stalest unselected cells (equal ages in index order) take the valid scored slots
+        // from the last one backwards
+        const int n_stale = block_sum_int(stale, S.red);
+        const int scored = any_scored ? n_valid - F : 0;
+        const int n_force = n_stale < scored ? n_stale : scored;
+        uint64_t before = ~0ull;
+        for (int j = 0; j < n_force; ++j) {
+            uint64_t best = 0ull;
+            for (int i = tid; i < N; i += nt) {
+                const bool chosen = i < F ? i < n_valid : (any_scored && pack_key(score[i], i) >= in_key);
+                const int64_t ag = age_row[i];
+                if (!chosen && ag > static_cast<int64_t>(P.age_max)) {
+                    const uint64_t key = pack_key(static_cast<float>(ag), i);
+                    if (key < before && key > best) best = key;
+                }
+            }
+            best = block_max_u64(best, S.red);
+            before = best;
+            if (tid == 0) {
+                const int pick = key_cell(best), k = n_valid - 1 - j;
+                S.out_cell[k] = pick;
+                S.out_unit[k] = unit[pick];
+                S.out_flag[k] |= 2;
+            }
+        }
+        __syncthreads();
+        if (tid == 0 && n_force > 0) {
+            // a row the probes pushed over the limit keeps its scored decision
+            float spent = 0.0f;
+            for (int k = 0; k < K; ++k)
+                spent += (S.out_flag[k] & 1) ? P.overhead + S.cost[S.out_unit[k]] : 0.0f;
+            if (P.shared_cost + spent > P.limit) {
+                for (int k = 0; k < K; ++k) {
+                    const bool ok = (S.out_flag[k] & 1) != 0;
+                    const int c = S.order[k];
+                    const int u = (P.fixed_units && k < F) ? k % P.M : unit[c];
+                    S.out_cell[k] = ok ? c : 0;
+                    S.out_unit[k] = ok ? u : 0;
+                    S.out_flag[k] &= 1;
+                }
+            }
+        }
+    }
+    __syncthreads();
+}
+
+}  // namespace hsnw

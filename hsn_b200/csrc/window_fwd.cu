@@ -1,0 +1,783 @@
+// The forward sweep of a window as batch-synchronous phases: every row advances one position per
+// round of four phases, and the phases' work is laid out for the hardware rather than per row:
+//
+//   front   weight-stationary: a block holds a 64-column slice of the shared path's first layer
+//           ([q -> 2H], S and P merged) and the matching rows of its second layer in shared
+//           memory and serves every row; the rows' partial sums are reduced in slice order later.
+//   row     one block per row: reduce the partials to (u, z_hat), the scorer's logits for every
+//           cell, the router's decision (select.cuh), the gather of the selected cells and of
+//           their message sources, the messages, the cell norm -> the pairs' inputs v.
+//   unit    weight-stationary: a block holds a 64-column slice of ONE unit's first layer and the
+//           matching rows of its second layer and serves the pairs (row, slot) routed to that
+//           unit, found by a ballot compaction of the pair list: no unit runs for a pair that did
+//           not choose it (the reference multiplies every pair by all M units,
+//           python/hsn/model/units.py:566-572). The gate's linear rides as extra jobs.
+//   update  one block per row: reduce the second layer's partials, W_out, candidate norm, tanh,
+//           sigmoid, the gated write-back, summary, ages, the tape's records and the next
+//           position's reset.
+//
+// What it computes per position is the reference's folded sweep (python/hsn/train/compile.py:
+// 1117-1193; per position python/hsn/model/hsn.py:1903-1980 and python/hsn/model/cell.py:349-505)
+// and it writes the reference's tape (compile.py:1196-1213). With prod_bf16 every product rounds
+// its operands and its output to bfloat16 and sums in fp32, the state and the norms stay fp32.
+#include "../../include/hsn_window_b200.h"
+#include "common.cuh"
+#include "select.cuh"
+#include "host_util.h"
+
+using namespace hsnw;
+
+namespace {
+
+constexpr int kSlice = 64;       // columns of a weight-stationary slice
+constexpr int kRowTile = 32;     // rows a front block serves
+constexpr int kPairTile = 256;   // pairs a unit block scans
+constexpr int kPairBatch = 8;    // pairs a unit block multiplies at a time
+constexpr int kMaxM = 16;        // units (registers of the scorer's thread)
+
+struct FwdCtx {
+    HsnwModel m;
+    HsnwForward io;
+    int nS;      // slices of one front MLP's hidden layer
+    int nHS;     // slices of a unit's hidden layer
+    int nG;      // slices of the gate's outputs
+    float* pre_s;     // [B*T, H]
+    float* part_front;  // [2 nS, B, d]
+    float* v;         // [B*K, 4d]
+    int* pair_unit;   // [B*K] the pair's unit, -1 on a padded slot
+    float* part_f;    // [nHS, B*K, d]
+    float* gate_pre;  // [B*K, d]
+    float* hidden;    // [B*K, H] when no record is kept
+};
+
+__device__ __forceinline__ const float* state_h(const FwdCtx& c, int row, int t) {
+    return c.io.tape_state ? c.io.tape_h + (static_cast<int64_t>(row) * (c.io.T + 1) + t) * c.m.N * c.m.d
+                           : c.io.h0 + static_cast<int64_t>(row) * c.m.N * c.m.d;
+}
+__device__ __forceinline__ const float* state_q(const FwdCtx& c, int row, int t) {
+    return c.io.tape_state ? c.io.tape_q + (static_cast<int64_t>(row) * (c.io.T + 1) + t) * c.m.d
+                           : c.io.q0 + static_cast<int64_t>(row) * c.m.d;
+}
+__device__ __forceinline__ const int64_t* state_age(const FwdCtx& c, int row, int t) {
+    return c.io.tape_state ? c.io.tape_age + (static_cast<int64_t>(row) * (c.io.T + 1) + t) * c.m.N
+                           : c.io.age0 + static_cast<int64_t>(row) * c.m.N;
+}
+
+// ------------------------------------------------------------------------------------------------
+// init: record 0 of the tape is the start state with column 0's reset applied (resident: the
+// reset is applied in place).
+// ------------------------------------------------------------------------------------------------
+__global__ void k_init(FwdCtx c) {
+    const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+    const int N = c.m.N, d = c.m.d, T = c.io.T;
+    const bool cut = c.io.reset[static_cast<int64_t>(row) * T] != 0;
+    float* h0 = c.io.h0 + static_cast<int64_t>(row) * N * d;
+    float* q0 = c.io.q0 + static_cast<int64_t>(row) * d;
+    int64_t* a0 = c.io.age0 + static_cast<int64_t>(row) * N;
+    if (c.io.tape_state) {
+        float* h = c.io.tape_h + static_cast<int64_t>(row) * (T + 1) * N * d;
+        float* q = c.io.tape_q + static_cast<int64_t>(row) * (T + 1) * d;
+        int64_t* a = c.io.tape_age + static_cast<int64_t>(row) * (T + 1) * N;
+        for (int e = tid; e < N * d; e += nt) h[e] = cut ? 0.0f : h0[e];
+        for (int x = tid; x < d; x += nt) q[x] = cut ? 0.0f : q0[x];
+        for (int n = tid; n < N; n += nt) a[n] = cut ? 0 : a0[n];
+    } else if (cut) {
+        for (int e = tid; e < N * d; e += nt) h0[e] = 0.0f;
+        for (int x = tid; x < d; x += nt) q0[x] = 0.0f;
+        for (int n = tid; n < N; n += nt) a0[n] = 0;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// pre: the window-invariant part of S's first layer for every (row, position):
+// pre_s[r, j] = b1[j] + sum_x [z; ctx][r, x] W[x, j]. A 64 x 64 tile per block, 16 deep.
+// ------------------------------------------------------------------------------------------------
+__global__ void k_pre(HsnwModel m, const float* z, const float* ctx, int64_t rows, float* out) {
+    __shared__ float xs[16][kSlice + 1];
+    __shared__ float ws[16][kSlice];
+    const int d = m.d, dc = m.dc, H = m.H, in = d + dc;
+    const bool bf = m.prod_bf16 != 0;
+    const int64_t r0 = static_cast<int64_t>(blockIdx.x) * kSlice;
+    const int c0 = blockIdx.y * kSlice;
+    const int tid = threadIdx.x;           // 256 threads: 16 x 16, a 4 x 4 register tile each
+    const int tr = tid >> 4, tc = tid & 15;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < in; k0 += 16) {
+        for (int e = tid; e < 16 * kSlice; e += 256) {
+            const int kk = e & 15, r = e >> 4;
+            const int64_t rr = r0 + r;
+            const int x = k0 + kk;
+            float v = 0.0f;
+            if (rr < rows && x < in) v = x < d ? z[rr * d + x] : ctx[rr * dc + (x - d)];
+            xs[kk][r] = maybe_bf16(v, bf);
+        }
+        for (int e = tid; e < 16 * kSlice; e += 256) {
+            const int cc = e & (kSlice - 1), kk = e >> 6;
+            const int x = k0 + kk, col = c0 + cc;
+            ws[kk][cc] = (x < in && col < H) ? m.s_w1zc_t[static_cast<int64_t>(x) * H + col] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < 16; ++kk) {
+            float xv[4], wv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) xv[i] = xs[kk][tr * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) wv[j] = ws[kk][tc * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] += xv[i] * wv[j];
+        }
+        __syncthreads();
+    }
+    for (int i = 0; i < 4; ++i) {
+        const int64_t rr = r0 + tr * 4 + i;
+        if (rr >= rows) continue;
+        for (int j = 0; j < 4; ++j) {
+            const int col = c0 + tc * 4 + j;
+            if (col < H) out[rr * H + col] = acc[i][j] + m.f_b1[col];
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// front: blockIdx.x = slice (0..nS-1: S; nS..2nS-1: P), blockIdx.y = row tile. 256 threads.
+// Shared: w1 [d][64], w2 [64][d], q [32][d], act [32][64].
+// ------------------------------------------------------------------------------------------------
+__global__ void k_front(FwdCtx c, int t) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    const int d = c.m.d, H = c.m.H, B = c.io.B, T = c.io.T;
+    const bool bf = c.m.prod_bf16 != 0;
+    const int tid = threadIdx.x;
+    const int slice = blockIdx.x, nS = c.nS;
+    const bool is_p = slice >= nS;
+    const int c0 = (is_p ? slice - nS : slice) * kSlice;
+    const int cols = min(kSlice, H - c0);
+    const int col_base = (is_p ? H : 0) + c0;   // column in the merged [d, 2H] first layer
+    const int r0 = blockIdx.y * kRowTile;
+    const int rows = min(kRowTile, B - r0);
+    float* w1 = reinterpret_cast<float*>(dyn);          // [d][64]
+    float* w2 = w1 + d * kSlice;                        // [64][d]
+    float* qs = w2 + kSlice * d;                        // [32][d]
+    float* act = qs + kRowTile * d;                     // [32][64]
+    for (int e = tid; e < d * kSlice; e += blockDim.x) {
+        const int x = e >> 6, cc = e & 63;
+        w1[e] = cc < cols ? c.m.f_w1q_t[static_cast<int64_t>(x) * 2 * H + col_base + cc] : 0.0f;
+    }
+    for (int e = tid; e < kSlice * d; e += blockDim.x) {
+        const int cc = e / d, x = e - cc * d;
+        w2[e] = cc < cols ? c.m.f_w2_t[static_cast<int64_t>(col_base + cc) * d + x] : 0.0f;
+    }
+    for (int e = tid; e < rows * d; e += blockDim.x) {
+        const int r = e / d, x = e - r * d;
+        qs[e] = maybe_bf16(state_q(c, r0 + r, t)[x], bf);
+    }
+    __syncthreads();
+    for (int e = tid; e < rows * kSlice; e += blockDim.x) {
+        const int r = e >> 6, cc = e & 63;
+        float a = 0.0f;
+        if (cc < cols) {
+            float sum = 0.0f;
+            for (int x = 0; x < d; ++x) sum += qs[r * d + x] * w1[x * kSlice + cc];
+            const float pre = is_p ? c.m.f_b1[H + c0 + cc]
+                                   : c.pre_s[(static_cast<int64_t>(r0 + r) * T + t) * H + c0 + cc];
+            a = maybe_bf16(gelu_erf(maybe_bf16(sum + pre, bf)), bf);
+        }
+        act[e] = a;
+    }
+    __syncthreads();
+    for (int e = tid; e < rows * d; e += blockDim.x) {
+        const int r = e / d, x = e - r * d;
+        float sum = 0.0f;
+        for (int cc = 0; cc < kSlice; ++cc) sum += act[r * kSlice + cc] * w2[cc * d + x];
+        c.part_front[(static_cast<int64_t>(slice) * B + r0 + r) * d + x] = sum;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// row: one block per row. Shared (dynamic): score [N], unit [N], sw [(3d+1+S) M], vt [d d],
+// ue [2d], rowterm [M], src [K D], ew [K D], vh [K D d], hold [K d], msg [K d], rms [K].
+// ------------------------------------------------------------------------------------------------
+__global__ void k_row(FwdCtx c, int t) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    __shared__ SelectShared S;
+    const int N = c.m.N, d = c.m.d, K = c.m.K, M = c.m.M, D = c.m.D, Sn = c.m.S;
+    const int B = c.io.B, T = c.io.T;
+    const bool bf = c.m.prod_bf16 != 0;
+    const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+    const int lane = tid & 31, warp = tid >> 5, warps = nt >> 5;
+    const int feat = 3 * d + 1 + Sn;
+    float* score = reinterpret_cast<float*>(dyn);
+    int* unit = reinterpret_cast<int*>(score + N);
+    float* sw = reinterpret_cast<float*>(unit + N);
+    float* vt = sw + feat * M;
+    float* ue = vt + d * d;
+    float* rowterm = ue + 2 * d;
+    int* src = reinterpret_cast<int*>(rowterm + kMaxM);
+    float* ew = reinterpret_cast<float*>(src + K * D);
+    float* vh = ew + K * D;
+    float* hold = vh + K * D * d;
+    float* msg = hold + K * d;
+    float* rms = msg + K * d;
+    const int64_t rt = static_cast<int64_t>(row) * T + t;
+    const float* h = state_h(c, row, t);
+    const int64_t* age = state_age(c, row, t);
+    for (int e = tid; e < feat * M; e += nt) sw[e] = c.m.score_w_t[e];
+    for (int e = tid; e < d * d; e += nt) vt[e] = c.m.v_t[e];
+    for (int j = tid; j < M; j += nt) S.cost[j] = c.m.cost[j];
+    // (u, z_hat) from the front's partial sums, slice by slice; eps = z - z_hat
+    for (int x = tid; x < 2 * d; x += nt) {
+        const bool is_p = x >= d;
+        const int xx = is_p ? x - d : x;
+        float sum = 0.0f;
+        for (int s = 0; s < c.nS; ++s)
+            sum += c.part_front[(static_cast<int64_t>((is_p ? c.nS : 0) + s) * B + row) * d + xx];
+        const float out = maybe_bf16(sum + c.m.f_b2[x], bf);
+        ue[x] = is_p ? c.io.z[rt * d + xx] - out : out;
+    }
+    __syncthreads();
+    if (tid < M) {
+        float sum = 0.0f;
+        for (int x = 0; x < 2 * d; ++x) sum += maybe_bf16(ue[x], bf) * sw[x * M + tid];
+        rowterm[tid] = sum;
+    }
+    __syncthreads();
+    // the scorer: a thread per cell, M logits in registers
+    const float lambda = c.m.lambda_cost;
+    const float* scal = c.io.scalars + rt * N * Sn;
+    const float age_div = static_cast<float>(c.m.age_max);
+    for (int i = tid; i < N; i += nt) {
+        float acc[kMaxM];
+#pragma unroll
+        for (int j = 0; j < kMaxM; ++j) acc[j] = j < M ? rowterm[j] : 0.0f;
+        const float4* hi = reinterpret_cast<const float4*>(h + static_cast<int64_t>(i) * d);
+        for (int x4 = 0; x4 < (d >> 2); ++x4) {
+            const float4 hv = hi[x4];
+            const float vals[4] = {hv.x, hv.y, hv.z, hv.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float a = maybe_bf16(vals[u], bf);
+                const float* w = sw + (2 * d + x4 * 4 + u) * M;
+#pragma unroll
+                for (int j = 0; j < kMaxM; ++j)
+                    if (j < M) acc[j] += a * w[j];
+            }
+        }
+        {
+            const float a = maybe_bf16(static_cast<float>(age[i]) / age_div, bf);
+            const float* w = sw + (3 * d) * M;
+#pragma unroll
+            for (int j = 0; j < kMaxM; ++j)
+                if (j < M) acc[j] += a * w[j];
+        }
+        for (int s = 0; s < Sn; ++s) {
+            const float a = maybe_bf16(scal[static_cast<int64_t>(i) * Sn + s], bf);
+            const float* w = sw + (3 * d + 1 + s) * M;
+#pragma unroll
+            for (int j = 0; j < kMaxM; ++j)
+                if (j < M) acc[j] += a * w[j];
+        }
+        float best = -INFINITY;
+        int arg = 0;
+#pragma unroll
+        for (int j = 0; j < kMaxM; ++j) {
+            if (j < M) {
+                const float logit = maybe_bf16(acc[j] + c.m.score_b[j], bf);
+                if (c.io.logits) c.io.logits[(rt * N + i) * M + j] = logit;
+                const float s = lambda > 0.0f ? __fsub_rn(logit, __fmul_rn(lambda, S.cost[j])) : logit;
+                if (j == 0 || s > best) {
+                    best = s;
+                    arg = j;
+                }
+            }
+        }
+        score[i] = best;
+        unit[i] = arg;
+    }
+    __syncthreads();
+    int64_t* cells_o = c.io.cells + rt * K;
+    int64_t* units_o = c.io.units + rt * K;
+    uint8_t* valid_o = c.io.valid + rt * K;
+    if (!c.io.forced) {
+        SelectParams P;
+        P.N = N; P.M = M; P.K = K; P.age_max = c.m.age_max; P.probes = c.m.probes;
+        P.reserved = 0; P.fixed_units = 0;
+        P.overhead = c.m.cell_overhead; P.shared_cost = c.m.shared_cost; P.limit = c.m.limit;
+        select_row(P, score, unit, age, S);
+        for (int k = tid; k < K; k += nt) {
+            cells_o[k] = S.out_cell[k];
+            units_o[k] = S.out_unit[k];
+            valid_o[k] = static_cast<uint8_t>(S.out_flag[k] & 1);
+            c.io.refreshed[rt * K + k] = static_cast<uint8_t>((S.out_flag[k] >> 1) & 1);
+        }
+        if (tid == 0) c.io.theta[rt] = S.theta;
+    } else {
+        for (int k = tid; k < K; k += nt) {
+            const bool ok = valid_o[k] != 0;
+            S.out_cell[k] = ok ? static_cast<int>(cells_o[k]) : 0;
+            S.out_unit[k] = ok ? static_cast<int>(units_o[k]) : 0;
+            S.out_flag[k] = ok ? 1 : 0;
+        }
+        __syncthreads();
+    }
+    // the selected cells, their message sources and edge weights
+    for (int e = tid; e < K * D; e += nt) {
+        const int k = e / D, j = e - k * D;
+        const int cell = S.out_cell[k];
+        src[e] = c.m.pad_src[cell * D + j];
+        ew[e] = maybe_bf16(c.m.edge_w[cell * D + j], bf);
+    }
+    for (int e = tid; e < K * d; e += nt) {
+        const int k = e / d, x = e - k * d;
+        hold[e] = h[static_cast<int64_t>(S.out_cell[k]) * d + x];
+    }
+    __syncthreads();
+    // V h of every source: K D d outputs, d products each
+    for (int e = tid; e < K * D * d; e += nt) {
+        const int s = e / d, x = e - s * d;
+        const float* hs = h + static_cast<int64_t>(src[s]) * d;
+        float sum = 0.0f;
+        for (int i = 0; i < d; ++i) sum += maybe_bf16(hs[i], bf) * vt[i * d + x];
+        vh[e] = maybe_bf16(sum, bf);
+    }
+    __syncthreads();
+    for (int e = tid; e < K * d; e += nt) {
+        const int k = e / d, x = e - k * d;
+        float sum = 0.0f;
+        for (int j = 0; j < D; ++j) sum += vh[(k * D + j) * d + x] * ew[k * D + j];  // edge order
+        msg[e] = maybe_bf16(sum, bf);
+    }
+    __syncthreads();
+    // the cell norm over [u; eps; h_old; m]: a warp per slot
+    for (int k = warp; k < K; k += warps) {
+        float sq = 0.0f;
+        for (int j = lane; j < 4 * d; j += 32) {
+            const int blk = j / d, x = j - blk * d;
+            const float v = blk == 0 ? ue[x] : blk == 1 ? ue[d + x] : blk == 2 ? hold[k * d + x] : msg[k * d + x];
+            sq += v * v;
+        }
+        sq = warp_sum(sq);
+        if (lane == 0) rms[k] = rsqrtf(sq / static_cast<float>(4 * d) + c.m.norm_eps);
+    }
+    __syncthreads();
+    const int64_t pair0 = static_cast<int64_t>(row) * K;
+    for (int e = tid; e < K * 4 * d; e += nt) {
+        const int k = e / (4 * d), j = e - k * 4 * d;
+        const int blk = j / d, x = j - blk * d;
+        const float v = blk == 0 ? ue[x] : blk == 1 ? ue[d + x] : blk == 2 ? hold[k * d + x] : msg[k * d + x];
+        c.v[(pair0 + k) * 4 * d + j] = maybe_bf16(v * rms[k] * c.m.norm_w[j], bf);
+    }
+    for (int k = tid; k < K; k += nt) c.pair_unit[pair0 + k] = (S.out_flag[k] & 1) ? S.out_unit[k] : -1;
+    if (c.io.rec_c) {
+        for (int e = tid; e < K * d; e += nt) {
+            c.io.rec_h_old[rt * K * d + e] = hold[e];
+            c.io.rec_m[rt * K * d + e] = msg[e];
+        }
+        for (int k = tid; k < K; k += nt) c.io.rec_rms[rt * K + k] = rms[k];
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// unit: blockIdx.x = job, blockIdx.y = pair tile. Jobs 0 .. M nHS - 1: (unit j, hidden slice s);
+// then nG jobs: a 64-column slice of the gate's linear for every valid pair. 256 threads.
+// Shared (dynamic): w1 [4d][64], w2 [64][d], vbuf [8][4d], act [8][64], list [256].
+// ------------------------------------------------------------------------------------------------
+__global__ void k_unit(FwdCtx c, int t) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    __shared__ int warp_count[8];
+    __shared__ int n_list;
+    const int d = c.m.d, K = c.m.K, H = c.m.H, M = c.m.M, in = 4 * c.m.d;
+    const int P = c.io.B * K, T = c.io.T;
+    const bool bf = c.m.prod_bf16 != 0;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int job = blockIdx.x;
+    const bool is_gate = job >= M * c.nHS;
+    const int j = is_gate ? -1 : job / c.nHS;
+    const int s = is_gate ? job - M * c.nHS : job - j * c.nHS;
+    const int c0 = s * kSlice;
+    const int cols = min(kSlice, (is_gate ? d : H) - c0);
+    float* w1 = reinterpret_cast<float*>(dyn);       // [4d][64]
+    float* w2 = w1 + in * kSlice;                    // [64][d]
+    float* vbuf = w2 + kSlice * d;                   // [8][4d]
+    float* act = vbuf + kPairBatch * in;             // [8][64]
+    int* list = reinterpret_cast<int*>(act + kPairBatch * kSlice);  // [256]
+    // the pairs of this tile that this job serves, in pair order (a ballot compaction)
+    const int p0 = blockIdx.y * kPairTile;
+    {
+        const int p = p0 + tid;
+        const int u = p < P ? c.pair_unit[p] : -1;
+        const bool mine = is_gate ? u >= 0 : u == j;
+        const unsigned mask = __ballot_sync(0xffffffffu, mine);
+        if (lane == 0) warp_count[warp] = __popc(mask);
+        __syncthreads();
+        int before = 0;
+        for (int w = 0; w < warp; ++w) before += warp_count[w];
+        if (mine) list[before + __popc(mask & ((1u << lane) - 1u))] = p;
+        if (tid == 0) {
+            int total = 0;
+            for (int w = 0; w < 8; ++w) total += warp_count[w];
+            n_list = total;
+        }
+        __syncthreads();
+    }
+    const int count = n_list;
+    if (count == 0) return;
+    if (is_gate) {
+        for (int e = tid; e < in * kSlice; e += blockDim.x) {
+            const int x = e >> 6, cc = e & 63;
+            w1[e] = cc < cols ? c.m.gate_t[static_cast<int64_t>(x) * d + c0 + cc] : 0.0f;
+        }
+    } else {
+        const float* W1 = c.m.w1 + static_cast<int64_t>(j) * in * H;
+        const float* W2 = c.m.w2 + static_cast<int64_t>(j) * H * d;
+        for (int e = tid; e < in * kSlice; e += blockDim.x) {
+            const int x = e >> 6, cc = e & 63;
+            w1[e] = cc < cols ? W1[static_cast<int64_t>(x) * H + c0 + cc] : 0.0f;
+        }
+        for (int e = tid; e < kSlice * d; e += blockDim.x) {
+            const int cc = e / d, x = e - cc * d;
+            w2[e] = cc < cols ? W2[static_cast<int64_t>(c0 + cc) * d + x] : 0.0f;
+        }
+    }
+    const int cc = tid & 63, pg = tid >> 6;  // a column and two pairs (pg, pg + 4) per thread
+    for (int base = 0; base < count; base += kPairBatch) {
+        const int nb = min(kPairBatch, count - base);
+        __syncthreads();
+        for (int e = tid; e < nb * in; e += blockDim.x) {
+            const int pb = e / in, x = e - pb * in;
+            vbuf[e] = c.v[static_cast<int64_t>(list[base + pb]) * in + x];
+        }
+        __syncthreads();
+        float a0 = 0.0f, a1 = 0.0f;
+        const float* v0 = vbuf + pg * in;
+        const float* v1 = vbuf + (pg + 4) * in;
+        for (int x = 0; x < in; ++x) {
+            const float w = w1[x * kSlice + cc];
+            a0 += v0[x] * w;
+            a1 += v1[x] * w;
+        }
+        for (int half = 0; half < 2; ++half) {
+            const int pb = pg + 4 * half;
+            const float acc = half ? a1 : a0;
+            if (pb < nb && cc < cols) {
+                const int p = list[base + pb];
+                if (is_gate) {
+                    c.gate_pre[static_cast<int64_t>(p) * d + c0 + cc] = maybe_bf16(acc + c.m.gate_b[c0 + cc], bf);
+                } else {
+                    const float hid = maybe_bf16(acc + c.m.b1[j * H + c0 + cc], bf);
+                    if (c.io.rec_c) {
+                        const int row = p / K, k = p - row * K;
+                        c.io.rec_hidden[((static_cast<int64_t>(row) * T + t) * K + k) * H + c0 + cc] = hid;
+                    }
+                    act[pb * kSlice + cc] = maybe_bf16(gelu_erf(hid), bf);
+                }
+            } else if (!is_gate) {
+                act[pb * kSlice + cc] = 0.0f;
+            }
+        }
+        if (is_gate) continue;
+        __syncthreads();
+        for (int e = tid; e < nb * d; e += blockDim.x) {
+            const int pb = e / d, x = e - pb * d;
+            float sum = 0.0f;
+            for (int k2 = 0; k2 < kSlice; ++k2) sum += act[pb * kSlice + k2] * w2[k2 * d + x];
+            c.part_f[(static_cast<int64_t>(s) * P + list[base + pb]) * d + x] = sum;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// update: one block per row. Shared (dynamic): slot_of [N], F [K d], y [K d], hnew [K d],
+// delta [K d], cell_of [K], scale [K], wo [d d].
+// ------------------------------------------------------------------------------------------------
+__global__ void k_update(FwdCtx c, int t) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    __shared__ int ired[32];
+    const int N = c.m.N, d = c.m.d, K = c.m.K;
+    const int B = c.io.B, T = c.io.T, P = B * K;
+    const bool bf = c.m.prod_bf16 != 0;
+    const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+    const int lane = tid & 31, warp = tid >> 5, warps = nt >> 5;
+    int* slot_of = reinterpret_cast<int*>(dyn);
+    float* Fs = reinterpret_cast<float*>(slot_of + ((N + 3) & ~3));  // keeps the rows 16-byte aligned
+    float* ys = Fs + K * d;
+    float* hnew = ys + K * d;
+    float* delta = hnew + K * d;
+    int* cell_of = reinterpret_cast<int*>(delta + K * d);
+    float* scale = reinterpret_cast<float*>(cell_of + K);
+    float* wo = scale + K;
+    const int64_t rt = static_cast<int64_t>(row) * T + t;
+    const int64_t pair0 = static_cast<int64_t>(row) * K;
+    const int64_t* cells = c.io.cells + rt * K;
+    const int64_t* units = c.io.units + rt * K;
+    const uint8_t* valid = c.io.valid + rt * K;
+    const float* h = state_h(c, row, t);
+    const float* q = state_q(c, row, t);
+    const int64_t* age = state_age(c, row, t);
+    const bool last = t + 1 == T;
+    const bool clear = !last && c.io.reset[rt + 1] != 0;
+    for (int e = tid; e < d * d; e += nt) wo[e] = c.m.wout_t[e];
+    for (int n = tid; n < N; n += nt) slot_of[n] = -1;
+    for (int k = tid; k < K; k += nt) cell_of[k] = valid[k] ? static_cast<int>(cells[k]) : -1;
+    __syncthreads();
+    for (int k = tid; k < K; k += nt)
+        if (cell_of[k] >= 0) slot_of[cell_of[k]] = k;
+    // the executed unit's output: the second layer's partial sums in slice order, plus its bias
+    for (int e = tid; e < K * d; e += nt) {
+        const int k = e / d, x = e - k * d;
+        float sum = 0.0f;
+        if (cell_of[k] >= 0) {
+            for (int s = 0; s < c.nHS; ++s) sum += c.part_f[(static_cast<int64_t>(s) * P + pair0 + k) * d + x];
+            sum = maybe_bf16(sum + c.m.b2[static_cast<int>(units[k]) * d + x], bf);
+        }
+        Fs[e] = sum;
+    }
+    __syncthreads();
+    for (int e = tid; e < K * d; e += nt) {
+        const int k = e / d, x = e - k * d;
+        float sum = 0.0f;
+        for (int i = 0; i < d; ++i) sum += Fs[k * d + i] * wo[i * d + x];
+        ys[e] = maybe_bf16(sum, bf);
+    }
+    __syncthreads();
+    for (int k = warp; k < K; k += warps) {
+        float sq = 0.0f;
+        for (int x = lane; x < d; x += 32) sq += ys[k * d + x] * ys[k * d + x];
+        sq = warp_sum(sq);
+        if (lane == 0) scale[k] = rsqrtf(sq / static_cast<float>(d) + c.m.cand_eps);
+    }
+    __syncthreads();
+    for (int e = tid; e < K * d; e += nt) {
+        const int k = e / d, x = e - k * d;
+        const int n = cell_of[k];
+        float value = 0.0f, change = 0.0f, cv = 0.0f, bv = 0.0f, gp = 0.0f;
+        if (n >= 0) {
+            const float old = h[static_cast<int64_t>(n) * d + x];
+            cv = tanhf(ys[e] * scale[k] * c.m.cand_w[x]);
+            gp = c.gate_pre[(pair0 + k) * d + x];
+            bv = sigmoid_f(gp);
+            value = (1.0f - bv) * old + bv * cv;
+            change = value - old;
+        }
+        hnew[e] = value;
+        delta[e] = change;
+        if (c.io.rec_c) {
+            c.io.rec_c[rt * K * d + e] = cv;
+            c.io.rec_b[rt * K * d + e] = bv;
+            c.io.rec_y[rt * K * d + e] = ys[e];
+            c.io.rec_gate_pre[rt * K * d + e] = gp;
+        }
+    }
+    __syncthreads();
+    // summary, the slots' cells after the update, ages
+    float* q_next = c.io.tape_state ? c.io.tape_q + (static_cast<int64_t>(row) * (T + 1) + t + 1) * d
+                                    : c.io.q0 + static_cast<int64_t>(row) * d;
+    for (int x = tid; x < d; x += nt) {
+        float sum = 0.0f;
+        for (int k = 0; k < K; ++k) sum += delta[k * d + x];
+        const float after = q[x] + sum / static_cast<float>(N);
+        c.io.qs[rt * d + x] = after;
+        q_next[x] = clear ? 0.0f : after;
+    }
+    for (int e = tid; e < K * d; e += nt) {
+        const int k = e / d, x = e - k * d;
+        float value;
+        if (cell_of[k] >= 0) value = hnew[e];
+        else {
+            const int zero = slot_of[0];
+            value = zero >= 0 ? hnew[zero * d + x] : h[x];
+        }
+        c.io.h_sel[rt * K * d + e] = value;
+    }
+    int64_t* age_next = c.io.tape_state ? c.io.tape_age + (static_cast<int64_t>(row) * (T + 1) + t + 1) * N
+                                        : c.io.age0 + static_cast<int64_t>(row) * N;
+    for (int n = tid; n < N; n += nt) age_next[n] = (clear || slot_of[n] >= 0) ? 0 : age[n] + 1;
+    int top = 0;
+    const int d4 = d >> 2;
+    if (c.io.tape_state) {
+        // the next record: written cells from shared memory, the others carried, 16 bytes a thread
+        const float4* srcv = reinterpret_cast<const float4*>(h);
+        float4* dst = reinterpret_cast<float4*>(c.io.tape_h + (static_cast<int64_t>(row) * (T + 1) + t + 1) * N * d);
+        for (int e = tid; e < N * d4; e += nt) {
+            const int n = e / d4, x4 = e - n * d4;
+            const int k = slot_of[n];
+            float4 v = k >= 0 ? reinterpret_cast<const float4*>(hnew + k * d)[x4] : srcv[e];
+            top = max(top, __float_as_int(fabsf(v.x)));
+            top = max(top, __float_as_int(fabsf(v.y)));
+            top = max(top, __float_as_int(fabsf(v.z)));
+            top = max(top, __float_as_int(fabsf(v.w)));
+            if (clear) v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            dst[e] = v;
+        }
+    } else {
+        // resident state: only the written rows move (all of them on a reset); the maximum needs
+        // every cell and is taken only when asked for
+        float* hw = c.io.h0 + static_cast<int64_t>(row) * N * d;
+        if (c.io.h_max) {
+            for (int e = tid; e < N * d; e += nt) {
+                const int n = e / d, x = e - n * d;
+                const int k = slot_of[n];
+                const float v = k >= 0 ? hnew[k * d + x] : hw[e];
+                top = max(top, __float_as_int(fabsf(v)));
+            }
+            __syncthreads();
+        }
+        if (clear) {
+            for (int e = tid; e < N * d; e += nt) hw[e] = 0.0f;
+        } else {
+            for (int e = tid; e < K * d; e += nt) {
+                const int k = e / d, x = e - k * d;
+                if (cell_of[k] >= 0) hw[static_cast<int64_t>(cell_of[k]) * d + x] = hnew[e];
+            }
+        }
+    }
+    if (c.io.h_max) {
+        for (int w = 16; w > 0; w >>= 1) top = max(top, __shfl_xor_sync(0xffffffffu, top, w));
+        if (lane == 0) ired[warp] = top;
+        __syncthreads();
+        if (tid == 0) {
+            int mx = 0;
+            for (int w = 0; w < warps; ++w) mx = max(mx, ired[w]);
+            c.io.h_max[rt] = __int_as_float(mx);
+        }
+    }
+    if (last && tid == 0) {
+        // the position counter after the window (reference compile.py:1194-1200)
+        int last_reset = 0;
+        for (int s = 0; s < T; ++s)
+            if (c.io.reset[static_cast<int64_t>(row) * T + s]) last_reset = s + 1;
+        c.io.pos[row] = last_reset > 0 ? T + 1 - last_reset : c.io.pos[row] + T;
+    }
+}
+
+size_t align_up(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+struct Layout {
+    size_t pre_s, part_front, v, pair_unit, part_f, gate_pre, hidden, total;
+};
+Layout layout(const HsnwModel& m, int B, int T) {
+    Layout L;
+    const int nS = (m.H + kSlice - 1) / kSlice;
+    size_t off = 0;
+    L.pre_s = off; off += align_up(sizeof(float) * static_cast<size_t>(B) * T * m.H);
+    L.part_front = off; off += align_up(sizeof(float) * 2 * nS * static_cast<size_t>(B) * m.d);
+    L.v = off; off += align_up(sizeof(float) * static_cast<size_t>(B) * m.K * 4 * m.d);
+    L.pair_unit = off; off += align_up(sizeof(int) * static_cast<size_t>(B) * m.K);
+    L.part_f = off; off += align_up(sizeof(float) * nS * static_cast<size_t>(B) * m.K * m.d);
+    L.gate_pre = off; off += align_up(sizeof(float) * static_cast<size_t>(B) * m.K * m.d);
+    L.hidden = off; off += align_up(sizeof(float) * static_cast<size_t>(B) * m.K * m.H);
+    L.total = off;
+    return L;
+}
+
+size_t row_shared(const HsnwModel& m) {
+    const int feat = 3 * m.d + 1 + m.S;
+    return sizeof(float) * (static_cast<size_t>(2) * m.N + static_cast<size_t>(feat) * m.M + static_cast<size_t>(m.d) * m.d
+        + 2 * m.d + kMaxM + 2 * static_cast<size_t>(m.K) * m.D + static_cast<size_t>(m.K) * m.D * m.d
+        + 2 * static_cast<size_t>(m.K) * m.d + m.K);
+}
+size_t front_shared(const HsnwModel& m) {
+    return sizeof(float) * (static_cast<size_t>(2) * m.d * kSlice + static_cast<size_t>(kRowTile) * m.d + kRowTile * kSlice);
+}
+size_t unit_shared(const HsnwModel& m) {
+    return sizeof(float) * (static_cast<size_t>(4) * m.d * kSlice + static_cast<size_t>(kSlice) * m.d
+        + static_cast<size_t>(kPairBatch) * 4 * m.d + kPairBatch * kSlice + kPairTile);
+}
+size_t update_shared(const HsnwModel& m) {
+    return sizeof(float) * (static_cast<size_t>((m.N + 3) & ~3) + 4 * static_cast<size_t>(m.K) * m.d + 2 * m.K + static_cast<size_t>(m.d) * m.d);
+}
+
+int check_model(const HsnwModel* m) {
+    if (!m) return hsnw_fail(HSNW_E_ARG, "model is null");
+    if (m->N < 1 || m->d < 4 || (m->d & 3) || m->K < 1 || m->K > m->N || m->H < 1 || m->M < 1 || m->D < 1
+        || m->S < 0 || m->dc < 0)
+        return hsnw_fail(HSNW_E_ARG, "window: sizes must be positive, K <= N and d a multiple of 4");
+    if (m->M > kMaxM) return hsnw_fail(HSNW_E_UNSUPPORTED, "window: at most 16 units (M)");
+    if (m->K > kMaxSlots) return hsnw_fail(HSNW_E_UNSUPPORTED, "window: at most 64 slots (K)");
+    const size_t cap = hsnw_max_shared();
+    if (row_shared(*m) > cap || front_shared(*m) > cap || unit_shared(*m) > cap || update_shared(*m) > cap)
+        return hsnw_fail(HSNW_E_UNSUPPORTED, "window: a phase's working set exceeds a block's shared memory");
+    return HSNW_OK;
+}
+
+}  // namespace
+
+extern "C" int64_t hsnw_forward_scratch_bytes(const HsnwModel* model, int32_t B, int32_t T) {
+    if (!model || B < 1 || T < 1) return 0;
+    return static_cast<int64_t>(layout(*model, B, T).total);
+}
+
+extern "C" int hsnw_front_projection(const HsnwModel* model, const float* z, const float* ctx, int64_t rows,
+                                     float* out, void* stream) {
+    if (!model || !z || !ctx || !out || rows < 1) return hsnw_fail(HSNW_E_ARG, "front_projection: null or empty");
+    const dim3 grid(static_cast<unsigned>((rows + kSlice - 1) / kSlice), static_cast<unsigned>((model->H + kSlice - 1) / kSlice));
+    k_pre<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(*model, z, ctx, rows, out);
+    return hsnw_check_launch("front_projection");
+}
+
+static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* stream_) {
+    if (int rc = hsnw_require_prepared()) return rc;
+    if (int rc = check_model(model)) return rc;
+    if (!io || io->B < 1 || io->T < 1) return hsnw_fail(HSNW_E_ARG, "window_forward: B and T must be positive");
+    if (!io->z || !io->ctx || !io->scalars || !io->reset || !io->h0 || !io->q0 || !io->age0 || !io->pos
+        || !io->cells || !io->units || !io->valid || !io->refreshed || !io->theta || !io->h_sel || !io->qs)
+        return hsnw_fail(HSNW_E_ARG, "window_forward: a required pointer is null");
+    if (io->tape_state && (!io->tape_h || !io->tape_q || !io->tape_age || !io->h_max))
+        return hsnw_fail(HSNW_E_ARG, "window_forward: the state tape is missing");
+    if (io->rec_c && (!io->rec_b || !io->rec_h_old || !io->rec_y || !io->rec_gate_pre || !io->rec_m
+        || !io->rec_rms || !io->rec_hidden))
+        return hsnw_fail(HSNW_E_ARG, "window_forward: the record is all or nothing");
+    const Layout L = layout(*model, io->B, io->T);
+    if (!io->scratch || io->scratch_bytes < static_cast<int64_t>(L.total)
+        || (reinterpret_cast<uintptr_t>(io->scratch) & 255))
+        return hsnw_fail(HSNW_E_ARG, "window_forward: scratch too small or not 256-byte aligned");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    FwdCtx c;
+    c.m = *model;
+    c.io = *io;
+    c.nS = (model->H + kSlice - 1) / kSlice;
+    c.nHS = c.nS;
+    c.nG = (model->d + kSlice - 1) / kSlice;
+    unsigned char* base = static_cast<unsigned char*>(io->scratch);
+    c.pre_s = reinterpret_cast<float*>(base + L.pre_s);
+    c.part_front = reinterpret_cast<float*>(base + L.part_front);
+    c.v = reinterpret_cast<float*>(base + L.v);
+    c.pair_unit = reinterpret_cast<int*>(base + L.pair_unit);
+    c.part_f = reinterpret_cast<float*>(base + L.part_f);
+    c.gate_pre = reinterpret_cast<float*>(base + L.gate_pre);
+    c.hidden = reinterpret_cast<float*>(base + L.hidden);
+    const int B = io->B, T = io->T;
+    const int row_threads = model->N >= 1024 ? 1024 : model->N >= 512 ? 512 : 256;
+    k_init<<<B, 256, 0, stream>>>(c);
+    if (int rc = hsnw_front_projection(model, io->z, io->ctx, static_cast<int64_t>(B) * T, c.pre_s, stream)) return rc;
+    const dim3 front_grid(2 * c.nS, (B + kRowTile - 1) / kRowTile);
+    const dim3 unit_grid(model->M * c.nHS + c.nG, (B * model->K + kPairTile - 1) / kPairTile);
+    const size_t sh_front = front_shared(*model), sh_row = row_shared(*model);
+    const size_t sh_unit = unit_shared(*model), sh_update = update_shared(*model);
+    for (int t = 0; t < T; ++t) {
+        k_front<<<front_grid, 256, sh_front, stream>>>(c, t);
+        k_row<<<B, row_threads, sh_row, stream>>>(c, t);
+        k_unit<<<unit_grid, 256, sh_unit, stream>>>(c, t);
+        k_update<<<B, 256, sh_update, stream>>>(c, t);
+    }
+    return hsnw_check_launch("window_forward");
+}
+
+extern "C" int hsnw_window_forward(const HsnwModel* model, const HsnwForward* io, void* stream) {
+    return forward_impl(model, io, stream);
+}
+
+extern "C" int hsnw_stream_step(const HsnwModel* model, const HsnwForward* io, void* stream) {
+    if (io && (io->T != 1 || io->tape_state))
+        return hsnw_fail(HSNW_E_ARG, "stream_step: one position on a resident state (T = 1, tape_state = 0)");
+    return forward_impl(model, io, stream);
+}
+
+void hsnw_forward_set_attributes() {
+    const int cap = static_cast<int>(hsnw_max_shared());
+    cudaFuncSetAttribute(k_front, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
+    cudaFuncSetAttribute(k_row, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
+    cudaFuncSetAttribute(k_unit, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
+    cudaFuncSetAttribute(k_update, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
+}

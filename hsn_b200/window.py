@@ -1,0 +1,390 @@
+"""The whole-window entry points on torch tensors: forward sweep, reverse sweep, streaming step.
+
+Thin host code over the C ABI (``include/hsn_window_b200.h``): it validates tensors, allocates
+outputs and scratch with torch's caching allocator, passes ``data_ptr()`` and the current stream,
+and names the results as the reference does (the tape keys of
+``python/hsn/train/compile.py:1196-1231``, the arguments of ``state_gradient_backward``,
+``python/hsn/train/state_gradient.py:357-376``). No arithmetic happens here.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from collections.abc import Mapping
+from dataclasses import dataclass
+from typing import Any
+
+import torch
+from torch import Tensor
+
+from . import _lib
+
+__all__ = ["WindowModel", "window_forward", "window_backward", "stream_step", "prepare"]
+
+_WEIGHT_KEYS = (
+    "s_w1 s_b1 s_w2 s_b2 p_w1 p_b1 p_w2 p_b2 score_w score_b v_w wout_w gate_w gate_b norm_w cand_w "
+    "w1 b1 w2 b2 pad_src edge_w cost"
+).split()
+#: The weights a matrix product reads: rounded to bfloat16 once per window in the bf16 mode.
+_PRODUCT_KEYS = (
+    "s_w1 s_b1 s_w2 s_b2 p_w1 p_b1 p_w2 p_b2 score_w score_b v_w wout_w gate_w gate_b w1 b1 w2 b2"
+).split()
+
+
+def prepare(device: int | torch.device = 0) -> None:
+    """Make the library ready on ``device`` (idempotent). Fails loudly without the library."""
+    index = device.index or 0 if isinstance(device, torch.device) else int(device)
+    _lib.check(_lib.library().hsnw_prepare(index))
+
+
+def _stream(device: torch.device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _ptr(t: Tensor | None) -> ctypes.c_void_p | None:
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+@dataclass
+class WindowModel:
+    """A window's weights on the device in the kernels' layouts (``HsnwModel``).
+
+    ``weights`` holds torch-layout tensors or arrays under the names of the reference's modules:
+    ``s_*`` = ``shared`` and ``p_*`` = ``predictor`` (``fc1``/``fc2`` weight and bias,
+    ``python/hsn/model/encoder.py``), ``score_w/score_b`` = the linear scorer
+    (``python/hsn/model/router.py:319-321``), ``v_w``, ``wout_w``, ``gate_w/gate_b``, ``norm_w``,
+    ``cand_w`` = the cell (``python/hsn/model/cell.py:192-212``), ``w1 b1 w2 b2`` = the unit bank,
+    ``pad_src`` / ``edge_w`` = the padded cell graph with the window's edge weights, ``cost`` = the
+    router's cost table. ``prod="bf16"`` rounds the products' weights to bfloat16 here, once, as
+    the reference's sweep twin does per window (``python/hsn/train/compile.py:776-840``).
+    """
+
+    struct: _lib.HsnwModel
+    tensors: dict[str, Tensor]
+    device: torch.device
+    dims: dict[str, int]
+    prod: str
+
+    @staticmethod
+    def build(
+        weights: Mapping[str, Any],
+        *,
+        k: int,
+        device: torch.device | str = "cuda",
+        prod: str = "fp32",
+        age_max: int = 64,
+        probes: bool = True,
+        lambda_cost: float = 0.0,
+        cell_overhead: float = 0.0,
+        shared_cost: float = 0.0,
+        limit: float = 1.00001,
+        norm_eps: float = 1e-6,
+        cand_eps: float = 1e-6,
+    ) -> "WindowModel":
+        if prod not in ("fp32", "bf16"):
+            raise ValueError(f"prod must be 'fp32' or 'bf16', got {prod!r}")
+        device = torch.device(device)
+        if device.type != "cuda":
+            raise RuntimeError("the window kernels run on a CUDA device only (no CPU path)")
+        missing = [key for key in _WEIGHT_KEYS if key not in weights]
+        if missing:
+            raise KeyError(f"window weights missing: {missing}")
+        w: dict[str, Tensor] = {}
+        for key in _WEIGHT_KEYS:
+            t = torch.as_tensor(weights[key]).detach()
+            if key == "pad_src":
+                w[key] = t.to(device=device, dtype=torch.int32).contiguous()
+                continue
+            t = t.to(device=device, dtype=torch.float32)
+            if prod == "bf16" and key in _PRODUCT_KEYS:
+                t = t.to(torch.bfloat16).to(torch.float32)
+            w[key] = t.contiguous()
+        M, in4, H = (int(n) for n in w["w1"].shape)
+        d = in4 // 4
+        N, D = (int(n) for n in w["pad_src"].shape)
+        dc = int(w["s_w1"].shape[1]) - 2 * d
+        S = int(w["score_w"].shape[1]) - 3 * d - 1
+        if in4 != 4 * d or dc < 0 or S < 0 or tuple(w["w2"].shape) != (M, H, d):
+            raise ValueError("window weights have inconsistent shapes")
+        s_w1 = w["s_w1"]
+        packed = {
+            "s_w1zc_t": torch.cat([s_w1[:, :d], s_w1[:, 2 * d :]], dim=1).t().contiguous(),
+            "f_w1q_t": torch.cat([s_w1[:, d : 2 * d].t(), w["p_w1"].t()], dim=1).contiguous(),
+            "f_b1": torch.cat([w["s_b1"], w["p_b1"]]).contiguous(),
+            "f_w2_t": torch.cat([w["s_w2"].t(), w["p_w2"].t()], dim=0).contiguous(),
+            "f_b2": torch.cat([w["s_b2"], w["p_b2"]]).contiguous(),
+            "score_w_t": w["score_w"].t().contiguous(),
+            "score_b": w["score_b"],
+            "v_t": w["v_w"].t().contiguous(),
+            "wout_t": w["wout_w"].t().contiguous(),
+            "gate_t": w["gate_w"].t().contiguous(),
+            "gate_b": w["gate_b"],
+            "norm_w": w["norm_w"],
+            "cand_w": w["cand_w"],
+            "w1": w["w1"],
+            "b1": w["b1"],
+            "w2": w["w2"],
+            "b2": w["b2"],
+            "pad_src": w["pad_src"],
+            "edge_w": w["edge_w"],
+            "cost": w["cost"],
+        }
+        struct = _lib.HsnwModel()
+        dims = dict(N=N, d=d, K=int(k), H=H, M=M, D=D, S=S, dc=dc)
+        for name, value in dims.items():
+            setattr(struct, name, value)
+        struct.prod_bf16 = int(prod == "bf16")
+        struct.probes = int(bool(probes))
+        struct.age_max = int(min(age_max, 2**31 - 1))
+        struct.lambda_cost, struct.cell_overhead = float(lambda_cost), float(cell_overhead)
+        struct.shared_cost, struct.limit = float(shared_cost), float(limit)
+        struct.norm_eps, struct.cand_eps = float(norm_eps), float(cand_eps)
+        for name in _lib.MODEL_POINTERS:
+            setattr(struct, name, packed[name].data_ptr())
+        prepare(device)
+        return WindowModel(struct=struct, tensors=packed, device=device, dims=dims, prod=prod)
+
+    @staticmethod
+    def from_oracle_weights(W: Any, *, device: torch.device | str = "cuda", prod: str = "fp32") -> "WindowModel":
+        """From an object with the weights as attributes and the router's scalars (the fixtures'
+        ``WindowWeights``): a convenience of the tests and the benchmark."""
+        weights = {key: getattr(W, key) for key in _WEIGHT_KEYS}
+        return WindowModel.build(
+            weights, k=W.k, device=device, prod=prod, age_max=W.age_max, probes=W.probes,
+            lambda_cost=W.lambda_cost, cell_overhead=W.cell_overhead, shared_cost=W.shared_cost,
+            limit=W.limit, norm_eps=W.norm_eps, cand_eps=W.cand_eps,
+        )  # fmt: skip
+
+    @staticmethod
+    def from_hsn(model: Any, *, prod: str = "fp32", probes: bool = True) -> "WindowModel":
+        """From a reference ``HSN`` module (``python/hsn/model/hsn.py``), inside or outside its
+        ``cell.window()``: reads the modules' parameters and the graph's padded edge weights."""
+        cell, router, scorer = model.cell, model.router, model.scorer
+        with cell.window():
+            edge_w = cell.graph._padded_weights().detach().clone()
+        weights = {
+            "s_w1": model.shared.fc1.weight, "s_b1": model.shared.fc1.bias,
+            "s_w2": model.shared.fc2.weight, "s_b2": model.shared.fc2.bias,
+            "p_w1": model.predictor.fc1.weight, "p_b1": model.predictor.fc1.bias,
+            "p_w2": model.predictor.fc2.weight, "p_b2": model.predictor.fc2.bias,
+            "score_w": scorer.net.weight, "score_b": scorer.net.bias,
+            "v_w": cell.V.weight, "wout_w": cell.W_out.weight,
+            "gate_w": cell.gate.weight, "gate_b": cell.gate.bias,
+            "norm_w": cell.norm.weight, "cand_w": cell.cand_norm.weight,
+            "w1": cell.units.W1, "b1": cell.units.b1, "w2": cell.units.W2, "b2": cell.units.b2,
+            "pad_src": cell.graph._pad_src, "edge_w": edge_w, "cost": router.cost_table,
+        }  # fmt: skip
+        device = next(model.parameters()).device
+        return WindowModel.build(
+            weights, k=int(model.cfg.k_select), device=device, prod=prod, age_max=int(router.age_max),
+            probes=probes, lambda_cost=float(router.lambda_cost),
+            cell_overhead=float(router.cell_overhead), shared_cost=float(router.shared_cost),
+            limit=float(model.cfg.budget) * (1.0 + 1e-5), norm_eps=float(cell.norm.eps),
+            cand_eps=float(cell.cand_norm.eps),
+        )  # fmt: skip
+
+
+def _check(name: str, t: Tensor, shape: tuple[int, ...], dtype: torch.dtype, device: torch.device) -> Tensor:
+    if t.device != device or t.dtype != dtype or tuple(t.shape) != shape:
+        raise ValueError(
+            f"{name} must be a {dtype} tensor of shape {shape} on {device}, got {t.dtype} "
+            f"{tuple(t.shape)} on {t.device}"
+        )
+    return t.contiguous()
+
+
+def window_forward(
+    model: WindowModel,
+    z: Tensor,
+    ctx: Tensor,
+    scalars: Tensor,
+    reset: Tensor,
+    state: tuple[Tensor, Tensor, Tensor, Tensor],
+    *,
+    record: bool = True,
+    tape_state: bool = True,
+    forced: tuple[Tensor, Tensor, Tensor] | None = None,
+    want_logits: bool = False,
+    scratch: Tensor | None = None,
+    out: dict[str, Tensor] | None = None,
+) -> dict[str, Tensor]:
+    """The forward sweep of one window (``hsnw_window_forward``): the reference's tape
+    (``python/hsn/train/compile.py:1196-1213``) for ``z [B,T,d]``, ``ctx [B,T,dc]``, ``scalars
+    [B,T,N,S]`` (the prologue's, ``python/hsn/model/hsn.py:1741-1830``), ``reset [B,T]`` bool and
+    the carried ``state = (h, q, age, pos)``, which is not modified with ``tape_state`` (the final
+    state is returned under ``h q age pos``). ``record`` adds ``rec_*``: the per-slot values the
+    state-gradient sweep reads. ``forced = (cells, units, valid)`` replays a recorded decision.
+    ``tape_state=False`` keeps no state tape and updates ``state`` in place (large ``N``).
+    ``out`` reuses the buffers of an earlier call's result (static addresses)."""
+    dm = model.dims
+    dev = model.device
+    B, T = int(reset.shape[0]), int(reset.shape[1])
+    N, d, K, H, M, S, dc = dm["N"], dm["d"], dm["K"], dm["H"], dm["M"], dm["S"], dm["dc"]
+    f32, i64 = torch.float32, torch.int64
+    z = _check("z", z, (B, T, d), f32, dev)
+    ctx = _check("ctx", ctx, (B, T, dc), f32, dev)
+    scalars = _check("scalars", scalars, (B, T, N, S), f32, dev)
+    reset_u8 = _check("reset", reset, (B, T), torch.bool, dev).view(torch.uint8)
+    h0 = _check("state.h", state[0], (B, N, d), f32, dev)
+    q0 = _check("state.q", state[1], (B, d), f32, dev)
+    age0 = _check("state.age", state[2], (B, N), i64, dev)
+    pos = _check("state.pos", state[3], (B,), i64, dev)
+    if tape_state:
+        pos = pos.clone()
+    lib = _lib.library()
+    o = out if out is not None else {}
+
+    def buf(name: str, shape: tuple[int, ...], dtype: torch.dtype) -> Tensor:
+        if name not in o:
+            o[name] = torch.empty(shape, dtype=dtype, device=dev)
+        return o[name]
+
+    io = _lib.HsnwForward()
+    io.B, io.T, io.tape_state, io.forced = B, T, int(tape_state), int(forced is not None)
+    io.z, io.ctx, io.scalars, io.reset = z.data_ptr(), ctx.data_ptr(), scalars.data_ptr(), reset_u8.data_ptr()
+    io.h0, io.q0, io.age0, io.pos = h0.data_ptr(), q0.data_ptr(), age0.data_ptr(), pos.data_ptr()
+    if tape_state:
+        io.tape_h = buf("_tape_h", (B, T + 1, N, d), f32).data_ptr()
+        io.tape_q = buf("_tape_q", (B, T + 1, d), f32).data_ptr()
+        io.tape_age = buf("_tape_age", (B, T + 1, N), i64).data_ptr()
+    cells = buf("sel_cell_idx", (B, T, K), i64)
+    units = buf("sel_unit_idx", (B, T, K), i64)
+    valid = buf("sel_valid", (B, T, K), torch.bool)
+    if forced is not None:
+        cells.copy_(_check("forced cells", forced[0], (B, T, K), i64, dev))
+        units.copy_(_check("forced units", forced[1], (B, T, K), i64, dev))
+        valid.copy_(_check("forced valid", forced[2], (B, T, K), torch.bool, dev))
+    io.cells, io.units, io.valid = cells.data_ptr(), units.data_ptr(), valid.data_ptr()
+    io.refreshed = buf("sel_refreshed", (B, T, K), torch.bool).data_ptr()
+    io.theta = buf("tape_theta", (B, T), f32).data_ptr()
+    io.h_sel = buf("tape_hsel", (B, T, K, d), f32).data_ptr()
+    io.qs = buf("qs", (B, T, d), f32).data_ptr()
+    if tape_state:
+        io.h_max = buf("h_max", (B, T), f32).data_ptr()
+    if record:
+        for name in ("c", "b", "h_old", "y", "gate_pre", "m"):
+            setattr(io, "rec_" + name, buf("rec_" + name, (B, T, K, d), f32).data_ptr())
+        io.rec_rms = buf("rec_rms", (B, T, K), f32).data_ptr()
+        io.rec_hidden = buf("rec_hidden", (B, T, K, H), f32).data_ptr()
+    if want_logits:
+        io.logits = buf("logits", (B, T, N, M), f32).data_ptr()
+    need = int(lib.hsnw_forward_scratch_bytes(ctypes.byref(model.struct), B, T))
+    if scratch is None:
+        scratch = buf("_scratch", (need,), torch.uint8)
+    if scratch.numel() < need or scratch.device != dev:
+        raise ValueError(f"scratch must hold {need} bytes on {dev}")
+    io.scratch, io.scratch_bytes = scratch.data_ptr(), scratch.numel()
+    with torch.cuda.device(dev):
+        _lib.check(lib.hsnw_window_forward(ctypes.byref(model.struct), ctypes.byref(io), _stream(dev)))
+    if tape_state:
+        o["tape_h"], o["tape_q"], o["tape_age"] = o["_tape_h"][:, :T], o["_tape_q"][:, :T], o["_tape_age"][:, :T]
+        o["h"], o["q"], o["age"] = o["_tape_h"][:, T], o["_tape_q"][:, T], o["_tape_age"][:, T]
+        o["state_abs_max"] = o["h_max"].amax(dim=0)
+    else:
+        o["h"], o["q"], o["age"] = h0, q0, age0
+    o["pos"] = pos
+    if forced is None:
+        o["refreshed"] = o["sel_refreshed"].float().sum(dim=2).mean(dim=0)
+    o["explored"] = torch.zeros(T, dtype=f32, device=dev)
+    return o
+
+
+def stream_step(
+    model: WindowModel,
+    z_t: Tensor,
+    ctx_t: Tensor,
+    scalars_t: Tensor,
+    reset_t: Tensor,
+    state: tuple[Tensor, Tensor, Tensor, Tensor],
+    *,
+    out: dict[str, Tensor] | None = None,
+) -> dict[str, Tensor]:
+    """One position on a resident state, updated in place (``hsnw_stream_step``): the serving
+    step's state update (``python/hsn/train/compile.py:1913-2006``). ``z_t [B,d]``, ``ctx_t
+    [B,dc]``, ``scalars_t [B,N,S]``, ``reset_t [B]`` bool. Returns the decision and the slots'
+    states (``sel_*``, ``tape_hsel``, ``qs``) of the position."""
+    return window_forward(
+        model, z_t[:, None], ctx_t[:, None], scalars_t[:, None], reset_t[:, None], state,
+        record=False, tape_state=False, out=out,
+    )  # fmt: skip
+
+
+def window_backward(
+    model: WindowModel,
+    c: Tensor,
+    b: Tensor,
+    h_old: Tensor,
+    cells: Tensor,
+    units: Tensor | None,
+    valid: Tensor,
+    reset: Tensor,
+    d_q_pre: Tensor | None,
+    d_q_post: Tensor | None,
+    d_h_sel: Tensor | None,
+    record: Mapping[str, Tensor] | None,
+    *,
+    initial: tuple[Tensor, Tensor] | None = None,
+    full_cut: bool = False,
+    scratch: Tensor | None = None,
+) -> tuple[Tensor, Tensor, tuple[Tensor, Tensor]]:
+    """The reverse sweep of one window (``hsnw_window_backward``): ``(dc, db, (A, R))``.
+
+    The arguments are ``state_gradient_backward``'s (``python/hsn/train/state_gradient.py:357-376``;
+    ``record`` holds ``y gate_pre m rms hidden``), or with ``full_cut`` ``recurrence_backward``'s
+    (``python/hsn/train/split.py:128-139``; ``units`` and ``record`` unused). ``initial`` is the
+    cotangent of the state after the last position (the next window's returned ``(A, R)``); the
+    returned ``(A, R)`` is the cotangent of the state this window started from."""
+    dm = model.dims
+    dev = model.device
+    B, T, K, d = (int(n) for n in c.shape)
+    N, H = dm["N"], dm["H"]
+    f32, i64 = torch.float32, torch.int64
+    if K != dm["K"] or d != dm["d"]:
+        raise ValueError(f"c must be [B, T, {dm['K']}, {dm['d']}], got {tuple(c.shape)}")
+    io = _lib.HsnwBackward()
+    io.B, io.T, io.full_cut = B, T, int(full_cut)
+    keep: list[Tensor] = []
+
+    def put(field: str, t: Tensor | None, shape: tuple[int, ...], dtype: torch.dtype) -> None:
+        if t is None:
+            return
+        t = _check(field, t, shape, dtype, dev)
+        keep.append(t)
+        setattr(io, field, t.data_ptr())
+
+    put("c", c, (B, T, K, d), f32)
+    put("b", b, (B, T, K, d), f32)
+    put("h_old", h_old, (B, T, K, d), f32)
+    put("cells", cells, (B, T, K), i64)
+    valid_u8 = _check("valid", valid, (B, T, K), torch.bool, dev).view(torch.uint8)
+    reset_u8 = _check("reset", reset, (B, T), torch.bool, dev).view(torch.uint8)
+    io.valid, io.reset = valid_u8.data_ptr(), reset_u8.data_ptr()
+    put("d_q_pre", d_q_pre, (B, T, d), f32)
+    put("d_q_post", d_q_post, (B, T, d), f32)
+    put("d_h_sel", d_h_sel, (B, T, K, d), f32)
+    if not full_cut:
+        if record is None or units is None:
+            raise ValueError("the state-gradient sweep needs units and the round's record")
+        put("units", units, (B, T, K), i64)
+        put("y", record["y"], (B, T, K, d), f32)
+        put("gate_pre", record["gate_pre"], (B, T, K, d), f32)
+        put("m", record["m"], (B, T, K, d), f32)
+        put("rms", record["rms"], (B, T, K), f32)
+        put("hidden", record["hidden"], (B, T, K, H), f32)
+    dc = torch.empty((B, T, K, d), dtype=f32, device=dev)
+    db = torch.empty((B, T, K, d), dtype=f32, device=dev)
+    if initial is None:
+        A = torch.zeros((B, N, d), dtype=f32, device=dev)
+        R = torch.zeros((B, d), dtype=f32, device=dev)
+    else:
+        A = _check("initial A", initial[0], (B, N, d), f32, dev).clone()
+        R = _check("initial R", initial[1], (B, d), f32, dev).clone()
+    io.dc, io.db, io.A, io.R = dc.data_ptr(), db.data_ptr(), A.data_ptr(), R.data_ptr()
+    lib = _lib.library()
+    need = int(lib.hsnw_backward_scratch_bytes(ctypes.byref(model.struct), B, T))
+    if scratch is None:
+        scratch = torch.empty((max(need, 256),), dtype=torch.uint8, device=dev)
+    io.scratch, io.scratch_bytes = scratch.data_ptr(), scratch.numel()
+    with torch.cuda.device(dev):
+        _lib.check(lib.hsnw_window_backward(ctypes.byref(model.struct), ctypes.byref(io), _stream(dev)))
+    return dc, db, (A, R)

@@ -1,0 +1,220 @@
+/* hsn_window_b200: the HSN TBPTT window path as hand-written sm_100a CUDA behind a C ABI.
+ *
+ * Plain pointers and sizes only: no torch types, no C++ in the signatures. Every pointer named
+ * "device" is an address in the caller's current CUDA context on the device given to
+ * hsnw_prepare. No entry point synchronises the device or the stream (except hsnw_prepare),
+ * and none allocates device memory: outputs and scratch are the caller's.
+ * Every function returns 0 on success and a negative HSNW_E_* code otherwise;
+ * hsnw_last_error() then holds a message (thread-local).
+ *
+ * Reference interfaces replaced (paths inside the reference project):
+ *   kernels/include/hsn_window_launch.h:9-16        HsnWinArgs, kept bit for bit
+ *   python/hsn/kernels/window_ext.cpp:41-56          prepare        -> hsnw_prepare
+ *   python/hsn/kernels/window_ext.cpp:105-115        launch         -> hsnw_launch
+ *   python/hsn/kernels/window_ext.cpp:117-127        launch_views   -> hsnw_launch (views are plain
+ *                                                                      addresses here)
+ *   python/hsn/kernels/window_ext.cpp:129-153        loop           -> hsnw_loop
+ *   kernels/cuda/hsn_window.cu:59,124,563,792,1014,1183,1334  the kernels launched by name
+ *   python/hsn/train/compile.py:1037-1213 (the folded forward sweep), python/hsn/train/
+ *   state_sweep.py:359-384 (the reverse sweep's loop), python/hsn/train/compile.py:1913-2006
+ *   (the serving step)                               -> hsnw_window_forward / _backward /
+ *                                                       hsnw_stream_step
+ */
+#ifndef HSN_WINDOW_B200_H
+#define HSN_WINDOW_B200_H
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HSNW_OK 0
+#define HSNW_E_ARG (-1)        /* a size, flag or pointer the entry point does not take */
+#define HSNW_E_UNSUPPORTED (-2) /* a shape beyond a kernel's limits (message says which) */
+#define HSNW_E_CUDA (-3)       /* the CUDA runtime reported an error */
+#define HSNW_E_NAME (-4)       /* hsnw_launch: no kernel of that name */
+#define HSNW_E_STATE (-5)      /* hsnw_prepare was not called on this device */
+
+/* The launch descriptor of the kernels launched by name: the reference's own
+ * (kernels/include/hsn_window_launch.h:9-16), same field order and sizes (544 bytes). Each
+ * kernel's p[] / i[] / f[] slots are the reference kernel's of the same name. */
+#define HSN_WIN_POINTERS 48
+#define HSN_WIN_INTS 32
+#define HSN_WIN_FLOATS 8
+typedef struct HsnWinArgs {
+    void* p[HSN_WIN_POINTERS];
+    int32_t i[HSN_WIN_INTS];
+    float f[HSN_WIN_FLOATS];
+} HsnWinArgs;
+
+/* Library version (major * 10000 + minor * 100 + patch). */
+int hsnw_version(void);
+/* The calling thread's last error message ("" if none). */
+const char* hsnw_last_error(void);
+/* Make `device` ready: checks that it is an sm_100 part, opts the kernels in to large dynamic
+ * shared memory and records the SM count. Idempotent; the only call that may synchronise.
+ * Replaces window_ext.cpp:41-56 (there: cuModuleLoad of a fatbin per context). */
+int hsnw_prepare(int device);
+/* 1 when hsnw_prepare succeeded for `device`. */
+int hsnw_prepared(int device);
+/* The number of SMs of a prepared device (0 otherwise). */
+int hsnw_sm_count(int device);
+
+/* One launch of the kernel `name` with `grid` blocks of `block` threads and `shared` bytes of
+ * dynamic shared memory on `stream` (a cudaStream_t; NULL: the default stream).
+ * Names: hsn_win_select, hsn_win_cell_update, hsn_win_recurrence, hsn_win_recurrence_dense,
+ * hsn_win_back_head, hsn_win_back_mid, hsn_win_back_tail.
+ * grid <= 0 launches nothing (window_ext.cpp:96). Capturable in a CUDA graph. */
+int hsnw_launch(const char* name, const HsnWinArgs* args, int64_t grid, int block, int shared,
+                void* stream);
+/* `steps` rounds of the kernels names[0..count) in order; round t runs them with
+ * args->i[slot] = t (window_ext.cpp:129-153). */
+int hsnw_loop(const char* const* names, int count, const int64_t* grids, const int* blocks,
+              const int* shareds, const HsnWinArgs* args, int64_t steps, int slot, void* stream);
+/* The launch shape this library wants for a by-name kernel at the sizes in `args` (the
+ * reference's Python wrappers hard-code theirs, window.py:38-53,1151-1162): fills grid, block,
+ * shared. Returns HSNW_E_UNSUPPORTED with a reason when the kernel cannot take the shape. */
+int hsnw_launch_shape(const char* name, const HsnWinArgs* args, int64_t* grid, int* block,
+                      int* shared);
+
+/* ------------------------------------------------------------------------------------------------
+ * Whole-window entry points.
+ * Sizes: B rows, T positions, N cells, d state width, K slots, H hidden width, M units,
+ * D padded in-degree, S scorer scalars per cell, dc context width.
+ * ---------------------------------------------------------------------------------------------- */
+
+/* The window's weights on the device, fp32, in the layouts the kernels read ("_t": transposed to
+ * input-major so that consecutive threads read consecutive outputs). With prod_bf16 the values
+ * must already be rounded to bfloat16 (the host rounds them once per window, as the reference's
+ * SweepTwin.refresh does, compile.py:776-840); the kernels then round the products' other
+ * operand and their outputs to bfloat16 and accumulate in fp32. */
+typedef struct HsnwModel {
+    int32_t N, d, K, H, M, D, S, dc;
+    int32_t prod_bf16;      /* 0: fp32 products; 1: bf16 operands, fp32 accumulation */
+    int32_t probes;         /* refresh probes on (router.py:1788-1850) */
+    int32_t age_max;
+    int32_t reserved_;      /* keep 0 */
+    float lambda_cost, cell_overhead, shared_cost, limit; /* limit = budget * (1 + 1e-5) */
+    float norm_eps, cand_eps;
+    const float* s_w1zc_t;  /* [d + dc, H]  shared.fc1 rows of z, then of ctx */
+    const float* f_w1q_t;   /* [d, 2H]      shared.fc1 rows of q | predictor.fc1 */
+    const float* f_b1;      /* [2H]         shared.fc1.bias | predictor.fc1.bias */
+    const float* f_w2_t;    /* [2H, d]      shared.fc2 (rows 0..H) ; predictor.fc2 (rows H..2H) */
+    const float* f_b2;      /* [2d]         shared.fc2.bias | predictor.fc2.bias */
+    const float* score_w_t; /* [3d + 1 + S, M] */
+    const float* score_b;   /* [M] */
+    const float* v_t;       /* [d, d]   (V h)[x] = sum_i h[i] v_t[i][x] */
+    const float* wout_t;    /* [d, d] */
+    const float* gate_t;    /* [4d, d] */
+    const float* gate_b;    /* [d] */
+    const float* norm_w;    /* [4d] */
+    const float* cand_w;    /* [d] */
+    const float* w1;        /* [M, 4d, H] */
+    const float* b1;        /* [M, H] */
+    const float* w2;        /* [M, H, d] */
+    const float* b2;        /* [M, d] */
+    const int32_t* pad_src; /* [N, D] */
+    const float* edge_w;    /* [N, D] (0 on padding) */
+    const float* cost;      /* [M] */
+} HsnwModel;
+
+/* Inputs, tape and record of a forward sweep. Row-major, contiguous. Null = not wanted, for the
+ * pointers marked optional.
+ *   tape_state != 0: the reference's tape (compile.py:1196-1213): tape_h [B,T+1,N,d],
+ *     tape_q [B,T+1,d], tape_age [B,T+1,N] (i64); record 0 is written from (h0, q0, age0) with
+ *     reset[:,0] applied, record t+1 after position t (zeroed when reset[:,t+1]); the final
+ *     state is record T.
+ *   tape_state == 0 ("resident"): h0/q0/age0 are updated in place, no state tape is kept;
+ *     tape_h/q/age are ignored.
+ */
+typedef struct HsnwForward {
+    int32_t B, T;
+    int32_t tape_state;
+    int32_t forced;            /* 1: cells/units/valid are inputs (a recorded decision replayed) */
+    const float* z;            /* [B,T,d] */
+    const float* ctx;          /* [B,T,dc] */
+    const float* scalars;      /* [B,T,N,S] */
+    const uint8_t* reset;      /* [B,T] */
+    float* h0;                 /* [B,N,d] start state (resident: updated in place) */
+    float* q0;                 /* [B,d] */
+    int64_t* age0;             /* [B,N] */
+    int64_t* pos;              /* [B] in/out (compile.py:1194-1200) */
+    float* tape_h;
+    float* tape_q;
+    int64_t* tape_age;
+    int64_t* cells;            /* [B,T,K] */
+    int64_t* units;            /* [B,T,K] */
+    uint8_t* valid;            /* [B,T,K] */
+    uint8_t* refreshed;        /* [B,T,K] */
+    float* theta;              /* [B,T] */
+    float* h_sel;              /* [B,T,K,d] */
+    float* qs;                 /* [B,T,d] */
+    float* h_max;              /* [B,T] */
+    /* the round's values per slot, what the state-gradient sweep reads (optional as a group:
+     * rec_c null = none): c, b, h_old, y, gate_pre, m [B,T,K,d]; rms [B,T,K]; hidden [B,T,K,H] */
+    float* rec_c;
+    float* rec_b;
+    float* rec_h_old;
+    float* rec_y;
+    float* rec_gate_pre;
+    float* rec_m;
+    float* rec_rms;
+    float* rec_hidden;
+    float* logits;             /* optional [B,T,N,M]: the scorer's logits (tests) */
+    void* scratch;             /* hsnw_forward_scratch_bytes() bytes, 256-byte aligned */
+    int64_t scratch_bytes;
+} HsnwForward;
+
+int64_t hsnw_forward_scratch_bytes(const HsnwModel* model, int32_t B, int32_t T);
+/* The forward sweep of one window for B rows: per position the shared path, the scorer, the
+ * router's decision, the gather of the selected cells and their messages, the executed unit,
+ * the gated update with write-back and the next position's reset. */
+int hsnw_window_forward(const HsnwModel* model, const HsnwForward* io, void* stream);
+/* One position on a resident state: hsnw_window_forward with T = 1, tape_state = 0. */
+int hsnw_stream_step(const HsnwModel* model, const HsnwForward* io, void* stream);
+
+/* The reverse sweep of one window (state_gradient.py:357-485; full_cut != 0: split.py:128-174).
+ * A [B,N,d] and R [B,d] are in/out: on entry the cotangent of the state after the last position
+ * (zeros for a window whose final state is detached; the next window's result when windows are
+ * chained), on return the cotangent of the state the window started from, already zeroed on the
+ * rows whose column 0 resets. */
+typedef struct HsnwBackward {
+    int32_t B, T;
+    int32_t full_cut;
+    int32_t pad_;
+    const float* c;            /* [B,T,K,d] */
+    const float* b;
+    const float* h_old;
+    const float* y;            /* state gradient only, as are gate_pre, m, rms, hidden, units */
+    const float* gate_pre;
+    const float* m;
+    const float* rms;          /* [B,T,K] */
+    const float* hidden;       /* [B,T,K,H] */
+    const int64_t* cells;      /* [B,T,K] (0 on padded slots) */
+    const int64_t* units;
+    const uint8_t* valid;
+    const uint8_t* reset;      /* [B,T] */
+    const float* d_q_pre;      /* optional [B,T,d] */
+    const float* d_q_post;     /* optional [B,T,d] */
+    const float* d_h_sel;      /* optional [B,T,K,d] */
+    float* dc;                 /* [B,T,K,d] out */
+    float* db;
+    float* A;                  /* [B,N,d] in/out */
+    float* R;                  /* [B,d] in/out */
+    void* scratch;             /* hsnw_backward_scratch_bytes() bytes, 256-byte aligned */
+    int64_t scratch_bytes;
+} HsnwBackward;
+
+int64_t hsnw_backward_scratch_bytes(const HsnwModel* model, int32_t B, int32_t T);
+int hsnw_window_backward(const HsnwModel* model, const HsnwBackward* io, void* stream);
+
+/* The window-invariant part of the shared path's first layer for every position:
+ * out [B*T, H] = [z ; ctx] [B*T, d+dc] x s_w1zc_t + shared.fc1.bias, one dense product
+ * (hsnw_window_forward calls it itself; exported for tests and measurements). */
+int hsnw_front_projection(const HsnwModel* model, const float* z, const float* ctx, int64_t rows,
+                          float* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,377 @@
+"""GPU parity of the whole-window entry points (forward sweep, reverse sweep, streaming step,
+carried state) against the reference's fixtures and the oracle, through the C ABI."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+from conftest import load_golden
+
+from oracle import window_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+F32 = torch.float32
+
+
+def dev(a, dtype=None):
+    t = torch.as_tensor(np.ascontiguousarray(a))
+    if dtype is not None:
+        t = t.to(dtype)
+    return t.cuda()
+
+
+def _model(z, K, prod="fp32"):
+    from hsn_b200.window import WindowModel
+
+    W = O.WindowWeights.from_npz(z, K, np.dtype(np.float32))
+    return W, WindowModel.from_oracle_weights(W, device="cuda", prod=prod)
+
+
+def _inputs(z):
+    return (
+        dev(z["z"], F32), dev(z["ctx"], F32), dev(z["scalars"], F32), dev(z["reset"].astype(bool)),
+        (dev(z["h0"], F32), dev(z["q0"], F32), dev(z["age0"]), dev(z["pos0"])),
+    )  # fmt: skip
+
+
+WINDOWS = ["c1_f32", "c1_f64", "c1p_f64", "c1p_f32", "probes_f64", "budget_f64", "odd_f64", "cut_f64", "mid_f32"]
+
+
+def _settled(tape_ref_logits: np.ndarray, cells: np.ndarray, valid: np.ndarray, margin: float) -> np.ndarray:
+    """Rows x positions that are safe to compare when two sweeps' logits differ in the last place
+    (the reference's protocol for discrete routing, its tests/kernels/test_p2_10c_window.py:380-440):
+    a position is risky when the gap between the last selected and the first unselected cell
+    score, or between the two best units of a selected cell, is within ``margin``."""
+    B, T, N, M = tape_ref_logits.shape
+    score = tape_ref_logits.max(axis=-1)
+    order = np.sort(score, axis=-1)[..., ::-1]
+    K = cells.shape[-1]
+    gap = order[..., K - 1] - order[..., K] if N > K else np.full((B, T), np.inf)
+    risky = gap <= margin
+    if M > 1:
+        two = np.sort(tape_ref_logits, axis=-1)[..., ::-1]
+        unit_gap = two[..., 0] - two[..., 1]  # [B,T,N]
+        picked = np.take_along_axis(unit_gap, cells, axis=-1)
+        risky |= (np.where(valid, picked, np.inf) <= margin).any(axis=-1)
+    return ~risky
+
+
+@pytest.mark.parametrize("name", WINDOWS + ["chain_f64"])
+def test_forward_sweep_reproduces_the_reference_tape(name: str) -> None:
+    """fp32 products against the reference's CPU sweep: routing bit for bit, state and tape within
+    1e-5 relative. (A fixture made in float64 is compared where its decision is not within 1e-4
+    of a tie, the reference's own rule; none of these fixtures has such a position.)"""
+    from hsn_b200.window import window_forward
+
+    z = load_golden(name if name.startswith("chain") else f"window_{name}")
+    K = z["tape_sel_cell_idx"].shape[-1]
+    W, model = _model(z, K)
+    zz, ctx, scalars, reset, state = _inputs(z)
+    start = [t.clone() for t in state]
+    out = window_forward(model, zz, ctx, scalars, reset, state, want_logits=True)
+    for a, b in zip(state, start):
+        assert torch.equal(a, b)  # the carried state is the caller's: not modified
+    ok = _settled(out["logits"].cpu().numpy(), z["tape_sel_cell_idx"], z["tape_sel_valid"].astype(bool), 1e-4)
+    good = np.logical_and.accumulate(ok, axis=1)  # a row counts up to its first near tie
+    assert good.mean() > 0.6, "fixture has too many near ties: regenerate it with another seed"
+    assert np.array_equal(out["sel_valid"].cpu().numpy()[good], z["tape_sel_valid"].astype(bool)[good])
+    assert np.array_equal(out["sel_cell_idx"].cpu().numpy()[good], z["tape_sel_cell_idx"][good])
+    assert np.array_equal(out["sel_unit_idx"].cpu().numpy()[good], z["tape_sel_unit_idx"][good])
+    assert np.array_equal(out["tape_age"].cpu().numpy()[good], z["tape_tape_age"][good])
+    whole = good.all(axis=1)  # rows without a near tie: their final state too
+    assert np.array_equal(out["age"].cpu().numpy()[whole], z["tape_age"][whole])
+    assert np.array_equal(out["pos"].cpu().numpy(), z["tape_pos"])
+    tol = 1e-5
+    for mine, ref in (
+        ("tape_h", "tape_tape_h"), ("tape_q", "tape_tape_q"), ("tape_hsel", "tape_tape_hsel"),
+        ("qs", "tape_qs"), ("tape_theta", "tape_tape_theta"),
+    ):  # fmt: skip
+        want = z[ref].astype(np.float64)
+        scale = max(1.0, float(np.abs(want).max()))
+        np.testing.assert_allclose(out[mine].cpu().numpy()[good], want[good], rtol=tol, atol=tol * scale, err_msg=mine)
+    for mine, ref in (("h", "tape_h"), ("q", "tape_q")):
+        np.testing.assert_allclose(out[mine].cpu().numpy()[whole], z[ref][whole], rtol=tol, atol=tol, err_msg=mine)
+    if whole.all():
+        for mine, ref in (("state_abs_max", "tape_state_abs_max"), ("refreshed", "tape_refreshed")):
+            np.testing.assert_allclose(out[mine].cpu().numpy(), z[ref], rtol=tol, atol=tol, err_msg=mine)
+    if "rec_y" in z.files:
+        mask = z["tape_sel_valid"].astype(bool) & good[..., None]
+        for key, ref in (("y", "rec_y"), ("gate_pre", "rec_gate_pre"), ("m", "rec_m"), ("rms", "rec_rms"),
+                         ("hidden", "rec_hidden"), ("c", "bw_c"), ("b", "bw_b"), ("h_old", "bw_h_old")):  # fmt: skip
+            want = z[ref].astype(np.float64)[mask]
+            scale = max(1.0, float(np.abs(want).max()))
+            np.testing.assert_allclose(out["rec_" + key].cpu().numpy()[mask], want, rtol=1e-4, atol=2e-5 * scale, err_msg=key)
+
+
+@pytest.mark.parametrize("name", [w for w in WINDOWS if w != "cut_f64"] + ["chain_f64"])
+def test_reverse_sweep_equals_the_reference(name: str) -> None:
+    """The state-gradient sweep on the reference's own record: dc, db and the cotangent of the
+    start state within 1e-5 relative of the float64 / float32 CPU sweep."""
+    from hsn_b200.window import window_backward
+
+    z = load_golden(name if name.startswith("chain") else f"window_{name}")
+    K = z["bw_cells"].shape[-1]
+    _, model = _model(z, K)
+    record = {k: dev(z["rec_" + k], F32) for k in ("y", "hidden", "gate_pre", "m", "rms")}
+    cot = lambda k: dev(z[k], F32) if k in z.files else None  # noqa: E731
+    dc, db, (A, R) = window_backward(
+        model, dev(z["bw_c"], F32), dev(z["bw_b"], F32), dev(z["bw_h_old"], F32), dev(z["bw_cells"]),
+        dev(z["bw_units"]), dev(z["bw_valid"].astype(bool)), dev(z["reset"].astype(bool)),
+        cot("bw_d_q_pre"), cot("bw_d_q_post"), cot("bw_d_h_sel"), record,
+    )  # fmt: skip
+    scale = max(1.0, float(np.abs(z["bw_dc"]).max()), float(np.abs(z["bw_A"]).max()))
+    tol = 2e-5 * scale
+    np.testing.assert_allclose(dc.cpu().numpy(), z["bw_dc"], rtol=1e-4, atol=tol)
+    np.testing.assert_allclose(db.cpu().numpy(), z["bw_db"], rtol=1e-4, atol=tol)
+    keep = ~z["reset"][:, 0].astype(bool)
+    np.testing.assert_allclose(A.cpu().numpy(), z["bw_A"][:, 0] * keep[:, None, None], rtol=1e-4, atol=tol)
+    np.testing.assert_allclose(R.cpu().numpy(), z["bw_R"][:, 0] * keep[:, None], rtol=1e-4, atol=tol)
+    assert bool((dc[~dev(z["bw_valid"].astype(bool))] == 0).all())
+
+
+def test_full_cut_window_equals_the_reference() -> None:
+    from hsn_b200.window import window_backward
+
+    z = load_golden("window_cut_f64")
+    K = z["bw_cells"].shape[-1]
+    _, model = _model(z, K)
+    cot = lambda k: dev(z[k], F32) if k in z.files else None  # noqa: E731
+    dc, db, _ = window_backward(
+        model, dev(z["bw_c"], F32), dev(z["bw_b"], F32), dev(z["bw_h_old"], F32), dev(z["bw_cells"]), None,
+        dev(z["bw_valid"].astype(bool)), dev(z["reset"].astype(bool)), cot("bw_d_q_pre"),
+        cot("bw_d_q_post"), cot("bw_d_h_sel"), None, full_cut=True,
+    )  # fmt: skip
+    scale = max(1.0, float(np.abs(z["bw_dc"]).max()))
+    np.testing.assert_allclose(dc.cpu().numpy(), z["bw_dc"], rtol=1e-4, atol=2e-5 * scale)
+    np.testing.assert_allclose(db.cpu().numpy(), z["bw_db"], rtol=1e-4, atol=2e-5 * scale)
+
+
+def test_chained_windows_equal_the_unsplit_window() -> None:
+    """Split-window TBPTT with the state-gradient carry: two windows of T positions, the state
+    handed forward and (A, R) handed back, against the reference's unsplit window of 2T."""
+    from hsn_b200.window import window_backward, window_forward
+
+    z = load_golden("chain_f64")
+    K = z["bw_cells"].shape[-1]
+    _, model = _model(z, K)
+    zz, ctx, scalars, reset, state = _inputs(z)
+    T2 = reset.shape[1]
+    T = T2 // 2
+    first = window_forward(model, zz[:, :T], ctx[:, :T], scalars[:, :T], reset[:, :T], state)
+    carried = (first["h"].clone(), first["q"].clone(), first["age"].clone(), first["pos"].clone())
+    second = window_forward(model, zz[:, T:], ctx[:, T:], scalars[:, T:], reset[:, T:], carried)
+    joined = torch.cat([first["sel_cell_idx"], second["sel_cell_idx"]], dim=1)
+    assert np.array_equal(joined.cpu().numpy(), z["tape_sel_cell_idx"])
+    for key in ("tape_h", "tape_q", "qs", "tape_hsel"):
+        got = torch.cat([first[key], second[key]], dim=1).cpu().numpy()
+        np.testing.assert_allclose(got, z["tape_" + key], rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(second["h"].cpu().numpy(), z["tape_h"], rtol=1e-5, atol=1e-5)
+    assert np.array_equal(second["pos"].cpu().numpy(), z["tape_pos"])
+    # backward on the sweeps' own record: the second window first, its (A, R) into the first
+    carry = None
+    halves = {}
+    for lo, tape in ((T, second), (0, first)):
+        s = slice(lo, lo + T)
+        rec = {k: tape["rec_" + k] for k in ("y", "hidden", "gate_pre", "m", "rms")}
+        cot = lambda k: dev(z[k][:, s], F32) if k in z.files else None  # noqa: E731, B023
+        dc, db, carry = window_backward(
+            model, tape["rec_c"], tape["rec_b"], tape["rec_h_old"],
+            torch.where(tape["sel_valid"], tape["sel_cell_idx"], 0),
+            torch.where(tape["sel_valid"], tape["sel_unit_idx"], 0), tape["sel_valid"], reset[:, s].contiguous(),
+            cot("bw_d_q_pre"), cot("bw_d_q_post"), cot("bw_d_h_sel"), rec, initial=carry,
+        )  # fmt: skip
+        halves[lo] = (dc, db)
+    dc = torch.cat([halves[0][0], halves[T][0]], dim=1).cpu().numpy()
+    db = torch.cat([halves[0][1], halves[T][1]], dim=1).cpu().numpy()
+    scale = max(1.0, float(np.abs(z["bw_dc"]).max()))
+    np.testing.assert_allclose(dc, z["bw_dc"], rtol=1e-3, atol=5e-5 * scale)
+    np.testing.assert_allclose(db, z["bw_db"], rtol=1e-3, atol=5e-5 * scale)
+    keep = ~z["reset"][:, 0].astype(bool)
+    np.testing.assert_allclose(carry[0].cpu().numpy(), z["bw_A"][:, 0] * keep[:, None, None], rtol=1e-3, atol=5e-5 * scale)
+
+
+def _synthetic(rng, B, T, N, d, K, H, M, D, p_reset, age_max=1 << 30, S=9, score_scale=40.0):
+    W = O.WindowWeights.random(rng, N=N, d=d, K=K, H=H, M=M, D=D, S=S, age_max=age_max)
+    W.score_w = (W.score_w * score_scale).astype(np.float32)  # scores spread well beyond the tie margin
+    z = rng.standard_normal((B, T, d)).astype(np.float32)
+    ctx = (rng.standard_normal((B, T, d)) * 0.02).astype(np.float32)
+    scalars = rng.random((B, T, N, S)).astype(np.float32)
+    reset = rng.random((B, T)) < p_reset
+    reset[:, 0] = True
+    h = np.zeros((B, N, d), np.float32)
+    q = np.zeros((B, d), np.float32)
+    age = np.zeros((B, N), np.int64)
+    pos = np.zeros(B, np.int64)
+    return W, z, ctx, scalars, reset, (h, q, age, pos)
+
+
+@pytest.mark.parametrize("prod", ["fp32", "bf16"])
+def test_forward_sweep_equals_the_oracle_on_a_slice_of_the_reference_shape(prod: str) -> None:
+    """N256 d64 K8 H512 M8 D4 (the benchmark's model) at B4 T12 with the probes on: teacher-forced
+    values within tolerance (fp32 1e-5 relative; bf16 products 2e-2), and the free-running fp32
+    decisions bit for bit wherever the oracle's decision is not within 1e-4 of a tie."""
+    from hsn_b200.window import WindowModel, window_forward
+
+    rng = np.random.default_rng(7)
+    W, z, ctx, scalars, reset, state = _synthetic(rng, 4, 12, 256, 64, 8, 512, 8, 4, 0.1, age_max=4)
+    bf = prod == "bf16"
+    want = O.window_forward(W, z, ctx, scalars, reset, *state, bf16=bf)
+    model = WindowModel.from_oracle_weights(W, device="cuda", prod=prod)
+    args = (dev(z), dev(ctx), dev(scalars), dev(reset), tuple(dev(s) for s in state))
+    forced = (dev(want["sel_cell_idx"]), dev(want["sel_unit_idx"]), dev(want["sel_valid"]))
+    got = window_forward(model, *args, forced=forced, want_logits=True)
+    tol = 2e-2 if bf else 1e-5
+    for key in ("tape_h", "tape_q", "qs", "tape_hsel", "h", "q", "rec_c", "rec_b", "rec_y", "rec_gate_pre",
+                "rec_m", "rec_rms", "rec_hidden", "logits"):  # fmt: skip
+        w = want[key].astype(np.float64)
+        scale = max(1e-3, float(np.abs(w).max()))
+        np.testing.assert_allclose(got[key].cpu().numpy(), w, rtol=tol, atol=tol * scale, err_msg=key)
+    assert np.array_equal(got["tape_age"].cpu().numpy(), want["tape_age"])
+    if not bf:
+        free = window_forward(model, *args)
+        ok = _settled(want["logits"], want["sel_cell_idx"], want["sel_valid"], 1e-4)
+        # a row is compared up to its first risky position
+        good = np.logical_and.accumulate(ok, axis=1)
+        assert good.mean() > 0.9
+        assert np.array_equal(free["sel_cell_idx"].cpu().numpy()[good], want["sel_cell_idx"][good])
+        assert np.array_equal(free["sel_unit_idx"].cpu().numpy()[good], want["sel_unit_idx"][good])
+        assert np.array_equal(free["sel_refreshed"].cpu().numpy()[good], want["sel_refreshed"][good])
+        assert int(free["sel_refreshed"].sum()) > 0
+
+
+def test_reverse_sweep_equals_the_oracle_on_a_slice_of_the_reference_shape() -> None:
+    from hsn_b200.window import WindowModel, window_backward, window_forward
+
+    rng = np.random.default_rng(8)
+    B, T, N, d, K = 3, 10, 256, 64, 8
+    W, z, ctx, scalars, reset, state = _synthetic(rng, B, T, N, d, K, 512, 8, 4, 0.1)
+    # weights away from the tiny init so that every path of the backward is live
+    for key in ("w1", "w2", "gate_w", "v_w", "wout_w"):
+        setattr(W, key, (getattr(W, key) * 6).astype(np.float32))
+    model = WindowModel.from_oracle_weights(W, device="cuda")
+    tape = window_forward(model, dev(z), dev(ctx), dev(scalars), dev(reset), tuple(dev(s) for s in state))
+    pre, post = rng.standard_normal((B, T, d)).astype(np.float32), rng.standard_normal((B, T, d)).astype(np.float32)
+    sel = rng.standard_normal((B, T, K, d)).astype(np.float32)
+    A0, R0 = rng.standard_normal((B, N, d)).astype(np.float32), rng.standard_normal((B, d)).astype(np.float32)
+    cpu = {k: v.cpu().numpy() for k, v in tape.items() if isinstance(v, torch.Tensor)}
+    valid = cpu["sel_valid"]
+    cells = np.where(valid, cpu["sel_cell_idx"], 0)
+    units = np.where(valid, cpu["sel_unit_idx"], 0)
+    rec = {k: cpu["rec_" + k].astype(np.float64) for k in ("y", "hidden", "gate_pre", "m", "rms")}
+    W64 = O.WindowWeights(**{k: (v.astype(np.float64) if isinstance(v, np.ndarray) and v.dtype == np.float32 else v)
+                             for k, v in W.__dict__.items()})  # fmt: skip
+    trace: dict = {}
+    want_dc, want_db = O.state_gradient_backward(
+        W64, cpu["rec_c"].astype(np.float64), cpu["rec_b"].astype(np.float64), cpu["rec_h_old"].astype(np.float64),
+        cells, units, valid, reset, N, pre.astype(np.float64), post.astype(np.float64), sel.astype(np.float64), rec,
+        initial=(A0.astype(np.float64), R0.astype(np.float64)), trace=trace,
+    )  # fmt: skip
+    dc, db, (A, R) = window_backward(
+        model, tape["rec_c"], tape["rec_b"], tape["rec_h_old"], dev(cells), dev(units), tape["sel_valid"],
+        dev(reset), dev(pre), dev(post), dev(sel), {k: tape["rec_" + k] for k in rec}, initial=(dev(A0), dev(R0)),
+    )  # fmt: skip
+    scale = max(1.0, float(np.abs(want_dc).max()), float(np.abs(trace["A"]).max()))
+    np.testing.assert_allclose(dc.cpu().numpy(), want_dc, rtol=1e-4, atol=1e-5 * scale)
+    np.testing.assert_allclose(db.cpu().numpy(), want_db, rtol=1e-4, atol=1e-5 * scale)
+    keep = ~reset[:, 0]
+    np.testing.assert_allclose(A.cpu().numpy(), trace["A"][:, 0] * keep[:, None, None], rtol=1e-4, atol=1e-5 * scale)
+    np.testing.assert_allclose(R.cpu().numpy(), trace["R"][:, 0] * keep[:, None], rtol=1e-4, atol=1e-5 * scale)
+
+
+def test_stream_step_updates_a_resident_state_in_place() -> None:
+    """The serving step (N1024 d64 K8 H512, the streaming configuration's model) for a few steps
+    on a resident state against the oracle, resets included."""
+    from hsn_b200.window import WindowModel, stream_step
+
+    rng = np.random.default_rng(9)
+    B, steps, N, d = 6, 5, 1024, 64
+    W, z, ctx, scalars, reset, state = _synthetic(rng, B, steps, N, d, 8, 512, 8, 4, 0.2, age_max=64)
+    reset[:, 0] = False
+    h = (rng.standard_normal((B, N, d)) * 0.3).astype(np.float32)
+    st = (h, h.mean(axis=1), rng.integers(0, 200, (B, N)), np.arange(B, dtype=np.int64))
+    model = WindowModel.from_oracle_weights(W, device="cuda")
+    gpu = tuple(dev(s) for s in st)
+    cur = st
+    alive = np.ones(B, dtype=bool)  # rows whose decisions were never within 1e-4 of a tie
+    for t in range(steps):
+        want = O.stream_step(W, z[:, t], ctx[:, t], scalars[:, t], reset[:, t], *cur)
+        got = stream_step(model, dev(z[:, t]), dev(ctx[:, t]), dev(scalars[:, t]), dev(reset[:, t]), gpu)
+        alive &= _settled(want["logits"][:, None], want["cells"][:, None], want["valid"][:, None], 1e-4)[:, 0]
+        assert np.array_equal(got["sel_cell_idx"][:, 0].cpu().numpy()[alive], want["cells"][alive])
+        assert np.array_equal(got["sel_unit_idx"][:, 0].cpu().numpy()[alive], want["units"][alive])
+        np.testing.assert_allclose(gpu[0].cpu().numpy()[alive], want["h"][alive], rtol=1e-5, atol=1e-5)
+        np.testing.assert_allclose(gpu[1].cpu().numpy()[alive], want["q"][alive], rtol=1e-5, atol=1e-5)
+        assert np.array_equal(gpu[2].cpu().numpy()[alive], want["age"][alive])
+        assert np.array_equal(gpu[3].cpu().numpy(), want["pos"])
+        cur = (want["h"], want["q"], want["age"], want["pos"])
+    assert alive.sum() >= B - 1
+
+
+def test_full_size_window_properties() -> None:
+    """The benchmark's configuration 2 (B32 T256 N256 d64 K8 H512, bf16 products) at full size:
+    size-independent properties. Two runs are bitwise equal (fixed reduction orders, no atomics);
+    replaying the recorded decision reproduces the tape bit for bit; valid slots name distinct
+    cells; the summary is the running mean of the state; ages restart at written cells; the
+    backward of a window split in two equals the backward of the whole bit for bit."""
+    from hsn_b200.window import WindowModel, window_backward, window_forward
+
+    rng = np.random.default_rng(2)
+    B, T, N, d, K = 32, 256, 256, 64, 8
+    W, z, ctx, scalars, reset, state = _synthetic(rng, B, T, N, d, K, 512, 8, 4, 1 / 1024)
+    model = WindowModel.from_oracle_weights(W, device="cuda", prod="bf16")
+    args = (dev(z), dev(ctx), dev(scalars), dev(reset), tuple(dev(s) for s in state))
+    one = window_forward(model, *args)
+    two = window_forward(model, *args)
+    for key in ("tape_h", "qs", "sel_cell_idx", "sel_unit_idx", "tape_theta", "rec_c", "rec_hidden"):
+        assert torch.equal(one[key], two[key]), key
+    replay = window_forward(model, *args, forced=(one["sel_cell_idx"], one["sel_unit_idx"], one["sel_valid"]))
+    for key in ("tape_h", "qs", "rec_c", "rec_b"):
+        assert torch.equal(one[key], replay[key]), key
+    cells = one["sel_cell_idx"]
+    assert bool(one["sel_valid"].all())  # budget 1.0: every slot fits
+    assert int((cells.sort(dim=-1).values.diff(dim=-1) == 0).sum()) == 0
+    mean = one["tape_h"].double().mean(dim=2)
+    assert float((one["tape_q"].double() - mean).abs().max()) < 1e-5
+    written = torch.zeros((B, T, N), dtype=torch.bool, device="cuda").scatter_(2, cells, True)
+    assert bool((one["_tape_age"][:, 1:][written] == 0).all())
+    cot = [dev(rng.standard_normal(s).astype(np.float32)) for s in ((B, T, d), (B, T, d), (B, T, K, d))]
+    rec = {k: one["rec_" + k] for k in ("y", "hidden", "gate_pre", "m", "rms")}
+    base = (one["rec_c"], one["rec_b"], one["rec_h_old"], cells, one["sel_unit_idx"], one["sel_valid"], args[3])
+    dc, db, (A, R) = window_backward(model, *base, *cot, rec)
+    assert bool(torch.isfinite(dc).all()) and bool(torch.isfinite(A).all())
+    half = T // 2
+    carry = None
+    parts = []
+    for s in (slice(half, T), slice(0, half)):
+        sub = tuple(t[:, s].contiguous() for t in base)
+        dcs, dbs, carry = window_backward(model, *sub, *(c[:, s].contiguous() for c in cot),
+                                          {k: v[:, s].contiguous() for k, v in rec.items()}, initial=carry)  # fmt: skip
+        parts.append((dcs, dbs))
+    assert torch.equal(torch.cat([parts[1][0], parts[0][0]], dim=1), dc)
+    assert torch.equal(torch.cat([parts[1][1], parts[0][1]], dim=1), db)
+    assert torch.equal(carry[0], A) and torch.equal(carry[1], R)
+
+
+def test_entry_points_refuse_what_they_do_not_take() -> None:
+    from hsn_b200 import _lib
+    from hsn_b200.window import WindowModel, window_forward
+
+    rng = np.random.default_rng(1)
+    W, z, ctx, scalars, reset, state = _synthetic(rng, 2, 3, 16, 32, 2, 32, 2, 2, 0.1)
+    model = WindowModel.from_oracle_weights(W, device="cuda")
+    args = [dev(z), dev(ctx), dev(scalars), dev(reset), tuple(dev(s) for s in state)]
+    with pytest.raises(ValueError):
+        window_forward(model, args[0].double(), *args[1:])
+    with pytest.raises(ValueError):
+        window_forward(model, args[0][:, :2], *args[1:])
+    with pytest.raises(ValueError):
+        window_forward(model, *args, scratch=torch.empty(16, dtype=torch.uint8, device="cuda"))
+    W.w1 = np.zeros((17, W.w1.shape[1], W.w1.shape[2]), np.float32)  # more units than the kernels take
+    W.b1, W.w2, W.b2 = np.zeros((17, 32), np.float32), np.zeros((17, 32, 32), np.float32), np.zeros((17, 32), np.float32)
+    W.score_w, W.score_b, W.cost = np.zeros((17, W.score_w.shape[1]), np.float32), np.zeros(17, np.float32), np.ones(17, np.float32)
+    big = WindowModel.from_oracle_weights(W, device="cuda")
+    with pytest.raises(_lib.WindowKernelError) as err:
+        window_forward(big, *args)
+    assert err.value.code == _lib.E_UNSUPPORTED

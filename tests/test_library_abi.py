@@ -1,0 +1,85 @@
+"""The C-ABI library without a GPU: it builds, loads and exports every symbol the header
+declares; the ctypes structures have the header's sizes; calls that need a device fail loudly."""
+
+from __future__ import annotations
+
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+from hsn_b200 import _lib, build
+
+ROOT = Path(__file__).resolve().parents[1]
+HEADER = ROOT / "include" / "hsn_window_b200.h"
+
+
+@pytest.fixture(scope="module")
+def lib() -> ctypes.CDLL:
+    build.build()
+    return _lib.library()
+
+
+def test_every_declared_symbol_is_exported(lib: ctypes.CDLL) -> None:
+    text = HEADER.read_text()
+    declared = set(re.findall(r"\b(hsnw_[a-z_]+)\s*\(", text))
+    assert declared, "no entry points found in the header"
+    assert declared == set(_lib.SYMBOLS), declared ^ set(_lib.SYMBOLS)
+    for name in declared:
+        assert hasattr(lib, name), name
+
+
+def test_structures_match_the_header() -> None:
+    assert ctypes.sizeof(_lib.HsnWinArgs) == 8 * 48 + 4 * 32 + 4 * 8  # the reference's 544 bytes
+    assert ctypes.sizeof(_lib.HsnwModel) == 12 * 4 + 6 * 4 + 20 * 8
+    assert ctypes.sizeof(_lib.HsnwForward) == 4 * 4 + 29 * 8 + 8
+    assert ctypes.sizeof(_lib.HsnwBackward) == 4 * 4 + 20 * 8 + 8
+
+
+def test_version_and_errors_without_a_device(lib: ctypes.CDLL) -> None:
+    assert lib.hsnw_version() >= 100
+    assert lib.hsnw_prepared(0) in (0, 1)
+    args = _lib.HsnWinArgs()
+    assert lib.hsnw_launch(b"no_such_kernel", ctypes.byref(args), 1, 64, 0, None) == _lib.E_NAME
+    assert b"no kernel" in lib.hsnw_last_error()
+    grid, block, shared = ctypes.c_int64(), ctypes.c_int(), ctypes.c_int()
+    args.i[0], args.i[1], args.i[2], args.i[3] = 4, 256, 8, 8
+    assert lib.hsnw_launch_shape(b"hsn_win_select", ctypes.byref(args), ctypes.byref(grid), ctypes.byref(block), ctypes.byref(shared)) == 0
+    assert (grid.value, block.value, shared.value) == (4, 256, 2048)
+    args.i[3] = 65  # more slots than the kernel takes
+    assert lib.hsnw_launch_shape(b"hsn_win_select", ctypes.byref(args), ctypes.byref(grid), ctypes.byref(block), ctypes.byref(shared)) == _lib.E_UNSUPPORTED
+
+
+def test_no_gpu_means_a_loud_failure_not_a_fallback(lib: ctypes.CDLL) -> None:
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    from hsn_b200.window import WindowModel
+
+    with pytest.raises(RuntimeError):
+        WindowModel.build({}, k=1, device="cpu")
+    args = _lib.HsnWinArgs()
+    code = lib.hsnw_launch(b"hsn_win_select", ctypes.byref(args), 1, 64, 0, None)
+    assert code == _lib.E_STATE
+
+
+def test_python_interface_keeps_the_reference_names() -> None:
+    from hsn_b200.kernels import window
+
+    for name in (
+        "available", "prepare", "prepared", "recurrence_backward", "dense_recurrence_backward",
+        "cell_round_error", "cell_round", "select", "select_tape", "select_fold", "select_unsupported",
+        "cell_update", "update_tape", "update_fold", "cell_update_unsupported", "select_op",
+        "select_tape_op", "select_fold_op", "cell_update_op", "update_tape_op", "update_fold_op",
+    ):  # fmt: skip
+        assert callable(getattr(window, name)), name
+    import torch
+
+    ns = getattr(torch.ops, window._NAMESPACE)
+    for op in ("window_select", "window_select_tape", "window_select_fold", "window_cell_update",
+               "window_update_tape", "window_update_fold"):  # fmt: skip
+        assert hasattr(ns, op), op
+    assert window.select_unsupported(4096, 16, 8) is None
+    assert window.select_unsupported(8, 16) is not None
