@@ -1,0 +1,327 @@
+"""Benchmark of the HSN window path: window row-positions per second, forward + backward.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config c2|c3|c1]
+
+A *step* is one TBPTT window for the rank's rows: the forward sweep (tape + record) and the
+state-gradient reverse sweep with synthetic cotangents, on seeded synthetic inputs of the
+benchmark configuration's shapes (uniform random bytes stand in for the reference's data set; the
+window reads them as encoder outputs ``z``, context embeddings and scorer scalars). One JSON line
+is printed by rank 0. ``--impl reference`` times the CPU restatement of the reference's window
+(``oracle/``) on the host cores instead, on a bounded sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+CONFIGS = {
+    # name: B (per GPU), T, N, d, K, H, M, D, S, p_reset, windows
+    "c1": dict(B=2, T=8, N=16, d=32, K=2, H=32, M=2, D=2, S=9, p=0.1, prod="fp32"),
+    "c2": dict(B=32, T=256, N=256, d=64, K=8, H=512, M=8, D=4, S=9, p=1 / 1024, prod="bf16"),
+    "c3": dict(B=64, T=512, N=512, d=64, K=8, H=512, M=8, D=4, S=9, p=1 / 1024, prod="bf16"),
+}
+WORKLOADS = {
+    "c1": "tiny gradcheck-shape window B2 T8 N16 d32 K2 H32",
+    "c2": "reference-shape window fwd+bwd: B32 T256 N256 d64 K8 H512 M8 D4, bf16 products, fp32 state, resets p=1/1024",
+    "c3": "one window of the split-window chain: B64 T512 N512 d64 K8 H512, bf16 products",
+}
+
+
+def bytes_per_row_position(c: dict) -> int:
+    """Algorithmic HBM bytes of one row-position, forward (taped contract) + state-gradient
+    backward: state = 4Nd + 4d + 8N per record; F = 2 state + 4(2d) + 4NS + (18K + 4) +
+    (4Kd + 4d + 4); B = 4(6Kd + 2d) + 9K + 1 + 4(3Kd) + 4K + 2KH + 8K."""
+    N, d, K, H, S = c["N"], c["d"], c["K"], c["H"], c["S"]
+    state = 4 * N * d + 4 * d + 8 * N
+    fwd = 2 * state + 4 * (2 * d) + 4 * N * S + (18 * K + 4) + (4 * K * d + 4 * d + 4)
+    full = 4 * (6 * K * d + 2 * d) + 9 * K + 1
+    bwd = full + 4 * (3 * K * d) + 4 * K + 2 * K * H + 8 * K
+    return fwd + bwd
+
+
+def synthetic(c: dict, rank: int, rows: int):
+    """Seeded inputs of the configuration's shapes; every row's data depends on its global row
+    index only, so the result does not depend on the number of GPUs."""
+    from oracle.window_oracle import WindowWeights
+
+    W = WindowWeights.random(np.random.default_rng(0), N=c["N"], d=c["d"], K=c["K"], H=c["H"], M=c["M"],
+                             D=c["D"], S=c["S"], age_max=2**31 - 1)  # fmt: skip
+    T, N, d, K, S = c["T"], c["N"], c["d"], c["K"], c["S"]
+    parts = []
+    for r in range(rows):
+        rng = np.random.default_rng(1000 + rank * rows + r)
+        tokens = rng.integers(0, 256, T)  # uniform bytes; the window sees them through z
+        z = rng.standard_normal((T, d)).astype(np.float32) * 0.5 + (tokens[:, None] / 255.0 - 0.5).astype(np.float32)
+        ctx = (rng.standard_normal((T, d)) * 0.02).astype(np.float32)
+        scalars = rng.random((T, N, S)).astype(np.float32)
+        reset = rng.random(T) < c["p"]
+        reset[0] = True
+        cot = [rng.standard_normal(s).astype(np.float32) * 0.1 for s in ((T, d), (T, d), (T, K, d))]
+        parts.append((z, ctx, scalars, reset, *cot))
+    stack = [np.stack([p[i] for p in parts]) for i in range(7)]
+    return W, stack
+
+
+def sample_clocks(stop: threading.Event, out: list) -> None:
+    cmd = ["nvidia-smi", "--query-gpu=index,clocks.sm,clocks.max.sm,clocks_event_reasons.active,"
+           "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+           "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap",
+           "--format=csv,noheader,nounits", "-lms", "200"]  # fmt: skip
+    try:
+        proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+    except OSError:
+        return
+    try:
+        while not stop.is_set():
+            line = proc.stdout.readline()
+            if not line:
+                break
+            out.append(line.strip())
+    finally:
+        proc.terminate()
+
+
+def clocks_summary(lines: list, device: int) -> dict:
+    sm, mx, reasons = [], 0.0, set()
+    names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+    for line in lines:
+        f = [x.strip() for x in line.split(",")]
+        if len(f) < 8 or not f[0].isdigit() or int(f[0]) != device:
+            continue
+        try:
+            sm.append(float(f[1]))
+            mx = max(mx, float(f[2]))
+        except ValueError:
+            continue
+        for name, v in zip(names, f[4:8]):
+            if v.lower().startswith("active"):
+                reasons.add(name)
+    return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+            "samples": len(sm)}  # fmt: skip
+
+
+def cpu_window(W, data, rows: int, positions: int):
+    """The oracle's window forward + state-gradient backward on ``rows`` x ``positions`` of the
+    workload; returns seconds."""
+    from oracle import window_oracle as O
+
+    z, ctx, scalars, reset, pre, post, sel = (a[:rows, :positions] for a in data)
+    N, d = W.pad_src.shape[0], z.shape[-1]
+    state = (np.zeros((rows, N, d), np.float32), np.zeros((rows, d), np.float32), np.zeros((rows, N), np.int64),
+             np.zeros(rows, np.int64))  # fmt: skip
+    t0 = time.perf_counter()
+    tape = O.window_forward(W, z, ctx, scalars, reset, *state)
+    valid = tape["sel_valid"]
+    rec = {k: tape["rec_" + k] for k in ("y", "hidden", "gate_pre", "m", "rms")}
+    O.state_gradient_backward(
+        W, tape["rec_c"], tape["rec_b"], tape["rec_h_old"], np.where(valid, tape["sel_cell_idx"], 0),
+        np.where(valid, tape["sel_unit_idx"], 0), valid, reset, N, pre, post, sel, rec,
+    )  # fmt: skip
+    return time.perf_counter() - t0
+
+
+def cpu_baseline(c: dict, W, data, budget_s: float = 12.0) -> dict:
+    rows = min(c["B"], data[0].shape[0])
+    probe = min(2, c["T"])
+    dt = cpu_window(W, data, rows, probe)
+    positions = int(max(probe, min(c["T"], budget_s / max(dt / probe, 1e-6))))
+    seconds = cpu_window(W, data, rows, positions)
+    try:
+        from threadpoolctl import threadpool_info
+
+        threads = max([p.get("num_threads", 1) for p in threadpool_info()] or [1])
+    except Exception:
+        threads = os.cpu_count() or 1
+    return {
+        "value": rows * positions / seconds,
+        "unit": "row-positions/s",
+        "cores": int(threads),
+        "kind": "port",
+        "sample": f"{rows} rows x {positions} positions of the workload, fp32, numpy oracle (BLAS threads = cores), {seconds:.1f} s",
+    }
+
+
+def run_reference(args, c: dict, name: str) -> None:
+    """The CPU arm: the reference's window as restated in oracle/ (the reference is Python and is
+    not present on the benchmark machine; the restatement is pinned to it by tests/golden)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    W, data = synthetic(c, 0, min(c["B"], 8))
+    rows = data[0].shape[0]
+    positions = min(c["T"], 4)
+    for _ in range(args.warmup):
+        cpu_window(W, data, rows, positions)
+    times = [cpu_window(W, data, rows, positions) for _ in range(args.steps)]
+    sec = float(np.mean(times))
+    value = rows * positions / sec
+    try:
+        from threadpoolctl import threadpool_info
+
+        threads = max([p.get("num_threads", 1) for p in threadpool_info()] or [1])
+    except Exception:
+        threads = os.cpu_count() or 1
+    line = {
+        "impl": "reference", "metric": "window row-positions/s fwd+bwd", "value": value, "unit": "row-positions/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOADS[name], "sample": f"{rows} rows x {positions} positions per step"},
+        "cpu_baseline": {"value": value, "unit": "row-positions/s", "cores": int(threads), "kind": "port",
+                         "sample": f"{rows} rows x {positions} positions per step, numpy oracle"},
+        "e2e": {"value": value, "unit": "row-positions/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }  # fmt: skip
+    print(json.dumps(line), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    c = CONFIGS[args.config]
+    if args.impl == "reference":
+        run_reference(args, c, args.config)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from hsn_b200.window import WindowModel, window_backward, window_forward
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the window path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    warmup = max(args.warmup, 3)
+    B, T, N, d, K = c["B"], c["T"], c["N"], c["d"], c["K"]
+    W, host = synthetic(c, rank, B)
+    model = WindowModel.from_oracle_weights(W, device=dev, prod=c["prod"])
+    pinned = [torch.from_numpy(a).pin_memory() for a in host]
+    z, ctx, scalars, reset, pre, post, sel = (t.to(dev, non_blocking=True) for t in pinned)
+    state = (torch.zeros((B, N, d), device=dev), torch.zeros((B, d), device=dev),
+             torch.zeros((B, N), dtype=torch.int64, device=dev), torch.zeros(B, dtype=torch.int64, device=dev))  # fmt: skip
+    n_params = sum(int(np.prod(getattr(W, k).shape)) for k in
+                   "s_w1 s_b1 s_w2 s_b2 p_w1 p_b1 p_w2 p_b2 score_w score_b v_w wout_w gate_w gate_b norm_w cand_w w1 b1 w2 b2".split())  # fmt: skip
+    grads = torch.zeros(n_params, device=dev)
+    out: dict = {}
+    bw_scratch = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
+
+    def step(zz, cc, ss, rr, cots):
+        tape = window_forward(model, zz, cc, ss, rr, state, out=out)
+        rec = {k: tape["rec_" + k] for k in ("y", "hidden", "gate_pre", "m", "rms")}
+        dc, db, carry = window_backward(
+            model, tape["rec_c"], tape["rec_b"], tape["rec_h_old"], tape["sel_cell_idx"], tape["sel_unit_idx"],
+            tape["sel_valid"], rr, cots[0], cots[1], cots[2], rec, scratch=bw_scratch,
+        )  # fmt: skip
+        if world > 1:  # the training-gradient exchange after each window backward
+            dist.all_reduce(grads)
+        return tape, dc, db, carry
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        step(z, ctx, scalars, reset, (pre, post, sel))
+    barrier()
+    stop, lines = threading.Event(), []
+    sampler = threading.Thread(target=sample_clocks, args=(stop, lines), daemon=True)
+    sampler.start()
+    time.sleep(0.3)
+    # device-resident steps
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step(z, ctx, scalars, reset, (pre, post, sel))
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    # end to end: host buffers in, results back to the host, every step
+    host_out = {k: torch.empty(s, dtype=t).pin_memory() for k, (s, t) in
+                {"dc": ((B, T, K, d), torch.float32), "db": ((B, T, K, d), torch.float32),
+                 "h": ((B, N, d), torch.float32), "q": ((B, d), torch.float32)}.items()}  # fmt: skip
+    staged = [torch.empty_like(t, device=dev) for t in pinned]
+
+    def e2e_step():
+        for dst, src in zip(staged, pinned):
+            dst.copy_(src, non_blocking=True)
+        tape, dc, db, _ = step(staged[0], staged[1], staged[2], staged[3], staged[4:7])
+        host_out["dc"].copy_(dc, non_blocking=True)
+        host_out["db"].copy_(db, non_blocking=True)
+        host_out["h"].copy_(tape["h"], non_blocking=True)
+        host_out["q"].copy_(tape["q"], non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1) / args.steps
+    stop.set()
+    sampler.join(timeout=2)
+    times = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = (float(x) for x in times.cpu())
+    if rank == 0:
+        peaks_file = ROOT / "MEASURED_PEAKS.json"
+        peaks = json.loads(peaks_file.read_text()) if peaks_file.exists() else {}
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        row_pos = B * T
+        per = bytes_per_row_position(c)
+        achieved = per * row_pos / (ms * 1e-3) / 1e9
+        h2d = sum(t.numel() * t.element_size() for t in pinned)
+        d2h = sum(t.numel() * t.element_size() for t in host_out.values())
+        line = {
+            "metric": "window row-positions/s fwd+bwd", "value": world * row_pos / (ms * 1e-3),
+            "unit": "row-positions/s", "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16 products, f32 state" if c["prod"] == "bf16" else "f32", "data": "synthetic",
+            "config": {"workload": WORKLOADS[args.config], "rows_per_gpu": B, "positions": T,
+                       "l2": "inputs larger than L2 (tape 0.5 GiB + scalars 75 MB per step)",
+                       "allreduce_floats_per_step": n_params if world > 1 else 0},
+            "e2e": {"value": world * row_pos / (ms_e2e * 1e-3), "unit": "row-positions/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": args.steps * (7 * T + 2),
+            "roofline": {"bound": "hbm", "kernel": "window forward + reverse sweep (all launches of a step)",
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": "measured" if peaks else "fallback", "bytes_per_row_position": per,
+                         "traffic": None},
+            "clocks": clocks_summary(lines, local),
+        }  # fmt: skip
+        if not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(c, W, host)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

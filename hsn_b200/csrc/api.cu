@@ -79,10 +79,27 @@ int hsnw_check_launch(const char* what) {
     return hsnw_fail(HSNW_E_CUDA, buffer);
 }
 
+bool hsnw_opt_in(const void* kernel, const char* name) {
+    cudaFuncAttributes attr;
+    cudaError_t status = cudaFuncGetAttributes(&attr, kernel);
+    if (status == cudaSuccess) {
+        const int room = static_cast<int>(hsnw_max_shared()) - static_cast<int>(attr.sharedSizeBytes);
+        status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, room);
+    }
+    if (status == cudaSuccess) return true;
+    cudaGetLastError();
+    char buffer[300];
+    snprintf(buffer, sizeof(buffer), "prepare: %s: %s", name, cudaGetErrorString(status));
+    hsnw_fail(HSNW_E_CUDA, buffer);
+    return false;
+}
+
+static bool attributes_ok = true;
+void hsnw_attribute_failed() { attributes_ok = false; }
+
 void hsnw_ops_set_attributes() {
-    const int cap = static_cast<int>(hsnw_max_shared());
     for (const Named& k : kKernels)
-        cudaFuncSetAttribute(k.kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
+        if (!hsnw_opt_in(reinterpret_cast<const void*>(k.kernel), k.name)) hsnw_attribute_failed();
 }
 
 extern "C" int hsnw_version(void) { return 100; }
@@ -112,11 +129,13 @@ extern "C" int hsnw_prepare(int device) {
     }
     devices[device].sm_count = prop.multiProcessorCount;
     devices[device].max_shared = prop.sharedMemPerBlockOptin;
+    attributes_ok = true;
     hsnw_ops_set_attributes();
     hsnw_forward_set_attributes();
     hsnw_backward_set_attributes();
     const cudaError_t status = cudaGetLastError();
     if (previous >= 0 && previous != device) cudaSetDevice(previous);
+    if (!attributes_ok) return HSNW_E_CUDA;  // the message names the kernel
     if (status != cudaSuccess) {
         char buffer[300];
         snprintf(buffer, sizeof(buffer), "prepare: %s", cudaGetErrorString(status));

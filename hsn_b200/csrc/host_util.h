@@ -12,6 +12,10 @@ int hsnw_require_prepared();
 size_t hsnw_max_shared();
 // cudaPeekAtLastError after a launch sequence: HSNW_OK or HSNW_E_CUDA with the runtime's message.
 int hsnw_check_launch(const char* what);
+// Opt `kernel` in to the largest dynamic shared memory its static shared memory leaves room for.
+// Returns false (and records the message) when the runtime refuses.
+bool hsnw_opt_in(const void* kernel, const char* name);
+void hsnw_attribute_failed();
 // Each translation unit opts its kernels in to large dynamic shared memory.
 void hsnw_forward_set_attributes();
 void hsnw_backward_set_attributes();

@@ -412,8 +412,9 @@ extern "C" int hsnw_window_backward(const HsnwModel* model, const HsnwBackward* 
 }
 
 void hsnw_backward_set_attributes() {
-    const int cap = static_cast<int>(hsnw_max_shared());
-    cudaFuncSetAttribute(k_head, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
-    cudaFuncSetAttribute(k_mid, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
-    cudaFuncSetAttribute(k_tail, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
+    const struct { const void* f; const char* n; } ks[] = {
+        {reinterpret_cast<const void*>(k_head), "head"}, {reinterpret_cast<const void*>(k_mid), "mid"},
+        {reinterpret_cast<const void*>(k_tail), "tail"}};
+    for (const auto& k : ks)
+        if (!hsnw_opt_in(k.f, k.n)) hsnw_attribute_failed();
 }

@@ -199,7 +199,7 @@ __global__ void k_front(FwdCtx c, int t) {
 // row: one block per row. Shared (dynamic): score [N], unit [N], sw [(3d+1+S) M], vt [d d],
 // ue [2d], rowterm [M], src [K D], ew [K D], vh [K D d], hold [K d], msg [K d], rms [K].
 // ------------------------------------------------------------------------------------------------
-__global__ void k_row(FwdCtx c, int t) {
+__global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
     extern __shared__ __align__(16) unsigned char dyn[];
     __shared__ SelectShared S;
     const int N = c.m.N, d = c.m.d, K = c.m.K, M = c.m.M, D = c.m.D, Sn = c.m.S;
@@ -748,7 +748,7 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
     c.gate_pre = reinterpret_cast<float*>(base + L.gate_pre);
     c.hidden = reinterpret_cast<float*>(base + L.hidden);
     const int B = io->B, T = io->T;
-    const int row_threads = model->N >= 1024 ? 1024 : model->N >= 512 ? 512 : 256;
+    const int row_threads = model->N >= 512 ? 512 : 256;
     k_init<<<B, 256, 0, stream>>>(c);
     if (int rc = hsnw_front_projection(model, io->z, io->ctx, static_cast<int64_t>(B) * T, c.pre_s, stream)) return rc;
     const dim3 front_grid(2 * c.nS, (B + kRowTile - 1) / kRowTile);
@@ -775,9 +775,9 @@ extern "C" int hsnw_stream_step(const HsnwModel* model, const HsnwForward* io, v
 }
 
 void hsnw_forward_set_attributes() {
-    const int cap = static_cast<int>(hsnw_max_shared());
-    cudaFuncSetAttribute(k_front, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
-    cudaFuncSetAttribute(k_row, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
-    cudaFuncSetAttribute(k_unit, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
-    cudaFuncSetAttribute(k_update, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
+    const struct { const void* f; const char* n; } ks[] = {
+        {reinterpret_cast<const void*>(k_front), "front"}, {reinterpret_cast<const void*>(k_row), "row"},
+        {reinterpret_cast<const void*>(k_unit), "unit"}, {reinterpret_cast<const void*>(k_update), "update"}};
+    for (const auto& k : ks)
+        if (!hsnw_opt_in(k.f, k.n)) hsnw_attribute_failed();
 }

@@ -86,6 +86,8 @@ class WindowModel:
         device = torch.device(device)
         if device.type != "cuda":
             raise RuntimeError("the window kernels run on a CUDA device only (no CPU path)")
+        if device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
         missing = [key for key in _WEIGHT_KEYS if key not in weights]
         if missing:
             raise KeyError(f"window weights missing: {missing}")
