@@ -309,7 +309,7 @@ def main() -> None:
                        "allreduce_floats_per_step": n_params if world > 1 else 0},
             "e2e": {"value": world * row_pos / (ms_e2e * 1e-3), "unit": "row-positions/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": args.steps * (7 * T + 2),
+            "gpu_launches": args.steps * (6 * T + 3),
             "roofline": {"bound": "hbm", "kernel": "window forward + reverse sweep (all launches of a step)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": "measured" if peaks else "fallback", "bytes_per_row_position": per,

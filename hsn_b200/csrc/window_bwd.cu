@@ -26,27 +26,27 @@ using namespace hsnw;
 
 namespace {
 
-constexpr int kSlice = 64;
+constexpr int kUS = 32;          // columns of a unit slice
+constexpr int kPB = 32;          // pairs a block multiplies at a time
 constexpr int kPairTile = 256;
-constexpr int kPairBatch = 8;
 
 struct BwdCtx {
     HsnwModel m;
     HsnwBackward io;
-    int nHS;
+    int nU;           // slices of a unit's hidden layer; slice nU of part_dv is the gate's
     float* d_unit;    // [P, d]   W_out^T dy
     float* dg;        // [P, d]   the gate's pre-activation cotangent
     float* sig_gate;  // [P]      <gate_pre - b_g, dg>
-    float* part_dv;   // [nHS, P, 2d]
-    float* part_sig;  // [nHS, P]
+    float* part_dv;   // [nU + 1, P, 2d]
+    float* part_sig;  // [nU, P]
     int* pair_unit;   // [P]  -1 on padded slots
 };
 
 // ------------------------------------------------------------------------------------------------
-// head. Shared (dynamic): Rs [d], cell_of [K], rho [K], dot [K], dy [K d], ysv [K d], wo [d (d+1)].
+// head. Shared (dynamic): Rs [d], cell_of [K], rho [K], dot [K], dzs [K d], ysv [K d], sgs [K d],
+// wo [d (d+1)].
 // ------------------------------------------------------------------------------------------------
-__global__ void k_head(BwdCtx c, int t) {
-    extern __shared__ __align__(16) unsigned char dyn[];
+__device__ __forceinline__ void head_phase(const BwdCtx& c, int t, unsigned char* dyn) {
     const int N = c.m.N, d = c.m.d, K = c.m.K, T = c.io.T;
     const bool full = c.io.full_cut != 0;
     const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
@@ -55,10 +55,10 @@ __global__ void k_head(BwdCtx c, int t) {
     int* cell_of = reinterpret_cast<int*>(Rs + d);
     float* rho = reinterpret_cast<float*>(cell_of + K);
     float* dot = rho + K;
-    float* sg = dot + K;
-    float* dzs = sg + K;          // [K d]  cand_w * dz
+    float* dzs = dot + K;         // [K d]  cand_w * dz, then dy
     float* ysv = dzs + K * d;     // [K d]
-    float* wo = ysv + K * d;      // [d][d+1]
+    float* sgs = ysv + K * d;     // [K d]  dg (gate_pre - b_g)
+    float* wo = sgs + K * d;      // [d][d+1]
     const int64_t rt = static_cast<int64_t>(row) * T + t;
     float* A = c.io.A + static_cast<int64_t>(row) * N * d;
     float* R = c.io.R + static_cast<int64_t>(row) * d;
@@ -100,9 +100,8 @@ __global__ void k_head(BwdCtx c, int t) {
         if (!full) {
             dzs[e] = dz;
             ysv[e] = yv;
+            sgs[e] = sgv;
             c.dg[(static_cast<int64_t>(row) * K + k) * d + x] = dgv;
-            // the gate's share of the inner product is folded per slot below
-            c.d_unit[(static_cast<int64_t>(row) * K + k) * d + x] = sgv;  // staged, overwritten below
         }
     }
     if (full) {
@@ -127,7 +126,7 @@ __global__ void k_head(BwdCtx c, int t) {
             const float yv = ysv[k * d + x];
             sq += yv * yv;
             dt += yv * dzs[k * d + x];
-            s += c.d_unit[(static_cast<int64_t>(row) * K + k) * d + x];
+            s += sgs[k * d + x];
         }
         sq = warp_sum(sq);
         dt = warp_sum(dt);
@@ -158,25 +157,29 @@ __global__ void k_head(BwdCtx c, int t) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// mid: blockIdx.x = (unit j, slice s), blockIdx.y = pair tile. 256 threads.
-// Shared (dynamic): w2 [64][d+1], w1 [2d][65], du [8][d], dh [8][64], list [256].
+// mid: blockIdx.x = (unit j, slice s), blockIdx.y = pair tile; 256 threads, a thread owns a column
+// and four pairs. Slices 0 .. nU-1: 32 hidden columns of unit j (second layer transposed, the
+// activation's derivative, the norm's inner product, first layer transposed on the state
+// columns); slice nU: the gate's transposed linear for unit j's pairs.
+// Shared (dynamic): w2 [32][d+1] | gate rows [2d][d+1], w1 [2d][33], du [32][d], dh [32][33], list.
 // ------------------------------------------------------------------------------------------------
-__global__ void k_mid(BwdCtx c, int t) {
+__global__ void __launch_bounds__(256) k_mid(BwdCtx c, int t) {
     extern __shared__ __align__(16) unsigned char dyn[];
     __shared__ int warp_count[8];
     __shared__ int n_list;
     const int d = c.m.d, K = c.m.K, H = c.m.H, in = 4 * c.m.d, two = 2 * c.m.d;
     const int P = c.io.B * K, T = c.io.T;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int j = blockIdx.x / c.nHS, s = blockIdx.x - j * c.nHS;
-    const int c0 = s * kSlice;
-    const int cols = min(kSlice, H - c0);
-    float* w2 = reinterpret_cast<float*>(dyn);          // [64][d+1]
-    float* w1 = w2 + kSlice * (d + 1);                  // [2d][65]
-    float* du = w1 + two * (kSlice + 1);                // [8][d]
-    float* dh = du + kPairBatch * d;                    // [8][64]
-    float* hm = dh + kPairBatch * kSlice;               // [8][64]  hid - b1
-    int* list = reinterpret_cast<int*>(hm + kPairBatch * kSlice);
+    const int per_unit = c.nU + 1;
+    const int j = blockIdx.x / per_unit, s = blockIdx.x - j * per_unit;
+    const bool is_gate = s == c.nU;
+    const int c0 = s * kUS;
+    const int cols = is_gate ? 0 : min(kUS, H - c0);
+    float* du = reinterpret_cast<float*>(dyn);                       // [32][d]
+    float* wA = du + kPB * d;                                        // w2 [32][d+1] or gate [2d][d+1]
+    float* w1 = wA + (is_gate ? two : kUS) * (d + 1);                // [2d][33]
+    float* dh = w1 + two * (kUS + 1);                                // [32][33]
+    int* list = reinterpret_cast<int*>(dh + kPB * (kUS + 1));
     const int p0 = blockIdx.y * kPairTile;
     {
         const int p = p0 + tid;
@@ -196,71 +199,95 @@ __global__ void k_mid(BwdCtx c, int t) {
     }
     const int count = n_list;
     if (count == 0) return;
+    if (is_gate) {
+        // the gate's transposed linear on the state columns: gate_pre[x] = sum_i v[i] gate_t[i][x]
+        for (int e = tid; e < two * d; e += 256) {
+            const int i = e / d, x = e - i * d;
+            wA[i * (d + 1) + x] = c.m.gate_t[static_cast<int64_t>(two + i) * d + x];
+        }
+        for (int base = 0; base < count; base += kPB) {
+            const int nb = min(kPB, count - base);
+            __syncthreads();
+            for (int e = tid; e < nb * d; e += 256) {
+                const int pb = e / d, x = e - pb * d;
+                du[e] = c.dg[static_cast<int64_t>(list[base + pb]) * d + x];
+            }
+            __syncthreads();
+            for (int e = tid; e < nb * two; e += 256) {
+                const int pb = e / two, i = e - pb * two;
+                float sum = 0.0f;
+                for (int x = 0; x < d; ++x) sum += du[pb * d + x] * wA[i * (d + 1) + x];
+                c.part_dv[(static_cast<int64_t>(c.nU) * P + list[base + pb]) * two + i] = sum;
+            }
+        }
+        return;
+    }
     const float* W1 = c.m.w1 + static_cast<int64_t>(j) * in * H;
     const float* W2 = c.m.w2 + static_cast<int64_t>(j) * H * d;
-    for (int e = tid; e < kSlice * d; e += blockDim.x) {
+    for (int e = tid; e < kUS * d; e += 256) {
         const int cc = e / d, x = e - cc * d;
-        w2[cc * (d + 1) + x] = cc < cols ? W2[static_cast<int64_t>(c0 + cc) * d + x] : 0.0f;
+        wA[cc * (d + 1) + x] = cc < cols ? W2[static_cast<int64_t>(c0 + cc) * d + x] : 0.0f;
     }
-    for (int e = tid; e < two * kSlice; e += blockDim.x) {
-        const int i = e >> 6, cc = e & 63;
-        w1[i * (kSlice + 1) + cc] = cc < cols ? W1[static_cast<int64_t>(two + i) * H + c0 + cc] : 0.0f;
+    for (int e = tid; e < two * kUS; e += 256) {
+        const int i = e >> 5, cc = e & 31;
+        w1[i * (kUS + 1) + cc] = cc < cols ? W1[static_cast<int64_t>(two + i) * H + c0 + cc] : 0.0f;
     }
-    const int cc = tid & 63, pg = tid >> 6;
-    for (int base = 0; base < count; base += kPairBatch) {
-        const int nb = min(kPairBatch, count - base);
+    const int cc = lane, pg = warp;
+    for (int base = 0; base < count; base += kPB) {
+        const int nb = min(kPB, count - base);
         __syncthreads();
-        for (int e = tid; e < nb * d; e += blockDim.x) {
+        for (int e = tid; e < nb * d; e += 256) {
             const int pb = e / d, x = e - pb * d;
             du[e] = c.d_unit[static_cast<int64_t>(list[base + pb]) * d + x];
         }
         __syncthreads();
-        // the transposed second layer and the activation's derivative
-        for (int half = 0; half < 2; ++half) {
-            const int pb = pg + 4 * half;
-            float dhid = 0.0f, centred = 0.0f;
+        // the transposed second layer, the activation's derivative, the inner product's share
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const int pb = pg * 4 + p;
+            float dhid = 0.0f, inner = 0.0f;
             if (pb < nb && cc < cols) {
                 float sum = 0.0f;
-                for (int x = 0; x < d; ++x) sum += du[pb * d + x] * w2[cc * (d + 1) + x];
-                const int p = list[base + pb];
-                const int row = p / K, k = p - row * K;
+                for (int x = 0; x < d; ++x) sum += du[pb * d + x] * wA[cc * (d + 1) + x];
+                const int pair = list[base + pb];
+                const int row = pair / K, k = pair - row * K;
                 const float hid = c.io.hidden[((static_cast<int64_t>(row) * T + t) * K + k) * H + c0 + cc];
                 dhid = sum * gelu_erf_grad(hid);
-                centred = hid - c.m.b1[j * H + c0 + cc];
+                inner = dhid * (hid - c.m.b1[j * H + c0 + cc]);
             }
-            dh[pb * kSlice + cc] = dhid;
-            hm[pb * kSlice + cc] = dhid * centred;
+            dh[pb * (kUS + 1) + cc] = dhid;
+            inner = warp_sum(inner);
+            if (lane == 0 && pb < nb) c.part_sig[static_cast<int64_t>(s) * P + list[base + pb]] = inner;
         }
         __syncthreads();
-        // the unit's part of the norm's inner product: a warp per pair
-        if (warp < nb) {
-            float sum = hm[warp * kSlice + lane] + hm[warp * kSlice + lane + 32];
-            sum = warp_sum(sum);
-            if (lane == 0) c.part_sig[static_cast<int64_t>(s) * P + list[base + warp]] = sum;
-        }
         // the transposed first layer on the state columns [h ; m] of the cell input
-        for (int e = tid; e < nb * two; e += blockDim.x) {
+        for (int e = tid; e < nb * two; e += 256) {
             const int pb = e / two, i = e - pb * two;
             float sum = 0.0f;
-            for (int k2 = 0; k2 < kSlice; ++k2) sum += dh[pb * kSlice + k2] * w1[i * (kSlice + 1) + k2];
+#pragma unroll 8
+            for (int k2 = 0; k2 < kUS; ++k2) sum += dh[pb * (kUS + 1) + k2] * w1[i * (kUS + 1) + k2];
             c.part_dv[(static_cast<int64_t>(s) * P + list[base + pb]) * two + i] = sum;
         }
     }
 }
 
 // ------------------------------------------------------------------------------------------------
-// tail. Shared (dynamic): cell_of [K], back [K], dv [K 2d], dvm [K d], vt [d (d+1)].
+// tail. Shared (dynamic): stage [K + K D][d], ds [K][2d], dvm [K][d], vt [d][d+1], cell_of [K],
+// back [K], tgt [K + K D], first [K + K D], ew [K D].
 // ------------------------------------------------------------------------------------------------
-__global__ void k_tail(BwdCtx c, int t) {
-    extern __shared__ __align__(16) unsigned char dyn[];
+__device__ __forceinline__ void tail_phase(const BwdCtx& c, int t, unsigned char* dyn) {
     const int N = c.m.N, d = c.m.d, K = c.m.K, D = c.m.D, T = c.io.T, two = 2 * c.m.d;
-    const int P = c.io.B * K;
+    const int P = c.io.B * K, U = K + K * D;
     const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
-    int* cell_of = reinterpret_cast<int*>(dyn);
+    float* stage = reinterpret_cast<float*>(dyn);   // [U][d] the rows of A this position touches
+    float* ds = stage + U * d;                      // [K][2d]
+    float* dvm = ds + K * two;                      // [K][d]
+    float* vt = dvm + K * d;                        // [d][d+1]
+    int* cell_of = reinterpret_cast<int*>(vt + d * (d + 1));
     float* back = reinterpret_cast<float*>(cell_of + K);  // [K] (rms^2 / n) sigma
-    float* ds = back + K;        // [K][2d]
-    float* dvm = ds + K * two;   // [K][d]
-    float* vt = dvm + K * d;     // [d][d+1]
+    int* tgt = reinterpret_cast<int*>(back + K);    // [U] the row of A update u adds to (-1: none)
+    int* first = tgt + U;                           // [U] the first update with the same target
+    float* ew = reinterpret_cast<float*>(first + U);  // [K D]
     const int64_t rt = static_cast<int64_t>(row) * T + t;
     const int64_t pair0 = static_cast<int64_t>(row) * K;
     float* A = c.io.A + static_cast<int64_t>(row) * N * d;
@@ -269,33 +296,51 @@ __global__ void k_tail(BwdCtx c, int t) {
     for (int e = tid; e < d * d; e += nt) vt[(e / d) * (d + 1) + (e % d)] = c.m.v_t[e];
     for (int k = tid; k < K; k += nt) {
         const bool ok = c.io.valid[rt * K + k] != 0;
-        cell_of[k] = ok ? static_cast<int>(c.io.cells[rt * K + k]) : -1;
+        const int n = ok ? static_cast<int>(c.io.cells[rt * K + k]) : -1;
+        cell_of[k] = n;
+        tgt[k] = n;
         float sigma = c.sig_gate[pair0 + k];
         if (ok)
-            for (int s = 0; s < c.nHS; ++s) sigma += c.part_sig[static_cast<int64_t>(s) * P + pair0 + k];
+            for (int s = 0; s < c.nU; ++s) sigma += c.part_sig[static_cast<int64_t>(s) * P + pair0 + k];
         const float r = c.io.rms[rt * K + k];
         back[k] = r * r / in_dim * sigma;
     }
+    for (int e = tid; e < K * D; e += nt) {
+        const int k = e / D, j = e - k * D;
+        const bool ok = c.io.valid[rt * K + k] != 0;
+        const int n = ok ? static_cast<int>(c.io.cells[rt * K + k]) : 0;
+        tgt[K + e] = ok ? c.m.pad_src[n * D + j] : -1;
+        ew[e] = ok ? c.m.edge_w[n * D + j] : 0.0f;
+    }
     __syncthreads();
+    for (int u = tid; u < U; u += nt) {
+        int f = u;
+        if (tgt[u] >= 0)
+            for (int w = 0; w < u; ++w)
+                if (tgt[w] == tgt[u]) {
+                    f = w;
+                    break;
+                }
+        first[u] = f;
+    }
     // ds = rms (g_n dv) - (rms^2 / n) sigma [h_old ; m] on the state columns
     for (int e = tid; e < K * two; e += nt) {
         const int k = e / two, i = e - k * two;
         float out = 0.0f;
         if (cell_of[k] >= 0) {
             float dv = 0.0f;
-            for (int s = 0; s < c.nHS; ++s) dv += c.part_dv[(static_cast<int64_t>(s) * P + pair0 + k) * two + i];
-            // the gate's transposed linear: gate_pre[x] = sum_j v[j] gate_t[j][x]
-            const float* g_row = c.m.gate_t + static_cast<int64_t>(two + i) * d;
-            const float* dg = c.dg + (pair0 + k) * d;
-            float gsum = 0.0f;
-            for (int x = 0; x < d; ++x) gsum += dg[x] * g_row[x];
-            dv += gsum;
+            for (int s = 0; s <= c.nU; ++s) dv += c.part_dv[(static_cast<int64_t>(s) * P + pair0 + k) * two + i];
             const float state = i < d ? c.io.h_old[(rt * K + k) * d + i] : c.io.m[(rt * K + k) * d + i - d];
             out = c.io.rms[rt * K + k] * (c.m.norm_w[two + i] * dv) - back[k] * state;
         }
         ds[e] = out;
     }
     __syncthreads();
+    // the touched rows of A, each loaded once (all loads in flight together)
+    for (int e = tid; e < U * d; e += nt) {
+        const int u = e / d, x = e - u * d;
+        if (tgt[u] >= 0 && first[u] == u) stage[e] = A[static_cast<int64_t>(tgt[u]) * d + x];
+    }
     // dvm = dm V: m = sum_e a_e (V h_src), (V h)[x] = sum_i h[i] v_t[i][x]
     for (int e = tid; e < K * d; e += nt) {
         const int k = e / d, i = e - k * d;
@@ -304,28 +349,41 @@ __global__ void k_tail(BwdCtx c, int t) {
         dvm[e] = sum;
     }
     __syncthreads();
-    // a thread owns a column x of the row's A: its own cells first, then every edge in slot order
+    // a thread owns a column: the cells' own cotangents first, then every edge in slot order
     const bool cut = c.io.reset[rt] != 0;
     for (int x = tid; x < d; x += nt) {
-        for (int k = 0; k < K; ++k) {
-            const int n = cell_of[k];
-            if (n >= 0) A[static_cast<int64_t>(n) * d + x] += ds[k * two + x];
-        }
-        for (int k = 0; k < K; ++k) {
-            const int n = cell_of[k];
-            if (n < 0) continue;
-            for (int j = 0; j < D; ++j) {
-                const int srcc = c.m.pad_src[n * D + j];
-                A[static_cast<int64_t>(srcc) * d + x] += c.m.edge_w[n * D + j] * dvm[k * d + x];
-            }
+        for (int u = 0; u < U; ++u) {
+            if (tgt[u] < 0) continue;
+            const float add = u < K ? ds[u * two + x] : ew[u - K] * dvm[((u - K) / D) * d + x];
+            stage[first[u] * d + x] += add;
         }
         float r = R[x];
         if (c.io.d_q_pre) r += c.io.d_q_pre[rt * d + x];
         R[x] = cut ? 0.0f : r;
     }
+    __syncthreads();
     if (cut) {
-        __syncthreads();
         for (int e = tid; e < N * d; e += nt) A[e] = 0.0f;
+    } else {
+        for (int e = tid; e < U * d; e += nt) {
+            const int u = e / d, x = e - u * d;
+            if (tgt[u] >= 0 && first[u] == u) A[static_cast<int64_t>(tgt[u]) * d + x] = stage[e];
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) k_head(BwdCtx c, int t) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    head_phase(c, t, dyn);
+}
+
+// The tail of position t and the head of position t - 1 of the same row in one launch.
+__global__ void __launch_bounds__(256) k_tail_head(BwdCtx c, int t) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    tail_phase(c, t, dyn);
+    if (t > 0) {
+        __syncthreads();
+        head_phase(c, t - 1, dyn);
     }
 }
 
@@ -336,28 +394,29 @@ struct Layout {
 Layout layout(const HsnwModel& m, int B) {
     Layout L;
     const size_t P = static_cast<size_t>(B) * m.K;
-    const int nHS = (m.H + kSlice - 1) / kSlice;
+    const int nU = (m.H + kUS - 1) / kUS;
     size_t off = 0;
     L.d_unit = off; off += align_up(sizeof(float) * P * m.d);
     L.dg = off; off += align_up(sizeof(float) * P * m.d);
     L.sig_gate = off; off += align_up(sizeof(float) * P);
-    L.part_dv = off; off += align_up(sizeof(float) * nHS * P * 2 * m.d);
-    L.part_sig = off; off += align_up(sizeof(float) * nHS * P);
+    L.part_dv = off; off += align_up(sizeof(float) * (nU + 1) * P * 2 * m.d);
+    L.part_sig = off; off += align_up(sizeof(float) * nU * P);
     L.pair_unit = off; off += align_up(sizeof(int) * P);
     L.total = off;
     return L;
 }
 size_t head_shared(const HsnwModel& m) {
-    return sizeof(float) * (static_cast<size_t>(m.d) + 4 * m.K + 2 * static_cast<size_t>(m.K) * m.d
+    return sizeof(float) * (static_cast<size_t>(m.d) + 3 * m.K + 3 * static_cast<size_t>(m.K) * m.d
         + static_cast<size_t>(m.d) * (m.d + 1));
 }
 size_t mid_shared(const HsnwModel& m) {
-    return sizeof(float) * (static_cast<size_t>(kSlice) * (m.d + 1) + static_cast<size_t>(2) * m.d * (kSlice + 1)
-        + static_cast<size_t>(kPairBatch) * m.d + 2 * kPairBatch * kSlice + kPairTile);
+    const size_t d = m.d;
+    const size_t wa = (2 * d > static_cast<size_t>(kUS) ? 2 * d : kUS) * (d + 1);
+    return sizeof(float) * (kPB * d + wa + 2 * d * (kUS + 1) + kPB * (kUS + 1) + kPairTile);
 }
 size_t tail_shared(const HsnwModel& m) {
-    return sizeof(float) * (static_cast<size_t>(2) * m.K + 3 * static_cast<size_t>(m.K) * m.d
-        + static_cast<size_t>(m.d) * (m.d + 1));
+    const size_t d = m.d, K = m.K, U = K + K * m.D;
+    return sizeof(float) * (U * d + 3 * K * d + d * (d + 1) + 2 * K + 2 * U + K * m.D);
 }
 
 }  // namespace
@@ -380,8 +439,10 @@ extern "C" int hsnw_window_backward(const HsnwModel* model, const HsnwBackward* 
     const bool full = io->full_cut != 0;
     if (!full && (!io->y || !io->gate_pre || !io->m || !io->rms || !io->hidden || !io->units))
         return hsnw_fail(HSNW_E_ARG, "window_backward: the state gradient needs the round's record");
-    const size_t cap = hsnw_max_shared();
-    if (head_shared(m) > cap || (!full && (mid_shared(m) > cap || tail_shared(m) > cap)))
+    const size_t cap = hsnw_max_shared() - 4096;
+    const size_t sh_head = head_shared(m), sh_mid = mid_shared(m), sh_tail = tail_shared(m);
+    const size_t sh_both = sh_head > sh_tail ? sh_head : sh_tail;
+    if (sh_head > cap || (!full && (sh_mid > cap || sh_tail > cap)))
         return hsnw_fail(HSNW_E_UNSUPPORTED, "window_backward: a phase's working set exceeds a block's shared memory");
     const Layout L = layout(m, io->B);
     if (!full && (!io->scratch || io->scratch_bytes < static_cast<int64_t>(L.total)
@@ -391,7 +452,7 @@ extern "C" int hsnw_window_backward(const HsnwModel* model, const HsnwBackward* 
     BwdCtx c;
     c.m = m;
     c.io = *io;
-    c.nHS = (m.H + kSlice - 1) / kSlice;
+    c.nU = (m.H + kUS - 1) / kUS;
     unsigned char* base = static_cast<unsigned char*>(io->scratch);
     c.d_unit = full ? nullptr : reinterpret_cast<float*>(base + L.d_unit);
     c.dg = full ? nullptr : reinterpret_cast<float*>(base + L.dg);
@@ -400,21 +461,25 @@ extern "C" int hsnw_window_backward(const HsnwModel* model, const HsnwBackward* 
     c.part_sig = full ? nullptr : reinterpret_cast<float*>(base + L.part_sig);
     c.pair_unit = full ? nullptr : reinterpret_cast<int*>(base + L.pair_unit);
     const int B = io->B, T = io->T;
-    const dim3 mid_grid(m.M * c.nHS, (B * m.K + kPairTile - 1) / kPairTile);
-    const size_t sh_head = head_shared(m), sh_mid = mid_shared(m), sh_tail = tail_shared(m);
-    for (int t = T - 1; t >= 0; --t) {
-        k_head<<<B, 256, sh_head, stream>>>(c, t);
-        if (full) continue;
-        k_mid<<<mid_grid, 256, sh_mid, stream>>>(c, t);
-        k_tail<<<B, 256, sh_tail, stream>>>(c, t);
+    const dim3 mid_grid(m.M * (c.nU + 1), (B * m.K + kPairTile - 1) / kPairTile);
+    if (full) {
+        for (int t = T - 1; t >= 0; --t) k_head<<<B, 256, sh_head, stream>>>(c, t);
+        return hsnw_check_launch("window_backward");
     }
-    return hsnw_check_launch("window_backward");
+    // head(T-1) | mid(T-1) | tail(T-1) + head(T-2) | mid(T-2) | ... | tail(0)
+    k_head<<<B, 256, sh_head, stream>>>(c, T - 1);
+    for (int t = T - 1; t >= 0; --t) {
+        k_mid<<<mid_grid, 256, sh_mid, stream>>>(c, t);
+        k_tail_head<<<B, 256, sh_both, stream>>>(c, t);
+        if (int rc = hsnw_check_launch("window_backward")) return rc;
+    }
+    return HSNW_OK;
 }
 
 void hsnw_backward_set_attributes() {
     const struct { const void* f; const char* n; } ks[] = {
         {reinterpret_cast<const void*>(k_head), "head"}, {reinterpret_cast<const void*>(k_mid), "mid"},
-        {reinterpret_cast<const void*>(k_tail), "tail"}};
+        {reinterpret_cast<const void*>(k_tail_head), "tail_head"}};
     for (const auto& k : ks)
         if (!hsnw_opt_in(k.f, k.n)) hsnw_attribute_failed();
 }

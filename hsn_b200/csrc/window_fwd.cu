@@ -29,25 +29,28 @@ using namespace hsnw;
 
 namespace {
 
-constexpr int kSlice = 64;       // columns of a weight-stationary slice
-constexpr int kRowTile = 32;     // rows a front block serves
+constexpr int kSlice = 64;       // tile edge of the window-invariant projection (k_pre)
+constexpr int kFS = 32;          // columns of a front slice
+constexpr int kFR = 8;           // rows a front block serves
+constexpr int kUS = 32;          // columns of a unit slice
+constexpr int kPB = 32;          // pairs a unit block multiplies at a time
 constexpr int kPairTile = 256;   // pairs a unit block scans
-constexpr int kPairBatch = 8;    // pairs a unit block multiplies at a time
-constexpr int kMaxM = 16;        // units (registers of the scorer's thread)
+constexpr int kCT = 16;          // cells of a warp's scorer tile
+constexpr int kMaxM = 16;        // units (registers of the scorer's lane)
 
 struct FwdCtx {
     HsnwModel m;
     HsnwForward io;
-    int nS;      // slices of one front MLP's hidden layer
-    int nHS;     // slices of a unit's hidden layer
+    int nF;      // slices of one front MLP's hidden layer
+    int nU;      // slices of a unit's hidden layer
     int nG;      // slices of the gate's outputs
-    float* pre_s;     // [B*T, H]
-    float* part_front;  // [2 nS, B, d]
-    float* v;         // [B*K, 4d]
-    int* pair_unit;   // [B*K] the pair's unit, -1 on a padded slot
-    float* part_f;    // [nHS, B*K, d]
-    float* gate_pre;  // [B*K, d]
-    float* hidden;    // [B*K, H] when no record is kept
+    float* pre_s;       // [B*T, H]
+    float* part_front;  // [2 nF, B, d]
+    float* v;           // [B*K, 4d]
+    int* pair_unit;     // [B*K] the pair's unit, -1 on a padded slot
+    float* part_f;      // [nU, B*K, d]
+    float* gate_pre;    // [B*K, d]
+    int* hmax_part;     // [B] bits of max |h| over the cells the position does not write
 };
 
 __device__ __forceinline__ const float* state_h(const FwdCtx& c, int row, int t) {
@@ -142,87 +145,101 @@ __global__ void k_pre(HsnwModel m, const float* z, const float* ctx, int64_t row
 }
 
 // ------------------------------------------------------------------------------------------------
-// front: blockIdx.x = slice (0..nS-1: S; nS..2nS-1: P), blockIdx.y = row tile. 256 threads.
-// Shared: w1 [d][64], w2 [64][d], q [32][d], act [32][64].
+// front: blockIdx.x = slice (0..nF-1: S; nF..2nF-1: P), blockIdx.y = row tile. 256 threads:
+// thread (row r, column cc) for the first layer, strided outputs for the second.
+// Shared: w1 [d][32], w2 [32][d], q [8][d], act [8][32].
 // ------------------------------------------------------------------------------------------------
-__global__ void k_front(FwdCtx c, int t) {
+__global__ void __launch_bounds__(256) k_front(FwdCtx c, int t) {
     extern __shared__ __align__(16) unsigned char dyn[];
     const int d = c.m.d, H = c.m.H, B = c.io.B, T = c.io.T;
     const bool bf = c.m.prod_bf16 != 0;
     const int tid = threadIdx.x;
-    const int slice = blockIdx.x, nS = c.nS;
-    const bool is_p = slice >= nS;
-    const int c0 = (is_p ? slice - nS : slice) * kSlice;
-    const int cols = min(kSlice, H - c0);
+    const int slice = blockIdx.x, nF = c.nF;
+    const bool is_p = slice >= nF;
+    const int c0 = (is_p ? slice - nF : slice) * kFS;
+    const int cols = min(kFS, H - c0);
     const int col_base = (is_p ? H : 0) + c0;   // column in the merged [d, 2H] first layer
-    const int r0 = blockIdx.y * kRowTile;
-    const int rows = min(kRowTile, B - r0);
-    float* w1 = reinterpret_cast<float*>(dyn);          // [d][64]
-    float* w2 = w1 + d * kSlice;                        // [64][d]
-    float* qs = w2 + kSlice * d;                        // [32][d]
-    float* act = qs + kRowTile * d;                     // [32][64]
-    for (int e = tid; e < d * kSlice; e += blockDim.x) {
-        const int x = e >> 6, cc = e & 63;
+    const int r0 = blockIdx.y * kFR;
+    const int rows = min(kFR, B - r0);
+    float* w1 = reinterpret_cast<float*>(dyn);          // [d][32]
+    float* w2 = w1 + d * kFS;                           // [32][d]
+    float* qs = w2 + kFS * d;                           // [8][d]
+    float* act = qs + kFR * d;                          // [8][32]
+    for (int e = tid; e < d * kFS; e += 256) {
+        const int x = e >> 5, cc = e & 31;
         w1[e] = cc < cols ? c.m.f_w1q_t[static_cast<int64_t>(x) * 2 * H + col_base + cc] : 0.0f;
     }
-    for (int e = tid; e < kSlice * d; e += blockDim.x) {
+    for (int e = tid; e < kFS * d; e += 256) {
         const int cc = e / d, x = e - cc * d;
         w2[e] = cc < cols ? c.m.f_w2_t[static_cast<int64_t>(col_base + cc) * d + x] : 0.0f;
     }
-    for (int e = tid; e < rows * d; e += blockDim.x) {
+    for (int e = tid; e < rows * d; e += 256) {
         const int r = e / d, x = e - r * d;
         qs[e] = maybe_bf16(state_q(c, r0 + r, t)[x], bf);
     }
     __syncthreads();
-    for (int e = tid; e < rows * kSlice; e += blockDim.x) {
-        const int r = e >> 6, cc = e & 63;
+    {
+        const int r = tid >> 5, cc = tid & 31;
         float a = 0.0f;
-        if (cc < cols) {
+        if (r < rows && cc < cols) {
             float sum = 0.0f;
-            for (int x = 0; x < d; ++x) sum += qs[r * d + x] * w1[x * kSlice + cc];
+            for (int x = 0; x < d; ++x) sum += qs[r * d + x] * w1[x * kFS + cc];
             const float pre = is_p ? c.m.f_b1[H + c0 + cc]
                                    : c.pre_s[(static_cast<int64_t>(r0 + r) * T + t) * H + c0 + cc];
             a = maybe_bf16(gelu_erf(maybe_bf16(sum + pre, bf)), bf);
         }
-        act[e] = a;
+        act[tid] = a;
     }
     __syncthreads();
-    for (int e = tid; e < rows * d; e += blockDim.x) {
+    for (int e = tid; e < rows * d; e += 256) {
         const int r = e / d, x = e - r * d;
         float sum = 0.0f;
-        for (int cc = 0; cc < kSlice; ++cc) sum += act[r * kSlice + cc] * w2[cc * d + x];
+#pragma unroll 8
+        for (int cc = 0; cc < kFS; ++cc) sum += act[r * kFS + cc] * w2[cc * d + x];
         c.part_front[(static_cast<int64_t>(slice) * B + r0 + r) * d + x] = sum;
     }
 }
 
 // ------------------------------------------------------------------------------------------------
-// row: one block per row. Shared (dynamic): score [N], unit [N], sw [(3d+1+S) M], vt [d d],
-// ue [2d], rowterm [M], src [K D], ew [K D], vh [K D d], hold [K d], msg [K d], rms [K].
+// row: one block per row (256 or 512 threads). The scorer walks the row's state once, a warp per
+// tile of 16 cells: 16-byte coalesced loads, the tile transposed through shared memory so that a
+// lane owns half a cell's row, and the same registers are stored as the next record of the state
+// tape (the update phase then only overwrites the K written cells).
+// Shared (dynamic): rows [(K + K D) d], tiles [warps][16 (d+1)], vh [K D d], msg [K d], vt [d d],
+// sw [(3d+1+S) M], score [N], unit [N], cellmax [N], ue [2d], rowterm [16], src [K D], ew [K D],
+// rms [K].
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
     extern __shared__ __align__(16) unsigned char dyn[];
     __shared__ SelectShared S;
+    __shared__ int ired[32];
     const int N = c.m.N, d = c.m.d, K = c.m.K, M = c.m.M, D = c.m.D, Sn = c.m.S;
     const int B = c.io.B, T = c.io.T;
     const bool bf = c.m.prod_bf16 != 0;
     const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
     const int lane = tid & 31, warp = tid >> 5, warps = nt >> 5;
-    const int feat = 3 * d + 1 + Sn;
-    float* score = reinterpret_cast<float*>(dyn);
+    const int feat = 3 * d + 1 + Sn, d4 = d >> 2, nrows = K + K * D;
+    float* rows = reinterpret_cast<float*>(dyn);            // gathered state rows: K own, K D sources
+    float* tiles = rows + nrows * d;
+    float* vh = tiles + warps * kCT * (d + 1);
+    float* msg = vh + K * D * d;
+    float* vt = msg + K * d;
+    float* sw = vt + d * d;
+    float* score = sw + feat * M;
     int* unit = reinterpret_cast<int*>(score + N);
-    float* sw = reinterpret_cast<float*>(unit + N);
-    float* vt = sw + feat * M;
-    float* ue = vt + d * d;
+    int* cellmax = unit + N;
+    float* ue = reinterpret_cast<float*>(cellmax + N);
     float* rowterm = ue + 2 * d;
     int* src = reinterpret_cast<int*>(rowterm + kMaxM);
     float* ew = reinterpret_cast<float*>(src + K * D);
-    float* vh = ew + K * D;
-    float* hold = vh + K * D * d;
-    float* msg = hold + K * d;
-    float* rms = msg + K * d;
+    float* rms = ew + K * D;
     const int64_t rt = static_cast<int64_t>(row) * T + t;
     const float* h = state_h(c, row, t);
     const int64_t* age = state_age(c, row, t);
+    const bool last = t + 1 == T;
+    const bool clear = !last && c.io.reset[rt + 1] != 0;
+    const bool copy = c.io.tape_state != 0;
+    float* h_next = copy ? c.io.tape_h + (static_cast<int64_t>(row) * (T + 1) + t + 1) * N * d : nullptr;
     for (int e = tid; e < feat * M; e += nt) sw[e] = c.m.score_w_t[e];
     for (int e = tid; e < d * d; e += nt) vt[e] = c.m.v_t[e];
     for (int j = tid; j < M; j += nt) S.cost[j] = c.m.cost[j];
@@ -231,10 +248,14 @@ __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
         const bool is_p = x >= d;
         const int xx = is_p ? x - d : x;
         float sum = 0.0f;
-        for (int s = 0; s < c.nS; ++s)
-            sum += c.part_front[(static_cast<int64_t>((is_p ? c.nS : 0) + s) * B + row) * d + xx];
+        for (int s = 0; s < c.nF; ++s)
+            sum += c.part_front[(static_cast<int64_t>((is_p ? c.nF : 0) + s) * B + row) * d + xx];
         const float out = maybe_bf16(sum + c.m.f_b2[x], bf);
         ue[x] = is_p ? c.io.z[rt * d + xx] - out : out;
+    }
+    if (copy) {  // the ages of the next record: every cell one older, the written ones zeroed later
+        int64_t* age_next = c.io.tape_age + (static_cast<int64_t>(row) * (T + 1) + t + 1) * N;
+        for (int n = tid; n < N; n += nt) age_next[n] = clear ? 0 : age[n] + 1;
     }
     __syncthreads();
     if (tid < M) {
@@ -243,57 +264,86 @@ __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
         rowterm[tid] = sum;
     }
     __syncthreads();
-    // the scorer: a thread per cell, M logits in registers
+    // the scorer
     const float lambda = c.m.lambda_cost;
     const float* scal = c.io.scalars + rt * N * Sn;
     const float age_div = static_cast<float>(c.m.age_max);
-    for (int i = tid; i < N; i += nt) {
+    float* tile = tiles + warp * kCT * (d + 1);
+    const int n_tiles = (N + kCT - 1) / kCT;
+    const int hx = d >> 1;
+    for (int tl = warp; tl < n_tiles; tl += warps) {
+        const int cell0 = tl * kCT;
+        const int ncell = min(kCT, N - cell0);
+        const float4* src4 = reinterpret_cast<const float4*>(h + static_cast<int64_t>(cell0) * d);
+        float4* dst4 = copy ? reinterpret_cast<float4*>(h_next + static_cast<int64_t>(cell0) * d) : nullptr;
+        for (int f = lane; f < ncell * d4; f += 32) {
+            const float4 v = src4[f];
+            const int cl = f / d4, x4 = f - cl * d4;
+            float* tp = tile + cl * (d + 1) + x4 * 4;
+            tp[0] = v.x; tp[1] = v.y; tp[2] = v.z; tp[3] = v.w;
+            if (dst4) dst4[f] = clear ? make_float4(0.0f, 0.0f, 0.0f, 0.0f) : v;
+        }
+        __syncwarp();
+        const int cl = lane & 15, half = lane >> 4;
+        const int i = cell0 + cl;
         float acc[kMaxM];
 #pragma unroll
-        for (int j = 0; j < kMaxM; ++j) acc[j] = j < M ? rowterm[j] : 0.0f;
-        const float4* hi = reinterpret_cast<const float4*>(h + static_cast<int64_t>(i) * d);
-        for (int x4 = 0; x4 < (d >> 2); ++x4) {
-            const float4 hv = hi[x4];
-            const float vals[4] = {hv.x, hv.y, hv.z, hv.w};
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const float a = maybe_bf16(vals[u], bf);
-                const float* w = sw + (2 * d + x4 * 4 + u) * M;
+        for (int j = 0; j < kMaxM; ++j) acc[j] = 0.0f;
+        int top = 0;
+        if (cl < ncell) {
+            const float* trow = tile + cl * (d + 1);
+            for (int s = 0; s < hx; ++s) {
+                // the second half walks its columns rotated by half a half: no bank is read twice
+                const int x = half ? hx + ((s + (hx >> 1)) % hx) : s;
+                const float raw = trow[x];
+                top = max(top, __float_as_int(fabsf(raw)));
+                const float a = maybe_bf16(raw, bf);
+                const float* w = sw + (2 * d + x) * M;
 #pragma unroll
                 for (int j = 0; j < kMaxM; ++j)
                     if (j < M) acc[j] += a * w[j];
             }
-        }
-        {
-            const float a = maybe_bf16(static_cast<float>(age[i]) / age_div, bf);
-            const float* w = sw + (3 * d) * M;
+            if (half == 0) {
+                {
+                    const float a = maybe_bf16(static_cast<float>(age[i]) / age_div, bf);
+                    const float* w = sw + (3 * d) * M;
 #pragma unroll
-            for (int j = 0; j < kMaxM; ++j)
-                if (j < M) acc[j] += a * w[j];
-        }
-        for (int s = 0; s < Sn; ++s) {
-            const float a = maybe_bf16(scal[static_cast<int64_t>(i) * Sn + s], bf);
-            const float* w = sw + (3 * d + 1 + s) * M;
+                    for (int j = 0; j < kMaxM; ++j)
+                        if (j < M) acc[j] += a * w[j];
+                }
+                for (int s = 0; s < Sn; ++s) {
+                    const float a = maybe_bf16(scal[static_cast<int64_t>(i) * Sn + s], bf);
+                    const float* w = sw + (3 * d + 1 + s) * M;
 #pragma unroll
-            for (int j = 0; j < kMaxM; ++j)
-                if (j < M) acc[j] += a * w[j];
-        }
-        float best = -INFINITY;
-        int arg = 0;
-#pragma unroll
-        for (int j = 0; j < kMaxM; ++j) {
-            if (j < M) {
-                const float logit = maybe_bf16(acc[j] + c.m.score_b[j], bf);
-                if (c.io.logits) c.io.logits[(rt * N + i) * M + j] = logit;
-                const float s = lambda > 0.0f ? __fsub_rn(logit, __fmul_rn(lambda, S.cost[j])) : logit;
-                if (j == 0 || s > best) {
-                    best = s;
-                    arg = j;
+                    for (int j = 0; j < kMaxM; ++j)
+                        if (j < M) acc[j] += a * w[j];
                 }
             }
         }
-        score[i] = best;
-        unit[i] = arg;
+#pragma unroll
+        for (int j = 0; j < kMaxM; ++j)
+            if (j < M) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 16);
+        top = max(top, __shfl_xor_sync(0xffffffffu, top, 16));
+        if (half == 0 && cl < ncell) {
+            float best = -INFINITY;
+            int arg = 0;
+#pragma unroll
+            for (int j = 0; j < kMaxM; ++j) {
+                if (j < M) {
+                    const float logit = maybe_bf16(acc[j] + rowterm[j] + c.m.score_b[j], bf);
+                    if (c.io.logits) c.io.logits[(rt * N + i) * M + j] = logit;
+                    const float sc = lambda > 0.0f ? __fsub_rn(logit, __fmul_rn(lambda, S.cost[j])) : logit;
+                    if (j == 0 || sc > best) {
+                        best = sc;
+                        arg = j;
+                    }
+                }
+            }
+            score[i] = best;
+            unit[i] = arg;
+            cellmax[i] = top;
+        }
+        __syncwarp();
     }
     __syncthreads();
     int64_t* cells_o = c.io.cells + rt * K;
@@ -321,22 +371,44 @@ __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
         }
         __syncthreads();
     }
-    // the selected cells, their message sources and edge weights
+    // the sources and edge weights of the selected cells, then every row they read, 16 bytes a thread
     for (int e = tid; e < K * D; e += nt) {
         const int k = e / D, j = e - k * D;
         const int cell = S.out_cell[k];
         src[e] = c.m.pad_src[cell * D + j];
         ew[e] = maybe_bf16(c.m.edge_w[cell * D + j], bf);
     }
-    for (int e = tid; e < K * d; e += nt) {
-        const int k = e / d, x = e - k * d;
-        hold[e] = h[static_cast<int64_t>(S.out_cell[k]) * d + x];
+    // max |h| over the cells this position does not write (the update adds the written ones)
+    {
+        int top = 0;
+        for (int i = tid; i < N; i += nt) {
+            bool written = false;
+            for (int k = 0; k < K; ++k) written = written || ((S.out_flag[k] & 1) && S.out_cell[k] == i);
+            if (!written) top = max(top, cellmax[i]);
+        }
+        for (int w = 16; w > 0; w >>= 1) top = max(top, __shfl_xor_sync(0xffffffffu, top, w));
+        if (lane == 0) ired[warp] = top;
     }
     __syncthreads();
-    // V h of every source: K D d outputs, d products each
+    if (tid == 0) {
+        int mx = 0;
+        for (int w = 0; w < warps; ++w) mx = max(mx, ired[w]);
+        c.hmax_part[row] = mx;
+    }
+    {
+        const float4* h4 = reinterpret_cast<const float4*>(h);
+        float4* rows4 = reinterpret_cast<float4*>(rows);
+        for (int f = tid; f < nrows * d4; f += nt) {
+            const int r = f / d4, x4 = f - r * d4;
+            const int cell = r < K ? S.out_cell[r] : src[r - K];
+            rows4[f] = h4[static_cast<int64_t>(cell) * d4 + x4];
+        }
+    }
+    __syncthreads();
+    // V h of every source: K D d outputs, d products each, from shared memory
     for (int e = tid; e < K * D * d; e += nt) {
         const int s = e / d, x = e - s * d;
-        const float* hs = h + static_cast<int64_t>(src[s]) * d;
+        const float* hs = rows + (K + s) * d;
         float sum = 0.0f;
         for (int i = 0; i < d; ++i) sum += maybe_bf16(hs[i], bf) * vt[i * d + x];
         vh[e] = maybe_bf16(sum, bf);
@@ -354,7 +426,7 @@ __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
         float sq = 0.0f;
         for (int j = lane; j < 4 * d; j += 32) {
             const int blk = j / d, x = j - blk * d;
-            const float v = blk == 0 ? ue[x] : blk == 1 ? ue[d + x] : blk == 2 ? hold[k * d + x] : msg[k * d + x];
+            const float v = blk == 0 ? ue[x] : blk == 1 ? ue[d + x] : blk == 2 ? rows[k * d + x] : msg[k * d + x];
             sq += v * v;
         }
         sq = warp_sum(sq);
@@ -365,13 +437,13 @@ __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
     for (int e = tid; e < K * 4 * d; e += nt) {
         const int k = e / (4 * d), j = e - k * 4 * d;
         const int blk = j / d, x = j - blk * d;
-        const float v = blk == 0 ? ue[x] : blk == 1 ? ue[d + x] : blk == 2 ? hold[k * d + x] : msg[k * d + x];
+        const float v = blk == 0 ? ue[x] : blk == 1 ? ue[d + x] : blk == 2 ? rows[k * d + x] : msg[k * d + x];
         c.v[(pair0 + k) * 4 * d + j] = maybe_bf16(v * rms[k] * c.m.norm_w[j], bf);
     }
     for (int k = tid; k < K; k += nt) c.pair_unit[pair0 + k] = (S.out_flag[k] & 1) ? S.out_unit[k] : -1;
     if (c.io.rec_c) {
         for (int e = tid; e < K * d; e += nt) {
-            c.io.rec_h_old[rt * K * d + e] = hold[e];
+            c.io.rec_h_old[rt * K * d + e] = rows[e];
             c.io.rec_m[rt * K * d + e] = msg[e];
         }
         for (int k = tid; k < K; k += nt) c.io.rec_rms[rt * K + k] = rms[k];
@@ -379,35 +451,36 @@ __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// unit: blockIdx.x = job, blockIdx.y = pair tile. Jobs 0 .. M nHS - 1: (unit j, hidden slice s);
-// then nG jobs: a 64-column slice of the gate's linear for every valid pair. 256 threads.
-// Shared (dynamic): w1 [4d][64], w2 [64][d], vbuf [8][4d], act [8][64], list [256].
+// unit: blockIdx.x = job (unit j, slice s), blockIdx.y = pair tile. Slices 0 .. nU-1 are 32 columns
+// of unit j's hidden layer (first layer, activation, the matching rows of the second layer as a
+// partial sum); slices nU .. nU+nG-1 are 32 columns of the gate's linear for unit j's pairs.
+// 256 threads: a thread owns one column and four pairs; the pairs' inputs are read 16 bytes at a
+// time. Shared (dynamic): vbuf [32][4d], w1 [4d][32], w2 [32][d], act [32][32], list [256].
 // ------------------------------------------------------------------------------------------------
-__global__ void k_unit(FwdCtx c, int t) {
+__global__ void __launch_bounds__(256) k_unit(FwdCtx c, int t) {
     extern __shared__ __align__(16) unsigned char dyn[];
     __shared__ int warp_count[8];
     __shared__ int n_list;
-    const int d = c.m.d, K = c.m.K, H = c.m.H, M = c.m.M, in = 4 * c.m.d;
+    const int d = c.m.d, K = c.m.K, H = c.m.H, in = 4 * c.m.d;
     const int P = c.io.B * K, T = c.io.T;
     const bool bf = c.m.prod_bf16 != 0;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int job = blockIdx.x;
-    const bool is_gate = job >= M * c.nHS;
-    const int j = is_gate ? -1 : job / c.nHS;
-    const int s = is_gate ? job - M * c.nHS : job - j * c.nHS;
-    const int c0 = s * kSlice;
-    const int cols = min(kSlice, (is_gate ? d : H) - c0);
-    float* w1 = reinterpret_cast<float*>(dyn);       // [4d][64]
-    float* w2 = w1 + in * kSlice;                    // [64][d]
-    float* vbuf = w2 + kSlice * d;                   // [8][4d]
-    float* act = vbuf + kPairBatch * in;             // [8][64]
-    int* list = reinterpret_cast<int*>(act + kPairBatch * kSlice);  // [256]
-    // the pairs of this tile that this job serves, in pair order (a ballot compaction)
+    const int per_unit = c.nU + c.nG;
+    const int j = blockIdx.x / per_unit, s = blockIdx.x - j * per_unit;
+    const bool is_gate = s >= c.nU;
+    const int sl = is_gate ? s - c.nU : s;
+    const int c0 = sl * kUS;
+    const int cols = min(kUS, (is_gate ? d : H) - c0);
+    float* vbuf = reinterpret_cast<float*>(dyn);     // [32][4d]
+    float* w1 = vbuf + kPB * in;                     // [4d][32]
+    float* w2 = w1 + in * kUS;                       // [32][d]
+    float* act = w2 + kUS * d;                       // [32][32]
+    int* list = reinterpret_cast<int*>(act + kPB * kUS);  // [256]
+    // the pairs of this tile routed to unit j, in pair order (a ballot compaction)
     const int p0 = blockIdx.y * kPairTile;
     {
         const int p = p0 + tid;
-        const int u = p < P ? c.pair_unit[p] : -1;
-        const bool mine = is_gate ? u >= 0 : u == j;
+        const bool mine = p < P && c.pair_unit[p] == j;
         const unsigned mask = __ballot_sync(0xffffffffu, mine);
         if (lane == 0) warp_count[warp] = __popc(mask);
         __syncthreads();
@@ -424,89 +497,97 @@ __global__ void k_unit(FwdCtx c, int t) {
     const int count = n_list;
     if (count == 0) return;
     if (is_gate) {
-        for (int e = tid; e < in * kSlice; e += blockDim.x) {
-            const int x = e >> 6, cc = e & 63;
+        for (int e = tid; e < in * kUS; e += 256) {
+            const int x = e >> 5, cc = e & 31;
             w1[e] = cc < cols ? c.m.gate_t[static_cast<int64_t>(x) * d + c0 + cc] : 0.0f;
         }
     } else {
         const float* W1 = c.m.w1 + static_cast<int64_t>(j) * in * H;
         const float* W2 = c.m.w2 + static_cast<int64_t>(j) * H * d;
-        for (int e = tid; e < in * kSlice; e += blockDim.x) {
-            const int x = e >> 6, cc = e & 63;
+        for (int e = tid; e < in * kUS; e += 256) {
+            const int x = e >> 5, cc = e & 31;
             w1[e] = cc < cols ? W1[static_cast<int64_t>(x) * H + c0 + cc] : 0.0f;
         }
-        for (int e = tid; e < kSlice * d; e += blockDim.x) {
+        for (int e = tid; e < kUS * d; e += 256) {
             const int cc = e / d, x = e - cc * d;
             w2[e] = cc < cols ? W2[static_cast<int64_t>(c0 + cc) * d + x] : 0.0f;
         }
     }
-    const int cc = tid & 63, pg = tid >> 6;  // a column and two pairs (pg, pg + 4) per thread
-    for (int base = 0; base < count; base += kPairBatch) {
-        const int nb = min(kPairBatch, count - base);
+    const int cc = lane, pg = warp;  // a column and the pairs 4 pg .. 4 pg + 3 of a batch
+    const float4* v4 = reinterpret_cast<const float4*>(c.v);
+    float4* vbuf4 = reinterpret_cast<float4*>(vbuf);
+    for (int base = 0; base < count; base += kPB) {
+        const int nb = min(kPB, count - base);
         __syncthreads();
-        for (int e = tid; e < nb * in; e += blockDim.x) {
-            const int pb = e / in, x = e - pb * in;
-            vbuf[e] = c.v[static_cast<int64_t>(list[base + pb]) * in + x];
+        for (int f = tid; f < nb * d; f += 256) {  // a pair's input is 4d floats = d float4
+            const int pb = f / d, x4 = f - pb * d;
+            vbuf4[f] = v4[static_cast<int64_t>(list[base + pb]) * d + x4];
         }
         __syncthreads();
-        float a0 = 0.0f, a1 = 0.0f;
-        const float* v0 = vbuf + pg * in;
-        const float* v1 = vbuf + (pg + 4) * in;
-        for (int x = 0; x < in; ++x) {
-            const float w = w1[x * kSlice + cc];
-            a0 += v0[x] * w;
-            a1 += v1[x] * w;
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int x4 = 0; x4 < d; ++x4) {
+            const float w0 = w1[(4 * x4 + 0) * kUS + cc], wa = w1[(4 * x4 + 1) * kUS + cc];
+            const float wb = w1[(4 * x4 + 2) * kUS + cc], wc = w1[(4 * x4 + 3) * kUS + cc];
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                const float4 vv = vbuf4[(pg * 4 + p) * d + x4];
+                acc[p] += vv.x * w0;
+                acc[p] += vv.y * wa;
+                acc[p] += vv.z * wb;
+                acc[p] += vv.w * wc;
+            }
         }
-        for (int half = 0; half < 2; ++half) {
-            const int pb = pg + 4 * half;
-            const float acc = half ? a1 : a0;
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const int pb = pg * 4 + p;
+            float a = 0.0f;
             if (pb < nb && cc < cols) {
-                const int p = list[base + pb];
+                const int pair = list[base + pb];
                 if (is_gate) {
-                    c.gate_pre[static_cast<int64_t>(p) * d + c0 + cc] = maybe_bf16(acc + c.m.gate_b[c0 + cc], bf);
+                    c.gate_pre[static_cast<int64_t>(pair) * d + c0 + cc] = maybe_bf16(acc[p] + c.m.gate_b[c0 + cc], bf);
                 } else {
-                    const float hid = maybe_bf16(acc + c.m.b1[j * H + c0 + cc], bf);
+                    const float hid = maybe_bf16(acc[p] + c.m.b1[j * H + c0 + cc], bf);
                     if (c.io.rec_c) {
-                        const int row = p / K, k = p - row * K;
+                        const int row = pair / K, k = pair - row * K;
                         c.io.rec_hidden[((static_cast<int64_t>(row) * T + t) * K + k) * H + c0 + cc] = hid;
                     }
-                    act[pb * kSlice + cc] = maybe_bf16(gelu_erf(hid), bf);
+                    a = maybe_bf16(gelu_erf(hid), bf);
                 }
-            } else if (!is_gate) {
-                act[pb * kSlice + cc] = 0.0f;
             }
+            if (!is_gate) act[pb * kUS + cc] = a;
         }
         if (is_gate) continue;
         __syncthreads();
-        for (int e = tid; e < nb * d; e += blockDim.x) {
+        for (int e = tid; e < nb * d; e += 256) {
             const int pb = e / d, x = e - pb * d;
             float sum = 0.0f;
-            for (int k2 = 0; k2 < kSlice; ++k2) sum += act[pb * kSlice + k2] * w2[k2 * d + x];
-            c.part_f[(static_cast<int64_t>(s) * P + list[base + pb]) * d + x] = sum;
+#pragma unroll 8
+            for (int k2 = 0; k2 < kUS; ++k2) sum += act[pb * kUS + k2] * w2[k2 * d + x];
+            c.part_f[(static_cast<int64_t>(sl) * P + list[base + pb]) * d + x] = sum;
         }
     }
 }
 
 // ------------------------------------------------------------------------------------------------
-// update: one block per row. Shared (dynamic): slot_of [N], F [K d], y [K d], hnew [K d],
-// delta [K d], cell_of [K], scale [K], wo [d d].
+// update: one block per row, 256 threads. Shared (dynamic): F [K d], y [K d], hnew [K d],
+// delta [K d], wo [d d], cell_of [K], scale [K].
 // ------------------------------------------------------------------------------------------------
-__global__ void k_update(FwdCtx c, int t) {
+__global__ void __launch_bounds__(256) k_update(FwdCtx c, int t) {
     extern __shared__ __align__(16) unsigned char dyn[];
-    __shared__ int ired[32];
+    __shared__ int ired[8];
+    __shared__ int zero_slot;
     const int N = c.m.N, d = c.m.d, K = c.m.K;
     const int B = c.io.B, T = c.io.T, P = B * K;
     const bool bf = c.m.prod_bf16 != 0;
     const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
     const int lane = tid & 31, warp = tid >> 5, warps = nt >> 5;
-    int* slot_of = reinterpret_cast<int*>(dyn);
-    float* Fs = reinterpret_cast<float*>(slot_of + ((N + 3) & ~3));  // keeps the rows 16-byte aligned
+    float* Fs = reinterpret_cast<float*>(dyn);
     float* ys = Fs + K * d;
     float* hnew = ys + K * d;
     float* delta = hnew + K * d;
-    int* cell_of = reinterpret_cast<int*>(delta + K * d);
+    float* wo = delta + K * d;
+    int* cell_of = reinterpret_cast<int*>(wo + d * d);
     float* scale = reinterpret_cast<float*>(cell_of + K);
-    float* wo = scale + K;
     const int64_t rt = static_cast<int64_t>(row) * T + t;
     const int64_t pair0 = static_cast<int64_t>(row) * K;
     const int64_t* cells = c.io.cells + rt * K;
@@ -514,21 +595,21 @@ __global__ void k_update(FwdCtx c, int t) {
     const uint8_t* valid = c.io.valid + rt * K;
     const float* h = state_h(c, row, t);
     const float* q = state_q(c, row, t);
-    const int64_t* age = state_age(c, row, t);
     const bool last = t + 1 == T;
     const bool clear = !last && c.io.reset[rt + 1] != 0;
+    const bool tape = c.io.tape_state != 0;
     for (int e = tid; e < d * d; e += nt) wo[e] = c.m.wout_t[e];
-    for (int n = tid; n < N; n += nt) slot_of[n] = -1;
     for (int k = tid; k < K; k += nt) cell_of[k] = valid[k] ? static_cast<int>(cells[k]) : -1;
+    if (tid == 0) zero_slot = -1;
     __syncthreads();
     for (int k = tid; k < K; k += nt)
-        if (cell_of[k] >= 0) slot_of[cell_of[k]] = k;
+        if (cell_of[k] == 0) zero_slot = k;  // at most one valid slot names cell 0
     // the executed unit's output: the second layer's partial sums in slice order, plus its bias
     for (int e = tid; e < K * d; e += nt) {
         const int k = e / d, x = e - k * d;
         float sum = 0.0f;
         if (cell_of[k] >= 0) {
-            for (int s = 0; s < c.nHS; ++s) sum += c.part_f[(static_cast<int64_t>(s) * P + pair0 + k) * d + x];
+            for (int s = 0; s < c.nU; ++s) sum += c.part_f[(static_cast<int64_t>(s) * P + pair0 + k) * d + x];
             sum = maybe_bf16(sum + c.m.b2[static_cast<int>(units[k]) * d + x], bf);
         }
         Fs[e] = sum;
@@ -548,6 +629,9 @@ __global__ void k_update(FwdCtx c, int t) {
         if (lane == 0) scale[k] = rsqrtf(sq / static_cast<float>(d) + c.m.cand_eps);
     }
     __syncthreads();
+    float* h_write = tape ? c.io.tape_h + (static_cast<int64_t>(row) * (T + 1) + t + 1) * N * d
+                          : c.io.h0 + static_cast<int64_t>(row) * N * d;
+    int top = 0;
     for (int e = tid; e < K * d; e += nt) {
         const int k = e / d, x = e - k * d;
         const int n = cell_of[k];
@@ -559,6 +643,7 @@ __global__ void k_update(FwdCtx c, int t) {
             bv = sigmoid_f(gp);
             value = (1.0f - bv) * old + bv * cv;
             change = value - old;
+            top = max(top, __float_as_int(fabsf(value)));
         }
         hnew[e] = value;
         delta[e] = change;
@@ -570,9 +655,18 @@ __global__ void k_update(FwdCtx c, int t) {
         }
     }
     __syncthreads();
-    // summary, the slots' cells after the update, ages
-    float* q_next = c.io.tape_state ? c.io.tape_q + (static_cast<int64_t>(row) * (T + 1) + t + 1) * d
-                                    : c.io.q0 + static_cast<int64_t>(row) * d;
+    // the state after the position: the tape's next record already holds a copy of this one (the
+    // row phase wrote it, zeroed if the next position resets), so only the written cells move
+    if (!clear) {
+        for (int e = tid; e < K * d; e += nt) {
+            const int k = e / d, x = e - k * d;
+            if (cell_of[k] >= 0) h_write[static_cast<int64_t>(cell_of[k]) * d + x] = hnew[e];
+        }
+    } else if (!tape) {
+        for (int e = tid; e < N * d; e += nt) h_write[e] = 0.0f;
+    }
+    float* q_next = tape ? c.io.tape_q + (static_cast<int64_t>(row) * (T + 1) + t + 1) * d
+                         : c.io.q0 + static_cast<int64_t>(row) * d;
     for (int x = tid; x < d; x += nt) {
         float sum = 0.0f;
         for (int k = 0; k < K; ++k) sum += delta[k * d + x];
@@ -584,60 +678,26 @@ __global__ void k_update(FwdCtx c, int t) {
         const int k = e / d, x = e - k * d;
         float value;
         if (cell_of[k] >= 0) value = hnew[e];
-        else {
-            const int zero = slot_of[0];
-            value = zero >= 0 ? hnew[zero * d + x] : h[x];
-        }
+        else value = zero_slot >= 0 ? hnew[zero_slot * d + x] : h[x];
         c.io.h_sel[rt * K * d + e] = value;
     }
-    int64_t* age_next = c.io.tape_state ? c.io.tape_age + (static_cast<int64_t>(row) * (T + 1) + t + 1) * N
-                                        : c.io.age0 + static_cast<int64_t>(row) * N;
-    for (int n = tid; n < N; n += nt) age_next[n] = (clear || slot_of[n] >= 0) ? 0 : age[n] + 1;
-    int top = 0;
-    const int d4 = d >> 2;
-    if (c.io.tape_state) {
-        // the next record: written cells from shared memory, the others carried, 16 bytes a thread
-        const float4* srcv = reinterpret_cast<const float4*>(h);
-        float4* dst = reinterpret_cast<float4*>(c.io.tape_h + (static_cast<int64_t>(row) * (T + 1) + t + 1) * N * d);
-        for (int e = tid; e < N * d4; e += nt) {
-            const int n = e / d4, x4 = e - n * d4;
-            const int k = slot_of[n];
-            float4 v = k >= 0 ? reinterpret_cast<const float4*>(hnew + k * d)[x4] : srcv[e];
-            top = max(top, __float_as_int(fabsf(v.x)));
-            top = max(top, __float_as_int(fabsf(v.y)));
-            top = max(top, __float_as_int(fabsf(v.z)));
-            top = max(top, __float_as_int(fabsf(v.w)));
-            if (clear) v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            dst[e] = v;
-        }
+    if (tape) {
+        int64_t* age_next = c.io.tape_age + (static_cast<int64_t>(row) * (T + 1) + t + 1) * N;
+        for (int k = tid; k < K; k += nt)
+            if (cell_of[k] >= 0) age_next[cell_of[k]] = 0;
     } else {
-        // resident state: only the written rows move (all of them on a reset); the maximum needs
-        // every cell and is taken only when asked for
-        float* hw = c.io.h0 + static_cast<int64_t>(row) * N * d;
-        if (c.io.h_max) {
-            for (int e = tid; e < N * d; e += nt) {
-                const int n = e / d, x = e - n * d;
-                const int k = slot_of[n];
-                const float v = k >= 0 ? hnew[k * d + x] : hw[e];
-                top = max(top, __float_as_int(fabsf(v)));
-            }
-            __syncthreads();
-        }
-        if (clear) {
-            for (int e = tid; e < N * d; e += nt) hw[e] = 0.0f;
-        } else {
-            for (int e = tid; e < K * d; e += nt) {
-                const int k = e / d, x = e - k * d;
-                if (cell_of[k] >= 0) hw[static_cast<int64_t>(cell_of[k]) * d + x] = hnew[e];
-            }
-        }
+        int64_t* ages = c.io.age0 + static_cast<int64_t>(row) * N;
+        for (int n = tid; n < N; n += nt) ages[n] = clear ? 0 : ages[n] + 1;
+        __syncthreads();
+        for (int k = tid; k < K; k += nt)
+            if (cell_of[k] >= 0) ages[cell_of[k]] = 0;
     }
     if (c.io.h_max) {
         for (int w = 16; w > 0; w >>= 1) top = max(top, __shfl_xor_sync(0xffffffffu, top, w));
         if (lane == 0) ired[warp] = top;
         __syncthreads();
         if (tid == 0) {
-            int mx = 0;
+            int mx = c.hmax_part[row];
             for (int w = 0; w < warps; ++w) mx = max(mx, ired[w]);
             c.io.h_max[rt] = __int_as_float(mx);
         }
@@ -654,38 +714,40 @@ __global__ void k_update(FwdCtx c, int t) {
 size_t align_up(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
 struct Layout {
-    size_t pre_s, part_front, v, pair_unit, part_f, gate_pre, hidden, total;
+    size_t pre_s, part_front, v, pair_unit, part_f, gate_pre, hmax_part, total;
 };
 Layout layout(const HsnwModel& m, int B, int T) {
     Layout L;
-    const int nS = (m.H + kSlice - 1) / kSlice;
+    const int nF = (m.H + kFS - 1) / kFS, nU = (m.H + kUS - 1) / kUS;
     size_t off = 0;
     L.pre_s = off; off += align_up(sizeof(float) * static_cast<size_t>(B) * T * m.H);
-    L.part_front = off; off += align_up(sizeof(float) * 2 * nS * static_cast<size_t>(B) * m.d);
+    L.part_front = off; off += align_up(sizeof(float) * 2 * nF * static_cast<size_t>(B) * m.d);
     L.v = off; off += align_up(sizeof(float) * static_cast<size_t>(B) * m.K * 4 * m.d);
     L.pair_unit = off; off += align_up(sizeof(int) * static_cast<size_t>(B) * m.K);
-    L.part_f = off; off += align_up(sizeof(float) * nS * static_cast<size_t>(B) * m.K * m.d);
+    L.part_f = off; off += align_up(sizeof(float) * nU * static_cast<size_t>(B) * m.K * m.d);
     L.gate_pre = off; off += align_up(sizeof(float) * static_cast<size_t>(B) * m.K * m.d);
-    L.hidden = off; off += align_up(sizeof(float) * static_cast<size_t>(B) * m.K * m.H);
+    L.hmax_part = off; off += align_up(sizeof(int) * static_cast<size_t>(B));
     L.total = off;
     return L;
 }
 
+int row_threads(const HsnwModel& m) { return m.N >= 256 ? 512 : 256; }
+
 size_t row_shared(const HsnwModel& m) {
-    const int feat = 3 * m.d + 1 + m.S;
-    return sizeof(float) * (static_cast<size_t>(2) * m.N + static_cast<size_t>(feat) * m.M + static_cast<size_t>(m.d) * m.d
-        + 2 * m.d + kMaxM + 2 * static_cast<size_t>(m.K) * m.D + static_cast<size_t>(m.K) * m.D * m.d
-        + 2 * static_cast<size_t>(m.K) * m.d + m.K);
+    const size_t feat = 3 * m.d + 1 + m.S, d = m.d, K = m.K, D = m.D, N = m.N;
+    const size_t warps = row_threads(m) / 32;
+    return sizeof(float) * ((K + K * D) * d + warps * kCT * (d + 1) + K * D * d + K * d + d * d + feat * m.M
+        + 3 * N + 2 * d + kMaxM + 2 * K * D + K);
 }
 size_t front_shared(const HsnwModel& m) {
-    return sizeof(float) * (static_cast<size_t>(2) * m.d * kSlice + static_cast<size_t>(kRowTile) * m.d + kRowTile * kSlice);
+    return sizeof(float) * (static_cast<size_t>(2) * m.d * kFS + static_cast<size_t>(kFR) * m.d + kFR * kFS);
 }
 size_t unit_shared(const HsnwModel& m) {
-    return sizeof(float) * (static_cast<size_t>(4) * m.d * kSlice + static_cast<size_t>(kSlice) * m.d
-        + static_cast<size_t>(kPairBatch) * 4 * m.d + kPairBatch * kSlice + kPairTile);
+    return sizeof(float) * (static_cast<size_t>(kPB) * 4 * m.d + static_cast<size_t>(4) * m.d * kUS
+        + static_cast<size_t>(kUS) * m.d + kPB * kUS + kPairTile);
 }
 size_t update_shared(const HsnwModel& m) {
-    return sizeof(float) * (static_cast<size_t>((m.N + 3) & ~3) + 4 * static_cast<size_t>(m.K) * m.d + 2 * m.K + static_cast<size_t>(m.d) * m.d);
+    return sizeof(float) * (4 * static_cast<size_t>(m.K) * m.d + static_cast<size_t>(m.d) * m.d + 2 * m.K);
 }
 
 int check_model(const HsnwModel* m) {
@@ -695,7 +757,7 @@ int check_model(const HsnwModel* m) {
         return hsnw_fail(HSNW_E_ARG, "window: sizes must be positive, K <= N and d a multiple of 4");
     if (m->M > kMaxM) return hsnw_fail(HSNW_E_UNSUPPORTED, "window: at most 16 units (M)");
     if (m->K > kMaxSlots) return hsnw_fail(HSNW_E_UNSUPPORTED, "window: at most 64 slots (K)");
-    const size_t cap = hsnw_max_shared();
+    const size_t cap = hsnw_max_shared() - 4096;  // room for the kernels' static shared memory
     if (row_shared(*m) > cap || front_shared(*m) > cap || unit_shared(*m) > cap || update_shared(*m) > cap)
         return hsnw_fail(HSNW_E_UNSUPPORTED, "window: a phase's working set exceeds a block's shared memory");
     return HSNW_OK;
@@ -736,9 +798,9 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
     FwdCtx c;
     c.m = *model;
     c.io = *io;
-    c.nS = (model->H + kSlice - 1) / kSlice;
-    c.nHS = c.nS;
-    c.nG = (model->d + kSlice - 1) / kSlice;
+    c.nF = (model->H + kFS - 1) / kFS;
+    c.nU = (model->H + kUS - 1) / kUS;
+    c.nG = (model->d + kUS - 1) / kUS;
     unsigned char* base = static_cast<unsigned char*>(io->scratch);
     c.pre_s = reinterpret_cast<float*>(base + L.pre_s);
     c.part_front = reinterpret_cast<float*>(base + L.part_front);
@@ -746,22 +808,23 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
     c.pair_unit = reinterpret_cast<int*>(base + L.pair_unit);
     c.part_f = reinterpret_cast<float*>(base + L.part_f);
     c.gate_pre = reinterpret_cast<float*>(base + L.gate_pre);
-    c.hidden = reinterpret_cast<float*>(base + L.hidden);
+    c.hmax_part = reinterpret_cast<int*>(base + L.hmax_part);
     const int B = io->B, T = io->T;
-    const int row_threads = model->N >= 512 ? 512 : 256;
+    const int rthreads = row_threads(*model);
     k_init<<<B, 256, 0, stream>>>(c);
     if (int rc = hsnw_front_projection(model, io->z, io->ctx, static_cast<int64_t>(B) * T, c.pre_s, stream)) return rc;
-    const dim3 front_grid(2 * c.nS, (B + kRowTile - 1) / kRowTile);
-    const dim3 unit_grid(model->M * c.nHS + c.nG, (B * model->K + kPairTile - 1) / kPairTile);
+    const dim3 front_grid(2 * c.nF, (B + kFR - 1) / kFR);
+    const dim3 unit_grid(model->M * (c.nU + c.nG), (B * model->K + kPairTile - 1) / kPairTile);
     const size_t sh_front = front_shared(*model), sh_row = row_shared(*model);
     const size_t sh_unit = unit_shared(*model), sh_update = update_shared(*model);
     for (int t = 0; t < T; ++t) {
         k_front<<<front_grid, 256, sh_front, stream>>>(c, t);
-        k_row<<<B, row_threads, sh_row, stream>>>(c, t);
+        k_row<<<B, rthreads, sh_row, stream>>>(c, t);
         k_unit<<<unit_grid, 256, sh_unit, stream>>>(c, t);
         k_update<<<B, 256, sh_update, stream>>>(c, t);
+        if (int rc = hsnw_check_launch("window_forward")) return rc;
     }
-    return hsnw_check_launch("window_forward");
+    return HSNW_OK;
 }
 
 extern "C" int hsnw_window_forward(const HsnwModel* model, const HsnwForward* io, void* stream) {
