@@ -94,6 +94,8 @@ SYMBOLS: dict[str, tuple[object, list[object]]] = {
     "hsnw_stream_step": (c_int, [POINTER(HsnwModel), POINTER(HsnwForward), c_void_p]),
     "hsnw_backward_scratch_bytes": (c_int64, [POINTER(HsnwModel), c_int32, c_int32]),
     "hsnw_window_backward": (c_int, [POINTER(HsnwModel), POINTER(HsnwBackward), c_void_p]),
+    "hsnw_static_scratch_bytes": (c_int64, []),
+    "hsnw_window_backward_static": (c_int, [POINTER(HsnwModel), POINTER(HsnwBackward), c_void_p]),
     "hsnw_front_projection": (c_int, [POINTER(HsnwModel), c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
 }
 

@@ -22,6 +22,9 @@
 #include "common.cuh"
 #include "host_util.h"
 
+#include <mutex>
+#include <stdio.h>
+
 using namespace hsnw;
 
 namespace {
@@ -474,6 +477,63 @@ extern "C" int hsnw_window_backward(const HsnwModel* model, const HsnwBackward* 
         if (int rc = hsnw_check_launch("window_backward")) return rc;
     }
     return HSNW_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// The reverse sweep for callers that cannot allocate: its scratch is this fixed array, part of the
+// library's image on every GPU that loads it (held until the process exits).
+// ------------------------------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = static_cast<size_t>(8) << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kStaticDevices = 64;
+std::mutex static_mutex;
+void* static_scratch_address[kStaticDevices] = {};  // the array's device address, per device
+}  // namespace
+
+extern "C" int64_t hsnw_static_scratch_bytes(void) { return static_cast<int64_t>(kStaticScratchBytes); }
+
+extern "C" int hsnw_window_backward_static(const HsnwModel* model, const HsnwBackward* io, void* stream) {
+    if (int rc = hsnw_require_prepared()) return rc;
+    if (!model || !io) return hsnw_fail(HSNW_E_ARG, "window_backward_static: null argument");
+    if (io->B < 1 || io->T < 1 || model->K < 1 || model->d < 1 || model->H < 1)
+        return hsnw_fail(HSNW_E_ARG, "window_backward_static: sizes must be positive");
+    const size_t need = layout(*model, io->B).total;
+    if (need > kStaticScratchBytes) {
+        char buffer[200];
+        snprintf(buffer, sizeof(buffer),
+                 "window_backward_static: B x K = %d x %d pairs need %zu bytes of scratch, the built-in array holds %zu;"
+                 " use hsnw_window_backward with the caller's scratch",
+                 io->B, model->K, need, kStaticScratchBytes);
+        return hsnw_fail(HSNW_E_UNSUPPORTED, buffer);
+    }
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kStaticDevices)
+        return hsnw_fail(HSNW_E_CUDA, "window_backward_static: no current device");
+    void* address = nullptr;
+    {
+        // In host code the array's name is only a handle; its address on the current device comes
+        // from the runtime. Looked up on the first call per device, with that device current.
+        std::lock_guard<std::mutex> lock(static_mutex);
+        if (!static_scratch_address[device]) {
+            void* found = nullptr;
+            const cudaError_t status = cudaGetSymbolAddress(&found, g_static_scratch);
+            if (status != cudaSuccess || !found) {
+                cudaGetLastError();
+                char buffer[200];
+                snprintf(buffer, sizeof(buffer), "window_backward_static: cudaGetSymbolAddress: %s",
+                         cudaGetErrorString(status));
+                return hsnw_fail(HSNW_E_CUDA, buffer);
+            }
+            static_scratch_address[device] = found;
+        }
+        address = static_scratch_address[device];
+    }
+    HsnwBackward local = *io;
+    local.scratch = address;
+    local.scratch_bytes = static_cast<int64_t>(kStaticScratchBytes);
+    return hsnw_window_backward(model, &local, stream);
 }
 
 void hsnw_backward_set_attributes() {

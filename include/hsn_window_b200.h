@@ -208,6 +208,23 @@ typedef struct HsnwBackward {
 int64_t hsnw_backward_scratch_bytes(const HsnwModel* model, int32_t B, int32_t T);
 int hsnw_window_backward(const HsnwModel* model, const HsnwBackward* io, void* stream);
 
+/* No counterpart in the reference. hsnw_window_backward for a caller that has no device memory to
+ * give as scratch and no way to get some: a host that only forwards buffers it was handed, or a
+ * process whose own pool already holds all free device memory, so that one more allocation would
+ * fail. Same arguments and results; io->scratch and io->scratch_bytes are ignored. The scratch is
+ * an array built into the library, hsnw_static_scratch_bytes() = 8 MiB of device memory that
+ * every GPU which loads the library keeps until the process ends. A window whose B x K pairs
+ * need more is refused with HSNW_E_UNSUPPORTED (the message says how much); it fits the
+ * reference shape (B 32, K 8, H 512, d 64: 2.4 MiB). The call allocates nothing, on the device or
+ * the host, and calls no allocating routine.
+ * The first call on a device looks the array's address up (cudaGetSymbolAddress, with that device
+ * current): make that first call before any stream capture begins.
+ * All calls on one device share the array, and it keeps the last call's contents. Nothing in it
+ * has to start at zero (every value is written before it is read within a call), so nothing is
+ * cleared; but two calls that overlap on the GPU, e.g. on two streams, race on it: order them. */
+int64_t hsnw_static_scratch_bytes(void);
+int hsnw_window_backward_static(const HsnwModel* model, const HsnwBackward* io, void* stream);
+
 /* The window-invariant part of the shared path's first layer for every position:
  * out [B*T, H] = [z ; ctx] [B*T, d+dc] x s_w1zc_t + shared.fc1.bias, one dense product
  * (hsnw_window_forward calls it itself; exported for tests and measurements). */
