@@ -6,7 +6,11 @@
 //           memory and serves every row; the rows' partial sums are reduced in slice order later.
 //   row     one block per row: reduce the partials to (u, z_hat), the scorer's logits for every
 //           cell, the router's decision (select.cuh), the gather of the selected cells and of
-//           their message sources, the messages, the cell norm -> the pairs' inputs v.
+//           their message sources, the messages, the cell norm -> the pairs' inputs v. What the
+//           scorer and the messages read of the state is kept as derived state that only the K
+//           written cells change per position (the state's part of every cell's logits, V h of
+//           every cell, every cell's max |h|), so no position walks the whole state; the row's
+//           inputs are staged into shared memory by the TMA's bulk copies on an mbarrier.
 //   unit    weight-stationary: a block holds a 64-column slice of ONE unit's first layer and the
 //           matching rows of its second layer and serves the pairs (row, slot) routed to that
 //           unit, found by a ballot compaction of the pair list: no unit runs for a pair that did
@@ -23,6 +27,7 @@
 #include "../../include/hsn_window_b200.h"
 #include "common.cuh"
 #include "select.cuh"
+#include "stage.cuh"
 #include "host_util.h"
 
 using namespace hsnw;
@@ -35,8 +40,9 @@ constexpr int kFR = 8;           // rows a front block serves
 constexpr int kUS = 32;          // columns of a unit slice
 constexpr int kPB = 32;          // pairs a unit block multiplies at a time
 constexpr int kPairTile = 256;   // pairs a unit block scans
-constexpr int kCT = 16;          // cells of a warp's scorer tile
-constexpr int kMaxM = 16;        // units (registers of the scorer's lane)
+constexpr int kCopyFloats = 4096;  // floats of the state a copy block moves
+constexpr int kInitCells = 32;   // cells of a block of the derived-state kernel
+constexpr int kMaxM = 16;        // units (registers of the scorer's thread)
 
 struct FwdCtx {
     HsnwModel m;
@@ -44,13 +50,19 @@ struct FwdCtx {
     int nF;      // slices of one front MLP's hidden layer
     int nU;      // slices of a unit's hidden layer
     int nG;      // slices of the gate's outputs
+    int n_front; // blocks of k_front that run the front (the rest copy the state tape)
+    int copy_per_row;
+    int* status;        // [1] 0, or 1 when a bounded wait ran out
     float* pre_s;       // [B*T, H]
-    float* part_front;  // [2 nF, B, d]
+    float* part_front;  // [B, 2 nF, d]
     float* v;           // [B*K, 4d]
     int* pair_unit;     // [B*K] the pair's unit, -1 on a padded slot
     float* part_f;      // [nU, B*K, d]
     float* gate_pre;    // [B*K, d]
     int* hmax_part;     // [B] bits of max |h| over the cells the position does not write
+    float* lh;          // [B, N, M] derived: the state's part of every cell's logits
+    float* vh;          // [B, N, d] derived: V h of every cell
+    int* cmax;          // [B, N]    derived: bits of every cell's max |h|
 };
 
 __device__ __forceinline__ const float* state_h(const FwdCtx& c, int row, int t) {
@@ -65,29 +77,76 @@ __device__ __forceinline__ const int64_t* state_age(const FwdCtx& c, int row, in
     return c.io.tape_state ? c.io.tape_age + (static_cast<int64_t>(row) * (c.io.T + 1) + t) * c.m.N
                            : c.io.age0 + static_cast<int64_t>(row) * c.m.N;
 }
+__host__ __device__ __forceinline__ int pad4(int n) { return (n + 3) & ~3; }
+
+// The derived state of one cell from its state row hrow [d] (shared memory): thread `lane_x` of a
+// group of nthreads computes outputs lane_x, lane_x + nthreads, ... of [M logit parts | d of V h].
+__device__ __forceinline__ void derive_outputs(const FwdCtx& c, const float* hrow, const float* swh,
+                                               const float* vt, float* lh_out, float* vh_out, int first,
+                                               int stride) {
+    const int d = c.m.d, M = c.m.M;
+    const bool bf = c.m.prod_bf16 != 0;
+    for (int o = first; o < M + d; o += stride) {
+        float sum = 0.0f;
+        if (o < M) {
+            for (int x = 0; x < d; ++x) sum += maybe_bf16(hrow[x], bf) * swh[x * M + o];
+            lh_out[o] = sum;
+        } else {
+            const int xo = o - M;
+            for (int i = 0; i < d; ++i) sum += maybe_bf16(hrow[i], bf) * vt[i * d + xo];
+            vh_out[xo] = maybe_bf16(sum, bf);
+        }
+    }
+}
 
 // ------------------------------------------------------------------------------------------------
 // init: record 0 of the tape is the start state with column 0's reset applied (resident: the
-// reset is applied in place).
+// reset is applied in place), and the derived state of every cell. blockIdx.x = row,
+// blockIdx.y = tile of 32 cells. Shared: hs [32][d], swh [d M], vt [d d].
 // ------------------------------------------------------------------------------------------------
-__global__ void k_init(FwdCtx c) {
+__global__ void __launch_bounds__(256) k_init(FwdCtx c) {
+    extern __shared__ __align__(16) unsigned char dyn[];
     const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
-    const int N = c.m.N, d = c.m.d, T = c.io.T;
+    const int N = c.m.N, d = c.m.d, M = c.m.M, T = c.io.T;
+    const int cell0 = blockIdx.y * kInitCells;
+    const int ncell = min(kInitCells, N - cell0);
+    float* hs = reinterpret_cast<float*>(dyn);
+    float* swh = hs + kInitCells * d;
+    float* vt = swh + d * M;
     const bool cut = c.io.reset[static_cast<int64_t>(row) * T] != 0;
     float* h0 = c.io.h0 + static_cast<int64_t>(row) * N * d;
-    float* q0 = c.io.q0 + static_cast<int64_t>(row) * d;
-    int64_t* a0 = c.io.age0 + static_cast<int64_t>(row) * N;
-    if (c.io.tape_state) {
-        float* h = c.io.tape_h + static_cast<int64_t>(row) * (T + 1) * N * d;
-        float* q = c.io.tape_q + static_cast<int64_t>(row) * (T + 1) * d;
-        int64_t* a = c.io.tape_age + static_cast<int64_t>(row) * (T + 1) * N;
-        for (int e = tid; e < N * d; e += nt) h[e] = cut ? 0.0f : h0[e];
-        for (int x = tid; x < d; x += nt) q[x] = cut ? 0.0f : q0[x];
-        for (int n = tid; n < N; n += nt) a[n] = cut ? 0 : a0[n];
-    } else if (cut) {
-        for (int e = tid; e < N * d; e += nt) h0[e] = 0.0f;
-        for (int x = tid; x < d; x += nt) q0[x] = 0.0f;
-        for (int n = tid; n < N; n += nt) a0[n] = 0;
+    if (row == 0 && blockIdx.y == 0 && tid == 0) *c.status = 0;
+    for (int e = tid; e < d * M; e += nt) swh[e] = c.m.score_w_t[2 * d * M + e];
+    for (int e = tid; e < d * d; e += nt) vt[e] = c.m.v_t[e];
+    for (int e = tid; e < ncell * d; e += nt) {
+        const float v = cut ? 0.0f : h0[static_cast<int64_t>(cell0) * d + e];
+        hs[e] = v;
+        if (c.io.tape_state) c.io.tape_h[(static_cast<int64_t>(row) * (T + 1)) * N * d + static_cast<int64_t>(cell0) * d + e] = v;
+        else if (cut) h0[static_cast<int64_t>(cell0) * d + e] = 0.0f;
+    }
+    for (int n = tid; n < ncell; n += nt) {
+        int64_t* a0 = c.io.age0 + static_cast<int64_t>(row) * N + cell0;
+        if (c.io.tape_state) c.io.tape_age[(static_cast<int64_t>(row) * (T + 1)) * N + cell0 + n] = cut ? 0 : a0[n];
+        else if (cut) a0[n] = 0;
+    }
+    if (blockIdx.y == 0) {
+        float* q0 = c.io.q0 + static_cast<int64_t>(row) * d;
+        for (int x = tid; x < d; x += nt) {
+            if (c.io.tape_state) c.io.tape_q[(static_cast<int64_t>(row) * (T + 1)) * d + x] = cut ? 0.0f : q0[x];
+            else if (cut) q0[x] = 0.0f;
+        }
+    }
+    __syncthreads();
+    // 8 threads per cell
+    const int cl = tid >> 3, sub = tid & 7;
+    if (cl < ncell) {
+        const int64_t cell = static_cast<int64_t>(row) * N + cell0 + cl;
+        derive_outputs(c, hs + cl * d, swh, vt, c.lh + cell * M, c.vh + cell * d, sub, 8);
+        if (sub == 0) {
+            int top = 0;
+            for (int x = 0; x < d; ++x) top = max(top, __float_as_int(fabsf(hs[cl * d + x])));
+            c.cmax[cell] = top;
+        }
     }
 }
 
@@ -145,38 +204,76 @@ __global__ void k_pre(HsnwModel m, const float* z, const float* ctx, int64_t row
 }
 
 // ------------------------------------------------------------------------------------------------
-// front: blockIdx.x = slice (0..nF-1: S; nF..2nF-1: P), blockIdx.y = row tile. 256 threads:
-// thread (row r, column cc) for the first layer, strided outputs for the second.
+// front: blocks [0, n_front): (slice, row tile) of the shared path, slices 0..nF-1: S, nF..2nF-1: P;
+// 256 threads: thread (row r, column cc) for the first layer, strided outputs for the second.
 // Shared: w1 [d][32], w2 [32][d], q [8][d], act [8][32].
+// Blocks [n_front, ...): the state tape's next record as a copy of this one, 16 KB a block (zeros
+// when the next position resets; the ages one older): off the critical path of the row phase,
+// which then only overwrites the K written cells.
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) k_front(FwdCtx c, int t) {
     extern __shared__ __align__(16) unsigned char dyn[];
-    const int d = c.m.d, H = c.m.H, B = c.io.B, T = c.io.T;
+    const int d = c.m.d, H = c.m.H, B = c.io.B, T = c.io.T, N = c.m.N;
     const bool bf = c.m.prod_bf16 != 0;
     const int tid = threadIdx.x;
-    const int slice = blockIdx.x, nF = c.nF;
+    if (static_cast<int>(blockIdx.x) >= c.n_front) {
+        const int job = blockIdx.x - c.n_front;
+        const int row = job / c.copy_per_row, chunk = job - row * c.copy_per_row;
+        const bool clear = t + 1 < T && c.io.reset[static_cast<int64_t>(row) * T + t + 1] != 0;
+        const int64_t rec = (static_cast<int64_t>(row) * (T + 1) + t) * N;
+        const float4* src = reinterpret_cast<const float4*>(c.io.tape_h + rec * d);
+        float4* dst = reinterpret_cast<float4*>(c.io.tape_h + (rec + N) * d);
+        const int total4 = (N * d) >> 2;
+        const int lo = chunk * (kCopyFloats >> 2), hi = min(total4, lo + (kCopyFloats >> 2));
+        for (int e = lo + tid; e < hi; e += 256) dst[e] = clear ? make_float4(0.0f, 0.0f, 0.0f, 0.0f) : src[e];
+        if (chunk == 0) {
+            const int64_t* age = c.io.tape_age + rec;
+            int64_t* age_next = c.io.tape_age + rec + N;
+            for (int n = tid; n < N; n += 256) age_next[n] = clear ? 0 : age[n] + 1;
+        }
+        return;
+    }
+    const int nF = c.nF;
+    const int slice = blockIdx.x % (2 * nF), tile = blockIdx.x / (2 * nF);
     const bool is_p = slice >= nF;
     const int c0 = (is_p ? slice - nF : slice) * kFS;
     const int cols = min(kFS, H - c0);
     const int col_base = (is_p ? H : 0) + c0;   // column in the merged [d, 2H] first layer
-    const int r0 = blockIdx.y * kFR;
+    const int r0 = tile * kFR;
     const int rows = min(kFR, B - r0);
     float* w1 = reinterpret_cast<float*>(dyn);          // [d][32]
     float* w2 = w1 + d * kFS;                           // [32][d]
     float* qs = w2 + kFS * d;                           // [8][d]
     float* act = qs + kFR * d;                          // [8][32]
-    for (int e = tid; e < d * kFS; e += 256) {
-        const int x = e >> 5, cc = e & 31;
-        w1[e] = cc < cols ? c.m.f_w1q_t[static_cast<int64_t>(x) * 2 * H + col_base + cc] : 0.0f;
-    }
-    for (int e = tid; e < kFS * d; e += 256) {
-        const int cc = e / d, x = e - cc * d;
-        w2[e] = cc < cols ? c.m.f_w2_t[static_cast<int64_t>(col_base + cc) * d + x] : 0.0f;
+    if (cols == kFS) {
+        // 16 bytes per request, every request in flight at once
+        for (int e = tid; e < d * (kFS >> 2); e += 256) {
+            const int x = e >> 3, c4 = e & 7;
+            cp_async16(w1 + x * kFS + c4 * 4, c.m.f_w1q_t + static_cast<int64_t>(x) * 2 * H + col_base + c4 * 4);
+        }
+        cp_async_floats(w2, c.m.f_w2_t + static_cast<int64_t>(col_base) * d, kFS * d);
+        cp_async_commit();
+    } else {
+        for (int e = tid; e < d * kFS; e += 256) {
+            const int x = e >> 5, cc = e & 31;
+            w1[e] = cc < cols ? c.m.f_w1q_t[static_cast<int64_t>(x) * 2 * H + col_base + cc] : 0.0f;
+        }
+        for (int e = tid; e < kFS * d; e += 256) {
+            const int cc = e / d, x = e - cc * d;
+            w2[e] = cc < cols ? c.m.f_w2_t[static_cast<int64_t>(col_base + cc) * d + x] : 0.0f;
+        }
     }
     for (int e = tid; e < rows * d; e += 256) {
         const int r = e / d, x = e - r * d;
         qs[e] = maybe_bf16(state_q(c, r0 + r, t)[x], bf);
     }
+    float pre = 0.0f;
+    {
+        const int r = tid >> 5, cc = tid & 31;
+        if (r < rows && cc < cols)
+            pre = is_p ? c.m.f_b1[H + c0 + cc] : c.pre_s[(static_cast<int64_t>(r0 + r) * T + t) * H + c0 + cc];
+    }
+    cp_async_wait_all();
     __syncthreads();
     {
         const int r = tid >> 5, cc = tid & 31;
@@ -184,8 +281,6 @@ __global__ void __launch_bounds__(256) k_front(FwdCtx c, int t) {
         if (r < rows && cc < cols) {
             float sum = 0.0f;
             for (int x = 0; x < d; ++x) sum += qs[r * d + x] * w1[x * kFS + cc];
-            const float pre = is_p ? c.m.f_b1[H + c0 + cc]
-                                   : c.pre_s[(static_cast<int64_t>(r0 + r) * T + t) * H + c0 + cc];
             a = maybe_bf16(gelu_erf(maybe_bf16(sum + pre, bf)), bf);
         }
         act[tid] = a;
@@ -196,154 +291,143 @@ __global__ void __launch_bounds__(256) k_front(FwdCtx c, int t) {
         float sum = 0.0f;
 #pragma unroll 8
         for (int cc = 0; cc < kFS; ++cc) sum += act[r * kFS + cc] * w2[cc * d + x];
-        c.part_front[(static_cast<int64_t>(slice) * B + r0 + r) * d + x] = sum;
+        c.part_front[(static_cast<int64_t>(r0 + r) * 2 * nF + slice) * d + x] = sum;
     }
 }
 
 // ------------------------------------------------------------------------------------------------
-// row: one block per row (256 or 512 threads). The scorer walks the row's state once, a warp per
-// tile of 16 cells: 16-byte coalesced loads, the tile transposed through shared memory so that a
-// lane owns half a cell's row, and the same registers are stored as the next record of the state
-// tape (the update phase then only overwrites the K written cells).
-// Shared (dynamic): rows [(K + K D) d], tiles [warps][16 (d+1)], vh [K D d], msg [K d], vt [d d],
-// sw [(3d+1+S) M], score [N], unit [N], cellmax [N], ue [2d], rowterm [16], src [K D], ew [K D],
-// rms [K].
+// row: one block per row. Everything the position reads of the row arrives in two stagings, each
+// one round trip to memory: (1) the front's partial sums, the derived logit parts of every cell,
+// the scorer's scalars, the ages and the cells' maxima as bulk copies on an mbarrier (contiguous,
+// 16-byte aligned runs; plain loads otherwise); (2) after the decision, the K selected cells' state
+// rows and the K D message sources' V h rows, one bulk copy per row.
+// Shared (dynamic), each segment padded to 16 bytes: pf [2 nF d], lh [N M], scal [N S], age [N] i64,
+// cmax [N], rows [(K + K D) d], msg [K d], sw_head [2d M], sw_tail [(1+S) M], score [N], unit [N],
+// ue [2d], rowterm [16], src [K D], ew [K D], rms [K].
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
     extern __shared__ __align__(16) unsigned char dyn[];
     __shared__ SelectShared S;
     __shared__ int ired[32];
+    __shared__ __align__(8) uint64_t bar;
     const int N = c.m.N, d = c.m.d, K = c.m.K, M = c.m.M, D = c.m.D, Sn = c.m.S;
-    const int B = c.io.B, T = c.io.T;
+    const int T = c.io.T;
     const bool bf = c.m.prod_bf16 != 0;
     const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
     const int lane = tid & 31, warp = tid >> 5, warps = nt >> 5;
-    const int feat = 3 * d + 1 + Sn, d4 = d >> 2, nrows = K + K * D;
-    float* rows = reinterpret_cast<float*>(dyn);            // gathered state rows: K own, K D sources
-    float* tiles = rows + nrows * d;
-    float* vh = tiles + warps * kCT * (d + 1);
-    float* msg = vh + K * D * d;
-    float* vt = msg + K * d;
-    float* sw = vt + d * d;
-    float* score = sw + feat * M;
-    int* unit = reinterpret_cast<int*>(score + N);
-    int* cellmax = unit + N;
-    float* ue = reinterpret_cast<float*>(cellmax + N);
+    const int nrows = K + K * D, nF2 = 2 * c.nF;
+    float* pf = reinterpret_cast<float*>(dyn);
+    float* lh = pf + pad4(nF2 * d);
+    float* scal = lh + pad4(N * M);
+    int64_t* age = reinterpret_cast<int64_t*>(scal + pad4(N * Sn));
+    int* cmax = reinterpret_cast<int*>(reinterpret_cast<float*>(age) + pad4(2 * N));
+    float* rows = reinterpret_cast<float*>(cmax + pad4(N));
+    float* msg = rows + nrows * d;
+    float* sw_head = msg + K * d;
+    float* sw_tail = sw_head + pad4(2 * d * M);
+    float* score = sw_tail + pad4((1 + Sn) * M);
+    int* unit = reinterpret_cast<int*>(score + pad4(N));
+    float* ue = reinterpret_cast<float*>(unit + pad4(N));
     float* rowterm = ue + 2 * d;
     int* src = reinterpret_cast<int*>(rowterm + kMaxM);
-    float* ew = reinterpret_cast<float*>(src + K * D);
-    float* rms = ew + K * D;
+    float* ew = reinterpret_cast<float*>(src + pad4(K * D));
+    float* rms = ew + pad4(K * D);
     const int64_t rt = static_cast<int64_t>(row) * T + t;
     const float* h = state_h(c, row, t);
-    const int64_t* age = state_age(c, row, t);
-    const bool last = t + 1 == T;
-    const bool clear = !last && c.io.reset[rt + 1] != 0;
-    const bool copy = c.io.tape_state != 0;
-    float* h_next = copy ? c.io.tape_h + (static_cast<int64_t>(row) * (T + 1) + t + 1) * N * d : nullptr;
-    for (int e = tid; e < feat * M; e += nt) sw[e] = c.m.score_w_t[e];
-    for (int e = tid; e < d * d; e += nt) vt[e] = c.m.v_t[e];
-    for (int j = tid; j < M; j += nt) S.cost[j] = c.m.cost[j];
+    if (tid == 0) mbar_init(&bar, 1);
+    __syncthreads();
+    // staging 1
+    {
+        const float* g_pf = c.part_front + static_cast<int64_t>(row) * nF2 * d;
+        const float* g_lh = c.lh + static_cast<int64_t>(row) * N * M;
+        const float* g_scal = c.io.scalars + rt * N * Sn;
+        const int64_t* g_age = state_age(c, row, t);
+        const int* g_cmax = c.cmax + static_cast<int64_t>(row) * N;
+        const void* srcs[5] = {g_pf, g_lh, g_scal, g_age, g_cmax};
+        void* dsts[5] = {pf, lh, scal, age, cmax};
+        const size_t bytes[5] = {sizeof(float) * nF2 * d, sizeof(float) * N * M, sizeof(float) * N * Sn,
+                                 sizeof(int64_t) * N, sizeof(int) * N};
+        uint32_t total = 0;
+        bool bulk[5];
+#pragma unroll
+        for (int s = 0; s < 5; ++s) {
+            bulk[s] = bulk_ok(srcs[s], dsts[s], bytes[s]);
+            if (bulk[s]) total += static_cast<uint32_t>(bytes[s]);
+        }
+        if (tid == 0) {
+            mbar_expect_tx(&bar, total);
+#pragma unroll
+            for (int s = 0; s < 5; ++s)
+                if (bulk[s]) bulk_g2s(dsts[s], srcs[s], static_cast<uint32_t>(bytes[s]), &bar);
+        }
+#pragma unroll
+        for (int s = 0; s < 5; ++s)
+            if (!bulk[s]) {
+                const int words = static_cast<int>(bytes[s] >> 2);
+                const uint32_t* from = static_cast<const uint32_t*>(srcs[s]);
+                uint32_t* to = static_cast<uint32_t*>(dsts[s]);
+                for (int e = tid; e < words; e += nt) to[e] = from[e];
+            }
+        cp_async_floats(sw_head, c.m.score_w_t, 2 * d * M);
+        cp_async_floats(sw_tail, c.m.score_w_t + static_cast<int64_t>(3 * d) * M, (1 + Sn) * M);
+        cp_async_commit();
+        for (int j = tid; j < M; j += nt) S.cost[j] = c.m.cost[j];
+        cp_async_wait_all();
+        mbar_wait(&bar, 0, c.status);
+    }
+    __syncthreads();
     // (u, z_hat) from the front's partial sums, slice by slice; eps = z - z_hat
     for (int x = tid; x < 2 * d; x += nt) {
         const bool is_p = x >= d;
         const int xx = is_p ? x - d : x;
         float sum = 0.0f;
-        for (int s = 0; s < c.nF; ++s)
-            sum += c.part_front[(static_cast<int64_t>((is_p ? c.nF : 0) + s) * B + row) * d + xx];
+        for (int s = 0; s < c.nF; ++s) sum += pf[((is_p ? c.nF : 0) + s) * d + xx];
         const float out = maybe_bf16(sum + c.m.f_b2[x], bf);
         ue[x] = is_p ? c.io.z[rt * d + xx] - out : out;
-    }
-    if (copy) {  // the ages of the next record: every cell one older, the written ones zeroed later
-        int64_t* age_next = c.io.tape_age + (static_cast<int64_t>(row) * (T + 1) + t + 1) * N;
-        for (int n = tid; n < N; n += nt) age_next[n] = clear ? 0 : age[n] + 1;
     }
     __syncthreads();
     if (tid < M) {
         float sum = 0.0f;
-        for (int x = 0; x < 2 * d; ++x) sum += maybe_bf16(ue[x], bf) * sw[x * M + tid];
+        for (int x = 0; x < 2 * d; ++x) sum += maybe_bf16(ue[x], bf) * sw_head[x * M + tid];
         rowterm[tid] = sum;
     }
     __syncthreads();
-    // the scorer
+    // the scorer: a thread per cell; the state's part of the logits is derived state
     const float lambda = c.m.lambda_cost;
-    const float* scal = c.io.scalars + rt * N * Sn;
     const float age_div = static_cast<float>(c.m.age_max);
-    float* tile = tiles + warp * kCT * (d + 1);
-    const int n_tiles = (N + kCT - 1) / kCT;
-    const int hx = d >> 1;
-    for (int tl = warp; tl < n_tiles; tl += warps) {
-        const int cell0 = tl * kCT;
-        const int ncell = min(kCT, N - cell0);
-        const float4* src4 = reinterpret_cast<const float4*>(h + static_cast<int64_t>(cell0) * d);
-        float4* dst4 = copy ? reinterpret_cast<float4*>(h_next + static_cast<int64_t>(cell0) * d) : nullptr;
-        for (int f = lane; f < ncell * d4; f += 32) {
-            const float4 v = src4[f];
-            const int cl = f / d4, x4 = f - cl * d4;
-            float* tp = tile + cl * (d + 1) + x4 * 4;
-            tp[0] = v.x; tp[1] = v.y; tp[2] = v.z; tp[3] = v.w;
-            if (dst4) dst4[f] = clear ? make_float4(0.0f, 0.0f, 0.0f, 0.0f) : v;
-        }
-        __syncwarp();
-        const int cl = lane & 15, half = lane >> 4;
-        const int i = cell0 + cl;
+    for (int i = tid; i < N; i += nt) {
         float acc[kMaxM];
 #pragma unroll
-        for (int j = 0; j < kMaxM; ++j) acc[j] = 0.0f;
-        int top = 0;
-        if (cl < ncell) {
-            const float* trow = tile + cl * (d + 1);
-            for (int s = 0; s < hx; ++s) {
-                // the second half walks its columns rotated by half a half: no bank is read twice
-                const int x = half ? hx + ((s + (hx >> 1)) % hx) : s;
-                const float raw = trow[x];
-                top = max(top, __float_as_int(fabsf(raw)));
-                const float a = maybe_bf16(raw, bf);
-                const float* w = sw + (2 * d + x) * M;
+        for (int j = 0; j < kMaxM; ++j) acc[j] = j < M ? lh[i * M + j] : 0.0f;
+        {
+            const float a = maybe_bf16(static_cast<float>(age[i]) / age_div, bf);
 #pragma unroll
-                for (int j = 0; j < kMaxM; ++j)
-                    if (j < M) acc[j] += a * w[j];
-            }
-            if (half == 0) {
-                {
-                    const float a = maybe_bf16(static_cast<float>(age[i]) / age_div, bf);
-                    const float* w = sw + (3 * d) * M;
+            for (int j = 0; j < kMaxM; ++j)
+                if (j < M) acc[j] += a * sw_tail[j];
+        }
+        for (int s = 0; s < Sn; ++s) {
+            const float a = maybe_bf16(scal[i * Sn + s], bf);
+            const float* w = sw_tail + (1 + s) * M;
 #pragma unroll
-                    for (int j = 0; j < kMaxM; ++j)
-                        if (j < M) acc[j] += a * w[j];
-                }
-                for (int s = 0; s < Sn; ++s) {
-                    const float a = maybe_bf16(scal[static_cast<int64_t>(i) * Sn + s], bf);
-                    const float* w = sw + (3 * d + 1 + s) * M;
+            for (int j = 0; j < kMaxM; ++j)
+                if (j < M) acc[j] += a * w[j];
+        }
+        float best = -INFINITY;
+        int arg = 0;
 #pragma unroll
-                    for (int j = 0; j < kMaxM; ++j)
-                        if (j < M) acc[j] += a * w[j];
+        for (int j = 0; j < kMaxM; ++j) {
+            if (j < M) {
+                const float logit = maybe_bf16(acc[j] + rowterm[j] + c.m.score_b[j], bf);
+                if (c.io.logits) c.io.logits[(rt * N + i) * M + j] = logit;
+                const float sc = lambda > 0.0f ? __fsub_rn(logit, __fmul_rn(lambda, S.cost[j])) : logit;
+                if (j == 0 || sc > best) {
+                    best = sc;
+                    arg = j;
                 }
             }
         }
-#pragma unroll
-        for (int j = 0; j < kMaxM; ++j)
-            if (j < M) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 16);
-        top = max(top, __shfl_xor_sync(0xffffffffu, top, 16));
-        if (half == 0 && cl < ncell) {
-            float best = -INFINITY;
-            int arg = 0;
-#pragma unroll
-            for (int j = 0; j < kMaxM; ++j) {
-                if (j < M) {
-                    const float logit = maybe_bf16(acc[j] + rowterm[j] + c.m.score_b[j], bf);
-                    if (c.io.logits) c.io.logits[(rt * N + i) * M + j] = logit;
-                    const float sc = lambda > 0.0f ? __fsub_rn(logit, __fmul_rn(lambda, S.cost[j])) : logit;
-                    if (j == 0 || sc > best) {
-                        best = sc;
-                        arg = j;
-                    }
-                }
-            }
-            score[i] = best;
-            unit[i] = arg;
-            cellmax[i] = top;
-        }
-        __syncwarp();
+        score[i] = best;
+        unit[i] = arg;
     }
     __syncthreads();
     int64_t* cells_o = c.io.cells + rt * K;
@@ -371,7 +455,7 @@ __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
         }
         __syncthreads();
     }
-    // the sources and edge weights of the selected cells, then every row they read, 16 bytes a thread
+    // the sources and edge weights of the selected cells
     for (int e = tid; e < K * D; e += nt) {
         const int k = e / D, j = e - k * D;
         const int cell = S.out_cell[k];
@@ -384,7 +468,7 @@ __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
         for (int i = tid; i < N; i += nt) {
             bool written = false;
             for (int k = 0; k < K; ++k) written = written || ((S.out_flag[k] & 1) && S.out_cell[k] == i);
-            if (!written) top = max(top, cellmax[i]);
+            if (!written) top = max(top, cmax[i]);
         }
         for (int w = 16; w > 0; w >>= 1) top = max(top, __shfl_xor_sync(0xffffffffu, top, w));
         if (lane == 0) ired[warp] = top;
@@ -395,29 +479,34 @@ __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
         for (int w = 0; w < warps; ++w) mx = max(mx, ired[w]);
         c.hmax_part[row] = mx;
     }
+    // staging 2: the selected cells' state rows and their sources' V h rows, one bulk copy a row
     {
-        const float4* h4 = reinterpret_cast<const float4*>(h);
-        float4* rows4 = reinterpret_cast<float4*>(rows);
-        for (int f = tid; f < nrows * d4; f += nt) {
-            const int r = f / d4, x4 = f - r * d4;
-            const int cell = r < K ? S.out_cell[r] : src[r - K];
-            rows4[f] = h4[static_cast<int64_t>(cell) * d4 + x4];
+        const float* g_vh = c.vh + static_cast<int64_t>(row) * N * d;
+        const uint32_t row_bytes = static_cast<uint32_t>(sizeof(float) * d);
+        const bool bulk = bulk_ok(h, rows, row_bytes) && bulk_ok(g_vh, rows, row_bytes);
+        if (bulk) {
+            if (warp == 0) {
+                if (lane == 0) mbar_expect_tx(&bar, row_bytes * nrows);
+                __syncwarp();
+                for (int r = lane; r < nrows; r += 32) {
+                    const float* from = r < K ? h + static_cast<int64_t>(S.out_cell[r]) * d
+                                              : g_vh + static_cast<int64_t>(src[r - K]) * d;
+                    bulk_g2s(rows + r * d, from, row_bytes, &bar);
+                }
+            }
+            mbar_wait(&bar, 1, c.status);
+        } else {
+            for (int e = tid; e < nrows * d; e += nt) {
+                const int r = e / d, x = e - r * d;
+                rows[e] = r < K ? h[static_cast<int64_t>(S.out_cell[r]) * d + x] : g_vh[static_cast<int64_t>(src[r - K]) * d + x];
+            }
         }
-    }
-    __syncthreads();
-    // V h of every source: K D d outputs, d products each, from shared memory
-    for (int e = tid; e < K * D * d; e += nt) {
-        const int s = e / d, x = e - s * d;
-        const float* hs = rows + (K + s) * d;
-        float sum = 0.0f;
-        for (int i = 0; i < d; ++i) sum += maybe_bf16(hs[i], bf) * vt[i * d + x];
-        vh[e] = maybe_bf16(sum, bf);
     }
     __syncthreads();
     for (int e = tid; e < K * d; e += nt) {
         const int k = e / d, x = e - k * d;
         float sum = 0.0f;
-        for (int j = 0; j < D; ++j) sum += vh[(k * D + j) * d + x] * ew[k * D + j];  // edge order
+        for (int j = 0; j < D; ++j) sum += rows[(K + k * D + j) * d + x] * ew[k * D + j];  // edge order
         msg[e] = maybe_bf16(sum, bf);
     }
     __syncthreads();
@@ -569,14 +658,17 @@ __global__ void __launch_bounds__(256) k_unit(FwdCtx c, int t) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// update: one block per row, 256 threads. Shared (dynamic): F [K d], y [K d], hnew [K d],
-// delta [K d], wo [d d], cell_of [K], scale [K].
+// update: one block per row, 256 threads. Reduces the second layer's partial sums, W_out, the
+// candidate norm, tanh, sigmoid, the gated write of the K cells, the summary, and the derived
+// state of the written cells (their logit parts, V h and maxima).
+// Shared (dynamic): F [K d], y [K d], hnew [K d], delta [K d], wo [d d], vt [d d], swh [d M],
+// cell_of [K], scale [K].
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) k_update(FwdCtx c, int t) {
     extern __shared__ __align__(16) unsigned char dyn[];
     __shared__ int ired[8];
     __shared__ int zero_slot;
-    const int N = c.m.N, d = c.m.d, K = c.m.K;
+    const int N = c.m.N, d = c.m.d, K = c.m.K, M = c.m.M;
     const int B = c.io.B, T = c.io.T, P = B * K;
     const bool bf = c.m.prod_bf16 != 0;
     const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
@@ -586,7 +678,9 @@ __global__ void __launch_bounds__(256) k_update(FwdCtx c, int t) {
     float* hnew = ys + K * d;
     float* delta = hnew + K * d;
     float* wo = delta + K * d;
-    int* cell_of = reinterpret_cast<int*>(wo + d * d);
+    float* vt = wo + d * d;
+    float* swh = vt + d * d;
+    int* cell_of = reinterpret_cast<int*>(swh + pad4(d * M));
     float* scale = reinterpret_cast<float*>(cell_of + K);
     const int64_t rt = static_cast<int64_t>(row) * T + t;
     const int64_t pair0 = static_cast<int64_t>(row) * K;
@@ -598,22 +692,34 @@ __global__ void __launch_bounds__(256) k_update(FwdCtx c, int t) {
     const bool last = t + 1 == T;
     const bool clear = !last && c.io.reset[rt + 1] != 0;
     const bool tape = c.io.tape_state != 0;
-    for (int e = tid; e < d * d; e += nt) wo[e] = c.m.wout_t[e];
+    cp_async_floats(wo, c.m.wout_t, d * d);
+    cp_async_floats(vt, c.m.v_t, d * d);
+    cp_async_floats(swh, c.m.score_w_t + static_cast<int64_t>(2 * d) * M, d * M);
+    cp_async_commit();
     for (int k = tid; k < K; k += nt) cell_of[k] = valid[k] ? static_cast<int>(cells[k]) : -1;
     if (tid == 0) zero_slot = -1;
     __syncthreads();
     for (int k = tid; k < K; k += nt)
         if (cell_of[k] == 0) zero_slot = k;  // at most one valid slot names cell 0
-    // the executed unit's output: the second layer's partial sums in slice order, plus its bias
+    // the executed unit's output: the second layer's partial sums in slice order, plus its bias;
+    // the loads of an element go out together, four slices at a time
     for (int e = tid; e < K * d; e += nt) {
         const int k = e / d, x = e - k * d;
         float sum = 0.0f;
         if (cell_of[k] >= 0) {
-            for (int s = 0; s < c.nU; ++s) sum += c.part_f[(static_cast<int64_t>(s) * P + pair0 + k) * d + x];
+            const float* p = c.part_f + (pair0 + k) * d + x;
+            const int64_t stride = static_cast<int64_t>(P) * d;
+            int s = 0;
+            for (; s + 4 <= c.nU; s += 4) {
+                const float a0 = p[s * stride], a1 = p[(s + 1) * stride], a2 = p[(s + 2) * stride], a3 = p[(s + 3) * stride];
+                sum += a0; sum += a1; sum += a2; sum += a3;
+            }
+            for (; s < c.nU; ++s) sum += p[s * stride];
             sum = maybe_bf16(sum + c.m.b2[static_cast<int>(units[k]) * d + x], bf);
         }
         Fs[e] = sum;
     }
+    cp_async_wait_all();
     __syncthreads();
     for (int e = tid; e < K * d; e += nt) {
         const int k = e / d, x = e - k * d;
@@ -656,14 +762,32 @@ __global__ void __launch_bounds__(256) k_update(FwdCtx c, int t) {
     }
     __syncthreads();
     // the state after the position: the tape's next record already holds a copy of this one (the
-    // row phase wrote it, zeroed if the next position resets), so only the written cells move
+    // front phase wrote it, zeroed if the next position resets), so only the written cells move
+    float* lh_row = c.lh + static_cast<int64_t>(row) * N * M;
+    float* vh_row = c.vh + static_cast<int64_t>(row) * N * d;
+    int* cmax_row = c.cmax + static_cast<int64_t>(row) * N;
     if (!clear) {
         for (int e = tid; e < K * d; e += nt) {
             const int k = e / d, x = e - k * d;
             if (cell_of[k] >= 0) h_write[static_cast<int64_t>(cell_of[k]) * d + x] = hnew[e];
         }
-    } else if (!tape) {
-        for (int e = tid; e < N * d; e += nt) h_write[e] = 0.0f;
+        // the written cells' derived state: 32 threads a slot
+        for (int k = warp; k < K; k += warps) {
+            const int n = cell_of[k];
+            if (n < 0) continue;
+            derive_outputs(c, hnew + k * d, swh, vt, lh_row + static_cast<int64_t>(n) * M,
+                           vh_row + static_cast<int64_t>(n) * d, lane, 32);
+            int m = 0;
+            for (int x = lane; x < d; x += 32) m = max(m, __float_as_int(fabsf(hnew[k * d + x])));
+            for (int w = 16; w > 0; w >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, w));
+            if (lane == 0) cmax_row[n] = m;
+        }
+    } else {
+        if (!tape)
+            for (int e = tid; e < N * d; e += nt) h_write[e] = 0.0f;
+        for (int e = tid; e < N * M; e += nt) lh_row[e] = 0.0f;
+        for (int e = tid; e < N * d; e += nt) vh_row[e] = 0.0f;
+        for (int n = tid; n < N; n += nt) cmax_row[n] = 0;
     }
     float* q_next = tape ? c.io.tape_q + (static_cast<int64_t>(row) * (T + 1) + t + 1) * d
                          : c.io.q0 + static_cast<int64_t>(row) * d;
@@ -682,9 +806,11 @@ __global__ void __launch_bounds__(256) k_update(FwdCtx c, int t) {
         c.io.h_sel[rt * K * d + e] = value;
     }
     if (tape) {
-        int64_t* age_next = c.io.tape_age + (static_cast<int64_t>(row) * (T + 1) + t + 1) * N;
-        for (int k = tid; k < K; k += nt)
-            if (cell_of[k] >= 0) age_next[cell_of[k]] = 0;
+        if (!clear) {
+            int64_t* age_next = c.io.tape_age + (static_cast<int64_t>(row) * (T + 1) + t + 1) * N;
+            for (int k = tid; k < K; k += nt)
+                if (cell_of[k] >= 0) age_next[cell_of[k]] = 0;
+        }
     } else {
         int64_t* ages = c.io.age0 + static_cast<int64_t>(row) * N;
         for (int n = tid; n < N; n += nt) ages[n] = clear ? 0 : ages[n] + 1;
@@ -714,30 +840,39 @@ __global__ void __launch_bounds__(256) k_update(FwdCtx c, int t) {
 size_t align_up(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
 struct Layout {
-    size_t pre_s, part_front, v, pair_unit, part_f, gate_pre, hmax_part, total;
+    size_t status, pre_s, part_front, v, pair_unit, part_f, gate_pre, hmax_part, lh, vh, cmax, total;
 };
 Layout layout(const HsnwModel& m, int B, int T) {
     Layout L;
     const int nF = (m.H + kFS - 1) / kFS, nU = (m.H + kUS - 1) / kUS;
+    const size_t Bz = static_cast<size_t>(B);
     size_t off = 0;
-    L.pre_s = off; off += align_up(sizeof(float) * static_cast<size_t>(B) * T * m.H);
-    L.part_front = off; off += align_up(sizeof(float) * 2 * nF * static_cast<size_t>(B) * m.d);
-    L.v = off; off += align_up(sizeof(float) * static_cast<size_t>(B) * m.K * 4 * m.d);
-    L.pair_unit = off; off += align_up(sizeof(int) * static_cast<size_t>(B) * m.K);
-    L.part_f = off; off += align_up(sizeof(float) * nU * static_cast<size_t>(B) * m.K * m.d);
-    L.gate_pre = off; off += align_up(sizeof(float) * static_cast<size_t>(B) * m.K * m.d);
-    L.hmax_part = off; off += align_up(sizeof(int) * static_cast<size_t>(B));
+    L.status = off; off += 256;
+    L.pre_s = off; off += align_up(sizeof(float) * Bz * T * m.H);
+    L.part_front = off; off += align_up(sizeof(float) * 2 * nF * Bz * m.d);
+    L.v = off; off += align_up(sizeof(float) * Bz * m.K * 4 * m.d);
+    L.pair_unit = off; off += align_up(sizeof(int) * Bz * m.K);
+    L.part_f = off; off += align_up(sizeof(float) * nU * Bz * m.K * m.d);
+    L.gate_pre = off; off += align_up(sizeof(float) * Bz * m.K * m.d);
+    L.hmax_part = off; off += align_up(sizeof(int) * Bz);
+    L.lh = off; off += align_up(sizeof(float) * Bz * m.N * m.M);
+    L.vh = off; off += align_up(sizeof(float) * Bz * m.N * m.d);
+    L.cmax = off; off += align_up(sizeof(int) * Bz * m.N);
     L.total = off;
     return L;
 }
 
-int row_threads(const HsnwModel& m) { return m.N >= 256 ? 512 : 256; }
+int row_threads(const HsnwModel& m) { return m.N > 512 ? 512 : 256; }
 
 size_t row_shared(const HsnwModel& m) {
-    const size_t feat = 3 * m.d + 1 + m.S, d = m.d, K = m.K, D = m.D, N = m.N;
-    const size_t warps = row_threads(m) / 32;
-    return sizeof(float) * ((K + K * D) * d + warps * kCT * (d + 1) + K * D * d + K * d + d * d + feat * m.M
-        + 3 * N + 2 * d + kMaxM + 2 * K * D + K);
+    const int d = m.d, K = m.K, D = m.D, N = m.N, nF2 = 2 * ((m.H + kFS - 1) / kFS);
+    const size_t words = static_cast<size_t>(pad4(nF2 * d)) + pad4(N * m.M) + pad4(N * m.S) + pad4(2 * N) + pad4(N)
+        + static_cast<size_t>(K + K * D) * d + static_cast<size_t>(K) * d + pad4(2 * d * m.M) + pad4((1 + m.S) * m.M)
+        + 2 * static_cast<size_t>(pad4(N)) + 2 * d + kMaxM + 2 * static_cast<size_t>(pad4(K * D)) + K;
+    return sizeof(float) * words;
+}
+size_t init_shared(const HsnwModel& m) {
+    return sizeof(float) * (static_cast<size_t>(kInitCells) * m.d + static_cast<size_t>(m.d) * m.M + static_cast<size_t>(m.d) * m.d);
 }
 size_t front_shared(const HsnwModel& m) {
     return sizeof(float) * (static_cast<size_t>(2) * m.d * kFS + static_cast<size_t>(kFR) * m.d + kFR * kFS);
@@ -747,7 +882,7 @@ size_t unit_shared(const HsnwModel& m) {
         + static_cast<size_t>(kUS) * m.d + kPB * kUS + kPairTile);
 }
 size_t update_shared(const HsnwModel& m) {
-    return sizeof(float) * (4 * static_cast<size_t>(m.K) * m.d + static_cast<size_t>(m.d) * m.d + 2 * m.K);
+    return sizeof(float) * (4 * static_cast<size_t>(m.K) * m.d + 2 * static_cast<size_t>(m.d) * m.d + pad4(m.d * m.M) + 2 * m.K);
 }
 
 int check_model(const HsnwModel* m) {
@@ -758,7 +893,8 @@ int check_model(const HsnwModel* m) {
     if (m->M > kMaxM) return hsnw_fail(HSNW_E_UNSUPPORTED, "window: at most 16 units (M)");
     if (m->K > kMaxSlots) return hsnw_fail(HSNW_E_UNSUPPORTED, "window: at most 64 slots (K)");
     const size_t cap = hsnw_max_shared() - 4096;  // room for the kernels' static shared memory
-    if (row_shared(*m) > cap || front_shared(*m) > cap || unit_shared(*m) > cap || update_shared(*m) > cap)
+    if (row_shared(*m) > cap || front_shared(*m) > cap || unit_shared(*m) > cap || update_shared(*m) > cap
+        || init_shared(*m) > cap)
         return hsnw_fail(HSNW_E_UNSUPPORTED, "window: a phase's working set exceeds a block's shared memory");
     return HSNW_OK;
 }
@@ -801,7 +937,11 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
     c.nF = (model->H + kFS - 1) / kFS;
     c.nU = (model->H + kUS - 1) / kUS;
     c.nG = (model->d + kUS - 1) / kUS;
+    const int B = io->B, T = io->T;
+    c.n_front = 2 * c.nF * ((B + kFR - 1) / kFR);
+    c.copy_per_row = io->tape_state ? (model->N * model->d + kCopyFloats - 1) / kCopyFloats : 0;
     unsigned char* base = static_cast<unsigned char*>(io->scratch);
+    c.status = reinterpret_cast<int*>(base + L.status);
     c.pre_s = reinterpret_cast<float*>(base + L.pre_s);
     c.part_front = reinterpret_cast<float*>(base + L.part_front);
     c.v = reinterpret_cast<float*>(base + L.v);
@@ -809,11 +949,14 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
     c.part_f = reinterpret_cast<float*>(base + L.part_f);
     c.gate_pre = reinterpret_cast<float*>(base + L.gate_pre);
     c.hmax_part = reinterpret_cast<int*>(base + L.hmax_part);
-    const int B = io->B, T = io->T;
+    c.lh = reinterpret_cast<float*>(base + L.lh);
+    c.vh = reinterpret_cast<float*>(base + L.vh);
+    c.cmax = reinterpret_cast<int*>(base + L.cmax);
     const int rthreads = row_threads(*model);
-    k_init<<<B, 256, 0, stream>>>(c);
+    const dim3 init_grid(B, (model->N + kInitCells - 1) / kInitCells);
+    k_init<<<init_grid, 256, init_shared(*model), stream>>>(c);
     if (int rc = hsnw_front_projection(model, io->z, io->ctx, static_cast<int64_t>(B) * T, c.pre_s, stream)) return rc;
-    const dim3 front_grid(2 * c.nF, (B + kFR - 1) / kFR);
+    const int front_grid = c.n_front + B * c.copy_per_row;
     const dim3 unit_grid(model->M * (c.nU + c.nG), (B * model->K + kPairTile - 1) / kPairTile);
     const size_t sh_front = front_shared(*model), sh_row = row_shared(*model);
     const size_t sh_unit = unit_shared(*model), sh_update = update_shared(*model);
@@ -839,8 +982,9 @@ extern "C" int hsnw_stream_step(const HsnwModel* model, const HsnwForward* io, v
 
 void hsnw_forward_set_attributes() {
     const struct { const void* f; const char* n; } ks[] = {
-        {reinterpret_cast<const void*>(k_front), "front"}, {reinterpret_cast<const void*>(k_row), "row"},
-        {reinterpret_cast<const void*>(k_unit), "unit"}, {reinterpret_cast<const void*>(k_update), "update"}};
+        {reinterpret_cast<const void*>(k_init), "init"}, {reinterpret_cast<const void*>(k_front), "front"},
+        {reinterpret_cast<const void*>(k_row), "row"}, {reinterpret_cast<const void*>(k_unit), "unit"},
+        {reinterpret_cast<const void*>(k_update), "update"}};
     for (const auto& k : ks)
         if (!hsnw_opt_in(k.f, k.n)) hsnw_attribute_failed();
 }

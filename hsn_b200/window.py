@@ -285,6 +285,7 @@ def window_forward(
     else:
         o["h"], o["q"], o["age"] = h0, q0, age0
     o["pos"] = pos
+    o["status"] = scratch[:4].view(torch.int32)  # 0, or 1 when a bounded device-side wait ran out
     if forced is None:
         o["refreshed"] = o["sel_refreshed"].float().sum(dim=2).mean(dim=0)
     o["explored"] = torch.zeros(T, dtype=f32, device=dev)

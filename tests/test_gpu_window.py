@@ -323,6 +323,7 @@ def test_full_size_window_properties() -> None:
     model = WindowModel.from_oracle_weights(W, device="cuda", prod="bf16")
     args = (dev(z), dev(ctx), dev(scalars), dev(reset), tuple(dev(s) for s in state))
     one = window_forward(model, *args)
+    assert int(one["status"]) == 0  # no bounded wait of the staging ran out
     two = window_forward(model, *args)
     for key in ("tape_h", "qs", "sel_cell_idx", "sel_unit_idx", "tape_theta", "rec_c", "rec_hidden"):
         assert torch.equal(one[key], two[key]), key
