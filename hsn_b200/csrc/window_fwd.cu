@@ -52,6 +52,7 @@ struct FwdCtx {
     int nG;      // slices of the gate's outputs
     int n_front; // blocks of k_front that run the front (the rest copy the state tape)
     int copy_per_row;
+    int stage_cells;    // 1: the row phase stages the per-cell logit parts and scalars in shared memory
     int* status;        // [1] 0, or 1 when a bounded wait ran out
     float* pre_s;       // [B*T, H]
     float* part_front;  // [B, 2 nF, d]
@@ -317,9 +318,10 @@ __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
     const int lane = tid & 31, warp = tid >> 5, warps = nt >> 5;
     const int nrows = K + K * D, nF2 = 2 * c.nF;
     float* pf = reinterpret_cast<float*>(dyn);
-    float* lh = pf + pad4(nF2 * d);
-    float* scal = lh + pad4(N * M);
-    int64_t* age = reinterpret_cast<int64_t*>(scal + pad4(N * Sn));
+    const bool staged = c.stage_cells != 0;  // else the per-cell inputs are read from memory in place
+    float* lh_s = pf + pad4(nF2 * d);
+    float* scal_s = lh_s + (staged ? pad4(N * M) : 0);
+    int64_t* age = reinterpret_cast<int64_t*>(scal_s + (staged ? pad4(N * Sn) : 0));
     int* cmax = reinterpret_cast<int*>(reinterpret_cast<float*>(age) + pad4(2 * N));
     float* rows = reinterpret_cast<float*>(cmax + pad4(N));
     float* msg = rows + nrows * d;
@@ -344,8 +346,9 @@ __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
         const int64_t* g_age = state_age(c, row, t);
         const int* g_cmax = c.cmax + static_cast<int64_t>(row) * N;
         const void* srcs[5] = {g_pf, g_lh, g_scal, g_age, g_cmax};
-        void* dsts[5] = {pf, lh, scal, age, cmax};
-        const size_t bytes[5] = {sizeof(float) * nF2 * d, sizeof(float) * N * M, sizeof(float) * N * Sn,
+        void* dsts[5] = {pf, lh_s, scal_s, age, cmax};
+        const size_t bytes[5] = {sizeof(float) * nF2 * d, staged ? sizeof(float) * N * M : 0,
+                                 staged ? sizeof(float) * N * Sn : 0,
                                  sizeof(int64_t) * N, sizeof(int) * N};
         uint32_t total = 0;
         bool bulk[5];
@@ -393,6 +396,8 @@ __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
     }
     __syncthreads();
     // the scorer: a thread per cell; the state's part of the logits is derived state
+    const float* lh = staged ? lh_s : c.lh + static_cast<int64_t>(row) * N * M;
+    const float* scal = staged ? scal_s : c.io.scalars + rt * N * Sn;
     const float lambda = c.m.lambda_cost;
     const float age_div = static_cast<float>(c.m.age_max);
     for (int i = tid; i < N; i += nt) {
@@ -863,10 +868,13 @@ Layout layout(const HsnwModel& m, int B, int T) {
 }
 
 int row_threads(const HsnwModel& m) { return m.N > 512 ? 512 : 256; }
+// the per-cell logit parts and scalars of a row are staged in shared memory while they are small
+bool stage_cells(const HsnwModel& m) { return sizeof(float) * static_cast<size_t>(m.N) * (m.M + m.S) <= 96 * 1024; }
 
 size_t row_shared(const HsnwModel& m) {
     const int d = m.d, K = m.K, D = m.D, N = m.N, nF2 = 2 * ((m.H + kFS - 1) / kFS);
-    const size_t words = static_cast<size_t>(pad4(nF2 * d)) + pad4(N * m.M) + pad4(N * m.S) + pad4(2 * N) + pad4(N)
+    const size_t cells = stage_cells(m) ? static_cast<size_t>(pad4(N * m.M)) + pad4(N * m.S) : 0;
+    const size_t words = static_cast<size_t>(pad4(nF2 * d)) + cells + pad4(2 * N) + pad4(N)
         + static_cast<size_t>(K + K * D) * d + static_cast<size_t>(K) * d + pad4(2 * d * m.M) + pad4((1 + m.S) * m.M)
         + 2 * static_cast<size_t>(pad4(N)) + 2 * d + kMaxM + 2 * static_cast<size_t>(pad4(K * D)) + K;
     return sizeof(float) * words;
@@ -939,6 +947,7 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
     c.nG = (model->d + kUS - 1) / kUS;
     const int B = io->B, T = io->T;
     c.n_front = 2 * c.nF * ((B + kFR - 1) / kFR);
+    c.stage_cells = stage_cells(*model) ? 1 : 0;
     c.copy_per_row = io->tape_state ? (model->N * model->d + kCopyFloats - 1) / kCopyFloats : 0;
     unsigned char* base = static_cast<unsigned char*>(io->scratch);
     c.status = reinterpret_cast<int*>(base + L.status);

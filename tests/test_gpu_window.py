@@ -376,3 +376,73 @@ def test_entry_points_refuse_what_they_do_not_take() -> None:
     with pytest.raises(_lib.WindowKernelError) as err:
         window_forward(big, *args)
     assert err.value.code == _lib.E_UNSUPPORTED
+
+
+@pytest.mark.parametrize(
+    "shape",
+    [
+        dict(N=512, d=64, K=8, H=512, M=8, D=4),     # the split-window chain's model
+        dict(N=4096, d=128, K=16, H=1024, M=8, D=4),  # the scaled sparse-routing model
+        dict(N=1024, d=64, K=8, H=512, M=8, D=4),    # the streaming model
+    ],
+)
+def test_models_of_the_larger_configurations(shape) -> None:
+    """The other benchmark configurations' models at a reduced batch (B2, T3): forward values with
+    the oracle's decisions forced, free-running decisions where not within 1e-4 of a tie, and the
+    reverse sweep against the float64 oracle, state tape on and off."""
+    from hsn_b200.window import WindowModel, window_backward, window_forward
+
+    rng = np.random.default_rng(shape["N"])
+    B, T = 2, 3
+    W, z, ctx, scalars, reset, state = _synthetic(rng, B, T, p_reset=0.2, age_max=64, **shape)
+    for key in ("w1", "w2", "gate_w", "v_w", "wout_w"):
+        setattr(W, key, (getattr(W, key) * 4).astype(np.float32))
+    h0 = (rng.standard_normal(state[0].shape) * 0.3).astype(np.float32)
+    reset[:, 0] = False
+    state = (h0, h0.mean(axis=1), rng.integers(0, 200, state[2].shape), state[3])
+    want = O.window_forward(W, z, ctx, scalars, reset, *state)
+    model = WindowModel.from_oracle_weights(W, device="cuda")
+    args = (dev(z), dev(ctx), dev(scalars), dev(reset))
+    forced = (dev(want["sel_cell_idx"]), dev(want["sel_unit_idx"]), dev(want["sel_valid"]))
+    got = window_forward(model, *args, tuple(dev(s) for s in state), forced=forced)
+    assert int(got["status"]) == 0
+    for key in ("tape_h", "tape_q", "qs", "tape_hsel", "h", "q", "rec_c", "rec_b", "rec_y", "rec_m", "rec_hidden"):
+        w = want[key].astype(np.float64)
+        scale = max(1e-3, float(np.abs(w).max()))
+        np.testing.assert_allclose(got[key].cpu().numpy(), w, rtol=1e-5, atol=1e-5 * scale, err_msg=key)
+    assert np.array_equal(got["tape_age"].cpu().numpy(), want["tape_age"])
+    good = np.logical_and.accumulate(_settled(want["logits"], want["sel_cell_idx"], want["sel_valid"], 1e-4), axis=1)
+    free = window_forward(model, *args, tuple(dev(s) for s in state))
+    assert good.mean() > 0.6
+    assert np.array_equal(free["sel_cell_idx"].cpu().numpy()[good], want["sel_cell_idx"][good])
+    assert np.array_equal(free["sel_refreshed"].cpu().numpy()[good], want["sel_refreshed"][good])
+    # the resident form: no state tape, the state updated in place
+    resident = tuple(dev(s) for s in state)
+    res = window_forward(model, *args, resident, forced=forced, tape_state=False)
+    np.testing.assert_allclose(resident[0].cpu().numpy(), want["h"], rtol=1e-5, atol=1e-5)
+    assert np.array_equal(resident[2].cpu().numpy(), want["age"])
+    np.testing.assert_allclose(res["qs"].cpu().numpy(), want["qs"], rtol=1e-5, atol=1e-5)
+    # the reverse sweep on the sweep's own record
+    N, d, K = shape["N"], shape["d"], shape["K"]
+    post = rng.standard_normal((B, T, d)).astype(np.float32)
+    sel = rng.standard_normal((B, T, K, d)).astype(np.float32)
+    cpu = {k: v.cpu().numpy() for k, v in got.items() if isinstance(v, torch.Tensor)}
+    rec = {k: cpu["rec_" + k].astype(np.float64) for k in ("y", "hidden", "gate_pre", "m", "rms")}
+    W64 = O.WindowWeights(**{k: (v.astype(np.float64) if isinstance(v, np.ndarray) and v.dtype == np.float32 else v)
+                             for k, v in W.__dict__.items()})  # fmt: skip
+    valid = cpu["sel_valid"]
+    cells, units = np.where(valid, cpu["sel_cell_idx"], 0), np.where(valid, cpu["sel_unit_idx"], 0)
+    trace: dict = {}
+    want_dc, want_db = O.state_gradient_backward(
+        W64, cpu["rec_c"].astype(np.float64), cpu["rec_b"].astype(np.float64), cpu["rec_h_old"].astype(np.float64),
+        cells, units, valid, reset, N, None, post.astype(np.float64), sel.astype(np.float64), rec, trace=trace,
+    )  # fmt: skip
+    dc, db, (A, R) = window_backward(
+        model, got["rec_c"], got["rec_b"], got["rec_h_old"], dev(cells), dev(units), got["sel_valid"], dev(reset),
+        None, dev(post), dev(sel), {k: got["rec_" + k] for k in rec},
+    )  # fmt: skip
+    scale = max(1.0, float(np.abs(want_dc).max()), float(np.abs(trace["A"]).max()))
+    np.testing.assert_allclose(dc.cpu().numpy(), want_dc, rtol=1e-4, atol=1e-5 * scale)
+    np.testing.assert_allclose(db.cpu().numpy(), want_db, rtol=1e-4, atol=1e-5 * scale)
+    keep = ~reset[:, 0]
+    np.testing.assert_allclose(A.cpu().numpy(), trace["A"][:, 0] * keep[:, None, None], rtol=1e-4, atol=1e-5 * scale)
