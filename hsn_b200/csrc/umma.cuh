@@ -1,0 +1,89 @@
+// 5th-generation tensor core primitives for sm_100a as inline PTX: tensor memory (TMEM)
+// allocation, shared-memory matrix descriptors, tcgen05.mma issue / commit, tcgen05.ld.
+//
+// Operand layout used throughout this library: K-major, no swizzle. An operand tile of R rows
+// (R = M for A, N for B) and KT elements along K (bf16) is stored as KT/8 planes; plane kc holds,
+// for every row r, the 8 consecutive K-elements 8 kc .. 8 kc + 7 as one 16-byte unit at byte
+// offset kc * (R * 16) + r * 16. Eight consecutive rows of a plane are one 8 x 16-byte core
+// matrix (128 contiguous bytes), so in the descriptor the stride between core matrices along the
+// rows ("stride byte offset") is 128 and the stride between the two K-halves of a K = 16
+// instruction ("leading byte offset") is R * 16. One tcgen05.mma consumes two planes; the next
+// K-step starts 2 * R * 16 bytes further on.
+//
+// The accumulator D [128, N] fp32 lives in TMEM: lane i holds row i, column j holds column j.
+// Warp w of the epilogue may touch lanes 32 w .. 32 w + 31 only.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "stage.cuh"
+
+namespace hsnw {
+
+// kind::f16 instruction descriptor: D fp32, A and B bf16, both K-major, dense, M x N.
+__device__ __forceinline__ uint32_t umma_idesc_bf16(int M, int N) {
+    return (1u << 4)                                  // D format: F32
+           | (1u << 7)                                // A format: BF16
+           | (1u << 10)                               // B format: BF16
+           | (static_cast<uint32_t>(N >> 3) << 17)    // N / 8
+           | (static_cast<uint32_t>(M >> 4) << 24);   // M / 16
+}
+
+// Shared-memory matrix descriptor for the layout above (rows = R of the tile).
+__device__ __forceinline__ uint64_t umma_desc(const void* smem_tile, int rows) {
+    const uint32_t addr = smem_addr(smem_tile);
+    uint64_t desc = 0;
+    desc |= static_cast<uint64_t>((addr >> 4) & 0x3fffu);                                   // start address
+    desc |= static_cast<uint64_t>((static_cast<uint32_t>(rows) * 16u >> 4) & 0x3fffu) << 16;  // leading byte offset
+    desc |= static_cast<uint64_t>((128u >> 4) & 0x3fffu) << 32;                             // stride byte offset
+    desc |= static_cast<uint64_t>(1) << 46;                                                 // descriptor version (sm_100)
+    return desc;                                                                            // layout type 0: no swizzle
+}
+
+// TMEM: `columns` is a power of two >= 32. Executed by one whole warp; the base address lands in
+// *slot (shared memory).
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(slot)), "r"(columns)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+// Generic-proxy writes to shared memory become visible to the tensor core's (async proxy) reads.
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] * B[smem]^T for one K = 16 step; issued by ONE thread.
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, bool accumulate) {
+    const uint32_t acc = accumulate ? 1u : 0u;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc)
+        : "memory");
+}
+// All MMAs issued so far by this thread arrive on `bar` when they have completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(bar)) : "memory");
+}
+// Eight consecutive fp32 columns of this thread's TMEM lane (lane = 32 * (warp % 4) + lane id).
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float out[8]) {
+    uint32_t r[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ uint32_t tmem_addr(uint32_t base, int lane, int column) {
+    return base + (static_cast<uint32_t>(lane) << 16) + static_cast<uint32_t>(column);
+}
+
+}  // namespace hsnw

@@ -28,6 +28,7 @@
 #include "common.cuh"
 #include "select.cuh"
 #include "stage.cuh"
+#include "umma.cuh"
 #include "host_util.h"
 
 using namespace hsnw;
@@ -202,6 +203,81 @@ __global__ void k_pre(HsnwModel m, const float* z, const float* ctx, int64_t row
             if (col < H) out[rr * H + col] = acc[i][j] + m.f_b1[col];
         }
     }
+}
+
+// ------------------------------------------------------------------------------------------------
+// pre on the tensor cores (bf16 products): a 128 x 128 tile of pre_s per block, K = d + dc.
+// Both operands are converted to bf16 while they are staged into the K-major core-matrix layout of
+// umma.cuh; one thread issues the tcgen05.mma chain into a 128-column TMEM accumulator and commits
+// it to an mbarrier; the four warps read their 32 lanes back (tcgen05.ld) and add the bias.
+// Shared (dynamic): A [Kp/8][128][8] bf16, B [Kp/8][128][8] bf16.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    return static_cast<uint32_t>(bf16_bits(lo)) | (static_cast<uint32_t>(bf16_bits(hi)) << 16);
+}
+
+__global__ void __launch_bounds__(128) k_pre_tc(HsnwModel m, const float* z, const float* ctx, int64_t rows, float* out,
+                                                int* status) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ uint32_t tmem_slot;
+    const int d = m.d, dc = m.dc, H = m.H, K = d + dc, Kp = (K + 15) & ~15, planes = Kp >> 3;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int64_t r0 = static_cast<int64_t>(blockIdx.x) * 128;
+    const int c0 = blockIdx.y * 128;
+    uint4* As = reinterpret_cast<uint4*>(dyn);
+    uint4* Bs = As + planes * 128;
+    if (tid == 0) mbar_init(&bar, 1);
+    for (int idx = tid; idx < planes * 128; idx += 128) {
+        const int r = idx & 127, kc = idx >> 7;
+        const int64_t row = r0 + r;
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int k = kc * 8 + j;
+            v[j] = (row < rows && k < K) ? (k < d ? z[row * d + k] : ctx[row * dc + (k - d)]) : 0.0f;
+        }
+        As[idx] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+        const int col = c0 + r;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int k = kc * 8 + j;
+            v[j] = (col < H && k < K) ? m.s_w1zc_t[static_cast<int64_t>(k) * H + col] : 0.0f;
+        }
+        Bs[idx] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+    }
+    fence_async_smem();
+    if (warp == 0) tmem_alloc(&tmem_slot, 128);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t taddr = tmem_slot;
+    if (tid == 0) {
+        const uint32_t idesc = umma_idesc_bf16(128, 128);
+        const uint64_t da = umma_desc(As, 128), db = umma_desc(Bs, 128);
+        for (int s = 0; s < (Kp >> 4); ++s) {
+            const uint64_t step = static_cast<uint64_t>(s) * ((2 * 128 * 16) >> 4);  // two planes per K = 16
+            umma_bf16(taddr, da + step, db + step, idesc, s > 0);
+        }
+        umma_commit(&bar);
+    }
+    mbar_wait(&bar, 0, status);
+    tcgen05_fence_after();
+    const int64_t row = r0 + warp * 32 + lane;
+    for (int cb = 0; cb < 128; cb += 8) {
+        float acc[8];
+        tmem_ld8(tmem_addr(taddr, warp * 32, cb), acc);
+        if (row < rows) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int col = c0 + cb + i;
+                if (col < H) out[row * H + col] = acc[i] + m.f_b1[col];
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(taddr, 128);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -914,9 +990,23 @@ extern "C" int64_t hsnw_forward_scratch_bytes(const HsnwModel* model, int32_t B,
     return static_cast<int64_t>(layout(*model, B, T).total);
 }
 
+// where k_pre_tc reports a bounded wait that ran out: the forward's scratch word while a forward
+// call is being enqueued, else nowhere
+static thread_local int* g_pre_status = nullptr;
+
 extern "C" int hsnw_front_projection(const HsnwModel* model, const float* z, const float* ctx, int64_t rows,
                                      float* out, void* stream) {
     if (!model || !z || !ctx || !out || rows < 1) return hsnw_fail(HSNW_E_ARG, "front_projection: null or empty");
+    if (model->prod_bf16) {
+        // bf16 products: the tensor-core tile kernel (status: the caller's scratch word, or none)
+        const int Kp = (model->d + model->dc + 15) & ~15;
+        const size_t shared = static_cast<size_t>(2) * (Kp / 8) * 128 * 16;
+        if (shared <= hsnw_max_shared() - 4096) {
+            const dim3 grid(static_cast<unsigned>((rows + 127) / 128), static_cast<unsigned>((model->H + 127) / 128));
+            k_pre_tc<<<grid, 128, shared, static_cast<cudaStream_t>(stream)>>>(*model, z, ctx, rows, out, g_pre_status);
+            return hsnw_check_launch("front_projection");
+        }
+    }
     const dim3 grid(static_cast<unsigned>((rows + kSlice - 1) / kSlice), static_cast<unsigned>((model->H + kSlice - 1) / kSlice));
     k_pre<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(*model, z, ctx, rows, out);
     return hsnw_check_launch("front_projection");
@@ -964,7 +1054,10 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
     const int rthreads = row_threads(*model);
     const dim3 init_grid(B, (model->N + kInitCells - 1) / kInitCells);
     k_init<<<init_grid, 256, init_shared(*model), stream>>>(c);
-    if (int rc = hsnw_front_projection(model, io->z, io->ctx, static_cast<int64_t>(B) * T, c.pre_s, stream)) return rc;
+    g_pre_status = c.status;
+    const int rc_pre = hsnw_front_projection(model, io->z, io->ctx, static_cast<int64_t>(B) * T, c.pre_s, stream);
+    g_pre_status = nullptr;
+    if (rc_pre) return rc_pre;
     const int front_grid = c.n_front + B * c.copy_per_row;
     const dim3 unit_grid(model->M * (c.nU + c.nG), (B * model->K + kPairTile - 1) / kPairTile);
     const size_t sh_front = front_shared(*model), sh_row = row_shared(*model);
@@ -991,7 +1084,8 @@ extern "C" int hsnw_stream_step(const HsnwModel* model, const HsnwForward* io, v
 
 void hsnw_forward_set_attributes() {
     const struct { const void* f; const char* n; } ks[] = {
-        {reinterpret_cast<const void*>(k_init), "init"}, {reinterpret_cast<const void*>(k_front), "front"},
+        {reinterpret_cast<const void*>(k_init), "init"}, {reinterpret_cast<const void*>(k_pre_tc), "pre_tc"},
+        {reinterpret_cast<const void*>(k_front), "front"},
         {reinterpret_cast<const void*>(k_row), "row"}, {reinterpret_cast<const void*>(k_unit), "unit"},
         {reinterpret_cast<const void*>(k_update), "update"}};
     for (const auto& k : ks)

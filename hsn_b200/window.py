@@ -19,7 +19,7 @@ from torch import Tensor
 
 from . import _lib
 
-__all__ = ["WindowModel", "window_forward", "window_backward", "stream_step", "prepare"]
+__all__ = ["WindowModel", "window_forward", "window_backward", "stream_step", "front_projection", "prepare"]
 
 _WEIGHT_KEYS = (
     "s_w1 s_b1 s_w2 s_b2 p_w1 p_b1 p_w2 p_b2 score_w score_b v_w wout_w gate_w gate_b norm_w cand_w "
@@ -391,3 +391,22 @@ def window_backward(
     with torch.cuda.device(dev):
         _lib.check(lib.hsnw_window_backward(ctypes.byref(model.struct), ctypes.byref(io), _stream(dev)))
     return dc, db, (A, R)
+
+
+def front_projection(model: WindowModel, z: Tensor, ctx: Tensor) -> Tensor:
+    """The window-invariant half of the shared path's first layer for every position
+    (``hsnw_front_projection``): ``[z; ctx] [R, d + dc] @ W + b -> [R, H]``, the part of
+    ``shared.fc1`` (``python/hsn/model/encoder.py``) that does not read the carried summary. With
+    bf16 products it runs as tcgen05 tensor-core tiles. ``window_forward`` calls it itself."""
+    dm, dev = model.dims, model.device
+    rows = int(z.shape[0])
+    z = _check("z", z, (rows, dm["d"]), torch.float32, dev)
+    ctx = _check("ctx", ctx, (rows, dm["dc"]), torch.float32, dev)
+    out = torch.empty((rows, dm["H"]), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(
+            _lib.library().hsnw_front_projection(
+                ctypes.byref(model.struct), z.data_ptr(), ctx.data_ptr(), rows, out.data_ptr(), _stream(dev)
+            )
+        )
+    return out

@@ -446,3 +446,31 @@ def test_models_of_the_larger_configurations(shape) -> None:
     np.testing.assert_allclose(db.cpu().numpy(), want_db, rtol=1e-4, atol=1e-5 * scale)
     keep = ~reset[:, 0]
     np.testing.assert_allclose(A.cpu().numpy(), trace["A"][:, 0] * keep[:, None, None], rtol=1e-4, atol=1e-5 * scale)
+
+
+@pytest.mark.parametrize("dims", [dict(N=256, d=64, K=8, H=512, M=8, D=4), dict(N=16, d=12, K=2, H=20, M=3, D=2),
+                                  dict(N=32, d=128, K=4, H=1024, M=8, D=4)])  # fmt: skip
+@pytest.mark.parametrize("prod", ["bf16", "fp32"])
+def test_front_projection_equals_a_plain_product(dims, prod: str) -> None:
+    """The window-invariant projection ([z; ctx] W + b for every position): tensor-core tiles with
+    bf16 products, CUDA cores with fp32 products, against torch on the same (rounded) operands;
+    rows and columns that are not multiples of the tile, several tiles in both directions."""
+    from hsn_b200.window import WindowModel, front_projection
+
+    rng = np.random.default_rng(5)
+    W = O.WindowWeights.random(rng, std=0.2, **dims)
+    W.s_b1 = rng.standard_normal(W.s_b1.shape).astype(np.float32)
+    model = WindowModel.from_oracle_weights(W, device="cuda", prod=prod)
+    d = dims["d"]
+    for rows in (1, 130, 1000):
+        z = dev(rng.standard_normal((rows, d)).astype(np.float32))
+        ctx = dev(rng.standard_normal((rows, d)).astype(np.float32))
+        got = front_projection(model, z, ctx)
+        x = torch.cat([z, ctx], dim=1)
+        w = torch.cat([dev(W.s_w1[:, :d]), dev(W.s_w1[:, 2 * d :])], dim=1)
+        b = dev(W.s_b1)
+        if prod == "bf16":
+            x, w, b = (t.to(torch.bfloat16).double() for t in (x, w, b))
+        want = (x.double() @ w.double().t() + b.double()).float()
+        scale = float(want.abs().max())
+        assert float((got - want).abs().max()) <= 2e-5 * scale, (rows, prod)
