@@ -739,6 +739,184 @@ __global__ void __launch_bounds__(256) k_unit(FwdCtx c, int t) {
 }
 
 // ------------------------------------------------------------------------------------------------
+// unit on the tensor cores (bf16 products). blockIdx.x = (unit j, block cb): blocks 0 .. nB-1 are
+// 128 hidden columns of unit j, block nB is the gate's linear for unit j's pairs; blockIdx.y = pair
+// tile. Per batch of 32 pairs:
+//   D1 [128 hidden columns, 32 pairs] = W1 tile [128, 4d] x v [32, 4d]^T      (tcgen05.mma, TMEM)
+//   epilogue 1: + bias, round, record, activation, written as the bf16 operand of the next product
+//   D2 [128 (d outputs, padded), 32 pairs] = W2 tile [128, 128] x act [32, 128]^T
+//   epilogue 2: the block's partial sum of the unit's output.
+// The weight tiles are bf16 images made on the host in the operand layout (umma.cuh) and arrive by
+// one bulk copy each; the pairs' inputs are converted and laid out while they are staged.
+// 256 threads: warp w reads TMEM lanes 32 (w % 4) .. +31 and the pairs 16 (w / 4) .. +15.
+// Shared (dynamic): A1 [4d/8][128][8], A2 [16][128][8], B1 [4d/8][32][8], B2 [16][32][8] bf16, list.
+// ------------------------------------------------------------------------------------------------
+constexpr int kTP = 32;  // pairs of a tensor-core batch
+
+__global__ void __launch_bounds__(256) k_unit_tc(FwdCtx c, int t) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    __shared__ int warp_count[8];
+    __shared__ int n_list;
+    __shared__ __align__(8) uint64_t bar_w, bar_m;
+    __shared__ uint32_t tmem_slot;
+    const int d = c.m.d, K = c.m.K, H = c.m.H, in = 4 * c.m.d, planes = in >> 3;
+    const int P = c.io.B * K, T = c.io.T;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nB = c.nU;
+    const int j = blockIdx.x / (nB + 1), cb = blockIdx.x - j * (nB + 1);
+    const bool is_gate = cb == nB;
+    const int c0 = cb * 128;
+    uint4* A1 = reinterpret_cast<uint4*>(dyn);                 // [planes][128]
+    uint4* A2 = A1 + planes * 128;                             // [16][128]
+    uint4* B1 = A2 + 16 * 128;                                 // [planes][32]
+    uint4* B2 = B1 + planes * kTP;                             // [16][32]
+    int* list = reinterpret_cast<int*>(B2 + 16 * kTP);         // [256]
+    const int p0 = blockIdx.y * kPairTile;
+    {
+        const int p = p0 + tid;
+        const bool mine = p < P && c.pair_unit[p] == j;
+        const unsigned mask = __ballot_sync(0xffffffffu, mine);
+        if (lane == 0) warp_count[warp] = __popc(mask);
+        if (tid == 0) {
+            mbar_init(&bar_w, 1);
+            mbar_init(&bar_m, 1);
+        }
+        __syncthreads();
+        int before = 0;
+        for (int w = 0; w < warp; ++w) before += warp_count[w];
+        if (mine) list[before + __popc(mask & ((1u << lane) - 1u))] = p;
+        if (tid == 0) {
+            int total = 0;
+            for (int w = 0; w < 8; ++w) total += warp_count[w];
+            n_list = total;
+        }
+        __syncthreads();
+    }
+    const int count = n_list;
+    if (count == 0) return;
+    // the weight tiles: one bulk copy each
+    if (tid == 0) {
+        const uint32_t a1_bytes = static_cast<uint32_t>(planes) * 128 * 16, a2_bytes = 16 * 128 * 16;
+        const unsigned char* g1 = is_gate ? static_cast<const unsigned char*>(c.m.umma_gate)
+                                          : static_cast<const unsigned char*>(c.m.umma_w1)
+                                                + (static_cast<size_t>(j) * nB + cb) * a1_bytes;
+        mbar_expect_tx(&bar_w, a1_bytes + (is_gate ? 0u : a2_bytes));
+        bulk_g2s(A1, g1, a1_bytes, &bar_w);
+        if (!is_gate)
+            bulk_g2s(A2, static_cast<const unsigned char*>(c.m.umma_w2) + (static_cast<size_t>(j) * nB + cb) * a2_bytes,
+                     a2_bytes, &bar_w);
+    }
+    if (warp == 0) tmem_alloc(&tmem_slot, 64);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t taddr = tmem_slot;
+    const uint32_t idesc = umma_idesc_bf16(128, kTP);
+    const int q = warp & 3, hf = warp >> 2;
+    const int m = q * 32 + lane;           // this thread's TMEM lane: a hidden column, then an output
+    uint32_t phase = 0;
+    bool weights_in = false;
+    const float4* v4 = reinterpret_cast<const float4*>(c.v);
+    for (int base = 0; base < count; base += kTP) {
+        const int nb = min(kTP, count - base);
+        // the pairs' inputs as the B operand: a thread converts 8 values and stores one 16-byte unit
+        for (int idx = tid; idx < planes * kTP; idx += 256) {
+            const int n = idx & (kTP - 1), kc = idx >> 5;
+            uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+            if (n < nb) {
+                const float4* src = v4 + static_cast<int64_t>(list[base + n]) * d + kc * 2;
+                const float4 lo = src[0], hi = src[1];
+                packed = make_uint4(pack_bf16x2(lo.x, lo.y), pack_bf16x2(lo.z, lo.w), pack_bf16x2(hi.x, hi.y),
+                                    pack_bf16x2(hi.z, hi.w));
+            }
+            B1[idx] = packed;
+        }
+        fence_async_smem();
+        if (!weights_in) {
+            mbar_wait(&bar_w, 0, c.status);
+            weights_in = true;
+        }
+        tcgen05_fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            tcgen05_fence_after();
+            const uint64_t da = umma_desc(A1, 128), db = umma_desc(B1, kTP);
+            for (int s = 0; s < (in >> 4); ++s)
+                umma_bf16(taddr, da + static_cast<uint64_t>(s) * ((2 * 128 * 16) >> 4),
+                          db + static_cast<uint64_t>(s) * ((2 * kTP * 16) >> 4), idesc, s > 0);
+            umma_commit(&bar_m);
+        }
+        mbar_wait(&bar_m, phase, c.status);
+        phase ^= 1u;
+        tcgen05_fence_after();
+        // epilogue 1
+        {
+            float acc[16];
+            tmem_ld8(tmem_addr(taddr, q * 32, hf * 16), acc);
+            tmem_ld8(tmem_addr(taddr, q * 32, hf * 16 + 8), acc + 8);
+            const bool col_ok = is_gate ? m < d : c0 + m < H;
+            const float bias = col_ok ? (is_gate ? c.m.gate_b[m] : c.m.b1[j * H + c0 + m]) : 0.0f;
+            uint16_t* b2_half = reinterpret_cast<uint16_t*>(B2);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int n = hf * 16 + i;
+                float a = 0.0f;
+                if (n < nb && col_ok) {
+                    const int pair = list[base + n];
+                    const float pre = bf16r(acc[i] + bias);
+                    if (is_gate) {
+                        c.gate_pre[static_cast<int64_t>(pair) * d + m] = pre;
+                    } else {
+                        if (c.io.rec_c) {
+                            const int row = pair / K, k = pair - row * K;
+                            c.io.rec_hidden[((static_cast<int64_t>(row) * T + t) * K + k) * H + c0 + m] = pre;
+                        }
+                        a = gelu_erf(pre);
+                    }
+                }
+                // B2 (n, k = m): plane m / 8, unit n, element m % 8
+                if (!is_gate) b2_half[((m >> 3) * kTP + n) * 8 + (m & 7)] = bf16_bits(a);
+            }
+        }
+        if (is_gate) {
+            tcgen05_fence_before();
+            __syncthreads();
+            continue;
+        }
+        fence_async_smem();
+        tcgen05_fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            tcgen05_fence_after();
+            const uint64_t da = umma_desc(A2, 128), db = umma_desc(B2, kTP);
+            for (int s = 0; s < 8; ++s)
+                umma_bf16(taddr + 32, da + static_cast<uint64_t>(s) * ((2 * 128 * 16) >> 4),
+                          db + static_cast<uint64_t>(s) * ((2 * kTP * 16) >> 4), idesc, s > 0);
+            umma_commit(&bar_m);
+        }
+        mbar_wait(&bar_m, phase, c.status);
+        phase ^= 1u;
+        tcgen05_fence_after();
+        // epilogue 2: lane m is output x of the unit
+        {
+            float acc[16];
+            tmem_ld8(tmem_addr(taddr, q * 32, 32 + hf * 16), acc);
+            tmem_ld8(tmem_addr(taddr, q * 32, 32 + hf * 16 + 8), acc + 8);
+            if (m < d) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int n = hf * 16 + i;
+                    if (n < nb) c.part_f[(static_cast<int64_t>(cb) * P + list[base + n]) * d + m] = acc[i];
+                }
+            }
+        }
+        tcgen05_fence_before();
+        __syncthreads();
+    }
+    if (warp == 0) tmem_dealloc(taddr, 64);
+}
+
+// ------------------------------------------------------------------------------------------------
 // update: one block per row, 256 threads. Reduces the second layer's partial sums, W_out, the
 // candidate norm, tanh, sigmoid, the gated write of the K cells, the summary, and the derived
 // state of the written cells (their logit parts, V h and maxima).
@@ -965,6 +1143,10 @@ size_t unit_shared(const HsnwModel& m) {
     return sizeof(float) * (static_cast<size_t>(kPB) * 4 * m.d + static_cast<size_t>(4) * m.d * kUS
         + static_cast<size_t>(kUS) * m.d + kPB * kUS + kPairTile);
 }
+size_t unit_tc_shared(const HsnwModel& m) {
+    const size_t planes = static_cast<size_t>(4 * m.d) / 8;
+    return 16 * (planes * 128 + 16 * 128 + planes * kTP + 16 * kTP) + sizeof(int) * kPairTile;
+}
 size_t update_shared(const HsnwModel& m) {
     return sizeof(float) * (4 * static_cast<size_t>(m.K) * m.d + 2 * static_cast<size_t>(m.d) * m.d + pad4(m.d * m.M) + 2 * m.K);
 }
@@ -1032,8 +1214,10 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
     FwdCtx c;
     c.m = *model;
     c.io = *io;
+    const bool unit_tc = model->prod_bf16 && model->umma_w1 && model->umma_gate && model->umma_w2 && model->d <= 128
+        && unit_tc_shared(*model) <= hsnw_max_shared() - 4096;
     c.nF = (model->H + kFS - 1) / kFS;
-    c.nU = (model->H + kUS - 1) / kUS;
+    c.nU = unit_tc ? (model->H + 127) / 128 : (model->H + kUS - 1) / kUS;
     c.nG = (model->d + kUS - 1) / kUS;
     const int B = io->B, T = io->T;
     c.n_front = 2 * c.nF * ((B + kFR - 1) / kFR);
@@ -1059,13 +1243,14 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
     g_pre_status = nullptr;
     if (rc_pre) return rc_pre;
     const int front_grid = c.n_front + B * c.copy_per_row;
-    const dim3 unit_grid(model->M * (c.nU + c.nG), (B * model->K + kPairTile - 1) / kPairTile);
+    const dim3 unit_grid(model->M * (unit_tc ? c.nU + 1 : c.nU + c.nG), (B * model->K + kPairTile - 1) / kPairTile);
     const size_t sh_front = front_shared(*model), sh_row = row_shared(*model);
-    const size_t sh_unit = unit_shared(*model), sh_update = update_shared(*model);
+    const size_t sh_unit = unit_shared(*model), sh_update = update_shared(*model), sh_unit_tc = unit_tc_shared(*model);
     for (int t = 0; t < T; ++t) {
         k_front<<<front_grid, 256, sh_front, stream>>>(c, t);
         k_row<<<B, rthreads, sh_row, stream>>>(c, t);
-        k_unit<<<unit_grid, 256, sh_unit, stream>>>(c, t);
+        if (unit_tc) k_unit_tc<<<unit_grid, 256, sh_unit_tc, stream>>>(c, t);
+        else k_unit<<<unit_grid, 256, sh_unit, stream>>>(c, t);
         k_update<<<B, 256, sh_update, stream>>>(c, t);
         if (int rc = hsnw_check_launch("window_forward")) return rc;
     }
@@ -1087,6 +1272,7 @@ void hsnw_forward_set_attributes() {
         {reinterpret_cast<const void*>(k_init), "init"}, {reinterpret_cast<const void*>(k_pre_tc), "pre_tc"},
         {reinterpret_cast<const void*>(k_front), "front"},
         {reinterpret_cast<const void*>(k_row), "row"}, {reinterpret_cast<const void*>(k_unit), "unit"},
+        {reinterpret_cast<const void*>(k_unit_tc), "unit_tc"},
         {reinterpret_cast<const void*>(k_update), "update"}};
     for (const auto& k : ks)
         if (!hsnw_opt_in(k.f, k.n)) hsnw_attribute_failed();

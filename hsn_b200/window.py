@@ -131,6 +131,8 @@ class WindowModel:
             "edge_w": w["edge_w"],
             "cost": w["cost"],
         }
+        if prod == "bf16":
+            packed.update(_umma_images(w["w1"], w["w2"], packed["gate_t"]))
         struct = _lib.HsnwModel()
         dims = dict(N=N, d=d, K=int(k), H=H, M=M, D=D, S=S, dc=dc)
         for name, value in dims.items():
@@ -142,7 +144,8 @@ class WindowModel:
         struct.shared_cost, struct.limit = float(shared_cost), float(limit)
         struct.norm_eps, struct.cand_eps = float(norm_eps), float(cand_eps)
         for name in _lib.MODEL_POINTERS:
-            setattr(struct, name, packed[name].data_ptr())
+            if name in packed:
+                setattr(struct, name, packed[name].data_ptr())
         prepare(device)
         return WindowModel(struct=struct, tensors=packed, device=device, dims=dims, prod=prod)
 
@@ -184,6 +187,23 @@ class WindowModel:
             limit=float(model.cfg.budget) * (1.0 + 1e-5), norm_eps=float(cell.norm.eps),
             cand_eps=float(cell.cand_norm.eps),
         )  # fmt: skip
+
+
+def _umma_images(w1: Tensor, w2: Tensor, gate_t: Tensor) -> dict[str, Tensor]:
+    """The unit bank as bf16 operand tiles for the tensor cores: 128-row tiles in the K-major
+    core-matrix layout ``[K/8][128][8]`` of ``hsn_b200/csrc/umma.cuh``, zero padded."""
+    M, in4, H = (int(n) for n in w1.shape)
+    d = int(w2.shape[2])
+    nB = (H + 127) // 128
+    pad_h = nB * 128 - H
+    bf = torch.bfloat16
+    a1 = torch.nn.functional.pad(w1, (0, pad_h))  # [M, 4d, nB*128]
+    a1 = a1.reshape(M, in4 // 8, 8, nB, 128).permute(0, 3, 1, 4, 2).to(bf).contiguous()
+    g = torch.nn.functional.pad(gate_t, (0, 128 - d))  # [4d, 128]
+    g = g.reshape(in4 // 8, 8, 128).permute(0, 2, 1).to(bf).contiguous()
+    a2 = torch.nn.functional.pad(w2, (0, 128 - d, 0, pad_h))  # [M, nB*128, 128]
+    a2 = a2.reshape(M, nB, 16, 8, 128).permute(0, 1, 2, 4, 3).to(bf).contiguous()
+    return {"umma_w1": a1, "umma_gate": g, "umma_w2": a2}
 
 
 def _check(name: str, t: Tensor, shape: tuple[int, ...], dtype: torch.dtype, device: torch.device) -> Tensor:

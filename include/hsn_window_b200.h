@@ -116,6 +116,14 @@ typedef struct HsnwModel {
     const int32_t* pad_src; /* [N, D] */
     const float* edge_w;    /* [N, D] (0 on padding) */
     const float* cost;      /* [M] */
+    /* bf16 images of the unit bank for the tensor cores (prod_bf16 only; null: CUDA-core path).
+     * Tiles of 128 rows in the K-major core-matrix layout [K/8][128][8] (hsn_b200/csrc/umma.cuh),
+     * zero padded: umma_w1 [M][ceil(H/128)][4d/8][128][8] (rows: hidden columns, K: the cell input),
+     * umma_gate [4d/8][128][8] (rows: the gate's outputs), umma_w2 [M][ceil(H/128)][16][128][8]
+     * (rows: the unit's outputs, K: the 128 hidden columns of the block). */
+    const void* umma_w1;
+    const void* umma_gate;
+    const void* umma_w2;
 } HsnwModel;
 
 /* Inputs, tape and record of a forward sweep. Row-major, contiguous. Null = not wanted, for the
