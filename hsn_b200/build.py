@@ -62,6 +62,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     nvcc = _nvcc()
     objects = []
     flags = ["-O3", "-std=c++17", "-lineinfo", *ARCH, "-Xcompiler", "-fPIC", "-Xptxas", "-v" if verbose else "-O3"]
+    flags += os.environ.get("HSNW_NVCC_FLAGS", "").split()  # e.g. -DHSNW_TRACE for the phase timestamps
     jobs = []
     for name in SOURCES:
         obj = LIB_DIR / (Path(name).stem + ".o")

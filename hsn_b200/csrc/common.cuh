@@ -104,6 +104,37 @@ __device__ __forceinline__ int block_sum_int(int v, uint64_t* scratch) {
     return r;
 }
 
+// sum_i a[i * sa] * b[i * sb], i < n, with four independent accumulators and eight products per
+// round, every operand of a round loaded before the first product: a single chain of dependent
+// multiply-adds would wait for each load in turn. The order of the sum is fixed.
+__device__ __forceinline__ float dot4(const float* a, int sa, const float* b, int sb, int n) {
+    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+    int i = 0;
+    for (; i + 8 <= n; i += 8) {
+        const float* pa = a + i * sa;
+        const float* pb = b + i * sb;
+        const float a0 = pa[0], a1 = pa[sa], a2 = pa[2 * sa], a3 = pa[3 * sa];
+        const float a4 = pa[4 * sa], a5 = pa[5 * sa], a6 = pa[6 * sa], a7 = pa[7 * sa];
+        const float b0 = pb[0], b1 = pb[sb], b2 = pb[2 * sb], b3 = pb[3 * sb];
+        const float b4 = pb[4 * sb], b5 = pb[5 * sb], b6 = pb[6 * sb], b7 = pb[7 * sb];
+        s0 += a0 * b0; s1 += a1 * b1; s2 += a2 * b2; s3 += a3 * b3;
+        s0 += a4 * b4; s1 += a5 * b5; s2 += a6 * b6; s3 += a7 * b7;
+    }
+    for (; i < n; ++i) s0 += a[i * sa] * b[i * sb];
+    return (s0 + s1) + (s2 + s3);
+}
+// sum_i a[i * sa], i < n, the same way.
+__device__ __forceinline__ float sum4(const float* a, int64_t sa, int n) {
+    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+    int i = 0;
+    for (; i + 4 <= n; i += 4) {
+        const float a0 = a[i * sa], a1 = a[(i + 1) * sa], a2 = a[(i + 2) * sa], a3 = a[(i + 3) * sa];
+        s0 += a0; s1 += a1; s2 += a2; s3 += a3;
+    }
+    for (; i < n; ++i) s0 += a[i * sa];
+    return (s0 + s1) + (s2 + s3);
+}
+
 // dst[0..n) = src[0..n) floats by the whole block; 16-byte transfers when both are aligned and
 // n is a multiple of 4.
 __device__ __forceinline__ void block_copy_f32(float* dst, const float* src, int n) {

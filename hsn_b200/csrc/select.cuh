@@ -147,4 +147,123 @@ __device__ __forceinline__ void select_row(const SelectParams& P, const float* s
     __syncthreads();
 }
 
+// The same decision by ONE warp (no reserved cells), for rows of up to a few thousand cells: the
+// whole selection then needs no block barrier. Lane l owns the cells l, l + 32, ...; it keeps its
+// best remaining key, the warp takes the maximum with two redux instructions (the score half,
+// then the index half among the lanes that hold that score), and only the winner's lane rescans
+// its cells. Called by every lane of one warp; the other warps wait at the caller's barrier.
+__device__ __forceinline__ uint64_t warp_argmax_key(uint64_t mine) {
+    const uint32_t hi = __reduce_max_sync(0xffffffffu, static_cast<uint32_t>(mine >> 32));
+    const uint32_t lo = __reduce_max_sync(0xffffffffu, static_cast<uint32_t>(mine >> 32) == hi ? static_cast<uint32_t>(mine) : 0u);
+    return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+
+__device__ __forceinline__ void select_row_warp(const SelectParams& P, const float* score, const int* unit,
+                                                const int64_t* age_row, SelectShared& S) {
+    const int lane = threadIdx.x & 31;
+    const int N = P.N, K = P.K;
+    // the scored decision: K + 1 rounds (the extra one is the highest unselected score)
+    uint64_t mine = 0ull;
+    for (int i = lane; i < N; i += 32) {
+        const uint64_t key = pack_key(score[i], i);
+        mine = key > mine ? key : mine;
+    }
+    uint64_t next_key = 0ull;
+    for (int r = 0; r <= K; ++r) {
+        const uint64_t win = warp_argmax_key(mine);
+        if (r < K) {
+            if (lane == 0) S.order[r] = win ? key_cell(win) : 0;
+        } else {
+            next_key = win;
+        }
+        if (win && (key_cell(win) & 31) == lane) {  // the winner's lane moves on to its next best
+            uint64_t best = 0ull;
+            for (int i = lane; i < N; i += 32) {
+                const uint64_t key = pack_key(score[i], i);
+                if (key < win && key > best) best = key;
+            }
+            mine = best;
+        }
+    }
+    __syncwarp();
+    int n_valid = 0;
+    if (lane == 0) {
+        float cumulative = 0.0f;
+        for (int k = 0; k < K; ++k) {
+            const int c = S.order[k];
+            const int u = unit[c];
+            cumulative += P.overhead + S.cost[u];
+            const bool ok = P.shared_cost + cumulative <= P.limit;
+            S.out_cell[k] = ok ? c : 0;
+            S.out_unit[k] = ok ? u : 0;
+            S.out_flag[k] = ok ? 1 : 0;
+            n_valid += ok ? 1 : 0;
+        }
+        S.n_valid = n_valid;
+    }
+    n_valid = __shfl_sync(0xffffffffu, n_valid, 0);
+    __syncwarp();
+    const bool any = n_valid > 0;
+    const int last = any ? S.order[n_valid - 1] : 0;
+    const uint64_t in_key = any ? pack_key(score[last], last) : ~0ull;
+    // the highest unselected score: the first slot the budget cut, else the (K + 1)-th best
+    float high;
+    if (n_valid < K) high = score[S.order[n_valid]];
+    else high = next_key ? score[key_cell(next_key)] : -INFINITY;
+    if (lane == 0) S.theta = 0.5f * ((any ? score[last] : INFINITY) + high);
+    if (P.probes) {
+        int stale = 0;
+        uint64_t oldest = 0ull;
+        for (int i = lane; i < N; i += 32) {
+            const bool chosen = any && pack_key(score[i], i) >= in_key;
+            const int64_t ag = age_row[i];
+            if (!chosen && ag > static_cast<int64_t>(P.age_max)) {
+                ++stale;
+                const uint64_t key = pack_key(static_cast<float>(ag), i);
+                oldest = key > oldest ? key : oldest;
+            }
+        }
+        const int n_stale = __reduce_add_sync(0xffffffffu, stale);
+        const int n_force = n_stale < n_valid ? n_stale : n_valid;
+        for (int j = 0; j < n_force; ++j) {
+            const uint64_t win = warp_argmax_key(oldest);
+            const int pick = key_cell(win);
+            if (lane == 0) {
+                const int k = n_valid - 1 - j;
+                S.out_cell[k] = pick;
+                S.out_unit[k] = unit[pick];
+                S.out_flag[k] |= 2;
+            }
+            if ((pick & 31) == lane) {
+                uint64_t best = 0ull;
+                for (int i = lane; i < N; i += 32) {
+                    const bool chosen = any && pack_key(score[i], i) >= in_key;
+                    const int64_t ag = age_row[i];
+                    if (!chosen && ag > static_cast<int64_t>(P.age_max)) {
+                        const uint64_t key = pack_key(static_cast<float>(ag), i);
+                        if (key < win && key > best) best = key;
+                    }
+                }
+                oldest = best;
+            }
+        }
+        __syncwarp();
+        if (lane == 0 && n_force > 0) {
+            float spent = 0.0f;
+            for (int k = 0; k < K; ++k)
+                spent += (S.out_flag[k] & 1) ? P.overhead + S.cost[S.out_unit[k]] : 0.0f;
+            if (P.shared_cost + spent > P.limit) {
+                for (int k = 0; k < K; ++k) {
+                    const bool ok = (S.out_flag[k] & 1) != 0;
+                    const int c = S.order[k];
+                    S.out_cell[k] = ok ? c : 0;
+                    S.out_unit[k] = ok ? unit[c] : 0;
+                    S.out_flag[k] &= 1;
+                }
+            }
+        }
+    }
+    __syncwarp();
+}
+
 }  // namespace hsnw

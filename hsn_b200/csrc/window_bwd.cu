@@ -151,9 +151,7 @@ __device__ __forceinline__ void head_phase(const BwdCtx& c, int t, unsigned char
     // d_unit = dy W_out (the transposed output projection): y[x] = sum_i F[i] wout_t[i][x]
     for (int e = tid; e < K * d; e += nt) {
         const int k = e / d, i = e - k * d;
-        float sum = 0.0f;
-        for (int x = 0; x < d; ++x) sum += dzs[k * d + x] * wo[i * (d + 1) + x];
-        c.d_unit[(static_cast<int64_t>(row) * K + k) * d + i] = sum;
+        c.d_unit[(static_cast<int64_t>(row) * K + k) * d + i] = dot4(dzs + k * d, 1, wo + i * (d + 1), 1, d);
     }
     for (int k = tid; k < K; k += nt)
         c.pair_unit[static_cast<int64_t>(row) * K + k] = cell_of[k] >= 0 ? static_cast<int>(c.io.units[rt * K + k]) : -1;
@@ -218,9 +216,8 @@ __global__ void __launch_bounds__(256) k_mid(BwdCtx c, int t) {
             __syncthreads();
             for (int e = tid; e < nb * two; e += 256) {
                 const int pb = e / two, i = e - pb * two;
-                float sum = 0.0f;
-                for (int x = 0; x < d; ++x) sum += du[pb * d + x] * wA[i * (d + 1) + x];
-                c.part_dv[(static_cast<int64_t>(c.nU) * P + list[base + pb]) * two + i] = sum;
+                c.part_dv[(static_cast<int64_t>(c.nU) * P + list[base + pb]) * two + i] =
+                    dot4(du + pb * d, 1, wA + i * (d + 1), 1, d);
             }
         }
         return;
@@ -250,8 +247,7 @@ __global__ void __launch_bounds__(256) k_mid(BwdCtx c, int t) {
             const int pb = pg * 4 + p;
             float dhid = 0.0f, inner = 0.0f;
             if (pb < nb && cc < cols) {
-                float sum = 0.0f;
-                for (int x = 0; x < d; ++x) sum += du[pb * d + x] * wA[cc * (d + 1) + x];
+                const float sum = dot4(du + pb * d, 1, wA + cc * (d + 1), 1, d);
                 const int pair = list[base + pb];
                 const int row = pair / K, k = pair - row * K;
                 const float hid = c.io.hidden[((static_cast<int64_t>(row) * T + t) * K + k) * H + c0 + cc];
@@ -266,10 +262,8 @@ __global__ void __launch_bounds__(256) k_mid(BwdCtx c, int t) {
         // the transposed first layer on the state columns [h ; m] of the cell input
         for (int e = tid; e < nb * two; e += 256) {
             const int pb = e / two, i = e - pb * two;
-            float sum = 0.0f;
-#pragma unroll 8
-            for (int k2 = 0; k2 < kUS; ++k2) sum += dh[pb * (kUS + 1) + k2] * w1[i * (kUS + 1) + k2];
-            c.part_dv[(static_cast<int64_t>(s) * P + list[base + pb]) * two + i] = sum;
+            c.part_dv[(static_cast<int64_t>(s) * P + list[base + pb]) * two + i] =
+                dot4(dh + pb * (kUS + 1), 1, w1 + i * (kUS + 1), 1, kUS);
         }
     }
 }
@@ -331,8 +325,7 @@ __device__ __forceinline__ void tail_phase(const BwdCtx& c, int t, unsigned char
         const int k = e / two, i = e - k * two;
         float out = 0.0f;
         if (cell_of[k] >= 0) {
-            float dv = 0.0f;
-            for (int s = 0; s <= c.nU; ++s) dv += c.part_dv[(static_cast<int64_t>(s) * P + pair0 + k) * two + i];
+            const float dv = sum4(c.part_dv + (pair0 + k) * two + i, static_cast<int64_t>(P) * two, c.nU + 1);
             const float state = i < d ? c.io.h_old[(rt * K + k) * d + i] : c.io.m[(rt * K + k) * d + i - d];
             out = c.io.rms[rt * K + k] * (c.m.norm_w[two + i] * dv) - back[k] * state;
         }
@@ -347,9 +340,7 @@ __device__ __forceinline__ void tail_phase(const BwdCtx& c, int t, unsigned char
     // dvm = dm V: m = sum_e a_e (V h_src), (V h)[x] = sum_i h[i] v_t[i][x]
     for (int e = tid; e < K * d; e += nt) {
         const int k = e / d, i = e - k * d;
-        float sum = 0.0f;
-        for (int x = 0; x < d; ++x) sum += ds[k * two + d + x] * vt[i * (d + 1) + x];
-        dvm[e] = sum;
+        dvm[e] = dot4(ds + k * two + d, 1, vt + i * (d + 1), 1, d);
     }
     __syncthreads();
     // a thread owns a column: the cells' own cotangents first, then every edge in slot order

@@ -45,6 +45,21 @@ constexpr int kCopyFloats = 4096;  // floats of the state a copy block moves
 constexpr int kInitCells = 32;   // cells of a block of the derived-state kernel
 constexpr int kMaxM = 16;        // units (registers of the scorer's thread)
 
+// Optional phase timestamps for tuning (compiled in with -DHSNW_TRACE): event i of block b of a
+// kernel lands at trace[(kernel * 512 + b) * 16 + i] (nanoseconds of the global timer).
+#ifdef HSNW_TRACE
+#define HSNW_MARK(kernel, i)                                                                     \
+    do {                                                                                         \
+        if (threadIdx.x == 0 && blockIdx.y == 0 && blockIdx.x < 512) {                           \
+            unsigned long long now;                                                              \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));                              \
+            c.trace[((kernel) * 512 + blockIdx.x) * 16 + (i)] = now;                             \
+        }                                                                                        \
+    } while (0)
+#else
+#define HSNW_MARK(kernel, i) do { } while (0)
+#endif
+
 struct FwdCtx {
     HsnwModel m;
     HsnwForward io;
@@ -55,6 +70,7 @@ struct FwdCtx {
     int copy_per_row;
     int stage_cells;    // 1: the row phase stages the per-cell logit parts and scalars in shared memory
     int* status;        // [1] 0, or 1 when a bounded wait ran out
+    unsigned long long* trace;  // phase timestamps (HSNW_TRACE builds)
     float* pre_s;       // [B*T, H]
     float* part_front;  // [B, 2 nF, d]
     float* v;           // [B*K, 4d]
@@ -81,23 +97,17 @@ __device__ __forceinline__ const int64_t* state_age(const FwdCtx& c, int row, in
 }
 __host__ __device__ __forceinline__ int pad4(int n) { return (n + 3) & ~3; }
 
-// The derived state of one cell from its state row hrow [d] (shared memory): thread `lane_x` of a
-// group of nthreads computes outputs lane_x, lane_x + nthreads, ... of [M logit parts | d of V h].
+// The derived state of one cell from its state row hrow [d] (shared memory, already rounded to the
+// products' operand precision): thread `first` of a group of `stride` threads computes outputs
+// first, first + stride, ... of [M logit parts | d of V h].
 __device__ __forceinline__ void derive_outputs(const FwdCtx& c, const float* hrow, const float* swh,
                                                const float* vt, float* lh_out, float* vh_out, int first,
                                                int stride) {
     const int d = c.m.d, M = c.m.M;
     const bool bf = c.m.prod_bf16 != 0;
     for (int o = first; o < M + d; o += stride) {
-        float sum = 0.0f;
-        if (o < M) {
-            for (int x = 0; x < d; ++x) sum += maybe_bf16(hrow[x], bf) * swh[x * M + o];
-            lh_out[o] = sum;
-        } else {
-            const int xo = o - M;
-            for (int i = 0; i < d; ++i) sum += maybe_bf16(hrow[i], bf) * vt[i * d + xo];
-            vh_out[xo] = maybe_bf16(sum, bf);
-        }
+        if (o < M) lh_out[o] = dot4(hrow, 1, swh + o, M, d);
+        else vh_out[o - M] = maybe_bf16(dot4(hrow, 1, vt + (o - M), d, d), bf);
     }
 }
 
@@ -113,8 +123,10 @@ __global__ void __launch_bounds__(256) k_init(FwdCtx c) {
     const int cell0 = blockIdx.y * kInitCells;
     const int ncell = min(kInitCells, N - cell0);
     float* hs = reinterpret_cast<float*>(dyn);
-    float* swh = hs + kInitCells * d;
+    float* hb = hs + kInitCells * d;     // the same rows at the products' operand precision
+    float* swh = hb + kInitCells * d;
     float* vt = swh + d * M;
+    const bool bf = c.m.prod_bf16 != 0;
     const bool cut = c.io.reset[static_cast<int64_t>(row) * T] != 0;
     float* h0 = c.io.h0 + static_cast<int64_t>(row) * N * d;
     if (row == 0 && blockIdx.y == 0 && tid == 0) *c.status = 0;
@@ -123,6 +135,7 @@ __global__ void __launch_bounds__(256) k_init(FwdCtx c) {
     for (int e = tid; e < ncell * d; e += nt) {
         const float v = cut ? 0.0f : h0[static_cast<int64_t>(cell0) * d + e];
         hs[e] = v;
+        hb[e] = maybe_bf16(v, bf);
         if (c.io.tape_state) c.io.tape_h[(static_cast<int64_t>(row) * (T + 1)) * N * d + static_cast<int64_t>(cell0) * d + e] = v;
         else if (cut) h0[static_cast<int64_t>(cell0) * d + e] = 0.0f;
     }
@@ -143,7 +156,7 @@ __global__ void __launch_bounds__(256) k_init(FwdCtx c) {
     const int cl = tid >> 3, sub = tid & 7;
     if (cl < ncell) {
         const int64_t cell = static_cast<int64_t>(row) * N + cell0 + cl;
-        derive_outputs(c, hs + cl * d, swh, vt, c.lh + cell * M, c.vh + cell * d, sub, 8);
+        derive_outputs(c, hb + cl * d, swh, vt, c.lh + cell * M, c.vh + cell * d, sub, 8);
         if (sub == 0) {
             int top = 0;
             for (int x = 0; x < d; ++x) top = max(top, __float_as_int(fabsf(hs[cl * d + x])));
@@ -412,6 +425,7 @@ __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
     float* rms = ew + pad4(K * D);
     const int64_t rt = static_cast<int64_t>(row) * T + t;
     const float* h = state_h(c, row, t);
+    HSNW_MARK(2, 0);
     if (tid == 0) mbar_init(&bar, 1);
     __syncthreads();
     // staging 1
@@ -455,22 +469,24 @@ __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
         mbar_wait(&bar, 0, c.status);
     }
     __syncthreads();
+    HSNW_MARK(2, 1);
     // (u, z_hat) from the front's partial sums, slice by slice; eps = z - z_hat
     for (int x = tid; x < 2 * d; x += nt) {
         const bool is_p = x >= d;
         const int xx = is_p ? x - d : x;
-        float sum = 0.0f;
-        for (int s = 0; s < c.nF; ++s) sum += pf[((is_p ? c.nF : 0) + s) * d + xx];
+        const float sum = sum4(pf + (is_p ? c.nF : 0) * d + xx, d, c.nF);
         const float out = maybe_bf16(sum + c.m.f_b2[x], bf);
         ue[x] = is_p ? c.io.z[rt * d + xx] - out : out;
     }
     __syncthreads();
-    if (tid < M) {
+    for (int j = warp; j < M; j += warps) {  // a warp per unit: lanes stride the 2d inputs
         float sum = 0.0f;
-        for (int x = 0; x < 2 * d; ++x) sum += maybe_bf16(ue[x], bf) * sw_head[x * M + tid];
-        rowterm[tid] = sum;
+        for (int x = lane; x < 2 * d; x += 32) sum += maybe_bf16(ue[x], bf) * sw_head[x * M + j];
+        sum = warp_sum(sum);
+        if (lane == 0) rowterm[j] = sum;
     }
     __syncthreads();
+    HSNW_MARK(2, 2);
     // the scorer: a thread per cell; the state's part of the logits is derived state
     const float* lh = staged ? lh_s : c.lh + static_cast<int64_t>(row) * N * M;
     const float* scal = staged ? scal_s : c.io.scalars + rt * N * Sn;
@@ -514,12 +530,19 @@ __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
     int64_t* cells_o = c.io.cells + rt * K;
     int64_t* units_o = c.io.units + rt * K;
     uint8_t* valid_o = c.io.valid + rt * K;
+    HSNW_MARK(2, 3);
     if (!c.io.forced) {
         SelectParams P;
         P.N = N; P.M = M; P.K = K; P.age_max = c.m.age_max; P.probes = c.m.probes;
         P.reserved = 0; P.fixed_units = 0;
         P.overhead = c.m.cell_overhead; P.shared_cost = c.m.shared_cost; P.limit = c.m.limit;
-        select_row(P, score, unit, age, S);
+        if (N <= 2048) {  // one warp decides; the others wait at the barrier
+            if (warp == 0) select_row_warp(P, score, unit, age, S);
+            __syncthreads();
+        } else {
+            select_row(P, score, unit, age, S);
+        }
+        HSNW_MARK(2, 4);
         for (int k = tid; k < K; k += nt) {
             cells_o[k] = S.out_cell[k];
             units_o[k] = S.out_unit[k];
@@ -560,6 +583,7 @@ __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
         for (int w = 0; w < warps; ++w) mx = max(mx, ired[w]);
         c.hmax_part[row] = mx;
     }
+    HSNW_MARK(2, 5);
     // staging 2: the selected cells' state rows and their sources' V h rows, one bulk copy a row
     {
         const float* g_vh = c.vh + static_cast<int64_t>(row) * N * d;
@@ -584,6 +608,7 @@ __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
         }
     }
     __syncthreads();
+    HSNW_MARK(2, 6);
     for (int e = tid; e < K * d; e += nt) {
         const int k = e / d, x = e - k * d;
         float sum = 0.0f;
@@ -618,6 +643,7 @@ __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
         }
         for (int k = tid; k < K; k += nt) c.io.rec_rms[rt * K + k] = rms[k];
     }
+    HSNW_MARK(2, 7);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -751,7 +777,9 @@ __global__ void __launch_bounds__(256) k_unit(FwdCtx c, int t) {
 // 256 threads: warp w reads TMEM lanes 32 (w % 4) .. +31 and the pairs 16 (w / 4) .. +15.
 // Shared (dynamic): A1 [4d/8][128][8], A2 [16][128][8], B1 [4d/8][32][8], B2 [16][32][8] bf16, list.
 // ------------------------------------------------------------------------------------------------
-constexpr int kTP = 32;  // pairs of a tensor-core batch
+constexpr int kTP = 32;       // pairs of a tensor-core batch
+constexpr int kTcPairTile = 64;  // pairs a tensor-core unit block scans: small tiles keep a popular
+                                 // unit's pairs spread over several blocks
 
 __global__ void __launch_bounds__(256) k_unit_tc(FwdCtx c, int t) {
     extern __shared__ __align__(16) unsigned char dyn[];
@@ -770,11 +798,12 @@ __global__ void __launch_bounds__(256) k_unit_tc(FwdCtx c, int t) {
     uint4* A2 = A1 + planes * 128;                             // [16][128]
     uint4* B1 = A2 + 16 * 128;                                 // [planes][32]
     uint4* B2 = B1 + planes * kTP;                             // [16][32]
-    int* list = reinterpret_cast<int*>(B2 + 16 * kTP);         // [256]
-    const int p0 = blockIdx.y * kPairTile;
+    int* list = reinterpret_cast<int*>(B2 + 16 * kTP);         // [64]
+    const int p0 = blockIdx.y * kTcPairTile;
+    HSNW_MARK(0, 11);
     {
         const int p = p0 + tid;
-        const bool mine = p < P && c.pair_unit[p] == j;
+        const bool mine = tid < kTcPairTile && p < P && c.pair_unit[p] == j;
         const unsigned mask = __ballot_sync(0xffffffffu, mine);
         if (lane == 0) warp_count[warp] = __popc(mask);
         if (tid == 0) {
@@ -793,6 +822,7 @@ __global__ void __launch_bounds__(256) k_unit_tc(FwdCtx c, int t) {
         __syncthreads();
     }
     const int count = n_list;
+    HSNW_MARK(0, 0);
     if (count == 0) return;
     // the weight tiles: one bulk copy each
     if (tid == 0) {
@@ -806,10 +836,13 @@ __global__ void __launch_bounds__(256) k_unit_tc(FwdCtx c, int t) {
             bulk_g2s(A2, static_cast<const unsigned char*>(c.m.umma_w2) + (static_cast<size_t>(j) * nB + cb) * a2_bytes,
                      a2_bytes, &bar_w);
     }
+    HSNW_MARK(0, 8);
     if (warp == 0) tmem_alloc(&tmem_slot, 64);
+    HSNW_MARK(0, 9);
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
+    HSNW_MARK(0, 10);
     const uint32_t taddr = tmem_slot;
     const uint32_t idesc = umma_idesc_bf16(128, kTP);
     const int q = warp & 3, hf = warp >> 2;
@@ -832,10 +865,12 @@ __global__ void __launch_bounds__(256) k_unit_tc(FwdCtx c, int t) {
             B1[idx] = packed;
         }
         fence_async_smem();
+        HSNW_MARK(0, 1);
         if (!weights_in) {
             mbar_wait(&bar_w, 0, c.status);
             weights_in = true;
         }
+        HSNW_MARK(0, 2);
         tcgen05_fence_before();
         __syncthreads();
         if (tid == 0) {
@@ -849,6 +884,7 @@ __global__ void __launch_bounds__(256) k_unit_tc(FwdCtx c, int t) {
         mbar_wait(&bar_m, phase, c.status);
         phase ^= 1u;
         tcgen05_fence_after();
+        HSNW_MARK(0, 3);
         // epilogue 1
         {
             float acc[16];
@@ -883,6 +919,7 @@ __global__ void __launch_bounds__(256) k_unit_tc(FwdCtx c, int t) {
             __syncthreads();
             continue;
         }
+        HSNW_MARK(0, 4);
         fence_async_smem();
         tcgen05_fence_before();
         __syncthreads();
@@ -897,6 +934,7 @@ __global__ void __launch_bounds__(256) k_unit_tc(FwdCtx c, int t) {
         mbar_wait(&bar_m, phase, c.status);
         phase ^= 1u;
         tcgen05_fence_after();
+        HSNW_MARK(0, 5);
         // epilogue 2: lane m is output x of the unit
         {
             float acc[16];
@@ -913,7 +951,9 @@ __global__ void __launch_bounds__(256) k_unit_tc(FwdCtx c, int t) {
         tcgen05_fence_before();
         __syncthreads();
     }
+    HSNW_MARK(0, 6);
     if (warp == 0) tmem_dealloc(taddr, 64);
+    HSNW_MARK(0, 7);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -951,6 +991,7 @@ __global__ void __launch_bounds__(256) k_update(FwdCtx c, int t) {
     const bool last = t + 1 == T;
     const bool clear = !last && c.io.reset[rt + 1] != 0;
     const bool tape = c.io.tape_state != 0;
+    HSNW_MARK(1, 0);
     cp_async_floats(wo, c.m.wout_t, d * d);
     cp_async_floats(vt, c.m.v_t, d * d);
     cp_async_floats(swh, c.m.score_w_t + static_cast<int64_t>(2 * d) * M, d * M);
@@ -966,25 +1007,18 @@ __global__ void __launch_bounds__(256) k_update(FwdCtx c, int t) {
         const int k = e / d, x = e - k * d;
         float sum = 0.0f;
         if (cell_of[k] >= 0) {
-            const float* p = c.part_f + (pair0 + k) * d + x;
-            const int64_t stride = static_cast<int64_t>(P) * d;
-            int s = 0;
-            for (; s + 4 <= c.nU; s += 4) {
-                const float a0 = p[s * stride], a1 = p[(s + 1) * stride], a2 = p[(s + 2) * stride], a3 = p[(s + 3) * stride];
-                sum += a0; sum += a1; sum += a2; sum += a3;
-            }
-            for (; s < c.nU; ++s) sum += p[s * stride];
+            sum = sum4(c.part_f + (pair0 + k) * d + x, static_cast<int64_t>(P) * d, c.nU);
             sum = maybe_bf16(sum + c.m.b2[static_cast<int>(units[k]) * d + x], bf);
         }
         Fs[e] = sum;
     }
+    HSNW_MARK(1, 1);
     cp_async_wait_all();
     __syncthreads();
+    HSNW_MARK(1, 2);
     for (int e = tid; e < K * d; e += nt) {
         const int k = e / d, x = e - k * d;
-        float sum = 0.0f;
-        for (int i = 0; i < d; ++i) sum += Fs[k * d + i] * wo[i * d + x];
-        ys[e] = maybe_bf16(sum, bf);
+        ys[e] = maybe_bf16(dot4(Fs + k * d, 1, wo + x, d, d), bf);
     }
     __syncthreads();
     for (int k = warp; k < K; k += warps) {
@@ -997,6 +1031,7 @@ __global__ void __launch_bounds__(256) k_update(FwdCtx c, int t) {
     float* h_write = tape ? c.io.tape_h + (static_cast<int64_t>(row) * (T + 1) + t + 1) * N * d
                           : c.io.h0 + static_cast<int64_t>(row) * N * d;
     int top = 0;
+    HSNW_MARK(1, 3);
     for (int e = tid; e < K * d; e += nt) {
         const int k = e / d, x = e - k * d;
         const int n = cell_of[k];
@@ -1011,6 +1046,7 @@ __global__ void __launch_bounds__(256) k_update(FwdCtx c, int t) {
             top = max(top, __float_as_int(fabsf(value)));
         }
         hnew[e] = value;
+        Fs[e] = maybe_bf16(value, bf);  // the new state at the products' operand precision (F is spent)
         delta[e] = change;
         if (c.io.rec_c) {
             c.io.rec_c[rt * K * d + e] = cv;
@@ -1025,6 +1061,7 @@ __global__ void __launch_bounds__(256) k_update(FwdCtx c, int t) {
     float* lh_row = c.lh + static_cast<int64_t>(row) * N * M;
     float* vh_row = c.vh + static_cast<int64_t>(row) * N * d;
     int* cmax_row = c.cmax + static_cast<int64_t>(row) * N;
+    HSNW_MARK(1, 4);
     if (!clear) {
         for (int e = tid; e < K * d; e += nt) {
             const int k = e / d, x = e - k * d;
@@ -1034,7 +1071,7 @@ __global__ void __launch_bounds__(256) k_update(FwdCtx c, int t) {
         for (int k = warp; k < K; k += warps) {
             const int n = cell_of[k];
             if (n < 0) continue;
-            derive_outputs(c, hnew + k * d, swh, vt, lh_row + static_cast<int64_t>(n) * M,
+            derive_outputs(c, Fs + k * d, swh, vt, lh_row + static_cast<int64_t>(n) * M,
                            vh_row + static_cast<int64_t>(n) * d, lane, 32);
             int m = 0;
             for (int x = lane; x < d; x += 32) m = max(m, __float_as_int(fabsf(hnew[k * d + x])));
@@ -1050,6 +1087,7 @@ __global__ void __launch_bounds__(256) k_update(FwdCtx c, int t) {
     }
     float* q_next = tape ? c.io.tape_q + (static_cast<int64_t>(row) * (T + 1) + t + 1) * d
                          : c.io.q0 + static_cast<int64_t>(row) * d;
+    HSNW_MARK(1, 5);
     for (int x = tid; x < d; x += nt) {
         float sum = 0.0f;
         for (int k = 0; k < K; ++k) sum += delta[k * d + x];
@@ -1087,6 +1125,7 @@ __global__ void __launch_bounds__(256) k_update(FwdCtx c, int t) {
             c.io.h_max[rt] = __int_as_float(mx);
         }
     }
+    HSNW_MARK(1, 6);
     if (last && tid == 0) {
         // the position counter after the window (reference compile.py:1194-1200)
         int last_reset = 0;
@@ -1106,7 +1145,7 @@ Layout layout(const HsnwModel& m, int B, int T) {
     const int nF = (m.H + kFS - 1) / kFS, nU = (m.H + kUS - 1) / kUS;
     const size_t Bz = static_cast<size_t>(B);
     size_t off = 0;
-    L.status = off; off += 256;
+    L.status = off; off += 256 + 4 * 512 * 16 * sizeof(unsigned long long);  // status word, then the trace area
     L.pre_s = off; off += align_up(sizeof(float) * Bz * T * m.H);
     L.part_front = off; off += align_up(sizeof(float) * 2 * nF * Bz * m.d);
     L.v = off; off += align_up(sizeof(float) * Bz * m.K * 4 * m.d);
@@ -1134,7 +1173,7 @@ size_t row_shared(const HsnwModel& m) {
     return sizeof(float) * words;
 }
 size_t init_shared(const HsnwModel& m) {
-    return sizeof(float) * (static_cast<size_t>(kInitCells) * m.d + static_cast<size_t>(m.d) * m.M + static_cast<size_t>(m.d) * m.d);
+    return sizeof(float) * (static_cast<size_t>(2 * kInitCells) * m.d + static_cast<size_t>(m.d) * m.M + static_cast<size_t>(m.d) * m.d);
 }
 size_t front_shared(const HsnwModel& m) {
     return sizeof(float) * (static_cast<size_t>(2) * m.d * kFS + static_cast<size_t>(kFR) * m.d + kFR * kFS);
@@ -1225,6 +1264,7 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
     c.copy_per_row = io->tape_state ? (model->N * model->d + kCopyFloats - 1) / kCopyFloats : 0;
     unsigned char* base = static_cast<unsigned char*>(io->scratch);
     c.status = reinterpret_cast<int*>(base + L.status);
+    c.trace = reinterpret_cast<unsigned long long*>(base + L.status + 256);
     c.pre_s = reinterpret_cast<float*>(base + L.pre_s);
     c.part_front = reinterpret_cast<float*>(base + L.part_front);
     c.v = reinterpret_cast<float*>(base + L.v);
@@ -1243,7 +1283,8 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
     g_pre_status = nullptr;
     if (rc_pre) return rc_pre;
     const int front_grid = c.n_front + B * c.copy_per_row;
-    const dim3 unit_grid(model->M * (unit_tc ? c.nU + 1 : c.nU + c.nG), (B * model->K + kPairTile - 1) / kPairTile);
+    const int pair_tile = unit_tc ? kTcPairTile : kPairTile;
+    const dim3 unit_grid(model->M * (unit_tc ? c.nU + 1 : c.nU + c.nG), (B * model->K + pair_tile - 1) / pair_tile);
     const size_t sh_front = front_shared(*model), sh_row = row_shared(*model);
     const size_t sh_unit = unit_shared(*model), sh_update = update_shared(*model), sh_unit_tc = unit_tc_shared(*model);
     for (int t = 0; t < T; ++t) {
