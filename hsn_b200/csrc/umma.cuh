@@ -41,13 +41,17 @@ __device__ __forceinline__ uint64_t umma_desc(const void* smem_tile, int rows) {
 }
 
 // TMEM: `columns` is a power of two >= 32. Executed by one whole warp; the base address lands in
-// *slot (shared memory).
+// *slot (shared memory). Every .sync.aligned instruction here is preceded by __syncwarp(): a warp
+// that left a polling loop or a single-thread branch is not necessarily converged, and an aligned
+// instruction run by a diverged warp returned the rows of the wrong lanes.
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t columns) {
+    __syncwarp();
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(slot)), "r"(columns)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
 }
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t columns) {
+    __syncwarp();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(columns) : "memory");
 }
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
@@ -67,6 +71,19 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
         "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc)
         : "memory");
 }
+// A chain of `steps` K = 16 products into one accumulator: D = sum_s A_s B_s^T, the descriptors
+// advancing by a_step / b_step (16-byte units) per product. Issued by ONE thread. Deliberately out
+// of line: the sequence is compiled once, on its own, and is the same machine code in every kernel
+// that uses it. Inlined into the reverse sweep's kernel, this loop gave accumulators whose rows
+// repeated with period 8 (as if the A tile's row stride were zero) or not, depending on unrelated
+// code elsewhere in the kernel; out of line it does not.
+static __device__ __noinline__ void umma_chain(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, int steps,
+                                               uint32_t a_step, uint32_t b_step) {
+    for (int s = 0; s < steps; ++s)
+        umma_bf16(tmem_d, desc_a + static_cast<uint64_t>(s) * a_step, desc_b + static_cast<uint64_t>(s) * b_step, idesc, s > 0);
+}
+// The step between two K = 16 products of a tile of `rows` rows in the layout above.
+__host__ __device__ constexpr uint32_t umma_kstep(int rows) { return static_cast<uint32_t>((2 * rows * 16) >> 4); }
 // All MMAs issued so far by this thread arrive on `bar` when they have completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(bar)) : "memory");
@@ -74,13 +91,29 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 // Eight consecutive fp32 columns of this thread's TMEM lane (lane = 32 * (warp % 4) + lane id).
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float out[8]) {
     uint32_t r[8];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr)
-                 : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+    __syncwarp();  // .sync.aligned: the warp must be converged (it may come out of a polling loop)
+    // The load and its wait are ONE asm statement: the registers are defined only after the wait,
+    // so the compiler cannot schedule a use of them between the two instructions.
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n"
+        "tcgen05.wait::ld.sync.aligned;\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+        : "r"(taddr)
+        : "memory");
 #pragma unroll
     for (int i = 0; i < 8; ++i) out[i] = __uint_as_float(r[i]);
+}
+// True in exactly one lane of a converged warp (the issuing lane of single-thread instructions).
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n"
+        ".reg .pred P;\n"
+        "elect.sync _|P, 0xffffffff;\n"
+        "selp.u32 %0, 1, 0, P;\n"
+        "}\n"
+        : "=r"(pred));
+    return pred != 0;
 }
 __device__ __forceinline__ uint32_t tmem_addr(uint32_t base, int lane, int column) {
     return base + (static_cast<uint32_t>(lane) << 16) + static_cast<uint32_t>(column);

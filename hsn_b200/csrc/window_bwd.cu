@@ -21,6 +21,8 @@
 #include "../../include/hsn_window_b200.h"
 #include "common.cuh"
 #include "host_util.h"
+#include "stage.cuh"
+#include "umma.cuh"
 
 #include <mutex>
 #include <stdio.h>
@@ -171,6 +173,7 @@ __global__ void __launch_bounds__(256) k_mid(BwdCtx c, int t) {
     const int d = c.m.d, K = c.m.K, H = c.m.H, in = 4 * c.m.d, two = 2 * c.m.d;
     const int P = c.io.B * K, T = c.io.T;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bool bf = c.m.prod_bf16 != 0;  // the products' operands are rounded as on the tensor cores
     const int per_unit = c.nU + 1;
     const int j = blockIdx.x / per_unit, s = blockIdx.x - j * per_unit;
     const bool is_gate = s == c.nU;
@@ -211,7 +214,7 @@ __global__ void __launch_bounds__(256) k_mid(BwdCtx c, int t) {
             __syncthreads();
             for (int e = tid; e < nb * d; e += 256) {
                 const int pb = e / d, x = e - pb * d;
-                du[e] = c.dg[static_cast<int64_t>(list[base + pb]) * d + x];
+                du[e] = maybe_bf16(c.dg[static_cast<int64_t>(list[base + pb]) * d + x], bf);
             }
             __syncthreads();
             for (int e = tid; e < nb * two; e += 256) {
@@ -238,7 +241,7 @@ __global__ void __launch_bounds__(256) k_mid(BwdCtx c, int t) {
         __syncthreads();
         for (int e = tid; e < nb * d; e += 256) {
             const int pb = e / d, x = e - pb * d;
-            du[e] = c.d_unit[static_cast<int64_t>(list[base + pb]) * d + x];
+            du[e] = maybe_bf16(c.d_unit[static_cast<int64_t>(list[base + pb]) * d + x], bf);
         }
         __syncthreads();
         // the transposed second layer, the activation's derivative, the inner product's share
@@ -251,7 +254,7 @@ __global__ void __launch_bounds__(256) k_mid(BwdCtx c, int t) {
                 const int pair = list[base + pb];
                 const int row = pair / K, k = pair - row * K;
                 const float hid = c.io.hidden[((static_cast<int64_t>(row) * T + t) * K + k) * H + c0 + cc];
-                dhid = sum * gelu_erf_grad(hid);
+                dhid = maybe_bf16(sum * gelu_erf_grad(hid), bf);
                 inner = dhid * (hid - c.m.b1[j * H + c0 + cc]);
             }
             dh[pb * (kUS + 1) + cc] = dhid;
@@ -266,6 +269,216 @@ __global__ void __launch_bounds__(256) k_mid(BwdCtx c, int t) {
                 dot4(dh + pb * (kUS + 1), 1, w1 + i * (kUS + 1), 1, kUS);
         }
     }
+}
+
+// ------------------------------------------------------------------------------------------------
+// mid on the tensor cores (bf16 products). blockIdx.x = (unit j, block cb): blocks 0 .. nB-1 are 128
+// hidden columns of unit j, block nB is the gate's transposed linear; blockIdx.y = tile of 64 pairs.
+// Per batch of 32 pairs:
+//   D1 [128 hidden columns, 32 pairs] = W2 tile [128, d] x d_unit [32, d]^T
+//   epilogue 1: times the activation's derivative at the recorded pre-activation, the block's
+//               share of the cell norm's inner product, dhid as the bf16 operand of the next product
+//   D2 [2d state columns (tiles of 128), 32 pairs] = W1 state tile [128, 128] x dhid [32, 128]^T
+//   epilogue 2: the block's partial sum of dv.
+// 256 threads: warp w reads TMEM lanes 32 (w % 4) .. +31 and the pairs 16 (w / 4) .. +15.
+// Shared (dynamic): A3 [d/8][128][8], A4 [nT][16][128][8], B1 [d/8][32][8], B2 [16][32][8] bf16,
+// sig [8][16] f32, list [64].
+// ------------------------------------------------------------------------------------------------
+constexpr int kTP = 32;
+constexpr int kTcPairTile = 64;
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    return static_cast<uint32_t>(bf16_bits(lo)) | (static_cast<uint32_t>(bf16_bits(hi)) << 16);
+}
+
+__global__ void __launch_bounds__(256) k_mid_tc(BwdCtx c, int t) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    __shared__ int warp_count[8];
+    __shared__ int n_list;
+    __shared__ __align__(8) uint64_t bar_w, bar_m;
+    __shared__ uint32_t tmem_slot;
+    const int d = c.m.d, K = c.m.K, H = c.m.H, two = 2 * c.m.d, dplanes = c.m.d >> 3;
+    const int P = c.io.B * K, T = c.io.T;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nB = c.nU, nT = (two + 127) / 128;
+    const int j = blockIdx.x / (nB + 1), cb = blockIdx.x - j * (nB + 1);
+    const bool is_gate = cb == nB;
+    const int c0 = cb * 128;
+    uint4* A3 = reinterpret_cast<uint4*>(dyn);                  // [d/8][128] (gate: [nT][d/8][128])
+    uint4* A4 = A3 + (is_gate ? nT : 1) * dplanes * 128;       // [nT][16][128]
+    uint4* B1 = A4 + (is_gate ? 0 : nT * 16 * 128);            // [d/8][32]
+    uint4* B2 = B1 + dplanes * kTP;                            // [16][32]
+    float* sig = reinterpret_cast<float*>(B2 + 16 * kTP);      // [8 warps][16 pairs]
+    int* list = reinterpret_cast<int*>(sig + 8 * 16);          // [64]
+    const int p0 = blockIdx.y * kTcPairTile;
+    {
+        const int p = p0 + tid;
+        const bool mine = tid < kTcPairTile && p < P && c.pair_unit[p] == j;
+        const unsigned mask = __ballot_sync(0xffffffffu, mine);
+        if (lane == 0) warp_count[warp] = __popc(mask);
+        if (tid == 0) {
+            mbar_init(&bar_w, 1);
+            mbar_init(&bar_m, 1);
+        }
+        __syncthreads();
+        int before = 0;
+        for (int w = 0; w < warp; ++w) before += warp_count[w];
+        if (mine) list[before + __popc(mask & ((1u << lane) - 1u))] = p;
+        if (tid == 0) {
+            int total = 0;
+            for (int w = 0; w < 8; ++w) total += warp_count[w];
+            n_list = total;
+        }
+        __syncthreads();
+    }
+    const int count = n_list;
+    if (count == 0) return;
+    if (tid == 0) {
+        const uint32_t a3_bytes = static_cast<uint32_t>(dplanes) * 128 * 16, a4_bytes = static_cast<uint32_t>(nT) * 16 * 128 * 16;
+        if (is_gate) {
+            mbar_expect_tx(&bar_w, a3_bytes * nT);
+            bulk_g2s(A3, c.m.umma_bw_gate, a3_bytes * nT, &bar_w);
+        } else {
+            const size_t blk = static_cast<size_t>(j) * nB + cb;
+            mbar_expect_tx(&bar_w, a3_bytes + a4_bytes);
+            bulk_g2s(A3, static_cast<const unsigned char*>(c.m.umma_bw_w2) + blk * a3_bytes, a3_bytes, &bar_w);
+            bulk_g2s(A4, static_cast<const unsigned char*>(c.m.umma_bw_w1) + blk * a4_bytes, a4_bytes, &bar_w);
+        }
+    }
+    if (warp == 0) tmem_alloc(&tmem_slot, 128);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t taddr = tmem_slot;
+    const uint32_t idesc = umma_idesc_bf16(128, kTP);
+    const int q = warp & 3, hf = warp >> 2;
+    const int m = q * 32 + lane;
+    uint32_t phase = 0;
+    bool weights_in = false;
+    const float* operand = is_gate ? c.dg : c.d_unit;
+    for (int base = 0; base < count; base += kTP) {
+        const int nb = min(kTP, count - base);
+        for (int idx = tid; idx < dplanes * kTP; idx += 256) {
+            const int n = idx & (kTP - 1), kc = idx >> 5;
+            uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+            if (n < nb) {
+                const float4* src = reinterpret_cast<const float4*>(operand + static_cast<int64_t>(list[base + n]) * d) + kc * 2;
+                const float4 lo = src[0], hi = src[1];
+                packed = make_uint4(pack_bf16x2(lo.x, lo.y), pack_bf16x2(lo.z, lo.w), pack_bf16x2(hi.x, hi.y),
+                                    pack_bf16x2(hi.z, hi.w));
+            }
+            B1[idx] = packed;
+        }
+        fence_async_smem();
+        if (!weights_in) {
+            mbar_wait(&bar_w, 0, nullptr);
+            weights_in = true;
+        }
+        tcgen05_fence_before();
+        __syncthreads();
+        if (is_gate) {
+            // dv's gate part: [2d state columns, pairs] = gate tile [128, d] x dg [32, d]^T
+            if (tid == 0) {
+                tcgen05_fence_after();
+                const uint64_t db = umma_desc(B1, kTP);
+                for (int tl = 0; tl < nT; ++tl) {
+                    const uint64_t da = umma_desc(A3 + tl * dplanes * 128, 128);
+                    umma_chain(taddr + tl * kTP, da, db, idesc, d >> 4, umma_kstep(128), umma_kstep(kTP));
+                }
+                umma_commit(&bar_m);
+            }
+            mbar_wait(&bar_m, phase, nullptr);
+            phase ^= 1u;
+            tcgen05_fence_after();
+            for (int tl = 0; tl < nT; ++tl) {
+                float acc[16];
+                tmem_ld8(tmem_addr(taddr, q * 32, tl * kTP + hf * 16), acc);
+                tmem_ld8(tmem_addr(taddr, q * 32, tl * kTP + hf * 16 + 8), acc + 8);
+                const int i = tl * 128 + m;
+                if (i < two) {
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        const int n = hf * 16 + e;
+                        if (n < nb) c.part_dv[(static_cast<int64_t>(nB) * P + list[base + n]) * two + i] = acc[e];
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncthreads();
+            continue;
+        }
+        if (tid == 0) {
+            tcgen05_fence_after();
+            const uint64_t da = umma_desc(A3, 128), db = umma_desc(B1, kTP);
+            umma_chain(taddr, da, db, idesc, d >> 4, umma_kstep(128), umma_kstep(kTP));
+            umma_commit(&bar_m);
+        }
+        mbar_wait(&bar_m, phase, nullptr);
+        phase ^= 1u;
+        tcgen05_fence_after();
+        // epilogue 1: lane m is hidden column c0 + m
+        {
+            float acc[16];
+            tmem_ld8(tmem_addr(taddr, q * 32, hf * 16), acc);
+            tmem_ld8(tmem_addr(taddr, q * 32, hf * 16 + 8), acc + 8);
+            const bool col_ok = c0 + m < H;
+            const float b1v = col_ok ? c.m.b1[j * H + c0 + m] : 0.0f;
+            uint16_t* b2_half = reinterpret_cast<uint16_t*>(B2);
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+                const int n = hf * 16 + e;
+                float dhid = 0.0f, inner = 0.0f;
+                if (n < nb && col_ok) {
+                    const int pair = list[base + n];
+                    const int row = pair / K, k = pair - row * K;
+                    const float hid = c.io.hidden[((static_cast<int64_t>(row) * T + t) * K + k) * H + c0 + m];
+                    dhid = bf16r(acc[e] * gelu_erf_grad(hid));
+                    inner = dhid * (hid - b1v);
+                }
+                b2_half[((m >> 3) * kTP + n) * 8 + (m & 7)] = bf16_bits(dhid);
+                inner = warp_sum(inner);
+                if (lane == 0) sig[warp * 16 + e] = inner;
+            }
+        }
+        fence_async_smem();
+        tcgen05_fence_before();
+        __syncthreads();
+        // the block's share of the inner product: the four lane quarters in order
+        if (tid < kTP && tid < nb) {
+            const int hf2 = tid >> 4, e = tid & 15;
+            float total = 0.0f;
+            for (int qq = 0; qq < 4; ++qq) total += sig[(hf2 * 4 + qq) * 16 + e];
+            c.part_sig[static_cast<int64_t>(cb) * P + list[base + tid]] = total;
+        }
+        if (tid == 0) {
+            tcgen05_fence_after();
+            const uint64_t db = umma_desc(B2, kTP);
+            for (int tl = 0; tl < nT; ++tl) {
+                const uint64_t da = umma_desc(A4 + tl * 16 * 128, 128);
+                umma_chain(taddr + kTP + tl * kTP, da, db, idesc, 8, umma_kstep(128), umma_kstep(kTP));
+            }
+            umma_commit(&bar_m);
+        }
+        mbar_wait(&bar_m, phase, nullptr);
+        phase ^= 1u;
+        tcgen05_fence_after();
+        for (int tl = 0; tl < nT; ++tl) {
+            float acc[16];
+            tmem_ld8(tmem_addr(taddr, q * 32, kTP + tl * kTP + hf * 16), acc);
+            tmem_ld8(tmem_addr(taddr, q * 32, kTP + tl * kTP + hf * 16 + 8), acc + 8);
+            const int i = tl * 128 + m;
+            if (i < two) {
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    const int n = hf * 16 + e;
+                    if (n < nb) c.part_dv[(static_cast<int64_t>(cb) * P + list[base + n]) * two + i] = acc[e];
+                }
+            }
+        }
+        tcgen05_fence_before();
+        __syncthreads();
+    }
+    if (warp == 0) tmem_dealloc(taddr, 128);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -408,6 +621,11 @@ size_t mid_shared(const HsnwModel& m) {
     const size_t wa = (2 * d > static_cast<size_t>(kUS) ? 2 * d : kUS) * (d + 1);
     return sizeof(float) * (kPB * d + wa + 2 * d * (kUS + 1) + kPB * (kUS + 1) + kPairTile);
 }
+size_t mid_tc_shared(const HsnwModel& m) {
+    const size_t dplanes = m.d / 8, nT = (2 * static_cast<size_t>(m.d) + 127) / 128;
+    const size_t a = nT * dplanes * 128 > dplanes * 128 + nT * 16 * 128 ? nT * dplanes * 128 : dplanes * 128 + nT * 16 * 128;
+    return 16 * (a + dplanes * kTP + 16 * kTP) + sizeof(float) * 8 * 16 + sizeof(int) * kTcPairTile;
+}
 size_t tail_shared(const HsnwModel& m) {
     const size_t d = m.d, K = m.K, U = K + K * m.D;
     return sizeof(float) * (U * d + 3 * K * d + d * (d + 1) + 2 * K + 2 * U + K * m.D);
@@ -446,7 +664,9 @@ extern "C" int hsnw_window_backward(const HsnwModel* model, const HsnwBackward* 
     BwdCtx c;
     c.m = m;
     c.io = *io;
-    c.nU = (m.H + kUS - 1) / kUS;
+    const bool mid_tc = !full && m.prod_bf16 && m.umma_bw_w2 && m.umma_bw_w1 && m.umma_bw_gate && m.d % 16 == 0
+        && m.d <= 128 && mid_tc_shared(m) <= cap;
+    c.nU = mid_tc ? (m.H + 127) / 128 : (m.H + kUS - 1) / kUS;
     unsigned char* base = static_cast<unsigned char*>(io->scratch);
     c.d_unit = full ? nullptr : reinterpret_cast<float*>(base + L.d_unit);
     c.dg = full ? nullptr : reinterpret_cast<float*>(base + L.dg);
@@ -455,7 +675,9 @@ extern "C" int hsnw_window_backward(const HsnwModel* model, const HsnwBackward* 
     c.part_sig = full ? nullptr : reinterpret_cast<float*>(base + L.part_sig);
     c.pair_unit = full ? nullptr : reinterpret_cast<int*>(base + L.pair_unit);
     const int B = io->B, T = io->T;
-    const dim3 mid_grid(m.M * (c.nU + 1), (B * m.K + kPairTile - 1) / kPairTile);
+    const int pair_tile = mid_tc ? kTcPairTile : kPairTile;
+    const dim3 mid_grid(m.M * (c.nU + 1), (B * m.K + pair_tile - 1) / pair_tile);
+    const size_t sh_mid_tc = mid_tc_shared(m);
     if (full) {
         for (int t = T - 1; t >= 0; --t) k_head<<<B, 256, sh_head, stream>>>(c, t);
         return hsnw_check_launch("window_backward");
@@ -463,7 +685,8 @@ extern "C" int hsnw_window_backward(const HsnwModel* model, const HsnwBackward* 
     // head(T-1) | mid(T-1) | tail(T-1) + head(T-2) | mid(T-2) | ... | tail(0)
     k_head<<<B, 256, sh_head, stream>>>(c, T - 1);
     for (int t = T - 1; t >= 0; --t) {
-        k_mid<<<mid_grid, 256, sh_mid, stream>>>(c, t);
+        if (mid_tc) k_mid_tc<<<mid_grid, 256, sh_mid_tc, stream>>>(c, t);
+        else k_mid<<<mid_grid, 256, sh_mid, stream>>>(c, t);
         k_tail_head<<<B, 256, sh_both, stream>>>(c, t);
         if (int rc = hsnw_check_launch("window_backward")) return rc;
     }
@@ -530,6 +753,7 @@ extern "C" int hsnw_window_backward_static(const HsnwModel* model, const HsnwBac
 void hsnw_backward_set_attributes() {
     const struct { const void* f; const char* n; } ks[] = {
         {reinterpret_cast<const void*>(k_head), "head"}, {reinterpret_cast<const void*>(k_mid), "mid"},
+        {reinterpret_cast<const void*>(k_mid_tc), "mid_tc"},
         {reinterpret_cast<const void*>(k_tail_head), "tail_head"}};
     for (const auto& k : ks)
         if (!hsnw_opt_in(k.f, k.n)) hsnw_attribute_failed();

@@ -268,10 +268,7 @@ __global__ void __launch_bounds__(128) k_pre_tc(HsnwModel m, const float* z, con
     if (tid == 0) {
         const uint32_t idesc = umma_idesc_bf16(128, 128);
         const uint64_t da = umma_desc(As, 128), db = umma_desc(Bs, 128);
-        for (int s = 0; s < (Kp >> 4); ++s) {
-            const uint64_t step = static_cast<uint64_t>(s) * ((2 * 128 * 16) >> 4);  // two planes per K = 16
-            umma_bf16(taddr, da + step, db + step, idesc, s > 0);
-        }
+        umma_chain(taddr, da, db, idesc, Kp >> 4, umma_kstep(128), umma_kstep(128));  // two planes per K = 16
         umma_commit(&bar);
     }
     mbar_wait(&bar, 0, status);
@@ -876,9 +873,7 @@ __global__ void __launch_bounds__(256) k_unit_tc(FwdCtx c, int t) {
         if (tid == 0) {
             tcgen05_fence_after();
             const uint64_t da = umma_desc(A1, 128), db = umma_desc(B1, kTP);
-            for (int s = 0; s < (in >> 4); ++s)
-                umma_bf16(taddr, da + static_cast<uint64_t>(s) * ((2 * 128 * 16) >> 4),
-                          db + static_cast<uint64_t>(s) * ((2 * kTP * 16) >> 4), idesc, s > 0);
+            umma_chain(taddr, da, db, idesc, in >> 4, umma_kstep(128), umma_kstep(kTP));
             umma_commit(&bar_m);
         }
         mbar_wait(&bar_m, phase, c.status);
@@ -926,9 +921,7 @@ __global__ void __launch_bounds__(256) k_unit_tc(FwdCtx c, int t) {
         if (tid == 0) {
             tcgen05_fence_after();
             const uint64_t da = umma_desc(A2, 128), db = umma_desc(B2, kTP);
-            for (int s = 0; s < 8; ++s)
-                umma_bf16(taddr + 32, da + static_cast<uint64_t>(s) * ((2 * 128 * 16) >> 4),
-                          db + static_cast<uint64_t>(s) * ((2 * kTP * 16) >> 4), idesc, s > 0);
+            umma_chain(taddr + 32, da, db, idesc, 8, umma_kstep(128), umma_kstep(kTP));
             umma_commit(&bar_m);
         }
         mbar_wait(&bar_m, phase, c.status);

@@ -56,7 +56,9 @@ class WindowModel:
     ``cand_w`` = the cell (``python/hsn/model/cell.py:192-212``), ``w1 b1 w2 b2`` = the unit bank,
     ``pad_src`` / ``edge_w`` = the padded cell graph with the window's edge weights, ``cost`` = the
     router's cost table. ``prod="bf16"`` rounds the products' weights to bfloat16 here, once, as
-    the reference's sweep twin does per window (``python/hsn/train/compile.py:776-840``).
+    the reference's sweep twin does per window (``python/hsn/train/compile.py:776-840``), and packs
+    the unit bank as bf16 operand tiles for the tcgen05 kernels (``tensor_cores=False`` keeps the
+    CUDA-core kernels with the same roundings: a cross-check for the tests).
     """
 
     struct: _lib.HsnwModel
@@ -80,6 +82,7 @@ class WindowModel:
         limit: float = 1.00001,
         norm_eps: float = 1e-6,
         cand_eps: float = 1e-6,
+        tensor_cores: bool = True,
     ) -> "WindowModel":
         if prod not in ("fp32", "bf16"):
             raise ValueError(f"prod must be 'fp32' or 'bf16', got {prod!r}")
@@ -131,7 +134,7 @@ class WindowModel:
             "edge_w": w["edge_w"],
             "cost": w["cost"],
         }
-        if prod == "bf16":
+        if prod == "bf16" and tensor_cores:
             packed.update(_umma_images(w["w1"], w["w2"], packed["gate_t"]))
         struct = _lib.HsnwModel()
         dims = dict(N=N, d=d, K=int(k), H=H, M=M, D=D, S=S, dc=dc)
@@ -150,14 +153,15 @@ class WindowModel:
         return WindowModel(struct=struct, tensors=packed, device=device, dims=dims, prod=prod)
 
     @staticmethod
-    def from_oracle_weights(W: Any, *, device: torch.device | str = "cuda", prod: str = "fp32") -> "WindowModel":
+    def from_oracle_weights(W: Any, *, device: torch.device | str = "cuda", prod: str = "fp32",
+                            tensor_cores: bool = True) -> "WindowModel":
         """From an object with the weights as attributes and the router's scalars (the fixtures'
         ``WindowWeights``): a convenience of the tests and the benchmark."""
         weights = {key: getattr(W, key) for key in _WEIGHT_KEYS}
         return WindowModel.build(
             weights, k=W.k, device=device, prod=prod, age_max=W.age_max, probes=W.probes,
             lambda_cost=W.lambda_cost, cell_overhead=W.cell_overhead, shared_cost=W.shared_cost,
-            limit=W.limit, norm_eps=W.norm_eps, cand_eps=W.cand_eps,
+            limit=W.limit, norm_eps=W.norm_eps, cand_eps=W.cand_eps, tensor_cores=tensor_cores,
         )  # fmt: skip
 
     @staticmethod
@@ -203,7 +207,19 @@ def _umma_images(w1: Tensor, w2: Tensor, gate_t: Tensor) -> dict[str, Tensor]:
     g = g.reshape(in4 // 8, 8, 128).permute(0, 2, 1).to(bf).contiguous()
     a2 = torch.nn.functional.pad(w2, (0, 128 - d, 0, pad_h))  # [M, nB*128, 128]
     a2 = a2.reshape(M, nB, 16, 8, 128).permute(0, 1, 2, 4, 3).to(bf).contiguous()
-    return {"umma_w1": a1, "umma_gate": g, "umma_w2": a2}
+    out = {"umma_w1": a1, "umma_gate": g, "umma_w2": a2}
+    if d % 16 == 0 and d <= 128:
+        # the reverse sweep's transposed products
+        nT = (2 * d + 127) // 128
+        pad_i = nT * 128 - 2 * d
+        b2 = torch.nn.functional.pad(w2, (0, 0, 0, pad_h))  # [M, nB*128, d]
+        b2 = b2.reshape(M, nB, 128, d // 8, 8).permute(0, 1, 3, 2, 4).to(bf).contiguous()
+        b1 = torch.nn.functional.pad(w1[:, 2 * d :, :], (0, pad_h, 0, pad_i))  # [M, nT*128, nB*128]
+        b1 = b1.reshape(M, nT, 128, nB, 16, 8).permute(0, 3, 1, 4, 2, 5).to(bf).contiguous()
+        bg = torch.nn.functional.pad(gate_t[2 * d :, :], (0, 0, 0, pad_i))  # [nT*128, d]
+        bg = bg.reshape(nT, 128, d // 8, 8).permute(0, 2, 1, 3).to(bf).contiguous()
+        out.update(umma_bw_w2=b2, umma_bw_w1=b1, umma_bw_gate=bg)
+    return out
 
 
 def _check(name: str, t: Tensor, shape: tuple[int, ...], dtype: torch.dtype, device: torch.device) -> Tensor:

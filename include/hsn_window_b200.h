@@ -124,6 +124,14 @@ typedef struct HsnwModel {
     const void* umma_w1;
     const void* umma_gate;
     const void* umma_w2;
+    /* the same for the reverse sweep's transposed products (null: CUDA-core path), nT = ceil(2d/128):
+     * umma_bw_w2 [M][ceil(H/128)][d/8][128][8] (rows: hidden columns, K: the unit's outputs),
+     * umma_bw_w1 [M][ceil(H/128)][nT][16][128][8] (rows: the 2d state columns of the cell input,
+     * K: the block's hidden columns), umma_bw_gate [nT][d/8][128][8] (rows: state columns,
+     * K: the gate's outputs). */
+    const void* umma_bw_w2;
+    const void* umma_bw_w1;
+    const void* umma_bw_gate;
 } HsnwModel;
 
 /* Inputs, tape and record of a forward sweep. Row-major, contiguous. Null = not wanted, for the

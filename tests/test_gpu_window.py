@@ -474,3 +474,79 @@ def test_front_projection_equals_a_plain_product(dims, prod: str) -> None:
         want = (x.double() @ w.double().t() + b.double()).float()
         scale = float(want.abs().max())
         assert float((got - want).abs().max()) <= 2e-5 * scale, (rows, prod)
+
+
+def _both_ways(rng, B, T, N, d, K, H, M, D, mult):
+    """The same bf16 model twice: tensor-core kernels, and the CUDA-core kernels with the same
+    roundings; a forward record by the first and the reverse sweep's inputs."""
+    from hsn_b200.window import WindowModel, window_forward
+
+    W, z, ctx, scalars, reset, state = _synthetic(rng, B, T, N, d, K, H, M, D, 0.1)
+    for key in ("w1", "w2", "gate_w", "v_w", "wout_w"):
+        setattr(W, key, O.bf16_round(getattr(W, key) * mult))
+    tc = WindowModel.from_oracle_weights(W, device="cuda", prod="bf16")
+    cc = WindowModel.from_oracle_weights(W, device="cuda", prod="bf16", tensor_cores=False)
+    args = (dev(z), dev(ctx), dev(scalars), dev(reset), tuple(dev(s) for s in state))
+    tape = window_forward(tc, *args)
+    cots = [dev(rng.standard_normal(s).astype(np.float32)) for s in ((B, T, d), (B, T, d), (B, T, K, d))]
+    rec = {k: tape["rec_" + k] for k in ("y", "hidden", "gate_pre", "m", "rms")}
+    base = (tape["rec_c"], tape["rec_b"], tape["rec_h_old"], tape["sel_cell_idx"], tape["sel_unit_idx"],
+            tape["sel_valid"], dev(reset))  # fmt: skip
+    return W, tc, cc, args, tape, base, cots, rec
+
+
+@pytest.mark.parametrize(
+    "B,T,N,d,K,H,M,D,mult",
+    [
+        (6, 9, 256, 64, 8, 512, 8, 4, 1.0),    # the benchmark's model
+        (6, 9, 256, 64, 8, 512, 8, 4, 6.0),    # large weights: the recurrence amplifies any difference
+        (40, 3, 64, 64, 8, 200, 2, 2, 1.0),    # 160 pairs a unit: several batches of 32 and pair tiles; H % 128 != 0
+        (5, 4, 96, 32, 4, 128, 3, 2, 1.0),     # d 32: half a state tile
+        (3, 3, 64, 128, 4, 256, 4, 2, 1.0),    # d 128: two state tiles
+    ],
+)
+def test_tensor_core_kernels_equal_the_cuda_core_kernels_with_the_same_roundings(B, T, N, d, K, H, M, D, mult) -> None:
+    """tcgen05 kernels (unit layers forward, transposed unit layers in the reverse sweep) against
+    the CUDA-core kernels on the same bf16 operands: the products are exact in fp32 and only the
+    order of the sums differs, so 2e-4 of the scale (forward, teacher-forced) and 1e-3 (reverse
+    sweep over T positions)."""
+    from hsn_b200.window import window_backward, window_forward
+
+    rng = np.random.default_rng(12)
+    W, tc, cc, args, tape, base, cots, rec = _both_ways(rng, B, T, N, d, K, H, M, D, mult)
+    forced = (tape["sel_cell_idx"], tape["sel_unit_idx"], tape["sel_valid"])
+    other = window_forward(cc, *args, forced=forced)
+    for key in ("rec_hidden", "rec_y", "rec_gate_pre", "rec_c", "rec_b", "tape_h", "tape_q", "h", "q"):
+        g, w = tape[key], other[key]
+        scale = max(1e-3, float(w.abs().max()))
+        # a bf16 rounding of an intermediate can flip on a last-bit difference of the sum: one
+        # bf16 step (2^-8 relative) on isolated values, so the bound is on the 99.9th percentile
+        diff = (g - w).abs().flatten()
+        assert float(diff.max()) <= 2e-2 * scale, (key, float(diff.max()), scale)
+        assert float(torch.quantile(diff[: 1 << 24].float(), 0.999)) <= 2e-3 * scale, key
+    got = window_backward(tc, *base, *cots, rec)
+    want = window_backward(cc, *base, *cots, rec)
+    for name, g, w in zip(("dc", "db", "A", "R"), (got[0], got[1], got[2][0], got[2][1]),
+                          (want[0], want[1], want[2][0], want[2][1])):  # fmt: skip
+        scale = max(1e-6, float(w.abs().max()))
+        worst = float((g - w).abs().max())
+        assert worst <= 1e-3 * scale, (name, worst, scale)
+    again = window_backward(tc, *base, *cots, rec)
+    assert torch.equal(again[0], got[0]) and torch.equal(again[2][0], got[2][0])  # run to run: bit for bit
+
+
+def test_reverse_sweep_with_bf16_products_stays_within_bf16_tolerance() -> None:
+    """The reverse sweep with bf16 products (tensor cores) against the sweep with fp32 products on
+    the same weights and record: 2e-2 of the scale."""
+    from hsn_b200.window import WindowModel, window_backward
+
+    rng = np.random.default_rng(13)
+    W, tc, _, _, _, base, cots, rec = _both_ways(rng, 6, 9, 256, 64, 8, 512, 8, 4, 1.0)
+    full = WindowModel.from_oracle_weights(W, device="cuda", prod="fp32")
+    got = window_backward(tc, *base, *cots, rec)
+    want = window_backward(full, *base, *cots, rec)
+    for name, g, w in zip(("dc", "db", "A", "R"), (got[0], got[1], got[2][0], got[2][1]),
+                          (want[0], want[1], want[2][0], want[2][1])):  # fmt: skip
+        scale = float(w.abs().max())
+        worst = float((g - w).abs().max())
+        assert worst <= 2e-2 * scale, (name, worst, scale)
