@@ -52,6 +52,31 @@ def bytes_per_row_position(c: dict) -> int:
     return fwd + bwd
 
 
+def kernel_bytes_per_row_position(c: dict) -> dict[str, int]:
+    """The same algorithmic bytes split by the kernel that moves them: ``front`` carries the state
+    tape (read record t, write record t + 1) and the position's inputs, ``row`` the scorer scalars
+    and the decision, ``update`` the selected rows and summaries, ``mid`` the recorded hidden
+    pre-activations, ``tail_head`` the rest of the reverse sweep; ``unit`` works on chip."""
+    N, d, K, H, S = c["N"], c["d"], c["K"], c["H"], c["S"]
+    state = 4 * N * d + 4 * d + 8 * N
+    full = 4 * (6 * K * d + 2 * d) + 9 * K + 1
+    return {
+        "front": 2 * state + 4 * (2 * d),
+        "row": 4 * N * S + 18 * K + 4,
+        "unit": 0,
+        "update": 4 * K * d + 4 * d + 4,
+        "mid": 2 * K * H,
+        "tail_head": full + 4 * (3 * K * d) + 4 * K + 8 * K,
+    }
+
+
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of each kernel of the c2
+# workload, from the ncu capture summarised in profiles/window_kernels_c2_dram.md.
+NCU_TRAFFIC_PER_LAUNCH: dict[str, dict[str, float]] = {
+    "c2": {"front": 2.798e6, "row": 1.375e6, "unit": 3.419e6, "update": 0.526e6, "mid": 2.254e6, "tail_head": 1.703e6},
+}
+
+
 def synthetic(c: dict, rank: int, rows: int):
     """Seeded inputs of the configuration's shapes; every row's data depends on its global row
     index only, so the result does not depend on the number of GPUs."""
@@ -195,8 +220,12 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--positions", type=int, default=0,
+                    help="shorten the window to this many positions (profiler captures only; not a benchmark number)")
     args = ap.parse_args()
-    c = CONFIGS[args.config]
+    c = dict(CONFIGS[args.config])
+    if args.positions > 0:
+        c["T"] = args.positions
     if args.impl == "reference":
         run_reference(args, c, args.config)
         return
@@ -204,7 +233,7 @@ def main() -> None:
     import torch
     import torch.distributed as dist
 
-    from hsn_b200.window import WindowModel, window_backward, window_forward
+    from hsn_b200.window import WindowModel, launch_profile, window_backward, window_forward
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -286,6 +315,10 @@ def main() -> None:
     ms_e2e = e0.elapsed_time(e1) / args.steps
     stop.set()
     sampler.join(timeout=2)
+    # one more step, untimed, with an event before every launch: the per-kernel times and counts
+    with launch_profile() as prof:
+        step(z, ctx, scalars, reset, (pre, post, sel))
+    barrier()
     times = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -297,6 +330,29 @@ def main() -> None:
         row_pos = B * T
         per = bytes_per_row_position(c)
         achieved = per * row_pos / (ms * 1e-3) / 1e9
+        # the step's kernels by measured time (the profiled step); the dominant one's roofline
+        launches_per_step = sum(prof.launches.values())
+        total_ms = sum(prof.ms.values()) or 1.0
+        split = kernel_bytes_per_row_position(c)
+        traffic = NCU_TRAFFIC_PER_LAUNCH.get(args.config, {}) if args.positions == 0 else {}
+        kernels = {}
+        for name, n in prof.launches.items():
+            if n:
+                us = 1e3 * prof.ms[name] / n
+                alg = split.get(name, 0) * B
+                kernels[name] = {"launches_per_step": n, "us_per_launch": round(us, 3),
+                                 "share": round(prof.ms[name] / total_ms, 4), "algorithmic_bytes_per_launch": alg,
+                                 "achieved_gbs": round(alg / (us * 1e-6) / 1e9, 3) if us > 0 else None,
+                                 "traffic": traffic.get(name)}  # fmt: skip
+        top = max(kernels, key=lambda k: kernels[k]["share"])
+        roofline = {
+            "bound": "hbm", "kernel": top, "achieved": kernels[top]["achieved_gbs"], "peak": peak, "unit": "GB/s",
+            "frac": kernels[top]["achieved_gbs"] / peak, "traffic": kernels[top]["traffic"],
+            "peak_source": "measured" if peaks else "fallback",
+            "how": "algorithmic bytes of the kernel's launch / its mean event-to-event time in a profiled step",
+            "step": {"achieved": achieved, "frac": achieved / peak, "bytes_per_row_position": per},
+            "kernels": kernels,
+        }  # fmt: skip
         h2d = sum(t.numel() * t.element_size() for t in pinned)
         d2h = sum(t.numel() * t.element_size() for t in host_out.values())
         line = {
@@ -304,16 +360,14 @@ def main() -> None:
             "unit": "row-positions/s", "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16 products, f32 state" if c["prod"] == "bf16" else "f32", "data": "synthetic",
-            "config": {"workload": WORKLOADS[args.config], "rows_per_gpu": B, "positions": T,
+            "config": {"workload": WORKLOADS[args.config] + (f" [shortened to {T} positions]" if args.positions else ""),
+                       "rows_per_gpu": B, "positions": T,
                        "l2": "inputs larger than L2 (tape 0.5 GiB + scalars 75 MB per step)",
                        "allreduce_floats_per_step": n_params if world > 1 else 0},
             "e2e": {"value": world * row_pos / (ms_e2e * 1e-3), "unit": "row-positions/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": args.steps * (6 * T + 3),
-            "roofline": {"bound": "hbm", "kernel": "window forward + reverse sweep (all launches of a step)",
-                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_source": "measured" if peaks else "fallback", "bytes_per_row_position": per,
-                         "traffic": None},
+            "gpu_launches": args.steps * launches_per_step,
+            "roofline": roofline,
             "clocks": clocks_summary(lines, local),
         }  # fmt: skip
         if not args.no_cpu_baseline:

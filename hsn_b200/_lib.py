@@ -7,7 +7,7 @@ on first use and raises if it is missing: there is no CPU or PyTorch fallback on
 from __future__ import annotations
 
 import ctypes
-from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
+from ctypes import POINTER, Structure, c_char_p, c_double, c_float, c_int, c_int32, c_int64, c_void_p
 from functools import lru_cache
 from pathlib import Path
 
@@ -98,6 +98,10 @@ SYMBOLS: dict[str, tuple[object, list[object]]] = {
     "hsnw_static_scratch_bytes": (c_int64, []),
     "hsnw_window_backward_static": (c_int, [POINTER(HsnwModel), POINTER(HsnwBackward), c_void_p]),
     "hsnw_front_projection": (c_int, [POINTER(HsnwModel), c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+    "hsnw_profile_begin": (c_int, []),
+    "hsnw_profile_kinds": (c_int, []),
+    "hsnw_profile_kind_name": (c_char_p, [c_int]),
+    "hsnw_profile_end": (c_int, [POINTER(c_double), POINTER(c_int64), c_int]),
 }
 
 

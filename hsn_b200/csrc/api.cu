@@ -5,6 +5,7 @@
 #include "host_util.h"
 
 #include <mutex>
+#include <vector>
 #include <stdio.h>
 #include <string.h>
 
@@ -221,4 +222,67 @@ extern "C" int hsnw_launch_shape(const char* name, const HsnWinArgs* a, int64_t*
     if (bytes > cap) return hsnw_fail(HSNW_E_UNSUPPORTED, "the row's working set exceeds a block's shared memory");
     *shared = static_cast<int>(bytes);
     return HSNW_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Launch timing (measurement runs only; one profile at a time, from one host thread).
+// ------------------------------------------------------------------------------------------------
+bool g_hsnw_profile_on = false;
+namespace {
+struct ProfileMark { cudaEvent_t event; int kind; };
+std::vector<ProfileMark> profile_marks;
+cudaStream_t profile_stream = nullptr;
+const char* const kind_names[HSNW_K_KINDS] = {"init", "pre", "front", "row", "unit", "update", "head", "mid", "tail_head"};
+}  // namespace
+
+void hsnw_profile_mark_slow(int kind, cudaStream_t stream) {
+    ProfileMark mark{nullptr, kind};
+    if (cudaEventCreate(&mark.event) != cudaSuccess) return;
+    cudaEventRecord(mark.event, stream);
+    profile_stream = stream;
+    profile_marks.push_back(mark);
+}
+
+extern "C" int hsnw_profile_begin(void) {
+    if (g_hsnw_profile_on) return hsnw_fail(HSNW_E_STATE, "profile_begin: a profile is already running");
+    profile_marks.clear();
+    g_hsnw_profile_on = true;
+    return HSNW_OK;
+}
+
+extern "C" int hsnw_profile_kinds(void) { return HSNW_K_KINDS; }
+extern "C" const char* hsnw_profile_kind_name(int kind) {
+    return kind >= 0 && kind < HSNW_K_KINDS ? kind_names[kind] : "";
+}
+
+extern "C" int hsnw_profile_end(double* ms_by_kind, int64_t* launches_by_kind, int kinds) {
+    if (!g_hsnw_profile_on) return hsnw_fail(HSNW_E_STATE, "profile_end: no profile is running");
+    g_hsnw_profile_on = false;
+    if (!ms_by_kind || !launches_by_kind || kinds < HSNW_K_KINDS)
+        return hsnw_fail(HSNW_E_ARG, "profile_end: needs room for hsnw_profile_kinds() entries");
+    for (int k = 0; k < kinds; ++k) {
+        ms_by_kind[k] = 0.0;
+        launches_by_kind[k] = 0;
+    }
+    int rc = HSNW_OK;
+    if (!profile_marks.empty()) {
+        cudaEvent_t last;
+        if (cudaEventCreate(&last) != cudaSuccess || cudaEventRecord(last, profile_stream) != cudaSuccess
+            || cudaEventSynchronize(last) != cudaSuccess) {
+            rc = hsnw_fail(HSNW_E_CUDA, "profile_end: could not record the closing event");
+        } else {
+            for (size_t i = 0; i < profile_marks.size(); ++i) {
+                float ms = 0.0f;
+                const cudaEvent_t next = i + 1 < profile_marks.size() ? profile_marks[i + 1].event : last;
+                if (cudaEventElapsedTime(&ms, profile_marks[i].event, next) == cudaSuccess) {
+                    ms_by_kind[profile_marks[i].kind] += ms;
+                    launches_by_kind[profile_marks[i].kind] += 1;
+                }
+            }
+        }
+        cudaEventDestroy(last);
+    }
+    for (ProfileMark& mark : profile_marks) cudaEventDestroy(mark.event);
+    profile_marks.clear();
+    return rc;
 }

@@ -20,3 +20,16 @@ void hsnw_attribute_failed();
 void hsnw_forward_set_attributes();
 void hsnw_backward_set_attributes();
 void hsnw_ops_set_attributes();
+
+// Launch timing for measurement runs (hsnw_profile_begin / hsnw_profile_end): while it is on, every
+// launch site records an event on its stream first; the time between two consecutive events is
+// charged to the kernel launched between them. Off (the default) this is one predictable branch.
+enum HsnwKernelKind {
+    HSNW_K_INIT = 0, HSNW_K_PRE, HSNW_K_FRONT, HSNW_K_ROW, HSNW_K_UNIT, HSNW_K_UPDATE,
+    HSNW_K_HEAD, HSNW_K_MID, HSNW_K_TAIL_HEAD, HSNW_K_KINDS
+};
+extern bool g_hsnw_profile_on;
+void hsnw_profile_mark_slow(int kind, cudaStream_t stream);
+inline void hsnw_profile_mark(int kind, cudaStream_t stream) {
+    if (g_hsnw_profile_on) hsnw_profile_mark_slow(kind, stream);
+}

@@ -679,14 +679,20 @@ extern "C" int hsnw_window_backward(const HsnwModel* model, const HsnwBackward* 
     const dim3 mid_grid(m.M * (c.nU + 1), (B * m.K + pair_tile - 1) / pair_tile);
     const size_t sh_mid_tc = mid_tc_shared(m);
     if (full) {
-        for (int t = T - 1; t >= 0; --t) k_head<<<B, 256, sh_head, stream>>>(c, t);
+        for (int t = T - 1; t >= 0; --t) {
+            hsnw_profile_mark(HSNW_K_HEAD, stream);
+            k_head<<<B, 256, sh_head, stream>>>(c, t);
+        }
         return hsnw_check_launch("window_backward");
     }
     // head(T-1) | mid(T-1) | tail(T-1) + head(T-2) | mid(T-2) | ... | tail(0)
+    hsnw_profile_mark(HSNW_K_HEAD, stream);
     k_head<<<B, 256, sh_head, stream>>>(c, T - 1);
     for (int t = T - 1; t >= 0; --t) {
+        hsnw_profile_mark(HSNW_K_MID, stream);
         if (mid_tc) k_mid_tc<<<mid_grid, 256, sh_mid_tc, stream>>>(c, t);
         else k_mid<<<mid_grid, 256, sh_mid, stream>>>(c, t);
+        hsnw_profile_mark(HSNW_K_TAIL_HEAD, stream);
         k_tail_head<<<B, 256, sh_both, stream>>>(c, t);
         if (int rc = hsnw_check_launch("window_backward")) return rc;
     }

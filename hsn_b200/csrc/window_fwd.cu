@@ -1217,11 +1217,13 @@ extern "C" int hsnw_front_projection(const HsnwModel* model, const float* z, con
         const size_t shared = static_cast<size_t>(2) * (Kp / 8) * 128 * 16;
         if (shared <= hsnw_max_shared() - 4096) {
             const dim3 grid(static_cast<unsigned>((rows + 127) / 128), static_cast<unsigned>((model->H + 127) / 128));
+            hsnw_profile_mark(HSNW_K_PRE, static_cast<cudaStream_t>(stream));
             k_pre_tc<<<grid, 128, shared, static_cast<cudaStream_t>(stream)>>>(*model, z, ctx, rows, out, g_pre_status);
             return hsnw_check_launch("front_projection");
         }
     }
     const dim3 grid(static_cast<unsigned>((rows + kSlice - 1) / kSlice), static_cast<unsigned>((model->H + kSlice - 1) / kSlice));
+    hsnw_profile_mark(HSNW_K_PRE, static_cast<cudaStream_t>(stream));
     k_pre<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(*model, z, ctx, rows, out);
     return hsnw_check_launch("front_projection");
 }
@@ -1270,6 +1272,7 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
     c.cmax = reinterpret_cast<int*>(base + L.cmax);
     const int rthreads = row_threads(*model);
     const dim3 init_grid(B, (model->N + kInitCells - 1) / kInitCells);
+    hsnw_profile_mark(HSNW_K_INIT, stream);
     k_init<<<init_grid, 256, init_shared(*model), stream>>>(c);
     g_pre_status = c.status;
     const int rc_pre = hsnw_front_projection(model, io->z, io->ctx, static_cast<int64_t>(B) * T, c.pre_s, stream);
@@ -1281,10 +1284,14 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
     const size_t sh_front = front_shared(*model), sh_row = row_shared(*model);
     const size_t sh_unit = unit_shared(*model), sh_update = update_shared(*model), sh_unit_tc = unit_tc_shared(*model);
     for (int t = 0; t < T; ++t) {
+        hsnw_profile_mark(HSNW_K_FRONT, stream);
         k_front<<<front_grid, 256, sh_front, stream>>>(c, t);
+        hsnw_profile_mark(HSNW_K_ROW, stream);
         k_row<<<B, rthreads, sh_row, stream>>>(c, t);
+        hsnw_profile_mark(HSNW_K_UNIT, stream);
         if (unit_tc) k_unit_tc<<<unit_grid, 256, sh_unit_tc, stream>>>(c, t);
         else k_unit<<<unit_grid, 256, sh_unit, stream>>>(c, t);
+        hsnw_profile_mark(HSNW_K_UPDATE, stream);
         k_update<<<B, 256, sh_update, stream>>>(c, t);
         if (int rc = hsnw_check_launch("window_forward")) return rc;
     }

@@ -446,3 +446,30 @@ def front_projection(model: WindowModel, z: Tensor, ctx: Tensor) -> Tensor:
             )
         )
     return out
+
+
+class launch_profile:
+    """``with launch_profile() as prof: ...`` times every kernel launch of the window entry points
+    made inside the block (``hsnw_profile_begin`` / ``hsnw_profile_end``): afterwards ``prof.ms``
+    and ``prof.launches`` map a kernel kind ("front", "row", "unit", "update", "head", "mid",
+    "tail_head", "init", "pre") to its summed time in milliseconds and its launch count. For
+    measurement runs: it adds an event per launch."""
+
+    def __init__(self) -> None:
+        self.ms: dict[str, float] = {}
+        self.launches: dict[str, int] = {}
+
+    def __enter__(self) -> "launch_profile":
+        _lib.check(_lib.library().hsnw_profile_begin())
+        return self
+
+    def __exit__(self, *exc: object) -> None:
+        lib = _lib.library()
+        kinds = int(lib.hsnw_profile_kinds())
+        ms = (ctypes.c_double * kinds)()
+        count = (ctypes.c_int64 * kinds)()
+        _lib.check(lib.hsnw_profile_end(ms, count, kinds))
+        for k in range(kinds):
+            name = lib.hsnw_profile_kind_name(k).decode()
+            self.ms[name] = float(ms[k])
+            self.launches[name] = int(count[k])

@@ -247,6 +247,19 @@ int hsnw_window_backward_static(const HsnwModel* model, const HsnwBackward* io, 
 int hsnw_front_projection(const HsnwModel* model, const float* z, const float* ctx, int64_t rows,
                           float* out, void* stream);
 
+/* ---- launch timing, for measurement runs --------------------------------------------------------
+ * No counterpart in the reference (it times whole steps on the host, scripts/bench_window.py:60-110).
+ * Between hsnw_profile_begin and hsnw_profile_end every kernel launch of the window entry points
+ * is preceded by an event on its stream; hsnw_profile_end synchronises, and fills for each kernel
+ * kind k < hsnw_profile_kinds() the summed time (ms, event to next event: the kernel and the gap
+ * before the next launch) and the number of launches. One profile at a time, one host thread, one
+ * stream. hsnw_profile_kind_name(k): "init" "pre" "front" "row" "unit" "update" "head" "mid"
+ * "tail_head". */
+int hsnw_profile_begin(void);
+int hsnw_profile_kinds(void);
+const char* hsnw_profile_kind_name(int kind);
+int hsnw_profile_end(double* ms_by_kind, int64_t* launches_by_kind, int kinds);
+
 #ifdef __cplusplus
 }
 #endif
