@@ -21,7 +21,11 @@ import threading
 import time
 from pathlib import Path
 
-import numpy as np
+if "reference" in sys.argv and "OMP_NUM_THREADS" in os.environ:
+    # the reference arm uses every host core; torchrun pins OMP_NUM_THREADS to 1 for its children
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
+
+import numpy as np  # noqa: E402
 
 ROOT = Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
@@ -370,7 +374,7 @@ def main() -> None:
             "roofline": roofline,
             "clocks": clocks_summary(lines, local),
         }  # fmt: skip
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_baseline(c, W, host)
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -209,15 +209,7 @@ extern "C" int hsnw_launch_shape(const char* name, const HsnWinArgs* a, int64_t*
         *block = 256;
         bytes = sizeof(float) * (static_cast<size_t>(N) + 1) * d;
     } else {
-        // the three kernels of the per-position reverse sweep (reference window.py:1151-1162)
-        const int K = a->i[2], d = a->i[3];
-        *block = 512;
-        if (strcmp(name, "hsn_win_back_head") == 0)
-            bytes = sizeof(float) * (2 * static_cast<size_t>(d) + 5 * K + 2 * static_cast<size_t>(K) * d + 3 * ((static_cast<size_t>(K) * d + 31) / 32));
-        else if (strcmp(name, "hsn_win_back_mid") == 0)
-            bytes = sizeof(float) * (3 * static_cast<size_t>(K) + static_cast<size_t>(K) * 16);
-        else
-            bytes = sizeof(float) * (3 * static_cast<size_t>(K) + a->i[4] + 2 * static_cast<size_t>(K) * d + 2 * static_cast<size_t>(a->i[4]) * a->i[7]);
+        return hsnw_fail(HSNW_E_NAME, "launch_shape: no kernel of that name");
     }
     if (bytes > cap) return hsnw_fail(HSNW_E_UNSUPPORTED, "the row's working set exceeds a block's shared memory");
     *shared = static_cast<int>(bytes);
