@@ -20,6 +20,12 @@ void hsnw_attribute_failed();
 void hsnw_forward_set_attributes();
 void hsnw_backward_set_attributes();
 void hsnw_ops_set_attributes();
+void hsnw_rows_set_attributes();
+struct HsnwModel;
+struct HsnwForward;
+// The forward sweep by one persistent cluster per row (window_rows.cu): HSNW_OK when launched, -1 when
+// the shape does not fit that kernel (the caller runs the phases instead), else an error code.
+int hsnw_rows_forward(const HsnwModel* model, const HsnwForward* io, const float* pre_s, int* status, cudaStream_t stream);
 
 // Launch timing for measurement runs (hsnw_profile_begin / hsnw_profile_end): while it is on, every
 // launch site records an event on its stream first; the time between two consecutive events is

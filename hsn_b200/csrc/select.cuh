@@ -158,33 +158,12 @@ __device__ __forceinline__ uint64_t warp_argmax_key(uint64_t mine) {
     return (static_cast<uint64_t>(hi) << 32) | lo;
 }
 
-__device__ __forceinline__ void select_row_warp(const SelectParams& P, const float* score, const int* unit,
-                                                const int64_t* age_row, SelectShared& S) {
+// The rest of the decision once the scored order is known (S.order[0..K) and next_key, the
+// (K + 1)-th best key or 0): the budget prefix, the threshold, the probes. One warp.
+__device__ __forceinline__ void select_finish_warp(const SelectParams& P, const float* score, const int* unit,
+                                                   const int64_t* age_row, SelectShared& S, uint64_t next_key) {
     const int lane = threadIdx.x & 31;
     const int N = P.N, K = P.K;
-    // the scored decision: K + 1 rounds (the extra one is the highest unselected score)
-    uint64_t mine = 0ull;
-    for (int i = lane; i < N; i += 32) {
-        const uint64_t key = pack_key(score[i], i);
-        mine = key > mine ? key : mine;
-    }
-    uint64_t next_key = 0ull;
-    for (int r = 0; r <= K; ++r) {
-        const uint64_t win = warp_argmax_key(mine);
-        if (r < K) {
-            if (lane == 0) S.order[r] = win ? key_cell(win) : 0;
-        } else {
-            next_key = win;
-        }
-        if (win && (key_cell(win) & 31) == lane) {  // the winner's lane moves on to its next best
-            uint64_t best = 0ull;
-            for (int i = lane; i < N; i += 32) {
-                const uint64_t key = pack_key(score[i], i);
-                if (key < win && key > best) best = key;
-            }
-            mine = best;
-        }
-    }
     __syncwarp();
     int n_valid = 0;
     if (lane == 0) {
@@ -264,6 +243,86 @@ __device__ __forceinline__ void select_row_warp(const SelectParams& P, const flo
         }
     }
     __syncwarp();
+}
+
+__device__ __forceinline__ void select_row_warp(const SelectParams& P, const float* score, const int* unit,
+                                                const int64_t* age_row, SelectShared& S) {
+    const int lane = threadIdx.x & 31;
+    const int N = P.N, K = P.K;
+    // the scored decision: K + 1 rounds (the extra one is the highest unselected score)
+    uint64_t mine = 0ull;
+    for (int i = lane; i < N; i += 32) {
+        const uint64_t key = pack_key(score[i], i);
+        mine = key > mine ? key : mine;
+    }
+    uint64_t next_key = 0ull;
+    for (int r = 0; r <= K; ++r) {
+        const uint64_t win = warp_argmax_key(mine);
+        if (r < K) {
+            if (lane == 0) S.order[r] = win ? key_cell(win) : 0;
+        } else {
+            next_key = win;
+        }
+        if (win && (key_cell(win) & 31) == lane) {  // the winner's lane moves on to its next best
+            uint64_t best = 0ull;
+            for (int i = lane; i < N; i += 32) {
+                const uint64_t key = pack_key(score[i], i);
+                if (key < win && key > best) best = key;
+            }
+            mine = best;
+        }
+    }
+    select_finish_warp(P, score, unit, age_row, S, next_key);
+}
+
+// The same scored order found by several warps: each warp first reduces the cells first, first +
+// stride, ... (first = its first thread's index in the group, stride = the group's thread count)
+// to its K + 1 best keys (select_candidates_warp, all warps at once), then ONE warp merges the
+// warps' candidates (select_merge_warp) and finishes. cand: [warps][K + 1] keys in shared memory.
+__device__ __forceinline__ void select_candidates_warp(int N, int K, const float* score, uint64_t* cand_row, int first,
+                                                       int stride) {
+    const int lane = threadIdx.x & 31;
+    uint64_t mine = 0ull;
+    for (int i = first + lane; i < N; i += stride) {
+        const uint64_t key = pack_key(score[i], i);
+        mine = key > mine ? key : mine;
+    }
+    for (int r = 0; r <= K; ++r) {
+        const uint64_t win = warp_argmax_key(mine);
+        if (lane == 0) cand_row[r] = win;
+        if (win && mine == win) {   // keys are unique: exactly one lane holds the winner
+            uint64_t best = 0ull;
+            for (int i = first + lane; i < N; i += stride) {
+                const uint64_t key = pack_key(score[i], i);
+                if (key < win && key > best) best = key;
+            }
+            mine = best;
+        }
+    }
+}
+__device__ __forceinline__ void select_merge_warp(const SelectParams& P, const float* score, const int* unit,
+                                                  const int64_t* age_row, const uint64_t* cand, int n_cand,
+                                                  SelectShared& S) {
+    const int lane = threadIdx.x & 31;
+    const int K = P.K;
+    uint64_t mine = 0ull;
+    for (int i = lane; i < n_cand; i += 32) mine = cand[i] > mine ? cand[i] : mine;
+    uint64_t next_key = 0ull;
+    for (int r = 0; r <= K; ++r) {
+        const uint64_t win = warp_argmax_key(mine);
+        if (r < K) {
+            if (lane == 0) S.order[r] = win ? key_cell(win) : 0;
+        } else {
+            next_key = win;
+        }
+        if (win && mine == win) {
+            uint64_t best = 0ull;
+            for (int i = lane; i < n_cand; i += 32)
+                if (cand[i] < win && cand[i] > best) best = cand[i];
+            mine = best;
+        }
+    }
+    select_finish_warp(P, score, unit, age_row, S, next_key);
 }
 
 }  // namespace hsnw

@@ -1270,6 +1270,16 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
     c.lh = reinterpret_cast<float*>(base + L.lh);
     c.vh = reinterpret_cast<float*>(base + L.vh);
     c.cmax = reinterpret_cast<int*>(base + L.cmax);
+    if (!model->phases_only && model->rows_bank) {
+        // one persistent cluster per row when the shape fits (window_rows.cu)
+        if (cudaMemsetAsync(c.status, 0, sizeof(int), stream) != cudaSuccess) return hsnw_check_launch("window_forward");
+        g_pre_status = c.status;
+        const int rc_pre = hsnw_front_projection(model, io->z, io->ctx, static_cast<int64_t>(B) * T, c.pre_s, stream);
+        g_pre_status = nullptr;
+        if (rc_pre) return rc_pre;
+        const int rc_rows = hsnw_rows_forward(model, io, c.pre_s, c.status, stream);
+        if (rc_rows >= 0) return rc_rows;
+    }
     const int rthreads = row_threads(*model);
     const dim3 init_grid(B, (model->N + kInitCells - 1) / kInitCells);
     hsnw_profile_mark(HSNW_K_INIT, stream);

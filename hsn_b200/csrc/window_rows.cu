@@ -1,0 +1,1127 @@
+// The forward sweep of a window as ONE persistent kernel: a thread-block cluster per batch row
+// walks the row's T positions with the row's state resident in the cluster's shared memory.
+//
+// Why: at a few dozen rows per GPU the batch-synchronous phases (window_fwd.cu) are bound by the
+// latency of 4 launches and ~20 dependent trips to L2 per position. Rows are independent in the
+// forward sweep, so a row can run alone: its state (h, V h, the state's part of the logits, ages)
+// lives in distributed shared memory for the whole window, the phases of a position are separated
+// by 4 hardware cluster barriers instead of kernel boundaries, and the only traffic per position
+// is the unit bank streamed from L2 by the TMA (bulk copies through a 3-deep ring, issued by a
+// producer warp, consumed by 8 compute warps without block-wide barriers) and the tape's records
+// written back.
+//
+// Cluster of C = H / 128 blocks; block r owns the cells [r N/C, (r+1) N/C), the hidden columns
+// [128 r, 128 r + 128) of every unit (two 64-column chunks), the columns [256 r, 256 r + 256) of
+// the merged front first layer, the rows [r 4d/C, (r+1) 4d/C) of the gate's input, and the slots
+// k = r (mod C) at the update. Per position:
+//   A  front MLPs on the block's columns -> partial (u, z_hat) pushed to every block   | sync 1
+//   B  u, eps, the scorer on the block's cells -> (score, unit, age) pushed everywhere  | sync 2
+//   C  the decision, by one warp of every block on the gathered scores (select.cuh)
+//   D  gather of the selected rows and message sources through distributed shared memory,
+//      messages, cell norm, the gate's partial, the units' two layers on the streamed chunks,
+//      partial F and gate pushed to the slots' owners                                   | sync 3
+//   E  W_out, candidate norm, tanh, sigmoid, the gated write pushed to the cell's owner with its
+//      derived state, the slot's change of the summary pushed everywhere                | sync 4
+//   F  summary, ages, the tape's next record from the block's cells, the next reset.
+//
+// The arithmetic, the rounding points (bf16 operands and outputs of every product, fp32 sums and
+// state) and every output are those of window_fwd.cu (reference: python/hsn/train/compile.py:
+// 1117-1193, python/hsn/model/hsn.py:1903-1980, python/hsn/model/cell.py:349-505); only the order
+// of fp32 partial sums differs. Fixed orders everywhere: no atomics.
+//
+// Every mbarrier wait is bounded (stage.cuh) and reports through the status word; the cluster
+// barriers are hardware barriers that every thread of the cluster reaches the same number of
+// times (all control flow around them depends on values that are identical in the cluster).
+#include "../../include/hsn_window_b200.h"
+#include "common.cuh"
+#include "select.cuh"
+#include "stage.cuh"
+#include "host_util.h"
+
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
+using namespace hsnw;
+
+namespace {
+
+constexpr int kConsumers = 256;       // compute threads (8 warps)
+constexpr int kRowThreads = 288;      // + the producer warp
+constexpr int kStages = 3;            // ring depth
+constexpr int kMaxK = 8;              // slots (register accumulators per slot)
+constexpr int kMaxMR = 16;            // units
+constexpr int kFrontCols = 256;       // merged front columns per block (2H / C with H = 128 C)
+
+struct RowsCtx {
+    HsnwModel m;
+    HsnwForward io;
+    int C, Nc, Ks;            // blocks of a cluster, cells a block owns, slots a block owns (ceil(K / C))
+    int gate_rows;            // 4d / C
+    uint32_t bank_bytes;      // one (unit, 64-column block) chunk
+    uint32_t w1_bytes;        // its W1 part
+    uint32_t front_bytes;     // one front chunk
+    uint32_t slot_bytes;      // ring slot
+    const float* pre_s;       // [B*T, H]
+    int* status;
+};
+
+__host__ __device__ inline size_t up16(size_t v) { return (v + 15) & ~static_cast<size_t>(15); }
+
+// Offsets (bytes) of the dynamic shared memory's segments.
+struct RowsSmem {
+    size_t ring, h, vh, lh, age, cmax, wout, vt, gate, swh, sw_head, sw_tail, norm_w, cand_w, fb2, gate_b, score_b,
+        fb1p, score_all, unit_all, age_all, q, ue, rowterm, hold, big, msg, rms, src, ew, facc, gacc, inbox_front,
+        inbox_f, inbox_delta, in_scal, in_pre, in_z, upd, cell_of, unit_of, ulist, umask, cand, total;
+};
+__host__ __device__ inline RowsSmem rows_smem(const HsnwModel& m, int C, uint32_t slot_bytes) {
+    RowsSmem L;
+    const size_t d = m.d, N = m.N, K = m.K, M = m.M, D = m.D, S = m.S, Nc = N / C, Ks = (K + C - 1) / C;
+    size_t o = 0;
+    auto take = [&o](size_t bytes) {
+        const size_t at = o;
+        o += up16(bytes);
+        return at;
+    };
+    L.ring = take(static_cast<size_t>(kStages) * slot_bytes);
+    L.h = take(4 * Nc * d);
+    L.vh = take(2 * Nc * d);            // bf16: the values are bf16 in this mode
+    L.lh = take(4 * Nc * M);
+    L.age = take(8 * Nc);
+    L.cmax = take(4 * Nc);
+    L.wout = take(2 * d * d);           // bf16
+    L.vt = take(2 * d * d);             // bf16
+    L.gate = take(2 * (4 * d / C) * d); // bf16, the block's input rows
+    L.swh = take(4 * d * M);
+    L.sw_head = take(4 * 2 * d * M);
+    L.sw_tail = take(4 * (1 + S) * M);
+    L.norm_w = take(4 * 4 * d);
+    L.cand_w = take(4 * d);
+    L.fb2 = take(4 * 2 * d);
+    L.gate_b = take(4 * d);
+    L.score_b = take(4 * 2 * kMaxMR);   // score_b, then cost
+    L.fb1p = take(4 * kFrontCols);      // the predictor's first-layer bias on the block's columns
+    L.score_all = take(4 * N);
+    L.unit_all = take(4 * N);
+    L.age_all = take(8 * N);
+    L.q = take(4 * d);
+    L.ue = take(4 * 2 * d);
+    L.rowterm = take(4 * kMaxMR);
+    L.hold = take(4 * K * d);           // the selected cells' rows
+    {
+        // sources [K D][d], then the pairs' inputs v [K][4d] over them; the front's act [256] and
+        // partial sums [256 / d][2d] use the same bytes in phase A
+        size_t big = 4 * K * D * d;
+        if (4 * K * 4 * d > big) big = 4 * K * 4 * d;
+        if (4 * (kFrontCols + 2 * kFrontCols) > big) big = 4 * 3 * kFrontCols;
+        L.big = take(big);
+    }
+    L.msg = take(4 * K * d);
+    L.rms = take(4 * K);
+    L.src = take(4 * K * D);
+    L.ew = take(4 * K * D);
+    L.facc = take(4 * K * d);
+    L.gacc = take(4 * K * d);
+    L.inbox_front = take(4 * C * (2 * d + 4));
+    L.inbox_f = take(4 * C * Ks * 2 * d);
+    L.inbox_delta = take(4 * K * d);
+    L.in_scal = take(4 * Nc * S + 16);
+    L.in_pre = take(4 * kFrontCols);
+    L.in_z = take(4 * d);
+    L.upd = take(4 * Ks * 6 * d + 4 * Ks);  // F, gate_pre, y, hnew, hb, delta per owned slot; scale
+    L.cell_of = take(4 * K);
+    L.unit_of = take(4 * K);
+    L.ulist = take(4 * (kMaxMR + 4));
+    L.umask = take(4 * (kMaxMR + 4));
+    L.cand = take(8 * N + 64);          // the cells' keys, then [8] stale counts per warp and [K] flags
+    L.total = o;
+    return L;
+}
+
+// Optional phase timestamps for tuning (-DHSNW_TRACE): thread 0 of row 0's blocks, at the middle
+// position, event i of block r at trace[r * 32 + i] (nanoseconds of the global timer); the trace
+// area follows the status word.
+#ifdef HSNW_TRACE
+#define RMARK(i)                                                                              \
+    do {                                                                                      \
+        if (tid == 0 && row == 0 && t == T / 2) {                                             \
+            unsigned long long now;                                                           \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));                           \
+            reinterpret_cast<unsigned long long*>(c.status + 64)[r * 32 + (i)] = now;         \
+        }                                                                                     \
+    } while (0)
+#else
+#define RMARK(i) do { } while (0)
+#endif
+
+template <class T>
+__device__ __forceinline__ T* peer(cg::cluster_group& cl, T* p, int rank) {
+    return cl.map_shared_rank(p, rank);
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumers) : "memory"); }
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+// A bounded wait on a ring barrier. After the first wait of the block that ran out (recorded in
+// *failed and in the status word) every later wait returns at once, so a broken pipeline costs one
+// time-out, not one per stage: the kernel still reaches every cluster barrier and ends.
+__device__ __forceinline__ void ring_wait(uint64_t* bar, uint32_t parity, int* status, volatile int* failed) {
+    if (*failed) return;
+    const uint32_t addr = smem_addr(bar);
+    for (uint32_t spin = 0; spin < (1u << 20); ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return;
+    }
+    *failed = 1;
+    atomicExch(status, 1);
+}
+
+// floats [0, n) from global to shared memory by the 256 compute threads, asynchronously.
+__device__ __forceinline__ void prefetch_floats(float* dst, const float* src, int n, int tid) {
+    const bool vec = ((reinterpret_cast<uintptr_t>(src) | static_cast<uintptr_t>(smem_addr(dst))) & 15) == 0;
+    if (vec) {
+        const int n4 = n >> 2;
+        for (int e = tid; e < n4; e += kConsumers) cp_async16(dst + 4 * e, src + 4 * e);
+        for (int e = (n4 << 2) + tid; e < n; e += kConsumers) cp_async4(dst + e, src + e);
+    } else {
+        for (int e = tid; e < n; e += kConsumers) cp_async4(dst + e, src + e);
+    }
+}
+
+// One streamed chunk (unit j, 64 hidden columns) for the NS slots that run unit j, by one warp
+// on the chunk's columns 8 warp .. 8 warp + 7: lane (c8 = lane & 7, pg = lane >> 3) multiplies
+// column c8 by the planes pg, pg + 4, ... of every slot's input, the four plane groups are folded
+// by shuffles, then bias, rounding, record, activation, and the warp's 8 columns of the second
+// layer for the outputs x0 = lane and x1 = lane + 32. fp0 / fp1 [s]: the partial outputs of slot
+// ks[s]. NS is a compile-time count so the slots' sums are independent chains without branches.
+template <int D_, int NS>
+__device__ __forceinline__ void unit_stage(const uint4* W1s, const uint4* W2s, const float* v, unsigned mask,
+                                           float bias, float* rec_hidden_col, int rec_stride, int warp, int lane,
+                                           float (&f0)[kMaxK], float (&f1)[kMaxK]) {
+    const int c8 = warp * 8 + (lane & 7), pg = lane >> 3;
+    int ks[NS];
+    const float4* vp[NS];
+    float h0[NS], h1[NS];
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+        ks[s] = __fns(mask, 0, s + 1);
+        vp[s] = reinterpret_cast<const float4*>(v + ks[s] * 4 * D_);
+        h0[s] = h1[s] = 0.0f;
+    }
+#pragma unroll
+    for (int p = pg; p < D_ / 2; p += 4) {
+        const uint4 w = W1s[p * 64 + c8];
+        const float w0 = bf16_lo(w.x), w1 = bf16_hi(w.x), w2 = bf16_lo(w.y), w3 = bf16_hi(w.y);
+        const float w4 = bf16_lo(w.z), w5 = bf16_hi(w.z), w6 = bf16_lo(w.w), w7 = bf16_hi(w.w);
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            const float4 a = vp[s][2 * p], b = vp[s][2 * p + 1];
+            h0[s] += a.x * w0;
+            h1[s] += a.y * w1;
+            h0[s] += a.z * w2;
+            h1[s] += a.w * w3;
+            h0[s] += b.x * w4;
+            h1[s] += b.y * w5;
+            h0[s] += b.z * w6;
+            h1[s] += b.w * w7;
+        }
+    }
+    const int x0 = lane, x1 = lane + 32;
+    uint4 wa = make_uint4(0u, 0u, 0u, 0u), wb = wa;
+    if (x0 < D_) wa = W2s[warp * D_ + x0];
+    if (x1 < D_) wb = W2s[warp * D_ + x1];
+    const float a0w = bf16_lo(wa.x), a1w = bf16_hi(wa.x), a2w = bf16_lo(wa.y), a3w = bf16_hi(wa.y);
+    const float a4w = bf16_lo(wa.z), a5w = bf16_hi(wa.z), a6w = bf16_lo(wa.w), a7w = bf16_hi(wa.w);
+    const float b0w = bf16_lo(wb.x), b1w = bf16_hi(wb.x), b2w = bf16_lo(wb.y), b3w = bf16_hi(wb.y);
+    const float b4w = bf16_lo(wb.z), b5w = bf16_hi(wb.z), b6w = bf16_lo(wb.w), b7w = bf16_hi(wb.w);
+    float fp0[NS], fp1[NS];
+    float sums[NS];
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+        float sum = h0[s] + h1[s];
+        sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+        sums[s] = sum;   // every plane group now holds the column's sum of slot s
+    }
+    // bias, rounding, record and activation for four slots at a time: plane group g takes slot 4q + g
+#pragma unroll
+    for (int q = 0; q < (NS + 3) / 4; ++q) {
+        float mine = sums[4 * q];
+        int my_slot = ks[4 * q];
+        if (4 * q + 1 < NS && pg == 1) { mine = sums[4 * q + 1 < NS ? 4 * q + 1 : 0]; my_slot = ks[4 * q + 1 < NS ? 4 * q + 1 : 0]; }
+        if (4 * q + 2 < NS && pg == 2) { mine = sums[4 * q + 2 < NS ? 4 * q + 2 : 0]; my_slot = ks[4 * q + 2 < NS ? 4 * q + 2 : 0]; }
+        if (4 * q + 3 < NS && pg == 3) { mine = sums[4 * q + 3 < NS ? 4 * q + 3 : 0]; my_slot = ks[4 * q + 3 < NS ? 4 * q + 3 : 0]; }
+        const bool active = 4 * q + pg < NS;
+        const float hid = bf16r(mine + bias);
+        if (rec_hidden_col && active) rec_hidden_col[my_slot * rec_stride] = hid;
+        const float a = bf16r(gelu_erf(hid));
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            if (4 * q + g < NS) {
+                // lane 8 g + cc holds the activation of column 8 warp + cc for slot 4q + g
+                const float a0 = __shfl_sync(0xffffffffu, a, 8 * g + 0), a1 = __shfl_sync(0xffffffffu, a, 8 * g + 1);
+                const float a2 = __shfl_sync(0xffffffffu, a, 8 * g + 2), a3 = __shfl_sync(0xffffffffu, a, 8 * g + 3);
+                const float a4 = __shfl_sync(0xffffffffu, a, 8 * g + 4), a5 = __shfl_sync(0xffffffffu, a, 8 * g + 5);
+                const float a6 = __shfl_sync(0xffffffffu, a, 8 * g + 6), a7 = __shfl_sync(0xffffffffu, a, 8 * g + 7);
+                fp0[4 * q + g < NS ? 4 * q + g : 0] =
+                    (a0 * a0w + a1 * a1w) + (a2 * a2w + a3 * a3w) + (a4 * a4w + a5 * a5w) + (a6 * a6w + a7 * a7w);
+                fp1[4 * q + g < NS ? 4 * q + g : 0] =
+                    (a0 * b0w + a1 * b1w) + (a2 * b2w + a3 * b3w) + (a4 * b4w + a5 * b5w) + (a6 * b6w + a7 * b7w);
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < kMaxK; ++k) {
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            if (ks[s] == k) {
+                f0[k] += fp0[s];
+                f1[k] += fp1[s];
+            }
+        }
+    }
+}
+
+
+template <int D_>
+__global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    __shared__ SelectShared S;
+    __shared__ __align__(8) uint64_t full[kStages], empty[kStages];
+    __shared__ int n_units_s;    // units some valid slot runs this position
+    __shared__ int hmax_local;   // bits of max |h| over the block's cells after the last position
+    __shared__ int failed_s;     // a ring wait ran out
+    __shared__ uint64_t next_key_s;   // the (K + 1)-th best key of the position's scored order
+
+    cg::cluster_group cl = cg::this_cluster();
+    const int C = c.C, r = static_cast<int>(cl.block_rank());
+    const int row = blockIdx.x / C;
+    constexpr int d = D_;   // compile time: the index arithmetic of every phase divides by it
+    const int N = c.m.N, K = c.m.K, M = c.m.M, D = c.m.D, Sn = c.m.S, H = c.m.H;
+    const int T = c.io.T, Nc = c.Nc, Ks = c.Ks, grows = c.gate_rows;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bool producer = warp == kConsumers / 32;
+    const bool tape = c.io.tape_state != 0;
+    const bool rec = c.io.rec_c != nullptr;
+    const int stride_in = 2 * d + 4;   // a block's line of the front inbox: u part, z_hat part, max |h|
+
+    const RowsSmem L = rows_smem(c.m, C, c.slot_bytes);
+    unsigned char* ring = dyn + L.ring;
+    float* h_s = reinterpret_cast<float*>(dyn + L.h);
+    uint16_t* vh_s = reinterpret_cast<uint16_t*>(dyn + L.vh);
+    float* lh_s = reinterpret_cast<float*>(dyn + L.lh);
+    int64_t* age_s = reinterpret_cast<int64_t*>(dyn + L.age);
+    int* cmax_s = reinterpret_cast<int*>(dyn + L.cmax);
+    uint16_t* wout = reinterpret_cast<uint16_t*>(dyn + L.wout);
+    uint16_t* vt = reinterpret_cast<uint16_t*>(dyn + L.vt);
+    uint16_t* gate = reinterpret_cast<uint16_t*>(dyn + L.gate);
+    float* swh = reinterpret_cast<float*>(dyn + L.swh);
+    float* sw_head = reinterpret_cast<float*>(dyn + L.sw_head);
+    float* sw_tail = reinterpret_cast<float*>(dyn + L.sw_tail);
+    float* norm_w = reinterpret_cast<float*>(dyn + L.norm_w);
+    float* cand_w = reinterpret_cast<float*>(dyn + L.cand_w);
+    float* fb2 = reinterpret_cast<float*>(dyn + L.fb2);
+    float* gate_b = reinterpret_cast<float*>(dyn + L.gate_b);
+    float* score_b = reinterpret_cast<float*>(dyn + L.score_b);
+    float* fb1p = reinterpret_cast<float*>(dyn + L.fb1p);
+    float* score_all = reinterpret_cast<float*>(dyn + L.score_all);
+    int* unit_all = reinterpret_cast<int*>(dyn + L.unit_all);
+    int64_t* age_all = reinterpret_cast<int64_t*>(dyn + L.age_all);
+    float* q_s = reinterpret_cast<float*>(dyn + L.q);
+    float* ue = reinterpret_cast<float*>(dyn + L.ue);
+    float* rowterm = reinterpret_cast<float*>(dyn + L.rowterm);
+    float* hold = reinterpret_cast<float*>(dyn + L.hold);
+    float* big = reinterpret_cast<float*>(dyn + L.big);
+    float* msg = reinterpret_cast<float*>(dyn + L.msg);
+    float* rms = reinterpret_cast<float*>(dyn + L.rms);
+    int* src = reinterpret_cast<int*>(dyn + L.src);
+    float* ew = reinterpret_cast<float*>(dyn + L.ew);
+    float* facc = reinterpret_cast<float*>(dyn + L.facc);
+    float* gacc = reinterpret_cast<float*>(dyn + L.gacc);
+    float* inbox_front = reinterpret_cast<float*>(dyn + L.inbox_front);
+    float* inbox_f = reinterpret_cast<float*>(dyn + L.inbox_f);
+    float* inbox_delta = reinterpret_cast<float*>(dyn + L.inbox_delta);
+    float* in_scal = reinterpret_cast<float*>(dyn + L.in_scal);
+    float* in_pre = reinterpret_cast<float*>(dyn + L.in_pre);
+    float* in_z = reinterpret_cast<float*>(dyn + L.in_z);
+    float* upd = reinterpret_cast<float*>(dyn + L.upd);
+    int* cell_of = reinterpret_cast<int*>(dyn + L.cell_of);
+    int* unit_of = reinterpret_cast<int*>(dyn + L.unit_of);
+    int* ulist = reinterpret_cast<int*>(dyn + L.ulist);
+    uint64_t* cand = reinterpret_cast<uint64_t*>(dyn + L.cand);
+    int* umask = reinterpret_cast<int*>(dyn + L.umask);
+    float* Fk = upd;
+    float* gp = upd + Ks * d;
+    float* ys = upd + 2 * Ks * d;
+    float* hnew = upd + 3 * Ks * d;
+    float* hb = upd + 4 * Ks * d;
+    float* dl = upd + 5 * Ks * d;
+    float* scale = upd + 6 * Ks * d;
+
+    const int cell0 = r * Nc;                 // the block's first cell
+    const int pre_cols = max(0, min(kFrontCols, H - r * kFrontCols));  // its columns that belong to S
+    const unsigned char* bank = static_cast<const unsigned char*>(c.m.rows_bank);
+    const unsigned char* front = static_cast<const unsigned char*>(c.m.rows_front);
+
+    // ---- once per window: barriers, the resident weights, the block's cells and their derived state
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kConsumers / 32);
+        }
+        hmax_local = 0;
+        n_units_s = 0;
+        failed_s = 0;
+    }
+    for (int e = tid; e < d * d; e += kRowThreads) {
+        wout[e] = bf16_bits(c.m.wout_t[e]);
+        vt[e] = bf16_bits(c.m.v_t[e]);
+    }
+    for (int e = tid; e < grows * d; e += kRowThreads) gate[e] = bf16_bits(c.m.gate_t[static_cast<int64_t>(r) * grows * d + e]);
+    for (int e = tid; e < d * M; e += kRowThreads) swh[e] = c.m.score_w_t[2 * d * M + e];
+    for (int e = tid; e < 2 * d * M; e += kRowThreads) sw_head[e] = c.m.score_w_t[e];
+    for (int e = tid; e < (1 + Sn) * M; e += kRowThreads) sw_tail[e] = c.m.score_w_t[3 * d * M + e];
+    for (int e = tid; e < 4 * d; e += kRowThreads) norm_w[e] = c.m.norm_w[e];
+    for (int e = tid; e < d; e += kRowThreads) {
+        cand_w[e] = c.m.cand_w[e];
+        gate_b[e] = c.m.gate_b[e];
+    }
+    for (int e = tid; e < 2 * d; e += kRowThreads) fb2[e] = c.m.f_b2[e];
+    for (int e = tid; e < M; e += kRowThreads) {
+        score_b[e] = c.m.score_b[e];
+        S.cost[e] = c.m.cost[e];
+    }
+    for (int e = tid; e < kFrontCols; e += kRowThreads) fb1p[e] = c.m.f_b1[r * kFrontCols + e];
+    const bool cut0 = c.io.reset[static_cast<int64_t>(row) * T] != 0;
+    {
+        const float* h0 = c.io.h0 + (static_cast<int64_t>(row) * N + cell0) * d;
+        for (int e = tid; e < Nc * d; e += kRowThreads) h_s[e] = cut0 ? 0.0f : h0[e];
+        const int64_t* a0 = c.io.age0 + static_cast<int64_t>(row) * N + cell0;
+        for (int n = tid; n < Nc; n += kRowThreads) age_s[n] = cut0 ? 0 : a0[n];
+        for (int x = tid; x < d; x += kRowThreads) q_s[x] = cut0 ? 0.0f : c.io.q0[static_cast<int64_t>(row) * d + x];
+        // the first position's inputs
+        const int64_t rt0 = static_cast<int64_t>(row) * T;
+        for (int e = tid; e < Nc * Sn; e += kRowThreads) in_scal[e] = c.io.scalars[(rt0 * N + cell0) * Sn + e];
+        for (int e = tid; e < pre_cols; e += kRowThreads) in_pre[e] = c.pre_s[rt0 * H + r * kFrontCols + e];
+        for (int x = tid; x < d; x += kRowThreads) in_z[x] = c.io.z[rt0 * d + x];
+    }
+    __syncthreads();
+    for (int o = tid; o < Nc * (M + d); o += kRowThreads) {
+        const int cell = o / (M + d), w = o - cell * (M + d);
+        const float* hr = h_s + cell * d;
+        float sum = 0.0f;
+        if (w < M) {
+            for (int x = 0; x < d; ++x) sum += bf16r(hr[x]) * swh[x * M + w];
+            lh_s[cell * M + w] = sum;
+        } else {
+            for (int x = 0; x < d; ++x) sum += bf16r(hr[x]) * bf16_value(vt[x * d + (w - M)]);
+            vh_s[cell * d + (w - M)] = bf16_bits(sum);
+        }
+    }
+    for (int n = tid; n < Nc; n += kRowThreads) {
+        int top = 0;
+        for (int x = 0; x < d; ++x) top = max(top, __float_as_int(fabsf(h_s[n * d + x])));
+        cmax_s[n] = top;
+    }
+    if (tape) {
+        const int64_t rec0 = static_cast<int64_t>(row) * (T + 1);
+        float* th = c.io.tape_h + (rec0 * N + cell0) * d;
+        for (int e = tid; e < Nc * d; e += kRowThreads) th[e] = h_s[e];
+        for (int n = tid; n < Nc; n += kRowThreads) c.io.tape_age[rec0 * N + cell0 + n] = age_s[n];
+        if (r == 0)
+            for (int x = tid; x < d; x += kRowThreads) c.io.tape_q[rec0 * d + x] = q_s[x];
+    }
+    uint32_t g_issue = 0, g_use = 0;   // copies issued (producer) / consumed (compute warps), in ring order
+    if (producer && lane == 0) {
+        for (int part = 0; part < 2; ++part) {
+            const uint32_t slot = g_issue % kStages;
+            mbar_expect_tx(&full[slot], c.front_bytes);
+            bulk_g2s(ring + slot * c.slot_bytes, front + (static_cast<size_t>(r) * 2 + part) * c.front_bytes, c.front_bytes, &full[slot]);
+            ++g_issue;
+        }
+    }
+    cl.sync();
+
+    for (int t = 0; t < T; ++t) {
+        const int64_t rt = static_cast<int64_t>(row) * T + t;
+        const bool last = t + 1 == T;
+        const bool clear = !last && c.io.reset[rt + 1] != 0;
+        // ---------------- A: the front MLPs on the block's columns
+        RMARK(0);
+        if (!producer) {
+            cp_async_wait_all();
+            if (tid < d) ue[tid] = bf16r(q_s[tid]);
+            consumer_sync();
+            float* act = big;                     // [256]
+            float* fpart = big + kFrontCols;      // [256 / d][2d]
+            {
+                const uint32_t slot = g_use % kStages;
+                ring_wait(&full[slot], (g_use / kStages) & 1u, c.status, &failed_s);
+                const uint16_t* w1c = reinterpret_cast<const uint16_t*>(ring + slot * c.slot_bytes);
+                const int col = tid, colg = r * kFrontCols + col;
+                float sum = 0.0f;
+#pragma unroll 8
+                for (int x = 0; x < d; ++x) sum += ue[x] * bf16_value(w1c[x * kFrontCols + col]);
+                const float pre = colg >= H ? fb1p[col] : in_pre[col];
+                act[col] = bf16r(gelu_erf(bf16r(sum + pre)));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[slot]);
+            }
+            consumer_sync();
+            {
+                const uint32_t slot = (g_use + 1) % kStages;
+                ring_wait(&full[slot], ((g_use + 1) / kStages) & 1u, c.status, &failed_s);
+                const uint16_t* w2c = reinterpret_cast<const uint16_t*>(ring + slot * c.slot_bytes);
+                const int x = tid % d, grp = tid / d;
+                const bool is_p = r * kFrontCols + grp * d >= H;
+                float sum = 0.0f;
+#pragma unroll 8
+                for (int cc = 0; cc < d; ++cc) sum += act[grp * d + cc] * bf16_value(w2c[(grp * d + cc) * d + x]);
+                fpart[grp * 2 * d + x] = is_p ? 0.0f : sum;
+                fpart[grp * 2 * d + d + x] = is_p ? sum : 0.0f;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[slot]);
+            }
+            g_use += 2;
+            consumer_sync();
+            if (tid < 2 * d) {
+                float tot = 0.0f;
+                for (int grp = 0; grp < kFrontCols / d; ++grp) tot += fpart[grp * 2 * d + tid];
+                for (int p = 0; p < C; ++p) peer(cl, inbox_front, p)[r * stride_in + tid] = tot;
+            }
+            if (tid == 0) peer(cl, inbox_front, 0)[r * stride_in + 2 * d] = __int_as_float(hmax_local);
+        }
+        RMARK(1);
+        cl.sync();   // 1
+        RMARK(2);
+        // ---------------- B: u, eps, the scorer on the block's cells
+        if (!producer) {
+            if (tid < 2 * d) {
+                float sum = 0.0f;
+                for (int p = 0; p < C; ++p) sum += inbox_front[p * stride_in + tid];
+                const float out = bf16r(sum + fb2[tid]);
+                ue[tid] = tid < d ? out : in_z[tid - d] - out;
+            }
+            if (r == 0 && tid == 0 && t > 0 && c.io.h_max) {
+                int mx = 0;
+                for (int p = 0; p < C; ++p) mx = max(mx, __float_as_int(inbox_front[p * stride_in + 2 * d]));
+                c.io.h_max[rt - 1] = __int_as_float(mx);
+            }
+            consumer_sync();
+            RMARK(14);
+            for (int j = warp; j < M; j += kConsumers / 32) {
+                float sum = 0.0f;
+                for (int x = lane; x < 2 * d; x += 32) sum += bf16r(ue[x]) * sw_head[x * M + j];
+                sum = warp_sum(sum);
+                if (lane == 0) rowterm[j] = sum;
+            }
+            consumer_sync();
+            RMARK(15);
+            const float lambda = c.m.lambda_cost;
+            const float age_div = static_cast<float>(c.m.age_max);
+            // four threads per cell, each with the units sub, sub + 4, ...; the quad then keeps the
+            // first maximiser (the higher score, the lower unit on a tie)
+            for (int i0 = 0; i0 < Nc; i0 += kConsumers / 4) {
+                const int i = i0 + (tid >> 2), sub = tid & 3;
+                float best = -INFINITY;
+                int arg = 0;
+                int64_t ag = 0;
+                if (i < Nc) {
+                    ag = age_s[i];
+                    float feat[17];   // the age term, then the scalars (S <= 16)
+                    feat[0] = bf16r(static_cast<float>(ag) / age_div);
+#pragma unroll
+                    for (int sI = 0; sI < 16; ++sI) feat[1 + sI] = sI < Sn ? bf16r(in_scal[i * Sn + sI]) : 0.0f;
+#pragma unroll
+                    for (int jj = 0; jj < kMaxMR / 4; ++jj) {
+                        const int j = sub + 4 * jj;
+                        if (j < M) {
+                            float acc = lh_s[i * M + j];
+#pragma unroll
+                            for (int sI = 0; sI < 17; ++sI)
+                                if (sI <= Sn) acc += feat[sI] * sw_tail[sI * M + j];
+                            const float logit = bf16r(acc + rowterm[j] + score_b[j]);
+                            if (c.io.logits) c.io.logits[(rt * N + cell0 + i) * M + j] = logit;
+                            const float sc = lambda > 0.0f ? __fsub_rn(logit, __fmul_rn(lambda, S.cost[j])) : logit;
+                            if (jj == 0 || sc > best) {
+                                best = sc;
+                                arg = j;
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int w = 1; w < 4; w <<= 1) {
+                    const float ob = __shfl_xor_sync(0xffffffffu, best, w);
+                    const int oa = __shfl_xor_sync(0xffffffffu, arg, w);
+                    if (ob > best || (ob == best && oa < arg)) {
+                        best = ob;
+                        arg = oa;
+                    }
+                }
+                if (i < Nc && sub < C) {   // thread `sub` of the quad writes block sub's copy
+                    peer(cl, score_all, sub)[cell0 + i] = best;
+                    peer(cl, unit_all, sub)[cell0 + i] = arg;
+                    peer(cl, age_all, sub)[cell0 + i] = ag;
+                }
+                if (i < Nc && C > 4 && sub == 0) {
+                    for (int p = 4; p < C; ++p) {
+                        peer(cl, score_all, p)[cell0 + i] = best;
+                        peer(cl, unit_all, p)[cell0 + i] = arg;
+                        peer(cl, age_all, p)[cell0 + i] = ag;
+                    }
+                }
+            }
+        }
+        RMARK(3);
+        cl.sync();   // 2
+        RMARK(4);
+        // ---------------- C: the decision (every block, on identical inputs). A cell's place in
+        // the scored order is the number of cells with a larger key, counted by the cell's thread
+        // against all keys: no rounds, no sort. One warp then finishes (budget, threshold, probes).
+        uint64_t* keys = cand;
+        int* stale_w = reinterpret_cast<int*>(cand + N);     // [8] cells older than age_max, per warp
+        int* old_rank = stale_w + 8;                          // [K] the same flag for the K best
+        if (!producer && !c.io.forced) {
+            int n_old = 0;
+            if (c.m.lambda_cost == 0.0f) {
+                // the scores are bf16 values here (rounded logits, no cost term): the low half of
+                // their order word carries nothing, so (score's high half, 0xffff - index) is a
+                // 32-bit key with the same order, unique per cell (N <= 2048)
+                uint32_t* key32 = reinterpret_cast<uint32_t*>(keys);   // [N] padded to a multiple of 4 with zeros
+                for (int i = tid; i < ((N + 3) & ~3); i += kConsumers)
+                    key32[i] = i < N ? ((float_order(score_all[i]) & 0xffff0000u) | (0xffffu - static_cast<uint32_t>(i))) : 0u;
+                if (tid == 0) next_key_s = 0ull;
+                consumer_sync();
+                const uint4* key4 = reinterpret_cast<const uint4*>(key32);
+                for (int i = tid; i < N; i += kConsumers) {
+                    const uint32_t mine = key32[i];
+                    int rank = 0;
+#pragma unroll 8
+                    for (int j4 = 0; j4 < (N + 3) >> 2; ++j4) {
+                        const uint4 o = key4[j4];
+                        rank += (o.x > mine) + (o.y > mine) + (o.z > mine) + (o.w > mine);
+                    }
+                    const bool old = age_all[i] > static_cast<int64_t>(c.m.age_max);
+                    n_old += old ? 1 : 0;
+                    if (rank < K) {
+                        S.order[rank] = i;
+                        old_rank[rank] = old ? 1 : 0;
+                    } else if (rank == K) {
+                        next_key_s = pack_key(score_all[i], i);
+                    }
+                }
+            } else {
+                for (int i = tid; i < N; i += kConsumers) keys[i] = pack_key(score_all[i], i);
+                if (tid == 0) next_key_s = 0ull;
+                consumer_sync();
+                for (int i = tid; i < N; i += kConsumers) {
+                    const uint64_t mine = keys[i];
+                    int rank = 0;
+#pragma unroll 8
+                    for (int j = 0; j < N; ++j) rank += keys[j] > mine ? 1 : 0;
+                    const bool old = age_all[i] > static_cast<int64_t>(c.m.age_max);
+                    n_old += old ? 1 : 0;
+                    if (rank < K) {
+                        S.order[rank] = i;
+                        old_rank[rank] = old ? 1 : 0;
+                    } else if (rank == K) {
+                        next_key_s = mine;
+                    }
+                }
+            }
+            n_old = __reduce_add_sync(0xffffffffu, n_old);
+            if (lane == 0) stale_w[warp] = n_old;
+            consumer_sync();
+        }
+        RMARK(16);
+        if (warp == 0) {
+            if (!c.io.forced) {
+                SelectParams P;
+                P.N = N; P.M = M; P.K = K; P.age_max = c.m.age_max; P.probes = c.m.probes;
+                P.reserved = 0; P.fixed_units = 0;
+                P.overhead = c.m.cell_overhead; P.shared_cost = c.m.shared_cost; P.limit = c.m.limit;
+                // the budget: costs summed in slot order, every lane follows the same running sum
+                const int cidx = lane < K ? S.order[lane] : 0;
+                const int u = unit_all[cidx];
+                const float cost = P.overhead + S.cost[u];
+                float running = 0.0f, mine_cum = 0.0f;
+                for (int i = 0; i < K; ++i) {
+                    running += __shfl_sync(0xffffffffu, cost, i);
+                    if (lane == i) mine_cum = running;
+                }
+                const bool ok = lane < K && P.shared_cost + mine_cum <= P.limit;
+                const unsigned okmask = __ballot_sync(0xffffffffu, ok);
+                const int n_valid = __popc(okmask);
+                if (lane < K) {
+                    S.out_cell[lane] = ok ? cidx : 0;
+                    S.out_unit[lane] = ok ? u : 0;
+                    S.out_flag[lane] = ok ? 1 : 0;
+                }
+                if (lane == 0) {
+                    const bool any = n_valid > 0;
+                    const float low = any ? score_all[S.order[n_valid - 1]] : INFINITY;
+                    float high;
+                    if (n_valid < K) high = score_all[S.order[n_valid]];
+                    else high = next_key_s ? score_all[key_cell(next_key_s)] : -INFINITY;
+                    S.theta = 0.5f * (low + high);
+                    S.n_valid = n_valid;
+                }
+                int n_force = 0;
+                if (P.probes) {
+                    const int total_old = __reduce_add_sync(0xffffffffu, lane < kConsumers / 32 ? stale_w[lane] : 0);
+                    const int chosen_old = __popc(__ballot_sync(0xffffffffu, lane < n_valid && old_rank[lane] != 0));
+                    const int n_stale = total_old - chosen_old;
+                    n_force = n_stale < n_valid ? n_stale : n_valid;
+                }
+                __syncwarp();
+                // a row with stale cells to refresh takes the one-warp routine from the scored order on
+                if (n_force > 0) select_finish_warp(P, score_all, unit_all, age_all, S, next_key_s);
+                RMARK(17);
+            } else {
+                for (int k = lane; k < K; k += 32) {
+                    const bool ok = c.io.valid[rt * K + k] != 0;
+                    S.out_cell[k] = ok ? static_cast<int>(c.io.cells[rt * K + k]) : 0;
+                    S.out_unit[k] = ok ? static_cast<int>(c.io.units[rt * K + k]) : 0;
+                    S.out_flag[k] = ok ? 1 : 0;
+                }
+            }
+            __syncwarp();
+            int my_unit = -1;
+            for (int k = lane; k < K; k += 32) {   // K <= 32: lane k holds slot k
+                const bool ok = (S.out_flag[k] & 1) != 0;
+                cell_of[k] = ok ? S.out_cell[k] : -1;
+                my_unit = ok ? S.out_unit[k] : -1;
+                unit_of[k] = my_unit;
+                if (r == 0 && !c.io.forced) {
+                    c.io.cells[rt * K + k] = S.out_cell[k];
+                    c.io.units[rt * K + k] = S.out_unit[k];
+                    c.io.valid[rt * K + k] = static_cast<uint8_t>(ok ? 1 : 0);
+                    c.io.refreshed[rt * K + k] = static_cast<uint8_t>((S.out_flag[k] >> 1) & 1);
+                }
+            }
+            if (r == 0 && !c.io.forced && lane == 0) c.io.theta[rt] = S.theta;
+            // the units in use, ascending, and each one's slots as a bit mask
+            int n = 0;
+            for (int j = 0; j < M; ++j) {
+                const unsigned mask = __ballot_sync(0xffffffffu, my_unit == j);
+                if (mask) {
+                    if (lane == 0) {
+                        ulist[n] = j;
+                        umask[n] = static_cast<int>(mask);
+                    }
+                    ++n;
+                }
+            }
+            if (lane == 0) n_units_s = n;
+            RMARK(18);
+        }
+        __syncthreads();
+        RMARK(5);
+        const int n_units = n_units_s;
+        // ---------------- D
+        if (producer) {
+            if (lane == 0) {
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                const int n_bank = n_units * 2;
+                const int total = n_bank + (last ? 0 : 2);
+                for (int i = 0; i < total; ++i) {
+                    const uint32_t slot = g_issue % kStages;
+                    if (g_issue >= kStages) ring_wait(&empty[slot], ((g_issue / kStages) - 1u) & 1u, c.status, &failed_s);
+                    const unsigned char* from;
+                    uint32_t bytes;
+                    if (i < n_bank) {
+                        const int j = ulist[i >> 1];
+                        from = bank + (static_cast<size_t>(j) * (H / 64) + r * 2 + (i & 1)) * c.bank_bytes;
+                        bytes = c.bank_bytes;
+                    } else {
+                        from = front + (static_cast<size_t>(r) * 2 + (i - n_bank)) * c.front_bytes;
+                        bytes = c.front_bytes;
+                    }
+                    mbar_expect_tx(&full[slot], bytes);
+                    bulk_g2s(ring + slot * c.slot_bytes, from, bytes, &full[slot]);
+                    ++g_issue;
+                }
+            }
+            __syncwarp();
+        } else {
+            // the next position's inputs, asynchronously
+            if (!last) {
+                prefetch_floats(in_scal, c.io.scalars + ((rt + 1) * N + cell0) * Sn, Nc * Sn, tid);
+                if (pre_cols > 0) prefetch_floats(in_pre, c.pre_s + (rt + 1) * H + r * kFrontCols, pre_cols, tid);
+                prefetch_floats(in_z, c.io.z + (rt + 1) * d, d, tid);
+            }
+            cp_async_commit();
+            for (int e = tid; e < K * D; e += kConsumers) {
+                const int k = e / D, jj = e - k * D;
+                const int cell = S.out_cell[k];
+                src[e] = c.m.pad_src[cell * D + jj];
+                ew[e] = bf16r(c.m.edge_w[cell * D + jj]);
+            }
+            for (int e = tid; e < K * d; e += kConsumers) {
+                const int k = e / d, x = e - k * d;
+                const int cell = S.out_cell[k];
+                hold[e] = peer(cl, h_s, cell / Nc)[(cell % Nc) * d + x];
+            }
+            consumer_sync();
+            for (int e = tid; e < K * d; e += kConsumers) {
+                const int k = e / d, x = e - k * d;
+                float sum = 0.0f;
+                for (int jj = 0; jj < D; ++jj) {   // edge order; the sources' V h rows at their owners
+                    const int sc = src[k * D + jj];
+                    sum += bf16_value(peer(cl, vh_s, sc / Nc)[(sc % Nc) * d + x]) * ew[k * D + jj];
+                }
+                msg[e] = bf16r(sum);
+            }
+            consumer_sync();
+            for (int k = warp; k < K; k += kConsumers / 32) {
+                float sq = 0.0f;
+                for (int jx = lane; jx < 4 * d; jx += 32) {
+                    const int blk = jx / d, x = jx - blk * d;
+                    const float v = blk == 0 ? ue[x] : blk == 1 ? ue[d + x] : blk == 2 ? hold[k * d + x] : msg[k * d + x];
+                    sq += v * v;
+                }
+                sq = warp_sum(sq);
+                if (lane == 0) rms[k] = rsqrtf(sq / static_cast<float>(4 * d) + c.m.norm_eps);
+            }
+            consumer_sync();
+            RMARK(6);
+            float* v = big;         // [K][4d]
+            for (int e = tid; e < K * 4 * d; e += kConsumers) {
+                const int k = e / (4 * d), jx = e - k * 4 * d;
+                const int blk = jx / d, x = jx - blk * d;
+                const float val = blk == 0 ? ue[x] : blk == 1 ? ue[d + x] : blk == 2 ? hold[k * d + x] : msg[k * d + x];
+                v[e] = bf16r(val * rms[k] * norm_w[jx]);
+            }
+            if (rec) {
+                for (int e = tid; e < K * d; e += kConsumers) {
+                    const int k = e / d;
+                    if (k % C == r) {
+                        c.io.rec_h_old[rt * K * d + e] = hold[e];
+                        c.io.rec_m[rt * K * d + e] = msg[e];
+                    }
+                }
+                for (int k = tid; k < K; k += kConsumers)
+                    if (k % C == r) c.io.rec_rms[rt * K + k] = rms[k];
+            }
+            consumer_sync();
+            // the gate's partial sum over the block's input rows
+            {
+                const int x = tid % d, grp = tid / d, ngrp = kConsumers / d;
+                for (int k = grp; k < K; k += ngrp) {
+                    float sum = 0.0f;
+                    if (cell_of[k] >= 0) {
+                        const float* vk = v + k * 4 * d + r * grows;
+#pragma unroll 8
+                        for (int xi = 0; xi < grows; ++xi) sum += vk[xi] * bf16_value(gate[xi * d + x]);
+                    }
+                    gacc[k * d + x] = sum;
+                }
+            }
+            RMARK(7);
+            // the units' two layers on the streamed chunks: warp w owns the chunk's columns 8w .. 8w+7
+            float f0[kMaxK], f1[kMaxK];
+#pragma unroll
+            for (int k = 0; k < kMaxK; ++k) f0[k] = f1[k] = 0.0f;
+            for (int ui = 0; ui < n_units; ++ui) {
+                const int j = ulist[ui];
+                const unsigned mask = static_cast<unsigned>(umask[ui]);
+                const int ns = __popc(mask);
+                for (int b = 0; b < 2; ++b) {
+                    const int colg = r * 128 + b * 64 + warp * 8 + (lane & 7);   // the hidden column of unit j
+                    const float bias = c.m.b1[j * H + colg];
+                    const uint32_t slot = g_use % kStages;
+                    ring_wait(&full[slot], (g_use / kStages) & 1u, c.status, &failed_s);
+                    ++g_use;
+                    const unsigned char* chunk = ring + slot * c.slot_bytes;
+                    const uint4* W1s = reinterpret_cast<const uint4*>(chunk);
+                    const uint4* W2s = reinterpret_cast<const uint4*>(chunk + c.w1_bytes);
+                    float* rh = rec ? c.io.rec_hidden + rt * K * H + colg : nullptr;
+                    switch (ns) {
+                        case 1: unit_stage<D_, 1>(W1s, W2s, v, mask, bias, rh, H, warp, lane, f0, f1); break;
+                        case 2: unit_stage<D_, 2>(W1s, W2s, v, mask, bias, rh, H, warp, lane, f0, f1); break;
+                        case 3: unit_stage<D_, 3>(W1s, W2s, v, mask, bias, rh, H, warp, lane, f0, f1); break;
+                        case 4: unit_stage<D_, 4>(W1s, W2s, v, mask, bias, rh, H, warp, lane, f0, f1); break;
+                        case 5: unit_stage<D_, 5>(W1s, W2s, v, mask, bias, rh, H, warp, lane, f0, f1); break;
+                        case 6: unit_stage<D_, 6>(W1s, W2s, v, mask, bias, rh, H, warp, lane, f0, f1); break;
+                        case 7: unit_stage<D_, 7>(W1s, W2s, v, mask, bias, rh, H, warp, lane, f0, f1); break;
+                        default: unit_stage<D_, 8>(W1s, W2s, v, mask, bias, rh, H, warp, lane, f0, f1); break;
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty[slot]);
+                }
+            }
+            RMARK(8);
+            // the block's partial of every slot's second layer: the warps' partials meet in the ring
+            // slot of the last chunk consumed (the producer's next copies go to the other two), are
+            // added in warp order and go straight to the slots' owners with the gate's partial
+            consumer_sync();   // every warp is done reading that slot
+            {
+                float* Fw = reinterpret_cast<float*>(ring + ((g_use + kStages - 1) % kStages) * c.slot_bytes);   // [8][K][d]
+                const int x0 = lane, x1 = lane + 32;
+#pragma unroll
+                for (int k = 0; k < kMaxK; ++k) {
+                    if (k < K) {
+                        if (x0 < d) Fw[(warp * K + k) * d + x0] = f0[k];
+                        if (x1 < d) Fw[(warp * K + k) * d + x1] = f1[k];
+                    }
+                }
+                consumer_sync();
+                for (int e = tid; e < K * 2 * d; e += kConsumers) {
+                    const int k = e / (2 * d), xx = e - k * 2 * d;
+                    float val;
+                    if (xx < d) {
+                        val = 0.0f;
+                        for (int w = 0; w < kConsumers / 32; ++w) val += Fw[(w * K + k) * d + xx];
+                    } else {
+                        val = gacc[k * d + xx - d];
+                    }
+                    peer(cl, inbox_f, k % C)[(r * Ks + k / C) * 2 * d + xx] = val;
+                }
+                // the slot goes back to the TMA: order these generic accesses before its next bulk copy
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            }
+        }
+        RMARK(9);
+        cl.sync();   // 3
+        RMARK(10);
+        // ---------------- E: the update of the block's slots (k = kl C + r)
+        if (!producer) {
+            for (int e = tid; e < Ks * d; e += kConsumers) {
+                const int kl = e / d, x = e - kl * d, k = kl * C + r;
+                const bool ok = k < K && cell_of[k] >= 0;
+                float F = 0.0f, G = 0.0f;
+                for (int p = 0; p < C; ++p) {   // the blocks' partial sums in rank order
+                    F += inbox_f[(p * Ks + kl) * 2 * d + x];
+                    G += inbox_f[(p * Ks + kl) * 2 * d + d + x];
+                }
+                Fk[e] = ok ? bf16r(F + c.m.b2[unit_of[k] * d + x]) : 0.0f;
+                gp[e] = ok ? bf16r(G + gate_b[x]) : 0.0f;
+            }
+            consumer_sync();
+            RMARK(19);
+            for (int e = tid; e < Ks * d; e += kConsumers) {
+                const int kl = e / d, x = e - kl * d;
+                float sum = 0.0f;
+#pragma unroll 8
+                for (int xi = 0; xi < d; ++xi) sum += Fk[kl * d + xi] * bf16_value(wout[xi * d + x]);
+                ys[e] = bf16r(sum);
+            }
+            consumer_sync();
+            RMARK(20);
+            for (int kl = warp; kl < Ks; kl += kConsumers / 32) {
+                float sq = 0.0f;
+                for (int x = lane; x < d; x += 32) sq += ys[kl * d + x] * ys[kl * d + x];
+                sq = warp_sum(sq);
+                if (lane == 0) scale[kl] = rsqrtf(sq / static_cast<float>(d) + c.m.cand_eps);
+            }
+            consumer_sync();
+            RMARK(21);
+            for (int e = tid; e < Ks * d; e += kConsumers) {
+                const int kl = e / d, x = e - kl * d, k = kl * C + r;
+                if (k >= K) continue;
+                const bool ok = cell_of[k] >= 0;
+                float value = 0.0f, change = 0.0f, cv = 0.0f, bv = 0.0f;
+                if (ok) {
+                    const float old = hold[k * d + x];
+                    cv = tanhf(ys[e] * scale[kl] * cand_w[x]);
+                    bv = sigmoid_f(gp[e]);
+                    value = (1.0f - bv) * old + bv * cv;
+                    change = value - old;
+                    c.io.h_sel[(rt * K + k) * d + x] = value;
+                }
+                hnew[e] = value;
+                hb[e] = bf16r(value);
+                dl[e] = change;
+                if (rec) {
+                    c.io.rec_c[(rt * K + k) * d + x] = cv;
+                    c.io.rec_b[(rt * K + k) * d + x] = bv;
+                    c.io.rec_y[(rt * K + k) * d + x] = ys[e];
+                    c.io.rec_gate_pre[(rt * K + k) * d + x] = gp[e];
+                }
+                for (int p = 0; p < C; ++p) peer(cl, inbox_delta, p)[k * d + x] = change;
+                if (ok) {   // also before a reset: the position's max |h| and a padded slot's h_sel read it
+                    const int cell = cell_of[k];
+                    peer(cl, h_s, cell / Nc)[(cell % Nc) * d + x] = value;
+                }
+            }
+            consumer_sync();
+            {
+                // the written cells' derived state, at their owners
+                for (int o = tid; o < Ks * (M + d); o += kConsumers) {
+                    const int kl = o / (M + d), w = o - kl * (M + d), k = kl * C + r;
+                    if (k >= K || cell_of[k] < 0) continue;
+                    const int cell = cell_of[k], owner = cell / Nc, cc = cell % Nc;
+                    const float* hr = hb + kl * d;
+                    float sum = 0.0f;
+                    if (w < M) {
+                        for (int x = 0; x < d; ++x) sum += hr[x] * swh[x * M + w];
+                        peer(cl, lh_s, owner)[cc * M + w] = sum;
+                    } else {
+                        for (int x = 0; x < d; ++x) sum += hr[x] * bf16_value(vt[x * d + (w - M)]);
+                        peer(cl, vh_s, owner)[cc * d + (w - M)] = bf16_bits(sum);
+                    }
+                }
+                for (int kl = warp; kl < Ks; kl += kConsumers / 32) {
+                    const int k = kl * C + r;
+                    if (k >= K || cell_of[k] < 0) continue;
+                    int top = 0;
+                    for (int x = lane; x < d; x += 32) top = max(top, __float_as_int(fabsf(hnew[kl * d + x])));
+                    for (int w = 16; w > 0; w >>= 1) top = max(top, __shfl_xor_sync(0xffffffffu, top, w));
+                    if (lane == 0) peer(cl, cmax_s, cell_of[k] / Nc)[cell_of[k] % Nc] = top;
+                }
+            }
+        }
+        RMARK(11);
+        cl.sync();   // 4
+        RMARK(12);
+        // ---------------- F: summary, ages, the tape's next record, the next reset
+        if (!producer) {
+            if (tid == 0) hmax_local = 0;
+            for (int x = tid; x < d; x += kConsumers) {
+                float sum = 0.0f;
+                for (int k = 0; k < K; ++k) sum += inbox_delta[k * d + x];   // slot order
+                const float after = q_s[x] + sum / static_cast<float>(N);
+                if (r == 0) {
+                    c.io.qs[rt * d + x] = after;
+                    if (tape) c.io.tape_q[(static_cast<int64_t>(row) * (T + 1) + t + 1) * d + x] = clear ? 0.0f : after;
+                }
+                q_s[x] = clear ? 0.0f : after;
+            }
+            if (r == 0) {
+                // a padded slot reads cell 0 after the position (reference compile.py: the tape's h_sel)
+                for (int e = tid; e < K * d; e += kConsumers) {
+                    const int k = e / d, x = e - k * d;
+                    if (cell_of[k] < 0) c.io.h_sel[(rt * K + k) * d + x] = h_s[x];
+                }
+            }
+            consumer_sync();
+            {
+                int top = 0;
+                for (int n = tid; n < Nc; n += kConsumers) top = max(top, cmax_s[n]);
+                for (int w = 16; w > 0; w >>= 1) top = max(top, __shfl_xor_sync(0xffffffffu, top, w));
+                if (lane == 0) atomicMax(&hmax_local, top);   // a maximum: any order gives the same bits
+            }
+            for (int n = tid; n < Nc; n += kConsumers) {
+                int64_t a = age_s[n] + 1;
+                for (int k = 0; k < K; ++k)
+                    if (cell_of[k] == cell0 + n) a = 0;
+                if (clear) a = 0;
+                age_s[n] = a;
+                if (tape) c.io.tape_age[(static_cast<int64_t>(row) * (T + 1) + t + 1) * N + cell0 + n] = a;
+            }
+            consumer_sync();
+            if (clear) {
+                for (int e = tid; e < Nc * d; e += kConsumers) {
+                    h_s[e] = 0.0f;
+                    vh_s[e] = 0;
+                }
+                for (int e = tid; e < Nc * M; e += kConsumers) lh_s[e] = 0.0f;
+                for (int n = tid; n < Nc; n += kConsumers) cmax_s[n] = 0;
+                consumer_sync();
+            }
+            if (tape) {
+                float4* dst = reinterpret_cast<float4*>(c.io.tape_h + ((static_cast<int64_t>(row) * (T + 1) + t + 1) * N + cell0) * d);
+                const float4* from = reinterpret_cast<const float4*>(h_s);
+                for (int e = tid; e < (Nc * d) >> 2; e += kConsumers) dst[e] = from[e];
+            }
+        }
+        RMARK(13);
+    }
+    // the last position's max |h|, and the state the window ends in
+    if (!producer && tid == 0) peer(cl, inbox_front, 0)[r * stride_in + 2 * d] = __int_as_float(hmax_local);
+    cl.sync();
+    if (!producer) {
+        if (r == 0 && tid == 0) {
+            if (c.io.h_max) {
+                int mx = 0;
+                for (int p = 0; p < C; ++p) mx = max(mx, __float_as_int(inbox_front[p * stride_in + 2 * d]));
+                c.io.h_max[static_cast<int64_t>(row) * T + T - 1] = __int_as_float(mx);
+            }
+            int last_reset = 0;
+            for (int s = 0; s < T; ++s)
+                if (c.io.reset[static_cast<int64_t>(row) * T + s]) last_reset = s + 1;
+            c.io.pos[row] = last_reset > 0 ? T + 1 - last_reset : c.io.pos[row] + T;
+        }
+        if (!tape) {
+            float* h0 = c.io.h0 + (static_cast<int64_t>(row) * N + cell0) * d;
+            for (int e = tid; e < Nc * d; e += kConsumers) h0[e] = h_s[e];
+            int64_t* a0 = c.io.age0 + static_cast<int64_t>(row) * N + cell0;
+            for (int n = tid; n < Nc; n += kConsumers) a0[n] = age_s[n];
+            if (r == 0)
+                for (int x = tid; x < d; x += kConsumers) c.io.q0[static_cast<int64_t>(row) * d + x] = q_s[x];
+        }
+    }
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------------
+// Host side: when the model and the window fit, hsnw_window_forward runs this kernel instead of
+// the phases. Returns HSNW_OK when launched, -1 when the shape does not fit (the caller falls back),
+// an error code otherwise.
+// ------------------------------------------------------------------------------------------------
+static bool rows_shape(const HsnwModel& m, RowsCtx* c) {
+    if (!m.prod_bf16 || m.phases_only || !m.rows_bank || !m.rows_front) return false;
+    if (m.H % 128) return false;
+    const int C = m.H / 128;
+    if (C != 1 && C != 2 && C != 4 && C != 8) return false;
+    if (m.N % C || (4 * m.d) % C || m.N > 2048) return false;
+    if (m.d != 16 && m.d != 32 && m.d != 64) return false;
+    if (m.K > kMaxK || m.M > kMaxMR || m.K < 1 || m.S > 16) return false;
+    c->C = C;
+    c->Nc = m.N / C;
+    c->Ks = (m.K + C - 1) / C;
+    c->gate_rows = 4 * m.d / C;
+    c->w1_bytes = static_cast<uint32_t>(512 * m.d);
+    c->bank_bytes = static_cast<uint32_t>(640 * m.d);
+    c->front_bytes = static_cast<uint32_t>(512 * m.d);
+    c->slot_bytes = c->bank_bytes;
+    return true;
+}
+
+int hsnw_rows_forward(const HsnwModel* model, const HsnwForward* io, const float* pre_s, int* status, cudaStream_t stream) {
+    RowsCtx c;
+    if (!rows_shape(*model, &c)) return -1;
+    const RowsSmem L = rows_smem(*model, c.C, c.slot_bytes);
+    if (L.total + 2048 > hsnw_max_shared()) return -1;
+    c.m = *model;
+    c.io = *io;
+    c.pre_s = pre_s;
+    c.status = status;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(io->B) * c.C, 1, 1);
+    cfg.blockDim = dim3(kRowThreads, 1, 1);
+    cfg.dynamicSmemBytes = L.total;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(c.C);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    void (*kernel)(RowsCtx) = model->d == 64 ? k_rows_fwd<64> : model->d == 32 ? k_rows_fwd<32> : k_rows_fwd<16>;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess || clusters < 1) {
+        cudaGetLastError();
+        return -1;
+    }
+    hsnw_profile_mark(HSNW_K_ROW, stream);
+    if (cudaLaunchKernelEx(&cfg, kernel, c) != cudaSuccess) return hsnw_check_launch("window_forward (row clusters)");
+    return hsnw_check_launch("window_forward (row clusters)");
+}
+
+void hsnw_rows_set_attributes() {
+    if (!hsnw_opt_in(reinterpret_cast<const void*>(k_rows_fwd<64>), "rows_fwd<64>")
+        || !hsnw_opt_in(reinterpret_cast<const void*>(k_rows_fwd<32>), "rows_fwd<32>")
+        || !hsnw_opt_in(reinterpret_cast<const void*>(k_rows_fwd<16>), "rows_fwd<16>"))
+        hsnw_attribute_failed();
+}

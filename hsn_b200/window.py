@@ -83,6 +83,7 @@ class WindowModel:
         norm_eps: float = 1e-6,
         cand_eps: float = 1e-6,
         tensor_cores: bool = True,
+        row_clusters: bool = True,
     ) -> "WindowModel":
         if prod not in ("fp32", "bf16"):
             raise ValueError(f"prod must be 'fp32' or 'bf16', got {prod!r}")
@@ -136,11 +137,14 @@ class WindowModel:
         }
         if prod == "bf16" and tensor_cores:
             packed.update(_umma_images(w["w1"], w["w2"], packed["gate_t"]))
+        if prod == "bf16" and row_clusters and H % 128 == 0 and d % 8 == 0:
+            packed.update(_row_images(w["w1"], w["w2"], packed["f_w1q_t"], packed["f_w2_t"]))
         struct = _lib.HsnwModel()
         dims = dict(N=N, d=d, K=int(k), H=H, M=M, D=D, S=S, dc=dc)
         for name, value in dims.items():
             setattr(struct, name, value)
         struct.prod_bf16 = int(prod == "bf16")
+        struct.phases_only = int(not row_clusters)
         struct.probes = int(bool(probes))
         struct.age_max = int(min(age_max, 2**31 - 1))
         struct.lambda_cost, struct.cell_overhead = float(lambda_cost), float(cell_overhead)
@@ -154,7 +158,7 @@ class WindowModel:
 
     @staticmethod
     def from_oracle_weights(W: Any, *, device: torch.device | str = "cuda", prod: str = "fp32",
-                            tensor_cores: bool = True) -> "WindowModel":
+                            tensor_cores: bool = True, row_clusters: bool = True) -> "WindowModel":
         """From an object with the weights as attributes and the router's scalars (the fixtures'
         ``WindowWeights``): a convenience of the tests and the benchmark."""
         weights = {key: getattr(W, key) for key in _WEIGHT_KEYS}
@@ -162,6 +166,7 @@ class WindowModel:
             weights, k=W.k, device=device, prod=prod, age_max=W.age_max, probes=W.probes,
             lambda_cost=W.lambda_cost, cell_overhead=W.cell_overhead, shared_cost=W.shared_cost,
             limit=W.limit, norm_eps=W.norm_eps, cand_eps=W.cand_eps, tensor_cores=tensor_cores,
+            row_clusters=row_clusters,
         )  # fmt: skip
 
     @staticmethod
@@ -191,6 +196,25 @@ class WindowModel:
             limit=float(model.cfg.budget) * (1.0 + 1e-5), norm_eps=float(cell.norm.eps),
             cand_eps=float(cell.cand_norm.eps),
         )  # fmt: skip
+
+
+def _row_images(w1: Tensor, w2: Tensor, f_w1q_t: Tensor, f_w2_t: Tensor) -> dict[str, Tensor]:
+    """bf16 images for the per-row cluster kernel (``hsn_b200/csrc/window_rows.cu``): one chunk per
+    unit and 64-column block of its hidden layer, ``W1`` as ``[4d/8][64][8]`` then ``W2`` as
+    ``[8][d][8]``; and per block of the cluster its 256 columns of the merged front first layer
+    ``[d][256]`` followed by the same columns' rows of the second layer ``[256][d]``."""
+    M, in4, H = (int(n) for n in w1.shape)
+    d = int(w2.shape[2])
+    bf = torch.bfloat16
+    nb = H // 64
+    a = w1.reshape(M, in4 // 8, 8, nb, 64).permute(0, 3, 1, 4, 2).to(bf).reshape(M, nb, -1)  # [M,nb,(4d/8)*64*8]
+    b = w2.reshape(M, nb, 8, 8, d).permute(0, 1, 2, 4, 3).to(bf).reshape(M, nb, -1)  # [M,nb,8*d*8]
+    bank = torch.cat([a, b], dim=2).contiguous()
+    C = H // 128
+    f1 = f_w1q_t.reshape(d, C, 256).permute(1, 0, 2).to(bf).reshape(C, -1)  # [C, d*256]
+    f2 = f_w2_t.reshape(C, 256, d).to(bf).reshape(C, -1)  # [C, 256*d]
+    front = torch.stack([f1, f2], dim=1).contiguous()  # [C, 2, 256 d]
+    return {"rows_bank": bank, "rows_front": front}
 
 
 def _umma_images(w1: Tensor, w2: Tensor, gate_t: Tensor) -> dict[str, Tensor]:

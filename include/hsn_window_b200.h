@@ -95,7 +95,7 @@ typedef struct HsnwModel {
     int32_t prod_bf16;      /* 0: fp32 products; 1: bf16 operands, fp32 accumulation */
     int32_t probes;         /* refresh probes on (router.py:1788-1850) */
     int32_t age_max;
-    int32_t reserved_;      /* keep 0 */
+    int32_t phases_only;    /* 1: never use the per-row cluster kernel (hsnw_window_forward picks it when it fits) */
     float lambda_cost, cell_overhead, shared_cost, limit; /* limit = budget * (1 + 1e-5) */
     float norm_eps, cand_eps;
     const float* s_w1zc_t;  /* [d + dc, H]  shared.fc1 rows of z, then of ctx */
@@ -134,6 +134,15 @@ typedef struct HsnwModel {
     const void* umma_bw_w2;
     const void* umma_bw_w1;
     const void* umma_bw_gate;
+    /* bf16 images for the per-row cluster kernel (prod_bf16, H a multiple of 128; null: not used).
+     * With C = H / 128 blocks of a row's cluster:
+     * rows_bank [M][H/64] chunks, one per unit and 64-column block of its hidden layer: first
+     *   W1 as [4d/8][64][8] (element (input x, column c) at ((x/8) 64 + c) 8 + x%8), then W2 as
+     *   [8][d][8] (element (column c, output x) at ((c/8) d + x) 8 + c%8);
+     * rows_front [C][2] chunks: the block's 256 columns of the merged front first layer
+     *   f_w1q_t as [d][256], then the same columns' rows of f_w2_t as [256][d]. */
+    const void* rows_bank;
+    const void* rows_front;
 } HsnwModel;
 
 /* Inputs, tape and record of a forward sweep. Row-major, contiguous. Null = not wanted, for the
