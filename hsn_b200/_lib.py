@@ -33,7 +33,7 @@ MODEL_FLOATS = ("lambda_cost", "cell_overhead", "shared_cost", "limit", "norm_ep
 MODEL_POINTERS = (
     "s_w1zc_t", "f_w1q_t", "f_b1", "f_w2_t", "f_b2", "score_w_t", "score_b", "v_t", "wout_t", "gate_t",
     "gate_b", "norm_w", "cand_w", "w1", "b1", "w2", "b2", "pad_src", "edge_w", "cost",
-    "umma_w1", "umma_gate", "umma_w2", "umma_bw_w2", "umma_bw_w1", "umma_bw_gate", "rows_bank", "rows_front",
+    "umma_w1", "umma_gate", "umma_w2", "umma_bw_w2", "umma_bw_w1", "umma_bw_gate", "rows_bank", "rows_front", "rows_bank_bw",
 )  # fmt: skip
 
 

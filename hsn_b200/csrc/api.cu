@@ -135,6 +135,7 @@ extern "C" int hsnw_prepare(int device) {
     hsnw_forward_set_attributes();
     hsnw_backward_set_attributes();
     hsnw_rows_set_attributes();
+    hsnw_rows_bwd_set_attributes();
     const cudaError_t status = cudaGetLastError();
     if (previous >= 0 && previous != device) cudaSetDevice(previous);
     if (!attributes_ok) return HSNW_E_CUDA;  // the message names the kernel

@@ -21,6 +21,10 @@ void hsnw_forward_set_attributes();
 void hsnw_backward_set_attributes();
 void hsnw_ops_set_attributes();
 void hsnw_rows_set_attributes();
+void hsnw_rows_bwd_set_attributes();
+struct HsnwBackward;
+// The reverse sweep by one persistent cluster per row (window_rows_bwd.cu): same return convention.
+int hsnw_rows_backward(const HsnwModel* model, const HsnwBackward* io, cudaStream_t stream);
 struct HsnwModel;
 struct HsnwForward;
 // The forward sweep by one persistent cluster per row (window_rows.cu): HSNW_OK when launched, -1 when

@@ -651,6 +651,11 @@ extern "C" int hsnw_window_backward(const HsnwModel* model, const HsnwBackward* 
     const bool full = io->full_cut != 0;
     if (!full && (!io->y || !io->gate_pre || !io->m || !io->rms || !io->hidden || !io->units))
         return hsnw_fail(HSNW_E_ARG, "window_backward: the state gradient needs the round's record");
+    if (!io->full_cut && io->y && io->gate_pre && io->m && io->rms && io->hidden && io->units) {
+        // one persistent cluster per row when the shape fits (window_rows_bwd.cu)
+        const int rc_rows = hsnw_rows_backward(model, io, static_cast<cudaStream_t>(stream_));
+        if (rc_rows >= 0) return rc_rows;
+    }
     const size_t cap = hsnw_max_shared() - 4096;
     const size_t sh_head = head_shared(m), sh_mid = mid_shared(m), sh_tail = tail_shared(m);
     const size_t sh_both = sh_head > sh_tail ? sh_head : sh_tail;

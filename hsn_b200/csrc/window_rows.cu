@@ -37,15 +37,12 @@
 #include "select.cuh"
 #include "stage.cuh"
 #include "host_util.h"
+#include "rows.cuh"
 
-#include <cooperative_groups.h>
-
-namespace cg = cooperative_groups;
 using namespace hsnw;
 
 namespace {
 
-constexpr int kConsumers = 256;       // compute threads (8 warps)
 constexpr int kRowThreads = 288;      // + the producer warp
 constexpr int kStages = 3;            // ring depth
 constexpr int kMaxK = 8;              // slots (register accumulators per slot)
@@ -152,48 +149,6 @@ __host__ __device__ inline RowsSmem rows_smem(const HsnwModel& m, int C, uint32_
 #else
 #define RMARK(i) do { } while (0)
 #endif
-
-template <class T>
-__device__ __forceinline__ T* peer(cg::cluster_group& cl, T* p, int rank) {
-    return cl.map_shared_rank(p, rank);
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(bar)) : "memory");
-}
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumers) : "memory"); }
-__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
-__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
-
-// A bounded wait on a ring barrier. After the first wait of the block that ran out (recorded in
-// *failed and in the status word) every later wait returns at once, so a broken pipeline costs one
-// time-out, not one per stage: the kernel still reaches every cluster barrier and ends.
-__device__ __forceinline__ void ring_wait(uint64_t* bar, uint32_t parity, int* status, volatile int* failed) {
-    if (*failed) return;
-    const uint32_t addr = smem_addr(bar);
-    for (uint32_t spin = 0; spin < (1u << 20); ++spin) {
-        uint32_t done;
-        asm volatile(
-            "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-            : "=r"(done)
-            : "r"(addr), "r"(parity)
-            : "memory");
-        if (done) return;
-    }
-    *failed = 1;
-    atomicExch(status, 1);
-}
-
-// floats [0, n) from global to shared memory by the 256 compute threads, asynchronously.
-__device__ __forceinline__ void prefetch_floats(float* dst, const float* src, int n, int tid) {
-    const bool vec = ((reinterpret_cast<uintptr_t>(src) | static_cast<uintptr_t>(smem_addr(dst))) & 15) == 0;
-    if (vec) {
-        const int n4 = n >> 2;
-        for (int e = tid; e < n4; e += kConsumers) cp_async16(dst + 4 * e, src + 4 * e);
-        for (int e = (n4 << 2) + tid; e < n; e += kConsumers) cp_async4(dst + e, src + e);
-    } else {
-        for (int e = tid; e < n; e += kConsumers) cp_async4(dst + e, src + e);
-    }
-}
 
 // One streamed chunk (unit j, 64 hidden columns) for the NS slots that run unit j, by one warp
 // on the chunk's columns 8 warp .. 8 warp + 7: lane (c8 = lane & 7, pg = lane >> 3) multiplies

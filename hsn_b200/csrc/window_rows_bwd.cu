@@ -1,0 +1,653 @@
+// The reverse sweep of a window (state gradient) as ONE persistent kernel: a thread-block cluster
+// per batch row walks t = T-1 .. 0 with the row's state cotangent A [N, d] resident in the
+// cluster's shared memory (block r owns the cells [r N/C, (r+1) N/C)) and R [d] replicated.
+// The counterpart of window_rows.cu for window_bwd.cu's phases; same arithmetic and rounding
+// points (reference python/hsn/train/state_gradient.py:288-485), other orders of fp32 partial sums.
+//
+// Per position, four cluster barriers:
+//   H   the slots' owners (slot k belongs to block k mod C): R += D_t, the gated carry through
+//       A[cell] at the cell's owner, dc, db, the candidate's and the gate's backward, d_unit = dy
+//       W_out; d_unit and dg go to every block                                          | sync 1
+//   M   every block, on its 128 hidden columns of the units the slots ran (two streamed chunks a
+//       unit: W2's rows and the state rows of W1): the transposed second layer, the activation's
+//       derivative at the recorded pre-activation, the norm's inner product, the transposed first
+//       layer on the 2d state columns; and its share of the gate's transposed linear; partial sums
+//       go to the slots' owners                                                         | sync 2
+//   T1  the owners: the cell norm's backward ds, dvm = dm V; both go to every block     | sync 3
+//   T2  every block adds, for its own cells, the slots' own cotangents and then every edge's
+//       share in slot order (the fixed order of window_bwd.cu's tail); R += P_t; the reset | sync 4
+// The decisions are recorded, so the chunks of the next position are requested (TMA bulk copies
+// into a 3-deep ring) while this one computes; the position's records are prefetched one position
+// ahead with cp.async. Every ring wait is bounded.
+#include "../../include/hsn_window_b200.h"
+#include "common.cuh"
+#include "stage.cuh"
+#include "host_util.h"
+#include "rows.cuh"
+
+using namespace hsnw;
+
+namespace {
+
+constexpr int kStagesB = 3;
+constexpr int kMaxKB = 8;
+constexpr int kMaxMB = 16;
+
+struct RowsBwdCtx {
+    HsnwModel m;
+    HsnwBackward io;
+    int C, Nc, Ks;
+    uint32_t bank_bytes, w2_bytes;   // a chunk, its W2 part
+};
+
+__host__ __device__ inline size_t up16b(size_t v) { return (v + 15) & ~static_cast<size_t>(15); }
+
+struct RowsBwdSmem {
+    size_t ring, A, wout, vt, gate, norm_w, cand_w, gate_b, b1, R, Rs, rec[2], hid[2], dq[2], dec[2], du_all, dg_all,
+        inbox_dv, inbox_sig, inbox_g, ds_all, dvm_all, red, own, total;
+};
+// rec: per owned slot c, b, h_old, y, gate_pre, m, d_h_sel [7][Ks][d], then rms [Ks]
+// dec: cell_of [K], unit_of [K], tgt [K D], ew [K D], ulist [16], umask [16], n_units
+__host__ __device__ inline RowsBwdSmem rows_bwd_smem(const HsnwModel& m, int C, uint32_t slot_bytes) {
+    RowsBwdSmem L;
+    const size_t d = m.d, N = m.N, K = m.K, M = m.M, D = m.D, Nc = N / C, Ks = (K + C - 1) / C;
+    size_t o = 0;
+    auto take = [&o](size_t bytes) {
+        const size_t at = o;
+        o += up16b(bytes);
+        return at;
+    };
+    L.ring = take(static_cast<size_t>(kStagesB) * slot_bytes);
+    L.A = take(4 * Nc * d);
+    L.wout = take(2 * d * d);
+    L.vt = take(2 * d * d);
+    L.gate = take(2 * (2 * d / C) * d);
+    L.norm_w = take(4 * 2 * d);
+    L.cand_w = take(4 * d);
+    L.gate_b = take(4 * d);
+    L.b1 = take(4 * M * 128);
+    L.R = take(4 * d);
+    L.Rs = take(4 * d);
+    for (int s = 0; s < 2; ++s) {
+        L.rec[s] = take(4 * (7 * Ks * d + Ks) + 16);
+        L.hid[s] = take(4 * K * 128);
+        L.dq[s] = take(4 * 2 * d);
+        L.dec[s] = take(4 * (2 * K + 2 * K * D + 2 * kMaxMB + 4));
+    }
+    L.du_all = take(4 * K * d);
+    L.dg_all = take(4 * K * d);
+    L.inbox_dv = take(4 * C * Ks * 2 * d);
+    L.inbox_sig = take(4 * C * Ks + 16);
+    L.inbox_g = take(4 * Ks * 2 * d);
+    L.ds_all = take(4 * K * d);
+    L.dvm_all = take(4 * K * d);
+    L.red = take(4 * 8 * K * (2 * d + 1));
+    L.own = take(4 * Ks * (6 * d + 8));   // dzs, ysv, sgs, dy, ds [2d] per owned slot; rho, dot, sig_gate, back
+    L.total = o;
+    return L;
+}
+
+// One streamed chunk of the reverse sweep (unit j, 64 hidden columns) for the NS slots that ran
+// unit j, by one warp on the chunk's columns 8 warp .. 8 warp + 7. du: the slots' d_unit rows
+// (bf16 values) [K][d]; hid: the recorded pre-activations of those columns, hid[k * 128 + column
+// of the block]. The warp's partial of dv (outputs lane, lane + 32, ... of the 2d state columns) and
+// of the norm's inner product are added to dv[k][.] / sig[k].
+template <int D_, int NS>
+__device__ __forceinline__ void bwd_stage(const uint4* W2s, const uint4* W1s, const float* du, const float* hid,
+                                          int hid_col, float bias, unsigned mask, int warp, int lane,
+                                          float (&dv)[kMaxKB][(2 * D_ + 31) / 32], float (&sig)[kMaxKB]) {
+    constexpr int NO = (2 * D_ + 31) / 32;   // state outputs per lane
+    const int c8 = warp * 8 + (lane & 7), pg = lane >> 3;
+    int ks[NS];
+    const float4* up[NS];
+    float h0[NS], h1[NS];
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+        ks[s] = __fns(mask, 0, s + 1);
+        up[s] = reinterpret_cast<const float4*>(du + ks[s] * D_);
+        h0[s] = h1[s] = 0.0f;
+    }
+    // the transposed second layer: dact[column] = sum_x d_unit[x] W2[column][x]
+#pragma unroll
+    for (int p = pg; p < D_ / 8; p += 4) {
+        const uint4 w = W2s[p * 64 + c8];
+        const float w0 = bf16_lo(w.x), w1 = bf16_hi(w.x), w2 = bf16_lo(w.y), w3 = bf16_hi(w.y);
+        const float w4 = bf16_lo(w.z), w5 = bf16_hi(w.z), w6 = bf16_lo(w.w), w7 = bf16_hi(w.w);
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            const float4 a = up[s][2 * p], b = up[s][2 * p + 1];
+            h0[s] += a.x * w0;
+            h1[s] += a.y * w1;
+            h0[s] += a.z * w2;
+            h1[s] += a.w * w3;
+            h0[s] += b.x * w4;
+            h1[s] += b.y * w5;
+            h0[s] += b.z * w6;
+            h1[s] += b.w * w7;
+        }
+    }
+    // the state rows of W1 for this warp's 8 columns: plane `warp` of [8][2d][8]
+    float wr[NO][8];
+#pragma unroll
+    for (int o = 0; o < NO; ++o) {
+        const int i = lane + 32 * o;
+        uint4 w = make_uint4(0u, 0u, 0u, 0u);
+        if (i < 2 * D_) w = W1s[warp * 2 * D_ + i];
+        wr[o][0] = bf16_lo(w.x); wr[o][1] = bf16_hi(w.x); wr[o][2] = bf16_lo(w.y); wr[o][3] = bf16_hi(w.y);
+        wr[o][4] = bf16_lo(w.z); wr[o][5] = bf16_hi(w.z); wr[o][6] = bf16_lo(w.w); wr[o][7] = bf16_hi(w.w);
+    }
+    float part[NS][NO], inner[NS];
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+        float sum = h0[s] + h1[s];
+        sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+        const float hv = hid[ks[s] * 128 + hid_col];
+        const float dh = bf16r(sum * gelu_erf_grad(hv));
+        // the norm's inner product over the warp's 8 columns (lanes 0..7 hold them)
+        float in = dh * (hv - bias);
+        in += __shfl_xor_sync(0xffffffffu, in, 1);
+        in += __shfl_xor_sync(0xffffffffu, in, 2);
+        in += __shfl_xor_sync(0xffffffffu, in, 4);
+        inner[s] = in;
+        const float a0 = __shfl_sync(0xffffffffu, dh, 0), a1 = __shfl_sync(0xffffffffu, dh, 1);
+        const float a2 = __shfl_sync(0xffffffffu, dh, 2), a3 = __shfl_sync(0xffffffffu, dh, 3);
+        const float a4 = __shfl_sync(0xffffffffu, dh, 4), a5 = __shfl_sync(0xffffffffu, dh, 5);
+        const float a6 = __shfl_sync(0xffffffffu, dh, 6), a7 = __shfl_sync(0xffffffffu, dh, 7);
+#pragma unroll
+        for (int o = 0; o < NO; ++o)
+            part[s][o] = (a0 * wr[o][0] + a1 * wr[o][1]) + (a2 * wr[o][2] + a3 * wr[o][3])
+                + (a4 * wr[o][4] + a5 * wr[o][5]) + (a6 * wr[o][6] + a7 * wr[o][7]);
+    }
+#pragma unroll
+    for (int k = 0; k < kMaxKB; ++k) {
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            if (ks[s] == k) {
+                sig[k] += inner[s];
+#pragma unroll
+                for (int o = 0; o < NO; ++o) dv[k][o] += part[s][o];
+            }
+        }
+    }
+}
+
+template <int D_>
+__global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    __shared__ __align__(8) uint64_t full[kStagesB], empty[kStagesB];
+    __shared__ int failed_s;
+
+    cg::cluster_group cl = cg::this_cluster();
+    constexpr int d = D_, two = 2 * D_, NO = (2 * D_ + 31) / 32;
+    const int C = c.C, r = static_cast<int>(cl.block_rank());
+    const int row = blockIdx.x / C;
+    const int N = c.m.N, K = c.m.K, M = c.m.M, D = c.m.D, H = c.m.H;
+    const int T = c.io.T, Nc = c.Nc, Ks = c.Ks;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int gcols = two / C;          // the gate's state outputs of this block
+    const int cell0 = r * Nc;
+    const int U = K + K * D;
+
+    const RowsBwdSmem L = rows_bwd_smem(c.m, C, c.bank_bytes);
+    unsigned char* ring = dyn + L.ring;
+    float* A_s = reinterpret_cast<float*>(dyn + L.A);
+    uint16_t* wout = reinterpret_cast<uint16_t*>(dyn + L.wout);
+    uint16_t* vt = reinterpret_cast<uint16_t*>(dyn + L.vt);
+    uint16_t* gate = reinterpret_cast<uint16_t*>(dyn + L.gate);
+    float* norm_w = reinterpret_cast<float*>(dyn + L.norm_w);
+    float* cand_w = reinterpret_cast<float*>(dyn + L.cand_w);
+    float* gate_b = reinterpret_cast<float*>(dyn + L.gate_b);
+    float* b1s = reinterpret_cast<float*>(dyn + L.b1);
+    float* R_s = reinterpret_cast<float*>(dyn + L.R);
+    float* Rs = reinterpret_cast<float*>(dyn + L.Rs);
+    float* du_all = reinterpret_cast<float*>(dyn + L.du_all);
+    float* dg_all = reinterpret_cast<float*>(dyn + L.dg_all);
+    float* inbox_dv = reinterpret_cast<float*>(dyn + L.inbox_dv);
+    float* inbox_sig = reinterpret_cast<float*>(dyn + L.inbox_sig);
+    float* inbox_g = reinterpret_cast<float*>(dyn + L.inbox_g);
+    float* ds_all = reinterpret_cast<float*>(dyn + L.ds_all);
+    float* dvm_all = reinterpret_cast<float*>(dyn + L.dvm_all);
+    float* red = reinterpret_cast<float*>(dyn + L.red);
+    float* own = reinterpret_cast<float*>(dyn + L.own);
+    float* dzs = own;
+    float* ysv = own + Ks * d;
+    float* sgs = own + 2 * Ks * d;
+    float* dy = own + 3 * Ks * d;
+    float* ds = own + 4 * Ks * d;          // [Ks][2d]
+    float* rho = own + 6 * Ks * d;
+    float* dot = rho + Ks;
+    float* sig_gate = dot + Ks;
+    float* back = sig_gate + Ks;
+    const unsigned char* bank = static_cast<const unsigned char*>(c.m.rows_bank_bw);
+
+    auto rec_of = [&](int buf) { return reinterpret_cast<float*>(dyn + L.rec[buf]); };
+    auto hid_of = [&](int buf) { return reinterpret_cast<float*>(dyn + L.hid[buf]); };
+    auto dq_of = [&](int buf) { return reinterpret_cast<float*>(dyn + L.dq[buf]); };
+    auto dec_of = [&](int buf) { return reinterpret_cast<int*>(dyn + L.dec[buf]); };
+    // a position's decision block: cell_of [K], unit_of [K], tgt [K D], ew [K D] (floats), ulist [16],
+    // umask [16], n_units
+    const int o_unit = K, o_tgt = 2 * K, o_ew = 2 * K + K * D, o_ulist = 2 * K + 2 * K * D, o_umask = o_ulist + kMaxMB,
+              o_n = o_umask + kMaxMB;
+
+    // the records of position t, asynchronously, into buffer t & 1
+    auto prefetch = [&](int t) {
+        const int buf = t & 1;
+        const int64_t rt = static_cast<int64_t>(row) * T + t;
+        float* rc = rec_of(buf);
+        const float* srcs[7] = {c.io.c, c.io.b, c.io.h_old, c.io.y, c.io.gate_pre, c.io.m, c.io.d_h_sel};
+        for (int e = tid; e < 7 * Ks * (d / 4); e += kConsumers) {
+            const int a = e / (Ks * (d / 4)), rem = e - a * Ks * (d / 4), kl = rem / (d / 4), x4 = rem - kl * (d / 4);
+            const int k = kl * C + r;
+            if (k < K && srcs[a]) cp_async16(rc + (a * Ks + kl) * d + 4 * x4, srcs[a] + (rt * K + k) * d + 4 * x4);
+        }
+        float* hd = hid_of(buf);
+        for (int e = tid; e < K * 32; e += kConsumers) {
+            const int k = e >> 5, c4 = e & 31;
+            cp_async16(hd + k * 128 + 4 * c4, c.io.hidden + (rt * K + k) * H + r * 128 + 4 * c4);
+        }
+        float* q = dq_of(buf);
+        for (int e = tid; e < 2 * (d / 4); e += kConsumers) {
+            const int which = e / (d / 4), x4 = e - which * (d / 4);
+            const float* from = which == 0 ? c.io.d_q_post : c.io.d_q_pre;
+            if (from) cp_async16(q + which * d + 4 * x4, from + rt * d + 4 * x4);
+        }
+        cp_async_commit();
+    };
+    // the decision of position t: each thread loads what it will store (decision_store), so the
+    // loads' latency is spent under other work
+    int ld_cell = -1, ld_unit = -1, ld_tgt = -1;
+    float ld_ew = 0.0f, ld_rms = 0.0f;
+    auto decision_load = [&](int t) {
+        const int64_t rt = static_cast<int64_t>(row) * T + t;
+        if (tid < K) {
+            const bool ok = c.io.valid[rt * K + tid] != 0;
+            ld_cell = ok ? static_cast<int>(c.io.cells[rt * K + tid]) : -1;
+            ld_unit = ok ? static_cast<int>(c.io.units[rt * K + tid]) : -1;
+        }
+        if (tid >= 32 && tid < 32 + K * D) {
+            const int e = tid - 32, k = e / D, jj = e - k * D;
+            const bool ok = c.io.valid[rt * K + k] != 0;
+            const int n = ok ? static_cast<int>(c.io.cells[rt * K + k]) : 0;
+            ld_tgt = ok ? c.m.pad_src[n * D + jj] : -1;
+            ld_ew = ok ? c.m.edge_w[n * D + jj] : 0.0f;
+        }
+        if (tid >= 128 && tid < 128 + Ks) {
+            const int k = (tid - 128) * C + r;
+            ld_rms = k < K ? c.io.rms[rt * K + k] : 0.0f;
+        }
+    };
+    auto decision_store = [&](int t) {
+        int* dc_ = dec_of(t & 1);
+        if (tid < K) {
+            dc_[tid] = ld_cell;
+            dc_[o_unit + tid] = ld_unit;
+        }
+        if (tid >= 32 && tid < 32 + K * D) {
+            dc_[o_tgt + tid - 32] = ld_tgt;
+            reinterpret_cast<float*>(dc_)[o_ew + tid - 32] = ld_ew;
+        }
+        if (tid >= 128 && tid < 128 + Ks) rec_of(t & 1)[7 * Ks * d + tid - 128] = ld_rms;
+    };
+    // the units a position's slots ran, ascending, with each one's slots as a bit mask (warp 0)
+    auto unit_lists = [&](int t) {
+        int* dc_ = dec_of(t & 1);
+        const int my_unit = lane < K ? dc_[o_unit + lane] : -1;
+        int n = 0;
+        for (int j = 0; j < M; ++j) {
+            const unsigned mask = __ballot_sync(0xffffffffu, my_unit == j);
+            if (mask) {
+                if (lane == 0) {
+                    dc_[o_ulist + n] = j;
+                    dc_[o_umask + n] = static_cast<int>(mask);
+                }
+                ++n;
+            }
+        }
+        if (lane == 0) dc_[o_n] = n;
+        __syncwarp();
+    };
+
+    if (tid == 0) {
+        for (int s = 0; s < kStagesB; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kConsumers / 32);
+        }
+        failed_s = 0;
+    }
+    for (int e = tid; e < d * d; e += kConsumers) {
+        wout[e] = bf16_bits(c.m.wout_t[e]);
+        vt[e] = bf16_bits(c.m.v_t[e]);
+    }
+    for (int e = tid; e < gcols * d; e += kConsumers) gate[e] = bf16_bits(c.m.gate_t[static_cast<int64_t>(two + r * gcols) * d + e]);
+    for (int e = tid; e < two; e += kConsumers) norm_w[e] = c.m.norm_w[two + e];
+    for (int e = tid; e < d; e += kConsumers) {
+        cand_w[e] = c.m.cand_w[e];
+        gate_b[e] = c.m.gate_b[e];
+        R_s[e] = c.io.R[static_cast<int64_t>(row) * d + e];
+    }
+    for (int e = tid; e < M * 128; e += kConsumers) b1s[e] = c.m.b1[(e >> 7) * H + r * 128 + (e & 127)];
+    {
+        const float* A = c.io.A + (static_cast<int64_t>(row) * N + cell0) * d;
+        for (int e = tid; e < Nc * d; e += kConsumers) A_s[e] = A[e];
+    }
+    for (int buf = 0; buf < 2; ++buf) {   // optional inputs that are absent read as zeros
+        for (int e = tid; e < 7 * Ks * d + Ks; e += kConsumers) rec_of(buf)[e] = 0.0f;
+        for (int e = tid; e < 2 * d; e += kConsumers) dq_of(buf)[e] = 0.0f;
+    }
+    __syncthreads();
+    prefetch(T - 1);
+    decision_load(T - 1);
+    decision_store(T - 1);
+    __syncthreads();
+    if (warp == 0) unit_lists(T - 1);
+    // the chunk stream: thread 0 keeps up to three copies in flight, across positions
+    uint32_t g_issue = 0, g_use = 0;
+    int cur_t = T - 1, cur_i = 0;       // the next chunk to request: position, index in its 2 n_units chunks
+    int ready_t = T - 1;                // decisions are known down to this position
+    auto issue_ahead = [&]() {
+        while (g_issue < g_use + kStagesB && cur_t >= ready_t && cur_t >= 0) {
+            const int* dc_ = dec_of(cur_t & 1);
+            const int n_chunks = 2 * dc_[o_n];
+            if (cur_i >= n_chunks) {
+                --cur_t;
+                cur_i = 0;
+                continue;
+            }
+            const uint32_t slot = g_issue % kStagesB;
+            if (g_issue >= kStagesB) ring_wait(&empty[slot], ((g_issue / kStagesB) - 1u) & 1u, nullptr, &failed_s);
+            const int j = dc_[o_ulist + (cur_i >> 1)];
+            const unsigned char* from = bank + (static_cast<size_t>(j) * (H / 64) + r * 2 + (cur_i & 1)) * c.bank_bytes;
+            mbar_expect_tx(&full[slot], c.bank_bytes);
+            bulk_g2s(ring + slot * c.bank_bytes, from, c.bank_bytes, &full[slot]);
+            ++g_issue;
+            ++cur_i;
+        }
+    };
+    __syncthreads();
+    if (tid == 0) issue_ahead();
+    cl.sync();
+
+    const float n_f = static_cast<float>(N);
+    for (int t = T - 1; t >= 0; --t) {
+        const int64_t rt = static_cast<int64_t>(row) * T + t;
+        const int buf = t & 1;
+        float* rc = rec_of(buf);
+        const float* hd = hid_of(buf);
+        const float* q = dq_of(buf);
+        const int* dc_ = dec_of(buf);
+        const float* ew = reinterpret_cast<const float*>(dc_) + o_ew;
+        const bool cut = c.io.reset[rt] != 0;
+        // ---------------- H
+        cp_async_wait_all();
+        __syncthreads();
+        if (t > 0) {
+            prefetch(t - 1);
+            decision_load(t - 1);
+        }
+        if (tid < d) Rs[tid] = R_s[tid] + q[tid];
+        __syncthreads();
+        for (int e = tid; e < Ks * d; e += kConsumers) {
+            const int kl = e / d, x = e - kl * d, k = kl * C + r;
+            if (k >= K) continue;
+            const int n = dc_[k];
+            float dcv = 0.0f, dbv = 0.0f, dz = 0.0f, dgv = 0.0f, yv = 0.0f, sgv = 0.0f;
+            if (n >= 0) {
+                float* a = peer(cl, A_s, n / Nc) + (n % Nc) * d + x;
+                const float carried = *a + rc[(6 * Ks + kl) * d + x];
+                const float share = Rs[x] / n_f;
+                const float g = carried + share;
+                const float cv = rc[(0 * Ks + kl) * d + x], gt = rc[(1 * Ks + kl) * d + x];
+                dcv = gt * g;
+                dbv = (cv - rc[(2 * Ks + kl) * d + x]) * g;
+                *a = (1.0f - gt) * carried - gt * share;
+                dz = cand_w[x] * (dcv * (1.0f - cv * cv));
+                dgv = dbv * gt * (1.0f - gt);
+                yv = rc[(3 * Ks + kl) * d + x];
+                sgv = dgv * (rc[(4 * Ks + kl) * d + x] - gate_b[x]);
+            }
+            c.io.dc[(rt * K + k) * d + x] = dcv;
+            c.io.db[(rt * K + k) * d + x] = dbv;
+            dzs[e] = dz;
+            ysv[e] = yv;
+            sgs[e] = sgv;
+            const float dgb = bf16r(dgv);
+            for (int p = 0; p < C; ++p) peer(cl, dg_all, p)[k * d + x] = dgb;
+        }
+        __syncthreads();
+        for (int kl = warp; kl < Ks; kl += kConsumers / 32) {
+            float sq = 0.0f, dt = 0.0f, s = 0.0f;
+            for (int x = lane; x < d; x += 32) {
+                const float yv = ysv[kl * d + x];
+                sq += yv * yv;
+                dt += yv * dzs[kl * d + x];
+                s += sgs[kl * d + x];
+            }
+            sq = warp_sum(sq);
+            dt = warp_sum(dt);
+            s = warp_sum(s);
+            if (lane == 0) {
+                rho[kl] = rsqrtf(sq / static_cast<float>(d) + c.m.cand_eps);
+                dot[kl] = dt / static_cast<float>(d);
+                sig_gate[kl] = s;
+            }
+        }
+        __syncthreads();
+        for (int e = tid; e < Ks * d; e += kConsumers) {
+            const int kl = e / d, k = kl * C + r;
+            const float rr = rho[kl];
+            dy[e] = (k < K && dc_[k] >= 0) ? rr * dzs[e] - rr * rr * rr * ysv[e] * dot[kl] : 0.0f;
+        }
+        __syncthreads();
+        for (int e = tid; e < Ks * d; e += kConsumers) {
+            const int kl = e / d, i = e - kl * d, k = kl * C + r;
+            if (k >= K) continue;
+            float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll 8
+            for (int x = 0; x < d; x += 2) {
+                s0 += dy[kl * d + x] * bf16_value(wout[i * d + x]);
+                s1 += dy[kl * d + x + 1] * bf16_value(wout[i * d + x + 1]);
+            }
+            const float dub = bf16r(s0 + s1);
+            for (int p = 0; p < C; ++p) peer(cl, du_all, p)[k * d + i] = dub;
+        }
+        cl.sync();   // 1
+        // ---------------- M
+        if (t > 0) decision_store(t - 1);
+        __syncthreads();
+        if (warp == 0) {
+            if (t > 0) {
+                unit_lists(t - 1);
+                ready_t = t - 1;
+            }
+            if (lane == 0) issue_ahead();
+            __syncwarp();
+        }
+        {
+            // the gate's transposed linear, this block's state outputs
+            const int k = tid / gcols, il = tid - k * gcols;
+            if (k < K) {
+                float s0 = 0.0f, s1 = 0.0f;
+                if (dc_[k] >= 0) {
+#pragma unroll 8
+                    for (int x = 0; x < d; x += 2) {
+                        s0 += dg_all[k * d + x] * bf16_value(gate[il * d + x]);
+                        s1 += dg_all[k * d + x + 1] * bf16_value(gate[il * d + x + 1]);
+                    }
+                }
+                peer(cl, inbox_g, k % C)[(k / C) * two + r * gcols + il] = s0 + s1;
+            }
+        }
+        float dv[kMaxKB][NO], sig[kMaxKB];
+#pragma unroll
+        for (int k = 0; k < kMaxKB; ++k) {
+            sig[k] = 0.0f;
+#pragma unroll
+            for (int o = 0; o < NO; ++o) dv[k][o] = 0.0f;
+        }
+        const int n_units = dc_[o_n];
+        for (int ui = 0; ui < n_units; ++ui) {
+            const int j = dc_[o_ulist + ui];
+            const unsigned mask = static_cast<unsigned>(dc_[o_umask + ui]);
+            const int ns = __popc(mask);
+            for (int b = 0; b < 2; ++b) {
+                const int hid_col = b * 64 + warp * 8 + (lane & 7);
+                const float bias = b1s[j * 128 + hid_col];
+                const uint32_t slot = g_use % kStagesB;
+                ring_wait(&full[slot], (g_use / kStagesB) & 1u, nullptr, &failed_s);
+                ++g_use;
+                const unsigned char* chunk = ring + slot * c.bank_bytes;
+                const uint4* W2s = reinterpret_cast<const uint4*>(chunk);
+                const uint4* W1s = reinterpret_cast<const uint4*>(chunk + c.w2_bytes);
+                switch (ns) {
+                    case 1: bwd_stage<D_, 1>(W2s, W1s, du_all, hd, hid_col, bias, mask, warp, lane, dv, sig); break;
+                    case 2: bwd_stage<D_, 2>(W2s, W1s, du_all, hd, hid_col, bias, mask, warp, lane, dv, sig); break;
+                    case 3: bwd_stage<D_, 3>(W2s, W1s, du_all, hd, hid_col, bias, mask, warp, lane, dv, sig); break;
+                    case 4: bwd_stage<D_, 4>(W2s, W1s, du_all, hd, hid_col, bias, mask, warp, lane, dv, sig); break;
+                    case 5: bwd_stage<D_, 5>(W2s, W1s, du_all, hd, hid_col, bias, mask, warp, lane, dv, sig); break;
+                    case 6: bwd_stage<D_, 6>(W2s, W1s, du_all, hd, hid_col, bias, mask, warp, lane, dv, sig); break;
+                    case 7: bwd_stage<D_, 7>(W2s, W1s, du_all, hd, hid_col, bias, mask, warp, lane, dv, sig); break;
+                    default: bwd_stage<D_, 8>(W2s, W1s, du_all, hd, hid_col, bias, mask, warp, lane, dv, sig); break;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[slot]);
+                if (tid == 0) issue_ahead();
+                __syncwarp();
+            }
+        }
+        // the warps' partials, added in warp order, go to the slots' owners
+#pragma unroll
+        for (int k = 0; k < kMaxKB; ++k) {
+            if (k < K) {
+#pragma unroll
+                for (int o = 0; o < NO; ++o)
+                    if (lane + 32 * o < two) red[(warp * K + k) * (two + 1) + lane + 32 * o] = dv[k][o];
+                if (lane == 0) red[(warp * K + k) * (two + 1) + two] = sig[k];
+            }
+        }
+        __syncthreads();
+        for (int e = tid; e < K * (two + 1); e += kConsumers) {
+            const int k = e / (two + 1), i = e - k * (two + 1);
+            float sum = 0.0f;
+            for (int w = 0; w < kConsumers / 32; ++w) sum += red[(w * K + k) * (two + 1) + i];
+            if (i < two) peer(cl, inbox_dv, k % C)[(r * Ks + k / C) * two + i] = sum;
+            else peer(cl, inbox_sig, k % C)[r * Ks + k / C] = sum;
+        }
+        cl.sync();   // 2
+        // ---------------- T1: the owners' slots
+        if (tid < Ks) {
+            const int kl = tid;
+            float sigma = sig_gate[kl];
+            for (int p = 0; p < C; ++p) sigma += inbox_sig[p * Ks + kl];
+            const float rm = rc[7 * Ks * d + kl];
+            back[kl] = rm * rm / static_cast<float>(4 * d) * sigma;
+        }
+        __syncthreads();
+        for (int e = tid; e < Ks * two; e += kConsumers) {
+            const int kl = e / two, i = e - kl * two, k = kl * C + r;
+            float out = 0.0f;
+            if (k < K && dc_[k] >= 0) {
+                float sum = 0.0f;
+                for (int p = 0; p < C; ++p) sum += inbox_dv[(p * Ks + kl) * two + i];
+                sum += inbox_g[kl * two + i];
+                const float state = i < d ? rc[(2 * Ks + kl) * d + i] : rc[(5 * Ks + kl) * d + i - d];
+                out = rc[7 * Ks * d + kl] * (norm_w[i] * sum) - back[kl] * state;
+            }
+            ds[e] = out;
+        }
+        __syncthreads();
+        for (int e = tid; e < Ks * d; e += kConsumers) {
+            const int kl = e / d, i = e - kl * d, k = kl * C + r;
+            if (k >= K) continue;
+            float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll 8
+            for (int x = 0; x < d; x += 2) {
+                s0 += ds[kl * two + d + x] * bf16_value(vt[i * d + x]);
+                s1 += ds[kl * two + d + x + 1] * bf16_value(vt[i * d + x + 1]);
+            }
+            const float dvm = s0 + s1, own_ds = ds[kl * two + i];
+            for (int p = 0; p < C; ++p) {
+                peer(cl, dvm_all, p)[k * d + i] = dvm;
+                peer(cl, ds_all, p)[k * d + i] = own_ds;
+            }
+        }
+        cl.sync();   // 3
+        // ---------------- T2: this block's cells; thread (x, g) takes the targets n = g (mod groups)
+        {
+            const int x = tid % d, g = tid / d, groups = kConsumers / d;
+            for (int u = 0; u < U; ++u) {
+                const int n = u < K ? dc_[u] : dc_[o_tgt + u - K];
+                if (n < cell0 || n >= cell0 + Nc || (n % groups) != g) continue;
+                const float add = u < K ? ds_all[u * d + x] : ew[u - K] * dvm_all[((u - K) / D) * d + x];
+                A_s[(n - cell0) * d + x] += add;
+            }
+            if (tid < d) R_s[tid] = cut ? 0.0f : Rs[tid] + q[d + tid];
+        }
+        if (cut) {
+            __syncthreads();
+            for (int e = tid; e < Nc * d; e += kConsumers) A_s[e] = 0.0f;
+        }
+        cl.sync();   // 4
+    }
+    {
+        float* A = c.io.A + (static_cast<int64_t>(row) * N + cell0) * d;
+        for (int e = tid; e < Nc * d; e += kConsumers) A[e] = A_s[e];
+        if (r == 0)
+            for (int x = tid; x < d; x += kConsumers) c.io.R[static_cast<int64_t>(row) * d + x] = R_s[x];
+    }
+}
+
+}  // namespace
+
+static bool rows_bwd_shape(const HsnwModel& m, RowsBwdCtx* c) {
+    if (!m.prod_bf16 || m.phases_only || !m.rows_bank_bw) return false;
+    if (m.H % 128) return false;
+    const int C = m.H / 128;
+    if (C != 1 && C != 2 && C != 4 && C != 8) return false;
+    if (m.N % C || (2 * m.d) % C || kConsumers % (2 * m.d / C)) return false;
+    if (m.d != 16 && m.d != 32 && m.d != 64) return false;
+    if (m.K > kMaxKB || m.M > kMaxMB || m.K < 1 || m.K * m.D > 96 || m.K * (2 * m.d / C) > kConsumers) return false;
+    c->C = C;
+    c->Nc = m.N / C;
+    c->Ks = (m.K + C - 1) / C;
+    c->w2_bytes = static_cast<uint32_t>(128 * m.d);
+    c->bank_bytes = static_cast<uint32_t>(384 * m.d);
+    return true;
+}
+
+int hsnw_rows_backward(const HsnwModel* model, const HsnwBackward* io, cudaStream_t stream) {
+    RowsBwdCtx c;
+    if (io->full_cut || !rows_bwd_shape(*model, &c)) return -1;
+    const RowsBwdSmem L = rows_bwd_smem(*model, c.C, c.bank_bytes);
+    if (L.total + 1024 > hsnw_max_shared()) return -1;
+    c.m = *model;
+    c.io = *io;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(io->B) * c.C, 1, 1);
+    cfg.blockDim = dim3(kConsumers, 1, 1);
+    cfg.dynamicSmemBytes = L.total;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(c.C);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    void (*kernel)(RowsBwdCtx) = model->d == 64 ? k_rows_bwd<64> : model->d == 32 ? k_rows_bwd<32> : k_rows_bwd<16>;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess || clusters < 1) {
+        cudaGetLastError();
+        return -1;
+    }
+    hsnw_profile_mark(HSNW_K_MID, stream);
+    if (cudaLaunchKernelEx(&cfg, kernel, c) != cudaSuccess) return hsnw_check_launch("window_backward (row clusters)");
+    return hsnw_check_launch("window_backward (row clusters)");
+}
+
+void hsnw_rows_bwd_set_attributes() {
+    if (!hsnw_opt_in(reinterpret_cast<const void*>(k_rows_bwd<64>), "rows_bwd<64>")
+        || !hsnw_opt_in(reinterpret_cast<const void*>(k_rows_bwd<32>), "rows_bwd<32>")
+        || !hsnw_opt_in(reinterpret_cast<const void*>(k_rows_bwd<16>), "rows_bwd<16>"))
+        hsnw_attribute_failed();
+}

@@ -214,7 +214,11 @@ def _row_images(w1: Tensor, w2: Tensor, f_w1q_t: Tensor, f_w2_t: Tensor) -> dict
     f1 = f_w1q_t.reshape(d, C, 256).permute(1, 0, 2).to(bf).reshape(C, -1)  # [C, d*256]
     f2 = f_w2_t.reshape(C, 256, d).to(bf).reshape(C, -1)  # [C, 256*d]
     front = torch.stack([f1, f2], dim=1).contiguous()  # [C, 2, 256 d]
-    return {"rows_bank": bank, "rows_front": front}
+    # the reverse sweep: W2 [M,H,d] as [d/8][64][8] per block, W1's state rows [2d,H] as [8][2d][8]
+    ba = w2.reshape(M, nb, 64, d // 8, 8).permute(0, 1, 3, 2, 4).to(bf).reshape(M, nb, -1)
+    bb = w1[:, 2 * d :, :].reshape(M, 2 * d, nb, 8, 8).permute(0, 2, 3, 1, 4).to(bf).reshape(M, nb, -1)
+    bank_bw = torch.cat([ba, bb], dim=2).contiguous()
+    return {"rows_bank": bank, "rows_front": front, "rows_bank_bw": bank_bw}
 
 
 def _umma_images(w1: Tensor, w2: Tensor, gate_t: Tensor) -> dict[str, Tensor]:

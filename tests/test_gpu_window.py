@@ -476,16 +476,18 @@ def test_front_projection_equals_a_plain_product(dims, prod: str) -> None:
         assert float((got - want).abs().max()) <= 2e-5 * scale, (rows, prod)
 
 
-def _both_ways(rng, B, T, N, d, K, H, M, D, mult):
-    """The same bf16 model twice: tensor-core kernels, and the CUDA-core kernels with the same
-    roundings; a forward record by the first and the reverse sweep's inputs."""
+def _both_ways(rng, B, T, N, d, K, H, M, D, mult, path="rows"):
+    """The same bf16 model twice: the kernels under test (``path``: "rows" = the per-row cluster
+    kernels where the shape fits them, "phases" = the batch-synchronous tensor-core kernels), and
+    the CUDA-core phases with the same roundings; a forward record by the first and the reverse
+    sweep's inputs."""
     from hsn_b200.window import WindowModel, window_forward
 
     W, z, ctx, scalars, reset, state = _synthetic(rng, B, T, N, d, K, H, M, D, 0.1)
     for key in ("w1", "w2", "gate_w", "v_w", "wout_w"):
         setattr(W, key, O.bf16_round(getattr(W, key) * mult))
-    tc = WindowModel.from_oracle_weights(W, device="cuda", prod="bf16")
-    cc = WindowModel.from_oracle_weights(W, device="cuda", prod="bf16", tensor_cores=False)
+    tc = WindowModel.from_oracle_weights(W, device="cuda", prod="bf16", row_clusters=path == "rows")
+    cc = WindowModel.from_oracle_weights(W, device="cuda", prod="bf16", tensor_cores=False, row_clusters=False)
     args = (dev(z), dev(ctx), dev(scalars), dev(reset), tuple(dev(s) for s in state))
     tape = window_forward(tc, *args)
     cots = [dev(rng.standard_normal(s).astype(np.float32)) for s in ((B, T, d), (B, T, d), (B, T, K, d))]
@@ -495,35 +497,43 @@ def _both_ways(rng, B, T, N, d, K, H, M, D, mult):
     return W, tc, cc, args, tape, base, cots, rec
 
 
+@pytest.mark.parametrize("path", ["rows", "phases"])
 @pytest.mark.parametrize(
     "B,T,N,d,K,H,M,D,mult",
     [
         (6, 9, 256, 64, 8, 512, 8, 4, 1.0),    # the benchmark's model
         (6, 9, 256, 64, 8, 512, 8, 4, 6.0),    # large weights: the recurrence amplifies any difference
         (40, 3, 64, 64, 8, 200, 2, 2, 1.0),    # 160 pairs a unit: several batches of 32 and pair tiles; H % 128 != 0
-        (5, 4, 96, 32, 4, 128, 3, 2, 1.0),     # d 32: half a state tile
+        (5, 4, 96, 32, 4, 128, 3, 2, 1.0),     # d 32: half a state tile; one block a row
         (3, 3, 64, 128, 4, 256, 4, 2, 1.0),    # d 128: two state tiles
+        (3, 7, 64, 16, 5, 256, 5, 3, 1.0),     # d 16, two blocks a row, K not a multiple of the blocks
+        (2, 5, 512, 64, 8, 1024, 8, 4, 1.0),   # eight blocks a row
     ],
 )
-def test_tensor_core_kernels_equal_the_cuda_core_kernels_with_the_same_roundings(B, T, N, d, K, H, M, D, mult) -> None:
-    """tcgen05 kernels (unit layers forward, transposed unit layers in the reverse sweep) against
-    the CUDA-core kernels on the same bf16 operands: the products are exact in fp32 and only the
-    order of the sums differs, so 2e-4 of the scale (forward, teacher-forced) and 1e-3 (reverse
-    sweep over T positions)."""
+def test_tensor_core_kernels_equal_the_cuda_core_kernels_with_the_same_roundings(path, B, T, N, d, K, H, M, D, mult) -> None:
+    """The per-row cluster kernels and the tcgen05 phase kernels (unit layers forward, transposed
+    unit layers in the reverse sweep) against the CUDA-core phase kernels on the same bf16 operands:
+    the products are exact in fp32 and only the order of the sums differs, so 5e-3 of the scale at
+    the 99.9th percentile forward (teacher-forced; a bf16 rounding may flip on a last-bit difference)
+    and 1e-3 for the reverse sweep over T positions."""
     from hsn_b200.window import window_backward, window_forward
 
     rng = np.random.default_rng(12)
-    W, tc, cc, args, tape, base, cots, rec = _both_ways(rng, B, T, N, d, K, H, M, D, mult)
+    W, tc, cc, args, tape, base, cots, rec = _both_ways(rng, B, T, N, d, K, H, M, D, mult, path)
     forced = (tape["sel_cell_idx"], tape["sel_unit_idx"], tape["sel_valid"])
     other = window_forward(cc, *args, forced=forced)
-    for key in ("rec_hidden", "rec_y", "rec_gate_pre", "rec_c", "rec_b", "tape_h", "tape_q", "h", "q"):
+    assert int(tape["status"]) == 0
+    for key in ("rec_hidden", "rec_y", "rec_gate_pre", "rec_c", "rec_b", "tape_h", "tape_q", "h", "q", "tape_hsel",
+                "qs", "h_max", "rec_m", "rec_h_old", "rec_rms"):  # fmt: skip
         g, w = tape[key], other[key]
+        if key == "rec_hidden":   # only the slots that ran are recorded
+            ok = tape["sel_valid"].unsqueeze(-1)
+            g, w = g * ok, w * ok
         scale = max(1e-3, float(w.abs().max()))
-        # a bf16 rounding of an intermediate can flip on a last-bit difference of the sum: one
-        # bf16 step (2^-8 relative) on isolated values, so the bound is on the 99.9th percentile
         diff = (g - w).abs().flatten()
         assert float(diff.max()) <= 2e-2 * scale, (key, float(diff.max()), scale)
-        assert float(torch.quantile(diff[: 1 << 24].float(), 0.999)) <= 2e-3 * scale, key
+        assert float(torch.quantile(diff[: 1 << 24].float(), 0.999)) <= 5e-3 * scale, key
+    assert torch.equal(tape["tape_age"], other["tape_age"]) and torch.equal(tape["pos"], other["pos"])
     got = window_backward(tc, *base, *cots, rec)
     want = window_backward(cc, *base, *cots, rec)
     for name, g, w in zip(("dc", "db", "A", "R"), (got[0], got[1], got[2][0], got[2][1]),
@@ -533,6 +543,13 @@ def test_tensor_core_kernels_equal_the_cuda_core_kernels_with_the_same_roundings
         assert worst <= 1e-3 * scale, (name, worst, scale)
     again = window_backward(tc, *base, *cots, rec)
     assert torch.equal(again[0], got[0]) and torch.equal(again[2][0], got[2][0])  # run to run: bit for bit
+    # a carried cotangent and a reset in the middle of the window
+    A0 = dev(rng.standard_normal((B, N, d)).astype(np.float32))
+    R0 = dev(rng.standard_normal((B, d)).astype(np.float32))
+    g2 = window_backward(tc, *base, *cots, rec, initial=(A0.clone(), R0.clone()))
+    w2 = window_backward(cc, *base, *cots, rec, initial=(A0.clone(), R0.clone()))
+    for g, w in ((g2[0], w2[0]), (g2[2][0], w2[2][0]), (g2[2][1], w2[2][1])):
+        assert float((g - w).abs().max()) <= 1e-3 * max(1e-6, float(w.abs().max()))
 
 
 def test_reverse_sweep_with_bf16_products_stays_within_bf16_tolerance() -> None:

@@ -32,7 +32,7 @@ def test_every_declared_symbol_is_exported(lib: ctypes.CDLL) -> None:
 
 def test_structures_match_the_header() -> None:
     assert ctypes.sizeof(_lib.HsnWinArgs) == 8 * 48 + 4 * 32 + 4 * 8  # the reference's 544 bytes
-    assert ctypes.sizeof(_lib.HsnwModel) == 12 * 4 + 6 * 4 + 28 * 8
+    assert ctypes.sizeof(_lib.HsnwModel) == 12 * 4 + 6 * 4 + 29 * 8
     assert ctypes.sizeof(_lib.HsnwForward) == 4 * 4 + 29 * 8 + 8
     assert ctypes.sizeof(_lib.HsnwBackward) == 4 * 4 + 20 * 8 + 8
 
