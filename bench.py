@@ -57,14 +57,20 @@ def bytes_per_row_position(c: dict) -> int:
 
 
 def kernel_bytes_per_row_position(c: dict) -> dict[str, int]:
-    """The same algorithmic bytes split by the kernel that moves them: ``front`` carries the state
+    """The same algorithmic bytes split by the kernel that moves them (per row and launch). The
+    per-row cluster kernels ``rows_fwd`` / ``rows_bwd`` do a whole sweep in one launch; of the
+    batch-synchronous phases ``front`` carries the state
     tape (read record t, write record t + 1) and the position's inputs, ``row`` the scorer scalars
     and the decision, ``update`` the selected rows and summaries, ``mid`` the recorded hidden
     pre-activations, ``tail_head`` the rest of the reverse sweep; ``unit`` works on chip."""
     N, d, K, H, S = c["N"], c["d"], c["K"], c["H"], c["S"]
     state = 4 * N * d + 4 * d + 8 * N
     full = 4 * (6 * K * d + 2 * d) + 9 * K + 1
+    fwd = 2 * state + 4 * (2 * d) + 4 * N * S + 18 * K + 4 + 4 * K * d + 4 * d + 4
+    bwd = full + 4 * (3 * K * d) + 4 * K + 2 * K * H + 8 * K
     return {
+        "rows_fwd": fwd * c["T"],   # the per-row cluster kernels: one launch does every position
+        "rows_bwd": bwd * c["T"],
         "front": 2 * state + 4 * (2 * d),
         "row": 4 * N * S + 18 * K + 4,
         "unit": 0,
@@ -75,9 +81,10 @@ def kernel_bytes_per_row_position(c: dict) -> dict[str, int]:
 
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of each kernel of the c2
-# workload, from the ncu capture summarised in profiles/window_kernels_c2_dram.md.
+# workload, from the ncu captures summarised in profiles/rows_kernels_c2.md (the per-row cluster
+# kernels) and profiles/phases_kernels_c2_dram.md (the phase kernels).
 NCU_TRAFFIC_PER_LAUNCH: dict[str, dict[str, float]] = {
-    "c2": {"front": 2.798e6, "row": 1.375e6, "unit": 3.419e6, "update": 0.526e6, "mid": 2.254e6, "tail_head": 1.703e6},
+    "c2": {"rows_fwd": 854.5e6, "rows_bwd": 293.4e6, "front": 2.798e6, "row": 1.375e6, "unit": 3.419e6, "update": 0.526e6, "mid": 2.254e6, "tail_head": 1.703e6},
 }
 
 
@@ -224,6 +231,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--phases", action="store_true",
+                    help="run the batch-synchronous phase kernels instead of the per-row cluster kernels")
     ap.add_argument("--positions", type=int, default=0,
                     help="shorten the window to this many positions (profiler captures only; not a benchmark number)")
     args = ap.parse_args()
@@ -251,7 +260,7 @@ def main() -> None:
     warmup = max(args.warmup, 3)
     B, T, N, d, K = c["B"], c["T"], c["N"], c["d"], c["K"]
     W, host = synthetic(c, rank, B)
-    model = WindowModel.from_oracle_weights(W, device=dev, prod=c["prod"])
+    model = WindowModel.from_oracle_weights(W, device=dev, prod=c["prod"], row_clusters=not args.phases)
     pinned = [torch.from_numpy(a).pin_memory() for a in host]
     z, ctx, scalars, reset, pre, post, sel = (t.to(dev, non_blocking=True) for t in pinned)
     state = (torch.zeros((B, N, d), device=dev), torch.zeros((B, d), device=dev),
@@ -366,6 +375,7 @@ def main() -> None:
             "dtype": "bf16 products, f32 state" if c["prod"] == "bf16" else "f32", "data": "synthetic",
             "config": {"workload": WORKLOADS[args.config] + (f" [shortened to {T} positions]" if args.positions else ""),
                        "rows_per_gpu": B, "positions": T,
+                       "kernels": "batch-synchronous phases" if args.phases else "per-row clusters",
                        "l2": "inputs larger than L2 (tape 0.5 GiB + scalars 75 MB per step)",
                        "allreduce_floats_per_step": n_params if world > 1 else 0},
             "e2e": {"value": world * row_pos / (ms_e2e * 1e-3), "unit": "row-positions/s",

@@ -1069,7 +1069,7 @@ int hsnw_rows_forward(const HsnwModel* model, const HsnwForward* io, const float
         cudaGetLastError();
         return -1;
     }
-    hsnw_profile_mark(HSNW_K_ROW, stream);
+    hsnw_profile_mark(HSNW_K_ROWS_FWD, stream);
     if (cudaLaunchKernelEx(&cfg, kernel, c) != cudaSuccess) return hsnw_check_launch("window_forward (row clusters)");
     return hsnw_check_launch("window_forward (row clusters)");
 }

@@ -640,7 +640,7 @@ int hsnw_rows_backward(const HsnwModel* model, const HsnwBackward* io, cudaStrea
         cudaGetLastError();
         return -1;
     }
-    hsnw_profile_mark(HSNW_K_MID, stream);
+    hsnw_profile_mark(HSNW_K_ROWS_BWD, stream);
     if (cudaLaunchKernelEx(&cfg, kernel, c) != cudaSuccess) return hsnw_check_launch("window_backward (row clusters)");
     return hsnw_check_launch("window_backward (row clusters)");
 }

@@ -479,8 +479,8 @@ def front_projection(model: WindowModel, z: Tensor, ctx: Tensor) -> Tensor:
 class launch_profile:
     """``with launch_profile() as prof: ...`` times every kernel launch of the window entry points
     made inside the block (``hsnw_profile_begin`` / ``hsnw_profile_end``): afterwards ``prof.ms``
-    and ``prof.launches`` map a kernel kind ("front", "row", "unit", "update", "head", "mid",
-    "tail_head", "init", "pre") to its summed time in milliseconds and its launch count. For
+    and ``prof.launches`` map a kernel kind ("rows_fwd", "rows_bwd", "pre", or the phases' "front",
+    "row", "unit", "update", "head", "mid", "tail_head", "init") to its summed time in milliseconds and its launch count. For
     measurement runs: it adds an event per launch."""
 
     def __init__(self) -> None:

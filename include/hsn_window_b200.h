@@ -269,7 +269,8 @@ int hsnw_front_projection(const HsnwModel* model, const float* z, const float* c
  * kind k < hsnw_profile_kinds() the summed time (ms, event to next event: the kernel and the gap
  * before the next launch) and the number of launches. One profile at a time, one host thread, one
  * stream. hsnw_profile_kind_name(k): "init" "pre" "front" "row" "unit" "update" "head" "mid"
- * "tail_head". */
+ * "tail_head" (the batch-synchronous phases) "rows_fwd" "rows_bwd" (the per-row cluster kernels: one
+ * launch a window). */
 int hsnw_profile_begin(void);
 int hsnw_profile_kinds(void);
 const char* hsnw_profile_kind_name(int kind);
