@@ -78,9 +78,11 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
 // repeated with period 8 (as if the A tile's row stride were zero) or not, depending on unrelated
 // code elsewhere in the kernel; out of line it does not.
 static __device__ __noinline__ void umma_chain(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, int steps,
-                                               uint32_t a_step, uint32_t b_step) {
+                                               uint32_t a_step, uint32_t b_step, bool onto = false) {
+    // onto: add to what the accumulator holds (a sum that runs over several chains)
     for (int s = 0; s < steps; ++s)
-        umma_bf16(tmem_d, desc_a + static_cast<uint64_t>(s) * a_step, desc_b + static_cast<uint64_t>(s) * b_step, idesc, s > 0);
+        umma_bf16(tmem_d, desc_a + static_cast<uint64_t>(s) * a_step, desc_b + static_cast<uint64_t>(s) * b_step, idesc,
+                  onto || s > 0);
 }
 // The step between two K = 16 products of a tile of `rows` rows in the layout above.
 __host__ __device__ constexpr uint32_t umma_kstep(int rows) { return static_cast<uint32_t>((2 * rows * 16) >> 4); }

@@ -38,6 +38,7 @@
 #include "stage.cuh"
 #include "host_util.h"
 #include "rows.cuh"
+#include "umma.cuh"
 
 using namespace hsnw;
 
@@ -67,7 +68,7 @@ __host__ __device__ inline size_t up16(size_t v) { return (v + 15) & ~static_cas
 // Offsets (bytes) of the dynamic shared memory's segments.
 struct RowsSmem {
     size_t ring, h, vh, lh, age, cmax, wout, vt, gate, swh, sw_head, sw_tail, norm_w, cand_w, fb2, gate_b, score_b,
-        fb1p, score_all, unit_all, age_all, q, ue, rowterm, hold, big, msg, rms, src, ew, facc, gacc, inbox_front,
+        fb1p, score_all, unit_all, age_all, q, ue, rowterm, hold, big, msg, rms, src, ew, b2, gacc, inbox_front,
         inbox_f, inbox_delta, in_scal, in_pre, in_z, upd, cell_of, unit_of, ulist, umask, cand, total;
 };
 __host__ __device__ inline RowsSmem rows_smem(const HsnwModel& m, int C, uint32_t slot_bytes) {
@@ -108,7 +109,7 @@ __host__ __device__ inline RowsSmem rows_smem(const HsnwModel& m, int C, uint32_
         // sources [K D][d], then the pairs' inputs v [K][4d] over them; the front's act [256] and
         // partial sums [256 / d][2d] use the same bytes in phase A
         size_t big = 4 * K * D * d;
-        if (4 * K * 4 * d > big) big = 4 * K * 4 * d;
+        if (2 * 16 * 4 * d > big) big = 2 * 16 * 4 * d;   // the pairs' inputs as a bf16 operand [4d/8][16][8]
         if (4 * (kFrontCols + 2 * kFrontCols) > big) big = 4 * 3 * kFrontCols;
         L.big = take(big);
     }
@@ -116,7 +117,7 @@ __host__ __device__ inline RowsSmem rows_smem(const HsnwModel& m, int C, uint32_
     L.rms = take(4 * K);
     L.src = take(4 * K * D);
     L.ew = take(4 * K * D);
-    L.facc = take(4 * K * d);
+    L.b2 = take(2 * 2 * 8 * 16 * 8);    // two bf16 operands [8][16][8]: the activations of a chunk's 64 columns
     L.gacc = take(4 * K * d);
     L.inbox_front = take(4 * C * (2 * d + 4));
     L.inbox_f = take(4 * C * Ks * 2 * d);
@@ -253,6 +254,8 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
     __shared__ int n_units_s;    // units some valid slot runs this position
     __shared__ int hmax_local;   // bits of max |h| over the block's cells after the last position
     __shared__ int failed_s;     // a ring wait ran out
+    __shared__ __align__(8) uint64_t bar_d1[2], bar_d2;   // a chunk's first product (two accumulators in turn); the position's second products
+    __shared__ uint32_t tmem_slot;
     __shared__ uint64_t next_key_s;   // the (K + 1)-th best key of the position's scored order
 
     cg::cluster_group cl = cg::this_cluster();
@@ -298,7 +301,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
     float* rms = reinterpret_cast<float*>(dyn + L.rms);
     int* src = reinterpret_cast<int*>(dyn + L.src);
     float* ew = reinterpret_cast<float*>(dyn + L.ew);
-    float* facc = reinterpret_cast<float*>(dyn + L.facc);
+    uint16_t* b2 = reinterpret_cast<uint16_t*>(dyn + L.b2);
     float* gacc = reinterpret_cast<float*>(dyn + L.gacc);
     float* inbox_front = reinterpret_cast<float*>(dyn + L.inbox_front);
     float* inbox_f = reinterpret_cast<float*>(dyn + L.inbox_f);
@@ -329,8 +332,11 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], kConsumers / 32);
+            mbar_init(&empty[s], 1);
         }
+        mbar_init(&bar_d1[0], 1);
+        mbar_init(&bar_d1[1], 1);
+        mbar_init(&bar_d2, 1);
         hmax_local = 0;
         n_units_s = 0;
         failed_s = 0;
@@ -354,6 +360,8 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
         S.cost[e] = c.m.cost[e];
     }
     for (int e = tid; e < kFrontCols; e += kRowThreads) fb1p[e] = c.m.f_b1[r * kFrontCols + e];
+    if (warp == 0) tmem_alloc(&tmem_slot, 64);
+    for (int e = tid; e < 2 * 8 * 16 * 8; e += kRowThreads) b2[e] = 0;
     const bool cut0 = c.io.reset[static_cast<int64_t>(row) * T] != 0;
     {
         const float* h0 = c.io.h0 + (static_cast<int64_t>(row) * N + cell0) * d;
@@ -367,7 +375,11 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
         for (int e = tid; e < pre_cols; e += kRowThreads) in_pre[e] = c.pre_s[rt0 * H + r * kFrontCols + e];
         for (int x = tid; x < d; x += kRowThreads) in_z[x] = c.io.z[rt0 * d + x];
     }
+    tcgen05_fence_before();
     __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t taddr = tmem_slot;
+    uint32_t d1_count0 = 0, d1_count1 = 0, d2_phase = 0;   // completed phases of the accumulators' barriers
     for (int o = tid; o < Nc * (M + d); o += kRowThreads) {
         const int cell = o / (M + d), w = o - cell * (M + d);
         const float* hr = h_s + cell * d;
@@ -426,10 +438,9 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 for (int x = 0; x < d; ++x) sum += ue[x] * bf16_value(w1c[x * kFrontCols + col]);
                 const float pre = colg >= H ? fb1p[col] : in_pre[col];
                 act[col] = bf16r(gelu_erf(bf16r(sum + pre)));
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&empty[slot]);
             }
             consumer_sync();
+            if (tid == 0) mbar_arrive(&empty[g_use % kStages]);
             {
                 const uint32_t slot = (g_use + 1) % kStages;
                 ring_wait(&full[slot], ((g_use + 1) / kStages) & 1u, c.status, &failed_s);
@@ -441,11 +452,10 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 for (int cc = 0; cc < d; ++cc) sum += act[grp * d + cc] * bf16_value(w2c[(grp * d + cc) * d + x]);
                 fpart[grp * 2 * d + x] = is_p ? 0.0f : sum;
                 fpart[grp * 2 * d + d + x] = is_p ? sum : 0.0f;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&empty[slot]);
             }
-            g_use += 2;
             consumer_sync();
+            if (tid == 0) mbar_arrive(&empty[(g_use + 1) % kStages]);
+            g_use += 2;
             if (tid < 2 * d) {
                 float tot = 0.0f;
                 for (int grp = 0; grp < kFrontCols / d; ++grp) tot += fpart[grp * 2 * d + tid];
@@ -748,12 +758,17 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
             }
             consumer_sync();
             RMARK(6);
-            float* v = big;         // [K][4d]
+            // the pairs' inputs as the tensor cores' B operand: bf16 [4d/8][16 slots][8] (slots K..15 stay zero)
+            uint16_t* vop = reinterpret_cast<uint16_t*>(big);
             for (int e = tid; e < K * 4 * d; e += kConsumers) {
                 const int k = e / (4 * d), jx = e - k * 4 * d;
                 const int blk = jx / d, x = jx - blk * d;
                 const float val = blk == 0 ? ue[x] : blk == 1 ? ue[d + x] : blk == 2 ? hold[k * d + x] : msg[k * d + x];
-                v[e] = bf16r(val * rms[k] * norm_w[jx]);
+                vop[((jx >> 3) * 16 + k) * 8 + (jx & 7)] = bf16_bits(val * rms[k] * norm_w[jx]);
+            }
+            for (int e = tid; e < (4 * d / 8) * (16 - K); e += kConsumers) {   // the front phase used these bytes
+                const int p = e / (16 - K), k = K + e - p * (16 - K);
+                reinterpret_cast<uint4*>(vop)[p * 16 + k] = make_uint4(0u, 0u, 0u, 0u);
             }
             if (rec) {
                 for (int e = tid; e < K * d; e += kConsumers) {
@@ -773,76 +788,111 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 for (int k = grp; k < K; k += ngrp) {
                     float sum = 0.0f;
                     if (cell_of[k] >= 0) {
-                        const float* vk = v + k * 4 * d + r * grows;
 #pragma unroll 8
-                        for (int xi = 0; xi < grows; ++xi) sum += vk[xi] * bf16_value(gate[xi * d + x]);
+                        for (int xi = 0; xi < grows; ++xi) {
+                            const int jx = r * grows + xi;
+                            sum += bf16_value(vop[((jx >> 3) * 16 + k) * 8 + (jx & 7)]) * bf16_value(gate[xi * d + x]);
+                        }
                     }
                     gacc[k * d + x] = sum;
                 }
             }
             RMARK(7);
-            // the units' two layers on the streamed chunks: warp w owns the chunk's columns 8w .. 8w+7
-            float f0[kMaxK], f1[kMaxK];
-#pragma unroll
-            for (int k = 0; k < kMaxK; ++k) f0[k] = f1[k] = 0.0f;
-            for (int ui = 0; ui < n_units; ++ui) {
-                const int j = ulist[ui];
-                const unsigned mask = static_cast<unsigned>(umask[ui]);
-                const int ns = __popc(mask);
-                for (int b = 0; b < 2; ++b) {
-                    const int colg = r * 128 + b * 64 + warp * 8 + (lane & 7);   // the hidden column of unit j
+            // the units' two layers on the streamed chunks, on the tensor cores. Per chunk (unit j, 64
+            // hidden columns): D1 [64 columns, 16 slots] = W1 part x inputs^T; the epilogue adds the
+            // bias, rounds, records, applies the activation for the slots that run unit j (zero for
+            // the others) and writes the bf16 operand of the second product; D2 [d outputs, 16 slots]
+            // += W2 part x activations^T accumulates over all the position's chunks in tensor memory.
+            // The chunk's rows are 64, the instruction's M is 128: rows 64..127 of both accumulators
+            // come from the bytes after the tile and are never read. The second product's commit
+            // hands the ring slot back. Thread 0 issues; warps 0, 1, 4, 5 read the accumulators.
+            fence_async_smem();   // the operand written above, before the tensor cores read it
+            consumer_sync();
+            const int n_chunks = 2 * n_units;
+            const bool epi = (warp & 2) == 0;                 // warps 0, 1, 4, 5
+            const int hc = lane + 32 * (warp & 1);            // the epilogue thread's column of the chunk (TMEM lane)
+            const int sh = warp >> 2;                         // its half of the slots: 4 sh .. 4 sh + 3
+            const uint32_t idesc = umma_idesc_bf16(128, 16);
+            const uint32_t g0 = g_use;
+            if (tid == 0 && n_chunks > 0) {
+                const uint32_t slot = g0 % kStages;
+                ring_wait(&full[slot], (g0 / kStages) & 1u, c.status, &failed_s);
+                tcgen05_fence_after();
+                umma_chain(taddr, umma_desc(ring + slot * c.slot_bytes, 64), umma_desc(vop, 16), idesc, (4 * d) >> 4,
+                           umma_kstep(64), umma_kstep(16));
+                umma_commit(&bar_d1[0]);
+            }
+            for (int i = 0; i < n_chunks; ++i) {
+                const int j = ulist[i >> 1];
+                const unsigned mask = static_cast<unsigned>(umask[i >> 1]);
+                const uint32_t slot = (g0 + i) % kStages;
+                if (tid == 0 && i + 1 < n_chunks) {   // the next chunk's first product runs under this epilogue
+                    const uint32_t nslot = (g0 + i + 1) % kStages;
+                    ring_wait(&full[nslot], ((g0 + i + 1) / kStages) & 1u, c.status, &failed_s);
+                    tcgen05_fence_after();
+                    umma_chain(taddr + 16 * ((i + 1) & 1), umma_desc(ring + nslot * c.slot_bytes, 64), umma_desc(vop, 16), idesc,
+                               (4 * d) >> 4, umma_kstep(64), umma_kstep(16));
+                    umma_commit(&bar_d1[(i + 1) & 1]);
+                }
+                if (epi) {
+                    const int colg = r * 128 + (i & 1) * 64 + hc;
                     const float bias = c.m.b1[j * H + colg];
-                    const uint32_t slot = g_use % kStages;
-                    ring_wait(&full[slot], (g_use / kStages) & 1u, c.status, &failed_s);
-                    ++g_use;
-                    const unsigned char* chunk = ring + slot * c.slot_bytes;
-                    const uint4* W1s = reinterpret_cast<const uint4*>(chunk);
-                    const uint4* W2s = reinterpret_cast<const uint4*>(chunk + c.w1_bytes);
-                    float* rh = rec ? c.io.rec_hidden + rt * K * H + colg : nullptr;
-                    switch (ns) {
-                        case 1: unit_stage<D_, 1>(W1s, W2s, v, mask, bias, rh, H, warp, lane, f0, f1); break;
-                        case 2: unit_stage<D_, 2>(W1s, W2s, v, mask, bias, rh, H, warp, lane, f0, f1); break;
-                        case 3: unit_stage<D_, 3>(W1s, W2s, v, mask, bias, rh, H, warp, lane, f0, f1); break;
-                        case 4: unit_stage<D_, 4>(W1s, W2s, v, mask, bias, rh, H, warp, lane, f0, f1); break;
-                        case 5: unit_stage<D_, 5>(W1s, W2s, v, mask, bias, rh, H, warp, lane, f0, f1); break;
-                        case 6: unit_stage<D_, 6>(W1s, W2s, v, mask, bias, rh, H, warp, lane, f0, f1); break;
-                        case 7: unit_stage<D_, 7>(W1s, W2s, v, mask, bias, rh, H, warp, lane, f0, f1); break;
-                        default: unit_stage<D_, 8>(W1s, W2s, v, mask, bias, rh, H, warp, lane, f0, f1); break;
-                    }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&empty[slot]);
-                }
-            }
-            RMARK(8);
-            // the block's partial of every slot's second layer: the warps' partials meet in the ring
-            // slot of the last chunk consumed (the producer's next copies go to the other two), are
-            // added in warp order and go straight to the slots' owners with the gate's partial
-            consumer_sync();   // every warp is done reading that slot
-            {
-                float* Fw = reinterpret_cast<float*>(ring + ((g_use + kStages - 1) % kStages) * c.slot_bytes);   // [8][K][d]
-                const int x0 = lane, x1 = lane + 32;
+                    uint16_t* b2i = b2 + (i & 1) * (8 * 16 * 8);
+                    ring_wait(&bar_d1[i & 1], ((i & 1) ? d1_count1 : d1_count0) & 1u, c.status, &failed_s);
+                    tcgen05_fence_after();
+                    float acc[8];
+                    tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 16 * (i & 1)), acc);
 #pragma unroll
-                for (int k = 0; k < kMaxK; ++k) {
-                    if (k < K) {
-                        if (x0 < d) Fw[(warp * K + k) * d + x0] = f0[k];
-                        if (x1 < d) Fw[(warp * K + k) * d + x1] = f1[k];
+                    for (int q = 0; q < 4; ++q) {
+                        const int k = 4 * sh + q;
+                        float a = 0.0f;
+                        if (mask & (1u << k)) {
+                            const float hid = bf16r((sh ? acc[4 + q] : acc[q]) + bias);
+                            if (rec) c.io.rec_hidden[(rt * K + k) * H + colg] = hid;
+                            a = gelu_erf(hid);
+                        }
+                        b2i[((hc >> 3) * 16 + k) * 8 + (hc & 7)] = bf16_bits(a);
                     }
+                    fence_async_smem();
+                    tcgen05_fence_before();
                 }
+                if (i & 1) ++d1_count1;
+                else ++d1_count0;
                 consumer_sync();
-                for (int e = tid; e < K * 2 * d; e += kConsumers) {
-                    const int k = e / (2 * d), xx = e - k * 2 * d;
-                    float val;
-                    if (xx < d) {
-                        val = 0.0f;
-                        for (int w = 0; w < kConsumers / 32; ++w) val += Fw[(w * K + k) * d + xx];
-                    } else {
-                        val = gacc[k * d + xx - d];
-                    }
-                    peer(cl, inbox_f, k % C)[(r * Ks + k / C) * 2 * d + xx] = val;
+                if (tid == 0) {
+                    tcgen05_fence_after();
+                    umma_chain(taddr + 32, umma_desc(ring + slot * c.slot_bytes + c.w1_bytes, d),
+                               umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), idesc, 64 >> 4, umma_kstep(d), umma_kstep(16),
+                               i > 0);   // D2 sums over the position's chunks
+                    umma_commit(&empty[slot]);
+                    if (i + 1 == n_chunks) umma_commit(&bar_d2);
                 }
-                // the slot goes back to the TMA: order these generic accesses before its next bulk copy
-                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             }
+            g_use += n_chunks;
+            RMARK(8);
+            // the block's partial of every slot's second layer from the accumulator, and the gate's
+            // partial, to the slots' owners
+            if (epi && sh == 0) {
+                float acc[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
+                if (n_chunks > 0) {
+                    ring_wait(&bar_d2, d2_phase & 1u, c.status, &failed_s);
+                    tcgen05_fence_after();
+                    tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 32), acc);
+                }
+                if (hc < d) {
+#pragma unroll
+                    for (int k = 0; k < kMaxK; ++k)
+                        if (k < K) peer(cl, inbox_f, k % C)[(r * Ks + k / C) * 2 * d + hc] = acc[k];
+                }
+            }
+            if (n_chunks > 0) ++d2_phase;
+            for (int e = tid; e < K * d; e += kConsumers) {
+                const int k = e / d, x = e - k * d;
+                peer(cl, inbox_f, k % C)[(r * Ks + k / C) * 2 * d + d + x] = gacc[e];
+            }
+            tcgen05_fence_before();
         }
         RMARK(9);
         cl.sync();   // 3
@@ -1014,6 +1064,9 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 for (int x = tid; x < d; x += kConsumers) c.io.q0[static_cast<int64_t>(row) * d + x] = q_s[x];
         }
     }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(taddr, 64);
 }
 
 }  // namespace

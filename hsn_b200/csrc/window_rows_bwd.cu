@@ -24,10 +24,24 @@
 #include "stage.cuh"
 #include "host_util.h"
 #include "rows.cuh"
+#include "umma.cuh"
 
 using namespace hsnw;
 
 namespace {
+
+#ifdef HSNW_TRACE
+#define BMARK(i)                                                                              \
+    do {                                                                                      \
+        if (tid == 0 && row == 0 && t == T / 2) {                                             \
+            unsigned long long now;                                                           \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));                           \
+            c.trace[r * 32 + (i)] = now;                                                      \
+        }                                                                                     \
+    } while (0)
+#else
+#define BMARK(i) do { } while (0)
+#endif
 
 constexpr int kStagesB = 3;
 constexpr int kMaxKB = 8;
@@ -38,12 +52,13 @@ struct RowsBwdCtx {
     HsnwBackward io;
     int C, Nc, Ks;
     uint32_t bank_bytes, w2_bytes;   // a chunk, its W2 part
+    unsigned long long* trace;       // phase timestamps (HSNW_TRACE builds): the head of the caller's scratch
 };
 
 __host__ __device__ inline size_t up16b(size_t v) { return (v + 15) & ~static_cast<size_t>(15); }
 
 struct RowsBwdSmem {
-    size_t ring, A, wout, vt, gate, norm_w, cand_w, gate_b, b1, R, Rs, rec[2], hid[2], dq[2], dec[2], du_all, dg_all,
+    size_t ring, A, wout, vt, gate, norm_w, cand_w, gate_b, b1, R, Rs, rec[2], hid[2], dq[2], dec[2], du_all, b2, dg_all,
         inbox_dv, inbox_sig, inbox_g, ds_all, dvm_all, red, own, total;
 };
 // rec: per owned slot c, b, h_old, y, gate_pre, m, d_h_sel [7][Ks][d], then rms [Ks]
@@ -74,14 +89,15 @@ __host__ __device__ inline RowsBwdSmem rows_bwd_smem(const HsnwModel& m, int C, 
         L.dq[s] = take(4 * 2 * d);
         L.dec[s] = take(4 * (2 * K + 2 * K * D + 2 * kMaxMB + 4));
     }
-    L.du_all = take(4 * K * d);
+    L.du_all = take(2 * 16 * d);        // d_unit of every slot as a bf16 operand [d/8][16][8]
+    L.b2 = take(2 * 2 * 8 * 16 * 8);    // two bf16 operands [8][16][8]: dhid of a chunk's 64 columns
     L.dg_all = take(4 * K * d);
     L.inbox_dv = take(4 * C * Ks * 2 * d);
     L.inbox_sig = take(4 * C * Ks + 16);
     L.inbox_g = take(4 * Ks * 2 * d);
     L.ds_all = take(4 * K * d);
     L.dvm_all = take(4 * K * d);
-    L.red = take(4 * 8 * K * (2 * d + 1));
+    L.red = take(4 * 8 * 8);            // the epilogue warps' shares of the slots' inner products
     L.own = take(4 * Ks * (6 * d + 8));   // dzs, ysv, sgs, dy, ds [2d] per owned slot; rho, dot, sig_gate, back
     L.total = o;
     return L;
@@ -177,6 +193,8 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
     extern __shared__ __align__(16) unsigned char dyn[];
     __shared__ __align__(8) uint64_t full[kStagesB], empty[kStagesB];
     __shared__ int failed_s;
+    __shared__ __align__(8) uint64_t bar_d1[2], bar_d2;
+    __shared__ uint32_t tmem_slot;
 
     cg::cluster_group cl = cg::this_cluster();
     constexpr int d = D_, two = 2 * D_, NO = (2 * D_ + 31) / 32;
@@ -201,7 +219,8 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
     float* b1s = reinterpret_cast<float*>(dyn + L.b1);
     float* R_s = reinterpret_cast<float*>(dyn + L.R);
     float* Rs = reinterpret_cast<float*>(dyn + L.Rs);
-    float* du_all = reinterpret_cast<float*>(dyn + L.du_all);
+    uint16_t* du_op = reinterpret_cast<uint16_t*>(dyn + L.du_all);
+    uint16_t* b2 = reinterpret_cast<uint16_t*>(dyn + L.b2);
     float* dg_all = reinterpret_cast<float*>(dyn + L.dg_all);
     float* inbox_dv = reinterpret_cast<float*>(dyn + L.inbox_dv);
     float* inbox_sig = reinterpret_cast<float*>(dyn + L.inbox_sig);
@@ -311,8 +330,11 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
     if (tid == 0) {
         for (int s = 0; s < kStagesB; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], kConsumers / 32);
+            mbar_init(&empty[s], 1);
         }
+        mbar_init(&bar_d1[0], 1);
+        mbar_init(&bar_d1[1], 1);
+        mbar_init(&bar_d2, 1);
         failed_s = 0;
     }
     for (int e = tid; e < d * d; e += kConsumers) {
@@ -335,7 +357,14 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
         for (int e = tid; e < 7 * Ks * d + Ks; e += kConsumers) rec_of(buf)[e] = 0.0f;
         for (int e = tid; e < 2 * d; e += kConsumers) dq_of(buf)[e] = 0.0f;
     }
+    for (int e = tid; e < 16 * d; e += kConsumers) du_op[e] = 0;
+    for (int e = tid; e < 2 * 8 * 16 * 8; e += kConsumers) b2[e] = 0;
+    if (warp == 0) tmem_alloc(&tmem_slot, 64);
+    tcgen05_fence_before();
     __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t taddr = tmem_slot;
+    uint32_t d1_count0 = 0, d1_count1 = 0, d2_phase = 0;
     prefetch(T - 1);
     decision_load(T - 1);
     decision_store(T - 1);
@@ -378,6 +407,7 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
         const int* dc_ = dec_of(buf);
         const float* ew = reinterpret_cast<const float*>(dc_) + o_ew;
         const bool cut = c.io.reset[rt] != 0;
+        BMARK(0);
         // ---------------- H
         cp_async_wait_all();
         __syncthreads();
@@ -448,10 +478,12 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
                 s0 += dy[kl * d + x] * bf16_value(wout[i * d + x]);
                 s1 += dy[kl * d + x + 1] * bf16_value(wout[i * d + x + 1]);
             }
-            const float dub = bf16r(s0 + s1);
-            for (int p = 0; p < C; ++p) peer(cl, du_all, p)[k * d + i] = dub;
+            const uint16_t dub = bf16_bits(s0 + s1);
+            for (int p = 0; p < C; ++p) peer(cl, du_op, p)[((i >> 3) * 16 + k) * 8 + (i & 7)] = dub;
         }
+        BMARK(1);
         cl.sync();   // 1
+        BMARK(2);
         // ---------------- M
         if (t > 0) decision_store(t - 1);
         __syncthreads();
@@ -478,62 +510,114 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
                 peer(cl, inbox_g, k % C)[(k / C) * two + r * gcols + il] = s0 + s1;
             }
         }
-        float dv[kMaxKB][NO], sig[kMaxKB];
-#pragma unroll
-        for (int k = 0; k < kMaxKB; ++k) {
-            sig[k] = 0.0f;
-#pragma unroll
-            for (int o = 0; o < NO; ++o) dv[k][o] = 0.0f;
-        }
+        BMARK(3);
+        // the transposed layers on the streamed chunks, on the tensor cores. Per chunk (unit j, 64
+        // hidden columns): D1 [64 columns, 16 slots] = W2 part x d_unit^T; the epilogue multiplies by
+        // the activation's derivative at the recorded pre-activation for the slots that ran unit j
+        // (zero for the others), adds to the norm's inner products and writes the bf16 operand of the
+        // second product; D2 [2d state inputs, 16 slots] += W1 state part x dhid^T accumulates over the
+        // position's chunks in tensor memory. M is 128 for both: the first product's rows 64..127 come
+        // from the bytes after the tile and are never read. Thread 0 issues; warps 0, 1, 4, 5 read D1.
         const int n_units = dc_[o_n];
-        for (int ui = 0; ui < n_units; ++ui) {
-            const int j = dc_[o_ulist + ui];
-            const unsigned mask = static_cast<unsigned>(dc_[o_umask + ui]);
-            const int ns = __popc(mask);
-            for (int b = 0; b < 2; ++b) {
-                const int hid_col = b * 64 + warp * 8 + (lane & 7);
+        const int n_chunks = 2 * n_units;
+        const bool epi = (warp & 2) == 0;
+        const int hc = lane + 32 * (warp & 1), sh = warp >> 2;
+        const uint32_t idesc = umma_idesc_bf16(128, 16);
+        const uint32_t g0 = g_use;
+        float inner[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        tcgen05_fence_after();
+        if (tid == 0 && n_chunks > 0) {
+            const uint32_t slot = g0 % kStagesB;
+            ring_wait(&full[slot], (g0 / kStagesB) & 1u, nullptr, &failed_s);
+            umma_chain(taddr, umma_desc(ring + slot * c.bank_bytes, 64), umma_desc(du_op, 16), idesc, d >> 4, umma_kstep(64),
+                       umma_kstep(16));
+            umma_commit(&bar_d1[0]);
+        }
+        for (int i = 0; i < n_chunks; ++i) {
+            const int j = dc_[o_ulist + (i >> 1)];
+            const unsigned mask = static_cast<unsigned>(dc_[o_umask + (i >> 1)]);
+            const uint32_t slot = (g0 + i) % kStagesB;
+            if (tid == 0 && i + 1 < n_chunks) {
+                const uint32_t nslot = (g0 + i + 1) % kStagesB;
+                ring_wait(&full[nslot], ((g0 + i + 1) / kStagesB) & 1u, nullptr, &failed_s);
+                umma_chain(taddr + 16 * ((i + 1) & 1), umma_desc(ring + nslot * c.bank_bytes, 64), umma_desc(du_op, 16), idesc,
+                           d >> 4, umma_kstep(64), umma_kstep(16));
+                umma_commit(&bar_d1[(i + 1) & 1]);
+            }
+            if (epi) {
+                const int hid_col = (i & 1) * 64 + hc;
                 const float bias = b1s[j * 128 + hid_col];
-                const uint32_t slot = g_use % kStagesB;
-                ring_wait(&full[slot], (g_use / kStagesB) & 1u, nullptr, &failed_s);
-                ++g_use;
-                const unsigned char* chunk = ring + slot * c.bank_bytes;
-                const uint4* W2s = reinterpret_cast<const uint4*>(chunk);
-                const uint4* W1s = reinterpret_cast<const uint4*>(chunk + c.w2_bytes);
-                switch (ns) {
-                    case 1: bwd_stage<D_, 1>(W2s, W1s, du_all, hd, hid_col, bias, mask, warp, lane, dv, sig); break;
-                    case 2: bwd_stage<D_, 2>(W2s, W1s, du_all, hd, hid_col, bias, mask, warp, lane, dv, sig); break;
-                    case 3: bwd_stage<D_, 3>(W2s, W1s, du_all, hd, hid_col, bias, mask, warp, lane, dv, sig); break;
-                    case 4: bwd_stage<D_, 4>(W2s, W1s, du_all, hd, hid_col, bias, mask, warp, lane, dv, sig); break;
-                    case 5: bwd_stage<D_, 5>(W2s, W1s, du_all, hd, hid_col, bias, mask, warp, lane, dv, sig); break;
-                    case 6: bwd_stage<D_, 6>(W2s, W1s, du_all, hd, hid_col, bias, mask, warp, lane, dv, sig); break;
-                    case 7: bwd_stage<D_, 7>(W2s, W1s, du_all, hd, hid_col, bias, mask, warp, lane, dv, sig); break;
-                    default: bwd_stage<D_, 8>(W2s, W1s, du_all, hd, hid_col, bias, mask, warp, lane, dv, sig); break;
+                uint16_t* b2i = b2 + (i & 1) * (8 * 16 * 8);
+                ring_wait(&bar_d1[i & 1], ((i & 1) ? d1_count1 : d1_count0) & 1u, nullptr, &failed_s);
+                tcgen05_fence_after();
+                float acc[8];
+                tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 16 * (i & 1)), acc);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int k = 4 * sh + q;
+                    float dh = 0.0f;
+                    if (mask & (1u << k)) {
+                        const float hv = hd[k * 128 + hid_col];
+                        dh = bf16r((sh ? acc[4 + q] : acc[q]) * gelu_erf_grad(hv));
+                        inner[q] += dh * (hv - bias);
+                    }
+                    b2i[((hc >> 3) * 16 + k) * 8 + (hc & 7)] = bf16_bits(dh);
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&empty[slot]);
-                if (tid == 0) issue_ahead();
-                __syncwarp();
+                fence_async_smem();
+                tcgen05_fence_before();
+            }
+            if (i & 1) ++d1_count1;
+            else ++d1_count0;
+            __syncthreads();
+            if (tid == 0) {
+                tcgen05_fence_after();
+                umma_chain(taddr + 32, umma_desc(ring + slot * c.bank_bytes + c.w2_bytes, two),
+                           umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), idesc, 64 >> 4, umma_kstep(two), umma_kstep(16), i > 0);
+                umma_commit(&empty[slot]);
+                if (i + 1 == n_chunks) umma_commit(&bar_d2);
+                ++g_use;
+                issue_ahead();
+            }
+            __syncwarp();
+        }
+        if (tid != 0) g_use += n_chunks;
+        BMARK(4);
+        // the slots' inner products: the epilogue warps' sums, then the pair of warps of each half
+        if (epi) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float sum = warp_sum(inner[q]);
+                if (lane == 0) red[warp * 4 + q] = sum;
             }
         }
-        // the warps' partials, added in warp order, go to the slots' owners
+        // the block's partial of dv from the accumulator, to the slots' owners
+        if (warp < 4 && 32 * warp < two) {
+            float acc[8];
 #pragma unroll
-        for (int k = 0; k < kMaxKB; ++k) {
-            if (k < K) {
+            for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
+            if (n_chunks > 0) {
+                ring_wait(&bar_d2, d2_phase & 1u, nullptr, &failed_s);
+                tcgen05_fence_after();
+                tmem_ld8(tmem_addr(taddr, 32 * warp, 32), acc);
+            }
+            const int i = 32 * warp + lane;
+            if (i < two) {
 #pragma unroll
-                for (int o = 0; o < NO; ++o)
-                    if (lane + 32 * o < two) red[(warp * K + k) * (two + 1) + lane + 32 * o] = dv[k][o];
-                if (lane == 0) red[(warp * K + k) * (two + 1) + two] = sig[k];
+                for (int k = 0; k < kMaxKB; ++k)
+                    if (k < K) peer(cl, inbox_dv, k % C)[(r * Ks + k / C) * two + i] = acc[k];
             }
         }
+        if (n_chunks > 0) ++d2_phase;
+        tcgen05_fence_before();
         __syncthreads();
-        for (int e = tid; e < K * (two + 1); e += kConsumers) {
-            const int k = e / (two + 1), i = e - k * (two + 1);
-            float sum = 0.0f;
-            for (int w = 0; w < kConsumers / 32; ++w) sum += red[(w * K + k) * (two + 1) + i];
-            if (i < two) peer(cl, inbox_dv, k % C)[(r * Ks + k / C) * two + i] = sum;
-            else peer(cl, inbox_sig, k % C)[r * Ks + k / C] = sum;
+        if (tid < K) {
+            const int k = tid, half = k >> 2, q = k & 3;
+            const float sum = red[(4 * half) * 4 + q] + red[(4 * half + 1) * 4 + q];   // warps 4 half, 4 half + 1
+            peer(cl, inbox_sig, k % C)[r * Ks + k / C] = sum;
         }
+        BMARK(5);
         cl.sync();   // 2
+        BMARK(6);
         // ---------------- T1: the owners' slots
         if (tid < Ks) {
             const int kl = tid;
@@ -571,7 +655,9 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
                 peer(cl, ds_all, p)[k * d + i] = own_ds;
             }
         }
+        BMARK(7);
         cl.sync();   // 3
+        BMARK(8);
         // ---------------- T2: this block's cells; thread (x, g) takes the targets n = g (mod groups)
         {
             const int x = tid % d, g = tid / d, groups = kConsumers / d;
@@ -587,7 +673,9 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
             __syncthreads();
             for (int e = tid; e < Nc * d; e += kConsumers) A_s[e] = 0.0f;
         }
+        BMARK(9);
         cl.sync();   // 4
+        BMARK(10);
     }
     {
         float* A = c.io.A + (static_cast<int64_t>(row) * N + cell0) * d;
@@ -595,6 +683,9 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
         if (r == 0)
             for (int x = tid; x < d; x += kConsumers) c.io.R[static_cast<int64_t>(row) * d + x] = R_s[x];
     }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(taddr, 64);
 }
 
 }  // namespace
@@ -622,6 +713,7 @@ int hsnw_rows_backward(const HsnwModel* model, const HsnwBackward* io, cudaStrea
     if (L.total + 1024 > hsnw_max_shared()) return -1;
     c.m = *model;
     c.io = *io;
+    c.trace = static_cast<unsigned long long*>(io->scratch);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(io->B) * c.C, 1, 1);
     cfg.blockDim = dim3(kConsumers, 1, 1);
