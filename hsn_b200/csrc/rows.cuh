@@ -24,6 +24,23 @@ __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
+// sum_i a[i * sa] * w[i * sw] with bf16 weights, n a multiple of 8: four independent sums, the loads
+// of a round issued before its products (a single chain of dependent multiply-adds waits for each).
+__device__ __forceinline__ float dot_bf16w(const float* a, int sa, const uint16_t* w, int sw, int n) {
+    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+    for (int i = 0; i < n; i += 8) {
+        const float* pa = a + i * sa;
+        const uint16_t* pw = w + i * sw;
+        const float a0 = pa[0], a1 = pa[sa], a2 = pa[2 * sa], a3 = pa[3 * sa];
+        const float a4 = pa[4 * sa], a5 = pa[5 * sa], a6 = pa[6 * sa], a7 = pa[7 * sa];
+        const uint16_t w0 = pw[0], w1 = pw[sw], w2 = pw[2 * sw], w3 = pw[3 * sw];
+        const uint16_t w4 = pw[4 * sw], w5 = pw[5 * sw], w6 = pw[6 * sw], w7 = pw[7 * sw];
+        s0 += a0 * bf16_value(w0); s1 += a1 * bf16_value(w1); s2 += a2 * bf16_value(w2); s3 += a3 * bf16_value(w3);
+        s0 += a4 * bf16_value(w4); s1 += a5 * bf16_value(w5); s2 += a6 * bf16_value(w6); s3 += a7 * bf16_value(w7);
+    }
+    return (s0 + s1) + (s2 + s3);
+}
+
 // A bounded wait on a ring barrier. After the first wait of the block that ran out (recorded in
 // *failed and in the status word) every later wait returns at once, so a broken pipeline costs one
 // time-out, not one per stage: the kernel still reaches every cluster barrier and ends.

@@ -45,7 +45,7 @@ using namespace hsnw;
 namespace {
 
 constexpr int kRowThreads = 288;      // + the producer warp
-constexpr int kStages = 3;            // ring depth
+constexpr int kMaxStages = 3;         // ring depth (2 when 3 slots do not fit beside a large state)
 constexpr int kMaxK = 8;              // slots (register accumulators per slot)
 constexpr int kMaxMR = 16;            // units
 constexpr int kFrontCols = 256;       // merged front columns per block (2H / C with H = 128 C)
@@ -59,6 +59,7 @@ struct RowsCtx {
     uint32_t w1_bytes;        // its W1 part
     uint32_t front_bytes;     // one front chunk
     uint32_t slot_bytes;      // ring slot
+    uint32_t stages;          // ring depth
     const float* pre_s;       // [B*T, H]
     int* status;
 };
@@ -71,7 +72,7 @@ struct RowsSmem {
         fb1p, score_all, unit_all, age_all, q, ue, rowterm, hold, big, msg, rms, src, ew, b2, gacc, inbox_front,
         inbox_f, inbox_delta, in_scal, in_pre, in_z, upd, cell_of, unit_of, ulist, umask, cand, total;
 };
-__host__ __device__ inline RowsSmem rows_smem(const HsnwModel& m, int C, uint32_t slot_bytes) {
+__host__ __device__ inline RowsSmem rows_smem(const HsnwModel& m, int C, uint32_t slot_bytes, uint32_t stages) {
     RowsSmem L;
     const size_t d = m.d, N = m.N, K = m.K, M = m.M, D = m.D, S = m.S, Nc = N / C, Ks = (K + C - 1) / C;
     size_t o = 0;
@@ -80,7 +81,7 @@ __host__ __device__ inline RowsSmem rows_smem(const HsnwModel& m, int C, uint32_
         o += up16(bytes);
         return at;
     };
-    L.ring = take(static_cast<size_t>(kStages) * slot_bytes);
+    L.ring = take(static_cast<size_t>(stages) * slot_bytes);
     L.h = take(4 * Nc * d);
     L.vh = take(2 * Nc * d);            // bf16: the values are bf16 in this mode
     L.lh = take(4 * Nc * M);
@@ -151,106 +152,11 @@ __host__ __device__ inline RowsSmem rows_smem(const HsnwModel& m, int C, uint32_
 #define RMARK(i) do { } while (0)
 #endif
 
-// One streamed chunk (unit j, 64 hidden columns) for the NS slots that run unit j, by one warp
-// on the chunk's columns 8 warp .. 8 warp + 7: lane (c8 = lane & 7, pg = lane >> 3) multiplies
-// column c8 by the planes pg, pg + 4, ... of every slot's input, the four plane groups are folded
-// by shuffles, then bias, rounding, record, activation, and the warp's 8 columns of the second
-// layer for the outputs x0 = lane and x1 = lane + 32. fp0 / fp1 [s]: the partial outputs of slot
-// ks[s]. NS is a compile-time count so the slots' sums are independent chains without branches.
-template <int D_, int NS>
-__device__ __forceinline__ void unit_stage(const uint4* W1s, const uint4* W2s, const float* v, unsigned mask,
-                                           float bias, float* rec_hidden_col, int rec_stride, int warp, int lane,
-                                           float (&f0)[kMaxK], float (&f1)[kMaxK]) {
-    const int c8 = warp * 8 + (lane & 7), pg = lane >> 3;
-    int ks[NS];
-    const float4* vp[NS];
-    float h0[NS], h1[NS];
-#pragma unroll
-    for (int s = 0; s < NS; ++s) {
-        ks[s] = __fns(mask, 0, s + 1);
-        vp[s] = reinterpret_cast<const float4*>(v + ks[s] * 4 * D_);
-        h0[s] = h1[s] = 0.0f;
-    }
-#pragma unroll
-    for (int p = pg; p < D_ / 2; p += 4) {
-        const uint4 w = W1s[p * 64 + c8];
-        const float w0 = bf16_lo(w.x), w1 = bf16_hi(w.x), w2 = bf16_lo(w.y), w3 = bf16_hi(w.y);
-        const float w4 = bf16_lo(w.z), w5 = bf16_hi(w.z), w6 = bf16_lo(w.w), w7 = bf16_hi(w.w);
-#pragma unroll
-        for (int s = 0; s < NS; ++s) {
-            const float4 a = vp[s][2 * p], b = vp[s][2 * p + 1];
-            h0[s] += a.x * w0;
-            h1[s] += a.y * w1;
-            h0[s] += a.z * w2;
-            h1[s] += a.w * w3;
-            h0[s] += b.x * w4;
-            h1[s] += b.y * w5;
-            h0[s] += b.z * w6;
-            h1[s] += b.w * w7;
-        }
-    }
-    const int x0 = lane, x1 = lane + 32;
-    uint4 wa = make_uint4(0u, 0u, 0u, 0u), wb = wa;
-    if (x0 < D_) wa = W2s[warp * D_ + x0];
-    if (x1 < D_) wb = W2s[warp * D_ + x1];
-    const float a0w = bf16_lo(wa.x), a1w = bf16_hi(wa.x), a2w = bf16_lo(wa.y), a3w = bf16_hi(wa.y);
-    const float a4w = bf16_lo(wa.z), a5w = bf16_hi(wa.z), a6w = bf16_lo(wa.w), a7w = bf16_hi(wa.w);
-    const float b0w = bf16_lo(wb.x), b1w = bf16_hi(wb.x), b2w = bf16_lo(wb.y), b3w = bf16_hi(wb.y);
-    const float b4w = bf16_lo(wb.z), b5w = bf16_hi(wb.z), b6w = bf16_lo(wb.w), b7w = bf16_hi(wb.w);
-    float fp0[NS], fp1[NS];
-    float sums[NS];
-#pragma unroll
-    for (int s = 0; s < NS; ++s) {
-        float sum = h0[s] + h1[s];
-        sum += __shfl_xor_sync(0xffffffffu, sum, 8);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 16);
-        sums[s] = sum;   // every plane group now holds the column's sum of slot s
-    }
-    // bias, rounding, record and activation for four slots at a time: plane group g takes slot 4q + g
-#pragma unroll
-    for (int q = 0; q < (NS + 3) / 4; ++q) {
-        float mine = sums[4 * q];
-        int my_slot = ks[4 * q];
-        if (4 * q + 1 < NS && pg == 1) { mine = sums[4 * q + 1 < NS ? 4 * q + 1 : 0]; my_slot = ks[4 * q + 1 < NS ? 4 * q + 1 : 0]; }
-        if (4 * q + 2 < NS && pg == 2) { mine = sums[4 * q + 2 < NS ? 4 * q + 2 : 0]; my_slot = ks[4 * q + 2 < NS ? 4 * q + 2 : 0]; }
-        if (4 * q + 3 < NS && pg == 3) { mine = sums[4 * q + 3 < NS ? 4 * q + 3 : 0]; my_slot = ks[4 * q + 3 < NS ? 4 * q + 3 : 0]; }
-        const bool active = 4 * q + pg < NS;
-        const float hid = bf16r(mine + bias);
-        if (rec_hidden_col && active) rec_hidden_col[my_slot * rec_stride] = hid;
-        const float a = bf16r(gelu_erf(hid));
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-            if (4 * q + g < NS) {
-                // lane 8 g + cc holds the activation of column 8 warp + cc for slot 4q + g
-                const float a0 = __shfl_sync(0xffffffffu, a, 8 * g + 0), a1 = __shfl_sync(0xffffffffu, a, 8 * g + 1);
-                const float a2 = __shfl_sync(0xffffffffu, a, 8 * g + 2), a3 = __shfl_sync(0xffffffffu, a, 8 * g + 3);
-                const float a4 = __shfl_sync(0xffffffffu, a, 8 * g + 4), a5 = __shfl_sync(0xffffffffu, a, 8 * g + 5);
-                const float a6 = __shfl_sync(0xffffffffu, a, 8 * g + 6), a7 = __shfl_sync(0xffffffffu, a, 8 * g + 7);
-                fp0[4 * q + g < NS ? 4 * q + g : 0] =
-                    (a0 * a0w + a1 * a1w) + (a2 * a2w + a3 * a3w) + (a4 * a4w + a5 * a5w) + (a6 * a6w + a7 * a7w);
-                fp1[4 * q + g < NS ? 4 * q + g : 0] =
-                    (a0 * b0w + a1 * b1w) + (a2 * b2w + a3 * b3w) + (a4 * b4w + a5 * b5w) + (a6 * b6w + a7 * b7w);
-            }
-        }
-    }
-#pragma unroll
-    for (int k = 0; k < kMaxK; ++k) {
-#pragma unroll
-        for (int s = 0; s < NS; ++s) {
-            if (ks[s] == k) {
-                f0[k] += fp0[s];
-                f1[k] += fp1[s];
-            }
-        }
-    }
-}
-
-
 template <int D_>
 __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
     extern __shared__ __align__(16) unsigned char dyn[];
     __shared__ SelectShared S;
-    __shared__ __align__(8) uint64_t full[kStages], empty[kStages];
+    __shared__ __align__(8) uint64_t full[kMaxStages], empty[kMaxStages];
     __shared__ int n_units_s;    // units some valid slot runs this position
     __shared__ int hmax_local;   // bits of max |h| over the block's cells after the last position
     __shared__ int failed_s;     // a ring wait ran out
@@ -270,7 +176,8 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
     const bool rec = c.io.rec_c != nullptr;
     const int stride_in = 2 * d + 4;   // a block's line of the front inbox: u part, z_hat part, max |h|
 
-    const RowsSmem L = rows_smem(c.m, C, c.slot_bytes);
+    const uint32_t kStages = c.stages;
+    const RowsSmem L = rows_smem(c.m, C, c.slot_bytes, kStages);
     unsigned char* ring = dyn + L.ring;
     float* h_s = reinterpret_cast<float*>(dyn + L.h);
     uint16_t* vh_s = reinterpret_cast<uint16_t*>(dyn + L.vh);
@@ -330,7 +237,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
 
     // ---- once per window: barriers, the resident weights, the block's cells and their derived state
     if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < kMaxStages; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
@@ -433,9 +340,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 ring_wait(&full[slot], (g_use / kStages) & 1u, c.status, &failed_s);
                 const uint16_t* w1c = reinterpret_cast<const uint16_t*>(ring + slot * c.slot_bytes);
                 const int col = tid, colg = r * kFrontCols + col;
-                float sum = 0.0f;
-#pragma unroll 8
-                for (int x = 0; x < d; ++x) sum += ue[x] * bf16_value(w1c[x * kFrontCols + col]);
+                const float sum = dot_bf16w(ue, 1, w1c + col, kFrontCols, d);
                 const float pre = colg >= H ? fb1p[col] : in_pre[col];
                 act[col] = bf16r(gelu_erf(bf16r(sum + pre)));
             }
@@ -447,9 +352,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 const uint16_t* w2c = reinterpret_cast<const uint16_t*>(ring + slot * c.slot_bytes);
                 const int x = tid % d, grp = tid / d;
                 const bool is_p = r * kFrontCols + grp * d >= H;
-                float sum = 0.0f;
-#pragma unroll 8
-                for (int cc = 0; cc < d; ++cc) sum += act[grp * d + cc] * bf16_value(w2c[(grp * d + cc) * d + x]);
+                const float sum = dot_bf16w(act + grp * d, 1, w2c + grp * d * d + x, d, d);
                 fpart[grp * 2 * d + x] = is_p ? 0.0f : sum;
                 fpart[grp * 2 * d + d + x] = is_p ? sum : 0.0f;
             }
@@ -786,15 +689,24 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
             {
                 const int x = tid % d, grp = tid / d, ngrp = kConsumers / d;
                 for (int k = grp; k < K; k += ngrp) {
-                    float sum = 0.0f;
+                    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
                     if (cell_of[k] >= 0) {
-#pragma unroll 8
-                        for (int xi = 0; xi < grows; ++xi) {
+                        // the slot's inputs r grows .. of the operand: 8 consecutive inputs are one 16-byte unit
+                        for (int xi = 0; xi < grows; xi += 8) {
                             const int jx = r * grows + xi;
-                            sum += bf16_value(vop[((jx >> 3) * 16 + k) * 8 + (jx & 7)]) * bf16_value(gate[xi * d + x]);
+                            const uint4 vv = *reinterpret_cast<const uint4*>(vop + ((jx >> 3) * 16 + k) * 8);
+                            const uint16_t* g = gate + xi * d + x;
+                            s0 += bf16_lo(vv.x) * bf16_value(g[0]);
+                            s1 += bf16_hi(vv.x) * bf16_value(g[d]);
+                            s2 += bf16_lo(vv.y) * bf16_value(g[2 * d]);
+                            s3 += bf16_hi(vv.y) * bf16_value(g[3 * d]);
+                            s0 += bf16_lo(vv.z) * bf16_value(g[4 * d]);
+                            s1 += bf16_hi(vv.z) * bf16_value(g[5 * d]);
+                            s2 += bf16_lo(vv.w) * bf16_value(g[6 * d]);
+                            s3 += bf16_hi(vv.w) * bf16_value(g[7 * d]);
                         }
                     }
-                    gacc[k * d + x] = sum;
+                    gacc[k * d + x] = (s0 + s1) + (s2 + s3);
                 }
             }
             RMARK(7);
@@ -814,6 +726,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
             const int sh = warp >> 2;                         // its half of the slots: 4 sh .. 4 sh + 3
             const uint32_t idesc = umma_idesc_bf16(128, 16);
             const uint32_t g0 = g_use;
+            float bias_next = (epi && n_chunks > 0) ? c.m.b1[ulist[0] * H + r * 128 + hc] : 0.0f;   // a chunk ahead
             if (tid == 0 && n_chunks > 0) {
                 const uint32_t slot = g0 % kStages;
                 ring_wait(&full[slot], (g0 / kStages) & 1u, c.status, &failed_s);
@@ -836,7 +749,8 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 }
                 if (epi) {
                     const int colg = r * 128 + (i & 1) * 64 + hc;
-                    const float bias = c.m.b1[j * H + colg];
+                    const float bias = bias_next;
+                    if (i + 1 < n_chunks) bias_next = c.m.b1[ulist[(i + 1) >> 1] * H + r * 128 + ((i + 1) & 1) * 64 + hc];
                     uint16_t* b2i = b2 + (i & 1) * (8 * 16 * 8);
                     ring_wait(&bar_d1[i & 1], ((i & 1) ? d1_count1 : d1_count0) & 1u, c.status, &failed_s);
                     tcgen05_fence_after();
@@ -914,10 +828,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
             RMARK(19);
             for (int e = tid; e < Ks * d; e += kConsumers) {
                 const int kl = e / d, x = e - kl * d;
-                float sum = 0.0f;
-#pragma unroll 8
-                for (int xi = 0; xi < d; ++xi) sum += Fk[kl * d + xi] * bf16_value(wout[xi * d + x]);
-                ys[e] = bf16r(sum);
+                ys[e] = bf16r(dot_bf16w(Fk + kl * d, 1, wout + x, d, d));
             }
             consumer_sync();
             RMARK(20);
@@ -967,10 +878,10 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                     const float* hr = hb + kl * d;
                     float sum = 0.0f;
                     if (w < M) {
-                        for (int x = 0; x < d; ++x) sum += hr[x] * swh[x * M + w];
+                        sum = dot4(hr, 1, swh + w, M, d);
                         peer(cl, lh_s, owner)[cc * M + w] = sum;
                     } else {
-                        for (int x = 0; x < d; ++x) sum += hr[x] * bf16_value(vt[x * d + (w - M)]);
+                        sum = dot_bf16w(hr, 1, vt + (w - M), d, d);
                         peer(cl, vh_s, owner)[cc * d + (w - M)] = bf16_bits(sum);
                     }
                 }
@@ -1098,8 +1009,13 @@ static bool rows_shape(const HsnwModel& m, RowsCtx* c) {
 int hsnw_rows_forward(const HsnwModel* model, const HsnwForward* io, const float* pre_s, int* status, cudaStream_t stream) {
     RowsCtx c;
     if (!rows_shape(*model, &c)) return -1;
-    const RowsSmem L = rows_smem(*model, c.C, c.slot_bytes);
-    if (L.total + 2048 > hsnw_max_shared()) return -1;
+    c.stages = kMaxStages;
+    RowsSmem L = rows_smem(*model, c.C, c.slot_bytes, c.stages);
+    if (L.total + 2048 > hsnw_max_shared()) {
+        c.stages = 2;
+        L = rows_smem(*model, c.C, c.slot_bytes, c.stages);
+        if (L.total + 2048 > hsnw_max_shared()) return -1;
+    }
     c.m = *model;
     c.io = *io;
     c.pre_s = pre_s;

@@ -103,91 +103,6 @@ __host__ __device__ inline RowsBwdSmem rows_bwd_smem(const HsnwModel& m, int C, 
     return L;
 }
 
-// One streamed chunk of the reverse sweep (unit j, 64 hidden columns) for the NS slots that ran
-// unit j, by one warp on the chunk's columns 8 warp .. 8 warp + 7. du: the slots' d_unit rows
-// (bf16 values) [K][d]; hid: the recorded pre-activations of those columns, hid[k * 128 + column
-// of the block]. The warp's partial of dv (outputs lane, lane + 32, ... of the 2d state columns) and
-// of the norm's inner product are added to dv[k][.] / sig[k].
-template <int D_, int NS>
-__device__ __forceinline__ void bwd_stage(const uint4* W2s, const uint4* W1s, const float* du, const float* hid,
-                                          int hid_col, float bias, unsigned mask, int warp, int lane,
-                                          float (&dv)[kMaxKB][(2 * D_ + 31) / 32], float (&sig)[kMaxKB]) {
-    constexpr int NO = (2 * D_ + 31) / 32;   // state outputs per lane
-    const int c8 = warp * 8 + (lane & 7), pg = lane >> 3;
-    int ks[NS];
-    const float4* up[NS];
-    float h0[NS], h1[NS];
-#pragma unroll
-    for (int s = 0; s < NS; ++s) {
-        ks[s] = __fns(mask, 0, s + 1);
-        up[s] = reinterpret_cast<const float4*>(du + ks[s] * D_);
-        h0[s] = h1[s] = 0.0f;
-    }
-    // the transposed second layer: dact[column] = sum_x d_unit[x] W2[column][x]
-#pragma unroll
-    for (int p = pg; p < D_ / 8; p += 4) {
-        const uint4 w = W2s[p * 64 + c8];
-        const float w0 = bf16_lo(w.x), w1 = bf16_hi(w.x), w2 = bf16_lo(w.y), w3 = bf16_hi(w.y);
-        const float w4 = bf16_lo(w.z), w5 = bf16_hi(w.z), w6 = bf16_lo(w.w), w7 = bf16_hi(w.w);
-#pragma unroll
-        for (int s = 0; s < NS; ++s) {
-            const float4 a = up[s][2 * p], b = up[s][2 * p + 1];
-            h0[s] += a.x * w0;
-            h1[s] += a.y * w1;
-            h0[s] += a.z * w2;
-            h1[s] += a.w * w3;
-            h0[s] += b.x * w4;
-            h1[s] += b.y * w5;
-            h0[s] += b.z * w6;
-            h1[s] += b.w * w7;
-        }
-    }
-    // the state rows of W1 for this warp's 8 columns: plane `warp` of [8][2d][8]
-    float wr[NO][8];
-#pragma unroll
-    for (int o = 0; o < NO; ++o) {
-        const int i = lane + 32 * o;
-        uint4 w = make_uint4(0u, 0u, 0u, 0u);
-        if (i < 2 * D_) w = W1s[warp * 2 * D_ + i];
-        wr[o][0] = bf16_lo(w.x); wr[o][1] = bf16_hi(w.x); wr[o][2] = bf16_lo(w.y); wr[o][3] = bf16_hi(w.y);
-        wr[o][4] = bf16_lo(w.z); wr[o][5] = bf16_hi(w.z); wr[o][6] = bf16_lo(w.w); wr[o][7] = bf16_hi(w.w);
-    }
-    float part[NS][NO], inner[NS];
-#pragma unroll
-    for (int s = 0; s < NS; ++s) {
-        float sum = h0[s] + h1[s];
-        sum += __shfl_xor_sync(0xffffffffu, sum, 8);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 16);
-        const float hv = hid[ks[s] * 128 + hid_col];
-        const float dh = bf16r(sum * gelu_erf_grad(hv));
-        // the norm's inner product over the warp's 8 columns (lanes 0..7 hold them)
-        float in = dh * (hv - bias);
-        in += __shfl_xor_sync(0xffffffffu, in, 1);
-        in += __shfl_xor_sync(0xffffffffu, in, 2);
-        in += __shfl_xor_sync(0xffffffffu, in, 4);
-        inner[s] = in;
-        const float a0 = __shfl_sync(0xffffffffu, dh, 0), a1 = __shfl_sync(0xffffffffu, dh, 1);
-        const float a2 = __shfl_sync(0xffffffffu, dh, 2), a3 = __shfl_sync(0xffffffffu, dh, 3);
-        const float a4 = __shfl_sync(0xffffffffu, dh, 4), a5 = __shfl_sync(0xffffffffu, dh, 5);
-        const float a6 = __shfl_sync(0xffffffffu, dh, 6), a7 = __shfl_sync(0xffffffffu, dh, 7);
-#pragma unroll
-        for (int o = 0; o < NO; ++o)
-            part[s][o] = (a0 * wr[o][0] + a1 * wr[o][1]) + (a2 * wr[o][2] + a3 * wr[o][3])
-                + (a4 * wr[o][4] + a5 * wr[o][5]) + (a6 * wr[o][6] + a7 * wr[o][7]);
-    }
-#pragma unroll
-    for (int k = 0; k < kMaxKB; ++k) {
-#pragma unroll
-        for (int s = 0; s < NS; ++s) {
-            if (ks[s] == k) {
-                sig[k] += inner[s];
-#pragma unroll
-                for (int o = 0; o < NO; ++o) dv[k][o] += part[s][o];
-            }
-        }
-    }
-}
-
 template <int D_>
 __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
     extern __shared__ __align__(16) unsigned char dyn[];
@@ -197,7 +112,7 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
     __shared__ uint32_t tmem_slot;
 
     cg::cluster_group cl = cg::this_cluster();
-    constexpr int d = D_, two = 2 * D_, NO = (2 * D_ + 31) / 32;
+    constexpr int d = D_, two = 2 * D_;
     const int C = c.C, r = static_cast<int>(cl.block_rank());
     const int row = blockIdx.x / C;
     const int N = c.m.N, K = c.m.K, M = c.m.M, D = c.m.D, H = c.m.H;
@@ -472,13 +387,7 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
         for (int e = tid; e < Ks * d; e += kConsumers) {
             const int kl = e / d, i = e - kl * d, k = kl * C + r;
             if (k >= K) continue;
-            float s0 = 0.0f, s1 = 0.0f;
-#pragma unroll 8
-            for (int x = 0; x < d; x += 2) {
-                s0 += dy[kl * d + x] * bf16_value(wout[i * d + x]);
-                s1 += dy[kl * d + x + 1] * bf16_value(wout[i * d + x + 1]);
-            }
-            const uint16_t dub = bf16_bits(s0 + s1);
+            const uint16_t dub = bf16_bits(dot_bf16w(dy + kl * d, 1, wout + i * d, 1, d));
             for (int p = 0; p < C; ++p) peer(cl, du_op, p)[((i >> 3) * 16 + k) * 8 + (i & 7)] = dub;
         }
         BMARK(1);
@@ -499,15 +408,8 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
             // the gate's transposed linear, this block's state outputs
             const int k = tid / gcols, il = tid - k * gcols;
             if (k < K) {
-                float s0 = 0.0f, s1 = 0.0f;
-                if (dc_[k] >= 0) {
-#pragma unroll 8
-                    for (int x = 0; x < d; x += 2) {
-                        s0 += dg_all[k * d + x] * bf16_value(gate[il * d + x]);
-                        s1 += dg_all[k * d + x + 1] * bf16_value(gate[il * d + x + 1]);
-                    }
-                }
-                peer(cl, inbox_g, k % C)[(k / C) * two + r * gcols + il] = s0 + s1;
+                const float sum = dc_[k] >= 0 ? dot_bf16w(dg_all + k * d, 1, gate + il * d, 1, d) : 0.0f;
+                peer(cl, inbox_g, k % C)[(k / C) * two + r * gcols + il] = sum;
             }
         }
         BMARK(3);
@@ -643,13 +545,7 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
         for (int e = tid; e < Ks * d; e += kConsumers) {
             const int kl = e / d, i = e - kl * d, k = kl * C + r;
             if (k >= K) continue;
-            float s0 = 0.0f, s1 = 0.0f;
-#pragma unroll 8
-            for (int x = 0; x < d; x += 2) {
-                s0 += ds[kl * two + d + x] * bf16_value(vt[i * d + x]);
-                s1 += ds[kl * two + d + x + 1] * bf16_value(vt[i * d + x + 1]);
-            }
-            const float dvm = s0 + s1, own_ds = ds[kl * two + i];
+            const float dvm = dot_bf16w(ds + kl * two + d, 1, vt + i * d, 1, d), own_ds = ds[kl * two + i];
             for (int p = 0; p < C; ++p) {
                 peer(cl, dvm_all, p)[k * d + i] = dvm;
                 peer(cl, ds_all, p)[k * d + i] = own_ds;
