@@ -40,6 +40,24 @@ __device__ __forceinline__ uint64_t umma_desc(const void* smem_tile, int rows) {
     return desc;                                                                            // layout type 0: no swizzle
 }
 
+// Shared-memory matrix descriptor for a K-major tile in the 128-byte swizzle: rows of 64 bf16 (128
+// bytes, one K-block), groups of 8 rows are 1024-byte atoms in which the 16-byte unit u of row r sits
+// at unit u ^ (r % 8); the tile starts on a 1024-byte boundary. Stride between row groups 1024 bytes;
+// the leading offset is not used by this layout. A K = 16 step inside the block moves the start
+// address by 32 bytes; the next K-block of a wider tile starts rows x 128 bytes further on. The
+// tensor cores fetch this layout a 128-byte row at a time (the unswizzled layout above goes 16 bytes
+// at a time: an M = 128 product then costs ~256 cycles of operand fetch whatever N is).
+__device__ __forceinline__ uint64_t umma_desc_sw128(const void* smem_tile) {
+    const uint32_t addr = smem_addr(smem_tile);
+    uint64_t desc = 0;
+    desc |= static_cast<uint64_t>((addr >> 4) & 0x3fffu);
+    desc |= static_cast<uint64_t>(1) << 16;                     // leading byte offset: unused, 1
+    desc |= static_cast<uint64_t>((1024u >> 4) & 0x3fffu) << 32;  // stride byte offset
+    desc |= static_cast<uint64_t>(1) << 46;                     // descriptor version (sm_100)
+    desc |= static_cast<uint64_t>(2) << 61;                     // layout type: 128-byte swizzle
+    return desc;
+}
+
 // TMEM: `columns` is a power of two >= 32. Executed by one whole warp; the base address lands in
 // *slot (shared memory). Every .sync.aligned instruction here is preceded by __syncwarp(): a warp
 // that left a polling loop or a single-thread branch is not necessarily converged, and an aligned
@@ -83,6 +101,38 @@ static __device__ __noinline__ void umma_chain(uint32_t tmem_d, uint64_t desc_a,
     for (int s = 0; s < steps; ++s)
         umma_bf16(tmem_d, desc_a + static_cast<uint64_t>(s) * a_step, desc_b + static_cast<uint64_t>(s) * b_step, idesc,
                   onto || s > 0);
+}
+// The same chain spread round-robin over n_acc accumulators acc_stride columns apart (their sum is
+// the product). Products into ONE accumulator execute one after the other, each waiting out the
+// tensor pipe's latency, which dominates when N is small; consecutive products into different
+// accumulators overlap.
+static __device__ __noinline__ void umma_chain_spread(uint32_t tmem_d, uint32_t acc_stride, int n_acc, uint64_t desc_a,
+                                                      uint64_t desc_b, uint32_t idesc, int steps, uint32_t a_step,
+                                                      uint32_t b_step, bool onto = false) {
+    for (int s = 0; s < steps; ++s)
+        umma_bf16(tmem_d + static_cast<uint32_t>(s % n_acc) * acc_stride, desc_a + static_cast<uint64_t>(s) * a_step,
+                  desc_b + static_cast<uint64_t>(s) * b_step, idesc, onto || s >= n_acc);
+}
+// The same with the counts known at compile time: the loop unrolls to a few instructions per product
+// (one thread issues them, so every instruction of the loop is on the critical path).
+template <int STEPS, int NACC>
+static __device__ __noinline__ void umma_chain_fixed(uint32_t tmem_d, uint32_t acc_stride, uint64_t desc_a, uint64_t desc_b,
+                                                     uint32_t idesc, uint32_t a_step, uint32_t b_step, bool onto) {
+#pragma unroll
+    for (int s = 0; s < STEPS; ++s)
+        umma_bf16(tmem_d + static_cast<uint32_t>(s % NACC) * acc_stride, desc_a + static_cast<uint64_t>(s) * a_step,
+                  desc_b + static_cast<uint64_t>(s) * b_step, idesc, onto || s >= NACC);
+}
+// The chain for an A tile in the 128-byte swizzle (K-blocks of 64: four K = 16 steps of 32 bytes, then
+// the next block a_block 16-byte units further on) and a B tile in the unswizzled layout.
+template <int STEPS, int NACC>
+static __device__ __noinline__ void umma_chain_sw128(uint32_t tmem_d, uint32_t acc_stride, uint64_t desc_a, uint32_t a_block,
+                                                     uint64_t desc_b, uint32_t b_step, uint32_t idesc, bool onto) {
+#pragma unroll
+    for (int s = 0; s < STEPS; ++s)
+        umma_bf16(tmem_d + static_cast<uint32_t>(s % NACC) * acc_stride,
+                  desc_a + static_cast<uint64_t>(s >> 2) * a_block + static_cast<uint64_t>(s & 3) * 2u,
+                  desc_b + static_cast<uint64_t>(s) * b_step, idesc, onto || s >= NACC);
 }
 // The step between two K = 16 products of a tile of `rows` rows in the layout above.
 __host__ __device__ constexpr uint32_t umma_kstep(int rows) { return static_cast<uint32_t>((2 * rows * 16) >> 4); }

@@ -69,7 +69,7 @@ __host__ __device__ inline size_t up16(size_t v) { return (v + 15) & ~static_cas
 // Offsets (bytes) of the dynamic shared memory's segments.
 struct RowsSmem {
     size_t ring, h, vh, lh, age, cmax, wout, vt, gate, swh, sw_head, sw_tail, norm_w, cand_w, fb2, gate_b, score_b,
-        fb1p, score_all, unit_all, age_all, q, ue, rowterm, hold, big, msg, rms, src, ew, b2, gacc, inbox_front,
+        fb1p, score_all, unit_all, age_all, q, ue, rowterm, hold, big, msg, rms, graph, b2, gacc, inbox_front,
         inbox_f, inbox_delta, in_scal, in_pre, in_z, upd, cell_of, unit_of, ulist, umask, cand, total;
 };
 __host__ __device__ inline RowsSmem rows_smem(const HsnwModel& m, int C, uint32_t slot_bytes, uint32_t stages) {
@@ -81,7 +81,7 @@ __host__ __device__ inline RowsSmem rows_smem(const HsnwModel& m, int C, uint32_
         o += up16(bytes);
         return at;
     };
-    L.ring = take(static_cast<size_t>(stages) * slot_bytes);
+    L.ring = take(static_cast<size_t>(stages) * slot_bytes + 1024);   // + room to start on a 1024-byte boundary (swizzled tiles)
     L.h = take(4 * Nc * d);
     L.vh = take(2 * Nc * d);            // bf16: the values are bf16 in this mode
     L.lh = take(4 * Nc * M);
@@ -116,13 +116,10 @@ __host__ __device__ inline RowsSmem rows_smem(const HsnwModel& m, int C, uint32_
     }
     L.msg = take(4 * K * d);
     L.rms = take(4 * K);
-    L.src = take(4 * K * D);
-    L.ew = take(4 * K * D);
-    L.b2 = take(2 * 2 * 8 * 16 * 8);    // two bf16 operands [8][16][8]: the activations of a chunk's 64 columns
+    L.graph = take(4 * N * D);          // every cell's sources and edge weights: (source << 16) | bf16 weight
     L.gacc = take(4 * K * d);
     L.inbox_front = take(4 * C * (2 * d + 4));
     L.inbox_f = take(4 * C * Ks * 2 * d);
-    L.inbox_delta = take(4 * K * d);
     L.in_scal = take(4 * Nc * S + 16);
     L.in_pre = take(4 * kFrontCols);
     L.in_z = take(4 * d);
@@ -131,7 +128,14 @@ __host__ __device__ inline RowsSmem rows_smem(const HsnwModel& m, int C, uint32_
     L.unit_of = take(4 * K);
     L.ulist = take(4 * (kMaxMR + 4));
     L.umask = take(4 * (kMaxMR + 4));
-    L.cand = take(8 * N + 64);          // the cells' keys, then [8] stale counts per warp and [K] flags
+    // phase C's keys ([N] then [8] stale counts per warp and [K] flags) and phase E/F's inbox of the
+    // slots' changes are adjacent: phase D's two activation operands (bf16 [8][16][8] each, 4 KB) use
+    // the same bytes between them (C is over when D starts; E's stores come after the barrier that
+    // ends D)
+    L.cand = take(8 * N + 64);
+    L.inbox_delta = take(4 * K * d);
+    L.b2 = L.cand;
+    if (L.inbox_delta + up16(4 * K * d) - L.cand < 2 * 2 * 8 * 16 * 8) o = L.cand + 2 * 2 * 8 * 16 * 8;
     L.total = o;
     return L;
 }
@@ -178,7 +182,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
 
     const uint32_t kStages = c.stages;
     const RowsSmem L = rows_smem(c.m, C, c.slot_bytes, kStages);
-    unsigned char* ring = dyn + L.ring;
+    unsigned char* ring = dyn + L.ring + ((1024u - (smem_addr(dyn + L.ring) & 1023u)) & 1023u);
     float* h_s = reinterpret_cast<float*>(dyn + L.h);
     uint16_t* vh_s = reinterpret_cast<uint16_t*>(dyn + L.vh);
     float* lh_s = reinterpret_cast<float*>(dyn + L.lh);
@@ -206,9 +210,8 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
     float* big = reinterpret_cast<float*>(dyn + L.big);
     float* msg = reinterpret_cast<float*>(dyn + L.msg);
     float* rms = reinterpret_cast<float*>(dyn + L.rms);
-    int* src = reinterpret_cast<int*>(dyn + L.src);
-    float* ew = reinterpret_cast<float*>(dyn + L.ew);
     uint16_t* b2 = reinterpret_cast<uint16_t*>(dyn + L.b2);
+    uint32_t* graph = reinterpret_cast<uint32_t*>(dyn + L.graph);
     float* gacc = reinterpret_cast<float*>(dyn + L.gacc);
     float* inbox_front = reinterpret_cast<float*>(dyn + L.inbox_front);
     float* inbox_f = reinterpret_cast<float*>(dyn + L.inbox_f);
@@ -231,6 +234,9 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
     float* scale = upd + 6 * Ks * d;
 
     const int cell0 = r * Nc;                 // the block's first cell
+    // cell n lives in block n / Nc at row n % Nc: a multiply-high by ceil(2^32 / Nc), exact for n Nc < 2^32
+    const uint32_t nc_magic = 0xffffffffu / static_cast<uint32_t>(Nc) + 1u;
+    auto owner_of = [&](int n) { return static_cast<int>(__umulhi(static_cast<uint32_t>(n), nc_magic)); };
     const int pre_cols = max(0, min(kFrontCols, H - r * kFrontCols));  // its columns that belong to S
     const unsigned char* bank = static_cast<const unsigned char*>(c.m.rows_bank);
     const unsigned char* front = static_cast<const unsigned char*>(c.m.rows_front);
@@ -267,8 +273,9 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
         S.cost[e] = c.m.cost[e];
     }
     for (int e = tid; e < kFrontCols; e += kRowThreads) fb1p[e] = c.m.f_b1[r * kFrontCols + e];
-    if (warp == 0) tmem_alloc(&tmem_slot, 64);
-    for (int e = tid; e < 2 * 8 * 16 * 8; e += kRowThreads) b2[e] = 0;
+    if (warp == 0) tmem_alloc(&tmem_slot, 512);
+    for (int e = tid; e < N * D; e += kRowThreads)
+        graph[e] = (static_cast<uint32_t>(c.m.pad_src[e]) << 16) | bf16_bits(c.m.edge_w[e]);
     const bool cut0 = c.io.reset[static_cast<int64_t>(row) * T] != 0;
     {
         const float* h0 = c.io.h0 + (static_cast<int64_t>(row) * N + cell0) * d;
@@ -627,28 +634,28 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 prefetch_floats(in_z, c.io.z + (rt + 1) * d, d, tid);
             }
             cp_async_commit();
-            for (int e = tid; e < K * D; e += kConsumers) {
-                const int k = e / D, jj = e - k * D;
-                const int cell = S.out_cell[k];
-                src[e] = c.m.pad_src[cell * D + jj];
-                ew[e] = bf16r(c.m.edge_w[cell * D + jj]);
-            }
+            RMARK(24);
             for (int e = tid; e < K * d; e += kConsumers) {
                 const int k = e / d, x = e - k * d;
                 const int cell = S.out_cell[k];
-                hold[e] = peer(cl, h_s, cell / Nc)[(cell % Nc) * d + x];
-            }
-            consumer_sync();
-            for (int e = tid; e < K * d; e += kConsumers) {
-                const int k = e / d, x = e - k * d;
+                const int co = owner_of(cell);
+                hold[e] = peer(cl, h_s, co)[(cell - co * Nc) * d + x];
                 float sum = 0.0f;
                 for (int jj = 0; jj < D; ++jj) {   // edge order; the sources' V h rows at their owners
-                    const int sc = src[k * D + jj];
-                    sum += bf16_value(peer(cl, vh_s, sc / Nc)[(sc % Nc) * d + x]) * ew[k * D + jj];
+                    const uint32_t edge = graph[cell * D + jj];
+                    const int sc = static_cast<int>(edge >> 16);
+                    const int so = owner_of(sc);
+                    sum += bf16_value(peer(cl, vh_s, so)[(sc - so * Nc) * d + x]) * bf16_lo(edge);
                 }
                 msg[e] = bf16r(sum);
             }
+            // rows 8..15 of the two activation operands (their bytes belong to other phases' data)
+            for (int e = tid; e < 2 * 8 * 8; e += kConsumers) {
+                const int which = e >> 6, p = (e >> 3) & 7, k = 8 + (e & 7);
+                reinterpret_cast<uint4*>(b2 + which * (8 * 16 * 8))[p * 16 + k] = make_uint4(0u, 0u, 0u, 0u);
+            }
             consumer_sync();
+            RMARK(22);
             for (int k = warp; k < K; k += kConsumers / 32) {
                 float sq = 0.0f;
                 for (int jx = lane; jx < 4 * d; jx += 32) {
@@ -660,6 +667,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 if (lane == 0) rms[k] = rsqrtf(sq / static_cast<float>(4 * d) + c.m.norm_eps);
             }
             consumer_sync();
+            RMARK(23);
             RMARK(6);
             // the pairs' inputs as the tensor cores' B operand: bf16 [4d/8][16 slots][8] (slots K..15 stay zero)
             uint16_t* vop = reinterpret_cast<uint16_t*>(big);
@@ -720,31 +728,42 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
             // hands the ring slot back. Thread 0 issues; warps 0, 1, 4, 5 read the accumulators.
             fence_async_smem();   // the operand written above, before the tensor cores read it
             consumer_sync();
+            RMARK(30);
             const int n_chunks = 2 * n_units;
             const bool epi = (warp & 2) == 0;                 // warps 0, 1, 4, 5
             const int hc = lane + 32 * (warp & 1);            // the epilogue thread's column of the chunk (TMEM lane)
             const int sh = warp >> 2;                         // its half of the slots: 4 sh .. 4 sh + 3
             const uint32_t idesc = umma_idesc_bf16(128, 16);
+            constexpr int steps1 = (4 * d) >> 4;            // K = 16 products of a chunk's first layer
+            constexpr int n1 = steps1 < 8 ? steps1 : 8;     // accumulators they are spread over (columns 128 b + 16 p)
             const uint32_t g0 = g_use;
             float bias_next = (epi && n_chunks > 0) ? c.m.b1[ulist[0] * H + r * 128 + hc] : 0.0f;   // a chunk ahead
             if (tid == 0 && n_chunks > 0) {
                 const uint32_t slot = g0 % kStages;
                 ring_wait(&full[slot], (g0 / kStages) & 1u, c.status, &failed_s);
                 tcgen05_fence_after();
-                umma_chain(taddr, umma_desc(ring + slot * c.slot_bytes, 64), umma_desc(vop, 16), idesc, (4 * d) >> 4,
-                           umma_kstep(64), umma_kstep(16));
+                if (d == 64)
+                    umma_chain_sw128<steps1, n1>(taddr, 16, umma_desc_sw128(ring + slot * c.slot_bytes), (64 * 128) >> 4,
+                                                 umma_desc(vop, 16), umma_kstep(16), idesc, false);
+                else
+                    umma_chain_fixed<steps1, n1>(taddr, 16, umma_desc(ring + slot * c.slot_bytes, 64), umma_desc(vop, 16), idesc,
+                                                 umma_kstep(64), umma_kstep(16), false);
                 umma_commit(&bar_d1[0]);
+                RMARK(29);
             }
             for (int i = 0; i < n_chunks; ++i) {
-                const int j = ulist[i >> 1];
                 const unsigned mask = static_cast<unsigned>(umask[i >> 1]);
                 const uint32_t slot = (g0 + i) % kStages;
                 if (tid == 0 && i + 1 < n_chunks) {   // the next chunk's first product runs under this epilogue
                     const uint32_t nslot = (g0 + i + 1) % kStages;
                     ring_wait(&full[nslot], ((g0 + i + 1) / kStages) & 1u, c.status, &failed_s);
                     tcgen05_fence_after();
-                    umma_chain(taddr + 16 * ((i + 1) & 1), umma_desc(ring + nslot * c.slot_bytes, 64), umma_desc(vop, 16), idesc,
-                               (4 * d) >> 4, umma_kstep(64), umma_kstep(16));
+                    if (d == 64)
+                        umma_chain_sw128<steps1, n1>(taddr + 128 * ((i + 1) & 1), 16, umma_desc_sw128(ring + nslot * c.slot_bytes),
+                                                     (64 * 128) >> 4, umma_desc(vop, 16), umma_kstep(16), idesc, false);
+                    else
+                        umma_chain_fixed<steps1, n1>(taddr + 128 * ((i + 1) & 1), 16, umma_desc(ring + nslot * c.slot_bytes, 64),
+                                                     umma_desc(vop, 16), idesc, umma_kstep(64), umma_kstep(16), false);
                     umma_commit(&bar_d1[(i + 1) & 1]);
                 }
                 if (epi) {
@@ -754,8 +773,16 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                     uint16_t* b2i = b2 + (i & 1) * (8 * 16 * 8);
                     ring_wait(&bar_d1[i & 1], ((i & 1) ? d1_count1 : d1_count0) & 1u, c.status, &failed_s);
                     tcgen05_fence_after();
+                    if (i == 0) RMARK(25);
                     float acc[8];
-                    tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 16 * (i & 1)), acc);
+                    tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 128 * (i & 1)), acc);
+#pragma unroll
+                    for (int p = 1; p < n1; ++p) {   // the partial accumulators
+                        float more[8];
+                        tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 128 * (i & 1) + 16 * p), more);
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) acc[q] += more[q];
+                    }
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         const int k = 4 * sh + q;
@@ -769,18 +796,25 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                     }
                     fence_async_smem();
                     tcgen05_fence_before();
+                    if (i == 0) RMARK(26);
                 }
                 if (i & 1) ++d1_count1;
                 else ++d1_count0;
                 consumer_sync();
                 if (tid == 0) {
                     tcgen05_fence_after();
-                    umma_chain(taddr + 32, umma_desc(ring + slot * c.slot_bytes + c.w1_bytes, d),
-                               umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), idesc, 64 >> 4, umma_kstep(d), umma_kstep(16),
-                               i > 0);   // D2 sums over the position's chunks
+                    // four partial sums of D2, each over the position's chunks
+                    if (d == 64)
+                        umma_chain_sw128<4, 4>(taddr + 256, 16, umma_desc_sw128(ring + slot * c.slot_bytes + c.w1_bytes), 0,
+                                               umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), umma_kstep(16), idesc, i > 0);
+                    else
+                        umma_chain_fixed<4, 4>(taddr + 256, 16, umma_desc(ring + slot * c.slot_bytes + c.w1_bytes, d),
+                                               umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), idesc, umma_kstep(d), umma_kstep(16),
+                                               i > 0);
                     umma_commit(&empty[slot]);
                     if (i + 1 == n_chunks) umma_commit(&bar_d2);
                 }
+                if (i == 0) RMARK(27);
             }
             g_use += n_chunks;
             RMARK(8);
@@ -793,8 +827,16 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 if (n_chunks > 0) {
                     ring_wait(&bar_d2, d2_phase & 1u, c.status, &failed_s);
                     tcgen05_fence_after();
-                    tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 32), acc);
+                    tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 256), acc);
+#pragma unroll
+                    for (int p = 1; p < 4; ++p) {
+                        float more[8];
+                        tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 256 + 16 * p), more);
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) acc[k] += more[k];
+                    }
                 }
+                RMARK(28);
                 if (hc < d) {
 #pragma unroll
                     for (int k = 0; k < kMaxK; ++k)
@@ -865,7 +907,8 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 for (int p = 0; p < C; ++p) peer(cl, inbox_delta, p)[k * d + x] = change;
                 if (ok) {   // also before a reset: the position's max |h| and a padded slot's h_sel read it
                     const int cell = cell_of[k];
-                    peer(cl, h_s, cell / Nc)[(cell % Nc) * d + x] = value;
+                    const int co = owner_of(cell);
+                    peer(cl, h_s, co)[(cell - co * Nc) * d + x] = value;
                 }
             }
             consumer_sync();
@@ -874,7 +917,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 for (int o = tid; o < Ks * (M + d); o += kConsumers) {
                     const int kl = o / (M + d), w = o - kl * (M + d), k = kl * C + r;
                     if (k >= K || cell_of[k] < 0) continue;
-                    const int cell = cell_of[k], owner = cell / Nc, cc = cell % Nc;
+                    const int cell = cell_of[k], owner = owner_of(cell), cc = cell - owner * Nc;
                     const float* hr = hb + kl * d;
                     float sum = 0.0f;
                     if (w < M) {
@@ -891,7 +934,8 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                     int top = 0;
                     for (int x = lane; x < d; x += 32) top = max(top, __float_as_int(fabsf(hnew[kl * d + x])));
                     for (int w = 16; w > 0; w >>= 1) top = max(top, __shfl_xor_sync(0xffffffffu, top, w));
-                    if (lane == 0) peer(cl, cmax_s, cell_of[k] / Nc)[cell_of[k] % Nc] = top;
+                    const int co = owner_of(cell_of[k]);
+                    if (lane == 0) peer(cl, cmax_s, co)[cell_of[k] - co * Nc] = top;
                 }
             }
         }
@@ -977,7 +1021,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
     }
     tcgen05_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(taddr, 64);
+    if (warp == 0) tmem_dealloc(taddr, 512);
 }
 
 }  // namespace

@@ -72,7 +72,7 @@ __host__ __device__ inline RowsBwdSmem rows_bwd_smem(const HsnwModel& m, int C, 
         o += up16b(bytes);
         return at;
     };
-    L.ring = take(static_cast<size_t>(kStagesB) * slot_bytes);
+    L.ring = take(static_cast<size_t>(kStagesB) * slot_bytes + 1024);   // + room to start on a 1024-byte boundary
     L.A = take(4 * Nc * d);
     L.wout = take(2 * d * d);
     L.vt = take(2 * d * d);
@@ -121,9 +121,10 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
     const int gcols = two / C;          // the gate's state outputs of this block
     const int cell0 = r * Nc;
     const int U = K + K * D;
+    const uint32_t nc_magic = 0xffffffffu / static_cast<uint32_t>(Nc) + 1u;   // n / Nc as a multiply-high
 
     const RowsBwdSmem L = rows_bwd_smem(c.m, C, c.bank_bytes);
-    unsigned char* ring = dyn + L.ring;
+    unsigned char* ring = dyn + L.ring + ((1024u - (smem_addr(dyn + L.ring) & 1023u)) & 1023u);
     float* A_s = reinterpret_cast<float*>(dyn + L.A);
     uint16_t* wout = reinterpret_cast<uint16_t*>(dyn + L.wout);
     uint16_t* vt = reinterpret_cast<uint16_t*>(dyn + L.vt);
@@ -274,7 +275,7 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
     }
     for (int e = tid; e < 16 * d; e += kConsumers) du_op[e] = 0;
     for (int e = tid; e < 2 * 8 * 16 * 8; e += kConsumers) b2[e] = 0;
-    if (warp == 0) tmem_alloc(&tmem_slot, 64);
+    if (warp == 0) tmem_alloc(&tmem_slot, 256);
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
@@ -338,7 +339,8 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
             const int n = dc_[k];
             float dcv = 0.0f, dbv = 0.0f, dz = 0.0f, dgv = 0.0f, yv = 0.0f, sgv = 0.0f;
             if (n >= 0) {
-                float* a = peer(cl, A_s, n / Nc) + (n % Nc) * d + x;
+                const int no = static_cast<int>(__umulhi(static_cast<uint32_t>(n), nc_magic));
+                float* a = peer(cl, A_s, no) + (n - no * Nc) * d + x;
                 const float carried = *a + rc[(6 * Ks + kl) * d + x];
                 const float share = Rs[x] / n_f;
                 const float g = carried + share;
@@ -431,8 +433,12 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
         if (tid == 0 && n_chunks > 0) {
             const uint32_t slot = g0 % kStagesB;
             ring_wait(&full[slot], (g0 / kStagesB) & 1u, nullptr, &failed_s);
-            umma_chain(taddr, umma_desc(ring + slot * c.bank_bytes, 64), umma_desc(du_op, 16), idesc, d >> 4, umma_kstep(64),
-                       umma_kstep(16));
+            if (d == 64)
+                umma_chain_sw128<4, 4>(taddr, 16, umma_desc_sw128(ring + slot * c.bank_bytes), 0, umma_desc(du_op, 16),
+                                       umma_kstep(16), idesc, false);
+            else
+                umma_chain_fixed<d / 16, d / 16>(taddr, 16, umma_desc(ring + slot * c.bank_bytes, 64), umma_desc(du_op, 16), idesc,
+                                                 umma_kstep(64), umma_kstep(16), false);
             umma_commit(&bar_d1[0]);
         }
         for (int i = 0; i < n_chunks; ++i) {
@@ -442,8 +448,12 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
             if (tid == 0 && i + 1 < n_chunks) {
                 const uint32_t nslot = (g0 + i + 1) % kStagesB;
                 ring_wait(&full[nslot], ((g0 + i + 1) / kStagesB) & 1u, nullptr, &failed_s);
-                umma_chain(taddr + 16 * ((i + 1) & 1), umma_desc(ring + nslot * c.bank_bytes, 64), umma_desc(du_op, 16), idesc,
-                           d >> 4, umma_kstep(64), umma_kstep(16));
+                if (d == 64)
+                    umma_chain_sw128<4, 4>(taddr + 64 * ((i + 1) & 1), 16, umma_desc_sw128(ring + nslot * c.bank_bytes), 0,
+                                           umma_desc(du_op, 16), umma_kstep(16), idesc, false);
+                else
+                    umma_chain_fixed<d / 16, d / 16>(taddr + 64 * ((i + 1) & 1), 16, umma_desc(ring + nslot * c.bank_bytes, 64),
+                                                     umma_desc(du_op, 16), idesc, umma_kstep(64), umma_kstep(16), false);
                 umma_commit(&bar_d1[(i + 1) & 1]);
             }
             if (epi) {
@@ -453,7 +463,14 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
                 ring_wait(&bar_d1[i & 1], ((i & 1) ? d1_count1 : d1_count0) & 1u, nullptr, &failed_s);
                 tcgen05_fence_after();
                 float acc[8];
-                tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 16 * (i & 1)), acc);
+                tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 64 * (i & 1)), acc);
+#pragma unroll
+                for (int p = 1; p < d / 16; ++p) {   // the partial accumulators (one per K = 16 step)
+                    float more[8];
+                    tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 64 * (i & 1) + 16 * p), more);
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) acc[q] += more[q];
+                }
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const int k = 4 * sh + q;
@@ -473,8 +490,12 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
             __syncthreads();
             if (tid == 0) {
                 tcgen05_fence_after();
-                umma_chain(taddr + 32, umma_desc(ring + slot * c.bank_bytes + c.w2_bytes, two),
-                           umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), idesc, 64 >> 4, umma_kstep(two), umma_kstep(16), i > 0);
+                if (d == 64)
+                    umma_chain_sw128<4, 4>(taddr + 128, 16, umma_desc_sw128(ring + slot * c.bank_bytes + c.w2_bytes), 0,
+                                           umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), umma_kstep(16), idesc, i > 0);
+                else
+                    umma_chain_fixed<4, 4>(taddr + 128, 16, umma_desc(ring + slot * c.bank_bytes + c.w2_bytes, two),
+                                           umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), idesc, umma_kstep(two), umma_kstep(16), i > 0);
                 umma_commit(&empty[slot]);
                 if (i + 1 == n_chunks) umma_commit(&bar_d2);
                 ++g_use;
@@ -500,7 +521,14 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
             if (n_chunks > 0) {
                 ring_wait(&bar_d2, d2_phase & 1u, nullptr, &failed_s);
                 tcgen05_fence_after();
-                tmem_ld8(tmem_addr(taddr, 32 * warp, 32), acc);
+                tmem_ld8(tmem_addr(taddr, 32 * warp, 128), acc);
+#pragma unroll
+                for (int p = 1; p < 4; ++p) {
+                    float more[8];
+                    tmem_ld8(tmem_addr(taddr, 32 * warp, 128 + 16 * p), more);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) acc[k] += more[k];
+                }
             }
             const int i = 32 * warp + lane;
             if (i < two) {
@@ -581,7 +609,7 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
     }
     tcgen05_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(taddr, 64);
+    if (warp == 0) tmem_dealloc(taddr, 256);
 }
 
 }  // namespace
