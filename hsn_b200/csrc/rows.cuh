@@ -61,14 +61,14 @@ __device__ __forceinline__ void ring_wait(uint64_t* bar, uint32_t parity, int* s
 }
 
 // floats [0, n) from global to shared memory by the 256 compute threads, asynchronously.
-__device__ __forceinline__ void prefetch_floats(float* dst, const float* src, int n, int tid) {
+__device__ __forceinline__ void prefetch_floats(float* dst, const float* src, int n, int tid, int threads = kConsumers) {
     const bool vec = ((reinterpret_cast<uintptr_t>(src) | static_cast<uintptr_t>(smem_addr(dst))) & 15) == 0;
     if (vec) {
         const int n4 = n >> 2;
-        for (int e = tid; e < n4; e += kConsumers) cp_async16(dst + 4 * e, src + 4 * e);
-        for (int e = (n4 << 2) + tid; e < n; e += kConsumers) cp_async4(dst + e, src + e);
+        for (int e = tid; e < n4; e += threads) cp_async16(dst + 4 * e, src + 4 * e);
+        for (int e = (n4 << 2) + tid; e < n; e += threads) cp_async4(dst + e, src + e);
     } else {
-        for (int e = tid; e < n; e += kConsumers) cp_async4(dst + e, src + e);
+        for (int e = tid; e < n; e += threads) cp_async4(dst + e, src + e);
     }
 }
 

@@ -516,6 +516,16 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
             if (lane == 0) stale_w[warp] = n_old;
             consumer_sync();
         }
+        if (!producer && warp != 0) {
+            // the next position's inputs, asynchronously, by the warps that wait for the decision
+            if (!last) {
+                prefetch_floats(in_scal, c.io.scalars + ((rt + 1) * N + cell0) * Sn, Nc * Sn, tid - 32, kConsumers - 32);
+                if (pre_cols > 0)
+                    prefetch_floats(in_pre, c.pre_s + (rt + 1) * H + r * kFrontCols, pre_cols, tid - 32, kConsumers - 32);
+                prefetch_floats(in_z, c.io.z + (rt + 1) * d, d, tid - 32, kConsumers - 32);
+            }
+            cp_async_commit();
+        }
         RMARK(16);
         if (warp == 0) {
             if (!c.io.forced) {
@@ -627,13 +637,6 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
             }
             __syncwarp();
         } else {
-            // the next position's inputs, asynchronously
-            if (!last) {
-                prefetch_floats(in_scal, c.io.scalars + ((rt + 1) * N + cell0) * Sn, Nc * Sn, tid);
-                if (pre_cols > 0) prefetch_floats(in_pre, c.pre_s + (rt + 1) * H + r * kFrontCols, pre_cols, tid);
-                prefetch_floats(in_z, c.io.z + (rt + 1) * d, d, tid);
-            }
-            cp_async_commit();
             RMARK(24);
             for (int e = tid; e < K * d; e += kConsumers) {
                 const int k = e / d, x = e - k * d;
@@ -692,31 +695,8 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 for (int k = tid; k < K; k += kConsumers)
                     if (k % C == r) c.io.rec_rms[rt * K + k] = rms[k];
             }
+            fence_async_smem();   // the operand written above, before the tensor cores read it
             consumer_sync();
-            // the gate's partial sum over the block's input rows
-            {
-                const int x = tid % d, grp = tid / d, ngrp = kConsumers / d;
-                for (int k = grp; k < K; k += ngrp) {
-                    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
-                    if (cell_of[k] >= 0) {
-                        // the slot's inputs r grows .. of the operand: 8 consecutive inputs are one 16-byte unit
-                        for (int xi = 0; xi < grows; xi += 8) {
-                            const int jx = r * grows + xi;
-                            const uint4 vv = *reinterpret_cast<const uint4*>(vop + ((jx >> 3) * 16 + k) * 8);
-                            const uint16_t* g = gate + xi * d + x;
-                            s0 += bf16_lo(vv.x) * bf16_value(g[0]);
-                            s1 += bf16_hi(vv.x) * bf16_value(g[d]);
-                            s2 += bf16_lo(vv.y) * bf16_value(g[2 * d]);
-                            s3 += bf16_hi(vv.y) * bf16_value(g[3 * d]);
-                            s0 += bf16_lo(vv.z) * bf16_value(g[4 * d]);
-                            s1 += bf16_hi(vv.z) * bf16_value(g[5 * d]);
-                            s2 += bf16_lo(vv.w) * bf16_value(g[6 * d]);
-                            s3 += bf16_hi(vv.w) * bf16_value(g[7 * d]);
-                        }
-                    }
-                    gacc[k * d + x] = (s0 + s1) + (s2 + s3);
-                }
-            }
             RMARK(7);
             // the units' two layers on the streamed chunks, on the tensor cores. Per chunk (unit j, 64
             // hidden columns): D1 [64 columns, 16 slots] = W1 part x inputs^T; the epilogue adds the
@@ -725,9 +705,8 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
             // += W2 part x activations^T accumulates over all the position's chunks in tensor memory.
             // The chunk's rows are 64, the instruction's M is 128: rows 64..127 of both accumulators
             // come from the bytes after the tile and are never read. The second product's commit
-            // hands the ring slot back. Thread 0 issues; warps 0, 1, 4, 5 read the accumulators.
-            fence_async_smem();   // the operand written above, before the tensor cores read it
-            consumer_sync();
+            // hands the ring slot back. Thread 0 issues; warps 0, 1, 4, 5 read the accumulators and keep
+            // their own barrier; warps 2, 3, 6, 7 meanwhile compute the gate's partial sums.
             RMARK(30);
             const int n_chunks = 2 * n_units;
             const bool epi = (warp & 2) == 0;                 // warps 0, 1, 4, 5
@@ -751,71 +730,98 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 umma_commit(&bar_d1[0]);
                 RMARK(29);
             }
-            for (int i = 0; i < n_chunks; ++i) {
-                const unsigned mask = static_cast<unsigned>(umask[i >> 1]);
-                const uint32_t slot = (g0 + i) % kStages;
-                if (tid == 0 && i + 1 < n_chunks) {   // the next chunk's first product runs under this epilogue
-                    const uint32_t nslot = (g0 + i + 1) % kStages;
-                    ring_wait(&full[nslot], ((g0 + i + 1) / kStages) & 1u, c.status, &failed_s);
-                    tcgen05_fence_after();
-                    if (d == 64)
-                        umma_chain_sw128<steps1, n1>(taddr + 128 * ((i + 1) & 1), 16, umma_desc_sw128(ring + nslot * c.slot_bytes),
-                                                     (64 * 128) >> 4, umma_desc(vop, 16), umma_kstep(16), idesc, false);
-                    else
-                        umma_chain_fixed<steps1, n1>(taddr + 128 * ((i + 1) & 1), 16, umma_desc(ring + nslot * c.slot_bytes, 64),
-                                                     umma_desc(vop, 16), idesc, umma_kstep(64), umma_kstep(16), false);
-                    umma_commit(&bar_d1[(i + 1) & 1]);
-                }
-                if (epi) {
-                    const int colg = r * 128 + (i & 1) * 64 + hc;
-                    const float bias = bias_next;
-                    if (i + 1 < n_chunks) bias_next = c.m.b1[ulist[(i + 1) >> 1] * H + r * 128 + ((i + 1) & 1) * 64 + hc];
-                    uint16_t* b2i = b2 + (i & 1) * (8 * 16 * 8);
-                    ring_wait(&bar_d1[i & 1], ((i & 1) ? d1_count1 : d1_count0) & 1u, c.status, &failed_s);
-                    tcgen05_fence_after();
-                    if (i == 0) RMARK(25);
-                    float acc[8];
-                    tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 128 * (i & 1)), acc);
-#pragma unroll
-                    for (int p = 1; p < n1; ++p) {   // the partial accumulators
-                        float more[8];
-                        tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 128 * (i & 1) + 16 * p), more);
-#pragma unroll
-                        for (int q = 0; q < 8; ++q) acc[q] += more[q];
+            if (epi) {
+                for (int i = 0; i < n_chunks; ++i) {
+                    const unsigned mask = static_cast<unsigned>(umask[i >> 1]);
+                    const uint32_t slot = (g0 + i) % kStages;
+                    if (tid == 0 && i + 1 < n_chunks) {   // the next chunk's first product runs under this epilogue
+                        const uint32_t nslot = (g0 + i + 1) % kStages;
+                        ring_wait(&full[nslot], ((g0 + i + 1) / kStages) & 1u, c.status, &failed_s);
+                        tcgen05_fence_after();
+                        if (d == 64)
+                            umma_chain_sw128<steps1, n1>(taddr + 128 * ((i + 1) & 1), 16, umma_desc_sw128(ring + nslot * c.slot_bytes),
+                                                         (64 * 128) >> 4, umma_desc(vop, 16), umma_kstep(16), idesc, false);
+                        else
+                            umma_chain_fixed<steps1, n1>(taddr + 128 * ((i + 1) & 1), 16, umma_desc(ring + nslot * c.slot_bytes, 64),
+                                                         umma_desc(vop, 16), idesc, umma_kstep(64), umma_kstep(16), false);
+                        umma_commit(&bar_d1[(i + 1) & 1]);
                     }
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int k = 4 * sh + q;
-                        float a = 0.0f;
-                        if (mask & (1u << k)) {
-                            const float hid = bf16r((sh ? acc[4 + q] : acc[q]) + bias);
-                            if (rec) c.io.rec_hidden[(rt * K + k) * H + colg] = hid;
-                            a = gelu_erf(hid);
+                    if (epi) {
+                        const int colg = r * 128 + (i & 1) * 64 + hc;
+                        const float bias = bias_next;
+                        if (i + 1 < n_chunks) bias_next = c.m.b1[ulist[(i + 1) >> 1] * H + r * 128 + ((i + 1) & 1) * 64 + hc];
+                        uint16_t* b2i = b2 + (i & 1) * (8 * 16 * 8);
+                        ring_wait(&bar_d1[i & 1], ((i & 1) ? d1_count1 : d1_count0) & 1u, c.status, &failed_s);
+                        tcgen05_fence_after();
+                        if (i == 0) RMARK(25);
+                        float acc[8];
+                        tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 128 * (i & 1)), acc);
+    #pragma unroll
+                        for (int p = 1; p < n1; ++p) {   // the partial accumulators
+                            float more[8];
+                            tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 128 * (i & 1) + 16 * p), more);
+    #pragma unroll
+                            for (int q = 0; q < 8; ++q) acc[q] += more[q];
                         }
-                        b2i[((hc >> 3) * 16 + k) * 8 + (hc & 7)] = bf16_bits(a);
+    #pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int k = 4 * sh + q;
+                            float a = 0.0f;
+                            if (mask & (1u << k)) {
+                                const float hid = bf16r((sh ? acc[4 + q] : acc[q]) + bias);
+                                if (rec) c.io.rec_hidden[(rt * K + k) * H + colg] = hid;
+                                a = gelu_erf(hid);
+                            }
+                            b2i[((hc >> 3) * 16 + k) * 8 + (hc & 7)] = bf16_bits(a);
+                        }
+                        fence_async_smem();
+                        tcgen05_fence_before();
+                        if (i == 0) RMARK(26);
                     }
-                    fence_async_smem();
-                    tcgen05_fence_before();
-                    if (i == 0) RMARK(26);
+                    if (i & 1) ++d1_count1;
+                    else ++d1_count0;
+                    asm volatile("bar.sync 2, 128;\n" ::: "memory");   // the four epilogue warps
+                    if (tid == 0) {
+                        tcgen05_fence_after();
+                        // four partial sums of D2, each over the position's chunks
+                        if (d == 64)
+                            umma_chain_sw128<4, 4>(taddr + 256, 16, umma_desc_sw128(ring + slot * c.slot_bytes + c.w1_bytes), 0,
+                                                   umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), umma_kstep(16), idesc, i > 0);
+                        else
+                            umma_chain_fixed<4, 4>(taddr + 256, 16, umma_desc(ring + slot * c.slot_bytes + c.w1_bytes, d),
+                                                   umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), idesc, umma_kstep(d), umma_kstep(16),
+                                                   i > 0);
+                        umma_commit(&empty[slot]);
+                        if (i + 1 == n_chunks) umma_commit(&bar_d2);
+                    }
+                    if (i == 0) RMARK(27);
                 }
-                if (i & 1) ++d1_count1;
-                else ++d1_count0;
-                consumer_sync();
-                if (tid == 0) {
-                    tcgen05_fence_after();
-                    // four partial sums of D2, each over the position's chunks
-                    if (d == 64)
-                        umma_chain_sw128<4, 4>(taddr + 256, 16, umma_desc_sw128(ring + slot * c.slot_bytes + c.w1_bytes), 0,
-                                               umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), umma_kstep(16), idesc, i > 0);
-                    else
-                        umma_chain_fixed<4, 4>(taddr + 256, 16, umma_desc(ring + slot * c.slot_bytes + c.w1_bytes, d),
-                                               umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), idesc, umma_kstep(d), umma_kstep(16),
-                                               i > 0);
-                    umma_commit(&empty[slot]);
-                    if (i + 1 == n_chunks) umma_commit(&bar_d2);
+            } else {
+                // the gate's partial sum over the block's input rows, by the other four warps
+                const int t2 = (warp >> 2) * 64 + (warp & 1) * 32 + lane;   // 0 .. 127
+                const int x = t2 % d, grp = t2 / d, ngrp = 128 / d;
+                for (int k = grp; k < K; k += ngrp) {
+                    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+                    if (cell_of[k] >= 0) {
+                        // the slot's inputs r grows .. of the operand: 8 consecutive inputs are one 16-byte unit
+                        for (int xi = 0; xi < grows; xi += 8) {
+                            const int jx = r * grows + xi;
+                            const uint4 vv = *reinterpret_cast<const uint4*>(vop + ((jx >> 3) * 16 + k) * 8);
+                            const uint16_t* g = gate + xi * d + x;
+                            s0 += bf16_lo(vv.x) * bf16_value(g[0]);
+                            s1 += bf16_hi(vv.x) * bf16_value(g[d]);
+                            s2 += bf16_lo(vv.y) * bf16_value(g[2 * d]);
+                            s3 += bf16_hi(vv.y) * bf16_value(g[3 * d]);
+                            s0 += bf16_lo(vv.z) * bf16_value(g[4 * d]);
+                            s1 += bf16_hi(vv.z) * bf16_value(g[5 * d]);
+                            s2 += bf16_lo(vv.w) * bf16_value(g[6 * d]);
+                            s3 += bf16_hi(vv.w) * bf16_value(g[7 * d]);
+                        }
+                    }
+                    gacc[k * d + x] = (s0 + s1) + (s2 + s3);
                 }
-                if (i == 0) RMARK(27);
             }
+            consumer_sync();
             g_use += n_chunks;
             RMARK(8);
             // the block's partial of every slot's second layer from the accumulator, and the gate's
@@ -913,21 +919,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
             }
             consumer_sync();
             {
-                // the written cells' derived state, at their owners
-                for (int o = tid; o < Ks * (M + d); o += kConsumers) {
-                    const int kl = o / (M + d), w = o - kl * (M + d), k = kl * C + r;
-                    if (k >= K || cell_of[k] < 0) continue;
-                    const int cell = cell_of[k], owner = owner_of(cell), cc = cell - owner * Nc;
-                    const float* hr = hb + kl * d;
-                    float sum = 0.0f;
-                    if (w < M) {
-                        sum = dot4(hr, 1, swh + w, M, d);
-                        peer(cl, lh_s, owner)[cc * M + w] = sum;
-                    } else {
-                        sum = dot_bf16w(hr, 1, vt + (w - M), d, d);
-                        peer(cl, vh_s, owner)[cc * d + (w - M)] = bf16_bits(sum);
-                    }
-                }
+                // the written cells' maxima, at their owners (their logit parts and V h follow in phase F)
                 for (int kl = warp; kl < Ks; kl += kConsumers / 32) {
                     const int k = kl * C + r;
                     if (k >= K || cell_of[k] < 0) continue;
@@ -945,6 +937,18 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
         // ---------------- F: summary, ages, the tape's next record, the next reset
         if (!producer) {
             if (tid == 0) hmax_local = 0;
+            if (tid >= 128 && !clear) {
+                // the written cells' logit parts and V h, at their owners, by the four warps that have
+                // nothing else to do here; the next position reads them after its cluster barriers
+                for (int o = tid - 128; o < Ks * (M + d); o += 128) {
+                    const int kl = o / (M + d), w = o - kl * (M + d), k = kl * C + r;
+                    if (k >= K || cell_of[k] < 0) continue;
+                    const int cell = cell_of[k], owner = owner_of(cell), cc = cell - owner * Nc;
+                    const float* hr = hb + kl * d;
+                    if (w < M) peer(cl, lh_s, owner)[cc * M + w] = dot4(hr, 1, swh + w, M, d);
+                    else peer(cl, vh_s, owner)[cc * d + (w - M)] = bf16_bits(dot_bf16w(hr, 1, vt + (w - M), d, d));
+                }
+            }
             for (int x = tid; x < d; x += kConsumers) {
                 float sum = 0.0f;
                 for (int k = 0; k < K; ++k) sum += inbox_delta[k * d + x];   // slot order

@@ -406,14 +406,6 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
             if (lane == 0) issue_ahead();
             __syncwarp();
         }
-        {
-            // the gate's transposed linear, this block's state outputs
-            const int k = tid / gcols, il = tid - k * gcols;
-            if (k < K) {
-                const float sum = dc_[k] >= 0 ? dot_bf16w(dg_all + k * d, 1, gate + il * d, 1, d) : 0.0f;
-                peer(cl, inbox_g, k % C)[(k / C) * two + r * gcols + il] = sum;
-            }
-        }
         BMARK(3);
         // the transposed layers on the streamed chunks, on the tensor cores. Per chunk (unit j, 64
         // hidden columns): D1 [64 columns, 16 slots] = W2 part x d_unit^T; the epilogue multiplies by
@@ -441,68 +433,79 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
                                                  umma_kstep(64), umma_kstep(16), false);
             umma_commit(&bar_d1[0]);
         }
-        for (int i = 0; i < n_chunks; ++i) {
-            const int j = dc_[o_ulist + (i >> 1)];
-            const unsigned mask = static_cast<unsigned>(dc_[o_umask + (i >> 1)]);
-            const uint32_t slot = (g0 + i) % kStagesB;
-            if (tid == 0 && i + 1 < n_chunks) {
-                const uint32_t nslot = (g0 + i + 1) % kStagesB;
-                ring_wait(&full[nslot], ((g0 + i + 1) / kStagesB) & 1u, nullptr, &failed_s);
-                if (d == 64)
-                    umma_chain_sw128<4, 4>(taddr + 64 * ((i + 1) & 1), 16, umma_desc_sw128(ring + nslot * c.bank_bytes), 0,
-                                           umma_desc(du_op, 16), umma_kstep(16), idesc, false);
-                else
-                    umma_chain_fixed<d / 16, d / 16>(taddr + 64 * ((i + 1) & 1), 16, umma_desc(ring + nslot * c.bank_bytes, 64),
-                                                     umma_desc(du_op, 16), idesc, umma_kstep(64), umma_kstep(16), false);
-                umma_commit(&bar_d1[(i + 1) & 1]);
-            }
-            if (epi) {
-                const int hid_col = (i & 1) * 64 + hc;
-                const float bias = b1s[j * 128 + hid_col];
-                uint16_t* b2i = b2 + (i & 1) * (8 * 16 * 8);
-                ring_wait(&bar_d1[i & 1], ((i & 1) ? d1_count1 : d1_count0) & 1u, nullptr, &failed_s);
-                tcgen05_fence_after();
-                float acc[8];
-                tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 64 * (i & 1)), acc);
-#pragma unroll
-                for (int p = 1; p < d / 16; ++p) {   // the partial accumulators (one per K = 16 step)
-                    float more[8];
-                    tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 64 * (i & 1) + 16 * p), more);
-#pragma unroll
-                    for (int q = 0; q < 8; ++q) acc[q] += more[q];
+        if (epi) {
+            for (int i = 0; i < n_chunks; ++i) {
+                const int j = dc_[o_ulist + (i >> 1)];
+                const unsigned mask = static_cast<unsigned>(dc_[o_umask + (i >> 1)]);
+                const uint32_t slot = (g0 + i) % kStagesB;
+                if (tid == 0 && i + 1 < n_chunks) {
+                    const uint32_t nslot = (g0 + i + 1) % kStagesB;
+                    ring_wait(&full[nslot], ((g0 + i + 1) / kStagesB) & 1u, nullptr, &failed_s);
+                    if (d == 64)
+                        umma_chain_sw128<4, 4>(taddr + 64 * ((i + 1) & 1), 16, umma_desc_sw128(ring + nslot * c.bank_bytes), 0,
+                                               umma_desc(du_op, 16), umma_kstep(16), idesc, false);
+                    else
+                        umma_chain_fixed<d / 16, d / 16>(taddr + 64 * ((i + 1) & 1), 16, umma_desc(ring + nslot * c.bank_bytes, 64),
+                                                         umma_desc(du_op, 16), idesc, umma_kstep(64), umma_kstep(16), false);
+                    umma_commit(&bar_d1[(i + 1) & 1]);
                 }
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int k = 4 * sh + q;
-                    float dh = 0.0f;
-                    if (mask & (1u << k)) {
-                        const float hv = hd[k * 128 + hid_col];
-                        dh = bf16r((sh ? acc[4 + q] : acc[q]) * gelu_erf_grad(hv));
-                        inner[q] += dh * (hv - bias);
+                if (epi) {
+                    const int hid_col = (i & 1) * 64 + hc;
+                    const float bias = b1s[j * 128 + hid_col];
+                    uint16_t* b2i = b2 + (i & 1) * (8 * 16 * 8);
+                    ring_wait(&bar_d1[i & 1], ((i & 1) ? d1_count1 : d1_count0) & 1u, nullptr, &failed_s);
+                    tcgen05_fence_after();
+                    float acc[8];
+                    tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 64 * (i & 1)), acc);
+    #pragma unroll
+                    for (int p = 1; p < d / 16; ++p) {   // the partial accumulators (one per K = 16 step)
+                        float more[8];
+                        tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 64 * (i & 1) + 16 * p), more);
+    #pragma unroll
+                        for (int q = 0; q < 8; ++q) acc[q] += more[q];
                     }
-                    b2i[((hc >> 3) * 16 + k) * 8 + (hc & 7)] = bf16_bits(dh);
+    #pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int k = 4 * sh + q;
+                        float dh = 0.0f;
+                        if (mask & (1u << k)) {
+                            const float hv = hd[k * 128 + hid_col];
+                            dh = bf16r((sh ? acc[4 + q] : acc[q]) * gelu_erf_grad(hv));
+                            inner[q] += dh * (hv - bias);
+                        }
+                        b2i[((hc >> 3) * 16 + k) * 8 + (hc & 7)] = bf16_bits(dh);
+                    }
+                    fence_async_smem();
+                    tcgen05_fence_before();
                 }
-                fence_async_smem();
-                tcgen05_fence_before();
+                if (i & 1) ++d1_count1;
+                else ++d1_count0;
+                asm volatile("bar.sync 2, 128;\n" ::: "memory");   // the four epilogue warps
+                if (tid == 0) {
+                    tcgen05_fence_after();
+                    if (d == 64)
+                        umma_chain_sw128<4, 4>(taddr + 128, 16, umma_desc_sw128(ring + slot * c.bank_bytes + c.w2_bytes), 0,
+                                               umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), umma_kstep(16), idesc, i > 0);
+                    else
+                        umma_chain_fixed<4, 4>(taddr + 128, 16, umma_desc(ring + slot * c.bank_bytes + c.w2_bytes, two),
+                                               umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), idesc, umma_kstep(two), umma_kstep(16), i > 0);
+                    umma_commit(&empty[slot]);
+                    if (i + 1 == n_chunks) umma_commit(&bar_d2);
+                    ++g_use;
+                    issue_ahead();
+                }
+                __syncwarp();
             }
-            if (i & 1) ++d1_count1;
-            else ++d1_count0;
-            __syncthreads();
-            if (tid == 0) {
-                tcgen05_fence_after();
-                if (d == 64)
-                    umma_chain_sw128<4, 4>(taddr + 128, 16, umma_desc_sw128(ring + slot * c.bank_bytes + c.w2_bytes), 0,
-                                           umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), umma_kstep(16), idesc, i > 0);
-                else
-                    umma_chain_fixed<4, 4>(taddr + 128, 16, umma_desc(ring + slot * c.bank_bytes + c.w2_bytes, two),
-                                           umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), idesc, umma_kstep(two), umma_kstep(16), i > 0);
-                umma_commit(&empty[slot]);
-                if (i + 1 == n_chunks) umma_commit(&bar_d2);
-                ++g_use;
-                issue_ahead();
+        } else {
+            // the gate's transposed linear, this block's state outputs, by the other four warps
+            const int t2 = (warp >> 2) * 64 + (warp & 1) * 32 + lane;   // 0 .. 127
+            for (int e = t2; e < K * gcols; e += 128) {
+                const int k = e / gcols, il = e - k * gcols;
+                const float sum = dc_[k] >= 0 ? dot_bf16w(dg_all + k * d, 1, gate + il * d, 1, d) : 0.0f;
+                peer(cl, inbox_g, k % C)[(k / C) * two + r * gcols + il] = sum;
             }
-            __syncwarp();
         }
+        __syncthreads();
         if (tid != 0) g_use += n_chunks;
         BMARK(4);
         // the slots' inner products: the epilogue warps' sums, then the pair of warps of each half
@@ -587,7 +590,7 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
             const int x = tid % d, g = tid / d, groups = kConsumers / d;
             for (int u = 0; u < U; ++u) {
                 const int n = u < K ? dc_[u] : dc_[o_tgt + u - K];
-                if (n < cell0 || n >= cell0 + Nc || (n % groups) != g) continue;
+                if (n < cell0 || n >= cell0 + Nc || (n & (groups - 1)) != g) continue;   // groups is a power of two
                 const float add = u < K ? ds_all[u * d + x] : ew[u - K] * dvm_all[((u - K) / D) * d + x];
                 A_s[(n - cell0) * d + x] += add;
             }
