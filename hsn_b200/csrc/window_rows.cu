@@ -123,7 +123,7 @@ __host__ __device__ inline RowsSmem rows_smem(const HsnwModel& m, int C, uint32_
     L.in_scal = take(4 * Nc * S + 16);
     L.in_pre = take(4 * kFrontCols);
     L.in_z = take(4 * d);
-    L.upd = take(4 * Ks * 6 * d + 4 * Ks);  // F, gate_pre, y, hnew, hb, delta per owned slot; scale
+    L.upd = take(4 * Ks * 6 * d + 4 * Ks);  // F, gate_pre, y, -, hb per owned slot
     L.cell_of = take(4 * K);
     L.unit_of = take(4 * K);
     L.ulist = take(4 * (kMaxMR + 4));
@@ -384,6 +384,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 const float out = bf16r(sum + fb2[tid]);
                 ue[tid] = tid < d ? out : in_z[tid - d] - out;
             }
+            if (tid == 0) hmax_local = 0;   // phase A sent it; phase F of this position takes the next maximum
             if (r == 0 && tid == 0 && t > 0 && c.io.h_max) {
                 int mx = 0;
                 for (int p = 0; p < C; ++p) mx = max(mx, __float_as_int(inbox_front[p * stride_in + 2 * d]));
@@ -936,11 +937,12 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
         RMARK(12);
         // ---------------- F: summary, ages, the tape's next record, the next reset
         if (!producer) {
-            if (tid == 0) hmax_local = 0;
-            if (tid >= 128 && !clear) {
-                // the written cells' logit parts and V h, at their owners, by the four warps that have
+            // no barrier in this phase unless the next position resets: every part reads what the
+            // cluster barrier above published and writes its own data
+            if (tid >= 96 && !clear) {
+                // the written cells' logit parts and V h, at their owners, by the five warps that have
                 // nothing else to do here; the next position reads them after its cluster barriers
-                for (int o = tid - 128; o < Ks * (M + d); o += 128) {
+                for (int o = tid - 96; o < Ks * (M + d); o += 160) {
                     const int kl = o / (M + d), w = o - kl * (M + d), k = kl * C + r;
                     if (k >= K || cell_of[k] < 0) continue;
                     const int cell = cell_of[k], owner = owner_of(cell), cc = cell - owner * Nc;
@@ -966,12 +968,11 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                     if (cell_of[k] < 0) c.io.h_sel[(rt * K + k) * d + x] = h_s[x];
                 }
             }
-            consumer_sync();
             {
                 int top = 0;
                 for (int n = tid; n < Nc; n += kConsumers) top = max(top, cmax_s[n]);
                 for (int w = 16; w > 0; w >>= 1) top = max(top, __shfl_xor_sync(0xffffffffu, top, w));
-                if (lane == 0) atomicMax(&hmax_local, top);   // a maximum: any order gives the same bits
+                if (lane == 0 && top > 0) atomicMax(&hmax_local, top);   // a maximum: any order gives the same bits
             }
             for (int n = tid; n < Nc; n += kConsumers) {
                 int64_t a = age_s[n] + 1;
@@ -981,8 +982,8 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 age_s[n] = a;
                 if (tape) c.io.tape_age[(static_cast<int64_t>(row) * (T + 1) + t + 1) * N + cell0 + n] = a;
             }
-            consumer_sync();
             if (clear) {
+                consumer_sync();   // the reads of the state above are over
                 for (int e = tid; e < Nc * d; e += kConsumers) {
                     h_s[e] = 0.0f;
                     vh_s[e] = 0;

@@ -87,7 +87,7 @@ __host__ __device__ inline RowsBwdSmem rows_bwd_smem(const HsnwModel& m, int C, 
         L.rec[s] = take(4 * (7 * Ks * d + Ks) + 16);
         L.hid[s] = take(4 * K * 128);
         L.dq[s] = take(4 * 2 * d);
-        L.dec[s] = take(4 * (2 * K + 2 * K * D + 2 * kMaxMB + 4));
+        L.dec[s] = take(4 * (2 * K + 2 * K * D + 2 * kMaxMB + 4 + K + K * D));
     }
     L.du_all = take(2 * 16 * d);        // d_unit of every slot as a bf16 operand [d/8][16][8]
     L.b2 = take(2 * 2 * 8 * 16 * 8);    // two bf16 operands [8][16][8]: dhid of a chunk's 64 columns
@@ -163,7 +163,7 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
     // a position's decision block: cell_of [K], unit_of [K], tgt [K D], ew [K D] (floats), ulist [16],
     // umask [16], n_units
     const int o_unit = K, o_tgt = 2 * K, o_ew = 2 * K + K * D, o_ulist = 2 * K + 2 * K * D, o_umask = o_ulist + kMaxMB,
-              o_n = o_umask + kMaxMB;
+              o_n = o_umask + kMaxMB, o_own_n = o_n + 1, o_own = o_n + 2;   // own: the updates u whose target is a cell of this block
 
     // the records of position t, asynchronously, into buffer t & 1
     auto prefetch = [&](int t) {
@@ -240,6 +240,17 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
             }
         }
         if (lane == 0) dc_[o_n] = n;
+        // the updates that land on this block's cells, in update order (slots, then edges)
+        int count = 0;
+        for (int u0 = 0; u0 < U; u0 += 32) {
+            const int u = u0 + lane;
+            const int tgt = u < U ? (u < K ? dc_[u] : dc_[o_tgt + u - K]) : -1;
+            const bool mine = tgt >= cell0 && tgt < cell0 + Nc;
+            const unsigned mask = __ballot_sync(0xffffffffu, mine);
+            if (mine) dc_[o_own + count + __popc(mask & ((1u << lane) - 1u))] = u;
+            count += __popc(mask);
+        }
+        if (lane == 0) dc_[o_own_n] = count;
         __syncwarp();
     };
 
@@ -362,7 +373,10 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
             for (int p = 0; p < C; ++p) peer(cl, dg_all, p)[k * d + x] = dgb;
         }
         __syncthreads();
+        // per owned slot, one warp without block barriers: rho, the mean, the gate's inner product,
+        // dy = rho (cand_w dz) - rho^3 y mean(y cand_w dz), then d_unit = dy W_out to every block
         for (int kl = warp; kl < Ks; kl += kConsumers / 32) {
+            const int k = kl * C + r;
             float sq = 0.0f, dt = 0.0f, s = 0.0f;
             for (int x = lane; x < d; x += 32) {
                 const float yv = ysv[kl * d + x];
@@ -373,24 +387,19 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
             sq = warp_sum(sq);
             dt = warp_sum(dt);
             s = warp_sum(s);
-            if (lane == 0) {
-                rho[kl] = rsqrtf(sq / static_cast<float>(d) + c.m.cand_eps);
-                dot[kl] = dt / static_cast<float>(d);
-                sig_gate[kl] = s;
+            const float rr = rsqrtf(sq / static_cast<float>(d) + c.m.cand_eps);
+            const float mean = dt / static_cast<float>(d);
+            if (lane == 0) sig_gate[kl] = s;
+            const bool ok = k < K && dc_[k] >= 0;
+            for (int x = lane; x < d; x += 32)
+                dy[kl * d + x] = ok ? rr * dzs[kl * d + x] - rr * rr * rr * ysv[kl * d + x] * mean : 0.0f;
+            __syncwarp();
+            if (k < K) {
+                for (int i = lane; i < d; i += 32) {
+                    const uint16_t dub = bf16_bits(dot_bf16w(dy + kl * d, 1, wout + i * d, 1, d));
+                    for (int p = 0; p < C; ++p) peer(cl, du_op, p)[((i >> 3) * 16 + k) * 8 + (i & 7)] = dub;
+                }
             }
-        }
-        __syncthreads();
-        for (int e = tid; e < Ks * d; e += kConsumers) {
-            const int kl = e / d, k = kl * C + r;
-            const float rr = rho[kl];
-            dy[e] = (k < K && dc_[k] >= 0) ? rr * dzs[e] - rr * rr * rr * ysv[e] * dot[kl] : 0.0f;
-        }
-        __syncthreads();
-        for (int e = tid; e < Ks * d; e += kConsumers) {
-            const int kl = e / d, i = e - kl * d, k = kl * C + r;
-            if (k >= K) continue;
-            const uint16_t dub = bf16_bits(dot_bf16w(dy + kl * d, 1, wout + i * d, 1, d));
-            for (int p = 0; p < C; ++p) peer(cl, du_op, p)[((i >> 3) * 16 + k) * 8 + (i & 7)] = dub;
         }
         BMARK(1);
         cl.sync();   // 1
@@ -588,9 +597,11 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
         // ---------------- T2: this block's cells; thread (x, g) takes the targets n = g (mod groups)
         {
             const int x = tid % d, g = tid / d, groups = kConsumers / d;
-            for (int u = 0; u < U; ++u) {
+            const int n_own = dc_[o_own_n];
+            for (int e = 0; e < n_own; ++e) {
+                const int u = dc_[o_own + e];
                 const int n = u < K ? dc_[u] : dc_[o_tgt + u - K];
-                if (n < cell0 || n >= cell0 + Nc || (n & (groups - 1)) != g) continue;   // groups is a power of two
+                if ((n & (groups - 1)) != g) continue;   // groups is a power of two
                 const float add = u < K ? ds_all[u * d + x] : ew[u - K] * dvm_all[((u - K) / D) * d + x];
                 A_s[(n - cell0) * d + x] += add;
             }
