@@ -3,11 +3,11 @@
 //
 // Why: at a few dozen rows per GPU the batch-synchronous phases (window_fwd.cu) are bound by the
 // latency of 4 launches and ~20 dependent trips to L2 per position. Rows are independent in the
-// forward sweep, so a row can run alone: its state (h, V h, the state's part of the logits, ages)
-// lives in distributed shared memory for the whole window, the phases of a position are separated
-// by 4 hardware cluster barriers instead of kernel boundaries, and the only traffic per position
-// is the unit bank streamed from L2 by the TMA (bulk copies through a 3-deep ring, issued by a
-// producer warp, consumed by 8 compute warps without block-wide barriers) and the tape's records
+// forward sweep, so a row can run alone: its state (h, V h, the state's part of the logits, ages,
+// the cell graph) lives in distributed shared memory for the whole window, the phases of a position
+// are separated by 4 hardware cluster barriers instead of kernel boundaries, and the only traffic
+// per position is the unit bank streamed from L2 by the TMA (bulk copies through a ring, issued by
+// a producer warp), the position's inputs (bulk copies, a position ahead) and the tape's records
 // written back.
 //
 // Cluster of C = H / 128 blocks; block r owns the cells [r N/C, (r+1) N/C), the hidden columns
@@ -15,23 +15,32 @@
 // the merged front first layer, the rows [r 4d/C, (r+1) 4d/C) of the gate's input, and the slots
 // k = r (mod C) at the update. Per position:
 //   A  front MLPs on the block's columns -> partial (u, z_hat) pushed to every block   | sync 1
-//   B  u, eps, the scorer on the block's cells -> (score, unit, age) pushed everywhere  | sync 2
-//   C  the decision, by one warp of every block on the gathered scores (select.cuh)
+//   B  u, eps, the scorer on the block's cells (4 threads a cell) -> (score, unit, age) pushed
+//      to every block                                                                  | sync 2
+//   C  the decision in every block on identical inputs: a cell's place in the scored order is the
+//      number of larger keys, counted by the cell's thread against all keys; the budget, the
+//      threshold and the probes by one warp
 //   D  gather of the selected rows and message sources through distributed shared memory,
-//      messages, cell norm, the gate's partial, the units' two layers on the streamed chunks,
-//      partial F and gate pushed to the slots' owners                                   | sync 3
-//   E  W_out, candidate norm, tanh, sigmoid, the gated write pushed to the cell's owner with its
-//      derived state, the slot's change of the summary pushed everywhere                | sync 4
-//   F  summary, ages, the tape's next record from the block's cells, the next reset.
+//      messages, cell norm -> the slots' inputs as a bf16 tensor-core operand; then per streamed
+//      chunk (unit, 64 columns) two tcgen05 products with accumulators in tensor memory: the first
+//      layer (its epilogue adds the bias, rounds, records, applies the activation for the slots
+//      that chose the unit), the second layer accumulating over all the position's chunks; four
+//      warps run the epilogues, the other four the gate's partial sums meanwhile; partial F and
+//      gate pushed to the slots' owners                                                | sync 3
+//   E  W_out, candidate norm, tanh, sigmoid, the gated write pushed to the cell's owner, the
+//      slot's change of the summary pushed everywhere                                  | sync 4
+//   F  summary, ages, the written cells' derived state (logit parts, V h) to their owners, the
+//      tape's next record from the block's cells, the next reset.
 //
 // The arithmetic, the rounding points (bf16 operands and outputs of every product, fp32 sums and
 // state) and every output are those of window_fwd.cu (reference: python/hsn/train/compile.py:
 // 1117-1193, python/hsn/model/hsn.py:1903-1980, python/hsn/model/cell.py:349-505); only the order
-// of fp32 partial sums differs. Fixed orders everywhere: no atomics.
+// of fp32 partial sums differs. Fixed orders everywhere: no atomics on values (one shared-memory
+// atomicMax on a maximum, which no order can change).
 //
-// Every mbarrier wait is bounded (stage.cuh) and reports through the status word; the cluster
-// barriers are hardware barriers that every thread of the cluster reaches the same number of
-// times (all control flow around them depends on values that are identical in the cluster).
+// Every mbarrier wait is bounded (rows.cuh: ring_wait) and reports through the status word; the
+// cluster barriers are hardware barriers that every thread of the cluster reaches the same number
+// of times (all control flow around them depends on values that are identical in the cluster).
 #include "../../include/hsn_window_b200.h"
 #include "common.cuh"
 #include "select.cuh"
@@ -149,7 +158,7 @@ __host__ __device__ inline RowsSmem rows_smem(const HsnwModel& m, int C, uint32_
         if (tid == 0 && row == 0 && t == T / 2) {                                             \
             unsigned long long now;                                                           \
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));                           \
-            reinterpret_cast<unsigned long long*>(c.status + 64)[r * 32 + (i)] = now;         \
+            reinterpret_cast<unsigned long long*>(c.status + 64)[r * 64 + (i)] = now;         \
         }                                                                                     \
     } while (0)
 #else
@@ -166,6 +175,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
     __shared__ int failed_s;     // a ring wait ran out
     __shared__ __align__(8) uint64_t bar_d1[2], bar_d2;   // a chunk's first product (two accumulators in turn); the position's second products
     __shared__ uint32_t tmem_slot;
+    __shared__ __align__(8) uint64_t in_bar;   // the next position's inputs (bulk copies by the producer)
     __shared__ uint64_t next_key_s;   // the (K + 1)-th best key of the position's scored order
 
     cg::cluster_group cl = cg::this_cluster();
@@ -250,6 +260,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
         mbar_init(&bar_d1[0], 1);
         mbar_init(&bar_d1[1], 1);
         mbar_init(&bar_d2, 1);
+        mbar_init(&in_bar, 1);
         hmax_local = 0;
         n_units_s = 0;
         failed_s = 0;
@@ -337,7 +348,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
         // ---------------- A: the front MLPs on the block's columns
         RMARK(0);
         if (!producer) {
-            cp_async_wait_all();
+            if (t > 0) ring_wait(&in_bar, static_cast<uint32_t>(t - 1) & 1u, c.status, &failed_s);
             if (tid < d) ue[tid] = bf16r(q_s[tid]);
             consumer_sync();
             float* act = big;                     // [256]
@@ -479,12 +490,16 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 const uint4* key4 = reinterpret_cast<const uint4*>(key32);
                 for (int i = tid; i < N; i += kConsumers) {
                     const uint32_t mine = key32[i];
-                    int rank = 0;
-#pragma unroll 8
+                    int r0 = 0, r1 = 0, r2 = 0, r3 = 0;   // four independent counts
+#pragma unroll 16
                     for (int j4 = 0; j4 < (N + 3) >> 2; ++j4) {
                         const uint4 o = key4[j4];
-                        rank += (o.x > mine) + (o.y > mine) + (o.z > mine) + (o.w > mine);
+                        r0 += o.x > mine;
+                        r1 += o.y > mine;
+                        r2 += o.z > mine;
+                        r3 += o.w > mine;
                     }
+                    const int rank = (r0 + r1) + (r2 + r3);
                     const bool old = age_all[i] > static_cast<int64_t>(c.m.age_max);
                     n_old += old ? 1 : 0;
                     if (rank < K) {
@@ -516,16 +531,6 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
             n_old = __reduce_add_sync(0xffffffffu, n_old);
             if (lane == 0) stale_w[warp] = n_old;
             consumer_sync();
-        }
-        if (!producer && warp != 0) {
-            // the next position's inputs, asynchronously, by the warps that wait for the decision
-            if (!last) {
-                prefetch_floats(in_scal, c.io.scalars + ((rt + 1) * N + cell0) * Sn, Nc * Sn, tid - 32, kConsumers - 32);
-                if (pre_cols > 0)
-                    prefetch_floats(in_pre, c.pre_s + (rt + 1) * H + r * kFrontCols, pre_cols, tid - 32, kConsumers - 32);
-                prefetch_floats(in_z, c.io.z + (rt + 1) * d, d, tid - 32, kConsumers - 32);
-            }
-            cp_async_commit();
         }
         RMARK(16);
         if (warp == 0) {
@@ -586,14 +591,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 cell_of[k] = ok ? S.out_cell[k] : -1;
                 my_unit = ok ? S.out_unit[k] : -1;
                 unit_of[k] = my_unit;
-                if (r == 0 && !c.io.forced) {
-                    c.io.cells[rt * K + k] = S.out_cell[k];
-                    c.io.units[rt * K + k] = S.out_unit[k];
-                    c.io.valid[rt * K + k] = static_cast<uint8_t>(ok ? 1 : 0);
-                    c.io.refreshed[rt * K + k] = static_cast<uint8_t>((S.out_flag[k] >> 1) & 1);
-                }
             }
-            if (r == 0 && !c.io.forced && lane == 0) c.io.theta[rt] = S.theta;
             // the units in use, ascending, and each one's slots as a bit mask
             int n = 0;
             for (int j = 0; j < M; ++j) {
@@ -616,6 +614,15 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
         if (producer) {
             if (lane == 0) {
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                if (!last) {
+                    // the next position's inputs (their buffers were last read before this position's decision)
+                    const uint32_t b_scal = static_cast<uint32_t>(sizeof(float)) * Nc * Sn, b_pre = static_cast<uint32_t>(sizeof(float)) * pre_cols;
+                    const uint32_t b_z = static_cast<uint32_t>(sizeof(float)) * d;
+                    mbar_expect_tx(&in_bar, b_scal + b_pre + b_z);
+                    bulk_g2s(in_scal, c.io.scalars + ((rt + 1) * N + cell0) * Sn, b_scal, &in_bar);
+                    if (pre_cols > 0) bulk_g2s(in_pre, c.pre_s + (rt + 1) * H + r * kFrontCols, b_pre, &in_bar);
+                    bulk_g2s(in_z, c.io.z + (rt + 1) * d, b_z, &in_bar);
+                }
                 const int n_bank = n_units * 2;
                 const int total = n_bank + (last ? 0 : 2);
                 for (int i = 0; i < total; ++i) {
@@ -639,6 +646,16 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
             __syncwarp();
         } else {
             RMARK(24);
+            if (r == 0 && !c.io.forced && warp == 7) {   // the decision's record, off the critical path
+                for (int k = lane; k < K; k += 32) {
+                    const bool ok = (S.out_flag[k] & 1) != 0;
+                    c.io.cells[rt * K + k] = S.out_cell[k];
+                    c.io.units[rt * K + k] = S.out_unit[k];
+                    c.io.valid[rt * K + k] = static_cast<uint8_t>(ok ? 1 : 0);
+                    c.io.refreshed[rt * K + k] = static_cast<uint8_t>((S.out_flag[k] >> 1) & 1);
+                }
+                if (lane == 0) c.io.theta[rt] = S.theta;
+            }
             for (int e = tid; e < K * d; e += kConsumers) {
                 const int k = e / d, x = e - k * d;
                 const int cell = S.out_cell[k];
@@ -1043,7 +1060,8 @@ static bool rows_shape(const HsnwModel& m, RowsCtx* c) {
     if (C != 1 && C != 2 && C != 4 && C != 8) return false;
     if (m.N % C || (4 * m.d) % C || m.N > 2048) return false;
     if (m.d != 16 && m.d != 32 && m.d != 64) return false;
-    if (m.K > kMaxK || m.M > kMaxMR || m.K < 1 || m.S > 16) return false;
+    if (m.K > kMaxK || m.M > kMaxMR || m.K < 1 || m.S > 16 || m.S < 1) return false;
+    if (((m.N / C) * m.S) % 4) return false;   // the position's scalars of a block's cells move as one 16-byte aligned bulk copy
     c->C = C;
     c->Nc = m.N / C;
     c->Ks = (m.K + C - 1) / C;
@@ -1058,6 +1076,7 @@ static bool rows_shape(const HsnwModel& m, RowsCtx* c) {
 int hsnw_rows_forward(const HsnwModel* model, const HsnwForward* io, const float* pre_s, int* status, cudaStream_t stream) {
     RowsCtx c;
     if (!rows_shape(*model, &c)) return -1;
+    if ((reinterpret_cast<uintptr_t>(io->scalars) | reinterpret_cast<uintptr_t>(io->z) | reinterpret_cast<uintptr_t>(pre_s)) & 15) return -1;
     c.stages = kMaxStages;
     RowsSmem L = rows_smem(*model, c.C, c.slot_bytes, c.stages);
     if (L.total + 2048 > hsnw_max_shared()) {
