@@ -307,22 +307,42 @@ def main() -> None:
     host_out = {k: torch.empty(s, dtype=t).pin_memory() for k, (s, t) in
                 {"dc": ((B, T, K, d), torch.float32), "db": ((B, T, K, d), torch.float32),
                  "h": ((B, N, d), torch.float32), "q": ((B, d), torch.float32)}.items()}  # fmt: skip
-    staged = [torch.empty_like(t, device=dev) for t in pinned]
+    # Two staging sets: step i + 1's inputs cross the bus on a copy stream while step i computes (what a
+    # data loader does); every step's host-to-device copy and read-back is inside the timed region.
+    staged = [[torch.empty_like(t, device=dev) for t in pinned] for _ in range(2)]
+    copy_stream = torch.cuda.Stream(device=dev)
+    main_stream = torch.cuda.current_stream(dev)
+    landed = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
 
-    def e2e_step():
-        for dst, src in zip(staged, pinned):
-            dst.copy_(src, non_blocking=True)
-        tape, dc, db, _ = step(staged[0], staged[1], staged[2], staged[3], staged[4:7])
+    def upload(i):
+        buf = i & 1
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(consumed[buf])   # the step that last read this set is done with it
+            for dst, src in zip(staged[buf], pinned):
+                dst.copy_(src, non_blocking=True)
+            landed[buf].record(copy_stream)
+
+    def e2e_step(i):
+        buf = i & 1
+        upload(i + 1)
+        main_stream.wait_event(landed[buf])
+        st = staged[buf]
+        tape, dc, db, _ = step(st[0], st[1], st[2], st[3], st[4:7])
+        consumed[buf].record(main_stream)
         host_out["dc"].copy_(dc, non_blocking=True)
         host_out["db"].copy_(db, non_blocking=True)
         host_out["h"].copy_(tape["h"], non_blocking=True)
         host_out["q"].copy_(tape["q"], non_blocking=True)
 
-    e2e_step()
+    for ev in consumed:
+        ev.record(main_stream)
+    upload(0)
+    e2e_step(0)   # untimed: fills the pipeline
     barrier()
     e0.record()
-    for _ in range(args.steps):
-        e2e_step()
+    for i in range(1, args.steps + 1):
+        e2e_step(i)
     e1.record()
     barrier()
     ms_e2e = e0.elapsed_time(e1) / args.steps
@@ -379,7 +399,8 @@ def main() -> None:
                        "l2": "inputs larger than L2 (tape 0.5 GiB + scalars 75 MB per step)",
                        "allreduce_floats_per_step": n_params if world > 1 else 0},
             "e2e": {"value": world * row_pos / (ms_e2e * 1e-3), "unit": "row-positions/s",
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "note": "the next step's inputs are uploaded on a copy stream while this step computes; results are read back on the compute stream"},
             "gpu_launches": args.steps * launches_per_step,
             "roofline": roofline,
             "clocks": clocks_summary(lines, local),
