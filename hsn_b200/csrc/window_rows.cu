@@ -478,10 +478,62 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
         int* old_rank = stale_w + 8;                          // [K] the same flag for the K best
         if (!producer && !c.io.forced) {
             int n_old = 0;
-            if (c.m.lambda_cost == 0.0f) {
+            if (c.m.lambda_cost == 0.0f && N <= kConsumers) {
                 // the scores are bf16 values here (rounded logits, no cost term): the low half of
                 // their order word carries nothing, so (score's high half, 0xffff - index) is a
-                // 32-bit key with the same order, unique per cell (N <= 2048)
+                // 32-bit key with the same order, unique per cell. One key a thread: every warp sorts
+                // its 32 keys (a bitonic network of shuffles), the warps' K + 1 best meet in shared
+                // memory and one warp ranks those 8 (K + 1) candidates by counting.
+                uint32_t* wtop = reinterpret_cast<uint32_t*>(keys);   // [8][K + 1], padded to a multiple of 4 with zeros
+                const int i = tid;
+                uint32_t key = i < N ? ((float_order(score_all[i]) & 0xffff0000u) | (0xffffu - static_cast<uint32_t>(i))) : 0u;
+                const bool old = i < N && age_all[i] > static_cast<int64_t>(c.m.age_max);
+                n_old = __popc(__ballot_sync(0xffffffffu, old));
+#pragma unroll
+                for (int k2 = 2; k2 <= 32; k2 <<= 1) {
+#pragma unroll
+                    for (int j = k2 >> 1; j > 0; j >>= 1) {
+                        const uint32_t other = __shfl_xor_sync(0xffffffffu, key, j);
+                        const bool keep_max = ((lane & j) == 0) == ((lane & k2) == 0);   // descending
+                        key = keep_max ? max(key, other) : min(key, other);
+                    }
+                }
+                RMARK(32);
+                const int n_cand = (kConsumers / 32) * (K + 1), n_cand_pad = (n_cand + 3) & ~3;
+                if (lane <= K) wtop[warp * (K + 1) + lane] = key;
+                if (tid >= n_cand && tid < n_cand_pad) wtop[tid] = 0u;
+                if (tid == 0) next_key_s = 0ull;
+                if (lane == 0) stale_w[warp] = n_old;
+                consumer_sync();
+                RMARK(33);
+                if (tid < n_cand) {   // a thread per candidate
+                    const uint4* cand4 = reinterpret_cast<const uint4*>(wtop);
+                    const uint32_t mine = wtop[tid];
+                    int r0 = 0, r1 = 0, r2 = 0, r3 = 0;
+#pragma unroll 6
+                    for (int j4 = 0; j4 < n_cand_pad >> 2; ++j4) {
+                        const uint4 o = cand4[j4];
+                        r0 += o.x > mine;
+                        r1 += o.y > mine;
+                        r2 += o.z > mine;
+                        r3 += o.w > mine;
+                    }
+                    const int rank = (r0 + r1) + (r2 + r3);
+                    if (mine != 0u && rank <= K) {
+                        const int cell = static_cast<int>(0xffffu - (mine & 0xffffu));
+                        if (rank < K) {
+                            S.order[rank] = cell;
+                            old_rank[rank] = age_all[cell] > static_cast<int64_t>(c.m.age_max) ? 1 : 0;
+                        } else {
+                            next_key_s = pack_key(score_all[cell], cell);
+                        }
+                    }
+                }
+                consumer_sync();
+                n_old = -1;   // the counts are in place
+            } else if (c.m.lambda_cost == 0.0f) {
+                // more cells than threads: a cell's place is the number of larger keys, counted by the
+                // cell's thread against all keys
                 uint32_t* key32 = reinterpret_cast<uint32_t*>(keys);   // [N] padded to a multiple of 4 with zeros
                 for (int i = tid; i < ((N + 3) & ~3); i += kConsumers)
                     key32[i] = i < N ? ((float_order(score_all[i]) & 0xffff0000u) | (0xffffu - static_cast<uint32_t>(i))) : 0u;
@@ -528,9 +580,11 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                     }
                 }
             }
-            n_old = __reduce_add_sync(0xffffffffu, n_old);
-            if (lane == 0) stale_w[warp] = n_old;
-            consumer_sync();
+            if (n_old >= 0) {
+                n_old = __reduce_add_sync(0xffffffffu, n_old);
+                if (lane == 0) stale_w[warp] = n_old;
+                consumer_sync();
+            }
         }
         RMARK(16);
         if (warp == 0) {
