@@ -157,7 +157,7 @@ __host__ __device__ inline RowsSmem rows_smem(const HsnwModel& m, int C, uint32_
     do {                                                                                      \
         if (tid == 0 && row == 0 && t == T / 2) {                                             \
             unsigned long long now;                                                           \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));                           \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now) : : "memory");              \
             reinterpret_cast<unsigned long long*>(c.status + 64)[r * 64 + (i)] = now;         \
         }                                                                                     \
     } while (0)
@@ -661,6 +661,13 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
             if (lane == 0) n_units_s = n;
             RMARK(18);
         }
+#ifdef HSNW_TRACE
+        if (lane == 0 && row == 0 && t == T / 2) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now) : : "memory");
+            reinterpret_cast<unsigned long long*>(c.status + 64)[r * 64 + 48 + warp] = now;
+        }
+#endif
         __syncthreads();
         RMARK(5);
         const int n_units = n_units_s;
@@ -756,17 +763,6 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 const int p = e / (16 - K), k = K + e - p * (16 - K);
                 reinterpret_cast<uint4*>(vop)[p * 16 + k] = make_uint4(0u, 0u, 0u, 0u);
             }
-            if (rec) {
-                for (int e = tid; e < K * d; e += kConsumers) {
-                    const int k = e / d;
-                    if (k % C == r) {
-                        c.io.rec_h_old[rt * K * d + e] = hold[e];
-                        c.io.rec_m[rt * K * d + e] = msg[e];
-                    }
-                }
-                for (int k = tid; k < K; k += kConsumers)
-                    if (k % C == r) c.io.rec_rms[rt * K + k] = rms[k];
-            }
             fence_async_smem();   // the operand written above, before the tensor cores read it
             consumer_sync();
             RMARK(7);
@@ -803,6 +799,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 RMARK(29);
             }
             if (epi) {
+                float hid_keep[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                 for (int i = 0; i < n_chunks; ++i) {
                     const unsigned mask = static_cast<unsigned>(umask[i >> 1]);
                     const uint32_t slot = (g0 + i) % kStages;
@@ -819,7 +816,6 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                         umma_commit(&bar_d1[(i + 1) & 1]);
                     }
                     if (epi) {
-                        const int colg = r * 128 + (i & 1) * 64 + hc;
                         const float bias = bias_next;
                         if (i + 1 < n_chunks) bias_next = c.m.b1[ulist[(i + 1) >> 1] * H + r * 128 + ((i + 1) & 1) * 64 + hc];
                         uint16_t* b2i = b2 + (i & 1) * (8 * 16 * 8);
@@ -839,9 +835,10 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                         for (int q = 0; q < 4; ++q) {
                             const int k = 4 * sh + q;
                             float a = 0.0f;
+                            hid_keep[q] = 0.0f;
                             if (mask & (1u << k)) {
                                 const float hid = bf16r((sh ? acc[4 + q] : acc[q]) + bias);
-                                if (rec) c.io.rec_hidden[(rt * K + k) * H + colg] = hid;
+                                hid_keep[q] = hid;
                                 a = gelu_erf(hid);
                             }
                             b2i[((hc >> 3) * 16 + k) * 8 + (hc & 7)] = bf16_bits(a);
@@ -853,6 +850,14 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                     if (i & 1) ++d1_count1;
                     else ++d1_count0;
                     asm volatile("bar.sync 2, 128;\n" ::: "memory");   // the four epilogue warps
+                    if (rec) {
+                        // the record of the pre-activations goes out after the barrier: a barrier waits
+                        // for the stores its threads have in flight
+                        const int colg = r * 128 + (i & 1) * 64 + hc;
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            if (mask & (1u << (4 * sh + q))) c.io.rec_hidden[(rt * K + 4 * sh + q) * H + colg] = hid_keep[q];
+                    }
                     if (tid == 0) {
                         tcgen05_fence_after();
                         // four partial sums of D2, each over the position's chunks
@@ -971,17 +976,11 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                     bv = sigmoid_f(gp[e]);
                     value = (1.0f - bv) * old + bv * cv;
                     change = value - old;
-                    c.io.h_sel[(rt * K + k) * d + x] = value;
                 }
                 hnew[e] = value;
                 hb[e] = bf16r(value);
-                dl[e] = change;
-                if (rec) {
-                    c.io.rec_c[(rt * K + k) * d + x] = cv;
-                    c.io.rec_b[(rt * K + k) * d + x] = bv;
-                    c.io.rec_y[(rt * K + k) * d + x] = ys[e];
-                    c.io.rec_gate_pre[(rt * K + k) * d + x] = gp[e];
-                }
+                Fk[e] = cv;   // F is spent: the candidate and the gate for the record, which the producer warp writes
+                dl[e] = bv;
                 for (int p = 0; p < C; ++p) peer(cl, inbox_delta, p)[k * d + x] = change;
                 if (ok) {   // also before a reset: the position's max |h| and a padded slot's h_sel read it
                     const int cell = cell_of[k];
@@ -1007,6 +1006,43 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
         cl.sync();   // 4
         RMARK(12);
         // ---------------- F: summary, ages, the tape's next record, the next reset
+        if (producer) {
+            // the position's records and the tape's next state record, from shared memory, by the warp
+            // that takes part in no block barrier of the compute warps: its stores delay nobody. The
+            // values stay where they are until the next position's phases D and E, which begin two
+            // cluster barriers after this warp is done.
+            if (rec) {
+                for (int kl = 0; kl < Ks; ++kl) {
+                    const int k = kl * C + r;
+                    if (k >= K) continue;
+                    const bool ok = cell_of[k] >= 0;
+                    for (int x = lane; x < d; x += 32) {
+                        const int e = kl * d + x;
+                        const int64_t at = (rt * K + k) * d + x;
+                        c.io.rec_c[at] = Fk[e];
+                        c.io.rec_b[at] = dl[e];
+                        c.io.rec_y[at] = ys[e];
+                        c.io.rec_gate_pre[at] = gp[e];
+                        c.io.rec_h_old[at] = hold[k * d + x];
+                        c.io.rec_m[at] = msg[k * d + x];
+                        if (ok) c.io.h_sel[at] = hnew[e];
+                    }
+                    if (lane == 0) c.io.rec_rms[rt * K + k] = rms[k];
+                }
+            } else {
+                for (int kl = 0; kl < Ks; ++kl) {
+                    const int k = kl * C + r;
+                    if (k >= K || cell_of[k] < 0) continue;
+                    for (int x = lane; x < d; x += 32) c.io.h_sel[(rt * K + k) * d + x] = hnew[kl * d + x];
+                }
+            }
+            if (tape) {
+                float4* dst = reinterpret_cast<float4*>(c.io.tape_h + ((static_cast<int64_t>(row) * (T + 1) + t + 1) * N + cell0) * d);
+                const float4* from = reinterpret_cast<const float4*>(h_s);
+                const float4 zero4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                for (int e = lane; e < (Nc * d) >> 2; e += 32) dst[e] = clear ? zero4 : from[e];   // a reset: zeros, whatever the compute warps do to h_s meanwhile
+            }
+        }
         if (!producer) {
             // no barrier in this phase unless the next position resets: every part reads what the
             // cluster barrier above published and writes its own data
@@ -1062,11 +1098,6 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 for (int e = tid; e < Nc * M; e += kConsumers) lh_s[e] = 0.0f;
                 for (int n = tid; n < Nc; n += kConsumers) cmax_s[n] = 0;
                 consumer_sync();
-            }
-            if (tape) {
-                float4* dst = reinterpret_cast<float4*>(c.io.tape_h + ((static_cast<int64_t>(row) * (T + 1) + t + 1) * N + cell0) * d);
-                const float4* from = reinterpret_cast<const float4*>(h_s);
-                for (int e = tid; e < (Nc * d) >> 2; e += kConsumers) dst[e] = from[e];
             }
         }
         RMARK(13);
