@@ -78,7 +78,7 @@ __host__ __device__ inline size_t up16(size_t v) { return (v + 15) & ~static_cas
 // Offsets (bytes) of the dynamic shared memory's segments.
 struct RowsSmem {
     size_t ring, h, vh, lh, age, cmax, wout, vt, gate, swh, sw_head, sw_tail, norm_w, cand_w, fb2, gate_b, score_b,
-        fb1p, score_all, unit_all, age_all, q, ue, rowterm, hold, big, msg, rms, graph, b2, gacc, inbox_front,
+        fb1p, score_all, unit_all, age_all, q, q_after, ue, rowterm, hold, big, msg, rms, graph, b2, gacc, inbox_front,
         inbox_f, inbox_delta, in_scal, in_pre, in_z, upd, cell_of, unit_of, ulist, umask, cand, total;
 };
 __host__ __device__ inline RowsSmem rows_smem(const HsnwModel& m, int C, uint32_t slot_bytes, uint32_t stages) {
@@ -112,6 +112,7 @@ __host__ __device__ inline RowsSmem rows_smem(const HsnwModel& m, int C, uint32_
     L.unit_all = take(4 * N);
     L.age_all = take(8 * N);
     L.q = take(4 * d);
+    L.q_after = take(4 * d);            // the summary after the position, before the next reset (for the tape)
     L.ue = take(4 * 2 * d);
     L.rowterm = take(4 * kMaxMR);
     L.hold = take(4 * K * d);           // the selected cells' rows
@@ -214,6 +215,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
     int* unit_all = reinterpret_cast<int*>(dyn + L.unit_all);
     int64_t* age_all = reinterpret_cast<int64_t*>(dyn + L.age_all);
     float* q_s = reinterpret_cast<float*>(dyn + L.q);
+    float* q_after = reinterpret_cast<float*>(dyn + L.q_after);
     float* ue = reinterpret_cast<float*>(dyn + L.ue);
     float* rowterm = reinterpret_cast<float*>(dyn + L.rowterm);
     float* hold = reinterpret_cast<float*>(dyn + L.hold);
@@ -387,6 +389,20 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
         RMARK(1);
         cl.sync();   // 1
         RMARK(2);
+        if (producer && t > 0) {
+            // the previous position's summary and ages for the tape: they are final since that position's
+            // phase F and stay until this position's
+            const int64_t rp = rt - 1;
+            const bool cleared = c.io.reset[rt] != 0;
+            if (r == 0) {
+                for (int x = lane; x < d; x += 32) {
+                    c.io.qs[rp * d + x] = q_after[x];
+                    if (tape) c.io.tape_q[(static_cast<int64_t>(row) * (T + 1) + t) * d + x] = cleared ? 0.0f : q_after[x];
+                }
+            }
+            if (tape)
+                for (int n = lane; n < Nc; n += 32) c.io.tape_age[(static_cast<int64_t>(row) * (T + 1) + t) * N + cell0 + n] = age_s[n];
+        }
         // ---------------- B: u, eps, the scorer on the block's cells
         if (!producer) {
             if (tid < 2 * d) {
@@ -705,9 +721,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 }
             }
             __syncwarp();
-        } else {
-            RMARK(24);
-            if (r == 0 && !c.io.forced && warp == 7) {   // the decision's record, off the critical path
+            if (r == 0 && !c.io.forced) {   // the decision's record
                 for (int k = lane; k < K; k += 32) {
                     const bool ok = (S.out_flag[k] & 1) != 0;
                     c.io.cells[rt * K + k] = S.out_cell[k];
@@ -717,6 +731,8 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 }
                 if (lane == 0) c.io.theta[rt] = S.theta;
             }
+        } else {
+            RMARK(24);
             for (int e = tid; e < K * d; e += kConsumers) {
                 const int k = e / d, x = e - k * d;
                 const int cell = S.out_cell[k];
@@ -1062,10 +1078,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 float sum = 0.0f;
                 for (int k = 0; k < K; ++k) sum += inbox_delta[k * d + x];   // slot order
                 const float after = q_s[x] + sum / static_cast<float>(N);
-                if (r == 0) {
-                    c.io.qs[rt * d + x] = after;
-                    if (tape) c.io.tape_q[(static_cast<int64_t>(row) * (T + 1) + t + 1) * d + x] = clear ? 0.0f : after;
-                }
+                q_after[x] = after;   // the producer warp writes qs and the tape's q after the next cluster barrier
                 q_s[x] = clear ? 0.0f : after;
             }
             if (r == 0) {
@@ -1086,8 +1099,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 for (int k = 0; k < K; ++k)
                     if (cell_of[k] == cell0 + n) a = 0;
                 if (clear) a = 0;
-                age_s[n] = a;
-                if (tape) c.io.tape_age[(static_cast<int64_t>(row) * (T + 1) + t + 1) * N + cell0 + n] = a;
+                age_s[n] = a;   // the tape's ages likewise
             }
             if (clear) {
                 consumer_sync();   // the reads of the state above are over
@@ -1105,6 +1117,17 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
     // the last position's max |h|, and the state the window ends in
     if (!producer && tid == 0) peer(cl, inbox_front, 0)[r * stride_in + 2 * d] = __int_as_float(hmax_local);
     cl.sync();
+    if (producer) {
+        const int64_t rp = static_cast<int64_t>(row) * T + T - 1;
+        if (r == 0) {
+            for (int x = lane; x < d; x += 32) {
+                c.io.qs[rp * d + x] = q_after[x];
+                if (tape) c.io.tape_q[(static_cast<int64_t>(row) * (T + 1) + T) * d + x] = q_after[x];
+            }
+        }
+        if (tape)
+            for (int n = lane; n < Nc; n += 32) c.io.tape_age[(static_cast<int64_t>(row) * (T + 1) + T) * N + cell0 + n] = age_s[n];
+    }
     if (!producer) {
         if (r == 0 && tid == 0) {
             if (c.io.h_max) {
