@@ -98,7 +98,7 @@ __host__ __device__ inline RowsBwdSmem rows_bwd_smem(const HsnwModel& m, int C, 
     L.ds_all = take(4 * K * d);
     L.dvm_all = take(4 * K * d);
     L.red = take(4 * 8 * 8);            // the epilogue warps' shares of the slots' inner products
-    L.own = take(4 * Ks * (6 * d + 8));   // dzs, ysv, sgs, dy, ds [2d] per owned slot; rho, dot, sig_gate, back
+    L.own = take(4 * Ks * (8 * d + 8));   // dzs, ysv, sgs, dy, ds [2d], dc, db per owned slot; rho, dot, sig_gate, back
     L.total = o;
     return L;
 }
@@ -154,6 +154,8 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
     float* dot = rho + Ks;
     float* sig_gate = dot + Ks;
     float* back = sig_gate + Ks;
+    float* dcs = back + Ks;                // [Ks][d] dc and db of the position, written to memory off the critical path
+    float* dbs = dcs + Ks * d;
     const unsigned char* bank = static_cast<const unsigned char*>(c.m.rows_bank_bw);
 
     auto rec_of = [&](int buf) { return reinterpret_cast<float*>(dyn + L.rec[buf]); };
@@ -364,8 +366,8 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
                 yv = rc[(3 * Ks + kl) * d + x];
                 sgv = dgv * (rc[(4 * Ks + kl) * d + x] - gate_b[x]);
             }
-            c.io.dc[(rt * K + k) * d + x] = dcv;
-            c.io.db[(rt * K + k) * d + x] = dbv;
+            dcs[e] = dcv;
+            dbs[e] = dbv;
             dzs[e] = dz;
             ysv[e] = yv;
             sgs[e] = sgv;
@@ -506,8 +508,16 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
                 __syncwarp();
             }
         } else {
-            // the gate's transposed linear, this block's state outputs, by the other four warps
+            // the gate's transposed linear, this block's state outputs, by the other four warps; first
+            // the position's dc and db go to memory (these warps meet no barrier for microseconds)
             const int t2 = (warp >> 2) * 64 + (warp & 1) * 32 + lane;   // 0 .. 127
+            for (int e = t2; e < Ks * d; e += 128) {
+                const int kl = e / d, x = e - kl * d, k = kl * C + r;
+                if (k < K) {
+                    c.io.dc[(rt * K + k) * d + x] = dcs[e];
+                    c.io.db[(rt * K + k) * d + x] = dbs[e];
+                }
+            }
             for (int e = t2; e < K * gcols; e += 128) {
                 const int k = e / gcols, il = e - k * gcols;
                 const float sum = dc_[k] >= 0 ? dot_bf16w(dg_all + k * d, 1, gate + il * d, 1, d) : 0.0f;
