@@ -13,6 +13,9 @@ extern "C" __global__ void hsn_win_select(HsnWinArgs a);
 extern "C" __global__ void hsn_win_cell_update(HsnWinArgs a);
 extern "C" __global__ void hsn_win_recurrence(HsnWinArgs a);
 extern "C" __global__ void hsn_win_recurrence_dense(HsnWinArgs a);
+extern "C" __global__ void hsn_win_back_head(HsnWinArgs a);
+extern "C" __global__ void hsn_win_back_mid(HsnWinArgs a);
+extern "C" __global__ void hsn_win_back_tail(HsnWinArgs a);
 
 namespace {
 
@@ -35,6 +38,9 @@ const Named kKernels[] = {
     {"hsn_win_cell_update", hsn_win_cell_update},
     {"hsn_win_recurrence", hsn_win_recurrence},
     {"hsn_win_recurrence_dense", hsn_win_recurrence_dense},
+    {"hsn_win_back_head", hsn_win_back_head},
+    {"hsn_win_back_mid", hsn_win_back_mid},
+    {"hsn_win_back_tail", hsn_win_back_tail},
 };
 
 const Named* find(const char* name) {
@@ -210,6 +216,16 @@ extern "C" int hsnw_launch_shape(const char* name, const HsnWinArgs* a, int64_t*
         if (N < 1 || d < 1) return hsnw_fail(HSNW_E_ARG, "recurrence_dense: sizes must be positive");
         *block = 256;
         bytes = sizeof(float) * (static_cast<size_t>(N) + 1) * d;
+    } else if (strcmp(name, "hsn_win_back_head") == 0 || strcmp(name, "hsn_win_back_mid") == 0 ||
+               strcmp(name, "hsn_win_back_tail") == 0) {
+        // one warp per slot; the sizes sit at different slots of the three descriptors
+        const bool head = name[13] == 'h', tail = name[13] == 't';
+        const int K = a->i[2], d = a->i[3], N = head || tail ? a->i[4] : 1;
+        const int F = head ? a->i[7] : tail ? a->i[5] : a->i[6];
+        if (K < 1 || d < 1 || N < 1 || a->i[1] < 1) return hsnw_fail(HSNW_E_ARG, "back: sizes must be positive");
+        if (F < 0 || F >= K) return hsnw_fail(HSNW_E_ARG, "back: the fixed slots must leave a routed slot");
+        *block = tail ? 256 : (K >= 32 ? 1024 : (K < 2 ? 64 : 32 * K));
+        bytes = head ? sizeof(float) * d : tail ? sizeof(float) * (2 * static_cast<size_t>(K) * d + N) : 0;
     } else {
         return hsnw_fail(HSNW_E_NAME, "launch_shape: no kernel of that name");
     }

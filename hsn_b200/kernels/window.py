@@ -14,7 +14,7 @@ PyTorch fallback in here: a missing library raises.
 from __future__ import annotations
 
 import ctypes
-from typing import TYPE_CHECKING, Any, cast
+from typing import TYPE_CHECKING, Any, NamedTuple, cast
 
 import torch
 from torch import Tensor, nn
@@ -638,4 +638,167 @@ def update_fold(
     update_fold_op(
         y, gate, tape_h, tape_q, tape_age, cells, valid, weight, reset, tape_hsel, h_max, qs, x, z,
         context, t, cand_norm, eps, n_fast,
+    )  # fmt: skip
+
+
+# --------------------------------------------------------------------------------------------------
+# The reverse sweep's glue kernels (reference window.py:1147-1290)
+# --------------------------------------------------------------------------------------------------
+
+ACTIVATION_CODES: dict[str, int] = {"gelu": 0, "relu": 1, "silu": 2, "tanh": 3}
+"""The activation's code in ``hsn_win_back_mid`` (reference ``python/hsn/train/state_sweep.py:67``)."""
+
+
+class SweepShape(NamedTuple):
+    """The sizes a reverse sweep is built for, in the reference's order
+    (``python/hsn/train/state_sweep.py:70-86``): ``n_fast`` leading slots have a fixed unit and
+    their own operands, ``n_read`` cells are read after every position, ``in_dim`` is the width the
+    cell norm averages over, ``d_out`` the largest number of cells one cell is a message source of."""
+
+    B: int
+    T: int
+    K: int
+    N: int
+    d: int
+    H: int
+    M: int
+    n_fast: int
+    n_read: int
+    in_dim: int
+    d_out: int
+
+
+class SweepBuffers:
+    """The static buffers of a reverse sweep under the reference's names, shapes and dtypes
+    (``ReverseSweep.__init__``, ``state_sweep.py:143-198``): what :func:`back_head`,
+    :func:`back_mid` and :func:`back_tail` read and write. The reference's own ``ReverseSweep``
+    can be passed to those functions instead; this class exists for callers that hold no
+    reference object. The two products between the kernels stay the caller's."""
+
+    def __init__(self, shape: SweepShape, *, device: torch.device, product_dtype: torch.dtype = torch.float32,
+                 activation: str = "gelu", cand_norm: bool = True, cand_eps: float = 1e-6,
+                 cell_norm: bool = True) -> None:  # fmt: skip
+        if product_dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError("the products' dtype is float32 or bfloat16")
+        B, T, K, N, d, H, M, F, n_read, _, d_out = shape
+        if not 0 <= F < K:
+            raise ValueError(f"n_fast={F} must leave a routed slot of the {K} slots")
+        self.shape, self.device = shape, device
+        self.state_dtype, self.product_dtype = torch.float32, product_dtype
+        self.activation, self.cand_norm, self.cand_eps, self.cell_norm = activation, cand_norm, float(cand_eps), cell_norm
+        self.routed = K - F
+        rows = B * self.routed
+
+        def state(*size: int) -> Tensor:
+            return torch.zeros(*size, dtype=torch.float32, device=device)
+
+        def product(*size: int) -> Tensor:
+            return torch.zeros(*size, dtype=product_dtype, device=device)
+
+        def index(*size: int) -> Tensor:
+            return torch.zeros(*size, dtype=torch.int64, device=device)
+
+        self.A, self.R = state(B, N, d), state(B, d)
+        self.c, self.b, self.h_old = state(B, T, K, d), state(B, T, K, d), state(B, T, K, d)
+        self.y, self.gate_pre, self.mv = state(B, T, K, d), state(B, T, K, d), state(B, T, K, d)
+        self.rms = state(B, T, K)
+        self.hidden = product(B, T, K, H)
+        self.cells, self.units = index(B, T, K), index(B, T, K)
+        self.valid = torch.zeros(B, T, K, dtype=torch.bool, device=device)
+        self.reset = torch.zeros(B, T, dtype=torch.bool, device=device)
+        self.d_q_pre, self.d_q_post = state(B, T, d), state(B, T, d)
+        self.d_h_sel = state(B, T, K, d)
+        self.d_h_fast = state(B, T, max(n_read, 1), d)
+        self.cand_gain, self.gate_bias, self.b1 = state(d), state(d), state(M, H)
+        self.out_tgt = torch.full((N, d_out), -1, dtype=torch.int32, device=device)
+        self.out_w = state(N, d_out)
+        self.op1, self.op2 = product(rows, M * d), product(rows, M * H + d)
+        self.op1_fast, self.op2_fast = product(max(F, 1), B, d), product(max(F, 1), B, H + d)
+        self.act_r, self.dv_r = product(rows, H), product(rows, 2 * d)
+        self.act_f, self.dv_f = product(max(F, 1), B, H), product(max(F, 1), B, 2 * d)
+        self.sigma = state(B, K)
+        self.dc, self.db = state(B, T, K, d), state(B, T, K, d)
+
+
+def _half(t: Tensor) -> int:
+    return int(t.dtype == torch.bfloat16)
+
+
+def _back_head_ints(s: SweepShape, t: int, cand_norm: bool, half: int) -> list[int]:
+    return [s.B, s.T, s.K, s.d, s.N, s.M, s.H, s.n_fast, t, s.n_read, int(cand_norm), half]
+
+
+def back_unsupported(shape: SweepShape) -> str | None:
+    """Why the reverse sweep's kernels cannot take this shape (``None``: they can; reference
+    ``window.py:1166-1178``, whose limits of 32 slots and of the reference kernels' shared memory
+    do not exist here: the only limit is the tail's ``2 K d + N`` words of shared memory)."""
+    s = SweepShape(*shape)
+    for name, ints in (
+        ("hsn_win_back_head", _back_head_ints(s, 0, True, 0)),
+        ("hsn_win_back_mid", [s.B, s.T, s.K, s.d, s.M, s.H, s.n_fast, 0, 0, 0, 0]),
+        ("hsn_win_back_tail", [s.B, s.T, s.K, s.d, s.N, s.n_fast, 0, s.d_out, 1, s.in_dim, 0]),
+    ):
+        reason = _shape_error(name, ints)
+        if reason is not None:
+            return reason
+    return None
+
+
+def _position(s: SweepShape, t: int) -> None:
+    if not 0 <= t < s.T:
+        raise ValueError(f"position {t} is outside the window's {s.T}")
+
+
+def back_head(sweep: Any, t: int) -> None:
+    """The head of position ``t`` of a reverse sweep on its buffers (``hsn_win_back_head``;
+    reference ``window.py:1185-1221``, contract ``ReverseSweep.head_reference``,
+    ``state_sweep.py:441-477``): ``R += d_q_post``, the read cells' and the selected cells'
+    cotangents into ``A``, ``dc``/``db`` of the position, the written cells' rows of ``A``
+    replaced, the candidate norm's backward, and the first product's operand ``op1`` (block of the
+    slot's unit, the block position ``t + 1`` used cleared), the gate columns of ``op2`` and
+    ``sigma``."""
+    s = SweepShape(*sweep.shape)
+    _position(s, t)
+    _launch(
+        "hsn_win_back_head",
+        [sweep.A, sweep.R, sweep.c, sweep.b, sweep.h_old, sweep.y, sweep.cells, sweep.units, sweep.valid,
+         sweep.d_q_post, sweep.d_h_sel, sweep.d_h_fast, sweep.cand_gain, sweep.gate_pre, sweep.gate_bias,
+         sweep.dc, sweep.db, sweep.op1, sweep.op1_fast, sweep.op2, sweep.op2_fast, sweep.sigma],
+        _back_head_ints(s, t, bool(sweep.cand_norm), _half(sweep.op1)),
+        [float(sweep.cand_eps)],
+    )  # fmt: skip
+
+
+def back_mid(sweep: Any, t: int) -> None:
+    """The middle of position ``t`` (``hsn_win_back_mid``; reference ``window.py:1224-1250``,
+    contract ``ReverseSweep.middle_reference``, ``state_sweep.py:487-495``): the first product's
+    result ``act_r``/``act_f`` through the activation's derivative at ``hidden`` into the hidden
+    blocks of ``op2``, and its part of ``sigma``."""
+    s = SweepShape(*sweep.shape)
+    _position(s, t)
+    _launch(
+        "hsn_win_back_mid",
+        [sweep.act_r, sweep.act_f, sweep.hidden, sweep.units, sweep.valid, sweep.b1, sweep.op2,
+         sweep.op2_fast, sweep.sigma],
+        [s.B, s.T, s.K, s.d, s.M, s.H, s.n_fast, t, _half(sweep.act_r), _half(sweep.hidden),
+         ACTIVATION_CODES[sweep.activation]],
+        [],
+    )  # fmt: skip
+
+
+def back_tail(sweep: Any, t: int) -> None:
+    """The tail of position ``t`` (``hsn_win_back_tail``; reference ``window.py:1253-1281``,
+    contract ``ReverseSweep.tail_reference``, ``state_sweep.py:497-533`` without a row limit): the
+    second product's result ``dv_r``/``dv_f`` through the cell norm, its state half added to the
+    selected cells' rows of ``A``, its message half to every source of a selected cell along
+    ``out_tgt``/``out_w``, ``R += d_q_pre``, and the reset."""
+    s = SweepShape(*sweep.shape)
+    _position(s, t)
+    _launch(
+        "hsn_win_back_tail",
+        [sweep.A, sweep.R, sweep.dv_r, sweep.dv_f, sweep.sigma, sweep.rms, sweep.h_old, sweep.mv, sweep.cells,
+         sweep.valid, sweep.out_tgt, sweep.out_w, sweep.d_q_pre, sweep.reset],
+        [s.B, s.T, s.K, s.d, s.N, s.n_fast, t, s.d_out, int(bool(sweep.cell_norm)), s.in_dim,
+         _half(sweep.dv_r)],
+        [],
     )  # fmt: skip

@@ -62,10 +62,11 @@ int hsnw_sm_count(int device);
 
 /* One launch of the kernel `name` with `grid` blocks of `block` threads and `shared` bytes of
  * dynamic shared memory on `stream` (a cudaStream_t; NULL: the default stream).
- * Names: hsn_win_select, hsn_win_cell_update, hsn_win_recurrence, hsn_win_recurrence_dense; any
- * other name returns HSNW_E_NAME. (The reference's per-position reverse-sweep kernels
- * hsn_win_back_head / _mid / _tail, hsn_window.cu:1014-1427, exist only between its two cuBLAS
- * products; here the whole sweep is hsnw_window_backward.)
+ * Names: hsn_win_select, hsn_win_cell_update, hsn_win_recurrence, hsn_win_recurrence_dense, and the
+ * reverse sweep's three per-position glue kernels hsn_win_back_head, hsn_win_back_mid,
+ * hsn_win_back_tail (hsn_window.cu:1014-1427; their slots are window.py:1181-1290's, and the two
+ * products between them stay the caller's; the whole sweep as one call is hsnw_window_backward).
+ * Any other name returns HSNW_E_NAME.
  * grid <= 0 launches nothing (window_ext.cpp:96). Capturable in a CUDA graph. */
 int hsnw_launch(const char* name, const HsnWinArgs* args, int64_t grid, int block, int shared,
                 void* stream);

@@ -663,3 +663,160 @@ def out_adjacency(pad_src: np.ndarray, pad_mask: np.ndarray):
     out_tgt[source, position_] = target
     out_edge[source, position_] = flat
     return out_tgt, out_edge
+
+
+# --------------------------------------------------------------------------------------------------
+# The reverse sweep's glue steps between its two products (the by-name kernels' contract)
+# --------------------------------------------------------------------------------------------------
+
+
+def activation_grad(name: str, x: np.ndarray) -> np.ndarray:
+    """``python/hsn/train/state_gradient.py:192-205``."""
+    if name == "gelu":
+        return gelu_grad(x)
+    if name == "relu":
+        return (x > 0).astype(x.dtype)
+    if name == "silu":
+        s = sigmoid(x)
+        return (s * (1.0 + x * (1.0 - s))).astype(x.dtype)
+    if name == "tanh":
+        return (1.0 - np.tanh(x) ** 2).astype(x.dtype)
+    raise ValueError(name)
+
+
+@dataclass
+class SweepSizes:
+    """``SweepShape`` (``python/hsn/train/state_sweep.py:70-86``)."""
+
+    B: int
+    T: int
+    K: int
+    N: int
+    d: int
+    H: int
+    M: int
+    n_fast: int
+    n_read: int
+    in_dim: int
+    d_out: int
+
+
+def _operand(x: np.ndarray, half: bool) -> np.ndarray:
+    return bf16_round(x) if half else x.astype(np.float32)
+
+
+def _sweep_write_blocks(s: SweepSizes, buf: dict, operand: str, fast: str, values, t: int, width: int,
+                        half: bool) -> None:
+    """``ReverseSweep._write_blocks`` (``state_sweep.py:424-439``): a routed slot's values into its
+    unit's block of its row of the operand, after the block position ``t + 1`` used is cleared; a
+    fixed slot's into the fast operand ``[F, B, ·]``."""
+    F, routed = s.n_fast, s.K - s.n_fast
+    for b in range(s.B):
+        for k in range(F, s.K):
+            row = b * routed + (k - F)
+            if t + 1 < s.T:
+                before = int(buf["units"][b, t + 1, k])
+                buf[operand][row, before * width:(before + 1) * width] = 0
+        for k in range(F, s.K):
+            row = b * routed + (k - F)
+            now = int(buf["units"][b, t, k])
+            buf[operand][row, now * width:(now + 1) * width] = _operand(values[b, k], half)
+        for k in range(F):
+            buf[fast][k, b, :width] = _operand(values[b, k], half)
+
+
+def sweep_head(s: SweepSizes, buf: dict, t: int, *, cand_norm: bool, cand_eps: float, half: bool) -> None:
+    """``ReverseSweep.head_reference`` (``state_sweep.py:441-477``) in place on ``buf`` (arrays by
+    the sweep's buffer names; fp32 state, operands bf16-valued when ``half``)."""
+    f32 = np.float32
+    F, d = s.n_fast, s.d
+    R = (buf["R"] + buf["d_q_post"][:, t]).astype(f32)
+    buf["R"][...] = R
+    d_unit = np.zeros((s.B, s.K, d), f32)
+    d_gate = np.zeros((s.B, s.K, d), f32)
+    for b in range(s.B):
+        A = buf["A"][b]
+        if s.n_read:
+            A[: s.n_read] += buf["d_h_fast"][b, t, : s.n_read]
+        share = (R[b] / f32(s.N)).astype(f32)
+        for k in range(s.K):
+            if not buf["valid"][b, t, k]:
+                buf["dc"][b, t, k] = 0
+                buf["db"][b, t, k] = 0
+                continue
+            n = int(buf["cells"][b, t, k])
+            carried = (A[n] + buf["d_h_sel"][b, t, k]).astype(f32)
+            g = carried + share
+            gate, c = buf["b"][b, t, k], buf["c"][b, t, k]
+            dc = (gate * g).astype(f32)
+            db = ((c - buf["h_old"][b, t, k]) * g).astype(f32)
+            buf["dc"][b, t, k], buf["db"][b, t, k] = dc, db
+            A[n] = ((f32(1) - gate) * carried - gate * share).astype(f32)
+            dz = (dc * (f32(1) - c * c)).astype(f32)
+            if cand_norm:
+                y = buf["y"][b, t, k]
+                scaled = (buf["cand_gain"] * dz).astype(f32)
+                rho = f32(1) / np.sqrt(np.mean(y * y, dtype=f32) + f32(cand_eps), dtype=f32)
+                dz = (rho * scaled - rho * rho * rho * y * np.mean(y * scaled, dtype=f32)).astype(f32)
+            d_unit[b, k] = dz
+            d_gate[b, k] = db * gate * (f32(1) - gate)
+    buf["sigma"][...] = (d_gate * (buf["gate_pre"][:, t] - buf["gate_bias"])).sum(axis=-1, dtype=f32)
+    _sweep_write_blocks(s, buf, "op1", "op1_fast", d_unit, t, d, half)
+    routed = s.K - F
+    buf["op2"][:, s.M * s.H:] = _operand(d_gate[:, F:].reshape(s.B * routed, d), half)
+    if F:
+        buf["op2_fast"][:, :, s.H:] = _operand(d_gate[:, :F].transpose(1, 0, 2), half)
+
+
+def _sweep_per_slot(s: SweepSizes, routed: np.ndarray, fast: np.ndarray) -> np.ndarray:
+    """``ReverseSweep._per_slot`` (``state_sweep.py:479-485``)."""
+    out = routed.reshape(s.B, s.K - s.n_fast, -1)
+    if s.n_fast:
+        out = np.concatenate([fast.transpose(1, 0, 2), out], axis=1)
+    return out.astype(np.float32)
+
+
+def sweep_middle(s: SweepSizes, buf: dict, t: int, *, activation: str, half: bool) -> None:
+    """``ReverseSweep.middle_reference`` (``state_sweep.py:487-495``)."""
+    f32 = np.float32
+    ok = buf["valid"][:, t].astype(bool)[:, :, None]
+    hidden = buf["hidden"][:, t].astype(f32)
+    d_act = _sweep_per_slot(s, buf["act_r"], buf["act_f"])
+    d_hid = np.where(ok, d_act * activation_grad(activation, hidden), f32(0)).astype(f32)
+    units = buf["units"][:, t]
+    buf["sigma"] += (d_hid * (hidden - buf["b1"][units])).sum(axis=-1, dtype=f32)
+    _sweep_write_blocks(s, buf, "op2", "op2_fast", d_hid, t, s.H, half)
+
+
+def sweep_tail(s: SweepSizes, buf: dict, t: int, *, cell_norm: bool) -> None:
+    """``ReverseSweep.tail_reference`` (``state_sweep.py:497-533``, no row limit)."""
+    f32 = np.float32
+    d = s.d
+    prod = _sweep_per_slot(s, buf["dv_r"], buf["dv_f"])
+    for b in range(s.B):
+        ds = np.zeros((s.K, 2 * d), f32)
+        slot_of = np.full(s.N, -1, np.int64)
+        for k in range(s.K):
+            if not buf["valid"][b, t, k]:
+                continue
+            if cell_norm:
+                r = buf["rms"][b, t, k]
+                back = (r * r / f32(s.in_dim)) * buf["sigma"][b, k]
+                state = np.concatenate([buf["h_old"][b, t, k], buf["mv"][b, t, k]])
+                ds[k] = (r * prod[b, k] - back * state).astype(f32)
+            else:
+                ds[k] = prod[b, k]
+            slot_of[int(buf["cells"][b, t, k])] = k
+        A = buf["A"][b]
+        for k in range(s.K):
+            if buf["valid"][b, t, k]:
+                A[int(buf["cells"][b, t, k])] += ds[k, :d]
+        for j in range(s.d_out):
+            for n in range(s.N):
+                target = int(buf["out_tgt"][n, j])
+                if target >= 0 and slot_of[target] >= 0:
+                    A[n] += buf["out_w"][n, j] * ds[slot_of[target], d:]
+        buf["R"][b] += buf["d_q_pre"][b, t]
+        if buf["reset"][b, t]:
+            A[...] = 0
+            buf["R"][b] = 0

@@ -17,6 +17,10 @@ inputs and outputs of every function on the window path as ``.npz`` files:
                         tape (``python/hsn/train/compile.py:1234``), the replay's record, the arguments
                         and results of ``state_gradient_backward``
                         (``python/hsn/train/state_gradient.py:357``) with its ``A``/``R`` trace.
+* ``sweep_*.npz``       the three glue steps of ``ReverseSweep`` between its two products
+                        (``python/hsn/train/state_sweep.py:441`` head, ``:487`` middle, ``:497`` tail)
+                        on seeded buffers, two positions in sweep order, every written buffer before
+                        and after each step.
 * ``chain_*.npz``       two chained windows against the unsplit window of twice the length: the
                         carried state forward, the state cotangent ``(A, R)`` backward.
 
@@ -479,6 +483,102 @@ def make_chain(root: Path) -> None:
         print("chain", name, "ok")
 
 
+SWEEP_WRITTEN = ("A", "R", "dc", "db", "op1", "op1_fast", "op2", "op2_fast", "sigma")
+SWEEP_READ = (
+    "c", "b", "h_old", "y", "gate_pre", "mv", "rms", "hidden", "cells", "units", "valid", "reset",
+    "d_q_pre", "d_q_post", "d_h_sel", "d_h_fast", "cand_gain", "gate_bias", "b1", "out_tgt", "out_w",
+)  # fmt: skip
+
+
+def make_sweep(root: Path) -> None:
+    """The reverse sweep's glue steps on their own: a ``ReverseSweep`` on the CPU (its PyTorch
+    steps are the kernels' contract), its buffers filled from a seed, then for the positions
+    ``T - 1`` and ``T - 2``: head, middle (after new ``act_r``/``act_f``), tail (after new
+    ``dv_r``/``dv_f``). Every written buffer is stored after every step."""
+    import types
+
+    import torch
+    from hsn.train.state_sweep import ReverseSweep, SweepShape, out_adjacency
+
+    cases = {
+        # name: (B, T, K, N, d, H, M, n_fast, n_read, D, product dtype, cand norm, cell norm, act)
+        "plain_f32": (3, 3, 4, 12, 8, 16, 3, 0, 0, 3, torch.float32, True, True, "gelu"),
+        "fast_bf16": (2, 3, 5, 10, 8, 16, 2, 1, 2, 2, torch.bfloat16, False, False, "silu"),
+        "fast2_bf16": (3, 2, 4, 9, 16, 32, 3, 2, 1, 4, torch.bfloat16, True, True, "tanh"),
+        "relu_f32": (2, 3, 3, 7, 4, 8, 2, 0, 3, 2, torch.float32, True, False, "relu"),
+    }
+    for name, (B, T, K, N, d, H, M, F, n_read, D, pdt, cand, cell, act) in cases.items():
+        gen = torch.Generator().manual_seed(len(name) * 7 + B)
+        pad_src = torch.randint(0, N, (N, D), generator=gen)
+        pad_mask = torch.rand(N, D, generator=gen) < 0.8
+        out_tgt, out_edge = out_adjacency(pad_src, pad_mask)
+        d_out = int(out_tgt.shape[1])
+        shape = SweepShape(B, T, K, N, d, H, M, F, n_read, 4 * d, d_out)
+        consts = types.SimpleNamespace(
+            activation=act,
+            cand_gain=torch.ones(d) if cand else None,
+            cand_eps=1e-5,
+            norm_gain_state=torch.ones(2 * d) if cell else None,
+        )
+        sweep = ReverseSweep(
+            shape, consts, device=torch.device("cpu"), state_dtype=torch.float32,
+            product_dtype=pdt, kernels=False,
+        )  # fmt: skip
+
+        def fill(t, scale=1.0):
+            t.copy_((torch.randn(t.shape, generator=gen) * scale).to(t.dtype))
+
+        for key in ("A", "R", "h_old", "y", "gate_pre", "mv", "hidden", "d_q_pre", "d_q_post",
+                    "d_h_sel", "d_h_fast", "gate_bias", "b1", "op1", "op1_fast", "op2", "op2_fast",
+                    "sigma", "dc", "db"):  # fmt: skip
+            fill(getattr(sweep, key))
+        sweep.c.copy_(torch.tanh(torch.randn(sweep.c.shape, generator=gen)))
+        sweep.b.copy_(torch.sigmoid(torch.randn(sweep.b.shape, generator=gen)))
+        sweep.rms.copy_(torch.rand(sweep.rms.shape, generator=gen) + 0.5)
+        sweep.cand_gain.copy_(1.0 + 0.1 * torch.randn(d, generator=gen))
+        for b in range(B):
+            for t in range(T):
+                sweep.cells[b, t] = torch.randperm(N, generator=gen)[:K]
+        sweep.units.copy_(torch.randint(0, M, sweep.units.shape, generator=gen))
+        sweep.valid.copy_(torch.rand(sweep.valid.shape, generator=gen) < 0.75)
+        sweep.valid[0, T - 1] = True
+        sweep.cells[~sweep.valid] = 0  # the tape's padded slots
+        sweep.units[~sweep.valid] = 0
+        sweep.reset.copy_(torch.rand(sweep.reset.shape, generator=gen) < 0.3)
+        sweep.reset[0, T - 1] = False
+        sweep.out_tgt.copy_(out_tgt.to(torch.int32))
+        sweep.out_w.copy_(torch.randn(N, d_out, generator=gen) * (out_tgt >= 0))
+
+        out: dict[str, np.ndarray] = {
+            "shape": np.asarray(list(shape), dtype=np.int64),
+            "half": np.asarray(int(pdt == torch.bfloat16)),
+            "cand_norm": np.asarray(int(cand)), "cell_norm": np.asarray(int(cell)),
+            "cand_eps": np.asarray(consts.cand_eps), "activation": np.asarray(act),
+        }  # fmt: skip
+        for key in SWEEP_READ:
+            out[key] = np.array(_np(getattr(sweep, key)))
+        for key in SWEEP_WRITTEN:
+            out[f"start_{key}"] = np.array(_np(getattr(sweep, key)))
+        for t in (T - 1, T - 2):
+            sweep.head_reference(t)
+            for key in SWEEP_WRITTEN:
+                out[f"head{t}_{key}"] = np.array(_np(getattr(sweep, key)))
+            fill(sweep.act_r)
+            fill(sweep.act_f)
+            out[f"mid{t}_act_r"], out[f"mid{t}_act_f"] = np.array(_np(sweep.act_r)), np.array(_np(sweep.act_f))
+            sweep.middle_reference(t)
+            for key in SWEEP_WRITTEN:
+                out[f"mid{t}_{key}"] = np.array(_np(getattr(sweep, key)))
+            fill(sweep.dv_r)
+            fill(sweep.dv_f)
+            out[f"tail{t}_dv_r"], out[f"tail{t}_dv_f"] = np.array(_np(sweep.dv_r)), np.array(_np(sweep.dv_f))
+            sweep.tail_reference(t)
+            for key in SWEEP_WRITTEN:
+                out[f"tail{t}_{key}"] = np.array(_np(getattr(sweep, key)))
+        np.savez_compressed(HERE / f"sweep_{name}.npz", **out)
+        print("sweep", name, "ok", "d_out", d_out)
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--reference", type=Path, required=True)
@@ -490,7 +590,7 @@ def main() -> None:
     torch.set_num_threads(1)
     steps = {
         "select": make_select, "update": make_update, "recurrence": make_recurrence,
-        "windows": make_windows, "chain": make_chain,
+        "windows": make_windows, "chain": make_chain, "sweep": make_sweep,
     }  # fmt: skip
     for key, fn in steps.items():
         if not args.only or key in args.only.split(","):

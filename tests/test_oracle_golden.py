@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import numpy as np
 import pytest
-from conftest import load_golden
+from conftest import SWEEP_SETS, SWEEP_WRITTEN, load_golden, sweep_fixture
 
 from oracle import window_oracle as O
 
@@ -229,3 +229,32 @@ def test_bf16_rounding_is_nearest_even() -> None:
     x[:4] = torch.tensor([1.00390625, 1.01171875, float("inf"), -0.0])
     want = x.to(torch.bfloat16).float().numpy()
     assert np.array_equal(O.bf16_round(x.numpy()), want)
+
+
+@pytest.mark.parametrize("name", SWEEP_SETS)
+def test_sweep_glue_steps_equal_the_reference(name: str) -> None:
+    """The head, middle and tail of two positions in sweep order against the reference's own
+    PyTorch steps on the same buffers: the operands (bf16 in two sets) to the bit where they are
+    copies or single roundings of fp32 values within an ulp, the fp32 sums to 1e-5."""
+    z, sizes, buf = sweep_fixture(name)
+    s = O.SweepSizes(*sizes)
+    half = bool(z["half"])
+
+    def check(stage: str) -> None:
+        for key in SWEEP_WRITTEN:
+            want = z[f"{stage}_{key}"]
+            tol = 1e-5 * max(1.0, float(np.abs(want).max()))
+            if half and key.startswith("op"):
+                tol = 2.0**-7 * max(1.0, float(np.abs(want).max()))  # one bf16 step at most
+                assert np.mean(buf[key] != want) < 0.02, (stage, key)
+            assert np.abs(buf[key] - want).max() <= tol, (stage, key)
+
+    for t in (s.T - 1, s.T - 2):
+        O.sweep_head(s, buf, t, cand_norm=bool(z["cand_norm"]), cand_eps=float(z["cand_eps"]), half=half)
+        check(f"head{t}")
+        buf["act_r"], buf["act_f"] = z[f"mid{t}_act_r"], z[f"mid{t}_act_f"]
+        O.sweep_middle(s, buf, t, activation=str(z["activation"]), half=half)
+        check(f"mid{t}")
+        buf["dv_r"], buf["dv_f"] = z[f"tail{t}_dv_r"], z[f"tail{t}_dv_f"]
+        O.sweep_tail(s, buf, t, cell_norm=bool(z["cell_norm"]))
+        check(f"tail{t}")
