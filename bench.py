@@ -36,11 +36,17 @@ CONFIGS = {
     "c1": dict(B=2, T=8, N=16, d=32, K=2, H=32, M=2, D=2, S=9, p=0.1, prod="fp32"),
     "c2": dict(B=32, T=256, N=256, d=64, K=8, H=512, M=8, D=4, S=9, p=1 / 1024, prod="bf16"),
     "c3": dict(B=64, T=512, N=512, d=64, K=8, H=512, M=8, D=4, S=9, p=1 / 1024, prod="bf16"),
+    # the resident contract (no state tape; the state lives in HBM between calls): one GPU's share at 8 GPUs
+    "c4": dict(B=32, T=1024, N=4096, d=128, K=16, H=1024, M=8, D=4, S=9, p=1 / 1024, prod="bf16", resident=True),
+    "c5": dict(B=512, T=32, N=1024, d=64, K=8, H=512, M=8, D=4, S=9, p=1 / 4096, prod="bf16", resident=True,
+               forward_only=True),
 }
 WORKLOADS = {
     "c1": "tiny gradcheck-shape window B2 T8 N16 d32 K2 H32",
     "c2": "reference-shape window fwd+bwd: B32 T256 N256 d64 K8 H512 M8 D4, bf16 products, fp32 state, resets p=1/1024",
     "c3": "one window of the split-window chain: B64 T512 N512 d64 K8 H512, bf16 products",
+    "c4": "scaled sparse routing, one GPU's 32 rows of B256: T1024 N4096 d128 K16 H1024, resident state, fwd+bwd",
+    "c5": "streaming, one GPU's 512 streams of 4096: N1024 d64 K8 H512, forward only on a resident state, 32 steps a call",
 }
 
 
@@ -51,9 +57,11 @@ def bytes_per_row_position(c: dict) -> int:
     N, d, K, H, S = c["N"], c["d"], c["K"], c["H"], c["S"]
     state = 4 * N * d + 4 * d + 8 * N
     fwd = 2 * state + 4 * (2 * d) + 4 * N * S + (18 * K + 4) + (4 * K * d + 4 * d + 4)
+    if c.get("resident"):  # read every cell, write the K written rows, q and the ages
+        fwd = state + (4 * K * d + 4 * d + 8 * N) + 4 * (2 * d) + 4 * N * S + (18 * K + 4) + (4 * K * d + 4 * d + 4)
     full = 4 * (6 * K * d + 2 * d) + 9 * K + 1
     bwd = full + 4 * (3 * K * d) + 4 * K + 2 * K * H + 8 * K
-    return fwd + bwd
+    return fwd if c.get("forward_only") else fwd + bwd
 
 
 def kernel_bytes_per_row_position(c: dict) -> dict[str, int]:
@@ -196,9 +204,11 @@ def run_reference(args, c: dict, name: str) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    positions = min(c["T"], 4)
+    if c.get("resident"):   # only the sampled positions are drawn: the full inputs are too large for the host
+        c = dict(c, T=positions)
     W, data = synthetic(c, 0, min(c["B"], 8))
     rows = data[0].shape[0]
-    positions = min(c["T"], 4)
     for _ in range(args.warmup):
         cpu_window(W, data, rows, positions)
     times = [cpu_window(W, data, rows, positions) for _ in range(args.steps)]
@@ -223,6 +233,89 @@ def run_reference(args, c: dict, name: str) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_resident(args, c: dict, name: str) -> None:
+    """The configurations of the resident contract (one GPU): inputs drawn on the device from a
+    seed (their host copies would not fit a pinned buffer), the state updated in place from call
+    to call, CUDA events around ``steps`` calls. Not the headline line: no end-to-end leg."""
+    import torch
+
+    from hsn_b200.window import WindowModel, launch_profile, window_backward, window_forward
+    from oracle.window_oracle import WindowWeights
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the window path has no CPU fallback")
+    dev = torch.device("cuda", 0)
+    B, T, N, d, K, S = c["B"], c["T"], c["N"], c["d"], c["K"], c["S"]
+    W = WindowWeights.random(np.random.default_rng(0), N=N, d=d, K=K, H=c["H"], M=c["M"], D=c["D"], S=S,
+                             age_max=2**31 - 1)  # fmt: skip
+    model = WindowModel.from_oracle_weights(W, device=dev, prod=c["prod"], row_clusters=not args.phases)
+    gen = torch.Generator(device=dev).manual_seed(1)
+    z = torch.randn((B, T, d), device=dev, generator=gen) * 0.5
+    ctx = torch.randn((B, T, model.dims["dc"]), device=dev, generator=gen) * 0.02
+    scalars = torch.rand((B, T, N, S), device=dev, generator=gen)
+    reset = torch.rand((B, T), device=dev, generator=gen) < c["p"]
+    cots = [torch.randn(shape, device=dev, generator=gen) * 0.1 for shape in ((B, T, d), (B, T, d), (B, T, K, d))]
+    state = (torch.zeros((B, N, d), device=dev), torch.zeros((B, d), device=dev),
+             torch.zeros((B, N), dtype=torch.int64, device=dev), torch.zeros(B, dtype=torch.int64, device=dev))  # fmt: skip
+    forward_only = bool(c.get("forward_only"))
+    out: dict = {}
+    bw_scratch = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def step():
+        tape = window_forward(model, z, ctx, scalars, reset, state, record=not forward_only, tape_state=False, out=out)
+        if forward_only:
+            return
+        rec = {k: tape["rec_" + k] for k in ("y", "hidden", "gate_pre", "m", "rms")}
+        window_backward(model, tape["rec_c"], tape["rec_b"], tape["rec_h_old"], tape["sel_cell_idx"],
+                        tape["sel_unit_idx"], tape["sel_valid"], reset, cots[0], cots[1], cots[2], rec,
+                        scratch=bw_scratch)  # fmt: skip
+
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    stop, lines = threading.Event(), []
+    sampler = threading.Thread(target=sample_clocks, args=(stop, lines), daemon=True)
+    sampler.start()
+    time.sleep(0.3)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    stop.set()
+    sampler.join(timeout=2)
+    with launch_profile() as prof:
+        step()
+    torch.cuda.synchronize()
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    peaks = json.loads(peaks_file.read_text()) if peaks_file.exists() else {}
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    per = bytes_per_row_position(c)
+    achieved = per * B * T / (ms * 1e-3) / 1e9
+    total_ms = sum(prof.ms.values()) or 1.0
+    kernels = {k: {"launches_per_step": n, "us_per_launch": round(1e3 * prof.ms[k] / n, 3),
+                   "share": round(prof.ms[k] / total_ms, 4)} for k, n in prof.launches.items() if n}  # fmt: skip
+    line = {
+        "metric": "window row-positions/s " + ("fwd" if forward_only else "fwd+bwd"), "value": B * T / (ms * 1e-3),
+        "unit": "row-positions/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 products, f32 state",
+        "data": "synthetic (drawn on the device)",
+        "config": {"workload": WORKLOADS[name], "rows_per_gpu": B, "positions": T,
+                   "kernels": "batch-synchronous phases" if args.phases else "library's choice",
+                   "l2": "state and inputs larger than L2"},
+        "e2e": None, "gpu_launches": args.steps * sum(prof.launches.values()),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_source": "measured" if peaks else "fallback",
+                     "bytes_per_row_position": per, "kernels": kernels},
+        "clocks": clocks_summary(lines, 0),
+    }  # fmt: skip
+    print(json.dumps(line), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -241,6 +334,9 @@ def main() -> None:
         c["T"] = args.positions
     if args.impl == "reference":
         run_reference(args, c, args.config)
+        return
+    if c.get("resident"):
+        run_resident(args, c, args.config)
         return
 
     import torch

@@ -553,6 +553,40 @@ def test_tensor_core_kernels_equal_the_cuda_core_kernels_with_the_same_roundings
         assert float((g - w).abs().max()) <= 1e-3 * max(1e-6, float(w.abs().max()))
 
 
+@pytest.mark.parametrize("N,H", [(1024, 512), (256, 512)])
+def test_row_clusters_on_a_resident_state_equal_the_phases(N: int, H: int) -> None:
+    """The serving form (no state tape, the state updated in place, no record) on the streaming
+    model's shape by the per-row cluster kernel, two calls in a row on the same state, against the
+    CUDA-core phases with the decisions forced: the state, the summaries and the ages."""
+    from hsn_b200.window import WindowModel, window_forward
+
+    rng = np.random.default_rng(N)
+    B, T, d, K = 5, 4, 64, 8
+    W, z, ctx, scalars, reset, state = _synthetic(rng, B, 2 * T, N, d, K, H, 8, 4, 0.1)
+    for key in ("w1", "w2", "gate_w", "v_w", "wout_w"):
+        setattr(W, key, O.bf16_round(getattr(W, key)))
+    reset[:, 0] = False
+    h0 = (rng.standard_normal(state[0].shape) * 0.3).astype(np.float32)
+    start = (h0, h0.mean(axis=1), rng.integers(0, 50, state[2].shape), state[3])
+    rows = WindowModel.from_oracle_weights(W, device="cuda", prod="bf16")
+    phases = WindowModel.from_oracle_weights(W, device="cuda", prod="bf16", tensor_cores=False, row_clusters=False)
+    mine, theirs = tuple(dev(s) for s in start), tuple(dev(s) for s in start)
+    for half in range(2):
+        cut = slice(half * T, (half + 1) * T)
+        args = tuple(dev(np.ascontiguousarray(a[:, cut])) for a in (z, ctx, scalars, reset))
+        got = window_forward(rows, *args, mine, record=False, tape_state=False)
+        assert int(got["status"]) == 0
+        forced = (got["sel_cell_idx"], got["sel_unit_idx"], got["sel_valid"])
+        want = window_forward(phases, *args, theirs, record=False, tape_state=False, forced=forced)
+        for name, g, w in (("h", mine[0], theirs[0]), ("q", mine[1], theirs[1]), ("qs", got["qs"], want["qs"]),
+                           ("hsel", got["tape_hsel"], want["tape_hsel"])):  # fmt: skip
+            scale = max(1e-3, float(w.abs().max()))
+            diff = (g - w).abs().flatten()
+            assert float(diff.max()) <= 2e-2 * scale, (half, name)
+            assert float(torch.quantile(diff.float(), 0.999)) <= 5e-3 * scale, (half, name)
+        assert torch.equal(mine[2], theirs[2]) and torch.equal(mine[3], theirs[3])
+
+
 def test_reverse_sweep_with_bf16_products_stays_within_bf16_tolerance() -> None:
     """The reverse sweep with bf16 products (tensor cores) against the sweep with fp32 products on
     the same weights and record: 2e-2 of the scale."""
