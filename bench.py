@@ -40,12 +40,16 @@ CONFIGS = {
     "c4": dict(B=32, T=1024, N=4096, d=128, K=16, H=1024, M=8, D=4, S=9, p=1 / 1024, prod="bf16", resident=True),
     "c5": dict(B=512, T=32, N=1024, d=64, K=8, H=512, M=8, D=4, S=9, p=1 / 4096, prod="bf16", resident=True,
                forward_only=True),
+    # the same streams token by token: one hsnw_stream_step, then hsnw_stream_continue per position
+    "c5s": dict(B=512, T=32, N=1024, d=64, K=8, H=512, M=8, D=4, S=9, p=1 / 4096, prod="bf16", resident=True,
+                forward_only=True, stream=True),
 }
 WORKLOADS = {
     "c1": "tiny gradcheck-shape window B2 T8 N16 d32 K2 H32",
     "c2": "reference-shape window fwd+bwd: B32 T256 N256 d64 K8 H512 M8 D4, bf16 products, fp32 state, resets p=1/1024",
     "c3": "one window of the split-window chain: B64 T512 N512 d64 K8 H512, bf16 products",
     "c4": "scaled sparse routing, one GPU's 32 rows of B256: T1024 N4096 d128 K16 H1024, resident state, fwd+bwd",
+    "c5s": "streaming token by token, one GPU's 512 streams of 4096: N1024 d64 K8 H512, one call per position (32 calls a step), derived values carried",
     "c5": "streaming, one GPU's 512 streams of 4096: N1024 d64 K8 H512, forward only on a resident state, 32 steps a call",
 }
 
@@ -261,7 +265,17 @@ def run_resident(args, c: dict, name: str) -> None:
     out: dict = {}
     bw_scratch = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
+    per_position = [tuple(a[:, t].contiguous() for a in (z, ctx, scalars, reset)) for t in range(T)] if c.get("stream") else []
+    calls = [0]
+
     def step():
+        if per_position:
+            from hsn_b200.window import stream_step
+
+            for now in per_position:
+                stream_step(model, *now, state, out=out, carried=calls[0] > 0)
+                calls[0] += 1
+            return
         tape = window_forward(model, z, ctx, scalars, reset, state, record=not forward_only, tape_state=False, out=out)
         if forward_only:
             return

@@ -93,6 +93,7 @@ SYMBOLS: dict[str, tuple[object, list[object]]] = {
     "hsnw_forward_scratch_bytes": (c_int64, [POINTER(HsnwModel), c_int32, c_int32]),
     "hsnw_window_forward": (c_int, [POINTER(HsnwModel), POINTER(HsnwForward), c_void_p]),
     "hsnw_stream_step": (c_int, [POINTER(HsnwModel), POINTER(HsnwForward), c_void_p]),
+    "hsnw_stream_continue": (c_int, [POINTER(HsnwModel), POINTER(HsnwForward), c_void_p]),
     "hsnw_backward_scratch_bytes": (c_int64, [POINTER(HsnwModel), c_int32, c_int32]),
     "hsnw_window_backward": (c_int, [POINTER(HsnwModel), POINTER(HsnwBackward), c_void_p]),
     "hsnw_static_scratch_bytes": (c_int64, []),

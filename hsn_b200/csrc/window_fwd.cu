@@ -69,6 +69,7 @@ struct FwdCtx {
     int n_front; // blocks of k_front that run the front (the rest copy the state tape)
     int copy_per_row;
     int stage_cells;    // 1: the row phase stages the per-cell logit parts and scalars in shared memory
+    int carried;        // 1: the derived state in the scratch is current (a resident state's next call)
     int* status;        // [1] 0, or 1 when a bounded wait ran out
     unsigned long long* trace;  // phase timestamps (HSNW_TRACE builds)
     float* pre_s;       // [B*T, H]
@@ -130,6 +131,7 @@ __global__ void __launch_bounds__(256) k_init(FwdCtx c) {
     const bool cut = c.io.reset[static_cast<int64_t>(row) * T] != 0;
     float* h0 = c.io.h0 + static_cast<int64_t>(row) * N * d;
     if (row == 0 && blockIdx.y == 0 && tid == 0) *c.status = 0;
+    if (c.carried && !cut) return;   // the previous call on this state left every cell's derived values
     for (int e = tid; e < d * M; e += nt) swh[e] = c.m.score_w_t[2 * d * M + e];
     for (int e = tid; e < d * d; e += nt) vt[e] = c.m.v_t[e];
     for (int e = tid; e < ncell * d; e += nt) {
@@ -1228,7 +1230,8 @@ extern "C" int hsnw_front_projection(const HsnwModel* model, const float* z, con
     return hsnw_check_launch("front_projection");
 }
 
-static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* stream_) {
+static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* stream_, bool phases = false,
+                        bool carried = false) {
     if (int rc = hsnw_require_prepared()) return rc;
     if (int rc = check_model(model)) return rc;
     if (!io || io->B < 1 || io->T < 1) return hsnw_fail(HSNW_E_ARG, "window_forward: B and T must be positive");
@@ -1256,6 +1259,7 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
     const int B = io->B, T = io->T;
     c.n_front = 2 * c.nF * ((B + kFR - 1) / kFR);
     c.stage_cells = stage_cells(*model) ? 1 : 0;
+    c.carried = carried ? 1 : 0;
     c.copy_per_row = io->tape_state ? (model->N * model->d + kCopyFloats - 1) / kCopyFloats : 0;
     unsigned char* base = static_cast<unsigned char*>(io->scratch);
     c.status = reinterpret_cast<int*>(base + L.status);
@@ -1270,13 +1274,15 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
     c.lh = reinterpret_cast<float*>(base + L.lh);
     c.vh = reinterpret_cast<float*>(base + L.vh);
     c.cmax = reinterpret_cast<int*>(base + L.cmax);
-    if (!model->phases_only && model->rows_bank) {
+    bool pre_done = false;   // the window-invariant front product is the same for both kernel families
+    if (!phases && !model->phases_only && model->rows_bank) {
         // one persistent cluster per row when the shape fits (window_rows.cu)
         if (cudaMemsetAsync(c.status, 0, sizeof(int), stream) != cudaSuccess) return hsnw_check_launch("window_forward");
         g_pre_status = c.status;
         const int rc_pre = hsnw_front_projection(model, io->z, io->ctx, static_cast<int64_t>(B) * T, c.pre_s, stream);
         g_pre_status = nullptr;
         if (rc_pre) return rc_pre;
+        pre_done = true;
         const int rc_rows = hsnw_rows_forward(model, io, c.pre_s, c.status, stream);
         if (rc_rows >= 0) return rc_rows;
     }
@@ -1284,10 +1290,12 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
     const dim3 init_grid(B, (model->N + kInitCells - 1) / kInitCells);
     hsnw_profile_mark(HSNW_K_INIT, stream);
     k_init<<<init_grid, 256, init_shared(*model), stream>>>(c);
-    g_pre_status = c.status;
-    const int rc_pre = hsnw_front_projection(model, io->z, io->ctx, static_cast<int64_t>(B) * T, c.pre_s, stream);
-    g_pre_status = nullptr;
-    if (rc_pre) return rc_pre;
+    if (!pre_done) {
+        g_pre_status = c.status;
+        const int rc_pre = hsnw_front_projection(model, io->z, io->ctx, static_cast<int64_t>(B) * T, c.pre_s, stream);
+        g_pre_status = nullptr;
+        if (rc_pre) return rc_pre;
+    }
     const int front_grid = c.n_front + B * c.copy_per_row;
     const int pair_tile = unit_tc ? kTcPairTile : kPairTile;
     const dim3 unit_grid(model->M * (unit_tc ? c.nU + 1 : c.nU + c.nG), (B * model->K + pair_tile - 1) / pair_tile);
@@ -1315,7 +1323,13 @@ extern "C" int hsnw_window_forward(const HsnwModel* model, const HsnwForward* io
 extern "C" int hsnw_stream_step(const HsnwModel* model, const HsnwForward* io, void* stream) {
     if (io && (io->T != 1 || io->tape_state))
         return hsnw_fail(HSNW_E_ARG, "stream_step: one position on a resident state (T = 1, tape_state = 0)");
-    return forward_impl(model, io, stream);
+    return forward_impl(model, io, stream, true);
+}
+
+extern "C" int hsnw_stream_continue(const HsnwModel* model, const HsnwForward* io, void* stream) {
+    if (io && io->tape_state)
+        return hsnw_fail(HSNW_E_ARG, "stream_continue: a resident state (tape_state = 0)");
+    return forward_impl(model, io, stream, true, true);
 }
 
 void hsnw_forward_set_attributes() {

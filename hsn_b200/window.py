@@ -298,6 +298,7 @@ def window_forward(
     want_logits: bool = False,
     scratch: Tensor | None = None,
     out: dict[str, Tensor] | None = None,
+    _entry: str = "hsnw_window_forward",
 ) -> dict[str, Tensor]:
     """The forward sweep of one window (``hsnw_window_forward``): the reference's tape
     (``python/hsn/train/compile.py:1196-1213``) for ``z [B,T,d]``, ``ctx [B,T,dc]``, ``scalars
@@ -366,7 +367,7 @@ def window_forward(
         raise ValueError(f"scratch must hold {need} bytes on {dev}")
     io.scratch, io.scratch_bytes = scratch.data_ptr(), scratch.numel()
     with torch.cuda.device(dev):
-        _lib.check(lib.hsnw_window_forward(ctypes.byref(model.struct), ctypes.byref(io), _stream(dev)))
+        _lib.check(getattr(lib, _entry)(ctypes.byref(model.struct), ctypes.byref(io), _stream(dev)))
     if tape_state:
         o["tape_h"], o["tape_q"], o["tape_age"] = o["_tape_h"][:, :T], o["_tape_q"][:, :T], o["_tape_age"][:, :T]
         o["h"], o["q"], o["age"] = o["_tape_h"][:, T], o["_tape_q"][:, T], o["_tape_age"][:, T]
@@ -390,14 +391,23 @@ def stream_step(
     state: tuple[Tensor, Tensor, Tensor, Tensor],
     *,
     out: dict[str, Tensor] | None = None,
+    carried: bool = False,
 ) -> dict[str, Tensor]:
     """One position on a resident state, updated in place (``hsnw_stream_step``): the serving
     step's state update (``python/hsn/train/compile.py:1913-2006``). ``z_t [B,d]``, ``ctx_t
     [B,dc]``, ``scalars_t [B,N,S]``, ``reset_t [B]`` bool. Returns the decision and the slots'
-    states (``sel_*``, ``tape_hsel``, ``qs``) of the position."""
+    states (``sel_*``, ``tape_hsel``, ``qs``) of the position.
+
+    ``carried`` (``hsnw_stream_continue``): ``out`` is the result of the previous step on this
+    state (it holds the scratch with every cell's derived values), the weights are the same and
+    the state was not touched in between; the step then skips the pass over the whole state that
+    recomputes them."""
+    if carried and (out is None or "_scratch" not in out):
+        raise ValueError("a carried step needs the previous step's result as `out`")
     return window_forward(
         model, z_t[:, None], ctx_t[:, None], scalars_t[:, None], reset_t[:, None], state,
         record=False, tape_state=False, out=out,
+        _entry="hsnw_stream_continue" if carried else "hsnw_stream_step",
     )  # fmt: skip
 
 

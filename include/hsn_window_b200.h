@@ -202,8 +202,17 @@ int64_t hsnw_forward_scratch_bytes(const HsnwModel* model, int32_t B, int32_t T)
  * router's decision, the gather of the selected cells and their messages, the executed unit,
  * the gated update with write-back and the next position's reset. */
 int hsnw_window_forward(const HsnwModel* model, const HsnwForward* io, void* stream);
-/* One position on a resident state: hsnw_window_forward with T = 1, tape_state = 0. */
+/* One position on a resident state: hsnw_window_forward with T = 1, tape_state = 0, always by the
+ * batch-synchronous kernels, which leave every cell's derived values (its part of the scorer's
+ * logits, V h, max |h|) in io->scratch. */
 int hsnw_stream_step(const HsnwModel* model, const HsnwForward* io, void* stream);
+/* The next call on the same resident state: like hsnw_stream_step (any T, tape_state = 0), but the
+ * derived values are taken from io->scratch instead of being recomputed from the whole state (at
+ * 512 streams of 1024 cells that recomputation is five times the step). The caller guarantees:
+ * the same model weights, B, T and scratch as the previous hsnw_stream_step / hsnw_stream_continue
+ * on this state, and h0 / q0 / age0 untouched in between. A stream whose reset[:,0] is set starts
+ * from zeros as usual. */
+int hsnw_stream_continue(const HsnwModel* model, const HsnwForward* io, void* stream);
 
 /* The reverse sweep of one window (state_gradient.py:357-485; full_cut != 0: split.py:128-174).
  * A [B,N,d] and R [B,d] are in/out: on entry the cotangent of the state after the last position

@@ -309,6 +309,42 @@ def test_stream_step_updates_a_resident_state_in_place() -> None:
     assert alive.sum() >= B - 1
 
 
+@pytest.mark.parametrize("prod", ["fp32", "bf16"])
+def test_carried_stream_steps_equal_one_resident_window(prod: str) -> None:
+    """Serving steps that carry the cells' derived values from step to step (no pass over the whole
+    state after the first) against the same positions as one resident window of the batch-synchronous
+    kernels: the same arithmetic, so to the bit, resets included; and against steps that recompute
+    the derived values every time."""
+    from hsn_b200.window import WindowModel, stream_step, window_forward
+
+    rng = np.random.default_rng(31)
+    B, steps, N, d, K = 7, 6, 1024, 64, 8
+    W, z, ctx, scalars, reset, state = _synthetic(rng, B, steps, N, d, K, 512, 8, 4, 0.25, age_max=64)
+    reset[:, 0] = rng.random(B) < 0.3
+    h = (rng.standard_normal((B, N, d)) * 0.3).astype(np.float32)
+    start = (h, h.mean(axis=1), rng.integers(0, 200, (B, N)), np.arange(B, dtype=np.int64))
+    model = WindowModel.from_oracle_weights(W, device="cuda", prod=prod, row_clusters=False)
+    args = tuple(dev(a) for a in (z, ctx, scalars, reset))
+    whole = tuple(dev(s) for s in start)
+    want = window_forward(model, *args, whole, record=False, tape_state=False)
+    carried, fresh = tuple(dev(s) for s in start), tuple(dev(s) for s in start)
+    out = None
+    for t in range(steps):
+        now = tuple(a[:, t].contiguous() for a in args)
+        out = stream_step(model, *now, carried, out=out, carried=t > 0)
+        assert int(out["status"]) == 0
+        for key in ("sel_cell_idx", "sel_unit_idx", "sel_valid", "qs", "tape_hsel"):
+            assert torch.equal(out[key][:, 0], want[key][:, t]), (t, key)
+        other = stream_step(model, *now, fresh)
+        assert torch.equal(other["sel_cell_idx"], out["sel_cell_idx"])
+        torch.testing.assert_close(other["qs"], out["qs"], rtol=1e-5, atol=1e-6)
+    for got, ref in zip(carried, whole):
+        assert torch.equal(got, ref)
+    torch.testing.assert_close(fresh[0], whole[0], rtol=1e-5, atol=1e-6)
+    with pytest.raises(ValueError):
+        stream_step(model, *now, carried, carried=True)
+
+
 def test_full_size_window_properties() -> None:
     """The benchmark's configuration 2 (B32 T256 N256 d64 K8 H512, bf16 products) at full size:
     size-independent properties. Two runs are bitwise equal (fixed reduction orders, no atomics);
