@@ -77,6 +77,11 @@ size_t hsnw_max_shared() {
     return (device >= 0 && device < kMaxDevices) ? devices[device].max_shared : 0;
 }
 
+int hsnw_sm_count_current() {
+    const int device = current_device();
+    return (device >= 0 && device < kMaxDevices) ? devices[device].sm_count : 0;
+}
+
 int hsnw_check_launch(const char* what) {
     const cudaError_t status = cudaPeekAtLastError();
     if (status == cudaSuccess) return HSNW_OK;

@@ -10,6 +10,8 @@ int hsnw_fail(int code, const char* message);
 int hsnw_require_prepared();
 // The largest dynamic shared memory a block may take on the current (prepared) device.
 size_t hsnw_max_shared();
+// The number of SMs of the current (prepared) device, 0 when it is not prepared.
+int hsnw_sm_count_current();
 // cudaPeekAtLastError after a launch sequence: HSNW_OK or HSNW_E_CUDA with the runtime's message.
 int hsnw_check_launch(const char* what);
 // Opt `kernel` in to the largest dynamic shared memory its static shared memory leaves room for.

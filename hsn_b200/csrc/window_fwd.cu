@@ -70,6 +70,7 @@ struct FwdCtx {
     int copy_per_row;
     int stage_cells;    // 1: the row phase stages the per-cell logit parts and scalars in shared memory
     int carried;        // 1: the derived state in the scratch is current (a resident state's next call)
+    int pair_tile;      // pairs a tensor-core unit block scans for its unit's
     int* status;        // [1] 0, or 1 when a bounded wait ran out
     unsigned long long* trace;  // phase timestamps (HSNW_TRACE builds)
     float* pre_s;       // [B*T, H]
@@ -779,6 +780,7 @@ __global__ void __launch_bounds__(256) k_unit(FwdCtx c, int t) {
 constexpr int kTP = 32;       // pairs of a tensor-core batch
 constexpr int kTcPairTile = 64;  // pairs a tensor-core unit block scans: small tiles keep a popular
                                  // unit's pairs spread over several blocks
+constexpr int kTcPairTileBig = 512;  // with thousands of pairs: about 64 pairs of the unit per weight tile loaded
 
 __global__ void __launch_bounds__(256) k_unit_tc(FwdCtx c, int t) {
     extern __shared__ __align__(16) unsigned char dyn[];
@@ -797,29 +799,31 @@ __global__ void __launch_bounds__(256) k_unit_tc(FwdCtx c, int t) {
     uint4* A2 = A1 + planes * 128;                             // [16][128]
     uint4* B1 = A2 + 16 * 128;                                 // [planes][32]
     uint4* B2 = B1 + planes * kTP;                             // [16][32]
-    int* list = reinterpret_cast<int*>(B2 + 16 * kTP);         // [64]
-    const int p0 = blockIdx.y * kTcPairTile;
+    int* list = reinterpret_cast<int*>(B2 + 16 * kTP);         // [pair_tile]
+    const int p0 = blockIdx.y * c.pair_tile;
     HSNW_MARK(0, 11);
-    {
-        const int p = p0 + tid;
-        const bool mine = tid < kTcPairTile && p < P && c.pair_unit[p] == j;
+    if (tid == 0) {
+        mbar_init(&bar_w, 1);
+        mbar_init(&bar_m, 1);
+        n_list = 0;
+    }
+    for (int first = 0; first < c.pair_tile; first += 256) {   // the tile's pairs of unit j, in their order
+        const int p = p0 + first + tid;
+        const bool mine = first + tid < c.pair_tile && p < P && c.pair_unit[p] == j;
         const unsigned mask = __ballot_sync(0xffffffffu, mine);
         if (lane == 0) warp_count[warp] = __popc(mask);
-        if (tid == 0) {
-            mbar_init(&bar_w, 1);
-            mbar_init(&bar_m, 1);
-        }
         __syncthreads();
-        int before = 0;
+        int before = n_list, total = 0;
         for (int w = 0; w < warp; ++w) before += warp_count[w];
-        if (mine) list[before + __popc(mask & ((1u << lane) - 1u))] = p;
         if (tid == 0) {
-            int total = 0;
+            total = before;
             for (int w = 0; w < 8; ++w) total += warp_count[w];
-            n_list = total;
         }
-        __syncthreads();
+        if (mine) list[before + __popc(mask & ((1u << lane) - 1u))] = p;
+        __syncthreads();   // every read of the counts and of n_list is done
+        if (tid == 0) n_list = total;
     }
+    __syncthreads();
     const int count = n_list;
     HSNW_MARK(0, 0);
     if (count == 0) return;
@@ -1157,15 +1161,22 @@ Layout layout(const HsnwModel& m, int B, int T) {
 
 int row_threads(const HsnwModel& m) { return m.N > 512 ? 512 : 256; }
 // the per-cell logit parts and scalars of a row are staged in shared memory while they are small
-bool stage_cells(const HsnwModel& m) { return sizeof(float) * static_cast<size_t>(m.N) * (m.M + m.S) <= 96 * 1024; }
+bool stage_cells_fit(const HsnwModel& m) { return sizeof(float) * static_cast<size_t>(m.N) * (m.M + m.S) <= 96 * 1024; }
 
-size_t row_shared(const HsnwModel& m) {
+size_t row_shared(const HsnwModel& m, bool staged) {
     const int d = m.d, K = m.K, D = m.D, N = m.N, nF2 = 2 * ((m.H + kFS - 1) / kFS);
-    const size_t cells = stage_cells(m) ? static_cast<size_t>(pad4(N * m.M)) + pad4(N * m.S) : 0;
+    const size_t cells = staged ? static_cast<size_t>(pad4(N * m.M)) + pad4(N * m.S) : 0;
     const size_t words = static_cast<size_t>(pad4(nF2 * d)) + cells + pad4(2 * N) + pad4(N)
         + static_cast<size_t>(K + K * D) * d + static_cast<size_t>(K) * d + pad4(2 * d * m.M) + pad4((1 + m.S) * m.M)
         + 2 * static_cast<size_t>(pad4(N)) + 2 * d + kMaxM + 2 * static_cast<size_t>(pad4(K * D)) + K;
     return sizeof(float) * words;
+}
+// Staging saves a second pass over memory when a row's block has the SM to itself; with more rows
+// than SMs the blocks' residency matters more: then stage only if two blocks still fit an SM.
+bool stage_cells(const HsnwModel& m, int B) {
+    if (!stage_cells_fit(m)) return false;
+    const int sms = hsnw_sm_count_current();
+    return !(sms > 0 && B > sms && 2 * (row_shared(m, true) + 2048) > hsnw_max_shared());
 }
 size_t init_shared(const HsnwModel& m) {
     return sizeof(float) * (static_cast<size_t>(2 * kInitCells) * m.d + static_cast<size_t>(m.d) * m.M + static_cast<size_t>(m.d) * m.d);
@@ -1179,7 +1190,7 @@ size_t unit_shared(const HsnwModel& m) {
 }
 size_t unit_tc_shared(const HsnwModel& m) {
     const size_t planes = static_cast<size_t>(4 * m.d) / 8;
-    return 16 * (planes * 128 + 16 * 128 + planes * kTP + 16 * kTP) + sizeof(int) * kPairTile;
+    return 16 * (planes * 128 + 16 * 128 + planes * kTP + 16 * kTP) + sizeof(int) * kTcPairTileBig;
 }
 size_t update_shared(const HsnwModel& m) {
     return sizeof(float) * (4 * static_cast<size_t>(m.K) * m.d + 2 * static_cast<size_t>(m.d) * m.d + pad4(m.d * m.M) + 2 * m.K);
@@ -1193,7 +1204,7 @@ int check_model(const HsnwModel* m) {
     if (m->M > kMaxM) return hsnw_fail(HSNW_E_UNSUPPORTED, "window: at most 16 units (M)");
     if (m->K > kMaxSlots) return hsnw_fail(HSNW_E_UNSUPPORTED, "window: at most 64 slots (K)");
     const size_t cap = hsnw_max_shared() - 4096;  // room for the kernels' static shared memory
-    if (row_shared(*m) > cap || front_shared(*m) > cap || unit_shared(*m) > cap || update_shared(*m) > cap
+    if (row_shared(*m, false) > cap || front_shared(*m) > cap || unit_shared(*m) > cap || update_shared(*m) > cap
         || init_shared(*m) > cap)
         return hsnw_fail(HSNW_E_UNSUPPORTED, "window: a phase's working set exceeds a block's shared memory");
     return HSNW_OK;
@@ -1258,7 +1269,7 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
     c.nG = (model->d + kUS - 1) / kUS;
     const int B = io->B, T = io->T;
     c.n_front = 2 * c.nF * ((B + kFR - 1) / kFR);
-    c.stage_cells = stage_cells(*model) ? 1 : 0;
+    c.stage_cells = stage_cells(*model, io->B) ? 1 : 0;
     c.carried = carried ? 1 : 0;
     c.copy_per_row = io->tape_state ? (model->N * model->d + kCopyFloats - 1) / kCopyFloats : 0;
     unsigned char* base = static_cast<unsigned char*>(io->scratch);
@@ -1297,9 +1308,10 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
         if (rc_pre) return rc_pre;
     }
     const int front_grid = c.n_front + B * c.copy_per_row;
-    const int pair_tile = unit_tc ? kTcPairTile : kPairTile;
+    c.pair_tile = B * model->K > 1024 ? kTcPairTileBig : kTcPairTile;
+    const int pair_tile = unit_tc ? c.pair_tile : kPairTile;
     const dim3 unit_grid(model->M * (unit_tc ? c.nU + 1 : c.nU + c.nG), (B * model->K + pair_tile - 1) / pair_tile);
-    const size_t sh_front = front_shared(*model), sh_row = row_shared(*model);
+    const size_t sh_front = front_shared(*model), sh_row = row_shared(*model, c.stage_cells != 0);
     const size_t sh_unit = unit_shared(*model), sh_update = update_shared(*model), sh_unit_tc = unit_tc_shared(*model);
     for (int t = 0; t < T; ++t) {
         hsnw_profile_mark(HSNW_K_FRONT, stream);
