@@ -50,7 +50,7 @@ WORKLOADS = {
     "c3": "one window of the split-window chain: B64 T512 N512 d64 K8 H512, bf16 products",
     "c4": "scaled sparse routing, one GPU's 32 rows of B256: T1024 N4096 d128 K16 H1024, resident state, fwd+bwd",
     "c5s": "streaming token by token, one GPU's 512 streams of 4096: N1024 d64 K8 H512, one call per position (32 calls a step), derived values carried",
-    "c5": "streaming, one GPU's 512 streams of 4096: N1024 d64 K8 H512, forward only on a resident state, 32 steps a call",
+    "c5": "streaming, one GPU's 512 streams of 4096: N1024 d64 K8 H512, forward only on a resident state, 32 steps a call, each call continuing the last",
 }
 
 
@@ -276,7 +276,10 @@ def run_resident(args, c: dict, name: str) -> None:
                 stream_step(model, *now, state, out=out, carried=calls[0] > 0)
                 calls[0] += 1
             return
-        tape = window_forward(model, z, ctx, scalars, reset, state, record=not forward_only, tape_state=False, out=out)
+        # a stream's next chunk continues the resident state: the cells' derived values carry over
+        tape = window_forward(model, z, ctx, scalars, reset, state, record=not forward_only, tape_state=False, out=out,
+                              carried=forward_only and calls[0] > 0)
+        calls[0] += 1
         if forward_only:
             return
         rec = {k: tape["rec_" + k] for k in ("y", "hidden", "gate_pre", "m", "rms")}

@@ -385,6 +385,79 @@ __global__ void __launch_bounds__(256) k_front(FwdCtx c, int t) {
     }
 }
 
+// The scorer on a row's cells, a thread per cell: logits = the cell's derived part + the age term +
+// the scalars' terms (in that order) + the row's term + the bias, rounded; the cell's score is its
+// best logit (less the unit's cost) and its unit the first maximiser. MM bounds the units (8 or
+// 16), so a model of eight units issues no idle lanes of a sixteen-wide loop; the scalars go four
+// at a time under a uniform branch for the same reason.
+template <int MM>
+__device__ __forceinline__ void score_cells(const FwdCtx& c, int64_t rt, const float* lh, const float* scal,
+                                            const int64_t* age, const float* sw_tail, const float* rowterm,
+                                            const float* score_b, const float* cost, float* score, int* unit) {
+    const int N = c.m.N, M = c.m.M, Sn = c.m.S;
+    const bool bf = c.m.prod_bf16 != 0;
+    const float lambda = c.m.lambda_cost;
+    const float age_div = static_cast<float>(c.m.age_max);
+    const bool wide = (M & 3) == 0;   // the weights' rows are then 16-byte aligned
+    for (int i = threadIdx.x; i < N; i += blockDim.x) {
+        float acc[MM];
+        if (wide) {
+#pragma unroll
+            for (int j = 0; j < MM; j += 4) {
+                if (j < M) {
+                    const float4 v = *reinterpret_cast<const float4*>(lh + static_cast<int64_t>(i) * M + j);
+                    acc[j] = v.x; acc[j + 1] = v.y; acc[j + 2] = v.z; acc[j + 3] = v.w;
+                } else {
+                    acc[j] = acc[j + 1] = acc[j + 2] = acc[j + 3] = 0.0f;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < MM; ++j) acc[j] = j < M ? lh[static_cast<int64_t>(i) * M + j] : 0.0f;
+        }
+        auto add_term = [&](float a, const float* w) {
+            if (wide) {
+#pragma unroll
+                for (int j = 0; j < MM; j += 4) {
+                    if (j < M) {
+                        const float4 wv = *reinterpret_cast<const float4*>(w + j);
+                        acc[j] += a * wv.x; acc[j + 1] += a * wv.y; acc[j + 2] += a * wv.z; acc[j + 3] += a * wv.w;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < MM; ++j)
+                    if (j < M) acc[j] += a * w[j];
+            }
+        };
+        add_term(maybe_bf16(static_cast<float>(age[i]) / age_div, bf), sw_tail);
+        for (int s0 = 0; s0 < Sn; s0 += 4) {   // four scalars at a time, their loads in flight together
+            float feat[4];
+#pragma unroll
+            for (int s = 0; s < 4; ++s) feat[s] = s0 + s < Sn ? scal[static_cast<int64_t>(i) * Sn + s0 + s] : 0.0f;
+#pragma unroll
+            for (int s = 0; s < 4; ++s)
+                if (s0 + s < Sn) add_term(maybe_bf16(feat[s], bf), sw_tail + (1 + s0 + s) * M);
+        }
+        float best = -INFINITY;
+        int arg = 0;
+#pragma unroll
+        for (int j = 0; j < MM; ++j) {
+            if (j < M) {
+                const float logit = maybe_bf16(acc[j] + rowterm[j] + score_b[j], bf);
+                if (c.io.logits) c.io.logits[(rt * N + i) * M + j] = logit;
+                const float sc = lambda > 0.0f ? __fsub_rn(logit, __fmul_rn(lambda, cost[j])) : logit;
+                if (j == 0 || sc > best) {
+                    best = sc;
+                    arg = j;
+                }
+            }
+        }
+        score[i] = best;
+        unit[i] = arg;
+    }
+}
+
 // ------------------------------------------------------------------------------------------------
 // row: one block per row. Everything the position reads of the row arrives in two stagings, each
 // one round trip to memory: (1) the front's partial sums, the derived logit parts of every cell,
@@ -393,7 +466,7 @@ __global__ void __launch_bounds__(256) k_front(FwdCtx c, int t) {
 // rows and the K D message sources' V h rows, one bulk copy per row.
 // Shared (dynamic), each segment padded to 16 bytes: pf [2 nF d], lh [N M], scal [N S], age [N] i64,
 // cmax [N], rows [(K + K D) d], msg [K d], sw_head [2d M], sw_tail [(1+S) M], score [N], unit [N],
-// ue [2d], rowterm [16], src [K D], ew [K D], rms [K].
+// ue [2d], rowterm [16], score_b [16], src [K D], ew [K D], rms [K].
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
     extern __shared__ __align__(16) unsigned char dyn[];
@@ -420,7 +493,8 @@ __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
     int* unit = reinterpret_cast<int*>(score + pad4(N));
     float* ue = reinterpret_cast<float*>(unit + pad4(N));
     float* rowterm = ue + 2 * d;
-    int* src = reinterpret_cast<int*>(rowterm + kMaxM);
+    float* score_b_s = rowterm + kMaxM;
+    int* src = reinterpret_cast<int*>(score_b_s + kMaxM);
     float* ew = reinterpret_cast<float*>(src + pad4(K * D));
     float* rms = ew + pad4(K * D);
     const int64_t rt = static_cast<int64_t>(row) * T + t;
@@ -464,7 +538,10 @@ __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
         cp_async_floats(sw_head, c.m.score_w_t, 2 * d * M);
         cp_async_floats(sw_tail, c.m.score_w_t + static_cast<int64_t>(3 * d) * M, (1 + Sn) * M);
         cp_async_commit();
-        for (int j = tid; j < M; j += nt) S.cost[j] = c.m.cost[j];
+        for (int j = tid; j < M; j += nt) {
+            S.cost[j] = c.m.cost[j];
+            score_b_s[j] = c.m.score_b[j];
+        }
         cp_async_wait_all();
         mbar_wait(&bar, 0, c.status);
     }
@@ -490,42 +567,8 @@ __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
     // the scorer: a thread per cell; the state's part of the logits is derived state
     const float* lh = staged ? lh_s : c.lh + static_cast<int64_t>(row) * N * M;
     const float* scal = staged ? scal_s : c.io.scalars + rt * N * Sn;
-    const float lambda = c.m.lambda_cost;
-    const float age_div = static_cast<float>(c.m.age_max);
-    for (int i = tid; i < N; i += nt) {
-        float acc[kMaxM];
-#pragma unroll
-        for (int j = 0; j < kMaxM; ++j) acc[j] = j < M ? lh[i * M + j] : 0.0f;
-        {
-            const float a = maybe_bf16(static_cast<float>(age[i]) / age_div, bf);
-#pragma unroll
-            for (int j = 0; j < kMaxM; ++j)
-                if (j < M) acc[j] += a * sw_tail[j];
-        }
-        for (int s = 0; s < Sn; ++s) {
-            const float a = maybe_bf16(scal[i * Sn + s], bf);
-            const float* w = sw_tail + (1 + s) * M;
-#pragma unroll
-            for (int j = 0; j < kMaxM; ++j)
-                if (j < M) acc[j] += a * w[j];
-        }
-        float best = -INFINITY;
-        int arg = 0;
-#pragma unroll
-        for (int j = 0; j < kMaxM; ++j) {
-            if (j < M) {
-                const float logit = maybe_bf16(acc[j] + rowterm[j] + c.m.score_b[j], bf);
-                if (c.io.logits) c.io.logits[(rt * N + i) * M + j] = logit;
-                const float sc = lambda > 0.0f ? __fsub_rn(logit, __fmul_rn(lambda, S.cost[j])) : logit;
-                if (j == 0 || sc > best) {
-                    best = sc;
-                    arg = j;
-                }
-            }
-        }
-        score[i] = best;
-        unit[i] = arg;
-    }
+    if (M <= 8) score_cells<8>(c, rt, lh, scal, age, sw_tail, rowterm, score_b_s, S.cost, score, unit);
+    else score_cells<kMaxM>(c, rt, lh, scal, age, sw_tail, rowterm, score_b_s, S.cost, score, unit);
     __syncthreads();
     int64_t* cells_o = c.io.cells + rt * K;
     int64_t* units_o = c.io.units + rt * K;
@@ -536,7 +579,15 @@ __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
         P.N = N; P.M = M; P.K = K; P.age_max = c.m.age_max; P.probes = c.m.probes;
         P.reserved = 0; P.fixed_units = 0;
         P.overhead = c.m.cell_overhead; P.shared_cost = c.m.shared_cost; P.limit = c.m.limit;
-        if (N <= 2048) {  // one warp decides; the others wait at the barrier
+        uint64_t* cand = reinterpret_cast<uint64_t*>(rows);   // [warps][K + 1]: the rows arrive after the decision
+        const bool cand_fits = sizeof(uint64_t) * warps * (K + 1) <= sizeof(float) * nrows * d;
+        if (N > 256 && N <= 2048 && cand_fits) {
+            // every warp reduces its cells to its K + 1 best keys, one warp merges them and finishes
+            select_candidates_warp(N, K, score, cand + warp * (K + 1), warp * 32, nt);
+            __syncthreads();
+            if (warp == 0) select_merge_warp(P, score, unit, age, cand, warps * (K + 1), S);
+            __syncthreads();
+        } else if (N <= 2048) {  // one warp decides; the others wait at the barrier
             if (warp == 0) select_row_warp(P, score, unit, age, S);
             __syncthreads();
         } else {
@@ -774,17 +825,18 @@ __global__ void __launch_bounds__(256) k_unit(FwdCtx c, int t) {
 //   epilogue 2: the block's partial sum of the unit's output.
 // The weight tiles are bf16 images made on the host in the operand layout (umma.cuh) and arrive by
 // one bulk copy each; the pairs' inputs are converted and laid out while they are staged.
-// 256 threads: warp w reads TMEM lanes 32 (w % 4) .. +31 and the pairs 16 (w / 4) .. +15.
+// 512 threads: warp w reads TMEM lanes 32 (w % 4) .. +31 and the pairs 8 (w / 4) .. +7.
 // Shared (dynamic): A1 [4d/8][128][8], A2 [16][128][8], B1 [4d/8][32][8], B2 [16][32][8] bf16, list.
 // ------------------------------------------------------------------------------------------------
 constexpr int kTP = 32;       // pairs of a tensor-core batch
 constexpr int kTcPairTile = 64;  // pairs a tensor-core unit block scans: small tiles keep a popular
                                  // unit's pairs spread over several blocks
-constexpr int kTcPairTileBig = 512;  // with thousands of pairs: about 64 pairs of the unit per weight tile loaded
+constexpr int kUnitTcThreads = 512;  // 16 warps: warp w reads TMEM lanes 32 (w % 4) .. +31, pairs 8 (w / 4) .. +7
+constexpr int kTcPairTileMax = 4096; // with thousands of pairs the tile grows until the grid is one wave of blocks
 
-__global__ void __launch_bounds__(256) k_unit_tc(FwdCtx c, int t) {
+__global__ void __launch_bounds__(kUnitTcThreads) k_unit_tc(FwdCtx c, int t) {
     extern __shared__ __align__(16) unsigned char dyn[];
-    __shared__ int warp_count[8];
+    __shared__ int warp_count[kUnitTcThreads / 32];
     __shared__ int n_list;
     __shared__ __align__(8) uint64_t bar_w, bar_m;
     __shared__ uint32_t tmem_slot;
@@ -807,7 +859,7 @@ __global__ void __launch_bounds__(256) k_unit_tc(FwdCtx c, int t) {
         mbar_init(&bar_m, 1);
         n_list = 0;
     }
-    for (int first = 0; first < c.pair_tile; first += 256) {   // the tile's pairs of unit j, in their order
+    for (int first = 0; first < c.pair_tile; first += kUnitTcThreads) {   // the tile's pairs of unit j, in their order
         const int p = p0 + first + tid;
         const bool mine = first + tid < c.pair_tile && p < P && c.pair_unit[p] == j;
         const unsigned mask = __ballot_sync(0xffffffffu, mine);
@@ -817,7 +869,7 @@ __global__ void __launch_bounds__(256) k_unit_tc(FwdCtx c, int t) {
         for (int w = 0; w < warp; ++w) before += warp_count[w];
         if (tid == 0) {
             total = before;
-            for (int w = 0; w < 8; ++w) total += warp_count[w];
+            for (int w = 0; w < kUnitTcThreads / 32; ++w) total += warp_count[w];
         }
         if (mine) list[before + __popc(mask & ((1u << lane) - 1u))] = p;
         __syncthreads();   // every read of the counts and of n_list is done
@@ -853,27 +905,41 @@ __global__ void __launch_bounds__(256) k_unit_tc(FwdCtx c, int t) {
     uint32_t phase = 0;
     bool weights_in = false;
     const float4* v4 = reinterpret_cast<const float4*>(c.v);
+    // the lane's bias is the same for every batch: its load is off the batches' critical path
+    const bool col_ok = is_gate ? m < d : c0 + m < H;
+    const float bias = col_ok ? (is_gate ? c.m.gate_b[m] : c.m.b1[j * H + c0 + m]) : 0.0f;
     for (int base = 0; base < count; base += kTP) {
         const int nb = min(kTP, count - base);
         // the pairs' inputs as the B operand: a thread converts 8 values and stores one 16-byte unit
-        for (int idx = tid; idx < planes * kTP; idx += 256) {
-            const int n = idx & (kTP - 1), kc = idx >> 5;
-            uint4 packed = make_uint4(0u, 0u, 0u, 0u);
-            if (n < nb) {
-                const float4* src = v4 + static_cast<int64_t>(list[base + n]) * d + kc * 2;
-                const float4 lo = src[0], hi = src[1];
-                packed = make_uint4(pack_bf16x2(lo.x, lo.y), pack_bf16x2(lo.z, lo.w), pack_bf16x2(hi.x, hi.y),
-                                    pack_bf16x2(hi.z, hi.w));
+        // (four units a thread per round, their eight loads in flight together)
+        for (int idx0 = tid; idx0 < planes * kTP; idx0 += 4 * kUnitTcThreads) {
+            float4 lo[4], hi[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int idx = idx0 + u * kUnitTcThreads;
+                const int n = idx & (kTP - 1), kc = idx >> 5;
+                lo[u] = hi[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (idx < planes * kTP && n < nb) {
+                    const float4* src = v4 + static_cast<int64_t>(list[base + n]) * d + kc * 2;
+                    lo[u] = src[0];
+                    hi[u] = src[1];
+                }
             }
-            B1[idx] = packed;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int idx = idx0 + u * kUnitTcThreads;
+                if (idx < planes * kTP)
+                    B1[idx] = make_uint4(pack_bf16x2(lo[u].x, lo[u].y), pack_bf16x2(lo[u].z, lo[u].w),
+                                         pack_bf16x2(hi[u].x, hi[u].y), pack_bf16x2(hi[u].z, hi[u].w));
+            }
         }
         fence_async_smem();
-        HSNW_MARK(0, 1);
+        if (base == 0) HSNW_MARK(0, 1);
         if (!weights_in) {
             mbar_wait(&bar_w, 0, c.status);
             weights_in = true;
         }
-        HSNW_MARK(0, 2);
+        if (base == 0) HSNW_MARK(0, 2);
         tcgen05_fence_before();
         __syncthreads();
         if (tid == 0) {
@@ -885,18 +951,15 @@ __global__ void __launch_bounds__(256) k_unit_tc(FwdCtx c, int t) {
         mbar_wait(&bar_m, phase, c.status);
         phase ^= 1u;
         tcgen05_fence_after();
-        HSNW_MARK(0, 3);
+        if (base == 0) HSNW_MARK(0, 3);
         // epilogue 1
         {
-            float acc[16];
-            tmem_ld8(tmem_addr(taddr, q * 32, hf * 16), acc);
-            tmem_ld8(tmem_addr(taddr, q * 32, hf * 16 + 8), acc + 8);
-            const bool col_ok = is_gate ? m < d : c0 + m < H;
-            const float bias = col_ok ? (is_gate ? c.m.gate_b[m] : c.m.b1[j * H + c0 + m]) : 0.0f;
+            float acc[8];
+            tmem_ld8(tmem_addr(taddr, q * 32, hf * 8), acc);
             uint16_t* b2_half = reinterpret_cast<uint16_t*>(B2);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const int n = hf * 16 + i;
+            for (int i = 0; i < 8; ++i) {
+                const int n = hf * 8 + i;
                 float a = 0.0f;
                 if (n < nb && col_ok) {
                     const int pair = list[base + n];
@@ -920,7 +983,7 @@ __global__ void __launch_bounds__(256) k_unit_tc(FwdCtx c, int t) {
             __syncthreads();
             continue;
         }
-        HSNW_MARK(0, 4);
+        if (base == 0) HSNW_MARK(0, 4);
         fence_async_smem();
         tcgen05_fence_before();
         __syncthreads();
@@ -933,22 +996,22 @@ __global__ void __launch_bounds__(256) k_unit_tc(FwdCtx c, int t) {
         mbar_wait(&bar_m, phase, c.status);
         phase ^= 1u;
         tcgen05_fence_after();
-        HSNW_MARK(0, 5);
+        if (base == 0) HSNW_MARK(0, 5);
         // epilogue 2: lane m is output x of the unit
         {
-            float acc[16];
-            tmem_ld8(tmem_addr(taddr, q * 32, 32 + hf * 16), acc);
-            tmem_ld8(tmem_addr(taddr, q * 32, 32 + hf * 16 + 8), acc + 8);
+            float acc[8];
+            tmem_ld8(tmem_addr(taddr, q * 32, 32 + hf * 8), acc);
             if (m < d) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int n = hf * 16 + i;
+                for (int i = 0; i < 8; ++i) {
+                    const int n = hf * 8 + i;
                     if (n < nb) c.part_f[(static_cast<int64_t>(cb) * P + list[base + n]) * d + m] = acc[i];
                 }
             }
         }
         tcgen05_fence_before();
         __syncthreads();
+        if (base == 0) HSNW_MARK(0, 12);
     }
     HSNW_MARK(0, 6);
     if (warp == 0) tmem_dealloc(taddr, 64);
@@ -1159,7 +1222,8 @@ Layout layout(const HsnwModel& m, int B, int T) {
     return L;
 }
 
-int row_threads(const HsnwModel& m) { return m.N > 512 ? 512 : 256; }
+// 512 threads shorten a large row's scorer; with more rows than SMs 256 let more blocks share an SM
+int row_threads(const HsnwModel& m, int B) { return m.N > 512 && B <= hsnw_sm_count_current() ? 512 : 256; }
 // the per-cell logit parts and scalars of a row are staged in shared memory while they are small
 bool stage_cells_fit(const HsnwModel& m) { return sizeof(float) * static_cast<size_t>(m.N) * (m.M + m.S) <= 96 * 1024; }
 
@@ -1168,7 +1232,7 @@ size_t row_shared(const HsnwModel& m, bool staged) {
     const size_t cells = staged ? static_cast<size_t>(pad4(N * m.M)) + pad4(N * m.S) : 0;
     const size_t words = static_cast<size_t>(pad4(nF2 * d)) + cells + pad4(2 * N) + pad4(N)
         + static_cast<size_t>(K + K * D) * d + static_cast<size_t>(K) * d + pad4(2 * d * m.M) + pad4((1 + m.S) * m.M)
-        + 2 * static_cast<size_t>(pad4(N)) + 2 * d + kMaxM + 2 * static_cast<size_t>(pad4(K * D)) + K;
+        + 2 * static_cast<size_t>(pad4(N)) + 2 * d + 2 * kMaxM + 2 * static_cast<size_t>(pad4(K * D)) + K;
     return sizeof(float) * words;
 }
 // Staging saves a second pass over memory when a row's block has the SM to itself; with more rows
@@ -1190,7 +1254,7 @@ size_t unit_shared(const HsnwModel& m) {
 }
 size_t unit_tc_shared(const HsnwModel& m) {
     const size_t planes = static_cast<size_t>(4 * m.d) / 8;
-    return 16 * (planes * 128 + 16 * 128 + planes * kTP + 16 * kTP) + sizeof(int) * kTcPairTileBig;
+    return 16 * (planes * 128 + 16 * 128 + planes * kTP + 16 * kTP) + sizeof(int) * kTcPairTileMax;
 }
 size_t update_shared(const HsnwModel& m) {
     return sizeof(float) * (4 * static_cast<size_t>(m.K) * m.d + 2 * static_cast<size_t>(m.d) * m.d + pad4(m.d * m.M) + 2 * m.K);
@@ -1297,7 +1361,7 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
         const int rc_rows = hsnw_rows_forward(model, io, c.pre_s, c.status, stream);
         if (rc_rows >= 0) return rc_rows;
     }
-    const int rthreads = row_threads(*model);
+    const int rthreads = row_threads(*model, B);
     const dim3 init_grid(B, (model->N + kInitCells - 1) / kInitCells);
     hsnw_profile_mark(HSNW_K_INIT, stream);
     k_init<<<init_grid, 256, init_shared(*model), stream>>>(c);
@@ -1308,7 +1372,7 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
         if (rc_pre) return rc_pre;
     }
     const int front_grid = c.n_front + B * c.copy_per_row;
-    c.pair_tile = B * model->K > 1024 ? kTcPairTileBig : kTcPairTile;
+    c.pair_tile = B * model->K > 1024 ? 512 : kTcPairTile;
     const int pair_tile = unit_tc ? c.pair_tile : kPairTile;
     const dim3 unit_grid(model->M * (unit_tc ? c.nU + 1 : c.nU + c.nG), (B * model->K + pair_tile - 1) / pair_tile);
     const size_t sh_front = front_shared(*model), sh_row = row_shared(*model, c.stage_cells != 0);
@@ -1319,7 +1383,7 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
         hsnw_profile_mark(HSNW_K_ROW, stream);
         k_row<<<B, rthreads, sh_row, stream>>>(c, t);
         hsnw_profile_mark(HSNW_K_UNIT, stream);
-        if (unit_tc) k_unit_tc<<<unit_grid, 256, sh_unit_tc, stream>>>(c, t);
+        if (unit_tc) k_unit_tc<<<unit_grid, kUnitTcThreads, sh_unit_tc, stream>>>(c, t);
         else k_unit<<<unit_grid, 256, sh_unit, stream>>>(c, t);
         hsnw_profile_mark(HSNW_K_UPDATE, stream);
         k_update<<<B, 256, sh_update, stream>>>(c, t);

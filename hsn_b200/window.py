@@ -298,6 +298,7 @@ def window_forward(
     want_logits: bool = False,
     scratch: Tensor | None = None,
     out: dict[str, Tensor] | None = None,
+    carried: bool = False,
     _entry: str = "hsnw_window_forward",
 ) -> dict[str, Tensor]:
     """The forward sweep of one window (``hsnw_window_forward``): the reference's tape
@@ -307,7 +308,15 @@ def window_forward(
     state is returned under ``h q age pos``). ``record`` adds ``rec_*``: the per-slot values the
     state-gradient sweep reads. ``forced = (cells, units, valid)`` replays a recorded decision.
     ``tape_state=False`` keeps no state tape and updates ``state`` in place (large ``N``).
-    ``out`` reuses the buffers of an earlier call's result (static addresses)."""
+    ``out`` reuses the buffers of an earlier call's result (static addresses).
+    ``carried`` (with ``tape_state=False`` and the previous call's result as ``out``, same ``B`` and
+    ``T``): the next chunk of positions on the same resident state, ``hsnw_stream_continue``; the
+    cells' derived values are taken from the previous call's scratch instead of being recomputed
+    from the whole state."""
+    if carried:
+        if tape_state or out is None or "_scratch" not in out:
+            raise ValueError("a carried call continues a resident state: tape_state=False and out=the previous result")
+        _entry = "hsnw_stream_continue"
     dm = model.dims
     dev = model.device
     B, T = int(reset.shape[0]), int(reset.shape[1])

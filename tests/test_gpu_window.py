@@ -343,6 +343,16 @@ def test_carried_stream_steps_equal_one_resident_window(prod: str) -> None:
     torch.testing.assert_close(fresh[0], whole[0], rtol=1e-5, atol=1e-6)
     with pytest.raises(ValueError):
         stream_step(model, *now, carried, carried=True)
+    # chunks of three positions, the second continuing the first
+    chunked = tuple(dev(s) for s in start)
+    res = None
+    for half in range(2):
+        part = tuple(a[:, 3 * half : 3 * half + 3].contiguous() for a in args)
+        res = window_forward(model, *part, chunked, record=False, tape_state=False, out=res, carried=half > 0)
+        assert torch.equal(res["qs"], want["qs"][:, 3 * half : 3 * half + 3])
+        assert torch.equal(res["sel_cell_idx"], want["sel_cell_idx"][:, 3 * half : 3 * half + 3])
+    for got, ref in zip(chunked, whole):
+        assert torch.equal(got, ref)
 
 
 def test_full_size_window_properties() -> None:
