@@ -123,6 +123,35 @@ __device__ __forceinline__ float dot4(const float* a, int sa, const float* b, in
     for (; i < n; ++i) s0 += a[i * sa] * b[i * sb];
     return (s0 + s1) + (s2 + s3);
 }
+// Up to four dot products that share b: out[r] = sum_i a[r * lda + i] * b[i], r < rows <= 4, both
+// contiguous, each in dot4's order (bit for bit the same sums). A value of b is loaded once for
+// the four rows.
+__device__ __forceinline__ void dot4_rows(const float* a, int lda, int rows, const float* b, int n, float out[4]) {
+    float s[4][4] = {};
+    int i = 0;
+    for (; i + 8 <= n; i += 8) {
+        float bv[8];
+#pragma unroll
+        for (int w = 0; w < 8; ++w) bv[w] = b[i + w];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            if (r < rows) {
+                const float* pa = a + r * lda + i;
+                float av[8];
+#pragma unroll
+                for (int w = 0; w < 8; ++w) av[w] = pa[w];
+#pragma unroll
+                for (int w = 0; w < 8; ++w) s[r][w & 3] += av[w] * bv[w];
+            }
+        }
+    }
+    for (; i < n; ++i)
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+            if (r < rows) s[r][0] += a[r * lda + i] * b[i];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) out[r] = (s[r][0] + s[r][1]) + (s[r][2] + s[r][3]);
+}
 // sum_i a[i * sa], i < n, the same way.
 __device__ __forceinline__ float sum4(const float* a, int64_t sa, int n) {
     float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;

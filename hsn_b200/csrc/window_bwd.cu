@@ -29,6 +29,25 @@
 
 using namespace hsnw;
 
+// Optional phase timestamps for tuning (compiled in with -DHSNW_TRACE): event i of block b of the
+// tail+head kernel lands at g_bwd_trace[b * 32 + i] (nanoseconds of the global timer).
+#ifdef HSNW_TRACE
+__device__ unsigned long long g_bwd_trace[64 * 32];
+#define BW_MARK(i)                                                              \
+    do {                                                                        \
+        if (threadIdx.x == 0 && blockIdx.x < 64) {                              \
+            unsigned long long now;                                             \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));             \
+            g_bwd_trace[blockIdx.x * 32 + (i)] = now;                           \
+        }                                                                       \
+    } while (0)
+extern "C" int hsnw_trace_read_bwd(unsigned long long* host) {
+    return static_cast<int>(cudaMemcpyFromSymbol(host, g_bwd_trace, sizeof(g_bwd_trace)));
+}
+#else
+#define BW_MARK(i) do { } while (0)
+#endif
+
 namespace {
 
 constexpr int kUS = 32;          // columns of a unit slice
@@ -70,15 +89,19 @@ __device__ __forceinline__ void head_phase(const BwdCtx& c, int t, unsigned char
     const int64_t* cells = c.io.cells + rt * K;
     const uint8_t* valid = c.io.valid + rt * K;
     const int64_t o0 = rt * K * d;
-    if (!full)
-        for (int e = tid; e < d * d; e += nt) wo[(e / d) * (d + 1) + (e % d)] = c.m.wout_t[e];
+    if (!full) {
+        for (int e = tid; e < d * d; e += nt) cp_async4(wo + (e / d) * (d + 1) + (e % d), c.m.wout_t + e);
+        cp_async_commit();   // needed only by the last step of the phase
+    }
     for (int x = tid; x < d; x += nt) {
         float r = R[x];
         if (c.io.d_q_post) r += c.io.d_q_post[rt * d + x];
         Rs[x] = r;
     }
     for (int k = tid; k < K; k += nt) cell_of[k] = valid[k] ? static_cast<int>(cells[k]) : -1;
+    BW_MARK(8);
     __syncthreads();
+    BW_MARK(9);
     const float n_f = static_cast<float>(N);
     for (int e = tid; e < K * d; e += nt) {
         const int k = e / d, x = e - k * d;
@@ -124,6 +147,7 @@ __device__ __forceinline__ void head_phase(const BwdCtx& c, int t, unsigned char
     }
     for (int x = tid; x < d; x += nt) R[x] = Rs[x];
     __syncthreads();
+    BW_MARK(10);
     // per slot: rho = rsqrt(mean(y^2) + eps), dot = mean(y * cand_w * dz), sigma_gate; a warp each
     for (int k = warp; k < K; k += warps) {
         float sq = 0.0f, dt = 0.0f, s = 0.0f;
@@ -149,14 +173,21 @@ __device__ __forceinline__ void head_phase(const BwdCtx& c, int t, unsigned char
         const float r = rho[k];
         dzs[e] = cell_of[k] >= 0 ? r * dzs[e] - r * r * r * ysv[e] * dot[k] : 0.0f;
     }
+    BW_MARK(11);
+    cp_async_wait_all();
     __syncthreads();
+    BW_MARK(12);
     // d_unit = dy W_out (the transposed output projection): y[x] = sum_i F[i] wout_t[i][x]
-    for (int e = tid; e < K * d; e += nt) {
-        const int k = e / d, i = e - k * d;
-        c.d_unit[(static_cast<int64_t>(row) * K + k) * d + i] = dot4(dzs + k * d, 1, wo + i * (d + 1), 1, d);
+    const int per = max(1, min(4, K * d / nt));   // slots a thread: a weight is read once for them
+    for (int e = tid; e < ((K + per - 1) / per) * d; e += nt) {
+        const int k0 = (e / d) * per, i = e - (e / d) * d;
+        float out[4];
+        dot4_rows(dzs + k0 * d, d, min(per, K - k0), wo + i * (d + 1), d, out);
+        for (int r = 0; r < per && k0 + r < K; ++r) c.d_unit[(static_cast<int64_t>(row) * K + k0 + r) * d + i] = out[r];
     }
     for (int k = tid; k < K; k += nt)
         c.pair_unit[static_cast<int64_t>(row) * K + k] = cell_of[k] >= 0 ? static_cast<int>(c.io.units[rt * K + k]) : -1;
+    BW_MARK(13);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -503,7 +534,9 @@ __device__ __forceinline__ void tail_phase(const BwdCtx& c, int t, unsigned char
     float* A = c.io.A + static_cast<int64_t>(row) * N * d;
     float* R = c.io.R + static_cast<int64_t>(row) * d;
     const float in_dim = static_cast<float>(4 * d);
-    for (int e = tid; e < d * d; e += nt) vt[(e / d) * (d + 1) + (e % d)] = c.m.v_t[e];
+    BW_MARK(0);
+    for (int e = tid; e < d * d; e += nt) cp_async4(vt + (e / d) * (d + 1) + (e % d), c.m.v_t + e);
+    cp_async_commit();   // in flight while the position's values are gathered
     for (int k = tid; k < K; k += nt) {
         const bool ok = c.io.valid[rt * K + k] != 0;
         const int n = ok ? static_cast<int>(c.io.cells[rt * K + k]) : -1;
@@ -523,6 +556,7 @@ __device__ __forceinline__ void tail_phase(const BwdCtx& c, int t, unsigned char
         ew[e] = ok ? c.m.edge_w[n * D + j] : 0.0f;
     }
     __syncthreads();
+    BW_MARK(1);
     for (int u = tid; u < U; u += nt) {
         int f = u;
         if (tgt[u] >= 0)
@@ -533,42 +567,91 @@ __device__ __forceinline__ void tail_phase(const BwdCtx& c, int t, unsigned char
                 }
         first[u] = f;
     }
+    BW_MARK(2);
     // ds = rms (g_n dv) - (rms^2 / n) sigma [h_old ; m] on the state columns
-    for (int e = tid; e < K * two; e += nt) {
-        const int k = e / two, i = e - k * two;
-        float out = 0.0f;
-        if (cell_of[k] >= 0) {
-            const float dv = sum4(c.part_dv + (pair0 + k) * two + i, static_cast<int64_t>(P) * two, c.nU + 1);
-            const float state = i < d ? c.io.h_old[(rt * K + k) * d + i] : c.io.m[(rt * K + k) * d + i - d];
-            out = c.io.rms[rt * K + k] * (c.m.norm_w[two + i] * dv) - back[k] * state;
+    // (four elements a thread per round: their partial sums' loads are in flight together)
+    for (int e0 = tid; e0 < K * two; e0 += 4 * nt) {
+        float dv[4], state[4];
+        const float* from[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int e = e0 + u * nt;
+            const int k = min(e / two, K - 1), i = e - (e / two) * two;
+            const bool ok = e < K * two && cell_of[k] >= 0;
+            from[u] = ok ? c.part_dv + (pair0 + k) * two + i : c.part_dv;   // a padded slot's sum is not used
+            state[u] = !ok ? 0.0f : i < d ? c.io.h_old[(rt * K + k) * d + i] : c.io.m[(rt * K + k) * d + i - d];
         }
-        ds[e] = out;
+        {   // the slices' partial sums in sum4's order (four running sums by slice mod 4), four elements abreast
+            const int64_t sa = static_cast<int64_t>(P) * two;
+            const int n = c.nU + 1;
+            float acc[4][4] = {};
+            int sl = 0;
+            for (; sl + 4 <= n; sl += 4)
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) acc[u][w] += from[u][(sl + w) * sa];
+            for (; sl < n; ++sl)
+#pragma unroll
+                for (int u = 0; u < 4; ++u) acc[u][0] += from[u][sl * sa];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) dv[u] = (acc[u][0] + acc[u][1]) + (acc[u][2] + acc[u][3]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int e = e0 + u * nt;
+            if (e >= K * two) continue;
+            const int k = e / two, i = e - k * two;
+            ds[e] = cell_of[k] >= 0 ? c.io.rms[rt * K + k] * (c.m.norm_w[two + i] * dv[u]) - back[k] * state[u] : 0.0f;
+        }
     }
+    BW_MARK(3);
+    cp_async_wait_all();
     __syncthreads();
+    BW_MARK(4);
     // the touched rows of A, each loaded once (all loads in flight together)
+#pragma unroll 4
     for (int e = tid; e < U * d; e += nt) {
         const int u = e / d, x = e - u * d;
         if (tgt[u] >= 0 && first[u] == u) stage[e] = A[static_cast<int64_t>(tgt[u]) * d + x];
     }
     // dvm = dm V: m = sum_e a_e (V h_src), (V h)[x] = sum_i h[i] v_t[i][x]
-    for (int e = tid; e < K * d; e += nt) {
-        const int k = e / d, i = e - k * d;
-        dvm[e] = dot4(ds + k * two + d, 1, vt + i * (d + 1), 1, d);
+    const int per = max(1, min(4, K * d / nt));   // slots a thread: a weight is read once for them
+    for (int e = tid; e < ((K + per - 1) / per) * d; e += nt) {
+        const int k0 = (e / d) * per, i = e - (e / d) * d;
+        float out[4];
+        dot4_rows(ds + k0 * two + d, two, min(per, K - k0), vt + i * (d + 1), d, out);
+        for (int r = 0; r < per && k0 + r < K; ++r) dvm[(k0 + r) * d + i] = out[r];
     }
     __syncthreads();
-    // a thread owns a column: the cells' own cotangents first, then every edge in slot order
+    BW_MARK(5);
+    // a thread owns a column of some of the touched rows (row first[u] belongs to group first[u] mod
+    // G, G = threads / d): a row's additions stay in slot order, the cells' own cotangents first,
+    // then every edge
     const bool cut = c.io.reset[rt] != 0;
-    for (int x = tid; x < d; x += nt) {
-        for (int u = 0; u < U; ++u) {
-            if (tgt[u] < 0) continue;
-            const float add = u < K ? ds[u * two + x] : ew[u - K] * dvm[((u - K) / D) * d + x];
-            stage[first[u] * d + x] += add;
+    int G = 1;
+    while (2 * G * d <= nt) G *= 2;   // a power of two: the group of a row is a mask, not a division
+    for (int e = tid; e < G * d; e += nt) {
+        const int g = e / d, x = e - g * d;
+        for (int k = 0; k < K; ++k) {
+            const int f = first[k];
+            if (tgt[k] >= 0 && (f & (G - 1)) == g) stage[f * d + x] += ds[k * two + x];
         }
+        for (int k = 0; k < K; ++k) {
+            const float dv = dvm[k * d + x];
+            for (int j = 0; j < D; ++j) {
+                const int u = K + k * D + j, f = first[u];
+                if (tgt[u] >= 0 && (f & (G - 1)) == g) stage[f * d + x] += ew[u - K] * dv;
+            }
+        }
+    }
+    for (int x = tid; x < d; x += nt) {
         float r = R[x];
         if (c.io.d_q_pre) r += c.io.d_q_pre[rt * d + x];
         R[x] = cut ? 0.0f : r;
     }
     __syncthreads();
+    BW_MARK(6);
     if (cut) {
         for (int e = tid; e < N * d; e += nt) A[e] = 0.0f;
     } else {
@@ -579,13 +662,13 @@ __device__ __forceinline__ void tail_phase(const BwdCtx& c, int t, unsigned char
     }
 }
 
-__global__ void __launch_bounds__(256) k_head(BwdCtx c, int t) {
+__global__ void __launch_bounds__(512) k_head(BwdCtx c, int t) {
     extern __shared__ __align__(16) unsigned char dyn[];
     head_phase(c, t, dyn);
 }
 
 // The tail of position t and the head of position t - 1 of the same row in one launch.
-__global__ void __launch_bounds__(256) k_tail_head(BwdCtx c, int t) {
+__global__ void __launch_bounds__(512) k_tail_head(BwdCtx c, int t) {
     extern __shared__ __align__(16) unsigned char dyn[];
     tail_phase(c, t, dyn);
     if (t > 0) {
@@ -680,25 +763,26 @@ extern "C" int hsnw_window_backward(const HsnwModel* model, const HsnwBackward* 
     c.part_sig = full ? nullptr : reinterpret_cast<float*>(base + L.part_sig);
     c.pair_unit = full ? nullptr : reinterpret_cast<int*>(base + L.pair_unit);
     const int B = io->B, T = io->T;
+    const int ht = m.K * m.d >= 2048 ? 512 : 256;   // threads of the head and tail: wide rows have the work for 16 warps
     const int pair_tile = mid_tc ? kTcPairTile : kPairTile;
     const dim3 mid_grid(m.M * (c.nU + 1), (B * m.K + pair_tile - 1) / pair_tile);
     const size_t sh_mid_tc = mid_tc_shared(m);
     if (full) {
         for (int t = T - 1; t >= 0; --t) {
             hsnw_profile_mark(HSNW_K_HEAD, stream);
-            k_head<<<B, 256, sh_head, stream>>>(c, t);
+            k_head<<<B, ht, sh_head, stream>>>(c, t);
         }
         return hsnw_check_launch("window_backward");
     }
     // head(T-1) | mid(T-1) | tail(T-1) + head(T-2) | mid(T-2) | ... | tail(0)
     hsnw_profile_mark(HSNW_K_HEAD, stream);
-    k_head<<<B, 256, sh_head, stream>>>(c, T - 1);
+    k_head<<<B, ht, sh_head, stream>>>(c, T - 1);
     for (int t = T - 1; t >= 0; --t) {
         hsnw_profile_mark(HSNW_K_MID, stream);
         if (mid_tc) k_mid_tc<<<mid_grid, 256, sh_mid_tc, stream>>>(c, t);
         else k_mid<<<mid_grid, 256, sh_mid, stream>>>(c, t);
         hsnw_profile_mark(HSNW_K_TAIL_HEAD, stream);
-        k_tail_head<<<B, 256, sh_both, stream>>>(c, t);
+        k_tail_head<<<B, ht, sh_both, stream>>>(c, t);
         if (int rc = hsnw_check_launch("window_backward")) return rc;
     }
     return HSNW_OK;

@@ -1019,15 +1019,15 @@ __global__ void __launch_bounds__(kUnitTcThreads) k_unit_tc(FwdCtx c, int t) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// update: one block per row, 256 threads. Reduces the second layer's partial sums, W_out, the
+// update: one block per row, 256 threads (512 when K d >= 2048). Reduces the second layer's partial sums, W_out, the
 // candidate norm, tanh, sigmoid, the gated write of the K cells, the summary, and the derived
 // state of the written cells (their logit parts, V h and maxima).
 // Shared (dynamic): F [K d], y [K d], hnew [K d], delta [K d], wo [d d], vt [d d], swh [d M],
 // cell_of [K], scale [K].
 // ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) k_update(FwdCtx c, int t) {
+__global__ void __launch_bounds__(512) k_update(FwdCtx c, int t) {
     extern __shared__ __align__(16) unsigned char dyn[];
-    __shared__ int ired[8];
+    __shared__ int ired[16];
     __shared__ int zero_slot;
     const int N = c.m.N, d = c.m.d, K = c.m.K, M = c.m.M;
     const int B = c.io.B, T = c.io.T, P = B * K;
@@ -1065,14 +1065,35 @@ __global__ void __launch_bounds__(256) k_update(FwdCtx c, int t) {
         if (cell_of[k] == 0) zero_slot = k;  // at most one valid slot names cell 0
     // the executed unit's output: the second layer's partial sums in slice order, plus its bias;
     // the loads of an element go out together, four slices at a time
-    for (int e = tid; e < K * d; e += nt) {
-        const int k = e / d, x = e - k * d;
-        float sum = 0.0f;
-        if (cell_of[k] >= 0) {
-            sum = sum4(c.part_f + (pair0 + k) * d + x, static_cast<int64_t>(P) * d, c.nU);
-            sum = maybe_bf16(sum + c.m.b2[static_cast<int>(units[k]) * d + x], bf);
+    // (and four elements abreast, in sum4's order: four running sums by slice mod 4)
+    for (int e0 = tid; e0 < K * d; e0 += 4 * nt) {
+        const float* from[4];
+        float bias[4];
+        bool ok[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int e = e0 + u * nt;
+            const int k = min(e / d, K - 1), x = e - (e / d) * d;
+            ok[u] = e < K * d && cell_of[k] >= 0;
+            from[u] = ok[u] ? c.part_f + (pair0 + k) * d + x : c.part_f;   // a padded slot's sum is not used
+            bias[u] = ok[u] ? c.m.b2[static_cast<int>(units[k]) * d + x] : 0.0f;
         }
-        Fs[e] = sum;
+        const int64_t sa = static_cast<int64_t>(P) * d;
+        float acc[4][4] = {};
+        int sl = 0;
+        for (; sl + 4 <= c.nU; sl += 4)
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int w = 0; w < 4; ++w) acc[u][w] += from[u][(sl + w) * sa];
+        for (; sl < c.nU; ++sl)
+#pragma unroll
+            for (int u = 0; u < 4; ++u) acc[u][0] += from[u][sl * sa];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int e = e0 + u * nt;
+            if (e < K * d) Fs[e] = ok[u] ? maybe_bf16((acc[u][0] + acc[u][1]) + (acc[u][2] + acc[u][3]) + bias[u], bf) : 0.0f;
+        }
     }
     HSNW_MARK(1, 1);
     cp_async_wait_all();
@@ -1386,7 +1407,7 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
         if (unit_tc) k_unit_tc<<<unit_grid, kUnitTcThreads, sh_unit_tc, stream>>>(c, t);
         else k_unit<<<unit_grid, 256, sh_unit, stream>>>(c, t);
         hsnw_profile_mark(HSNW_K_UPDATE, stream);
-        k_update<<<B, 256, sh_update, stream>>>(c, t);
+        k_update<<<B, model->K * model->d >= 2048 ? 512 : 256, sh_update, stream>>>(c, t);
         if (int rc = hsnw_check_launch("window_forward")) return rc;
     }
     return HSNW_OK;
