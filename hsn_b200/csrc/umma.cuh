@@ -155,18 +155,6 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float out[8]) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) out[i] = __uint_as_float(r[i]);
 }
-// True in exactly one lane of a converged warp (the issuing lane of single-thread instructions).
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred;
-    asm volatile(
-        "{\n"
-        ".reg .pred P;\n"
-        "elect.sync _|P, 0xffffffff;\n"
-        "selp.u32 %0, 1, 0, P;\n"
-        "}\n"
-        : "=r"(pred));
-    return pred != 0;
-}
 __device__ __forceinline__ uint32_t tmem_addr(uint32_t base, int lane, int column) {
     return base + (static_cast<uint32_t>(lane) << 16) + static_cast<uint32_t>(column);
 }
