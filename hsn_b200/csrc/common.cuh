@@ -123,16 +123,16 @@ __device__ __forceinline__ float dot4(const float* a, int sa, const float* b, in
     for (; i < n; ++i) s0 += a[i * sa] * b[i * sb];
     return (s0 + s1) + (s2 + s3);
 }
-// Up to four dot products that share b: out[r] = sum_i a[r * lda + i] * b[i], r < rows <= 4, both
-// contiguous, each in dot4's order (bit for bit the same sums). A value of b is loaded once for
-// the four rows.
-__device__ __forceinline__ void dot4_rows(const float* a, int lda, int rows, const float* b, int n, float out[4]) {
+// Up to four dot products that share b: out[r] = sum_i a[r * lda + i] * b[i * sb], r < rows <= 4,
+// each in dot4's order (bit for bit the same sums). A value of b is loaded once for the four rows.
+__device__ __forceinline__ void dot4_rows(const float* a, int lda, int rows, const float* b, int sb, int n,
+                                          float out[4]) {
     float s[4][4] = {};
     int i = 0;
     for (; i + 8 <= n; i += 8) {
         float bv[8];
 #pragma unroll
-        for (int w = 0; w < 8; ++w) bv[w] = b[i + w];
+        for (int w = 0; w < 8; ++w) bv[w] = b[(i + w) * sb];
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
             if (r < rows) {
@@ -148,7 +148,7 @@ __device__ __forceinline__ void dot4_rows(const float* a, int lda, int rows, con
     for (; i < n; ++i)
 #pragma unroll
         for (int r = 0; r < 4; ++r)
-            if (r < rows) s[r][0] += a[r * lda + i] * b[i];
+            if (r < rows) s[r][0] += a[r * lda + i] * b[i * sb];
 #pragma unroll
     for (int r = 0; r < 4; ++r) out[r] = (s[r][0] + s[r][1]) + (s[r][2] + s[r][3]);
 }

@@ -182,7 +182,7 @@ __device__ __forceinline__ void head_phase(const BwdCtx& c, int t, unsigned char
     for (int e = tid; e < ((K + per - 1) / per) * d; e += nt) {
         const int k0 = (e / d) * per, i = e - (e / d) * d;
         float out[4];
-        dot4_rows(dzs + k0 * d, d, min(per, K - k0), wo + i * (d + 1), d, out);
+        dot4_rows(dzs + k0 * d, d, min(per, K - k0), wo + i * (d + 1), 1, d, out);
         for (int r = 0; r < per && k0 + r < K; ++r) c.d_unit[(static_cast<int64_t>(row) * K + k0 + r) * d + i] = out[r];
     }
     for (int k = tid; k < K; k += nt)
@@ -620,7 +620,7 @@ __device__ __forceinline__ void tail_phase(const BwdCtx& c, int t, unsigned char
     for (int e = tid; e < ((K + per - 1) / per) * d; e += nt) {
         const int k0 = (e / d) * per, i = e - (e / d) * d;
         float out[4];
-        dot4_rows(ds + k0 * two + d, two, min(per, K - k0), vt + i * (d + 1), d, out);
+        dot4_rows(ds + k0 * two + d, two, min(per, K - k0), vt + i * (d + 1), 1, d, out);
         for (int r = 0; r < per && k0 + r < K; ++r) dvm[(k0 + r) * d + i] = out[r];
     }
     __syncthreads();

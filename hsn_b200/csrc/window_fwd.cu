@@ -392,14 +392,31 @@ __global__ void __launch_bounds__(256) k_front(FwdCtx c, int t) {
 // at a time under a uniform branch for the same reason.
 template <int MM>
 __device__ __forceinline__ void score_cells(const FwdCtx& c, int64_t rt, const float* lh, const float* scal,
-                                            const int64_t* age, const float* sw_tail, const float* rowterm,
-                                            const float* score_b, const float* cost, float* score, int* unit) {
+                                            const int64_t* age, const float* sw_tail,
+                                            const float* rowterm, const float* score_b, const float* cost,
+                                            float* score, int* unit) {
     const int N = c.m.N, M = c.m.M, Sn = c.m.S;
+    const int nt = blockDim.x, lane = threadIdx.x & 31;
     const bool bf = c.m.prod_bf16 != 0;
     const float lambda = c.m.lambda_cost;
     const float age_div = static_cast<float>(c.m.age_max);
     const bool wide = (M & 3) == 0;   // the weights' rows are then 16-byte aligned
-    for (int i = threadIdx.x; i < N; i += blockDim.x) {
+    for (int i0 = threadIdx.x - lane; i0 < N; i0 += nt) {
+        const int i = i0 + lane;
+        const bool live = i < N;
+        if (!live) continue;
+        const float* mine = scal + static_cast<int64_t>(i) * Sn;
+        // every load of the cell goes out before the first use: the scalars (up to sixteen, four at
+        // a time under a uniform branch), then the derived logit parts and the age
+        float feat[16];
+#pragma unroll
+        for (int s0 = 0; s0 < 16; s0 += 4) {
+            if (s0 < Sn) {
+#pragma unroll
+                for (int s = 0; s < 4; ++s) feat[s0 + s] = s0 + s < Sn ? mine[s0 + s] : 0.0f;
+            }
+        }
+        const float age_f = static_cast<float>(age[i]);
         float acc[MM];
         if (wide) {
 #pragma unroll
@@ -430,15 +447,16 @@ __device__ __forceinline__ void score_cells(const FwdCtx& c, int64_t rt, const f
                     if (j < M) acc[j] += a * w[j];
             }
         };
-        add_term(maybe_bf16(static_cast<float>(age[i]) / age_div, bf), sw_tail);
-        for (int s0 = 0; s0 < Sn; s0 += 4) {   // four scalars at a time, their loads in flight together
-            float feat[4];
+        add_term(maybe_bf16(age_f / age_div, bf), sw_tail);
 #pragma unroll
-            for (int s = 0; s < 4; ++s) feat[s] = s0 + s < Sn ? scal[static_cast<int64_t>(i) * Sn + s0 + s] : 0.0f;
+        for (int s0 = 0; s0 < 16; s0 += 4) {
+            if (s0 < Sn) {
 #pragma unroll
-            for (int s = 0; s < 4; ++s)
-                if (s0 + s < Sn) add_term(maybe_bf16(feat[s], bf), sw_tail + (1 + s0 + s) * M);
+                for (int s = 0; s < 4; ++s)
+                    if (s0 + s < Sn) add_term(maybe_bf16(feat[s0 + s], bf), sw_tail + (1 + s0 + s) * M);
+            }
         }
+        for (int s = 16; s < Sn; ++s) add_term(maybe_bf16(mine[s], bf), sw_tail + (1 + s) * M);   // rare: more than sixteen scalars
         float best = -INFINITY;
         int arg = 0;
 #pragma unroll
@@ -468,7 +486,7 @@ __device__ __forceinline__ void score_cells(const FwdCtx& c, int64_t rt, const f
 // cmax [N], rows [(K + K D) d], msg [K d], sw_head [2d M], sw_tail [(1+S) M], score [N], unit [N],
 // ue [2d], rowterm [16], score_b [16], src [K D], ew [K D], rms [K].
 // ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
+__global__ void __launch_bounds__(512, 2) k_row(FwdCtx c, int t) {
     extern __shared__ __align__(16) unsigned char dyn[];
     __shared__ SelectShared S;
     __shared__ int ired[32];
@@ -617,14 +635,14 @@ __global__ void __launch_bounds__(512) k_row(FwdCtx c, int t) {
         src[e] = c.m.pad_src[cell * D + j];
         ew[e] = maybe_bf16(c.m.edge_w[cell * D + j], bf);
     }
-    // max |h| over the cells this position does not write (the update adds the written ones)
+    // max |h| over the cells this position does not write (the update adds the written ones): the
+    // written cells' entries of the block's copy are cleared first
+    for (int k = tid; k < K; k += nt)
+        if (S.out_flag[k] & 1) cmax[S.out_cell[k]] = 0;
+    __syncthreads();
     {
         int top = 0;
-        for (int i = tid; i < N; i += nt) {
-            bool written = false;
-            for (int k = 0; k < K; ++k) written = written || ((S.out_flag[k] & 1) && S.out_cell[k] == i);
-            if (!written) top = max(top, cmax[i]);
-        }
+        for (int i = tid; i < N; i += nt) top = max(top, cmax[i]);
         for (int w = 16; w > 0; w >>= 1) top = max(top, __shfl_xor_sync(0xffffffffu, top, w));
         if (lane == 0) ired[warp] = top;
     }
@@ -1099,9 +1117,14 @@ __global__ void __launch_bounds__(512) k_update(FwdCtx c, int t) {
     cp_async_wait_all();
     __syncthreads();
     HSNW_MARK(1, 2);
-    for (int e = tid; e < K * d; e += nt) {
-        const int k = e / d, x = e - k * d;
-        ys[e] = maybe_bf16(dot4(Fs + k * d, 1, wo + x, d, d), bf);
+    {
+        const int per = max(1, min(4, K * d / nt));   // slots a thread: a weight is read once for them
+        for (int e = tid; e < ((K + per - 1) / per) * d; e += nt) {
+            const int k0 = (e / d) * per, x = e - (e / d) * d;
+            float out[4];
+            dot4_rows(Fs + k0 * d, d, min(per, K - k0), wo + x, d, d, out);
+            for (int r = 0; r < per && k0 + r < K; ++r) ys[(k0 + r) * d + x] = maybe_bf16(out[r], bf);
+        }
     }
     __syncthreads();
     for (int k = warp; k < K; k += warps) {
@@ -1253,7 +1276,7 @@ size_t row_shared(const HsnwModel& m, bool staged) {
     const size_t cells = staged ? static_cast<size_t>(pad4(N * m.M)) + pad4(N * m.S) : 0;
     const size_t words = static_cast<size_t>(pad4(nF2 * d)) + cells + pad4(2 * N) + pad4(N)
         + static_cast<size_t>(K + K * D) * d + static_cast<size_t>(K) * d + pad4(2 * d * m.M) + pad4((1 + m.S) * m.M)
-        + 2 * static_cast<size_t>(pad4(N)) + 2 * d + 2 * kMaxM + 2 * static_cast<size_t>(pad4(K * D)) + K;
+        + 2 * static_cast<size_t>(pad4(N)) + 2 * d + 2 * kMaxM + 2 * static_cast<size_t>(pad4(K * D)) + pad4(K);
     return sizeof(float) * words;
 }
 // Staging saves a second pass over memory when a row's block has the SM to itself; with more rows
