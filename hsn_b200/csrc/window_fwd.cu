@@ -850,7 +850,7 @@ constexpr int kTP = 32;       // pairs of a tensor-core batch
 constexpr int kTcPairTile = 64;  // pairs a tensor-core unit block scans: small tiles keep a popular
                                  // unit's pairs spread over several blocks
 constexpr int kUnitTcThreads = 512;  // 16 warps: warp w reads TMEM lanes 32 (w % 4) .. +31, pairs 8 (w / 4) .. +7
-constexpr int kTcPairTileMax = 4096; // with thousands of pairs the tile grows until the grid is one wave of blocks
+constexpr int kTcPairTileMax = 512;  // the tile with thousands of pairs: about 64 pairs of the unit per weight tile loaded
 
 __global__ void __launch_bounds__(kUnitTcThreads) k_unit_tc(FwdCtx c, int t) {
     extern __shared__ __align__(16) unsigned char dyn[];
@@ -1416,7 +1416,7 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
         if (rc_pre) return rc_pre;
     }
     const int front_grid = c.n_front + B * c.copy_per_row;
-    c.pair_tile = B * model->K > 1024 ? 512 : kTcPairTile;
+    c.pair_tile = B * model->K > 1024 ? kTcPairTileMax : kTcPairTile;
     const int pair_tile = unit_tc ? c.pair_tile : kPairTile;
     const dim3 unit_grid(model->M * (unit_tc ? c.nU + 1 : c.nU + c.nG), (B * model->K + pair_tile - 1) / pair_tile);
     const size_t sh_front = front_shared(*model), sh_row = row_shared(*model, c.stage_cells != 0);
