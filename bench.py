@@ -103,10 +103,10 @@ NCU_TRAFFIC_PER_LAUNCH: dict[str, dict[str, float]] = {
 def synthetic(c: dict, rank: int, rows: int):
     """Seeded inputs of the configuration's shapes; every row's data depends on its global row
     index only, so the result does not depend on the number of GPUs."""
-    from oracle.window_oracle import WindowWeights
+    from hsn_b200.window import synthetic_weights
 
-    W = WindowWeights.random(np.random.default_rng(0), N=c["N"], d=c["d"], K=c["K"], H=c["H"], M=c["M"],
-                             D=c["D"], S=c["S"], age_max=2**31 - 1)  # fmt: skip
+    W = synthetic_weights(np.random.default_rng(0), N=c["N"], d=c["d"], K=c["K"], H=c["H"], M=c["M"],
+                          D=c["D"], S=c["S"], age_max=2**31 - 1)  # fmt: skip
     T, N, d, K, S = c["T"], c["N"], c["d"], c["K"], c["S"]
     parts = []
     for r in range(rows):
@@ -166,6 +166,7 @@ def cpu_window(W, data, rows: int, positions: int):
     workload; returns seconds."""
     from oracle import window_oracle as O
 
+    W = O.WindowWeights(**vars(W))   # the same weights in the oracle's container
     z, ctx, scalars, reset, pre, post, sel = (a[:rows, :positions] for a in data)
     N, d = W.pad_src.shape[0], z.shape[-1]
     state = (np.zeros((rows, N, d), np.float32), np.zeros((rows, d), np.float32), np.zeros((rows, N), np.int64),
@@ -243,16 +244,15 @@ def run_resident(args, c: dict, name: str) -> None:
     to call, CUDA events around ``steps`` calls. Not the headline line: no end-to-end leg."""
     import torch
 
-    from hsn_b200.window import WindowModel, launch_profile, window_backward, window_forward
-    from oracle.window_oracle import WindowWeights
+    from hsn_b200.window import WindowModel, launch_profile, synthetic_weights, window_backward, window_forward
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the window path has no CPU fallback")
     dev = torch.device("cuda", 0)
     B, T, N, d, K, S = c["B"], c["T"], c["N"], c["d"], c["K"], c["S"]
-    W = WindowWeights.random(np.random.default_rng(0), N=N, d=d, K=K, H=c["H"], M=c["M"], D=c["D"], S=S,
-                             age_max=2**31 - 1)  # fmt: skip
-    model = WindowModel.from_oracle_weights(W, device=dev, prod=c["prod"], row_clusters=not args.phases)
+    W = synthetic_weights(np.random.default_rng(0), N=N, d=d, K=K, H=c["H"], M=c["M"], D=c["D"], S=S,
+                          age_max=2**31 - 1)  # fmt: skip
+    model = WindowModel.from_weights(W, device=dev, prod=c["prod"], row_clusters=not args.phases)
     gen = torch.Generator(device=dev).manual_seed(1)
     z = torch.randn((B, T, d), device=dev, generator=gen) * 0.5
     ctx = torch.randn((B, T, model.dims["dc"]), device=dev, generator=gen) * 0.02
@@ -373,7 +373,7 @@ def main() -> None:
     warmup = max(args.warmup, 3)
     B, T, N, d, K = c["B"], c["T"], c["N"], c["d"], c["K"]
     W, host = synthetic(c, rank, B)
-    model = WindowModel.from_oracle_weights(W, device=dev, prod=c["prod"], row_clusters=not args.phases)
+    model = WindowModel.from_weights(W, device=dev, prod=c["prod"], row_clusters=not args.phases)
     pinned = [torch.from_numpy(a).pin_memory() for a in host]
     z, ctx, scalars, reset, pre, post, sel = (t.to(dev, non_blocking=True) for t in pinned)
     state = (torch.zeros((B, N, d), device=dev), torch.zeros((B, d), device=dev),

@@ -169,6 +169,8 @@ class WindowModel:
             row_clusters=row_clusters,
         )  # fmt: skip
 
+    from_weights = from_oracle_weights
+
     @staticmethod
     def from_hsn(model: Any, *, prod: str = "fp32", probes: bool = True) -> "WindowModel":
         """From a reference ``HSN`` module (``python/hsn/model/hsn.py``), inside or outside its
@@ -196,6 +198,39 @@ class WindowModel:
             limit=float(model.cfg.budget) * (1.0 + 1e-5), norm_eps=float(cell.norm.eps),
             cand_eps=float(cell.cand_norm.eps),
         )  # fmt: skip
+
+
+def synthetic_weights(rng: Any, *, N: int, d: int, K: int, H: int, M: int, D: int, S: int = 9,
+                      dc: int | None = None, std: float = 0.02, age_max: int = 1 << 30) -> Any:  # fmt: skip
+    """Seeded N(0, ``std``) weights of the reference's shapes for a benchmark or a demonstration
+    (biases zero, the gate's bias -3, gains one, a ring-like padded graph with softmax edge weights):
+    an object with one numpy array per weight under the names :meth:`WindowModel.from_weights`
+    reads (``nn.Linear`` layouts, ``[out, in]``) and the router's scalars. ``rng`` is a
+    ``numpy.random.Generator``."""
+    import types
+
+    import numpy as np
+
+    dc = d if dc is None else dc
+    f32 = np.float32
+
+    def w(*shape: int) -> Any:
+        return (rng.standard_normal(shape) * std).astype(f32)
+
+    src = np.stack([(np.arange(N) + 1 + e * 7) % N for e in range(D)], axis=1).astype(np.int64)
+    logit = rng.standard_normal((N, D))
+    edge = np.exp(logit) / np.exp(logit).sum(axis=1, keepdims=True)
+    return types.SimpleNamespace(
+        s_w1=w(H, 2 * d + dc), s_b1=np.zeros(H, f32), s_w2=w(d, H), s_b2=np.zeros(d, f32),
+        p_w1=w(H, d), p_b1=np.zeros(H, f32), p_w2=w(d, H), p_b2=np.zeros(d, f32),
+        score_w=w(M, 3 * d + 1 + S), score_b=np.zeros(M, f32),
+        v_w=w(d, d), wout_w=w(d, d), gate_w=w(d, 4 * d), gate_b=np.full(d, -3.0, f32),
+        norm_w=np.ones(4 * d, f32), cand_w=np.ones(d, f32),
+        w1=w(M, 4 * d, H), b1=np.zeros((M, H), f32), w2=w(M, H, d), b2=np.zeros((M, d), f32),
+        pad_src=src, edge_w=edge.astype(f32), cost=np.full(M, 1.0 / (8 * N), f32),
+        age_max=age_max, lambda_cost=0.0, cell_overhead=0.0, shared_cost=0.0, limit=1.00001,
+        norm_eps=1e-6, cand_eps=1e-6, k=K, probes=True,
+    )  # fmt: skip
 
 
 def _sw128(tile: Tensor) -> Tensor:
