@@ -83,3 +83,20 @@ def test_python_interface_keeps_the_reference_names() -> None:
         assert hasattr(ns, op), op
     assert window.select_unsupported(4096, 16, 8) is None
     assert window.select_unsupported(8, 16) is not None
+
+
+def test_synthetic_weights_are_the_oracles_random_weights() -> None:
+    """The package's seeded benchmark weights and the oracle's: the same arrays from the same seed,
+    so the benchmark's CPU leg and its GPU leg run one model."""
+    import numpy as np
+
+    from hsn_b200.window import synthetic_weights
+    from oracle.window_oracle import WindowWeights
+
+    sizes = dict(N=24, d=8, K=3, H=32, M=3, D=2, S=5, age_max=77)
+    mine = synthetic_weights(np.random.default_rng(4), **sizes)
+    theirs = WindowWeights.random(np.random.default_rng(4), **sizes)
+    for key, want in vars(theirs).items():
+        got = getattr(mine, key)
+        assert np.array_equal(got, want) if isinstance(want, np.ndarray) else got == want, key
+    WindowWeights(**vars(mine))
