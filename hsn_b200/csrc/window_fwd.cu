@@ -71,6 +71,7 @@ struct FwdCtx {
     int stage_cells;    // 1: the row phase stages the per-cell logit parts and scalars in shared memory
     int carried;        // 1: the derived state in the scratch is current (a resident state's next call)
     int pair_tile;      // pairs a tensor-core unit block scans for its unit's
+    int marker;         // status[4] holds it while the scratch's derived state is current for this B, T, resident
     int* status;        // [1] 0, or 1 when a bounded wait ran out
     unsigned long long* trace;  // phase timestamps (HSNW_TRACE builds)
     float* pre_s;       // [B*T, H]
@@ -132,7 +133,9 @@ __global__ void __launch_bounds__(256) k_init(FwdCtx c) {
     const bool cut = c.io.reset[static_cast<int64_t>(row) * T] != 0;
     float* h0 = c.io.h0 + static_cast<int64_t>(row) * N * d;
     if (row == 0 && blockIdx.y == 0 && tid == 0) *c.status = 0;
-    if (c.carried && !cut) return;   // the previous call on this state left every cell's derived values
+    // carried: the previous call on this state left every cell's derived values, if it was one of the
+    // batch-synchronous kind with the same sizes (its last kernel then wrote the marker)
+    if (c.carried && c.status[4] == c.marker && !cut) return;
     for (int e = tid; e < d * M; e += nt) swh[e] = c.m.score_w_t[2 * d * M + e];
     for (int e = tid; e < d * d; e += nt) vt[e] = c.m.v_t[e];
     for (int e = tid; e < ncell * d; e += nt) {
@@ -1232,6 +1235,7 @@ __global__ void __launch_bounds__(512) k_update(FwdCtx c, int t) {
         }
     }
     HSNW_MARK(1, 6);
+    if (last && row == 0 && tid == 0) c.status[4] = c.io.tape_state ? 0 : c.marker;
     if (last && tid == 0) {
         // the position counter after the window (reference compile.py:1194-1200)
         int last_reset = 0;
@@ -1379,6 +1383,7 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
     c.n_front = 2 * c.nF * ((B + kFR - 1) / kFR);
     c.stage_cells = stage_cells(*model, io->B) ? 1 : 0;
     c.carried = carried ? 1 : 0;
+    c.marker = 0x5eed0000 ^ io->B ^ (io->T << 12);
     c.copy_per_row = io->tape_state ? (model->N * model->d + kCopyFloats - 1) / kCopyFloats : 0;
     unsigned char* base = static_cast<unsigned char*>(io->scratch);
     c.status = reinterpret_cast<int*>(base + L.status);
@@ -1396,7 +1401,8 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
     bool pre_done = false;   // the window-invariant front product is the same for both kernel families
     if (!phases && !model->phases_only && model->rows_bank) {
         // one persistent cluster per row when the shape fits (window_rows.cu)
-        if (cudaMemsetAsync(c.status, 0, sizeof(int), stream) != cudaSuccess) return hsnw_check_launch("window_forward");
+        // (the status word, and the marker of derived values in the scratch: the row kernels keep none there)
+        if (cudaMemsetAsync(c.status, 0, 8 * sizeof(int), stream) != cudaSuccess) return hsnw_check_launch("window_forward");
         g_pre_status = c.status;
         const int rc_pre = hsnw_front_projection(model, io->z, io->ctx, static_cast<int64_t>(B) * T, c.pre_s, stream);
         g_pre_status = nullptr;

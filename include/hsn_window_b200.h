@@ -211,7 +211,8 @@ int hsnw_stream_step(const HsnwModel* model, const HsnwForward* io, void* stream
  * 512 streams of 1024 cells that recomputation is five times the step). The caller guarantees:
  * the same model weights, B, T and scratch as the previous hsnw_stream_step / hsnw_stream_continue
  * on this state, and h0 / q0 / age0 untouched in between. A stream whose reset[:,0] is set starts
- * from zeros as usual. */
+ * from zeros as usual. When the scratch's last call was of another kind or size (the library marks
+ * the scratch), the derived values are recomputed as in hsnw_stream_step. */
 int hsnw_stream_continue(const HsnwModel* model, const HsnwForward* io, void* stream);
 
 /* The reverse sweep of one window (state_gradient.py:357-485; full_cut != 0: split.py:128-174).

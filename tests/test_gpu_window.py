@@ -631,6 +631,15 @@ def test_row_clusters_on_a_resident_state_equal_the_phases(N: int, H: int) -> No
             assert float(diff.max()) <= 2e-2 * scale, (half, name)
             assert float(torch.quantile(diff.float(), 0.999)) <= 5e-3 * scale, (half, name)
         assert torch.equal(mine[2], theirs[2]) and torch.equal(mine[3], theirs[3])
+    # a continuation asked of a scratch that the row kernel used (it keeps no derived values there):
+    # the library notices and recomputes them, so the result is the plain call's
+    again = tuple(t.clone() for t in mine)
+    plain = window_forward(rows, *args, mine, record=False, tape_state=False, forced=forced)
+    cont = window_forward(rows, *args, again, record=False, tape_state=False, forced=forced, out=got, carried=True)
+    for g, w in ((again[0], mine[0]), (again[1], mine[1]), (cont["qs"], plain["qs"])):
+        scale = max(1e-3, float(w.abs().max()))
+        assert float((g - w).abs().max()) <= 2e-2 * scale
+    assert torch.equal(again[2], mine[2])
 
 
 def test_reverse_sweep_with_bf16_products_stays_within_bf16_tolerance() -> None:
