@@ -855,7 +855,9 @@ constexpr int kTcPairTile = 64;  // pairs a tensor-core unit block scans: small 
 constexpr int kUnitTcThreads = 512;  // 16 warps: warp w reads TMEM lanes 32 (w % 4) .. +31, pairs 8 (w / 4) .. +7
 constexpr int kTcPairTileMax = 512;  // the tile with thousands of pairs: about 64 pairs of the unit per weight tile loaded
 
+template <int TP>
 __global__ void __launch_bounds__(kUnitTcThreads) k_unit_tc(FwdCtx c, int t) {
+    constexpr int CW = TP / 4;   // columns (pairs) of a warp's share of an accumulator
     extern __shared__ __align__(16) unsigned char dyn[];
     __shared__ int warp_count[kUnitTcThreads / 32];
     __shared__ int n_list;
@@ -871,8 +873,8 @@ __global__ void __launch_bounds__(kUnitTcThreads) k_unit_tc(FwdCtx c, int t) {
     uint4* A1 = reinterpret_cast<uint4*>(dyn);                 // [planes][128]
     uint4* A2 = A1 + planes * 128;                             // [16][128]
     uint4* B1 = A2 + 16 * 128;                                 // [planes][32]
-    uint4* B2 = B1 + planes * kTP;                             // [16][32]
-    int* list = reinterpret_cast<int*>(B2 + 16 * kTP);         // [pair_tile]
+    uint4* B2 = B1 + planes * TP;                             // [16][32]
+    int* list = reinterpret_cast<int*>(B2 + 16 * TP);         // [pair_tile]
     const int p0 = blockIdx.y * c.pair_tile;
     HSNW_MARK(0, 11);
     if (tid == 0) {
@@ -913,14 +915,14 @@ __global__ void __launch_bounds__(kUnitTcThreads) k_unit_tc(FwdCtx c, int t) {
                      a2_bytes, &bar_w);
     }
     HSNW_MARK(0, 8);
-    if (warp == 0) tmem_alloc(&tmem_slot, 64);
+    if (warp == 0) tmem_alloc(&tmem_slot, 2 * TP);
     HSNW_MARK(0, 9);
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
     HSNW_MARK(0, 10);
     const uint32_t taddr = tmem_slot;
-    const uint32_t idesc = umma_idesc_bf16(128, kTP);
+    const uint32_t idesc = umma_idesc_bf16(128, TP);
     const int q = warp & 3, hf = warp >> 2;
     const int m = q * 32 + lane;           // this thread's TMEM lane: a hidden column, then an output
     uint32_t phase = 0;
@@ -929,18 +931,18 @@ __global__ void __launch_bounds__(kUnitTcThreads) k_unit_tc(FwdCtx c, int t) {
     // the lane's bias is the same for every batch: its load is off the batches' critical path
     const bool col_ok = is_gate ? m < d : c0 + m < H;
     const float bias = col_ok ? (is_gate ? c.m.gate_b[m] : c.m.b1[j * H + c0 + m]) : 0.0f;
-    for (int base = 0; base < count; base += kTP) {
-        const int nb = min(kTP, count - base);
+    for (int base = 0; base < count; base += TP) {
+        const int nb = min(TP, count - base);
         // the pairs' inputs as the B operand: a thread converts 8 values and stores one 16-byte unit
         // (four units a thread per round, their eight loads in flight together)
-        for (int idx0 = tid; idx0 < planes * kTP; idx0 += 4 * kUnitTcThreads) {
+        for (int idx0 = tid; idx0 < planes * TP; idx0 += 4 * kUnitTcThreads) {
             float4 lo[4], hi[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int idx = idx0 + u * kUnitTcThreads;
-                const int n = idx & (kTP - 1), kc = idx >> 5;
+                const int n = idx & (TP - 1), kc = idx / TP;
                 lo[u] = hi[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                if (idx < planes * kTP && n < nb) {
+                if (idx < planes * TP && n < nb) {
                     const float4* src = v4 + static_cast<int64_t>(list[base + n]) * d + kc * 2;
                     lo[u] = src[0];
                     hi[u] = src[1];
@@ -949,7 +951,7 @@ __global__ void __launch_bounds__(kUnitTcThreads) k_unit_tc(FwdCtx c, int t) {
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int idx = idx0 + u * kUnitTcThreads;
-                if (idx < planes * kTP)
+                if (idx < planes * TP)
                     B1[idx] = make_uint4(pack_bf16x2(lo[u].x, lo[u].y), pack_bf16x2(lo[u].z, lo[u].w),
                                          pack_bf16x2(hi[u].x, hi[u].y), pack_bf16x2(hi[u].z, hi[u].w));
             }
@@ -965,8 +967,8 @@ __global__ void __launch_bounds__(kUnitTcThreads) k_unit_tc(FwdCtx c, int t) {
         __syncthreads();
         if (tid == 0) {
             tcgen05_fence_after();
-            const uint64_t da = umma_desc(A1, 128), db = umma_desc(B1, kTP);
-            umma_chain(taddr, da, db, idesc, in >> 4, umma_kstep(128), umma_kstep(kTP));
+            const uint64_t da = umma_desc(A1, 128), db = umma_desc(B1, TP);
+            umma_chain(taddr, da, db, idesc, in >> 4, umma_kstep(128), umma_kstep(TP));
             umma_commit(&bar_m);
         }
         mbar_wait(&bar_m, phase, c.status);
@@ -975,12 +977,13 @@ __global__ void __launch_bounds__(kUnitTcThreads) k_unit_tc(FwdCtx c, int t) {
         if (base == 0) HSNW_MARK(0, 3);
         // epilogue 1
         {
-            float acc[8];
-            tmem_ld8(tmem_addr(taddr, q * 32, hf * 8), acc);
+            float acc[CW];
+#pragma unroll
+            for (int c8 = 0; c8 < CW; c8 += 8) tmem_ld8(tmem_addr(taddr, q * 32, hf * CW + c8), acc + c8);
             uint16_t* b2_half = reinterpret_cast<uint16_t*>(B2);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int n = hf * 8 + i;
+            for (int i = 0; i < CW; ++i) {
+                const int n = hf * CW + i;
                 float a = 0.0f;
                 if (n < nb && col_ok) {
                     const int pair = list[base + n];
@@ -996,7 +999,7 @@ __global__ void __launch_bounds__(kUnitTcThreads) k_unit_tc(FwdCtx c, int t) {
                     }
                 }
                 // B2 (n, k = m): plane m / 8, unit n, element m % 8
-                if (!is_gate) b2_half[((m >> 3) * kTP + n) * 8 + (m & 7)] = bf16_bits(a);
+                if (!is_gate) b2_half[((m >> 3) * TP + n) * 8 + (m & 7)] = bf16_bits(a);
             }
         }
         if (is_gate) {
@@ -1010,8 +1013,8 @@ __global__ void __launch_bounds__(kUnitTcThreads) k_unit_tc(FwdCtx c, int t) {
         __syncthreads();
         if (tid == 0) {
             tcgen05_fence_after();
-            const uint64_t da = umma_desc(A2, 128), db = umma_desc(B2, kTP);
-            umma_chain(taddr + 32, da, db, idesc, 8, umma_kstep(128), umma_kstep(kTP));
+            const uint64_t da = umma_desc(A2, 128), db = umma_desc(B2, TP);
+            umma_chain(taddr + TP, da, db, idesc, 8, umma_kstep(128), umma_kstep(TP));
             umma_commit(&bar_m);
         }
         mbar_wait(&bar_m, phase, c.status);
@@ -1020,12 +1023,13 @@ __global__ void __launch_bounds__(kUnitTcThreads) k_unit_tc(FwdCtx c, int t) {
         if (base == 0) HSNW_MARK(0, 5);
         // epilogue 2: lane m is output x of the unit
         {
-            float acc[8];
-            tmem_ld8(tmem_addr(taddr, q * 32, 32 + hf * 8), acc);
+            float acc[CW];
+#pragma unroll
+            for (int c8 = 0; c8 < CW; c8 += 8) tmem_ld8(tmem_addr(taddr, q * 32, TP + hf * CW + c8), acc + c8);
             if (m < d) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int n = hf * 8 + i;
+                for (int i = 0; i < CW; ++i) {
+                    const int n = hf * CW + i;
                     if (n < nb) c.part_f[(static_cast<int64_t>(cb) * P + list[base + n]) * d + m] = acc[i];
                 }
             }
@@ -1035,7 +1039,7 @@ __global__ void __launch_bounds__(kUnitTcThreads) k_unit_tc(FwdCtx c, int t) {
         if (base == 0) HSNW_MARK(0, 12);
     }
     HSNW_MARK(0, 6);
-    if (warp == 0) tmem_dealloc(taddr, 64);
+    if (warp == 0) tmem_dealloc(taddr, 2 * TP);
     HSNW_MARK(0, 7);
 }
 
@@ -1300,9 +1304,9 @@ size_t unit_shared(const HsnwModel& m) {
     return sizeof(float) * (static_cast<size_t>(kPB) * 4 * m.d + static_cast<size_t>(4) * m.d * kUS
         + static_cast<size_t>(kUS) * m.d + kPB * kUS + kPairTile);
 }
-size_t unit_tc_shared(const HsnwModel& m) {
+size_t unit_tc_shared(const HsnwModel& m, int tp = kTP) {
     const size_t planes = static_cast<size_t>(4 * m.d) / 8;
-    return 16 * (planes * 128 + 16 * 128 + planes * kTP + 16 * kTP) + sizeof(int) * kTcPairTileMax;
+    return 16 * (planes * 128 + 16 * 128 + planes * tp + 16 * tp) + sizeof(int) * kTcPairTileMax;
 }
 size_t update_shared(const HsnwModel& m) {
     return sizeof(float) * (4 * static_cast<size_t>(m.K) * m.d + 2 * static_cast<size_t>(m.d) * m.d + pad4(m.d * m.M) + 2 * m.K);
@@ -1423,17 +1427,20 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
     }
     const int front_grid = c.n_front + B * c.copy_per_row;
     c.pair_tile = B * model->K > 1024 ? kTcPairTileMax : kTcPairTile;
+    // batches of 64 pairs where there are thousands of pairs and the wider operands still fit
+    const bool tp64 = unit_tc && B * model->K > 1024 && unit_tc_shared(*model, 64) <= hsnw_max_shared() - 4096;
     const int pair_tile = unit_tc ? c.pair_tile : kPairTile;
     const dim3 unit_grid(model->M * (unit_tc ? c.nU + 1 : c.nU + c.nG), (B * model->K + pair_tile - 1) / pair_tile);
     const size_t sh_front = front_shared(*model), sh_row = row_shared(*model, c.stage_cells != 0);
-    const size_t sh_unit = unit_shared(*model), sh_update = update_shared(*model), sh_unit_tc = unit_tc_shared(*model);
+    const size_t sh_unit = unit_shared(*model), sh_update = update_shared(*model), sh_unit_tc = unit_tc_shared(*model, tp64 ? 64 : kTP);
     for (int t = 0; t < T; ++t) {
         hsnw_profile_mark(HSNW_K_FRONT, stream);
         k_front<<<front_grid, 256, sh_front, stream>>>(c, t);
         hsnw_profile_mark(HSNW_K_ROW, stream);
         k_row<<<B, rthreads, sh_row, stream>>>(c, t);
         hsnw_profile_mark(HSNW_K_UNIT, stream);
-        if (unit_tc) k_unit_tc<<<unit_grid, kUnitTcThreads, sh_unit_tc, stream>>>(c, t);
+        if (unit_tc && tp64) k_unit_tc<64><<<unit_grid, kUnitTcThreads, sh_unit_tc, stream>>>(c, t);
+        else if (unit_tc) k_unit_tc<32><<<unit_grid, kUnitTcThreads, sh_unit_tc, stream>>>(c, t);
         else k_unit<<<unit_grid, 256, sh_unit, stream>>>(c, t);
         hsnw_profile_mark(HSNW_K_UPDATE, stream);
         k_update<<<B, model->K * model->d >= 2048 ? 512 : 256, sh_update, stream>>>(c, t);
@@ -1463,7 +1470,8 @@ void hsnw_forward_set_attributes() {
         {reinterpret_cast<const void*>(k_init), "init"}, {reinterpret_cast<const void*>(k_pre_tc), "pre_tc"},
         {reinterpret_cast<const void*>(k_front), "front"},
         {reinterpret_cast<const void*>(k_row), "row"}, {reinterpret_cast<const void*>(k_unit), "unit"},
-        {reinterpret_cast<const void*>(k_unit_tc), "unit_tc"},
+        {reinterpret_cast<const void*>(k_unit_tc<32>), "unit_tc"},
+        {reinterpret_cast<const void*>(k_unit_tc<64>), "unit_tc64"},
         {reinterpret_cast<const void*>(k_update), "update"}};
     for (const auto& k : ks)
         if (!hsnw_opt_in(k.f, k.n)) hsnw_attribute_failed();
