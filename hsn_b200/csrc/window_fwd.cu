@@ -37,7 +37,8 @@ namespace {
 
 constexpr int kSlice = 64;       // tile edge of the window-invariant projection (k_pre)
 constexpr int kFS = 32;          // columns of a front slice
-constexpr int kFR = 8;           // rows a front block serves
+constexpr int kFR = 8;           // rows a front block serves (kFRBig of them where the batch has hundreds of rows)
+constexpr int kFRBig = 32;
 constexpr int kUS = 32;          // columns of a unit slice
 constexpr int kPB = 32;          // pairs a unit block multiplies at a time
 constexpr int kPairTile = 256;   // pairs a unit block scans
@@ -71,6 +72,7 @@ struct FwdCtx {
     int stage_cells;    // 1: the row phase stages the per-cell logit parts and scalars in shared memory
     int carried;        // 1: the derived state in the scratch is current (a resident state's next call)
     int pair_tile;      // pairs a tensor-core unit block scans for its unit's
+    int front_rows;     // rows a front block serves: kFR, or kFRBig for large batches (a weight slice is loaded once for them)
     int marker;         // status[4] holds it while the scratch's derived state is current for this B, T, resident
     int* status;        // [1] 0, or 1 when a bounded wait ran out
     unsigned long long* trace;  // phase timestamps (HSNW_TRACE builds)
@@ -332,12 +334,13 @@ __global__ void __launch_bounds__(256) k_front(FwdCtx c, int t) {
     const int c0 = (is_p ? slice - nF : slice) * kFS;
     const int cols = min(kFS, H - c0);
     const int col_base = (is_p ? H : 0) + c0;   // column in the merged [d, 2H] first layer
-    const int r0 = tile * kFR;
-    const int rows = min(kFR, B - r0);
+    const int FR = c.front_rows;
+    const int r0 = tile * FR;
+    const int rows = min(FR, B - r0);
     float* w1 = reinterpret_cast<float*>(dyn);          // [d][32]
     float* w2 = w1 + d * kFS;                           // [32][d]
     float* qs = w2 + kFS * d;                           // [8][d]
-    float* act = qs + kFR * d;                          // [8][32]
+    float* act = qs + FR * d;                           // [rows][32]
     if (cols == kFS) {
         // 16 bytes per request, every request in flight at once
         for (int e = tid; e < d * (kFS >> 2); e += 256) {
@@ -360,31 +363,64 @@ __global__ void __launch_bounds__(256) k_front(FwdCtx c, int t) {
         const int r = e / d, x = e - r * d;
         qs[e] = maybe_bf16(state_q(c, r0 + r, t)[x], bf);
     }
-    float pre = 0.0f;
+    // thread (r, cc) serves rows r, r + 8, ... of the tile: a weight is read once for them
+    constexpr int kRI = kFRBig / 8;
+    float pre[kRI];
     {
         const int r = tid >> 5, cc = tid & 31;
-        if (r < rows && cc < cols)
-            pre = is_p ? c.m.f_b1[H + c0 + cc] : c.pre_s[(static_cast<int64_t>(r0 + r) * T + t) * H + c0 + cc];
+#pragma unroll
+        for (int i = 0; i < kRI; ++i) {
+            const int rr = r + 8 * i;
+            pre[i] = 0.0f;
+            if (rr < rows && cc < cols)
+                pre[i] = is_p ? c.m.f_b1[H + c0 + cc] : c.pre_s[(static_cast<int64_t>(r0 + rr) * T + t) * H + c0 + cc];
+        }
     }
     cp_async_wait_all();
     __syncthreads();
     {
         const int r = tid >> 5, cc = tid & 31;
-        float a = 0.0f;
-        if (r < rows && cc < cols) {
-            float sum = 0.0f;
-            for (int x = 0; x < d; ++x) sum += qs[r * d + x] * w1[x * kFS + cc];
-            a = maybe_bf16(gelu_erf(maybe_bf16(sum + pre, bf)), bf);
+        float sum[kRI] = {};
+        if (rows <= 8) {
+            if (r < rows)
+                for (int x = 0; x < d; ++x) sum[0] += qs[r * d + x] * w1[x * kFS + cc];
+        } else {
+            for (int x = 0; x < d; ++x) {
+                const float w = w1[x * kFS + cc];
+#pragma unroll
+                for (int i = 0; i < kRI; ++i) sum[i] += qs[min(r + 8 * i, rows - 1) * d + x] * w;
+            }
         }
-        act[tid] = a;
+#pragma unroll
+        for (int i = 0; i < kRI; ++i) {
+            const int rr = r + 8 * i;
+            if (rr < FR) act[rr * kFS + cc] = rr < rows && cc < cols ? maybe_bf16(gelu_erf(maybe_bf16(sum[i] + pre[i], bf)), bf) : 0.0f;
+        }
     }
     __syncthreads();
-    for (int e = tid; e < rows * d; e += 256) {
-        const int r = e / d, x = e - r * d;
-        float sum = 0.0f;
+    if (rows <= 8) {
+        for (int e = tid; e < rows * d; e += 256) {
+            const int r = e / d, x = e - r * d;
+            float sum = 0.0f;
 #pragma unroll 8
-        for (int cc = 0; cc < kFS; ++cc) sum += act[r * kFS + cc] * w2[cc * d + x];
-        c.part_front[(static_cast<int64_t>(r0 + r) * 2 * nF + slice) * d + x] = sum;
+            for (int cc = 0; cc < kFS; ++cc) sum += act[r * kFS + cc] * w2[cc * d + x];
+            c.part_front[(static_cast<int64_t>(r0 + r) * 2 * nF + slice) * d + x] = sum;
+        }
+    } else {
+        // four rows a thread (r4, r4 + 1, .. of a group of four): a weight is read once for them
+        for (int e = tid; e < ((rows + 3) / 4) * d; e += 256) {
+            const int g = e / d, x = e - g * d;
+            float sum[4] = {};
+#pragma unroll 8
+            for (int cc = 0; cc < kFS; ++cc) {
+                const float w = w2[cc * d + x];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) sum[i] += act[min(g * 4 + i, FR - 1) * kFS + cc] * w;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (g * 4 + i < rows) c.part_front[(static_cast<int64_t>(r0 + g * 4 + i) * 2 * nF + slice) * d + x] = sum[i];
+        }
     }
 }
 
@@ -1298,7 +1334,7 @@ size_t init_shared(const HsnwModel& m) {
     return sizeof(float) * (static_cast<size_t>(2 * kInitCells) * m.d + static_cast<size_t>(m.d) * m.M + static_cast<size_t>(m.d) * m.d);
 }
 size_t front_shared(const HsnwModel& m) {
-    return sizeof(float) * (static_cast<size_t>(2) * m.d * kFS + static_cast<size_t>(kFR) * m.d + kFR * kFS);
+    return sizeof(float) * (static_cast<size_t>(2) * m.d * kFS + static_cast<size_t>(kFRBig) * m.d + kFRBig * kFS);
 }
 size_t unit_shared(const HsnwModel& m) {
     return sizeof(float) * (static_cast<size_t>(kPB) * 4 * m.d + static_cast<size_t>(4) * m.d * kUS
@@ -1384,7 +1420,8 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
     c.nU = unit_tc ? (model->H + 127) / 128 : (model->H + kUS - 1) / kUS;
     c.nG = (model->d + kUS - 1) / kUS;
     const int B = io->B, T = io->T;
-    c.n_front = 2 * c.nF * ((B + kFR - 1) / kFR);
+    c.front_rows = B >= 256 ? kFRBig : kFR;
+    c.n_front = 2 * c.nF * ((B + c.front_rows - 1) / c.front_rows);
     c.stage_cells = stage_cells(*model, io->B) ? 1 : 0;
     c.carried = carried ? 1 : 0;
     c.marker = 0x5eed0000 ^ io->B ^ (io->T << 12);

@@ -556,6 +556,7 @@ def _both_ways(rng, B, T, N, d, K, H, M, D, mult, path="rows"):
         (2, 5, 512, 64, 8, 1024, 8, 4, 1.0),   # eight blocks a row
         (3, 6, 512, 64, 8, 512, 8, 4, 1.0),    # 128 cells a block: the forward ring has two slots
         (160, 2, 64, 64, 8, 256, 3, 2, 1.0),   # 1280 pairs a position: 512-pair tiles, batches of 64 pairs
+        (270, 2, 64, 32, 4, 128, 3, 2, 1.0),   # 270 rows: front tiles of 32 rows, the last one of 14
     ],
 )
 def test_tensor_core_kernels_equal_the_cuda_core_kernels_with_the_same_roundings(path, B, T, N, d, K, H, M, D, mult) -> None:
