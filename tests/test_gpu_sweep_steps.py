@@ -129,6 +129,7 @@ def _random_buffers(sizes, half: bool, seed: int):
         ((32, 3, 8, 256, 64, 512, 8, 0, 0, 256), True, "gelu"),  # the benchmark's cell
         ((5, 4, 8, 96, 32, 96, 3, 2, 4, 128), True, "silu"),
         ((3, 3, 40, 700, 24, 40, 5, 1, 3, 72), False, "tanh"),  # more than 32 slots, odd widths
+        ((4, 1, 6, 40, 16, 48, 3, 5, 0, 64), False, "relu"),    # one position, a single routed slot
     ],
 )
 def test_sweep_kernels_equal_the_oracle_at_larger_sizes(window, sizes, half: bool, activation: str) -> None:
