@@ -1,6 +1,7 @@
 // Shared device helpers of the window kernels: bf16 rounding, activations, block reductions and
 // 16-byte row copies. Device code only.
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
@@ -11,15 +12,13 @@ constexpr float kSqrtHalf = 0.7071067811865475244f;
 constexpr float kInvSqrt2Pi = 0.3989422804014326779f;
 
 // float32 -> nearest bfloat16 (ties to even), returned as the float32 of that value. A NaN stays
-// a quiet NaN. The cast up from bfloat16 is exact, so a value rounded here is what a bf16 buffer
-// would hold.
+// a NaN (the canonical one). The cast up from bfloat16 is exact, so a value rounded here is what a
+// bf16 buffer would hold.
 __device__ __forceinline__ float bf16r(float x) {
-    const uint32_t u = __float_as_uint(x);
-    if ((u & 0x7fffffffu) > 0x7f800000u) return __uint_as_float((u | 0x00400000u) & 0xffff0000u);
-    return __uint_as_float((u + 0x7fffu + ((u >> 16) & 1u)) & 0xffff0000u);
+    return __bfloat162float(__float2bfloat16_rn(x));   // one conversion instruction each way
 }
 __device__ __forceinline__ float maybe_bf16(float x, bool on) { return on ? bf16r(x) : x; }
-__device__ __forceinline__ uint16_t bf16_bits(float x) { return static_cast<uint16_t>(__float_as_uint(bf16r(x)) >> 16); }
+__device__ __forceinline__ uint16_t bf16_bits(float x) { return __bfloat16_as_ushort(__float2bfloat16_rn(x)); }
 __device__ __forceinline__ float bf16_value(uint16_t h) { return __uint_as_float(static_cast<uint32_t>(h) << 16); }
 
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * kSqrtHalf)); }

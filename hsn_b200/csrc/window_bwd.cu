@@ -319,7 +319,8 @@ constexpr int kTP = 32;
 constexpr int kTcPairTile = 64;
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-    return static_cast<uint32_t>(bf16_bits(lo)) | (static_cast<uint32_t>(bf16_bits(hi)) << 16);
+    const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);   // one conversion for both halves
+    return *reinterpret_cast<const uint32_t*>(&pair);
 }
 
 __global__ void __launch_bounds__(256) k_mid_tc(BwdCtx c, int t) {

@@ -234,7 +234,8 @@ __global__ void k_pre(HsnwModel m, const float* z, const float* ctx, int64_t row
 // Shared (dynamic): A [Kp/8][128][8] bf16, B [Kp/8][128][8] bf16.
 // ------------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-    return static_cast<uint32_t>(bf16_bits(lo)) | (static_cast<uint32_t>(bf16_bits(hi)) << 16);
+    const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);   // one conversion for both halves
+    return *reinterpret_cast<const uint32_t*>(&pair);
 }
 
 __global__ void __launch_bounds__(128) k_pre_tc(HsnwModel m, const float* z, const float* ctx, int64_t rows, float* out,
