@@ -96,7 +96,7 @@ def kernel_bytes_per_row_position(c: dict) -> dict[str, int]:
 # workload, from the ncu captures summarised in profiles/rows_kernels_c2.md (the per-row cluster
 # kernels) and profiles/phases_kernels_c2_dram.md (the phase kernels).
 NCU_TRAFFIC_PER_LAUNCH: dict[str, dict[str, float]] = {
-    "c2": {"rows_fwd": 853.6e6, "rows_bwd": 293.3e6, "front": 2.798e6, "row": 1.375e6, "unit": 3.419e6, "update": 0.526e6, "mid": 2.254e6, "tail_head": 1.703e6},
+    "c2": {"rows_fwd": 852.4e6, "rows_bwd": 293.3e6, "front": 2.798e6, "row": 1.375e6, "unit": 3.419e6, "update": 0.526e6, "mid": 2.254e6, "tail_head": 1.703e6},
 }
 
 
