@@ -191,7 +191,11 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
     const bool rec = c.io.rec_c != nullptr;
     const int stride_in = 2 * d + 4;   // a block's line of the front inbox: u part, z_hat part, max |h|
 
-    const uint32_t kStages = c.stages;
+    const uint32_t kStages = c.stages;   // 2 or 3: a ring index by a constant division or a mask, never a runtime division
+    const bool three = kStages == 3u;
+    auto ring_slot = [&](uint32_t g) { return three ? g % 3u : g & 1u; };
+    auto ring_round = [&](uint32_t g) { return three ? g / 3u : g >> 1; };
+    const int cmask = c.C - 1, cshift = __ffs(c.C) - 1;   // the cluster size is a power of two
     const RowsSmem L = rows_smem(c.m, C, c.slot_bytes, kStages);
     unsigned char* ring = dyn + L.ring + ((1024u - (smem_addr(dyn + L.ring) & 1023u)) & 1023u);
     float* h_s = reinterpret_cast<float*>(dyn + L.h);
@@ -335,7 +339,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
     uint32_t g_issue = 0, g_use = 0;   // copies issued (producer) / consumed (compute warps), in ring order
     if (producer && lane == 0) {
         for (int part = 0; part < 2; ++part) {
-            const uint32_t slot = g_issue % kStages;
+            const uint32_t slot = ring_slot(g_issue);
             mbar_expect_tx(&full[slot], c.front_bytes);
             bulk_g2s(ring + slot * c.slot_bytes, front + (static_cast<size_t>(r) * 2 + part) * c.front_bytes, c.front_bytes, &full[slot]);
             ++g_issue;
@@ -356,8 +360,8 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
             float* act = big;                     // [256]
             float* fpart = big + kFrontCols;      // [256 / d][2d]
             {
-                const uint32_t slot = g_use % kStages;
-                ring_wait(&full[slot], (g_use / kStages) & 1u, c.status, &failed_s);
+                const uint32_t slot = ring_slot(g_use);
+                ring_wait(&full[slot], ring_round(g_use) & 1u, c.status, &failed_s);
                 const uint16_t* w1c = reinterpret_cast<const uint16_t*>(ring + slot * c.slot_bytes);
                 const int col = tid, colg = r * kFrontCols + col;
                 const float sum = dot_bf16w(ue, 1, w1c + col, kFrontCols, d);
@@ -365,10 +369,10 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 act[col] = bf16r(gelu_erf(bf16r(sum + pre)));
             }
             consumer_sync();
-            if (tid == 0) mbar_arrive(&empty[g_use % kStages]);
+            if (tid == 0) mbar_arrive(&empty[ring_slot(g_use)]);
             {
-                const uint32_t slot = (g_use + 1) % kStages;
-                ring_wait(&full[slot], ((g_use + 1) / kStages) & 1u, c.status, &failed_s);
+                const uint32_t slot = ring_slot(g_use + 1);
+                ring_wait(&full[slot], ring_round(g_use + 1) & 1u, c.status, &failed_s);
                 const uint16_t* w2c = reinterpret_cast<const uint16_t*>(ring + slot * c.slot_bytes);
                 const int x = tid % d, grp = tid / d;
                 const bool is_p = r * kFrontCols + grp * d >= H;
@@ -377,7 +381,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 fpart[grp * 2 * d + d + x] = is_p ? sum : 0.0f;
             }
             consumer_sync();
-            if (tid == 0) mbar_arrive(&empty[(g_use + 1) % kStages]);
+            if (tid == 0) mbar_arrive(&empty[ring_slot(g_use + 1)]);
             g_use += 2;
             if (tid < 2 * d) {
                 float tot = 0.0f;
@@ -703,8 +707,8 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 const int n_bank = n_units * 2;
                 const int total = n_bank + (last ? 0 : 2);
                 for (int i = 0; i < total; ++i) {
-                    const uint32_t slot = g_issue % kStages;
-                    if (g_issue >= kStages) ring_wait(&empty[slot], ((g_issue / kStages) - 1u) & 1u, c.status, &failed_s);
+                    const uint32_t slot = ring_slot(g_issue);
+                    if (g_issue >= kStages) ring_wait(&empty[slot], (ring_round(g_issue) - 1u) & 1u, c.status, &failed_s);
                     const unsigned char* from;
                     uint32_t bytes;
                     if (i < n_bank) {
@@ -802,8 +806,8 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
             const uint32_t g0 = g_use;
             float bias_next = (epi && n_chunks > 0) ? c.m.b1[ulist[0] * H + r * 128 + hc] : 0.0f;   // a chunk ahead
             if (tid == 0 && n_chunks > 0) {
-                const uint32_t slot = g0 % kStages;
-                ring_wait(&full[slot], (g0 / kStages) & 1u, c.status, &failed_s);
+                const uint32_t slot = ring_slot(g0);
+                ring_wait(&full[slot], ring_round(g0) & 1u, c.status, &failed_s);
                 tcgen05_fence_after();
                 if (d == 64)
                     umma_chain_sw128<steps1, n1>(taddr, 16, umma_desc_sw128(ring + slot * c.slot_bytes), (64 * 128) >> 4,
@@ -818,10 +822,10 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 float hid_keep[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                 for (int i = 0; i < n_chunks; ++i) {
                     const unsigned mask = static_cast<unsigned>(umask[i >> 1]);
-                    const uint32_t slot = (g0 + i) % kStages;
+                    const uint32_t slot = ring_slot(g0 + i);
                     if (tid == 0 && i + 1 < n_chunks) {   // the next chunk's first product runs under this epilogue
-                        const uint32_t nslot = (g0 + i + 1) % kStages;
-                        ring_wait(&full[nslot], ((g0 + i + 1) / kStages) & 1u, c.status, &failed_s);
+                        const uint32_t nslot = ring_slot(g0 + i + 1);
+                        ring_wait(&full[nslot], ring_round(g0 + i + 1) & 1u, c.status, &failed_s);
                         tcgen05_fence_after();
                         if (d == 64)
                             umma_chain_sw128<steps1, n1>(taddr + 128 * ((i + 1) & 1), 16, umma_desc_sw128(ring + nslot * c.slot_bytes),
@@ -939,13 +943,13 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 if (hc < d) {
 #pragma unroll
                     for (int k = 0; k < kMaxK; ++k)
-                        if (k < K) peer(cl, inbox_f, k % C)[(r * Ks + k / C) * 2 * d + hc] = acc[k];
+                        if (k < K) peer(cl, inbox_f, k & cmask)[(r * Ks + (k >> cshift)) * 2 * d + hc] = acc[k];
                 }
             }
             if (n_chunks > 0) ++d2_phase;
             for (int e = tid; e < K * d; e += kConsumers) {
                 const int k = e / d, x = e - k * d;
-                peer(cl, inbox_f, k % C)[(r * Ks + k / C) * 2 * d + d + x] = gacc[e];
+                peer(cl, inbox_f, k & cmask)[(r * Ks + (k >> cshift)) * 2 * d + d + x] = gacc[e];
             }
             tcgen05_fence_before();
         }

@@ -119,6 +119,8 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
     const int T = c.io.T, Nc = c.Nc, Ks = c.Ks;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gcols = two / C;          // the gate's state outputs of this block
+    const int cmask = C - 1, cshift = __ffs(C) - 1;   // the cluster size is a power of two
+    const int gshift = __ffs(gcols) - 1;              // so is 2d / C (d is 16, 32 or 64)
     const int cell0 = r * Nc;
     const int U = K + K * D;
     const uint32_t nc_magic = 0xffffffffu / static_cast<uint32_t>(Nc) + 1u;   // n / Nc as a multiply-high
@@ -519,9 +521,9 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
                 }
             }
             for (int e = t2; e < K * gcols; e += 128) {
-                const int k = e / gcols, il = e - k * gcols;
+                const int k = e >> gshift, il = e - k * gcols;
                 const float sum = dc_[k] >= 0 ? dot_bf16w(dg_all + k * d, 1, gate + il * d, 1, d) : 0.0f;
-                peer(cl, inbox_g, k % C)[(k / C) * two + r * gcols + il] = sum;
+                peer(cl, inbox_g, k & cmask)[(k >> cshift) * two + r * gcols + il] = sum;
             }
         }
         __syncthreads();
@@ -556,7 +558,7 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
             if (i < two) {
 #pragma unroll
                 for (int k = 0; k < kMaxKB; ++k)
-                    if (k < K) peer(cl, inbox_dv, k % C)[(r * Ks + k / C) * two + i] = acc[k];
+                    if (k < K) peer(cl, inbox_dv, k & cmask)[(r * Ks + (k >> cshift)) * two + i] = acc[k];
             }
         }
         if (n_chunks > 0) ++d2_phase;
@@ -565,7 +567,7 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
         if (tid < K) {
             const int k = tid, half = k >> 2, q = k & 3;
             const float sum = red[(4 * half) * 4 + q] + red[(4 * half + 1) * 4 + q];   // warps 4 half, 4 half + 1
-            peer(cl, inbox_sig, k % C)[r * Ks + k / C] = sum;
+            peer(cl, inbox_sig, k & cmask)[r * Ks + (k >> cshift)] = sum;
         }
         BMARK(5);
         cl.sync();   // 2
