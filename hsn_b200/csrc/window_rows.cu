@@ -253,6 +253,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
     // cell n lives in block n / Nc at row n % Nc: a multiply-high by ceil(2^32 / Nc), exact for n Nc < 2^32
     const uint32_t nc_magic = 0xffffffffu / static_cast<uint32_t>(Nc) + 1u;
     auto owner_of = [&](int n) { return static_cast<int>(__umulhi(static_cast<uint32_t>(n), nc_magic)); };
+    const uint32_t md_magic = 0xffffffffu / static_cast<uint32_t>(M + d) + 1u;   // o / (M + d) the same way
     const int pre_cols = max(0, min(kFrontCols, H - r * kFrontCols));  // its columns that belong to S
     const unsigned char* bank = static_cast<const unsigned char*>(c.m.rows_bank);
     const unsigned char* front = static_cast<const unsigned char*>(c.m.rows_front);
@@ -779,10 +780,8 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 const float val = blk == 0 ? ue[x] : blk == 1 ? ue[d + x] : blk == 2 ? hold[k * d + x] : msg[k * d + x];
                 vop[((jx >> 3) * 16 + k) * 8 + (jx & 7)] = bf16_bits(val * rms[k] * norm_w[jx]);
             }
-            for (int e = tid; e < (4 * d / 8) * (16 - K); e += kConsumers) {   // the front phase used these bytes
-                const int p = e / (16 - K), k = K + e - p * (16 - K);
-                reinterpret_cast<uint4*>(vop)[p * 16 + k] = make_uint4(0u, 0u, 0u, 0u);
-            }
+            for (int e = tid; e < (4 * d / 8) * 16; e += kConsumers)   // the front phase used the padded slots' bytes
+                if ((e & 15) >= K) reinterpret_cast<uint4*>(vop)[e] = make_uint4(0u, 0u, 0u, 0u);
             fence_async_smem();   // the operand written above, before the tensor cores read it
             consumer_sync();
             RMARK(7);
@@ -1070,7 +1069,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 // the written cells' logit parts and V h, at their owners, by the five warps that have
                 // nothing else to do here; the next position reads them after its cluster barriers
                 for (int o = tid - 96; o < Ks * (M + d); o += 160) {
-                    const int kl = o / (M + d), w = o - kl * (M + d), k = kl * C + r;
+                    const int kl = static_cast<int>(__umulhi(static_cast<uint32_t>(o), md_magic)), w = o - kl * (M + d), k = kl * C + r;
                     if (k >= K || cell_of[k] < 0) continue;
                     const int cell = cell_of[k], owner = owner_of(cell), cc = cell - owner * Nc;
                     const float* hr = hb + kl * d;

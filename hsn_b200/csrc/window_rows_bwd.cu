@@ -124,6 +124,8 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
     const int cell0 = r * Nc;
     const int U = K + K * D;
     const uint32_t nc_magic = 0xffffffffu / static_cast<uint32_t>(Nc) + 1u;   // n / Nc as a multiply-high
+    const uint32_t d_magic = 0xffffffffu / static_cast<uint32_t>(D) + 1u;      // e / D the same way (the magic wraps to 0 for D = 1)
+    auto div_D = [&](int e) { return D == 1 ? e : static_cast<int>(__umulhi(static_cast<uint32_t>(e), d_magic)); };
 
     const RowsBwdSmem L = rows_bwd_smem(c.m, C, c.bank_bytes);
     unsigned char* ring = dyn + L.ring + ((1024u - (smem_addr(dyn + L.ring) & 1023u)) & 1023u);
@@ -175,10 +177,14 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
         const int64_t rt = static_cast<int64_t>(row) * T + t;
         float* rc = rec_of(buf);
         const float* srcs[7] = {c.io.c, c.io.b, c.io.h_old, c.io.y, c.io.gate_pre, c.io.m, c.io.d_h_sel};
-        for (int e = tid; e < 7 * Ks * (d / 4); e += kConsumers) {
-            const int a = e / (Ks * (d / 4)), rem = e - a * Ks * (d / 4), kl = rem / (d / 4), x4 = rem - kl * (d / 4);
-            const int k = kl * C + r;
-            if (k < K && srcs[a]) cp_async16(rc + (a * Ks + kl) * d + 4 * x4, srcs[a] + (rt * K + k) * d + 4 * x4);
+#pragma unroll
+        for (int a = 0; a < 7; ++a) {   // the array's index is a constant in every copy of the body
+            if (!srcs[a]) continue;
+            for (int e = tid; e < Ks * (d / 4); e += kConsumers) {
+                const int kl = e / (d / 4), x4 = e - kl * (d / 4);
+                const int k = kl * C + r;
+                if (k < K) cp_async16(rc + (a * Ks + kl) * d + 4 * x4, srcs[a] + (rt * K + k) * d + 4 * x4);
+            }
         }
         float* hd = hid_of(buf);
         for (int e = tid; e < K * 32; e += kConsumers) {
@@ -205,7 +211,7 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
             ld_unit = ok ? static_cast<int>(c.io.units[rt * K + tid]) : -1;
         }
         if (tid >= 32 && tid < 32 + K * D) {
-            const int e = tid - 32, k = e / D, jj = e - k * D;
+            const int e = tid - 32, k = div_D(e), jj = e - k * D;
             const bool ok = c.io.valid[rt * K + k] != 0;
             const int n = ok ? static_cast<int>(c.io.cells[rt * K + k]) : 0;
             ld_tgt = ok ? c.m.pad_src[n * D + jj] : -1;
@@ -614,7 +620,7 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
                 const int u = dc_[o_own + e];
                 const int n = u < K ? dc_[u] : dc_[o_tgt + u - K];
                 if ((n & (groups - 1)) != g) continue;   // groups is a power of two
-                const float add = u < K ? ds_all[u * d + x] : ew[u - K] * dvm_all[((u - K) / D) * d + x];
+                const float add = u < K ? ds_all[u * d + x] : ew[u - K] * dvm_all[div_D(max(u - K, 0)) * d + x];
                 A_s[(n - cell0) * d + x] += add;
             }
             if (tid < d) R_s[tid] = cut ? 0.0f : Rs[tid] + q[d + tid];
