@@ -1169,7 +1169,7 @@ static bool rows_shape(const HsnwModel& m, RowsCtx* c) {
     if (m.H % 128) return false;
     const int C = m.H / 128;
     if (C != 1 && C != 2 && C != 4 && C != 8) return false;
-    if (m.N % C || (4 * m.d) % C || m.N > 2048) return false;
+    if (m.N % C || m.N / C < 2 || (4 * m.d) % C || m.N > 2048) return false;   // (a block owns at least two cells: n / Nc is a multiply-high)
     if (m.d != 16 && m.d != 32 && m.d != 64) return false;
     if (m.K > kMaxK || m.M > kMaxMR || m.K < 1 || m.S > 16 || m.S < 1) return false;
     if (((m.N / C) * m.S) % 4) return false;   // the position's scalars of a block's cells move as one 16-byte aligned bulk copy

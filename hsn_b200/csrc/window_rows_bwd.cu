@@ -651,7 +651,7 @@ static bool rows_bwd_shape(const HsnwModel& m, RowsBwdCtx* c) {
     if (m.H % 128) return false;
     const int C = m.H / 128;
     if (C != 1 && C != 2 && C != 4 && C != 8) return false;
-    if (m.N % C || (2 * m.d) % C || kConsumers % (2 * m.d / C)) return false;
+    if (m.N % C || m.N / C < 2 || (2 * m.d) % C || kConsumers % (2 * m.d / C)) return false;
     if (m.d != 16 && m.d != 32 && m.d != 64) return false;
     if (m.K > kMaxKB || m.M > kMaxMB || m.K < 1 || m.K * m.D > 96 || m.K * (2 * m.d / C) > kConsumers) return false;
     c->C = C;
