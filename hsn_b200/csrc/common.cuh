@@ -151,6 +151,13 @@ __device__ __forceinline__ void dot4_rows(const float* a, int lda, int rows, con
 #pragma unroll
     for (int r = 0; r < 4; ++r) out[r] = (s[r][0] + s[r][1]) + (s[r][2] + s[r][3]);
 }
+// e / n for a run-time n >= 2 as one multiply-high: magic_of(n) = ceil(2^32 / n), exact while e n < 2^32
+// (an integer division by a run-time value costs about twenty instructions, and the index arithmetic
+// of the element loops is full of them).
+__device__ __forceinline__ uint32_t magic_of(int n) { return 0xffffffffu / static_cast<uint32_t>(n) + 1u; }
+__device__ __forceinline__ int div_magic(int e, uint32_t magic) {
+    return static_cast<int>(__umulhi(static_cast<uint32_t>(e), magic));
+}
 // sum_i a[i * sa], i < n, the same way.
 __device__ __forceinline__ float sum4(const float* a, int64_t sa, int n) {
     float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;

@@ -72,6 +72,7 @@ struct BwdCtx {
 // ------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void head_phase(const BwdCtx& c, int t, unsigned char* dyn) {
     const int N = c.m.N, d = c.m.d, K = c.m.K, T = c.io.T;
+    const uint32_t dmag = magic_of(d);   // e / d as a multiply-high
     const bool full = c.io.full_cut != 0;
     const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
     const int lane = tid & 31, warp = tid >> 5, warps = nt >> 5;
@@ -90,7 +91,7 @@ __device__ __forceinline__ void head_phase(const BwdCtx& c, int t, unsigned char
     const uint8_t* valid = c.io.valid + rt * K;
     const int64_t o0 = rt * K * d;
     if (!full) {
-        for (int e = tid; e < d * d; e += nt) cp_async4(wo + (e / d) * (d + 1) + (e % d), c.m.wout_t + e);
+        for (int e = tid; e < d * d; e += nt) cp_async4(wo + (div_magic(e, dmag)) * (d + 1) + (e - div_magic(e, dmag) * d), c.m.wout_t + e);
         cp_async_commit();   // needed only by the last step of the phase
     }
     for (int x = tid; x < d; x += nt) {
@@ -104,7 +105,7 @@ __device__ __forceinline__ void head_phase(const BwdCtx& c, int t, unsigned char
     BW_MARK(9);
     const float n_f = static_cast<float>(N);
     for (int e = tid; e < K * d; e += nt) {
-        const int k = e / d, x = e - k * d;
+        const int k = div_magic(e, dmag), x = e - k * d;
         const int n = cell_of[k];
         float dcv = 0.0f, dbv = 0.0f, dz = 0.0f, dgv = 0.0f, yv = 0.0f, sgv = 0.0f;
         if (n >= 0) {
@@ -169,7 +170,7 @@ __device__ __forceinline__ void head_phase(const BwdCtx& c, int t, unsigned char
     __syncthreads();
     // dy = rho (cand_w dz) - rho^3 y mean(y cand_w dz), in place of dzs
     for (int e = tid; e < K * d; e += nt) {
-        const int k = e / d;
+        const int k = div_magic(e, dmag);
         const float r = rho[k];
         dzs[e] = cell_of[k] >= 0 ? r * dzs[e] - r * r * r * ysv[e] * dot[k] : 0.0f;
     }
@@ -180,7 +181,7 @@ __device__ __forceinline__ void head_phase(const BwdCtx& c, int t, unsigned char
     // d_unit = dy W_out (the transposed output projection): y[x] = sum_i F[i] wout_t[i][x]
     const int per = max(1, min(4, K * d / nt));   // slots a thread: a weight is read once for them
     for (int e = tid; e < ((K + per - 1) / per) * d; e += nt) {
-        const int k0 = (e / d) * per, i = e - (e / d) * d;
+        const int k0 = (div_magic(e, dmag)) * per, i = e - (div_magic(e, dmag)) * d;
         float out[4];
         dot4_rows(dzs + k0 * d, d, min(per, K - k0), wo + i * (d + 1), 1, d, out);
         for (int r = 0; r < per && k0 + r < K; ++r) c.d_unit[(static_cast<int64_t>(row) * K + k0 + r) * d + i] = out[r];
@@ -202,6 +203,7 @@ __global__ void __launch_bounds__(256) k_mid(BwdCtx c, int t) {
     __shared__ int warp_count[8];
     __shared__ int n_list;
     const int d = c.m.d, K = c.m.K, H = c.m.H, in = 4 * c.m.d, two = 2 * c.m.d;
+    const uint32_t dmag = magic_of(d);   // e / d as a multiply-high
     const int P = c.io.B * K, T = c.io.T;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const bool bf = c.m.prod_bf16 != 0;  // the products' operands are rounded as on the tensor cores
@@ -237,14 +239,14 @@ __global__ void __launch_bounds__(256) k_mid(BwdCtx c, int t) {
     if (is_gate) {
         // the gate's transposed linear on the state columns: gate_pre[x] = sum_i v[i] gate_t[i][x]
         for (int e = tid; e < two * d; e += 256) {
-            const int i = e / d, x = e - i * d;
+            const int i = div_magic(e, dmag), x = e - i * d;
             wA[i * (d + 1) + x] = c.m.gate_t[static_cast<int64_t>(two + i) * d + x];
         }
         for (int base = 0; base < count; base += kPB) {
             const int nb = min(kPB, count - base);
             __syncthreads();
             for (int e = tid; e < nb * d; e += 256) {
-                const int pb = e / d, x = e - pb * d;
+                const int pb = div_magic(e, dmag), x = e - pb * d;
                 du[e] = maybe_bf16(c.dg[static_cast<int64_t>(list[base + pb]) * d + x], bf);
             }
             __syncthreads();
@@ -259,7 +261,7 @@ __global__ void __launch_bounds__(256) k_mid(BwdCtx c, int t) {
     const float* W1 = c.m.w1 + static_cast<int64_t>(j) * in * H;
     const float* W2 = c.m.w2 + static_cast<int64_t>(j) * H * d;
     for (int e = tid; e < kUS * d; e += 256) {
-        const int cc = e / d, x = e - cc * d;
+        const int cc = div_magic(e, dmag), x = e - cc * d;
         wA[cc * (d + 1) + x] = cc < cols ? W2[static_cast<int64_t>(c0 + cc) * d + x] : 0.0f;
     }
     for (int e = tid; e < two * kUS; e += 256) {
@@ -271,7 +273,7 @@ __global__ void __launch_bounds__(256) k_mid(BwdCtx c, int t) {
         const int nb = min(kPB, count - base);
         __syncthreads();
         for (int e = tid; e < nb * d; e += 256) {
-            const int pb = e / d, x = e - pb * d;
+            const int pb = div_magic(e, dmag), x = e - pb * d;
             du[e] = maybe_bf16(c.d_unit[static_cast<int64_t>(list[base + pb]) * d + x], bf);
         }
         __syncthreads();
@@ -519,6 +521,7 @@ __global__ void __launch_bounds__(256) k_mid_tc(BwdCtx c, int t) {
 // ------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tail_phase(const BwdCtx& c, int t, unsigned char* dyn) {
     const int N = c.m.N, d = c.m.d, K = c.m.K, D = c.m.D, T = c.io.T, two = 2 * c.m.d;
+    const uint32_t dmag = magic_of(d);   // e / d as a multiply-high
     const int P = c.io.B * K, U = K + K * D;
     const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
     float* stage = reinterpret_cast<float*>(dyn);   // [U][d] the rows of A this position touches
@@ -536,7 +539,7 @@ __device__ __forceinline__ void tail_phase(const BwdCtx& c, int t, unsigned char
     float* R = c.io.R + static_cast<int64_t>(row) * d;
     const float in_dim = static_cast<float>(4 * d);
     BW_MARK(0);
-    for (int e = tid; e < d * d; e += nt) cp_async4(vt + (e / d) * (d + 1) + (e % d), c.m.v_t + e);
+    for (int e = tid; e < d * d; e += nt) cp_async4(vt + (div_magic(e, dmag)) * (d + 1) + (e - div_magic(e, dmag) * d), c.m.v_t + e);
     cp_async_commit();   // in flight while the position's values are gathered
     for (int k = tid; k < K; k += nt) {
         const bool ok = c.io.valid[rt * K + k] != 0;
@@ -613,13 +616,13 @@ __device__ __forceinline__ void tail_phase(const BwdCtx& c, int t, unsigned char
     // the touched rows of A, each loaded once (all loads in flight together)
 #pragma unroll 4
     for (int e = tid; e < U * d; e += nt) {
-        const int u = e / d, x = e - u * d;
+        const int u = div_magic(e, dmag), x = e - u * d;
         if (tgt[u] >= 0 && first[u] == u) stage[e] = A[static_cast<int64_t>(tgt[u]) * d + x];
     }
     // dvm = dm V: m = sum_e a_e (V h_src), (V h)[x] = sum_i h[i] v_t[i][x]
     const int per = max(1, min(4, K * d / nt));   // slots a thread: a weight is read once for them
     for (int e = tid; e < ((K + per - 1) / per) * d; e += nt) {
-        const int k0 = (e / d) * per, i = e - (e / d) * d;
+        const int k0 = (div_magic(e, dmag)) * per, i = e - (div_magic(e, dmag)) * d;
         float out[4];
         dot4_rows(ds + k0 * two + d, two, min(per, K - k0), vt + i * (d + 1), 1, d, out);
         for (int r = 0; r < per && k0 + r < K; ++r) dvm[(k0 + r) * d + i] = out[r];
@@ -633,7 +636,7 @@ __device__ __forceinline__ void tail_phase(const BwdCtx& c, int t, unsigned char
     int G = 1;
     while (2 * G * d <= nt) G *= 2;   // a power of two: the group of a row is a mask, not a division
     for (int e = tid; e < G * d; e += nt) {
-        const int g = e / d, x = e - g * d;
+        const int g = div_magic(e, dmag), x = e - g * d;
         for (int k = 0; k < K; ++k) {
             const int f = first[k];
             if (tgt[k] >= 0 && (f & (G - 1)) == g) stage[f * d + x] += ds[k * two + x];
@@ -657,7 +660,7 @@ __device__ __forceinline__ void tail_phase(const BwdCtx& c, int t, unsigned char
         for (int e = tid; e < N * d; e += nt) A[e] = 0.0f;
     } else {
         for (int e = tid; e < U * d; e += nt) {
-            const int u = e / d, x = e - u * d;
+            const int u = div_magic(e, dmag), x = e - u * d;
             if (tgt[u] >= 0 && first[u] == u) A[static_cast<int64_t>(tgt[u]) * d + x] = stage[e];
         }
     }

@@ -310,6 +310,7 @@ __global__ void __launch_bounds__(128) k_pre_tc(HsnwModel m, const float* z, con
 __global__ void __launch_bounds__(256) k_front(FwdCtx c, int t) {
     extern __shared__ __align__(16) unsigned char dyn[];
     const int d = c.m.d, H = c.m.H, B = c.io.B, T = c.io.T, N = c.m.N;
+    const uint32_t dmag = magic_of(d);   // e / d as a multiply-high
     const bool bf = c.m.prod_bf16 != 0;
     const int tid = threadIdx.x;
     if (static_cast<int>(blockIdx.x) >= c.n_front) {
@@ -356,12 +357,12 @@ __global__ void __launch_bounds__(256) k_front(FwdCtx c, int t) {
             w1[e] = cc < cols ? c.m.f_w1q_t[static_cast<int64_t>(x) * 2 * H + col_base + cc] : 0.0f;
         }
         for (int e = tid; e < kFS * d; e += 256) {
-            const int cc = e / d, x = e - cc * d;
+            const int cc = div_magic(e, dmag), x = e - cc * d;
             w2[e] = cc < cols ? c.m.f_w2_t[static_cast<int64_t>(col_base + cc) * d + x] : 0.0f;
         }
     }
     for (int e = tid; e < rows * d; e += 256) {
-        const int r = e / d, x = e - r * d;
+        const int r = div_magic(e, dmag), x = e - r * d;
         qs[e] = maybe_bf16(state_q(c, r0 + r, t)[x], bf);
     }
     // thread (r, cc) serves rows r, r + 8, ... of the tile: a weight is read once for them
@@ -401,7 +402,7 @@ __global__ void __launch_bounds__(256) k_front(FwdCtx c, int t) {
     __syncthreads();
     if (rows <= 8) {
         for (int e = tid; e < rows * d; e += 256) {
-            const int r = e / d, x = e - r * d;
+            const int r = div_magic(e, dmag), x = e - r * d;
             float sum = 0.0f;
 #pragma unroll 8
             for (int cc = 0; cc < kFS; ++cc) sum += act[r * kFS + cc] * w2[cc * d + x];
@@ -410,7 +411,7 @@ __global__ void __launch_bounds__(256) k_front(FwdCtx c, int t) {
     } else {
         // four rows a thread (r4, r4 + 1, .. of a group of four): a weight is read once for them
         for (int e = tid; e < ((rows + 3) / 4) * d; e += 256) {
-            const int g = e / d, x = e - g * d;
+            const int g = div_magic(e, dmag), x = e - g * d;
             float sum[4] = {};
 #pragma unroll 8
             for (int cc = 0; cc < kFS; ++cc) {
@@ -532,6 +533,7 @@ __global__ void __launch_bounds__(512, 2) k_row(FwdCtx c, int t) {
     __shared__ int ired[32];
     __shared__ __align__(8) uint64_t bar;
     const int N = c.m.N, d = c.m.d, K = c.m.K, M = c.m.M, D = c.m.D, Sn = c.m.S;
+    const uint32_t dmag = magic_of(d);   // e / d as a multiply-high
     const int T = c.io.T;
     const bool bf = c.m.prod_bf16 != 0;
     const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
@@ -711,7 +713,7 @@ __global__ void __launch_bounds__(512, 2) k_row(FwdCtx c, int t) {
             mbar_wait(&bar, 1, c.status);
         } else {
             for (int e = tid; e < nrows * d; e += nt) {
-                const int r = e / d, x = e - r * d;
+                const int r = div_magic(e, dmag), x = e - r * d;
                 rows[e] = r < K ? h[static_cast<int64_t>(S.out_cell[r]) * d + x] : g_vh[static_cast<int64_t>(src[r - K]) * d + x];
             }
         }
@@ -719,7 +721,7 @@ __global__ void __launch_bounds__(512, 2) k_row(FwdCtx c, int t) {
     __syncthreads();
     HSNW_MARK(2, 6);
     for (int e = tid; e < K * d; e += nt) {
-        const int k = e / d, x = e - k * d;
+        const int k = div_magic(e, dmag), x = e - k * d;
         float sum = 0.0f;
         for (int j = 0; j < D; ++j) sum += rows[(K + k * D + j) * d + x] * ew[k * D + j];  // edge order
         msg[e] = maybe_bf16(sum, bf);
@@ -729,7 +731,7 @@ __global__ void __launch_bounds__(512, 2) k_row(FwdCtx c, int t) {
     for (int k = warp; k < K; k += warps) {
         float sq = 0.0f;
         for (int j = lane; j < 4 * d; j += 32) {
-            const int blk = j / d, x = j - blk * d;
+            const int blk = div_magic(j, dmag), x = j - blk * d;
             const float v = blk == 0 ? ue[x] : blk == 1 ? ue[d + x] : blk == 2 ? rows[k * d + x] : msg[k * d + x];
             sq += v * v;
         }
@@ -740,7 +742,7 @@ __global__ void __launch_bounds__(512, 2) k_row(FwdCtx c, int t) {
     const int64_t pair0 = static_cast<int64_t>(row) * K;
     for (int e = tid; e < K * 4 * d; e += nt) {
         const int k = e / (4 * d), j = e - k * 4 * d;
-        const int blk = j / d, x = j - blk * d;
+        const int blk = div_magic(j, dmag), x = j - blk * d;
         const float v = blk == 0 ? ue[x] : blk == 1 ? ue[d + x] : blk == 2 ? rows[k * d + x] : msg[k * d + x];
         c.v[(pair0 + k) * 4 * d + j] = maybe_bf16(v * rms[k] * c.m.norm_w[j], bf);
     }
@@ -767,6 +769,7 @@ __global__ void __launch_bounds__(256) k_unit(FwdCtx c, int t) {
     __shared__ int warp_count[8];
     __shared__ int n_list;
     const int d = c.m.d, K = c.m.K, H = c.m.H, in = 4 * c.m.d;
+    const uint32_t dmag = magic_of(d);   // e / d as a multiply-high
     const int P = c.io.B * K, T = c.io.T;
     const bool bf = c.m.prod_bf16 != 0;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -814,7 +817,7 @@ __global__ void __launch_bounds__(256) k_unit(FwdCtx c, int t) {
             w1[e] = cc < cols ? W1[static_cast<int64_t>(x) * H + c0 + cc] : 0.0f;
         }
         for (int e = tid; e < kUS * d; e += 256) {
-            const int cc = e / d, x = e - cc * d;
+            const int cc = div_magic(e, dmag), x = e - cc * d;
             w2[e] = cc < cols ? W2[static_cast<int64_t>(c0 + cc) * d + x] : 0.0f;
         }
     }
@@ -825,7 +828,7 @@ __global__ void __launch_bounds__(256) k_unit(FwdCtx c, int t) {
         const int nb = min(kPB, count - base);
         __syncthreads();
         for (int f = tid; f < nb * d; f += 256) {  // a pair's input is 4d floats = d float4
-            const int pb = f / d, x4 = f - pb * d;
+            const int pb = div_magic(f, dmag), x4 = f - pb * d;
             vbuf4[f] = v4[static_cast<int64_t>(list[base + pb]) * d + x4];
         }
         __syncthreads();
@@ -864,7 +867,7 @@ __global__ void __launch_bounds__(256) k_unit(FwdCtx c, int t) {
         if (is_gate) continue;
         __syncthreads();
         for (int e = tid; e < nb * d; e += 256) {
-            const int pb = e / d, x = e - pb * d;
+            const int pb = div_magic(e, dmag), x = e - pb * d;
             float sum = 0.0f;
 #pragma unroll 8
             for (int k2 = 0; k2 < kUS; ++k2) sum += act[pb * kUS + k2] * w2[k2 * d + x];
@@ -1092,6 +1095,7 @@ __global__ void __launch_bounds__(512) k_update(FwdCtx c, int t) {
     __shared__ int ired[16];
     __shared__ int zero_slot;
     const int N = c.m.N, d = c.m.d, K = c.m.K, M = c.m.M;
+    const uint32_t dmag = magic_of(d);   // e / d as a multiply-high
     const int B = c.io.B, T = c.io.T, P = B * K;
     const bool bf = c.m.prod_bf16 != 0;
     const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
@@ -1135,7 +1139,7 @@ __global__ void __launch_bounds__(512) k_update(FwdCtx c, int t) {
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             const int e = e0 + u * nt;
-            const int k = min(e / d, K - 1), x = e - (e / d) * d;
+            const int k = min(div_magic(e, dmag), K - 1), x = e - (div_magic(e, dmag)) * d;
             ok[u] = e < K * d && cell_of[k] >= 0;
             from[u] = ok[u] ? c.part_f + (pair0 + k) * d + x : c.part_f;   // a padded slot's sum is not used
             bias[u] = ok[u] ? c.m.b2[static_cast<int>(units[k]) * d + x] : 0.0f;
@@ -1164,7 +1168,7 @@ __global__ void __launch_bounds__(512) k_update(FwdCtx c, int t) {
     {
         const int per = max(1, min(4, K * d / nt));   // slots a thread: a weight is read once for them
         for (int e = tid; e < ((K + per - 1) / per) * d; e += nt) {
-            const int k0 = (e / d) * per, x = e - (e / d) * d;
+            const int k0 = (div_magic(e, dmag)) * per, x = e - (div_magic(e, dmag)) * d;
             float out[4];
             dot4_rows(Fs + k0 * d, d, min(per, K - k0), wo + x, d, d, out);
             for (int r = 0; r < per && k0 + r < K; ++r) ys[(k0 + r) * d + x] = maybe_bf16(out[r], bf);
@@ -1183,7 +1187,7 @@ __global__ void __launch_bounds__(512) k_update(FwdCtx c, int t) {
     int top = 0;
     HSNW_MARK(1, 3);
     for (int e = tid; e < K * d; e += nt) {
-        const int k = e / d, x = e - k * d;
+        const int k = div_magic(e, dmag), x = e - k * d;
         const int n = cell_of[k];
         float value = 0.0f, change = 0.0f, cv = 0.0f, bv = 0.0f, gp = 0.0f;
         if (n >= 0) {
@@ -1214,7 +1218,7 @@ __global__ void __launch_bounds__(512) k_update(FwdCtx c, int t) {
     HSNW_MARK(1, 4);
     if (!clear) {
         for (int e = tid; e < K * d; e += nt) {
-            const int k = e / d, x = e - k * d;
+            const int k = div_magic(e, dmag), x = e - k * d;
             if (cell_of[k] >= 0) h_write[static_cast<int64_t>(cell_of[k]) * d + x] = hnew[e];
         }
         // the written cells' derived state: 32 threads a slot
@@ -1246,7 +1250,7 @@ __global__ void __launch_bounds__(512) k_update(FwdCtx c, int t) {
         q_next[x] = clear ? 0.0f : after;
     }
     for (int e = tid; e < K * d; e += nt) {
-        const int k = e / d, x = e - k * d;
+        const int k = div_magic(e, dmag), x = e - k * d;
         float value;
         if (cell_of[k] >= 0) value = hnew[e];
         else value = zero_slot >= 0 ? hnew[zero_slot * d + x] : h[x];
