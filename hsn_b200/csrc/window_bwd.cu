@@ -521,6 +521,7 @@ __global__ void __launch_bounds__(256) k_mid_tc(BwdCtx c, int t) {
 // ------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tail_phase(const BwdCtx& c, int t, unsigned char* dyn) {
     const int N = c.m.N, d = c.m.d, K = c.m.K, D = c.m.D, T = c.io.T, two = 2 * c.m.d;
+    const uint32_t twomag = magic_of(2 * c.m.d);
     const uint32_t dmag = magic_of(d);   // e / d as a multiply-high
     const int P = c.io.B * K, U = K + K * D;
     const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
@@ -580,7 +581,7 @@ __device__ __forceinline__ void tail_phase(const BwdCtx& c, int t, unsigned char
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             const int e = e0 + u * nt;
-            const int k = min(e / two, K - 1), i = e - (e / two) * two;
+            const int k = min(div_magic(e, twomag), K - 1), i = e - div_magic(e, twomag) * two;
             const bool ok = e < K * two && cell_of[k] >= 0;
             from[u] = ok ? c.part_dv + (pair0 + k) * two + i : c.part_dv;   // a padded slot's sum is not used
             state[u] = !ok ? 0.0f : i < d ? c.io.h_old[(rt * K + k) * d + i] : c.io.m[(rt * K + k) * d + i - d];
@@ -605,7 +606,7 @@ __device__ __forceinline__ void tail_phase(const BwdCtx& c, int t, unsigned char
         for (int u = 0; u < 4; ++u) {
             const int e = e0 + u * nt;
             if (e >= K * two) continue;
-            const int k = e / two, i = e - k * two;
+            const int k = div_magic(e, twomag), i = e - k * two;
             ds[e] = cell_of[k] >= 0 ? c.io.rms[rt * K + k] * (c.m.norm_w[two + i] * dv[u]) - back[k] * state[u] : 0.0f;
         }
     }

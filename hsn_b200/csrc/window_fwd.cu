@@ -741,7 +741,7 @@ __global__ void __launch_bounds__(512, 2) k_row(FwdCtx c, int t) {
     __syncthreads();
     const int64_t pair0 = static_cast<int64_t>(row) * K;
     for (int e = tid; e < K * 4 * d; e += nt) {
-        const int k = e / (4 * d), j = e - k * 4 * d;
+        const int k = div_magic(e, magic_of(4 * d)), j = e - k * 4 * d;
         const int blk = div_magic(j, dmag), x = j - blk * d;
         const float v = blk == 0 ? ue[x] : blk == 1 ? ue[d + x] : blk == 2 ? rows[k * d + x] : msg[k * d + x];
         c.v[(pair0 + k) * 4 * d + j] = maybe_bf16(v * rms[k] * c.m.norm_w[j], bf);
