@@ -78,6 +78,7 @@ class HsnwBackward(Structure):
 SYMBOLS: dict[str, tuple[object, list[object]]] = {
     "hsnw_version": (c_int, []),
     "hsnw_last_error": (c_char_p, []),
+    "hsnw_last_path": (c_char_p, []),
     "hsnw_prepare": (c_int, [c_int]),
     "hsnw_prepared": (c_int, [c_int]),
     "hsnw_sm_count": (c_int, [c_int]),
@@ -99,6 +100,7 @@ SYMBOLS: dict[str, tuple[object, list[object]]] = {
     "hsnw_static_scratch_bytes": (c_int64, []),
     "hsnw_window_backward_static": (c_int, [POINTER(HsnwModel), POINTER(HsnwBackward), c_void_p]),
     "hsnw_front_projection": (c_int, [POINTER(HsnwModel), c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+    "hsnw_selftest_wait_timeout": (c_int, [c_void_p, c_void_p]),
     "hsnw_profile_begin": (c_int, []),
     "hsnw_profile_kinds": (c_int, []),
     "hsnw_profile_kind_name": (c_char_p, [c_int]),

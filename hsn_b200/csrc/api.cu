@@ -21,6 +21,7 @@ namespace {
 
 constexpr int kMaxDevices = 64;
 thread_local char last_error[512] = "";
+thread_local int last_path = HSNW_PATH_NONE;
 std::mutex prepare_mutex;
 struct DeviceInfo {
     bool ready = false;
@@ -117,6 +118,11 @@ void hsnw_ops_set_attributes() {
 extern "C" int hsnw_version(void) { return 100; }
 
 extern "C" const char* hsnw_last_error(void) { return last_error; }
+
+void hsnw_set_path(int path) { last_path = path; }
+extern "C" const char* hsnw_last_path(void) {
+    return last_path == HSNW_PATH_ROWS ? "rows" : last_path == HSNW_PATH_PHASES ? "phases" : "";
+}
 
 extern "C" int hsnw_prepare(int device) {
     if (device < 0 || device >= kMaxDevices) return hsnw_fail(HSNW_E_ARG, "prepare: device out of range");

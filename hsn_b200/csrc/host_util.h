@@ -25,13 +25,19 @@ void hsnw_ops_set_attributes();
 void hsnw_rows_set_attributes();
 void hsnw_rows_bwd_set_attributes();
 struct HsnwBackward;
-// The reverse sweep by one persistent cluster per row (window_rows_bwd.cu): same return convention.
-int hsnw_rows_backward(const HsnwModel* model, const HsnwBackward* io, cudaStream_t stream);
 struct HsnwModel;
 struct HsnwForward;
-// The forward sweep by one persistent cluster per row (window_rows.cu): HSNW_OK when launched, -1 when
-// the shape does not fit that kernel (the caller runs the phases instead), else an error code.
+// What the per-row cluster kernels answer when a shape does not fit them: not an error (every HSNW_E_*
+// is negative and is passed on to the caller), the entry point then runs the batch-synchronous phases.
+constexpr int HSNW_DECLINED = 1;
+// The forward sweep by one persistent cluster per row (window_rows.cu): HSNW_OK when launched,
+// HSNW_DECLINED when the shape does not fit that kernel, else a negative error code.
 int hsnw_rows_forward(const HsnwModel* model, const HsnwForward* io, const float* pre_s, int* status, cudaStream_t stream);
+// The reverse sweep by one persistent cluster per row (window_rows_bwd.cu): same return convention.
+int hsnw_rows_backward(const HsnwModel* model, const HsnwBackward* io, int* status, cudaStream_t stream);
+// Which kernels served the calling thread's last whole-window call (hsnw_last_path reports it).
+enum HsnwPath { HSNW_PATH_NONE = 0, HSNW_PATH_ROWS = 1, HSNW_PATH_PHASES = 2 };
+void hsnw_set_path(int path);
 
 // Launch timing for measurement runs (hsnw_profile_begin / hsnw_profile_end): while it is on, every
 // launch site records an event on its stream first; the time between two consecutive events is

@@ -251,95 +251,261 @@ extern "C" __global__ void hsn_win_cell_update(HsnWinArgs a) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// hsn_win_recurrence: the full-cut backward state recurrence of a window, t = T-1 .. 0, with the
-// row's cotangents A [N,d] and R [d] in shared memory.
+// hsn_win_recurrence: the full-cut backward state recurrence of a window (reference semantics:
+// python/hsn/train/split.py:128-174), t = T-1 .. 0, one block per row.
 //   p: 0 c, 1 b, 2 h_old [B,T,K,d] f32; 3 cells [B,T,K] i64; 4 valid [B,T,K] u8; 5 reset [B,T] u8;
 //      6 d_q_pre, 7 d_q_post [B,T,d], 8 d_h_sel [B,T,K,d] (read when flagged); 9 dc, 10 db out.
 //      This library adds (zero in the reference's calls): 11 A [B,N,d], 12 R [B,d] in/out.
 //   i: 0 B, 1 T, 2 K, 3 d, 4 N, 5 has_pre, 6 has_post, 7 has_sel, 8 carry: start from p11/p12 and
 //      store the final cotangents there (zeroed on rows whose position 0 resets).
-// Dynamic shared memory: (N + 1) d words (up to 227 KB after hsnw_prepare).
+// Dynamic shared memory: (N + 1) d words (up to 227 KB after hsnw_prepare): the row's cotangent A.
+//
+// How the work is laid out. A position touches only the K selected cells, and along the state
+// width every column is independent. A thread owns one (slot, group of V columns) item, V = 4 when
+// d is a multiple of 4 (16-byte loads and stores) and 1 otherwise; it keeps the summary's
+// cotangent R for its own columns in registers (every item of a column group adds the same
+// d_q_post / d_q_pre, so the copies stay equal and R never crosses threads). The valid slots of a
+// position name distinct cells, so a position's items never meet in A; across positions a cell
+// may change hands, hence ONE block barrier a position. The position's record is loaded into
+// registers one position ahead, so the loads of t-1 are in flight under the arithmetic of t.
 // ------------------------------------------------------------------------------------------------
-extern "C" __global__ void hsn_win_recurrence(HsnWinArgs a) {
-    extern __shared__ __align__(16) unsigned char dyn[];
-    const int T = a.i[1], K = a.i[2], d = a.i[3], N = a.i[4];
-    const bool has_pre = a.i[5] != 0, has_post = a.i[6] != 0, has_sel = a.i[7] != 0, carry = a.i[8] != 0;
-    const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
-    const float* c = static_cast<const float*>(a.p[0]);
-    const float* b = static_cast<const float*>(a.p[1]);
-    const float* h_old = static_cast<const float*>(a.p[2]);
-    const int64_t* cells = static_cast<const int64_t*>(a.p[3]);
-    const uint8_t* valid = static_cast<const uint8_t*>(a.p[4]);
-    const uint8_t* reset = static_cast<const uint8_t*>(a.p[5]);
-    const float* pre = static_cast<const float*>(a.p[6]);
-    const float* post = static_cast<const float*>(a.p[7]);
-    const float* sel = static_cast<const float*>(a.p[8]);
-    float* dc = static_cast<float*>(a.p[9]);
-    float* db = static_cast<float*>(a.p[10]);
-    float* A = reinterpret_cast<float*>(dyn);
-    float* R = A + static_cast<int64_t>(N) * d;
-    if (carry) {
-        block_copy_f32(A, static_cast<const float*>(a.p[11]) + static_cast<int64_t>(row) * N * d, N * d);
-        for (int x = tid; x < d; x += nt) R[x] = static_cast<const float*>(a.p[12])[static_cast<int64_t>(row) * d + x];
+namespace {
+
+template <int V>
+struct Pack {
+    float v[V];
+};
+template <int V>
+__device__ __forceinline__ Pack<V> load_pack(const float* p) {
+    Pack<V> r;
+    if constexpr (V == 4) {
+        const float4 q = *reinterpret_cast<const float4*>(p);
+        r.v[0] = q.x; r.v[1] = q.y; r.v[2] = q.z; r.v[3] = q.w;
     } else {
-        for (int e = tid; e < N * d; e += nt) A[e] = 0.0f;
-        for (int x = tid; x < d; x += nt) R[x] = 0.0f;
+        r.v[0] = *p;
+    }
+    return r;
+}
+template <int V>
+__device__ __forceinline__ void store_pack(float* p, const Pack<V>& r) {
+    if constexpr (V == 4) *reinterpret_cast<float4*>(p) = make_float4(r.v[0], r.v[1], r.v[2], r.v[3]);
+    else *p = r.v[0];
+}
+template <int V>
+__device__ __forceinline__ Pack<V> zero_pack() {
+    Pack<V> r;
+#pragma unroll
+    for (int i = 0; i < V; ++i) r.v[i] = 0.0f;
+    return r;
+}
+
+// What one item reads at one position.
+template <int V>
+struct RecurrenceItem {
+    Pack<V> c, b, h_old, sel, pre, post;
+    int cell;      // -1 on a padded slot: its values never enter (a select, not a product with a mask)
+    bool cut;
+};
+
+struct RecurrenceArgs {
+    const float *c, *b, *h_old, *pre, *post, *sel;
+    const int64_t* cells;
+    const uint8_t *valid, *reset;
+    float *dc, *db;
+    int T, K, d, N;
+    bool has_pre, has_post, has_sel;
+};
+
+template <int V>
+__device__ __forceinline__ RecurrenceItem<V> recurrence_fetch(const RecurrenceArgs& g, int row, int t, int k, int x) {
+    RecurrenceItem<V> it;
+    const int64_t rt = static_cast<int64_t>(row) * g.T + t, slot = rt * g.K + k, at = slot * g.d + x;
+    it.cell = g.valid[slot] ? static_cast<int>(g.cells[slot]) : -1;
+    it.cut = g.reset[rt] != 0;
+    it.c = load_pack<V>(g.c + at);
+    it.b = load_pack<V>(g.b + at);
+    it.h_old = load_pack<V>(g.h_old + at);
+    it.sel = g.has_sel ? load_pack<V>(g.sel + at) : zero_pack<V>();
+    it.pre = g.has_pre ? load_pack<V>(g.pre + rt * g.d + x) : zero_pack<V>();
+    it.post = g.has_post ? load_pack<V>(g.post + rt * g.d + x) : zero_pack<V>();
+    return it;
+}
+
+// One row's sweep when there are more items than threads (K d / V > blockDim.x): the items are taken in
+// rounds, R stays in shared memory (row N of A) and a position costs two barriers.
+template <int V>
+__device__ void recurrence_row_rounds(const RecurrenceArgs& g, float* A, int row, bool carry) {
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const int per_slot = g.d / V, items = g.K * per_slot;
+    const float n_f = static_cast<float>(g.N);
+    float* R = A + static_cast<int64_t>(g.N) * g.d;
+    for (int t = g.T - 1; t >= 0; --t) {
+        const int64_t rt = static_cast<int64_t>(row) * g.T + t;
+        for (int item = tid; item < items; item += nt) {
+            const int k = item / per_slot, x = (item - k * per_slot) * V;
+            const RecurrenceItem<V> it = recurrence_fetch<V>(g, row, t, k, x);
+            Pack<V> dcv = zero_pack<V>(), dbv = zero_pack<V>();
+            if (it.cell >= 0) {
+                float* a = A + static_cast<int64_t>(it.cell) * g.d + x;
+#pragma unroll
+                for (int i = 0; i < V; ++i) {
+                    const float carried = a[i] + it.sel.v[i];
+                    const float share = (R[x + i] + it.post.v[i]) / n_f;
+                    const float grad = carried + share;
+                    dcv.v[i] = it.b.v[i] * grad;
+                    dbv.v[i] = (it.c.v[i] - it.h_old.v[i]) * grad;
+                    a[i] = (1.0f - it.b.v[i]) * carried - it.b.v[i] * share;
+                }
+            }
+            const int64_t at = (rt * g.K + k) * g.d + x;
+            store_pack<V>(g.dc + at, dcv);
+            store_pack<V>(g.db + at, dbv);
+        }
+        __syncthreads();   // every item has read R; the cells' new values are in place
+        const bool clear = g.reset[rt] != 0 && !(carry && t == 0);
+        for (int x = tid; x < g.d; x += nt) {
+            float r = R[x];
+            if (g.has_post) r += g.post[rt * g.d + x];
+            if (g.has_pre) r += g.pre[rt * g.d + x];
+            R[x] = clear ? 0.0f : r;
+        }
+        if (clear)
+            for (int e = tid; e < g.N * g.d; e += nt) A[e] = 0.0f;
+        __syncthreads();
+    }
+}
+
+// The same sweep with an item per thread, R in registers, the next position's record in flight and one
+// barrier a position. Requires K d / V <= blockDim.x.
+template <int V>
+__device__ void recurrence_row_fast(const RecurrenceArgs& g, float* A, int row, bool carry, Pack<V> R) {
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const int per_slot = g.d / V, items = g.K * per_slot;
+    const bool mine = tid < items;
+    const int k = mine ? tid / per_slot : 0, x = mine ? (tid - k * per_slot) * V : 0;
+    const float n_f = static_cast<float>(g.N);
+    RecurrenceItem<V> now{};
+    if (mine) now = recurrence_fetch<V>(g, row, g.T - 1, k, x);
+    for (int t = g.T - 1; t >= 0; --t) {
+        RecurrenceItem<V> next{};
+        if (mine && t > 0) next = recurrence_fetch<V>(g, row, t - 1, k, x);   // in flight under this position
+        const bool cut = g.reset[static_cast<int64_t>(row) * g.T + t] != 0;      // the same for every thread
+        if (mine) {
+            Pack<V> dcv = zero_pack<V>(), dbv = zero_pack<V>();
+#pragma unroll
+            for (int i = 0; i < V; ++i) R.v[i] += now.post.v[i];
+            if (now.cell >= 0) {
+                float* a = A + static_cast<int64_t>(now.cell) * g.d + x;
+                const Pack<V> held = load_pack<V>(a);
+                Pack<V> left;
+#pragma unroll
+                for (int i = 0; i < V; ++i) {
+                    const float carried = held.v[i] + now.sel.v[i];
+                    const float share = R.v[i] / n_f;
+                    const float grad = carried + share;
+                    dcv.v[i] = now.b.v[i] * grad;
+                    dbv.v[i] = (now.c.v[i] - now.h_old.v[i]) * grad;
+                    left.v[i] = (1.0f - now.b.v[i]) * carried - now.b.v[i] * share;
+                }
+                store_pack<V>(a, left);
+            }
+            const int64_t at = ((static_cast<int64_t>(row) * g.T + t) * g.K + k) * g.d + x;
+            store_pack<V>(g.dc + at, dcv);
+            store_pack<V>(g.db + at, dbv);
+#pragma unroll
+            for (int i = 0; i < V; ++i) R.v[i] += now.pre.v[i];
+        }
+        const bool clear = cut && !(carry && t == 0);
+        if (clear) {
+            __syncthreads();   // the position's writes to A are over
+            for (int e = tid; e < g.N * g.d; e += nt) A[e] = 0.0f;
+            R = zero_pack<V>();
+        }
+        __syncthreads();       // the one barrier of a position: a cell may change hands at the next
+        now = next;
+    }
+    // R of the row's columns, for the carry: slot 0's items hold one copy of every column group
+    if (mine && k == 0) store_pack<V>(A + static_cast<int64_t>(g.N) * g.d + x, R);
+    __syncthreads();
+}
+
+template <int V>
+__device__ void recurrence_run(const HsnWinArgs& a, float* A) {
+    RecurrenceArgs g;
+    g.T = a.i[1]; g.K = a.i[2]; g.d = a.i[3]; g.N = a.i[4];
+    g.has_pre = a.i[5] != 0; g.has_post = a.i[6] != 0; g.has_sel = a.i[7] != 0;
+    const bool carry = a.i[8] != 0;
+    g.c = static_cast<const float*>(a.p[0]);
+    g.b = static_cast<const float*>(a.p[1]);
+    g.h_old = static_cast<const float*>(a.p[2]);
+    g.cells = static_cast<const int64_t*>(a.p[3]);
+    g.valid = static_cast<const uint8_t*>(a.p[4]);
+    g.reset = static_cast<const uint8_t*>(a.p[5]);
+    g.pre = static_cast<const float*>(a.p[6]);
+    g.post = static_cast<const float*>(a.p[7]);
+    g.sel = static_cast<const float*>(a.p[8]);
+    g.dc = static_cast<float*>(a.p[9]);
+    g.db = static_cast<float*>(a.p[10]);
+    const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+    const int64_t Nd = static_cast<int64_t>(g.N) * g.d;
+    float* R = A + Nd;
+    float* A_io = carry ? static_cast<float*>(a.p[11]) + static_cast<int64_t>(row) * Nd : nullptr;
+    float* R_io = carry ? static_cast<float*>(a.p[12]) + static_cast<int64_t>(row) * g.d : nullptr;
+    if (carry) {
+        block_copy_f32(A, A_io, static_cast<int>(Nd));
+        for (int x = tid; x < g.d; x += nt) R[x] = R_io[x];
+    } else {
+        for (int e = tid; e < Nd + g.d; e += nt) A[e] = 0.0f;
     }
     __syncthreads();
-    const float n_f = static_cast<float>(N);
-    const int KD = K * d;
-    for (int t = T - 1; t >= 0; --t) {
-        const int64_t rt = static_cast<int64_t>(row) * T + t;
-        if (has_post) {
-            for (int x = tid; x < d; x += nt) R[x] += post[rt * d + x];
-            __syncthreads();
-        }
-        for (int e = tid; e < KD; e += nt) {
-            const int k = e / d, x = e - k * d;
-            const int64_t s = rt * K + k, o = s * d + x;
-            float dcv = 0.0f, dbv = 0.0f;
-            if (valid[s]) {  // a padded slot's values never enter: a select, not a product with a mask
-                const int n = static_cast<int>(cells[s]);
-                float carried = A[n * d + x];
-                if (has_sel) carried += sel[o];
-                const float share = R[x] / n_f;
-                const float g = carried + share;
-                const float gate = b[o];
-                dcv = gate * g;
-                dbv = (c[o] - h_old[o]) * g;
-                A[n * d + x] = (1.0f - gate) * carried - gate * share;
-            }
-            dc[o] = dcv;
-            db[o] = dbv;
-        }
+    const int items = g.K * (g.d / V);
+    if (items <= nt) {
+        Pack<V> mineR = zero_pack<V>();
+        if (tid < items) mineR = load_pack<V>(R + (tid % (g.d / V)) * V);
         __syncthreads();
-        const bool cut = reset[rt] != 0;
-        if (has_pre)
-            for (int x = tid; x < d; x += nt) R[x] += pre[rt * d + x];
-        if (cut && !(carry && t == 0)) {
-            for (int e = tid; e < N * d; e += nt) A[e] = 0.0f;
-            for (int x = tid; x < d; x += nt) R[x] = 0.0f;
-        }
-        __syncthreads();
+        recurrence_row_fast<V>(g, A, row, carry, mineR);
+    } else {
+        recurrence_row_rounds<V>(g, A, row, carry);
     }
     if (carry) {
-        const bool cut = reset[static_cast<int64_t>(row) * T] != 0;
-        float* A_out = static_cast<float*>(a.p[11]) + static_cast<int64_t>(row) * N * d;
-        float* R_out = static_cast<float*>(a.p[12]) + static_cast<int64_t>(row) * d;
-        for (int e = tid; e < N * d; e += nt) A_out[e] = cut ? 0.0f : A[e];
-        for (int x = tid; x < d; x += nt) R_out[x] = cut ? 0.0f : R[x];
+        const bool cut = g.reset[static_cast<int64_t>(row) * g.T] != 0;
+        for (int e = tid; e < Nd; e += nt) A_io[e] = cut ? 0.0f : A[e];
+        for (int x = tid; x < g.d; x += nt) R_io[x] = cut ? 0.0f : R[x];
     }
+}
+
+}  // namespace
+
+extern "C" __global__ void hsn_win_recurrence(HsnWinArgs a) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    float* A = reinterpret_cast<float*>(dyn);
+    // 16-byte items when every row of the record and of A starts on a 16-byte boundary
+    bool wide = (a.i[3] & 3) == 0;
+    for (int s : {0, 1, 2, 9, 10}) wide = wide && (reinterpret_cast<uintptr_t>(a.p[s]) & 15) == 0;
+    if (a.i[5]) wide = wide && (reinterpret_cast<uintptr_t>(a.p[6]) & 15) == 0;
+    if (a.i[6]) wide = wide && (reinterpret_cast<uintptr_t>(a.p[7]) & 15) == 0;
+    if (a.i[7]) wide = wide && (reinterpret_cast<uintptr_t>(a.p[8]) & 15) == 0;
+    if (wide) recurrence_run<4>(a, A);
+    else recurrence_run<1>(a, A);
 }
 
 // ------------------------------------------------------------------------------------------------
 // hsn_win_recurrence_dense: the recurrence of the rows that ran the dense round (every cell is
-// written, q' = mean(h') does not read q).
+// written, q' = mean(h') does not read q; reference: python/hsn/train/split.py:177-209).
 //   p: 0 c, 1 b, 2 h_old [B',T,N,d]; 3 reset [B',T] u8; 4 d_q_pre, 5 d_q_post [B',T,d];
 //      6 dc, 7 db [B',T,N,d].   i: 0 B', 1 T, 2 N, 3 d, 4 has_pre, 5 has_post.
-// Dynamic shared memory: (N + 1) d words.
+// Dynamic shared memory: (N + 1) d words (the reference's launch size; A lives there).
+//
+// Every element of the state is written at every position and reads only itself and the summary's
+// cotangent of its column, which here is stateless: before position t it equals d_q_post[t] plus,
+// when position t+1 exists and does not reset, d_q_pre[t+1]. So an element's whole history belongs to
+// one thread, no value crosses threads and the sweep needs no barrier at all; each thread walks its
+// elements (16 bytes at a time when d is a multiple of 4) with the next position's loads in flight.
 // ------------------------------------------------------------------------------------------------
-extern "C" __global__ void hsn_win_recurrence_dense(HsnWinArgs a) {
-    extern __shared__ __align__(16) unsigned char dyn[];
+namespace {
+
+template <int V>
+__device__ void dense_run(const HsnWinArgs& a, float* A) {
     const int T = a.i[1], N = a.i[2], d = a.i[3];
     const bool has_pre = a.i[4] != 0, has_post = a.i[5] != 0;
     const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
@@ -351,31 +517,47 @@ extern "C" __global__ void hsn_win_recurrence_dense(HsnWinArgs a) {
     const float* post = static_cast<const float*>(a.p[5]);
     float* dc = static_cast<float*>(a.p[6]);
     float* db = static_cast<float*>(a.p[7]);
-    float* A = reinterpret_cast<float*>(dyn);
-    float* R = A + static_cast<int64_t>(N) * d;
-    for (int e = tid; e < N * d; e += nt) A[e] = 0.0f;
-    for (int x = tid; x < d; x += nt) R[x] = 0.0f;
-    __syncthreads();
+    const int64_t Nd = static_cast<int64_t>(N) * d;
+    const int groups = static_cast<int>(Nd / V);
     const float n_f = static_cast<float>(N);
+    for (int e = tid; e < groups; e += nt) store_pack<V>(A + static_cast<int64_t>(e) * V, zero_pack<V>());
+    // (no barrier: a thread reads back only what it wrote itself)
     for (int t = T - 1; t >= 0; --t) {
         const int64_t rt = static_cast<int64_t>(row) * T + t;
-        if (has_post) {
-            for (int x = tid; x < d; x += nt) R[x] += post[rt * d + x];
-            __syncthreads();
-        }
-        for (int e = tid; e < N * d; e += nt) {
-            const int64_t o = rt * N * d + e;
-            const float g = A[e] + R[e % d] / n_f;
-            const float gate = b[o];
-            dc[o] = gate * g;
-            db[o] = (c[o] - h_old[o]) * g;
-            A[e] = (1.0f - gate) * g;
-        }
-        __syncthreads();
         const bool cut = reset[rt] != 0;
-        for (int x = tid; x < d; x += nt) R[x] = (cut || !has_pre) ? 0.0f : pre[rt * d + x];
-        if (cut)
-            for (int e = tid; e < N * d; e += nt) A[e] = 0.0f;
-        __syncthreads();
+        const bool from_next = has_pre && t + 1 < T && reset[rt + 1] == 0;
+        for (int e = tid; e < groups; e += nt) {
+            const int64_t at = static_cast<int64_t>(e) * V;
+            const int x = static_cast<int>(at % d);
+            const int64_t o = rt * Nd + at;
+            const Pack<V> cv = load_pack<V>(c + o), bv = load_pack<V>(b + o), hv = load_pack<V>(h_old + o);
+            const Pack<V> po = has_post ? load_pack<V>(post + rt * d + x) : zero_pack<V>();
+            const Pack<V> pr = from_next ? load_pack<V>(pre + (rt + 1) * d + x) : zero_pack<V>();
+            const Pack<V> held = load_pack<V>(A + at);
+            Pack<V> dcv, dbv, left;
+#pragma unroll
+            for (int i = 0; i < V; ++i) {
+                const float grad = held.v[i] + (pr.v[i] + po.v[i]) / n_f;
+                dcv.v[i] = bv.v[i] * grad;
+                dbv.v[i] = (cv.v[i] - hv.v[i]) * grad;
+                left.v[i] = cut ? 0.0f : (1.0f - bv.v[i]) * grad;
+            }
+            store_pack<V>(dc + o, dcv);
+            store_pack<V>(db + o, dbv);
+            store_pack<V>(A + at, left);
+        }
     }
+}
+
+}  // namespace
+
+extern "C" __global__ void hsn_win_recurrence_dense(HsnWinArgs a) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    float* A = reinterpret_cast<float*>(dyn);
+    bool wide = (a.i[3] & 3) == 0;
+    for (int s : {0, 1, 2, 6, 7}) wide = wide && (reinterpret_cast<uintptr_t>(a.p[s]) & 15) == 0;
+    if (a.i[4]) wide = wide && (reinterpret_cast<uintptr_t>(a.p[4]) & 15) == 0;
+    if (a.i[5]) wide = wide && (reinterpret_cast<uintptr_t>(a.p[5]) & 15) == 0;
+    if (wide) dense_run<4>(a, A);
+    else dense_run<1>(a, A);
 }

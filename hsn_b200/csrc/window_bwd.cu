@@ -64,6 +64,7 @@ struct BwdCtx {
     float* part_dv;   // [nU + 1, P, 2d]
     float* part_sig;  // [nU, P]
     int* pair_unit;   // [P]  -1 on padded slots
+    int* status;      // set to 1 by a bounded wait that ran out (the head of the caller's scratch; null with full_cut and no scratch)
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -405,7 +406,7 @@ __global__ void __launch_bounds__(256) k_mid_tc(BwdCtx c, int t) {
         }
         fence_async_smem();
         if (!weights_in) {
-            mbar_wait(&bar_w, 0, nullptr);
+            mbar_wait(&bar_w, 0, c.status);
             weights_in = true;
         }
         tcgen05_fence_before();
@@ -421,7 +422,7 @@ __global__ void __launch_bounds__(256) k_mid_tc(BwdCtx c, int t) {
                 }
                 umma_commit(&bar_m);
             }
-            mbar_wait(&bar_m, phase, nullptr);
+            mbar_wait(&bar_m, phase, c.status);
             phase ^= 1u;
             tcgen05_fence_after();
             for (int tl = 0; tl < nT; ++tl) {
@@ -447,7 +448,7 @@ __global__ void __launch_bounds__(256) k_mid_tc(BwdCtx c, int t) {
             umma_chain(taddr, da, db, idesc, d >> 4, umma_kstep(128), umma_kstep(kTP));
             umma_commit(&bar_m);
         }
-        mbar_wait(&bar_m, phase, nullptr);
+        mbar_wait(&bar_m, phase, c.status);
         phase ^= 1u;
         tcgen05_fence_after();
         // epilogue 1: lane m is hidden column c0 + m
@@ -493,7 +494,7 @@ __global__ void __launch_bounds__(256) k_mid_tc(BwdCtx c, int t) {
             }
             umma_commit(&bar_m);
         }
-        mbar_wait(&bar_m, phase, nullptr);
+        mbar_wait(&bar_m, phase, c.status);
         phase ^= 1u;
         tcgen05_fence_after();
         for (int tl = 0; tl < nT; ++tl) {
@@ -690,7 +691,7 @@ Layout layout(const HsnwModel& m, int B) {
     Layout L;
     const size_t P = static_cast<size_t>(B) * m.K;
     const int nU = (m.H + kUS - 1) / kUS;
-    size_t off = 0;
+    size_t off = 256;   // the status area: int 0 is the error word of the bounded waits
     L.d_unit = off; off += align_up(sizeof(float) * P * m.d);
     L.dg = off; off += align_up(sizeof(float) * P * m.d);
     L.sig_gate = off; off += align_up(sizeof(float) * P);
@@ -727,6 +728,14 @@ extern "C" int64_t hsnw_backward_scratch_bytes(const HsnwModel* model, int32_t B
     return static_cast<int64_t>(layout(*model, B).total);
 }
 
+// The sizes the reverse sweep's kernels take (the forward's check_model has the same bounds): the index
+// arithmetic divides by multiply-highs that need d >= 2, and rows move 16 bytes at a time.
+static int check_backward_model(const HsnwModel& m) {
+    if (m.d < 4 || m.d % 4) return hsnw_fail(HSNW_E_UNSUPPORTED, "window_backward: d must be a multiple of 4");
+    if (m.H < 1 || m.M < 1 || m.D < 1) return hsnw_fail(HSNW_E_ARG, "window_backward: H, M and D must be positive");
+    return HSNW_OK;
+}
+
 extern "C" int hsnw_window_backward(const HsnwModel* model, const HsnwBackward* io, void* stream_) {
     if (int rc = hsnw_require_prepared()) return rc;
     if (!model || !io) return hsnw_fail(HSNW_E_ARG, "window_backward: null argument");
@@ -739,11 +748,24 @@ extern "C" int hsnw_window_backward(const HsnwModel* model, const HsnwBackward* 
     const bool full = io->full_cut != 0;
     if (!full && (!io->y || !io->gate_pre || !io->m || !io->rms || !io->hidden || !io->units))
         return hsnw_fail(HSNW_E_ARG, "window_backward: the state gradient needs the round's record");
-    if (!io->full_cut && io->y && io->gate_pre && io->m && io->rms && io->hidden && io->units) {
-        // one persistent cluster per row when the shape fits (window_rows_bwd.cu)
-        const int rc_rows = hsnw_rows_backward(model, io, static_cast<cudaStream_t>(stream_));
-        if (rc_rows >= 0) return rc_rows;
+    if (int rc = check_backward_model(m)) return rc;
+    // the status area at the head of the scratch: int 0 is set to 1 by a bounded wait that ran out
+    const bool has_scratch = io->scratch && io->scratch_bytes >= 256 && !(reinterpret_cast<uintptr_t>(io->scratch) & 255);
+    if (!full && !has_scratch)
+        return hsnw_fail(HSNW_E_ARG, "window_backward: scratch too small or not 256-byte aligned");
+    int* status = has_scratch ? static_cast<int*>(io->scratch) : nullptr;
+    if (status && cudaMemsetAsync(status, 0, 256, static_cast<cudaStream_t>(stream_)) != cudaSuccess)
+        return hsnw_check_launch("window_backward");
+    if (!full) {
+        // one persistent cluster per row when the shape fits (window_rows_bwd.cu); an error of its launch is
+        // the call's error, only a shape it does not take goes on to the phases
+        const int rc_rows = hsnw_rows_backward(model, io, status, static_cast<cudaStream_t>(stream_));
+        if (rc_rows != HSNW_DECLINED) {
+            if (rc_rows == HSNW_OK) hsnw_set_path(HSNW_PATH_ROWS);
+            return rc_rows;
+        }
     }
+    hsnw_set_path(HSNW_PATH_PHASES);
     const size_t cap = hsnw_max_shared() - 4096;
     const size_t sh_head = head_shared(m), sh_mid = mid_shared(m), sh_tail = tail_shared(m);
     const size_t sh_both = sh_head > sh_tail ? sh_head : sh_tail;
@@ -767,6 +789,7 @@ extern "C" int hsnw_window_backward(const HsnwModel* model, const HsnwBackward* 
     c.part_dv = full ? nullptr : reinterpret_cast<float*>(base + L.part_dv);
     c.part_sig = full ? nullptr : reinterpret_cast<float*>(base + L.part_sig);
     c.pair_unit = full ? nullptr : reinterpret_cast<int*>(base + L.pair_unit);
+    c.status = status;
     const int B = io->B, T = io->T;
     const int ht = m.K * m.d >= 2048 ? 512 : 256;   // threads of the head and tail: wide rows have the work for 16 warps
     const int pair_tile = mid_tc ? kTcPairTile : kPairTile;

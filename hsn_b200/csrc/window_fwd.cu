@@ -1454,9 +1454,14 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
         g_pre_status = nullptr;
         if (rc_pre) return rc_pre;
         pre_done = true;
+        // an error of the row kernel's launch is the call's error; only a shape it does not take goes on
         const int rc_rows = hsnw_rows_forward(model, io, c.pre_s, c.status, stream);
-        if (rc_rows >= 0) return rc_rows;
+        if (rc_rows != HSNW_DECLINED) {
+            if (rc_rows == HSNW_OK) hsnw_set_path(HSNW_PATH_ROWS);
+            return rc_rows;
+        }
     }
+    hsnw_set_path(HSNW_PATH_PHASES);
     const int rthreads = row_threads(*model, B);
     const dim3 init_grid(B, (model->N + kInitCells - 1) / kInitCells);
     hsnw_profile_mark(HSNW_K_INIT, stream);

@@ -1161,8 +1161,8 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
 
 // ------------------------------------------------------------------------------------------------
 // Host side: when the model and the window fit, hsnw_window_forward runs this kernel instead of
-// the phases. Returns HSNW_OK when launched, -1 when the shape does not fit (the caller falls back),
-// an error code otherwise.
+// the phases. Returns HSNW_OK when launched, HSNW_DECLINED when the shape does not fit (the caller runs
+// the phases), a negative error code otherwise (the caller passes it on).
 // ------------------------------------------------------------------------------------------------
 static bool rows_shape(const HsnwModel& m, RowsCtx* c) {
     if (!m.prod_bf16 || m.phases_only || !m.rows_bank || !m.rows_front) return false;
@@ -1186,14 +1186,14 @@ static bool rows_shape(const HsnwModel& m, RowsCtx* c) {
 
 int hsnw_rows_forward(const HsnwModel* model, const HsnwForward* io, const float* pre_s, int* status, cudaStream_t stream) {
     RowsCtx c;
-    if (!rows_shape(*model, &c)) return -1;
-    if ((reinterpret_cast<uintptr_t>(io->scalars) | reinterpret_cast<uintptr_t>(io->z) | reinterpret_cast<uintptr_t>(pre_s)) & 15) return -1;
+    if (!rows_shape(*model, &c)) return HSNW_DECLINED;
+    if ((reinterpret_cast<uintptr_t>(io->scalars) | reinterpret_cast<uintptr_t>(io->z) | reinterpret_cast<uintptr_t>(pre_s)) & 15) return HSNW_DECLINED;
     c.stages = kMaxStages;
     RowsSmem L = rows_smem(*model, c.C, c.slot_bytes, c.stages);
     if (L.total + 2048 > hsnw_max_shared()) {
         c.stages = 2;
         L = rows_smem(*model, c.C, c.slot_bytes, c.stages);
-        if (L.total + 2048 > hsnw_max_shared()) return -1;
+        if (L.total + 2048 > hsnw_max_shared()) return HSNW_DECLINED;
     }
     c.m = *model;
     c.io = *io;
@@ -1215,7 +1215,7 @@ int hsnw_rows_forward(const HsnwModel* model, const HsnwForward* io, const float
     int clusters = 0;
     if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess || clusters < 1) {
         cudaGetLastError();
-        return -1;
+        return HSNW_DECLINED;   // no cluster of this size and shared memory fits the device
     }
     hsnw_profile_mark(HSNW_K_ROWS_FWD, stream);
     if (cudaLaunchKernelEx(&cfg, kernel, c) != cudaSuccess) return hsnw_check_launch("window_forward (row clusters)");

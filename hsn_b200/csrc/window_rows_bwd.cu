@@ -33,7 +33,7 @@ namespace {
 #ifdef HSNW_TRACE
 #define BMARK(i)                                                                              \
     do {                                                                                      \
-        if (tid == 0 && row == 0 && t == T / 2) {                                             \
+        if (tid == 0 && row == 0 && t == T / 2 && c.trace) {                                  \
             unsigned long long now;                                                           \
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));                           \
             c.trace[r * 32 + (i)] = now;                                                      \
@@ -52,7 +52,8 @@ struct RowsBwdCtx {
     HsnwBackward io;
     int C, Nc, Ks;
     uint32_t bank_bytes, w2_bytes;   // a chunk, its W2 part
-    unsigned long long* trace;       // phase timestamps (HSNW_TRACE builds): the head of the caller's scratch
+    unsigned long long* trace;       // phase timestamps (HSNW_TRACE builds): after the status area of the caller's scratch, or null
+    int* status;                     // set to 1 by a ring wait that ran out
 };
 
 __host__ __device__ inline size_t up16b(size_t v) { return (v + 15) & ~static_cast<size_t>(15); }
@@ -321,7 +322,7 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
                 continue;
             }
             const uint32_t slot = g_issue % kStagesB;
-            if (g_issue >= kStagesB) ring_wait(&empty[slot], ((g_issue / kStagesB) - 1u) & 1u, nullptr, &failed_s);
+            if (g_issue >= kStagesB) ring_wait(&empty[slot], ((g_issue / kStagesB) - 1u) & 1u, c.status, &failed_s);
             const int j = dc_[o_ulist + (cur_i >> 1)];
             const unsigned char* from = bank + (static_cast<size_t>(j) * (H / 64) + r * 2 + (cur_i & 1)) * c.bank_bytes;
             mbar_expect_tx(&full[slot], c.bank_bytes);
@@ -443,7 +444,7 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
         tcgen05_fence_after();
         if (tid == 0 && n_chunks > 0) {
             const uint32_t slot = g0 % kStagesB;
-            ring_wait(&full[slot], (g0 / kStagesB) & 1u, nullptr, &failed_s);
+            ring_wait(&full[slot], (g0 / kStagesB) & 1u, c.status, &failed_s);
             if (d == 64)
                 umma_chain_sw128<4, 4>(taddr, 16, umma_desc_sw128(ring + slot * c.bank_bytes), 0, umma_desc(du_op, 16),
                                        umma_kstep(16), idesc, false);
@@ -459,7 +460,7 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
                 const uint32_t slot = (g0 + i) % kStagesB;
                 if (tid == 0 && i + 1 < n_chunks) {
                     const uint32_t nslot = (g0 + i + 1) % kStagesB;
-                    ring_wait(&full[nslot], ((g0 + i + 1) / kStagesB) & 1u, nullptr, &failed_s);
+                    ring_wait(&full[nslot], ((g0 + i + 1) / kStagesB) & 1u, c.status, &failed_s);
                     if (d == 64)
                         umma_chain_sw128<4, 4>(taddr + 64 * ((i + 1) & 1), 16, umma_desc_sw128(ring + nslot * c.bank_bytes), 0,
                                                umma_desc(du_op, 16), umma_kstep(16), idesc, false);
@@ -472,7 +473,7 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
                     const int hid_col = (i & 1) * 64 + hc;
                     const float bias = b1s[j * 128 + hid_col];
                     uint16_t* b2i = b2 + (i & 1) * (8 * 16 * 8);
-                    ring_wait(&bar_d1[i & 1], ((i & 1) ? d1_count1 : d1_count0) & 1u, nullptr, &failed_s);
+                    ring_wait(&bar_d1[i & 1], ((i & 1) ? d1_count1 : d1_count0) & 1u, c.status, &failed_s);
                     tcgen05_fence_after();
                     float acc[8];
                     tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 64 * (i & 1)), acc);
@@ -549,7 +550,7 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
 #pragma unroll
             for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
             if (n_chunks > 0) {
-                ring_wait(&bar_d2, d2_phase & 1u, nullptr, &failed_s);
+                ring_wait(&bar_d2, d2_phase & 1u, c.status, &failed_s);
                 tcgen05_fence_after();
                 tmem_ld8(tmem_addr(taddr, 32 * warp, 128), acc);
 #pragma unroll
@@ -662,14 +663,17 @@ static bool rows_bwd_shape(const HsnwModel& m, RowsBwdCtx* c) {
     return true;
 }
 
-int hsnw_rows_backward(const HsnwModel* model, const HsnwBackward* io, cudaStream_t stream) {
+int hsnw_rows_backward(const HsnwModel* model, const HsnwBackward* io, int* status, cudaStream_t stream) {
     RowsBwdCtx c;
-    if (io->full_cut || !rows_bwd_shape(*model, &c)) return -1;
+    if (io->full_cut || !rows_bwd_shape(*model, &c)) return HSNW_DECLINED;
     const RowsBwdSmem L = rows_bwd_smem(*model, c.C, c.bank_bytes);
-    if (L.total + 1024 > hsnw_max_shared()) return -1;
+    if (L.total + 1024 > hsnw_max_shared()) return HSNW_DECLINED;
     c.m = *model;
     c.io = *io;
-    c.trace = static_cast<unsigned long long*>(io->scratch);
+    c.status = status;
+    // the phase timestamps of HSNW_TRACE builds follow the status area, when the scratch has the room
+    c.trace = (io->scratch && io->scratch_bytes >= 256 + static_cast<int64_t>(c.C) * 32 * 8)
+        ? reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(io->scratch) + 256) : nullptr;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(io->B) * c.C, 1, 1);
     cfg.blockDim = dim3(kConsumers, 1, 1);
@@ -686,7 +690,7 @@ int hsnw_rows_backward(const HsnwModel* model, const HsnwBackward* io, cudaStrea
     int clusters = 0;
     if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess || clusters < 1) {
         cudaGetLastError();
-        return -1;
+        return HSNW_DECLINED;
     }
     hsnw_profile_mark(HSNW_K_ROWS_BWD, stream);
     if (cudaLaunchKernelEx(&cfg, kernel, c) != cudaSuccess) return hsnw_check_launch("window_backward (row clusters)");

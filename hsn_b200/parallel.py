@@ -60,13 +60,19 @@ def reduce_window_stats(refreshed: Tensor, state_abs_max: Tensor, rows: Sequence
                         group: dist.ProcessGroup | None = None) -> tuple[Tensor, Tensor]:  # fmt: skip
     """The tape's per-position batch statistics over all ranks: ``refreshed [T]`` is each rank's
     mean over its rows (``rows[r]`` rows on rank ``r``) and becomes the mean over all rows;
-    ``state_abs_max [T]`` becomes the maximum."""
+    ``state_abs_max [T]`` becomes the maximum (a maximum of absolute values: a rank that owns no rows
+    contributes zeros, whatever it passes in)."""
     if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) == 1:
         return refreshed, state_abs_max
     rank = dist.get_rank(group)
     total = float(sum(rows))
-    weighted = refreshed * (rows[rank] / total)
+    if rows[rank] > 0:
+        weighted = refreshed * (rows[rank] / total)
+        peak = state_abs_max.clone()
+    else:
+        # a rank without rows (fewer rows than ranks): its mean over nothing is NaN and would poison the sum
+        weighted = torch.zeros_like(refreshed)
+        peak = torch.zeros_like(state_abs_max)
     dist.all_reduce(weighted, group=group)
-    peak = state_abs_max.clone()
     dist.all_reduce(peak, op=dist.ReduceOp.MAX, group=group)
     return weighted, peak

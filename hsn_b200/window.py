@@ -310,12 +310,18 @@ def _umma_images(w1: Tensor, w2: Tensor, gate_t: Tensor) -> dict[str, Tensor]:
     return out
 
 
-def _check(name: str, t: Tensor, shape: tuple[int, ...], dtype: torch.dtype, device: torch.device) -> Tensor:
+def _check(name: str, t: Tensor, shape: tuple[int, ...], dtype: torch.dtype, device: torch.device,
+           in_place: bool = False) -> Tensor:  # fmt: skip
+    """``t`` if it is what the kernels take. A read-only tensor that is not contiguous is copied; one the
+    kernels update in place (``in_place``) must be contiguous already: a copy would take the update and
+    leave the caller's tensor stale."""
     if t.device != device or t.dtype != dtype or tuple(t.shape) != shape:
         raise ValueError(
             f"{name} must be a {dtype} tensor of shape {shape} on {device}, got {t.dtype} "
             f"{tuple(t.shape)} on {t.device}"
         )
+    if in_place and not t.is_contiguous():
+        raise ValueError(f"{name} is updated in place and must be contiguous")
     return t.contiguous()
 
 
@@ -361,19 +367,31 @@ def window_forward(
     ctx = _check("ctx", ctx, (B, T, dc), f32, dev)
     scalars = _check("scalars", scalars, (B, T, N, S), f32, dev)
     reset_u8 = _check("reset", reset, (B, T), torch.bool, dev).view(torch.uint8)
-    h0 = _check("state.h", state[0], (B, N, d), f32, dev)
-    q0 = _check("state.q", state[1], (B, d), f32, dev)
-    age0 = _check("state.age", state[2], (B, N), i64, dev)
-    pos = _check("state.pos", state[3], (B,), i64, dev)
+    resident = not tape_state
+    h0 = _check("state.h", state[0], (B, N, d), f32, dev, in_place=resident)
+    q0 = _check("state.q", state[1], (B, d), f32, dev, in_place=resident)
+    age0 = _check("state.age", state[2], (B, N), i64, dev, in_place=resident)
+    pos = _check("state.pos", state[3], (B,), i64, dev, in_place=resident)
     if tape_state:
         pos = pos.clone()
     lib = _lib.library()
     o = out if out is not None else {}
 
     def buf(name: str, shape: tuple[int, ...], dtype: torch.dtype) -> Tensor:
-        if name not in o:
-            o[name] = torch.empty(shape, dtype=dtype, device=dev)
-        return o[name]
+        # a buffer of an earlier call is reused only if it is exactly what this call writes: the kernels
+        # take sizes from the call, not from the buffer
+        have = o.get(name)
+        if have is not None and (tuple(have.shape) != shape or have.dtype != dtype or have.device != dev
+                                 or not have.is_contiguous()):  # fmt: skip
+            if carried:
+                raise ValueError(
+                    f"out[{name!r}] is {have.dtype} {tuple(have.shape)}; a carried call needs the previous "
+                    f"call's buffers of the same B and T ({dtype} {shape})"
+                )
+            have = None
+        if have is None:
+            o[name] = have = torch.empty(shape, dtype=dtype, device=dev)
+        return have
 
     io = _lib.HsnwForward()
     io.B, io.T, io.tape_state, io.forced = B, T, int(tape_state), int(forced is not None)
@@ -407,8 +425,8 @@ def window_forward(
     need = int(lib.hsnw_forward_scratch_bytes(ctypes.byref(model.struct), B, T))
     if scratch is None:
         scratch = buf("_scratch", (need,), torch.uint8)
-    if scratch.numel() < need or scratch.device != dev:
-        raise ValueError(f"scratch must hold {need} bytes on {dev}")
+    if scratch.numel() < need or scratch.device != dev or scratch.dtype != torch.uint8 or not scratch.is_contiguous():
+        raise ValueError(f"scratch must be a contiguous uint8 tensor of at least {need} bytes on {dev}")
     io.scratch, io.scratch_bytes = scratch.data_ptr(), scratch.numel()
     with torch.cuda.device(dev):
         _lib.check(getattr(lib, _entry)(ctypes.byref(model.struct), ctypes.byref(io), _stream(dev)))
@@ -420,6 +438,7 @@ def window_forward(
         o["h"], o["q"], o["age"] = h0, q0, age0
     o["pos"] = pos
     o["status"] = scratch[:4].view(torch.int32)  # 0, or 1 when a bounded device-side wait ran out
+    o["path"] = lib.hsnw_last_path().decode()  # "rows": the per-row cluster kernel ran; "phases": the batch-synchronous kernels
     if forced is None:
         o["refreshed"] = o["sel_refreshed"].float().sum(dim=2).mean(dim=0)
     o["explored"] = torch.zeros(T, dtype=f32, device=dev)
@@ -472,6 +491,7 @@ def window_backward(
     initial: tuple[Tensor, Tensor] | None = None,
     full_cut: bool = False,
     scratch: Tensor | None = None,
+    info: dict[str, Any] | None = None,
 ) -> tuple[Tensor, Tensor, tuple[Tensor, Tensor]]:
     """The reverse sweep of one window (``hsnw_window_backward``): ``(dc, db, (A, R))``.
 
@@ -479,7 +499,10 @@ def window_backward(
     ``record`` holds ``y gate_pre m rms hidden``), or with ``full_cut`` ``recurrence_backward``'s
     (``python/hsn/train/split.py:128-139``; ``units`` and ``record`` unused). ``initial`` is the
     cotangent of the state after the last position (the next window's returned ``(A, R)``); the
-    returned ``(A, R)`` is the cotangent of the state this window started from."""
+    returned ``(A, R)`` is the cotangent of the state this window started from. ``info``, a dict,
+    receives ``status`` (an int32 tensor of one element on the device: 0, or 1 when a bounded
+    device-side wait ran out and the results are not to be trusted) and ``path`` (``"rows"`` or
+    ``"phases"``: the kernels that served the call)."""
     dm = model.dims
     dev = model.device
     B, T, K, d = (int(n) for n in c.shape)
@@ -530,9 +553,15 @@ def window_backward(
     need = int(lib.hsnw_backward_scratch_bytes(ctypes.byref(model.struct), B, T))
     if scratch is None:
         scratch = torch.empty((max(need, 256),), dtype=torch.uint8, device=dev)
+    if scratch.numel() < need or scratch.device != dev or scratch.dtype != torch.uint8 or not scratch.is_contiguous():
+        raise ValueError(f"scratch must be a contiguous uint8 tensor of at least {need} bytes on {dev}")
     io.scratch, io.scratch_bytes = scratch.data_ptr(), scratch.numel()
     with torch.cuda.device(dev):
         _lib.check(lib.hsnw_window_backward(ctypes.byref(model.struct), ctypes.byref(io), _stream(dev)))
+    if info is not None:
+        info["status"] = scratch[:4].view(torch.int32)
+        info["path"] = lib.hsnw_last_path().decode()
+        info["_scratch"] = scratch
     return dc, db, (A, R)
 
 

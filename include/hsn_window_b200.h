@@ -51,6 +51,12 @@ typedef struct HsnWinArgs {
 int hsnw_version(void);
 /* The calling thread's last error message ("" if none). */
 const char* hsnw_last_error(void);
+/* Which kernels served the calling thread's last successful hsnw_window_forward / hsnw_stream_* /
+ * hsnw_window_backward call: "rows" (one persistent thread-block cluster per row) or "phases" (the
+ * batch-synchronous kernels, a few launches per position); "" before the first call. The row
+ * kernels are taken when the model's shape fits them; an error of their launch is returned to the
+ * caller, never hidden behind the other kernels. No counterpart in the reference. */
+const char* hsnw_last_path(void);
 /* Make `device` ready: checks that it is an sm_100 part, opts the kernels in to large dynamic
  * shared memory and records the SM count. Idempotent; the only call that may synchronise.
  * Replaces window_ext.cpp:41-56 (there: cuModuleLoad of a fatbin per context). */
@@ -193,7 +199,10 @@ typedef struct HsnwForward {
     float* rec_rms;
     float* rec_hidden;
     float* logits;             /* optional [B,T,N,M]: the scorer's logits (tests) */
-    void* scratch;             /* hsnw_forward_scratch_bytes() bytes, 256-byte aligned */
+    /* hsnw_forward_scratch_bytes() bytes, 256-byte aligned. Its first int32 is the call's status word:
+     * cleared when the call is enqueued, set to 1 by a device-side wait (an mbarrier of the TMA
+     * pipeline) that gave up after its iteration limit; the results of such a call are not valid. */
+    void* scratch;
     int64_t scratch_bytes;
 } HsnwForward;
 
@@ -243,7 +252,10 @@ typedef struct HsnwBackward {
     float* db;
     float* A;                  /* [B,N,d] in/out */
     float* R;                  /* [B,d] in/out */
-    void* scratch;             /* hsnw_backward_scratch_bytes() bytes, 256-byte aligned */
+    /* hsnw_backward_scratch_bytes() bytes, 256-byte aligned (optional with full_cut). Its first int32
+     * is the call's status word, as in HsnwForward: cleared when the call is enqueued, set to 1 by a
+     * device-side wait that gave up. */
+    void* scratch;
     int64_t scratch_bytes;
 } HsnwBackward;
 
@@ -261,9 +273,10 @@ int hsnw_window_backward(const HsnwModel* model, const HsnwBackward* io, void* s
  * the host, and calls no allocating routine.
  * The first call on a device looks the array's address up (cudaGetSymbolAddress, with that device
  * current): make that first call before any stream capture begins.
- * All calls on one device share the array, and it keeps the last call's contents. Nothing in it
- * has to start at zero (every value is written before it is read within a call), so nothing is
- * cleared; but two calls that overlap on the GPU, e.g. on two streams, race on it: order them. */
+ * All calls on one device share the array, and it keeps the last call's contents. Only its status
+ * word has to start at zero and is cleared by every call (every other value is written before it
+ * is read within a call); but two calls that overlap on the GPU, e.g. on two streams, race on it:
+ * order them. */
 int64_t hsnw_static_scratch_bytes(void);
 int hsnw_window_backward_static(const HsnwModel* model, const HsnwBackward* io, void* stream);
 
@@ -286,6 +299,15 @@ int hsnw_profile_begin(void);
 int hsnw_profile_kinds(void);
 const char* hsnw_profile_kind_name(int kind);
 int hsnw_profile_end(double* ms_by_kind, int64_t* launches_by_kind, int kinds);
+
+/* ---- self-test of the bounded device-side waits --------------------------------------------------
+ * No counterpart in the reference (its kernels have no waits). Every mbarrier wait of the window
+ * kernels polls a bounded number of times, then gives up, sets the call's status word and lets the
+ * kernel run to its end. This launches one small kernel whose barrier nothing ever completes and
+ * fills words[0..4) (device, int32): [0] = 1 the ring wait of the row kernels ran out, [1] = 1 the
+ * staging wait of the phase kernels ran out, [2] = 7 the kernel reached its end, [3] = 0 a wait after
+ * the block's first time-out returned at once. Takes up to a few seconds; the context stays usable. */
+int hsnw_selftest_wait_timeout(int32_t* words, void* stream);
 
 #ifdef __cplusplus
 }

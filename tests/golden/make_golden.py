@@ -21,6 +21,10 @@ inputs and outputs of every function on the window path as ``.npz`` files:
                         (``python/hsn/train/state_sweep.py:441`` head, ``:487`` middle, ``:497`` tail)
                         on seeded buffers, two positions in sweep order, every written buffer before
                         and after each step.
+* ``window_bf16_*.npz`` the same split window run under ``torch.autocast("cpu", dtype=torch.bfloat16)``, what
+                        ``train.precision=bf16`` (``python/hsn/config.py:1113``) turns on through
+                        ``python/hsn/train/amp.py:30-39``: every linear's operands and output in bfloat16,
+                        state and norms in float32. Pins the oracle's ``bf16=True`` mode.
 * ``chain_*.npz``       two chained windows against the unsplit window of twice the length: the
                         carried state forward, the state cotangent ``(A, R)`` backward.
 
@@ -460,6 +464,31 @@ def make_windows(root: Path) -> None:
         print(name, "ok")
 
 
+def make_windows_bf16(root: Path) -> None:
+    """Windows under bf16 autocast on the CPU, at shapes the per-row cluster kernels take (hidden width
+    a multiple of 128, state width 32 or 64): one block a row, and two blocks a row with the
+    128-byte-swizzled operand tiles. The refresh probes fire in the first."""
+    import torch
+
+    SG = "[summary,eps,router]"
+    cases = {
+        "bf16_a": dict(shape=dict(B=3, T=8, N=64, d=32, K=4, H=128, M=4, D=3), perturb=0.3, p=0.15,
+                       extra=("model.age_max=3",)),
+        "bf16_b": dict(shape=dict(B=2, T=6, N=64, d=64, K=8, H=256, M=4, D=4), perturb=0.1, p=0.1,
+                       extra=("model.age_max=1000000",)),
+    }  # fmt: skip
+    for name, case in cases.items():
+        shape = case["shape"]
+        cfg = _cfg(root, **shape, fd=SG, extra=case["extra"], precision="bf16")
+        model = _model(cfg, torch.float32, case["perturb"])
+        tokens, ctx, reset = _inputs(cfg, shape["B"], shape["T"], case["p"])
+        state = model.init_state(shape["B"])
+        with torch.autocast("cpu", dtype=torch.bfloat16):
+            cap = _run_window(root, cfg, model, torch.float32, tokens, ctx, reset, state)
+        _dump_window(HERE / f"window_{name}.npz", model, cap, reset, state)
+        print(name, "ok")
+
+
 def make_chain(root: Path) -> None:
     """Two chained windows of T positions against one window of 2T: the forward carry is the
     final state; the backward carry is the unsplit sweep's (A, R) at position T (what the second
@@ -590,7 +619,7 @@ def main() -> None:
     torch.set_num_threads(1)
     steps = {
         "select": make_select, "update": make_update, "recurrence": make_recurrence,
-        "windows": make_windows, "chain": make_chain, "sweep": make_sweep,
+        "windows": make_windows, "bf16": make_windows_bf16, "chain": make_chain, "sweep": make_sweep,
     }  # fmt: skip
     for key, fn in steps.items():
         if not args.only or key in args.only.split(","):

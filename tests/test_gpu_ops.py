@@ -258,3 +258,19 @@ def test_recurrence_kernel_keeps_a_padded_nan_out_and_declines_other_dtypes(wind
     assert got is not None and bool(torch.isfinite(got[0]).all()) and bool(torch.isfinite(got[1]).all())
     assert window.recurrence_backward(case["c"].double(), case["b"].double(), case["h_old"].double(), cells, valid, reset, N, None, post.double(), None) is None
     assert window.recurrence_backward(case["c"].cpu(), case["b"].cpu(), case["h_old"].cpu(), cells.cpu(), valid.cpu(), reset.cpu(), N, None, None, None) is None
+
+
+def test_a_wait_that_nothing_completes_runs_out_and_reports() -> None:
+    """Every mbarrier wait of the window kernels is bounded. A small kernel waits on a barrier that
+    nothing arrives at (no copy in flight, nothing faults): both kinds of wait give up after their
+    limit and set their status word, a later wait of the same block returns at once, the kernel
+    reaches its end, and the context still runs work afterwards."""
+    from hsn_b200 import _lib
+    from hsn_b200.window import prepare
+
+    prepare(0)
+    words = torch.full((4,), -1, dtype=torch.int32, device="cuda")
+    _lib.check(_lib.library().hsnw_selftest_wait_timeout(words.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert words.tolist() == [1, 1, 7, 0]
+    assert float((torch.ones(8, device="cuda") * 2).sum()) == 16.0

@@ -149,6 +149,72 @@ def test_state_gradient_sweep_equals_the_reference(name: str) -> None:
     np.testing.assert_allclose(trace["dvm"], z["bw_dvm"], rtol=tol, atol=tol * scale)
 
 
+@pytest.mark.parametrize("name", ["bf16_a", "bf16_b"])
+def test_bf16_mode_reproduces_the_reference_under_autocast(name: str) -> None:
+    """The oracle's ``bf16=True`` against the reference's CPU sweep under bf16 autocast (its
+    ``train.precision=bf16``): the decisions of every position, then state, tape and the round's
+    record within 2e-2 of each array's scale with the reference's decision replayed."""
+    z = load_golden(f"window_{name}")
+    K = z["tape_sel_cell_idx"].shape[-1]
+    W = O.WindowWeights.from_npz(z, K, np.dtype(np.float32))
+    args = (z["z"], z["ctx"], z["scalars"], z["reset"].astype(bool), z["h0"], z["q0"], z["age0"], z["pos0"])
+    valid = z["tape_sel_valid"].astype(bool)
+    ref_cells, ref_units = z["tape_sel_cell_idx"], z["tape_sel_unit_idx"]
+    B, T = valid.shape[:2]
+    # decisions, position by position from the reference's own pre-round state (so one flipped
+    # decision does not cost the rest of its row): equal, or different only among cells whose scores
+    # are within one bfloat16 unit of the last selected score (a float32 sum on a rounding boundary:
+    # bf16_a has one, its reference score lies half a unit from the oracle's)
+    same = np.zeros((B, T), dtype=bool)
+    fired = 0
+    for t in range(T):
+        p = O.position(W, z["tape_tape_h"][:, t], z["tape_tape_q"][:, t], z["tape_tape_age"][:, t],
+                       z["z"][:, t], z["ctx"][:, t], z["scalars"][:, t], bf16=True)  # fmt: skip
+        fired += int(p["refreshed"].sum())
+        score = p["logits"].max(axis=-1)
+        for b in range(B):
+            same[b, t] = (np.array_equal(p["cells"][b], ref_cells[b, t]) and np.array_equal(p["units"][b], ref_units[b, t])
+                          and np.array_equal(p["valid"][b], valid[b, t]))  # fmt: skip
+            if not same[b, t]:
+                assert np.array_equal(p["valid"][b], valid[b, t])
+                mine, theirs = set(p["cells"][b][valid[b, t]].tolist()), set(ref_cells[b, t][valid[b, t]].tolist())
+                moved = sorted(mine ^ theirs) or sorted(mine)
+                last = np.sort(score[b])[::-1][K - 1]
+                assert np.abs(score[b][moved] - last).max() <= abs(last) * 2.0**-7, (b, t, moved)
+    assert same.mean() >= 0.9, same
+    if name == "bf16_a":
+        assert fired > 0
+    # values with the reference's decision replayed: every row and position counts
+    tape = O.window_forward(W, *args, bf16=True, forced=(z["tape_sel_cell_idx"], z["tape_sel_unit_idx"], valid))
+    tol = 2e-2
+    for mine, ref in (
+        ("tape_h", "tape_tape_h"), ("tape_q", "tape_tape_q"), ("tape_hsel", "tape_tape_hsel"),
+        ("qs", "tape_qs"), ("h", "tape_h"), ("q", "tape_q"),
+    ):  # fmt: skip
+        scale = float(np.abs(z[ref]).max())
+        np.testing.assert_allclose(tape[mine], z[ref], rtol=tol, atol=tol * scale, err_msg=mine)
+    for key, ref in (("y", "rec_y"), ("gate_pre", "rec_gate_pre"), ("m", "rec_m"), ("rms", "rec_rms"),
+                     ("hidden", "rec_hidden"), ("c", "bw_c"), ("b", "bw_b"), ("h_old", "bw_h_old")):  # fmt: skip
+        got, want = tape["rec_" + key][valid], z[ref][valid]
+        scale = float(np.abs(want).max())
+        np.testing.assert_allclose(got, want, rtol=tol, atol=tol * scale, err_msg=key)
+    # the reverse sweep on the reference's own record: the oracle in float32 against the reference's
+    # sweep (whose two transposed products ran under the same autocast)
+    N = z["h0"].shape[1]
+    record = {k: z["rec_" + k] for k in ("y", "hidden", "gate_pre", "m", "rms")}
+    cot = lambda k: z[k] if k in z.files else None  # noqa: E731
+    trace: dict = {}
+    dc, db = O.state_gradient_backward(
+        W, z["bw_c"], z["bw_b"], z["bw_h_old"], z["bw_cells"], z["bw_units"], z["bw_valid"],
+        z["reset"], N, cot("bw_d_q_pre"), cot("bw_d_q_post"), cot("bw_d_h_sel"), record, trace=trace,
+    )  # fmt: skip
+    scale = max(float(np.abs(z["bw_dc"]).max()), float(np.abs(z["bw_A"]).max()))
+    np.testing.assert_allclose(dc, z["bw_dc"], rtol=tol, atol=tol * scale)
+    np.testing.assert_allclose(db, z["bw_db"], rtol=tol, atol=tol * scale)
+    np.testing.assert_allclose(trace["A"], z["bw_A"], rtol=tol, atol=tol * scale)
+    np.testing.assert_allclose(trace["R"], z["bw_R"], rtol=tol, atol=tol * scale)
+
+
 def test_full_cut_window_equals_the_reference() -> None:
     z = load_golden("window_cut_f64")
     N = z["h0"].shape[1]
