@@ -77,68 +77,73 @@ __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fe
 // Generic-proxy writes to shared memory become visible to the tensor core's (async proxy) reads.
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 
-// D[tmem] (+)= A[smem] * B[smem]^T for one K = 16 step; issued by ONE thread.
+// ---- issuing products ------------------------------------------------------------------------------
+// Every function below is executed by ALL 32 lanes of a CONVERGED warp; one lane, elected inside the
+// instruction sequence itself (elect.sync, the same lane every time for a full warp), issues. The
+// control flow around a tcgen05.mma therefore stays warp-uniform, and that matters: measured on a
+// B200, a chain issued from a one-thread branch (`if (tid == 0)`) costs about 200 cycles per product
+// whatever its shape (16 products M 128 x N 16: 3370 cycles from the first issue to the commit's
+// arrival), the same chain issued this way 728 cycles (about 35 a product after a fixed ~250), and
+// M 128 x N 256 products then run at the tensor pipe's own rate (136 cycles each). With this issue
+// rate consecutive products into ONE accumulator are as fast as products spread over several (727
+// cycles either way), so a product's K steps simply accumulate in place.
+//
+// D[tmem] (+)= A[smem] * B[smem]^T for one K = 16 step.
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, bool accumulate) {
     const uint32_t acc = accumulate ? 1u : 0u;
     asm volatile(
         "{\n"
-        ".reg .pred p;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        ".reg .pred lead, acc;\n"
+        "elect.sync _|lead, 0xffffffff;\n"
+        "setp.ne.b32 acc, %4, 0;\n"
+        "@lead tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, acc;\n"
         "}\n" ::"r"(tmem_d),
         "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc)
         : "memory");
 }
 // A chain of `steps` K = 16 products into one accumulator: D = sum_s A_s B_s^T, the descriptors
-// advancing by a_step / b_step (16-byte units) per product. Issued by ONE thread. Deliberately out
-// of line: the sequence is compiled once, on its own, and is the same machine code in every kernel
-// that uses it. Inlined into the reverse sweep's kernel, this loop gave accumulators whose rows
-// repeated with period 8 (as if the A tile's row stride were zero) or not, depending on unrelated
-// code elsewhere in the kernel; out of line it does not.
-static __device__ __noinline__ void umma_chain(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, int steps,
-                                               uint32_t a_step, uint32_t b_step, bool onto = false) {
-    // onto: add to what the accumulator holds (a sum that runs over several chains)
+// advancing by a_step / b_step (16-byte units) per product. `onto`: add to what the accumulator holds
+// (a sum that runs over several chains).
+__device__ __forceinline__ void umma_chain(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, int steps,
+                                           uint32_t a_step, uint32_t b_step, bool onto = false) {
+    __syncwarp();
     for (int s = 0; s < steps; ++s)
         umma_bf16(tmem_d, desc_a + static_cast<uint64_t>(s) * a_step, desc_b + static_cast<uint64_t>(s) * b_step, idesc,
                   onto || s > 0);
 }
-// The same chain spread round-robin over n_acc accumulators acc_stride columns apart (their sum is
-// the product). Products into ONE accumulator execute one after the other, each waiting out the
-// tensor pipe's latency, which dominates when N is small; consecutive products into different
-// accumulators overlap.
-static __device__ __noinline__ void umma_chain_spread(uint32_t tmem_d, uint32_t acc_stride, int n_acc, uint64_t desc_a,
-                                                      uint64_t desc_b, uint32_t idesc, int steps, uint32_t a_step,
-                                                      uint32_t b_step, bool onto = false) {
-    for (int s = 0; s < steps; ++s)
-        umma_bf16(tmem_d + static_cast<uint32_t>(s % n_acc) * acc_stride, desc_a + static_cast<uint64_t>(s) * a_step,
-                  desc_b + static_cast<uint64_t>(s) * b_step, idesc, onto || s >= n_acc);
-}
-// The same with the counts known at compile time: the loop unrolls to a few instructions per product
-// (one thread issues them, so every instruction of the loop is on the critical path).
-template <int STEPS, int NACC>
-static __device__ __noinline__ void umma_chain_fixed(uint32_t tmem_d, uint32_t acc_stride, uint64_t desc_a, uint64_t desc_b,
-                                                     uint32_t idesc, uint32_t a_step, uint32_t b_step, bool onto) {
+// The same with the count known at compile time: the loop unrolls to a few instructions per product.
+template <int STEPS>
+__device__ __forceinline__ void umma_chain_fixed(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                 uint32_t a_step, uint32_t b_step, bool onto) {
+    __syncwarp();
 #pragma unroll
     for (int s = 0; s < STEPS; ++s)
-        umma_bf16(tmem_d + static_cast<uint32_t>(s % NACC) * acc_stride, desc_a + static_cast<uint64_t>(s) * a_step,
-                  desc_b + static_cast<uint64_t>(s) * b_step, idesc, onto || s >= NACC);
+        umma_bf16(tmem_d, desc_a + static_cast<uint64_t>(s) * a_step, desc_b + static_cast<uint64_t>(s) * b_step, idesc,
+                  onto || s > 0);
 }
 // The chain for an A tile in the 128-byte swizzle (K-blocks of 64: four K = 16 steps of 32 bytes, then
 // the next block a_block 16-byte units further on) and a B tile in the unswizzled layout.
-template <int STEPS, int NACC>
-static __device__ __noinline__ void umma_chain_sw128(uint32_t tmem_d, uint32_t acc_stride, uint64_t desc_a, uint32_t a_block,
-                                                     uint64_t desc_b, uint32_t b_step, uint32_t idesc, bool onto) {
+template <int STEPS>
+__device__ __forceinline__ void umma_chain_sw128(uint32_t tmem_d, uint64_t desc_a, uint32_t a_block, uint64_t desc_b,
+                                                 uint32_t b_step, uint32_t idesc, bool onto) {
+    __syncwarp();
 #pragma unroll
     for (int s = 0; s < STEPS; ++s)
-        umma_bf16(tmem_d + static_cast<uint32_t>(s % NACC) * acc_stride,
-                  desc_a + static_cast<uint64_t>(s >> 2) * a_block + static_cast<uint64_t>(s & 3) * 2u,
-                  desc_b + static_cast<uint64_t>(s) * b_step, idesc, onto || s >= NACC);
+        umma_bf16(tmem_d, desc_a + static_cast<uint64_t>(s >> 2) * a_block + static_cast<uint64_t>(s & 3) * 2u,
+                  desc_b + static_cast<uint64_t>(s) * b_step, idesc, onto || s > 0);
 }
 // The step between two K = 16 products of a tile of `rows` rows in the layout above.
 __host__ __device__ constexpr uint32_t umma_kstep(int rows) { return static_cast<uint32_t>((2 * rows * 16) >> 4); }
-// All MMAs issued so far by this thread arrive on `bar` when they have completed.
+// All products issued so far by the elected lane arrive on `bar` when they have completed (executed by
+// the whole converged warp, like the products themselves: the commit tracks the issuing thread's).
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(bar)) : "memory");
+    asm volatile(
+        "{\n"
+        ".reg .pred lead;\n"
+        "elect.sync _|lead, 0xffffffff;\n"
+        "@lead tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+        "}\n" ::"r"(smem_addr(bar))
+        : "memory");
 }
 // Eight consecutive fp32 columns of this thread's TMEM lane (lane = 32 * (warp % 4) + lane id).
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float out[8]) {

@@ -413,7 +413,7 @@ __global__ void __launch_bounds__(256) k_mid_tc(BwdCtx c, int t) {
         __syncthreads();
         if (is_gate) {
             // dv's gate part: [2d state columns, pairs] = gate tile [128, d] x dg [32, d]^T
-            if (tid == 0) {
+            if (tid < 32) {   // the whole first warp, converged after the barrier: one elected lane issues
                 tcgen05_fence_after();
                 const uint64_t db = umma_desc(B1, kTP);
                 for (int tl = 0; tl < nT; ++tl) {
@@ -442,7 +442,7 @@ __global__ void __launch_bounds__(256) k_mid_tc(BwdCtx c, int t) {
             __syncthreads();
             continue;
         }
-        if (tid == 0) {
+        if (tid < 32) {   // the whole first warp, converged after the barrier: one elected lane issues
             tcgen05_fence_after();
             const uint64_t da = umma_desc(A3, 128), db = umma_desc(B1, kTP);
             umma_chain(taddr, da, db, idesc, d >> 4, umma_kstep(128), umma_kstep(kTP));
@@ -485,7 +485,7 @@ __global__ void __launch_bounds__(256) k_mid_tc(BwdCtx c, int t) {
             for (int qq = 0; qq < 4; ++qq) total += sig[(hf2 * 4 + qq) * 16 + e];
             c.part_sig[static_cast<int64_t>(cb) * P + list[base + tid]] = total;
         }
-        if (tid == 0) {
+        if (tid < 32) {   // the whole first warp, converged after the barrier: one elected lane issues
             tcgen05_fence_after();
             const uint64_t db = umma_desc(B2, kTP);
             for (int tl = 0; tl < nT; ++tl) {

@@ -274,7 +274,7 @@ __global__ void __launch_bounds__(128) k_pre_tc(HsnwModel m, const float* z, con
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t taddr = tmem_slot;
-    if (tid == 0) {
+    if (tid < 32) {   // the whole first warp, converged after the barrier: one elected lane issues
         const uint32_t idesc = umma_idesc_bf16(128, 128);
         const uint64_t da = umma_desc(As, 128), db = umma_desc(Bs, 128);
         umma_chain(taddr, da, db, idesc, Kp >> 4, umma_kstep(128), umma_kstep(128));  // two planes per K = 16
@@ -1005,7 +1005,7 @@ __global__ void __launch_bounds__(kUnitTcThreads) k_unit_tc(FwdCtx c, int t) {
         if (base == 0) HSNW_MARK(0, 2);
         tcgen05_fence_before();
         __syncthreads();
-        if (tid == 0) {
+        if (tid < 32) {   // the whole first warp, converged after the barrier: one elected lane issues
             tcgen05_fence_after();
             const uint64_t da = umma_desc(A1, 128), db = umma_desc(B1, TP);
             umma_chain(taddr, da, db, idesc, in >> 4, umma_kstep(128), umma_kstep(TP));
@@ -1051,7 +1051,7 @@ __global__ void __launch_bounds__(kUnitTcThreads) k_unit_tc(FwdCtx c, int t) {
         fence_async_smem();
         tcgen05_fence_before();
         __syncthreads();
-        if (tid == 0) {
+        if (tid < 32) {   // the whole first warp, converged after the barrier: one elected lane issues
             tcgen05_fence_after();
             const uint64_t da = umma_desc(A2, 128), db = umma_desc(B2, TP);
             umma_chain(taddr + TP, da, db, idesc, 8, umma_kstep(128), umma_kstep(TP));

@@ -154,12 +154,14 @@ __host__ __device__ inline RowsSmem rows_smem(const HsnwModel& m, int C, uint32_
 // position, event i of block r at trace[r * 32 + i] (nanoseconds of the global timer); the trace
 // area follows the status word.
 #ifdef HSNW_TRACE
+// (kept in shared memory until the kernel ends: a global store here would make the next block barrier
+// wait for it and distort the very phases being timed)
 #define RMARK(i)                                                                              \
     do {                                                                                      \
         if (tid == 0 && row == 0 && t == T / 2) {                                             \
             unsigned long long now;                                                           \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now) : : "memory");              \
-            reinterpret_cast<unsigned long long*>(c.status + 64)[r * 64 + (i)] = now;         \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));                           \
+            trace_s[(i)] = now;                                                               \
         }                                                                                     \
     } while (0)
 #else
@@ -178,6 +180,9 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
     __shared__ uint32_t tmem_slot;
     __shared__ __align__(8) uint64_t in_bar;   // the next position's inputs (bulk copies by the producer)
     __shared__ uint64_t next_key_s;   // the (K + 1)-th best key of the position's scored order
+#ifdef HSNW_TRACE
+    __shared__ unsigned long long trace_s[64];
+#endif
 
     cg::cluster_group cl = cg::this_cluster();
     const int C = c.C, r = static_cast<int>(cl.block_rank());
@@ -685,8 +690,8 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
 #ifdef HSNW_TRACE
         if (lane == 0 && row == 0 && t == T / 2) {
             unsigned long long now;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now) : : "memory");
-            reinterpret_cast<unsigned long long*>(c.status + 64)[r * 64 + 48 + warp] = now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            trace_s[48 + warp] = now;
         }
 #endif
         __syncthreads();
@@ -801,20 +806,24 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
             const int sh = warp >> 2;                         // its half of the slots: 4 sh .. 4 sh + 3
             const uint32_t idesc = umma_idesc_bf16(128, 16);
             constexpr int steps1 = (4 * d) >> 4;            // K = 16 products of a chunk's first layer
-            constexpr int n1 = steps1 < 8 ? steps1 : 8;     // accumulators they are spread over (columns 128 b + 16 p)
             const uint32_t g0 = g_use;
             float bias_next = (epi && n_chunks > 0) ? c.m.b1[ulist[0] * H + r * 128 + hc] : 0.0f;   // a chunk ahead
-            if (tid == 0 && n_chunks > 0) {
-                const uint32_t slot = ring_slot(g0);
-                ring_wait(&full[slot], ring_round(g0) & 1u, c.status, &failed_s);
+            // a chunk's first product: D1 (tensor memory columns 128 b .. 128 b + 15, b = chunk parity);
+            // issued by warp 0 as a whole (umma.cuh: one elected lane, warp-uniform control flow)
+            auto first_product = [&](int i) {
+                const uint32_t slot = ring_slot(g0 + i);
+                ring_wait(&full[slot], ring_round(g0 + i) & 1u, c.status, &failed_s);
                 tcgen05_fence_after();
                 if (d == 64)
-                    umma_chain_sw128<steps1, n1>(taddr, 16, umma_desc_sw128(ring + slot * c.slot_bytes), (64 * 128) >> 4,
-                                                 umma_desc(vop, 16), umma_kstep(16), idesc, false);
+                    umma_chain_sw128<steps1>(taddr + 128 * (i & 1), umma_desc_sw128(ring + slot * c.slot_bytes), (64 * 128) >> 4,
+                                             umma_desc(vop, 16), umma_kstep(16), idesc, false);
                 else
-                    umma_chain_fixed<steps1, n1>(taddr, 16, umma_desc(ring + slot * c.slot_bytes, 64), umma_desc(vop, 16), idesc,
-                                                 umma_kstep(64), umma_kstep(16), false);
-                umma_commit(&bar_d1[0]);
+                    umma_chain_fixed<steps1>(taddr + 128 * (i & 1), umma_desc(ring + slot * c.slot_bytes, 64), umma_desc(vop, 16), idesc,
+                                             umma_kstep(64), umma_kstep(16), false);
+                umma_commit(&bar_d1[i & 1]);
+            };
+            if (warp == 0 && n_chunks > 0) {
+                first_product(0);
                 RMARK(29);
             }
             if (epi) {
@@ -822,19 +831,8 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 for (int i = 0; i < n_chunks; ++i) {
                     const unsigned mask = static_cast<unsigned>(umask[i >> 1]);
                     const uint32_t slot = ring_slot(g0 + i);
-                    if (tid == 0 && i + 1 < n_chunks) {   // the next chunk's first product runs under this epilogue
-                        const uint32_t nslot = ring_slot(g0 + i + 1);
-                        ring_wait(&full[nslot], ring_round(g0 + i + 1) & 1u, c.status, &failed_s);
-                        tcgen05_fence_after();
-                        if (d == 64)
-                            umma_chain_sw128<steps1, n1>(taddr + 128 * ((i + 1) & 1), 16, umma_desc_sw128(ring + nslot * c.slot_bytes),
-                                                         (64 * 128) >> 4, umma_desc(vop, 16), umma_kstep(16), idesc, false);
-                        else
-                            umma_chain_fixed<steps1, n1>(taddr + 128 * ((i + 1) & 1), 16, umma_desc(ring + nslot * c.slot_bytes, 64),
-                                                         umma_desc(vop, 16), idesc, umma_kstep(64), umma_kstep(16), false);
-                        umma_commit(&bar_d1[(i + 1) & 1]);
-                    }
-                    if (epi) {
+                    if (warp == 0 && i + 1 < n_chunks) first_product(i + 1);   // the next chunk's first product runs under this epilogue
+                    {
                         const float bias = bias_next;
                         if (i + 1 < n_chunks) bias_next = c.m.b1[ulist[(i + 1) >> 1] * H + r * 128 + ((i + 1) & 1) * 64 + hc];
                         uint16_t* b2i = b2 + (i & 1) * (8 * 16 * 8);
@@ -843,13 +841,6 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                         if (i == 0) RMARK(25);
                         float acc[8];
                         tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 128 * (i & 1)), acc);
-    #pragma unroll
-                        for (int p = 1; p < n1; ++p) {   // the partial accumulators
-                            float more[8];
-                            tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 128 * (i & 1) + 16 * p), more);
-    #pragma unroll
-                            for (int q = 0; q < 8; ++q) acc[q] += more[q];
-                        }
     #pragma unroll
                         for (int q = 0; q < 4; ++q) {
                             const int k = 4 * sh + q;
@@ -877,16 +868,15 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                         for (int q = 0; q < 4; ++q)
                             if (mask & (1u << (4 * sh + q))) c.io.rec_hidden[(rt * K + 4 * sh + q) * H + colg] = hid_keep[q];
                     }
-                    if (tid == 0) {
+                    if (warp == 0) {
                         tcgen05_fence_after();
-                        // four partial sums of D2, each over the position's chunks
+                        // D2 (columns 256 .. 271) accumulates over the position's chunks
                         if (d == 64)
-                            umma_chain_sw128<4, 4>(taddr + 256, 16, umma_desc_sw128(ring + slot * c.slot_bytes + c.w1_bytes), 0,
-                                                   umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), umma_kstep(16), idesc, i > 0);
+                            umma_chain_sw128<4>(taddr + 256, umma_desc_sw128(ring + slot * c.slot_bytes + c.w1_bytes), 0,
+                                                umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), umma_kstep(16), idesc, i > 0);
                         else
-                            umma_chain_fixed<4, 4>(taddr + 256, 16, umma_desc(ring + slot * c.slot_bytes + c.w1_bytes, d),
-                                                   umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), idesc, umma_kstep(d), umma_kstep(16),
-                                                   i > 0);
+                            umma_chain_fixed<4>(taddr + 256, umma_desc(ring + slot * c.slot_bytes + c.w1_bytes, d),
+                                                umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), idesc, umma_kstep(d), umma_kstep(16), i > 0);
                         umma_commit(&empty[slot]);
                         if (i + 1 == n_chunks) umma_commit(&bar_d2);
                     }
@@ -930,13 +920,6 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                     ring_wait(&bar_d2, d2_phase & 1u, c.status, &failed_s);
                     tcgen05_fence_after();
                     tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 256), acc);
-#pragma unroll
-                    for (int p = 1; p < 4; ++p) {
-                        float more[8];
-                        tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 256 + 16 * p), more);
-#pragma unroll
-                        for (int k = 0; k < 8; ++k) acc[k] += more[k];
-                    }
                 }
                 RMARK(28);
                 if (hc < d) {
@@ -1154,6 +1137,9 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
     }
     tcgen05_fence_before();
     __syncthreads();
+#ifdef HSNW_TRACE
+    if (row == 0 && tid < 64) reinterpret_cast<unsigned long long*>(c.status + 64)[r * 64 + tid] = trace_s[tid];
+#endif
     if (warp == 0) tmem_dealloc(taddr, 512);
 }
 

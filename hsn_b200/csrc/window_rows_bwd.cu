@@ -33,10 +33,10 @@ namespace {
 #ifdef HSNW_TRACE
 #define BMARK(i)                                                                              \
     do {                                                                                      \
-        if (tid == 0 && row == 0 && t == T / 2 && c.trace) {                                  \
+        if (tid == 0 && row == 0 && t == T / 2) {                                             \
             unsigned long long now;                                                           \
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));                           \
-            c.trace[r * 32 + (i)] = now;                                                      \
+            trace_s[(i)] = now;                                                               \
         }                                                                                     \
     } while (0)
 #else
@@ -111,6 +111,9 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
     __shared__ int failed_s;
     __shared__ __align__(8) uint64_t bar_d1[2], bar_d2;
     __shared__ uint32_t tmem_slot;
+#ifdef HSNW_TRACE
+    __shared__ unsigned long long trace_s[32];   // written to memory when the kernel ends (a store before a barrier delays it)
+#endif
 
     cg::cluster_group cl = cg::this_cluster();
     constexpr int d = D_, two = 2 * D_;
@@ -442,34 +445,27 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
         const uint32_t g0 = g_use;
         float inner[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         tcgen05_fence_after();
-        if (tid == 0 && n_chunks > 0) {
-            const uint32_t slot = g0 % kStagesB;
-            ring_wait(&full[slot], (g0 / kStagesB) & 1u, c.status, &failed_s);
+        // a chunk's first product: D1 (tensor memory columns 64 b .. 64 b + 15, b = chunk parity); issued by
+        // warp 0 as a whole (umma.cuh: one elected lane, warp-uniform control flow)
+        auto first_product = [&](int i) {
+            const uint32_t slot = (g0 + i) % kStagesB;
+            ring_wait(&full[slot], ((g0 + i) / kStagesB) & 1u, c.status, &failed_s);
             if (d == 64)
-                umma_chain_sw128<4, 4>(taddr, 16, umma_desc_sw128(ring + slot * c.bank_bytes), 0, umma_desc(du_op, 16),
-                                       umma_kstep(16), idesc, false);
+                umma_chain_sw128<4>(taddr + 64 * (i & 1), umma_desc_sw128(ring + slot * c.bank_bytes), 0, umma_desc(du_op, 16),
+                                    umma_kstep(16), idesc, false);
             else
-                umma_chain_fixed<d / 16, d / 16>(taddr, 16, umma_desc(ring + slot * c.bank_bytes, 64), umma_desc(du_op, 16), idesc,
-                                                 umma_kstep(64), umma_kstep(16), false);
-            umma_commit(&bar_d1[0]);
-        }
+                umma_chain_fixed<d / 16>(taddr + 64 * (i & 1), umma_desc(ring + slot * c.bank_bytes, 64), umma_desc(du_op, 16), idesc,
+                                         umma_kstep(64), umma_kstep(16), false);
+            umma_commit(&bar_d1[i & 1]);
+        };
+        if (warp == 0 && n_chunks > 0) first_product(0);
         if (epi) {
             for (int i = 0; i < n_chunks; ++i) {
                 const int j = dc_[o_ulist + (i >> 1)];
                 const unsigned mask = static_cast<unsigned>(dc_[o_umask + (i >> 1)]);
                 const uint32_t slot = (g0 + i) % kStagesB;
-                if (tid == 0 && i + 1 < n_chunks) {
-                    const uint32_t nslot = (g0 + i + 1) % kStagesB;
-                    ring_wait(&full[nslot], ((g0 + i + 1) / kStagesB) & 1u, c.status, &failed_s);
-                    if (d == 64)
-                        umma_chain_sw128<4, 4>(taddr + 64 * ((i + 1) & 1), 16, umma_desc_sw128(ring + nslot * c.bank_bytes), 0,
-                                               umma_desc(du_op, 16), umma_kstep(16), idesc, false);
-                    else
-                        umma_chain_fixed<d / 16, d / 16>(taddr + 64 * ((i + 1) & 1), 16, umma_desc(ring + nslot * c.bank_bytes, 64),
-                                                         umma_desc(du_op, 16), idesc, umma_kstep(64), umma_kstep(16), false);
-                    umma_commit(&bar_d1[(i + 1) & 1]);
-                }
-                if (epi) {
+                if (warp == 0 && i + 1 < n_chunks) first_product(i + 1);
+                {
                     const int hid_col = (i & 1) * 64 + hc;
                     const float bias = b1s[j * 128 + hid_col];
                     uint16_t* b2i = b2 + (i & 1) * (8 * 16 * 8);
@@ -477,13 +473,6 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
                     tcgen05_fence_after();
                     float acc[8];
                     tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 64 * (i & 1)), acc);
-    #pragma unroll
-                    for (int p = 1; p < d / 16; ++p) {   // the partial accumulators (one per K = 16 step)
-                        float more[8];
-                        tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 64 * (i & 1) + 16 * p), more);
-    #pragma unroll
-                        for (int q = 0; q < 8; ++q) acc[q] += more[q];
-                    }
     #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         const int k = 4 * sh + q;
@@ -501,20 +490,23 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
                 if (i & 1) ++d1_count1;
                 else ++d1_count0;
                 asm volatile("bar.sync 2, 128;\n" ::: "memory");   // the four epilogue warps
-                if (tid == 0) {
+                if (warp == 0) {
                     tcgen05_fence_after();
+                    // D2 (columns 128 .. 143) accumulates over the position's chunks
                     if (d == 64)
-                        umma_chain_sw128<4, 4>(taddr + 128, 16, umma_desc_sw128(ring + slot * c.bank_bytes + c.w2_bytes), 0,
-                                               umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), umma_kstep(16), idesc, i > 0);
+                        umma_chain_sw128<4>(taddr + 128, umma_desc_sw128(ring + slot * c.bank_bytes + c.w2_bytes), 0,
+                                            umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), umma_kstep(16), idesc, i > 0);
                     else
-                        umma_chain_fixed<4, 4>(taddr + 128, 16, umma_desc(ring + slot * c.bank_bytes + c.w2_bytes, two),
-                                               umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), idesc, umma_kstep(two), umma_kstep(16), i > 0);
+                        umma_chain_fixed<4>(taddr + 128, umma_desc(ring + slot * c.bank_bytes + c.w2_bytes, two),
+                                            umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), idesc, umma_kstep(two), umma_kstep(16), i > 0);
                     umma_commit(&empty[slot]);
                     if (i + 1 == n_chunks) umma_commit(&bar_d2);
-                    ++g_use;
-                    issue_ahead();
+                    if (lane == 0) {
+                        ++g_use;
+                        issue_ahead();
+                    }
+                    __syncwarp();
                 }
-                __syncwarp();
             }
         } else {
             // the gate's transposed linear, this block's state outputs, by the other four warps; first
@@ -553,13 +545,6 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
                 ring_wait(&bar_d2, d2_phase & 1u, c.status, &failed_s);
                 tcgen05_fence_after();
                 tmem_ld8(tmem_addr(taddr, 32 * warp, 128), acc);
-#pragma unroll
-                for (int p = 1; p < 4; ++p) {
-                    float more[8];
-                    tmem_ld8(tmem_addr(taddr, 32 * warp, 128 + 16 * p), more);
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) acc[k] += more[k];
-                }
             }
             const int i = 32 * warp + lane;
             if (i < two) {
@@ -642,6 +627,9 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
     }
     tcgen05_fence_before();
     __syncthreads();
+#ifdef HSNW_TRACE
+    if (row == 0 && tid < 32 && c.trace) c.trace[r * 32 + tid] = trace_s[tid];
+#endif
     if (warp == 0) tmem_dealloc(taddr, 256);
 }
 
