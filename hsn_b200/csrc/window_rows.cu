@@ -49,6 +49,8 @@
 #include "rows.cuh"
 #include "umma.cuh"
 
+#include <type_traits>
+
 using namespace hsnw;
 
 namespace {
@@ -127,7 +129,7 @@ __host__ __device__ inline RowsSmem rows_smem(const HsnwModel& m, int C, uint32_
     L.msg = take(4 * K * d);
     L.rms = take(4 * K);
     L.graph = take(4 * N * D);          // every cell's sources and edge weights: (source << 16) | bf16 weight
-    L.gacc = take(4 * K * d);
+    L.gacc = take(4 * (K * d > Nc * M ? K * d : Nc * M));   // phase D: the gate's partial sums; phases A-B: the cells' part of the logits
     L.inbox_front = take(4 * C * (2 * d + 4));
     L.inbox_f = take(4 * C * Ks * 2 * d);
     L.in_scal = take(4 * Nc * S + 16);
@@ -151,22 +153,48 @@ __host__ __device__ inline RowsSmem rows_smem(const HsnwModel& m, int C, uint32_
 }
 
 // Optional phase timestamps for tuning (-DHSNW_TRACE): thread 0 of row 0's blocks, at the middle
-// position, event i of block r at trace[r * 32 + i] (nanoseconds of the global timer); the trace
+// position, event i of block r at trace[r * 32 + i] (cycles of the SM's clock: reading the global timer takes about a microsecond, which back-to-back marks would show as phase time); the trace
 // area follows the status word.
 #ifdef HSNW_TRACE
 // (kept in shared memory until the kernel ends: a global store here would make the next block barrier
-// wait for it and distort the very phases being timed)
+// wait for it and distort the very phases being timed; the clock read takes a value just loaded from
+// shared memory as an operand, because the assembler otherwise moves a clock read across a barrier)
 #define RMARK(i)                                                                              \
     do {                                                                                      \
         if (tid == 0 && row == 0 && t == T / 2) {                                             \
             unsigned long long now;                                                           \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));                           \
+            const int pin = *reinterpret_cast<volatile int*>(&failed_s);                     \
+            asm volatile("mov.u64 %0, %%clock64;" : "=l"(now) : "r"(pin) : "memory");        \
             trace_s[(i)] = now;                                                               \
         }                                                                                     \
     } while (0)
 #else
 #define RMARK(i) do { } while (0)
 #endif
+
+// The K + 1 largest of the unique, non-zero 32-bit keys a warp holds (PER a lane, 0 = none), in
+// descending order: lane r returns the r-th largest (0 when there are fewer). K + 1 rounds of a
+// warp-wide maximum (one redux instruction); the lane that holds the winner drops it.
+template <int PER>
+__device__ __forceinline__ uint32_t warp_top_keys(uint32_t (&key)[PER], int K, int lane) {
+    uint32_t best = 0u;
+#pragma unroll
+    for (int s = 0; s < PER; ++s) best = max(best, key[s]);
+    uint32_t kept = 0u;
+    for (int r = 0; r <= K; ++r) {
+        const uint32_t win = __reduce_max_sync(0xffffffffu, best);
+        if (lane == r) kept = win;
+        if (win != 0u && best == win) {
+            best = 0u;
+#pragma unroll
+            for (int s = 0; s < PER; ++s) {
+                if (key[s] == win) key[s] = 0u;
+                best = max(best, key[s]);
+            }
+        }
+    }
+    return kept;
+}
 
 template <int D_>
 __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
@@ -234,6 +262,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
     uint16_t* b2 = reinterpret_cast<uint16_t*>(dyn + L.b2);
     uint32_t* graph = reinterpret_cast<uint32_t*>(dyn + L.graph);
     float* gacc = reinterpret_cast<float*>(dyn + L.gacc);
+    float* part_s = gacc;   // [Nc][M] between phase A and phase B
     float* inbox_front = reinterpret_cast<float*>(dyn + L.inbox_front);
     float* inbox_f = reinterpret_cast<float*>(dyn + L.inbox_f);
     float* inbox_delta = reinterpret_cast<float*>(dyn + L.inbox_delta);
@@ -353,6 +382,18 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
     }
     cl.sync();
 
+    // The part of a cell's logit for unit j that does not depend on the row's (u, eps): the state's part,
+    // the age term and the scalars, summed in the scorer's order (the row term and the bias are added to
+    // it in phase B, so the sum is the one the whole scorer makes).
+    const float age_div = static_cast<float>(c.m.age_max);
+    auto cell_part = [&](int i, int j) {
+        float acc = lh_s[i * M + j];
+        acc += bf16r(static_cast<float>(age_s[i]) / age_div) * sw_tail[j];
+        for (int sI = 0; sI < Sn; ++sI) acc += bf16r(in_scal[i * Sn + sI]) * sw_tail[(1 + sI) * M + j];
+        return acc;
+    };
+    const uint32_t m_magic = M > 1 ? magic_of(M) : 0u;
+
     for (int t = 0; t < T; ++t) {
         const int64_t rt = static_cast<int64_t>(row) * T + t;
         const bool last = t + 1 == T;
@@ -427,6 +468,11 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 for (int p = 0; p < C; ++p) mx = max(mx, __float_as_int(inbox_front[p * stride_in + 2 * d]));
                 c.io.h_max[rt - 1] = __int_as_float(mx);
             }
+            // the block's cells' part of the logits (everything but the row's term), a (cell, unit) pair a thread
+            for (int o = tid; o < Nc * M; o += kConsumers) {
+                const int i = M > 1 ? div_magic(o, m_magic) : o;
+                part_s[o] = cell_part(i, o - i * M);
+            }
             consumer_sync();
             RMARK(14);
             for (int j = warp; j < M; j += kConsumers / 32) {
@@ -438,7 +484,6 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
             consumer_sync();
             RMARK(15);
             const float lambda = c.m.lambda_cost;
-            const float age_div = static_cast<float>(c.m.age_max);
             // four threads per cell, each with the units sub, sub + 4, ...; the quad then keeps the
             // first maximiser (the higher score, the lower unit on a tie)
             for (int i0 = 0; i0 < Nc; i0 += kConsumers / 4) {
@@ -448,19 +493,11 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 int64_t ag = 0;
                 if (i < Nc) {
                     ag = age_s[i];
-                    float feat[17];   // the age term, then the scalars (S <= 16)
-                    feat[0] = bf16r(static_cast<float>(ag) / age_div);
-#pragma unroll
-                    for (int sI = 0; sI < 16; ++sI) feat[1 + sI] = sI < Sn ? bf16r(in_scal[i * Sn + sI]) : 0.0f;
 #pragma unroll
                     for (int jj = 0; jj < kMaxMR / 4; ++jj) {
                         const int j = sub + 4 * jj;
                         if (j < M) {
-                            float acc = lh_s[i * M + j];
-#pragma unroll
-                            for (int sI = 0; sI < 17; ++sI)
-                                if (sI <= Sn) acc += feat[sI] * sw_tail[sI * M + j];
-                            const float logit = bf16r(acc + rowterm[j] + score_b[j]);
+                            const float logit = bf16r(part_s[i * M + j] + rowterm[j] + score_b[j]);
                             if (c.io.logits) c.io.logits[(rt * N + cell0 + i) * M + j] = logit;
                             const float sc = lambda > 0.0f ? __fsub_rn(logit, __fmul_rn(lambda, S.cost[j])) : logit;
                             if (jj == 0 || sc > best) {
@@ -504,89 +541,55 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
         int* old_rank = stale_w + 8;                          // [K] the same flag for the K best
         if (!producer && !c.io.forced) {
             int n_old = 0;
-            if (c.m.lambda_cost == 0.0f && N <= kConsumers) {
+            if (c.m.lambda_cost == 0.0f) {
                 // the scores are bf16 values here (rounded logits, no cost term): the low half of
                 // their order word carries nothing, so (score's high half, 0xffff - index) is a
-                // 32-bit key with the same order, unique per cell. One key a thread: every warp sorts
-                // its 32 keys (a bitonic network of shuffles), the warps' K + 1 best meet in shared
-                // memory and one warp ranks those 8 (K + 1) candidates by counting.
-                uint32_t* wtop = reinterpret_cast<uint32_t*>(keys);   // [8][K + 1], padded to a multiple of 4 with zeros
-                const int i = tid;
-                uint32_t key = i < N ? ((float_order(score_all[i]) & 0xffff0000u) | (0xffffu - static_cast<uint32_t>(i))) : 0u;
-                const bool old = i < N && age_all[i] > static_cast<int64_t>(c.m.age_max);
-                n_old = __popc(__ballot_sync(0xffffffffu, old));
+                // 32-bit key with the same order, unique per cell. A thread holds the keys of the cells
+                // tid, tid + 256, ...; every warp finds its K + 1 best by rounds of a warp-wide
+                // maximum, the warps' lists meet in shared memory and warp 0 takes the K + 1 best of
+                // those the same way: lane r then holds the cell of rank r.
+                uint32_t* wtop = reinterpret_cast<uint32_t*>(keys);   // [8][K + 1]
+                const int64_t age_max = static_cast<int64_t>(c.m.age_max);
+                auto own_keys = [&](auto per) {
+                    constexpr int PER = decltype(per)::value;
+                    uint32_t key[PER];
+                    int old = 0;
 #pragma unroll
-                for (int k2 = 2; k2 <= 32; k2 <<= 1) {
-#pragma unroll
-                    for (int j = k2 >> 1; j > 0; j >>= 1) {
-                        const uint32_t other = __shfl_xor_sync(0xffffffffu, key, j);
-                        const bool keep_max = ((lane & j) == 0) == ((lane & k2) == 0);   // descending
-                        key = keep_max ? max(key, other) : min(key, other);
-                    }
-                }
-                RMARK(32);
-                const int n_cand = (kConsumers / 32) * (K + 1), n_cand_pad = (n_cand + 3) & ~3;
-                if (lane <= K) wtop[warp * (K + 1) + lane] = key;
-                if (tid >= n_cand && tid < n_cand_pad) wtop[tid] = 0u;
-                if (tid == 0) next_key_s = 0ull;
-                if (lane == 0) stale_w[warp] = n_old;
-                consumer_sync();
-                RMARK(33);
-                if (tid < n_cand) {   // a thread per candidate
-                    const uint4* cand4 = reinterpret_cast<const uint4*>(wtop);
-                    const uint32_t mine = wtop[tid];
-                    int r0 = 0, r1 = 0, r2 = 0, r3 = 0;
-#pragma unroll 6
-                    for (int j4 = 0; j4 < n_cand_pad >> 2; ++j4) {
-                        const uint4 o = cand4[j4];
-                        r0 += o.x > mine;
-                        r1 += o.y > mine;
-                        r2 += o.z > mine;
-                        r3 += o.w > mine;
-                    }
-                    const int rank = (r0 + r1) + (r2 + r3);
-                    if (mine != 0u && rank <= K) {
-                        const int cell = static_cast<int>(0xffffu - (mine & 0xffffu));
-                        if (rank < K) {
-                            S.order[rank] = cell;
-                            old_rank[rank] = age_all[cell] > static_cast<int64_t>(c.m.age_max) ? 1 : 0;
-                        } else {
-                            next_key_s = pack_key(score_all[cell], cell);
+                    for (int sI = 0; sI < PER; ++sI) {
+                        const int i = tid + sI * kConsumers;
+                        key[sI] = 0u;
+                        if (i < N) {
+                            key[sI] = (float_order(score_all[i]) & 0xffff0000u) | (0xffffu - static_cast<uint32_t>(i));
+                            old += age_all[i] > age_max ? 1 : 0;
                         }
                     }
-                }
+                    const uint32_t kept = warp_top_keys<PER>(key, K, lane);
+                    if (lane <= K) wtop[warp * (K + 1) + lane] = kept;
+                    old = __reduce_add_sync(0xffffffffu, old);
+                    if (lane == 0) stale_w[warp] = old;
+                };
+                if (N <= kConsumers) own_keys(std::integral_constant<int, 1>{});
+                else if (N <= 2 * kConsumers) own_keys(std::integral_constant<int, 2>{});
+                else if (N <= 4 * kConsumers) own_keys(std::integral_constant<int, 4>{});
+                else own_keys(std::integral_constant<int, 8>{});
+                RMARK(32);
                 consumer_sync();
+                RMARK(33);
+                if (warp == 0) {
+                    const int n_cand = (kConsumers / 32) * (K + 1);   // at most 72
+                    uint32_t cand3[3];
+#pragma unroll
+                    for (int sI = 0; sI < 3; ++sI) cand3[sI] = lane + 32 * sI < n_cand ? wtop[lane + 32 * sI] : 0u;
+                    const uint32_t kept = warp_top_keys<3>(cand3, K, lane);
+                    const int cell = static_cast<int>(0xffffu - (kept & 0xffffu));
+                    if (lane < K && kept != 0u) {
+                        S.order[lane] = cell;
+                        old_rank[lane] = age_all[cell] > age_max ? 1 : 0;
+                    }
+                    if (lane == K) next_key_s = kept != 0u ? pack_key(score_all[cell], cell) : 0ull;
+                    __syncwarp();
+                }
                 n_old = -1;   // the counts are in place
-            } else if (c.m.lambda_cost == 0.0f) {
-                // more cells than threads: a cell's place is the number of larger keys, counted by the
-                // cell's thread against all keys
-                uint32_t* key32 = reinterpret_cast<uint32_t*>(keys);   // [N] padded to a multiple of 4 with zeros
-                for (int i = tid; i < ((N + 3) & ~3); i += kConsumers)
-                    key32[i] = i < N ? ((float_order(score_all[i]) & 0xffff0000u) | (0xffffu - static_cast<uint32_t>(i))) : 0u;
-                if (tid == 0) next_key_s = 0ull;
-                consumer_sync();
-                const uint4* key4 = reinterpret_cast<const uint4*>(key32);
-                for (int i = tid; i < N; i += kConsumers) {
-                    const uint32_t mine = key32[i];
-                    int r0 = 0, r1 = 0, r2 = 0, r3 = 0;   // four independent counts
-#pragma unroll 16
-                    for (int j4 = 0; j4 < (N + 3) >> 2; ++j4) {
-                        const uint4 o = key4[j4];
-                        r0 += o.x > mine;
-                        r1 += o.y > mine;
-                        r2 += o.z > mine;
-                        r3 += o.w > mine;
-                    }
-                    const int rank = (r0 + r1) + (r2 + r3);
-                    const bool old = age_all[i] > static_cast<int64_t>(c.m.age_max);
-                    n_old += old ? 1 : 0;
-                    if (rank < K) {
-                        S.order[rank] = i;
-                        old_rank[rank] = old ? 1 : 0;
-                    } else if (rank == K) {
-                        next_key_s = pack_key(score_all[i], i);
-                    }
-                }
             } else {
                 for (int i = tid; i < N; i += kConsumers) keys[i] = pack_key(score_all[i], i);
                 if (tid == 0) next_key_s = 0ull;
@@ -672,29 +675,37 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 my_unit = ok ? S.out_unit[k] : -1;
                 unit_of[k] = my_unit;
             }
-            // the units in use, ascending, and each one's slots as a bit mask
-            int n = 0;
-            for (int j = 0; j < M; ++j) {
-                const unsigned mask = __ballot_sync(0xffffffffu, my_unit == j);
-                if (mask) {
-                    if (lane == 0) {
-                        ulist[n] = j;
-                        umask[n] = static_cast<int>(mask);
-                    }
-                    ++n;
-                }
+            // the units in use, ascending, and each one's slots as a bit mask: the set of units by one
+            // warp-wide OR, a unit's place = the number of smaller units in the set, its slots = the
+            // lanes that hold the same unit
+            const unsigned in_use = __reduce_or_sync(0xffffffffu, my_unit >= 0 ? 1u << my_unit : 0u);
+            const unsigned same = __match_any_sync(0xffffffffu, my_unit);
+            if (my_unit >= 0 && (same & ((1u << lane) - 1u)) == 0u) {   // the unit's first slot writes its entry
+                const int at = __popc(in_use & ((1u << my_unit) - 1u));
+                ulist[at] = my_unit;
+                umask[at] = static_cast<int>(same);
             }
+            const int n = __popc(in_use);
             if (lane == 0) n_units_s = n;
             RMARK(18);
         }
 #ifdef HSNW_TRACE
         if (lane == 0 && row == 0 && t == T / 2) {
             unsigned long long now;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            const int pin = *reinterpret_cast<volatile int*>(&failed_s);
+            asm volatile("mov.u64 %0, %%clock64;" : "=l"(now) : "r"(pin) : "memory");
             trace_s[48 + warp] = now;
         }
 #endif
         __syncthreads();
+#ifdef HSNW_TRACE
+        if (lane == 0 && row == 0 && t == T / 2) {
+            unsigned long long now;
+            const int pin = *reinterpret_cast<volatile int*>(&failed_s);
+            asm volatile("mov.u64 %0, %%clock64;" : "=l"(now) : "r"(pin) : "memory");
+            trace_s[36 + warp] = now;   // when each warp leaves the barrier
+        }
+#endif
         RMARK(5);
         const int n_units = n_units_s;
         // ---------------- D
@@ -938,6 +949,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
         RMARK(9);
         cl.sync();   // 3
         RMARK(10);
+
         // ---------------- E: the update of the block's slots (k = kl C + r)
         if (!producer) {
             for (int e = tid; e < Ks * d; e += kConsumers) {
