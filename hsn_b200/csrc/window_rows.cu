@@ -754,19 +754,59 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
             }
         } else {
             RMARK(24);
-            for (int e = tid; e < K * d; e += kConsumers) {
-                const int k = e / d, x = e - k * d;
-                const int cell = S.out_cell[k];
-                const int co = owner_of(cell);
-                hold[e] = peer(cl, h_s, co)[(cell - co * Nc) * d + x];
-                float sum = 0.0f;
-                for (int jj = 0; jj < D; ++jj) {   // edge order; the sources' V h rows at their owners
-                    const uint32_t edge = graph[cell * D + jj];
-                    const int sc = static_cast<int>(edge >> 16);
-                    const int so = owner_of(sc);
-                    sum += bf16_value(peer(cl, vh_s, so)[(sc - so * Nc) * d + x]) * bf16_lo(edge);
+            // Every value comes from another block's shared memory (a few hundred cycles each): all the loads
+            // of a thread's elements are issued before the first use, four edges at a time, instead of one
+            // after the other.
+            for (int e0 = tid; e0 < K * d; e0 += 2 * kConsumers) {
+                const float* hp[2];
+                const uint16_t* vp[2][4];
+                float ew[2][4];
+                float hv[2], sum[2] = {0.0f, 0.0f};
+                uint16_t vv[2][4];
+                int cellv[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int e = e0 + u * kConsumers;
+                    const int k = e < K * d ? e / d : 0, x = e < K * d ? e - k * d : 0;
+                    const int cell = S.out_cell[k];
+                    cellv[u] = cell;
+                    const int co = owner_of(cell);
+                    hp[u] = peer(cl, h_s, co) + (cell - co * Nc) * d + x;
                 }
-                msg[e] = bf16r(sum);
+#pragma unroll
+                for (int u = 0; u < 2; ++u) hv[u] = *hp[u];
+                for (int j0 = 0; j0 < D; j0 += 4) {   // edge order
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int e = e0 + u * kConsumers;
+                        const int x = e < K * d ? e % d : 0;
+#pragma unroll
+                        for (int jj = 0; jj < 4; ++jj) {
+                            const uint32_t edge = j0 + jj < D ? graph[cellv[u] * D + j0 + jj] : 0u;
+                            const int sc = static_cast<int>(edge >> 16);
+                            const int so = owner_of(sc);
+                            vp[u][jj] = peer(cl, vh_s, so) + (sc - so * Nc) * d + x;
+                            ew[u][jj] = bf16_lo(edge);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 2; ++u)
+#pragma unroll
+                        for (int jj = 0; jj < 4; ++jj) vv[u][jj] = *vp[u][jj];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u)
+#pragma unroll
+                        for (int jj = 0; jj < 4; ++jj)
+                            if (j0 + jj < D) sum[u] += bf16_value(vv[u][jj]) * ew[u][jj];
+                }
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int e = e0 + u * kConsumers;
+                    if (e < K * d) {
+                        hold[e] = hv[u];
+                        msg[e] = bf16r(sum[u]);
+                    }
+                }
             }
             // rows 8..15 of the two activation operands (their bytes belong to other phases' data)
             for (int e = tid; e < 2 * 8 * 8; e += kConsumers) {
