@@ -177,7 +177,7 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
               o_n = o_umask + kMaxMB, o_own_n = o_n + 1, o_own = o_n + 2;   // own: the updates u whose target is a cell of this block
 
     // the records of position t, asynchronously, into buffer t & 1
-    auto prefetch = [&](int t) {
+    auto prefetch = [&](int t, int me, int crew) {   // by `crew` threads, `me` this one's index among them
         const int buf = t & 1;
         const int64_t rt = static_cast<int64_t>(row) * T + t;
         float* rc = rec_of(buf);
@@ -185,19 +185,19 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
 #pragma unroll
         for (int a = 0; a < 7; ++a) {   // the array's index is a constant in every copy of the body
             if (!srcs[a]) continue;
-            for (int e = tid; e < Ks * (d / 4); e += kConsumers) {
+            for (int e = me; e < Ks * (d / 4); e += crew) {
                 const int kl = e / (d / 4), x4 = e - kl * (d / 4);
                 const int k = kl * C + r;
                 if (k < K) cp_async16(rc + (a * Ks + kl) * d + 4 * x4, srcs[a] + (rt * K + k) * d + 4 * x4);
             }
         }
         float* hd = hid_of(buf);
-        for (int e = tid; e < K * 32; e += kConsumers) {
+        for (int e = me; e < K * 32; e += crew) {
             const int k = e >> 5, c4 = e & 31;
             cp_async16(hd + k * 128 + 4 * c4, c.io.hidden + (rt * K + k) * H + r * 128 + 4 * c4);
         }
         float* q = dq_of(buf);
-        for (int e = tid; e < 2 * (d / 4); e += kConsumers) {
+        for (int e = me; e < 2 * (d / 4); e += crew) {
             const int which = e / (d / 4), x4 = e - which * (d / 4);
             const float* from = which == 0 ? c.io.d_q_post : c.io.d_q_pre;
             if (from) cp_async16(q + which * d + 4 * x4, from + rt * d + 4 * x4);
@@ -208,36 +208,36 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
     // loads' latency is spent under other work
     int ld_cell = -1, ld_unit = -1, ld_tgt = -1;
     float ld_ew = 0.0f, ld_rms = 0.0f;
-    auto decision_load = [&](int t) {
+    auto decision_load = [&](int t, int me) {   // `me`: the thread's index among the (at least 128) that call it
         const int64_t rt = static_cast<int64_t>(row) * T + t;
-        if (tid < K) {
-            const bool ok = c.io.valid[rt * K + tid] != 0;
-            ld_cell = ok ? static_cast<int>(c.io.cells[rt * K + tid]) : -1;
-            ld_unit = ok ? static_cast<int>(c.io.units[rt * K + tid]) : -1;
+        if (me < K) {
+            const bool ok = c.io.valid[rt * K + me] != 0;
+            ld_cell = ok ? static_cast<int>(c.io.cells[rt * K + me]) : -1;
+            ld_unit = ok ? static_cast<int>(c.io.units[rt * K + me]) : -1;
         }
-        if (tid >= 32 && tid < 32 + K * D) {
-            const int e = tid - 32, k = div_D(e), jj = e - k * D;
+        if (me >= 32 && me < 32 + K * D) {
+            const int e = me - 32, k = div_D(e), jj = e - k * D;
             const bool ok = c.io.valid[rt * K + k] != 0;
             const int n = ok ? static_cast<int>(c.io.cells[rt * K + k]) : 0;
             ld_tgt = ok ? c.m.pad_src[n * D + jj] : -1;
             ld_ew = ok ? c.m.edge_w[n * D + jj] : 0.0f;
         }
-        if (tid >= 128 && tid < 128 + Ks) {
-            const int k = (tid - 128) * C + r;
+        if (me >= 128 - 8 && me < 128 - 8 + Ks) {
+            const int k = (me - (128 - 8)) * C + r;
             ld_rms = k < K ? c.io.rms[rt * K + k] : 0.0f;
         }
     };
-    auto decision_store = [&](int t) {
+    auto decision_store = [&](int t, int me) {
         int* dc_ = dec_of(t & 1);
-        if (tid < K) {
-            dc_[tid] = ld_cell;
-            dc_[o_unit + tid] = ld_unit;
+        if (me < K) {
+            dc_[me] = ld_cell;
+            dc_[o_unit + me] = ld_unit;
         }
-        if (tid >= 32 && tid < 32 + K * D) {
-            dc_[o_tgt + tid - 32] = ld_tgt;
-            reinterpret_cast<float*>(dc_)[o_ew + tid - 32] = ld_ew;
+        if (me >= 32 && me < 32 + K * D) {
+            dc_[o_tgt + me - 32] = ld_tgt;
+            reinterpret_cast<float*>(dc_)[o_ew + me - 32] = ld_ew;
         }
-        if (tid >= 128 && tid < 128 + Ks) rec_of(t & 1)[7 * Ks * d + tid - 128] = ld_rms;
+        if (me >= 128 - 8 && me < 128 - 8 + Ks) rec_of(t & 1)[7 * Ks * d + me - (128 - 8)] = ld_rms;
     };
     // the units a position's slots ran, ascending, with each one's slots as a bit mask (warp 0)
     auto unit_lists = [&](int t) {
@@ -307,9 +307,9 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
     tcgen05_fence_after();
     const uint32_t taddr = tmem_slot;
     uint32_t d1_count0 = 0, d1_count1 = 0, d2_phase = 0;
-    prefetch(T - 1);
-    decision_load(T - 1);
-    decision_store(T - 1);
+    prefetch(T - 1, tid, kConsumers);
+    decision_load(T - 1, tid);
+    decision_store(T - 1, tid);
     __syncthreads();
     if (warp == 0) unit_lists(T - 1);
     // the chunk stream: thread 0 keeps up to three copies in flight, across positions
@@ -351,12 +351,8 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
         const bool cut = c.io.reset[rt] != 0;
         BMARK(0);
         // ---------------- H
-        cp_async_wait_all();
+        cp_async_wait_all();   // (the copies of this position's record, requested a position ago by the gate's warps)
         __syncthreads();
-        if (t > 0) {
-            prefetch(t - 1);
-            decision_load(t - 1);
-        }
         if (tid < d) Rs[tid] = R_s[tid] + q[tid];
         __syncthreads();
         for (int e = tid; e < Ks * d; e += kConsumers) {
@@ -420,16 +416,6 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
         cl.sync();   // 1
         BMARK(2);
         // ---------------- M
-        if (t > 0) decision_store(t - 1);
-        __syncthreads();
-        if (warp == 0) {
-            if (t > 0) {
-                unit_lists(t - 1);
-                ready_t = t - 1;
-            }
-            if (lane == 0) issue_ahead();
-            __syncwarp();
-        }
         BMARK(3);
         // the transposed layers on the streamed chunks, on the tensor cores. Per chunk (unit j, 64
         // hidden columns): D1 [64 columns, 16 slots] = W2 part x d_unit^T; the epilogue multiplies by
@@ -525,10 +511,18 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
                 const float sum = dc_[k] >= 0 ? dot_bf16w(dg_all + k * d, 1, gate + il * d, 1, d) : 0.0f;
                 peer(cl, inbox_g, k & cmask)[(k >> cshift) * two + r * gcols + il] = sum;
             }
+            // these warps wait for the epilogues anyway: the next position's record is requested here, and
+            // its decision read, off the position's critical path
+            if (t > 0) {
+                prefetch(t - 1, t2, 128);
+                decision_load(t - 1, t2);
+                decision_store(t - 1, t2);
+            }
         }
         __syncthreads();
         if (tid != 0) g_use += n_chunks;
         BMARK(4);
+        if (warp == 7 && t > 0) unit_lists(t - 1);   // (a warp with nothing else to do here)
         // the slots' inner products: the epilogue warps' sums, then the pair of warps of each half
         if (epi) {
 #pragma unroll
@@ -557,6 +551,10 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
         if (n_chunks > 0) ++d2_phase;
         tcgen05_fence_before();
         __syncthreads();
+        if (tid == 0) {   // the next position's decision is in place: its chunks may be requested
+            if (t > 0) ready_t = t - 1;
+            issue_ahead();
+        }
         if (tid < K) {
             const int k = tid, half = k >> 2, q = k & 3;
             const float sum = red[(4 * half) * 4 + q] + red[(4 * half + 1) * 4 + q];   // warps 4 half, 4 half + 1
