@@ -74,6 +74,23 @@ class HsnwBackward(Structure):
     )
 
 
+PROLOGUE_INTS = ("B", "T", "V", "d", "H", "dc", "N", "S", "prod_bf16", "position_mode", "ema_per_row", "bos")
+PROLOGUE_FLOATS = ("budget_frac", "round_frac", "n_context", "unroll")
+PROLOGUE_POINTERS = (
+    "byte_emb", "enc_w1", "enc_b1", "enc_w2", "enc_b2", "ctx_emb", "byte_codes", "cell_addresses", "ema_utility",
+    "ema_selected", "tokens", "ctx_ids", "reset", "pos0", "prev_tokens", "z", "ctx", "scalars", "positions", "scratch",
+)  # fmt: skip
+
+
+class HsnwPrologue(Structure):
+    _fields_ = (
+        [(n, c_int32) for n in PROLOGUE_INTS]
+        + [(n, c_float) for n in PROLOGUE_FLOATS]
+        + [(n, c_void_p) for n in PROLOGUE_POINTERS]
+        + [("scratch_bytes", c_int64)]
+    )
+
+
 #: Every symbol ``include/hsn_window_b200.h`` declares: (restype, argtypes).
 SYMBOLS: dict[str, tuple[object, list[object]]] = {
     "hsnw_version": (c_int, []),
@@ -101,6 +118,8 @@ SYMBOLS: dict[str, tuple[object, list[object]]] = {
     "hsnw_window_backward_static": (c_int, [POINTER(HsnwModel), POINTER(HsnwBackward), c_void_p]),
     "hsnw_front_projection": (c_int, [POINTER(HsnwModel), c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "hsnw_selftest_wait_timeout": (c_int, [c_void_p, c_void_p]),
+    "hsnw_prologue_scratch_bytes": (c_int64, [POINTER(HsnwPrologue)]),
+    "hsnw_window_prologue": (c_int, [POINTER(HsnwPrologue), c_void_p]),
     "hsnw_profile_begin": (c_int, []),
     "hsnw_profile_kinds": (c_int, []),
     "hsnw_profile_kind_name": (c_char_p, [c_int]),

@@ -253,7 +253,7 @@ namespace {
 struct ProfileMark { cudaEvent_t event; int kind; };
 std::vector<ProfileMark> profile_marks;
 cudaStream_t profile_stream = nullptr;
-const char* const kind_names[HSNW_K_KINDS] = {"init", "pre", "front", "row", "unit", "update", "head", "mid", "tail_head", "rows_fwd", "rows_bwd"};
+const char* const kind_names[HSNW_K_KINDS] = {"init", "pre", "front", "row", "unit", "update", "head", "mid", "tail_head", "rows_fwd", "rows_bwd", "prologue"};
 }  // namespace
 
 void hsnw_profile_mark_slow(int kind, cudaStream_t stream) {

@@ -1,0 +1,160 @@
+// The window's prologue on the device: from the token and context ids of a window to what the forward
+// sweep reads per position (reference python/hsn/model/hsn.py:1707-1860 with model.key_address on,
+// one address byte, no reader; python/hsn/model/router.py:597-765):
+//   z [B,T,d]        = E(byte_emb(x_t)), the encoder's two-layer MLP (python/hsn/model/encoder.py:74-128)
+//   ctx [B,T,dc]     = ctx_emb(context id)
+//   scalars [B,T,N,S] = budget, round, context id / n_context, the two running averages per cell,
+//                       position / unroll, one, and (S = 9) the two address features
+//                       sqrt(d) <byte_codes[x], cell_addresses[n]> of the current and the previous byte
+//   positions [B,T]  = the session position before each step (hsn.py:347-355)
+// Everything here is a function of an id: the encoder's output depends on the byte alone, the address
+// feature on (byte, cell). So two small tables are built per call, z_table [V,d] and addr_table [V,N]
+// (the weights change between windows, the tables are cheap: V rows), and the window itself is gathers
+// and one coalesced write of the scalars, which is what bounds it (HBM writes: 4 N S bytes a row-position).
+#include "../../include/hsn_window_b200.h"
+#include "common.cuh"
+#include "host_util.h"
+
+using namespace hsnw;
+
+namespace {
+
+constexpr int kTableThreads = 128;
+
+// One block per byte value v: z_table[v] = fc2(act(fc1(emb[v]))), addr_table[v][n].
+// Dynamic shared memory: d + H floats.
+__global__ void k_pro_tables(HsnwPrologue p, float* z_table, float* addr_table) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    float* x = reinterpret_cast<float*>(dyn);   // [d]  the byte's embedding
+    float* hid = x + p.d;                        // [H]
+    const int v = blockIdx.x, tid = threadIdx.x;
+    const bool bf = p.prod_bf16 != 0;
+    for (int i = tid; i < p.d; i += kTableThreads) x[i] = maybe_bf16(p.byte_emb[static_cast<int64_t>(v) * p.d + i], bf);
+    __syncthreads();
+    for (int h = tid; h < p.H; h += kTableThreads) {
+        const float* w = p.enc_w1 + static_cast<int64_t>(h) * p.d;   // nn.Linear layout [out, in]
+        float sum = 0.0f;
+        for (int i = 0; i < p.d; ++i) sum += x[i] * maybe_bf16(w[i], bf);
+        const float pre = maybe_bf16(sum + maybe_bf16(p.enc_b1[h], bf), bf);
+        hid[h] = maybe_bf16(gelu_erf(pre), bf);
+    }
+    __syncthreads();
+    for (int o = tid; o < p.d; o += kTableThreads) {
+        const float* w = p.enc_w2 + static_cast<int64_t>(o) * p.H;
+        float sum = 0.0f;
+        for (int h = 0; h < p.H; ++h) sum += hid[h] * maybe_bf16(w[h], bf);
+        z_table[static_cast<int64_t>(v) * p.d + o] = maybe_bf16(sum + maybe_bf16(p.enc_b2[o], bf), bf);
+    }
+    if (addr_table) {   // float32 whatever the products' precision: the reference takes these outside autocast
+        const float root = sqrtf(static_cast<float>(p.d));
+        const float* code = p.byte_codes + static_cast<int64_t>(v) * p.d;
+        for (int n = tid; n < p.N; n += kTableThreads) {
+            const float* a = p.cell_addresses + static_cast<int64_t>(n) * p.d;
+            float sum = 0.0f;
+            for (int i = 0; i < p.d; ++i) sum += code[i] * a[i];
+            addr_table[static_cast<int64_t>(v) * p.N + n] = sum * root;
+        }
+    }
+}
+
+// One thread per row: the position before each step and the byte before each position.
+__global__ void k_pro_positions(HsnwPrologue p, int64_t* positions, int32_t* previous) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= p.B) return;
+    const int64_t base = static_cast<int64_t>(b) * p.T;
+    int last = -1;
+    int32_t before = p.prev_tokens ? static_cast<int32_t>(p.prev_tokens[b]) : p.bos;
+    const int64_t start = p.pos0[b];
+    for (int t = 0; t < p.T; ++t) {
+        const bool cut = p.reset[base + t] != 0;
+        if (cut) last = t;
+        positions[base + t] = last >= 0 ? t - last : start + t;
+        previous[base + t] = cut ? p.bos : before;
+        before = static_cast<int32_t>(p.tokens[base + t]);
+    }
+}
+
+// One block per (row, position): the gathers and the scalars of every cell.
+__global__ void k_pro_rows(HsnwPrologue p, const float* z_table, const float* addr_table, const int64_t* positions,
+                           const int32_t* previous) {
+    const int64_t rt = blockIdx.x;
+    const int b = static_cast<int>(rt / p.T);
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const int token = static_cast<int>(p.tokens[rt]);
+    const int ctx_id = static_cast<int>(p.ctx_ids[rt]);
+    block_copy_f32(p.z + rt * p.d, z_table + static_cast<int64_t>(token) * p.d, p.d);
+    block_copy_f32(p.ctx + rt * p.dc, p.ctx_emb + static_cast<int64_t>(ctx_id) * p.dc, p.dc);
+    int64_t pos = positions[rt];
+    if (p.position_mode == 1) pos = pos < static_cast<int64_t>(p.unroll) - 1 ? pos : static_cast<int64_t>(p.unroll) - 1;
+    else if (p.position_mode == 2) pos = pos % static_cast<int64_t>(p.unroll);
+    const float f_ctx = static_cast<float>(ctx_id) / p.n_context;
+    const float f_pos = static_cast<float>(pos) / p.unroll;
+    const float* util = p.ema_utility + (p.ema_per_row ? static_cast<int64_t>(b) * p.N : 0);
+    const float* chosen = p.ema_selected + (p.ema_per_row ? static_cast<int64_t>(b) * p.N : 0);
+    const float* cur = addr_table ? addr_table + static_cast<int64_t>(token) * p.N : nullptr;
+    const float* prev = addr_table ? addr_table + static_cast<int64_t>(previous[rt]) * p.N : nullptr;
+    float* out = p.scalars + rt * p.N * p.S;
+    const uint32_t s_magic = magic_of(p.S);
+    for (int e = tid; e < p.N * p.S; e += nt) {   // consecutive threads write consecutive floats
+        const int n = div_magic(e, s_magic), s = e - n * p.S;
+        float value;
+        switch (s) {
+            case 0: value = p.budget_frac; break;
+            case 1: value = p.round_frac; break;
+            case 2: value = f_ctx; break;
+            case 3: value = util[n]; break;
+            case 4: value = chosen[n]; break;
+            case 5: value = f_pos; break;
+            case 6: value = 1.0f; break;
+            case 7: value = cur[n]; break;
+            default: value = prev[n]; break;
+        }
+        out[e] = value;
+    }
+}
+
+size_t table_floats(const HsnwPrologue& p) {
+    return static_cast<size_t>(p.V) * p.d + (p.S == 9 ? static_cast<size_t>(p.V) * p.N : 0);
+}
+size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+}  // namespace
+
+extern "C" int64_t hsnw_prologue_scratch_bytes(const HsnwPrologue* p) {
+    if (!p || p->B < 1 || p->T < 1 || p->V < 1) return 0;
+    return static_cast<int64_t>(align256(sizeof(float) * table_floats(*p)) + align256(sizeof(int64_t) * p->B * p->T)
+                                + align256(sizeof(int32_t) * static_cast<size_t>(p->B) * p->T));
+}
+
+extern "C" int hsnw_window_prologue(const HsnwPrologue* p, void* stream_) {
+    if (int rc = hsnw_require_prepared()) return rc;
+    if (!p) return hsnw_fail(HSNW_E_ARG, "window_prologue: null argument");
+    if (p->B < 1 || p->T < 1 || p->V < 2 || p->d < 1 || p->H < 1 || p->dc < 1 || p->N < 1)
+        return hsnw_fail(HSNW_E_ARG, "window_prologue: sizes must be positive");
+    if (p->S != 7 && p->S != 9)
+        return hsnw_fail(HSNW_E_UNSUPPORTED, "window_prologue: 7 scalars, or 9 with the address features of one byte");
+    if (!p->byte_emb || !p->enc_w1 || !p->enc_b1 || !p->enc_w2 || !p->enc_b2 || !p->ctx_emb || !p->ema_utility
+        || !p->ema_selected || !p->tokens || !p->ctx_ids || !p->reset || !p->pos0 || !p->z || !p->ctx || !p->scalars)
+        return hsnw_fail(HSNW_E_ARG, "window_prologue: a required pointer is null");
+    if (p->S == 9 && (!p->byte_codes || !p->cell_addresses))
+        return hsnw_fail(HSNW_E_ARG, "window_prologue: the address features need byte_codes and cell_addresses");
+    if (p->unroll <= 0.0f || p->n_context <= 0.0f || p->bos < 0 || p->bos >= p->V)
+        return hsnw_fail(HSNW_E_ARG, "window_prologue: unroll and n_context must be positive, bos a byte value");
+    if (!p->scratch || p->scratch_bytes < hsnw_prologue_scratch_bytes(p) || (reinterpret_cast<uintptr_t>(p->scratch) & 255))
+        return hsnw_fail(HSNW_E_ARG, "window_prologue: scratch too small or not 256-byte aligned");
+    const size_t shared = sizeof(float) * (static_cast<size_t>(p->d) + p->H);
+    if (shared > 48 * 1024) return hsnw_fail(HSNW_E_UNSUPPORTED, "window_prologue: d + H beyond 12288");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    unsigned char* base = static_cast<unsigned char*>(p->scratch);
+    float* z_table = reinterpret_cast<float*>(base);
+    float* addr_table = p->S == 9 ? z_table + static_cast<size_t>(p->V) * p->d : nullptr;
+    size_t off = align256(sizeof(float) * table_floats(*p));
+    int64_t* positions = p->positions ? p->positions : reinterpret_cast<int64_t*>(base + off);
+    off += align256(sizeof(int64_t) * p->B * p->T);
+    int32_t* previous = reinterpret_cast<int32_t*>(base + off);
+    hsnw_profile_mark(HSNW_K_PROLOGUE, stream);
+    k_pro_tables<<<p->V, kTableThreads, shared, stream>>>(*p, z_table, addr_table);
+    k_pro_positions<<<(p->B + 63) / 64, 64, 0, stream>>>(*p, positions, previous);
+    k_pro_rows<<<static_cast<unsigned>(static_cast<int64_t>(p->B) * p->T), 256, 0, stream>>>(*p, z_table, addr_table, positions, previous);
+    return hsnw_check_launch("window_prologue");
+}

@@ -19,7 +19,8 @@ from torch import Tensor
 
 from . import _lib
 
-__all__ = ["WindowModel", "window_forward", "window_backward", "stream_step", "front_projection", "prepare"]
+__all__ = ["WindowModel", "WindowPrologue", "window_forward", "window_backward", "window_prologue", "stream_step",
+           "front_projection", "prepare"]  # fmt: skip
 
 _WEIGHT_KEYS = (
     "s_w1 s_b1 s_w2 s_b2 p_w1 p_b1 p_w2 p_b2 score_w score_b v_w wout_w gate_w gate_b norm_w cand_w "
@@ -563,6 +564,99 @@ def window_backward(
         info["path"] = lib.hsnw_last_path().decode()
         info["_scratch"] = scratch
     return dc, db, (A, R)
+
+
+_PROLOGUE_KEYS = ("byte_emb enc_w1 enc_b1 enc_w2 enc_b2 ctx_emb byte_codes cell_addresses ema_utility ema_selected").split()
+
+
+@dataclass
+class WindowPrologue:
+    """The tables and numbers ``HSN._window_prologue`` reads (``python/hsn/model/hsn.py:1707-1860``), on
+    the device: the byte embedding, the encoder ``E`` (``fc1``/``fc2`` in ``nn.Linear`` layout), the
+    context embedding, the scorer's fixed byte codes and cell addresses (``model.key_address``), its two
+    running averages, and ``budget``, ``round / r_max``, ``n_context``, ``unroll`` and the position
+    rule (``python/hsn/model/router.py:727-765``)."""
+
+    struct: _lib.HsnwPrologue
+    tensors: dict[str, Tensor]
+    device: torch.device
+
+    @staticmethod
+    def build(tables: Mapping[str, Any], *, device: torch.device | str = "cuda", prod: str = "fp32",
+              budget_frac: float = 1.0, round_frac: float = 0.0, n_context: float = 16.0, unroll: float = 256.0,
+              position: str = "document", bos: int = 1) -> "WindowPrologue":  # fmt: skip
+        device = torch.device(device)
+        if device.type != "cuda":
+            raise RuntimeError("the window kernels run on a CUDA device only (no CPU path)")
+        if device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        if position not in ("document", "clamp", "wrap") or prod not in ("fp32", "bf16"):
+            raise ValueError("position must be document | clamp | wrap (model.scorer_position) and prod fp32 | bf16")
+        t = {k: torch.as_tensor(tables[k]).detach().to(device=device, dtype=torch.float32).contiguous()
+             for k in _PROLOGUE_KEYS if tables.get(k) is not None}  # fmt: skip
+        for key in ("byte_emb", "enc_w1", "enc_b1", "enc_w2", "enc_b2", "ctx_emb", "ema_utility", "ema_selected"):
+            if key not in t:
+                raise KeyError(f"prologue tables missing: {key}")
+        V, d = (int(n) for n in t["byte_emb"].shape)
+        H = int(t["enc_w1"].shape[0])
+        addressed = "byte_codes" in t and "cell_addresses" in t
+        N = int(t["ema_utility"].shape[-1])
+        if tuple(t["enc_w1"].shape) != (H, d) or tuple(t["enc_w2"].shape) != (d, H) or (addressed and tuple(t["cell_addresses"].shape) != (N, d)):
+            raise ValueError("prologue tables have inconsistent shapes")
+        st = _lib.HsnwPrologue()
+        st.V, st.d, st.H, st.dc, st.N, st.S = V, d, H, int(t["ctx_emb"].shape[1]), N, 9 if addressed else 7
+        st.prod_bf16 = int(prod == "bf16")
+        st.position_mode = ("document", "clamp", "wrap").index(position)
+        st.ema_per_row = int(t["ema_utility"].ndim == 2)
+        st.bos = int(bos)
+        st.budget_frac, st.round_frac, st.n_context, st.unroll = float(budget_frac), float(round_frac), float(n_context), float(unroll)
+        for key, value in t.items():
+            setattr(st, key, value.data_ptr())
+        prepare(device)
+        return WindowPrologue(struct=st, tensors=t, device=device)
+
+
+def window_prologue(pro: WindowPrologue, tokens: Tensor, ctx_ids: Tensor, reset: Tensor, pos0: Tensor,
+                    prev_tokens: Tensor | None = None, *, out: dict[str, Tensor] | None = None) -> dict[str, Tensor]:  # fmt: skip
+    """``hsnw_window_prologue``: ``tokens``, ``ctx_ids`` ``[B, T]`` int64, ``reset [B, T]`` bool, ``pos0
+    [B]`` int64 (the carried state's ``pos``) and optionally the byte before the window ``prev_tokens
+    [B]`` to ``z [B,T,d]``, ``ctx [B,T,dc]``, ``scalars [B,T,N,S]`` and ``positions [B,T]``: the inputs
+    of :func:`window_forward`. ``out`` reuses an earlier result's buffers."""
+    dev = pro.device
+    B, T = (int(n) for n in tokens.shape)
+    i64, f32 = torch.int64, torch.float32
+    st = pro.struct
+    io = _lib.HsnwPrologue.from_buffer_copy(st)
+    io.B, io.T = B, T
+    tokens = _check("tokens", tokens, (B, T), i64, dev)
+    ctx_ids = _check("ctx_ids", ctx_ids, (B, T), i64, dev)
+    reset_u8 = _check("reset", reset, (B, T), torch.bool, dev).view(torch.uint8)
+    pos0 = _check("pos0", pos0, (B,), i64, dev)
+    if st.ema_per_row and int(pro.tensors["ema_utility"].shape[0]) != B:
+        raise ValueError("the running averages are per row and do not have this window's rows")
+    io.tokens, io.ctx_ids, io.reset, io.pos0 = tokens.data_ptr(), ctx_ids.data_ptr(), reset_u8.data_ptr(), pos0.data_ptr()
+    if prev_tokens is not None:
+        prev_tokens = _check("prev_tokens", prev_tokens, (B,), i64, dev)
+        io.prev_tokens = prev_tokens.data_ptr()
+    o = out if out is not None else {}
+
+    def buf(name: str, shape: tuple[int, ...], dtype: torch.dtype) -> Tensor:
+        have = o.get(name)
+        if have is None or tuple(have.shape) != shape or have.dtype != dtype or have.device != dev:
+            o[name] = have = torch.empty(shape, dtype=dtype, device=dev)
+        return have
+
+    io.z = buf("z", (B, T, st.d), f32).data_ptr()
+    io.ctx = buf("ctx", (B, T, st.dc), f32).data_ptr()
+    io.scalars = buf("scalars", (B, T, st.N, st.S), f32).data_ptr()
+    io.positions = buf("positions", (B, T), i64).data_ptr()
+    lib = _lib.library()
+    need = int(lib.hsnw_prologue_scratch_bytes(ctypes.byref(io)))
+    scratch = buf("_scratch", (need,), torch.uint8)
+    io.scratch, io.scratch_bytes = scratch.data_ptr(), need
+    with torch.cuda.device(dev):
+        _lib.check(lib.hsnw_window_prologue(ctypes.byref(io), _stream(dev)))
+    return o
 
 
 def front_projection(model: WindowModel, z: Tensor, ctx: Tensor) -> Tensor:

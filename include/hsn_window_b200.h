@@ -286,6 +286,48 @@ int hsnw_window_backward_static(const HsnwModel* model, const HsnwBackward* io, 
 int hsnw_front_projection(const HsnwModel* model, const float* z, const float* ctx, int64_t rows,
                           float* out, void* stream);
 
+/* ---- the window's prologue -----------------------------------------------------------------------
+ * From a window's token and context ids to what hsnw_window_forward reads per position: replaces the
+ * inference side of HSN._window_prologue (python/hsn/model/hsn.py:1707-1860) for model.key_address
+ * with one address byte (S = 9) or without it (S = 7), no reader, no word addresses:
+ * z = E(byte_emb(x)) (python/hsn/model/encoder.py:74-128), ctx = ctx_emb(id), positions
+ * (hsn.py:347-355) and Scorer.window_scalars (python/hsn/model/router.py:597-765). Weights are in
+ * torch's nn.Linear layout [out, in]; with prod_bf16 the encoder's two linears round their operands
+ * and outputs to bfloat16 (what bf16 autocast does), the address features stay float32. All pointers
+ * are device addresses. A caller that uploads only ids (B T of each) thus never moves the
+ * [B,T,N,S] scalars across the bus. */
+typedef struct HsnwPrologue {
+    int32_t B, T, V, d, H, dc, N, S;   /* V byte values, H the encoder's hidden width */
+    int32_t prod_bf16;
+    int32_t position_mode;             /* 0: the position as it is, 1: clamped to unroll - 1, 2: modulo unroll */
+    int32_t ema_per_row;               /* 0: ema_* are [N], 1: [B,N] */
+    int32_t bos;                       /* the byte that stands for "no previous byte" */
+    float budget_frac, round_frac, n_context, unroll;
+    const float* byte_emb;             /* [V,d] */
+    const float* enc_w1;               /* [H,d] */
+    const float* enc_b1;               /* [H] */
+    const float* enc_w2;               /* [d,H] */
+    const float* enc_b2;               /* [d] */
+    const float* ctx_emb;              /* [context ids, dc] */
+    const float* byte_codes;           /* [V,d]  (S = 9) */
+    const float* cell_addresses;       /* [N,d]  (S = 9) */
+    const float* ema_utility;
+    const float* ema_selected;
+    const int64_t* tokens;             /* [B,T] */
+    const int64_t* ctx_ids;            /* [B,T] */
+    const uint8_t* reset;              /* [B,T] */
+    const int64_t* pos0;               /* [B] the session position the window starts at */
+    const int64_t* prev_tokens;        /* optional [B]: the byte before the window (null: none, reads as bos) */
+    float* z;                          /* [B,T,d] out */
+    float* ctx;                        /* [B,T,dc] out */
+    float* scalars;                    /* [B,T,N,S] out */
+    int64_t* positions;                /* optional [B,T] out */
+    void* scratch;                     /* hsnw_prologue_scratch_bytes() bytes, 256-byte aligned */
+    int64_t scratch_bytes;
+} HsnwPrologue;
+int64_t hsnw_prologue_scratch_bytes(const HsnwPrologue* prologue);
+int hsnw_window_prologue(const HsnwPrologue* prologue, void* stream);
+
 /* ---- launch timing, for measurement runs --------------------------------------------------------
  * No counterpart in the reference (it times whole steps on the host, scripts/bench_window.py:60-110).
  * Between hsnw_profile_begin and hsnw_profile_end every kernel launch of the window entry points
@@ -294,7 +336,7 @@ int hsnw_front_projection(const HsnwModel* model, const float* z, const float* c
  * before the next launch) and the number of launches. One profile at a time, one host thread, one
  * stream. hsnw_profile_kind_name(k): "init" "pre" "front" "row" "unit" "update" "head" "mid"
  * "tail_head" (the batch-synchronous phases) "rows_fwd" "rows_bwd" (the per-row cluster kernels: one
- * launch a window). */
+ * launch a window) "prologue" (hsnw_window_prologue's three launches as one). */
 int hsnw_profile_begin(void);
 int hsnw_profile_kinds(void);
 const char* hsnw_profile_kind_name(int kind);

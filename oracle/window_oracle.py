@@ -820,3 +820,78 @@ def sweep_tail(s: SweepSizes, buf: dict, t: int, *, cell_norm: bool) -> None:
         if buf["reset"][b, t]:
             A[...] = 0
             buf["R"][b] = 0
+
+
+# --------------------------------------------------------------------------------------------------
+# The window's prologue: what the sweep reads per position, from the token and context ids
+# --------------------------------------------------------------------------------------------------
+
+BOS = 1  # the byte that stands for "no previous byte" (python/hsn/data/synthetic.py:117)
+
+
+def window_positions(pos: np.ndarray, reset: np.ndarray) -> np.ndarray:
+    """``_window_positions`` (``python/hsn/model/hsn.py:347-355``): the session position before each
+    step, int64 ``[B, T]``: ``t - s`` after the row's last reset ``s <= t``, ``pos + t`` without one."""
+    B, T = reset.shape
+    steps = np.arange(T, dtype=np.int64)
+    last = np.maximum.accumulate(np.where(reset.astype(bool), steps, -1), axis=1)
+    return np.where(last >= 0, steps - last, pos[:, None] + steps)
+
+
+def window_prologue(P: dict, tokens, ctx_ids, reset, pos0, prev_tokens=None, *, bf16: bool = False):
+    """The part of ``HSN._window_prologue`` (``python/hsn/model/hsn.py:1707-1860``) that the forward
+    sweep reads, with ``model.key_address`` on, one address byte, no reader, no word addresses:
+
+    * ``z = E(byte_emb(x))`` ``[B, T, d]`` (``:1741-1742``; ``MLP2``, ``python/hsn/model/encoder.py:74``),
+    * ``context = ctx_emb(ctx)`` ``[B, T, dc]`` (``:1744``),
+    * ``positions`` (``:1772``), the previous byte of each position, BOS at resets (``:1787-1789``),
+    * ``scalars [B, T, N, 9]`` = ``Scorer.window_scalars`` (``python/hsn/model/router.py:597-640``):
+      budget, round, context id / n_context, the two running averages, position / unroll, one
+      (``_scalars``, ``:727-765``), then ``a_cur, a_prev = sqrt(d) <byte_codes[x], cell_addresses[n]>``
+      for the current and the previous byte in float32 (``address_features``, ``:653-725``).
+
+    ``P``: ``byte_emb [V, d]``, ``enc_w1 [H, d]``, ``enc_b1``, ``enc_w2 [d, H]``, ``enc_b2``, ``ctx_emb
+    [n_context, dc]``, ``byte_codes [V, d]``, ``cell_addresses [N, d]``, ``ema_utility``, ``ema_selected``
+    (``[N]`` or ``[B, N]``) and the numbers ``budget_frac, round_frac, n_context, unroll, position``
+    (``model.scorer_position``: ``"document" | "clamp" | "wrap"``). ``bf16``: the encoder's two linears as under bf16 autocast.
+    Returns ``dict(z, ctx, scalars, positions, previous)``."""
+    tokens = np.asarray(tokens)
+    B, T = tokens.shape
+    f32 = np.float32
+    emb = P["byte_emb"][tokens]
+    act = (lambda v: bf16_round(gelu(v))) if bf16 else gelu
+    z = _lin(act(_lin(emb, P["enc_w1"], P["enc_b1"], bf16)), P["enc_w2"], P["enc_b2"], bf16)
+    context = P["ctx_emb"][np.asarray(ctx_ids)]
+    reset = np.asarray(reset).astype(bool)
+    positions = window_positions(np.asarray(pos0, dtype=np.int64), reset)
+    first = np.full(B, BOS, dtype=tokens.dtype) if prev_tokens is None else np.asarray(prev_tokens, dtype=tokens.dtype)
+    previous = np.where(reset, BOS, np.concatenate([first[:, None], tokens[:, :-1]], axis=1))
+    N, d = P["cell_addresses"].shape
+    dtype = z.dtype if z.dtype == np.float64 else f32
+    pos = positions
+    if P["position"] == "clamp":
+        pos = np.minimum(pos, int(P["unroll"]) - 1)
+    elif P["position"] == "wrap":
+        pos = np.remainder(pos, int(P["unroll"]))
+
+    def per_cell(x):  # [N] or [B, N] -> [B, T, N]
+        x = np.asarray(x, dtype=dtype)
+        x = np.broadcast_to(x, (B, N)) if x.ndim == 1 else x
+        return np.broadcast_to(x[:, None, :], (B, T, N))
+
+    def per_step(x):  # [B, T] -> [B, T, N]
+        return np.broadcast_to(np.asarray(x, dtype=dtype)[:, :, None], (B, T, N))
+
+    ones = np.ones((B, T, N), dtype=dtype)
+    parts = [
+        ones * dtype(P["budget_frac"]), ones * dtype(P["round_frac"]),
+        per_step(np.asarray(ctx_ids).astype(dtype) / dtype(P["n_context"])),
+        per_cell(P["ema_utility"]), per_cell(P["ema_selected"]),
+        per_step(pos.astype(dtype) / dtype(P["unroll"])), ones,
+    ]  # fmt: skip
+    addresses = P["cell_addresses"].astype(f32).T  # the two products run in float32, outside autocast
+    root = f32(np.sqrt(f32(d)))
+    for ids in (tokens, previous):
+        parts.append(((P["byte_codes"].astype(f32)[ids] @ addresses) * root).astype(dtype))
+    scalars = np.stack(parts, axis=-1)
+    return dict(z=z, ctx=context, scalars=scalars, positions=positions, previous=previous)

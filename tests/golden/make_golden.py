@@ -25,6 +25,8 @@ inputs and outputs of every function on the window path as ``.npz`` files:
                         ``train.precision=bf16`` (``python/hsn/config.py:1113``) turns on through
                         ``python/hsn/train/amp.py:30-39``: every linear's operands and output in bfloat16,
                         state and norms in float32. Pins the oracle's ``bf16=True`` mode.
+* ``prologue_*.npz``    ``HSN._window_prologue`` (``python/hsn/model/hsn.py:1707``): token and context ids in, ``z``,
+                        the context embeddings and the scorer's scalars out, with the tables it reads.
 * ``chain_*.npz``       two chained windows against the unsplit window of twice the length: the
                         carried state forward, the state cotangent ``(A, R)`` backward.
 
@@ -489,6 +491,52 @@ def make_windows_bf16(root: Path) -> None:
         print(name, "ok")
 
 
+def make_prologue(root: Path) -> None:
+    """``HSN._window_prologue`` on seeded token and context ids: the weights and buffers it reads and
+    what the sweep takes from it (``z``, the context embeddings, the scorer's scalars), for a fresh
+    stream, for a carried position with carried previous bytes and non-zero running averages, and under
+    bf16 autocast."""
+    import torch
+    from hsn.model.state import CellGraphState
+
+    shape = dict(B=3, T=10, N=12, d=16, K=3, H=24, M=3, D=2)
+    for name, precision, carried in (("fresh_f32", "fp32", False), ("carried_f32", "fp32", True), ("fresh_bf16", "bf16", False)):
+        cfg = _cfg(root, **shape, fd="[summary,eps,router]", precision=precision)
+        model = _model(cfg, torch.float32, 0.3)
+        tokens, ctx, reset = _inputs(cfg, shape["B"], shape["T"], 0.2, seed=7)
+        state = model.init_state(shape["B"])
+        prev = None
+        if carried:
+            g = torch.Generator().manual_seed(11)
+            reset[:, 0] = False
+            state = CellGraphState._make(h=state.h, q=state.q, age=state.age,
+                                         pos=torch.randint(0, 500, (shape["B"],), generator=g))  # fmt: skip
+            prev = torch.randint(0, cfg.model.vocab_size, (shape["B"],), generator=g)
+            with torch.no_grad():
+                model.scorer.ema_utility.copy_(torch.rand(shape["N"], generator=g))
+                model.scorer.ema_selected.copy_(torch.rand(shape["N"], generator=g))
+        ctxm = torch.autocast("cpu", dtype=torch.bfloat16) if precision == "bf16" else torch.autocast("cpu", enabled=False)
+        with torch.no_grad(), ctxm:
+            pro = model._window_prologue(tokens, ctx, state, reset, "topk", reset_first=True, prev_tokens=prev, steps=False)
+        sc = model.scorer
+        out = dict(
+            tokens=_np(tokens), ctx_ids=_np(ctx), reset=_np(reset), pos0=_np(state.pos),
+            byte_emb=_np(model.byte_emb.weight if hasattr(model.byte_emb, "weight") else model.byte_emb.emb.weight),
+            enc_w1=_np(model.encoder.fc1.weight), enc_b1=_np(model.encoder.fc1.bias),
+            enc_w2=_np(model.encoder.fc2.weight), enc_b2=_np(model.encoder.fc2.bias),
+            ctx_emb=_np(model.ctx_emb.weight if hasattr(model.ctx_emb, "weight") else model.ctx_emb.emb.weight),
+            byte_codes=_np(sc.byte_codes), cell_addresses=_np(sc.cell_addresses),
+            ema_utility=_np(sc.ema.utility), ema_selected=_np(sc.ema.selected),
+            numbers=np.array([float(cfg.model.budget), 0.0 / sc.r_max, float(sc.n_context), float(sc.unroll)], dtype=np.float64),
+            position=np.array(str(sc.position)),
+            z=_np(pro.z), context=_np(pro.context), scalars=_np(pro.scalars),
+        )  # fmt: skip
+        if prev is not None:
+            out["prev_tokens"] = _np(prev)
+        np.savez_compressed(HERE / f"prologue_{name}.npz", **out)
+        print("prologue", name, "ok")
+
+
 def make_chain(root: Path) -> None:
     """Two chained windows of T positions against one window of 2T: the forward carry is the
     final state; the backward carry is the unsplit sweep's (A, R) at position T (what the second
@@ -619,7 +667,8 @@ def main() -> None:
     torch.set_num_threads(1)
     steps = {
         "select": make_select, "update": make_update, "recurrence": make_recurrence,
-        "windows": make_windows, "bf16": make_windows_bf16, "chain": make_chain, "sweep": make_sweep,
+        "windows": make_windows, "bf16": make_windows_bf16, "prologue": make_prologue, "chain": make_chain,
+        "sweep": make_sweep,
     }  # fmt: skip
     for key, fn in steps.items():
         if not args.only or key in args.only.split(","):

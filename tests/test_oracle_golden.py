@@ -324,3 +324,30 @@ def test_sweep_glue_steps_equal_the_reference(name: str) -> None:
         buf["dv_r"], buf["dv_f"] = z[f"tail{t}_dv_r"], z[f"tail{t}_dv_f"]
         O.sweep_tail(s, buf, t, cell_norm=bool(z["cell_norm"]))
         check(f"tail{t}")
+
+
+def _prologue_tables(z) -> dict:
+    budget, round_frac, n_context, unroll = (float(v) for v in z["numbers"])
+    P = {k: z[k] for k in ("byte_emb", "enc_w1", "enc_b1", "enc_w2", "enc_b2", "ctx_emb", "byte_codes",
+                           "cell_addresses", "ema_utility", "ema_selected")}  # fmt: skip
+    P.update(budget_frac=budget, round_frac=round_frac, n_context=n_context, unroll=unroll, position=str(z["position"]))
+    return P
+
+
+@pytest.mark.parametrize("name", ["fresh_f32", "carried_f32", "fresh_bf16"])
+def test_window_prologue_equals_the_reference(name: str) -> None:
+    """Token and context ids to what the sweep reads (z, context embeddings, scorer scalars) against
+    ``HSN._window_prologue`` on the CPU: a fresh stream, a carried position with carried previous
+    bytes and non-zero running averages, and the encoder under bf16 autocast."""
+    z = load_golden(f"prologue_{name}")
+    prev = z["prev_tokens"] if "prev_tokens" in z.files else None
+    bf = name.endswith("bf16")
+    got = O.window_prologue(_prologue_tables(z), z["tokens"], z["ctx_ids"], z["reset"], z["pos0"], prev, bf16=bf)
+    tol = 2e-2 if bf else 1e-5
+    scale = float(np.abs(z["z"]).max())
+    np.testing.assert_allclose(got["z"], z["z"], rtol=tol, atol=tol * scale)
+    assert np.array_equal(got["ctx"], z["context"])
+    np.testing.assert_allclose(got["scalars"], z["scalars"], rtol=1e-5, atol=1e-5)
+    assert got["scalars"].shape[-1] == 9
+    if name == "carried_f32":
+        assert float(np.abs(got["scalars"][..., 3]).max()) > 0 and int(got["positions"].max()) > 100
