@@ -2,11 +2,11 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config c2|c3|c1]
 
-A *step* is one TBPTT window for the rank's rows: the forward sweep (tape + record) and the
-state-gradient reverse sweep with synthetic cotangents, on seeded synthetic inputs of the
-benchmark configuration's shapes (uniform random bytes stand in for the reference's data set; the
-window reads them as encoder outputs ``z``, context embeddings and scorer scalars). One JSON line
-is printed by rank 0. ``--impl reference`` times the CPU restatement of the reference's window
+A *step* is one TBPTT window (configuration 3: a chain of four) for the rank's rows, from the
+window's token and context ids: the prologue (ids to encoder outputs ``z``, context embeddings and
+scorer scalars), the forward sweep (tape + record) and the state-gradient reverse sweep with
+synthetic cotangents. Uniform random bytes stand in for the reference's data set. One JSON line is
+printed by rank 0. ``--impl reference`` times the CPU restatement of the reference's window
 (``oracle/``) on the host cores instead, on a bounded sample of the same workload.
 """
 
@@ -35,9 +35,12 @@ CONFIGS = {
     # name: B (per GPU), T, N, d, K, H, M, D, S, p_reset, windows
     "c1": dict(B=2, T=8, N=16, d=32, K=2, H=32, M=2, D=2, S=9, p=0.1, prod="fp32"),
     "c2": dict(B=32, T=256, N=256, d=64, K=8, H=512, M=8, D=4, S=9, p=1 / 1024, prod="bf16"),
-    "c3": dict(B=64, T=512, N=512, d=64, K=8, H=512, M=8, D=4, S=9, p=1 / 1024, prod="bf16"),
-    # the resident contract (no state tape; the state lives in HBM between calls): one GPU's share at 8 GPUs
-    "c4": dict(B=32, T=1024, N=4096, d=128, K=16, H=1024, M=8, D=4, S=9, p=1 / 1024, prod="bf16", resident=True),
+    # four chained windows: the state carried forward, its cotangent (A, R) carried back across every boundary
+    "c3": dict(B=64, T=512, N=512, d=64, K=8, H=512, M=8, D=4, S=9, p=1 / 1024, prod="bf16", windows=4),
+    # the resident contract (no state tape; the state lives in HBM between calls). B is the GLOBAL batch:
+    # `--gpus N` gives every rank 256 / N rows (strong scaling); on one GPU without --rows, one eighth of it
+    "c4": dict(B=256, T=1024, N=4096, d=128, K=16, H=1024, M=8, D=4, S=9, p=1 / 1024, prod="bf16", resident=True,
+               global_batch=True),
     "c5": dict(B=512, T=32, N=1024, d=64, K=8, H=512, M=8, D=4, S=9, p=1 / 4096, prod="bf16", resident=True,
                forward_only=True),
     # the same streams token by token: one hsnw_stream_step, then hsnw_stream_continue per position
@@ -47,8 +50,8 @@ CONFIGS = {
 WORKLOADS = {
     "c1": "tiny gradcheck-shape window B2 T8 N16 d32 K2 H32",
     "c2": "reference-shape window fwd+bwd: B32 T256 N256 d64 K8 H512 M8 D4, bf16 products, fp32 state, resets p=1/1024",
-    "c3": "one window of the split-window chain: B64 T512 N512 d64 K8 H512, bf16 products",
-    "c4": "scaled sparse routing, one GPU's 32 rows of B256: T1024 N4096 d128 K16 H1024, resident state, fwd+bwd",
+    "c3": "split-window chain: B64, 4 chained windows of T512 (state carried forward, its cotangent back), N512 d64 K8 H512, bf16 products",
+    "c4": "scaled sparse routing, global B256 sharded over the ranks: T1024 N4096 d128 K16 H1024, resident state, fwd+bwd, gradient all-reduce",
     "c5s": "streaming token by token, one GPU's 512 streams of 4096: N1024 d64 K8 H512, one call per position (32 calls a step), derived values carried",
     "c5": "streaming, one GPU's 512 streams of 4096: N1024 d64 K8 H512, forward only on a resident state, 32 steps a call, each call continuing the last",
 }
@@ -95,32 +98,62 @@ def kernel_bytes_per_row_position(c: dict) -> dict[str, int]:
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of each kernel of the c2
 # workload, from the ncu captures summarised in profiles/rows_kernels_c2.md (the per-row cluster
 # kernels) and profiles/phases_kernels_c2_dram.md (the phase kernels).
+NCU_TRAFFIC_SOURCE = "ncu capture of bench.py --steps 1 --warmup 3 (profiles/rows_kernels_c2.md)"
 NCU_TRAFFIC_PER_LAUNCH: dict[str, dict[str, float]] = {
     "c2": {"rows_fwd": 852.4e6, "rows_bwd": 293.3e6, "front": 2.798e6, "row": 1.375e6, "unit": 3.419e6, "update": 0.526e6, "mid": 2.254e6, "tail_head": 1.703e6},
 }
 
 
-def synthetic(c: dict, rank: int, rows: int):
-    """Seeded inputs of the configuration's shapes; every row's data depends on its global row
-    index only, so the result does not depend on the number of GPUs."""
+def synthetic_model(c: dict):
+    """Seeded N(0, 0.02) weights of the configuration's shapes, and the tables the window's prologue
+    reads (byte and context embeddings and the encoder at the same scale, the scorer's fixed byte codes
+    and cell addresses N(0, 1) / sqrt(d) as the reference draws them, running averages at zero)."""
     from hsn_b200.window import synthetic_weights
 
     W = synthetic_weights(np.random.default_rng(0), N=c["N"], d=c["d"], K=c["K"], H=c["H"], M=c["M"],
                           D=c["D"], S=c["S"], age_max=2**31 - 1)  # fmt: skip
-    T, N, d, K, S = c["T"], c["N"], c["d"], c["K"], c["S"]
-    parts = []
+    rng = np.random.default_rng(5)
+    N, d, H = c["N"], c["d"], c["H"]
+    f = lambda *shape: (rng.standard_normal(shape) * 0.02).astype(np.float32)  # noqa: E731
+    tables = dict(
+        byte_emb=f(256, d), enc_w1=f(H, d), enc_b1=np.zeros(H, np.float32), enc_w2=f(d, H), enc_b2=np.zeros(d, np.float32),
+        ctx_emb=f(16, d), byte_codes=(rng.standard_normal((256, d)) / np.sqrt(d)).astype(np.float32),
+        cell_addresses=(rng.standard_normal((N, d)) / np.sqrt(d)).astype(np.float32),
+        ema_utility=np.zeros(N, np.float32), ema_selected=np.zeros(N, np.float32),
+        budget_frac=1.0, round_frac=0.0, n_context=16.0, unroll=float(c["T"]), position="document",
+    )  # fmt: skip
+    return W, tables
+
+
+def synthetic_ids(c: dict, first_row: int, rows: int):
+    """Seeded ids and cotangents for ``rows`` rows from global row ``first_row`` on, for every window of
+    the configuration's chain: uniform bytes, uniform context ids, Bernoulli resets (column 0 of the
+    first window starts every stream), N(0, 0.1) cotangents. A row's data depends on its global index
+    only, so results do not depend on the number of GPUs. Returns a list over windows of
+    ``(tokens, ctx_ids, reset, d_q_pre, d_q_post, d_h_sel)``."""
+    T, d, K, W = c["T"], c["d"], c["K"], c.get("windows", 1)
+    per_row = []
     for r in range(rows):
-        rng = np.random.default_rng(1000 + rank * rows + r)
-        tokens = rng.integers(0, 256, T)  # uniform bytes; the window sees them through z
-        z = rng.standard_normal((T, d)).astype(np.float32) * 0.5 + (tokens[:, None] / 255.0 - 0.5).astype(np.float32)
-        ctx = (rng.standard_normal((T, d)) * 0.02).astype(np.float32)
-        scalars = rng.random((T, N, S)).astype(np.float32)
-        reset = rng.random(T) < c["p"]
+        rng = np.random.default_rng(1000 + first_row + r)
+        tokens = rng.integers(0, 256, W * T)
+        ctx_ids = rng.integers(0, 16, W * T)
+        reset = rng.random(W * T) < c["p"]
         reset[0] = True
-        cot = [rng.standard_normal(s).astype(np.float32) * 0.1 for s in ((T, d), (T, d), (T, K, d))]
-        parts.append((z, ctx, scalars, reset, *cot))
-    stack = [np.stack([p[i] for p in parts]) for i in range(7)]
-    return W, stack
+        cot = [(rng.standard_normal(shape) * 0.1).astype(np.float32) for shape in ((W * T, d), (W * T, d), (W * T, K, d))]
+        per_row.append((tokens, ctx_ids, reset, *cot))
+    whole = [np.stack([p[i] for p in per_row]) for i in range(6)]
+    return [tuple(np.ascontiguousarray(a[:, w * T : (w + 1) * T]) for a in whole) for w in range(W)]
+
+
+def synthetic(c: dict, rank: int, rows: int):
+    """The weights and ONE window's direct inputs ``[z, ctx, scalars, reset, d_q_pre, d_q_post, d_h_sel]``
+    (numpy): the ids of :func:`synthetic_ids` through the oracle's prologue. The CPU legs use it."""
+    from oracle import window_oracle as O
+
+    W, tables = synthetic_model(c)
+    tokens, ctx_ids, reset, pre, post, sel = synthetic_ids(dict(c, windows=1), rank * rows, rows)[0]
+    pro = O.window_prologue(tables, tokens, ctx_ids, reset, np.zeros(rows, np.int64))
+    return W, [pro["z"], pro["ctx"].astype(np.float32), pro["scalars"].astype(np.float32), reset, pre, post, sel]
 
 
 def sample_clocks(stop: threading.Event, out: list) -> None:
@@ -161,18 +194,19 @@ def clocks_summary(lines: list, device: int) -> dict:
             "samples": len(sm)}  # fmt: skip
 
 
-def cpu_window(W, data, rows: int, positions: int):
-    """The oracle's window forward + state-gradient backward on ``rows`` x ``positions`` of the
-    workload; returns seconds."""
+def cpu_window(W, tables, ids, rows: int, positions: int):
+    """The oracle's prologue, window forward and state-gradient backward on ``rows`` x ``positions``
+    of the workload (the first window's first positions); returns seconds."""
     from oracle import window_oracle as O
 
     W = O.WindowWeights(**vars(W))   # the same weights in the oracle's container
-    z, ctx, scalars, reset, pre, post, sel = (a[:rows, :positions] for a in data)
-    N, d = W.pad_src.shape[0], z.shape[-1]
+    tokens, ctx_ids, reset, pre, post, sel = (a[:rows, :positions] for a in ids)
+    N, d = W.pad_src.shape[0], pre.shape[-1]
     state = (np.zeros((rows, N, d), np.float32), np.zeros((rows, d), np.float32), np.zeros((rows, N), np.int64),
              np.zeros(rows, np.int64))  # fmt: skip
     t0 = time.perf_counter()
-    tape = O.window_forward(W, z, ctx, scalars, reset, *state)
+    pro = O.window_prologue(tables, tokens, ctx_ids, reset, state[3])
+    tape = O.window_forward(W, pro["z"], pro["ctx"].astype(np.float32), pro["scalars"].astype(np.float32), reset, *state)
     valid = tape["sel_valid"]
     rec = {k: tape["rec_" + k] for k in ("y", "hidden", "gate_pre", "m", "rms")}
     O.state_gradient_backward(
@@ -182,22 +216,25 @@ def cpu_window(W, data, rows: int, positions: int):
     return time.perf_counter() - t0
 
 
-def cpu_baseline(c: dict, W, data, budget_s: float = 12.0) -> dict:
-    rows = min(c["B"], data[0].shape[0])
-    probe = min(2, c["T"])
-    dt = cpu_window(W, data, rows, probe)
-    positions = int(max(probe, min(c["T"], budget_s / max(dt / probe, 1e-6))))
-    seconds = cpu_window(W, data, rows, positions)
+def blas_threads() -> int:
     try:
         from threadpoolctl import threadpool_info
 
-        threads = max([p.get("num_threads", 1) for p in threadpool_info()] or [1])
+        return int(max([p.get("num_threads", 1) for p in threadpool_info()] or [1]))
     except Exception:
-        threads = os.cpu_count() or 1
+        return os.cpu_count() or 1
+
+
+def cpu_baseline(c: dict, W, tables, ids, budget_s: float = 12.0) -> dict:
+    rows = min(c["B"], ids[0].shape[0])
+    probe = min(2, c["T"])
+    dt = cpu_window(W, tables, ids, rows, probe)
+    positions = int(max(probe, min(c["T"], budget_s / max(dt / probe, 1e-6))))
+    seconds = cpu_window(W, tables, ids, rows, positions)
     return {
         "value": rows * positions / seconds,
         "unit": "row-positions/s",
-        "cores": int(threads),
+        "cores": blas_threads(),
         "kind": "port",
         "sample": f"{rows} rows x {positions} positions of the workload, fp32, numpy oracle (BLAS threads = cores), {seconds:.1f} s",
     }
@@ -205,32 +242,27 @@ def cpu_baseline(c: dict, W, data, budget_s: float = 12.0) -> dict:
 
 def run_reference(args, c: dict, name: str) -> None:
     """The CPU arm: the reference's window as restated in oracle/ (the reference is Python and is
-    not present on the benchmark machine; the restatement is pinned to it by tests/golden)."""
+    not present on the benchmark machine; the restatement is pinned to it by tests/golden). A step is
+    a sample of the workload: 8 rows x 32 positions (256 row-positions), prologue + forward + backward."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    positions = min(c["T"], 4)
-    if c.get("resident"):   # only the sampled positions are drawn: the full inputs are too large for the host
-        c = dict(c, T=positions)
-    W, data = synthetic(c, 0, min(c["B"], 8))
-    rows = data[0].shape[0]
+    rows, positions = min(c["B"], 8), min(c["T"], 32)
+    c = dict(c, T=positions, windows=1)   # only the sampled positions are drawn
+    W, tables = synthetic_model(c)
+    ids = synthetic_ids(c, 0, rows)[0]
     for _ in range(args.warmup):
-        cpu_window(W, data, rows, positions)
-    times = [cpu_window(W, data, rows, positions) for _ in range(args.steps)]
+        cpu_window(W, tables, ids, rows, positions)
+    times = [cpu_window(W, tables, ids, rows, positions) for _ in range(args.steps)]
     sec = float(np.mean(times))
     value = rows * positions / sec
-    try:
-        from threadpoolctl import threadpool_info
-
-        threads = max([p.get("num_threads", 1) for p in threadpool_info()] or [1])
-    except Exception:
-        threads = os.cpu_count() or 1
+    threads = blas_threads()
     line = {
         "impl": "reference", "metric": "window row-positions/s fwd+bwd", "value": value, "unit": "row-positions/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOADS[name], "sample": f"{rows} rows x {positions} positions per step"},
-        "cpu_baseline": {"value": value, "unit": "row-positions/s", "cores": int(threads), "kind": "port",
+        "cpu_baseline": {"value": value, "unit": "row-positions/s", "cores": threads, "kind": "port",
                          "sample": f"{rows} rows x {positions} positions per step, numpy oracle"},
         "e2e": {"value": value, "unit": "row-positions/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -238,22 +270,80 @@ def run_reference(args, c: dict, name: str) -> None:
     print(json.dumps(line), flush=True)
 
 
-def run_resident(args, c: dict, name: str) -> None:
-    """The configurations of the resident contract (one GPU): inputs drawn on the device from a
-    seed (their host copies would not fit a pinned buffer), the state updated in place from call
-    to call, CUDA events around ``steps`` calls. Not the headline line: no end-to-end leg."""
+def dist_setup():
+    """(world, rank, local rank, device) with the NCCL process group up when launched by torchrun."""
     import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the window path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
+    return world, rank, local, dev
+
+
+def n_parameters(c: dict) -> int:
+    """The parameter count of the configuration's window model: the size of the training-gradient
+    exchange after a window's backward (the gradients themselves come from the batched replay, which is
+    outside this path; the benchmark exchanges a buffer of their size)."""
+    d, H, M, S = c["d"], c["H"], c["M"], c["S"]
+    shared = (3 * d) * H + H + H * d + d
+    predictor = d * H + H + H * d + d
+    scorer = M * (3 * d + 1 + S) + M
+    cell = 2 * d * d + 4 * d * d + d + 4 * d + d
+    units = M * (4 * d * H + H + H * d + d)
+    return shared + predictor + scorer + cell + units
+
+
+def timed_steps(step, steps: int, barrier):
+    """``steps`` calls of ``step`` between two barriers, an event after every one: total milliseconds
+    and the per-step times."""
+    import torch
+
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    barrier()
+    marks[0].record()
+    for i in range(steps):
+        step(i)
+        marks[i + 1].record()
+    barrier()
+    each = [marks[i].elapsed_time(marks[i + 1]) for i in range(steps)]
+    return marks[0].elapsed_time(marks[steps]), each
+
+
+def spread(each: list) -> dict:
+    return {"median": float(np.median(each)), "p95": float(np.percentile(each, 95)), "min": float(np.min(each)),
+            "max": float(np.max(each)), "n": len(each)}  # fmt: skip
+
+
+def run_resident(args, c: dict, name: str) -> None:
+    """The configurations of the resident contract: inputs drawn on the device from a seed (their host
+    copies would not fit a pinned buffer), the state updated in place from call to call. Configuration
+    4 shards its GLOBAL batch over the ranks (strong scaling) and exchanges a gradient-sized buffer
+    after every backward; the streaming configurations run one GPU's share. No end-to-end leg."""
+    import torch
+    import torch.distributed as dist
 
     from hsn_b200.window import WindowModel, launch_profile, synthetic_weights, window_backward, window_forward
 
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the window path has no CPU fallback")
-    dev = torch.device("cuda", 0)
-    B, T, N, d, K, S = c["B"], c["T"], c["N"], c["d"], c["K"], c["S"]
+    world, rank, local, dev = dist_setup()
+    T, N, d, K, S = c["T"], c["N"], c["d"], c["K"], c["S"]
+    global_rows = c["B"]
+    if c.get("global_batch"):
+        B = args.rows if args.rows > 0 else (global_rows // world if world > 1 else global_rows // 8)
+        global_rows = B * world
+    else:
+        B = args.rows if args.rows > 0 else c["B"]
+        global_rows = B * world
     W = synthetic_weights(np.random.default_rng(0), N=N, d=d, K=K, H=c["H"], M=c["M"], D=c["D"], S=S,
                           age_max=2**31 - 1)  # fmt: skip
     model = WindowModel.from_weights(W, device=dev, prod=c["prod"], row_clusters=not args.phases)
-    gen = torch.Generator(device=dev).manual_seed(1)
+    gen = torch.Generator(device=dev).manual_seed(1 + rank)
     z = torch.randn((B, T, d), device=dev, generator=gen) * 0.5
     ctx = torch.randn((B, T, model.dims["dc"]), device=dev, generator=gen) * 0.02
     scalars = torch.rand((B, T, N, S), device=dev, generator=gen)
@@ -262,13 +352,16 @@ def run_resident(args, c: dict, name: str) -> None:
     state = (torch.zeros((B, N, d), device=dev), torch.zeros((B, d), device=dev),
              torch.zeros((B, N), dtype=torch.int64, device=dev), torch.zeros(B, dtype=torch.int64, device=dev))  # fmt: skip
     forward_only = bool(c.get("forward_only"))
+    grads = torch.zeros(n_parameters(c), device=dev)
     out: dict = {}
-    bw_scratch = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    info: dict = {}
+    bw_scratch = None
 
     per_position = [tuple(a[:, t].contiguous() for a in (z, ctx, scalars, reset)) for t in range(T)] if c.get("stream") else []
     calls = [0]
 
-    def step():
+    def step(_i=0):
+        nonlocal bw_scratch
         if per_position:
             from hsn_b200.window import stream_step
 
@@ -283,117 +376,148 @@ def run_resident(args, c: dict, name: str) -> None:
         if forward_only:
             return
         rec = {k: tape["rec_" + k] for k in ("y", "hidden", "gate_pre", "m", "rms")}
+        if bw_scratch is None:
+            from hsn_b200 import _lib
+
+            need = int(_lib.library().hsnw_backward_scratch_bytes(model.struct, B, T))
+            bw_scratch = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
         window_backward(model, tape["rec_c"], tape["rec_b"], tape["rec_h_old"], tape["sel_cell_idx"],
                         tape["sel_unit_idx"], tape["sel_valid"], reset, cots[0], cots[1], cots[2], rec,
-                        scratch=bw_scratch)  # fmt: skip
+                        scratch=bw_scratch, info=info)  # fmt: skip
+        if world > 1:  # the training-gradient exchange after each window backward
+            dist.all_reduce(grads)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
 
     warmup = max(args.warmup, 3)
     for _ in range(warmup):
         step()
-    torch.cuda.synchronize()
+    barrier()
     stop, lines = threading.Event(), []
     sampler = threading.Thread(target=sample_clocks, args=(stop, lines), daemon=True)
     sampler.start()
     time.sleep(0.3)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / args.steps
+    total_ms, each = timed_steps(step, args.steps, barrier)
     stop.set()
     sampler.join(timeout=2)
     with launch_profile() as prof:
         step()
-    torch.cuda.synchronize()
-    peaks_file = ROOT / "MEASURED_PEAKS.json"
-    peaks = json.loads(peaks_file.read_text()) if peaks_file.exists() else {}
-    peak = float(peaks.get("hbm_gbs", 6650.0))
-    per = bytes_per_row_position(c)
-    achieved = per * B * T / (ms * 1e-3) / 1e9
-    total_ms = sum(prof.ms.values()) or 1.0
-    kernels = {k: {"launches_per_step": n, "us_per_launch": round(1e3 * prof.ms[k] / n, 3),
-                   "share": round(prof.ms[k] / total_ms, 4)} for k, n in prof.launches.items() if n}  # fmt: skip
-    line = {
-        "metric": "window row-positions/s " + ("fwd" if forward_only else "fwd+bwd"), "value": B * T / (ms * 1e-3),
-        "unit": "row-positions/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": ms,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 products, f32 state",
-        "data": "synthetic (drawn on the device)",
-        "config": {"workload": WORKLOADS[name], "rows_per_gpu": B, "positions": T,
-                   "kernels": "batch-synchronous phases" if args.phases else "library's choice",
-                   "l2": "state and inputs larger than L2"},
-        "e2e": None, "gpu_launches": args.steps * sum(prof.launches.values()),
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_source": "measured" if peaks else "fallback",
-                     "bytes_per_row_position": per, "kernels": kernels},
-        "clocks": clocks_summary(lines, 0),
-    }  # fmt: skip
-    print(json.dumps(line), flush=True)
+    barrier()
+    times = torch.tensor([total_ms / args.steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms = float(times.cpu()[0])
+    if rank == 0:
+        peaks_file = ROOT / "MEASURED_PEAKS.json"
+        peaks = json.loads(peaks_file.read_text()) if peaks_file.exists() else {}
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        per = bytes_per_row_position(c)
+        achieved = per * B * T / (ms * 1e-3) / 1e9   # per GPU
+        total_prof = sum(prof.ms.values()) or 1.0
+        kernels = {k: {"launches_per_step": n, "us_per_launch": round(1e3 * prof.ms[k] / n, 3),
+                       "share": round(prof.ms[k] / total_prof, 4)} for k, n in prof.launches.items() if n}  # fmt: skip
+        paths = {"forward": out.get("path"), "backward": info.get("path")}
+        line = {
+            "metric": "window row-positions/s " + ("fwd" if forward_only else "fwd+bwd"),
+            "value": global_rows * T / (ms * 1e-3), "unit": "row-positions/s", "n_gpus": world, "steps": args.steps,
+            "warmup": warmup, "ms_per_step": ms, "step_ms": spread(each), "higher_is_better": True,
+            "scaling": "strong" if c.get("global_batch") and world > 1 and args.rows <= 0 else "weak", "vs_baseline": None,
+            "dtype": "bf16 products, f32 state", "data": "synthetic (drawn on the device)",
+            "config": {"workload": WORKLOADS[name], "rows_per_gpu": B, "global_rows": global_rows, "positions": T,
+                       "kernels": paths, "l2": "state and inputs larger than L2",
+                       "allreduce_floats_per_step": int(grads.numel()) if world > 1 and not forward_only else 0},
+            "e2e": None, "gpu_launches": args.steps * sum(prof.launches.values()),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": "measured" if peaks else "fallback", "per": "GPU",
+                         "bytes_per_row_position": per, "kernels": kernels},
+            "clocks": clocks_summary(lines, local),
+        }  # fmt: skip
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
 
-def main() -> None:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--phases", action="store_true",
-                    help="run the batch-synchronous phase kernels instead of the per-row cluster kernels")
-    ap.add_argument("--positions", type=int, default=0,
-                    help="shorten the window to this many positions (profiler captures only; not a benchmark number)")
-    args = ap.parse_args()
-    c = dict(CONFIGS[args.config])
-    if args.positions > 0:
-        c["T"] = args.positions
-    if args.impl == "reference":
-        run_reference(args, c, args.config)
-        return
-    if c.get("resident"):
-        run_resident(args, c, args.config)
-        return
+class TapedJob:
+    """One rank's windows of a taped configuration on the device: the prologue, the forward sweep of
+    every window of the chain (state carried forward) and the reverse sweeps in reverse order (the state's
+    cotangent carried back), from ids that already are on the device."""
 
+    def __init__(self, c: dict, dev, rows: int, phases: bool) -> None:
+        import torch
+
+        from hsn_b200.window import WindowModel, WindowPrologue
+
+        self.c, self.dev, self.rows = c, dev, rows
+        W, tables = synthetic_model(c)
+        numbers = {k: tables.pop(k) for k in ("budget_frac", "round_frac", "n_context", "unroll", "position")}
+        self.model = WindowModel.from_weights(W, device=dev, prod=c["prod"], row_clusters=not phases)
+        self.pro = WindowPrologue.build(tables, device=dev, prod=c["prod"], **numbers)
+        self.windows = c.get("windows", 1)
+        N, d = c["N"], c["d"]
+        self.start = (torch.zeros((rows, N, d), device=dev), torch.zeros((rows, d), device=dev),
+                      torch.zeros((rows, N), dtype=torch.int64, device=dev), torch.zeros(rows, dtype=torch.int64, device=dev))  # fmt: skip
+        self.pro_out = [dict() for _ in range(self.windows)]
+        self.fw_out = [dict() for _ in range(self.windows)]
+        self.bw_scratch = None
+        self.paths: dict = {}
+
+    def step(self, ids):
+        """``ids``: per window ``(tokens, ctx_ids, reset, d_q_pre, d_q_post, d_h_sel)`` on the device.
+        Returns the tapes, ``[(dc, db)]`` per window and the start state's cotangent."""
+        import torch
+
+        from hsn_b200 import _lib
+        from hsn_b200.window import window_backward, window_forward, window_prologue
+
+        state, prev, tapes = self.start, None, []
+        for w in range(self.windows):
+            tokens, ctx_ids, reset = ids[w][:3]
+            p = window_prologue(self.pro, tokens, ctx_ids, reset, state[3], prev, out=self.pro_out[w])
+            tape = window_forward(self.model, p["z"], p["ctx"], p["scalars"], reset, state, out=self.fw_out[w])
+            tapes.append(tape)
+            state = (tape["h"], tape["q"], tape["age"], tape["pos"])
+            prev = tokens[:, -1].contiguous()
+        if self.bw_scratch is None:
+            need = int(_lib.library().hsnw_backward_scratch_bytes(self.model.struct, self.rows, self.c["T"]))
+            self.bw_scratch = torch.empty(max(need, 256), dtype=torch.uint8, device=self.dev)
+        carry, grads, info = None, [None] * self.windows, {}
+        for w in reversed(range(self.windows)):
+            tape = tapes[w]
+            rec = {k: tape["rec_" + k] for k in ("y", "hidden", "gate_pre", "m", "rms")}
+            dc, db, carry = window_backward(
+                self.model, tape["rec_c"], tape["rec_b"], tape["rec_h_old"], tape["sel_cell_idx"], tape["sel_unit_idx"],
+                tape["sel_valid"], ids[w][2], ids[w][3], ids[w][4], ids[w][5], rec, initial=carry,
+                scratch=self.bw_scratch, info=info,
+            )  # fmt: skip
+            grads[w] = (dc, db)
+        self.paths = {"forward": tapes[0]["path"], "backward": info.get("path")}
+        return tapes, grads, carry
+
+
+def run_taped(args, c: dict, name: str) -> None:
     import torch
     import torch.distributed as dist
 
-    from hsn_b200.window import WindowModel, launch_profile, window_backward, window_forward
+    from hsn_b200.window import launch_profile
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the window path has no CPU fallback")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    world, rank, local, dev = dist_setup()
     warmup = max(args.warmup, 3)
-    B, T, N, d, K = c["B"], c["T"], c["N"], c["d"], c["K"]
-    W, host = synthetic(c, rank, B)
-    model = WindowModel.from_weights(W, device=dev, prod=c["prod"], row_clusters=not args.phases)
-    pinned = [torch.from_numpy(a).pin_memory() for a in host]
-    z, ctx, scalars, reset, pre, post, sel = (t.to(dev, non_blocking=True) for t in pinned)
-    state = (torch.zeros((B, N, d), device=dev), torch.zeros((B, d), device=dev),
-             torch.zeros((B, N), dtype=torch.int64, device=dev), torch.zeros(B, dtype=torch.int64, device=dev))  # fmt: skip
-    n_params = sum(int(np.prod(getattr(W, k).shape)) for k in
-                   "s_w1 s_b1 s_w2 s_b2 p_w1 p_b1 p_w2 p_b2 score_w score_b v_w wout_w gate_w gate_b norm_w cand_w w1 b1 w2 b2".split())  # fmt: skip
-    grads = torch.zeros(n_params, device=dev)
-    out: dict = {}
-    bw_scratch = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
+    B = args.rows if args.rows > 0 else c["B"]
+    T, N, d, K, nW = c["T"], c["N"], c["d"], c["K"], c.get("windows", 1)
+    job = TapedJob(c, dev, B, args.phases)
+    host = synthetic_ids(c, rank * B, B)
+    pinned = [[torch.from_numpy(a).pin_memory() for a in window] for window in host]
+    ids = [[t.to(dev, non_blocking=True) for t in window] for window in pinned]
+    grads = torch.zeros(n_parameters(c), device=dev)
 
-    def step(zz, cc, ss, rr, cots):
-        tape = window_forward(model, zz, cc, ss, rr, state, out=out)
-        rec = {k: tape["rec_" + k] for k in ("y", "hidden", "gate_pre", "m", "rms")}
-        dc, db, carry = window_backward(
-            model, tape["rec_c"], tape["rec_b"], tape["rec_h_old"], tape["sel_cell_idx"], tape["sel_unit_idx"],
-            tape["sel_valid"], rr, cots[0], cots[1], cots[2], rec, scratch=bw_scratch,
-        )  # fmt: skip
-        if world > 1:  # the training-gradient exchange after each window backward
+    def step(on_device):
+        out = job.step(on_device)
+        if world > 1:  # the training-gradient exchange after the window's backward
             dist.all_reduce(grads)
-        return tape, dc, db, carry
+        return out
 
     def barrier():
         if world > 1:
@@ -401,28 +525,21 @@ def main() -> None:
         torch.cuda.synchronize()
 
     for _ in range(warmup):
-        step(z, ctx, scalars, reset, (pre, post, sel))
+        step(ids)
     barrier()
     stop, lines = threading.Event(), []
     sampler = threading.Thread(target=sample_clocks, args=(stop, lines), daemon=True)
     sampler.start()
     time.sleep(0.3)
-    # device-resident steps
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        step(z, ctx, scalars, reset, (pre, post, sel))
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1) / args.steps
-    # end to end: host buffers in, results back to the host, every step
-    host_out = {k: torch.empty(s, dtype=t).pin_memory() for k, (s, t) in
-                {"dc": ((B, T, K, d), torch.float32), "db": ((B, T, K, d), torch.float32),
-                 "h": ((B, N, d), torch.float32), "q": ((B, d), torch.float32)}.items()}  # fmt: skip
+    # device-resident steps: the ids are on the device
+    total_ms, each = timed_steps(lambda i: step(ids), args.steps, barrier)
+    ms = total_ms / args.steps
+    # end to end: ids and cotangents from pinned host memory in, gradients and the final state back, every step
+    out_shapes = {"dc": (nW, B, T, K, d), "db": (nW, B, T, K, d), "h": (B, N, d), "q": (B, d)}
+    host_out = {k: torch.empty(shape, dtype=torch.float32).pin_memory() for k, shape in out_shapes.items()}
     # Two staging sets: step i + 1's inputs cross the bus on a copy stream while step i computes (what a
     # data loader does); every step's host-to-device copy and read-back is inside the timed region.
-    staged = [[torch.empty_like(t, device=dev) for t in pinned] for _ in range(2)]
+    staged = [[[torch.empty_like(t, device=dev) for t in window] for window in pinned] for _ in range(2)]
     copy_stream = torch.cuda.Stream(device=dev)
     main_stream = torch.cuda.current_stream(dev)
     landed = [torch.cuda.Event() for _ in range(2)]
@@ -432,8 +549,9 @@ def main() -> None:
         buf = i & 1
         with torch.cuda.stream(copy_stream):
             copy_stream.wait_event(consumed[buf])   # the step that last read this set is done with it
-            for dst, src in zip(staged[buf], pinned):
-                dst.copy_(src, non_blocking=True)
+            for dst_w, src_w in zip(staged[buf], pinned):
+                for dst, src in zip(dst_w, src_w):
+                    dst.copy_(src, non_blocking=True)
             landed[buf].record(copy_stream)
 
     readback = torch.cuda.Stream(device=dev)
@@ -443,97 +561,152 @@ def main() -> None:
         buf = i & 1
         upload(i + 1)
         main_stream.wait_event(landed[buf])
-        st = staged[buf]
-        tape, dc, db, _ = step(st[0], st[1], st[2], st[3], st[4:7])
+        tapes, grad_list, _ = step(staged[buf])
         consumed[buf].record(main_stream)
         # the final state lives in the tape's static buffer, which the next step rewrites: read it back
         # in order; the gradients are this step's own tensors and cross the bus beside the next step
-        host_out["h"].copy_(tape["h"], non_blocking=True)
-        host_out["q"].copy_(tape["q"], non_blocking=True)
+        host_out["h"].copy_(tapes[-1]["h"], non_blocking=True)
+        host_out["q"].copy_(tapes[-1]["q"], non_blocking=True)
         computed.record(main_stream)
         with torch.cuda.stream(readback):
             readback.wait_event(computed)
-            host_out["dc"].copy_(dc, non_blocking=True)
-            host_out["db"].copy_(db, non_blocking=True)
-        dc.record_stream(readback)
-        db.record_stream(readback)
+            for w, (dc, db) in enumerate(grad_list):
+                host_out["dc"][w].copy_(dc, non_blocking=True)
+                host_out["db"][w].copy_(db, non_blocking=True)
+        for dc, db in grad_list:
+            dc.record_stream(readback)
+            db.record_stream(readback)
 
     for ev in consumed:
         ev.record(main_stream)
     upload(0)
     e2e_step(0)   # untimed: fills the pipeline
-    barrier()
-    e0.record()
-    for i in range(1, args.steps + 1):
-        e2e_step(i)
-    main_stream.wait_stream(readback)   # the last step's read-back ends before the closing event
-    e1.record()
-    barrier()
-    ms_e2e = e0.elapsed_time(e1) / args.steps
+    e2e_steps = max(3, min(args.steps, 20))
+
+    def e2e_run(i):
+        e2e_step(i + 1)
+        if i + 1 == e2e_steps:
+            main_stream.wait_stream(readback)   # the last step's read-back ends before the closing event
+
+    total_e2e, _ = timed_steps(e2e_run, e2e_steps, barrier)
+    ms_e2e = total_e2e / e2e_steps
     stop.set()
     sampler.join(timeout=2)
     # one more step, untimed, with an event before every launch: the per-kernel times and counts
     with launch_profile() as prof:
-        step(z, ctx, scalars, reset, (pre, post, sel))
+        step(ids)
     barrier()
-    times = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
+    # the same global batch spread over the ranks (strong scaling), when there are several
+    strong = None
+    if world > 1 and args.rows <= 0 and c["B"] % world == 0 and c["B"] // world >= 1:
+        rows = c["B"] // world
+        small = TapedJob(c, dev, rows, args.phases)
+        small_ids = [[torch.from_numpy(a).to(dev) for a in window] for window in synthetic_ids(c, rank * rows, rows)]
+
+        def small_step(_i):
+            small.step(small_ids)
+            dist.all_reduce(grads)
+
+        for _ in range(3):
+            small_step(0)
+        n = max(3, min(args.steps, 20))
+        total_small, _ = timed_steps(small_step, n, barrier)
+        strong = [total_small / n, rows]
+    times = torch.tensor([ms, ms_e2e, strong[0] if strong else 0.0], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms, ms_e2e = (float(x) for x in times.cpu())
+    ms, ms_e2e, ms_strong = (float(x) for x in times.cpu())
     if rank == 0:
         peaks_file = ROOT / "MEASURED_PEAKS.json"
         peaks = json.loads(peaks_file.read_text()) if peaks_file.exists() else {}
         peak = float(peaks.get("hbm_gbs", 6650.0))
-        row_pos = B * T
+        row_pos = B * T * nW
         per = bytes_per_row_position(c)
         achieved = per * row_pos / (ms * 1e-3) / 1e9
         # the step's kernels by measured time (the profiled step); the dominant one's roofline
         launches_per_step = sum(prof.launches.values())
-        total_ms = sum(prof.ms.values()) or 1.0
+        total_prof = sum(prof.ms.values()) or 1.0
         split = kernel_bytes_per_row_position(c)
-        traffic = NCU_TRAFFIC_PER_LAUNCH.get(args.config, {}) if args.positions == 0 else {}
+        traffic = NCU_TRAFFIC_PER_LAUNCH.get(name, {}) if args.positions == 0 and args.rows <= 0 else {}
         kernels = {}
-        for name, n in prof.launches.items():
+        for kind, n in prof.launches.items():
             if n:
-                us = 1e3 * prof.ms[name] / n
-                alg = split.get(name, 0) * B
-                kernels[name] = {"launches_per_step": n, "us_per_launch": round(us, 3),
-                                 "share": round(prof.ms[name] / total_ms, 4), "algorithmic_bytes_per_launch": alg,
+                us = 1e3 * prof.ms[kind] / n
+                alg = split.get(kind, 0) * B
+                kernels[kind] = {"launches_per_step": n, "us_per_launch": round(us, 3),
+                                 "share": round(prof.ms[kind] / total_prof, 4), "algorithmic_bytes_per_launch": alg,
                                  "achieved_gbs": round(alg / (us * 1e-6) / 1e9, 3) if us > 0 else None,
-                                 "traffic": traffic.get(name)}  # fmt: skip
+                                 "traffic": traffic.get(kind)}  # fmt: skip
         top = max(kernels, key=lambda k: kernels[k]["share"])
         roofline = {
             "bound": "hbm", "kernel": top, "achieved": kernels[top]["achieved_gbs"], "peak": peak, "unit": "GB/s",
             "frac": kernels[top]["achieved_gbs"] / peak, "traffic": kernels[top]["traffic"],
+            "traffic_source": NCU_TRAFFIC_SOURCE if kernels[top]["traffic"] else None,
             "peak_source": "measured" if peaks else "fallback",
             "how": "algorithmic bytes of the kernel's launch / its mean event-to-event time in a profiled step",
             "step": {"achieved": achieved, "frac": achieved / peak, "bytes_per_row_position": per},
             "kernels": kernels,
         }  # fmt: skip
-        h2d = sum(t.numel() * t.element_size() for t in pinned)
+        h2d = sum(t.numel() * t.element_size() for window in pinned for t in window)
         d2h = sum(t.numel() * t.element_size() for t in host_out.values())
         line = {
             "metric": "window row-positions/s fwd+bwd", "value": world * row_pos / (ms * 1e-3),
             "unit": "row-positions/s", "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "step_ms": spread(each), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16 products, f32 state" if c["prod"] == "bf16" else "f32", "data": "synthetic",
-            "config": {"workload": WORKLOADS[args.config] + (f" [shortened to {T} positions]" if args.positions else ""),
-                       "rows_per_gpu": B, "positions": T,
-                       "kernels": "batch-synchronous phases" if args.phases else "per-row clusters",
-                       "l2": "inputs larger than L2 (tape 0.5 GiB + scalars 75 MB per step)",
-                       "allreduce_floats_per_step": n_params if world > 1 else 0},
+            "config": {"workload": WORKLOADS[name] + (f" [shortened to {T} positions]" if args.positions else ""),
+                       "rows_per_gpu": B, "positions": T, "windows": nW, "kernels": job.paths,
+                       "step": "prologue from ids + forward sweep(s) + reverse sweep(s)" + (" + gradient all-reduce" if world > 1 else ""),
+                       "l2": "tape and scalars per step far larger than L2",
+                       "allreduce_floats_per_step": int(grads.numel()) if world > 1 else 0},
             "e2e": {"value": world * row_pos / (ms_e2e * 1e-3), "unit": "row-positions/s",
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "note": "the next step's inputs are uploaded on a copy stream while this step computes; the final state is read back on the compute stream, the gradients dc/db on a read-back stream beside the next step; every copy ends inside the timed region"},
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                    "note": "token and context ids, resets and the cotangents come from pinned host memory on a copy stream while the previous step computes; the final state is read back on the compute stream, the gradients dc/db on a read-back stream beside the next step; every copy ends inside the timed region"},
             "gpu_launches": args.steps * launches_per_step,
             "roofline": roofline,
             "clocks": clocks_summary(lines, local),
         }  # fmt: skip
+        if strong:
+            line["strong"] = {"value": c["B"] * T * nW / (ms_strong * 1e-3), "unit": "row-positions/s", "ms_per_step": ms_strong,
+                              "rows_per_gpu": strong[1], "global_rows": c["B"],
+                              "note": "the same global batch spread over the ranks: a row's positions are sequential, so fewer rows per GPU do not shorten a step"}  # fmt: skip
         if not args.no_cpu_baseline and world == 1:
-            line["cpu_baseline"] = cpu_baseline(c, W, host)
+            W, tables = synthetic_model(c)
+            line["cpu_baseline"] = cpu_baseline(c, W, tables, host[0])
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--phases", action="store_true",
+                    help="run the batch-synchronous phase kernels instead of the per-row cluster kernels")
+    ap.add_argument("--positions", type=int, default=0,
+                    help="shorten the window to this many positions (profiler captures only; not a benchmark number)")
+    ap.add_argument("--rows", type=int, default=0, help="rows per GPU instead of the configuration's")
+    args = ap.parse_args()
+    c = dict(CONFIGS[args.config])
+    if args.positions > 0:
+        c["T"] = args.positions
+    if args.impl == "reference":
+        if args.steps == 100:   # the default is sized for the GPU arm
+            args.steps = 20
+        run_reference(args, c, args.config)
+    elif c.get("resident"):
+        if args.steps == 100:
+            args.steps = 10
+        run_resident(args, c, args.config)
+    else:
+        if args.steps == 100 and c.get("windows", 1) > 1:
+            args.steps = 10
+        run_taped(args, c, args.config)
 
 
 if __name__ == "__main__":
