@@ -60,14 +60,15 @@ constexpr int kMaxStages = 3;         // ring depth (2 when 3 slots do not fit b
 constexpr int kMaxK = 8;              // slots (register accumulators per slot)
 constexpr int kMaxMR = 16;            // units
 constexpr int kFrontCols = 256;       // merged front columns per block (2H / C with H = 128 C)
+constexpr int kActOperand = 2 * 16 * 16 * 8;   // bytes of a unit's activations as a bf16 operand [128 / 8][16 slots][8]
 
 struct RowsCtx {
     HsnwModel m;
     HsnwForward io;
     int C, Nc, Ks;            // blocks of a cluster, cells a block owns, slots a block owns (ceil(K / C))
     int gate_rows;            // 4d / C
-    uint32_t bank_bytes;      // one (unit, 64-column block) chunk
-    uint32_t w1_bytes;        // its W1 part
+    uint32_t bank_bytes;      // a unit's weights on the block's 128 hidden columns: three pieces, W1 (inputs 0..2d), W1 (2d..4d), W2
+    uint32_t w1_bytes;        // one W1 piece (= the ring slot); the W2 piece is half of it
     uint32_t front_bytes;     // one front chunk
     uint32_t slot_bytes;      // ring slot
     uint32_t stages;          // ring depth
@@ -141,13 +142,13 @@ __host__ __device__ inline RowsSmem rows_smem(const HsnwModel& m, int C, uint32_
     L.ulist = take(4 * (kMaxMR + 4));
     L.umask = take(4 * (kMaxMR + 4));
     // phase C's keys ([N] then [8] stale counts per warp and [K] flags) and phase E/F's inbox of the
-    // slots' changes are adjacent: phase D's two activation operands (bf16 [8][16][8] each, 4 KB) use
+    // slots' changes are adjacent: phase D's two activation operands (bf16 [16][16][8] each, 8 KB) use
     // the same bytes between them (C is over when D starts; E's stores come after the barrier that
     // ends D)
     L.cand = take(8 * N + 64);
     L.inbox_delta = take(4 * K * d);
     L.b2 = L.cand;
-    if (L.inbox_delta + up16(4 * K * d) - L.cand < 2 * 2 * 8 * 16 * 8) o = L.cand + 2 * 2 * 8 * 16 * 8;
+    if (L.inbox_delta + up16(4 * K * d) - L.cand < 2 * kActOperand) o = L.cand + 2 * kActOperand;
     L.total = o;
     return L;
 }
@@ -721,7 +722,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                     if (pre_cols > 0) bulk_g2s(in_pre, c.pre_s + (rt + 1) * H + r * kFrontCols, b_pre, &in_bar);
                     bulk_g2s(in_z, c.io.z + (rt + 1) * d, b_z, &in_bar);
                 }
-                const int n_bank = n_units * 2;
+                const int n_bank = n_units * 3;
                 const int total = n_bank + (last ? 0 : 2);
                 for (int i = 0; i < total; ++i) {
                     const uint32_t slot = ring_slot(g_issue);
@@ -729,9 +730,10 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                     const unsigned char* from;
                     uint32_t bytes;
                     if (i < n_bank) {
-                        const int j = ulist[i >> 1];
-                        from = bank + (static_cast<size_t>(j) * (H / 64) + r * 2 + (i & 1)) * c.bank_bytes;
-                        bytes = c.bank_bytes;
+                        const int ui = i / 3, piece = i - 3 * ui;
+                        const int j = ulist[ui];
+                        from = bank + (static_cast<size_t>(j) * C + r) * c.bank_bytes + piece * c.w1_bytes;
+                        bytes = piece == 2 ? c.w1_bytes / 2 : c.w1_bytes;
                     } else {
                         from = front + (static_cast<size_t>(r) * 2 + (i - n_bank)) * c.front_bytes;
                         bytes = c.front_bytes;
@@ -809,9 +811,9 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 }
             }
             // rows 8..15 of the two activation operands (their bytes belong to other phases' data)
-            for (int e = tid; e < 2 * 8 * 8; e += kConsumers) {
-                const int which = e >> 6, p = (e >> 3) & 7, k = 8 + (e & 7);
-                reinterpret_cast<uint4*>(b2 + which * (8 * 16 * 8))[p * 16 + k] = make_uint4(0u, 0u, 0u, 0u);
+            for (int e = tid; e < 2 * 16 * 8; e += kConsumers) {
+                const int which = e >> 7, p = (e >> 3) & 15, k = 8 + (e & 7);
+                reinterpret_cast<uint4*>(b2 + which * (kActOperand / 2))[p * 16 + k] = make_uint4(0u, 0u, 0u, 0u);
             }
             consumer_sync();
             RMARK(22);
@@ -841,102 +843,51 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
             fence_async_smem();   // the operand written above, before the tensor cores read it
             consumer_sync();
             RMARK(7);
-            // the units' two layers on the streamed chunks, on the tensor cores. Per chunk (unit j, 64
-            // hidden columns): D1 [64 columns, 16 slots] = W1 part x inputs^T; the epilogue adds the
-            // bias, rounds, records, applies the activation for the slots that run unit j (zero for
-            // the others) and writes the bf16 operand of the second product; D2 [d outputs, 16 slots]
-            // += W2 part x activations^T accumulates over all the position's chunks in tensor memory.
-            // The chunk's rows are 64, the instruction's M is 128: rows 64..127 of both accumulators
-            // come from the bytes after the tile and are never read. The second product's commit
-            // hands the ring slot back. Thread 0 issues; warps 0, 1, 4, 5 read the accumulators and keep
-            // their own barrier; warps 2, 3, 6, 7 meanwhile compute the gate's partial sums.
+            // The units' two layers on the streamed weights, on the tensor cores. A unit's weights on the
+            // block's 128 hidden columns arrive as three pieces, each a ring slot of its own: W1's rows for
+            // the inputs [0, 2d) and [2d, 4d) (A tiles [128 columns][2d]), then W2 ([d outputs][128
+            // columns]). D1 [128 columns, 16 slots] = W1 x inputs^T accumulates over the two pieces, and
+            // each piece's slot is handed back as soon as its products have run; the epilogue adds the
+            // bias, rounds, records, applies the activation for the slots that run the unit (zero for the
+            // others) and writes the bf16 operand of the second product; D2 [d outputs, 16 slots] += W2 x
+            // activations^T accumulates over the position's units (rows d..127 of D2 come from the bytes
+            // after the tile and are never read). Warp 0 issues (as a whole: umma.cuh). All eight warps
+            // read D1: warp w the columns 32 (w % 4) .. and the slots 4 (w / 4) .. 4 (w / 4) + 3; before
+            // the first accumulator is ready they compute the gate's partial sums.
             RMARK(30);
-            const int n_chunks = 2 * n_units;
-            const bool epi = (warp & 2) == 0;                 // warps 0, 1, 4, 5
-            const int hc = lane + 32 * (warp & 1);            // the epilogue thread's column of the chunk (TMEM lane)
+            const int hc = lane + 32 * (warp & 3);            // the thread's hidden column of the block (TMEM lane)
             const int sh = warp >> 2;                         // its half of the slots: 4 sh .. 4 sh + 3
             const uint32_t idesc = umma_idesc_bf16(128, 16);
-            constexpr int steps1 = (4 * d) >> 4;            // K = 16 products of a chunk's first layer
+            constexpr int steps_piece = (2 * d) >> 4;       // K = 16 products of one W1 piece
             const uint32_t g0 = g_use;
-            float bias_next = (epi && n_chunks > 0) ? c.m.b1[ulist[0] * H + r * 128 + hc] : 0.0f;   // a chunk ahead
-            // a chunk's first product: D1 (tensor memory columns 128 b .. 128 b + 15, b = chunk parity);
-            // issued by warp 0 as a whole (umma.cuh: one elected lane, warp-uniform control flow)
+            float bias_next = n_units > 0 ? c.m.b1[ulist[0] * H + r * 128 + hc] : 0.0f;   // a unit ahead
+            // a unit's first layer: D1 (tensor memory columns 128 b .. 128 b + 15, b = unit parity)
             auto first_product = [&](int i) {
-                const uint32_t slot = ring_slot(g0 + i);
-                ring_wait(&full[slot], ring_round(g0 + i) & 1u, c.status, &failed_s);
-                tcgen05_fence_after();
-                if (d == 64)
-                    umma_chain_sw128<steps1>(taddr + 128 * (i & 1), umma_desc_sw128(ring + slot * c.slot_bytes), (64 * 128) >> 4,
-                                             umma_desc(vop, 16), umma_kstep(16), idesc, false);
-                else
-                    umma_chain_fixed<steps1>(taddr + 128 * (i & 1), umma_desc(ring + slot * c.slot_bytes, 64), umma_desc(vop, 16), idesc,
-                                             umma_kstep(64), umma_kstep(16), false);
+#pragma unroll
+                for (int piece = 0; piece < 2; ++piece) {
+                    const uint32_t g = g0 + 3 * i + piece, slot = ring_slot(g);
+                    ring_wait(&full[slot], ring_round(g) & 1u, c.status, &failed_s);
+                    tcgen05_fence_after();
+                    const unsigned char* tile = ring + slot * c.slot_bytes;
+                    if (d == 64)   // (a piece is two 128-byte-swizzled K-blocks of 64 inputs, 128 rows each)
+                        umma_chain_sw128<steps_piece>(taddr + 128 * (i & 1), umma_desc_sw128(tile), (128 * 128) >> 4,
+                                                      umma_desc(vop + piece * steps_piece * 2 * 16 * 8, 16), umma_kstep(16), idesc,
+                                                      piece > 0);
+                    else
+                        umma_chain_fixed<steps_piece>(taddr + 128 * (i & 1), umma_desc(tile, 128),
+                                                      umma_desc(vop + piece * steps_piece * 2 * 16 * 8, 16), idesc, umma_kstep(128),
+                                                      umma_kstep(16), piece > 0);
+                    umma_commit(&empty[slot]);   // the piece is spent when these products have read it
+                }
                 umma_commit(&bar_d1[i & 1]);
             };
-            if (warp == 0 && n_chunks > 0) {
+            if (warp == 0 && n_units > 0) {
                 first_product(0);
                 RMARK(29);
             }
-            if (epi) {
-                float hid_keep[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                for (int i = 0; i < n_chunks; ++i) {
-                    const unsigned mask = static_cast<unsigned>(umask[i >> 1]);
-                    const uint32_t slot = ring_slot(g0 + i);
-                    if (warp == 0 && i + 1 < n_chunks) first_product(i + 1);   // the next chunk's first product runs under this epilogue
-                    {
-                        const float bias = bias_next;
-                        if (i + 1 < n_chunks) bias_next = c.m.b1[ulist[(i + 1) >> 1] * H + r * 128 + ((i + 1) & 1) * 64 + hc];
-                        uint16_t* b2i = b2 + (i & 1) * (8 * 16 * 8);
-                        ring_wait(&bar_d1[i & 1], ((i & 1) ? d1_count1 : d1_count0) & 1u, c.status, &failed_s);
-                        tcgen05_fence_after();
-                        if (i == 0) RMARK(25);
-                        float acc[8];
-                        tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 128 * (i & 1)), acc);
-    #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const int k = 4 * sh + q;
-                            float a = 0.0f;
-                            hid_keep[q] = 0.0f;
-                            if (mask & (1u << k)) {
-                                const float hid = bf16r((sh ? acc[4 + q] : acc[q]) + bias);
-                                hid_keep[q] = hid;
-                                a = gelu_erf(hid);
-                            }
-                            b2i[((hc >> 3) * 16 + k) * 8 + (hc & 7)] = bf16_bits(a);
-                        }
-                        fence_async_smem();
-                        tcgen05_fence_before();
-                        if (i == 0) RMARK(26);
-                    }
-                    if (i & 1) ++d1_count1;
-                    else ++d1_count0;
-                    asm volatile("bar.sync 2, 128;\n" ::: "memory");   // the four epilogue warps
-                    if (rec) {
-                        // the record of the pre-activations goes out after the barrier: a barrier waits
-                        // for the stores its threads have in flight
-                        const int colg = r * 128 + (i & 1) * 64 + hc;
-#pragma unroll
-                        for (int q = 0; q < 4; ++q)
-                            if (mask & (1u << (4 * sh + q))) c.io.rec_hidden[(rt * K + 4 * sh + q) * H + colg] = hid_keep[q];
-                    }
-                    if (warp == 0) {
-                        tcgen05_fence_after();
-                        // D2 (columns 256 .. 271) accumulates over the position's chunks
-                        if (d == 64)
-                            umma_chain_sw128<4>(taddr + 256, umma_desc_sw128(ring + slot * c.slot_bytes + c.w1_bytes), 0,
-                                                umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), umma_kstep(16), idesc, i > 0);
-                        else
-                            umma_chain_fixed<4>(taddr + 256, umma_desc(ring + slot * c.slot_bytes + c.w1_bytes, d),
-                                                umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), idesc, umma_kstep(d), umma_kstep(16), i > 0);
-                        umma_commit(&empty[slot]);
-                        if (i + 1 == n_chunks) umma_commit(&bar_d2);
-                    }
-                    if (i == 0) RMARK(27);
-                }
-            } else {
-                // the gate's partial sum over the block's input rows, by the other four warps
-                const int t2 = (warp >> 2) * 64 + (warp & 1) * 32 + lane;   // 0 .. 127
-                const int x = t2 % d, grp = t2 / d, ngrp = 128 / d;
+            {
+                // the gate's partial sum over the block's input rows (under the first unit's first layer)
+                const int x = tid % d, grp = tid / d, ngrp = kConsumers / d;
                 for (int k = grp; k < K; k += ngrp) {
                     float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
                     if (cell_of[k] >= 0) {
@@ -958,19 +909,81 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                     gacc[k * d + x] = (s0 + s1) + (s2 + s3);
                 }
             }
+            float hid_keep[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            for (int i = 0; i < n_units; ++i) {
+                const unsigned mask = static_cast<unsigned>(umask[i]);
+                // the next unit's first layer runs under this epilogue when the ring holds its two pieces beside
+                // this unit's third (three slots; with two it would wait for a slot that only this unit's
+                // second product frees)
+                if (warp == 0 && i + 1 < n_units && three) first_product(i + 1);
+                {
+                    const float bias = bias_next;
+                    if (i + 1 < n_units) bias_next = c.m.b1[ulist[i + 1] * H + r * 128 + hc];
+                    uint16_t* b2i = b2 + (i & 1) * (kActOperand / 2);
+                    ring_wait(&bar_d1[i & 1], ((i & 1) ? d1_count1 : d1_count0) & 1u, c.status, &failed_s);
+                    tcgen05_fence_after();
+                    if (i == 0) RMARK(25);
+                    float acc[8];
+                    tmem_ld8(tmem_addr(taddr, 32 * (warp & 3), 128 * (i & 1)), acc);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int k = 4 * sh + q;
+                        float a = 0.0f;
+                        hid_keep[q] = 0.0f;
+                        if (mask & (1u << k)) {
+                            const float hid = bf16r((sh ? acc[4 + q] : acc[q]) + bias);
+                            hid_keep[q] = hid;
+                            a = gelu_erf(hid);
+                        }
+                        b2i[((hc >> 3) * 16 + k) * 8 + (hc & 7)] = bf16_bits(a);
+                    }
+                    fence_async_smem();
+                    tcgen05_fence_before();
+                    if (i == 0) RMARK(26);
+                }
+                if (i & 1) ++d1_count1;
+                else ++d1_count0;
+                consumer_sync();   // every epilogue thread's activations are written
+                if (rec) {
+                    // the record of the pre-activations goes out after the barrier: a barrier waits
+                    // for the stores its threads have in flight
+                    const int colg = r * 128 + hc;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        if (mask & (1u << (4 * sh + q))) c.io.rec_hidden[(rt * K + 4 * sh + q) * H + colg] = hid_keep[q];
+                }
+                if (warp == 0) {
+                    const uint32_t g = g0 + 3 * i + 2, slot = ring_slot(g);
+                    ring_wait(&full[slot], ring_round(g) & 1u, c.status, &failed_s);
+                    tcgen05_fence_after();
+                    const unsigned char* tile = ring + slot * c.slot_bytes;
+                    // D2 (columns 256 .. 271) accumulates over the position's units
+                    if (d == 64)   // (two K-blocks of 64 hidden columns, d rows each)
+                        umma_chain_sw128<8>(taddr + 256, umma_desc_sw128(tile), (64 * 128) >> 4,
+                                            umma_desc(b2 + (i & 1) * (kActOperand / 2), 16), umma_kstep(16), idesc, i > 0);
+                    else
+                        umma_chain_fixed<8>(taddr + 256, umma_desc(tile, d), umma_desc(b2 + (i & 1) * (kActOperand / 2), 16), idesc,
+                                            umma_kstep(d), umma_kstep(16), i > 0);
+                    umma_commit(&empty[slot]);
+                    if (i + 1 == n_units) umma_commit(&bar_d2);
+                    if (i + 1 < n_units && !three) first_product(i + 1);
+                }
+                if (i == 0) RMARK(27);
+            }
+            const int n_chunks = 3 * n_units;
             consumer_sync();
             g_use += n_chunks;
             RMARK(8);
             // the block's partial of every slot's second layer from the accumulator, and the gate's
             // partial, to the slots' owners
-            if (epi && sh == 0) {
+            if (sh == 0 && 32 * warp < d) {   // the outputs x < d sit in the accumulator's lanes 0 .. d - 1
                 float acc[8];
 #pragma unroll
                 for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
                 if (n_chunks > 0) {
                     ring_wait(&bar_d2, d2_phase & 1u, c.status, &failed_s);
                     tcgen05_fence_after();
-                    tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 256), acc);
+                    tmem_ld8(tmem_addr(taddr, 32 * warp, 256), acc);
                 }
                 RMARK(28);
                 if (hc < d) {
@@ -1216,9 +1229,9 @@ static bool rows_shape(const HsnwModel& m, RowsCtx* c) {
     c->Ks = (m.K + C - 1) / C;
     c->gate_rows = 4 * m.d / C;
     c->w1_bytes = static_cast<uint32_t>(512 * m.d);
-    c->bank_bytes = static_cast<uint32_t>(640 * m.d);
+    c->bank_bytes = static_cast<uint32_t>(1280 * m.d);
     c->front_bytes = static_cast<uint32_t>(512 * m.d);
-    c->slot_bytes = c->bank_bytes;
+    c->slot_bytes = c->w1_bytes;
     return true;
 }
 

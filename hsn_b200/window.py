@@ -249,33 +249,36 @@ def _sw128(tile: Tensor) -> Tensor:
 
 def _row_images(w1: Tensor, w2: Tensor, f_w1q_t: Tensor, f_w2_t: Tensor) -> dict[str, Tensor]:
     """bf16 images for the per-row cluster kernels (``hsn_b200/csrc/window_rows.cu``,
-    ``window_rows_bwd.cu``): one chunk per unit and 64-column block of its hidden layer, and per
-    block of the cluster its 256 columns of the merged front first layer ``[d][256]`` followed by
-    the same columns' rows of the second layer ``[256][d]``. A chunk is two K-major tensor-core
-    tiles. ``d == 64``: 128-byte swizzled K-blocks of 64 (forward ``W1`` as 4 blocks ``[64 columns]
-    [64 inputs]`` then ``W2`` as ``[d outputs][64 columns]``; reverse ``W2`` as ``[64 columns][d]``
-    then the state rows of ``W1`` as ``[2d][64 columns]``). Other ``d``: the unswizzled core-matrix
-    layout ``[K/8][rows][8]`` of ``umma.cuh``."""
+    ``window_rows_bwd.cu``) and per block of the cluster its 256 columns of the merged front first
+    layer ``[d][256]`` followed by the same columns' rows of the second layer ``[256][d]``. Forward
+    (``rows_bank``): per unit and block of 128 hidden columns three K-major tensor-core tiles, ``W1``'s
+    rows of the inputs ``[0, 2d)``, of ``[2d, 4d)`` (each ``[128 columns][2d]``) and ``W2`` (``[d
+    outputs][128 columns]``). Reverse (``rows_bank_bw``): per unit and block of 64 columns ``W2`` as
+    ``[64 columns][d]`` then the state rows of ``W1`` as ``[2d][64 columns]``. ``d == 64``: 128-byte
+    swizzled K-blocks of 64. Other ``d``: the unswizzled core-matrix layout ``[K/8][rows][8]`` of
+    ``umma.cuh``."""
     M, in4, H = (int(n) for n in w1.shape)
     d = int(w2.shape[2])
     bf = torch.bfloat16
     nb = H // 64
+    C = H // 128
     if d == 64:
-        a = w1.reshape(M, in4 // 64, 64, nb, 64).permute(0, 3, 1, 4, 2).to(bf)  # [M, nb, K-block, column, input]
-        a = _sw128(a).reshape(M, nb, -1)
-        b = w2.reshape(M, nb, 64, d).permute(0, 1, 3, 2).to(bf)  # [M, nb, output, column]
-        b = _sw128(b).reshape(M, nb, -1)
+        # forward: per unit and block of 128 columns, W1 as four K-blocks [128 columns][64 inputs] (two pieces of
+        # two), then W2 as two K-blocks [d outputs][64 columns]
+        a = w1.reshape(M, in4 // 64, 64, C, 128).permute(0, 3, 1, 4, 2).to(bf)  # [M, C, K-block, column, input]
+        a = _sw128(a).reshape(M, C, -1)
+        b = w2.reshape(M, C, 2, 64, d).permute(0, 1, 2, 4, 3).to(bf)  # [M, C, K-block, output, column]
+        b = _sw128(b).reshape(M, C, -1)
         ba = _sw128(w2.reshape(M, nb, 64, d).to(bf)).reshape(M, nb, -1)  # [M, nb, column, output]
         bb = w1[:, 2 * d :, :].reshape(M, 2 * d, nb, 64).permute(0, 2, 1, 3).to(bf)  # [M, nb, state input, column]
         bb = _sw128(bb).reshape(M, nb, -1)
     else:
-        a = w1.reshape(M, in4 // 8, 8, nb, 64).permute(0, 3, 1, 4, 2).to(bf).reshape(M, nb, -1)  # [M,nb,(4d/8)*64*8]
-        b = w2.reshape(M, nb, 8, 8, d).permute(0, 1, 2, 4, 3).to(bf).reshape(M, nb, -1)  # [M,nb,8*d*8]
+        a = w1.reshape(M, in4 // 8, 8, C, 128).permute(0, 3, 1, 4, 2).to(bf).reshape(M, C, -1)  # [M,C,(4d/8)*128*8]
+        b = w2.reshape(M, C, 16, 8, d).permute(0, 1, 2, 4, 3).to(bf).reshape(M, C, -1)  # [M,C,16*d*8]
         ba = w2.reshape(M, nb, 64, d // 8, 8).permute(0, 1, 3, 2, 4).to(bf).reshape(M, nb, -1)
         bb = w1[:, 2 * d :, :].reshape(M, 2 * d, nb, 8, 8).permute(0, 2, 3, 1, 4).to(bf).reshape(M, nb, -1)
     bank = torch.cat([a, b], dim=2).contiguous()
     bank_bw = torch.cat([ba, bb], dim=2).contiguous()
-    C = H // 128
     f1 = f_w1q_t.reshape(d, C, 256).permute(1, 0, 2).to(bf).reshape(C, -1)  # [C, d*256]
     f2 = f_w2_t.reshape(C, 256, d).to(bf).reshape(C, -1)  # [C, 256*d]
     front = torch.stack([f1, f2], dim=1).contiguous()  # [C, 2, 256 d]

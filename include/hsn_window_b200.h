@@ -143,9 +143,10 @@ typedef struct HsnwModel {
     const void* umma_bw_gate;
     /* bf16 images for the per-row cluster kernel (prod_bf16, H a multiple of 128; null: not used).
      * With C = H / 128 blocks of a row's cluster:
-     * rows_bank [M][H/64] chunks, one per unit and 64-column block of its hidden layer: first
-     *   W1 as [4d/8][64][8] (element (input x, column c) at ((x/8) 64 + c) 8 + x%8), then W2 as
-     *   [8][d][8] (element (column c, output x) at ((c/8) d + x) 8 + c%8);
+     * rows_bank [M][C]: a unit's weights on a block's 128 hidden columns as three K-major tiles, W1's
+     *   rows of the inputs [0, 2d) as [2d/8][128][8] (element (input x, column c) at ((x/8) 128 + c) 8 +
+     *   x%8), the same for the inputs [2d, 4d), then W2 as [16][d][8] (element (column c, output x) at
+     *   ((c/8) d + x) 8 + c%8); with d = 64 the tiles are 128-byte-swizzled K-blocks of 64 instead;
      * rows_front [C][2] chunks: the block's 256 columns of the merged front first layer
      *   f_w1q_t as [d][256], then the same columns' rows of f_w2_t as [256][d]. */
     const void* rows_bank;
