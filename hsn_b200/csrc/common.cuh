@@ -21,6 +21,16 @@ __device__ __forceinline__ float maybe_bf16(float x, bool on) { return on ? bf16
 __device__ __forceinline__ uint16_t bf16_bits(float x) { return __bfloat16_as_ushort(__float2bfloat16_rn(x)); }
 __device__ __forceinline__ float bf16_value(uint16_t h) { return __uint_as_float(static_cast<uint32_t>(h) << 16); }
 
+// The record of the hidden pre-activations: float32, or bfloat16 when the products are bf16 (the values
+// are bfloat16 then, so nothing is lost and the record is half the bytes).
+__device__ __forceinline__ void store_hidden(void* base, int64_t at, float v, bool half) {
+    if (half) static_cast<uint16_t*>(base)[at] = bf16_bits(v);
+    else static_cast<float*>(base)[at] = v;
+}
+__device__ __forceinline__ float load_hidden(const void* base, int64_t at, bool half) {
+    return half ? bf16_value(static_cast<const uint16_t*>(base)[at]) : static_cast<const float*>(base)[at];
+}
+
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * kSqrtHalf)); }
 __device__ __forceinline__ float gelu_erf_grad(float x) {
     return 0.5f * (1.0f + erff(x * kSqrtHalf)) + x * expf(-0.5f * x * x) * kInvSqrt2Pi;

@@ -287,7 +287,7 @@ __global__ void __launch_bounds__(256) k_mid(BwdCtx c, int t) {
                 const float sum = dot4(du + pb * d, 1, wA + cc * (d + 1), 1, d);
                 const int pair = list[base + pb];
                 const int row = pair / K, k = pair - row * K;
-                const float hid = c.io.hidden[((static_cast<int64_t>(row) * T + t) * K + k) * H + c0 + cc];
+                const float hid = load_hidden(c.io.hidden, ((static_cast<int64_t>(row) * T + t) * K + k) * H + c0 + cc, c.m.prod_bf16 != 0);
                 dhid = maybe_bf16(sum * gelu_erf_grad(hid), bf);
                 inner = dhid * (hid - c.m.b1[j * H + c0 + cc]);
             }
@@ -466,7 +466,7 @@ __global__ void __launch_bounds__(256) k_mid_tc(BwdCtx c, int t) {
                 if (n < nb && col_ok) {
                     const int pair = list[base + n];
                     const int row = pair / K, k = pair - row * K;
-                    const float hid = c.io.hidden[((static_cast<int64_t>(row) * T + t) * K + k) * H + c0 + m];
+                    const float hid = load_hidden(c.io.hidden, ((static_cast<int64_t>(row) * T + t) * K + k) * H + c0 + m, true);
                     dhid = bf16r(acc[e] * gelu_erf_grad(hid));
                     inner = dhid * (hid - b1v);
                 }

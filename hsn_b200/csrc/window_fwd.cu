@@ -857,7 +857,7 @@ __global__ void __launch_bounds__(256) k_unit(FwdCtx c, int t) {
                     const float hid = maybe_bf16(acc[p] + c.m.b1[j * H + c0 + cc], bf);
                     if (c.io.rec_c) {
                         const int row = pair / K, k = pair - row * K;
-                        c.io.rec_hidden[((static_cast<int64_t>(row) * T + t) * K + k) * H + c0 + cc] = hid;
+                        store_hidden(c.io.rec_hidden, ((static_cast<int64_t>(row) * T + t) * K + k) * H + c0 + cc, hid, c.m.prod_bf16 != 0);
                     }
                     a = maybe_bf16(gelu_erf(hid), bf);
                 }
@@ -1033,7 +1033,7 @@ __global__ void __launch_bounds__(kUnitTcThreads) k_unit_tc(FwdCtx c, int t) {
                     } else {
                         if (c.io.rec_c) {
                             const int row = pair / K, k = pair - row * K;
-                            c.io.rec_hidden[((static_cast<int64_t>(row) * T + t) * K + k) * H + c0 + m] = pre;
+                            store_hidden(c.io.rec_hidden, ((static_cast<int64_t>(row) * T + t) * K + k) * H + c0 + m, pre, true);
                         }
                         a = gelu_erf(pre);
                     }

@@ -950,7 +950,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                     const int colg = r * 128 + hc;
 #pragma unroll
                     for (int q = 0; q < 4; ++q)
-                        if (mask & (1u << (4 * sh + q))) c.io.rec_hidden[(rt * K + 4 * sh + q) * H + colg] = hid_keep[q];
+                        if (mask & (1u << (4 * sh + q))) static_cast<uint16_t*>(c.io.rec_hidden)[(rt * K + 4 * sh + q) * H + colg] = bf16_bits(hid_keep[q]);
                 }
                 if (warp == 0) {
                     const uint32_t g = g0 + 3 * i + 2, slot = ring_slot(g);

@@ -87,7 +87,7 @@ __host__ __device__ inline RowsBwdSmem rows_bwd_smem(const HsnwModel& m, int C, 
     L.Rs = take(4 * d);
     for (int s = 0; s < 2; ++s) {
         L.rec[s] = take(4 * (7 * Ks * d + Ks) + 16);
-        L.hid[s] = take(4 * K * 128);
+        L.hid[s] = take(2 * K * 128);   // the recorded pre-activations of the block's columns, bfloat16
         L.dq[s] = take(4 * 2 * d);
         L.dec[s] = take(4 * (2 * K + 2 * K * D + 2 * kMaxMB + 4 + K + K * D));
     }
@@ -168,7 +168,7 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
     const unsigned char* bank = static_cast<const unsigned char*>(c.m.rows_bank_bw);
 
     auto rec_of = [&](int buf) { return reinterpret_cast<float*>(dyn + L.rec[buf]); };
-    auto hid_of = [&](int buf) { return reinterpret_cast<float*>(dyn + L.hid[buf]); };
+    auto hid_of = [&](int buf) { return reinterpret_cast<uint16_t*>(dyn + L.hid[buf]); };
     auto dq_of = [&](int buf) { return reinterpret_cast<float*>(dyn + L.dq[buf]); };
     auto dec_of = [&](int buf) { return reinterpret_cast<int*>(dyn + L.dec[buf]); };
     // a position's decision block: cell_of [K], unit_of [K], tgt [K D], ew [K D] (floats), ulist [16],
@@ -191,10 +191,11 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
                 if (k < K) cp_async16(rc + (a * Ks + kl) * d + 4 * x4, srcs[a] + (rt * K + k) * d + 4 * x4);
             }
         }
-        float* hd = hid_of(buf);
-        for (int e = me; e < K * 32; e += crew) {
-            const int k = e >> 5, c4 = e & 31;
-            cp_async16(hd + k * 128 + 4 * c4, c.io.hidden + (rt * K + k) * H + r * 128 + 4 * c4);
+        uint16_t* hd = hid_of(buf);
+        const uint16_t* recorded = static_cast<const uint16_t*>(c.io.hidden);
+        for (int e = me; e < K * 16; e += crew) {   // 128 bfloat16 a slot: sixteen 16-byte copies
+            const int k = e >> 4, c8 = e & 15;
+            cp_async16(hd + k * 128 + 8 * c8, recorded + (rt * K + k) * H + r * 128 + 8 * c8);
         }
         float* q = dq_of(buf);
         for (int e = me; e < 2 * (d / 4); e += crew) {
@@ -344,7 +345,7 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
         const int64_t rt = static_cast<int64_t>(row) * T + t;
         const int buf = t & 1;
         float* rc = rec_of(buf);
-        const float* hd = hid_of(buf);
+        const uint16_t* hd = hid_of(buf);
         const float* q = dq_of(buf);
         const int* dc_ = dec_of(buf);
         const float* ew = reinterpret_cast<const float*>(dc_) + o_ew;
@@ -465,7 +466,7 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
                         const int k = 4 * sh + q;
                         float dh = 0.0f;
                         if (mask & (1u << k)) {
-                            const float hv = hd[k * 128 + hid_col];
+                            const float hv = bf16_value(hd[k * 128 + hid_col]);
                             dh = bf16r((sh ? acc[4 + q] : acc[q]) * gelu_erf_grad(hv));
                             inner[q] += dh * (hv - bias);
                         }

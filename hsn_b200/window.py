@@ -423,7 +423,8 @@ def window_forward(
         for name in ("c", "b", "h_old", "y", "gate_pre", "m"):
             setattr(io, "rec_" + name, buf("rec_" + name, (B, T, K, d), f32).data_ptr())
         io.rec_rms = buf("rec_rms", (B, T, K), f32).data_ptr()
-        io.rec_hidden = buf("rec_hidden", (B, T, K, H), f32).data_ptr()
+        # (bfloat16 with bf16 products: the values are bfloat16, and the reference's record holds them so)
+        io.rec_hidden = buf("rec_hidden", (B, T, K, H), torch.bfloat16 if model.prod == "bf16" else f32).data_ptr()
     if want_logits:
         io.logits = buf("logits", (B, T, N, M), f32).data_ptr()
     need = int(lib.hsnw_forward_scratch_bytes(ctypes.byref(model.struct), B, T))
@@ -500,7 +501,8 @@ def window_backward(
     """The reverse sweep of one window (``hsnw_window_backward``): ``(dc, db, (A, R))``.
 
     The arguments are ``state_gradient_backward``'s (``python/hsn/train/state_gradient.py:357-376``;
-    ``record`` holds ``y gate_pre m rms hidden``), or with ``full_cut`` ``recurrence_backward``'s
+    ``record`` holds ``y gate_pre m rms hidden``; ``hidden`` is bfloat16 with bf16 products, as the
+    forward sweep records it, and a float32 one is converted), or with ``full_cut`` ``recurrence_backward``'s
     (``python/hsn/train/split.py:128-139``; ``units`` and ``record`` unused). ``initial`` is the
     cotangent of the state after the last position (the next window's returned ``(A, R)``); the
     returned ``(A, R)`` is the cotangent of the state this window started from. ``info``, a dict,
@@ -543,7 +545,11 @@ def window_backward(
         put("gate_pre", record["gate_pre"], (B, T, K, d), f32)
         put("m", record["m"], (B, T, K, d), f32)
         put("rms", record["rms"], (B, T, K), f32)
-        put("hidden", record["hidden"], (B, T, K, H), f32)
+        hidden_dtype = torch.bfloat16 if model.prod == "bf16" else f32
+        hidden = record["hidden"]
+        if hidden.dtype != hidden_dtype and hidden.dtype in (f32, torch.bfloat16):
+            hidden = hidden.to(hidden_dtype)   # (exact for a record made with bf16 products)
+        put("hidden", hidden, (B, T, K, H), hidden_dtype)
     dc = torch.empty((B, T, K, d), dtype=f32, device=dev)
     db = torch.empty((B, T, K, d), dtype=f32, device=dev)
     if initial is None:

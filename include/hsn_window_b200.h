@@ -190,7 +190,9 @@ typedef struct HsnwForward {
     float* qs;                 /* [B,T,d] */
     float* h_max;              /* [B,T] */
     /* the round's values per slot, what the state-gradient sweep reads (optional as a group:
-     * rec_c null = none): c, b, h_old, y, gate_pre, m [B,T,K,d]; rms [B,T,K]; hidden [B,T,K,H] */
+     * rec_c null = none): c, b, h_old, y, gate_pre, m [B,T,K,d]; rms [B,T,K]; hidden [B,T,K,H].
+     * rec_hidden holds float32 with fp32 products and bfloat16 (2 bytes an element: the values are
+     * bfloat16 anyway, and the reference's record holds them so under autocast) with prod_bf16. */
     float* rec_c;
     float* rec_b;
     float* rec_h_old;
@@ -198,7 +200,7 @@ typedef struct HsnwForward {
     float* rec_gate_pre;
     float* rec_m;
     float* rec_rms;
-    float* rec_hidden;
+    void* rec_hidden;
     float* logits;             /* optional [B,T,N,M]: the scorer's logits (tests) */
     /* hsnw_forward_scratch_bytes() bytes, 256-byte aligned. Its first int32 is the call's status word:
      * cleared when the call is enqueued, set to 1 by a device-side wait (an mbarrier of the TMA
@@ -241,7 +243,7 @@ typedef struct HsnwBackward {
     const float* gate_pre;
     const float* m;
     const float* rms;          /* [B,T,K] */
-    const float* hidden;       /* [B,T,K,H] */
+    const void* hidden;        /* [B,T,K,H]: float32, or bfloat16 with prod_bf16 (as HsnwForward.rec_hidden) */
     const int64_t* cells;      /* [B,T,K] (0 on padded slots) */
     const int64_t* units;
     const uint8_t* valid;

@@ -115,3 +115,10 @@ def synthetic_window(rng, B, T, N, d, K, H, M, D, p_reset, age_max=1 << 30, S=9,
     reset[:, 0] = True
     state = (np.zeros((B, N, d), np.float32), np.zeros((B, d), np.float32), np.zeros((B, N), np.int64), np.zeros(B, np.int64))
     return W, z, ctx, scalars, reset, state
+
+
+def to_np(t):
+    """A device tensor as a numpy array (bfloat16, which numpy lacks, as float32: exact)."""
+    import torch
+
+    return t.float().cpu().numpy() if t.dtype == torch.bfloat16 else t.cpu().numpy()

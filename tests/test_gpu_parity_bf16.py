@@ -8,7 +8,7 @@ from __future__ import annotations
 import numpy as np
 import pytest
 import torch
-from conftest import dev, load_golden, synthetic_window
+from conftest import dev, load_golden, synthetic_window, to_np
 
 from oracle import window_oracle as O
 
@@ -124,7 +124,7 @@ def test_row_clusters_reproduce_the_reference_under_bf16_autocast(name: str, rev
                      ("hidden", "rec_hidden"), ("c", "bw_c"), ("b", "bw_b"), ("h_old", "bw_h_old")):  # fmt: skip
         want = z[ref][valid]
         scale = float(np.abs(want).max())
-        np.testing.assert_allclose(got["rec_" + key].cpu().numpy()[valid], want, rtol=tol, atol=tol * scale, err_msg=key)
+        np.testing.assert_allclose(to_np(got["rec_" + key])[valid], want, rtol=tol, atol=tol * scale, err_msg=key)
     # every position on its own: B T rows of one position, each from the reference's pre-round state
     B, T = valid.shape[:2]
     flat = lambda a: np.ascontiguousarray(a.reshape((B * T, 1) + a.shape[2:]))  # noqa: E731
@@ -203,7 +203,7 @@ def test_larger_configurations_in_bf16_equal_the_oracle(name: str) -> None:
                 "rec_rms", "rec_hidden", "logits"):  # fmt: skip
         w = want[key].astype(np.float64)
         scale = max(1e-3, float(np.abs(w).max()))
-        np.testing.assert_allclose(got[key].cpu().numpy(), w, rtol=tol, atol=tol * scale, err_msg=key)
+        np.testing.assert_allclose(to_np(got[key]), w, rtol=tol, atol=tol * scale, err_msg=key)
     assert np.array_equal(got["tape_age"].cpu().numpy(), want["tape_age"])
     free = window_forward(model, *args, tuple(dev(s) for s in state), want_logits=True)
     assert free["path"] == path
@@ -212,7 +212,7 @@ def test_larger_configurations_in_bf16_equal_the_oracle(name: str) -> None:
     N, d, K = shape["N"], shape["d"], shape["K"]
     post = rng.standard_normal((B, T, d)).astype(np.float32)
     sel = rng.standard_normal((B, T, K, d)).astype(np.float32)
-    cpu = {k: v.cpu().numpy() for k, v in got.items() if isinstance(v, torch.Tensor)}
+    cpu = {k: to_np(v) for k, v in got.items() if isinstance(v, torch.Tensor)}
     rec = {k: cpu["rec_" + k].astype(np.float64) for k in ("y", "hidden", "gate_pre", "m", "rms")}
     W64 = O.WindowWeights(**{k: (O.bf16_round(v).astype(np.float64) if isinstance(v, np.ndarray) and v.dtype == np.float32 else v)
                              for k, v in W.__dict__.items()})  # fmt: skip

@@ -6,7 +6,7 @@ from __future__ import annotations
 import numpy as np
 import pytest
 import torch
-from conftest import load_golden
+from conftest import load_golden, to_np
 
 from oracle import window_oracle as O
 
@@ -227,7 +227,7 @@ def test_forward_sweep_equals_the_oracle_on_a_slice_of_the_reference_shape(prod:
                 "rec_m", "rec_rms", "rec_hidden", "logits"):  # fmt: skip
         w = want[key].astype(np.float64)
         scale = max(1e-3, float(np.abs(w).max()))
-        np.testing.assert_allclose(got[key].cpu().numpy(), w, rtol=tol, atol=tol * scale, err_msg=key)
+        np.testing.assert_allclose(to_np(got[key]), w, rtol=tol, atol=tol * scale, err_msg=key)
     assert np.array_equal(got["tape_age"].cpu().numpy(), want["tape_age"])
     if not bf:
         free = window_forward(model, *args)
