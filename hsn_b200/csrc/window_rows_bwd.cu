@@ -45,6 +45,7 @@ namespace {
 #endif
 
 constexpr int kStagesB = 3;
+constexpr int kDhidOperand = 2 * 16 * 16 * 8;   // bytes of one
 constexpr int kMaxKB = 8;
 constexpr int kMaxMB = 16;
 
@@ -52,7 +53,7 @@ struct RowsBwdCtx {
     HsnwModel m;
     HsnwBackward io;
     int C, Nc, Ks;
-    uint32_t bank_bytes, w2_bytes;   // a chunk, its W2 part
+    uint32_t bank_bytes, w2_bytes;   // a unit's weights on the block's 128 columns (two pieces: W2's, then W1's state rows = a ring slot), the first piece
     unsigned long long* trace;       // phase timestamps (HSNW_TRACE builds): after the status area of the caller's scratch, or null
     int* status;                     // set to 1 by a ring wait that ran out
 };
@@ -92,7 +93,7 @@ __host__ __device__ inline RowsBwdSmem rows_bwd_smem(const HsnwModel& m, int C, 
         L.dec[s] = take(4 * (2 * K + 2 * K * D + 2 * kMaxMB + 4 + K + K * D));
     }
     L.du_all = take(2 * 16 * d);        // d_unit of every slot as a bf16 operand [d/8][16][8]
-    L.b2 = take(2 * 2 * 8 * 16 * 8);    // two bf16 operands [8][16][8]: dhid of a chunk's 64 columns
+    L.b2 = take(2 * kDhidOperand);      // two bf16 operands [16][16][8]: dhid of a unit on the block's 128 columns
     L.dg_all = take(4 * K * d);
     L.inbox_dv = take(4 * C * Ks * 2 * d);
     L.inbox_sig = take(4 * C * Ks + 16);
@@ -132,7 +133,8 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
     const uint32_t d_magic = 0xffffffffu / static_cast<uint32_t>(D) + 1u;      // e / D the same way (the magic wraps to 0 for D = 1)
     auto div_D = [&](int e) { return D == 1 ? e : static_cast<int>(__umulhi(static_cast<uint32_t>(e), d_magic)); };
 
-    const RowsBwdSmem L = rows_bwd_smem(c.m, C, c.bank_bytes);
+    const RowsBwdSmem L = rows_bwd_smem(c.m, C, c.bank_bytes - c.w2_bytes);
+    const uint32_t slot_bytes = c.bank_bytes - c.w2_bytes;   // the larger piece
     unsigned char* ring = dyn + L.ring + ((1024u - (smem_addr(dyn + L.ring) & 1023u)) & 1023u);
     float* A_s = reinterpret_cast<float*>(dyn + L.A);
     uint16_t* wout = reinterpret_cast<uint16_t*>(dyn + L.wout);
@@ -301,7 +303,7 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
         for (int e = tid; e < 2 * d; e += kConsumers) dq_of(buf)[e] = 0.0f;
     }
     for (int e = tid; e < 16 * d; e += kConsumers) du_op[e] = 0;
-    for (int e = tid; e < 2 * 8 * 16 * 8; e += kConsumers) b2[e] = 0;
+    for (int e = tid; e < kDhidOperand; e += kConsumers) b2[e] = 0;   // (uint16 elements: both operands)
     if (warp == 0) tmem_alloc(&tmem_slot, 256);
     tcgen05_fence_before();
     __syncthreads();
@@ -317,7 +319,7 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
     uint32_t g_issue = 0, g_use = 0;
     int cur_t = T - 1, cur_i = 0;       // the next chunk to request: position, index in its 2 n_units chunks
     int ready_t = T - 1;                // decisions are known down to this position
-    auto issue_ahead = [&]() {
+    auto issue_ahead = [&](bool wait_for_slots) {   // false: request only into slots that are free now
         while (g_issue < g_use + kStagesB && cur_t >= ready_t && cur_t >= 0) {
             const int* dc_ = dec_of(cur_t & 1);
             const int n_chunks = 2 * dc_[o_n];
@@ -327,17 +329,31 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
                 continue;
             }
             const uint32_t slot = g_issue % kStagesB;
-            if (g_issue >= kStagesB) ring_wait(&empty[slot], ((g_issue / kStagesB) - 1u) & 1u, c.status, &failed_s);
+            if (g_issue >= kStagesB) {
+                const uint32_t parity = ((g_issue / kStagesB) - 1u) & 1u;
+                if (wait_for_slots) {
+                    ring_wait(&empty[slot], parity, c.status, &failed_s);
+                } else {
+                    uint32_t done;
+                    asm volatile(
+                        "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                        : "=r"(done)
+                        : "r"(smem_addr(&empty[slot])), "r"(parity)
+                        : "memory");
+                    if (!done) break;
+                }
+            }
             const int j = dc_[o_ulist + (cur_i >> 1)];
-            const unsigned char* from = bank + (static_cast<size_t>(j) * (H / 64) + r * 2 + (cur_i & 1)) * c.bank_bytes;
-            mbar_expect_tx(&full[slot], c.bank_bytes);
-            bulk_g2s(ring + slot * c.bank_bytes, from, c.bank_bytes, &full[slot]);
+            const unsigned char* from = bank + (static_cast<size_t>(j) * C + r) * c.bank_bytes + ((cur_i & 1) ? c.w2_bytes : 0u);
+            const uint32_t bytes = (cur_i & 1) ? slot_bytes : c.w2_bytes;
+            mbar_expect_tx(&full[slot], bytes);
+            bulk_g2s(ring + slot * slot_bytes, from, bytes, &full[slot]);
             ++g_issue;
             ++cur_i;
         }
     };
     __syncthreads();
-    if (tid == 0) issue_ahead();
+    if (tid == 0) issue_ahead(true);
     cl.sync();
 
     const float n_f = static_cast<float>(N);
@@ -418,119 +434,117 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
         BMARK(2);
         // ---------------- M
         BMARK(3);
-        // the transposed layers on the streamed chunks, on the tensor cores. Per chunk (unit j, 64
-        // hidden columns): D1 [64 columns, 16 slots] = W2 part x d_unit^T; the epilogue multiplies by
-        // the activation's derivative at the recorded pre-activation for the slots that ran unit j
-        // (zero for the others), adds to the norm's inner products and writes the bf16 operand of the
-        // second product; D2 [2d state inputs, 16 slots] += W1 state part x dhid^T accumulates over the
-        // position's chunks in tensor memory. M is 128 for both: the first product's rows 64..127 come
-        // from the bytes after the tile and are never read. Thread 0 issues; warps 0, 1, 4, 5 read D1.
+        // The transposed layers on the streamed weights, on the tensor cores. A unit's weights on the block's
+        // 128 hidden columns arrive as two pieces, each a ring slot of its own: W2's ([128 columns][d outputs])
+        // and the state rows of W1 ([2d state inputs][128 columns]). D1 [128 columns, 16 slots] = W2 x
+        // d_unit^T (its slot is handed back as soon as the product has run); the epilogue multiplies by the
+        // activation's derivative at the recorded pre-activation for the slots that ran the unit (zero for
+        // the others), adds to the norm's inner products and writes the bf16 operand of the second product;
+        // D2 [2d state inputs, 16 slots] += W1 state part x dhid^T accumulates over the position's units in
+        // tensor memory. Warp 0 issues (as a whole: umma.cuh); all eight warps read D1: warp w the columns
+        // 32 (w % 4) .. and the slots 4 (w / 4) .. 4 (w / 4) + 3.
         const int n_units = dc_[o_n];
         const int n_chunks = 2 * n_units;
-        const bool epi = (warp & 2) == 0;
-        const int hc = lane + 32 * (warp & 1), sh = warp >> 2;
+        const int hc = lane + 32 * (warp & 3), sh = warp >> 2;
         const uint32_t idesc = umma_idesc_bf16(128, 16);
         const uint32_t g0 = g_use;
         float inner[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         tcgen05_fence_after();
-        // a chunk's first product: D1 (tensor memory columns 64 b .. 64 b + 15, b = chunk parity); issued by
-        // warp 0 as a whole (umma.cuh: one elected lane, warp-uniform control flow)
+        // a unit's first product: D1 (tensor memory columns 64 b .. 64 b + 15, b = unit parity)
         auto first_product = [&](int i) {
-            const uint32_t slot = (g0 + i) % kStagesB;
-            ring_wait(&full[slot], ((g0 + i) / kStagesB) & 1u, c.status, &failed_s);
+            const uint32_t g = g0 + 2 * i, slot = g % kStagesB;
+            ring_wait(&full[slot], (g / kStagesB) & 1u, c.status, &failed_s);
+            const unsigned char* tile = ring + slot * slot_bytes;
             if (d == 64)
-                umma_chain_sw128<4>(taddr + 64 * (i & 1), umma_desc_sw128(ring + slot * c.bank_bytes), 0, umma_desc(du_op, 16),
-                                    umma_kstep(16), idesc, false);
+                umma_chain_sw128<4>(taddr + 64 * (i & 1), umma_desc_sw128(tile), 0, umma_desc(du_op, 16), umma_kstep(16), idesc, false);
             else
-                umma_chain_fixed<d / 16>(taddr + 64 * (i & 1), umma_desc(ring + slot * c.bank_bytes, 64), umma_desc(du_op, 16), idesc,
-                                         umma_kstep(64), umma_kstep(16), false);
+                umma_chain_fixed<d / 16>(taddr + 64 * (i & 1), umma_desc(tile, 128), umma_desc(du_op, 16), idesc, umma_kstep(128),
+                                         umma_kstep(16), false);
+            umma_commit(&empty[slot]);   // the piece is spent when this product has read it
             umma_commit(&bar_d1[i & 1]);
+            if (lane == 0) ++g_use;
         };
-        if (warp == 0 && n_chunks > 0) first_product(0);
-        if (epi) {
-            for (int i = 0; i < n_chunks; ++i) {
-                const int j = dc_[o_ulist + (i >> 1)];
-                const unsigned mask = static_cast<unsigned>(dc_[o_umask + (i >> 1)]);
-                const uint32_t slot = (g0 + i) % kStagesB;
-                if (warp == 0 && i + 1 < n_chunks) first_product(i + 1);
-                {
-                    const int hid_col = (i & 1) * 64 + hc;
-                    const float bias = b1s[j * 128 + hid_col];
-                    uint16_t* b2i = b2 + (i & 1) * (8 * 16 * 8);
-                    ring_wait(&bar_d1[i & 1], ((i & 1) ? d1_count1 : d1_count0) & 1u, c.status, &failed_s);
-                    tcgen05_fence_after();
-                    float acc[8];
-                    tmem_ld8(tmem_addr(taddr, 32 * (warp & 1), 64 * (i & 1)), acc);
-    #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int k = 4 * sh + q;
-                        float dh = 0.0f;
-                        if (mask & (1u << k)) {
-                            const float hv = bf16_value(hd[k * 128 + hid_col]);
-                            dh = bf16r((sh ? acc[4 + q] : acc[q]) * gelu_erf_grad(hv));
-                            inner[q] += dh * (hv - bias);
-                        }
-                        b2i[((hc >> 3) * 16 + k) * 8 + (hc & 7)] = bf16_bits(dh);
-                    }
-                    fence_async_smem();
-                    tcgen05_fence_before();
-                }
-                if (i & 1) ++d1_count1;
-                else ++d1_count0;
-                asm volatile("bar.sync 2, 128;\n" ::: "memory");   // the four epilogue warps
-                if (warp == 0) {
-                    tcgen05_fence_after();
-                    // D2 (columns 128 .. 143) accumulates over the position's chunks
-                    if (d == 64)
-                        umma_chain_sw128<4>(taddr + 128, umma_desc_sw128(ring + slot * c.bank_bytes + c.w2_bytes), 0,
-                                            umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), umma_kstep(16), idesc, i > 0);
-                    else
-                        umma_chain_fixed<4>(taddr + 128, umma_desc(ring + slot * c.bank_bytes + c.w2_bytes, two),
-                                            umma_desc(b2 + (i & 1) * (8 * 16 * 8), 16), idesc, umma_kstep(two), umma_kstep(16), i > 0);
-                    umma_commit(&empty[slot]);
-                    if (i + 1 == n_chunks) umma_commit(&bar_d2);
-                    if (lane == 0) {
-                        ++g_use;
-                        issue_ahead();
-                    }
-                    __syncwarp();
-                }
-            }
-        } else {
-            // the gate's transposed linear, this block's state outputs, by the other four warps; first
-            // the position's dc and db go to memory (these warps meet no barrier for microseconds)
-            const int t2 = (warp >> 2) * 64 + (warp & 1) * 32 + lane;   // 0 .. 127
-            for (int e = t2; e < Ks * d; e += 128) {
+        if (warp == 0 && n_units > 0) first_product(0);
+        {
+            // under the first product, what waits for nothing: the position's dc and db go to memory, the
+            // gate's transposed linear on this block's state outputs, and the next position's record
+            // requests and decision (off the position's critical path)
+            for (int e = tid; e < Ks * d; e += kConsumers) {
                 const int kl = e / d, x = e - kl * d, k = kl * C + r;
                 if (k < K) {
                     c.io.dc[(rt * K + k) * d + x] = dcs[e];
                     c.io.db[(rt * K + k) * d + x] = dbs[e];
                 }
             }
-            for (int e = t2; e < K * gcols; e += 128) {
+            for (int e = tid; e < K * gcols; e += kConsumers) {
                 const int k = e >> gshift, il = e - k * gcols;
                 const float sum = dc_[k] >= 0 ? dot_bf16w(dg_all + k * d, 1, gate + il * d, 1, d) : 0.0f;
                 peer(cl, inbox_g, k & cmask)[(k >> cshift) * two + r * gcols + il] = sum;
             }
-            // these warps wait for the epilogues anyway: the next position's record is requested here, and
-            // its decision read, off the position's critical path
             if (t > 0) {
-                prefetch(t - 1, t2, 128);
-                decision_load(t - 1, t2);
-                decision_store(t - 1, t2);
+                prefetch(t - 1, tid, kConsumers);
+                decision_load(t - 1, tid);
+                decision_store(t - 1, tid);
+            }
+        }
+        for (int i = 0; i < n_units; ++i) {
+            const int j = dc_[o_ulist + i];
+            const unsigned mask = static_cast<unsigned>(dc_[o_umask + i]);
+            if (warp == 0 && i + 1 < n_units) first_product(i + 1);   // the next unit's first product runs under this epilogue
+            {
+                const float bias = b1s[j * 128 + hc];
+                uint16_t* b2i = b2 + (i & 1) * (kDhidOperand / 2);
+                ring_wait(&bar_d1[i & 1], ((i & 1) ? d1_count1 : d1_count0) & 1u, c.status, &failed_s);
+                tcgen05_fence_after();
+                float acc[8];
+                tmem_ld8(tmem_addr(taddr, 32 * (warp & 3), 64 * (i & 1)), acc);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int k = 4 * sh + q;
+                    float dh = 0.0f;
+                    if (mask & (1u << k)) {
+                        const float hv = bf16_value(hd[k * 128 + hc]);
+                        dh = bf16r((sh ? acc[4 + q] : acc[q]) * gelu_erf_grad(hv));
+                        inner[q] += dh * (hv - bias);
+                    }
+                    b2i[((hc >> 3) * 16 + k) * 8 + (hc & 7)] = bf16_bits(dh);
+                }
+                fence_async_smem();
+                tcgen05_fence_before();
+            }
+            if (i & 1) ++d1_count1;
+            else ++d1_count0;
+            __syncthreads();   // every thread's part of the operand is written
+            if (warp == 0) {
+                const uint32_t g = g0 + 2 * i + 1, slot = g % kStagesB;
+                ring_wait(&full[slot], (g / kStagesB) & 1u, c.status, &failed_s);
+                tcgen05_fence_after();
+                const unsigned char* tile = ring + slot * slot_bytes;
+                // D2 (columns 128 .. 143) accumulates over the position's units
+                if (d == 64)   // (two K-blocks of 64 hidden columns, 2d rows each)
+                    umma_chain_sw128<8>(taddr + 128, umma_desc_sw128(tile), (128 * 128) >> 4,
+                                        umma_desc(b2 + (i & 1) * (kDhidOperand / 2), 16), umma_kstep(16), idesc, i > 0);
+                else
+                    umma_chain_fixed<8>(taddr + 128, umma_desc(tile, two), umma_desc(b2 + (i & 1) * (kDhidOperand / 2), 16), idesc,
+                                        umma_kstep(two), umma_kstep(16), i > 0);
+                umma_commit(&empty[slot]);
+                if (i + 1 == n_units) umma_commit(&bar_d2);
+                if (lane == 0) {
+                    ++g_use;
+                    issue_ahead(false);   // (a slot whose product was only just issued is taken at the next chance)
+                }
+                __syncwarp();
             }
         }
         __syncthreads();
         if (tid != 0) g_use += n_chunks;
         BMARK(4);
         if (warp == 7 && t > 0) unit_lists(t - 1);   // (a warp with nothing else to do here)
-        // the slots' inner products: the epilogue warps' sums, then the pair of warps of each half
-        if (epi) {
+        // the slots' inner products: every warp's sums, then the four warps of each half in order
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const float sum = warp_sum(inner[q]);
-                if (lane == 0) red[warp * 4 + q] = sum;
-            }
+        for (int q = 0; q < 4; ++q) {
+            const float sum = warp_sum(inner[q]);
+            if (lane == 0) red[warp * 4 + q] = sum;
         }
         // the block's partial of dv from the accumulator, to the slots' owners
         if (warp < 4 && 32 * warp < two) {
@@ -554,11 +568,12 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
         __syncthreads();
         if (tid == 0) {   // the next position's decision is in place: its chunks may be requested
             if (t > 0) ready_t = t - 1;
-            issue_ahead();
+            issue_ahead(true);
         }
         if (tid < K) {
             const int k = tid, half = k >> 2, q = k & 3;
-            const float sum = red[(4 * half) * 4 + q] + red[(4 * half + 1) * 4 + q];   // warps 4 half, 4 half + 1
+            const float* part = red + (4 * half) * 4 + q;   // warps 4 half .. 4 half + 3
+            const float sum = (part[0] + part[4]) + (part[8] + part[12]);
             peer(cl, inbox_sig, k & cmask)[r * Ks + (k >> cshift)] = sum;
         }
         BMARK(5);
@@ -646,15 +661,15 @@ static bool rows_bwd_shape(const HsnwModel& m, RowsBwdCtx* c) {
     c->C = C;
     c->Nc = m.N / C;
     c->Ks = (m.K + C - 1) / C;
-    c->w2_bytes = static_cast<uint32_t>(128 * m.d);
-    c->bank_bytes = static_cast<uint32_t>(384 * m.d);
+    c->w2_bytes = static_cast<uint32_t>(256 * m.d);
+    c->bank_bytes = static_cast<uint32_t>(768 * m.d);
     return true;
 }
 
 int hsnw_rows_backward(const HsnwModel* model, const HsnwBackward* io, int* status, cudaStream_t stream) {
     RowsBwdCtx c;
     if (io->full_cut || !rows_bwd_shape(*model, &c)) return HSNW_DECLINED;
-    const RowsBwdSmem L = rows_bwd_smem(*model, c.C, c.bank_bytes);
+    const RowsBwdSmem L = rows_bwd_smem(*model, c.C, c.bank_bytes - c.w2_bytes);
     if (L.total + 1024 > hsnw_max_shared()) return HSNW_DECLINED;
     c.m = *model;
     c.io = *io;

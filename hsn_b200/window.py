@@ -253,14 +253,13 @@ def _row_images(w1: Tensor, w2: Tensor, f_w1q_t: Tensor, f_w2_t: Tensor) -> dict
     layer ``[d][256]`` followed by the same columns' rows of the second layer ``[256][d]``. Forward
     (``rows_bank``): per unit and block of 128 hidden columns three K-major tensor-core tiles, ``W1``'s
     rows of the inputs ``[0, 2d)``, of ``[2d, 4d)`` (each ``[128 columns][2d]``) and ``W2`` (``[d
-    outputs][128 columns]``). Reverse (``rows_bank_bw``): per unit and block of 64 columns ``W2`` as
-    ``[64 columns][d]`` then the state rows of ``W1`` as ``[2d][64 columns]``. ``d == 64``: 128-byte
+    outputs][128 columns]``). Reverse (``rows_bank_bw``): per unit and block of 128 columns ``W2`` as
+    ``[128 columns][d]`` then the state rows of ``W1`` as ``[2d][128 columns]``. ``d == 64``: 128-byte
     swizzled K-blocks of 64. Other ``d``: the unswizzled core-matrix layout ``[K/8][rows][8]`` of
     ``umma.cuh``."""
     M, in4, H = (int(n) for n in w1.shape)
     d = int(w2.shape[2])
     bf = torch.bfloat16
-    nb = H // 64
     C = H // 128
     if d == 64:
         # forward: per unit and block of 128 columns, W1 as four K-blocks [128 columns][64 inputs] (two pieces of
@@ -269,14 +268,16 @@ def _row_images(w1: Tensor, w2: Tensor, f_w1q_t: Tensor, f_w2_t: Tensor) -> dict
         a = _sw128(a).reshape(M, C, -1)
         b = w2.reshape(M, C, 2, 64, d).permute(0, 1, 2, 4, 3).to(bf)  # [M, C, K-block, output, column]
         b = _sw128(b).reshape(M, C, -1)
-        ba = _sw128(w2.reshape(M, nb, 64, d).to(bf)).reshape(M, nb, -1)  # [M, nb, column, output]
-        bb = w1[:, 2 * d :, :].reshape(M, 2 * d, nb, 64).permute(0, 2, 1, 3).to(bf)  # [M, nb, state input, column]
-        bb = _sw128(bb).reshape(M, nb, -1)
+        # reverse: per unit and block of 128 columns, W2 as [128 columns][d outputs], then the state rows of W1 as
+        # two K-blocks [2d state inputs][64 columns]
+        ba = _sw128(w2.reshape(M, C, 128, d).to(bf)).reshape(M, C, -1)  # [M, C, column, output]
+        bb = w1[:, 2 * d :, :].reshape(M, 2 * d, C, 2, 64).permute(0, 2, 3, 1, 4).to(bf)  # [M, C, K-block, state input, column]
+        bb = _sw128(bb).reshape(M, C, -1)
     else:
         a = w1.reshape(M, in4 // 8, 8, C, 128).permute(0, 3, 1, 4, 2).to(bf).reshape(M, C, -1)  # [M,C,(4d/8)*128*8]
         b = w2.reshape(M, C, 16, 8, d).permute(0, 1, 2, 4, 3).to(bf).reshape(M, C, -1)  # [M,C,16*d*8]
-        ba = w2.reshape(M, nb, 64, d // 8, 8).permute(0, 1, 3, 2, 4).to(bf).reshape(M, nb, -1)
-        bb = w1[:, 2 * d :, :].reshape(M, 2 * d, nb, 8, 8).permute(0, 2, 3, 1, 4).to(bf).reshape(M, nb, -1)
+        ba = w2.reshape(M, C, 128, d // 8, 8).permute(0, 1, 3, 2, 4).to(bf).reshape(M, C, -1)  # [M,C,(d/8)*128*8]
+        bb = w1[:, 2 * d :, :].reshape(M, 2 * d, C, 16, 8).permute(0, 2, 3, 1, 4).to(bf).reshape(M, C, -1)  # [M,C,16*2d*8]
     bank = torch.cat([a, b], dim=2).contiguous()
     bank_bw = torch.cat([ba, bb], dim=2).contiguous()
     f1 = f_w1q_t.reshape(d, C, 256).permute(1, 0, 2).to(bf).reshape(C, -1)  # [C, d*256]

@@ -151,9 +151,10 @@ typedef struct HsnwModel {
      *   f_w1q_t as [d][256], then the same columns' rows of f_w2_t as [256][d]. */
     const void* rows_bank;
     const void* rows_front;
-    /* the same for the reverse sweep's per-row cluster kernel: rows_bank_bw [M][H/64] chunks, first W2
-     * as [d/8][64][8] (element (column c, output x) at ((x/8) 64 + c) 8 + x%8), then the 2d state rows
-     * of W1 as [8][2d][8] (element (state input i, column c) at ((c/8) 2d + i) 8 + c%8). */
+    /* the same for the reverse sweep's per-row cluster kernel: rows_bank_bw [M][C], first W2 as [d/8][128][8]
+     * (element (column c, output x) at ((x/8) 128 + c) 8 + x%8), then the 2d state rows of W1 as
+     * [16][2d][8] (element (state input i, column c) at ((c/8) 2d + i) 8 + c%8); 128-byte-swizzled
+     * K-blocks of 64 instead with d = 64. */
     const void* rows_bank_bw;
 } HsnwModel;
 
