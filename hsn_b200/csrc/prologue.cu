@@ -19,58 +19,85 @@ using namespace hsnw;
 
 namespace {
 
-constexpr int kTableThreads = 128;
+constexpr int kTableThreads = 256;
 
 // One block per byte value v: z_table[v] = fc2(act(fc1(emb[v]))), addr_table[v][n].
-// Dynamic shared memory: d + H floats.
-__global__ void k_pro_tables(HsnwPrologue p, float* z_table, float* addr_table) {
+// Dynamic shared memory: d + H floats. A warp per output: its lanes walk the weight row (consecutive
+// addresses) and the partial sums meet by shuffles, in a fixed order.
+__global__ void __launch_bounds__(kTableThreads) k_pro_tables(HsnwPrologue p, float* z_table, float* addr_table) {
     extern __shared__ __align__(16) unsigned char dyn[];
     float* x = reinterpret_cast<float*>(dyn);   // [d]  the byte's embedding
     float* hid = x + p.d;                        // [H]
-    const int v = blockIdx.x, tid = threadIdx.x;
+    const int v = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int kWarps = kTableThreads / 32;
     const bool bf = p.prod_bf16 != 0;
     for (int i = tid; i < p.d; i += kTableThreads) x[i] = maybe_bf16(p.byte_emb[static_cast<int64_t>(v) * p.d + i], bf);
     __syncthreads();
-    for (int h = tid; h < p.H; h += kTableThreads) {
+    for (int h = warp; h < p.H; h += kWarps) {
         const float* w = p.enc_w1 + static_cast<int64_t>(h) * p.d;   // nn.Linear layout [out, in]
         float sum = 0.0f;
-        for (int i = 0; i < p.d; ++i) sum += x[i] * maybe_bf16(w[i], bf);
-        const float pre = maybe_bf16(sum + maybe_bf16(p.enc_b1[h], bf), bf);
-        hid[h] = maybe_bf16(gelu_erf(pre), bf);
+        for (int i = lane; i < p.d; i += 32) sum += x[i] * maybe_bf16(w[i], bf);
+        sum = warp_sum(sum);
+        if (lane == 0) {
+            const float pre = maybe_bf16(sum + maybe_bf16(p.enc_b1[h], bf), bf);
+            hid[h] = maybe_bf16(gelu_erf(pre), bf);
+        }
     }
     __syncthreads();
-    for (int o = tid; o < p.d; o += kTableThreads) {
+    for (int o = warp; o < p.d; o += kWarps) {
         const float* w = p.enc_w2 + static_cast<int64_t>(o) * p.H;
         float sum = 0.0f;
-        for (int h = 0; h < p.H; ++h) sum += hid[h] * maybe_bf16(w[h], bf);
-        z_table[static_cast<int64_t>(v) * p.d + o] = maybe_bf16(sum + maybe_bf16(p.enc_b2[o], bf), bf);
+        for (int h = lane; h < p.H; h += 32) sum += hid[h] * maybe_bf16(w[h], bf);
+        sum = warp_sum(sum);
+        if (lane == 0) z_table[static_cast<int64_t>(v) * p.d + o] = maybe_bf16(sum + maybe_bf16(p.enc_b2[o], bf), bf);
     }
     if (addr_table) {   // float32 whatever the products' precision: the reference takes these outside autocast
         const float root = sqrtf(static_cast<float>(p.d));
         const float* code = p.byte_codes + static_cast<int64_t>(v) * p.d;
-        for (int n = tid; n < p.N; n += kTableThreads) {
+        for (int n = warp; n < p.N; n += kWarps) {
             const float* a = p.cell_addresses + static_cast<int64_t>(n) * p.d;
             float sum = 0.0f;
-            for (int i = 0; i < p.d; ++i) sum += code[i] * a[i];
-            addr_table[static_cast<int64_t>(v) * p.N + n] = sum * root;
+            for (int i = lane; i < p.d; i += 32) sum += code[i] * a[i];
+            sum = warp_sum(sum);
+            if (lane == 0) addr_table[static_cast<int64_t>(v) * p.N + n] = sum * root;
         }
     }
 }
 
-// One thread per row: the position before each step and the byte before each position.
-__global__ void k_pro_positions(HsnwPrologue p, int64_t* positions, int32_t* previous) {
-    const int b = blockIdx.x * blockDim.x + threadIdx.x;
-    if (b >= p.B) return;
+// One block per row: the position before each step (t - s after the row's last reset s <= t, else the
+// carried position + t: a running maximum of the reset indices) and the byte before each position.
+__global__ void __launch_bounds__(256) k_pro_positions(HsnwPrologue p, int64_t* positions, int32_t* previous) {
+    __shared__ int warp_top[8];
+    __shared__ int carried_s;
+    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t base = static_cast<int64_t>(b) * p.T;
-    int last = -1;
-    int32_t before = p.prev_tokens ? static_cast<int32_t>(p.prev_tokens[b]) : p.bos;
     const int64_t start = p.pos0[b];
-    for (int t = 0; t < p.T; ++t) {
-        const bool cut = p.reset[base + t] != 0;
-        if (cut) last = t;
-        positions[base + t] = last >= 0 ? t - last : start + t;
-        previous[base + t] = cut ? p.bos : before;
-        before = static_cast<int32_t>(p.tokens[base + t]);
+    if (tid == 0) carried_s = -1;
+    __syncthreads();
+    for (int t0 = 0; t0 < p.T; t0 += 256) {
+        const int t = t0 + tid;
+        const bool in = t < p.T;
+        const bool cut = in && p.reset[base + t] != 0;
+        int last = cut ? t : -1;
+#pragma unroll
+        for (int w = 1; w < 32; w <<= 1) {   // the running maximum inside the warp
+            const int other = __shfl_up_sync(0xffffffffu, last, w);
+            if (lane >= w) last = max(last, other);
+        }
+        if (lane == 31) warp_top[warp] = last;
+        __syncthreads();
+        int before = carried_s;
+        for (int w = 0; w < warp; ++w) before = max(before, warp_top[w]);
+        last = max(last, before);
+        if (in) {
+            positions[base + t] = last >= 0 ? t - last : start + t;
+            const int32_t prior = t > 0 ? static_cast<int32_t>(p.tokens[base + t - 1])
+                                        : (p.prev_tokens ? static_cast<int32_t>(p.prev_tokens[b]) : p.bos);
+            previous[base + t] = cut ? p.bos : prior;
+        }
+        __syncthreads();
+        if (tid == 255) carried_s = last;   // the chunk's last thread holds the maximum so far
+        __syncthreads();
     }
 }
 
@@ -154,7 +181,7 @@ extern "C" int hsnw_window_prologue(const HsnwPrologue* p, void* stream_) {
     int32_t* previous = reinterpret_cast<int32_t*>(base + off);
     hsnw_profile_mark(HSNW_K_PROLOGUE, stream);
     k_pro_tables<<<p->V, kTableThreads, shared, stream>>>(*p, z_table, addr_table);
-    k_pro_positions<<<(p->B + 63) / 64, 64, 0, stream>>>(*p, positions, previous);
+    k_pro_positions<<<p->B, 256, 0, stream>>>(*p, positions, previous);
     k_pro_rows<<<static_cast<unsigned>(static_cast<int64_t>(p->B) * p->T), 256, 0, stream>>>(*p, z_table, addr_table, positions, previous);
     return hsnw_check_launch("window_prologue");
 }
