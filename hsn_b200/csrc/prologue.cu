@@ -33,33 +33,59 @@ __global__ void __launch_bounds__(kTableThreads) k_pro_tables(HsnwPrologue p, fl
     const bool bf = p.prod_bf16 != 0;
     for (int i = tid; i < p.d; i += kTableThreads) x[i] = maybe_bf16(p.byte_emb[static_cast<int64_t>(v) * p.d + i], bf);
     __syncthreads();
-    for (int h = warp; h < p.H; h += kWarps) {
-        const float* w = p.enc_w1 + static_cast<int64_t>(h) * p.d;   // nn.Linear layout [out, in]
-        float sum = 0.0f;
-        for (int i = lane; i < p.d; i += 32) sum += x[i] * maybe_bf16(w[i], bf);
-        sum = warp_sum(sum);
-        if (lane == 0) {
-            const float pre = maybe_bf16(sum + maybe_bf16(p.enc_b1[h], bf), bf);
-            hid[h] = maybe_bf16(gelu_erf(pre), bf);
+    // (four outputs a round: the rows' loads, each a trip to L2, are in flight together)
+    for (int h0 = 4 * warp; h0 < p.H; h0 += 4 * kWarps) {
+        float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int i = lane; i < p.d; i += 32) {
+            float w[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) w[u] = h0 + u < p.H ? p.enc_w1[static_cast<int64_t>(h0 + u) * p.d + i] : 0.0f;   // [out, in]
+#pragma unroll
+            for (int u = 0; u < 4; ++u) sum[u] += x[i] * maybe_bf16(w[u], bf);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) sum[u] = warp_sum(sum[u]);
+        if (lane < 4 && h0 + lane < p.H) {
+            const float mine = lane == 0 ? sum[0] : lane == 1 ? sum[1] : lane == 2 ? sum[2] : sum[3];
+            const float pre = maybe_bf16(mine + maybe_bf16(p.enc_b1[h0 + lane], bf), bf);
+            hid[h0 + lane] = maybe_bf16(gelu_erf(pre), bf);
         }
     }
     __syncthreads();
-    for (int o = warp; o < p.d; o += kWarps) {
-        const float* w = p.enc_w2 + static_cast<int64_t>(o) * p.H;
-        float sum = 0.0f;
-        for (int h = lane; h < p.H; h += 32) sum += hid[h] * maybe_bf16(w[h], bf);
-        sum = warp_sum(sum);
-        if (lane == 0) z_table[static_cast<int64_t>(v) * p.d + o] = maybe_bf16(sum + maybe_bf16(p.enc_b2[o], bf), bf);
+    for (int o0 = 4 * warp; o0 < p.d; o0 += 4 * kWarps) {
+        float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int h = lane; h < p.H; h += 32) {
+            float w[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) w[u] = o0 + u < p.d ? p.enc_w2[static_cast<int64_t>(o0 + u) * p.H + h] : 0.0f;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) sum[u] += hid[h] * maybe_bf16(w[u], bf);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) sum[u] = warp_sum(sum[u]);
+        if (lane < 4 && o0 + lane < p.d) {
+            const float mine = lane == 0 ? sum[0] : lane == 1 ? sum[1] : lane == 2 ? sum[2] : sum[3];
+            z_table[static_cast<int64_t>(v) * p.d + o0 + lane] = maybe_bf16(mine + maybe_bf16(p.enc_b2[o0 + lane], bf), bf);
+        }
     }
     if (addr_table) {   // float32 whatever the products' precision: the reference takes these outside autocast
         const float root = sqrtf(static_cast<float>(p.d));
         const float* code = p.byte_codes + static_cast<int64_t>(v) * p.d;
-        for (int n = warp; n < p.N; n += kWarps) {
-            const float* a = p.cell_addresses + static_cast<int64_t>(n) * p.d;
-            float sum = 0.0f;
-            for (int i = lane; i < p.d; i += 32) sum += code[i] * a[i];
-            sum = warp_sum(sum);
-            if (lane == 0) addr_table[static_cast<int64_t>(v) * p.N + n] = sum * root;
+        for (int n0 = 4 * warp; n0 < p.N; n0 += 4 * kWarps) {
+            float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            for (int i = lane; i < p.d; i += 32) {
+                float a[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) a[u] = n0 + u < p.N ? p.cell_addresses[static_cast<int64_t>(n0 + u) * p.d + i] : 0.0f;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) sum[u] += code[i] * a[u];
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) sum[u] = warp_sum(sum[u]);
+            if (lane < 4 && n0 + lane < p.N) {
+                const float mine = lane == 0 ? sum[0] : lane == 1 ? sum[1] : lane == 2 ? sum[2] : sum[3];
+                addr_table[static_cast<int64_t>(v) * p.N + n0 + lane] = mine * root;
+            }
         }
     }
 }
@@ -120,6 +146,18 @@ __global__ void k_pro_rows(HsnwPrologue p, const float* z_table, const float* ad
     const float* chosen = p.ema_selected + (p.ema_per_row ? static_cast<int64_t>(b) * p.N : 0);
     const float* cur = addr_table ? addr_table + static_cast<int64_t>(token) * p.N : nullptr;
     const float* prev = addr_table ? addr_table + static_cast<int64_t>(previous[rt]) * p.N : nullptr;
+    // the per-cell values first (four loads a cell, all in flight), then the writes from shared memory
+    extern __shared__ __align__(16) unsigned char dyn[];
+    float* cell = reinterpret_cast<float*>(dyn);   // [4][N]: utility, selected, a_cur, a_prev
+    for (int n = tid; n < p.N; n += nt) {
+        const float a = util[n], b2 = chosen[n];
+        const float c2 = cur ? cur[n] : 0.0f, d2 = prev ? prev[n] : 0.0f;
+        cell[n] = a;
+        cell[p.N + n] = b2;
+        cell[2 * p.N + n] = c2;
+        cell[3 * p.N + n] = d2;
+    }
+    __syncthreads();
     float* out = p.scalars + rt * p.N * p.S;
     const uint32_t s_magic = magic_of(p.S);
     for (int e = tid; e < p.N * p.S; e += nt) {   // consecutive threads write consecutive floats
@@ -129,12 +167,12 @@ __global__ void k_pro_rows(HsnwPrologue p, const float* z_table, const float* ad
             case 0: value = p.budget_frac; break;
             case 1: value = p.round_frac; break;
             case 2: value = f_ctx; break;
-            case 3: value = util[n]; break;
-            case 4: value = chosen[n]; break;
+            case 3: value = cell[n]; break;
+            case 4: value = cell[p.N + n]; break;
             case 5: value = f_pos; break;
             case 6: value = 1.0f; break;
-            case 7: value = cur[n]; break;
-            default: value = prev[n]; break;
+            case 7: value = cell[2 * p.N + n]; break;
+            default: value = cell[3 * p.N + n]; break;
         }
         out[e] = value;
     }
@@ -182,6 +220,8 @@ extern "C" int hsnw_window_prologue(const HsnwPrologue* p, void* stream_) {
     hsnw_profile_mark(HSNW_K_PROLOGUE, stream);
     k_pro_tables<<<p->V, kTableThreads, shared, stream>>>(*p, z_table, addr_table);
     k_pro_positions<<<p->B, 256, 0, stream>>>(*p, positions, previous);
-    k_pro_rows<<<static_cast<unsigned>(static_cast<int64_t>(p->B) * p->T), 256, 0, stream>>>(*p, z_table, addr_table, positions, previous);
+    if (sizeof(float) * 4 * static_cast<size_t>(p->N) > 48 * 1024)
+        return hsnw_fail(HSNW_E_UNSUPPORTED, "window_prologue: more than 3072 cells");
+    k_pro_rows<<<static_cast<unsigned>(static_cast<int64_t>(p->B) * p->T), 256, sizeof(float) * 4 * p->N, stream>>>(*p, z_table, addr_table, positions, previous);
     return hsnw_check_launch("window_prologue");
 }

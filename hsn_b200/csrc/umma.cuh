@@ -86,7 +86,11 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 // arrival), the same chain issued this way 728 cycles (about 35 a product after a fixed ~250), and
 // M 128 x N 256 products then run at the tensor pipe's own rate (136 cycles each). With this issue
 // rate consecutive products into ONE accumulator are as fast as products spread over several (727
-// cycles either way), so a product's K steps simply accumulate in place.
+// cycles either way), so a product's K steps simply accumulate in place. Inside a kernel whose other
+// warps are busy the issuing warp needs about 70 cycles of instructions per product (the chains are
+// unrolled: as a rolled loop with run-time descriptor arithmetic they cost 50 cycles more each), twice
+// the tensor pipe's time for an N = 16 product: chains that do not depend on one another are therefore
+// issued by different warps (window_rows.cu).
 //
 // D[tmem] (+)= A[smem] * B[smem]^T for one K = 16 step.
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, bool accumulate) {
@@ -156,6 +160,21 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float out[8]) {
         "tcgen05.wait::ld.sync.aligned;\n"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
         : "r"(taddr)
+        : "memory");
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = __uint_as_float(r[i]);
+}
+// Four consecutive fp32 columns at taddr and the four 16 columns further on (an accumulator pair's
+// same four slots), one wait for both loads.
+__device__ __forceinline__ void tmem_ld4x2(uint32_t taddr, float out[8]) {
+    uint32_t r[8];
+    __syncwarp();
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%8];\n"
+        "tcgen05.ld.sync.aligned.32x32b.x4.b32 {%4, %5, %6, %7}, [%9];\n"
+        "tcgen05.wait::ld.sync.aligned;\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+        : "r"(taddr), "r"(taddr + 16u)
         : "memory");
 #pragma unroll
     for (int i = 0; i < 8; ++i) out[i] = __uint_as_float(r[i]);

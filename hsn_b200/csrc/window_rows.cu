@@ -55,7 +55,7 @@ using namespace hsnw;
 
 namespace {
 
-constexpr int kRowThreads = 288;      // + the producer warp
+constexpr int kRowThreads = 384;      // + the producer warp (copies, records) and three issuer warps (tensor-core products)
 constexpr int kMaxStages = 3;         // ring depth (2 when 3 slots do not fit beside a large state)
 constexpr int kMaxK = 8;              // slots (register accumulators per slot)
 constexpr int kMaxMR = 16;            // units
@@ -169,8 +169,18 @@ __host__ __device__ inline RowsSmem rows_smem(const HsnwModel& m, int C, uint32_
             trace_s[(i)] = now;                                                               \
         }                                                                                     \
     } while (0)
+#define UMARK(w, i, m)                                                                        \
+    do {                                                                                      \
+        if ((tid == 0 || tid == 128 || tid == 288) && row == 0 && t == T / 2 && (i) < 6) {    \
+            unsigned long long now;                                                           \
+            const int pin = *reinterpret_cast<volatile int*>(&failed_s);                     \
+            asm volatile("mov.u64 %0, %%clock64;" : "=l"(now) : "r"(pin) : "memory");        \
+            utrace_s[(w)][(i)][(m)] = now;                                                    \
+        }                                                                                     \
+    } while (0)
 #else
 #define RMARK(i) do { } while (0)
+#define UMARK(w, i, m) do { } while (0)
 #endif
 
 // The K + 1 largest of the unique, non-zero 32-bit keys a warp holds (PER a lane, 0 = none), in
@@ -205,12 +215,19 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
     __shared__ int n_units_s;    // units some valid slot runs this position
     __shared__ int hmax_local;   // bits of max |h| over the block's cells after the last position
     __shared__ int failed_s;     // a ring wait ran out
-    __shared__ __align__(8) uint64_t bar_d1[2], bar_d2;   // a chunk's first product (two accumulators in turn); the position's second products
+    __shared__ __align__(8) uint64_t bar_d1[2], bar_d2;   // a unit's first product (two accumulator pairs in turn); the position's second products
+    __shared__ __align__(8) uint64_t bar_sp[2];           // a unit's second product has read its activation buffer
+    __shared__ __align__(8) uint64_t bar_v;               // the position's cell inputs are written (the first products' operand)
+    __shared__ __align__(8) uint64_t bar_act[2];          // a unit's activations are written (the second product's operand, two buffers in turn)
     __shared__ uint32_t tmem_slot;
     __shared__ __align__(8) uint64_t in_bar;   // the next position's inputs (bulk copies by the producer)
     __shared__ uint64_t next_key_s;   // the (K + 1)-th best key of the position's scored order
 #ifdef HSNW_TRACE
     __shared__ unsigned long long trace_s[64];
+    __shared__ unsigned long long utrace_s[3][6][8];
+#ifdef HSNW_TRACE
+    if (threadIdx.x < 144) (&utrace_s[0][0][0])[threadIdx.x] = 0ull;
+#endif
 #endif
 
     cg::cluster_group cl = cg::this_cluster();
@@ -221,6 +238,8 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
     const int T = c.io.T, Nc = c.Nc, Ks = c.Ks, grows = c.gate_rows;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const bool producer = warp == kConsumers / 32;
+    const bool issuer = warp > kConsumers / 32;          // three warps that issue the tensor-core products
+    const int issue_role = warp - kConsumers / 32 - 1;   // 0, 1: a W1 piece each; 2: W2
     const bool tape = c.io.tape_state != 0;
     const bool rec = c.io.rec_c != nullptr;
     const int stride_in = 2 * d + 4;   // a block's line of the front inbox: u part, z_hat part, max |h|
@@ -299,9 +318,14 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
-        mbar_init(&bar_d1[0], 1);
-        mbar_init(&bar_d1[1], 1);
+        mbar_init(&bar_d1[0], 2);   // one arrival per W1 piece's chain
+        mbar_init(&bar_d1[1], 2);
+        mbar_init(&bar_sp[0], 1);
+        mbar_init(&bar_sp[1], 1);
         mbar_init(&bar_d2, 1);
+        mbar_init(&bar_v, 1);
+        mbar_init(&bar_act[0], kConsumers / 32);   // one arrival per compute warp
+        mbar_init(&bar_act[1], kConsumers / 32);
         mbar_init(&in_bar, 1);
         hmax_local = 0;
         n_units_s = 0;
@@ -346,7 +370,9 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t taddr = tmem_slot;
-    uint32_t d1_count0 = 0, d1_count1 = 0, d2_phase = 0;   // completed phases of the accumulators' barriers
+    // completed phases of the per-unit barriers before this position (bar_d1, bar_act and bar_sp complete once per
+    // unit, the even-numbered units of a position on [0], the odd ones on [1]), and of bar_d2
+    uint32_t units_even = 0, units_odd = 0, d2_phase = 0;
     for (int o = tid; o < Nc * (M + d); o += kRowThreads) {
         const int cell = o / (M + d), w = o - cell * (M + d);
         const float* hr = h_s + cell * d;
@@ -401,7 +427,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
         const bool clear = !last && c.io.reset[rt + 1] != 0;
         // ---------------- A: the front MLPs on the block's columns
         RMARK(0);
-        if (!producer) {
+        if (!producer && !issuer) {
             if (t > 0) ring_wait(&in_bar, static_cast<uint32_t>(t - 1) & 1u, c.status, &failed_s);
             if (tid < d) ue[tid] = bf16r(q_s[tid]);
             consumer_sync();
@@ -430,7 +456,6 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
             }
             consumer_sync();
             if (tid == 0) mbar_arrive(&empty[ring_slot(g_use + 1)]);
-            g_use += 2;
             if (tid < 2 * d) {
                 float tot = 0.0f;
                 for (int grp = 0; grp < kFrontCols / d; ++grp) tot += fpart[grp * 2 * d + tid];
@@ -438,6 +463,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
             }
             if (tid == 0) peer(cl, inbox_front, 0)[r * stride_in + 2 * d] = __int_as_float(hmax_local);
         }
+        g_use += 2;
         RMARK(1);
         cl.sync();   // 1
         RMARK(2);
@@ -456,7 +482,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 for (int n = lane; n < Nc; n += 32) c.io.tape_age[(static_cast<int64_t>(row) * (T + 1) + t) * N + cell0 + n] = age_s[n];
         }
         // ---------------- B: u, eps, the scorer on the block's cells
-        if (!producer) {
+        if (!producer && !issuer) {
             if (tid < 2 * d) {
                 float sum = 0.0f;
                 for (int p = 0; p < C; ++p) sum += inbox_front[p * stride_in + tid];
@@ -540,7 +566,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
         uint64_t* keys = cand;
         int* stale_w = reinterpret_cast<int*>(cand + N);     // [8] cells older than age_max, per warp
         int* old_rank = stale_w + 8;                          // [K] the same flag for the K best
-        if (!producer && !c.io.forced) {
+        if (!producer && !issuer && !c.io.forced) {
             int n_old = 0;
             if (c.m.lambda_cost == 0.0f) {
                 // the scores are bf16 values here (rounded logits, no cost term): the low half of
@@ -754,6 +780,82 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 }
                 if (lane == 0) c.io.theta[rt] = S.theta;
             }
+        } else if (issuer) {
+            // The units' two layers on the streamed weights, on the tensor cores. A unit's weights on the
+            // block's 128 hidden columns arrive as three pieces, each a ring slot of its own: W1's rows for
+            // the inputs [0, 2d) and [2d, 4d) (A tiles [128 columns][2d]), then W2 ([d outputs][128
+            // columns]). Each piece has its own issuer warp (a product costs its issuing warp about 70
+            // cycles of instructions, twice the tensor pipe's time for it: one warp issuing a unit's 24
+            // products was the unit's critical path). Warps 0 and 1: D1a, D1b [128 columns, 16 slots] =
+            // a W1 piece x its half of the inputs^T (the epilogue adds the two); the piece's slot is
+            // handed back when its products have run. Warp 2: D2 [d outputs, 16 slots] += W2 x
+            // activations^T, accumulating over the position's units (rows d..127 of D2 come from the
+            // bytes after the tile and are never read). Each product is issued as soon as its operands
+            // are in place: a first-layer chain of unit i waits for the piece and, from the third unit on,
+            // for the epilogue of unit i - 2 (which read the accumulators it overwrites); a second-layer
+            // chain for the unit's activations and its piece.
+            const uint16_t* vop = reinterpret_cast<const uint16_t*>(big);
+            const uint32_t idesc = umma_idesc_bf16(128, 16);
+            constexpr int steps_piece = (2 * d) >> 4;       // K = 16 products of one W1 piece
+            const uint32_t g0 = g_use;
+            auto unit_parity = [&](int i) { return (((i & 1) ? units_odd : units_even) + static_cast<uint32_t>(i >> 1)) & 1u; };
+            // (A slot's barrier tells two consecutive rounds apart, no more: a warp may wait for a slot's
+            // round only if it also consumed, or waited for, the round before. With three slots every piece
+            // kind has a slot and a warp of its own. With two the kinds rotate through the slots, so one
+            // warp issues everything in ring order: first layer, second layer, unit after unit.)
+            auto first_piece = [&](int i, int piece) {
+                UMARK(2, i, 0);
+                if (i >= 2) ring_wait(&bar_act[i & 1], unit_parity(i - 2), c.status, &failed_s);
+                const uint32_t g = g0 + 3 * i + piece, slot = ring_slot(g);
+                ring_wait(&full[slot], ring_round(g) & 1u, c.status, &failed_s);
+                tcgen05_fence_after();
+                UMARK(2, i, 1);
+                const unsigned char* tile = ring + slot * c.slot_bytes;
+                const uint32_t acc = taddr + 32 * (i & 1) + 16 * piece;   // D1a, D1b of the unit's parity
+                if (d == 64)   // (a piece is two 128-byte-swizzled K-blocks of 64 inputs, 128 rows each)
+                    umma_chain_sw128<steps_piece>(acc, umma_desc_sw128(tile), (128 * 128) >> 4,
+                                                  umma_desc(vop + piece * steps_piece * 2 * 16 * 8, 16), umma_kstep(16), idesc, false);
+                else
+                    umma_chain_fixed<steps_piece>(acc, umma_desc(tile, 128), umma_desc(vop + piece * steps_piece * 2 * 16 * 8, 16),
+                                                  idesc, umma_kstep(128), umma_kstep(16), false);
+                umma_commit(&empty[slot]);   // the piece is spent when these products have read it
+                umma_commit(&bar_d1[i & 1]);
+                UMARK(2, i, 2);
+            };
+            auto second_layer = [&](int i) {
+                UMARK(2, i, 3);
+                ring_wait(&bar_act[i & 1], unit_parity(i), c.status, &failed_s);
+                UMARK(2, i, 4);
+                const uint32_t g = g0 + 3 * i + 2, slot = ring_slot(g);
+                ring_wait(&full[slot], ring_round(g) & 1u, c.status, &failed_s);
+                tcgen05_fence_after();
+                UMARK(2, i, 5);
+                const unsigned char* tile = ring + slot * c.slot_bytes;
+                if (d == 64)   // (two K-blocks of 64 hidden columns, d rows each)
+                    umma_chain_sw128<8>(taddr + 256, umma_desc_sw128(tile), (64 * 128) >> 4,
+                                        umma_desc(b2 + (i & 1) * (kActOperand / 2), 16), umma_kstep(16), idesc, i > 0);
+                else
+                    umma_chain_fixed<8>(taddr + 256, umma_desc(tile, d), umma_desc(b2 + (i & 1) * (kActOperand / 2), 16), idesc,
+                                        umma_kstep(d), umma_kstep(16), i > 0);
+                umma_commit(&empty[slot]);
+                umma_commit(&bar_sp[i & 1]);
+                if (i + 1 == n_units) umma_commit(&bar_d2);
+                UMARK(2, i, 6);
+            };
+            if (issue_role < 2) ring_wait(&bar_v, static_cast<uint32_t>(t) & 1u, c.status, &failed_s);
+            if (three) {
+                for (int i = 0; i < n_units; ++i) {
+                    if (issue_role < 2) first_piece(i, issue_role);
+                    else second_layer(i);
+                }
+            } else if (issue_role == 0) {
+                for (int i = 0; i < n_units; ++i) {
+                    first_piece(i, 0);
+                    first_piece(i, 1);
+                    second_layer(i);
+                }
+            }
+            tcgen05_fence_before();
         } else {
             RMARK(24);
             // Every value comes from another block's shared memory (a few hundred cycles each): all the loads
@@ -842,49 +944,18 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 if ((e & 15) >= K) reinterpret_cast<uint4*>(vop)[e] = make_uint4(0u, 0u, 0u, 0u);
             fence_async_smem();   // the operand written above, before the tensor cores read it
             consumer_sync();
+            if (tid == 0) mbar_arrive(&bar_v);   // the issuer warp starts the units' first layers
             RMARK(7);
-            // The units' two layers on the streamed weights, on the tensor cores. A unit's weights on the
-            // block's 128 hidden columns arrive as three pieces, each a ring slot of its own: W1's rows for
-            // the inputs [0, 2d) and [2d, 4d) (A tiles [128 columns][2d]), then W2 ([d outputs][128
-            // columns]). D1 [128 columns, 16 slots] = W1 x inputs^T accumulates over the two pieces, and
-            // each piece's slot is handed back as soon as its products have run; the epilogue adds the
-            // bias, rounds, records, applies the activation for the slots that run the unit (zero for the
-            // others) and writes the bf16 operand of the second product; D2 [d outputs, 16 slots] += W2 x
-            // activations^T accumulates over the position's units (rows d..127 of D2 come from the bytes
-            // after the tile and are never read). Warp 0 issues (as a whole: umma.cuh). All eight warps
-            // read D1: warp w the columns 32 (w % 4) .. and the slots 4 (w / 4) .. 4 (w / 4) + 3; before
-            // the first accumulator is ready they compute the gate's partial sums.
+            // The epilogues of the units' first layers (the issuer warp runs the products): a unit's epilogue
+            // adds the bias, rounds, records, applies the activation for the slots that run the unit (zero
+            // for the others) and writes the bf16 operand of the second product. All eight warps read D1:
+            // warp w the columns 32 (w % 4) .. and the slots 4 (w / 4) .. 4 (w / 4) + 3, and go on to the
+            // next unit without a block barrier (a warp's arrival on the operand's barrier says its part is
+            // written); before the first accumulator is ready they compute the gate's partial sums.
             RMARK(30);
             const int hc = lane + 32 * (warp & 3);            // the thread's hidden column of the block (TMEM lane)
             const int sh = warp >> 2;                         // its half of the slots: 4 sh .. 4 sh + 3
-            const uint32_t idesc = umma_idesc_bf16(128, 16);
-            constexpr int steps_piece = (2 * d) >> 4;       // K = 16 products of one W1 piece
-            const uint32_t g0 = g_use;
             float bias_next = n_units > 0 ? c.m.b1[ulist[0] * H + r * 128 + hc] : 0.0f;   // a unit ahead
-            // a unit's first layer: D1 (tensor memory columns 128 b .. 128 b + 15, b = unit parity)
-            auto first_product = [&](int i) {
-#pragma unroll
-                for (int piece = 0; piece < 2; ++piece) {
-                    const uint32_t g = g0 + 3 * i + piece, slot = ring_slot(g);
-                    ring_wait(&full[slot], ring_round(g) & 1u, c.status, &failed_s);
-                    tcgen05_fence_after();
-                    const unsigned char* tile = ring + slot * c.slot_bytes;
-                    if (d == 64)   // (a piece is two 128-byte-swizzled K-blocks of 64 inputs, 128 rows each)
-                        umma_chain_sw128<steps_piece>(taddr + 128 * (i & 1), umma_desc_sw128(tile), (128 * 128) >> 4,
-                                                      umma_desc(vop + piece * steps_piece * 2 * 16 * 8, 16), umma_kstep(16), idesc,
-                                                      piece > 0);
-                    else
-                        umma_chain_fixed<steps_piece>(taddr + 128 * (i & 1), umma_desc(tile, 128),
-                                                      umma_desc(vop + piece * steps_piece * 2 * 16 * 8, 16), idesc, umma_kstep(128),
-                                                      umma_kstep(16), piece > 0);
-                    umma_commit(&empty[slot]);   // the piece is spent when these products have read it
-                }
-                umma_commit(&bar_d1[i & 1]);
-            };
-            if (warp == 0 && n_units > 0) {
-                first_product(0);
-                RMARK(29);
-            }
             {
                 // the gate's partial sum over the block's input rows (under the first unit's first layer)
                 const int x = tid % d, grp = tid / d, ngrp = kConsumers / d;
@@ -912,26 +983,28 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
             float hid_keep[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             for (int i = 0; i < n_units; ++i) {
                 const unsigned mask = static_cast<unsigned>(umask[i]);
-                // the next unit's first layer runs under this epilogue when the ring holds its two pieces beside
-                // this unit's third (three slots; with two it would wait for a slot that only this unit's
-                // second product frees)
-                if (warp == 0 && i + 1 < n_units && three) first_product(i + 1);
+                UMARK(tid == 0 ? 0 : 1, i, 0);
                 {
                     const float bias = bias_next;
                     if (i + 1 < n_units) bias_next = c.m.b1[ulist[i + 1] * H + r * 128 + hc];
                     uint16_t* b2i = b2 + (i & 1) * (kActOperand / 2);
-                    ring_wait(&bar_d1[i & 1], ((i & 1) ? d1_count1 : d1_count0) & 1u, c.status, &failed_s);
+                    const uint32_t parity = (((i & 1) ? units_odd : units_even) + static_cast<uint32_t>(i >> 1)) & 1u;
+                    // (the buffer's previous tenant, unit i - 2: its second product has read it)
+                    if (i >= 2) ring_wait(&bar_sp[i & 1], parity ^ 1u, c.status, &failed_s);
+                    ring_wait(&bar_d1[i & 1], parity, c.status, &failed_s);
                     tcgen05_fence_after();
                     if (i == 0) RMARK(25);
+                    UMARK(tid == 0 ? 0 : 1, i, 2);
                     float acc[8];
-                    tmem_ld8(tmem_addr(taddr, 32 * (warp & 3), 128 * (i & 1)), acc);
+                    tmem_ld4x2(tmem_addr(taddr, 32 * (warp & 3), 32 * (i & 1) + 4 * sh), acc);   // D1a, D1b: the thread's four slots
+                    UMARK(tid == 0 ? 0 : 1, i, 3);
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         const int k = 4 * sh + q;
                         float a = 0.0f;
                         hid_keep[q] = 0.0f;
                         if (mask & (1u << k)) {
-                            const float hid = bf16r((sh ? acc[4 + q] : acc[q]) + bias);
+                            const float hid = bf16r((acc[q] + acc[4 + q]) + bias);
                             hid_keep[q] = hid;
                             a = gelu_erf(hid);
                         }
@@ -940,10 +1013,11 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                     fence_async_smem();
                     tcgen05_fence_before();
                     if (i == 0) RMARK(26);
+                    UMARK(tid == 0 ? 0 : 1, i, 4);
                 }
-                if (i & 1) ++d1_count1;
-                else ++d1_count0;
-                consumer_sync();   // every epilogue thread's activations are written
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_act[i & 1]);   // this warp's activations are written
+                UMARK(tid == 0 ? 0 : 1, i, 5);
                 if (rec) {
                     // the record of the pre-activations goes out after the barrier: a barrier waits
                     // for the stores its threads have in flight
@@ -952,27 +1026,10 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                     for (int q = 0; q < 4; ++q)
                         if (mask & (1u << (4 * sh + q))) static_cast<uint16_t*>(c.io.rec_hidden)[(rt * K + 4 * sh + q) * H + colg] = bf16_bits(hid_keep[q]);
                 }
-                if (warp == 0) {
-                    const uint32_t g = g0 + 3 * i + 2, slot = ring_slot(g);
-                    ring_wait(&full[slot], ring_round(g) & 1u, c.status, &failed_s);
-                    tcgen05_fence_after();
-                    const unsigned char* tile = ring + slot * c.slot_bytes;
-                    // D2 (columns 256 .. 271) accumulates over the position's units
-                    if (d == 64)   // (two K-blocks of 64 hidden columns, d rows each)
-                        umma_chain_sw128<8>(taddr + 256, umma_desc_sw128(tile), (64 * 128) >> 4,
-                                            umma_desc(b2 + (i & 1) * (kActOperand / 2), 16), umma_kstep(16), idesc, i > 0);
-                    else
-                        umma_chain_fixed<8>(taddr + 256, umma_desc(tile, d), umma_desc(b2 + (i & 1) * (kActOperand / 2), 16), idesc,
-                                            umma_kstep(d), umma_kstep(16), i > 0);
-                    umma_commit(&empty[slot]);
-                    if (i + 1 == n_units) umma_commit(&bar_d2);
-                    if (i + 1 < n_units && !three) first_product(i + 1);
-                }
                 if (i == 0) RMARK(27);
             }
             const int n_chunks = 3 * n_units;
-            consumer_sync();
-            g_use += n_chunks;
+            consumer_sync();   // (the gate's partial sums are written)
             RMARK(8);
             // the block's partial of every slot's second layer from the accumulator, and the gate's
             // partial, to the slots' owners
@@ -999,12 +1056,15 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
             }
             tcgen05_fence_before();
         }
+        g_use += 3 * n_units;
+        units_even += static_cast<uint32_t>((n_units + 1) >> 1);
+        units_odd += static_cast<uint32_t>(n_units >> 1);
         RMARK(9);
         cl.sync();   // 3
         RMARK(10);
 
         // ---------------- E: the update of the block's slots (k = kl C + r)
-        if (!producer) {
+        if (!producer && !issuer) {
             for (int e = tid; e < Ks * d; e += kConsumers) {
                 const int kl = e / d, x = e - kl * d, k = kl * C + r;
                 const bool ok = k < K && cell_of[k] >= 0;
@@ -1110,7 +1170,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 for (int e = lane; e < (Nc * d) >> 2; e += 32) dst[e] = clear ? zero4 : from[e];   // a reset: zeros, whatever the compute warps do to h_s meanwhile
             }
         }
-        if (!producer) {
+        if (!producer && !issuer) {
             // no barrier in this phase unless the next position resets: every part reads what the
             // cluster barrier above published and writes its own data
             if (tid >= 96 && !clear) {
@@ -1166,7 +1226,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
         RMARK(13);
     }
     // the last position's max |h|, and the state the window ends in
-    if (!producer && tid == 0) peer(cl, inbox_front, 0)[r * stride_in + 2 * d] = __int_as_float(hmax_local);
+    if (tid == 0) peer(cl, inbox_front, 0)[r * stride_in + 2 * d] = __int_as_float(hmax_local);
     cl.sync();
     if (producer) {
         const int64_t rp = static_cast<int64_t>(row) * T + T - 1;
@@ -1179,7 +1239,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
         if (tape)
             for (int n = lane; n < Nc; n += 32) c.io.tape_age[(static_cast<int64_t>(row) * (T + 1) + T) * N + cell0 + n] = age_s[n];
     }
-    if (!producer) {
+    if (!producer && !issuer) {
         if (r == 0 && tid == 0) {
             if (c.io.h_max) {
                 int mx = 0;
@@ -1204,6 +1264,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
     __syncthreads();
 #ifdef HSNW_TRACE
     if (row == 0 && tid < 64) reinterpret_cast<unsigned long long*>(c.status + 64)[r * 64 + tid] = trace_s[tid];
+    if (row == 0 && tid < 144) reinterpret_cast<unsigned long long*>(c.status + 64)[256 + r * 144 + tid] = (&utrace_s[0][0][0])[tid];
 #endif
     if (warp == 0) tmem_dealloc(taddr, 512);
 }
