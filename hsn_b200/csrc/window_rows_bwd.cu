@@ -44,7 +44,7 @@ namespace {
 #define BMARK(i) do { } while (0)
 #endif
 
-constexpr int kStagesB = 3;
+constexpr int kRowThreadsB = kConsumers + 96;   // + the producer warp (copies) and two issuer warps (tensor-core products)
 constexpr int kDhidOperand = 2 * 16 * 16 * 8;   // bytes of one
 constexpr int kMaxKB = 8;
 constexpr int kMaxMB = 16;
@@ -75,7 +75,7 @@ __host__ __device__ inline RowsBwdSmem rows_bwd_smem(const HsnwModel& m, int C, 
         o += up16b(bytes);
         return at;
     };
-    L.ring = take(static_cast<size_t>(kStagesB) * slot_bytes + 1024);   // + room to start on a 1024-byte boundary
+    L.ring = take(3 * static_cast<size_t>(slot_bytes) + 1024);   // two slots of each kind (the first kind's are half as large) + room to start on a 1024-byte boundary
     L.A = take(4 * Nc * d);
     L.wout = take(2 * d * d);
     L.vt = take(2 * d * d);
@@ -107,11 +107,14 @@ __host__ __device__ inline RowsBwdSmem rows_bwd_smem(const HsnwModel& m, int C, 
 }
 
 template <int D_>
-__global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
+__global__ void __launch_bounds__(kRowThreadsB, 1) k_rows_bwd(RowsBwdCtx c) {
     extern __shared__ __align__(16) unsigned char dyn[];
-    __shared__ __align__(8) uint64_t full[kStagesB], empty[kStagesB];
+    __shared__ __align__(8) uint64_t full_p[2], empty_p[2], full_q[2], empty_q[2];   // the two rings' slots
     __shared__ int failed_s;
-    __shared__ __align__(8) uint64_t bar_d1[2], bar_d2;
+    __shared__ __align__(8) uint64_t bar_d1[2], bar_d2;   // a unit's first product (two accumulators in turn); the position's second products
+    __shared__ __align__(8) uint64_t bar_act[2];          // a unit's dhid operand is written (two buffers in turn): one arrival per compute warp
+    __shared__ __align__(8) uint64_t bar_sp[2];           // a unit's second product has read its operand buffer
+    __shared__ __align__(8) uint64_t bar_dec;             // the next position's unit lists are in place
     __shared__ uint32_t tmem_slot;
 #ifdef HSNW_TRACE
     __shared__ unsigned long long trace_s[32];   // written to memory when the kernel ends (a store before a barrier delays it)
@@ -124,6 +127,8 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
     const int N = c.m.N, K = c.m.K, M = c.m.M, D = c.m.D, H = c.m.H;
     const int T = c.io.T, Nc = c.Nc, Ks = c.Ks;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bool consumer = warp < kConsumers / 32;
+    const int role = warp - kConsumers / 32;   // 0: copies; 1: the first products; 2: the second products
     const int gcols = two / C;          // the gate's state outputs of this block
     const int cmask = C - 1, cshift = __ffs(C) - 1;   // the cluster size is a power of two
     const int gshift = __ffs(gcols) - 1;              // so is 2d / C (d is 16, 32 or 64)
@@ -273,13 +278,20 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
     };
 
     if (tid == 0) {
-        for (int s = 0; s < kStagesB; ++s) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&full_p[s], 1);
+            mbar_init(&empty_p[s], 1);
+            mbar_init(&full_q[s], 1);
+            mbar_init(&empty_q[s], 1);
         }
         mbar_init(&bar_d1[0], 1);
         mbar_init(&bar_d1[1], 1);
         mbar_init(&bar_d2, 1);
+        mbar_init(&bar_act[0], kConsumers / 32);
+        mbar_init(&bar_act[1], kConsumers / 32);
+        mbar_init(&bar_sp[0], 1);
+        mbar_init(&bar_sp[1], 1);
+        mbar_init(&bar_dec, 1);
         failed_s = 0;
     }
     for (int e = tid; e < d * d; e += kConsumers) {
@@ -309,51 +321,44 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t taddr = tmem_slot;
-    uint32_t d1_count0 = 0, d1_count1 = 0, d2_phase = 0;
-    prefetch(T - 1, tid, kConsumers);
-    decision_load(T - 1, tid);
-    decision_store(T - 1, tid);
+    // completed phases of the per-unit barriers before this position (bar_d1, bar_act and bar_sp complete once per
+    // unit, a position's even-numbered units on [0], the odd ones on [1]), of bar_d2 and of bar_dec
+    uint32_t units_even = 0, units_odd = 0, d2_phase = 0, dec_phase = 0;
+    if (consumer) {
+        prefetch(T - 1, tid, kConsumers);
+        decision_load(T - 1, tid);
+        decision_store(T - 1, tid);
+    }
     __syncthreads();
     if (warp == 0) unit_lists(T - 1);
-    // the chunk stream: thread 0 keeps up to three copies in flight, across positions
-    uint32_t g_issue = 0, g_use = 0;
-    int cur_t = T - 1, cur_i = 0;       // the next chunk to request: position, index in its 2 n_units chunks
-    int ready_t = T - 1;                // decisions are known down to this position
-    auto issue_ahead = [&](bool wait_for_slots) {   // false: request only into slots that are free now
-        while (g_issue < g_use + kStagesB && cur_t >= ready_t && cur_t >= 0) {
-            const int* dc_ = dec_of(cur_t & 1);
-            const int n_chunks = 2 * dc_[o_n];
-            if (cur_i >= n_chunks) {
-                --cur_t;
-                cur_i = 0;
-                continue;
-            }
-            const uint32_t slot = g_issue % kStagesB;
-            if (g_issue >= kStagesB) {
-                const uint32_t parity = ((g_issue / kStagesB) - 1u) & 1u;
-                if (wait_for_slots) {
-                    ring_wait(&empty[slot], parity, c.status, &failed_s);
-                } else {
-                    uint32_t done;
-                    asm volatile(
-                        "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                        : "=r"(done)
-                        : "r"(smem_addr(&empty[slot])), "r"(parity)
-                        : "memory");
-                    if (!done) break;
-                }
-            }
+    __syncthreads();
+    // The stream of weight pieces, two a unit: W2's (the first product's) and W1's state rows (the second's). Each
+    // kind has a ring of two slots and one consumer, its issuer warp (a slot's barrier tells two consecutive rounds
+    // apart, no more: a warp that waited for a slot's round must have seen the round before, which holds when it
+    // consumes every round itself). The producer warp requests the pieces in order of use, across the positions, two
+    // units ahead. Unit number n (counted over the window) uses slot n & 1 of both rings, round n >> 1.
+    uint32_t units_before = 0;          // units of the positions before this one
+    unsigned char* ring_q = ring + 2 * c.w2_bytes;
+    int cur_t = T - 1, cur_i = 0;       // the next piece to request (producer's lane 0): position, index among its 2 n_units pieces
+    // request pieces of position cur_t, whose first unit is number `base`, at most `limit` of them; a request waits
+    // for its slot's previous tenant to be spent
+    auto request = [&](uint32_t base, int limit) {
+        const int* dc_ = dec_of(cur_t & 1);
+        const int n_pieces = 2 * dc_[o_n];
+        for (int n = 0; n < limit && cur_i < n_pieces; ++n) {
+            const uint32_t unit = base + static_cast<uint32_t>(cur_i >> 1), slot = unit & 1u;
+            const bool second = (cur_i & 1) != 0;
+            uint64_t* full = second ? &full_q[slot] : &full_p[slot];
+            if (unit >= 2) ring_wait(second ? &empty_q[slot] : &empty_p[slot], ((unit >> 1) - 1u) & 1u, c.status, &failed_s);
             const int j = dc_[o_ulist + (cur_i >> 1)];
-            const unsigned char* from = bank + (static_cast<size_t>(j) * C + r) * c.bank_bytes + ((cur_i & 1) ? c.w2_bytes : 0u);
-            const uint32_t bytes = (cur_i & 1) ? slot_bytes : c.w2_bytes;
-            mbar_expect_tx(&full[slot], bytes);
-            bulk_g2s(ring + slot * slot_bytes, from, bytes, &full[slot]);
-            ++g_issue;
+            const unsigned char* from = bank + (static_cast<size_t>(j) * C + r) * c.bank_bytes + (second ? c.w2_bytes : 0u);
+            const uint32_t bytes = second ? slot_bytes : c.w2_bytes;
+            mbar_expect_tx(full, bytes);
+            bulk_g2s(second ? ring_q + slot * slot_bytes : ring + slot * c.w2_bytes, from, bytes, full);
             ++cur_i;
         }
     };
-    __syncthreads();
-    if (tid == 0) issue_ahead(true);
+    if (role == 0 && lane == 0) request(0u, 4);
     cl.sync();
 
     const float n_f = static_cast<float>(N);
@@ -368,64 +373,66 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
         const bool cut = c.io.reset[rt] != 0;
         BMARK(0);
         // ---------------- H
-        cp_async_wait_all();   // (the copies of this position's record, requested a position ago by the gate's warps)
-        __syncthreads();
-        if (tid < d) Rs[tid] = R_s[tid] + q[tid];
-        __syncthreads();
-        for (int e = tid; e < Ks * d; e += kConsumers) {
-            const int kl = e / d, x = e - kl * d, k = kl * C + r;
-            if (k >= K) continue;
-            const int n = dc_[k];
-            float dcv = 0.0f, dbv = 0.0f, dz = 0.0f, dgv = 0.0f, yv = 0.0f, sgv = 0.0f;
-            if (n >= 0) {
-                const int no = static_cast<int>(__umulhi(static_cast<uint32_t>(n), nc_magic));
-                float* a = peer(cl, A_s, no) + (n - no * Nc) * d + x;
-                const float carried = *a + rc[(6 * Ks + kl) * d + x];
-                const float share = Rs[x] / n_f;
-                const float g = carried + share;
-                const float cv = rc[(0 * Ks + kl) * d + x], gt = rc[(1 * Ks + kl) * d + x];
-                dcv = gt * g;
-                dbv = (cv - rc[(2 * Ks + kl) * d + x]) * g;
-                *a = (1.0f - gt) * carried - gt * share;
-                dz = cand_w[x] * (dcv * (1.0f - cv * cv));
-                dgv = dbv * gt * (1.0f - gt);
-                yv = rc[(3 * Ks + kl) * d + x];
-                sgv = dgv * (rc[(4 * Ks + kl) * d + x] - gate_b[x]);
+        if (consumer) {
+            cp_async_wait_all();   // (the copies of this position's record, requested a position ago by the gate's warps)
+            consumer_sync();
+            if (tid < d) Rs[tid] = R_s[tid] + q[tid];
+            consumer_sync();
+            for (int e = tid; e < Ks * d; e += kConsumers) {
+                const int kl = e / d, x = e - kl * d, k = kl * C + r;
+                if (k >= K) continue;
+                const int n = dc_[k];
+                float dcv = 0.0f, dbv = 0.0f, dz = 0.0f, dgv = 0.0f, yv = 0.0f, sgv = 0.0f;
+                if (n >= 0) {
+                    const int no = static_cast<int>(__umulhi(static_cast<uint32_t>(n), nc_magic));
+                    float* a = peer(cl, A_s, no) + (n - no * Nc) * d + x;
+                    const float carried = *a + rc[(6 * Ks + kl) * d + x];
+                    const float share = Rs[x] / n_f;
+                    const float g = carried + share;
+                    const float cv = rc[(0 * Ks + kl) * d + x], gt = rc[(1 * Ks + kl) * d + x];
+                    dcv = gt * g;
+                    dbv = (cv - rc[(2 * Ks + kl) * d + x]) * g;
+                    *a = (1.0f - gt) * carried - gt * share;
+                    dz = cand_w[x] * (dcv * (1.0f - cv * cv));
+                    dgv = dbv * gt * (1.0f - gt);
+                    yv = rc[(3 * Ks + kl) * d + x];
+                    sgv = dgv * (rc[(4 * Ks + kl) * d + x] - gate_b[x]);
+                }
+                dcs[e] = dcv;
+                dbs[e] = dbv;
+                dzs[e] = dz;
+                ysv[e] = yv;
+                sgs[e] = sgv;
+                const float dgb = bf16r(dgv);
+                for (int p = 0; p < C; ++p) peer(cl, dg_all, p)[k * d + x] = dgb;
             }
-            dcs[e] = dcv;
-            dbs[e] = dbv;
-            dzs[e] = dz;
-            ysv[e] = yv;
-            sgs[e] = sgv;
-            const float dgb = bf16r(dgv);
-            for (int p = 0; p < C; ++p) peer(cl, dg_all, p)[k * d + x] = dgb;
-        }
-        __syncthreads();
-        // per owned slot, one warp without block barriers: rho, the mean, the gate's inner product,
-        // dy = rho (cand_w dz) - rho^3 y mean(y cand_w dz), then d_unit = dy W_out to every block
-        for (int kl = warp; kl < Ks; kl += kConsumers / 32) {
-            const int k = kl * C + r;
-            float sq = 0.0f, dt = 0.0f, s = 0.0f;
-            for (int x = lane; x < d; x += 32) {
-                const float yv = ysv[kl * d + x];
-                sq += yv * yv;
-                dt += yv * dzs[kl * d + x];
-                s += sgs[kl * d + x];
-            }
-            sq = warp_sum(sq);
-            dt = warp_sum(dt);
-            s = warp_sum(s);
-            const float rr = rsqrtf(sq / static_cast<float>(d) + c.m.cand_eps);
-            const float mean = dt / static_cast<float>(d);
-            if (lane == 0) sig_gate[kl] = s;
-            const bool ok = k < K && dc_[k] >= 0;
-            for (int x = lane; x < d; x += 32)
-                dy[kl * d + x] = ok ? rr * dzs[kl * d + x] - rr * rr * rr * ysv[kl * d + x] * mean : 0.0f;
-            __syncwarp();
-            if (k < K) {
-                for (int i = lane; i < d; i += 32) {
-                    const uint16_t dub = bf16_bits(dot_bf16w(dy + kl * d, 1, wout + i * d, 1, d));
-                    for (int p = 0; p < C; ++p) peer(cl, du_op, p)[((i >> 3) * 16 + k) * 8 + (i & 7)] = dub;
+            consumer_sync();
+            // per owned slot, one warp without block barriers: rho, the mean, the gate's inner product,
+            // dy = rho (cand_w dz) - rho^3 y mean(y cand_w dz), then d_unit = dy W_out to every block
+            for (int kl = warp; kl < Ks; kl += kConsumers / 32) {
+                const int k = kl * C + r;
+                float sq = 0.0f, dt = 0.0f, s = 0.0f;
+                for (int x = lane; x < d; x += 32) {
+                    const float yv = ysv[kl * d + x];
+                    sq += yv * yv;
+                    dt += yv * dzs[kl * d + x];
+                    s += sgs[kl * d + x];
+                }
+                sq = warp_sum(sq);
+                dt = warp_sum(dt);
+                s = warp_sum(s);
+                const float rr = rsqrtf(sq / static_cast<float>(d) + c.m.cand_eps);
+                const float mean = dt / static_cast<float>(d);
+                if (lane == 0) sig_gate[kl] = s;
+                const bool ok = k < K && dc_[k] >= 0;
+                for (int x = lane; x < d; x += 32)
+                    dy[kl * d + x] = ok ? rr * dzs[kl * d + x] - rr * rr * rr * ysv[kl * d + x] * mean : 0.0f;
+                __syncwarp();
+                if (k < K) {
+                    for (int i = lane; i < d; i += 32) {
+                        const uint16_t dub = bf16_bits(dot_bf16w(dy + kl * d, 1, wout + i * d, 1, d));
+                        for (int p = 0; p < C; ++p) peer(cl, du_op, p)[((i >> 3) * 16 + k) * 8 + (i & 7)] = dub;
+                    }
                 }
             }
         }
@@ -441,60 +448,99 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
         // activation's derivative at the recorded pre-activation for the slots that ran the unit (zero for
         // the others), adds to the norm's inner products and writes the bf16 operand of the second product;
         // D2 [2d state inputs, 16 slots] += W1 state part x dhid^T accumulates over the position's units in
-        // tensor memory. Warp 0 issues (as a whole: umma.cuh); all eight warps read D1: warp w the columns
-        // 32 (w % 4) .. and the slots 4 (w / 4) .. 4 (w / 4) + 3.
+        // tensor memory. Each kind of product has an issuer warp of its own (a product costs its issuing warp
+        // about 70 cycles of instructions: one warp that issued a unit's 12 products between its epilogues was
+        // the unit's critical path); the eight compute warps read D1, warp w the columns 32 (w % 4) .. and the
+        // slots 4 (w / 4) .. 4 (w / 4) + 3, and go from unit to unit without a block barrier.
         const int n_units = dc_[o_n];
         const int n_chunks = 2 * n_units;
-        const int hc = lane + 32 * (warp & 3), sh = warp >> 2;
         const uint32_t idesc = umma_idesc_bf16(128, 16);
-        const uint32_t g0 = g_use;
-        float inner[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        tcgen05_fence_after();
-        // a unit's first product: D1 (tensor memory columns 64 b .. 64 b + 15, b = unit parity)
-        auto first_product = [&](int i) {
-            const uint32_t g = g0 + 2 * i, slot = g % kStagesB;
-            ring_wait(&full[slot], (g / kStagesB) & 1u, c.status, &failed_s);
-            const unsigned char* tile = ring + slot * slot_bytes;
-            if (d == 64)
-                umma_chain_sw128<4>(taddr + 64 * (i & 1), umma_desc_sw128(tile), 0, umma_desc(du_op, 16), umma_kstep(16), idesc, false);
-            else
-                umma_chain_fixed<d / 16>(taddr + 64 * (i & 1), umma_desc(tile, 128), umma_desc(du_op, 16), idesc, umma_kstep(128),
-                                         umma_kstep(16), false);
-            umma_commit(&empty[slot]);   // the piece is spent when this product has read it
-            umma_commit(&bar_d1[i & 1]);
-            if (lane == 0) ++g_use;
-        };
-        if (warp == 0 && n_units > 0) first_product(0);
-        {
-            // under the first product, what waits for nothing: the position's dc and db go to memory, the
-            // gate's transposed linear on this block's state outputs, and the next position's record
-            // requests and decision (off the position's critical path)
-            for (int e = tid; e < Ks * d; e += kConsumers) {
-                const int kl = e / d, x = e - kl * d, k = kl * C + r;
-                if (k < K) {
-                    c.io.dc[(rt * K + k) * d + x] = dcs[e];
-                    c.io.db[(rt * K + k) * d + x] = dbs[e];
+        auto unit_parity = [&](int i) { return (((i & 1) ? units_odd : units_even) + static_cast<uint32_t>(i >> 1)) & 1u; };
+        if (role == 0) {
+            if (lane == 0) {
+                if (cur_t == t) request(units_before, 1 << 30);   // the rest of this position's pieces, each as its slot is handed back
+                if (t > 0) {
+                    // the next position's first two units, as soon as its unit lists are in place (their slots' tenants
+                    // are pieces of this position or older: spent before this stage ends)
+                    ring_wait(&bar_dec, dec_phase & 1u, c.status, &failed_s);
+                    cur_t = t - 1;
+                    cur_i = 0;
+                    request(units_before + static_cast<uint32_t>(n_units), 4);
                 }
             }
-            for (int e = tid; e < K * gcols; e += kConsumers) {
-                const int k = e >> gshift, il = e - k * gcols;
-                const float sum = dc_[k] >= 0 ? dot_bf16w(dg_all + k * d, 1, gate + il * d, 1, d) : 0.0f;
-                peer(cl, inbox_g, k & cmask)[(k >> cshift) * two + r * gcols + il] = sum;
+            __syncwarp();
+        } else if (role == 1) {
+            fence_async_smem();
+            tcgen05_fence_after();
+            for (int i = 0; i < n_units; ++i) {
+                // D1: tensor memory columns 64 b .. 64 b + 15, b = unit parity; unit i - 2's epilogue has read them
+                if (i >= 2) ring_wait(&bar_act[i & 1], unit_parity(i - 2), c.status, &failed_s);
+                const uint32_t unit = units_before + static_cast<uint32_t>(i), slot = unit & 1u;
+                ring_wait(&full_p[slot], (unit >> 1) & 1u, c.status, &failed_s);
+                tcgen05_fence_after();
+                const unsigned char* tile = ring + slot * c.w2_bytes;
+                if (d == 64)
+                    umma_chain_sw128<4>(taddr + 64 * (i & 1), umma_desc_sw128(tile), 0, umma_desc(du_op, 16), umma_kstep(16), idesc, false);
+                else
+                    umma_chain_fixed<d / 16>(taddr + 64 * (i & 1), umma_desc(tile, 128), umma_desc(du_op, 16), idesc, umma_kstep(128),
+                                             umma_kstep(16), false);
+                umma_commit(&empty_p[slot]);   // the piece is spent when this product has read it
+                umma_commit(&bar_d1[i & 1]);
             }
-            if (t > 0) {
-                prefetch(t - 1, tid, kConsumers);
-                decision_load(t - 1, tid);
-                decision_store(t - 1, tid);
+            tcgen05_fence_before();
+        } else if (role == 2) {
+            for (int i = 0; i < n_units; ++i) {
+                ring_wait(&bar_act[i & 1], unit_parity(i), c.status, &failed_s);
+                const uint32_t unit = units_before + static_cast<uint32_t>(i), slot = unit & 1u;
+                ring_wait(&full_q[slot], (unit >> 1) & 1u, c.status, &failed_s);
+                tcgen05_fence_after();
+                const unsigned char* tile = ring_q + slot * slot_bytes;
+                // D2 (columns 128 .. 143) accumulates over the position's units
+                if (d == 64)   // (two K-blocks of 64 hidden columns, 2d rows each)
+                    umma_chain_sw128<8>(taddr + 128, umma_desc_sw128(tile), (128 * 128) >> 4,
+                                        umma_desc(b2 + (i & 1) * (kDhidOperand / 2), 16), umma_kstep(16), idesc, i > 0);
+                else
+                    umma_chain_fixed<8>(taddr + 128, umma_desc(tile, two), umma_desc(b2 + (i & 1) * (kDhidOperand / 2), 16), idesc,
+                                        umma_kstep(two), umma_kstep(16), i > 0);
+                umma_commit(&empty_q[slot]);
+                umma_commit(&bar_sp[i & 1]);
+                if (i + 1 == n_units) umma_commit(&bar_d2);
             }
-        }
-        for (int i = 0; i < n_units; ++i) {
-            const int j = dc_[o_ulist + i];
-            const unsigned mask = static_cast<unsigned>(dc_[o_umask + i]);
-            if (warp == 0 && i + 1 < n_units) first_product(i + 1);   // the next unit's first product runs under this epilogue
+            tcgen05_fence_before();
+        } else {
+            const int hc = lane + 32 * (warp & 3), sh = warp >> 2;
+            float inner[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             {
+                // under the first product, what waits for nothing: the position's dc and db go to memory, the
+                // gate's transposed linear on this block's state outputs, and the next position's record
+                // requests and decision (off the position's critical path)
+                for (int e = tid; e < Ks * d; e += kConsumers) {
+                    const int kl = e / d, x = e - kl * d, k = kl * C + r;
+                    if (k < K) {
+                        c.io.dc[(rt * K + k) * d + x] = dcs[e];
+                        c.io.db[(rt * K + k) * d + x] = dbs[e];
+                    }
+                }
+                for (int e = tid; e < K * gcols; e += kConsumers) {
+                    const int k = e >> gshift, il = e - k * gcols;
+                    const float sum = dc_[k] >= 0 ? dot_bf16w(dg_all + k * d, 1, gate + il * d, 1, d) : 0.0f;
+                    peer(cl, inbox_g, k & cmask)[(k >> cshift) * two + r * gcols + il] = sum;
+                }
+                if (t > 0) {
+                    prefetch(t - 1, tid, kConsumers);
+                    decision_load(t - 1, tid);
+                    decision_store(t - 1, tid);
+                }
+            }
+            for (int i = 0; i < n_units; ++i) {
+                const int j = dc_[o_ulist + i];
+                const unsigned mask = static_cast<unsigned>(dc_[o_umask + i]);
                 const float bias = b1s[j * 128 + hc];
                 uint16_t* b2i = b2 + (i & 1) * (kDhidOperand / 2);
-                ring_wait(&bar_d1[i & 1], ((i & 1) ? d1_count1 : d1_count0) & 1u, c.status, &failed_s);
+                const uint32_t parity = unit_parity(i);
+                // (the buffer's previous tenant, unit i - 2: its second product has read it)
+                if (i >= 2) ring_wait(&bar_sp[i & 1], parity ^ 1u, c.status, &failed_s);
+                ring_wait(&bar_d1[i & 1], parity, c.status, &failed_s);
                 tcgen05_fence_after();
                 float acc[8];
                 tmem_ld8(tmem_addr(taddr, 32 * (warp & 3), 64 * (i & 1)), acc);
@@ -511,124 +557,109 @@ __global__ void __launch_bounds__(kConsumers, 1) k_rows_bwd(RowsBwdCtx c) {
                 }
                 fence_async_smem();
                 tcgen05_fence_before();
-            }
-            if (i & 1) ++d1_count1;
-            else ++d1_count0;
-            __syncthreads();   // every thread's part of the operand is written
-            if (warp == 0) {
-                const uint32_t g = g0 + 2 * i + 1, slot = g % kStagesB;
-                ring_wait(&full[slot], (g / kStagesB) & 1u, c.status, &failed_s);
-                tcgen05_fence_after();
-                const unsigned char* tile = ring + slot * slot_bytes;
-                // D2 (columns 128 .. 143) accumulates over the position's units
-                if (d == 64)   // (two K-blocks of 64 hidden columns, 2d rows each)
-                    umma_chain_sw128<8>(taddr + 128, umma_desc_sw128(tile), (128 * 128) >> 4,
-                                        umma_desc(b2 + (i & 1) * (kDhidOperand / 2), 16), umma_kstep(16), idesc, i > 0);
-                else
-                    umma_chain_fixed<8>(taddr + 128, umma_desc(tile, two), umma_desc(b2 + (i & 1) * (kDhidOperand / 2), 16), idesc,
-                                        umma_kstep(two), umma_kstep(16), i > 0);
-                umma_commit(&empty[slot]);
-                if (i + 1 == n_units) umma_commit(&bar_d2);
-                if (lane == 0) {
-                    ++g_use;
-                    issue_ahead(false);   // (a slot whose product was only just issued is taken at the next chance)
-                }
                 __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_act[i & 1]);   // this warp's part of the operand is written
+            }
+            consumer_sync();   // (the next position's decision is stored)
+            BMARK(4);
+            if (warp == 7 && t > 0) {   // (a warp with nothing else to do here)
+                unit_lists(t - 1);
+                if (lane == 0) mbar_arrive(&bar_dec);
+            }
+            // the slots' inner products: every warp's sums, then the four warps of each half in order
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float sum = warp_sum(inner[q]);
+                if (lane == 0) red[warp * 4 + q] = sum;
+            }
+            // the block's partial of dv from the accumulator, to the slots' owners
+            if (warp < 4 && 32 * warp < two) {
+                float acc[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
+                if (n_chunks > 0) {
+                    ring_wait(&bar_d2, d2_phase & 1u, c.status, &failed_s);
+                    tcgen05_fence_after();
+                    tmem_ld8(tmem_addr(taddr, 32 * warp, 128), acc);
+                }
+                const int i = 32 * warp + lane;
+                if (i < two) {
+#pragma unroll
+                    for (int k = 0; k < kMaxKB; ++k)
+                        if (k < K) peer(cl, inbox_dv, k & cmask)[(r * Ks + (k >> cshift)) * two + i] = acc[k];
+                }
+            }
+            tcgen05_fence_before();
+            consumer_sync();
+            if (tid < K) {
+                const int k = tid, half = k >> 2, q = k & 3;
+                const float* part = red + (4 * half) * 4 + q;   // warps 4 half .. 4 half + 3
+                const float sum = (part[0] + part[4]) + (part[8] + part[12]);
+                peer(cl, inbox_sig, k & cmask)[r * Ks + (k >> cshift)] = sum;
             }
         }
-        __syncthreads();
-        if (tid != 0) g_use += n_chunks;
-        BMARK(4);
-        if (warp == 7 && t > 0) unit_lists(t - 1);   // (a warp with nothing else to do here)
-        // the slots' inner products: every warp's sums, then the four warps of each half in order
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const float sum = warp_sum(inner[q]);
-            if (lane == 0) red[warp * 4 + q] = sum;
-        }
-        // the block's partial of dv from the accumulator, to the slots' owners
-        if (warp < 4 && 32 * warp < two) {
-            float acc[8];
-#pragma unroll
-            for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
-            if (n_chunks > 0) {
-                ring_wait(&bar_d2, d2_phase & 1u, c.status, &failed_s);
-                tcgen05_fence_after();
-                tmem_ld8(tmem_addr(taddr, 32 * warp, 128), acc);
-            }
-            const int i = 32 * warp + lane;
-            if (i < two) {
-#pragma unroll
-                for (int k = 0; k < kMaxKB; ++k)
-                    if (k < K) peer(cl, inbox_dv, k & cmask)[(r * Ks + (k >> cshift)) * two + i] = acc[k];
-            }
-        }
+        units_before += static_cast<uint32_t>(n_units);
+        units_even += static_cast<uint32_t>((n_units + 1) >> 1);
+        units_odd += static_cast<uint32_t>(n_units >> 1);
         if (n_chunks > 0) ++d2_phase;
-        tcgen05_fence_before();
-        __syncthreads();
-        if (tid == 0) {   // the next position's decision is in place: its chunks may be requested
-            if (t > 0) ready_t = t - 1;
-            issue_ahead(true);
-        }
-        if (tid < K) {
-            const int k = tid, half = k >> 2, q = k & 3;
-            const float* part = red + (4 * half) * 4 + q;   // warps 4 half .. 4 half + 3
-            const float sum = (part[0] + part[4]) + (part[8] + part[12]);
-            peer(cl, inbox_sig, k & cmask)[r * Ks + (k >> cshift)] = sum;
-        }
+        if (t > 0) ++dec_phase;
         BMARK(5);
         cl.sync();   // 2
         BMARK(6);
         // ---------------- T1: the owners' slots
-        if (tid < Ks) {
-            const int kl = tid;
-            float sigma = sig_gate[kl];
-            for (int p = 0; p < C; ++p) sigma += inbox_sig[p * Ks + kl];
-            const float rm = rc[7 * Ks * d + kl];
-            back[kl] = rm * rm / static_cast<float>(4 * d) * sigma;
-        }
-        __syncthreads();
-        for (int e = tid; e < Ks * two; e += kConsumers) {
-            const int kl = e / two, i = e - kl * two, k = kl * C + r;
-            float out = 0.0f;
-            if (k < K && dc_[k] >= 0) {
-                float sum = 0.0f;
-                for (int p = 0; p < C; ++p) sum += inbox_dv[(p * Ks + kl) * two + i];
-                sum += inbox_g[kl * two + i];
-                const float state = i < d ? rc[(2 * Ks + kl) * d + i] : rc[(5 * Ks + kl) * d + i - d];
-                out = rc[7 * Ks * d + kl] * (norm_w[i] * sum) - back[kl] * state;
+        if (consumer) {
+            if (tid < Ks) {
+                const int kl = tid;
+                float sigma = sig_gate[kl];
+                for (int p = 0; p < C; ++p) sigma += inbox_sig[p * Ks + kl];
+                const float rm = rc[7 * Ks * d + kl];
+                back[kl] = rm * rm / static_cast<float>(4 * d) * sigma;
             }
-            ds[e] = out;
-        }
-        __syncthreads();
-        for (int e = tid; e < Ks * d; e += kConsumers) {
-            const int kl = e / d, i = e - kl * d, k = kl * C + r;
-            if (k >= K) continue;
-            const float dvm = dot_bf16w(ds + kl * two + d, 1, vt + i * d, 1, d), own_ds = ds[kl * two + i];
-            for (int p = 0; p < C; ++p) {
-                peer(cl, dvm_all, p)[k * d + i] = dvm;
-                peer(cl, ds_all, p)[k * d + i] = own_ds;
+            consumer_sync();
+            for (int e = tid; e < Ks * two; e += kConsumers) {
+                const int kl = e / two, i = e - kl * two, k = kl * C + r;
+                float out = 0.0f;
+                if (k < K && dc_[k] >= 0) {
+                    float sum = 0.0f;
+                    for (int p = 0; p < C; ++p) sum += inbox_dv[(p * Ks + kl) * two + i];
+                    sum += inbox_g[kl * two + i];
+                    const float state = i < d ? rc[(2 * Ks + kl) * d + i] : rc[(5 * Ks + kl) * d + i - d];
+                    out = rc[7 * Ks * d + kl] * (norm_w[i] * sum) - back[kl] * state;
+                }
+                ds[e] = out;
+            }
+            consumer_sync();
+            for (int e = tid; e < Ks * d; e += kConsumers) {
+                const int kl = e / d, i = e - kl * d, k = kl * C + r;
+                if (k >= K) continue;
+                const float dvm = dot_bf16w(ds + kl * two + d, 1, vt + i * d, 1, d), own_ds = ds[kl * two + i];
+                for (int p = 0; p < C; ++p) {
+                    peer(cl, dvm_all, p)[k * d + i] = dvm;
+                    peer(cl, ds_all, p)[k * d + i] = own_ds;
+                }
             }
         }
         BMARK(7);
         cl.sync();   // 3
         BMARK(8);
-        // ---------------- T2: this block's cells; thread (x, g) takes the targets n = g (mod groups)
-        {
-            const int x = tid % d, g = tid / d, groups = kConsumers / d;
-            const int n_own = dc_[o_own_n];
-            for (int e = 0; e < n_own; ++e) {
-                const int u = dc_[o_own + e];
-                const int n = u < K ? dc_[u] : dc_[o_tgt + u - K];
-                if ((n & (groups - 1)) != g) continue;   // groups is a power of two
-                const float add = u < K ? ds_all[u * d + x] : ew[u - K] * dvm_all[div_D(max(u - K, 0)) * d + x];
-                A_s[(n - cell0) * d + x] += add;
+        if (consumer) {
+            // ---------------- T2: this block's cells; thread (x, g) takes the targets n = g (mod groups)
+            {
+                const int x = tid % d, g = tid / d, groups = kConsumers / d;
+                const int n_own = dc_[o_own_n];
+                for (int e = 0; e < n_own; ++e) {
+                    const int u = dc_[o_own + e];
+                    const int n = u < K ? dc_[u] : dc_[o_tgt + u - K];
+                    if ((n & (groups - 1)) != g) continue;   // groups is a power of two
+                    const float add = u < K ? ds_all[u * d + x] : ew[u - K] * dvm_all[div_D(max(u - K, 0)) * d + x];
+                    A_s[(n - cell0) * d + x] += add;
+                }
+                if (tid < d) R_s[tid] = cut ? 0.0f : Rs[tid] + q[d + tid];
             }
-            if (tid < d) R_s[tid] = cut ? 0.0f : Rs[tid] + q[d + tid];
-        }
-        if (cut) {
-            __syncthreads();
-            for (int e = tid; e < Nc * d; e += kConsumers) A_s[e] = 0.0f;
+            if (cut) {
+                consumer_sync();
+                for (int e = tid; e < Nc * d; e += kConsumers) A_s[e] = 0.0f;
+            }
         }
         BMARK(9);
         cl.sync();   // 4
@@ -679,7 +710,7 @@ int hsnw_rows_backward(const HsnwModel* model, const HsnwBackward* io, int* stat
         ? reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(io->scratch) + 256) : nullptr;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(io->B) * c.C, 1, 1);
-    cfg.blockDim = dim3(kConsumers, 1, 1);
+    cfg.blockDim = dim3(kRowThreadsB, 1, 1);
     cfg.dynamicSmemBytes = L.total;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
