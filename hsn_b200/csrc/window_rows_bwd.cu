@@ -44,7 +44,7 @@ namespace {
 #define BMARK(i) do { } while (0)
 #endif
 
-constexpr int kRowThreadsB = kConsumers + 96;   // + the producer warp (copies) and two issuer warps (tensor-core products)
+constexpr int kRowThreadsB = kConsumers + 128;   // + the producer warp (copies), two issuer warps (tensor-core products), the decision warp
 constexpr int kDhidOperand = 2 * 16 * 16 * 8;   // bytes of one
 constexpr int kMaxKB = 8;
 constexpr int kMaxMB = 16;
@@ -128,7 +128,7 @@ __global__ void __launch_bounds__(kRowThreadsB, 1) k_rows_bwd(RowsBwdCtx c) {
     const int T = c.io.T, Nc = c.Nc, Ks = c.Ks;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const bool consumer = warp < kConsumers / 32;
-    const int role = warp - kConsumers / 32;   // 0: copies; 1: the first products; 2: the second products
+    const int role = warp - kConsumers / 32;   // 0: copies; 1: the first products; 2: the second products; 3: the next position's decision
     const int gcols = two / C;          // the gate's state outputs of this block
     const int cmask = C - 1, cshift = __ffs(C) - 1;   // the cluster size is a power of two
     const int gshift = __ffs(gcols) - 1;              // so is 2d / C (d is 16, 32 or 64)
@@ -372,6 +372,18 @@ __global__ void __launch_bounds__(kRowThreadsB, 1) k_rows_bwd(RowsBwdCtx c) {
         const float* ew = reinterpret_cast<const float*>(dc_) + o_ew;
         const bool cut = c.io.reset[rt] != 0;
         BMARK(0);
+        if (role == 3 && t > 0) {
+            // The next position's decision block (recorded: it depends on nothing this sweep computes), a position
+            // ahead and off every critical path: cells, units, edges and rms from memory, then the unit lists; the
+            // producer warp requests that position's first pieces when this is in place.
+            for (int pass = 0; pass < 4; ++pass) {
+                decision_load(t - 1, lane + 32 * pass);
+                decision_store(t - 1, lane + 32 * pass);
+            }
+            __syncwarp();
+            unit_lists(t - 1);
+            if (lane == 0) mbar_arrive(&bar_dec);
+        }
         // ---------------- H
         if (consumer) {
             cp_async_wait_all();   // (the copies of this position's record, requested a position ago by the gate's warps)
@@ -507,13 +519,13 @@ __global__ void __launch_bounds__(kRowThreadsB, 1) k_rows_bwd(RowsBwdCtx c) {
                 if (i + 1 == n_units) umma_commit(&bar_d2);
             }
             tcgen05_fence_before();
-        } else {
+        } else if (consumer) {
             const int hc = lane + 32 * (warp & 3), sh = warp >> 2;
             float inner[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             {
                 // under the first product, what waits for nothing: the position's dc and db go to memory, the
                 // gate's transposed linear on this block's state outputs, and the next position's record
-                // requests and decision (off the position's critical path)
+                // requests (off the position's critical path)
                 for (int e = tid; e < Ks * d; e += kConsumers) {
                     const int kl = e / d, x = e - kl * d, k = kl * C + r;
                     if (k < K) {
@@ -526,11 +538,7 @@ __global__ void __launch_bounds__(kRowThreadsB, 1) k_rows_bwd(RowsBwdCtx c) {
                     const float sum = dc_[k] >= 0 ? dot_bf16w(dg_all + k * d, 1, gate + il * d, 1, d) : 0.0f;
                     peer(cl, inbox_g, k & cmask)[(k >> cshift) * two + r * gcols + il] = sum;
                 }
-                if (t > 0) {
-                    prefetch(t - 1, tid, kConsumers);
-                    decision_load(t - 1, tid);
-                    decision_store(t - 1, tid);
-                }
+                if (t > 0) prefetch(t - 1, tid, kConsumers);
             }
             for (int i = 0; i < n_units; ++i) {
                 const int j = dc_[o_ulist + i];
@@ -560,12 +568,7 @@ __global__ void __launch_bounds__(kRowThreadsB, 1) k_rows_bwd(RowsBwdCtx c) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bar_act[i & 1]);   // this warp's part of the operand is written
             }
-            consumer_sync();   // (the next position's decision is stored)
             BMARK(4);
-            if (warp == 7 && t > 0) {   // (a warp with nothing else to do here)
-                unit_lists(t - 1);
-                if (lane == 0) mbar_arrive(&bar_dec);
-            }
             // the slots' inner products: every warp's sums, then the four warps of each half in order
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
@@ -603,6 +606,14 @@ __global__ void __launch_bounds__(kRowThreadsB, 1) k_rows_bwd(RowsBwdCtx c) {
         units_odd += static_cast<uint32_t>(n_units >> 1);
         if (n_chunks > 0) ++d2_phase;
         if (t > 0) ++dec_phase;
+#ifdef HSNW_TRACE
+        if (!consumer && lane == 0 && row == 0 && t == T / 2) {
+            unsigned long long now;
+            const int pin = *reinterpret_cast<volatile int*>(&failed_s);
+            asm volatile("mov.u64 %0, %%clock64;" : "=l"(now) : "r"(pin) : "memory");
+            trace_s[16 + role] = now;   // when the producer and the issuers reach the barrier
+        }
+#endif
         BMARK(5);
         cl.sync();   // 2
         BMARK(6);
