@@ -1059,6 +1059,14 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
         g_use += 3 * n_units;
         units_even += static_cast<uint32_t>((n_units + 1) >> 1);
         units_odd += static_cast<uint32_t>(n_units >> 1);
+#ifdef HSNW_TRACE
+        if (warp >= 8 && lane == 0 && row == 0 && t == T / 2) {
+            unsigned long long now;
+            const int pin = *reinterpret_cast<volatile int*>(&failed_s);
+            asm volatile("mov.u64 %0, %%clock64;" : "=l"(now) : "r"(pin) : "memory");
+            trace_s[58 + warp - 8] = now;   // when the producer and the issuers reach the barrier
+        }
+#endif
         RMARK(9);
         cl.sync();   // 3
         RMARK(10);
@@ -1185,6 +1193,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                     else peer(cl, vh_s, owner)[cc * d + (w - M)] = bf16_bits(dot_bf16w(hr, 1, vt + (w - M), d, d));
                 }
             }
+            RMARK(31);
             for (int x = tid; x < d; x += kConsumers) {
                 float sum = 0.0f;
                 for (int k = 0; k < K; ++k) sum += inbox_delta[k * d + x];   // slot order
@@ -1199,12 +1208,14 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                     if (cell_of[k] < 0) c.io.h_sel[(rt * K + k) * d + x] = h_s[x];
                 }
             }
+            RMARK(34);
             {
                 int top = 0;
                 for (int n = tid; n < Nc; n += kConsumers) top = max(top, cmax_s[n]);
                 for (int w = 16; w > 0; w >>= 1) top = max(top, __shfl_xor_sync(0xffffffffu, top, w));
                 if (lane == 0 && top > 0) atomicMax(&hmax_local, top);   // a maximum: any order gives the same bits
             }
+            RMARK(35);
             for (int n = tid; n < Nc; n += kConsumers) {
                 int64_t a = age_s[n] + 1;
                 for (int k = 0; k < K; ++k)

@@ -469,8 +469,13 @@ __global__ void __launch_bounds__(kRowThreadsB, 1) k_rows_bwd(RowsBwdCtx c) {
         const uint32_t idesc = umma_idesc_bf16(128, 16);
         auto unit_parity = [&](int i) { return (((i & 1) ? units_odd : units_even) + static_cast<uint32_t>(i >> 1)) & 1u; };
         if (role == 0) {
+            if (lane == 0 && cur_t == t) request(units_before, 1 << 30);   // the rest of this position's pieces, each as its slot is handed back
+            __syncwarp();
+            // This warp arrives at the stage's cluster barrier now and waits for it after the next position's
+            // first requests: the last of them waits for this position's last product, and the other warps
+            // should not wait for this one on top of that.
+            cl.barrier_arrive();
             if (lane == 0) {
-                if (cur_t == t) request(units_before, 1 << 30);   // the rest of this position's pieces, each as its slot is handed back
                 if (t > 0) {
                     // the next position's first two units, as soon as its unit lists are in place (their slots' tenants
                     // are pieces of this position or older: spent before this stage ends)
@@ -615,7 +620,8 @@ __global__ void __launch_bounds__(kRowThreadsB, 1) k_rows_bwd(RowsBwdCtx c) {
         }
 #endif
         BMARK(5);
-        cl.sync();   // 2
+        if (role == 0) cl.barrier_wait();   // 2 (the producer warp arrived above)
+        else cl.sync();
         BMARK(6);
         // ---------------- T1: the owners' slots
         if (consumer) {
