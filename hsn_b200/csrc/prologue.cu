@@ -127,6 +127,8 @@ __global__ void __launch_bounds__(256) k_pro_positions(HsnwPrologue p, int64_t* 
     }
 }
 
+constexpr int kProTile = 1024;   // cells of a row staged in shared memory at a time (36 KB of scalars)
+
 // One block per (row, position): the gathers and the scalars of every cell.
 __global__ void k_pro_rows(HsnwPrologue p, const float* z_table, const float* addr_table, const int64_t* positions,
                            const int32_t* previous) {
@@ -146,35 +148,40 @@ __global__ void k_pro_rows(HsnwPrologue p, const float* z_table, const float* ad
     const float* chosen = p.ema_selected + (p.ema_per_row ? static_cast<int64_t>(b) * p.N : 0);
     const float* cur = addr_table ? addr_table + static_cast<int64_t>(token) * p.N : nullptr;
     const float* prev = addr_table ? addr_table + static_cast<int64_t>(previous[rt]) * p.N : nullptr;
-    // the per-cell values first (four loads a cell, all in flight), then the writes from shared memory
+    // A cell's S scalars by the cell's thread into shared memory (one control flow for every lane: a thread per
+    // output element took a nine-way divergent branch per element and made the kernel instruction bound), then the
+    // row's N S floats to memory as 16-byte stores.
     extern __shared__ __align__(16) unsigned char dyn[];
-    float* cell = reinterpret_cast<float*>(dyn);   // [4][N]: utility, selected, a_cur, a_prev
-    for (int n = tid; n < p.N; n += nt) {
-        const float a = util[n], b2 = chosen[n];
-        const float c2 = cur ? cur[n] : 0.0f, d2 = prev ? prev[n] : 0.0f;
-        cell[n] = a;
-        cell[p.N + n] = b2;
-        cell[2 * p.N + n] = c2;
-        cell[3 * p.N + n] = d2;
-    }
-    __syncthreads();
+    float* row_s = reinterpret_cast<float*>(dyn);   // [kProTile][S]: a tile of the row's cells
     float* out = p.scalars + rt * p.N * p.S;
-    const uint32_t s_magic = magic_of(p.S);
-    for (int e = tid; e < p.N * p.S; e += nt) {   // consecutive threads write consecutive floats
-        const int n = div_magic(e, s_magic), s = e - n * p.S;
-        float value;
-        switch (s) {
-            case 0: value = p.budget_frac; break;
-            case 1: value = p.round_frac; break;
-            case 2: value = f_ctx; break;
-            case 3: value = cell[n]; break;
-            case 4: value = cell[p.N + n]; break;
-            case 5: value = f_pos; break;
-            case 6: value = 1.0f; break;
-            case 7: value = cell[2 * p.N + n]; break;
-            default: value = cell[3 * p.N + n]; break;
+    const bool wide = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+    for (int n0 = 0; n0 < p.N; n0 += kProTile) {
+        const int cells = min(kProTile, p.N - n0);
+        for (int i = tid; i < cells; i += nt) {
+            const int n = n0 + i;
+            float v[9];
+            v[0] = p.budget_frac;
+            v[1] = p.round_frac;
+            v[2] = f_ctx;
+            v[3] = util[n];
+            v[4] = chosen[n];
+            v[5] = f_pos;
+            v[6] = 1.0f;
+            v[7] = cur ? cur[n] : 0.0f;
+            v[8] = prev ? prev[n] : 0.0f;
+#pragma unroll
+            for (int s = 0; s < 9; ++s)
+                if (s < p.S) row_s[i * p.S + s] = v[s];
         }
-        out[e] = value;
+        __syncthreads();
+        const int total = cells * p.S;
+        float* to = out + static_cast<int64_t>(n0) * p.S;   // (kProTile S floats are a multiple of 16 bytes)
+        if (wide && (total & 3) == 0) {
+            for (int e = tid; e < total >> 2; e += nt) reinterpret_cast<float4*>(to)[e] = reinterpret_cast<const float4*>(row_s)[e];
+        } else {
+            for (int e = tid; e < total; e += nt) to[e] = row_s[e];
+        }
+        __syncthreads();
     }
 }
 
@@ -220,8 +227,7 @@ extern "C" int hsnw_window_prologue(const HsnwPrologue* p, void* stream_) {
     hsnw_profile_mark(HSNW_K_PROLOGUE, stream);
     k_pro_tables<<<p->V, kTableThreads, shared, stream>>>(*p, z_table, addr_table);
     k_pro_positions<<<p->B, 256, 0, stream>>>(*p, positions, previous);
-    if (sizeof(float) * 4 * static_cast<size_t>(p->N) > 48 * 1024)
-        return hsnw_fail(HSNW_E_UNSUPPORTED, "window_prologue: more than 3072 cells");
-    k_pro_rows<<<static_cast<unsigned>(static_cast<int64_t>(p->B) * p->T), 256, sizeof(float) * 4 * p->N, stream>>>(*p, z_table, addr_table, positions, previous);
+    const size_t row_bytes = sizeof(float) * static_cast<size_t>(p->N < kProTile ? p->N : kProTile) * p->S;
+    k_pro_rows<<<static_cast<unsigned>(static_cast<int64_t>(p->B) * p->T), 256, row_bytes, stream>>>(*p, z_table, addr_table, positions, previous);
     return hsnw_check_launch("window_prologue");
 }

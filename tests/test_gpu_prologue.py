@@ -74,3 +74,25 @@ def test_prologue_equals_the_oracle_at_the_reference_shape(position: str) -> Non
     assert again["scalars"].data_ptr() == got["scalars"].data_ptr()
     with pytest.raises(ValueError):
         window_prologue(pro, dev(tokens[:4]), dev(ctx_ids[:4]), dev(reset[:4]), dev(pos0[:4]))  # per-row averages of 8 rows
+
+
+def test_prologue_with_more_cells_than_one_staging_tile() -> None:
+    """N 2304: the scalars of a row leave in tiles of 1024 cells, the last one of 256 (the scaling
+    configuration has 4096 cells)."""
+    from hsn_b200.window import window_prologue
+
+    rng = np.random.default_rng(9)
+    B, T, N, d, H, V = 2, 5, 2304, 16, 32, 256
+    f = lambda *s: (rng.standard_normal(s) * 0.3).astype(np.float32)  # noqa: E731
+    P = dict(byte_emb=f(V, d), enc_w1=f(H, d), enc_b1=f(H), enc_w2=f(d, H), enc_b2=f(d), ctx_emb=f(16, d),
+             byte_codes=f(V, d), cell_addresses=f(N, d), ema_utility=rng.random(N).astype(np.float32),
+             ema_selected=rng.random(N).astype(np.float32))  # fmt: skip
+    numbers = (0.5, 0.25, 16.0, 8.0)
+    tokens, ctx_ids = rng.integers(0, V, (B, T)), rng.integers(0, 16, (B, T))
+    reset = rng.random((B, T)) < 0.3
+    pos0 = rng.integers(0, 20, B)
+    want = O.window_prologue(dict(P, budget_frac=numbers[0], round_frac=numbers[1], n_context=numbers[2], unroll=numbers[3],
+                                  position="wrap"), tokens, ctx_ids, reset, pos0, None)  # fmt: skip
+    got = window_prologue(_build(P, "fp32", numbers, "wrap"), dev(tokens), dev(ctx_ids), dev(reset), dev(pos0))
+    np.testing.assert_allclose(got["scalars"].cpu().numpy(), want["scalars"], rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(got["z"].cpu().numpy(), want["z"], rtol=1e-5, atol=1e-5 * float(np.abs(want["z"]).max()))
