@@ -47,7 +47,10 @@ CONFIGS = {
     "c5s": dict(B=512, T=32, N=1024, d=64, K=8, H=512, M=8, D=4, S=9, p=1 / 4096, prod="bf16", resident=True,
                 forward_only=True, stream=True),
 }
+# the trainer's AdamW pass (not the headline): forty tensors of a few million elements, one launch a step
+CONFIGS["adamw"] = dict(tensors=40, elements=4_194_304 + 1031, trainer=True)
 WORKLOADS = {
+    "adamw": "the trainer's AdamW step over 40 fp32 tensors of 4,195,335 elements (671 MB of parameters), one launch",
     "c1": "tiny gradcheck-shape window B2 T8 N16 d32 K2 H32",
     "c2": "reference-shape window fwd+bwd: B32 T256 N256 d64 K8 H512 M8 D4, bf16 products, fp32 state, resets p=1/1024",
     "c3": "split-window chain: B64, 4 chained windows of T512 (state carried forward, its cotangent back), N512 d64 K8 H512, bf16 products",
@@ -679,6 +682,93 @@ def run_taped(args, c: dict, name: str) -> None:
         dist.destroy_process_group()
 
 
+def run_trainer(args, c: dict, name: str) -> None:
+    """One AdamW step a "step": `hsn_tr_adamw` over the configuration's tensors in one launch (parameters and
+    moments far larger than L2), with torch's multi-tensor sequence it replaces timed beside it on the same
+    device. 28 algorithmic bytes an element: p, g, m, v read, p, m, v written."""
+    import torch
+
+    from hsn_b200.kernels import trainer
+
+    if args.impl == "reference":   # the reference's CPU path: torch's multi-tensor operations on the host cores
+        n, elements = 8, c["elements"]
+        gen = torch.Generator().manual_seed(0)
+        ps, gs = ([torch.randn(elements, generator=gen) * 0.1 for _ in range(n)] for _ in range(2))
+        ms, vs = [torch.zeros_like(p) for p in ps], [torch.zeros_like(p) for p in ps]
+        times = []
+        for step in range(1, args.warmup + args.steps + 1):
+            t0 = time.perf_counter()
+            _torch_adamw(torch, ps, gs, ms, vs, step)
+            if step > args.warmup:
+                times.append(time.perf_counter() - t0)
+        value = n * elements / float(np.mean(times))
+        print(json.dumps({
+            "impl": "reference", "metric": "trainer AdamW elements/s", "value": value, "unit": "elements/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * float(np.mean(times)), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOADS[name] + f" [sample: {n} of the tensors a step]"},
+            "cpu_baseline": {"value": value, "unit": "elements/s", "cores": torch.get_num_threads(), "kind": "reference",
+                             "sample": f"{n} tensors a step, torch multi-tensor operations on the host"},
+            "e2e": {"value": value, "unit": "elements/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))  # fmt: skip
+        return
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    n, elements = c["tensors"], c["elements"]
+    gen = torch.Generator(device=dev).manual_seed(0)
+    make = lambda scale: [torch.randn(elements, generator=gen, device=dev) * scale for _ in range(n)]  # noqa: E731
+    ps, gs = make(0.1), make(1.0)
+    ms, vs = [torch.zeros_like(p) for p in ps], [torch.zeros_like(p) for p in ps]
+    hyper = dict(lr=2.5e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.01)
+    clock_lines: list = []
+    stop = threading.Event()
+    sampler = threading.Thread(target=sample_clocks, args=(stop, clock_lines), daemon=True)
+    sampler.start()
+    count = [0]
+
+    def ours(i):
+        count[0] += 1
+        if not trainer.adamw(ps, gs, ms, vs, step=count[0], **hyper):
+            raise RuntimeError("the trainer kernels declined fp32 CUDA tensors")
+
+    for i in range(args.warmup):
+        ours(i)
+    torch.cuda.synchronize()
+    ms_total, each = timed_steps(ours, args.steps, torch.cuda.synchronize)
+    ps2, ms2, vs2 = [p.clone() for p in ps], [m.clone() for m in ms], [v.clone() for v in vs]
+    for i in range(3):
+        _torch_adamw(torch, ps2, gs, ms2, vs2, i + 1)
+    torch.cuda.synchronize()
+    torch_total, _ = timed_steps(lambda i: _torch_adamw(torch, ps2, gs, ms2, vs2, i + 4), max(3, args.steps // 4), torch.cuda.synchronize)
+    stop.set()
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    step_ms = ms_total / args.steps
+    achieved = 28.0 * n * elements / (step_ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "trainer AdamW elements/s", "value": n * elements / (step_ms * 1e-3), "unit": "elements/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "step_ms": spread(each), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOADS[name], "l2": "parameters, gradients and moments larger than L2",
+                   "torch_multi_tensor_ms_per_step": torch_total / max(3, args.steps // 4)},
+        "gpu_launches": args.steps,
+        "roofline": {"bound": "hbm", "kernel": "hsn_tr_adamw", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": None, "peak_source": "measured" if peaks else "fallback",
+                     "how": "28 bytes an element (p, g, m, v read; p, m, v written) / the step's mean event time"},
+        "clocks": clocks_summary(clock_lines, 0)}))  # fmt: skip
+
+
+def _torch_adamw(torch, ps, gs, ms, vs, step, lr=2.5e-3, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.01) -> None:
+    """The multi-tensor sequence `hsn_tr_adamw` replaces (reference python/hsn/train/lazy_adam.py:462-486)."""
+    torch._foreach_mul_(ps, 1 - lr * wd)
+    torch._foreach_lerp_(ms, gs, 1 - beta1)
+    torch._foreach_mul_(vs, beta2)
+    torch._foreach_addcmul_(vs, gs, gs, value=1 - beta2)
+    den = torch._foreach_sqrt(vs)
+    torch._foreach_div_(den, (1 - beta2**step) ** 0.5)
+    torch._foreach_add_(den, eps)
+    torch._foreach_addcdiv_(ps, ms, den, value=-(lr / (1 - beta1**step)))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -696,7 +786,11 @@ def main() -> None:
     c = dict(CONFIGS[args.config])
     if args.positions > 0:
         c["T"] = args.positions
-    if args.impl == "reference":
+    if c.get("trainer"):
+        if args.steps == 100:
+            args.steps = 20 if args.impl == "ours" else 5
+        run_trainer(args, c, args.config)
+    elif args.impl == "reference":
         if args.steps == 100:   # the default is sized for the GPU arm
             args.steps = 20
         run_reference(args, c, args.config)

@@ -28,6 +28,23 @@ class HsnWinArgs(Structure):
     ]
 
 
+HSN_TR_ROWS, HSN_TR_TENSORS, HSN_TR_INTS, HSN_TR_FLOATS, HSN_TR_DOUBLES, HSN_TR_COEFS, HSN_TR_UNITS = 4, 40, 8, 8, 2, 6, 64
+
+
+class HsnTrainArgs(Structure):
+    """The launch descriptor of the trainer kernels (``include/hsn_trainer_b200.h``; 3760 bytes, the
+    reference's ``kernels/include/hsn_trainer_launch.h``)."""
+
+    _fields_ = [
+        ("p", (c_void_p * HSN_TR_TENSORS) * HSN_TR_ROWS),
+        ("end", c_int64 * HSN_TR_TENSORS),
+        ("g", c_double * HSN_TR_DOUBLES),
+        ("i", c_int32 * HSN_TR_INTS),
+        ("f", c_float * HSN_TR_FLOATS),
+        ("u", (c_float * HSN_TR_UNITS) * HSN_TR_COEFS),
+    ]
+
+
 MODEL_INTS = ("N", "d", "K", "H", "M", "D", "S", "dc", "prod_bf16", "probes", "age_max", "phases_only")
 MODEL_FLOATS = ("lambda_cost", "cell_overhead", "shared_cost", "limit", "norm_eps", "cand_eps")
 MODEL_POINTERS = (
@@ -91,7 +108,7 @@ class HsnwPrologue(Structure):
     )
 
 
-#: Every symbol ``include/hsn_window_b200.h`` declares: (restype, argtypes).
+#: Every symbol ``include/hsn_window_b200.h`` and ``include/hsn_trainer_b200.h`` declare: (restype, argtypes).
 SYMBOLS: dict[str, tuple[object, list[object]]] = {
     "hsnw_version": (c_int, []),
     "hsnw_last_error": (c_char_p, []),
@@ -120,6 +137,7 @@ SYMBOLS: dict[str, tuple[object, list[object]]] = {
     "hsnw_selftest_wait_timeout": (c_int, [c_void_p, c_void_p]),
     "hsnw_prologue_scratch_bytes": (c_int64, [POINTER(HsnwPrologue)]),
     "hsnw_window_prologue": (c_int, [POINTER(HsnwPrologue), c_void_p]),
+    "hsnw_launch_table": (c_int, [c_char_p, POINTER(HsnTrainArgs), c_void_p]),
     "hsnw_profile_begin": (c_int, []),
     "hsnw_profile_kinds": (c_int, []),
     "hsnw_profile_kind_name": (c_char_p, [c_int]),

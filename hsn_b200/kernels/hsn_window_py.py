@@ -10,9 +10,8 @@ reference's names and ``HsnWinArgs`` slot layouts. Two differences, both on purp
   (``window.py:38-53``); these kernels use other block sizes and shared-memory layouts, so the shape
   is taken from ``hsnw_launch_shape`` for the sizes in the descriptor instead (``grid <= 0`` still
   launches nothing, ``window_ext.cpp:96``);
-* ``launch_table`` (the trainer's multi-tensor kernels, ``window_ext.cpp:155-213``) always answers
-  ``False``, "nothing launched": those kernels are not part of this library and the caller keeps its
-  PyTorch path, as it does on a device without the extension.
+* ``launch_table`` (the trainer's multi-tensor kernels, ``window_ext.cpp:155-213``) ignores ``block``
+  for the same reason: ``hsnw_launch_table`` sizes its own grid.
 """
 
 from __future__ import annotations
@@ -121,7 +120,54 @@ def loop(names: Sequence[str], grids: Sequence[int], blocks: Sequence[int], shar
 
 def launch_table(name: str, block: int, rows: Sequence[Sequence[Tensor]], elementwise: int, ints: Sequence[int],
                  floats: Sequence[float], doubles: Sequence[float], units: Sequence[Sequence[float]]) -> bool:  # fmt: skip
-    """``window_ext.cpp:155-213``, the trainer's multi-tensor kernels: not part of this library.
-    ``False`` = nothing was launched; the caller keeps its PyTorch path."""
-    del name, block, rows, elementwise, ints, floats, doubles, units
-    return False
+    """``window_ext.cpp:155-213``: launch the trainer kernel ``name`` over the tensors of ``rows`` (up to four
+    operands per tensor, ``rows[r][j]`` the r-th operand of tensor ``j``; an empty row is one the kernel
+    does not read). The first ``elementwise`` rows are fp32 tensors of row 0's element counts; the other
+    rows only have to be on the device. ``False``, with nothing launched, when a tensor is not a contiguous
+    tensor of the expected kind on row 0's CUDA device (the caller keeps its PyTorch path); an overflowing
+    descriptor raises. More tensors than a descriptor holds go out in several launches; tensors without
+    elements are skipped. ``ints`` fill ``i[1..]``."""
+    if not rows or len(rows) > _lib.HSN_TR_ROWS or not rows[0] or len(ints) >= _lib.HSN_TR_INTS \
+            or len(floats) > _lib.HSN_TR_FLOATS or len(doubles) > _lib.HSN_TR_DOUBLES or len(units) > _lib.HSN_TR_COEFS \
+            or not 1 <= elementwise <= len(rows) or block <= 0:  # fmt: skip
+        raise RuntimeError("HSN trainer kernels: launch descriptor overflow")
+    first = rows[0]
+    if not first[0].is_cuda:
+        return False
+    device = first[0].device
+    for r, row in enumerate(rows):
+        if row and len(row) != len(first):
+            raise RuntimeError(f"HSN trainer kernels: row {r} must be empty or hold one tensor per tensor of row 0")
+        for j, t in enumerate(row):
+            if not t.is_cuda or t.device != device or not t.is_contiguous():
+                return False
+            if r < elementwise and (t.dtype != torch.float32 or t.numel() != first[j].numel()):
+                return False
+    args = _lib.HsnTrainArgs()
+    for k, v in enumerate(ints):
+        if not -(2**31) <= int(v) < 2**31:
+            raise RuntimeError("HSN trainer kernels: int range")
+        args.i[k + 1] = int(v)
+    for k, v in enumerate(floats):
+        args.f[k] = float(v)
+    for k, v in enumerate(doubles):
+        args.g[k] = float(v)
+    for c, coefficients in enumerate(units):
+        if len(coefficients) > _lib.HSN_TR_UNITS:
+            raise RuntimeError("HSN trainer kernels: too many units")
+        for m, v in enumerate(coefficients):
+            args.u[c][m] = float(v)
+    lib = _lib.library()
+    with torch.cuda.device(device):
+        stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+        todo = [j for j in range(len(first)) if first[j].numel() > 0]
+        for at in range(0, len(todo), _lib.HSN_TR_TENSORS):
+            total = 0
+            for count, j in enumerate(todo[at : at + _lib.HSN_TR_TENSORS]):
+                for r, row in enumerate(rows):
+                    args.p[r][count] = row[j].data_ptr() if row else None
+                total += first[j].numel()
+                args.end[count] = total
+            args.i[0] = len(todo[at : at + _lib.HSN_TR_TENSORS])
+            _lib.check(lib.hsnw_launch_table(name.encode(), ctypes.byref(args), stream))
+    return True

@@ -27,6 +27,8 @@ inputs and outputs of every function on the window path as ``.npz`` files:
                         state and norms in float32. Pins the oracle's ``bf16=True`` mode.
 * ``prologue_*.npz``    ``HSN._window_prologue`` (``python/hsn/model/hsn.py:1707``): token and context ids in, ``z``,
                         the context embeddings and the scorer's scalars out, with the tables it reads.
+* ``snapshot_*.npz``    ``CellGraphState.snapshot`` (``python/hsn/model/state.py:363``): seeded states, their metas
+                        and the reference's digests.
 * ``chain_*.npz``       two chained windows against the unsplit window of twice the length: the
                         carried state forward, the state cotangent ``(A, R)`` backward.
 
@@ -656,6 +658,37 @@ def make_sweep(root: Path) -> None:
         print("sweep", name, "ok", "d_out", d_out)
 
 
+def make_snapshot(root: Path) -> None:
+    """``CellGraphState.snapshot`` (``python/hsn/model/state.py:363``) and ``pack_cell_state``
+    (``python/hsn/train/checkpoint.py:260``): seeded states in float32 and bfloat16, their metas and the
+    reference's digests. bfloat16 tensors are stored as their 16-bit patterns."""
+    import torch
+    from hsn.model.state import CellGraphState, StateMeta
+    from hsn.train.checkpoint import pack_cell_state
+
+    cases = {
+        "f32": (torch.float32, StateMeta("hsn-test-r1", 1, "tenant-a", None)),
+        "bf16": (torch.bfloat16, StateMeta("hsn-b200/é", 3, "tenant-ü", 4102444800.5)),
+    }
+    for name, (dtype, meta) in cases.items():
+        gen = torch.Generator().manual_seed(11)
+        B, N, d = 3, 7, 5
+        h = torch.randn(B, N, d, generator=gen).to(dtype)
+        state = CellGraphState(h=h, q=h.float().mean(dim=1).to(dtype), age=torch.randint(0, 90, (B, N), generator=gen),
+                               pos=torch.randint(0, 4000, (B,), generator=gen))  # fmt: skip
+        snap = state.snapshot(meta)
+        packed = pack_cell_state(state)
+        assert sorted(packed) == ["age", "h", "pos", "q"]
+        bits = (lambda t: t.view(torch.int16).numpy()) if dtype == torch.bfloat16 else (lambda t: t.numpy())
+        np.savez_compressed(
+            HERE / f"snapshot_{name}.npz", h=bits(snap.h), q=bits(snap.q), age=snap.age.numpy(), pos=snap.pos.numpy(),
+            dtype=np.array(str(dtype)), digest=np.array(snap.digest), meta_json=np.array(meta.to_bytes().decode("utf-8")),
+            model_version=np.array(meta.model_version), state_schema_version=np.array(meta.state_schema_version),
+            tenant_id=np.array(meta.tenant_id), expires_at=np.array(np.nan if meta.expires_at is None else meta.expires_at),
+        )  # fmt: skip
+        print("snapshot", name, snap.digest[:16])
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--reference", type=Path, required=True)
@@ -668,7 +701,7 @@ def main() -> None:
     steps = {
         "select": make_select, "update": make_update, "recurrence": make_recurrence,
         "windows": make_windows, "bf16": make_windows_bf16, "prologue": make_prologue, "chain": make_chain,
-        "sweep": make_sweep,
+        "sweep": make_sweep, "snapshot": make_snapshot,
     }  # fmt: skip
     for key, fn in steps.items():
         if not args.only or key in args.only.split(","):

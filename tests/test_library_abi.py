@@ -22,7 +22,7 @@ def lib() -> ctypes.CDLL:
 
 
 def test_every_declared_symbol_is_exported(lib: ctypes.CDLL) -> None:
-    text = HEADER.read_text()
+    text = HEADER.read_text() + (HEADER.parent / "hsn_trainer_b200.h").read_text()
     declared = set(re.findall(r"\b(hsnw_[a-z_]+)\s*\(", text))
     assert declared, "no entry points found in the header"
     assert declared == set(_lib.SYMBOLS), declared ^ set(_lib.SYMBOLS)
@@ -32,6 +32,8 @@ def test_every_declared_symbol_is_exported(lib: ctypes.CDLL) -> None:
 
 def test_structures_match_the_header() -> None:
     assert ctypes.sizeof(_lib.HsnWinArgs) == 8 * 48 + 4 * 32 + 4 * 8  # the reference's 544 bytes
+    assert ctypes.sizeof(_lib.HsnTrainArgs) == 8 * 4 * 40 + 8 * 40 + 8 * 2 + 4 * 8 + 4 * 8 + 4 * 6 * 64  # its 3760
+    assert _lib.HsnTrainArgs.end.offset == 1280 and _lib.HsnTrainArgs.u.offset == 1280 + 320 + 16 + 32 + 32
     assert ctypes.sizeof(_lib.HsnwModel) == 12 * 4 + 6 * 4 + 29 * 8
     assert ctypes.sizeof(_lib.HsnwForward) == 4 * 4 + 29 * 8 + 8
     assert ctypes.sizeof(_lib.HsnwBackward) == 4 * 4 + 20 * 8 + 8
@@ -41,6 +43,11 @@ def test_version_and_errors_without_a_device(lib: ctypes.CDLL) -> None:
     assert lib.hsnw_version() >= 100
     assert lib.hsnw_prepared(0) in (0, 1)
     args = _lib.HsnWinArgs()
+    table = _lib.HsnTrainArgs()
+    assert lib.hsnw_launch_table(b"hsn_tr_adamw", ctypes.byref(table), None) == _lib.E_ARG   # no tensors
+    table.i[0], table.end[0] = 1, 16
+    assert lib.hsnw_launch_table(b"no_such_kernel", ctypes.byref(table), None) == _lib.E_NAME
+    assert lib.hsnw_launch_table(b"hsn_tr_copy", ctypes.byref(table), None) == _lib.E_ARG    # null rows
     assert lib.hsnw_launch(b"no_such_kernel", ctypes.byref(args), 1, 64, 0, None) == _lib.E_NAME
     assert b"no kernel" in lib.hsnw_last_error()
     grid, block, shared = ctypes.c_int64(), ctypes.c_int(), ctypes.c_int()
