@@ -65,7 +65,7 @@ class HsnwModel(Structure):
 FORWARD_POINTERS = (
     "z", "ctx", "scalars", "reset", "h0", "q0", "age0", "pos", "tape_h", "tape_q", "tape_age", "cells",
     "units", "valid", "refreshed", "theta", "h_sel", "qs", "h_max", "rec_c", "rec_b", "rec_h_old", "rec_y",
-    "rec_gate_pre", "rec_m", "rec_rms", "rec_hidden", "logits", "scratch",
+    "rec_gate_pre", "rec_m", "rec_rms", "rec_hidden", "logits", "us", "scratch",
 )  # fmt: skip
 
 
@@ -97,6 +97,12 @@ PROLOGUE_POINTERS = (
     "byte_emb", "enc_w1", "enc_b1", "enc_w2", "enc_b2", "ctx_emb", "byte_codes", "cell_addresses", "ema_utility",
     "ema_selected", "tokens", "ctx_ids", "reset", "pos0", "prev_tokens", "z", "ctx", "scalars", "positions", "scratch",
 )  # fmt: skip
+
+
+class HsnwDecoder(Structure):
+    _fields_ = [(n, c_int32) for n in ("d_q", "d_u", "H", "V", "prod_bf16", "reserved")] + [
+        (n, c_void_p) for n in ("w1", "b1", "w2", "b2")
+    ]
 
 
 class HsnwPrologue(Structure):
@@ -137,6 +143,8 @@ SYMBOLS: dict[str, tuple[object, list[object]]] = {
     "hsnw_selftest_wait_timeout": (c_int, [c_void_p, c_void_p]),
     "hsnw_prologue_scratch_bytes": (c_int64, [POINTER(HsnwPrologue)]),
     "hsnw_window_prologue": (c_int, [POINTER(HsnwPrologue), c_void_p]),
+    "hsnw_decode_scratch_bytes": (c_int64, [POINTER(HsnwDecoder), c_int64]),
+    "hsnw_window_decode": (c_int, [POINTER(HsnwDecoder), c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p]),
     "hsnw_launch_table": (c_int, [c_char_p, POINTER(HsnTrainArgs), c_void_p]),
     "hsnw_profile_begin": (c_int, []),
     "hsnw_profile_kinds": (c_int, []),

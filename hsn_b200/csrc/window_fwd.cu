@@ -614,6 +614,7 @@ __global__ void __launch_bounds__(512, 2) k_row(FwdCtx c, int t) {
         const float sum = sum4(pf + (is_p ? c.nF : 0) * d + xx, d, c.nF);
         const float out = maybe_bf16(sum + c.m.f_b2[x], bf);
         ue[x] = is_p ? c.io.z[rt * d + xx] - out : out;
+        if (!is_p && c.io.us) c.io.us[rt * d + xx] = out;
     }
     __syncthreads();
     for (int j = warp; j < M; j += warps) {  // a warp per unit: lanes stride the 2d inputs

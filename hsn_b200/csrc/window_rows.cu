@@ -770,6 +770,8 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
                 }
             }
             __syncwarp();
+            if (r == 0 && c.io.us)   // u: in place since phase B, until the next position's phase A
+                for (int x = lane; x < d; x += 32) c.io.us[rt * d + x] = ue[x];
             if (r == 0 && !c.io.forced) {   // the decision's record
                 for (int k = lane; k < K; k += 32) {
                     const bool ok = (S.out_flag[k] & 1) != 0;

@@ -10,6 +10,7 @@ and names the results as the reference does (the tape keys of
 from __future__ import annotations
 
 import ctypes
+import math
 from collections.abc import Mapping
 from dataclasses import dataclass
 from typing import Any
@@ -19,8 +20,8 @@ from torch import Tensor
 
 from . import _lib
 
-__all__ = ["WindowModel", "WindowPrologue", "window_forward", "window_backward", "window_prologue", "stream_step",
-           "front_projection", "prepare"]  # fmt: skip
+__all__ = ["WindowModel", "WindowPrologue", "WindowDecoder", "window_forward", "window_backward", "window_prologue",
+           "window_decode", "stream_step", "front_projection", "prepare"]  # fmt: skip
 
 _WEIGHT_KEYS = (
     "s_w1 s_b1 s_w2 s_b2 p_w1 p_b1 p_w2 p_b2 score_w score_b v_w wout_w gate_w gate_b norm_w cand_w "
@@ -342,6 +343,7 @@ def window_forward(
     tape_state: bool = True,
     forced: tuple[Tensor, Tensor, Tensor] | None = None,
     want_logits: bool = False,
+    want_us: bool = False,
     scratch: Tensor | None = None,
     out: dict[str, Tensor] | None = None,
     carried: bool = False,
@@ -354,7 +356,8 @@ def window_forward(
     state is returned under ``h q age pos``). ``record`` adds ``rec_*``: the per-slot values the
     state-gradient sweep reads. ``forced = (cells, units, valid)`` replays a recorded decision.
     ``tape_state=False`` keeps no state tape and updates ``state`` in place (large ``N``).
-    ``out`` reuses the buffers of an earlier call's result (static addresses).
+    ``want_us`` adds ``us [B,T,d]``, the shared path's output ``u_t`` (with ``qs`` the decoder's input,
+    :func:`window_decode`). ``out`` reuses the buffers of an earlier call's result (static addresses).
     ``carried`` (with ``tape_state=False`` and the previous call's result as ``out``, same ``B`` and
     ``T``): the next chunk of positions on the same resident state, ``hsnw_stream_continue``; the
     cells' derived values are taken from the previous call's scratch instead of being recomputed
@@ -428,6 +431,8 @@ def window_forward(
         io.rec_hidden = buf("rec_hidden", (B, T, K, H), torch.bfloat16 if model.prod == "bf16" else f32).data_ptr()
     if want_logits:
         io.logits = buf("logits", (B, T, N, M), f32).data_ptr()
+    if want_us:
+        io.us = buf("us", (B, T, d), f32).data_ptr()
     need = int(lib.hsnw_forward_scratch_bytes(ctypes.byref(model.struct), B, T))
     if scratch is None:
         scratch = buf("_scratch", (need,), torch.uint8)
@@ -686,6 +691,74 @@ def front_projection(model: WindowModel, z: Tensor, ctx: Tensor) -> Tensor:
             )
         )
     return out
+
+
+@dataclass
+class WindowDecoder:
+    """The decoder ``D`` (``python/hsn/model/encoder.py:175-182``: ``fc1 [H, 2d]``, ``fc2 [V, H]`` with biases, in
+    ``nn.Linear`` layout) on the device; with ``prod="bf16"`` the weights are rounded to bfloat16 once here, as
+    autocast rounds them at every use."""
+
+    struct: _lib.HsnwDecoder
+    tensors: dict[str, Tensor]
+    device: torch.device
+
+    @staticmethod
+    def build(w1: Any, b1: Any, w2: Any, b2: Any, *, d_q: int, device: torch.device | str = "cuda",
+              prod: str = "fp32") -> "WindowDecoder":  # fmt: skip
+        device = torch.device(device)
+        if device.type != "cuda":
+            raise RuntimeError("the window kernels run on a CUDA device only (no CPU path)")
+        if device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        if prod not in ("fp32", "bf16"):
+            raise ValueError("prod must be fp32 | bf16")
+        t = {k: torch.as_tensor(v).detach().to(device=device, dtype=torch.float32).contiguous()
+             for k, v in (("w1", w1), ("b1", b1), ("w2", w2), ("b2", b2))}  # fmt: skip
+        if prod == "bf16":
+            t = {k: v.to(torch.bfloat16).to(torch.float32) for k, v in t.items()}
+        H, K = (int(n) for n in t["w1"].shape)
+        V = int(t["w2"].shape[0])
+        if tuple(t["w2"].shape) != (V, H) or tuple(t["b1"].shape) != (H,) or tuple(t["b2"].shape) != (V,) or not 0 < d_q <= K:
+            raise ValueError("decoder weights have inconsistent shapes")
+        st = _lib.HsnwDecoder()
+        st.d_q, st.d_u, st.H, st.V, st.prod_bf16 = int(d_q), K - int(d_q), H, V, int(prod == "bf16")
+        for key, value in t.items():
+            setattr(st, key, value.data_ptr())
+        prepare(device)
+        return WindowDecoder(struct=st, tensors=t, device=device)
+
+
+def window_decode(decoder: WindowDecoder, qs: Tensor, us: Tensor | None, *, out: dict[str, Tensor] | None = None) -> Tensor:
+    """``hsnw_window_decode``: the logits ``D([q_t; u_t])`` for ``qs [..., d_q]`` and ``us [..., d_u]`` (the forward
+    sweep's outputs of those names: ``window_forward(..., want_us=True)``), shape ``[..., V]``; the window's
+    epilogue (``python/hsn/model/hsn.py:2004-2049``, ``:2374-2390``) without its diagnostics. ``out`` reuses an
+    earlier call's buffers (``out["logits"]`` is the result)."""
+    dev, st = decoder.device, decoder.struct
+    lead = tuple(int(n) for n in qs.shape[:-1])
+    rows = math.prod(lead)
+    qs = _check("qs", qs, lead + (st.d_q,), torch.float32, dev)
+    if st.d_u:
+        if us is None:
+            raise ValueError("this decoder reads [q; u]: us is missing")
+        us = _check("us", us, lead + (st.d_u,), torch.float32, dev)
+    o = out if out is not None else {}
+    lib = _lib.library()
+    need = int(lib.hsnw_decode_scratch_bytes(ctypes.byref(st), rows))
+
+    def buf(name: str, shape: tuple[int, ...], dtype: torch.dtype) -> Tensor:
+        have = o.get(name)
+        if have is None or tuple(have.shape) != shape or have.dtype != dtype or have.device != dev:
+            o[name] = have = torch.empty(shape, dtype=dtype, device=dev)
+        return have
+
+    logits = buf("logits", lead + (st.V,), torch.float32)
+    scratch = buf("_decode_scratch", (need,), torch.uint8)
+    with torch.cuda.device(dev):
+        _lib.check(lib.hsnw_window_decode(ctypes.byref(st), qs.data_ptr(), us.data_ptr() if st.d_u else None, rows,
+                                          logits.data_ptr(), scratch.data_ptr(), need, _stream(dev)))  # fmt: skip
+    o["decode_status"] = scratch[:4].view(torch.int32)
+    return logits
 
 
 class launch_profile:

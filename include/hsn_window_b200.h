@@ -203,6 +203,8 @@ typedef struct HsnwForward {
     float* rec_rms;
     void* rec_hidden;
     float* logits;             /* optional [B,T,N,M]: the scorer's logits (tests) */
+    float* us;                 /* optional [B,T,d]: u_t, the shared path's output at every position (the
+                                * decoder's second input beside qs; hsnw_window_decode) */
     /* hsnw_forward_scratch_bytes() bytes, 256-byte aligned. Its first int32 is the call's status word:
      * cleared when the call is enqueued, set to 1 by a device-side wait (an mbarrier of the TMA
      * pipeline) that gave up after its iteration limit; the results of such a call are not valid. */
@@ -332,6 +334,29 @@ typedef struct HsnwPrologue {
 int64_t hsnw_prologue_scratch_bytes(const HsnwPrologue* prologue);
 int hsnw_window_prologue(const HsnwPrologue* prologue, void* stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * The window's epilogue: the decoder D([q_t; u_t]) = fc2(act(fc1(.))) over rows (python/hsn/model/
+ * hsn.py:2374-2390, python/hsn/model/encoder.py:175-182), for a window's B T positions or a serving
+ * step's B rows. Weights in nn.Linear's layout, fp32 (with prod_bf16 already rounded to bfloat16);
+ * qs [rows, d_q] and us [rows, d_u] are the forward sweep's outputs of those names. With prod_bf16 every
+ * linear's operands, bias and output are bfloat16 values and its sums float32 (autocast); the
+ * activation is the exact-erf GELU.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct HsnwDecoder {
+    int32_t d_q, d_u, H, V;    /* widths of the two input parts, the hidden layer, the vocabulary */
+    int32_t prod_bf16;
+    int32_t reserved;
+    const float* w1;           /* [H, d_q + d_u] */
+    const float* b1;           /* [H] */
+    const float* w2;           /* [V, H] */
+    const float* b2;           /* [V] */
+} HsnwDecoder;
+int64_t hsnw_decode_scratch_bytes(const HsnwDecoder* decoder, int64_t rows);
+/* logits [rows, V]. scratch: hsnw_decode_scratch_bytes() bytes, 256-byte aligned; its first int32 is the
+ * call's status word (0, or 1 after a bounded device-side wait gave up). */
+int hsnw_window_decode(const HsnwDecoder* decoder, const float* qs, const float* us, int64_t rows, float* logits,
+                       void* scratch, int64_t scratch_bytes, void* stream);
+
 /* ---- launch timing, for measurement runs --------------------------------------------------------
  * No counterpart in the reference (it times whole steps on the host, scripts/bench_window.py:60-110).
  * Between hsnw_profile_begin and hsnw_profile_end every kernel launch of the window entry points
@@ -340,7 +365,8 @@ int hsnw_window_prologue(const HsnwPrologue* prologue, void* stream);
  * before the next launch) and the number of launches. One profile at a time, one host thread, one
  * stream. hsnw_profile_kind_name(k): "init" "pre" "front" "row" "unit" "update" "head" "mid"
  * "tail_head" (the batch-synchronous phases) "rows_fwd" "rows_bwd" (the per-row cluster kernels: one
- * launch a window) "prologue" (hsnw_window_prologue's three launches as one). */
+ * launch a window) "prologue" (hsnw_window_prologue's three launches as one) "decode" (hsnw_window_decode's
+ * two). */
 int hsnw_profile_begin(void);
 int hsnw_profile_kinds(void);
 const char* hsnw_profile_kind_name(int kind);

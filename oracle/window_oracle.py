@@ -419,7 +419,7 @@ def window_forward(W: WindowWeights, z, ctx, scalars, reset, h, q, age, pos, *, 
     reset = reset.astype(bool)
     keys = ("tape_h tape_q tape_age tape_hsel tape_theta qs sel_cell_idx sel_unit_idx sel_valid "
             "sel_refreshed h_max rec_c rec_b rec_h_old rec_y rec_gate_pre rec_m rec_rms rec_hidden "
-            "logits").split()  # fmt: skip
+            "logits us").split()  # fmt: skip
     out: dict[str, list] = {k: [] for k in keys}
     pos = pos.copy()
     for t in range(T):
@@ -448,6 +448,7 @@ def window_forward(W: WindowWeights, z, ctx, scalars, reset, h, q, age, pos, *, 
         for name in ("c", "b", "h_old", "y", "gate_pre", "m", "rms", "hidden"):
             out["rec_" + name].append(p[name])
         out["logits"].append(p["logits"])
+        out["us"].append(p["u"])
     tape = {k: np.stack(v, axis=1) for k, v in out.items()}
     tape.update(h=h, q=q, age=age, pos=pos)
     tape["refreshed"] = tape["sel_refreshed"].astype(np.float32).sum(axis=2).mean(axis=0)
@@ -825,6 +826,16 @@ def sweep_tail(s: SweepSizes, buf: dict, t: int, *, cell_norm: bool) -> None:
 # --------------------------------------------------------------------------------------------------
 # The window's prologue: what the sweep reads per position, from the token and context ids
 # --------------------------------------------------------------------------------------------------
+
+def window_decode(P: dict, qs, us, *, bf16: bool = False):
+    """The window's epilogue without its diagnostics: ``HSN._decode`` in evaluation mode, no selected
+    readout (``python/hsn/model/hsn.py:2374-2390``): ``D([q_t; u_t])`` with ``D`` the two-layer ``MLP2``
+    ``2d -> H -> V`` (``python/hsn/model/encoder.py:74-126``, ``:175-182``). ``P``: ``dec_w1 [H, 2d]``,
+    ``dec_b1``, ``dec_w2 [V, H]``, ``dec_b2``. With ``bf16`` each linear runs as under autocast."""
+    x = np.concatenate([np.asarray(qs), np.asarray(us)], axis=-1)
+    act = (lambda v: bf16_round(gelu(v))) if bf16 else gelu
+    return _lin(act(_lin(x, P["dec_w1"], P["dec_b1"], bf16)), P["dec_w2"], P["dec_b2"], bf16)
+
 
 BOS = 1  # the byte that stands for "no previous byte" (python/hsn/data/synthetic.py:117)
 

@@ -27,6 +27,7 @@ inputs and outputs of every function on the window path as ``.npz`` files:
                         state and norms in float32. Pins the oracle's ``bf16=True`` mode.
 * ``prologue_*.npz``    ``HSN._window_prologue`` (``python/hsn/model/hsn.py:1707``): token and context ids in, ``z``,
                         the context embeddings and the scorer's scalars out, with the tables it reads.
+* ``decode_*.npz``      ``HSN._decode`` (``python/hsn/model/hsn.py:2374``): the decoder on seeded ``q``, ``u``.
 * ``snapshot_*.npz``    ``CellGraphState.snapshot`` (``python/hsn/model/state.py:363``): seeded states, their metas
                         and the reference's digests.
 * ``chain_*.npz``       two chained windows against the unsplit window of twice the length: the
@@ -658,6 +659,35 @@ def make_sweep(root: Path) -> None:
         print("sweep", name, "ok", "d_out", d_out)
 
 
+def make_decode(root: Path) -> None:
+    """``HSN._decode`` (``python/hsn/model/hsn.py:2374``) in evaluation mode on seeded ``q``, ``u``: float64,
+    float32 and under ``torch.autocast("cpu", dtype=torch.bfloat16)``, with the decoder's weights."""
+    import torch
+
+    B, T = 3, 5
+    cfg = _cfg(root, B=B, T=T, N=12, d=16, K=3, H=40, M=3, D=2, fd="[summary,eps,state,router]",
+               extra=("model.selected_readout=false",))
+    for name, dtype, auto in (("f64", torch.float64, False), ("f32", torch.float32, False), ("bf16", torch.float32, True)):
+        model = _model(cfg, dtype, 0.3)
+        model.eval()
+        gen = torch.Generator().manual_seed(21)
+        d = cfg.model.d
+        qs = (torch.randn(B, T, d, generator=gen) * 0.5).to(dtype)
+        us = (torch.randn(B, T, d, generator=gen) * 0.8).to(dtype)
+        with torch.no_grad():
+            if auto:
+                with torch.autocast("cpu", dtype=torch.bfloat16):
+                    logits = model._decode(qs, us, None)
+            else:
+                logits = model._decode(qs, us, None)
+        dec = model.decoder
+        np.savez_compressed(
+            HERE / f"decode_{name}.npz", qs=_np(qs), us=_np(us), logits=_np(logits.to(dtype)),
+            dec_w1=_np(dec.fc1.weight), dec_b1=_np(dec.fc1.bias), dec_w2=_np(dec.fc2.weight), dec_b2=_np(dec.fc2.bias),
+        )  # fmt: skip
+        print("decode", name, tuple(logits.shape), logits.dtype)
+
+
 def make_snapshot(root: Path) -> None:
     """``CellGraphState.snapshot`` (``python/hsn/model/state.py:363``) and ``pack_cell_state``
     (``python/hsn/train/checkpoint.py:260``): seeded states in float32 and bfloat16, their metas and the
@@ -701,7 +731,7 @@ def main() -> None:
     steps = {
         "select": make_select, "update": make_update, "recurrence": make_recurrence,
         "windows": make_windows, "bf16": make_windows_bf16, "prologue": make_prologue, "chain": make_chain,
-        "sweep": make_sweep, "snapshot": make_snapshot,
+        "sweep": make_sweep, "snapshot": make_snapshot, "decode": make_decode,
     }  # fmt: skip
     for key, fn in steps.items():
         if not args.only or key in args.only.split(","):

@@ -35,7 +35,7 @@ def test_structures_match_the_header() -> None:
     assert ctypes.sizeof(_lib.HsnTrainArgs) == 8 * 4 * 40 + 8 * 40 + 8 * 2 + 4 * 8 + 4 * 8 + 4 * 6 * 64  # its 3760
     assert _lib.HsnTrainArgs.end.offset == 1280 and _lib.HsnTrainArgs.u.offset == 1280 + 320 + 16 + 32 + 32
     assert ctypes.sizeof(_lib.HsnwModel) == 12 * 4 + 6 * 4 + 29 * 8
-    assert ctypes.sizeof(_lib.HsnwForward) == 4 * 4 + 29 * 8 + 8
+    assert ctypes.sizeof(_lib.HsnwForward) == 4 * 4 + 30 * 8 + 8
     assert ctypes.sizeof(_lib.HsnwBackward) == 4 * 4 + 20 * 8 + 8
 
 

@@ -351,3 +351,16 @@ def test_window_prologue_equals_the_reference(name: str) -> None:
     assert got["scalars"].shape[-1] == 9
     if name == "carried_f32":
         assert float(np.abs(got["scalars"][..., 3]).max()) > 0 and int(got["positions"].max()) > 100
+
+
+@pytest.mark.parametrize("name,tol", [("f64", 1e-12), ("f32", 1e-5), ("bf16", 0.0)])
+def test_window_decode_equals_the_reference(name: str, tol: float) -> None:
+    """The decoder over ``[q; u]`` against ``HSN._decode`` on the CPU: float64, float32, and under bf16
+    autocast, where the restatement reproduces the reference's bfloat16 logits exactly."""
+    z = load_golden(f"decode_{name}")
+    got = O.window_decode({k: z[k] for k in ("dec_w1", "dec_b1", "dec_w2", "dec_b2")}, z["qs"], z["us"], bf16=name == "bf16")
+    assert got.shape == z["logits"].shape == z["qs"].shape[:-1] + (256,)
+    if tol == 0.0:
+        assert np.array_equal(got, z["logits"])
+    else:
+        np.testing.assert_allclose(got, z["logits"], rtol=tol, atol=tol * float(np.abs(z["logits"]).max()))
