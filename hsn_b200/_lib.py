@@ -45,6 +45,16 @@ class HsnTrainArgs(Structure):
     ]
 
 
+class HsnwExchange(Structure):
+    """``include/hsn_trainer_b200.h``: the fused gradient exchange and AdamW step of one rank."""
+
+    _fields_ = [
+        ("world", c_int32), ("rank", c_int32), ("average", c_int32), ("weight_decay_on", c_int32), ("shard", c_int64),
+        ("grads", c_void_p * 8), ("params", c_void_p * 8), ("exp_avg", c_void_p), ("exp_avg_sq", c_void_p),
+        ("f", c_float * HSN_TR_FLOATS),
+    ]  # fmt: skip
+
+
 MODEL_INTS = ("N", "d", "K", "H", "M", "D", "S", "dc", "prod_bf16", "probes", "age_max", "phases_only")
 MODEL_FLOATS = ("lambda_cost", "cell_overhead", "shared_cost", "limit", "norm_eps", "cand_eps")
 MODEL_POINTERS = (
@@ -145,6 +155,7 @@ SYMBOLS: dict[str, tuple[object, list[object]]] = {
     "hsnw_window_prologue": (c_int, [POINTER(HsnwPrologue), c_void_p]),
     "hsnw_decode_scratch_bytes": (c_int64, [POINTER(HsnwDecoder), c_int64]),
     "hsnw_window_decode": (c_int, [POINTER(HsnwDecoder), c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p]),
+    "hsnw_exchange_adamw": (c_int, [POINTER(HsnwExchange), c_void_p]),
     "hsnw_launch_table": (c_int, [c_char_p, POINTER(HsnTrainArgs), c_void_p]),
     "hsnw_profile_begin": (c_int, []),
     "hsnw_profile_kinds": (c_int, []),

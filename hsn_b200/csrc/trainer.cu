@@ -193,6 +193,72 @@ int launch(const HsnTrainArgs& a, int64_t runs, cudaStream_t stream) {
 
 }  // namespace
 
+namespace {
+
+// One thread: four consecutive elements of the rank's shard (the shard is a multiple of four elements and
+// every buffer 16-byte aligned: checked on the host). Loads from the peers' gradients are issued together,
+// then summed in rank order.
+__global__ void __launch_bounds__(kThreads) k_exchange_adamw(const __grid_constant__ HsnwExchange x) {
+    const int64_t quads = x.shard >> 2;
+    const int64_t base = static_cast<int64_t>(x.rank) * x.shard;
+    const float inv = 1.0f / static_cast<float>(x.world);
+    for (int64_t q = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; q < quads; q += static_cast<int64_t>(gridDim.x) * kThreads) {
+        const int64_t e = 4 * q;
+        float4 part[HSN_EX_RANKS];
+#pragma unroll
+        for (int k = 0; k < HSN_EX_RANKS; ++k)
+            if (k < x.world) part[k] = *reinterpret_cast<const float4*>(x.grads[k] + base + e);
+        float g[4] = {part[0].x, part[0].y, part[0].z, part[0].w};
+#pragma unroll
+        for (int k = 1; k < HSN_EX_RANKS; ++k)
+            if (k < x.world) {
+                g[0] = __fadd_rn(g[0], part[k].x);
+                g[1] = __fadd_rn(g[1], part[k].y);
+                g[2] = __fadd_rn(g[2], part[k].z);
+                g[3] = __fadd_rn(g[3], part[k].w);
+            }
+        const float4 p4 = *reinterpret_cast<const float4*>(x.params[x.rank] + base + e);
+        const float4 m4 = *reinterpret_cast<const float4*>(x.exp_avg + e);
+        const float4 v4 = *reinterpret_cast<const float4*>(x.exp_avg_sq + e);
+        float p[4] = {p4.x, p4.y, p4.z, p4.w}, m[4] = {m4.x, m4.y, m4.z, m4.w}, v[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float gi = x.average ? __fmul_rn(g[i], inv) : g[i];
+            if (x.weight_decay_on) p[i] = __fmul_rn(p[i], x.f[0]);
+            m[i] = lerp_rn(m[i], gi, x.f[1]);
+            v[i] = addcmul_rn(__fmul_rn(v[i], x.f[2]), gi, gi, x.f[3]);
+            const float den = __fadd_rn(__fmul_rn(__fsqrt_rn(v[i]), x.f[4]), x.f[5]);
+            p[i] = addcdiv_rn(p[i], m[i], den, x.f[6]);
+        }
+        *reinterpret_cast<float4*>(x.exp_avg + e) = make_float4(m[0], m[1], m[2], m[3]);
+        *reinterpret_cast<float4*>(x.exp_avg_sq + e) = make_float4(v[0], v[1], v[2], v[3]);
+        const float4 out = make_float4(p[0], p[1], p[2], p[3]);
+#pragma unroll
+        for (int k = 0; k < HSN_EX_RANKS; ++k)
+            if (k < x.world) *reinterpret_cast<float4*>(x.params[k] + base + e) = out;
+    }
+}
+
+}  // namespace
+
+extern "C" int hsnw_exchange_adamw(const HsnwExchange* exchange, void* stream_) {
+    if (!exchange) return hsnw_fail(HSNW_E_ARG, "exchange_adamw: null argument");
+    const HsnwExchange& x = *exchange;
+    if (x.world < 1 || x.world > HSN_EX_RANKS || x.rank < 0 || x.rank >= x.world) return hsnw_fail(HSNW_E_ARG, "exchange_adamw: world must be 1..8 and rank inside it");
+    if (x.shard < 4 || x.shard % 4) return hsnw_fail(HSNW_E_ARG, "exchange_adamw: the shard must be a positive multiple of 4 elements");
+    uintptr_t bits = reinterpret_cast<uintptr_t>(x.exp_avg) | reinterpret_cast<uintptr_t>(x.exp_avg_sq);
+    if (!x.exp_avg || !x.exp_avg_sq) return hsnw_fail(HSNW_E_ARG, "exchange_adamw: the moments are missing");
+    for (int k = 0; k < x.world; ++k) {
+        if (!x.grads[k] || !x.params[k]) return hsnw_fail(HSNW_E_ARG, "exchange_adamw: a rank's buffer is missing");
+        bits |= reinterpret_cast<uintptr_t>(x.grads[k]) | reinterpret_cast<uintptr_t>(x.params[k]);
+    }
+    if (bits & 15) return hsnw_fail(HSNW_E_ARG, "exchange_adamw: every buffer must start on a 16-byte boundary");
+    const int64_t blocks = (x.shard / 4 + kThreads - 1) / kThreads;
+    const int64_t cap = static_cast<int64_t>(hsnw_sm_count_current()) * 8;
+    k_exchange_adamw<<<static_cast<unsigned>(blocks < cap ? blocks : cap), kThreads, 0, static_cast<cudaStream_t>(stream_)>>>(x);
+    return hsnw_check_launch("exchange_adamw");
+}
+
 extern "C" int hsnw_launch_table(const char* name, const HsnTrainArgs* args, void* stream_) {
     if (!name || !args) return hsnw_fail(HSNW_E_ARG, "launch_table: null argument");
     const HsnTrainArgs& a = *args;

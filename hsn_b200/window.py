@@ -466,11 +466,13 @@ def stream_step(
     *,
     out: dict[str, Tensor] | None = None,
     carried: bool = False,
+    want_us: bool = False,
 ) -> dict[str, Tensor]:
     """One position on a resident state, updated in place (``hsnw_stream_step``): the serving
     step's state update (``python/hsn/train/compile.py:1913-2006``). ``z_t [B,d]``, ``ctx_t
     [B,dc]``, ``scalars_t [B,N,S]``, ``reset_t [B]`` bool. Returns the decision and the slots'
-    states (``sel_*``, ``tape_hsel``, ``qs``) of the position.
+    states (``sel_*``, ``tape_hsel``, ``qs``) of the position; with ``want_us`` also ``us``, so that
+    ``window_decode(decoder, step["qs"][:, 0], step["us"][:, 0])`` are the step's logits ``[B, V]``.
 
     ``carried`` (``hsnw_stream_continue``): ``out`` is the result of the previous step on this
     state (it holds the scratch with every cell's derived values), the weights are the same and
@@ -480,7 +482,7 @@ def stream_step(
         raise ValueError("a carried step needs the previous step's result as `out`")
     return window_forward(
         model, z_t[:, None], ctx_t[:, None], scalars_t[:, None], reset_t[:, None], state,
-        record=False, tape_state=False, out=out,
+        record=False, tape_state=False, out=out, want_us=want_us,
         _entry="hsnw_stream_continue" if carried else "hsnw_stream_step",
     )  # fmt: skip
 

@@ -57,6 +57,31 @@ typedef struct HsnTrainArgs {
  * thread where the addresses allow). Returns 0, HSNW_E_NAME, HSNW_E_ARG or HSNW_E_CUDA. */
 int hsnw_launch_table(const char* name, const HsnTrainArgs* args, void* stream);
 
+/* The gradient exchange fused with the optimiser step, for data-parallel ranks of one box whose gradient
+ * and parameter buffers are mapped into each other's address spaces (peer memory over NVLink): ONE
+ * kernel per rank that, for the rank's shard of a flat parameter vector, reads every rank's gradients
+ * of the shard from that rank's memory, sums them in rank order (a fixed order: every rank computes the
+ * same bits), averages, applies hsn_tr_adamw's step to the shard's parameters and moments, and writes the
+ * new parameters into every rank's parameter buffer. That is reduce-scatter, AdamW and all-gather with
+ * the transfers inside the arithmetic's loop instead of two collectives around a kernel. No counterpart
+ * in the reference (its trainer all-reduces, then steps: scripts and python/hsn/train/loop.py).
+ * The caller orders the ranks around the launch: every rank's gradients are complete before any rank's
+ * kernel starts, and no rank reads its parameters before every rank's kernel has ended (two barriers on
+ * the stream; hsn_b200/parallel.py uses a one-element NCCL all-reduce for each). */
+#define HSN_EX_RANKS 8
+typedef struct HsnwExchange {
+    int32_t world, rank;        /* 1..8 ranks; this rank */
+    int32_t average;            /* 1: divide the sum by world (multiply by 1 / world) */
+    int32_t weight_decay_on;
+    int64_t shard;              /* elements per rank; rank r owns [r shard, (r + 1) shard) of the flat vector */
+    const float* grads[HSN_EX_RANKS];   /* every rank's gradient buffer [world shard], as mapped on this rank */
+    float* params[HSN_EX_RANKS];        /* every rank's parameter buffer [world shard], as mapped on this rank */
+    float* exp_avg;             /* [shard] this rank's moments */
+    float* exp_avg_sq;
+    float f[HSN_TR_FLOATS];     /* hsn_tr_adamw's f0 .. f6 */
+} HsnwExchange;
+int hsnw_exchange_adamw(const HsnwExchange* exchange, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -143,3 +143,16 @@ def limit_project(param, old, scale, clipped):
         param = old + (param - old) * f32(scale)
     applied = param - old
     return param.astype(f32), (applied * applied).astype(f32)
+
+
+@_quiet
+def exchange_adamw(grads_by_rank, p, m, v, *, average=True, **hyper):
+    """The fused exchange's arithmetic for a whole flat vector (``hsn_b200/csrc/trainer.cu: k_exchange_adamw``;
+    no counterpart in the reference, which all-reduces and then steps): the ranks' gradients summed in rank order,
+    multiplied by ``1 / world`` when averaging, then :func:`adamw`. Returns ``(p, m, v)``."""
+    g = np.asarray(grads_by_rank[0], f32)
+    for other in grads_by_rank[1:]:
+        g = g + np.asarray(other, f32)
+    if average:
+        g = g * (f32(1.0) / f32(len(grads_by_rank)))
+    return adamw(p, g, m, v, **hyper)

@@ -104,3 +104,30 @@ def test_decode_refuses_what_it_cannot_take() -> None:
         window_decode(fp, dev(f(3, 10)), None)
     with pytest.raises(ValueError):
         window_decode(fp, dev(f(3, 11)), dev(f(3, 10)))
+
+
+def test_serving_step_with_logits() -> None:
+    """The reference's serving step returns logits: two streamed positions (the second carried) and the decoder
+    on each step's ``qs`` and ``us``, against the oracle's step and decoder."""
+    from hsn_b200.window import WindowModel, stream_step, window_decode
+
+    rng = np.random.default_rng(10)
+    B, N, d, K, H, M, D = 6, 64, 32, 4, 128, 3, 2
+    W, z, ctx, scalars, reset, state = synthetic_window(rng, B, 2, N, d, K, H, M, D, 0.0)
+    reset[:, 0] = False
+    f = lambda *s: (rng.standard_normal(s) * 0.2).astype(np.float32)  # noqa: E731
+    P = dict(dec_w1=f(96, 2 * d), dec_b1=f(96), dec_w2=f(256, 96), dec_b2=f(256))
+    model = WindowModel.from_oracle_weights(W, device="cuda", prod="fp32")
+    dec = _decoder(P, d, "fp32")
+    live = tuple(dev(s) for s in state)
+    h, q, age, pos = state
+    step = None
+    for t in range(2):
+        step = stream_step(model, dev(z[:, t]), dev(ctx[:, t]), dev(scalars[:, t]), dev(reset[:, t]), live, out=step,
+                           carried=t > 0, want_us=True)  # fmt: skip
+        logits = window_decode(dec, step["qs"][:, 0], step["us"][:, 0])
+        p = O.stream_step(W, z[:, t], ctx[:, t], scalars[:, t], reset[:, t], h, q, age, pos)
+        h, q, age, pos = p["h"], p["q"], p["age"], p["pos"]
+        want = O.window_decode(P, p["q"], p["u"])
+        assert tuple(logits.shape) == (B, 256)
+        np.testing.assert_allclose(to_np(logits), want, rtol=1e-5, atol=1e-5 * float(np.abs(want).max()))

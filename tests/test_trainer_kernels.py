@@ -233,3 +233,44 @@ def test_kernels_equal_the_oracle_at_other_sizes_and_decline_what_they_cannot_ta
     assert torch.equal(wide, before)
     empty = torch.empty(0, device="cuda")
     assert trainer.copy([empty, wide.clone()], [empty, wide]) is True                  # tensors without elements are skipped
+
+
+def test_shards_are_whole_16_byte_groups() -> None:
+    from hsn_b200.parallel import shard_elements
+
+    assert shard_elements(1, 1) == 4 and shard_elements(8, 2) == 4 and shard_elements(9, 2) == 8
+    assert shard_elements(1000003, 8) == 125004 and 8 * shard_elements(1000003, 8) >= 1000003
+    with pytest.raises(ValueError):
+        shard_elements(0, 2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_fused_exchange_equals_the_oracle_with_every_rank_on_one_device(world: int) -> None:
+    """The ranks' buffers side by side on one GPU, each rank's kernel launched in turn (nothing in the kernel
+    waits for another rank): after three steps every rank's parameter buffer holds the same bits, those of the
+    oracle's rank-ordered sum, average and AdamW step."""
+    from hsn_b200.parallel import ShardedAdamW, shard_elements
+
+    rng = np.random.default_rng(7)
+    n = 10007
+    shard = shard_elements(n, world)
+    hyper = dict(lr=2.5e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.01)
+    p0 = np.zeros(world * shard, np.float32)
+    p0[:n] = rng.standard_normal(n).astype(np.float32) * 0.1
+    grads = [torch.zeros(world * shard, device="cuda") for _ in range(world)]
+    params = [_dev(p0) for _ in range(world)]
+    ranks = [ShardedAdamW(n, lr=hyper["lr"], betas=(0.9, 0.95), eps=1e-8, weight_decay=0.01, buffers=(grads, params), rank=r)
+             for r in range(world)]  # fmt: skip
+    p, m, v = p0, np.zeros_like(p0), np.zeros_like(p0)
+    for step in range(1, 4):
+        gs = [rng.standard_normal(world * shard).astype(np.float32) * (1e-3, 1.0, 30.0)[step - 1] for _ in range(world)]
+        for r in range(world):
+            grads[r].copy_(_dev(gs[r]))
+        for opt in ranks:
+            opt.step()
+        p, m, v = TO.exchange_adamw(gs, p, m, v, step=step, **hyper)
+        for r in range(world):
+            assert same(_np(params[r]), p), (step, r)
+        moments = np.concatenate([_np(opt.exp_avg) for opt in ranks])
+        assert same(moments, m)
