@@ -691,6 +691,8 @@ def run_trainer(args, c: dict, name: str) -> None:
     from hsn_b200.kernels import trainer
 
     if args.impl == "reference":   # the reference's CPU path: torch's multi-tensor operations on the host cores
+        if int(os.environ.get("RANK", "0")) != 0:
+            return
         n, elements = 8, c["elements"]
         gen = torch.Generator().manual_seed(0)
         ps, gs = ([torch.randn(elements, generator=gen) * 0.1 for _ in range(n)] for _ in range(2))
@@ -711,8 +713,9 @@ def run_trainer(args, c: dict, name: str) -> None:
                              "sample": f"{n} tensors a step, torch multi-tensor operations on the host"},
             "e2e": {"value": value, "unit": "elements/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))  # fmt: skip
         return
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
+    world, rank, local, dev = dist_setup()
+    if world > 1:
+        return run_trainer_sharded(args, c, name, world, rank, dev)
     n, elements = c["tensors"], c["elements"]
     gen = torch.Generator(device=dev).manual_seed(0)
     make = lambda scale: [torch.randn(elements, generator=gen, device=dev) * scale for _ in range(n)]  # noqa: E731
@@ -755,6 +758,63 @@ def run_trainer(args, c: dict, name: str) -> None:
                      "frac": achieved / peak, "traffic": None, "peak_source": "measured" if peaks else "fallback",
                      "how": "28 bytes an element (p, g, m, v read; p, m, v written) / the step's mean event time"},
         "clocks": clocks_summary(clock_lines, 0)}))  # fmt: skip
+
+
+def run_trainer_sharded(args, c: dict, name: str, world: int, rank: int, dev) -> None:
+    """`--config adamw --gpus N`: the same parameter vector replicated on N ranks, a step = the gradient exchange
+    and the AdamW step as ONE kernel per rank over peer memory (`ShardedAdamW`: reduce-scatter, step, all-gather),
+    with the unfused sequence beside it (NCCL all-reduce of the flat gradients, then `hsn_tr_adamw` on every
+    rank). Strong scaling: the vector does not grow with N."""
+    import torch
+    import torch.distributed as dist
+
+    from hsn_b200.kernels import trainer
+    from hsn_b200.parallel import ShardedAdamW
+
+    total = c["tensors"] * c["elements"]
+    hyper = dict(lr=2.5e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.01)
+    opt = ShardedAdamW(total, **hyper)
+    gen = torch.Generator(device=dev).manual_seed(rank)
+    opt.params.copy_(torch.randn(opt.params.numel(), generator=torch.Generator(device=dev).manual_seed(0), device=dev) * 0.1)
+    opt.grads.copy_(torch.randn(opt.grads.numel(), generator=gen, device=dev))
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        opt.step()
+    ms_total, each = timed_steps(lambda i: opt.step(), args.steps, barrier)
+    # the unfused sequence on plain buffers
+    flat_g = opt.grads.clone()
+    p, m, v = opt.params.clone(), torch.zeros_like(opt.params), torch.zeros_like(opt.params)
+    count = [0]
+
+    def unfused(i):
+        count[0] += 1
+        dist.all_reduce(flat_g)
+        flat_g.mul_(1.0 / world)
+        trainer.adamw([p], [flat_g], [m], [v], lr=2.5e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.01, step=count[0])
+
+    for i in range(3):
+        unfused(i)
+    other_total, _ = timed_steps(unfused, max(3, args.steps // 2), barrier)
+    times = torch.tensor([ms_total, other_total], device=dev)
+    dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        step_ms, other_ms = float(times[0]) / args.steps, float(times[1]) / max(3, args.steps // 2)
+        link = 4.0 * (world - 1) * opt.shard   # bytes a rank reads from its peers (and as many it writes to them) a step
+        print(json.dumps({
+            "metric": "trainer AdamW elements/s", "value": total / (step_ms * 1e-3), "unit": "elements/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "step_ms": spread(each), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOADS[name] + f", replicated on {world} ranks: gradient exchange + step fused over peer memory",
+                       "shard_elements": opt.shard, "unfused_nccl_allreduce_then_adamw_ms_per_step": other_ms},
+            "gpu_launches": args.steps,
+            "roofline": {"bound": "nvlink", "kernel": "k_exchange_adamw", "achieved": link / (step_ms * 1e-3) / 1e9, "peak": 770.0,
+                         "unit": "GB/s", "frac": link / (step_ms * 1e-3) / 1e9 / 770.0, "traffic": None,
+                         "how": "bytes a rank reads from its peers a step (it writes as many) / the step's time, of the measured 770 GB/s a direction"}}))  # fmt: skip
+    dist.destroy_process_group()
 
 
 def _torch_adamw(torch, ps, gs, ms, vs, step, lr=2.5e-3, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.01) -> None:
