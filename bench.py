@@ -49,7 +49,10 @@ CONFIGS = {
 }
 # the trainer's AdamW pass (not the headline): forty tensors of a few million elements, one launch a step
 CONFIGS["adamw"] = dict(tensors=40, elements=4_194_304 + 1031, trainer=True)
+# the window's epilogue (not the headline): the decoder over the c2 window's 8192 rows
+CONFIGS["decode"] = dict(rows=32 * 256, d=64, H=512, V=256, decoder=True)
 WORKLOADS = {
+    "decode": "the decoder D([q; u]) over a window's 8192 rows: 128 -> 512 -> 256, bf16 products",
     "adamw": "the trainer's AdamW step over 40 fp32 tensors of 4,195,335 elements (671 MB of parameters), one launch",
     "c1": "tiny gradcheck-shape window B2 T8 N16 d32 K2 H32",
     "c2": "reference-shape window fwd+bwd: B32 T256 N256 d64 K8 H512 M8 D4, bf16 products, fp32 state, resets p=1/1024",
@@ -760,6 +763,44 @@ def run_trainer(args, c: dict, name: str) -> None:
         "clocks": clocks_summary(clock_lines, 0)}))  # fmt: skip
 
 
+def run_decoder(args, c: dict, name: str) -> None:
+    """`--config decode`: `hsnw_window_decode` over the benchmark window's rows; a step = both layers."""
+    import torch
+
+    from hsn_b200.window import WindowDecoder, launch_profile, window_decode
+
+    world, rank, local, dev = dist_setup()
+    rows, d, H, V = c["rows"], c["d"], c["H"], c["V"]
+    gen = torch.Generator(device=dev).manual_seed(0)
+    f = lambda *shape: torch.randn(*shape, generator=gen, device=dev) * 0.2  # noqa: E731
+    dec = WindowDecoder.build(f(H, 2 * d), f(H), f(V, H), f(V), d_q=d, device=dev, prod="bf16")
+    qs, us = f(rows, d), f(rows, d)
+    out: dict = {}
+    for _ in range(max(3, args.warmup)):
+        window_decode(dec, qs, us, out=out)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def step(i):
+        flush.zero_()   # (the operands are smaller than L2: written over between the steps)
+        window_decode(dec, qs, us, out=out)
+
+    with launch_profile() as prof:
+        step(0)
+    ms_total, each = timed_steps(step, args.steps, torch.cuda.synchronize)
+    kernel_ms = prof.ms.get("decode", 0.0)
+    flops = 2.0 * rows * (2 * d * H + H * V)
+    print(json.dumps({
+        "metric": "decoder rows/s", "value": rows / (kernel_ms * 1e-3), "unit": "rows/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": kernel_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 products", "data": "synthetic",
+        "config": {"workload": WORKLOADS[name], "l2": "a 256 MB buffer is written between the steps",
+                   "step_with_flush_ms": ms_total / args.steps},
+        "gpu_launches": 2 * args.steps,
+        "roofline": {"bound": "tensor", "kernel": "k_linear_tc", "achieved": flops / (kernel_ms * 1e-3) / 1e12, "peak": 1590.0,
+                     "unit": "TFLOP/s", "frac": flops / (kernel_ms * 1e-3) / 1e12 / 1590.0, "traffic": None,
+                     "how": "the two layers' 2 M N K flops / the two launches' event time in a profiled step; 3.2 GFLOP: the kernels are latency bound at this size"}}))  # fmt: skip
+
+
 def run_trainer_sharded(args, c: dict, name: str, world: int, rank: int, dev) -> None:
     """`--config adamw --gpus N`: the same parameter vector replicated on N ranks, a step = the gradient exchange
     and the AdamW step as ONE kernel per rank over peer memory (`ShardedAdamW`: reduce-scatter, step, all-gather),
@@ -846,7 +887,11 @@ def main() -> None:
     c = dict(CONFIGS[args.config])
     if args.positions > 0:
         c["T"] = args.positions
-    if c.get("trainer"):
+    if c.get("decoder"):
+        if args.steps == 100:
+            args.steps = 20
+        run_decoder(args, c, args.config)
+    elif c.get("trainer"):
         if args.steps == 100:
             args.steps = 20 if args.impl == "ours" else 5
         run_trainer(args, c, args.config)
