@@ -67,4 +67,7 @@ def test_launch_and_loop_run_the_kernels_by_name() -> None:
         ext.launch("hsn_win_select", B, 256, 0, [torch.zeros(3)], ints(0), floats)
     with pytest.raises(RuntimeError):
         ext.loop(["hsn_win_select"], [B], [256], [0], tensors(untouched), ints(0), floats, T, 40)
-    assert ext.launch_table("hsn_tr_adamw", 256, [[torch.zeros(3, device="cuda")]], 1, [], [], [], []) is False
+    # the trainer's kernels by name through the same module (tests/test_trainer_kernels.py checks their values)
+    a, b = torch.zeros(3, device="cuda"), torch.ones(3, device="cuda")
+    assert ext.launch_table("hsn_tr_copy", 256, [[a], [b]], 2, [], [], [], []) is True and torch.equal(a, b)
+    assert ext.launch_table("hsn_tr_copy", 256, [[torch.zeros(3)], [torch.ones(3)]], 2, [], [], [], []) is False   # CPU tensors
