@@ -1297,6 +1297,7 @@ __global__ void __launch_bounds__(kRowThreads, 1) k_rows_fwd(RowsCtx c) {
         RMARK(13);
     }
     // the last position's max |h|, and the state the window ends in
+    if (!producer && !issuer) consumer_sync();   // (every warp's share of the maximum is in)
     if (tid == 0) peer(cl, inbox_front, 0)[r * stride_in + 2 * d] = __int_as_float(hmax_local);
     cl.sync();
     if (producer) {
