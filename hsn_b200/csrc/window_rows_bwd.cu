@@ -115,6 +115,7 @@ __global__ void __launch_bounds__(kRowThreadsB, 1) k_rows_bwd(RowsBwdCtx c) {
     __shared__ __align__(8) uint64_t bar_act[2];          // a unit's dhid operand is written (two buffers in turn): one arrival per compute warp
     __shared__ __align__(8) uint64_t bar_sp[2];           // a unit's second product has read its operand buffer
     __shared__ __align__(8) uint64_t bar_dec;             // the next position's unit lists are in place
+    __shared__ __align__(8) uint64_t bar_rec;             // the next position's records have landed (bulk copies by the decision warp)
     __shared__ uint32_t tmem_slot;
 #ifdef HSNW_TRACE
     __shared__ unsigned long long trace_s[32];   // written to memory when the kernel ends (a store before a barrier delays it)
@@ -212,6 +213,34 @@ __global__ void __launch_bounds__(kRowThreadsB, 1) k_rows_bwd(RowsBwdCtx c) {
         }
         cp_async_commit();
     };
+    // the same as bulk copies by ONE thread (the decision warp's, during the unit stage), arriving on bar_rec: a
+    // slot's row of an array is d floats, the slot's recorded pre-activations 128 bfloat16, both whole 16-byte units
+    auto prefetch_bulk = [&](int t) {
+        const int buf = t & 1;
+        const int64_t rt = static_cast<int64_t>(row) * T + t;
+        float* rc = rec_of(buf);
+        const float* srcs[7] = {c.io.c, c.io.b, c.io.h_old, c.io.y, c.io.gate_pre, c.io.m, c.io.d_h_sel};
+        int owned = 0;
+        for (int kl = 0; kl < Ks; ++kl) owned += kl * C + r < K ? 1 : 0;
+        int present = 0;
+        for (int a = 0; a < 7; ++a) present += srcs[a] ? 1 : 0;
+        const uint32_t row_bytes = static_cast<uint32_t>(sizeof(float)) * d;
+        mbar_expect_tx(&bar_rec, static_cast<uint32_t>(present * owned) * row_bytes + static_cast<uint32_t>(K) * 256u
+                                     + ((c.io.d_q_post ? 1u : 0u) + (c.io.d_q_pre ? 1u : 0u)) * row_bytes);
+        for (int a = 0; a < 7; ++a) {
+            if (!srcs[a]) continue;
+            for (int kl = 0; kl < Ks; ++kl) {
+                const int k = kl * C + r;
+                if (k < K) bulk_g2s(rc + (a * Ks + kl) * d, srcs[a] + (rt * K + k) * d, row_bytes, &bar_rec);
+            }
+        }
+        uint16_t* hd = hid_of(buf);
+        const uint16_t* recorded = static_cast<const uint16_t*>(c.io.hidden);
+        for (int k = 0; k < K; ++k) bulk_g2s(hd + k * 128, recorded + (rt * K + k) * H + r * 128, 256u, &bar_rec);
+        float* q = dq_of(buf);
+        if (c.io.d_q_post) bulk_g2s(q, c.io.d_q_post + rt * d, row_bytes, &bar_rec);
+        if (c.io.d_q_pre) bulk_g2s(q + d, c.io.d_q_pre + rt * d, row_bytes, &bar_rec);
+    };
     // the decision of position t: each thread loads what it will store (decision_store), so the
     // loads' latency is spent under other work
     int ld_cell = -1, ld_unit = -1, ld_tgt = -1;
@@ -292,6 +321,7 @@ __global__ void __launch_bounds__(kRowThreadsB, 1) k_rows_bwd(RowsBwdCtx c) {
         mbar_init(&bar_sp[0], 1);
         mbar_init(&bar_sp[1], 1);
         mbar_init(&bar_dec, 1);
+        mbar_init(&bar_rec, 1);
         failed_s = 0;
     }
     for (int e = tid; e < d * d; e += kConsumers) {
@@ -386,7 +416,9 @@ __global__ void __launch_bounds__(kRowThreadsB, 1) k_rows_bwd(RowsBwdCtx c) {
         }
         // ---------------- H
         if (consumer) {
-            cp_async_wait_all();   // (the copies of this position's record, requested a position ago by the gate's warps)
+            // this position's records: requested a position ago (the first position's by these warps before the loop)
+            if (t == T - 1) cp_async_wait_all();
+            else ring_wait(&bar_rec, static_cast<uint32_t>(T - 2 - t) & 1u, c.status, &failed_s);
             consumer_sync();
             if (tid < d) Rs[tid] = R_s[tid] + q[tid];
             consumer_sync();
@@ -524,26 +556,29 @@ __global__ void __launch_bounds__(kRowThreadsB, 1) k_rows_bwd(RowsBwdCtx c) {
                 if (i + 1 == n_units) umma_commit(&bar_d2);
             }
             tcgen05_fence_before();
+        } else if (role == 3) {
+            // off every critical path: the position's dc and db to memory, the next position's records into their buffer
+            for (int e = lane; e < Ks * d; e += 32) {
+                const int kl = e / d, x = e - kl * d, k = kl * C + r;
+                if (k < K) {
+                    c.io.dc[(rt * K + k) * d + x] = dcs[e];
+                    c.io.db[(rt * K + k) * d + x] = dbs[e];
+                }
+            }
+            if (lane == 0 && t > 0) prefetch_bulk(t - 1);
+            __syncwarp();
         } else if (consumer) {
             const int hc = lane + 32 * (warp & 3), sh = warp >> 2;
             float inner[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             {
-                // under the first product, what waits for nothing: the position's dc and db go to memory, the
-                // gate's transposed linear on this block's state outputs, and the next position's record
-                // requests (off the position's critical path)
-                for (int e = tid; e < Ks * d; e += kConsumers) {
-                    const int kl = e / d, x = e - kl * d, k = kl * C + r;
-                    if (k < K) {
-                        c.io.dc[(rt * K + k) * d + x] = dcs[e];
-                        c.io.db[(rt * K + k) * d + x] = dbs[e];
-                    }
-                }
+                // under the first product, what waits for nothing: the gate's transposed linear on this block's
+                // state outputs (the position's dc and db go to memory and the next position's records are
+                // requested by the decision warp meanwhile)
                 for (int e = tid; e < K * gcols; e += kConsumers) {
                     const int k = e >> gshift, il = e - k * gcols;
                     const float sum = dc_[k] >= 0 ? dot_bf16w(dg_all + k * d, 1, gate + il * d, 1, d) : 0.0f;
                     peer(cl, inbox_g, k & cmask)[(k >> cshift) * two + r * gcols + il] = sum;
                 }
-                if (t > 0) prefetch(t - 1, tid, kConsumers);
             }
             for (int i = 0; i < n_units; ++i) {
                 const int j = dc_[o_ulist + i];
