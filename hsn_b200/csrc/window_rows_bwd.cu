@@ -369,26 +369,48 @@ __global__ void __launch_bounds__(kRowThreadsB, 1) k_rows_bwd(RowsBwdCtx c) {
     // units ahead. Unit number n (counted over the window) uses slot n & 1 of both rings, round n >> 1.
     uint32_t units_before = 0;          // units of the positions before this one
     unsigned char* ring_q = ring + 2 * c.w2_bytes;
-    int cur_t = T - 1, cur_i = 0;       // the next piece to request (producer's lane 0): position, index among its 2 n_units pieces
-    // request pieces of position cur_t, whose first unit is number `base`, at most `limit` of them; a request waits
-    // for its slot's previous tenant to be spent
+    int cur_t = T - 1, cur_p = 0, cur_q = 0;   // the next pieces to request (producer's lane 0): position, unit index per kind
+    // Request pieces of position cur_t, whose first unit is number `base`, up to its unit `limit` (exclusive). The two
+    // rings are served independently, whichever slot is handed back first: a second-layer slot comes back only after
+    // its unit's epilogue, and requests in order of use would hold the next first-layer pieces behind it.
     auto request = [&](uint32_t base, int limit) {
         const int* dc_ = dec_of(cur_t & 1);
-        const int n_pieces = 2 * dc_[o_n];
-        for (int n = 0; n < limit && cur_i < n_pieces; ++n) {
-            const uint32_t unit = base + static_cast<uint32_t>(cur_i >> 1), slot = unit & 1u;
-            const bool second = (cur_i & 1) != 0;
+        const int n = min(limit, dc_[o_n]);
+        auto try_one = [&](bool second, bool wait) {   // the kind's next piece, if its slot is free (or after waiting for it)
+            int& cur = second ? cur_q : cur_p;
+            if (cur >= n) return false;
+            const uint32_t unit = base + static_cast<uint32_t>(cur), slot = unit & 1u;
+            uint64_t* empty = second ? &empty_q[slot] : &empty_p[slot];
+            if (unit >= 2) {
+                const uint32_t parity = ((unit >> 1) - 1u) & 1u;
+                if (wait) {
+                    ring_wait(empty, parity, c.status, &failed_s);
+                } else {
+                    uint32_t done;
+                    asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                                 : "=r"(done)
+                                 : "r"(smem_addr(empty)), "r"(parity)
+                                 : "memory");
+                    if (!done) return false;
+                }
+            }
             uint64_t* full = second ? &full_q[slot] : &full_p[slot];
-            if (unit >= 2) ring_wait(second ? &empty_q[slot] : &empty_p[slot], ((unit >> 1) - 1u) & 1u, c.status, &failed_s);
-            const int j = dc_[o_ulist + (cur_i >> 1)];
+            const int j = dc_[o_ulist + cur];
             const unsigned char* from = bank + (static_cast<size_t>(j) * C + r) * c.bank_bytes + (second ? c.w2_bytes : 0u);
             const uint32_t bytes = second ? slot_bytes : c.w2_bytes;
             mbar_expect_tx(full, bytes);
             bulk_g2s(second ? ring_q + slot * slot_bytes : ring + slot * c.w2_bytes, from, bytes, full);
-            ++cur_i;
+            ++cur;
+            return true;
+        };
+        while ((cur_p < n || cur_q < n) && !failed_s) {
+            const bool a = try_one(false, false), b = try_one(true, false);
+            // nothing was handed back: sleep on the first-layer ring's slot if a piece of it is outstanding (it comes
+            // back first), else on the other's (ring_wait: bounded, with a suspend-time hint)
+            if (!a && !b) try_one(cur_p >= n, true);
         }
     };
-    if (role == 0 && lane == 0) request(0u, 4);
+    if (role == 0 && lane == 0) request(0u, 2);
     cl.sync();
 
     const float n_f = static_cast<float>(N);
@@ -513,8 +535,8 @@ __global__ void __launch_bounds__(kRowThreadsB, 1) k_rows_bwd(RowsBwdCtx c) {
                     // are pieces of this position or older: spent before this stage ends)
                     ring_wait(&bar_dec, dec_phase & 1u, c.status, &failed_s);
                     cur_t = t - 1;
-                    cur_i = 0;
-                    request(units_before + static_cast<uint32_t>(n_units), 4);
+                    cur_p = cur_q = 0;
+                    request(units_before + static_cast<uint32_t>(n_units), 2);
                 }
             }
             __syncwarp();
@@ -571,9 +593,12 @@ __global__ void __launch_bounds__(kRowThreadsB, 1) k_rows_bwd(RowsBwdCtx c) {
             const int hc = lane + 32 * (warp & 3), sh = warp >> 2;
             float inner[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             {
-                // under the first product, what waits for nothing: the gate's transposed linear on this block's
+                // under the first products, what waits for nothing: the gate's transposed linear on this block's
                 // state outputs (the position's dc and db go to memory and the next position's records are
-                // requested by the decision warp meanwhile)
+                // requested by the decision warp meanwhile). Before the epilogues on purpose: the copies and the
+                // issuer warps get ahead meanwhile and every unit then costs less. (After them, under the last
+                // unit's second product, a position of one or two units is 0.9 us shorter and one of four or more
+                // longer; choosing by the unit count cost the benchmark's windows 0.15 us a position.)
                 for (int e = tid; e < K * gcols; e += kConsumers) {
                     const int k = e >> gshift, il = e - k * gcols;
                     const float sum = dc_[k] >= 0 ? dot_bf16w(dg_all + k * d, 1, gate + il * d, 1, d) : 0.0f;
