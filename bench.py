@@ -105,7 +105,7 @@ def kernel_bytes_per_row_position(c: dict) -> dict[str, int]:
 # workload, from the ncu captures summarised in profiles/rows_kernels_c2.md (the per-row cluster
 # kernels) and profiles/phases_kernels_c2_dram.md (the phase kernels).
 NCU_TRAFFIC_SOURCE = ("ncu capture of bench.py --steps 1 --warmup 3 at the kernels of commit 59d6e77 "
-                      "(profiles/rows_kernels_c2.md); the prologue's row kernel was rewritten after it")
+                      "(profiles/rows_kernels_c2.md); later changes reorder requests and stores, not bytes")
 NCU_TRAFFIC_PER_LAUNCH: dict[str, dict[str, float]] = {
     "c2": {"rows_fwd": 784.5e6, "rows_bwd": 227.4e6, "pre": 4.6e6, "front": 2.798e6, "row": 1.375e6, "unit": 3.419e6, "update": 0.526e6, "mid": 2.254e6, "tail_head": 1.703e6},
 }
