@@ -844,7 +844,7 @@ def run_trainer_sharded(args, c: dict, name: str, world: int, rank: int, dev) ->
     dist.all_reduce(times, op=dist.ReduceOp.MAX)
     if rank == 0:
         step_ms, other_ms = float(times[0]) / args.steps, float(times[1]) / max(3, args.steps // 2)
-        link = 4.0 * (world - 1) * opt.shard   # bytes a rank reads from its peers (and as many it writes to them) a step
+        link = 2 * 4.0 * (world - 1) * opt.shard   # bytes that ARRIVE at a rank a step: what it reads from its peers and what they write into it (as many leave)
         print(json.dumps({
             "metric": "trainer AdamW elements/s", "value": total / (step_ms * 1e-3), "unit": "elements/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "step_ms": spread(each), "higher_is_better": True,
@@ -854,7 +854,7 @@ def run_trainer_sharded(args, c: dict, name: str, world: int, rank: int, dev) ->
             "gpu_launches": args.steps,
             "roofline": {"bound": "nvlink", "kernel": "k_exchange_adamw", "achieved": link / (step_ms * 1e-3) / 1e9, "peak": 770.0,
                          "unit": "GB/s", "frac": link / (step_ms * 1e-3) / 1e9 / 770.0, "traffic": None,
-                         "how": "bytes a rank reads from its peers a step (it writes as many) / the step's time, of the measured 770 GB/s a direction"}}))  # fmt: skip
+                         "how": "bytes arriving at a rank a step (its reads of the peers' gradients + the peers' writes of its parameters; as many leave) / the step's time, of the measured 770 GB/s a direction"}}))  # fmt: skip
     dist.destroy_process_group()
 
 

@@ -199,43 +199,55 @@ namespace {
 // every buffer 16-byte aligned: checked on the host). Loads from the peers' gradients are issued together,
 // then summed in rank order.
 __global__ void __launch_bounds__(kThreads) k_exchange_adamw(const __grid_constant__ HsnwExchange x) {
+    constexpr int U = 2;   // quads a thread has in flight: the peers' memory is microseconds away
     const int64_t quads = x.shard >> 2;
     const int64_t base = static_cast<int64_t>(x.rank) * x.shard;
     const float inv = 1.0f / static_cast<float>(x.world);
-    for (int64_t q = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; q < quads; q += static_cast<int64_t>(gridDim.x) * kThreads) {
-        const int64_t e = 4 * q;
-        float4 part[HSN_EX_RANKS];
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+    for (int64_t q0 = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; q0 < quads; q0 += U * stride) {
+        float4 part[U][HSN_EX_RANKS], p4[U], m4[U], v4[U];
 #pragma unroll
-        for (int k = 0; k < HSN_EX_RANKS; ++k)
-            if (k < x.world) part[k] = *reinterpret_cast<const float4*>(x.grads[k] + base + e);
-        float g[4] = {part[0].x, part[0].y, part[0].z, part[0].w};
+        for (int u = 0; u < U; ++u) {
+            const int64_t e = 4 * (q0 + u * stride);
+            if (q0 + u * stride >= quads) continue;
 #pragma unroll
-        for (int k = 1; k < HSN_EX_RANKS; ++k)
-            if (k < x.world) {
-                g[0] = __fadd_rn(g[0], part[k].x);
-                g[1] = __fadd_rn(g[1], part[k].y);
-                g[2] = __fadd_rn(g[2], part[k].z);
-                g[3] = __fadd_rn(g[3], part[k].w);
-            }
-        const float4 p4 = *reinterpret_cast<const float4*>(x.params[x.rank] + base + e);
-        const float4 m4 = *reinterpret_cast<const float4*>(x.exp_avg + e);
-        const float4 v4 = *reinterpret_cast<const float4*>(x.exp_avg_sq + e);
-        float p[4] = {p4.x, p4.y, p4.z, p4.w}, m[4] = {m4.x, m4.y, m4.z, m4.w}, v[4] = {v4.x, v4.y, v4.z, v4.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float gi = x.average ? __fmul_rn(g[i], inv) : g[i];
-            if (x.weight_decay_on) p[i] = __fmul_rn(p[i], x.f[0]);
-            m[i] = lerp_rn(m[i], gi, x.f[1]);
-            v[i] = addcmul_rn(__fmul_rn(v[i], x.f[2]), gi, gi, x.f[3]);
-            const float den = __fadd_rn(__fmul_rn(__fsqrt_rn(v[i]), x.f[4]), x.f[5]);
-            p[i] = addcdiv_rn(p[i], m[i], den, x.f[6]);
+            for (int k = 0; k < HSN_EX_RANKS; ++k)
+                if (k < x.world) part[u][k] = *reinterpret_cast<const float4*>(x.grads[k] + base + e);
+            p4[u] = *reinterpret_cast<const float4*>(x.params[x.rank] + base + e);
+            m4[u] = *reinterpret_cast<const float4*>(x.exp_avg + e);
+            v4[u] = *reinterpret_cast<const float4*>(x.exp_avg_sq + e);
         }
-        *reinterpret_cast<float4*>(x.exp_avg + e) = make_float4(m[0], m[1], m[2], m[3]);
-        *reinterpret_cast<float4*>(x.exp_avg_sq + e) = make_float4(v[0], v[1], v[2], v[3]);
-        const float4 out = make_float4(p[0], p[1], p[2], p[3]);
 #pragma unroll
-        for (int k = 0; k < HSN_EX_RANKS; ++k)
-            if (k < x.world) *reinterpret_cast<float4*>(x.params[k] + base + e) = out;
+        for (int u = 0; u < U; ++u) {
+            const int64_t e = 4 * (q0 + u * stride);
+            if (q0 + u * stride >= quads) continue;
+            float g[4] = {part[u][0].x, part[u][0].y, part[u][0].z, part[u][0].w};
+#pragma unroll
+            for (int k = 1; k < HSN_EX_RANKS; ++k)
+                if (k < x.world) {   // rank order: every rank computes the same bits
+                    g[0] = __fadd_rn(g[0], part[u][k].x);
+                    g[1] = __fadd_rn(g[1], part[u][k].y);
+                    g[2] = __fadd_rn(g[2], part[u][k].z);
+                    g[3] = __fadd_rn(g[3], part[u][k].w);
+                }
+            float p[4] = {p4[u].x, p4[u].y, p4[u].z, p4[u].w}, m[4] = {m4[u].x, m4[u].y, m4[u].z, m4[u].w},
+                  v[4] = {v4[u].x, v4[u].y, v4[u].z, v4[u].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float gi = x.average ? __fmul_rn(g[i], inv) : g[i];
+                if (x.weight_decay_on) p[i] = __fmul_rn(p[i], x.f[0]);
+                m[i] = lerp_rn(m[i], gi, x.f[1]);
+                v[i] = addcmul_rn(__fmul_rn(v[i], x.f[2]), gi, gi, x.f[3]);
+                const float den = __fadd_rn(__fmul_rn(__fsqrt_rn(v[i]), x.f[4]), x.f[5]);
+                p[i] = addcdiv_rn(p[i], m[i], den, x.f[6]);
+            }
+            *reinterpret_cast<float4*>(x.exp_avg + e) = make_float4(m[0], m[1], m[2], m[3]);
+            *reinterpret_cast<float4*>(x.exp_avg_sq + e) = make_float4(v[0], v[1], v[2], v[3]);
+            const float4 out = make_float4(p[0], p[1], p[2], p[3]);
+#pragma unroll
+            for (int k = 0; k < HSN_EX_RANKS; ++k)
+                if (k < x.world) *reinterpret_cast<float4*>(x.params[k] + base + e) = out;
+        }
     }
 }
 
