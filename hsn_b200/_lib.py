@@ -115,6 +115,12 @@ class HsnwDecoder(Structure):
     ]
 
 
+class HsnwUnits(Structure):
+    _fields_ = [(n, c_int32) for n in ("n_units", "d_in", "hidden", "d_out", "prod_bf16", "reserved")] + [
+        (n, c_void_p) for n in ("w1", "b1", "w2", "b2")
+    ]
+
+
 class HsnwPrologue(Structure):
     _fields_ = (
         [(n, c_int32) for n in PROLOGUE_INTS]
@@ -155,6 +161,10 @@ SYMBOLS: dict[str, tuple[object, list[object]]] = {
     "hsnw_window_prologue": (c_int, [POINTER(HsnwPrologue), c_void_p]),
     "hsnw_decode_scratch_bytes": (c_int64, [POINTER(HsnwDecoder), c_int64]),
     "hsnw_window_decode": (c_int, [POINTER(HsnwDecoder), c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p]),
+    "hsnw_units_scratch_bytes": (c_int64, [POINTER(HsnwUnits), c_int64, c_int]),
+    "hsnw_units_forward": (c_int, [POINTER(HsnwUnits), c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "hsnw_units_backward": (c_int, [POINTER(HsnwUnits), c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "hsnw_exchange_adamw": (c_int, [POINTER(HsnwExchange), c_void_p]),
     "hsnw_launch_table": (c_int, [c_char_p, POINTER(HsnTrainArgs), c_void_p]),
     "hsnw_profile_begin": (c_int, []),

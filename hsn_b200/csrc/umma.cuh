@@ -111,6 +111,11 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
 __device__ __forceinline__ void umma_chain(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, int steps,
                                            uint32_t a_step, uint32_t b_step, bool onto = false) {
     __syncwarp();
+    // Kept rolled: left to the compiler's own four-fold unrolling of this run-time count, one instantiation
+    // (the grouped unit pass's first weight gradient) issued the first four products of a six-step chain
+    // with the rows of A taken modulo 8, as if the descriptor's stride between core matrices were zero,
+    // and the two of the remainder loop correctly; with one product per iteration every chain is right.
+#pragma unroll 1
     for (int s = 0; s < steps; ++s)
         umma_bf16(tmem_d, desc_a + static_cast<uint64_t>(s) * a_step, desc_b + static_cast<uint64_t>(s) * b_step, idesc,
                   onto || s > 0);

@@ -1,0 +1,743 @@
+// The replay's grouped unit pass and its backward on the device: for P pairs (v_p [4d], unit_p) the chosen
+// unit's two-layer perceptron out_p = act(v_p W1[u] + b1[u]) W2[u] + b2[u], every pair of a window at once,
+// and the gradients of v and of the four stacked parameters for a cotangent of out (reference
+// python/hsn/model/units.py:356-414, UnitBank.forward_grouped, and autograd's backward of its addmm /
+// activation / addmm per present unit; python/hsn/model/cell.py:716 is the call in the replay).
+//
+// The reference sorts the pairs by unit on the host's reading of the unit histogram, cuts the sorted rows
+// with one split and runs two addmm per present unit. Here nothing is read by the host: three small kernels
+// sort the pairs stably by unit (per-block unit counts, one scan, placement) and cut the sorted order into
+// tiles of 128 pairs (never across two units) and, for the weight gradients, into segments of `seg` pairs;
+// every product then is ONE launch over all units' tiles:
+//
+//   forward   pre  = v W1[u] + b1[u]                     rows: a tile's pairs,   K = 4d
+//             out  = act(pre) W2[u] + b2[u]              rows: a tile's pairs,   K = H
+//   backward  dpre = (dout W2[u]^T) * act'(pre)          rows: a tile's pairs,   K = d   (kept in sorted order)
+//             dv   = dpre W1[u]^T                        rows: a tile's pairs,   K = H
+//             dW1 += v^T dpre, dW2 += act(pre)^T dout    rows: 4d resp. H,       K = a segment's pairs
+//             db1  = sum dpre, db2 = sum dout            column sums per unit
+//
+// With bf16 products each is a tcgen05 tile product: a 128 x BN output tile per block with the accumulator
+// in tensor memory, K in chunks of 128 staged by the block's threads as K-major core-matrix planes — a
+// source whose K runs along its rows is read 8 consecutive elements at a time, a source whose K runs across
+// its rows (the weights [K, N], and both operands of the weight gradients, whose K is the pair) is read with
+// the warp's lanes along the contiguous dimension, eight strided loads per 16-byte unit — with the operand's
+// own transformation (rounding to bfloat16, the activation) applied while it is staged. The epilogue adds
+// the bias, rounds, applies the activation's derivative, and writes through the sorted order so that every
+// result lands in the pairs' input order. The weight gradients' segments write float32 partial tiles that a
+// last kernel sums per unit in segment order (a fixed order: the same bits every run), rounds as the
+// reference's bfloat16 product does and widens to the parameters' float32. With fp32 products the same
+// operand and result functions feed a CUDA-core tile kernel (sums in K order).
+#include "../../include/hsn_units_b200.h"
+#include "../../include/hsn_window_b200.h"
+#include "common.cuh"
+#include "stage.cuh"
+#include "host_util.h"
+#include "umma.cuh"
+
+#include <algorithm>
+
+using namespace hsnw;
+
+namespace {
+
+constexpr int kTile = 128;       // pairs of a row tile = rows of a tensor-core product
+constexpr int kChunk = 128;      // K elements staged at a time
+constexpr int kSortBlock = 1024;
+constexpr int kMaxUnits = 256;
+
+struct Tables {
+    int* order;        // [P] sorted position -> pair
+    int* block_off;    // [blocks][M] pairs of unit u in earlier sort blocks
+    int* unit_base;    // [M + 1] first sorted position of a unit
+    int* tile_first;   // [M + 1] first tile of a unit
+    int* seg_first;    // [M + 1] first segment of a unit
+    int* tile_unit;    // [max tiles]
+    int* tile_start;   // sorted position of the tile's first pair
+    int* tile_rows;
+    int* seg_unit;     // [max segments]
+    int* seg_start;
+    int* seg_len;
+    int* counts;       // [0] tiles, [1] segments
+};
+
+// ---- sorting the pairs by unit ----------------------------------------------------------------------
+
+// A warp's lanes with the same unit, in lane order: the rank of this lane among them and their number.
+__device__ __forceinline__ void warp_rank(int unit, int lane, int& rank, int& peers_n) {
+    const unsigned peers = __match_any_sync(0xffffffffu, unit);
+    rank = __popc(peers & ((1u << lane) - 1u));
+    peers_n = __popc(peers);
+}
+
+__device__ __forceinline__ int read_unit(const int64_t* unit_idx, int64_t p, int64_t pairs, int M, int* status) {
+    if (p >= pairs) return -1;
+    const int64_t u = unit_idx[p];
+    if (u < 0 || u >= M) {
+        atomicExch(status, 2);
+        return -1;
+    }
+    return static_cast<int>(u);
+}
+
+// counts[warp][unit] of one sort block in shared memory (all 1024 threads call)
+__device__ __forceinline__ void block_unit_counts(int* warp_count, int unit, int M, int& rank) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int e = tid; e < 32 * M; e += kSortBlock) warp_count[e] = 0;
+    __syncthreads();
+    int peers_n;
+    warp_rank(unit, lane, rank, peers_n);
+    if (unit >= 0 && rank == 0) warp_count[warp * M + unit] = peers_n;
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(kSortBlock) k_units_count(const int64_t* unit_idx, int64_t pairs, int M, Tables tb, int* status) {
+    extern __shared__ int warp_count[];
+    const int64_t p = static_cast<int64_t>(blockIdx.x) * kSortBlock + threadIdx.x;
+    int rank;
+    block_unit_counts(warp_count, read_unit(unit_idx, p, pairs, M, status), M, rank);
+    for (int u = threadIdx.x; u < M; u += kSortBlock) {
+        int n = 0;
+        for (int w = 0; w < 32; ++w) n += warp_count[w * M + u];
+        tb.block_off[static_cast<int64_t>(blockIdx.x) * M + u] = n;   // the scan turns counts into offsets
+    }
+}
+
+// One block: per unit the exclusive scan of its counts over the sort blocks, then the units' bases and the
+// lists of tiles and segments.
+__global__ void __launch_bounds__(256) k_units_scan(int blocks, int M, int seg, Tables tb) {
+    __shared__ int total[kMaxUnits];
+    const int tid = threadIdx.x;
+    for (int u = tid; u < M; u += 256) {
+        int run = 0;
+        for (int b = 0; b < blocks; ++b) {
+            const int n = tb.block_off[static_cast<int64_t>(b) * M + u];
+            tb.block_off[static_cast<int64_t>(b) * M + u] = run;
+            run += n;
+        }
+        total[u] = run;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int base = 0, tiles = 0, segs = 0;
+        for (int u = 0; u < M; ++u) {
+            tb.unit_base[u] = base;
+            tb.tile_first[u] = tiles;
+            tb.seg_first[u] = segs;
+            base += total[u];
+            tiles += (total[u] + kTile - 1) / kTile;
+            segs += (total[u] + seg - 1) / seg;
+        }
+        tb.unit_base[M] = base;
+        tb.tile_first[M] = tiles;
+        tb.seg_first[M] = segs;
+        tb.counts[0] = tiles;
+        tb.counts[1] = segs;
+    }
+    __syncthreads();
+    const int tiles = tb.tile_first[M], segs = tb.seg_first[M];
+    for (int t = tid; t < tiles; t += 256) {
+        int u = 0;
+        while (tb.tile_first[u + 1] <= t) ++u;
+        const int at = (t - tb.tile_first[u]) * kTile;
+        tb.tile_unit[t] = u;
+        tb.tile_start[t] = tb.unit_base[u] + at;
+        tb.tile_rows[t] = min(kTile, total[u] - at);
+    }
+    for (int s = tid; s < segs; s += 256) {
+        int u = 0;
+        while (tb.seg_first[u + 1] <= s) ++u;
+        const int at = (s - tb.seg_first[u]) * seg;
+        tb.seg_unit[s] = u;
+        tb.seg_start[s] = tb.unit_base[u] + at;
+        tb.seg_len[s] = min(seg, total[u] - at);
+    }
+}
+
+__global__ void __launch_bounds__(kSortBlock) k_units_place(const int64_t* unit_idx, int64_t pairs, int M, Tables tb, int* status) {
+    extern __shared__ int warp_count[];
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int64_t p = static_cast<int64_t>(blockIdx.x) * kSortBlock + tid;
+    const int unit = read_unit(unit_idx, p, pairs, M, status);
+    int rank;
+    block_unit_counts(warp_count, unit, M, rank);
+    for (int u = tid; u < M; u += kSortBlock) {   // exclusive scan over the block's warps
+        int run = 0;
+        for (int w = 0; w < 32; ++w) {
+            const int n = warp_count[w * M + u];
+            warp_count[w * M + u] = run;
+            run += n;
+        }
+    }
+    __syncthreads();
+    if (unit >= 0)
+        tb.order[tb.unit_base[unit] + tb.block_off[static_cast<int64_t>(blockIdx.x) * M + unit] + warp_count[warp * M + unit] + rank] =
+            static_cast<int>(p);
+}
+
+// ---- operands and results of the six products -------------------------------------------------------------
+// E: the type of pre, out, dout and dpre (bfloat16 with bf16 products, else float); BF: round as the bf16 pass does.
+
+template <bool BF>
+__device__ __forceinline__ float rnd(float x) {
+    return BF ? bf16r(x) : x;
+}
+__device__ __forceinline__ void load8(const float* src, float x[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* src, float x[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(src);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        x[2 * i] = __uint_as_float(w[i] << 16);
+        x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+__device__ __forceinline__ float load1(const float* src) { return *src; }
+__device__ __forceinline__ float load1(const __nv_bfloat16* src) { return __bfloat162float(*src); }
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&pair);
+}
+__device__ __forceinline__ void store8(float* dst, const float x[8]) {
+    *reinterpret_cast<float4*>(dst) = make_float4(x[0], x[1], x[2], x[3]);
+    *reinterpret_cast<float4*>(dst + 4) = make_float4(x[4], x[5], x[6], x[7]);
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* dst, const float x[8]) {
+    *reinterpret_cast<uint4*>(dst) = make_uint4(pack2(x[0], x[1]), pack2(x[2], x[3]), pack2(x[4], x[5]), pack2(x[6], x[7]));
+}
+__device__ __forceinline__ void zero8(float x[8]) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] = 0.0f;
+}
+
+// What every product knows: the sizes, the weights, the tables, and (after setup) its unit and range.
+struct Base {
+    int Din, H, D;
+    const float *w1, *b1, *w2, *b2;
+    Tables tb;
+    int unit, start, len;   // a row tile's pairs or a segment's
+    int item;               // the tile's or segment's number
+    __device__ bool tile(int x) {
+        if (x >= tb.counts[0]) return false;
+        item = x, unit = tb.tile_unit[x], start = tb.tile_start[x], len = tb.tile_rows[x];
+        return true;
+    }
+    __device__ bool segment(int x) {
+        if (x >= tb.counts[1]) return false;
+        item = x, unit = tb.seg_unit[x], start = tb.seg_start[x], len = tb.seg_len[x];
+        return true;
+    }
+    __device__ int64_t pair(int sorted_offset) const { return tb.order[start + sorted_offset]; }
+};
+
+// pre[pair] = v[pair] W1[u] + b1[u]
+template <class E, bool BF>
+struct First : Base {
+    const float* v;
+    E* pre;
+    __device__ bool setup(int x) { return tile(x); }
+    __device__ int rows() const { return len; }
+    __device__ int cols() const { return H; }
+    __device__ int depth() const { return Din; }
+    __device__ void a(int m, int k, float x[8]) const {
+        if (m < len && k < Din) load8(v + pair(m) * Din + k, x);
+        else zero8(x);
+    }
+    __device__ void b(int c, int k, float x[8]) const {
+        const float* src = w1 + (static_cast<int64_t>(unit) * Din + k) * H + c;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = (c < H && k + i < Din) ? src[static_cast<int64_t>(i) * H] : 0.0f;
+    }
+    __device__ void store(int m, int c0, float acc[8]) const {
+        if (m >= len || c0 >= H) return;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = rnd<BF>(acc[i] + rnd<BF>(b1[unit * H + c0 + i]));
+        store8(pre + pair(m) * H + c0, acc);
+    }
+};
+
+// out[pair] = act(pre[pair]) W2[u] + b2[u]
+template <class E, bool BF>
+struct Second : Base {
+    const E* pre;
+    E* out;
+    __device__ bool setup(int x) { return tile(x); }
+    __device__ int rows() const { return len; }
+    __device__ int cols() const { return D; }
+    __device__ int depth() const { return H; }
+    __device__ void a(int m, int k, float x[8]) const {
+        if (m < len && k < H) {
+            load8(pre + pair(m) * H + k, x);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = rnd<BF>(gelu_erf(x[i]));
+        } else {
+            zero8(x);
+        }
+    }
+    __device__ void b(int c, int k, float x[8]) const {
+        const float* src = w2 + (static_cast<int64_t>(unit) * H + k) * D + c;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = (c < D && k + i < H) ? src[static_cast<int64_t>(i) * D] : 0.0f;
+    }
+    __device__ void store(int m, int c0, float acc[8]) const {
+        if (m >= len || c0 >= D) return;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = rnd<BF>(acc[i] + rnd<BF>(b2[unit * D + c0 + i]));
+        store8(out + pair(m) * D + c0, acc);
+    }
+};
+
+// dpre[sorted] = (dout[pair] W2[u]^T) * act'(pre[pair])
+template <class E, bool BF>
+struct DPre : Base {
+    const E *pre, *dout;
+    E* dpre;   // in sorted order
+    __device__ bool setup(int x) { return tile(x); }
+    __device__ int rows() const { return len; }
+    __device__ int cols() const { return H; }
+    __device__ int depth() const { return D; }
+    __device__ void a(int m, int k, float x[8]) const {
+        if (m < len && k < D) load8(dout + pair(m) * D + k, x);
+        else zero8(x);
+    }
+    __device__ void b(int c, int k, float x[8]) const {
+        if (c < H && k < D) load8(w2 + (static_cast<int64_t>(unit) * H + c) * D + k, x);
+        else zero8(x);
+    }
+    __device__ void store(int m, int c0, float acc[8]) const {
+        if (m >= len || c0 >= H) return;
+        float p[8];
+        load8(pre + pair(m) * H + c0, p);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = rnd<BF>(rnd<BF>(acc[i]) * gelu_erf_grad(p[i]));
+        store8(dpre + static_cast<int64_t>(start + m) * H + c0, acc);
+    }
+};
+
+// dv[pair] = dpre[sorted] W1[u]^T
+template <class E, bool BF>
+struct DInput : Base {
+    const E* dpre;
+    float* dv;
+    __device__ bool setup(int x) { return tile(x); }
+    __device__ int rows() const { return len; }
+    __device__ int cols() const { return Din; }
+    __device__ int depth() const { return H; }
+    __device__ void a(int m, int k, float x[8]) const {
+        if (m < len && k < H) load8(dpre + static_cast<int64_t>(start + m) * H + k, x);
+        else zero8(x);
+    }
+    __device__ void b(int c, int k, float x[8]) const {
+        if (c < Din && k < H) load8(w1 + (static_cast<int64_t>(unit) * Din + c) * H + k, x);
+        else zero8(x);
+    }
+    __device__ void store(int m, int c0, float acc[8]) const {
+        if (m >= len || c0 >= Din) return;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = rnd<BF>(acc[i]);
+        store8(dv + pair(m) * Din + c0, acc);
+    }
+};
+
+// partial[segment] = v[pairs]^T dpre[sorted]      [4d, H], K = the segment's pairs
+template <class E, bool BF>
+struct DWeight1 : Base {
+    const float* v;
+    const E* dpre;
+    float* partial;
+    __device__ bool setup(int x) { return segment(x); }
+    __device__ int rows() const { return Din; }
+    __device__ int cols() const { return H; }
+    __device__ int depth() const { return len; }
+    __device__ void a(int m, int k, float x[8]) const {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = (m < Din && k + i < len) ? v[pair(k + i) * Din + m] : 0.0f;
+    }
+    __device__ void b(int c, int k, float x[8]) const {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = (c < H && k + i < len) ? load1(dpre + static_cast<int64_t>(start + k + i) * H + c) : 0.0f;
+    }
+    __device__ void store(int m, int c0, float acc[8]) const {
+        if (m >= Din || c0 >= H) return;
+        store8(partial + (static_cast<int64_t>(item) * Din + m) * H + c0, acc);
+    }
+};
+
+// partial[segment] = act(pre[pairs])^T dout[pairs]      [H, d], K = the segment's pairs
+template <class E, bool BF>
+struct DWeight2 : Base {
+    const E *pre, *dout;
+    float* partial;
+    __device__ bool setup(int x) { return segment(x); }
+    __device__ int rows() const { return H; }
+    __device__ int cols() const { return D; }
+    __device__ int depth() const { return len; }
+    __device__ void a(int m, int k, float x[8]) const {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = (m < H && k + i < len) ? rnd<BF>(gelu_erf(load1(pre + pair(k + i) * H + m))) : 0.0f;
+    }
+    __device__ void b(int c, int k, float x[8]) const {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = (c < D && k + i < len) ? load1(dout + pair(k + i) * D + c) : 0.0f;
+    }
+    __device__ void store(int m, int c0, float acc[8]) const {
+        if (m >= H || c0 >= D) return;
+        store8(partial + (static_cast<int64_t>(item) * H + m) * D + c0, acc);
+    }
+};
+
+// ---- the tile products ----------------------------------------------------------------------------------
+
+// bf16 operands on the tensor cores: block (x: tile or segment, y: 128 rows, z: BN columns).
+template <class Op, int BN>
+__global__ void __launch_bounds__(128) k_units_tc(Op op, int* status) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ uint32_t tmem_slot;
+    if (!op.setup(blockIdx.x)) return;   // the same answer for the whole block
+    const int m0 = blockIdx.y * 128, n0 = blockIdx.z * BN;
+    if (m0 >= op.rows() || n0 >= op.cols()) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    uint4* As = reinterpret_cast<uint4*>(dyn);
+    uint4* Bs = As + (kChunk / 8) * 128;
+    if (tid == 0) mbar_init(&bar, 1);
+    if (warp == 0) tmem_alloc(&tmem_slot, BN < 32 ? 32 : BN);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t taddr = tmem_slot;
+    const uint32_t idesc = umma_idesc_bf16(128, BN);
+    const int K = op.depth();
+    int phase = 0;
+    float x[8];
+    for (int k0 = 0; k0 < K; k0 += kChunk, ++phase) {
+        const int planes = min(kChunk, ((K - k0) + 15) & ~15) >> 3;   // whole K = 16 steps
+        for (int idx = tid; idx < planes * 128; idx += 128) {
+            op.a(m0 + (idx & 127), k0 + (idx >> 7) * 8, x);
+            As[idx] = make_uint4(pack2(x[0], x[1]), pack2(x[2], x[3]), pack2(x[4], x[5]), pack2(x[6], x[7]));
+        }
+        for (int idx = tid; idx < planes * BN; idx += 128) {
+            op.b(n0 + idx % BN, k0 + (idx / BN) * 8, x);
+            Bs[idx] = make_uint4(pack2(x[0], x[1]), pack2(x[2], x[3]), pack2(x[4], x[5]), pack2(x[6], x[7]));
+        }
+        fence_async_smem();
+        __syncthreads();
+        if (tid < 32) {   // the whole first warp, converged after the barrier: one elected lane issues
+            tcgen05_fence_after();
+            umma_chain(taddr, umma_desc(As, 128), umma_desc(Bs, BN), idesc, planes >> 1, umma_kstep(128), umma_kstep(BN), k0 > 0);
+            umma_commit(&bar);
+        }
+        mbar_wait(&bar, phase & 1, status);   // the products have read the operands: the next chunk may be staged
+        tcgen05_fence_after();
+    }
+    for (int cb = 0; cb < BN; cb += 8) {
+        tmem_ld8(tmem_addr(taddr, warp * 32, cb), x);
+        op.store(m0 + warp * 32 + lane, n0 + cb, x);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(taddr, BN < 32 ? 32 : BN);
+}
+
+// fp32 operands on the CUDA cores: block (x: tile or segment, y: 64 rows, z: 64 columns), a thread 2 x 8
+// outputs, K in chunks of 16, every sum in K order.
+template <class Op>
+__global__ void __launch_bounds__(256) k_units_simt(Op op) {
+    __shared__ float As[16][64], Bs[16][64];
+    if (!op.setup(blockIdx.x)) return;
+    const int m0 = blockIdx.y * 64, n0 = blockIdx.z * 64;
+    if (m0 >= op.rows() || n0 >= op.cols()) return;
+    const int tid = threadIdx.x, ty = tid >> 3, tx = tid & 7;
+    const int K = op.depth();
+    float acc[2][8] = {};
+    float x[8];
+    for (int k0 = 0; k0 < K; k0 += 16) {
+        const int r = tid & 63, half = (tid >> 6) & 1;
+        if (tid < 128) op.a(m0 + r, k0 + 8 * half, x);
+        else op.b(n0 + r, k0 + 8 * half, x);
+        float(*dst)[64] = tid < 128 ? As : Bs;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dst[8 * half + i][r] = x[i];
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < 16; ++kk) {
+            const float a0 = As[kk][2 * ty], a1 = As[kk][2 * ty + 1];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float bv = Bs[kk][8 * tx + i];
+                acc[0][i] = fmaf(a0, bv, acc[0][i]);
+                acc[1][i] = fmaf(a1, bv, acc[1][i]);
+            }
+        }
+        __syncthreads();
+    }
+    op.store(m0 + 2 * ty, n0 + 8 * tx, acc[0]);
+    op.store(m0 + 2 * ty + 1, n0 + 8 * tx, acc[1]);
+}
+
+// d_w[u][e] = round(sum over the unit's segments, in order, of partial[segment][e]); zero for a unit no pair chose
+template <bool BF>
+__global__ void __launch_bounds__(256) k_units_wgrad(const float* partial, int64_t elems, int M, Tables tb, float* dw) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * 256;
+    for (int64_t e = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; e < elems * M; e += stride) {
+        const int u = static_cast<int>(e / elems);
+        const int64_t at = e - static_cast<int64_t>(u) * elems;
+        float sum = 0.0f;
+        for (int s = tb.seg_first[u]; s < tb.seg_first[u + 1]; ++s) sum += partial[static_cast<int64_t>(s) * elems + at];
+        dw[e] = rnd<BF>(sum);
+    }
+}
+
+// d_b[u][c] = round(sum over the unit's pairs of x[row][c]): block (unit, 32 columns), 8 rows at a time
+template <class E, bool BF, bool SORTED>
+__global__ void __launch_bounds__(256) k_units_bgrad(const E* x, int width, Tables tb, float* db) {
+    __shared__ float part[8][33];
+    const int u = blockIdx.x, c = blockIdx.y * 32 + (threadIdx.x & 31), lane_row = threadIdx.x >> 5;
+    const int begin = tb.unit_base[u], end = tb.unit_base[u + 1];
+    float sum = 0.0f;
+    if (c < width)
+        for (int p = begin + lane_row; p < end; p += 8) {
+            const int64_t row = SORTED ? p : tb.order[p];
+            sum += load1(x + row * width + c);
+        }
+    part[lane_row][threadIdx.x & 31] = sum;
+    __syncthreads();
+    if (lane_row == 0 && c < width) {
+        float total = 0.0f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) total += part[r][threadIdx.x & 31];
+        db[static_cast<int64_t>(u) * width + c] = rnd<BF>(total);
+    }
+}
+
+// ---- host ---------------------------------------------------------------------------------------------
+
+size_t up256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+struct Plan {
+    int blocks, max_tiles, seg, max_segs;
+    size_t bytes;
+    size_t off_tables[12];
+    size_t off_dpre, off_partial1, off_partial2;
+};
+
+Plan make_plan(const HsnwUnits* u, int64_t pairs, bool backward) {
+    Plan p{};
+    const int M = u->n_units;
+    p.blocks = static_cast<int>((pairs + kSortBlock - 1) / kSortBlock);
+    p.max_tiles = static_cast<int>((pairs + kTile - 1) / kTile) + M;
+    int64_t seg = (pairs + 63) / 64;
+    seg = (seg + kChunk - 1) / kChunk * kChunk;
+    p.seg = static_cast<int>(seg < 1024 ? 1024 : seg);
+    p.max_segs = static_cast<int>((pairs + p.seg - 1) / p.seg) + M;
+    size_t at = 256;   // the status word
+    const size_t sizes[12] = {
+        static_cast<size_t>(pairs), static_cast<size_t>(p.blocks) * M, static_cast<size_t>(M) + 1, static_cast<size_t>(M) + 1,
+        static_cast<size_t>(M) + 1, static_cast<size_t>(p.max_tiles), static_cast<size_t>(p.max_tiles), static_cast<size_t>(p.max_tiles),
+        static_cast<size_t>(p.max_segs), static_cast<size_t>(p.max_segs), static_cast<size_t>(p.max_segs), 2};
+    for (int i = 0; i < 12; ++i) {
+        p.off_tables[i] = at;
+        at += up256(sizes[i] * sizeof(int));
+    }
+    if (backward) {
+        const size_t elem = u->prod_bf16 ? 2 : 4;
+        p.off_dpre = at;
+        at += up256(static_cast<size_t>(pairs) * u->hidden * elem);
+        p.off_partial1 = at;
+        at += up256(static_cast<size_t>(p.max_segs) * u->d_in * u->hidden * sizeof(float));
+        p.off_partial2 = at;
+        at += up256(static_cast<size_t>(p.max_segs) * u->hidden * u->d_out * sizeof(float));
+    }
+    p.bytes = at;
+    return p;
+}
+
+Tables make_tables(const Plan& p, void* scratch) {
+    unsigned char* base = static_cast<unsigned char*>(scratch);
+    auto at = [&](int i) { return reinterpret_cast<int*>(base + p.off_tables[i]); };
+    return Tables{at(0), at(1), at(2), at(3), at(4), at(5), at(6), at(7), at(8), at(9), at(10), at(11)};
+}
+
+int check_units(const HsnwUnits* u, int64_t pairs, const char* what) {
+    if (!u || pairs < 0) return hsnw_fail(HSNW_E_ARG, what);
+    if (u->n_units < 1 || u->d_in < 1 || u->hidden < 1 || u->d_out < 1 || !u->w1 || !u->b1 || !u->w2 || !u->b2)
+        return hsnw_fail(HSNW_E_ARG, "units: sizes or weights missing");
+    if (u->n_units > kMaxUnits) return hsnw_fail(HSNW_E_UNSUPPORTED, "units: at most 256 units");
+    if (u->d_in % 8 || u->hidden % 8 || u->d_out % 8) return hsnw_fail(HSNW_E_UNSUPPORTED, "units: the three widths in multiples of 8");
+    if (pairs >= (static_cast<int64_t>(1) << 31) - kSortBlock) return hsnw_fail(HSNW_E_UNSUPPORTED, "units: fewer than 2^31 pairs");
+    if ((reinterpret_cast<uintptr_t>(u->w1) | reinterpret_cast<uintptr_t>(u->w2)) & 15)
+        return hsnw_fail(HSNW_E_ARG, "units: weights not 16-byte aligned");
+    return HSNW_OK;
+}
+
+int sort_pairs(const HsnwUnits* u, const int64_t* unit_idx, int64_t pairs, const Plan& p, const Tables& tb, int* status, cudaStream_t stream) {
+    const size_t shared = sizeof(int) * 32 * u->n_units;
+    k_units_count<<<p.blocks, kSortBlock, shared, stream>>>(unit_idx, pairs, u->n_units, tb, status);
+    k_units_scan<<<1, 256, 0, stream>>>(p.blocks, u->n_units, p.seg, tb);
+    k_units_place<<<p.blocks, kSortBlock, shared, stream>>>(unit_idx, pairs, u->n_units, tb, status);
+    return hsnw_check_launch("units: sort");
+}
+
+template <class Op>
+void fill_base(Op& op, const HsnwUnits* u, const Tables& tb) {
+    op.Din = u->d_in, op.H = u->hidden, op.D = u->d_out;
+    op.w1 = u->w1, op.b1 = u->b1, op.w2 = u->w2, op.b2 = u->b2;
+    op.tb = tb;
+}
+
+template <class Op, int BN>
+void launch_tc(const Op& op, int items, int rows, int cols, int* status, cudaStream_t stream) {
+    const size_t shared = static_cast<size_t>(kChunk / 8) * (128 + BN) * 16;
+    k_units_tc<Op, BN><<<dim3(items, (rows + 127) / 128, (cols + BN - 1) / BN), 128, shared, stream>>>(op, status);
+}
+template <class Op>
+void launch_simt(const Op& op, int items, int rows, int cols, cudaStream_t stream) {
+    k_units_simt<Op><<<dim3(items, (rows + 63) / 64, (cols + 63) / 64), 256, 0, stream>>>(op);
+}
+
+template <class E, bool BF>
+int forward_t(const HsnwUnits* u, const float* v, int64_t pairs, E* pre, E* out, const Plan& p, const Tables& tb, int* status,
+              cudaStream_t stream) {
+    First<E, BF> first;
+    fill_base(first, u, tb);
+    first.v = v, first.pre = pre;
+    Second<E, BF> second;
+    fill_base(second, u, tb);
+    second.pre = pre, second.out = out;
+    if (BF) {
+        launch_tc<First<E, BF>, 128>(first, p.max_tiles, kTile, u->hidden, status, stream);
+        if (u->d_out <= 64) launch_tc<Second<E, BF>, 64>(second, p.max_tiles, kTile, u->d_out, status, stream);
+        else launch_tc<Second<E, BF>, 128>(second, p.max_tiles, kTile, u->d_out, status, stream);
+    } else {
+        launch_simt(first, p.max_tiles, kTile, u->hidden, stream);
+        launch_simt(second, p.max_tiles, kTile, u->d_out, stream);
+    }
+    return hsnw_check_launch("units_forward");
+}
+
+template <class E, bool BF>
+int backward_t(const HsnwUnits* u, const float* v, int64_t pairs, const E* pre, const E* dout, float* dv, float* dw1, float* db1, float* dw2,
+               float* db2, const Plan& p, const Tables& tb, void* scratch, int* status, cudaStream_t stream) {
+    unsigned char* base = static_cast<unsigned char*>(scratch);
+    E* dpre = reinterpret_cast<E*>(base + p.off_dpre);
+    float* partial1 = reinterpret_cast<float*>(base + p.off_partial1);
+    float* partial2 = reinterpret_cast<float*>(base + p.off_partial2);
+    DPre<E, BF> dp;
+    fill_base(dp, u, tb);
+    dp.pre = pre, dp.dout = dout, dp.dpre = dpre;
+    DInput<E, BF> di;
+    fill_base(di, u, tb);
+    di.dpre = dpre, di.dv = dv;
+    DWeight1<E, BF> g1;
+    fill_base(g1, u, tb);
+    g1.v = v, g1.dpre = dpre, g1.partial = partial1;
+    DWeight2<E, BF> g2;
+    fill_base(g2, u, tb);
+    g2.pre = pre, g2.dout = dout, g2.partial = partial2;
+    if (BF) {
+        launch_tc<DPre<E, BF>, 128>(dp, p.max_tiles, kTile, u->hidden, status, stream);
+        launch_tc<DInput<E, BF>, 128>(di, p.max_tiles, kTile, u->d_in, status, stream);
+        launch_tc<DWeight1<E, BF>, 128>(g1, p.max_segs, u->d_in, u->hidden, status, stream);
+        if (u->d_out <= 64) launch_tc<DWeight2<E, BF>, 64>(g2, p.max_segs, u->hidden, u->d_out, status, stream);
+        else launch_tc<DWeight2<E, BF>, 128>(g2, p.max_segs, u->hidden, u->d_out, status, stream);
+    } else {
+        launch_simt(dp, p.max_tiles, kTile, u->hidden, stream);
+        launch_simt(di, p.max_tiles, kTile, u->d_in, stream);
+        launch_simt(g1, p.max_segs, u->d_in, u->hidden, stream);
+        launch_simt(g2, p.max_segs, u->hidden, u->d_out, stream);
+    }
+    const int M = u->n_units;
+    const int64_t e1 = static_cast<int64_t>(u->d_in) * u->hidden, e2 = static_cast<int64_t>(u->hidden) * u->d_out;
+    k_units_wgrad<BF><<<static_cast<unsigned>(std::min<int64_t>((e1 * M + 255) / 256, 4096)), 256, 0, stream>>>(partial1, e1, M, tb, dw1);
+    k_units_wgrad<BF><<<static_cast<unsigned>(std::min<int64_t>((e2 * M + 255) / 256, 4096)), 256, 0, stream>>>(partial2, e2, M, tb, dw2);
+    k_units_bgrad<E, BF, true><<<dim3(M, (u->hidden + 31) / 32), 256, 0, stream>>>(dpre, u->hidden, tb, db1);
+    k_units_bgrad<E, BF, false><<<dim3(M, (u->d_out + 31) / 32), 256, 0, stream>>>(dout, u->d_out, tb, db2);
+    return hsnw_check_launch("units_backward");
+}
+
+int check_scratch(const Plan& p, void* scratch, int64_t bytes) {
+    if (!scratch || bytes < static_cast<int64_t>(p.bytes) || (reinterpret_cast<uintptr_t>(scratch) & 255))
+        return hsnw_fail(HSNW_E_ARG, "units: scratch too small or not 256-byte aligned (hsnw_units_scratch_bytes)");
+    return HSNW_OK;
+}
+
+}  // namespace
+
+extern "C" int64_t hsnw_units_scratch_bytes(const HsnwUnits* units, int64_t pairs, int backward) {
+    if (!units || pairs < 0 || units->n_units < 1 || units->n_units > kMaxUnits) return 0;
+    return static_cast<int64_t>(make_plan(units, pairs, backward != 0).bytes);
+}
+
+extern "C" int hsnw_units_forward(const HsnwUnits* units, const float* v, const int64_t* unit_idx, int64_t pairs, void* pre, void* out,
+                                  void* scratch, int64_t scratch_bytes, void* stream_) {
+    if (int rc = hsnw_require_prepared()) return rc;
+    if (int rc = check_units(units, pairs, "units_forward: null or negative")) return rc;
+    const Plan p = make_plan(units, pairs, false);
+    if (int rc = check_scratch(p, scratch, scratch_bytes)) return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int* status = static_cast<int*>(scratch);
+    if (cudaMemsetAsync(status, 0, sizeof(int), stream) != cudaSuccess) return hsnw_check_launch("units_forward");
+    if (pairs == 0) return HSNW_OK;
+    if (!v || !unit_idx || !pre || !out) return hsnw_fail(HSNW_E_ARG, "units_forward: null tensor");
+    if ((reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(pre) | reinterpret_cast<uintptr_t>(out)) & 15)
+        return hsnw_fail(HSNW_E_ARG, "units_forward: tensors not 16-byte aligned");
+    const Tables tb = make_tables(p, scratch);
+    hsnw_profile_mark(HSNW_K_UNITS_FWD, stream);
+    if (int rc = sort_pairs(units, unit_idx, pairs, p, tb, status, stream)) return rc;
+    if (units->prod_bf16)
+        return forward_t<__nv_bfloat16, true>(units, v, pairs, static_cast<__nv_bfloat16*>(pre), static_cast<__nv_bfloat16*>(out), p, tb, status,
+                                              stream);
+    return forward_t<float, false>(units, v, pairs, static_cast<float*>(pre), static_cast<float*>(out), p, tb, status, stream);
+}
+
+extern "C" int hsnw_units_backward(const HsnwUnits* units, const float* v, const int64_t* unit_idx, int64_t pairs, const void* pre,
+                                   const void* d_out, float* d_v, float* d_w1, float* d_b1, float* d_w2, float* d_b2, void* scratch,
+                                   int64_t scratch_bytes, void* stream_) {
+    if (int rc = hsnw_require_prepared()) return rc;
+    if (int rc = check_units(units, pairs, "units_backward: null or negative")) return rc;
+    const Plan p = make_plan(units, pairs, true);
+    if (int rc = check_scratch(p, scratch, scratch_bytes)) return rc;
+    if (!d_w1 || !d_b1 || !d_w2 || !d_b2) return hsnw_fail(HSNW_E_ARG, "units_backward: null gradient");
+    if (pairs > 0 && (!v || !unit_idx || !pre || !d_out || !d_v)) return hsnw_fail(HSNW_E_ARG, "units_backward: null tensor");
+    if ((reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(pre) | reinterpret_cast<uintptr_t>(d_out) | reinterpret_cast<uintptr_t>(d_v)
+         | reinterpret_cast<uintptr_t>(d_w1) | reinterpret_cast<uintptr_t>(d_w2)) & 15)
+        return hsnw_fail(HSNW_E_ARG, "units_backward: tensors not 16-byte aligned");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int* status = static_cast<int*>(scratch);
+    if (cudaMemsetAsync(status, 0, sizeof(int), stream) != cudaSuccess) return hsnw_check_launch("units_backward");
+    if (pairs == 0) {   // no pair chose any unit: zero gradients
+        const size_t m = static_cast<size_t>(units->n_units) * sizeof(float);
+        if (cudaMemsetAsync(d_w1, 0, m * units->d_in * units->hidden, stream) != cudaSuccess
+            || cudaMemsetAsync(d_b1, 0, m * units->hidden, stream) != cudaSuccess
+            || cudaMemsetAsync(d_w2, 0, m * units->hidden * units->d_out, stream) != cudaSuccess
+            || cudaMemsetAsync(d_b2, 0, m * units->d_out, stream) != cudaSuccess)
+            return hsnw_check_launch("units_backward");
+        return HSNW_OK;
+    }
+    const Tables tb = make_tables(p, scratch);
+    hsnw_profile_mark(HSNW_K_UNITS_BWD, stream);
+    if (int rc = sort_pairs(units, unit_idx, pairs, p, tb, status, stream)) return rc;
+    if (units->prod_bf16)
+        return backward_t<__nv_bfloat16, true>(units, v, pairs, static_cast<const __nv_bfloat16*>(pre), static_cast<const __nv_bfloat16*>(d_out),
+                                               d_v, d_w1, d_b1, d_w2, d_b2, p, tb, scratch, status, stream);
+    return backward_t<float, false>(units, v, pairs, static_cast<const float*>(pre), static_cast<const float*>(d_out), d_v, d_w1, d_b1, d_w2,
+                                    d_b2, p, tb, scratch, status, stream);
+}
+
+void hsnw_units_set_attributes() {
+    bool ok = true;
+#define HSNW_UNITS_OPT(OP, BN) ok = ok && hsnw_opt_in(reinterpret_cast<const void*>(k_units_tc<OP<__nv_bfloat16, true>, BN>), #OP)
+    HSNW_UNITS_OPT(First, 128);
+    HSNW_UNITS_OPT(Second, 64);
+    HSNW_UNITS_OPT(Second, 128);
+    HSNW_UNITS_OPT(DPre, 128);
+    HSNW_UNITS_OPT(DInput, 128);
+    HSNW_UNITS_OPT(DWeight1, 128);
+    HSNW_UNITS_OPT(DWeight2, 64);
+    HSNW_UNITS_OPT(DWeight2, 128);
+#undef HSNW_UNITS_OPT
+    if (!ok) hsnw_attribute_failed();
+}

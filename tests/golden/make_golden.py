@@ -688,6 +688,43 @@ def make_decode(root: Path) -> None:
         print("decode", name, tuple(logits.shape), logits.dtype)
 
 
+def make_units(root: Path) -> None:
+    """``UnitBank.forward_grouped`` (``python/hsn/model/units.py:356-414``) with its autograd backward on seeded
+    pairs: float64, float32 and under ``torch.autocast("cpu", dtype=torch.bfloat16)``; a unit that no pair chose,
+    a count that is no multiple of a tile, the ``record`` of the first layer's pre-activation."""
+    import torch
+    from hsn.model.units import UnitBank
+
+    cases = {"a": dict(M=5, d=16, H=48, P=333, absent=(3,)), "b": dict(M=3, d=8, H=32, P=70, absent=())}
+    for case, c in cases.items():
+        for name, dtype, auto in (("f64", torch.float64, False), ("f32", torch.float32, False), ("bf16", torch.float32, True)):
+            torch.manual_seed(31)
+            bank = UnitBank(c["M"], c["d"], c["H"], "gelu", init="fan_in").to(dtype)
+            gen = torch.Generator().manual_seed(32)
+            with torch.no_grad():
+                bank.b1.copy_((torch.randn(bank.b1.shape, generator=gen) * 0.3).to(dtype))
+                bank.b2.copy_((torch.randn(bank.b2.shape, generator=gen) * 0.3).to(dtype))
+            present = [j for j in range(c["M"]) if j not in c["absent"]]
+            idx = torch.tensor(present)[torch.randint(0, len(present), (c["P"],), generator=gen)]
+            v = torch.randn(c["P"], 4 * c["d"], generator=gen).to(dtype).requires_grad_(True)
+            cot = torch.randn(c["P"], c["d"], generator=gen).to(dtype)
+            record: dict = {}
+            if auto:
+                with torch.autocast("cpu", dtype=torch.bfloat16):
+                    out = bank.forward_grouped(v, idx, record=record)
+                    loss = (out.to(dtype) * cot).sum()   # the cotangent reaches the pass as bfloat16(cot)
+            else:
+                out = bank.forward_grouped(v, idx, record=record)
+                loss = (out * cot).sum()
+            loss.backward()
+            np.savez_compressed(
+                HERE / f"units_{case}_{name}.npz", v=_np(v), unit_idx=idx.numpy(), cot=_np(cot), out=_np(out.to(dtype)),
+                hidden=_np(record["hidden"].to(dtype)), W1=_np(bank.W1), b1=_np(bank.b1), W2=_np(bank.W2), b2=_np(bank.b2),
+                d_v=_np(v.grad), d_W1=_np(bank.W1.grad), d_b1=_np(bank.b1.grad), d_W2=_np(bank.W2.grad), d_b2=_np(bank.b2.grad),
+            )  # fmt: skip
+            print("units", case, name, tuple(out.shape), out.dtype, record["hidden"].dtype)
+
+
 def make_snapshot(root: Path) -> None:
     """``CellGraphState.snapshot`` (``python/hsn/model/state.py:363``) and ``pack_cell_state``
     (``python/hsn/train/checkpoint.py:260``): seeded states in float32 and bfloat16, their metas and the
@@ -731,7 +768,7 @@ def main() -> None:
     steps = {
         "select": make_select, "update": make_update, "recurrence": make_recurrence,
         "windows": make_windows, "bf16": make_windows_bf16, "prologue": make_prologue, "chain": make_chain,
-        "sweep": make_sweep, "snapshot": make_snapshot, "decode": make_decode,
+        "sweep": make_sweep, "snapshot": make_snapshot, "decode": make_decode, "units": make_units,
     }  # fmt: skip
     for key, fn in steps.items():
         if not args.only or key in args.only.split(","):

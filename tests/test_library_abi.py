@@ -22,7 +22,7 @@ def lib() -> ctypes.CDLL:
 
 
 def test_every_declared_symbol_is_exported(lib: ctypes.CDLL) -> None:
-    text = HEADER.read_text() + (HEADER.parent / "hsn_trainer_b200.h").read_text()
+    text = "".join((HEADER.parent / name).read_text() for name in ("hsn_window_b200.h", "hsn_trainer_b200.h", "hsn_units_b200.h"))
     declared = set(re.findall(r"\b(hsnw_[a-z_]+)\s*\(", text))
     assert declared, "no entry points found in the header"
     assert declared == set(_lib.SYMBOLS), declared ^ set(_lib.SYMBOLS)
@@ -37,6 +37,7 @@ def test_structures_match_the_header() -> None:
     assert ctypes.sizeof(_lib.HsnwModel) == 12 * 4 + 6 * 4 + 29 * 8
     assert ctypes.sizeof(_lib.HsnwForward) == 4 * 4 + 30 * 8 + 8
     assert ctypes.sizeof(_lib.HsnwBackward) == 4 * 4 + 20 * 8 + 8
+    assert ctypes.sizeof(_lib.HsnwUnits) == 6 * 4 + 4 * 8 and _lib.HsnwUnits.w1.offset == 24
 
 
 def test_version_and_errors_without_a_device(lib: ctypes.CDLL) -> None:
@@ -70,6 +71,11 @@ def test_no_gpu_means_a_loud_failure_not_a_fallback(lib: ctypes.CDLL) -> None:
     args = _lib.HsnWinArgs()
     code = lib.hsnw_launch(b"hsn_win_select", ctypes.byref(args), 1, 64, 0, None)
     assert code == _lib.E_STATE
+    from hsn_b200.kernels.units import grouped_forward
+
+    with pytest.raises(RuntimeError):   # the grouped unit pass has no CPU path either
+        grouped_forward(torch.zeros(4, 32), torch.zeros(4, dtype=torch.int64), torch.zeros(2, 32, 16), torch.zeros(2, 16),
+                        torch.zeros(2, 16, 8), torch.zeros(2, 8))
 
 
 def test_python_interface_keeps_the_reference_names() -> None:

@@ -364,3 +364,27 @@ def test_window_decode_equals_the_reference(name: str, tol: float) -> None:
         assert np.array_equal(got, z["logits"])
     else:
         np.testing.assert_allclose(got, z["logits"], rtol=tol, atol=tol * float(np.abs(z["logits"]).max()))
+
+
+@pytest.mark.parametrize("case", ["a", "b"])
+@pytest.mark.parametrize("name,tol", [("f64", 1e-12), ("f32", 1e-5), ("bf16", 1e-5)])
+def test_grouped_units_equal_the_reference(case: str, name: str, tol: float) -> None:
+    """The replay's grouped unit pass and its backward against ``UnitBank.forward_grouped`` with autograd on the
+    CPU: float64, float32, and under bf16 autocast, where the restatement reproduces the reference's bfloat16
+    values (the record to the bit, the gradients but for a rounding boundary of the activation's derivative)."""
+    from oracle import units_oracle as U
+
+    z = load_golden(f"units_{case}_{name}")
+    bf = name == "bf16"
+    bank = tuple(z[k] for k in ("W1", "b1", "W2", "b2"))
+    out, pre = U.forward_grouped(z["v"], z["unit_idx"], *bank, bf16=bf)
+    grads = U.backward_grouped(z["v"], z["unit_idx"], *bank, pre, z["cot"], bf16=bf)
+    if bf:
+        assert np.array_equal(pre, z["hidden"]) and np.array_equal(out, z["out"])
+    got = dict(out=out, hidden=pre, **dict(zip(("d_v", "d_W1", "d_b1", "d_W2", "d_b2"), grads, strict=True)))
+    for key, value in got.items():
+        np.testing.assert_allclose(value, z[key], rtol=0, atol=tol * float(np.abs(z[key]).max()), err_msg=key)
+    if case == "a":   # a unit no pair chose: zero gradients, as autograd leaves them
+        assert not np.any(z["unit_idx"] == 3) and not np.any(grads[1][3]) and not np.any(grads[4][3])
+    with pytest.raises(IndexError):
+        U.forward_grouped(z["v"], np.full_like(z["unit_idx"], z["W1"].shape[0]), *bank)
