@@ -18,16 +18,19 @@
 //             db1  = sum dpre, db2 = sum dout            column sums per unit
 //
 // With bf16 products each is a tcgen05 tile product: a 128 x BN output tile per block with the accumulator
-// in tensor memory, K in chunks of 128 staged by the block's threads as K-major core-matrix planes — a
-// source whose K runs along its rows is read 8 consecutive elements at a time, a source whose K runs across
-// its rows (the weights [K, N], and both operands of the weight gradients, whose K is the pair) is read with
-// the warp's lanes along the contiguous dimension, eight strided loads per 16-byte unit — with the operand's
-// own transformation (rounding to bfloat16, the activation) applied while it is staged. The epilogue adds
-// the bias, rounds, applies the activation's derivative, and writes through the sorted order so that every
-// result lands in the pairs' input order. The weight gradients' segments write float32 partial tiles that a
-// last kernel sums per unit in segment order (a fixed order: the same bits every run), rounds as the
-// reference's bfloat16 product does and widens to the parameters' float32. With fp32 products the same
-// operand and result functions feed a CUDA-core tile kernel (sums in K order).
+// in tensor memory, K in chunks of 128 staged by the block's threads as K-major core-matrix planes, 16 bytes
+// (8 consecutive K elements of one row) per store. Every operand is therefore kept with its K contiguous:
+// the weights are packed once per call as bfloat16 in both orientations ([K, N] and [N, K]); the operands of
+// the weight gradients, whose K is the pair, are written transposed — v and dout by a transposing gather
+// through the sorted order, dpre and act(pre) by the epilogue of the dpre product itself, which holds both
+// — as [width, sorted position] with every unit's range starting on a multiple of 8 and zeros in the
+// padding, so that a segment's 8 pairs are one aligned 16-byte load. The epilogues add the bias, round,
+// apply the activation's derivative, and write through the sorted order so that every result lands in the
+// pairs' input order. The weight gradients' segments write float32 partial tiles that a last kernel sums per
+// unit in segment order (a fixed order: the same bits every run), rounds as the reference's bfloat16
+// product does and widens to the parameters' float32; the bias gradients are row sums of the transposed
+// operands. With fp32 products the operand functions read the tensors as they are and feed a CUDA-core tile
+// kernel (sums in K order).
 #include "../../include/hsn_units_b200.h"
 #include "../../include/hsn_window_b200.h"
 #include "common.cuh"
@@ -49,7 +52,9 @@ constexpr int kMaxUnits = 256;
 struct Tables {
     int* order;        // [P] sorted position -> pair
     int* block_off;    // [blocks][M] pairs of unit u in earlier sort blocks
-    int* unit_base;    // [M + 1] first sorted position of a unit
+    int* unit_base;    // [M + 1] first sorted position of a unit, a multiple of 8 (the positions between a
+                       // unit's last pair and the next unit's first hold no pair: order = -1)
+    int* unit_count;   // [M] pairs of a unit
     int* tile_first;   // [M + 1] first tile of a unit
     int* seg_first;    // [M + 1] first segment of a unit
     int* tile_unit;    // [max tiles]
@@ -122,9 +127,10 @@ __global__ void __launch_bounds__(256) k_units_scan(int blocks, int M, int seg, 
         int base = 0, tiles = 0, segs = 0;
         for (int u = 0; u < M; ++u) {
             tb.unit_base[u] = base;
+            tb.unit_count[u] = total[u];
             tb.tile_first[u] = tiles;
             tb.seg_first[u] = segs;
-            base += total[u];
+            base += (total[u] + 7) & ~7;
             tiles += (total[u] + kTile - 1) / kTile;
             segs += (total[u] + seg - 1) / seg;
         }
@@ -176,7 +182,10 @@ __global__ void __launch_bounds__(kSortBlock) k_units_place(const int64_t* unit_
 }
 
 // ---- operands and results of the six products -------------------------------------------------------------
-// E: the type of pre, out, dout and dpre (bfloat16 with bf16 products, else float); BF: round as the bf16 pass does.
+// E: the type of pre, out, dout and dpre (bfloat16 with bf16 products, else float); BF: round as the bf16 pass
+// does. Every product has two views of its operands: a(), b() give 8 consecutive K elements as floats from
+// the tensors as the caller holds them (the CUDA-core kernel); a16(), b16() give them as one 16-byte unit of
+// bfloat16 from the packed and transposed copies (the tensor-core kernel, BF only).
 
 template <bool BF>
 __device__ __forceinline__ float rnd(float x) {
@@ -201,22 +210,28 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&pair);
 }
+__device__ __forceinline__ uint4 pack8(const float x[8]) {
+    return make_uint4(pack2(x[0], x[1]), pack2(x[2], x[3]), pack2(x[4], x[5]), pack2(x[6], x[7]));
+}
+__device__ __forceinline__ uint4 unit16(const __nv_bfloat16* src) { return *reinterpret_cast<const uint4*>(src); }
 __device__ __forceinline__ void store8(float* dst, const float x[8]) {
     *reinterpret_cast<float4*>(dst) = make_float4(x[0], x[1], x[2], x[3]);
     *reinterpret_cast<float4*>(dst + 4) = make_float4(x[4], x[5], x[6], x[7]);
 }
-__device__ __forceinline__ void store8(__nv_bfloat16* dst, const float x[8]) {
-    *reinterpret_cast<uint4*>(dst) = make_uint4(pack2(x[0], x[1]), pack2(x[2], x[3]), pack2(x[4], x[5]), pack2(x[6], x[7]));
-}
+__device__ __forceinline__ void store8(__nv_bfloat16* dst, const float x[8]) { *reinterpret_cast<uint4*>(dst) = pack8(x); }
 __device__ __forceinline__ void zero8(float x[8]) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) x[i] = 0.0f;
 }
+constexpr uint4 kZero16 = {0u, 0u, 0u, 0u};
 
-// What every product knows: the sizes, the weights, the tables, and (after setup) its unit and range.
+// What every product knows: the sizes, the weights (float32 as the caller holds them; bfloat16 packed
+// [N, K] for the product that reads them), the tables, and (after setup) its unit and range.
 struct Base {
     int Din, H, D;
+    int ld;                 // sorted positions a row of a transposed operand holds
     const float *w1, *b1, *w2, *b2;
+    const __nv_bfloat16* wp;   // this product's packed weights
     Tables tb;
     int unit, start, len;   // a row tile's pairs or a segment's
     int item;               // the tile's or segment's number
@@ -233,7 +248,7 @@ struct Base {
     __device__ int64_t pair(int sorted_offset) const { return tb.order[start + sorted_offset]; }
 };
 
-// pre[pair] = v[pair] W1[u] + b1[u]
+// pre[pair] = v[pair] W1[u] + b1[u]                      wp: W1 as [M, H, Din]
 template <class E, bool BF>
 struct First : Base {
     const float* v;
@@ -251,6 +266,12 @@ struct First : Base {
 #pragma unroll
         for (int i = 0; i < 8; ++i) x[i] = (c < H && k + i < Din) ? src[static_cast<int64_t>(i) * H] : 0.0f;
     }
+    __device__ uint4 a16(int m, int k) const {
+        float x[8];
+        a(m, k, x);
+        return pack8(x);
+    }
+    __device__ uint4 b16(int c, int k) const { return (c < H && k < Din) ? unit16(wp + (static_cast<int64_t>(unit) * H + c) * Din + k) : kZero16; }
     __device__ void store(int m, int c0, float acc[8]) const {
         if (m >= len || c0 >= H) return;
 #pragma unroll
@@ -259,7 +280,7 @@ struct First : Base {
     }
 };
 
-// out[pair] = act(pre[pair]) W2[u] + b2[u]
+// out[pair] = act(pre[pair]) W2[u] + b2[u]               wp: W2 as [M, D, H]
 template <class E, bool BF>
 struct Second : Base {
     const E* pre;
@@ -282,6 +303,12 @@ struct Second : Base {
 #pragma unroll
         for (int i = 0; i < 8; ++i) x[i] = (c < D && k + i < H) ? src[static_cast<int64_t>(i) * D] : 0.0f;
     }
+    __device__ uint4 a16(int m, int k) const {
+        float x[8];
+        a(m, k, x);
+        return pack8(x);
+    }
+    __device__ uint4 b16(int c, int k) const { return (c < D && k < H) ? unit16(wp + (static_cast<int64_t>(unit) * D + c) * H + k) : kZero16; }
     __device__ void store(int m, int c0, float acc[8]) const {
         if (m >= len || c0 >= D) return;
 #pragma unroll
@@ -290,11 +317,13 @@ struct Second : Base {
     }
 };
 
-// dpre[sorted] = (dout[pair] W2[u]^T) * act'(pre[pair])
+// dpre[sorted] = (dout[pair] W2[u]^T) * act'(pre[pair])   wp: W2 as [M, H, D]; with bf16 products also
+// dpre and act(pre) transposed, [H, ld], zeros in the positions up to the next multiple of 8
 template <class E, bool BF>
 struct DPre : Base {
     const E *pre, *dout;
     E* dpre;   // in sorted order
+    __nv_bfloat16 *dpre_t, *hid_t;
     __device__ bool setup(int x) { return tile(x); }
     __device__ int rows() const { return len; }
     __device__ int cols() const { return H; }
@@ -307,17 +336,38 @@ struct DPre : Base {
         if (c < H && k < D) load8(w2 + (static_cast<int64_t>(unit) * H + c) * D + k, x);
         else zero8(x);
     }
+    __device__ uint4 a16(int m, int k) const { return (m < len && k < D) ? unit16(dout + pair(m) * D + k) : kZero16; }
+    __device__ uint4 b16(int c, int k) const { return (c < H && k < D) ? unit16(wp + (static_cast<int64_t>(unit) * H + c) * D + k) : kZero16; }
     __device__ void store(int m, int c0, float acc[8]) const {
-        if (m >= len || c0 >= H) return;
+        if (c0 >= H) return;
+        if (m >= len) {
+            if (BF && m < ((len + 7) & ~7)) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int64_t at = static_cast<int64_t>(c0 + i) * ld + start + m;
+                    dpre_t[at] = __float2bfloat16_rn(0.0f);
+                    hid_t[at] = __float2bfloat16_rn(0.0f);
+                }
+            }
+            return;
+        }
         float p[8];
         load8(pre + pair(m) * H + c0, p);
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = rnd<BF>(rnd<BF>(acc[i]) * gelu_erf_grad(p[i]));
         store8(dpre + static_cast<int64_t>(start + m) * H + c0, acc);
+        if (BF) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {   // a warp's lanes are consecutive sorted positions: 64 contiguous bytes a store
+                const int64_t at = static_cast<int64_t>(c0 + i) * ld + start + m;
+                dpre_t[at] = __float2bfloat16_rn(acc[i]);
+                hid_t[at] = __float2bfloat16_rn(gelu_erf(p[i]));
+            }
+        }
     }
 };
 
-// dv[pair] = dpre[sorted] W1[u]^T
+// dv[pair] = dpre[sorted] W1[u]^T                          wp: W1 as [M, Din, H]
 template <class E, bool BF>
 struct DInput : Base {
     const E* dpre;
@@ -334,6 +384,8 @@ struct DInput : Base {
         if (c < Din && k < H) load8(w1 + (static_cast<int64_t>(unit) * Din + c) * H + k, x);
         else zero8(x);
     }
+    __device__ uint4 a16(int m, int k) const { return (m < len && k < H) ? unit16(dpre + static_cast<int64_t>(start + m) * H + k) : kZero16; }
+    __device__ uint4 b16(int c, int k) const { return (c < Din && k < H) ? unit16(wp + (static_cast<int64_t>(unit) * Din + c) * H + k) : kZero16; }
     __device__ void store(int m, int c0, float acc[8]) const {
         if (m >= len || c0 >= Din) return;
 #pragma unroll
@@ -347,6 +399,7 @@ template <class E, bool BF>
 struct DWeight1 : Base {
     const float* v;
     const E* dpre;
+    const __nv_bfloat16 *v_t, *dpre_t;   // [Din, ld], [H, ld]
     float* partial;
     __device__ bool setup(int x) { return segment(x); }
     __device__ int rows() const { return Din; }
@@ -360,6 +413,8 @@ struct DWeight1 : Base {
 #pragma unroll
         for (int i = 0; i < 8; ++i) x[i] = (c < H && k + i < len) ? load1(dpre + static_cast<int64_t>(start + k + i) * H + c) : 0.0f;
     }
+    __device__ uint4 a16(int m, int k) const { return (m < Din && k < len) ? unit16(v_t + static_cast<int64_t>(m) * ld + start + k) : kZero16; }
+    __device__ uint4 b16(int c, int k) const { return (c < H && k < len) ? unit16(dpre_t + static_cast<int64_t>(c) * ld + start + k) : kZero16; }
     __device__ void store(int m, int c0, float acc[8]) const {
         if (m >= Din || c0 >= H) return;
         store8(partial + (static_cast<int64_t>(item) * Din + m) * H + c0, acc);
@@ -370,6 +425,7 @@ struct DWeight1 : Base {
 template <class E, bool BF>
 struct DWeight2 : Base {
     const E *pre, *dout;
+    const __nv_bfloat16 *hid_t, *dout_t;   // [H, ld], [D, ld]
     float* partial;
     __device__ bool setup(int x) { return segment(x); }
     __device__ int rows() const { return H; }
@@ -383,6 +439,8 @@ struct DWeight2 : Base {
 #pragma unroll
         for (int i = 0; i < 8; ++i) x[i] = (c < D && k + i < len) ? load1(dout + pair(k + i) * D + c) : 0.0f;
     }
+    __device__ uint4 a16(int m, int k) const { return (m < H && k < len) ? unit16(hid_t + static_cast<int64_t>(m) * ld + start + k) : kZero16; }
+    __device__ uint4 b16(int c, int k) const { return (c < D && k < len) ? unit16(dout_t + static_cast<int64_t>(c) * ld + start + k) : kZero16; }
     __device__ void store(int m, int c0, float acc[8]) const {
         if (m >= H || c0 >= D) return;
         store8(partial + (static_cast<int64_t>(item) * H + m) * D + c0, acc);
@@ -412,17 +470,10 @@ __global__ void __launch_bounds__(128) k_units_tc(Op op, int* status) {
     const uint32_t idesc = umma_idesc_bf16(128, BN);
     const int K = op.depth();
     int phase = 0;
-    float x[8];
     for (int k0 = 0; k0 < K; k0 += kChunk, ++phase) {
         const int planes = min(kChunk, ((K - k0) + 15) & ~15) >> 3;   // whole K = 16 steps
-        for (int idx = tid; idx < planes * 128; idx += 128) {
-            op.a(m0 + (idx & 127), k0 + (idx >> 7) * 8, x);
-            As[idx] = make_uint4(pack2(x[0], x[1]), pack2(x[2], x[3]), pack2(x[4], x[5]), pack2(x[6], x[7]));
-        }
-        for (int idx = tid; idx < planes * BN; idx += 128) {
-            op.b(n0 + idx % BN, k0 + (idx / BN) * 8, x);
-            Bs[idx] = make_uint4(pack2(x[0], x[1]), pack2(x[2], x[3]), pack2(x[4], x[5]), pack2(x[6], x[7]));
-        }
+        for (int idx = tid; idx < planes * 128; idx += 128) As[idx] = op.a16(m0 + (idx & 127), k0 + (idx >> 7) * 8);
+        for (int idx = tid; idx < planes * BN; idx += 128) Bs[idx] = op.b16(n0 + idx % BN, k0 + (idx / BN) * 8);
         fence_async_smem();
         __syncthreads();
         if (tid < 32) {   // the whole first warp, converged after the barrier: one elected lane issues
@@ -433,6 +484,7 @@ __global__ void __launch_bounds__(128) k_units_tc(Op op, int* status) {
         mbar_wait(&bar, phase & 1, status);   // the products have read the operands: the next chunk may be staged
         tcgen05_fence_after();
     }
+    float x[8];
     for (int cb = 0; cb < BN; cb += 8) {
         tmem_ld8(tmem_addr(taddr, warp * 32, cb), x);
         op.store(m0 + warp * 32 + lane, n0 + cb, x);
@@ -478,6 +530,44 @@ __global__ void __launch_bounds__(256) k_units_simt(Op op) {
     op.store(m0 + 2 * ty + 1, n0 + 8 * tx, acc[1]);
 }
 
+// out[b][c][r] = bfloat16(src[b][row(r)][c]) for r < rows, c < cols: 32 x 32 tiles through shared memory. With
+// `order`, row(r) = order[r] and a position that holds no pair (order < 0) becomes a column of zeros.
+template <class S>
+__global__ void __launch_bounds__(256) k_units_transpose(const S* src, int64_t src_batch, int rows, int cols, const int* order,
+                                                         __nv_bfloat16* out, int64_t out_batch, int ld) {
+    __shared__ float tile[32][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int r0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+    src += static_cast<int64_t>(blockIdx.z) * src_batch;
+    out += static_cast<int64_t>(blockIdx.z) * out_batch;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int r = r0 + ty + 8 * j, c = c0 + tx;
+        float value = 0.0f;
+        if (r < rows && c < cols) {
+            const int64_t row = order ? order[r] : r;
+            if (row >= 0) value = load1(src + row * cols + c);
+        }
+        tile[ty + 8 * j][tx] = value;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int c = c0 + ty + 8 * j, r = r0 + tx;
+        if (c < cols && r < rows) out[static_cast<int64_t>(c) * ld + r] = __float2bfloat16_rn(tile[tx][ty + 8 * j]);
+    }
+}
+
+// out[e] = bfloat16(src[e])
+__global__ void __launch_bounds__(256) k_units_cast(const float* src, int64_t n8, __nv_bfloat16* out) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * 256;
+    float x[8];
+    for (int64_t e = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; e < n8; e += stride) {
+        load8(src + 8 * e, x);
+        store8(out + 8 * e, x);
+    }
+}
+
 // d_w[u][e] = round(sum over the unit's segments, in order, of partial[segment][e]); zero for a unit no pair chose
 template <bool BF>
 __global__ void __launch_bounds__(256) k_units_wgrad(const float* partial, int64_t elems, int M, Tables tb, float* dw) {
@@ -496,7 +586,7 @@ template <class E, bool BF, bool SORTED>
 __global__ void __launch_bounds__(256) k_units_bgrad(const E* x, int width, Tables tb, float* db) {
     __shared__ float part[8][33];
     const int u = blockIdx.x, c = blockIdx.y * 32 + (threadIdx.x & 31), lane_row = threadIdx.x >> 5;
-    const int begin = tb.unit_base[u], end = tb.unit_base[u + 1];
+    const int begin = tb.unit_base[u], end = begin + tb.unit_count[u];
     float sum = 0.0f;
     if (c < width)
         for (int p = begin + lane_row; p < end; p += 8) {
@@ -513,15 +603,37 @@ __global__ void __launch_bounds__(256) k_units_bgrad(const E* x, int width, Tabl
     }
 }
 
+// The same from a transposed operand [width, ld]: block (unit, column), the unit's positions are one contiguous
+// run that starts on a multiple of 8 and is padded with zeros to one.
+__global__ void __launch_bounds__(128) k_units_bgrad_t(const __nv_bfloat16* x_t, int ld, int width, Tables tb, float* db) {
+    __shared__ float part[4];
+    const int u = blockIdx.x, c = blockIdx.y, tid = threadIdx.x;
+    const int units8 = (tb.unit_count[u] + 7) >> 3;
+    const __nv_bfloat16* row = x_t + static_cast<int64_t>(c) * ld + tb.unit_base[u];
+    float sum = 0.0f, x[8];
+    for (int e = tid; e < units8; e += 128) {
+        load8(row + 8 * e, x);
+        sum += ((x[0] + x[1]) + (x[2] + x[3])) + ((x[4] + x[5]) + (x[6] + x[7]));
+    }
+    sum = warp_sum(sum);
+    if ((tid & 31) == 0) part[tid >> 5] = sum;
+    __syncthreads();
+    if (tid == 0) db[static_cast<int64_t>(u) * width + c] = bf16r((part[0] + part[1]) + (part[2] + part[3]));
+}
+
 // ---- host ---------------------------------------------------------------------------------------------
 
 size_t up256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
+constexpr int kTables = 13;
+
 struct Plan {
     int blocks, max_tiles, seg, max_segs;
+    int ld;   // sorted positions: the pairs and every unit's padding to a multiple of 8
     size_t bytes;
-    size_t off_tables[12];
-    size_t off_dpre, off_partial1, off_partial2;
+    size_t off_tables[kTables];
+    size_t off_wa, off_wb;   // this call's two packed weights
+    size_t off_dpre, off_partial1, off_partial2, off_vt, off_doutt, off_dpret, off_hidt;
 };
 
 Plan make_plan(const HsnwUnits* u, int64_t pairs, bool backward) {
@@ -533,23 +645,40 @@ Plan make_plan(const HsnwUnits* u, int64_t pairs, bool backward) {
     seg = (seg + kChunk - 1) / kChunk * kChunk;
     p.seg = static_cast<int>(seg < 1024 ? 1024 : seg);
     p.max_segs = static_cast<int>((pairs + p.seg - 1) / p.seg) + M;
+    p.ld = static_cast<int>(((pairs + 7) & ~static_cast<int64_t>(7)) + 8 * M);
     size_t at = 256;   // the status word
-    const size_t sizes[12] = {
-        static_cast<size_t>(pairs), static_cast<size_t>(p.blocks) * M, static_cast<size_t>(M) + 1, static_cast<size_t>(M) + 1,
-        static_cast<size_t>(M) + 1, static_cast<size_t>(p.max_tiles), static_cast<size_t>(p.max_tiles), static_cast<size_t>(p.max_tiles),
-        static_cast<size_t>(p.max_segs), static_cast<size_t>(p.max_segs), static_cast<size_t>(p.max_segs), 2};
-    for (int i = 0; i < 12; ++i) {
+    const size_t sizes[kTables] = {
+        static_cast<size_t>(p.ld), static_cast<size_t>(p.blocks) * M, static_cast<size_t>(M) + 1, static_cast<size_t>(M),
+        static_cast<size_t>(M) + 1, static_cast<size_t>(M) + 1, static_cast<size_t>(p.max_tiles), static_cast<size_t>(p.max_tiles),
+        static_cast<size_t>(p.max_tiles), static_cast<size_t>(p.max_segs), static_cast<size_t>(p.max_segs), static_cast<size_t>(p.max_segs), 2};
+    for (int i = 0; i < kTables; ++i) {
         p.off_tables[i] = at;
         at += up256(sizes[i] * sizeof(int));
+    }
+    if (u->prod_bf16) {
+        p.off_wa = at;
+        at += up256(static_cast<size_t>(M) * u->d_in * u->hidden * 2);
+        p.off_wb = at;
+        at += up256(static_cast<size_t>(M) * u->hidden * u->d_out * 2);
     }
     if (backward) {
         const size_t elem = u->prod_bf16 ? 2 : 4;
         p.off_dpre = at;
-        at += up256(static_cast<size_t>(pairs) * u->hidden * elem);
+        at += up256(static_cast<size_t>(p.ld) * u->hidden * elem);
         p.off_partial1 = at;
         at += up256(static_cast<size_t>(p.max_segs) * u->d_in * u->hidden * sizeof(float));
         p.off_partial2 = at;
         at += up256(static_cast<size_t>(p.max_segs) * u->hidden * u->d_out * sizeof(float));
+        if (u->prod_bf16) {
+            p.off_vt = at;
+            at += up256(static_cast<size_t>(p.ld) * u->d_in * 2);
+            p.off_doutt = at;
+            at += up256(static_cast<size_t>(p.ld) * u->d_out * 2);
+            p.off_dpret = at;
+            at += up256(static_cast<size_t>(p.ld) * u->hidden * 2);
+            p.off_hidt = at;
+            at += up256(static_cast<size_t>(p.ld) * u->hidden * 2);
+        }
     }
     p.bytes = at;
     return p;
@@ -558,7 +687,7 @@ Plan make_plan(const HsnwUnits* u, int64_t pairs, bool backward) {
 Tables make_tables(const Plan& p, void* scratch) {
     unsigned char* base = static_cast<unsigned char*>(scratch);
     auto at = [&](int i) { return reinterpret_cast<int*>(base + p.off_tables[i]); };
-    return Tables{at(0), at(1), at(2), at(3), at(4), at(5), at(6), at(7), at(8), at(9), at(10), at(11)};
+    return Tables{at(0), at(1), at(2), at(3), at(4), at(5), at(6), at(7), at(8), at(9), at(10), at(11), at(12)};
 }
 
 int check_units(const HsnwUnits* u, int64_t pairs, const char* what) {
@@ -567,7 +696,7 @@ int check_units(const HsnwUnits* u, int64_t pairs, const char* what) {
         return hsnw_fail(HSNW_E_ARG, "units: sizes or weights missing");
     if (u->n_units > kMaxUnits) return hsnw_fail(HSNW_E_UNSUPPORTED, "units: at most 256 units");
     if (u->d_in % 8 || u->hidden % 8 || u->d_out % 8) return hsnw_fail(HSNW_E_UNSUPPORTED, "units: the three widths in multiples of 8");
-    if (pairs >= (static_cast<int64_t>(1) << 31) - kSortBlock) return hsnw_fail(HSNW_E_UNSUPPORTED, "units: fewer than 2^31 pairs");
+    if (pairs >= (static_cast<int64_t>(1) << 31) - kSortBlock - 8 * kMaxUnits) return hsnw_fail(HSNW_E_UNSUPPORTED, "units: fewer than 2^31 pairs");
     if ((reinterpret_cast<uintptr_t>(u->w1) | reinterpret_cast<uintptr_t>(u->w2)) & 15)
         return hsnw_fail(HSNW_E_ARG, "units: weights not 16-byte aligned");
     return HSNW_OK;
@@ -575,16 +704,29 @@ int check_units(const HsnwUnits* u, int64_t pairs, const char* what) {
 
 int sort_pairs(const HsnwUnits* u, const int64_t* unit_idx, int64_t pairs, const Plan& p, const Tables& tb, int* status, cudaStream_t stream) {
     const size_t shared = sizeof(int) * 32 * u->n_units;
+    if (cudaMemsetAsync(tb.order, 0xff, sizeof(int) * static_cast<size_t>(p.ld), stream) != cudaSuccess) return hsnw_check_launch("units: sort");
     k_units_count<<<p.blocks, kSortBlock, shared, stream>>>(unit_idx, pairs, u->n_units, tb, status);
     k_units_scan<<<1, 256, 0, stream>>>(p.blocks, u->n_units, p.seg, tb);
     k_units_place<<<p.blocks, kSortBlock, shared, stream>>>(unit_idx, pairs, u->n_units, tb, status);
     return hsnw_check_launch("units: sort");
 }
 
+// the weights as bfloat16: as they are (k_units_cast) or with the last two dimensions exchanged
+void pack_weights(const float* w, int M, int rows, int cols, bool transpose, __nv_bfloat16* out, cudaStream_t stream) {
+    if (transpose) {
+        k_units_transpose<float><<<dim3((rows + 31) / 32, (cols + 31) / 32, M), 256, 0, stream>>>(
+            w, static_cast<int64_t>(rows) * cols, rows, cols, nullptr, out, static_cast<int64_t>(rows) * cols, rows);
+    } else {
+        const int64_t n8 = static_cast<int64_t>(M) * rows * cols / 8;
+        k_units_cast<<<static_cast<unsigned>(std::min<int64_t>((n8 + 255) / 256, 1024)), 256, 0, stream>>>(w, n8, out);
+    }
+}
+
 template <class Op>
-void fill_base(Op& op, const HsnwUnits* u, const Tables& tb) {
-    op.Din = u->d_in, op.H = u->hidden, op.D = u->d_out;
+void fill_base(Op& op, const HsnwUnits* u, const Tables& tb, const Plan& p, const __nv_bfloat16* packed) {
+    op.Din = u->d_in, op.H = u->hidden, op.D = u->d_out, op.ld = p.ld;
     op.w1 = u->w1, op.b1 = u->b1, op.w2 = u->w2, op.b2 = u->b2;
+    op.wp = packed;
     op.tb = tb;
 }
 
@@ -599,15 +741,20 @@ void launch_simt(const Op& op, int items, int rows, int cols, cudaStream_t strea
 }
 
 template <class E, bool BF>
-int forward_t(const HsnwUnits* u, const float* v, int64_t pairs, E* pre, E* out, const Plan& p, const Tables& tb, int* status,
-              cudaStream_t stream) {
+int forward_t(const HsnwUnits* u, const float* v, int64_t pairs, E* pre, E* out, const Plan& p, const Tables& tb, void* scratch,
+              int* status, cudaStream_t stream) {
+    unsigned char* base = static_cast<unsigned char*>(scratch);
+    __nv_bfloat16* w1t = reinterpret_cast<__nv_bfloat16*>(base + p.off_wa);   // [M, H, Din]
+    __nv_bfloat16* w2t = reinterpret_cast<__nv_bfloat16*>(base + p.off_wb);   // [M, D, H]
     First<E, BF> first;
-    fill_base(first, u, tb);
+    fill_base(first, u, tb, p, w1t);
     first.v = v, first.pre = pre;
     Second<E, BF> second;
-    fill_base(second, u, tb);
+    fill_base(second, u, tb, p, w2t);
     second.pre = pre, second.out = out;
-    if (BF) {
+    if constexpr (BF) {
+        pack_weights(u->w1, u->n_units, u->d_in, u->hidden, true, w1t, stream);
+        pack_weights(u->w2, u->n_units, u->hidden, u->d_out, true, w2t, stream);
         launch_tc<First<E, BF>, 128>(first, p.max_tiles, kTile, u->hidden, status, stream);
         if (u->d_out <= 64) launch_tc<Second<E, BF>, 64>(second, p.max_tiles, kTile, u->d_out, status, stream);
         else launch_tc<Second<E, BF>, 128>(second, p.max_tiles, kTile, u->d_out, status, stream);
@@ -622,39 +769,48 @@ template <class E, bool BF>
 int backward_t(const HsnwUnits* u, const float* v, int64_t pairs, const E* pre, const E* dout, float* dv, float* dw1, float* db1, float* dw2,
                float* db2, const Plan& p, const Tables& tb, void* scratch, int* status, cudaStream_t stream) {
     unsigned char* base = static_cast<unsigned char*>(scratch);
+    auto half = [&](size_t off) { return reinterpret_cast<__nv_bfloat16*>(base + off); };
     E* dpre = reinterpret_cast<E*>(base + p.off_dpre);
     float* partial1 = reinterpret_cast<float*>(base + p.off_partial1);
     float* partial2 = reinterpret_cast<float*>(base + p.off_partial2);
+    __nv_bfloat16 *w1k = half(p.off_wa), *w2k = half(p.off_wb);   // [M, Din, H], [M, H, D]: the weights as they are
+    __nv_bfloat16 *v_t = half(p.off_vt), *dout_t = half(p.off_doutt), *dpre_t = half(p.off_dpret), *hid_t = half(p.off_hidt);
     DPre<E, BF> dp;
-    fill_base(dp, u, tb);
-    dp.pre = pre, dp.dout = dout, dp.dpre = dpre;
+    fill_base(dp, u, tb, p, w2k);
+    dp.pre = pre, dp.dout = dout, dp.dpre = dpre, dp.dpre_t = dpre_t, dp.hid_t = hid_t;
     DInput<E, BF> di;
-    fill_base(di, u, tb);
+    fill_base(di, u, tb, p, w1k);
     di.dpre = dpre, di.dv = dv;
     DWeight1<E, BF> g1;
-    fill_base(g1, u, tb);
-    g1.v = v, g1.dpre = dpre, g1.partial = partial1;
+    fill_base(g1, u, tb, p, nullptr);
+    g1.v = v, g1.dpre = dpre, g1.v_t = v_t, g1.dpre_t = dpre_t, g1.partial = partial1;
     DWeight2<E, BF> g2;
-    fill_base(g2, u, tb);
-    g2.pre = pre, g2.dout = dout, g2.partial = partial2;
-    if (BF) {
+    fill_base(g2, u, tb, p, nullptr);
+    g2.pre = pre, g2.dout = dout, g2.hid_t = hid_t, g2.dout_t = dout_t, g2.partial = partial2;
+    const int M = u->n_units;
+    if constexpr (BF) {
+        pack_weights(u->w1, M, u->d_in, u->hidden, false, w1k, stream);
+        pack_weights(u->w2, M, u->hidden, u->d_out, false, w2k, stream);
+        k_units_transpose<float><<<dim3((p.ld + 31) / 32, (u->d_in + 31) / 32, 1), 256, 0, stream>>>(v, 0, p.ld, u->d_in, tb.order, v_t, 0, p.ld);
+        k_units_transpose<E><<<dim3((p.ld + 31) / 32, (u->d_out + 31) / 32, 1), 256, 0, stream>>>(dout, 0, p.ld, u->d_out, tb.order, dout_t, 0, p.ld);
         launch_tc<DPre<E, BF>, 128>(dp, p.max_tiles, kTile, u->hidden, status, stream);
         launch_tc<DInput<E, BF>, 128>(di, p.max_tiles, kTile, u->d_in, status, stream);
         launch_tc<DWeight1<E, BF>, 128>(g1, p.max_segs, u->d_in, u->hidden, status, stream);
         if (u->d_out <= 64) launch_tc<DWeight2<E, BF>, 64>(g2, p.max_segs, u->hidden, u->d_out, status, stream);
         else launch_tc<DWeight2<E, BF>, 128>(g2, p.max_segs, u->hidden, u->d_out, status, stream);
+        k_units_bgrad_t<<<dim3(M, u->hidden), 128, 0, stream>>>(dpre_t, p.ld, u->hidden, tb, db1);
+        k_units_bgrad_t<<<dim3(M, u->d_out), 128, 0, stream>>>(dout_t, p.ld, u->d_out, tb, db2);
     } else {
         launch_simt(dp, p.max_tiles, kTile, u->hidden, stream);
         launch_simt(di, p.max_tiles, kTile, u->d_in, stream);
         launch_simt(g1, p.max_segs, u->d_in, u->hidden, stream);
         launch_simt(g2, p.max_segs, u->hidden, u->d_out, stream);
+        k_units_bgrad<E, BF, true><<<dim3(M, (u->hidden + 31) / 32), 256, 0, stream>>>(dpre, u->hidden, tb, db1);
+        k_units_bgrad<E, BF, false><<<dim3(M, (u->d_out + 31) / 32), 256, 0, stream>>>(dout, u->d_out, tb, db2);
     }
-    const int M = u->n_units;
     const int64_t e1 = static_cast<int64_t>(u->d_in) * u->hidden, e2 = static_cast<int64_t>(u->hidden) * u->d_out;
     k_units_wgrad<BF><<<static_cast<unsigned>(std::min<int64_t>((e1 * M + 255) / 256, 4096)), 256, 0, stream>>>(partial1, e1, M, tb, dw1);
     k_units_wgrad<BF><<<static_cast<unsigned>(std::min<int64_t>((e2 * M + 255) / 256, 4096)), 256, 0, stream>>>(partial2, e2, M, tb, dw2);
-    k_units_bgrad<E, BF, true><<<dim3(M, (u->hidden + 31) / 32), 256, 0, stream>>>(dpre, u->hidden, tb, db1);
-    k_units_bgrad<E, BF, false><<<dim3(M, (u->d_out + 31) / 32), 256, 0, stream>>>(dout, u->d_out, tb, db2);
     return hsnw_check_launch("units_backward");
 }
 
@@ -688,9 +844,9 @@ extern "C" int hsnw_units_forward(const HsnwUnits* units, const float* v, const 
     hsnw_profile_mark(HSNW_K_UNITS_FWD, stream);
     if (int rc = sort_pairs(units, unit_idx, pairs, p, tb, status, stream)) return rc;
     if (units->prod_bf16)
-        return forward_t<__nv_bfloat16, true>(units, v, pairs, static_cast<__nv_bfloat16*>(pre), static_cast<__nv_bfloat16*>(out), p, tb, status,
-                                              stream);
-    return forward_t<float, false>(units, v, pairs, static_cast<float*>(pre), static_cast<float*>(out), p, tb, status, stream);
+        return forward_t<__nv_bfloat16, true>(units, v, pairs, static_cast<__nv_bfloat16*>(pre), static_cast<__nv_bfloat16*>(out), p, tb, scratch,
+                                              status, stream);
+    return forward_t<float, false>(units, v, pairs, static_cast<float*>(pre), static_cast<float*>(out), p, tb, scratch, status, stream);
 }
 
 extern "C" int hsnw_units_backward(const HsnwUnits* units, const float* v, const int64_t* unit_idx, int64_t pairs, const void* pre,
