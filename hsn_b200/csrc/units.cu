@@ -45,7 +45,7 @@ using namespace hsnw;
 namespace {
 
 constexpr int kTile = 128;       // pairs of a row tile = rows of a tensor-core product
-constexpr int kChunk = 128;      // K elements staged at a time
+constexpr int kChunk = 64;       // K elements of one stage of the tensor-core products
 constexpr int kSortBlock = 1024;
 constexpr int kMaxUnits = 256;
 
@@ -184,8 +184,9 @@ __global__ void __launch_bounds__(kSortBlock) k_units_place(const int64_t* unit_
 // ---- operands and results of the six products -------------------------------------------------------------
 // E: the type of pre, out, dout and dpre (bfloat16 with bf16 products, else float); BF: round as the bf16 pass
 // does. Every product has two views of its operands: a(), b() give 8 consecutive K elements as floats from
-// the tensors as the caller holds them (the CUDA-core kernel); a16(), b16() give them as one 16-byte unit of
-// bfloat16 from the packed and transposed copies (the tensor-core kernel, BF only).
+// the tensors as the caller holds them (the CUDA-core kernel); a_row(), b_row() give the address of a row's
+// K elements, contiguous, in the packed, sorted and transposed bfloat16 copies (the tensor-core kernel, BF only;
+// a product's store() takes its 8 biases from `bias8`).
 
 template <bool BF>
 __device__ __forceinline__ float rnd(float x) {
@@ -213,7 +214,6 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 __device__ __forceinline__ uint4 pack8(const float x[8]) {
     return make_uint4(pack2(x[0], x[1]), pack2(x[2], x[3]), pack2(x[4], x[5]), pack2(x[6], x[7]));
 }
-__device__ __forceinline__ uint4 unit16(const __nv_bfloat16* src) { return *reinterpret_cast<const uint4*>(src); }
 __device__ __forceinline__ void store8(float* dst, const float x[8]) {
     *reinterpret_cast<float4*>(dst) = make_float4(x[0], x[1], x[2], x[3]);
     *reinterpret_cast<float4*>(dst + 4) = make_float4(x[4], x[5], x[6], x[7]);
@@ -248,15 +248,20 @@ struct Base {
     __device__ int64_t pair(int sorted_offset) const { return tb.order[start + sorted_offset]; }
 };
 
-// pre[pair] = v[pair] W1[u] + b1[u]                      wp: W1 as [M, H, Din]
+// pre[pair] = v[pair] W1[u] + b1[u]                      wp: W1 as [M, H, Din]; with bf16 products A is the
+// sorted bfloat16 copy of v, and act(pre) is also written in sorted order for the second layer
 template <class E, bool BF>
 struct First : Base {
+    static constexpr bool kTransposed = false;
     const float* v;
+    const __nv_bfloat16* v_s;   // [ld, Din]
     E* pre;
+    __nv_bfloat16* hid_s;       // [ld, H]
     __device__ bool setup(int x) { return tile(x); }
     __device__ int rows() const { return len; }
     __device__ int cols() const { return H; }
     __device__ int depth() const { return Din; }
+    __device__ const float* bias_row() const { return b1 + static_cast<int64_t>(unit) * H; }
     __device__ void a(int m, int k, float x[8]) const {
         if (m < len && k < Din) load8(v + pair(m) * Din + k, x);
         else zero8(x);
@@ -266,29 +271,35 @@ struct First : Base {
 #pragma unroll
         for (int i = 0; i < 8; ++i) x[i] = (c < H && k + i < Din) ? src[static_cast<int64_t>(i) * H] : 0.0f;
     }
-    __device__ uint4 a16(int m, int k) const {
-        float x[8];
-        a(m, k, x);
-        return pack8(x);
-    }
-    __device__ uint4 b16(int c, int k) const { return (c < H && k < Din) ? unit16(wp + (static_cast<int64_t>(unit) * H + c) * Din + k) : kZero16; }
-    __device__ void store(int m, int c0, float acc[8]) const {
-        if (m >= len || c0 >= H) return;
+    __device__ const __nv_bfloat16* a_row(int m) const { return m < len ? v_s + static_cast<int64_t>(start + m) * Din : nullptr; }
+    __device__ const __nv_bfloat16* b_row(int c) const { return c < H ? wp + (static_cast<int64_t>(unit) * H + c) * Din : nullptr; }
+    __device__ bool store(int m, int c0, float acc[8], const float* bias8, float*) const {
+        if (m >= len || c0 >= H) return false;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = rnd<BF>(acc[i] + rnd<BF>(b1[unit * H + c0 + i]));
+        for (int i = 0; i < 8; ++i) acc[i] = rnd<BF>(acc[i] + rnd<BF>(bias8[i]));
         store8(pre + pair(m) * H + c0, acc);
+        if (BF) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = gelu_erf(acc[i]);
+            store8(hid_s + static_cast<int64_t>(start + m) * H + c0, acc);
+        }
+        return true;
     }
 };
 
-// out[pair] = act(pre[pair]) W2[u] + b2[u]               wp: W2 as [M, D, H]
+// out[pair] = act(pre[pair]) W2[u] + b2[u]               wp: W2 as [M, D, H]; with bf16 products A is act(pre)
+// in sorted order as the first layer left it
 template <class E, bool BF>
 struct Second : Base {
+    static constexpr bool kTransposed = false;
     const E* pre;
+    const __nv_bfloat16* hid_s;
     E* out;
     __device__ bool setup(int x) { return tile(x); }
     __device__ int rows() const { return len; }
     __device__ int cols() const { return D; }
     __device__ int depth() const { return H; }
+    __device__ const float* bias_row() const { return b2 + static_cast<int64_t>(unit) * D; }
     __device__ void a(int m, int k, float x[8]) const {
         if (m < len && k < H) {
             load8(pre + pair(m) * H + k, x);
@@ -303,17 +314,14 @@ struct Second : Base {
 #pragma unroll
         for (int i = 0; i < 8; ++i) x[i] = (c < D && k + i < H) ? src[static_cast<int64_t>(i) * D] : 0.0f;
     }
-    __device__ uint4 a16(int m, int k) const {
-        float x[8];
-        a(m, k, x);
-        return pack8(x);
-    }
-    __device__ uint4 b16(int c, int k) const { return (c < D && k < H) ? unit16(wp + (static_cast<int64_t>(unit) * D + c) * H + k) : kZero16; }
-    __device__ void store(int m, int c0, float acc[8]) const {
-        if (m >= len || c0 >= D) return;
+    __device__ const __nv_bfloat16* a_row(int m) const { return m < len ? hid_s + static_cast<int64_t>(start + m) * H : nullptr; }
+    __device__ const __nv_bfloat16* b_row(int c) const { return c < D ? wp + (static_cast<int64_t>(unit) * D + c) * H : nullptr; }
+    __device__ bool store(int m, int c0, float acc[8], const float* bias8, float*) const {
+        if (m >= len || c0 >= D) return false;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = rnd<BF>(acc[i] + rnd<BF>(b2[unit * D + c0 + i]));
+        for (int i = 0; i < 8; ++i) acc[i] = rnd<BF>(acc[i] + rnd<BF>(bias8[i]));
         store8(out + pair(m) * D + c0, acc);
+        return true;
     }
 };
 
@@ -321,6 +329,7 @@ struct Second : Base {
 // dpre and act(pre) transposed, [H, ld], zeros in the positions up to the next multiple of 8
 template <class E, bool BF>
 struct DPre : Base {
+    static constexpr bool kTransposed = BF;
     const E *pre, *dout;
     E* dpre;   // in sorted order
     __nv_bfloat16 *dpre_t, *hid_t;
@@ -328,6 +337,7 @@ struct DPre : Base {
     __device__ int rows() const { return len; }
     __device__ int cols() const { return H; }
     __device__ int depth() const { return D; }
+    __device__ const float* bias_row() const { return nullptr; }
     __device__ void a(int m, int k, float x[8]) const {
         if (m < len && k < D) load8(dout + pair(m) * D + k, x);
         else zero8(x);
@@ -336,33 +346,29 @@ struct DPre : Base {
         if (c < H && k < D) load8(w2 + (static_cast<int64_t>(unit) * H + c) * D + k, x);
         else zero8(x);
     }
-    __device__ uint4 a16(int m, int k) const { return (m < len && k < D) ? unit16(dout + pair(m) * D + k) : kZero16; }
-    __device__ uint4 b16(int c, int k) const { return (c < H && k < D) ? unit16(wp + (static_cast<int64_t>(unit) * H + c) * D + k) : kZero16; }
-    __device__ void store(int m, int c0, float acc[8]) const {
-        if (c0 >= H) return;
-        if (m >= len) {
-            if (BF && m < ((len + 7) & ~7)) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int64_t at = static_cast<int64_t>(c0 + i) * ld + start + m;
-                    dpre_t[at] = __float2bfloat16_rn(0.0f);
-                    hid_t[at] = __float2bfloat16_rn(0.0f);
-                }
-            }
-            return;
-        }
+    __device__ const E* a_row(int m) const { return m < len ? dout + pair(m) * D : nullptr; }
+    __device__ const __nv_bfloat16* b_row(int c) const { return c < H ? wp + (static_cast<int64_t>(unit) * H + c) * D : nullptr; }
+    // acc: in the product, out dpre; second: out act(pre)
+    __device__ bool store(int m, int c0, float acc[8], const float*, float* second) const {
+        if (m >= len || c0 >= H) return false;
         float p[8];
         load8(pre + pair(m) * H + c0, p);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = rnd<BF>(rnd<BF>(acc[i]) * gelu_erf_grad(p[i]));
+        for (int i = 0; i < 8; ++i) {
+            acc[i] = rnd<BF>(rnd<BF>(acc[i]) * gelu_erf_grad(p[i]));
+            second[i] = gelu_erf(p[i]);
+        }
         store8(dpre + static_cast<int64_t>(start + m) * H + c0, acc);
-        if (BF) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {   // a warp's lanes are consecutive sorted positions: 64 contiguous bytes a store
-                const int64_t at = static_cast<int64_t>(c0 + i) * ld + start + m;
-                dpre_t[at] = __float2bfloat16_rn(acc[i]);
-                hid_t[at] = __float2bfloat16_rn(gelu_erf(p[i]));
-            }
+        return true;
+    }
+    // column c of the two transposed tiles (128 sorted positions from the tile's first, zeros past its pairs)
+    __device__ void store_column(int c, int m0, const __nv_bfloat16* first, const __nv_bfloat16* second) const {
+        if (c >= H) return;
+        const int units8 = (min(len - m0, 128) + 7) >> 3;
+        const int64_t at = static_cast<int64_t>(c) * ld + start + m0;
+        for (int j = 0; j < units8; ++j) {
+            *reinterpret_cast<uint4*>(dpre_t + at + 8 * j) = *reinterpret_cast<const uint4*>(first + 8 * j);
+            *reinterpret_cast<uint4*>(hid_t + at + 8 * j) = *reinterpret_cast<const uint4*>(second + 8 * j);
         }
     }
 };
@@ -370,12 +376,14 @@ struct DPre : Base {
 // dv[pair] = dpre[sorted] W1[u]^T                          wp: W1 as [M, Din, H]
 template <class E, bool BF>
 struct DInput : Base {
+    static constexpr bool kTransposed = false;
     const E* dpre;
     float* dv;
     __device__ bool setup(int x) { return tile(x); }
     __device__ int rows() const { return len; }
     __device__ int cols() const { return Din; }
     __device__ int depth() const { return H; }
+    __device__ const float* bias_row() const { return nullptr; }
     __device__ void a(int m, int k, float x[8]) const {
         if (m < len && k < H) load8(dpre + static_cast<int64_t>(start + m) * H + k, x);
         else zero8(x);
@@ -384,19 +392,21 @@ struct DInput : Base {
         if (c < Din && k < H) load8(w1 + (static_cast<int64_t>(unit) * Din + c) * H + k, x);
         else zero8(x);
     }
-    __device__ uint4 a16(int m, int k) const { return (m < len && k < H) ? unit16(dpre + static_cast<int64_t>(start + m) * H + k) : kZero16; }
-    __device__ uint4 b16(int c, int k) const { return (c < Din && k < H) ? unit16(wp + (static_cast<int64_t>(unit) * Din + c) * H + k) : kZero16; }
-    __device__ void store(int m, int c0, float acc[8]) const {
-        if (m >= len || c0 >= Din) return;
+    __device__ const E* a_row(int m) const { return m < len ? dpre + static_cast<int64_t>(start + m) * H : nullptr; }
+    __device__ const __nv_bfloat16* b_row(int c) const { return c < Din ? wp + (static_cast<int64_t>(unit) * Din + c) * H : nullptr; }
+    __device__ bool store(int m, int c0, float acc[8], const float*, float*) const {
+        if (m >= len || c0 >= Din) return false;
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = rnd<BF>(acc[i]);
         store8(dv + pair(m) * Din + c0, acc);
+        return true;
     }
 };
 
 // partial[segment] = v[pairs]^T dpre[sorted]      [4d, H], K = the segment's pairs
 template <class E, bool BF>
 struct DWeight1 : Base {
+    static constexpr bool kTransposed = false;
     const float* v;
     const E* dpre;
     const __nv_bfloat16 *v_t, *dpre_t;   // [Din, ld], [H, ld]
@@ -405,6 +415,7 @@ struct DWeight1 : Base {
     __device__ int rows() const { return Din; }
     __device__ int cols() const { return H; }
     __device__ int depth() const { return len; }
+    __device__ const float* bias_row() const { return nullptr; }
     __device__ void a(int m, int k, float x[8]) const {
 #pragma unroll
         for (int i = 0; i < 8; ++i) x[i] = (m < Din && k + i < len) ? v[pair(k + i) * Din + m] : 0.0f;
@@ -413,17 +424,19 @@ struct DWeight1 : Base {
 #pragma unroll
         for (int i = 0; i < 8; ++i) x[i] = (c < H && k + i < len) ? load1(dpre + static_cast<int64_t>(start + k + i) * H + c) : 0.0f;
     }
-    __device__ uint4 a16(int m, int k) const { return (m < Din && k < len) ? unit16(v_t + static_cast<int64_t>(m) * ld + start + k) : kZero16; }
-    __device__ uint4 b16(int c, int k) const { return (c < H && k < len) ? unit16(dpre_t + static_cast<int64_t>(c) * ld + start + k) : kZero16; }
-    __device__ void store(int m, int c0, float acc[8]) const {
-        if (m >= Din || c0 >= H) return;
+    __device__ const __nv_bfloat16* a_row(int m) const { return m < Din ? v_t + static_cast<int64_t>(m) * ld + start : nullptr; }
+    __device__ const __nv_bfloat16* b_row(int c) const { return c < H ? dpre_t + static_cast<int64_t>(c) * ld + start : nullptr; }
+    __device__ bool store(int m, int c0, float acc[8], const float*, float*) const {
+        if (m >= Din || c0 >= H) return false;
         store8(partial + (static_cast<int64_t>(item) * Din + m) * H + c0, acc);
+        return true;
     }
 };
 
 // partial[segment] = act(pre[pairs])^T dout[pairs]      [H, d], K = the segment's pairs
 template <class E, bool BF>
 struct DWeight2 : Base {
+    static constexpr bool kTransposed = false;
     const E *pre, *dout;
     const __nv_bfloat16 *hid_t, *dout_t;   // [H, ld], [D, ld]
     float* partial;
@@ -431,6 +444,7 @@ struct DWeight2 : Base {
     __device__ int rows() const { return H; }
     __device__ int cols() const { return D; }
     __device__ int depth() const { return len; }
+    __device__ const float* bias_row() const { return nullptr; }
     __device__ void a(int m, int k, float x[8]) const {
 #pragma unroll
         for (int i = 0; i < 8; ++i) x[i] = (m < H && k + i < len) ? rnd<BF>(gelu_erf(load1(pre + pair(k + i) * H + m))) : 0.0f;
@@ -439,55 +453,138 @@ struct DWeight2 : Base {
 #pragma unroll
         for (int i = 0; i < 8; ++i) x[i] = (c < D && k + i < len) ? load1(dout + pair(k + i) * D + c) : 0.0f;
     }
-    __device__ uint4 a16(int m, int k) const { return (m < H && k < len) ? unit16(hid_t + static_cast<int64_t>(m) * ld + start + k) : kZero16; }
-    __device__ uint4 b16(int c, int k) const { return (c < D && k < len) ? unit16(dout_t + static_cast<int64_t>(c) * ld + start + k) : kZero16; }
-    __device__ void store(int m, int c0, float acc[8]) const {
-        if (m >= H || c0 >= D) return;
+    __device__ const __nv_bfloat16* a_row(int m) const { return m < H ? hid_t + static_cast<int64_t>(m) * ld + start : nullptr; }
+    __device__ const __nv_bfloat16* b_row(int c) const { return c < D ? dout_t + static_cast<int64_t>(c) * ld + start : nullptr; }
+    __device__ bool store(int m, int c0, float acc[8], const float*, float*) const {
+        if (m >= H || c0 >= D) return false;
         store8(partial + (static_cast<int64_t>(item) * H + m) * D + c0, acc);
+        return true;
     }
 };
 
 // ---- the tile products ----------------------------------------------------------------------------------
 
-// bf16 operands on the tensor cores: block (x: tile or segment, y: 128 rows, z: BN columns).
+// 16 bytes global -> shared without passing through registers; `src` null: 16 zero bytes (nothing is read,
+// `safe` only has to be an address of the same space)
+__device__ __forceinline__ void copy16_or_zero(void* dst_smem, const void* src, const void* safe) {
+    const unsigned bytes = src ? 16u : 0u;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr(dst_smem)), "l"(src ? src : safe), "r"(bytes) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait_but() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+constexpr int kStages = 2;
+
+// One K = 16 step of a product whose two operands are in the 128-byte swizzle: inside the 128-byte K block a
+// step moves both start addresses by 32 bytes.
+template <int STEPS>
+__device__ __forceinline__ void umma_block_sw128(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, int steps, bool onto) {
+    __syncwarp();
+#pragma unroll
+    for (int s = 0; s < STEPS; ++s)
+        if (s < steps) umma_bf16(tmem_d, desc_a + static_cast<uint64_t>(2 * s), desc_b + static_cast<uint64_t>(2 * s), idesc, onto || s > 0);
+}
+
+// bf16 operands on the tensor cores: block (x: tile or segment, y: 128 rows, z: BN columns). K goes in
+// blocks of 64 elements — one 128-byte row of the 128-byte swizzle per operand row — through the stages of
+// shared memory: 8 consecutive lanes request the 8 units of one row (a fully used 128-byte line of global
+// memory) as asynchronous 16-byte copies to their swizzled places (unit u of row r at u ^ (r % 8), so a
+// warp's 4 rows fill 512 contiguous bytes), the next block while the tensor cores work on this one; a stage
+// is requested again when the commit of the products that read it has arrived. The epilogue reads the
+// accumulator 8 columns at a time, a thread its own row; a product whose result is also wanted transposed
+// (dpre) collects it as two bfloat16 tiles [column, row] in the stages' memory and writes them a column per
+// thread, 16 bytes a store.
 template <class Op, int BN>
 __global__ void __launch_bounds__(128) k_units_tc(Op op, int* status) {
-    extern __shared__ __align__(16) unsigned char dyn[];
-    __shared__ __align__(8) uint64_t bar;
+    static_assert(kChunk == 64, "a K block is one 128-byte swizzle row");
+    constexpr int kStageBytes = (128 + BN) * 128;   // A tile then B tile, 128 bytes a row
+    constexpr int kRowsA = 8, kRowsB = BN / 16;     // rows of a tile a thread requests: 16 rows a pass of the block
+    extern __shared__ unsigned char dyn_raw[];
+    __shared__ __align__(8) uint64_t bar[kStages];
     __shared__ uint32_t tmem_slot;
+    __shared__ float bias_s[BN];
     if (!op.setup(blockIdx.x)) return;   // the same answer for the whole block
     const int m0 = blockIdx.y * 128, n0 = blockIdx.z * BN;
     if (m0 >= op.rows() || n0 >= op.cols()) return;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    uint4* As = reinterpret_cast<uint4*>(dyn);
-    uint4* Bs = As + (kChunk / 8) * 128;
-    if (tid == 0) mbar_init(&bar, 1);
+    const int tid = threadIdx.x, warp = tid >> 5;
+    unsigned char* dyn = dyn_raw + ((1024u - (smem_addr(dyn_raw) & 1023u)) & 1023u);   // swizzle atoms are 1024 bytes
+    if (tid == 0)
+        for (int s = 0; s < kStages; ++s) mbar_init(&bar[s], 1);
     if (warp == 0) tmem_alloc(&tmem_slot, BN < 32 ? 32 : BN);
+    if (tid < BN) {
+        const float* bias = op.bias_row();
+        bias_s[tid] = (bias && n0 + tid < op.cols()) ? bias[n0 + tid] : 0.0f;
+    }
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t taddr = tmem_slot;
     const uint32_t idesc = umma_idesc_bf16(128, BN);
     const int K = op.depth();
-    int phase = 0;
-    for (int k0 = 0; k0 < K; k0 += kChunk, ++phase) {
-        const int planes = min(kChunk, ((K - k0) + 15) & ~15) >> 3;   // whole K = 16 steps
-        for (int idx = tid; idx < planes * 128; idx += 128) As[idx] = op.a16(m0 + (idx & 127), k0 + (idx >> 7) * 8);
-        for (int idx = tid; idx < planes * BN; idx += 128) Bs[idx] = op.b16(n0 + idx % BN, k0 + (idx / BN) * 8);
+    const int chunks = (K + kChunk - 1) / kChunk;
+    const int unit = tid & 7, row0 = tid >> 3;   // this thread's unit of a row, and its row in each pass of 16
+    decltype(op.a_row(0)) a_rows[kRowsA];
+    decltype(op.b_row(0)) b_rows[kRowsB];
+#pragma unroll
+    for (int j = 0; j < kRowsA; ++j) a_rows[j] = op.a_row(m0 + 16 * j + row0);
+#pragma unroll
+    for (int j = 0; j < kRowsB; ++j) b_rows[j] = op.b_row(n0 + 16 * j + row0);
+    auto request = [&](int c) {   // K block c into stage c % kStages; one group per call, block or not
+        if (c < chunks) {
+            unsigned char* As = dyn + (c % kStages) * kStageBytes;
+            unsigned char* Bs = As + 128 * 128;
+            const int k = c * kChunk + 8 * unit;
+            const bool in = k < K;
+#pragma unroll
+            for (int j = 0; j < kRowsA; ++j) {
+                const int r = 16 * j + row0;
+                copy16_or_zero(As + r * 128 + ((unit ^ (r & 7)) << 4), (in && a_rows[j]) ? a_rows[j] + k : nullptr, op.w1);
+            }
+#pragma unroll
+            for (int j = 0; j < kRowsB; ++j) {
+                const int r = 16 * j + row0;
+                copy16_or_zero(Bs + r * 128 + ((unit ^ (r & 7)) << 4), (in && b_rows[j]) ? b_rows[j] + k : nullptr, op.w1);
+            }
+        }
+        cp_async_commit();
+    };
+    for (int c = 0; c < kStages - 1; ++c) request(c);
+    for (int c = 0; c < chunks; ++c) {
+        cp_async_wait_but<kStages - 2>();   // the groups complete in order: block c has landed
         fence_async_smem();
         __syncthreads();
         if (tid < 32) {   // the whole first warp, converged after the barrier: one elected lane issues
+            const unsigned char* As = dyn + (c % kStages) * kStageBytes;
+            const int steps = (min(kChunk, K - c * kChunk) + 15) >> 4;
             tcgen05_fence_after();
-            umma_chain(taddr, umma_desc(As, 128), umma_desc(Bs, BN), idesc, planes >> 1, umma_kstep(128), umma_kstep(BN), k0 > 0);
-            umma_commit(&bar);
+            umma_block_sw128<4>(taddr, umma_desc_sw128(As), umma_desc_sw128(As + 128 * 128), idesc, steps, c > 0);
+            umma_commit(&bar[c % kStages]);
         }
-        mbar_wait(&bar, phase & 1, status);   // the products have read the operands: the next chunk may be staged
-        tcgen05_fence_after();
+        // block c + kStages - 1 goes where block c - 1 was: its products (issued an iteration ago) must have read it
+        if (c >= 1 && c + kStages - 1 < chunks) mbar_wait(&bar[(c - 1) % kStages], ((c - 1) / kStages) & 1, status);
+        request(c + kStages - 1);
     }
-    float x[8];
+    mbar_wait(&bar[(chunks - 1) % kStages], ((chunks - 1) / kStages) & 1, status);   // the last commit covers every product before it
+    tcgen05_fence_after();
+    float x[8], second[8];
+    __nv_bfloat16* tile_a = reinterpret_cast<__nv_bfloat16*>(dyn);   // [BN][128] each, in the stages' memory (every product has read it)
+    __nv_bfloat16* tile_b = tile_a + BN * 128;
     for (int cb = 0; cb < BN; cb += 8) {
         tmem_ld8(tmem_addr(taddr, warp * 32, cb), x);
-        op.store(m0 + warp * 32 + lane, n0 + cb, x);
+        const bool wrote = op.store(m0 + tid, n0 + cb, x, bias_s + cb, second);
+        if constexpr (Op::kTransposed) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                tile_a[(cb + i) * 128 + tid] = __float2bfloat16_rn(wrote ? x[i] : 0.0f);
+                tile_b[(cb + i) * 128 + tid] = __float2bfloat16_rn(wrote ? second[i] : 0.0f);
+            }
+        }
+    }
+    if constexpr (Op::kTransposed) {
+        __syncthreads();
+        if (tid < BN) op.store_column(n0 + tid, m0, tile_a + tid * 128, tile_b + tid * 128);
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -526,8 +623,11 @@ __global__ void __launch_bounds__(256) k_units_simt(Op op) {
         }
         __syncthreads();
     }
-    op.store(m0 + 2 * ty, n0 + 8 * tx, acc[0]);
-    op.store(m0 + 2 * ty + 1, n0 + 8 * tx, acc[1]);
+    const float* bias = op.bias_row();
+    float second[8];
+    if (bias) bias += n0 + 8 * tx;   // read only where the store takes the columns
+    op.store(m0 + 2 * ty, n0 + 8 * tx, acc[0], bias, second);
+    op.store(m0 + 2 * ty + 1, n0 + 8 * tx, acc[1], bias, second);
 }
 
 // out[b][c][r] = bfloat16(src[b][row(r)][c]) for r < rows, c < cols: 32 x 32 tiles through shared memory. With
@@ -565,6 +665,20 @@ __global__ void __launch_bounds__(256) k_units_cast(const float* src, int64_t n8
     for (int64_t e = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; e < n8; e += stride) {
         load8(src + 8 * e, x);
         store8(out + 8 * e, x);
+    }
+}
+
+// out[s] = bfloat16(v[order[s]]) for every sorted position that holds a pair: 8 elements a thread
+__global__ void __launch_bounds__(256) k_units_gather(const float* v, int width8, int64_t n, const int* order, __nv_bfloat16* out) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * 256;
+    float x[8];
+    for (int64_t e = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; e < n; e += stride) {
+        const int64_t s = e / width8;
+        const int k = static_cast<int>(e - s * width8) * 8;
+        const int64_t row = order[s];
+        if (row < 0) continue;
+        load8(v + (row * width8) * 8 + k, x);
+        store8(out + (s * width8) * 8 + k, x);
     }
 }
 
@@ -633,6 +747,7 @@ struct Plan {
     size_t bytes;
     size_t off_tables[kTables];
     size_t off_wa, off_wb;   // this call's two packed weights
+    size_t off_vs, off_hids;   // forward: v and act(pre) in sorted order
     size_t off_dpre, off_partial1, off_partial2, off_vt, off_doutt, off_dpret, off_hidt;
 };
 
@@ -642,7 +757,7 @@ Plan make_plan(const HsnwUnits* u, int64_t pairs, bool backward) {
     p.blocks = static_cast<int>((pairs + kSortBlock - 1) / kSortBlock);
     p.max_tiles = static_cast<int>((pairs + kTile - 1) / kTile) + M;
     int64_t seg = (pairs + 63) / 64;
-    seg = (seg + kChunk - 1) / kChunk * kChunk;
+    seg = (seg + kTile - 1) / kTile * kTile;
     p.seg = static_cast<int>(seg < 1024 ? 1024 : seg);
     p.max_segs = static_cast<int>((pairs + p.seg - 1) / p.seg) + M;
     p.ld = static_cast<int>(((pairs + 7) & ~static_cast<int64_t>(7)) + 8 * M);
@@ -660,6 +775,12 @@ Plan make_plan(const HsnwUnits* u, int64_t pairs, bool backward) {
         at += up256(static_cast<size_t>(M) * u->d_in * u->hidden * 2);
         p.off_wb = at;
         at += up256(static_cast<size_t>(M) * u->hidden * u->d_out * 2);
+    }
+    if (!backward && u->prod_bf16) {
+        p.off_vs = at;
+        at += up256(static_cast<size_t>(p.ld) * u->d_in * 2);
+        p.off_hids = at;
+        at += up256(static_cast<size_t>(p.ld) * u->hidden * 2);
     }
     if (backward) {
         const size_t elem = u->prod_bf16 ? 2 : 4;
@@ -732,7 +853,9 @@ void fill_base(Op& op, const HsnwUnits* u, const Tables& tb, const Plan& p, cons
 
 template <class Op, int BN>
 void launch_tc(const Op& op, int items, int rows, int cols, int* status, cudaStream_t stream) {
-    const size_t shared = static_cast<size_t>(kChunk / 8) * (128 + BN) * 16;
+    size_t shared = static_cast<size_t>(kStages) * (128 + BN) * 128;
+    if (Op::kTransposed) shared = std::max(shared, static_cast<size_t>(2) * BN * 128 * 2);   // the two transposed tiles
+    shared += 1024;   // the kernel starts its stages on a 1024-byte boundary
     k_units_tc<Op, BN><<<dim3(items, (rows + 127) / 128, (cols + BN - 1) / BN), 128, shared, stream>>>(op, status);
 }
 template <class Op>
@@ -748,11 +871,15 @@ int forward_t(const HsnwUnits* u, const float* v, int64_t pairs, E* pre, E* out,
     __nv_bfloat16* w2t = reinterpret_cast<__nv_bfloat16*>(base + p.off_wb);   // [M, D, H]
     First<E, BF> first;
     fill_base(first, u, tb, p, w1t);
-    first.v = v, first.pre = pre;
+    __nv_bfloat16* v_s = reinterpret_cast<__nv_bfloat16*>(base + p.off_vs);
+    __nv_bfloat16* hid_s = reinterpret_cast<__nv_bfloat16*>(base + p.off_hids);
+    first.v = v, first.pre = pre, first.v_s = v_s, first.hid_s = hid_s;
     Second<E, BF> second;
     fill_base(second, u, tb, p, w2t);
-    second.pre = pre, second.out = out;
+    second.pre = pre, second.out = out, second.hid_s = hid_s;
     if constexpr (BF) {
+        const int64_t n = static_cast<int64_t>(p.ld) * (u->d_in / 8);
+        k_units_gather<<<static_cast<unsigned>(std::min<int64_t>((n + 255) / 256, 148 * 16)), 256, 0, stream>>>(v, u->d_in / 8, n, tb.order, v_s);
         pack_weights(u->w1, u->n_units, u->d_in, u->hidden, true, w1t, stream);
         pack_weights(u->w2, u->n_units, u->hidden, u->d_out, true, w2t, stream);
         launch_tc<First<E, BF>, 128>(first, p.max_tiles, kTile, u->hidden, status, stream);
