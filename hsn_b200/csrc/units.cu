@@ -476,6 +476,7 @@ __device__ __forceinline__ void cp_async_wait_but() {
 }
 
 constexpr int kStages = 2;
+constexpr int kTcThreads = 256;
 
 // One K = 16 step of a product whose two operands are in the 128-byte swizzle: inside the 128-byte K block a
 // step moves both start addresses by 32 bytes.
@@ -493,14 +494,15 @@ __device__ __forceinline__ void umma_block_sw128(uint32_t tmem_d, uint64_t desc_
 // memory) as asynchronous 16-byte copies to their swizzled places (unit u of row r at u ^ (r % 8), so a
 // warp's 4 rows fill 512 contiguous bytes), the next block while the tensor cores work on this one; a stage
 // is requested again when the commit of the products that read it has arrived. The epilogue reads the
-// accumulator 8 columns at a time, a thread its own row; a product whose result is also wanted transposed
+// accumulator 8 columns at a time, a thread its own row and half of the columns; a product whose result is also wanted transposed
 // (dpre) collects it as two bfloat16 tiles [column, row] in the stages' memory and writes them a column per
 // thread, 16 bytes a store.
 template <class Op, int BN>
-__global__ void __launch_bounds__(128) k_units_tc(Op op, int* status) {
+__global__ void __launch_bounds__(kTcThreads) k_units_tc(Op op, int* status) {
     static_assert(kChunk == 64, "a K block is one 128-byte swizzle row");
     constexpr int kStageBytes = (128 + BN) * 128;   // A tile then B tile, 128 bytes a row
-    constexpr int kRowsA = 8, kRowsB = BN / 16;     // rows of a tile a thread requests: 16 rows a pass of the block
+    constexpr int kPass = kTcThreads / 8;                   // rows the block requests in one pass: 8 lanes a row
+    constexpr int kRowsA = 128 / kPass, kRowsB = BN / kPass;   // rows of a tile a thread requests
     extern __shared__ unsigned char dyn_raw[];
     __shared__ __align__(8) uint64_t bar[kStages];
     __shared__ uint32_t tmem_slot;
@@ -524,13 +526,13 @@ __global__ void __launch_bounds__(128) k_units_tc(Op op, int* status) {
     const uint32_t idesc = umma_idesc_bf16(128, BN);
     const int K = op.depth();
     const int chunks = (K + kChunk - 1) / kChunk;
-    const int unit = tid & 7, row0 = tid >> 3;   // this thread's unit of a row, and its row in each pass of 16
+    const int unit = tid & 7, row0 = tid >> 3;   // this thread's unit of a row, and its row in each pass
     decltype(op.a_row(0)) a_rows[kRowsA];
     decltype(op.b_row(0)) b_rows[kRowsB];
 #pragma unroll
-    for (int j = 0; j < kRowsA; ++j) a_rows[j] = op.a_row(m0 + 16 * j + row0);
+    for (int j = 0; j < kRowsA; ++j) a_rows[j] = op.a_row(m0 + kPass * j + row0);
 #pragma unroll
-    for (int j = 0; j < kRowsB; ++j) b_rows[j] = op.b_row(n0 + 16 * j + row0);
+    for (int j = 0; j < kRowsB; ++j) b_rows[j] = op.b_row(n0 + kPass * j + row0);
     auto request = [&](int c) {   // K block c into stage c % kStages; one group per call, block or not
         if (c < chunks) {
             unsigned char* As = dyn + (c % kStages) * kStageBytes;
@@ -539,12 +541,12 @@ __global__ void __launch_bounds__(128) k_units_tc(Op op, int* status) {
             const bool in = k < K;
 #pragma unroll
             for (int j = 0; j < kRowsA; ++j) {
-                const int r = 16 * j + row0;
+                const int r = kPass * j + row0;
                 copy16_or_zero(As + r * 128 + ((unit ^ (r & 7)) << 4), (in && a_rows[j]) ? a_rows[j] + k : nullptr, op.w1);
             }
 #pragma unroll
             for (int j = 0; j < kRowsB; ++j) {
-                const int r = 16 * j + row0;
+                const int r = kPass * j + row0;
                 copy16_or_zero(Bs + r * 128 + ((unit ^ (r & 7)) << 4), (in && b_rows[j]) ? b_rows[j] + k : nullptr, op.w1);
             }
         }
@@ -571,14 +573,16 @@ __global__ void __launch_bounds__(128) k_units_tc(Op op, int* status) {
     float x[8], second[8];
     __nv_bfloat16* tile_a = reinterpret_cast<__nv_bfloat16*>(dyn);   // [BN][128] each, in the stages' memory (every product has read it)
     __nv_bfloat16* tile_b = tile_a + BN * 128;
-    for (int cb = 0; cb < BN; cb += 8) {
-        tmem_ld8(tmem_addr(taddr, warp * 32, cb), x);
-        const bool wrote = op.store(m0 + tid, n0 + cb, x, bias_s + cb, second);
+    // warps w and w + 4 reach the same 32 rows of the accumulator: each takes half of the columns
+    const int row = (warp & 3) * 32 + (tid & 31), half = (warp >> 2) * (BN / 2);
+    for (int cb = half; cb < half + BN / 2; cb += 8) {
+        tmem_ld8(tmem_addr(taddr, (warp & 3) * 32, cb), x);
+        const bool wrote = op.store(m0 + row, n0 + cb, x, bias_s + cb, second);
         if constexpr (Op::kTransposed) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                tile_a[(cb + i) * 128 + tid] = __float2bfloat16_rn(wrote ? x[i] : 0.0f);
-                tile_b[(cb + i) * 128 + tid] = __float2bfloat16_rn(wrote ? second[i] : 0.0f);
+                tile_a[(cb + i) * 128 + row] = __float2bfloat16_rn(wrote ? x[i] : 0.0f);
+                tile_b[(cb + i) * 128 + row] = __float2bfloat16_rn(wrote ? second[i] : 0.0f);
             }
         }
     }
@@ -856,7 +860,7 @@ void launch_tc(const Op& op, int items, int rows, int cols, int* status, cudaStr
     size_t shared = static_cast<size_t>(kStages) * (128 + BN) * 128;
     if (Op::kTransposed) shared = std::max(shared, static_cast<size_t>(2) * BN * 128 * 2);   // the two transposed tiles
     shared += 1024;   // the kernel starts its stages on a 1024-byte boundary
-    k_units_tc<Op, BN><<<dim3(items, (rows + 127) / 128, (cols + BN - 1) / BN), 128, shared, stream>>>(op, status);
+    k_units_tc<Op, BN><<<dim3(items, (rows + 127) / 128, (cols + BN - 1) / BN), kTcThreads, shared, stream>>>(op, status);
 }
 template <class Op>
 void launch_simt(const Op& op, int items, int rows, int cols, cudaStream_t stream) {
