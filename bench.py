@@ -51,7 +51,10 @@ CONFIGS = {
 CONFIGS["adamw"] = dict(tensors=40, elements=4_194_304 + 1031, trainer=True)
 # the window's epilogue (not the headline): the decoder over the c2 window's 8192 rows
 CONFIGS["decode"] = dict(rows=32 * 256, d=64, H=512, V=256, decoder=True)
+# the replay's grouped unit pass (not the headline): every pair of the c2 window at once, forward and backward
+CONFIGS["units"] = dict(pairs=32 * 256 * 8, M=8, d=64, H=512, units=True)
 WORKLOADS = {
+    "units": "the replay's grouped unit pass over a window's 65,536 pairs: 8 units 256 -> 512 -> 64, bf16 products, forward + backward",
     "decode": "the decoder D([q; u]) over a window's 8192 rows: 128 -> 512 -> 256, bf16 products",
     "adamw": "the trainer's AdamW step over 40 fp32 tensors of 4,195,335 elements (671 MB of parameters), one launch",
     "c1": "tiny gradcheck-shape window B2 T8 N16 d32 K2 H32",
@@ -801,6 +804,96 @@ def run_decoder(args, c: dict, name: str) -> None:
                      "how": "the two layers' 2 M N K flops / the two launches' event time in a profiled step; 3.2 GFLOP: the kernels are latency bound at this size"}}))  # fmt: skip
 
 
+def run_units(args, c: dict, name: str) -> None:
+    """`--config units`: `hsnw_units_forward` + `hsnw_units_backward` over every pair of the benchmark window; a step =
+    the pass and its backward (sort, packing, eight tile products, reductions). Beside it the CPU restatement on a
+    sample of the pairs, and PyTorch's own grouped bf16 products on the same device."""
+    import torch
+
+    from hsn_b200.kernels.units import grouped_backward, grouped_forward
+    from hsn_b200.window import launch_profile
+
+    world, rank, local, dev = dist_setup()
+    P, M, d, H = c["pairs"], c["M"], c["d"], c["H"]
+    gen = torch.Generator(device=dev).manual_seed(0)
+    f = lambda *shape, scale=1.0: torch.randn(*shape, generator=gen, device=dev) * scale  # noqa: E731
+    bank = [f(M, 4 * d, H, scale=(4 * d) ** -0.5), f(M, H, scale=0.3), f(M, H, d, scale=H**-0.5), f(M, d, scale=0.3)]
+    v, cot = f(P, 4 * d), f(P, d).bfloat16()
+    idx = torch.randint(0, M, (P,), generator=gen, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    kept: dict = {}
+
+    def step(i):
+        flush.zero_()   # (the window's operands are about the size of L2: written over between the steps)
+        out, pre, _ = grouped_forward(v, idx, *bank, check=False)
+        kept["grads"] = grouped_backward(v, idx, *bank, pre, cot, check=False)
+        kept["out"] = out
+
+    for i in range(max(3, args.warmup)):
+        step(i)
+    clock_lines: list = []
+    stop = threading.Event()
+    threading.Thread(target=sample_clocks, args=(stop, clock_lines), daemon=True).start()
+    with launch_profile() as prof:
+        step(0)
+    ms_total, each = timed_steps(step, args.steps, torch.cuda.synchronize)
+    stop.set()
+    fwd_ms, bwd_ms = prof.ms.get("units_fwd", 0.0), prof.ms.get("units_bwd", 0.0)
+    # PyTorch's own: pairs sorted by unit, bf16 addmm per unit and layer, autograd backward
+    order = torch.argsort(idx, stable=True)
+    counts = torch.bincount(idx, minlength=M).tolist()
+    leaves = [b.clone().requires_grad_(True) for b in bank]
+
+    def torch_step(i):
+        vs = v.index_select(0, order).requires_grad_(True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            outs, start = [], 0
+            for j, n in enumerate(counts):
+                hidden = torch.nn.functional.gelu(torch.addmm(leaves[1][j], vs[start:start + n], leaves[0][j]))
+                outs.append(torch.addmm(leaves[3][j], hidden, leaves[2][j]))
+                start += n
+            out = torch.cat(outs)
+        out.backward(cot.index_select(0, order))
+        for leaf in leaves:
+            leaf.grad = None
+
+    for i in range(3):
+        torch_step(i)
+    torch_total, _ = timed_steps(torch_step, max(3, args.steps // 4), torch.cuda.synchronize)
+    cpu = None
+    if not args.no_cpu_baseline:
+        from oracle import units_oracle as U
+
+        n = 4096   # a sample of the pairs: about a second of numpy
+        hv, hi, hc = v[:n].cpu().numpy(), idx[:n].cpu().numpy(), cot[:n].float().cpu().numpy()
+        hb = [b.cpu().numpy() for b in bank]
+        t0 = time.perf_counter()
+        reps = 0
+        while time.perf_counter() - t0 < 10.0:
+            _, hp = U.forward_grouped(hv, hi, *hb, bf16=True)
+            U.backward_grouped(hv, hi, *hb, hp, hc, bf16=True)
+            reps += 1
+        cpu = {"value": reps * n / (time.perf_counter() - t0), "unit": "pairs/s", "cores": 1, "kind": "port",
+               "sample": f"{reps} passes of forward + backward over {n} of the window's pairs (numpy restatement, bf16 rounding emulated)"}
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    kernel_ms = fwd_ms + bwd_ms
+    flops = 3 * 2.0 * P * (4 * d * H + H * d)   # forward once, backward twice (inputs and weights)
+    achieved = flops / (kernel_ms * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": "grouped unit pass pairs/s (forward + backward)", "value": P / (kernel_ms * 1e-3), "unit": "pairs/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": kernel_ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 products", "data": "synthetic",
+        "config": {"workload": WORKLOADS[name], "l2": "a 256 MB buffer is written between the steps",
+                   "forward_ms": fwd_ms, "backward_ms": bwd_ms, "step_with_flush_ms": spread(each),
+                   "torch_grouped_bf16_addmm_autograd_ms": torch_total / max(3, args.steps // 4)},
+        "gpu_launches": 23 * args.steps,
+        "roofline": {"bound": "tensor", "kernel": "k_units_tc", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                     "frac": achieved / peak, "traffic": None, "peak_source": "measured (sustained)" if peaks else "fallback",
+                     "how": "3 x 2 P (4d H + H d) flops (forward, and the backward's input and weight products) / the two calls' event time in a profiled step"},
+        "cpu_baseline": cpu, "clocks": clocks_summary(clock_lines, 0)}))  # fmt: skip
+
+
 def run_trainer_sharded(args, c: dict, name: str, world: int, rank: int, dev) -> None:
     """`--config adamw --gpus N`: the same parameter vector replicated on N ranks, a step = the gradient exchange
     and the AdamW step as ONE kernel per rank over peer memory (`ShardedAdamW`: reduce-scatter, step, all-gather),
@@ -891,6 +984,10 @@ def main() -> None:
         if args.steps == 100:
             args.steps = 20
         run_decoder(args, c, args.config)
+    elif c.get("units"):
+        if args.steps == 100:
+            args.steps = 20
+        run_units(args, c, args.config)
     elif c.get("trainer"):
         if args.steps == 100:
             args.steps = 20 if args.impl == "ours" else 5

@@ -354,21 +354,27 @@ struct DPre : Base {
         float p[8];
         load8(pre + pair(m) * H + c0, p);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            acc[i] = rnd<BF>(rnd<BF>(acc[i]) * gelu_erf_grad(p[i]));
-            second[i] = gelu_erf(p[i]);
+        for (int i = 0; i < 8; ++i) {   // one erf for the activation and its derivative
+            const float cdf = 0.5f * (1.0f + erff(p[i] * kSqrtHalf));
+            acc[i] = rnd<BF>(rnd<BF>(acc[i]) * (cdf + p[i] * expf(-0.5f * p[i] * p[i]) * kInvSqrt2Pi));
+            second[i] = p[i] * cdf;
         }
         store8(dpre + static_cast<int64_t>(start + m) * H + c0, acc);
         return true;
     }
-    // column c of the two transposed tiles (128 sorted positions from the tile's first, zeros past its pairs)
-    __device__ void store_column(int c, int m0, const __nv_bfloat16* first, const __nv_bfloat16* second) const {
+    // column c of the transposed tile: 128 sorted positions from the tile's first, a word {dpre, act(pre)} each,
+    // zeros past the tile's pairs
+    __device__ void store_column(int c, int m0, const uint32_t* both) const {
         if (c >= H) return;
         const int units8 = (min(len - m0, 128) + 7) >> 3;
         const int64_t at = static_cast<int64_t>(c) * ld + start + m0;
         for (int j = 0; j < units8; ++j) {
-            *reinterpret_cast<uint4*>(dpre_t + at + 8 * j) = *reinterpret_cast<const uint4*>(first + 8 * j);
-            *reinterpret_cast<uint4*>(hid_t + at + 8 * j) = *reinterpret_cast<const uint4*>(second + 8 * j);
+            const uint4 lo = *reinterpret_cast<const uint4*>(both + 8 * j), hi = *reinterpret_cast<const uint4*>(both + 8 * j + 4);
+            // __byte_perm(a, b, 0x5410): the low halves of a and b; 0x7632: their high halves
+            *reinterpret_cast<uint4*>(dpre_t + at + 8 * j) = make_uint4(__byte_perm(lo.x, lo.y, 0x5410), __byte_perm(lo.z, lo.w, 0x5410),
+                                                                         __byte_perm(hi.x, hi.y, 0x5410), __byte_perm(hi.z, hi.w, 0x5410));
+            *reinterpret_cast<uint4*>(hid_t + at + 8 * j) = make_uint4(__byte_perm(lo.x, lo.y, 0x7632), __byte_perm(lo.z, lo.w, 0x7632),
+                                                                        __byte_perm(hi.x, hi.y, 0x7632), __byte_perm(hi.z, hi.w, 0x7632));
         }
     }
 };
@@ -495,8 +501,8 @@ __device__ __forceinline__ void umma_block_sw128(uint32_t tmem_d, uint64_t desc_
 // warp's 4 rows fill 512 contiguous bytes), the next block while the tensor cores work on this one; a stage
 // is requested again when the commit of the products that read it has arrived. The epilogue reads the
 // accumulator 8 columns at a time, a thread its own row and half of the columns; a product whose result is also wanted transposed
-// (dpre) collects it as two bfloat16 tiles [column, row] in the stages' memory and writes them a column per
-// thread, 16 bytes a store.
+// (dpre) collects it with its companion as a tile [column, row] of bfloat16 pairs in the stages' memory and
+// writes the two a column per thread, 16 bytes a store.
 template <class Op, int BN>
 __global__ void __launch_bounds__(kTcThreads) k_units_tc(Op op, int* status) {
     static_assert(kChunk == 64, "a K block is one 128-byte swizzle row");
@@ -571,8 +577,7 @@ __global__ void __launch_bounds__(kTcThreads) k_units_tc(Op op, int* status) {
     mbar_wait(&bar[(chunks - 1) % kStages], ((chunks - 1) / kStages) & 1, status);   // the last commit covers every product before it
     tcgen05_fence_after();
     float x[8], second[8];
-    __nv_bfloat16* tile_a = reinterpret_cast<__nv_bfloat16*>(dyn);   // [BN][128] each, in the stages' memory (every product has read it)
-    __nv_bfloat16* tile_b = tile_a + BN * 128;
+    uint32_t* tile = reinterpret_cast<uint32_t*>(dyn);   // [BN][128] words {result, second}, in the stages' memory (every product has read it)
     // warps w and w + 4 reach the same 32 rows of the accumulator: each takes half of the columns
     const int row = (warp & 3) * 32 + (tid & 31), half = (warp >> 2) * (BN / 2);
     for (int cb = half; cb < half + BN / 2; cb += 8) {
@@ -580,15 +585,12 @@ __global__ void __launch_bounds__(kTcThreads) k_units_tc(Op op, int* status) {
         const bool wrote = op.store(m0 + row, n0 + cb, x, bias_s + cb, second);
         if constexpr (Op::kTransposed) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                tile_a[(cb + i) * 128 + row] = __float2bfloat16_rn(wrote ? x[i] : 0.0f);
-                tile_b[(cb + i) * 128 + row] = __float2bfloat16_rn(wrote ? second[i] : 0.0f);
-            }
+            for (int i = 0; i < 8; ++i) tile[(cb + i) * 128 + row] = wrote ? pack2(x[i], second[i]) : 0u;
         }
     }
     if constexpr (Op::kTransposed) {
         __syncthreads();
-        if (tid < BN) op.store_column(n0 + tid, m0, tile_a + tid * 128, tile_b + tid * 128);
+        if (tid < BN) op.store_column(n0 + tid, m0, tile + tid * 128);
     }
     tcgen05_fence_before();
     __syncthreads();
