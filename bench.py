@@ -370,7 +370,7 @@ def run_resident(args, c: dict, name: str) -> None:
     per_position = [tuple(a[:, t].contiguous() for a in (z, ctx, scalars, reset)) for t in range(T)] if c.get("stream") else []
     calls = [0]
 
-    def step(_i=0):
+    def step(_i=0, exchange=True):
         nonlocal bw_scratch
         if per_position:
             from hsn_b200.window import stream_step
@@ -394,7 +394,7 @@ def run_resident(args, c: dict, name: str) -> None:
         window_backward(model, tape["rec_c"], tape["rec_b"], tape["rec_h_old"], tape["sel_cell_idx"],
                         tape["sel_unit_idx"], tape["sel_valid"], reset, cots[0], cots[1], cots[2], rec,
                         scratch=bw_scratch, info=info)  # fmt: skip
-        if world > 1:  # the training-gradient exchange after each window backward
+        if world > 1 and exchange:  # the training-gradient exchange after each window backward
             dist.all_reduce(grads)
 
     def barrier():
@@ -413,8 +413,9 @@ def run_resident(args, c: dict, name: str) -> None:
     total_ms, each = timed_steps(step, args.steps, barrier)
     stop.set()
     sampler.join(timeout=2)
-    with launch_profile() as prof:
-        step()
+    barrier()
+    with launch_profile() as prof:   # (without the exchange: its wait for the other ranks would be charged to the launch before it)
+        step(exchange=False)
     barrier()
     times = torch.tensor([total_ms / args.steps], device=dev, dtype=torch.float64)
     if world > 1:
@@ -602,9 +603,11 @@ def run_taped(args, c: dict, name: str) -> None:
     ms_e2e = total_e2e / e2e_steps
     stop.set()
     sampler.join(timeout=2)
-    # one more step, untimed, with an event before every launch: the per-kernel times and counts
+    # one more step, untimed, with an event before every launch: the per-kernel times and counts (without the
+    # gradient exchange: its wait for the other ranks would be charged to the launch before it)
+    barrier()
     with launch_profile() as prof:
-        step(ids)
+        job.step(ids)
     barrier()
     # the same global batch spread over the ranks (strong scaling), when there are several
     strong = None
