@@ -223,7 +223,6 @@ __device__ __forceinline__ void zero8(float x[8]) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) x[i] = 0.0f;
 }
-constexpr uint4 kZero16 = {0u, 0u, 0u, 0u};
 
 // What every product knows: the sizes, the weights (float32 as the caller holds them; bfloat16 packed
 // [N, K] for the product that reads them), the tables, and (after setup) its unit and range.
@@ -246,6 +245,7 @@ struct Base {
         return true;
     }
     __device__ int64_t pair(int sorted_offset) const { return tb.order[start + sorted_offset]; }
+    __device__ uint4 aux(int, int) const { return make_uint4(0, 0, 0, 0); }   // nothing to request ahead
 };
 
 // pre[pair] = v[pair] W1[u] + b1[u]                      wp: W1 as [M, H, Din]; with bf16 products A is the
@@ -273,7 +273,7 @@ struct First : Base {
     }
     __device__ const __nv_bfloat16* a_row(int m) const { return m < len ? v_s + static_cast<int64_t>(start + m) * Din : nullptr; }
     __device__ const __nv_bfloat16* b_row(int c) const { return c < H ? wp + (static_cast<int64_t>(unit) * H + c) * Din : nullptr; }
-    __device__ bool store(int m, int c0, float acc[8], const float* bias8, float*) const {
+    __device__ bool store(int m, int c0, float acc[8], const float* bias8, float*, uint4) const {
         if (m >= len || c0 >= H) return false;
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = rnd<BF>(acc[i] + rnd<BF>(bias8[i]));
@@ -316,7 +316,7 @@ struct Second : Base {
     }
     __device__ const __nv_bfloat16* a_row(int m) const { return m < len ? hid_s + static_cast<int64_t>(start + m) * H : nullptr; }
     __device__ const __nv_bfloat16* b_row(int c) const { return c < D ? wp + (static_cast<int64_t>(unit) * D + c) * H : nullptr; }
-    __device__ bool store(int m, int c0, float acc[8], const float* bias8, float*) const {
+    __device__ bool store(int m, int c0, float acc[8], const float* bias8, float*, uint4) const {
         if (m >= len || c0 >= D) return false;
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = rnd<BF>(acc[i] + rnd<BF>(bias8[i]));
@@ -349,10 +349,26 @@ struct DPre : Base {
     __device__ const E* a_row(int m) const { return m < len ? dout + pair(m) * D : nullptr; }
     __device__ const __nv_bfloat16* b_row(int c) const { return c < H ? wp + (static_cast<int64_t>(unit) * H + c) * D : nullptr; }
     // acc: in the product, out dpre; second: out act(pre)
-    __device__ bool store(int m, int c0, float acc[8], const float*, float* second) const {
+    // the 8 pre-activations the store of (m, c0) reads, requested ahead of the accumulator
+    __device__ uint4 aux(int m, int c0) const {
+        if (m >= len || c0 >= H) return make_uint4(0, 0, 0, 0);
+        const E* src = pre + pair(m) * H + c0;
+        if constexpr (BF) return *reinterpret_cast<const uint4*>(src);
+        else return make_uint4(0, 0, 0, 0);
+    }
+    __device__ bool store(int m, int c0, float acc[8], const float*, float* second, uint4 held) const {
         if (m >= len || c0 >= H) return false;
         float p[8];
-        load8(pre + pair(m) * H + c0, p);
+        if constexpr (BF) {
+            const uint32_t w[4] = {held.x, held.y, held.z, held.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                p[2 * i] = __uint_as_float(w[i] << 16);
+                p[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+            }
+        } else {
+            load8(pre + pair(m) * H + c0, p);
+        }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {   // one erf for the activation and its derivative
             const float cdf = 0.5f * (1.0f + erff(p[i] * kSqrtHalf));
@@ -400,7 +416,7 @@ struct DInput : Base {
     }
     __device__ const E* a_row(int m) const { return m < len ? dpre + static_cast<int64_t>(start + m) * H : nullptr; }
     __device__ const __nv_bfloat16* b_row(int c) const { return c < Din ? wp + (static_cast<int64_t>(unit) * Din + c) * H : nullptr; }
-    __device__ bool store(int m, int c0, float acc[8], const float*, float*) const {
+    __device__ bool store(int m, int c0, float acc[8], const float*, float*, uint4) const {
         if (m >= len || c0 >= Din) return false;
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = rnd<BF>(acc[i]);
@@ -432,7 +448,7 @@ struct DWeight1 : Base {
     }
     __device__ const __nv_bfloat16* a_row(int m) const { return m < Din ? v_t + static_cast<int64_t>(m) * ld + start : nullptr; }
     __device__ const __nv_bfloat16* b_row(int c) const { return c < H ? dpre_t + static_cast<int64_t>(c) * ld + start : nullptr; }
-    __device__ bool store(int m, int c0, float acc[8], const float*, float*) const {
+    __device__ bool store(int m, int c0, float acc[8], const float*, float*, uint4) const {
         if (m >= Din || c0 >= H) return false;
         store8(partial + (static_cast<int64_t>(item) * Din + m) * H + c0, acc);
         return true;
@@ -461,7 +477,7 @@ struct DWeight2 : Base {
     }
     __device__ const __nv_bfloat16* a_row(int m) const { return m < H ? hid_t + static_cast<int64_t>(m) * ld + start : nullptr; }
     __device__ const __nv_bfloat16* b_row(int c) const { return c < D ? dout_t + static_cast<int64_t>(c) * ld + start : nullptr; }
-    __device__ bool store(int m, int c0, float acc[8], const float*, float*) const {
+    __device__ bool store(int m, int c0, float acc[8], const float*, float*, uint4) const {
         if (m >= H || c0 >= D) return false;
         store8(partial + (static_cast<int64_t>(item) * H + m) * D + c0, acc);
         return true;
@@ -500,7 +516,7 @@ __device__ __forceinline__ void umma_block_sw128(uint32_t tmem_d, uint64_t desc_
 // memory) as asynchronous 16-byte copies to their swizzled places (unit u of row r at u ^ (r % 8), so a
 // warp's 4 rows fill 512 contiguous bytes), the next block while the tensor cores work on this one; a stage
 // is requested again when the commit of the products that read it has arrived. The epilogue reads the
-// accumulator 8 columns at a time, a thread its own row and half of the columns; a product whose result is also wanted transposed
+// accumulator 32 columns at a time, a thread its own row and half of the columns; a product whose result is also wanted transposed
 // (dpre) collects it with its companion as a tile [column, row] of bfloat16 pairs in the stages' memory and
 // writes the two a column per thread, 16 bytes a store.
 template <class Op, int BN>
@@ -576,16 +592,22 @@ __global__ void __launch_bounds__(kTcThreads) k_units_tc(Op op, int* status) {
     }
     mbar_wait(&bar[(chunks - 1) % kStages], ((chunks - 1) / kStages) & 1, status);   // the last commit covers every product before it
     tcgen05_fence_after();
-    float x[8], second[8];
+    float x[32], second[8];
     uint32_t* tile = reinterpret_cast<uint32_t*>(dyn);   // [BN][128] words {result, second}, in the stages' memory (every product has read it)
     // warps w and w + 4 reach the same 32 rows of the accumulator: each takes half of the columns
     const int row = (warp & 3) * 32 + (tid & 31), half = (warp >> 2) * (BN / 2);
-    for (int cb = half; cb < half + BN / 2; cb += 8) {
-        tmem_ld8(tmem_addr(taddr, (warp & 3) * 32, cb), x);
-        const bool wrote = op.store(m0 + row, n0 + cb, x, bias_s + cb, second);
-        if constexpr (Op::kTransposed) {
+    for (int cb = half; cb < half + BN / 2; cb += 32) {   // 32 columns a wait on tensor memory
+        uint4 held[4];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) tile[(cb + i) * 128 + row] = wrote ? pack2(x[i], second[i]) : 0u;
+        for (int j = 0; j < 4; ++j) held[j] = op.aux(m0 + row, n0 + cb + 8 * j);
+        tmem_ld32(tmem_addr(taddr, (warp & 3) * 32, cb), x);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const bool wrote = op.store(m0 + row, n0 + cb + 8 * j, x + 8 * j, bias_s + cb + 8 * j, second, held[j]);
+            if constexpr (Op::kTransposed) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) tile[(cb + 8 * j + i) * 128 + row] = wrote ? pack2(x[8 * j + i], second[i]) : 0u;
+            }
         }
     }
     if constexpr (Op::kTransposed) {
@@ -632,8 +654,8 @@ __global__ void __launch_bounds__(256) k_units_simt(Op op) {
     const float* bias = op.bias_row();
     float second[8];
     if (bias) bias += n0 + 8 * tx;   // read only where the store takes the columns
-    op.store(m0 + 2 * ty, n0 + 8 * tx, acc[0], bias, second);
-    op.store(m0 + 2 * ty + 1, n0 + 8 * tx, acc[1], bias, second);
+    op.store(m0 + 2 * ty, n0 + 8 * tx, acc[0], bias, second, make_uint4(0, 0, 0, 0));
+    op.store(m0 + 2 * ty + 1, n0 + 8 * tx, acc[1], bias, second, make_uint4(0, 0, 0, 0));
 }
 
 // out[b][c][r] = bfloat16(src[b][row(r)][c]) for r < rows, c < cols: 32 x 32 tiles through shared memory. With
