@@ -113,14 +113,22 @@ __global__ void __launch_bounds__(kSortBlock) k_units_count(const int64_t* unit_
 __global__ void __launch_bounds__(256) k_units_scan(int blocks, int M, int seg, Tables tb) {
     __shared__ int total[kMaxUnits];
     const int tid = threadIdx.x;
-    for (int u = tid; u < M; u += 256) {
+    for (int u = tid >> 5; u < M; u += 8) {   // a warp a unit: 32 sort blocks a round, an exclusive scan by shuffles
+        const int lane = tid & 31;
         int run = 0;
-        for (int b = 0; b < blocks; ++b) {
-            const int n = tb.block_off[static_cast<int64_t>(b) * M + u];
-            tb.block_off[static_cast<int64_t>(b) * M + u] = run;
-            run += n;
+        for (int b0 = 0; b0 < blocks; b0 += 32) {
+            const int b = b0 + lane;
+            const int n = b < blocks ? tb.block_off[static_cast<int64_t>(b) * M + u] : 0;
+            int inc = n;
+#pragma unroll
+            for (int w = 1; w < 32; w <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, inc, w);
+                if (lane >= w) inc += up;
+            }
+            if (b < blocks) tb.block_off[static_cast<int64_t>(b) * M + u] = run + inc - n;
+            run += __shfl_sync(0xffffffffu, inc, 31);
         }
-        total[u] = run;
+        if (lane == 0) total[u] = run;
     }
     __syncthreads();
     if (tid == 0) {
