@@ -261,6 +261,8 @@ struct Base {
 template <class E, bool BF>
 struct First : Base {
     static constexpr bool kTransposed = false;
+    static constexpr int kStagedTiles = BF ? 2 : 0;   // pre and act(pre) leave through shared memory, whole rows at a time
+    using Staged = __nv_bfloat16;
     const float* v;
     const __nv_bfloat16* v_s;   // [ld, Din]
     E* pre;
@@ -281,17 +283,27 @@ struct First : Base {
     }
     __device__ const __nv_bfloat16* a_row(int m) const { return m < len ? v_s + static_cast<int64_t>(start + m) * Din : nullptr; }
     __device__ const __nv_bfloat16* b_row(int c) const { return c < H ? wp + (static_cast<int64_t>(unit) * H + c) * Din : nullptr; }
-    __device__ bool store(int m, int c0, float acc[8], const float* bias8, float*, uint4) const {
+    __device__ bool store(int m, int c0, float acc[8], const float* bias8, float* second, uint4) const {
         if (m >= len || c0 >= H) return false;
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = rnd<BF>(acc[i] + rnd<BF>(bias8[i]));
-        store8(pre + pair(m) * H + c0, acc);
-        if (BF) {
+        if constexpr (BF) {   // the tensor-core kernel collects pre and act(pre) in shared memory and writes whole rows
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] = gelu_erf(acc[i]);
-            store8(hid_s + static_cast<int64_t>(start + m) * H + c0, acc);
+            for (int i = 0; i < 8; ++i) second[i] = gelu_erf(acc[i]);
+        } else {
+            store8(pre + pair(m) * H + c0, acc);
         }
         return true;
+    }
+    // where row m of the tile's two results goes (column 0 of the tensors), null past the tile's pairs
+    __device__ void row_out(int m, __nv_bfloat16*& first, __nv_bfloat16*& other) const {
+        first = other = nullptr;
+        if constexpr (BF) {
+            if (m < len) {
+                first = pre + pair(m) * H;
+                other = hid_s + static_cast<int64_t>(start + m) * H;
+            }
+        }
     }
 };
 
@@ -300,6 +312,8 @@ struct First : Base {
 template <class E, bool BF>
 struct Second : Base {
     static constexpr bool kTransposed = false;
+    static constexpr int kStagedTiles = BF ? 1 : 0;
+    using Staged = __nv_bfloat16;
     const E* pre;
     const __nv_bfloat16* hid_s;
     E* out;
@@ -328,8 +342,14 @@ struct Second : Base {
         if (m >= len || c0 >= D) return false;
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = rnd<BF>(acc[i] + rnd<BF>(bias8[i]));
-        store8(out + pair(m) * D + c0, acc);
+        if constexpr (!BF) store8(out + pair(m) * D + c0, acc);
         return true;
+    }
+    __device__ void row_out(int m, __nv_bfloat16*& first, __nv_bfloat16*& other) const {
+        other = nullptr;
+        first = nullptr;
+        if constexpr (BF)
+            if (m < len) first = out + pair(m) * D;
     }
 };
 
@@ -338,6 +358,8 @@ struct Second : Base {
 template <class E, bool BF>
 struct DPre : Base {
     static constexpr bool kTransposed = BF;
+    static constexpr int kStagedTiles = BF ? 1 : 0;
+    using Staged = __nv_bfloat16;
     const E *pre, *dout;
     E* dpre;   // in sorted order
     __nv_bfloat16 *dpre_t, *hid_t;
@@ -383,8 +405,14 @@ struct DPre : Base {
             acc[i] = rnd<BF>(rnd<BF>(acc[i]) * (cdf + p[i] * expf(-0.5f * p[i] * p[i]) * kInvSqrt2Pi));
             second[i] = p[i] * cdf;
         }
-        store8(dpre + static_cast<int64_t>(start + m) * H + c0, acc);
+        if constexpr (!BF) store8(dpre + static_cast<int64_t>(start + m) * H + c0, acc);
         return true;
+    }
+    __device__ void row_out(int m, __nv_bfloat16*& first, __nv_bfloat16*& other) const {
+        other = nullptr;
+        first = nullptr;
+        if constexpr (BF)
+            if (m < len) first = dpre + static_cast<int64_t>(start + m) * H;
     }
     // column c of the transposed tile: 128 sorted positions from the tile's first, a word {dpre, act(pre)} each,
     // zeros past the tile's pairs
@@ -407,6 +435,8 @@ struct DPre : Base {
 template <class E, bool BF>
 struct DInput : Base {
     static constexpr bool kTransposed = false;
+    static constexpr int kStagedTiles = BF ? 1 : 0;
+    using Staged = float;
     const E* dpre;
     float* dv;
     __device__ bool setup(int x) { return tile(x); }
@@ -428,8 +458,12 @@ struct DInput : Base {
         if (m >= len || c0 >= Din) return false;
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = rnd<BF>(acc[i]);
-        store8(dv + pair(m) * Din + c0, acc);
+        if constexpr (!BF) store8(dv + pair(m) * Din + c0, acc);
         return true;
+    }
+    __device__ void row_out(int m, float*& first, float*& other) const {
+        other = nullptr;
+        first = m < len ? dv + pair(m) * Din : nullptr;
     }
 };
 
@@ -437,6 +471,8 @@ struct DInput : Base {
 template <class E, bool BF>
 struct DWeight1 : Base {
     static constexpr bool kTransposed = false;
+    static constexpr int kStagedTiles = 0;
+    using Staged = float;
     const float* v;
     const E* dpre;
     const __nv_bfloat16 *v_t, *dpre_t;   // [Din, ld], [H, ld]
@@ -467,6 +503,8 @@ struct DWeight1 : Base {
 template <class E, bool BF>
 struct DWeight2 : Base {
     static constexpr bool kTransposed = false;
+    static constexpr int kStagedTiles = 0;
+    using Staged = float;
     const E *pre, *dout;
     const __nv_bfloat16 *hid_t, *dout_t;   // [H, ld], [D, ld]
     float* partial;
@@ -507,6 +545,7 @@ __device__ __forceinline__ void cp_async_wait_but() {
 
 constexpr int kStages = 2;
 constexpr int kTcThreads = 256;
+constexpr int kTilePitch = 128 + 4;   // words between the columns of a transposed tile: a quarter warp's 16-byte reads of 8 columns fall on 8 groups of banks
 
 // One K = 16 step of a product whose two operands are in the 128-byte swizzle: inside the 128-byte K block a
 // step moves both start addresses by 32 bytes.
@@ -531,6 +570,9 @@ template <class Op, int BN>
 __global__ void __launch_bounds__(kTcThreads) k_units_tc(Op op, int* status) {
     static_assert(kChunk == 64, "a K block is one 128-byte swizzle row");
     constexpr int kStageBytes = (128 + BN) * 128;   // A tile then B tile, 128 bytes a row
+    using ST = typename Op::Staged;
+    constexpr int kRowPitch = BN * static_cast<int>(sizeof(ST)) + 16;   // a row of a staged result tile
+    constexpr int kStagedBase = Op::kTransposed ? BN * kTilePitch * 4 : 0;   // behind the transposed tile
     constexpr int kPass = kTcThreads / 8;                   // rows the block requests in one pass: 8 lanes a row
     constexpr int kRowsA = 128 / kPass, kRowsB = BN / kPass;   // rows of a tile a thread requests
     extern __shared__ unsigned char dyn_raw[];
@@ -614,13 +656,33 @@ __global__ void __launch_bounds__(kTcThreads) k_units_tc(Op op, int* status) {
             const bool wrote = op.store(m0 + row, n0 + cb + 8 * j, x + 8 * j, bias_s + cb + 8 * j, second, held[j]);
             if constexpr (Op::kTransposed) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) tile[(cb + 8 * j + i) * 128 + row] = wrote ? pack2(x[8 * j + i], second[i]) : 0u;
+                for (int i = 0; i < 8; ++i) tile[(cb + 8 * j + i) * kTilePitch + row] = wrote ? pack2(x[8 * j + i], second[i]) : 0u;
+            }
+            if constexpr (Op::kStagedTiles > 0) {   // row-major tiles, rows kRowPitch bytes apart (a quarter warp's 8 rows on 8 groups of banks)
+                ST* at = reinterpret_cast<ST*>(dyn + kStagedBase + row * kRowPitch) + cb + 8 * j;
+                store8(at, x + 8 * j);
+                if constexpr (Op::kStagedTiles > 1) store8(reinterpret_cast<ST*>(reinterpret_cast<unsigned char*>(at) + 128 * kRowPitch), second);
             }
         }
     }
     if constexpr (Op::kTransposed) {
         __syncthreads();
-        if (tid < BN) op.store_column(n0 + tid, m0, tile + tid * 128);
+        if (tid < BN) op.store_column(n0 + tid, m0, tile + tid * kTilePitch);
+    }
+    if constexpr (Op::kStagedTiles > 0) {   // consecutive threads write one row's 16-byte units: whole lines of global memory
+        __syncthreads();
+        constexpr int kPer = 16 / static_cast<int>(sizeof(ST)), kUnits = BN / kPer;   // elements a unit, units a row
+        const int units = min(BN, op.cols() - n0) / kPer;
+        for (int e = tid; e < 128 * kUnits; e += kTcThreads) {
+            const int r = e / kUnits, u = e % kUnits;
+            ST *first, *other;
+            op.row_out(m0 + r, first, other);
+            if (u < units && first) {
+                const unsigned char* at = dyn + kStagedBase + r * kRowPitch + u * 16;
+                *reinterpret_cast<uint4*>(first + n0 + kPer * u) = *reinterpret_cast<const uint4*>(at);
+                if constexpr (Op::kStagedTiles > 1) *reinterpret_cast<uint4*>(other + n0 + kPer * u) = *reinterpret_cast<const uint4*>(at + 128 * kRowPitch);
+            }
+        }
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -890,7 +952,8 @@ void fill_base(Op& op, const HsnwUnits* u, const Tables& tb, const Plan& p, cons
 template <class Op, int BN>
 void launch_tc(const Op& op, int items, int rows, int cols, int* status, cudaStream_t stream) {
     size_t shared = static_cast<size_t>(kStages) * (128 + BN) * 128;
-    if (Op::kTransposed) shared = std::max(shared, static_cast<size_t>(2) * BN * 128 * 2);   // the two transposed tiles
+    shared = std::max(shared, (Op::kTransposed ? static_cast<size_t>(BN) * kTilePitch * 4 : 0)
+                                  + static_cast<size_t>(Op::kStagedTiles) * 128 * (BN * sizeof(typename Op::Staged) + 16));   // the result tiles
     shared += 1024;   // the kernel starts its stages on a 1024-byte boundary
     k_units_tc<Op, BN><<<dim3(items, (rows + 127) / 128, (cols + BN - 1) / BN), kTcThreads, shared, stream>>>(op, status);
 }
