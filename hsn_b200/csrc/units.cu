@@ -414,20 +414,17 @@ struct DPre : Base {
         if constexpr (BF)
             if (m < len) first = dpre + static_cast<int64_t>(start + m) * H;
     }
-    // column c of the transposed tile: 128 sorted positions from the tile's first, a word {dpre, act(pre)} each,
-    // zeros past the tile's pairs
-    __device__ void store_column(int c, int m0, const uint32_t* both) const {
-        if (c >= H) return;
-        const int units8 = (min(len - m0, 128) + 7) >> 3;
-        const int64_t at = static_cast<int64_t>(c) * ld + start + m0;
-        for (int j = 0; j < units8; ++j) {
-            const uint4 lo = *reinterpret_cast<const uint4*>(both + 8 * j), hi = *reinterpret_cast<const uint4*>(both + 8 * j + 4);
-            // __byte_perm(a, b, 0x5410): the low halves of a and b; 0x7632: their high halves
-            *reinterpret_cast<uint4*>(dpre_t + at + 8 * j) = make_uint4(__byte_perm(lo.x, lo.y, 0x5410), __byte_perm(lo.z, lo.w, 0x5410),
-                                                                         __byte_perm(hi.x, hi.y, 0x5410), __byte_perm(hi.z, hi.w, 0x5410));
-            *reinterpret_cast<uint4*>(hid_t + at + 8 * j) = make_uint4(__byte_perm(lo.x, lo.y, 0x7632), __byte_perm(lo.z, lo.w, 0x7632),
-                                                                        __byte_perm(hi.x, hi.y, 0x7632), __byte_perm(hi.z, hi.w, 0x7632));
-        }
+    // unit j (8 sorted positions) of column c of the transposed tile, a word {dpre, act(pre)} a position: 16
+    // consecutive threads write a column's 256 contiguous bytes of each result; zeros past the tile's pairs
+    __device__ void store_unit(int c, int m0, int j, const uint32_t* column) const {
+        if (c >= H || 8 * j >= ((min(len - m0, 128) + 7) & ~7)) return;
+        const int64_t at = static_cast<int64_t>(c) * ld + start + m0 + 8 * j;
+        const uint4 lo = *reinterpret_cast<const uint4*>(column + 8 * j), hi = *reinterpret_cast<const uint4*>(column + 8 * j + 4);
+        // __byte_perm(a, b, 0x5410): the low halves of a and b; 0x7632: their high halves
+        *reinterpret_cast<uint4*>(dpre_t + at) = make_uint4(__byte_perm(lo.x, lo.y, 0x5410), __byte_perm(lo.z, lo.w, 0x5410),
+                                                             __byte_perm(hi.x, hi.y, 0x5410), __byte_perm(hi.z, hi.w, 0x5410));
+        *reinterpret_cast<uint4*>(hid_t + at) = make_uint4(__byte_perm(lo.x, lo.y, 0x7632), __byte_perm(lo.z, lo.w, 0x7632),
+                                                            __byte_perm(hi.x, hi.y, 0x7632), __byte_perm(hi.z, hi.w, 0x7632));
     }
 };
 
@@ -565,7 +562,7 @@ __device__ __forceinline__ void umma_block_sw128(uint32_t tmem_d, uint64_t desc_
 // is requested again when the commit of the products that read it has arrived. The epilogue reads the
 // accumulator 32 columns at a time, a thread its own row and half of the columns; a product whose result is also wanted transposed
 // (dpre) collects it with its companion as a tile [column, row] of bfloat16 pairs in the stages' memory and
-// writes the two a column per thread, 16 bytes a store.
+// writes the two 16 threads a column, 16 bytes a store.
 template <class Op, int BN>
 __global__ void __launch_bounds__(kTcThreads) k_units_tc(Op op, int* status) {
     static_assert(kChunk == 64, "a K block is one 128-byte swizzle row");
@@ -667,7 +664,7 @@ __global__ void __launch_bounds__(kTcThreads) k_units_tc(Op op, int* status) {
     }
     if constexpr (Op::kTransposed) {
         __syncthreads();
-        if (tid < BN) op.store_column(n0 + tid, m0, tile + tid * kTilePitch);
+        for (int e = tid; e < BN * 16; e += kTcThreads) op.store_unit(n0 + (e >> 4), m0, e & 15, tile + (e >> 4) * kTilePitch);
     }
     if constexpr (Op::kStagedTiles > 0) {   // consecutive threads write one row's 16-byte units: whole lines of global memory
         __syncthreads();
