@@ -157,3 +157,39 @@ def test_the_pairs_order_does_not_matter_at_full_size(prod: str) -> None:
     want_out, want_pre = U.forward_grouped(v[rows], idx[rows], *bank, bf16=bf)
     _close(to_np(out[rows].float()), want_out, tol, "out")
     _close(to_np(pre[rows].float()), want_pre, tol, "pre")
+
+
+@pytest.mark.parametrize("prod", ["bf16", "fp32"])
+def test_against_pytorch_on_the_device(prod: str) -> None:
+    """The reference's own formulation run live on the GPU (pairs sorted by unit, one ``addmm`` per layer and present
+    unit, under bf16 autocast or not, autograd's backward) against ``forward_grouped`` with the same leaves."""
+    from hsn_b200.kernels.units import forward_grouped
+
+    bf = prod == "bf16"
+    P, M, d, H = 3000, 6, 32, 256
+    v, idx, bank, cot = _case(np.random.default_rng(21), P, M, d, H, bf)
+    idx[idx == 4] = 1   # a unit nobody chose
+
+    def leaves():
+        return dev(v).requires_grad_(True), [dev(b).requires_grad_(True) for b in bank]
+
+    tv, tb = leaves()
+    out = forward_grouped(tv, dev(idx), *tb, prod=prod)
+    (out.float() * dev(cot)).sum().backward()
+    rv, rb = leaves()
+    order = torch.argsort(dev(idx), stable=True)
+    counts = torch.bincount(dev(idx), minlength=M).tolist()
+    with torch.autocast("cuda", dtype=torch.bfloat16, enabled=bf):
+        sorted_v, outs, start = rv.index_select(0, order), [], 0
+        for j, n in enumerate(counts):
+            if n:
+                hidden = torch.nn.functional.gelu(torch.addmm(rb[1][j], sorted_v[start:start + n], rb[0][j]))
+                outs.append(torch.addmm(rb[3][j], hidden, rb[2][j]))
+            start += n
+        want = torch.empty_like(torch.cat(outs)).index_copy_(0, order, torch.cat(outs))
+    (want.float() * dev(cot)).sum().backward()
+    tol = 2e-2 if bf else 1e-5
+    _close(to_np(out.detach().float()), to_np(want.detach().float()), tol, "out")
+    for name, a, b in zip(GRADS, [tv, *tb], [rv, *rb], strict=True):
+        want_grad = b.grad if b.grad is not None else torch.zeros_like(b)
+        _close(to_np(a.grad), to_np(want_grad), tol, name)
