@@ -121,6 +121,12 @@ class HsnwUnits(Structure):
     ]
 
 
+class HsnwScorer(Structure):
+    _fields_ = [(n, c_int32) for n in ("d", "n_cells", "n_units", "n_scalars", "prod_bf16")] + [("age_max", c_float)] + [
+        (n, c_void_p) for n in ("weight", "bias")
+    ]
+
+
 class HsnwPrologue(Structure):
     _fields_ = (
         [(n, c_int32) for n in PROLOGUE_INTS]
@@ -161,6 +167,11 @@ SYMBOLS: dict[str, tuple[object, list[object]]] = {
     "hsnw_window_prologue": (c_int, [POINTER(HsnwPrologue), c_void_p]),
     "hsnw_decode_scratch_bytes": (c_int64, [POINTER(HsnwDecoder), c_int64]),
     "hsnw_window_decode": (c_int, [POINTER(HsnwDecoder), c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p]),
+    "hsnw_scorer_scratch_bytes": (c_int64, [POINTER(HsnwScorer), c_int64, c_int]),
+    "hsnw_scorer_logits": (c_int, [POINTER(HsnwScorer), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
+                                   c_int64, c_void_p]),
+    "hsnw_scorer_logits_backward": (c_int, [POINTER(HsnwScorer), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
+                                            c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "hsnw_units_scratch_bytes": (c_int64, [POINTER(HsnwUnits), c_int64, c_int]),
     "hsnw_units_forward": (c_int, [POINTER(HsnwUnits), c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "hsnw_units_backward": (c_int, [POINTER(HsnwUnits), c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

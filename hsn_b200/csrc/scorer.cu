@@ -1,0 +1,526 @@
+// The replay's scorer logits over every cell of every window position, and the gradients of the scorer's
+// weight and bias (reference python/hsn/train/split.py:305-342, _scorer_logits, and autograd's backward of
+// it; the features are constants of the replay).
+//
+//   logits[r, n, :] = (W_h h[r, n] + (W_t [age[r, n] / age_max; scalars[r, n]] + b)) + W_row [u[r]; eps[r]]
+//   d W_h = sum_{r, n} g[r, n]^T h[r, n],  d W_t, d b likewise,  d W_row = sum_r (sum_n g[r, n])^T [u[r]; eps[r]]
+//
+// Both passes are one read of the recorded state h (R N d floats: 0.5 GB for a B32 T256 N256 d64 window) and are
+// bound by it. A persistent block takes tiles of 128 cells of one position: the tile of h (contiguous, 32 KB at
+// d = 64) arrives by one bulk copy into one of two stages while the block works on the other; age and scalars
+// (a few KB) go through registers into shared memory. Eight lanes share a cell, one per unit, and a warp works
+// on four cells at a time: the eight lanes read the same 16 bytes of the cell's row (a broadcast), and the four
+// cells read different quarters of their rows in the same instruction (cell c starts 2 c float4s further on and
+// wraps around), so a warp's load touches every bank once; a lane keeps its unit's weights in registers in the
+// order it meets them. The backward keeps a lane's gradient sums in registers over all of its block's tiles and
+// reduces them once at the end: lanes of a warp in turn into shared memory, warps and then blocks in order, so
+// two runs give the same bits.
+#include "../../include/hsn_scorer_b200.h"
+#include "../../include/hsn_window_b200.h"
+#include "common.cuh"
+#include "stage.cuh"
+#include "host_util.h"
+
+#include <algorithm>
+
+using namespace hsnw;
+
+namespace {
+
+constexpr int kCells = 128;    // cells of a tile
+constexpr int kThreads = 256;  // 8 warps x 4 cells x 8 units
+constexpr int kMaxTail = 16;   // 1 + scalars
+constexpr int kRowChunks = 64; // partial sums of the row block's gradient
+
+struct Ctx {
+    int d, N, M, S, F, tiles;
+    float age_max;
+    int64_t rows, items;
+    const float *weight, *bias, *u, *eps, *h, *scalars;
+    const int64_t* age;
+    float* rowterm;         // [rows, M]
+    float* logits;
+    const float* dlogits;
+    float* partial;         // [blocks][M][d + 1 + S + 1]: the state block, the tail block, the bias
+    float* rowsum;          // [rows][tiles][M] sums of the cotangent over a tile's cells
+    float* partial_row;     // [kRowChunks][M][2 d]
+    int* status;
+};
+
+template <bool BF>
+__device__ __forceinline__ float rnd(float x) {
+    return BF ? bf16r(x) : x;
+}
+
+// rowterm[r, j] = [u[r]; eps[r]] . W[j, :2d]
+template <bool BF>
+__global__ void __launch_bounds__(256) k_scorer_row(Ctx c) {
+    const int64_t e = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (e >= c.rows * c.M) return;
+    const int64_t r = e / c.M;
+    const int j = static_cast<int>(e - r * c.M);
+    const float* w = c.weight + static_cast<int64_t>(j) * c.F;
+    float sum = 0.0f;
+    for (int x = 0; x < c.d; ++x) sum = fmaf(rnd<BF>(c.u[r * c.d + x]), rnd<BF>(w[x]), sum);
+    for (int x = 0; x < c.d; ++x) sum = fmaf(rnd<BF>(c.eps[r * c.d + x]), rnd<BF>(w[c.d + x]), sum);
+    c.rowterm[e] = rnd<BF>(sum);
+}
+
+// What the two passes share: the stages, the requests, a lane's place.
+template <int D4, bool BF>
+struct Tiles {
+    static constexpr int d = 4 * D4;
+    float* h_s;      // [2][kCells * d]
+    float* tail_s;   // [2][kCells * kMaxTail], a cell's [age / age_max, scalars] at pitch T1
+    uint64_t* bar;
+    const Ctx& c;
+    int T1;
+    float held[(kCells * kMaxTail) / kThreads];   // the next tile's tail values on their way to shared memory
+
+    __device__ Tiles(unsigned char* dyn, uint64_t* bars, const Ctx& ctx) : bar(bars), c(ctx) {
+        h_s = reinterpret_cast<float*>(dyn);
+        tail_s = h_s + 2 * kCells * d;
+        T1 = c.S + 1;
+    }
+    __device__ int cells_of(int64_t item) const { return min(kCells, c.N - static_cast<int>(item % c.tiles) * kCells); }
+    __device__ int64_t first_cell(int64_t item) const { return (item / c.tiles) * c.N + (item % c.tiles) * kCells; }
+    // thread 0: the tile of h into stage s
+    __device__ void request(int64_t item, int s) const {
+        const uint32_t bytes = static_cast<uint32_t>(cells_of(item)) * d * sizeof(float);
+        mbar_expect_tx(&bar[s], bytes);
+        bulk_g2s(h_s + s * kCells * d, c.h + first_cell(item) * d, bytes, &bar[s]);
+    }
+    __device__ void tail_load(int64_t item) {
+        const int n = cells_of(item) * T1;
+        const int64_t cell0 = first_cell(item);
+#pragma unroll
+        for (int q = 0; q < (kCells * kMaxTail) / kThreads; ++q) {
+            const int e = threadIdx.x + q * kThreads;
+            held[q] = 0.0f;
+            if (e < n) {
+                const int cell = e / T1, s = e - cell * T1;
+                const float v = s == 0 ? static_cast<float>(c.age[cell0 + cell]) / c.age_max : c.scalars[(cell0 + cell) * c.S + s - 1];
+                held[q] = rnd<BF>(v);
+            }
+        }
+    }
+    __device__ void tail_store(int s) const {
+#pragma unroll
+        for (int q = 0; q < (kCells * kMaxTail) / kThreads; ++q) {
+            const int e = threadIdx.x + q * kThreads;
+            if (e < kCells * T1) tail_s[s * kCells * kMaxTail + e] = held[q];
+        }
+    }
+    // the bf16 pass reads h as bfloat16 values: round the landed tile in place, once for its eight readers
+    __device__ void round_tile(int s, int cells) const {
+        if (!BF) return;
+        float4* t = reinterpret_cast<float4*>(h_s + s * kCells * d);
+        for (int e = threadIdx.x; e < cells * D4; e += kThreads) {
+            float4 v = t[e];
+            v.x = bf16r(v.x), v.y = bf16r(v.y), v.z = bf16r(v.z), v.w = bf16r(v.w);
+            t[e] = v;
+        }
+    }
+};
+
+// a lane's float4 number i of its cell's row: cell c of the warp's four starts 2 c further on (d = 16: c / 2)
+template <int D4>
+__device__ __forceinline__ int quarter(int i, int cc) {
+    return (i + (D4 >= 8 ? 2 * cc : cc >> 1)) & (D4 - 1);
+}
+
+template <int D4, bool BF>
+__global__ void __launch_bounds__(kThreads) k_scorer_fwd(Ctx c) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    __shared__ __align__(8) uint64_t bar[2];
+    constexpr int d = 4 * D4;
+    Tiles<D4, BF> tl(dyn, bar, c);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, cc = lane >> 3, j = lane & 7;
+    const int T1 = tl.T1;
+    if (tid == 0) {
+        mbar_init(&bar[0], 1);
+        mbar_init(&bar[1], 1);
+    }
+    float4 wh[D4];
+    float wt[kMaxTail], bj = 0.0f;
+    {
+        const float* w = c.weight + static_cast<int64_t>(min(j, c.M - 1)) * c.F;
+#pragma unroll
+        for (int i = 0; i < D4; ++i) {
+            const float* p = w + 2 * d + 4 * quarter<D4>(i, cc);
+            wh[i] = make_float4(rnd<BF>(p[0]), rnd<BF>(p[1]), rnd<BF>(p[2]), rnd<BF>(p[3]));
+        }
+#pragma unroll
+        for (int s = 0; s < kMaxTail; ++s) wt[s] = s < T1 ? rnd<BF>(w[3 * d + s]) : 0.0f;
+        bj = rnd<BF>(c.bias[min(j, c.M - 1)]);
+    }
+    int64_t item = blockIdx.x;
+    if (item < c.items) {
+        tl.tail_load(item);
+        tl.tail_store(0);
+    }
+    __syncthreads();   // the barriers are initialised
+    if (item < c.items && tid == 0) tl.request(item, 0);
+    for (int n_it = 0; item < c.items; item += gridDim.x, ++n_it) {
+        const int s = n_it & 1;
+        const int64_t next = item + gridDim.x;
+        const int cells = tl.cells_of(item);
+        mbar_wait(&bar[s], (n_it >> 1) & 1, c.status);
+        tl.round_tile(s, cells);
+        __syncthreads();   // tile s and its tail are complete; everyone is done with stage s ^ 1
+        if (next < c.items) {
+            if (tid == 0) {
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // the stage was read (and rounded) by ordinary accesses
+                tl.request(next, s ^ 1);
+            }
+            tl.tail_load(next);
+        }
+        const float* ht = tl.h_s + s * kCells * d;
+        const float* tt = tl.tail_s + s * kCells * kMaxTail;
+        const int64_t r = item / c.tiles;
+        const float row = j < c.M ? c.rowterm[r * c.M + j] : 0.0f;
+        const int64_t cell0 = tl.first_cell(item);
+#pragma unroll
+        for (int round = 0; round < 4; ++round) {
+            const int cell = warp * 16 + round * 4 + cc;
+            if (cell < cells) {   // (a whole group of eight lanes at once)
+                const float4* hp = reinterpret_cast<const float4*>(ht + cell * d);
+                float a = 0.0f, t = 0.0f;
+#pragma unroll
+                for (int i = 0; i < D4; ++i) {
+                    const float4 x = hp[quarter<D4>(i, cc)];
+                    a = fmaf(x.x, wh[i].x, a);
+                    a = fmaf(x.y, wh[i].y, a);
+                    a = fmaf(x.z, wh[i].z, a);
+                    a = fmaf(x.w, wh[i].w, a);
+                }
+#pragma unroll
+                for (int sI = 0; sI < kMaxTail; ++sI)
+                    if (sI < T1) t = fmaf(tt[cell * T1 + sI], wt[sI], t);
+                if (j < c.M) c.logits[(cell0 + cell) * c.M + j] = (rnd<BF>(a) + rnd<BF>(t + bj)) + row;
+            }
+        }
+        if (next < c.items) tl.tail_store(s ^ 1);
+    }
+}
+
+template <int D4, bool BF>
+__global__ void __launch_bounds__(kThreads) k_scorer_bwd(Ctx c) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    __shared__ __align__(8) uint64_t bar[2];
+    __shared__ float warp_sum_s[2][8][8];   // a tile's cotangent summed over a warp's cells, per unit
+    constexpr int d = 4 * D4;
+    Tiles<D4, BF> tl(dyn, bar, c);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, cc = lane >> 3, j = lane & 7;
+    const int T1 = tl.T1;
+    if (tid == 0) {
+        mbar_init(&bar[0], 1);
+        mbar_init(&bar[1], 1);
+    }
+    float4 ah[D4];
+    float at[kMaxTail], ab = 0.0f;
+#pragma unroll
+    for (int i = 0; i < D4; ++i) ah[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+    for (int s = 0; s < kMaxTail; ++s) at[s] = 0.0f;
+    int64_t item = blockIdx.x, last_item = -1;
+    if (item < c.items) {
+        tl.tail_load(item);
+        tl.tail_store(0);
+    }
+    __syncthreads();
+    if (item < c.items && tid == 0) tl.request(item, 0);
+    int n_it = 0;
+    for (; item < c.items; item += gridDim.x, ++n_it) {
+        const int s = n_it & 1;
+        const int64_t next = item + gridDim.x;
+        const int cells = tl.cells_of(item);
+        const int64_t cell0 = tl.first_cell(item);
+        float g[4];
+#pragma unroll
+        for (int round = 0; round < 4; ++round) {   // the tile's cotangent: 128 contiguous bytes a warp load
+            const int cell = warp * 16 + round * 4 + cc;
+            g[round] = (cell < cells && j < c.M) ? c.dlogits[(cell0 + cell) * c.M + j] : 0.0f;
+        }
+        mbar_wait(&bar[s], (n_it >> 1) & 1, c.status);
+        tl.round_tile(s, cells);
+        __syncthreads();   // tile s and its tail are complete; everyone is done with stage s ^ 1 and the last tile's sums are written
+        if (last_item >= 0 && tid < 8 && tid < c.M) {   // the last tile's cotangent summed over its cells, warps in order
+            float total = 0.0f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) total += warp_sum_s[s ^ 1][w][tid];
+            c.rowsum[last_item * c.M + tid] = total;
+        }
+        if (next < c.items) {
+            if (tid == 0) {
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                tl.request(next, s ^ 1);
+            }
+            tl.tail_load(next);
+        }
+        const float* ht = tl.h_s + s * kCells * d;
+        const float* tt = tl.tail_s + s * kCells * kMaxTail;
+        float raw = 0.0f;
+#pragma unroll
+        for (int round = 0; round < 4; ++round) {
+            const int cell = warp * 16 + round * 4 + cc;
+            raw += g[round];
+            if (cell < cells) {
+                const float gr = rnd<BF>(g[round]);
+                const float4* hp = reinterpret_cast<const float4*>(ht + cell * d);
+#pragma unroll
+                for (int i = 0; i < D4; ++i) {
+                    const float4 x = hp[quarter<D4>(i, cc)];
+                    ah[i].x = fmaf(gr, x.x, ah[i].x);
+                    ah[i].y = fmaf(gr, x.y, ah[i].y);
+                    ah[i].z = fmaf(gr, x.z, ah[i].z);
+                    ah[i].w = fmaf(gr, x.w, ah[i].w);
+                }
+#pragma unroll
+                for (int sI = 0; sI < kMaxTail; ++sI)
+                    if (sI < T1) at[sI] = fmaf(gr, tt[cell * T1 + sI], at[sI]);
+                ab += gr;
+            }
+        }
+        raw += __shfl_xor_sync(0xffffffffu, raw, 8);
+        raw += __shfl_xor_sync(0xffffffffu, raw, 16);
+        if (cc == 0) warp_sum_s[s][warp][j] = raw;
+        last_item = item;
+        if (next < c.items) tl.tail_store(s ^ 1);
+    }
+    __syncthreads();
+    if (last_item >= 0 && tid < 8 && tid < c.M) {
+        float total = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) total += warp_sum_s[(n_it - 1) & 1][w][tid];
+        c.rowsum[last_item * c.M + tid] = total;
+    }
+    // a block's sums: the four cells' lanes of a warp in turn into the warp's slice of shared memory (the stages
+    // are free now), then the warps in order
+    const int width = d + T1 + 1;
+    float* red = reinterpret_cast<float*>(dyn);   // [8 warps][8 units][width]
+    float* mine = red + (warp * 8 + j) * width;
+    for (int turn = 0; turn < 4; ++turn) {
+        if (cc == turn) {
+#pragma unroll
+            for (int i = 0; i < D4; ++i) {
+                float* at4 = mine + 4 * quarter<D4>(i, cc);
+                if (turn == 0) at4[0] = ah[i].x, at4[1] = ah[i].y, at4[2] = ah[i].z, at4[3] = ah[i].w;
+                else at4[0] += ah[i].x, at4[1] += ah[i].y, at4[2] += ah[i].z, at4[3] += ah[i].w;
+            }
+#pragma unroll
+            for (int sI = 0; sI < kMaxTail; ++sI)
+                if (sI < T1) mine[d + sI] = turn == 0 ? at[sI] : mine[d + sI] + at[sI];
+            mine[d + T1] = turn == 0 ? ab : mine[d + T1] + ab;
+        }
+        __syncwarp();
+    }
+    __syncthreads();
+    for (int e = tid; e < c.M * width; e += kThreads) {
+        const int unit = e / width, col = e - unit * width;
+        float total = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) total += red[(w * 8 + unit) * width + col];
+        c.partial[static_cast<int64_t>(blockIdx.x) * c.M * width + e] = total;
+    }
+}
+
+// the row block's gradient: chunk of rows x (unit, input) -> partial_row[chunk][unit][input]
+template <bool BF>
+__global__ void __launch_bounds__(256) k_scorer_rowgrad(Ctx c) {
+    const int64_t per = (c.rows + kRowChunks - 1) / kRowChunks;
+    const int64_t r0 = blockIdx.x * per, r1 = min(c.rows, r0 + per);
+    const int two_d = 2 * c.d;
+    for (int e = threadIdx.x; e < c.M * two_d; e += 256) {
+        const int unit = e / two_d, x = e - unit * two_d;
+        float sum = 0.0f;
+        for (int64_t r = r0; r < r1; ++r) {
+            float g = 0.0f;
+            for (int t = 0; t < c.tiles; ++t) g += c.rowsum[(r * c.tiles + t) * c.M + unit];
+            const float in = x < c.d ? c.u[r * c.d + x] : c.eps[r * c.d + x - c.d];
+            sum = fmaf(rnd<BF>(g), rnd<BF>(in), sum);
+        }
+        c.partial_row[static_cast<int64_t>(blockIdx.x) * c.M * two_d + e] = sum;
+    }
+}
+
+// d_weight and d_bias from the blocks' and the row chunks' partial sums, in order
+template <bool BF>
+__global__ void __launch_bounds__(256) k_scorer_wgrad(Ctx c, int blocks, float* d_weight, float* d_bias) {
+    const int width = c.d + c.S + 2, two_d = 2 * c.d;
+    const int e = blockIdx.x * 256 + threadIdx.x;
+    if (e >= c.M * (c.F + 1)) return;
+    const int unit = e / (c.F + 1), col = e - unit * (c.F + 1);   // col F: the bias
+    float total = 0.0f;
+    if (col < two_d) {
+        for (int k = 0; k < kRowChunks; ++k) total += c.partial_row[(static_cast<int64_t>(k) * c.M + unit) * two_d + col];
+    } else {
+        const int at = col - two_d;   // the state block, the tail block, the bias: the blocks' layout
+        for (int b = 0; b < blocks; ++b) total += c.partial[(static_cast<int64_t>(b) * c.M + unit) * width + at];
+    }
+    if (col < c.F) d_weight[unit * c.F + col] = rnd<BF>(total);
+    else d_bias[unit] = rnd<BF>(total);
+}
+
+size_t up256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+struct Plan {
+    int tiles, blocks;
+    size_t shared;
+    size_t off_rowterm, off_partial, off_rowsum, off_partial_row, bytes;
+};
+
+Plan make_plan(const HsnwScorer* s, int64_t rows, bool backward) {
+    Plan p{};
+    p.tiles = (s->n_cells + kCells - 1) / kCells;
+    p.shared = sizeof(float) * (2 * kCells * static_cast<size_t>(s->d) + 2 * kCells * kMaxTail);
+    const int sms = std::max(1, hsnw_sm_count_current());
+    const int per_sm = static_cast<int>(std::max<size_t>(1, std::min<size_t>(4, (200 * 1024) / (p.shared + 1024))));
+    p.blocks = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(rows * p.tiles, static_cast<int64_t>(sms) * per_sm)));
+    size_t at = 256;
+    p.off_rowterm = at;
+    at += up256(sizeof(float) * static_cast<size_t>(rows) * s->n_units);
+    if (backward) {
+        p.off_partial = at;
+        at += up256(sizeof(float) * static_cast<size_t>(p.blocks) * s->n_units * (s->d + s->n_scalars + 2));
+        p.off_rowsum = at;
+        at += up256(sizeof(float) * static_cast<size_t>(rows) * p.tiles * s->n_units);
+        p.off_partial_row = at;
+        at += up256(sizeof(float) * kRowChunks * s->n_units * 2 * s->d);
+    }
+    p.bytes = at;
+    return p;
+}
+
+int check(const HsnwScorer* s, int64_t rows, const char* what) {
+    if (!s || rows < 0) return hsnw_fail(HSNW_E_ARG, what);
+    if (s->d < 4 || s->n_cells < 1 || s->n_units < 1 || s->n_scalars < 0 || !s->weight || !s->bias || !(s->age_max > 0.0f))
+        return hsnw_fail(HSNW_E_ARG, "scorer: sizes, age_max or weights missing");
+    if ((s->d != 16 && s->d != 32 && s->d != 64 && s->d != 128) || s->n_units > 8 || s->n_scalars + 1 > kMaxTail)
+        return hsnw_fail(HSNW_E_UNSUPPORTED, "scorer: d in {16, 32, 64, 128}, at most 8 units, at most 15 scalars");
+    return HSNW_OK;
+}
+
+Ctx make_ctx(const HsnwScorer* s, const Plan& p, const float* u, const float* eps, const float* h, const int64_t* age, const float* scalars,
+             int64_t rows, void* scratch) {
+    unsigned char* base = static_cast<unsigned char*>(scratch);
+    Ctx c{};
+    c.d = s->d, c.N = s->n_cells, c.M = s->n_units, c.S = s->n_scalars, c.F = 3 * s->d + 1 + s->n_scalars, c.tiles = p.tiles;
+    c.age_max = s->age_max;
+    c.rows = rows, c.items = rows * p.tiles;
+    c.weight = s->weight, c.bias = s->bias, c.u = u, c.eps = eps, c.h = h, c.scalars = scalars, c.age = age;
+    c.rowterm = reinterpret_cast<float*>(base + p.off_rowterm);
+    c.partial = reinterpret_cast<float*>(base + p.off_partial);
+    c.rowsum = reinterpret_cast<float*>(base + p.off_rowsum);
+    c.partial_row = reinterpret_cast<float*>(base + p.off_partial_row);
+    c.status = reinterpret_cast<int*>(base);
+    return c;
+}
+
+template <bool BF>
+void launch_fwd(const Ctx& c, const Plan& p, cudaStream_t stream) {
+    switch (c.d) {
+        case 16: k_scorer_fwd<4, BF><<<p.blocks, kThreads, p.shared, stream>>>(c); break;
+        case 32: k_scorer_fwd<8, BF><<<p.blocks, kThreads, p.shared, stream>>>(c); break;
+        case 64: k_scorer_fwd<16, BF><<<p.blocks, kThreads, p.shared, stream>>>(c); break;
+        default: k_scorer_fwd<32, BF><<<p.blocks, kThreads, p.shared, stream>>>(c); break;
+    }
+}
+template <bool BF>
+void launch_bwd(const Ctx& c, const Plan& p, cudaStream_t stream) {
+    switch (c.d) {
+        case 16: k_scorer_bwd<4, BF><<<p.blocks, kThreads, p.shared, stream>>>(c); break;
+        case 32: k_scorer_bwd<8, BF><<<p.blocks, kThreads, p.shared, stream>>>(c); break;
+        case 64: k_scorer_bwd<16, BF><<<p.blocks, kThreads, p.shared, stream>>>(c); break;
+        default: k_scorer_bwd<32, BF><<<p.blocks, kThreads, p.shared, stream>>>(c); break;
+    }
+}
+
+int check_call(const Plan& p, const void* u, const void* eps, const void* h, const void* age, const void* scalars, int n_scalars,
+               void* scratch, int64_t bytes) {
+    if (!u || !eps || !h || !age || (n_scalars > 0 && !scalars)) return hsnw_fail(HSNW_E_ARG, "scorer: null tensor");
+    if (reinterpret_cast<uintptr_t>(h) & 15) return hsnw_fail(HSNW_E_ARG, "scorer: h not 16-byte aligned");
+    if (!scratch || bytes < static_cast<int64_t>(p.bytes) || (reinterpret_cast<uintptr_t>(scratch) & 255))
+        return hsnw_fail(HSNW_E_ARG, "scorer: scratch too small or not 256-byte aligned (hsnw_scorer_scratch_bytes)");
+    return HSNW_OK;
+}
+
+}  // namespace
+
+extern "C" int64_t hsnw_scorer_scratch_bytes(const HsnwScorer* scorer, int64_t rows, int backward) {
+    if (!scorer || rows < 0 || scorer->n_units < 1 || scorer->d < 4 || scorer->n_cells < 1) return 0;
+    return static_cast<int64_t>(make_plan(scorer, rows, backward != 0).bytes);
+}
+
+extern "C" int hsnw_scorer_logits(const HsnwScorer* scorer, const float* u, const float* eps, const float* h, const int64_t* age,
+                                  const float* scalars, int64_t rows, float* logits, void* scratch, int64_t scratch_bytes, void* stream_) {
+    if (int rc = hsnw_require_prepared()) return rc;
+    if (int rc = check(scorer, rows, "scorer_logits: null or negative")) return rc;
+    const Plan p = make_plan(scorer, rows, false);
+    if (rows == 0) return HSNW_OK;
+    if (int rc = check_call(p, u, eps, h, age, scalars, scorer->n_scalars, scratch, scratch_bytes)) return rc;
+    if (!logits) return hsnw_fail(HSNW_E_ARG, "scorer_logits: null output");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    Ctx c = make_ctx(scorer, p, u, eps, h, age, scalars, rows, scratch);
+    c.logits = logits;
+    if (cudaMemsetAsync(c.status, 0, sizeof(int), stream) != cudaSuccess) return hsnw_check_launch("scorer_logits");
+    hsnw_profile_mark(HSNW_K_SCORER_FWD, stream);
+    const unsigned row_blocks = static_cast<unsigned>((rows * c.M + 255) / 256);
+    if (scorer->prod_bf16) {
+        k_scorer_row<true><<<row_blocks, 256, 0, stream>>>(c);
+        launch_fwd<true>(c, p, stream);
+    } else {
+        k_scorer_row<false><<<row_blocks, 256, 0, stream>>>(c);
+        launch_fwd<false>(c, p, stream);
+    }
+    return hsnw_check_launch("scorer_logits");
+}
+
+extern "C" int hsnw_scorer_logits_backward(const HsnwScorer* scorer, const float* u, const float* eps, const float* h, const int64_t* age,
+                                           const float* scalars, int64_t rows, const float* d_logits, float* d_weight, float* d_bias,
+                                           void* scratch, int64_t scratch_bytes, void* stream_) {
+    if (int rc = hsnw_require_prepared()) return rc;
+    if (int rc = check(scorer, rows, "scorer_logits_backward: null or negative")) return rc;
+    if (!d_weight || !d_bias) return hsnw_fail(HSNW_E_ARG, "scorer_logits_backward: null gradient");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const int F = 3 * scorer->d + 1 + scorer->n_scalars;
+    if (rows == 0) {
+        if (cudaMemsetAsync(d_weight, 0, sizeof(float) * scorer->n_units * F, stream) != cudaSuccess
+            || cudaMemsetAsync(d_bias, 0, sizeof(float) * scorer->n_units, stream) != cudaSuccess)
+            return hsnw_check_launch("scorer_logits_backward");
+        return HSNW_OK;
+    }
+    const Plan p = make_plan(scorer, rows, true);
+    if (int rc = check_call(p, u, eps, h, age, scalars, scorer->n_scalars, scratch, scratch_bytes)) return rc;
+    if (!d_logits) return hsnw_fail(HSNW_E_ARG, "scorer_logits_backward: null cotangent");
+    Ctx c = make_ctx(scorer, p, u, eps, h, age, scalars, rows, scratch);
+    c.dlogits = d_logits;
+    if (cudaMemsetAsync(c.status, 0, sizeof(int), stream) != cudaSuccess) return hsnw_check_launch("scorer_logits_backward");
+    hsnw_profile_mark(HSNW_K_SCORER_BWD, stream);
+    const unsigned out_blocks = static_cast<unsigned>((c.M * (F + 1) + 255) / 256);
+    if (scorer->prod_bf16) {
+        launch_bwd<true>(c, p, stream);
+        k_scorer_rowgrad<true><<<kRowChunks, 256, 0, stream>>>(c);
+        k_scorer_wgrad<true><<<out_blocks, 256, 0, stream>>>(c, p.blocks, d_weight, d_bias);
+    } else {
+        launch_bwd<false>(c, p, stream);
+        k_scorer_rowgrad<false><<<kRowChunks, 256, 0, stream>>>(c);
+        k_scorer_wgrad<false><<<out_blocks, 256, 0, stream>>>(c, p.blocks, d_weight, d_bias);
+    }
+    return hsnw_check_launch("scorer_logits_backward");
+}
+
+void hsnw_scorer_set_attributes() {
+    bool ok = true;
+#define HSNW_SCORER_OPT(D4) \
+    ok = ok && hsnw_opt_in(reinterpret_cast<const void*>(k_scorer_fwd<D4, true>), "scorer_fwd") \
+         && hsnw_opt_in(reinterpret_cast<const void*>(k_scorer_fwd<D4, false>), "scorer_fwd") \
+         && hsnw_opt_in(reinterpret_cast<const void*>(k_scorer_bwd<D4, true>), "scorer_bwd") \
+         && hsnw_opt_in(reinterpret_cast<const void*>(k_scorer_bwd<D4, false>), "scorer_bwd")
+    HSNW_SCORER_OPT(4);
+    HSNW_SCORER_OPT(8);
+    HSNW_SCORER_OPT(16);
+    HSNW_SCORER_OPT(32);
+#undef HSNW_SCORER_OPT
+    if (!ok) hsnw_attribute_failed();
+}

@@ -725,6 +725,43 @@ def make_units(root: Path) -> None:
             print("units", case, name, tuple(out.shape), out.dtype, record["hidden"].dtype)
 
 
+def make_scorer(root: Path) -> None:
+    """The replay's scorer logits ``_scorer_logits`` (``python/hsn/train/split.py:305-342``) with autograd's gradients
+    of the scorer's weight and bias for a seeded cotangent: float64, float32 and under
+    ``torch.autocast("cpu", dtype=torch.bfloat16)``; features in the reference's layout (``u, eps, h, age, 7 scalars,
+    a_cur, a_prev``), no address gate, no excluded features."""
+    import torch
+    from hsn.train.split import _scorer_logits
+
+    R, N, d, M = 6, 20, 16, 5
+    cfg = _cfg(root, B=2, T=3, N=N, d=d, K=3, H=40, M=M, D=2, fd="[summary,eps,state,router]")
+    for name, dtype, auto in (("f64", torch.float64, False), ("f32", torch.float32, False), ("bf16", torch.float32, True)):
+        model = _model(cfg, dtype, 0.3)
+        scorer = model.scorer
+        assert isinstance(scorer.net, torch.nn.Linear) and not scorer.exclude and scorer.address_gate is None
+        S = scorer.in_features - 3 * d - 1
+        gen = torch.Generator().manual_seed(41)
+        u = (torch.randn(R, d, generator=gen) * 0.7).to(dtype)
+        eps = (torch.randn(R, d, generator=gen) * 0.4).to(dtype)
+        h = (torch.randn(R, N, d, generator=gen) * 0.5).to(dtype)
+        age = torch.randint(0, 3 * int(scorer.age_max), (R, N), generator=gen)
+        scalars = torch.randn(R, N, S, generator=gen).to(dtype)
+        cot = torch.randn(R, N, M, generator=gen).to(dtype)
+        scorer.zero_grad()
+        if auto:
+            with torch.autocast("cpu", dtype=torch.bfloat16):
+                logits = _scorer_logits(scorer, u, eps, h, age, scalars)
+        else:
+            logits = _scorer_logits(scorer, u, eps, h, age, scalars)
+        (logits * cot).sum().backward()
+        np.savez_compressed(
+            HERE / f"scorer_{name}.npz", u=_np(u), eps=_np(eps), h=_np(h), age=age.numpy(), scalars=_np(scalars), cot=_np(cot),
+            weight=_np(scorer.net.weight), bias=_np(scorer.net.bias), age_max=np.array(float(scorer.age_max)),
+            logits=_np(logits), d_weight=_np(scorer.net.weight.grad), d_bias=_np(scorer.net.bias.grad),
+        )  # fmt: skip
+        print("scorer", name, tuple(logits.shape), logits.dtype, "S", S)
+
+
 def make_snapshot(root: Path) -> None:
     """``CellGraphState.snapshot`` (``python/hsn/model/state.py:363``) and ``pack_cell_state``
     (``python/hsn/train/checkpoint.py:260``): seeded states in float32 and bfloat16, their metas and the
@@ -768,7 +805,7 @@ def main() -> None:
     steps = {
         "select": make_select, "update": make_update, "recurrence": make_recurrence,
         "windows": make_windows, "bf16": make_windows_bf16, "prologue": make_prologue, "chain": make_chain,
-        "sweep": make_sweep, "snapshot": make_snapshot, "decode": make_decode, "units": make_units,
+        "sweep": make_sweep, "snapshot": make_snapshot, "decode": make_decode, "units": make_units, "scorer": make_scorer,
     }  # fmt: skip
     for key, fn in steps.items():
         if not args.only or key in args.only.split(","):

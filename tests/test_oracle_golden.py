@@ -388,3 +388,23 @@ def test_grouped_units_equal_the_reference(case: str, name: str, tol: float) -> 
         assert not np.any(z["unit_idx"] == 3) and not np.any(grads[1][3]) and not np.any(grads[4][3])
     with pytest.raises(IndexError):
         U.forward_grouped(z["v"], np.full_like(z["unit_idx"], z["W1"].shape[0]), *bank)
+
+
+@pytest.mark.parametrize("name,tol", [("f64", 1e-12), ("f32", 1e-5), ("bf16", 0.0)])
+def test_scorer_logits_equal_the_reference(name: str, tol: float) -> None:
+    """The replay's scorer logits and the gradients of the scorer's weight and bias against ``_scorer_logits`` with
+    autograd on the CPU: float64, float32, and under bf16 autocast, where the restatement reproduces the reference's
+    values to the bit."""
+    from oracle import scorer_oracle as S
+
+    z = load_golden(f"scorer_{name}")
+    bf = name == "bf16"
+    feats = tuple(z[k] for k in ("u", "eps", "h", "age", "scalars"))
+    out = S.scorer_logits(z["weight"], z["bias"], *feats, float(z["age_max"]), bf16=bf)
+    d_w, d_b = S.scorer_logits_backward(z["weight"], *feats, float(z["age_max"]), z["cot"], bf16=bf)
+    for got, key in ((out, "logits"), (d_w, "d_weight"), (d_b, "d_bias")):
+        assert got.shape == z[key].shape
+        if tol == 0.0:
+            assert np.array_equal(got, z[key]), key
+        else:
+            np.testing.assert_allclose(got, z[key], rtol=0, atol=tol * float(np.abs(z[key]).max()), err_msg=key)
