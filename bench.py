@@ -53,7 +53,10 @@ CONFIGS["adamw"] = dict(tensors=40, elements=4_194_304 + 1031, trainer=True)
 CONFIGS["decode"] = dict(rows=32 * 256, d=64, H=512, V=256, decoder=True)
 # the replay's grouped unit pass (not the headline): every pair of the c2 window at once, forward and backward
 CONFIGS["units"] = dict(pairs=32 * 256 * 8, M=8, d=64, H=512, units=True)
+# the replay's scorer logits (not the headline): every cell of every position of the c2 window, forward and backward
+CONFIGS["scorer"] = dict(R=32 * 256, N=256, d=64, M=8, S=9, scorer=True)
 WORKLOADS = {
+    "scorer": "the replay's scorer logits over a window's 8192 positions x 256 cells (d 64, 8 units, 9 scalars), bf16 products, forward + weight gradients",
     "units": "the replay's grouped unit pass over a window's 65,536 pairs: 8 units 256 -> 512 -> 64, bf16 products, forward + backward",
     "decode": "the decoder D([q; u]) over a window's 8192 rows: 128 -> 512 -> 256, bf16 products",
     "adamw": "the trainer's AdamW step over 40 fp32 tensors of 4,195,335 elements (671 MB of parameters), one launch",
@@ -897,6 +900,93 @@ def run_units(args, c: dict, name: str) -> None:
         "cpu_baseline": cpu, "clocks": clocks_summary(clock_lines, 0)}))  # fmt: skip
 
 
+def run_scorer(args, c: dict, name: str) -> None:
+    """`--config scorer`: `hsnw_scorer_logits` + `hsnw_scorer_logits_backward` over the benchmark window's recorded
+    state; a step = both (each one read of the state, 0.5 GB). Beside it the CPU restatement on a sample of the
+    positions, and the reference's own formulation in PyTorch on the same device."""
+    import torch
+
+    from hsn_b200.kernels.scorer import scorer_logits_backward, scorer_logits_forward
+    from hsn_b200.window import launch_profile
+
+    world, rank, local, dev = dist_setup()
+    R, N, d, M, S = c["R"], c["N"], c["d"], c["M"], c["S"]
+    gen = torch.Generator(device=dev).manual_seed(0)
+    f = lambda *shape, scale=1.0: torch.randn(*shape, generator=gen, device=dev) * scale  # noqa: E731
+    weight, bias = f(M, 3 * d + 1 + S, scale=0.2), f(M, scale=0.3)
+    feats = [f(R, d, scale=0.7), f(R, d, scale=0.4), f(R, N, d, scale=0.5), torch.randint(0, 300, (R, N), generator=gen, device=dev),
+             f(R, N, S)]  # fmt: skip
+    cot = f(R, N, M)
+    kept: dict = {}
+
+    def step(i):   # (the state alone is four times L2: nothing of one pass survives to the next)
+        kept["out"] = scorer_logits_forward(weight, bias, *feats, age_max=100.0, check=False)
+        kept["grads"] = scorer_logits_backward(weight, bias, *feats, cot, age_max=100.0, check=False)
+
+    for i in range(max(3, args.warmup)):
+        step(i)
+    clock_lines: list = []
+    stop = threading.Event()
+    threading.Thread(target=sample_clocks, args=(stop, clock_lines), daemon=True).start()
+    with launch_profile() as prof:
+        step(0)
+    ms_total, each = timed_steps(step, args.steps, torch.cuda.synchronize)
+    stop.set()
+    fwd_ms, bwd_ms = prof.ms.get("scorer_fwd", 0.0), prof.ms.get("scorer_bwd", 0.0)
+    # the reference's formulation live: three linear maps under autocast, autograd's backward
+    lw, lb = weight.clone().requires_grad_(True), bias.clone().requires_grad_(True)
+
+    def torch_step(i):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            row = torch.nn.functional.linear(torch.cat(feats[:2], dim=-1), lw[:, : 2 * d])
+            tail = torch.cat([(feats[3].float() / 100.0)[:, :, None], feats[4]], dim=-1)
+            cells = torch.nn.functional.linear(feats[2], lw[:, 2 * d : 3 * d]).float()
+            cells = cells + torch.nn.functional.linear(tail, lw[:, 3 * d :], lb).float()
+            out = cells + row.float()[:, None, :]
+        (out * cot).sum().backward()
+        lw.grad = lb.grad = None
+
+    for i in range(3):
+        torch_step(i)
+    torch_total, _ = timed_steps(torch_step, max(3, args.steps // 4), torch.cuda.synchronize)
+    cpu = None
+    if not args.no_cpu_baseline:
+        from oracle import scorer_oracle as SO
+
+        n = 64   # a sample of the positions
+        host = [t[:n].cpu().numpy() for t in feats]
+        hw, hb, hc = weight.cpu().numpy(), bias.cpu().numpy(), cot[:n].cpu().numpy()
+        t0 = time.perf_counter()
+        reps = 0
+        while time.perf_counter() - t0 < 10.0:
+            SO.scorer_logits(hw, hb, *host, 100.0, bf16=True)
+            SO.scorer_logits_backward(hw, *host, 100.0, hc, bf16=True)
+            reps += 1
+        cpu = {"value": reps * n * N / (time.perf_counter() - t0), "unit": "cells/s", "cores": 1, "kind": "port",
+               "sample": f"{reps} passes of forward + backward over {n} of the window's positions (numpy restatement, bf16 rounding emulated)"}
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    cells = float(R) * N
+    fwd_bytes = cells * (4 * d + 8 + 4 * S + 4 * M)   # state, age, scalars read; logits written
+    bwd_bytes = cells * (4 * d + 8 + 4 * S + 4 * M)   # state, age, scalars and the cotangent read
+    kernel_ms = fwd_ms + bwd_ms
+    achieved = (fwd_bytes + bwd_bytes) / (kernel_ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "scorer logits cells/s (forward + weight gradients)", "value": cells / (kernel_ms * 1e-3), "unit": "cells/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": kernel_ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16 products, f32 tensors", "data": "synthetic",
+        "config": {"workload": WORKLOADS[name], "l2": "the recorded state (537 MB) is larger than L2",
+                   "forward_ms": fwd_ms, "backward_ms": bwd_ms, "step_ms": spread(each),
+                   "torch_three_linear_maps_autocast_autograd_ms": torch_total / max(3, args.steps // 4)},
+        "gpu_launches": 5 * args.steps,
+        "roofline": {"bound": "hbm", "kernel": "k_scorer_fwd + k_scorer_bwd", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": None, "peak_source": "measured" if peaks else "fallback",
+                     "forward": {"achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9, "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak},
+                     "backward": {"achieved": bwd_bytes / (bwd_ms * 1e-3) / 1e9, "frac": bwd_bytes / (bwd_ms * 1e-3) / 1e9 / peak},
+                     "how": "per cell 4 d + 8 + 4 S + 4 M bytes each way (state, age, scalars, and logits written or cotangent read) / the calls' event time in a profiled step"},
+        "cpu_baseline": cpu, "clocks": clocks_summary(clock_lines, 0)}))  # fmt: skip
+
+
 def run_trainer_sharded(args, c: dict, name: str, world: int, rank: int, dev) -> None:
     """`--config adamw --gpus N`: the same parameter vector replicated on N ranks, a step = the gradient exchange
     and the AdamW step as ONE kernel per rank over peer memory (`ShardedAdamW`: reduce-scatter, step, all-gather),
@@ -991,6 +1081,10 @@ def main() -> None:
         if args.steps == 100:
             args.steps = 20
         run_units(args, c, args.config)
+    elif c.get("scorer"):
+        if args.steps == 100:
+            args.steps = 20
+        run_scorer(args, c, args.config)
     elif c.get("trainer"):
         if args.steps == 100:
             args.steps = 20 if args.impl == "ours" else 5

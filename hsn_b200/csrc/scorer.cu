@@ -7,7 +7,7 @@
 //
 // Both passes are one read of the recorded state h (R N d floats: 0.5 GB for a B32 T256 N256 d64 window) and are
 // bound by it. A persistent block takes tiles of 128 cells of one position: the tile of h (contiguous, 32 KB at
-// d = 64) arrives by one bulk copy into one of two stages while the block works on the other; age and scalars
+// d = 64) arrives by one bulk copy into one of three stages, two tiles ahead of the one the block works on; age and scalars
 // (a few KB) go through registers into shared memory. Eight lanes share a cell, one per unit, and a warp works
 // on four cells at a time: the eight lanes read the same 16 bytes of the cell's row (a broadcast), and the four
 // cells read different quarters of their rows in the same instruction (cell c starts 2 c float4s further on and
@@ -31,6 +31,7 @@ constexpr int kCells = 128;    // cells of a tile
 constexpr int kThreads = 256;  // 8 warps x 4 cells x 8 units
 constexpr int kMaxTail = 16;   // 1 + scalars
 constexpr int kRowChunks = 64; // partial sums of the row block's gradient
+constexpr int kStages = 3;     // tiles of h in shared memory: the block works on one, two are on their way
 
 struct Ctx {
     int d, N, M, S, F, tiles;
@@ -70,16 +71,17 @@ __global__ void __launch_bounds__(256) k_scorer_row(Ctx c) {
 template <int D4, bool BF>
 struct Tiles {
     static constexpr int d = 4 * D4;
-    float* h_s;      // [2][kCells * d]
+    float* h_s;      // [kStages][kCells * d]
     float* tail_s;   // [2][kCells * kMaxTail], a cell's [age / age_max, scalars] at pitch T1
     uint64_t* bar;
     const Ctx& c;
     int T1;
-    float held[(kCells * kMaxTail) / kThreads];   // the next tile's tail values on their way to shared memory
+    float held[(kCells * (kMaxTail - 1) + kThreads - 1) / kThreads];   // the next tile's scalars and ages on their way to shared
+    long long held_age;                                               // memory: loaded before the tile's work, stored after it
 
     __device__ Tiles(unsigned char* dyn, uint64_t* bars, const Ctx& ctx) : bar(bars), c(ctx) {
         h_s = reinterpret_cast<float*>(dyn);
-        tail_s = h_s + 2 * kCells * d;
+        tail_s = h_s + kStages * kCells * d;
         T1 = c.S + 1;
     }
     __device__ int cells_of(int64_t item) const { return min(kCells, c.N - static_cast<int>(item % c.tiles) * kCells); }
@@ -90,25 +92,26 @@ struct Tiles {
         mbar_expect_tx(&bar[s], bytes);
         bulk_g2s(h_s + s * kCells * d, c.h + first_cell(item) * d, bytes, &bar[s]);
     }
-    __device__ void tail_load(int64_t item) {
-        const int n = cells_of(item) * T1;
+    __device__ void tail_load(int64_t item) {   // contiguous reads: a tile's scalars are one run, its ages another
+        const int cells = cells_of(item);
         const int64_t cell0 = first_cell(item);
+        held_age = static_cast<int>(threadIdx.x) < cells ? c.age[cell0 + threadIdx.x] : 0;
 #pragma unroll
-        for (int q = 0; q < (kCells * kMaxTail) / kThreads; ++q) {
+        for (int q = 0; q < static_cast<int>(sizeof(held) / sizeof(float)); ++q) {
             const int e = threadIdx.x + q * kThreads;
-            held[q] = 0.0f;
-            if (e < n) {
-                const int cell = e / T1, s = e - cell * T1;
-                const float v = s == 0 ? static_cast<float>(c.age[cell0 + cell]) / c.age_max : c.scalars[(cell0 + cell) * c.S + s - 1];
-                held[q] = rnd<BF>(v);
-            }
+            held[q] = e < cells * c.S ? c.scalars[cell0 * c.S + e] : 0.0f;
         }
     }
     __device__ void tail_store(int s) const {
+        float* t = tail_s + s * kCells * kMaxTail;
+        if (threadIdx.x < kCells) t[threadIdx.x * T1] = rnd<BF>(static_cast<float>(held_age) / c.age_max);
 #pragma unroll
-        for (int q = 0; q < (kCells * kMaxTail) / kThreads; ++q) {
+        for (int q = 0; q < static_cast<int>(sizeof(held) / sizeof(float)); ++q) {
             const int e = threadIdx.x + q * kThreads;
-            if (e < kCells * T1) tail_s[s * kCells * kMaxTail + e] = held[q];
+            if (e < kCells * c.S) {
+                const int cell = e / c.S;
+                t[cell * T1 + 1 + (e - cell * c.S)] = rnd<BF>(held[q]);
+            }
         }
     }
     // the bf16 pass reads h as bfloat16 values: round the landed tile in place, once for its eight readers
@@ -130,17 +133,15 @@ __device__ __forceinline__ int quarter(int i, int cc) {
 }
 
 template <int D4, bool BF>
-__global__ void __launch_bounds__(kThreads) k_scorer_fwd(Ctx c) {
+__global__ void __launch_bounds__(kThreads, D4 <= 16 ? 2 : 1) k_scorer_fwd(Ctx c) {
     extern __shared__ __align__(16) unsigned char dyn[];
-    __shared__ __align__(8) uint64_t bar[2];
+    __shared__ __align__(8) uint64_t bar[kStages];
     constexpr int d = 4 * D4;
     Tiles<D4, BF> tl(dyn, bar, c);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, cc = lane >> 3, j = lane & 7;
     const int T1 = tl.T1;
-    if (tid == 0) {
-        mbar_init(&bar[0], 1);
-        mbar_init(&bar[1], 1);
-    }
+    if (tid == 0)
+        for (int st = 0; st < kStages; ++st) mbar_init(&bar[st], 1);
     float4 wh[D4];
     float wt[kMaxTail], bj = 0.0f;
     {
@@ -160,23 +161,23 @@ __global__ void __launch_bounds__(kThreads) k_scorer_fwd(Ctx c) {
         tl.tail_store(0);
     }
     __syncthreads();   // the barriers are initialised
-    if (item < c.items && tid == 0) tl.request(item, 0);
+    if (tid == 0)
+        for (int k = 0; k < kStages - 1; ++k)
+            if (item + k * static_cast<int64_t>(gridDim.x) < c.items) tl.request(item + k * static_cast<int64_t>(gridDim.x), k);
     for (int n_it = 0; item < c.items; item += gridDim.x, ++n_it) {
-        const int s = n_it & 1;
-        const int64_t next = item + gridDim.x;
+        const int s = n_it % kStages, ts = n_it & 1;
+        const int64_t next = item + gridDim.x, ahead = item + (kStages - 1) * static_cast<int64_t>(gridDim.x);
         const int cells = tl.cells_of(item);
-        mbar_wait(&bar[s], (n_it >> 1) & 1, c.status);
+        mbar_wait(&bar[s], (n_it / kStages) & 1, c.status);
         tl.round_tile(s, cells);
-        __syncthreads();   // tile s and its tail are complete; everyone is done with stage s ^ 1
-        if (next < c.items) {
-            if (tid == 0) {
-                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // the stage was read (and rounded) by ordinary accesses
-                tl.request(next, s ^ 1);
-            }
-            tl.tail_load(next);
+        __syncthreads();   // tile s and its tail are complete; everyone is done with the stage of the tile before
+        if (tid == 0 && ahead < c.items) {
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // that stage was read (and rounded) by ordinary accesses
+            tl.request(ahead, (n_it + kStages - 1) % kStages);
         }
+        if (next < c.items) tl.tail_load(next);
         const float* ht = tl.h_s + s * kCells * d;
-        const float* tt = tl.tail_s + s * kCells * kMaxTail;
+        const float* tt = tl.tail_s + ts * kCells * kMaxTail;
         const int64_t r = item / c.tiles;
         const float row = j < c.M ? c.rowterm[r * c.M + j] : 0.0f;
         const int64_t cell0 = tl.first_cell(item);
@@ -185,38 +186,38 @@ __global__ void __launch_bounds__(kThreads) k_scorer_fwd(Ctx c) {
             const int cell = warp * 16 + round * 4 + cc;
             if (cell < cells) {   // (a whole group of eight lanes at once)
                 const float4* hp = reinterpret_cast<const float4*>(ht + cell * d);
-                float a = 0.0f, t = 0.0f;
+                float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f, t0 = 0.0f, t1 = 0.0f;   // independent sums: no chain of 4 d additions
 #pragma unroll
                 for (int i = 0; i < D4; ++i) {
                     const float4 x = hp[quarter<D4>(i, cc)];
-                    a = fmaf(x.x, wh[i].x, a);
-                    a = fmaf(x.y, wh[i].y, a);
-                    a = fmaf(x.z, wh[i].z, a);
-                    a = fmaf(x.w, wh[i].w, a);
+                    a0 = fmaf(x.x, wh[i].x, a0);
+                    a1 = fmaf(x.y, wh[i].y, a1);
+                    a2 = fmaf(x.z, wh[i].z, a2);
+                    a3 = fmaf(x.w, wh[i].w, a3);
                 }
 #pragma unroll
-                for (int sI = 0; sI < kMaxTail; ++sI)
-                    if (sI < T1) t = fmaf(tt[cell * T1 + sI], wt[sI], t);
-                if (j < c.M) c.logits[(cell0 + cell) * c.M + j] = (rnd<BF>(a) + rnd<BF>(t + bj)) + row;
+                for (int sI = 0; sI < kMaxTail; sI += 2) {
+                    if (sI < T1) t0 = fmaf(tt[cell * T1 + sI], wt[sI], t0);
+                    if (sI + 1 < T1) t1 = fmaf(tt[cell * T1 + sI + 1], wt[sI + 1], t1);
+                }
+                if (j < c.M) c.logits[(cell0 + cell) * c.M + j] = (rnd<BF>((a0 + a1) + (a2 + a3)) + rnd<BF>((t0 + t1) + bj)) + row;
             }
         }
-        if (next < c.items) tl.tail_store(s ^ 1);
+        if (next < c.items) tl.tail_store(ts ^ 1);
     }
 }
 
 template <int D4, bool BF>
-__global__ void __launch_bounds__(kThreads) k_scorer_bwd(Ctx c) {
+__global__ void __launch_bounds__(kThreads, D4 <= 16 ? 2 : 1) k_scorer_bwd(Ctx c) {
     extern __shared__ __align__(16) unsigned char dyn[];
-    __shared__ __align__(8) uint64_t bar[2];
+    __shared__ __align__(8) uint64_t bar[kStages];
     __shared__ float warp_sum_s[2][8][8];   // a tile's cotangent summed over a warp's cells, per unit
     constexpr int d = 4 * D4;
     Tiles<D4, BF> tl(dyn, bar, c);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, cc = lane >> 3, j = lane & 7;
     const int T1 = tl.T1;
-    if (tid == 0) {
-        mbar_init(&bar[0], 1);
-        mbar_init(&bar[1], 1);
-    }
+    if (tid == 0)
+        for (int st = 0; st < kStages; ++st) mbar_init(&bar[st], 1);
     float4 ah[D4];
     float at[kMaxTail], ab = 0.0f;
 #pragma unroll
@@ -229,11 +230,13 @@ __global__ void __launch_bounds__(kThreads) k_scorer_bwd(Ctx c) {
         tl.tail_store(0);
     }
     __syncthreads();
-    if (item < c.items && tid == 0) tl.request(item, 0);
+    if (tid == 0)
+        for (int k = 0; k < kStages - 1; ++k)
+            if (item + k * static_cast<int64_t>(gridDim.x) < c.items) tl.request(item + k * static_cast<int64_t>(gridDim.x), k);
     int n_it = 0;
     for (; item < c.items; item += gridDim.x, ++n_it) {
-        const int s = n_it & 1;
-        const int64_t next = item + gridDim.x;
+        const int s = n_it % kStages, ts = n_it & 1;
+        const int64_t next = item + gridDim.x, ahead = item + (kStages - 1) * static_cast<int64_t>(gridDim.x);
         const int cells = tl.cells_of(item);
         const int64_t cell0 = tl.first_cell(item);
         float g[4];
@@ -242,24 +245,22 @@ __global__ void __launch_bounds__(kThreads) k_scorer_bwd(Ctx c) {
             const int cell = warp * 16 + round * 4 + cc;
             g[round] = (cell < cells && j < c.M) ? c.dlogits[(cell0 + cell) * c.M + j] : 0.0f;
         }
-        mbar_wait(&bar[s], (n_it >> 1) & 1, c.status);
+        mbar_wait(&bar[s], (n_it / kStages) & 1, c.status);
         tl.round_tile(s, cells);
-        __syncthreads();   // tile s and its tail are complete; everyone is done with stage s ^ 1 and the last tile's sums are written
+        __syncthreads();   // tile s and its tail are complete; everyone is done with the tile before and its sums are written
         if (last_item >= 0 && tid < 8 && tid < c.M) {   // the last tile's cotangent summed over its cells, warps in order
             float total = 0.0f;
 #pragma unroll
-            for (int w = 0; w < 8; ++w) total += warp_sum_s[s ^ 1][w][tid];
+            for (int w = 0; w < 8; ++w) total += warp_sum_s[ts ^ 1][w][tid];
             c.rowsum[last_item * c.M + tid] = total;
         }
-        if (next < c.items) {
-            if (tid == 0) {
-                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-                tl.request(next, s ^ 1);
-            }
-            tl.tail_load(next);
+        if (tid == 0 && ahead < c.items) {
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            tl.request(ahead, (n_it + kStages - 1) % kStages);
         }
+        if (next < c.items) tl.tail_load(next);
         const float* ht = tl.h_s + s * kCells * d;
-        const float* tt = tl.tail_s + s * kCells * kMaxTail;
+        const float* tt = tl.tail_s + ts * kCells * kMaxTail;
         float raw = 0.0f;
 #pragma unroll
         for (int round = 0; round < 4; ++round) {
@@ -284,9 +285,9 @@ __global__ void __launch_bounds__(kThreads) k_scorer_bwd(Ctx c) {
         }
         raw += __shfl_xor_sync(0xffffffffu, raw, 8);
         raw += __shfl_xor_sync(0xffffffffu, raw, 16);
-        if (cc == 0) warp_sum_s[s][warp][j] = raw;
+        if (cc == 0) warp_sum_s[ts][warp][j] = raw;
         last_item = item;
-        if (next < c.items) tl.tail_store(s ^ 1);
+        if (next < c.items) tl.tail_store(ts ^ 1);
     }
     __syncthreads();
     if (last_item >= 0 && tid < 8 && tid < c.M) {
@@ -373,9 +374,9 @@ struct Plan {
 Plan make_plan(const HsnwScorer* s, int64_t rows, bool backward) {
     Plan p{};
     p.tiles = (s->n_cells + kCells - 1) / kCells;
-    p.shared = sizeof(float) * (2 * kCells * static_cast<size_t>(s->d) + 2 * kCells * kMaxTail);
+    p.shared = sizeof(float) * (kStages * kCells * static_cast<size_t>(s->d) + 2 * kCells * kMaxTail);
     const int sms = std::max(1, hsnw_sm_count_current());
-    const int per_sm = static_cast<int>(std::max<size_t>(1, std::min<size_t>(4, (200 * 1024) / (p.shared + 1024))));
+    const int per_sm = static_cast<int>(std::max<size_t>(1, std::min<size_t>(2, (226 * 1024) / (p.shared + 1024))));   // (128 registers a thread: two blocks)
     p.blocks = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(rows * p.tiles, static_cast<int64_t>(sms) * per_sm)));
     size_t at = 256;
     p.off_rowterm = at;
