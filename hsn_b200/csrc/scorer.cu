@@ -20,6 +20,7 @@
 #include "common.cuh"
 #include "stage.cuh"
 #include "host_util.h"
+#include "umma.cuh"
 
 #include <algorithm>
 
@@ -68,10 +69,10 @@ __global__ void __launch_bounds__(256) k_scorer_row(Ctx c) {
 }
 
 // What the two passes share: the stages, the requests, a lane's place.
-template <int D4, bool BF>
+template <int D4, bool BF, int NS = kStages>
 struct Tiles {
     static constexpr int d = 4 * D4;
-    float* h_s;      // [kStages][kCells * d]
+    float* h_s;      // [NS][kCells * d]
     float* tail_s;   // [2][kCells * kMaxTail], a cell's [age / age_max, scalars] at pitch T1
     uint64_t* bar;
     const Ctx& c;
@@ -81,7 +82,7 @@ struct Tiles {
 
     __device__ Tiles(unsigned char* dyn, uint64_t* bars, const Ctx& ctx) : bar(bars), c(ctx) {
         h_s = reinterpret_cast<float*>(dyn);
-        tail_s = h_s + kStages * kCells * d;
+        tail_s = h_s + NS * kCells * d;
         T1 = c.S + 1;
     }
     __device__ int cells_of(int64_t item) const { return min(kCells, c.N - static_cast<int>(item % c.tiles) * kCells); }
@@ -205,6 +206,148 @@ __global__ void __launch_bounds__(kThreads, D4 <= 16 ? 2 : 1) k_scorer_fwd(Ctx c
         }
         if (next < c.items) tl.tail_store(ts ^ 1);
     }
+}
+
+// ---- bf16 products on the tensor cores (d = 64) ------------------------------------------------------------
+// The state block's product of a tile is [128 cells, d] x [d, units]: one tcgen05.mma chain with the cells as
+// the rows of A. The landed float32 tile is converted once to bfloat16 in the 128-byte swizzle (rows of 64
+// elements, unit u of row r at u ^ (r % 8); d = 128: two such K blocks), which is at once A K-major for this
+// product and, read the other way, B MN-major for the gradient's product [units, cells] x [cells, d].
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&pair);
+}
+
+// all threads: the float32 tile in stage memory -> the bfloat16 operand tile; rows past `cells` become zeros
+template <int KB>
+__device__ __forceinline__ void convert_tile(const float* h_tile, unsigned char* a_tile, int cells) {
+    constexpr int d = 64 * KB;
+    for (int e = threadIdx.x; e < kCells * 8 * KB; e += kThreads) {
+        const int row = e / (8 * KB), u = e - row * (8 * KB), kb = u >> 3, uu = u & 7;
+        uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+        if (row < cells) {
+            const float4 a = *reinterpret_cast<const float4*>(h_tile + row * d + 8 * u);
+            const float4 b = *reinterpret_cast<const float4*>(h_tile + row * d + 8 * u + 4);
+            packed = make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(b.x, b.y), pack_bf16x2(b.z, b.w));
+        }
+        *reinterpret_cast<uint4*>(a_tile + kb * (kCells * 128) + row * 128 + ((uu ^ (row & 7)) << 4)) = packed;
+    }
+}
+
+constexpr int kTcStages = 2;   // two blocks an SM take turns on the tensor cores; each has one tile on its way
+
+template <int KB>
+__global__ void __launch_bounds__(kThreads, 2) k_scorer_fwd_tc(Ctx c) {
+    extern __shared__ unsigned char dyn_raw[];
+    __shared__ __align__(8) uint64_t bar[kTcStages];
+    __shared__ __align__(8) uint64_t bar_mma;
+    __shared__ uint32_t tmem_slot;
+    __shared__ float wt_s[8][kMaxTail];   // the tail block's weights, bfloat16 values
+    __shared__ float bias_s[8];
+    constexpr int d = 64 * KB, D4 = d / 4;
+    // [kTcStages] float32 tiles | 2 tail tiles | (1024-aligned) the bfloat16 operand tile | the weights' operand tile
+    unsigned char* dyn = dyn_raw + ((1024u - (smem_addr(dyn_raw) & 1023u)) & 1023u);
+    unsigned char* a_tile = dyn;                           // KB x [128 rows x 128 bytes]
+    unsigned char* b_tile = a_tile + KB * kCells * 128;    // KB x [16 rows x 128 bytes]: the units, padded with zero rows
+    Tiles<D4, true, kTcStages> tl(b_tile + KB * 16 * 128, bar, c);
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int T1 = tl.T1;
+    if (tid == 0) {
+        for (int st = 0; st < kTcStages; ++st) mbar_init(&bar[st], 1);
+        mbar_init(&bar_mma, 1);
+    }
+    if (warp == 0) tmem_alloc(&tmem_slot, 32);
+    for (int e = tid; e < 16 * 8 * KB; e += kThreads) {   // W[:, 2d:3d] as the B operand: row = unit, K = d
+        const int row = e / (8 * KB), u = e - row * (8 * KB), kb = u >> 3, uu = u & 7;
+        uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+        if (row < c.M) {
+            const float* w = c.weight + static_cast<int64_t>(row) * c.F + 2 * d + 8 * u;
+            packed = make_uint4(pack_bf16x2(w[0], w[1]), pack_bf16x2(w[2], w[3]), pack_bf16x2(w[4], w[5]), pack_bf16x2(w[6], w[7]));
+        }
+        *reinterpret_cast<uint4*>(b_tile + kb * (16 * 128) + row * 128 + ((uu ^ (row & 7)) << 4)) = packed;
+    }
+    for (int e = tid; e < 8 * kMaxTail; e += kThreads) {
+        const int unit = e / kMaxTail, sI = e - unit * kMaxTail;
+        wt_s[unit][sI] = (unit < c.M && sI < T1) ? bf16r(c.weight[static_cast<int64_t>(unit) * c.F + 3 * d + sI]) : 0.0f;
+    }
+    if (tid < 8) bias_s[tid] = tid < c.M ? bf16r(c.bias[tid]) : 0.0f;
+    int64_t item = blockIdx.x;
+    if (item < c.items) {
+        tl.tail_load(item);
+        tl.tail_store(0);
+    }
+    tcgen05_fence_before();
+    __syncthreads();   // the barriers, tensor memory and the weights' tile are in place
+    tcgen05_fence_after();
+    const uint32_t taddr = tmem_slot;
+    const uint32_t idesc = umma_idesc_bf16(128, 16);
+    if (tid == 0)
+        for (int k = 0; k < kTcStages - 1; ++k)
+            if (item + k * static_cast<int64_t>(gridDim.x) < c.items) tl.request(item + k * static_cast<int64_t>(gridDim.x), k);
+    for (int n_it = 0; item < c.items; item += gridDim.x, ++n_it) {
+        const int s = n_it % kTcStages, ts = n_it & 1;
+        const int64_t next = item + gridDim.x, ahead = item + (kTcStages - 1) * static_cast<int64_t>(gridDim.x);
+        const int cells = tl.cells_of(item);
+        mbar_wait(&bar[s], (n_it / kTcStages) & 1, c.status);
+        convert_tile<KB>(tl.h_s + s * kCells * d, a_tile, cells);   // (the last tile's products were waited for before its epilogue)
+        fence_async_smem();
+        __syncthreads();   // the operand tile and the tail are complete; everyone is done with the stage of the tile before
+        if (tid < 32) {    // the whole first warp, converged after the barrier: one elected lane issues
+            tcgen05_fence_after();
+            __syncwarp();
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb) {   // a K block of 64 is one 128-byte row: a K = 16 step moves both operands by 32 bytes
+                const uint64_t da = umma_desc_sw128(a_tile + kb * (kCells * 128)), db = umma_desc_sw128(b_tile + kb * (16 * 128));
+#pragma unroll
+                for (int st = 0; st < 4; ++st) umma_bf16(taddr, da + 2 * st, db + 2 * st, idesc, kb > 0 || st > 0);
+            }
+            umma_commit(&bar_mma);
+        }
+        if (tid == 0 && ahead < c.items) {
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // stage s was read by ordinary loads before the barrier... and the stage before it
+            tl.request(ahead, (n_it + kTcStages - 1) % kTcStages);
+        }
+        if (next < c.items) tl.tail_load(next);
+        mbar_wait(&bar_mma, n_it & 1, c.status);
+        tcgen05_fence_after();
+        if (warp < 4) {   // a thread a cell: the accumulator's 8 units, the tail block, the row term
+            float acc[8];
+            tmem_ld8(tmem_addr(taddr, warp * 32, 0), acc);
+            const int cell = tid;
+            if (cell < cells) {
+                const float* tt = tl.tail_s + ts * kCells * kMaxTail + cell * T1;
+                float tail[kMaxTail];
+#pragma unroll
+                for (int sI = 0; sI < kMaxTail; ++sI) tail[sI] = sI < T1 ? tt[sI] : 0.0f;
+                const int64_t r = item / c.tiles;
+                float out[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    float t0 = 0.0f, t1 = 0.0f;
+#pragma unroll
+                    for (int sI = 0; sI < kMaxTail; sI += 2) {
+                        t0 = fmaf(tail[sI], wt_s[j][sI], t0);
+                        t1 = fmaf(tail[sI + 1], wt_s[j][sI + 1], t1);
+                    }
+                    out[j] = (bf16r(acc[j]) + bf16r((t0 + t1) + bias_s[j])) + (j < c.M ? c.rowterm[r * c.M + j] : 0.0f);
+                }
+                float* dst = c.logits + (tl.first_cell(item) + cell) * c.M;
+                if (c.M == 8) {
+                    *reinterpret_cast<float4*>(dst) = make_float4(out[0], out[1], out[2], out[3]);
+                    *reinterpret_cast<float4*>(dst + 4) = make_float4(out[4], out[5], out[6], out[7]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if (j < c.M) dst[j] = out[j];
+                }
+            }
+        }
+        tcgen05_fence_before();
+        if (next < c.items) tl.tail_store(ts ^ 1);
+    }
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(taddr, 32);
 }
 
 template <int D4, bool BF>
@@ -366,7 +509,7 @@ __global__ void __launch_bounds__(256) k_scorer_wgrad(Ctx c, int blocks, float* 
 size_t up256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
 struct Plan {
-    int tiles, blocks;
+    int tiles, blocks, blocks_tc;
     size_t shared;
     size_t off_rowterm, off_partial, off_rowsum, off_partial_row, bytes;
 };
@@ -378,6 +521,7 @@ Plan make_plan(const HsnwScorer* s, int64_t rows, bool backward) {
     const int sms = std::max(1, hsnw_sm_count_current());
     const int per_sm = static_cast<int>(std::max<size_t>(1, std::min<size_t>(2, (226 * 1024) / (p.shared + 1024))));   // (128 registers a thread: two blocks)
     p.blocks = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(rows * p.tiles, static_cast<int64_t>(sms) * per_sm)));
+    p.blocks_tc = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(rows * p.tiles, 2 * static_cast<int64_t>(sms))));   // two blocks an SM
     size_t at = 256;
     p.off_rowterm = at;
     at += up256(sizeof(float) * static_cast<size_t>(rows) * s->n_units);
@@ -418,8 +562,17 @@ Ctx make_ctx(const HsnwScorer* s, const Plan& p, const float* u, const float* ep
     return c;
 }
 
+size_t tc_shared(int d) {   // 1024 of slack for the alignment, the two operand tiles, then the stages and the tail tiles
+    const int KB = d / 64;
+    return 1024 + static_cast<size_t>(KB) * (kCells + 16) * 128 + sizeof(float) * (kTcStages * kCells * static_cast<size_t>(d) + 2 * kCells * kMaxTail);
+}
+
 template <bool BF>
 void launch_fwd(const Ctx& c, const Plan& p, cudaStream_t stream) {
+    if (BF && c.d == 64) {
+        k_scorer_fwd_tc<1><<<p.blocks_tc, kThreads, tc_shared(64), stream>>>(c);
+        return;
+    }
     switch (c.d) {
         case 16: k_scorer_fwd<4, BF><<<p.blocks, kThreads, p.shared, stream>>>(c); break;
         case 32: k_scorer_fwd<8, BF><<<p.blocks, kThreads, p.shared, stream>>>(c); break;
@@ -523,5 +676,6 @@ void hsnw_scorer_set_attributes() {
     HSNW_SCORER_OPT(16);
     HSNW_SCORER_OPT(32);
 #undef HSNW_SCORER_OPT
+    ok = ok && hsnw_opt_in(reinterpret_cast<const void*>(k_scorer_fwd_tc<1>), "scorer_fwd_tc");
     if (!ok) hsnw_attribute_failed();
 }
