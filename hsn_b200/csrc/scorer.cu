@@ -235,7 +235,34 @@ __device__ __forceinline__ void convert_tile(const float* h_tile, unsigned char*
     }
 }
 
-constexpr int kTcStages = 2;   // two blocks an SM take turns on the tensor cores; each has one tile on its way
+constexpr int kTcStages = 2;   // two blocks an SM take turns on the tensor cores; each has two tiles on their way (a stage is
+                               // free as soon as its tile is converted)
+
+// a tile's tail operand: thread (cell, half) holds [age / age_max, scalars] numbers 8 half .. 8 half + 7 of its cell
+struct TailRegs {
+    float v[8];
+    long long age;
+    __device__ void load(const Ctx& c, int64_t cell0, int cells) {
+        const int cell = threadIdx.x >> 1, half = threadIdx.x & 1;
+        age = -1;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int k = 8 * half + i;   // 0: the age, k > 0: scalar k - 1
+            v[i] = 0.0f;
+            if (cell < cells) {
+                if (k == 0) age = c.age[cell0 + cell];
+                else if (k - 1 < c.S) v[i] = c.scalars[(cell0 + cell) * c.S + k - 1];
+            }
+        }
+    }
+    // as bfloat16 into the unswizzled K-major operand tile [2 planes][128 rows][16 bytes]
+    __device__ void store(const Ctx& c, unsigned char* tile) const {
+        const int cell = threadIdx.x >> 1, half = threadIdx.x & 1;
+        const float first = age >= 0 ? static_cast<float>(age) / c.age_max : v[0];
+        *reinterpret_cast<uint4*>(tile + half * (kCells * 16) + cell * 16) =
+            make_uint4(pack_bf16x2(first, v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+    }
+};
 
 template <int KB>
 __global__ void __launch_bounds__(kThreads, 2) k_scorer_fwd_tc(Ctx c) {
@@ -243,16 +270,16 @@ __global__ void __launch_bounds__(kThreads, 2) k_scorer_fwd_tc(Ctx c) {
     __shared__ __align__(8) uint64_t bar[kTcStages];
     __shared__ __align__(8) uint64_t bar_mma;
     __shared__ uint32_t tmem_slot;
-    __shared__ float wt_s[8][kMaxTail];   // the tail block's weights, bfloat16 values
     __shared__ float bias_s[8];
     constexpr int d = 64 * KB, D4 = d / 4;
-    // [kTcStages] float32 tiles | 2 tail tiles | (1024-aligned) the bfloat16 operand tile | the weights' operand tile
+    // (1024-aligned) the state operand tile | the state weights' tile | the tail operand tile | the tail weights' tile | float32 stages
     unsigned char* dyn = dyn_raw + ((1024u - (smem_addr(dyn_raw) & 1023u)) & 1023u);
-    unsigned char* a_tile = dyn;                           // KB x [128 rows x 128 bytes]
+    unsigned char* a_tile = dyn;                           // KB x [128 rows x 128 bytes], 128-byte swizzle
     unsigned char* b_tile = a_tile + KB * kCells * 128;    // KB x [16 rows x 128 bytes]: the units, padded with zero rows
-    Tiles<D4, true, kTcStages> tl(b_tile + KB * 16 * 128, bar, c);
+    unsigned char* a2_tile = b_tile + KB * 16 * 128;       // [2 planes][128 rows][16 bytes], unswizzled: a cell's 16 tail numbers
+    unsigned char* b2_tile = a2_tile + 2 * kCells * 16;    // [2 planes][16 rows][16 bytes]
+    Tiles<D4, true, kTcStages> tl(b2_tile + 2 * 16 * 16, bar, c);
     const int tid = threadIdx.x, warp = tid >> 5;
-    const int T1 = tl.T1;
     if (tid == 0) {
         for (int st = 0; st < kTcStages; ++st) mbar_init(&bar[st], 1);
         mbar_init(&bar_mma, 1);
@@ -267,32 +294,40 @@ __global__ void __launch_bounds__(kThreads, 2) k_scorer_fwd_tc(Ctx c) {
         }
         *reinterpret_cast<uint4*>(b_tile + kb * (16 * 128) + row * 128 + ((uu ^ (row & 7)) << 4)) = packed;
     }
-    for (int e = tid; e < 8 * kMaxTail; e += kThreads) {
-        const int unit = e / kMaxTail, sI = e - unit * kMaxTail;
-        wt_s[unit][sI] = (unit < c.M && sI < T1) ? bf16r(c.weight[static_cast<int64_t>(unit) * c.F + 3 * d + sI]) : 0.0f;
+    if (tid < 32) {   // W[:, 3d:] as the tail product's B operand: (plane, unit) -> 8 weights
+        const int plane = tid >> 4, unit = tid & 15;
+        float w[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int k = 8 * plane + i;
+            w[i] = (unit < c.M && k <= c.S) ? c.weight[static_cast<int64_t>(unit) * c.F + 3 * d + k] : 0.0f;
+        }
+        *reinterpret_cast<uint4*>(b2_tile + plane * (16 * 16) + unit * 16) =
+            make_uint4(pack_bf16x2(w[0], w[1]), pack_bf16x2(w[2], w[3]), pack_bf16x2(w[4], w[5]), pack_bf16x2(w[6], w[7]));
     }
     if (tid < 8) bias_s[tid] = tid < c.M ? bf16r(c.bias[tid]) : 0.0f;
+    TailRegs tail;
     int64_t item = blockIdx.x;
     if (item < c.items) {
-        tl.tail_load(item);
-        tl.tail_store(0);
+        tail.load(c, tl.first_cell(item), tl.cells_of(item));
+        tail.store(c, a2_tile);
     }
     tcgen05_fence_before();
-    __syncthreads();   // the barriers, tensor memory and the weights' tile are in place
+    __syncthreads();   // the barriers, tensor memory and the weights' tiles are in place
     tcgen05_fence_after();
     const uint32_t taddr = tmem_slot;
     const uint32_t idesc = umma_idesc_bf16(128, 16);
     if (tid == 0)
-        for (int k = 0; k < kTcStages - 1; ++k)
+        for (int k = 0; k < kTcStages; ++k)
             if (item + k * static_cast<int64_t>(gridDim.x) < c.items) tl.request(item + k * static_cast<int64_t>(gridDim.x), k);
     for (int n_it = 0; item < c.items; item += gridDim.x, ++n_it) {
-        const int s = n_it % kTcStages, ts = n_it & 1;
-        const int64_t next = item + gridDim.x, ahead = item + (kTcStages - 1) * static_cast<int64_t>(gridDim.x);
+        const int s = n_it % kTcStages;
+        const int64_t next = item + gridDim.x, ahead = item + kTcStages * static_cast<int64_t>(gridDim.x);
         const int cells = tl.cells_of(item);
         mbar_wait(&bar[s], (n_it / kTcStages) & 1, c.status);
         convert_tile<KB>(tl.h_s + s * kCells * d, a_tile, cells);   // (the last tile's products were waited for before its epilogue)
         fence_async_smem();
-        __syncthreads();   // the operand tile and the tail are complete; everyone is done with the stage of the tile before
+        __syncthreads();   // both operand tiles are complete; the float32 stage has been read: it is free again
         if (tid < 32) {    // the whole first warp, converged after the barrier: one elected lane issues
             tcgen05_fence_after();
             __syncwarp();
@@ -302,36 +337,27 @@ __global__ void __launch_bounds__(kThreads, 2) k_scorer_fwd_tc(Ctx c) {
 #pragma unroll
                 for (int st = 0; st < 4; ++st) umma_bf16(taddr, da + 2 * st, db + 2 * st, idesc, kb > 0 || st > 0);
             }
+            umma_bf16(taddr + 16, umma_desc(a2_tile, kCells), umma_desc(b2_tile, 16), idesc, false);   // the tail block: its own sum
             umma_commit(&bar_mma);
         }
         if (tid == 0 && ahead < c.items) {
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // stage s was read by ordinary loads before the barrier... and the stage before it
-            tl.request(ahead, (n_it + kTcStages - 1) % kTcStages);
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // the stage was read by ordinary loads
+            tl.request(ahead, s);
         }
-        if (next < c.items) tl.tail_load(next);
+        if (next < c.items) tail.load(c, tl.first_cell(next), tl.cells_of(next));
         mbar_wait(&bar_mma, n_it & 1, c.status);
         tcgen05_fence_after();
-        if (warp < 4) {   // a thread a cell: the accumulator's 8 units, the tail block, the row term
-            float acc[8];
-            tmem_ld8(tmem_addr(taddr, warp * 32, 0), acc);
+        if (warp < 4) {   // a thread a cell: the two sums' 8 units, the bias, the row term
+            float state[8], rest[8];
+            tmem_ld8(tmem_addr(taddr, warp * 32, 0), state);
+            tmem_ld8(tmem_addr(taddr, warp * 32, 16), rest);
             const int cell = tid;
             if (cell < cells) {
-                const float* tt = tl.tail_s + ts * kCells * kMaxTail + cell * T1;
-                float tail[kMaxTail];
-#pragma unroll
-                for (int sI = 0; sI < kMaxTail; ++sI) tail[sI] = sI < T1 ? tt[sI] : 0.0f;
                 const int64_t r = item / c.tiles;
                 float out[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    float t0 = 0.0f, t1 = 0.0f;
-#pragma unroll
-                    for (int sI = 0; sI < kMaxTail; sI += 2) {
-                        t0 = fmaf(tail[sI], wt_s[j][sI], t0);
-                        t1 = fmaf(tail[sI + 1], wt_s[j][sI + 1], t1);
-                    }
-                    out[j] = (bf16r(acc[j]) + bf16r((t0 + t1) + bias_s[j])) + (j < c.M ? c.rowterm[r * c.M + j] : 0.0f);
-                }
+                for (int j = 0; j < 8; ++j)
+                    out[j] = (bf16r(state[j]) + bf16r(rest[j] + bias_s[j])) + (j < c.M ? c.rowterm[r * c.M + j] : 0.0f);
                 float* dst = c.logits + (tl.first_cell(item) + cell) * c.M;
                 if (c.M == 8) {
                     *reinterpret_cast<float4*>(dst) = make_float4(out[0], out[1], out[2], out[3]);
@@ -344,7 +370,7 @@ __global__ void __launch_bounds__(kThreads, 2) k_scorer_fwd_tc(Ctx c) {
             }
         }
         tcgen05_fence_before();
-        if (next < c.items) tl.tail_store(ts ^ 1);
+        if (next < c.items) tail.store(c, a2_tile);   // (this tile's products have read the tile: waited for above)
     }
     __syncthreads();
     if (warp == 0) tmem_dealloc(taddr, 32);
@@ -564,7 +590,7 @@ Ctx make_ctx(const HsnwScorer* s, const Plan& p, const float* u, const float* ep
 
 size_t tc_shared(int d) {   // 1024 of slack for the alignment, the two operand tiles, then the stages and the tail tiles
     const int KB = d / 64;
-    return 1024 + static_cast<size_t>(KB) * (kCells + 16) * 128 + sizeof(float) * (kTcStages * kCells * static_cast<size_t>(d) + 2 * kCells * kMaxTail);
+    return 1024 + static_cast<size_t>(KB) * (kCells + 16) * 128 + 2 * (kCells + 16) * 16 + sizeof(float) * (kTcStages * kCells * static_cast<size_t>(d) + 2 * kCells * kMaxTail);
 }
 
 template <bool BF>
