@@ -376,6 +376,141 @@ __global__ void __launch_bounds__(kThreads, 2) k_scorer_fwd_tc(Ctx c) {
     if (warp == 0) tmem_dealloc(taddr, 32);
 }
 
+// The gradients of the state block and of the tail block (with the bias as a column of ones) as two accumulating
+// products over all of a block's tiles: D1 [units, d] += g^T [units, cells] x h [cells, d], D2 [units, 16] += g^T x
+// [tail, 1] [cells, 16]. g^T is the A operand (K = the cells; unswizzled planes of 8 cells, 128 rows of which the
+// first `units` are not zero), h is the forward's bfloat16 tile read as B MN-major (a K row = a cell's 64 elements =
+// one 128-byte swizzled row), the tail is written transposed as B K-major. Nothing is read back per tile: the
+// accumulators stay in tensor memory until the block's last tile.
+constexpr int kBwdStages = 1;   // (g^T's zero rows take 32 KB: one stage a block keeps two blocks an SM)
+__global__ void __launch_bounds__(kThreads, 2) k_scorer_bwd_tc(Ctx c) {
+    extern __shared__ unsigned char dyn_raw[];
+    __shared__ __align__(8) uint64_t bar[kBwdStages];
+    __shared__ __align__(8) uint64_t bar_mma;
+    __shared__ uint32_t tmem_slot;
+    __shared__ float part_s[2][16][8];   // a tile's raw cotangent summed over 8 cells, per plane and unit
+    constexpr int d = 64, D4 = 16;
+    unsigned char* dyn = dyn_raw + ((1024u - (smem_addr(dyn_raw) & 1023u)) & 1023u);
+    unsigned char* h_tile = dyn;                        // [128 cells x 128 bytes], 128-byte swizzle
+    unsigned char* g_tile = h_tile + kCells * 128;      // [16 planes][128 rows][16 bytes]: g^T, rows >= units stay zero
+    unsigned char* t_tile = g_tile + 16 * 128 * 16;     // [16 planes][16 rows][16 bytes]: the tail and the ones, transposed
+    Tiles<D4, true, kBwdStages> tl(t_tile + 16 * 16 * 16, bar, c);
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int T1 = tl.T1;
+    if (tid == 0) {
+        for (int st = 0; st < kBwdStages; ++st) mbar_init(&bar[st], 1);
+        mbar_init(&bar_mma, 1);
+    }
+    if (warp == 0) tmem_alloc(&tmem_slot, 128);
+    for (int e = tid; e < 16 * 128; e += kThreads) reinterpret_cast<uint4*>(g_tile)[e] = make_uint4(0u, 0u, 0u, 0u);
+    for (int e = tid; e < 16 * 16; e += kThreads) reinterpret_cast<uint4*>(t_tile)[e] = make_uint4(0u, 0u, 0u, 0u);
+    TailRegs tail;
+    // thread (cell, half) writes its 8 tail numbers (and the one) into rows 8 half .. of column `cell`
+    auto tail_store = [&](int cells) {
+        const int cell = tid >> 1, half = tid & 1;
+        __nv_bfloat16* col = reinterpret_cast<__nv_bfloat16*>(t_tile + (cell >> 3) * (16 * 16)) + (cell & 7);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int k = 8 * half + i;
+            float v = k == 0 ? (tail.age >= 0 ? static_cast<float>(tail.age) / c.age_max : 0.0f) : tail.v[i];
+            if (k == T1) v = 1.0f;   // the bias: a column of ones
+            if (cell >= cells) v = 0.0f;
+            col[k * 8] = __float2bfloat16_rn(v);
+        }
+    };
+    int64_t item = blockIdx.x;
+    if (item < c.items) tail.load(c, tl.first_cell(item), tl.cells_of(item));
+    tcgen05_fence_before();
+    __syncthreads();   // the barriers, tensor memory and the zeroed tiles are in place
+    tcgen05_fence_after();
+    if (item < c.items) tail_store(tl.cells_of(item));
+    const uint32_t taddr = tmem_slot;
+    const uint32_t idesc_state = umma_idesc_bf16(128, 64) | (1u << 16);   // B MN-major
+    const uint32_t idesc_tail = umma_idesc_bf16(128, 16);
+    if (tid == 0)
+        for (int k = 0; k < kBwdStages; ++k)
+            if (item + k * static_cast<int64_t>(gridDim.x) < c.items) tl.request(item + k * static_cast<int64_t>(gridDim.x), k);
+    int n_it = 0;
+    int64_t last_item = -1;
+    for (; item < c.items; item += gridDim.x, ++n_it) {
+        const int s = n_it % kBwdStages, ts = n_it & 1;
+        const int64_t next = item + gridDim.x, ahead = item + kBwdStages * static_cast<int64_t>(gridDim.x);
+        const int cells = tl.cells_of(item);
+        const int64_t cell0 = tl.first_cell(item);
+        float g[8];
+        const int unit = tid & 7, plane = tid >> 3;   // threads 0..127: 8 cells of one unit
+        if (tid < 128) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int cell = 8 * plane + i;
+                g[i] = (cell < cells && unit < c.M) ? c.dlogits[(cell0 + cell) * c.M + unit] : 0.0f;
+            }
+        }
+        mbar_wait(&bar[s], (n_it / kBwdStages) & 1, c.status);
+        if (n_it > 0) mbar_wait(&bar_mma, (n_it - 1) & 1, c.status);   // the last tile's products have read the three operand tiles
+        convert_tile<1>(tl.h_s + s * kCells * d, h_tile, cells);
+        if (tid < 128) {
+            *reinterpret_cast<uint4*>(g_tile + plane * (128 * 16) + unit * 16) =
+                make_uint4(pack_bf16x2(g[0], g[1]), pack_bf16x2(g[2], g[3]), pack_bf16x2(g[4], g[5]), pack_bf16x2(g[6], g[7]));
+            part_s[ts][plane][unit] = ((g[0] + g[1]) + (g[2] + g[3])) + ((g[4] + g[5]) + (g[6] + g[7]));
+        }
+        if (n_it > 0) tail_store(cells);   // (the first tile's went in before the loop)
+        fence_async_smem();
+        __syncthreads();   // the operand tiles are complete; the float32 stage has been read: it is free again
+        if (tid < 32) {
+            tcgen05_fence_after();
+            __syncwarp();
+            const uint64_t da = umma_desc(g_tile, 128), db = umma_desc_sw128(h_tile), dt = umma_desc(t_tile, 16);
+#pragma unroll
+            for (int st = 0; st < 8; ++st) {   // 16 cells a step
+                umma_bf16(taddr, da + st * umma_kstep(128), db + st * 128u, idesc_state, n_it > 0 || st > 0);
+                umma_bf16(taddr + 64, da + st * umma_kstep(128), dt + st * umma_kstep(16), idesc_tail, n_it > 0 || st > 0);
+            }
+            umma_commit(&bar_mma);
+        }
+        if (tid < 8 && tid < c.M) {   // the tile's raw cotangent summed over its cells, planes in order
+            float total = 0.0f;
+#pragma unroll
+            for (int p = 0; p < 16; ++p) total += part_s[ts][p][tid];
+            c.rowsum[item * c.M + tid] = total;
+        }
+        if (tid == 0 && ahead < c.items) {
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            tl.request(ahead, s);
+        }
+        if (next < c.items) tail.load(c, tl.first_cell(next), tl.cells_of(next));
+        last_item = item;
+    }
+    if (n_it > 0) mbar_wait(&bar_mma, (n_it - 1) & 1, c.status);
+    tcgen05_fence_after();
+    const int width = d + T1 + 1;
+    if (warp == 0) {   // lanes = units: the block's sums out of tensor memory
+        const int lane = tid;
+        float* dst = c.partial + (static_cast<int64_t>(blockIdx.x) * c.M + lane) * width;
+        float x[8];
+#pragma unroll
+        for (int cb = 0; cb < 64; cb += 8) {
+            tmem_ld8(tmem_addr(taddr, 0, cb), x);
+            if (lane < c.M && last_item >= 0)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) dst[cb + i] = x[i];
+        }
+#pragma unroll
+        for (int cb = 0; cb < 16; cb += 8) {
+            tmem_ld8(tmem_addr(taddr, 0, 64 + cb), x);
+            if (lane < c.M && last_item >= 0)
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (cb + i <= T1) dst[d + cb + i] = x[i];   // the tail block, then the bias at d + T1
+        }
+        if (lane < c.M && last_item < 0)
+            for (int e = 0; e < width; ++e) dst[e] = 0.0f;
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(taddr, 128);
+}
+
 template <int D4, bool BF>
 __global__ void __launch_bounds__(kThreads, D4 <= 16 ? 2 : 1) k_scorer_bwd(Ctx c) {
     extern __shared__ __align__(16) unsigned char dyn[];
@@ -535,7 +670,7 @@ __global__ void __launch_bounds__(256) k_scorer_wgrad(Ctx c, int blocks, float* 
 size_t up256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
 struct Plan {
-    int tiles, blocks, blocks_tc;
+    int tiles, blocks, blocks_tc, blocks_bwd;
     size_t shared;
     size_t off_rowterm, off_partial, off_rowsum, off_partial_row, bytes;
 };
@@ -548,12 +683,13 @@ Plan make_plan(const HsnwScorer* s, int64_t rows, bool backward) {
     const int per_sm = static_cast<int>(std::max<size_t>(1, std::min<size_t>(2, (226 * 1024) / (p.shared + 1024))));   // (128 registers a thread: two blocks)
     p.blocks = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(rows * p.tiles, static_cast<int64_t>(sms) * per_sm)));
     p.blocks_tc = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(rows * p.tiles, 2 * static_cast<int64_t>(sms))));   // two blocks an SM
+    p.blocks_bwd = (s->prod_bf16 && s->d == 64 && s->n_scalars + 2 <= kMaxTail) ? p.blocks_tc : p.blocks;
     size_t at = 256;
     p.off_rowterm = at;
     at += up256(sizeof(float) * static_cast<size_t>(rows) * s->n_units);
     if (backward) {
         p.off_partial = at;
-        at += up256(sizeof(float) * static_cast<size_t>(p.blocks) * s->n_units * (s->d + s->n_scalars + 2));
+        at += up256(sizeof(float) * static_cast<size_t>(p.blocks_bwd) * s->n_units * (s->d + s->n_scalars + 2));
         p.off_rowsum = at;
         at += up256(sizeof(float) * static_cast<size_t>(rows) * p.tiles * s->n_units);
         p.off_partial_row = at;
@@ -606,8 +742,16 @@ void launch_fwd(const Ctx& c, const Plan& p, cudaStream_t stream) {
         default: k_scorer_fwd<32, BF><<<p.blocks, kThreads, p.shared, stream>>>(c); break;
     }
 }
+size_t tc_shared_bwd() {   // the alignment's slack, the three operand tiles, the stages (and the tail tiles the stage helper lays out)
+    return 1024 + kCells * 128 + 16 * 128 * 16 + 16 * 16 * 16 + sizeof(float) * (kBwdStages * kCells * 64);
+}
+
 template <bool BF>
 void launch_bwd(const Ctx& c, const Plan& p, cudaStream_t stream) {
+    if (BF && c.d == 64 && c.S + 2 <= kMaxTail) {   // (make_plan's condition for blocks_bwd)
+        k_scorer_bwd_tc<<<p.blocks_bwd, kThreads, tc_shared_bwd(), stream>>>(c);
+        return;
+    }
     switch (c.d) {
         case 16: k_scorer_bwd<4, BF><<<p.blocks, kThreads, p.shared, stream>>>(c); break;
         case 32: k_scorer_bwd<8, BF><<<p.blocks, kThreads, p.shared, stream>>>(c); break;
@@ -681,11 +825,11 @@ extern "C" int hsnw_scorer_logits_backward(const HsnwScorer* scorer, const float
     if (scorer->prod_bf16) {
         launch_bwd<true>(c, p, stream);
         k_scorer_rowgrad<true><<<kRowChunks, 256, 0, stream>>>(c);
-        k_scorer_wgrad<true><<<out_blocks, 256, 0, stream>>>(c, p.blocks, d_weight, d_bias);
+        k_scorer_wgrad<true><<<out_blocks, 256, 0, stream>>>(c, p.blocks_bwd, d_weight, d_bias);
     } else {
         launch_bwd<false>(c, p, stream);
         k_scorer_rowgrad<false><<<kRowChunks, 256, 0, stream>>>(c);
-        k_scorer_wgrad<false><<<out_blocks, 256, 0, stream>>>(c, p.blocks, d_weight, d_bias);
+        k_scorer_wgrad<false><<<out_blocks, 256, 0, stream>>>(c, p.blocks_bwd, d_weight, d_bias);
     }
     return hsnw_check_launch("scorer_logits_backward");
 }
@@ -702,6 +846,7 @@ void hsnw_scorer_set_attributes() {
     HSNW_SCORER_OPT(16);
     HSNW_SCORER_OPT(32);
 #undef HSNW_SCORER_OPT
-    ok = ok && hsnw_opt_in(reinterpret_cast<const void*>(k_scorer_fwd_tc<1>), "scorer_fwd_tc");
+    ok = ok && hsnw_opt_in(reinterpret_cast<const void*>(k_scorer_fwd_tc<1>), "scorer_fwd_tc")
+         && hsnw_opt_in(reinterpret_cast<const void*>(k_scorer_bwd_tc), "scorer_bwd_tc");
     if (!ok) hsnw_attribute_failed();
 }
