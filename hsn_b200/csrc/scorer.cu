@@ -31,7 +31,7 @@ namespace {
 constexpr int kCells = 128;    // cells of a tile
 constexpr int kThreads = 256;  // 8 warps x 4 cells x 8 units
 constexpr int kMaxTail = 16;   // 1 + scalars
-constexpr int kRowChunks = 64; // partial sums of the row block's gradient
+constexpr int kRowChunks = 128; // partial sums of the row block's gradient
 constexpr int kStages = 3;     // tiles of h in shared memory: the block works on one, two are on their way
 
 struct Ctx {
@@ -630,41 +630,64 @@ __global__ void __launch_bounds__(kThreads, D4 <= 16 ? 2 : 1) k_scorer_bwd(Ctx c
     }
 }
 
-// the row block's gradient: chunk of rows x (unit, input) -> partial_row[chunk][unit][input]
+// the row block's gradient: a chunk of positions -> partial_row[chunk][unit][input]. The chunk's cotangents
+// (a position's, summed over its tiles, rounded as the row map's cotangent is) go to shared memory; a thread
+// then owns an input column and four units and walks the chunk's rows, whose loads do not depend on one another.
 template <bool BF>
 __global__ void __launch_bounds__(256) k_scorer_rowgrad(Ctx c) {
-    const int64_t per = (c.rows + kRowChunks - 1) / kRowChunks;
+    __shared__ float g_s[64][8];
+    const int64_t per = (c.rows + kRowChunks - 1) / kRowChunks;   // at most 64 a block: the host splits the chunks so
     const int64_t r0 = blockIdx.x * per, r1 = min(c.rows, r0 + per);
-    const int two_d = 2 * c.d;
-    for (int e = threadIdx.x; e < c.M * two_d; e += 256) {
-        const int unit = e / two_d, x = e - unit * two_d;
-        float sum = 0.0f;
-        for (int64_t r = r0; r < r1; ++r) {
+    const int n = static_cast<int>(max(static_cast<int64_t>(0), r1 - r0)), two_d = 2 * c.d, tid = threadIdx.x;
+    float* out = c.partial_row + static_cast<int64_t>(blockIdx.x) * c.M * two_d;
+    for (int base = 0; base < max(n, 1); base += 64) {   // (n <= 64 with the host's chunks; the loop keeps any n right)
+        const int m = min(64, n - base);
+        __syncthreads();
+        for (int e = tid; e < 64 * 8; e += 256) {
+            const int rr = e >> 3, unit = e & 7;
             float g = 0.0f;
-            for (int t = 0; t < c.tiles; ++t) g += c.rowsum[(r * c.tiles + t) * c.M + unit];
-            const float in = x < c.d ? c.u[r * c.d + x] : c.eps[r * c.d + x - c.d];
-            sum = fmaf(rnd<BF>(g), rnd<BF>(in), sum);
+            if (rr < m && unit < c.M)
+                for (int t = 0; t < c.tiles; ++t) g += c.rowsum[((r0 + base + rr) * c.tiles + t) * c.M + unit];
+            g_s[rr][unit] = rnd<BF>(g);
         }
-        c.partial_row[static_cast<int64_t>(blockIdx.x) * c.M * two_d + e] = sum;
+        __syncthreads();
+        for (int x = tid & 127; x < two_d; x += 128) {
+            const int u0 = 4 * (tid >> 7);
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 8
+            for (int rr = 0; rr < m; ++rr) {
+                const int64_t r = r0 + base + rr;
+                const float in = rnd<BF>(x < c.d ? c.u[r * c.d + x] : c.eps[r * c.d + x - c.d]);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) acc[k] = fmaf(g_s[rr][u0 + k], in, acc[k]);
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (u0 + k < c.M) out[(u0 + k) * two_d + x] = (base == 0 ? 0.0f : out[(u0 + k) * two_d + x]) + acc[k];
+        }
     }
 }
 
-// d_weight and d_bias from the blocks' and the row chunks' partial sums, in order
+// d_weight and d_bias from the blocks' and the row chunks' partial sums: a warp an output, a lane every 32nd
+// partial in order, then a fixed tree over the lanes (the same bits every run)
 template <bool BF>
 __global__ void __launch_bounds__(256) k_scorer_wgrad(Ctx c, int blocks, float* d_weight, float* d_bias) {
     const int width = c.d + c.S + 2, two_d = 2 * c.d;
-    const int e = blockIdx.x * 256 + threadIdx.x;
+    const int e = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (e >= c.M * (c.F + 1)) return;
     const int unit = e / (c.F + 1), col = e - unit * (c.F + 1);   // col F: the bias
     float total = 0.0f;
     if (col < two_d) {
-        for (int k = 0; k < kRowChunks; ++k) total += c.partial_row[(static_cast<int64_t>(k) * c.M + unit) * two_d + col];
+        for (int k = lane; k < kRowChunks; k += 32) total += c.partial_row[(static_cast<int64_t>(k) * c.M + unit) * two_d + col];
     } else {
         const int at = col - two_d;   // the state block, the tail block, the bias: the blocks' layout
-        for (int b = 0; b < blocks; ++b) total += c.partial[(static_cast<int64_t>(b) * c.M + unit) * width + at];
+        for (int b = lane; b < blocks; b += 32) total += c.partial[(static_cast<int64_t>(b) * c.M + unit) * width + at];
     }
-    if (col < c.F) d_weight[unit * c.F + col] = rnd<BF>(total);
-    else d_bias[unit] = rnd<BF>(total);
+    total = warp_sum(total);
+    if (lane == 0) {
+        if (col < c.F) d_weight[unit * c.F + col] = rnd<BF>(total);
+        else d_bias[unit] = rnd<BF>(total);
+    }
 }
 
 size_t up256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
@@ -821,7 +844,7 @@ extern "C" int hsnw_scorer_logits_backward(const HsnwScorer* scorer, const float
     c.dlogits = d_logits;
     if (cudaMemsetAsync(c.status, 0, sizeof(int), stream) != cudaSuccess) return hsnw_check_launch("scorer_logits_backward");
     hsnw_profile_mark(HSNW_K_SCORER_BWD, stream);
-    const unsigned out_blocks = static_cast<unsigned>((c.M * (F + 1) + 255) / 256);
+    const unsigned out_blocks = static_cast<unsigned>((c.M * (F + 1) + 7) / 8);   // a warp an output
     if (scorer->prod_bf16) {
         launch_bwd<true>(c, p, stream);
         k_scorer_rowgrad<true><<<kRowChunks, 256, 0, stream>>>(c);
