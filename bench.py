@@ -979,8 +979,9 @@ def run_scorer(args, c: dict, name: str) -> None:
                    "forward_ms": fwd_ms, "backward_ms": bwd_ms, "step_ms": spread(each),
                    "torch_three_linear_maps_autocast_autograd_ms": torch_total / max(3, args.steps // 4)},
         "gpu_launches": 5 * args.steps,
-        "roofline": {"bound": "hbm", "kernel": "k_scorer_fwd + k_scorer_bwd", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": None, "peak_source": "measured" if peaks else "fallback",
+        "roofline": {"bound": "hbm", "kernel": "k_scorer_fwd_tc + k_scorer_bwd_tc", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": 686.4e6 + 697.1e6,
+                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of the two kernels at this size (profiles/scorer_c2.md)", "peak_source": "measured" if peaks else "fallback",
                      "forward": {"achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9, "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak},
                      "backward": {"achieved": bwd_bytes / (bwd_ms * 1e-3) / 1e9, "frac": bwd_bytes / (bwd_ms * 1e-3) / 1e9 / peak},
                      "how": "per cell 4 d + 8 + 4 S + 4 M bytes each way (state, age, scalars, and logits written or cotangent read) / the calls' event time in a profiled step"},
