@@ -378,11 +378,11 @@ __global__ void __launch_bounds__(kThreads, 2) k_scorer_fwd_tc(Ctx c) {
 
 // The gradients of the state block and of the tail block (with the bias as a column of ones) as two accumulating
 // products over all of a block's tiles: D1 [units, d] += g^T [units, cells] x h [cells, d], D2 [units, 16] += g^T x
-// [tail, 1] [cells, 16]. g^T is the A operand (K = the cells; unswizzled planes of 8 cells, 128 rows of which the
-// first `units` are not zero), h is the forward's bfloat16 tile read as B MN-major (a K row = a cell's 64 elements =
+// [tail, 1] [cells, 16]. g^T is the A operand (K = the cells; 8 rows in the 128-byte swizzle, which every row group
+// of the product's 128 rows reads again), h is the forward's bfloat16 tile read as B MN-major (a K row = a cell's 64 elements =
 // one 128-byte swizzled row), the tail is written transposed as B K-major. Nothing is read back per tile: the
 // accumulators stay in tensor memory until the block's last tile.
-constexpr int kBwdStages = 1;   // (g^T's zero rows take 32 KB: one stage a block keeps two blocks an SM)
+constexpr int kBwdStages = 2;
 __global__ void __launch_bounds__(kThreads, 2) k_scorer_bwd_tc(Ctx c) {
     extern __shared__ unsigned char dyn_raw[];
     __shared__ __align__(8) uint64_t bar[kBwdStages];
@@ -392,8 +392,10 @@ __global__ void __launch_bounds__(kThreads, 2) k_scorer_bwd_tc(Ctx c) {
     constexpr int d = 64, D4 = 16;
     unsigned char* dyn = dyn_raw + ((1024u - (smem_addr(dyn_raw) & 1023u)) & 1023u);
     unsigned char* h_tile = dyn;                        // [128 cells x 128 bytes], 128-byte swizzle
-    unsigned char* g_tile = h_tile + kCells * 128;      // [16 planes][128 rows][16 bytes]: g^T, rows >= units stay zero
-    unsigned char* t_tile = g_tile + 16 * 128 * 16;     // [16 planes][16 rows][16 bytes]: the tail and the ones, transposed
+    unsigned char* g_tile = h_tile + kCells * 128;      // [2 K blocks of 64 cells][8 rows x 128 bytes], 128-byte swizzle: g^T; the
+                                                        // descriptor's stride between row groups is zero, so the product's rows
+                                                        // 8 .. 127 repeat rows 0 .. 7 (never read)
+    unsigned char* t_tile = g_tile + 2 * 8 * 128;       // [16 planes][16 rows][16 bytes]: the tail and the ones, transposed
     Tiles<D4, true, kBwdStages> tl(t_tile + 16 * 16 * 16, bar, c);
     const int tid = threadIdx.x, warp = tid >> 5;
     const int T1 = tl.T1;
@@ -402,7 +404,6 @@ __global__ void __launch_bounds__(kThreads, 2) k_scorer_bwd_tc(Ctx c) {
         mbar_init(&bar_mma, 1);
     }
     if (warp == 0) tmem_alloc(&tmem_slot, 128);
-    for (int e = tid; e < 16 * 128; e += kThreads) reinterpret_cast<uint4*>(g_tile)[e] = make_uint4(0u, 0u, 0u, 0u);
     for (int e = tid; e < 16 * 16; e += kThreads) reinterpret_cast<uint4*>(t_tile)[e] = make_uint4(0u, 0u, 0u, 0u);
     TailRegs tail;
     // thread (cell, half) writes its 8 tail numbers (and the one) into rows 8 half .. of column `cell`
@@ -450,7 +451,7 @@ __global__ void __launch_bounds__(kThreads, 2) k_scorer_bwd_tc(Ctx c) {
         if (n_it > 0) mbar_wait(&bar_mma, (n_it - 1) & 1, c.status);   // the last tile's products have read the three operand tiles
         convert_tile<1>(tl.h_s + s * kCells * d, h_tile, cells);
         if (tid < 128) {
-            *reinterpret_cast<uint4*>(g_tile + plane * (128 * 16) + unit * 16) =
+            *reinterpret_cast<uint4*>(g_tile + (plane >> 3) * (8 * 128) + unit * 128 + (((plane & 7) ^ unit) << 4)) =
                 make_uint4(pack_bf16x2(g[0], g[1]), pack_bf16x2(g[2], g[3]), pack_bf16x2(g[4], g[5]), pack_bf16x2(g[6], g[7]));
             part_s[ts][plane][unit] = ((g[0] + g[1]) + (g[2] + g[3])) + ((g[4] + g[5]) + (g[6] + g[7]));
         }
@@ -460,11 +461,13 @@ __global__ void __launch_bounds__(kThreads, 2) k_scorer_bwd_tc(Ctx c) {
         if (tid < 32) {
             tcgen05_fence_after();
             __syncwarp();
-            const uint64_t da = umma_desc(g_tile, 128), db = umma_desc_sw128(h_tile), dt = umma_desc(t_tile, 16);
+            const uint64_t no_stride = ~(static_cast<uint64_t>(0x3fffu) << 32);   // the row groups of g^T all start at its first
+            const uint64_t db = umma_desc_sw128(h_tile), dt = umma_desc(t_tile, 16);
 #pragma unroll
             for (int st = 0; st < 8; ++st) {   // 16 cells a step
-                umma_bf16(taddr, da + st * umma_kstep(128), db + st * 128u, idesc_state, n_it > 0 || st > 0);
-                umma_bf16(taddr + 64, da + st * umma_kstep(128), dt + st * umma_kstep(16), idesc_tail, n_it > 0 || st > 0);
+                const uint64_t da = (umma_desc_sw128(g_tile + (st >> 2) * (8 * 128)) & no_stride) + 2u * (st & 3);
+                umma_bf16(taddr, da, db + st * 128u, idesc_state, n_it > 0 || st > 0);
+                umma_bf16(taddr + 64, da, dt + st * umma_kstep(16), idesc_tail, n_it > 0 || st > 0);
             }
             umma_commit(&bar_mma);
         }
@@ -766,7 +769,7 @@ void launch_fwd(const Ctx& c, const Plan& p, cudaStream_t stream) {
     }
 }
 size_t tc_shared_bwd() {   // the alignment's slack, the three operand tiles, the stages (and the tail tiles the stage helper lays out)
-    return 1024 + kCells * 128 + 16 * 128 * 16 + 16 * 16 * 16 + sizeof(float) * (kBwdStages * kCells * 64);
+    return 1024 + kCells * 128 + 2 * 8 * 128 + 16 * 16 * 16 + sizeof(float) * (kBwdStages * kCells * 64);
 }
 
 template <bool BF>
