@@ -386,30 +386,35 @@ constexpr int kBwdStages = 2;
 __global__ void __launch_bounds__(kThreads, 2) k_scorer_bwd_tc(Ctx c) {
     extern __shared__ unsigned char dyn_raw[];
     __shared__ __align__(8) uint64_t bar[kBwdStages];
-    __shared__ __align__(8) uint64_t bar_mma;
+    __shared__ __align__(8) uint64_t bar_mma[2];   // the products of a tile have read operand set (tile & 1)
     __shared__ uint32_t tmem_slot;
     __shared__ float part_s[2][16][8];   // a tile's raw cotangent summed over 8 cells, per plane and unit
     constexpr int d = 64, D4 = 16;
     unsigned char* dyn = dyn_raw + ((1024u - (smem_addr(dyn_raw) & 1023u)) & 1023u);
-    unsigned char* h_tile = dyn;                        // [128 cells x 128 bytes], 128-byte swizzle
+    constexpr int kSet = kCells * 128 + 2 * 8 * 128 + 16 * 16 * 16;   // two sets of the three operand tiles: a tile is staged
+    unsigned char* h_tile = dyn;                        // beside the products of the one before. [128 cells x 128 bytes], 128-byte swizzle
     unsigned char* g_tile = h_tile + kCells * 128;      // [2 K blocks of 64 cells][8 rows x 128 bytes], 128-byte swizzle: g^T; the
                                                         // descriptor's stride between row groups is zero, so the product's rows
                                                         // 8 .. 127 repeat rows 0 .. 7 (never read)
     unsigned char* t_tile = g_tile + 2 * 8 * 128;       // [16 planes][16 rows][16 bytes]: the tail and the ones, transposed
-    Tiles<D4, true, kBwdStages> tl(t_tile + 16 * 16 * 16, bar, c);
+    Tiles<D4, true, kBwdStages> tl(dyn + 2 * kSet, bar, c);
     const int tid = threadIdx.x, warp = tid >> 5;
     const int T1 = tl.T1;
     if (tid == 0) {
         for (int st = 0; st < kBwdStages; ++st) mbar_init(&bar[st], 1);
-        mbar_init(&bar_mma, 1);
+        mbar_init(&bar_mma[0], 1);
+        mbar_init(&bar_mma[1], 1);
     }
     if (warp == 0) tmem_alloc(&tmem_slot, 128);
-    for (int e = tid; e < 16 * 16; e += kThreads) reinterpret_cast<uint4*>(t_tile)[e] = make_uint4(0u, 0u, 0u, 0u);
+    for (int e = tid; e < 16 * 16; e += kThreads) {
+        reinterpret_cast<uint4*>(t_tile)[e] = make_uint4(0u, 0u, 0u, 0u);
+        reinterpret_cast<uint4*>(t_tile + kSet)[e] = make_uint4(0u, 0u, 0u, 0u);
+    }
     TailRegs tail;
     // thread (cell, half) writes its 8 tail numbers (and the one) into rows 8 half .. of column `cell`
-    auto tail_store = [&](int cells) {
+    auto tail_store = [&](int cells, int set) {
         const int cell = tid >> 1, half = tid & 1;
-        __nv_bfloat16* col = reinterpret_cast<__nv_bfloat16*>(t_tile + (cell >> 3) * (16 * 16)) + (cell & 7);
+        __nv_bfloat16* col = reinterpret_cast<__nv_bfloat16*>(t_tile + set * kSet + (cell >> 3) * (16 * 16)) + (cell & 7);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const int k = 8 * half + i;
@@ -424,7 +429,7 @@ __global__ void __launch_bounds__(kThreads, 2) k_scorer_bwd_tc(Ctx c) {
     tcgen05_fence_before();
     __syncthreads();   // the barriers, tensor memory and the zeroed tiles are in place
     tcgen05_fence_after();
-    if (item < c.items) tail_store(tl.cells_of(item));
+    if (item < c.items) tail_store(tl.cells_of(item), 0);
     const uint32_t taddr = tmem_slot;
     const uint32_t idesc_state = umma_idesc_bf16(128, 64) | (1u << 16);   // B MN-major
     const uint32_t idesc_tail = umma_idesc_bf16(128, 16);
@@ -433,43 +438,46 @@ __global__ void __launch_bounds__(kThreads, 2) k_scorer_bwd_tc(Ctx c) {
             if (item + k * static_cast<int64_t>(gridDim.x) < c.items) tl.request(item + k * static_cast<int64_t>(gridDim.x), k);
     int n_it = 0;
     int64_t last_item = -1;
+    float g[8];   // threads 0..127: the tile's cotangent for 8 cells of one unit, requested a tile ahead
+    auto g_load = [&](int64_t it) {
+        const int n = tl.cells_of(it);
+        const int64_t first = tl.first_cell(it);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int cell = 8 * (tid >> 3) + i;
+            g[i] = (tid < 128 && cell < n && (tid & 7) < c.M) ? c.dlogits[(first + cell) * c.M + (tid & 7)] : 0.0f;
+        }
+    };
+    if (item < c.items) g_load(item);
     for (; item < c.items; item += gridDim.x, ++n_it) {
         const int s = n_it % kBwdStages, ts = n_it & 1;
         const int64_t next = item + gridDim.x, ahead = item + kBwdStages * static_cast<int64_t>(gridDim.x);
         const int cells = tl.cells_of(item);
-        const int64_t cell0 = tl.first_cell(item);
-        float g[8];
         const int unit = tid & 7, plane = tid >> 3;   // threads 0..127: 8 cells of one unit
-        if (tid < 128) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int cell = 8 * plane + i;
-                g[i] = (cell < cells && unit < c.M) ? c.dlogits[(cell0 + cell) * c.M + unit] : 0.0f;
-            }
-        }
         mbar_wait(&bar[s], (n_it / kBwdStages) & 1, c.status);
-        if (n_it > 0) mbar_wait(&bar_mma, (n_it - 1) & 1, c.status);   // the last tile's products have read the three operand tiles
-        convert_tile<1>(tl.h_s + s * kCells * d, h_tile, cells);
+        const int set = n_it & 1;
+        if (n_it > 1) mbar_wait(&bar_mma[set], ((n_it >> 1) - 1) & 1, c.status);   // the products of two tiles ago have read this set
+        convert_tile<1>(tl.h_s + s * kCells * d, h_tile + set * kSet, cells);
         if (tid < 128) {
-            *reinterpret_cast<uint4*>(g_tile + (plane >> 3) * (8 * 128) + unit * 128 + (((plane & 7) ^ unit) << 4)) =
+            *reinterpret_cast<uint4*>(g_tile + set * kSet + (plane >> 3) * (8 * 128) + unit * 128 + (((plane & 7) ^ unit) << 4)) =
                 make_uint4(pack_bf16x2(g[0], g[1]), pack_bf16x2(g[2], g[3]), pack_bf16x2(g[4], g[5]), pack_bf16x2(g[6], g[7]));
             part_s[ts][plane][unit] = ((g[0] + g[1]) + (g[2] + g[3])) + ((g[4] + g[5]) + (g[6] + g[7]));
         }
-        if (n_it > 0) tail_store(cells);   // (the first tile's went in before the loop)
+        if (n_it > 0) tail_store(cells, set);   // (the first tile's went in before the loop)
         fence_async_smem();
         __syncthreads();   // the operand tiles are complete; the float32 stage has been read: it is free again
         if (tid < 32) {
             tcgen05_fence_after();
             __syncwarp();
             const uint64_t no_stride = ~(static_cast<uint64_t>(0x3fffu) << 32);   // the row groups of g^T all start at its first
-            const uint64_t db = umma_desc_sw128(h_tile), dt = umma_desc(t_tile, 16);
+            const uint64_t db = umma_desc_sw128(h_tile + set * kSet), dt = umma_desc(t_tile + set * kSet, 16);
 #pragma unroll
             for (int st = 0; st < 8; ++st) {   // 16 cells a step
-                const uint64_t da = (umma_desc_sw128(g_tile + (st >> 2) * (8 * 128)) & no_stride) + 2u * (st & 3);
+                const uint64_t da = (umma_desc_sw128(g_tile + set * kSet + (st >> 2) * (8 * 128)) & no_stride) + 2u * (st & 3);
                 umma_bf16(taddr, da, db + st * 128u, idesc_state, n_it > 0 || st > 0);
                 umma_bf16(taddr + 64, da, dt + st * umma_kstep(16), idesc_tail, n_it > 0 || st > 0);
             }
-            umma_commit(&bar_mma);
+            umma_commit(&bar_mma[set]);
         }
         if (tid < 8 && tid < c.M) {   // the tile's raw cotangent summed over its cells, planes in order
             float total = 0.0f;
@@ -481,10 +489,13 @@ __global__ void __launch_bounds__(kThreads, 2) k_scorer_bwd_tc(Ctx c) {
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             tl.request(ahead, s);
         }
-        if (next < c.items) tail.load(c, tl.first_cell(next), tl.cells_of(next));
+        if (next < c.items) {
+            tail.load(c, tl.first_cell(next), tl.cells_of(next));
+            g_load(next);   // (this tile's were packed into the operand tile before the barrier)
+        }
         last_item = item;
     }
-    if (n_it > 0) mbar_wait(&bar_mma, (n_it - 1) & 1, c.status);
+    if (n_it > 0) mbar_wait(&bar_mma[(n_it - 1) & 1], ((n_it - 1) >> 1) & 1, c.status);   // the last commit covers every product before it
     tcgen05_fence_after();
     const int width = d + T1 + 1;
     if (warp == 0) {   // lanes = units: the block's sums out of tensor memory
@@ -769,7 +780,7 @@ void launch_fwd(const Ctx& c, const Plan& p, cudaStream_t stream) {
     }
 }
 size_t tc_shared_bwd() {   // the alignment's slack, the three operand tiles, the stages (and the tail tiles the stage helper lays out)
-    return 1024 + kCells * 128 + 2 * 8 * 128 + 16 * 16 * 16 + sizeof(float) * (kBwdStages * kCells * 64);
+    return 1024 + 2 * (kCells * 128 + 2 * 8 * 128 + 16 * 16 * 16) + sizeof(float) * (kBwdStages * kCells * 64);
 }
 
 template <bool BF>
