@@ -3,8 +3,12 @@ reset masking, reverse state recurrence, carried state) as hand-written sm_100a 
 C ABI, with the reference's Python interface on top.
 
 * :mod:`hsn_b200.kernels.window` mirrors the reference's ``hsn.kernels.window`` (custom ops kept).
-* :mod:`hsn_b200.window` holds the whole-window entry points (forward sweep, reverse sweep,
-  streaming step).
+* :mod:`hsn_b200.window` holds the whole-window entry points (prologue, forward sweep, reverse sweep,
+  streaming step, decoder).
+* :mod:`hsn_b200.kernels.trainer` mirrors ``hsn.kernels.trainer``; :mod:`hsn_b200.parallel` holds the fused
+  gradient exchange + AdamW; :mod:`hsn_b200.state` the carried state's snapshots and checkpoint payload.
+* :mod:`hsn_b200.kernels.units` and :mod:`hsn_b200.kernels.scorer` are two pieces of the split window's replay:
+  ``UnitBank.forward_grouped`` and ``_scorer_logits`` as autograd functions.
 * :mod:`hsn_b200.build` compiles ``csrc`` into ``lib/libhsn_window_b200.so``.
 
 Importing the package neither initialises CUDA nor loads the library.
