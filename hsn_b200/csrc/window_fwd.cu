@@ -125,8 +125,6 @@ __global__ void __launch_bounds__(256) k_init(FwdCtx c) {
     extern __shared__ __align__(16) unsigned char dyn[];
     const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
     const int N = c.m.N, d = c.m.d, M = c.m.M, T = c.io.T;
-    const int cell0 = blockIdx.y * kInitCells;
-    const int ncell = min(kInitCells, N - cell0);
     float* hs = reinterpret_cast<float*>(dyn);
     float* hb = hs + kInitCells * d;     // the same rows at the products' operand precision
     float* swh = hb + kInitCells * d;
@@ -140,6 +138,11 @@ __global__ void __launch_bounds__(256) k_init(FwdCtx c) {
     if (c.carried && c.status[4] == c.marker && !cut) return;
     for (int e = tid; e < d * M; e += nt) swh[e] = c.m.score_w_t[2 * d * M + e];
     for (int e = tid; e < d * d; e += nt) vt[e] = c.m.v_t[e];
+    // (a carried call launches at most 8 blocks a row: they walk the row's tiles themselves on the rare row that was reset)
+    for (int tile = blockIdx.y; tile * kInitCells < N; tile += gridDim.y) {
+    const int cell0 = tile * kInitCells;
+    const int ncell = min(kInitCells, N - cell0);
+    __syncthreads();   // the last tile's rows have been read
     for (int e = tid; e < ncell * d; e += nt) {
         const float v = cut ? 0.0f : h0[static_cast<int64_t>(cell0) * d + e];
         hs[e] = v;
@@ -152,7 +155,7 @@ __global__ void __launch_bounds__(256) k_init(FwdCtx c) {
         if (c.io.tape_state) c.io.tape_age[(static_cast<int64_t>(row) * (T + 1)) * N + cell0 + n] = cut ? 0 : a0[n];
         else if (cut) a0[n] = 0;
     }
-    if (blockIdx.y == 0) {
+    if (tile == 0) {
         float* q0 = c.io.q0 + static_cast<int64_t>(row) * d;
         for (int x = tid; x < d; x += nt) {
             if (c.io.tape_state) c.io.tape_q[(static_cast<int64_t>(row) * (T + 1)) * d + x] = cut ? 0.0f : q0[x];
@@ -170,6 +173,7 @@ __global__ void __launch_bounds__(256) k_init(FwdCtx c) {
             for (int x = 0; x < d; ++x) top = max(top, __float_as_int(fabsf(hs[cl * d + x])));
             c.cmax[cell] = top;
         }
+    }
     }
 }
 
@@ -1464,7 +1468,8 @@ static int forward_impl(const HsnwModel* model, const HsnwForward* io, void* str
     }
     hsnw_set_path(HSNW_PATH_PHASES);
     const int rthreads = row_threads(*model, B);
-    const dim3 init_grid(B, (model->N + kInitCells - 1) / kInitCells);
+    const int init_tiles = (model->N + kInitCells - 1) / kInitCells;
+    const dim3 init_grid(B, c.carried ? (init_tiles < 8 ? init_tiles : 8) : init_tiles);   // carried: few blocks a row; as a rule they only look at the marker
     hsnw_profile_mark(HSNW_K_INIT, stream);
     k_init<<<init_grid, 256, init_shared(*model), stream>>>(c);
     if (!pre_done) {
