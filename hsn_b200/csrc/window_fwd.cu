@@ -242,6 +242,8 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&pair);
 }
 
+// BN: the columns of a block's tile (128; 32 for few rows, so that a serving step's 512 rows still give 64 blocks)
+template <int BN>
 __global__ void __launch_bounds__(128) k_pre_tc(HsnwModel m, const float* z, const float* ctx, int64_t rows, float* out,
                                                 int* status) {
     extern __shared__ __align__(16) unsigned char dyn[];
@@ -250,21 +252,34 @@ __global__ void __launch_bounds__(128) k_pre_tc(HsnwModel m, const float* z, con
     const int d = m.d, dc = m.dc, H = m.H, K = d + dc, Kp = (K + 15) & ~15, planes = Kp >> 3;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int64_t r0 = static_cast<int64_t>(blockIdx.x) * 128;
-    const int c0 = blockIdx.y * 128;
+    const int c0 = blockIdx.y * BN;
     uint4* As = reinterpret_cast<uint4*>(dyn);
     uint4* Bs = As + planes * 128;
     if (tid == 0) mbar_init(&bar, 1);
+    // eight consecutive inputs of a row are 32 contiguous bytes of z or of ctx when both widths are multiples of 8
+    const bool vec = ((d | dc) & 7) == 0 && ((reinterpret_cast<uintptr_t>(z) | reinterpret_cast<uintptr_t>(ctx)) & 15) == 0;
     for (int idx = tid; idx < planes * 128; idx += 128) {
         const int r = idx & 127, kc = idx >> 7;
         const int64_t row = r0 + r;
         float v[8];
+        const int k0 = kc * 8;
+        if (vec && row < rows && k0 < K) {
+            const float* src = k0 < d ? z + row * d + k0 : ctx + row * dc + (k0 - d);
+            const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
+            v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+        } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int k = kc * 8 + j;
-            v[j] = (row < rows && k < K) ? (k < d ? z[row * d + k] : ctx[row * dc + (k - d)]) : 0.0f;
+            for (int j = 0; j < 8; ++j) {
+                const int k = k0 + j;
+                v[j] = (row < rows && k < K) ? (k < d ? z[row * d + k] : ctx[row * dc + (k - d)]) : 0.0f;
+            }
         }
         As[idx] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+    }
+    for (int idx = tid; idx < planes * BN; idx += 128) {
+        const int r = idx % BN, kc = idx / BN;
         const int col = c0 + r;
+        float v[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int k = kc * 8 + j;
@@ -273,21 +288,21 @@ __global__ void __launch_bounds__(128) k_pre_tc(HsnwModel m, const float* z, con
         Bs[idx] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
     }
     fence_async_smem();
-    if (warp == 0) tmem_alloc(&tmem_slot, 128);
+    if (warp == 0) tmem_alloc(&tmem_slot, BN);
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t taddr = tmem_slot;
     if (tid < 32) {   // the whole first warp, converged after the barrier: one elected lane issues
-        const uint32_t idesc = umma_idesc_bf16(128, 128);
-        const uint64_t da = umma_desc(As, 128), db = umma_desc(Bs, 128);
-        umma_chain(taddr, da, db, idesc, Kp >> 4, umma_kstep(128), umma_kstep(128));  // two planes per K = 16
+        const uint32_t idesc = umma_idesc_bf16(128, BN);
+        const uint64_t da = umma_desc(As, 128), db = umma_desc(Bs, BN);
+        umma_chain(taddr, da, db, idesc, Kp >> 4, umma_kstep(128), umma_kstep(BN));  // two planes per K = 16
         umma_commit(&bar);
     }
     mbar_wait(&bar, 0, status);
     tcgen05_fence_after();
     const int64_t row = r0 + warp * 32 + lane;
-    for (int cb = 0; cb < 128; cb += 8) {
+    for (int cb = 0; cb < BN; cb += 8) {
         float acc[8];
         tmem_ld8(tmem_addr(taddr, warp * 32, cb), acc);
         if (row < rows) {
@@ -300,7 +315,7 @@ __global__ void __launch_bounds__(128) k_pre_tc(HsnwModel m, const float* z, con
     }
     tcgen05_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(taddr, 128);
+    if (warp == 0) tmem_dealloc(taddr, BN);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1391,9 +1406,15 @@ extern "C" int hsnw_front_projection(const HsnwModel* model, const float* z, con
         const int Kp = (model->d + model->dc + 15) & ~15;
         const size_t shared = static_cast<size_t>(2) * (Kp / 8) * 128 * 16;
         if (shared <= hsnw_max_shared() - 4096) {
-            const dim3 grid(static_cast<unsigned>((rows + 127) / 128), static_cast<unsigned>((model->H + 127) / 128));
+            const unsigned row_tiles = static_cast<unsigned>((rows + 127) / 128);
             hsnw_profile_mark(HSNW_K_PRE, static_cast<cudaStream_t>(stream));
-            k_pre_tc<<<grid, 128, shared, static_cast<cudaStream_t>(stream)>>>(*model, z, ctx, rows, out, g_pre_status);
+            if (row_tiles * ((model->H + 127) / 128) >= 64) {
+                const dim3 grid(row_tiles, static_cast<unsigned>((model->H + 127) / 128));
+                k_pre_tc<128><<<grid, 128, shared, static_cast<cudaStream_t>(stream)>>>(*model, z, ctx, rows, out, g_pre_status);
+            } else {   // few rows (a serving step): narrow tiles, four times the blocks
+                const dim3 grid(row_tiles, static_cast<unsigned>((model->H + 31) / 32));
+                k_pre_tc<32><<<grid, 128, shared, static_cast<cudaStream_t>(stream)>>>(*model, z, ctx, rows, out, g_pre_status);
+            }
             return hsnw_check_launch("front_projection");
         }
     }
@@ -1520,7 +1541,7 @@ extern "C" int hsnw_stream_continue(const HsnwModel* model, const HsnwForward* i
 
 void hsnw_forward_set_attributes() {
     const struct { const void* f; const char* n; } ks[] = {
-        {reinterpret_cast<const void*>(k_init), "init"}, {reinterpret_cast<const void*>(k_pre_tc), "pre_tc"},
+        {reinterpret_cast<const void*>(k_init), "init"}, {reinterpret_cast<const void*>(k_pre_tc<128>), "pre_tc"}, {reinterpret_cast<const void*>(k_pre_tc<32>), "pre_tc32"},
         {reinterpret_cast<const void*>(k_front), "front"},
         {reinterpret_cast<const void*>(k_row), "row"}, {reinterpret_cast<const void*>(k_unit), "unit"},
         {reinterpret_cast<const void*>(k_unit_tc<32>), "unit_tc"},
