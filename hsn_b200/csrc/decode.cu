@@ -27,7 +27,8 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 }
 
 // out[r, c] = f(sum_k x[r, k] w[c, k] + b[c]); x = [in0 | in1] (in1 may be null: d1 = 0)
-template <bool GELU>
+// BN: the columns of a block's tile (128; 32 when there are few rows, so that a serving step still fills the SMs)
+template <bool GELU, int BN>
 __global__ void __launch_bounds__(128) k_linear_tc(const float* in0, int d0, const float* in1, int d1, const float* w, const float* bias,
                                                    int64_t rows, int n_out, float* out, int* status) {
     extern __shared__ __align__(16) unsigned char dyn[];
@@ -36,16 +37,16 @@ __global__ void __launch_bounds__(128) k_linear_tc(const float* in0, int d0, con
     const int K = d0 + d1;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int64_t r0 = static_cast<int64_t>(blockIdx.x) * 128;
-    const int c0 = blockIdx.y * 128;
+    const int c0 = blockIdx.y * BN;
     uint4* As = reinterpret_cast<uint4*>(dyn);
     uint4* Bs = As + (kChunk / 8) * 128;
     if (tid == 0) mbar_init(&bar, 1);
-    if (warp == 0) tmem_alloc(&tmem_slot, 128);
+    if (warp == 0) tmem_alloc(&tmem_slot, BN);
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t taddr = tmem_slot;
-    const uint32_t idesc = umma_idesc_bf16(128, 128);
+    const uint32_t idesc = umma_idesc_bf16(128, BN);
     int phase = 0;
     for (int k0 = 0; k0 < K; k0 += kChunk, ++phase) {
         const int kc_n = min(kChunk, ((K - k0) + 15) & ~15) >> 3;   // planes of this chunk (whole K = 16 steps)
@@ -62,7 +63,12 @@ __global__ void __launch_bounds__(128) k_linear_tc(const float* in0, int d0, con
                 v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
             }
             As[idx] = make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
+        }
+        for (int idx = tid; idx < kc_n * BN; idx += 128) {
+            const int r = idx % BN, kc = idx / BN;
+            const int k = k0 + kc * 8;
             const int col = c0 + r;
+            float v[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] = 0.0f;
             if (col < n_out && k < K) {
@@ -76,14 +82,14 @@ __global__ void __launch_bounds__(128) k_linear_tc(const float* in0, int d0, con
         __syncthreads();
         if (tid < 32) {   // the whole first warp, converged after the barrier: one elected lane issues
             tcgen05_fence_after();
-            umma_chain(taddr, umma_desc(As, 128), umma_desc(Bs, 128), idesc, kc_n >> 1, umma_kstep(128), umma_kstep(128), k0 > 0);
+            umma_chain(taddr, umma_desc(As, 128), umma_desc(Bs, BN), idesc, kc_n >> 1, umma_kstep(128), umma_kstep(BN), k0 > 0);
             umma_commit(&bar);
         }
         mbar_wait(&bar, phase & 1, status);   // the products have read the operands: the next chunk may be staged
         tcgen05_fence_after();
     }
     const int64_t row = r0 + warp * 32 + lane;
-    for (int cb = 0; cb < 128; cb += 8) {
+    for (int cb = 0; cb < BN; cb += 8) {
         float acc[8];
         tmem_ld8(tmem_addr(taddr, warp * 32, cb), acc);
         if (row < rows) {
@@ -100,7 +106,7 @@ __global__ void __launch_bounds__(128) k_linear_tc(const float* in0, int d0, con
     }
     tcgen05_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(taddr, 128);
+    if (warp == 0) tmem_dealloc(taddr, BN);
 }
 
 // fp32 products: a block takes 8 rows (staged in shared memory), a warp an output at a time with its lanes
@@ -169,12 +175,21 @@ extern "C" int hsnw_window_decode(const HsnwDecoder* dec, const float* qs, const
         const size_t shared = static_cast<size_t>(2) * (kChunk / 8) * 128 * 16;
         const unsigned row_tiles = static_cast<unsigned>((rows + 127) / 128);
         hsnw_profile_mark(HSNW_K_DECODE, stream);
-        k_linear_tc<true><<<dim3(row_tiles, (dec->H + 127) / 128), 128, shared, stream>>>(qs, dec->d_q, us, dec->d_u, dec->w1, dec->b1, rows,
-                                                                                          dec->H, hidden, status);
+        // few rows (a serving step): 32-column tiles, four times the blocks
+        if (row_tiles * ((dec->H + 127) / 128) >= 64)
+            k_linear_tc<true, 128><<<dim3(row_tiles, (dec->H + 127) / 128), 128, shared, stream>>>(qs, dec->d_q, us, dec->d_u, dec->w1, dec->b1,
+                                                                                                   rows, dec->H, hidden, status);
+        else
+            k_linear_tc<true, 32><<<dim3(row_tiles, (dec->H + 31) / 32), 128, shared, stream>>>(qs, dec->d_q, us, dec->d_u, dec->w1, dec->b1, rows,
+                                                                                                dec->H, hidden, status);
         if (int rc = hsnw_check_launch("window_decode")) return rc;
         hsnw_profile_mark(HSNW_K_DECODE, stream);
-        k_linear_tc<false><<<dim3(row_tiles, (dec->V + 127) / 128), 128, shared, stream>>>(hidden, dec->H, nullptr, 0, dec->w2, dec->b2, rows,
-                                                                                           dec->V, logits, status);
+        if (row_tiles * ((dec->V + 127) / 128) >= 64)
+            k_linear_tc<false, 128><<<dim3(row_tiles, (dec->V + 127) / 128), 128, shared, stream>>>(hidden, dec->H, nullptr, 0, dec->w2, dec->b2,
+                                                                                                    rows, dec->V, logits, status);
+        else
+            k_linear_tc<false, 32><<<dim3(row_tiles, (dec->V + 31) / 32), 128, shared, stream>>>(hidden, dec->H, nullptr, 0, dec->w2, dec->b2, rows,
+                                                                                                 dec->V, logits, status);
         return hsnw_check_launch("window_decode");
     }
     const unsigned blocks = static_cast<unsigned>((rows + 7) / 8);
@@ -189,7 +204,9 @@ extern "C" int hsnw_window_decode(const HsnwDecoder* dec, const float* qs, const
 }
 
 void hsnw_decode_set_attributes() {
-    if (!hsnw_opt_in(reinterpret_cast<const void*>(k_linear_tc<true>), "linear_tc<gelu>")
-        || !hsnw_opt_in(reinterpret_cast<const void*>(k_linear_tc<false>), "linear_tc"))
+    if (!hsnw_opt_in(reinterpret_cast<const void*>(k_linear_tc<true, 128>), "linear_tc<gelu>")
+        || !hsnw_opt_in(reinterpret_cast<const void*>(k_linear_tc<false, 128>), "linear_tc")
+        || !hsnw_opt_in(reinterpret_cast<const void*>(k_linear_tc<true, 32>), "linear_tc<gelu, 32>")
+        || !hsnw_opt_in(reinterpret_cast<const void*>(k_linear_tc<false, 32>), "linear_tc<32>"))
         hsnw_attribute_failed();
 }
