@@ -283,6 +283,53 @@ def run_reference(args, c: dict, name: str) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_side_reference(args, c: dict, name: str) -> None:
+    """`--impl reference` for the side configurations `units` and `scorer`: the numpy restatement of the pass
+    (forward + backward, bf16 rounding emulated) on a sample of the workload, on the host's cores."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    rng = np.random.default_rng(0)
+    f = lambda *shape, scale=1.0: (rng.standard_normal(shape) * scale).astype(np.float32)  # noqa: E731
+    if name == "units":
+        from oracle import units_oracle as U
+
+        n, M, d, H = 4096, c["M"], c["d"], c["H"]
+        bank = [f(M, 4 * d, H, scale=(4 * d) ** -0.5), f(M, H, scale=0.3), f(M, H, d, scale=H**-0.5), f(M, d, scale=0.3)]
+        v, cot, idx = f(n, 4 * d), f(n, d), rng.integers(0, M, n)
+        unit, sample = "pairs/s", f"{n} of the window's pairs per step"
+
+        def step():
+            _, pre = U.forward_grouped(v, idx, *bank, bf16=True)
+            U.backward_grouped(v, idx, *bank, pre, cot, bf16=True)
+            return n
+    else:
+        from oracle import scorer_oracle as SO
+
+        n, N, d, M, S = 64, c["N"], c["d"], c["M"], c["S"]
+        weight, bias = f(M, 3 * d + 1 + S, scale=0.2), f(M, scale=0.3)
+        feats = [f(n, d), f(n, d), f(n, N, d), rng.integers(0, 300, (n, N)), f(n, N, S)]
+        cot = f(n, N, M)
+        unit, sample = "cells/s", f"{n} of the window's positions per step"
+
+        def step():
+            SO.scorer_logits(weight, bias, *feats, 100.0, bf16=True)
+            SO.scorer_logits_backward(weight, *feats, 100.0, cot, bf16=True)
+            return n * N
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    done = sum(step() for _ in range(args.steps))
+    sec = time.perf_counter() - t0
+    value = done / sec
+    metric = "grouped unit pass pairs/s (forward + backward)" if name == "units" else "scorer logits cells/s (forward + weight gradients)"
+    print(json.dumps({
+        "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 with bf16 rounding emulated", "data": "synthetic", "config": {"workload": WORKLOADS[name], "sample": sample},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": blas_threads(), "kind": "port", "sample": sample + ", numpy oracle"},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}), flush=True)  # fmt: skip
+
+
 def dist_setup():
     """(world, rank, local rank, device) with the NCCL process group up when launched by torchrun."""
     import torch
@@ -1078,14 +1125,15 @@ def main() -> None:
         if args.steps == 100:
             args.steps = 20
         run_decoder(args, c, args.config)
-    elif c.get("units"):
+    elif c.get("units") or c.get("scorer"):
         if args.steps == 100:
             args.steps = 20
-        run_units(args, c, args.config)
-    elif c.get("scorer"):
-        if args.steps == 100:
-            args.steps = 20
-        run_scorer(args, c, args.config)
+        if args.impl == "reference":
+            run_side_reference(args, c, args.config)
+        elif c.get("units"):
+            run_units(args, c, args.config)
+        else:
+            run_scorer(args, c, args.config)
     elif c.get("trainer"):
         if args.steps == 100:
             args.steps = 20 if args.impl == "ours" else 5
