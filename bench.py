@@ -110,10 +110,10 @@ def kernel_bytes_per_row_position(c: dict) -> dict[str, int]:
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of each kernel of the c2
 # workload, from the ncu captures summarised in profiles/rows_kernels_c2.md (the per-row cluster
 # kernels) and profiles/phases_kernels_c2_dram.md (the phase kernels).
-NCU_TRAFFIC_SOURCE = ("ncu capture of bench.py --steps 1 --warmup 3 at the kernels of commit 59d6e77 "
-                      "(profiles/rows_kernels_c2.md); later changes reorder requests and stores, not bytes")
+NCU_TRAFFIC_SOURCE = ("ncu capture of bench.py --steps 1 --warmup 3 at the kernels of commit 9acb6c0 "
+                      "(profiles/rows_kernels_c2.md)")
 NCU_TRAFFIC_PER_LAUNCH: dict[str, dict[str, float]] = {
-    "c2": {"rows_fwd": 784.5e6, "rows_bwd": 227.4e6, "pre": 4.6e6, "front": 2.798e6, "row": 1.375e6, "unit": 3.419e6, "update": 0.526e6, "mid": 2.254e6, "tail_head": 1.703e6},
+    "c2": {"rows_fwd": 783.8e6, "rows_bwd": 227.0e6, "pre": 4.6e6, "front": 2.798e6, "row": 1.375e6, "unit": 3.419e6, "update": 0.526e6, "mid": 2.254e6, "tail_head": 1.703e6},
 }
 
 
