@@ -55,7 +55,10 @@ CONFIGS["decode"] = dict(rows=32 * 256, d=64, H=512, V=256, decoder=True)
 CONFIGS["units"] = dict(pairs=32 * 256 * 8, M=8, d=64, H=512, units=True)
 # the replay's scorer logits (not the headline): every cell of every position of the c2 window, forward and backward
 CONFIGS["scorer"] = dict(R=32 * 256, N=256, d=64, M=8, S=9, scorer=True)
+# the end of the replay's cell pass (not the headline): every slot of the c2 window, forward and backward
+CONFIGS["tail"] = dict(slots=32 * 256 * 8, d=64, tail=True)
 WORKLOADS = {
+    "tail": "the replay's W_out + candidate norm + weighted tanh over a window's 65,536 slots (d 64), bf16 products, forward + backward",
     "scorer": "the replay's scorer logits over a window's 8192 positions x 256 cells (d 64, 8 units, 9 scalars), bf16 products, forward + weight gradients",
     "units": "the replay's grouped unit pass over a window's 65,536 pairs: 8 units 256 -> 512 -> 64, bf16 products, forward + backward",
     "decode": "the decoder D([q; u]) over a window's 8192 rows: 128 -> 512 -> 256, bf16 products",
@@ -284,7 +287,7 @@ def run_reference(args, c: dict, name: str) -> None:
 
 
 def run_side_reference(args, c: dict, name: str) -> None:
-    """`--impl reference` for the side configurations `units` and `scorer`: the numpy restatement of the pass
+    """`--impl reference` for the side configurations `units`, `scorer` and `tail`: the numpy restatement of the pass
     (forward + backward, bf16 rounding emulated) on a sample of the workload, on the host's cores."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
@@ -301,6 +304,17 @@ def run_side_reference(args, c: dict, name: str) -> None:
         def step():
             _, pre = U.forward_grouped(v, idx, *bank, bf16=True)
             U.backward_grouped(v, idx, *bank, pre, cot, bf16=True)
+            return n
+    elif name == "tail":
+        from oracle import tail_oracle as TO
+
+        n, d = 16384, c["d"]
+        x, alpha, w, g, cot = f(n, d, scale=0.6), np.ones(n, np.float32), f(d, d, scale=d**-0.5), 1.0 + f(d, scale=0.2), f(n, d)
+        unit, sample = "slots/s", f"{n} of the window's slots per step"
+
+        def step():
+            _, y = TO.forward_tail(x, alpha, w, g, bf16=True)
+            TO.backward_tail(x, alpha, w, g, y, cot, bf16=True)
             return n
     else:
         from oracle import scorer_oracle as SO
@@ -321,7 +335,7 @@ def run_side_reference(args, c: dict, name: str) -> None:
     done = sum(step() for _ in range(args.steps))
     sec = time.perf_counter() - t0
     value = done / sec
-    metric = "grouped unit pass pairs/s (forward + backward)" if name == "units" else "scorer logits cells/s (forward + weight gradients)"
+    metric = {"units": "grouped unit pass pairs/s (forward + backward)", "tail": TAIL_METRIC}.get(name, "scorer logits cells/s (forward + weight gradients)")
     print(json.dumps({
         "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": sec / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -1035,6 +1049,96 @@ def run_scorer(args, c: dict, name: str) -> None:
         "cpu_baseline": cpu, "clocks": clocks_summary(clock_lines, 0)}))  # fmt: skip
 
 
+TAIL_METRIC = "replay tail slots/s (forward + backward)"
+
+
+def run_tail(args, c: dict, name: str) -> None:
+    """`--config tail`: `hsnw_tail_forward` + `hsnw_tail_backward` over the benchmark window's slots; a step = both.
+    Beside it the CPU restatement on a sample of the slots, and the reference's three lines in PyTorch on the same
+    device."""
+    import torch
+
+    from hsn_b200.kernels.tail import tail_backward, tail_forward
+    from hsn_b200.window import launch_profile
+
+    world, rank, local, dev = dist_setup()
+    P, d = c["slots"], c["d"]
+    gen = torch.Generator(device=dev).manual_seed(0)
+    f = lambda *shape, scale=1.0: torch.randn(*shape, generator=gen, device=dev) * scale  # noqa: E731
+    x = f(P, d, scale=0.6).to(torch.bfloat16)
+    alpha = (torch.rand(P, generator=gen, device=dev) > 0.05).float()
+    w, g, cot = f(d, d, scale=d**-0.5), 1.0 + f(d, scale=0.2), f(P, d)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # the pass's tensors (76 MB) fit L2: flushed between steps
+    kept: dict = {}
+
+    def step(i):
+        flush.zero_()
+        kept["c"], kept["y"] = tail_forward(x, alpha, w, g)
+        kept["grads"] = tail_backward(x, alpha, w, g, kept["y"], cot)
+
+    for i in range(max(3, args.warmup)):
+        step(i)
+    clock_lines: list = []
+    stop = threading.Event()
+    threading.Thread(target=sample_clocks, args=(stop, clock_lines), daemon=True).start()
+    fwd_ms = bwd_ms = 0.0
+    for i in range(5):   # the calls are tens of microseconds: the mean of five profiled steps
+        with launch_profile() as prof:
+            step(i)
+        fwd_ms += prof.ms.get("tail_fwd", 0.0) / 5
+        bwd_ms += prof.ms.get("tail_bwd", 0.0) / 5
+    ms_total, each = timed_steps(step, args.steps, torch.cuda.synchronize)
+    stop.set()
+    lin = torch.nn.Linear(d, d, bias=False, device=dev)
+    norm = torch.nn.RMSNorm(d, eps=1e-6, device=dev)
+
+    def torch_step(i):
+        flush.zero_()
+        xr, ar = x.clone().requires_grad_(True), alpha.clone().requires_grad_(True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            y = lin(xr).to(torch.float32)
+        torch.tanh(ar[:, None] * norm(y)).backward(cot)
+        lin.weight.grad = norm.weight.grad = None
+
+    for i in range(3):
+        torch_step(i)
+    torch_total, torch_each = timed_steps(torch_step, max(3, args.steps // 4), torch.cuda.synchronize)
+    cpu = None
+    if not args.no_cpu_baseline:
+        from oracle import tail_oracle as TO
+
+        n = 16384
+        hx, ha, hw, hg, hc = (t.float().cpu().numpy() for t in (x[:n], alpha[:n], w, g, cot[:n]))
+        t0 = time.perf_counter()
+        reps = 0
+        while time.perf_counter() - t0 < 10.0:
+            _, hy = TO.forward_tail(hx, ha, hw, hg, bf16=True)
+            TO.backward_tail(hx, ha, hw, hg, hy, hc, bf16=True)
+            reps += 1
+        cpu = {"value": reps * n / (time.perf_counter() - t0), "unit": "slots/s", "cores": blas_threads(), "kind": "port",
+               "sample": f"{reps} passes of forward + backward over {n} of the window's slots (numpy restatement, bf16 rounding emulated)"}
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    fwd_bytes = float(P) * (2 * d + 4 + 8 * d)            # unit_out (bf16), alpha read; y, c written
+    bwd_bytes = float(P) * (2 * d + 4 + 8 * d + 2 * d + 4)   # unit_out, alpha, y, d_c read; d_unit_out (bf16), d_alpha written
+    kernel_ms = fwd_ms + bwd_ms
+    achieved = (fwd_bytes + bwd_bytes) / (kernel_ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": TAIL_METRIC, "value": P / (kernel_ms * 1e-3), "unit": "slots/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": kernel_ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16 products, f32 norm and tanh", "data": "synthetic",
+        "config": {"workload": WORKLOADS[name], "l2": "256 MB written between steps (the pass's tensors fit L2)",
+                   "forward_ms": fwd_ms, "backward_ms": bwd_ms, "step_ms_with_flush_and_host": spread(each),
+                   "torch_linear_rmsnorm_tanh_autocast_autograd_ms_with_flush": spread(torch_each)},
+        "gpu_launches": 3 * args.steps,
+        "roofline": {"bound": "hbm", "kernel": "k_tail_fwd + k_tail_bwd", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": None, "peak_source": "measured" if peaks else "fallback",
+                     "forward": {"achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9, "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak},
+                     "backward": {"achieved": bwd_bytes / (bwd_ms * 1e-3) / 1e9, "frac": bwd_bytes / (bwd_ms * 1e-3) / 1e9 / peak},
+                     "how": "per slot 10 d + 4 bytes forward (unit_out as bf16, alpha, y and c written) and 12 d + 8 backward / the calls' event time, mean of five profiled steps"},
+        "cpu_baseline": cpu, "clocks": clocks_summary(clock_lines, 0)}))  # fmt: skip
+
+
 def run_trainer_sharded(args, c: dict, name: str, world: int, rank: int, dev) -> None:
     """`--config adamw --gpus N`: the same parameter vector replicated on N ranks, a step = the gradient exchange
     and the AdamW step as ONE kernel per rank over peer memory (`ShardedAdamW`: reduce-scatter, step, all-gather),
@@ -1125,13 +1229,15 @@ def main() -> None:
         if args.steps == 100:
             args.steps = 20
         run_decoder(args, c, args.config)
-    elif c.get("units") or c.get("scorer"):
+    elif c.get("units") or c.get("scorer") or c.get("tail"):
         if args.steps == 100:
             args.steps = 20
         if args.impl == "reference":
             run_side_reference(args, c, args.config)
         elif c.get("units"):
             run_units(args, c, args.config)
+        elif c.get("tail"):
+            run_tail(args, c, args.config)
         else:
             run_scorer(args, c, args.config)
     elif c.get("trainer"):

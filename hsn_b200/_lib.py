@@ -127,6 +127,10 @@ class HsnwScorer(Structure):
     ]
 
 
+class HsnwTail(Structure):
+    _fields_ = [("d", c_int32), ("prod_bf16", c_int32), ("norm_eps", c_float), ("reserved", c_int32), ("w_out", c_void_p), ("norm_weight", c_void_p)]  # fmt: skip
+
+
 class HsnwPrologue(Structure):
     _fields_ = (
         [(n, c_int32) for n in PROLOGUE_INTS]
@@ -172,6 +176,10 @@ SYMBOLS: dict[str, tuple[object, list[object]]] = {
                                    c_int64, c_void_p]),
     "hsnw_scorer_logits_backward": (c_int, [POINTER(HsnwScorer), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
                                             c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "hsnw_tail_scratch_bytes": (c_int64, [POINTER(HsnwTail), c_int64]),
+    "hsnw_tail_forward": (c_int, [POINTER(HsnwTail), c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
+    "hsnw_tail_backward": (c_int, [POINTER(HsnwTail), c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_void_p, c_int64, c_void_p]),
     "hsnw_units_scratch_bytes": (c_int64, [POINTER(HsnwUnits), c_int64, c_int]),
     "hsnw_units_forward": (c_int, [POINTER(HsnwUnits), c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "hsnw_units_backward": (c_int, [POINTER(HsnwUnits), c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -30,6 +30,10 @@ inputs and outputs of every function on the window path as ``.npz`` files:
 * ``decode_*.npz``      ``HSN._decode`` (``python/hsn/model/hsn.py:2374``): the decoder on seeded ``q``, ``u``.
 * ``snapshot_*.npz``    ``CellGraphState.snapshot`` (``python/hsn/model/state.py:363``): seeded states, their metas
                         and the reference's digests.
+* ``replay_*.npz``      ``PDGCell.replay_sparse`` (``python/hsn/model/cell.py:655-734``) as the split window's replay
+                        calls it (``python/hsn/train/split.py:657``), on that call's own arguments: inputs, results,
+                        the record, ``W_out``'s input and its gradient, and autograd's gradients of the inputs and of
+                        every cell parameter for seeded cotangents of ``(c, b)``.
 * ``chain_*.npz``       two chained windows against the unsplit window of twice the length: the
                         carried state forward, the state cotangent ``(A, R)`` backward.
 
@@ -762,6 +766,76 @@ def make_scorer(root: Path) -> None:
         print("scorer", name, tuple(logits.shape), logits.dtype, "S", S)
 
 
+def make_replay(root: Path) -> None:
+    """``PDGCell.replay_sparse`` (``python/hsn/model/cell.py:655-734``) on the arguments the split window's replay
+    gives it (``python/hsn/train/split.py:657``), taken by a wrapper around the bound method while a whole window runs:
+    the call is made once more on leaf copies of ``u``, ``eps`` and the slot weights, with seeded cotangents of
+    ``(c, b)``, so that the gradients written here are this function's alone. float32, float32 with slots the budget
+    cut, and under ``torch.autocast("cpu", dtype=torch.bfloat16)``."""
+    import dataclasses
+
+    import torch
+
+    SG = "[summary,eps,router]"
+    cases = {
+        "f32": dict(shape=dict(B=3, T=8, N=64, d=32, K=4, H=128, M=4, D=3), extra=("model.age_max=3",), precision="fp32"),
+        "cut_f32": dict(shape=dict(B=3, T=10, N=12, d=16, K=4, H=24, M=3, D=3), extra=("model.budget=0.06",), precision="fp32"),
+        "bf16": dict(shape=dict(B=3, T=8, N=64, d=32, K=4, H=128, M=4, D=3), extra=("model.age_max=3",), precision="bf16"),
+        "wide_bf16": dict(shape=dict(B=2, T=6, N=32, d=64, K=8, H=128, M=2, D=4), extra=("model.age_max=1000000",), precision="bf16"),
+    }  # fmt: skip
+    for name, case in cases.items():
+        shape = case["shape"]
+        cfg = _cfg(root, **shape, fd=SG, extra=case["extra"], precision=case["precision"])
+        model = _model(cfg, torch.float32, 0.3)
+        tokens, ctx, reset = _inputs(cfg, shape["B"], shape["T"], 0.15)
+        state = model.init_state(shape["B"])
+        cell = model.cell
+        real = cell.replay_sparse
+        out: dict[str, np.ndarray] = {}
+
+        def wrapper(u, eps, h_read, sel, *, record=None, real=real, cell=cell, out=out):
+            leaves = [t.detach().clone().requires_grad_(True) for t in (u, eps, sel.alpha)]
+            seen: dict[str, torch.Tensor] = {}
+            hook = cell.W_out.register_forward_hook(lambda mod, inp, res: seen.update(unit_out=inp[0]))
+            try:
+                rec: dict[str, torch.Tensor] = {}
+                c, b = real(leaves[0], leaves[1], h_read, dataclasses.replace(sel, alpha=leaves[2]), record=rec)
+            finally:
+                hook.remove()
+            gen = torch.Generator().manual_seed(51)
+            d_c = torch.randn(c.shape, generator=gen).to(c.dtype)
+            d_b = torch.randn(b.shape, generator=gen).to(b.dtype)
+            params = dict(cell.named_parameters())
+            grads = torch.autograd.grad([c, b], [*leaves, seen["unit_out"], *params.values()], [d_c, d_b], allow_unused=True,
+                                        retain_graph=True)   # the window caches casts of the weights: the real call below shares them
+            f32 = torch.float32
+            out.update(u=_np(u), eps=_np(eps), h_read=_np(h_read), cells=sel.cell_idx.numpy(), units=sel.unit_idx.numpy(),
+                       valid=sel.valid.numpy(), alpha=_np(sel.alpha), c=_np(c), b=_np(b), d_c=_np(d_c), d_b=_np(d_b),
+                       unit_out=_np(seen["unit_out"].to(f32)), d_u=_np(grads[0]), d_eps=_np(grads[1]), d_alpha=_np(grads[2]),
+                       d_unit_out=_np(grads[3].to(f32)), cand_eps=np.array(float(cell.cand_norm.eps)))  # fmt: skip
+            for key, value in rec.items():
+                out["rec_" + key] = _np(value.to(f32))
+            for (key, value), grad in zip(params.items(), grads[4:], strict=True):
+                out["w_" + key] = _np(value)
+                if grad is not None:
+                    out["g_" + key] = _np(grad.to(f32))
+            return real(u, eps, h_read, sel, record=record)
+
+        cell.replay_sparse = wrapper
+        try:
+            if case["precision"] == "bf16":
+                with torch.autocast("cpu", dtype=torch.bfloat16):
+                    _run_window(root, cfg, model, torch.float32, tokens, ctx, reset, state)
+            else:
+                _run_window(root, cfg, model, torch.float32, tokens, ctx, reset, state)
+        finally:
+            del cell.replay_sparse
+        assert out, "the window never reached the replay"
+        np.savez_compressed(HERE / f"replay_{name}.npz", **out)
+        print("replay", name, {k: v.shape for k, v in out.items() if k in ("unit_out", "c", "rec_y", "g_W_out.weight")},
+              "valid", float(out["valid"].mean()))  # fmt: skip
+
+
 def make_snapshot(root: Path) -> None:
     """``CellGraphState.snapshot`` (``python/hsn/model/state.py:363``) and ``pack_cell_state``
     (``python/hsn/train/checkpoint.py:260``): seeded states in float32 and bfloat16, their metas and the
@@ -806,6 +880,7 @@ def main() -> None:
         "select": make_select, "update": make_update, "recurrence": make_recurrence,
         "windows": make_windows, "bf16": make_windows_bf16, "prologue": make_prologue, "chain": make_chain,
         "sweep": make_sweep, "snapshot": make_snapshot, "decode": make_decode, "units": make_units, "scorer": make_scorer,
+        "replay": make_replay,
     }  # fmt: skip
     for key, fn in steps.items():
         if not args.only or key in args.only.split(","):

@@ -408,3 +408,38 @@ def test_scorer_logits_equal_the_reference(name: str, tol: float) -> None:
             assert np.array_equal(got, z[key]), key
         else:
             np.testing.assert_allclose(got, z[key], rtol=0, atol=tol * float(np.abs(z[key]).max()), err_msg=key)
+
+
+def _tail_case(name: str):
+    z = load_golden(f"replay_{name}")
+    d = z["unit_out"].shape[-1]
+    flat = lambda key: z[key].reshape(-1, d)  # noqa: E731
+    args = (flat("unit_out"), z["alpha"].reshape(-1), z["w_W_out.weight"], z["w_cand_norm.weight"])
+    want = dict(c=flat("c"), y=flat("rec_y"), d_unit_out=flat("d_unit_out"), d_alpha=z["d_alpha"].reshape(-1),
+                d_w_out=z["g_W_out.weight"], d_cand_w=z["g_cand_norm.weight"])  # fmt: skip
+    return z, args, flat("d_c"), want
+
+
+@pytest.mark.parametrize("name", ["f32", "cut_f32", "bf16", "wide_bf16"])
+def test_replay_tail_equals_the_reference(name: str) -> None:
+    """``W_out``, the candidate norm and the weighted ``tanh`` of ``replay_sparse`` with autograd's gradients, on the
+    values the reference's own replay held inside a split window: float32 (also with slots the budget cut, whose
+    weight is zero) and under bf16 autocast, where ``y`` and the linear's two gradients equal the reference's to the
+    bit and the float32 parts to rounding."""
+    from oracle import tail_oracle as T
+
+    z, args, d_c, want = _tail_case(name)
+    bf = "bf16" in name
+    eps = float(z["cand_eps"])
+    c, y = T.forward_tail(*args, cand_eps=eps, bf16=bf)
+    assert np.array_equal(y, want["y"])
+    grads = T.backward_tail(*args, want["y"], d_c, cand_eps=eps, bf16=bf)
+    got = dict(c=c, d_unit_out=grads[0], d_alpha=grads[1], d_w_out=grads[2], d_cand_w=grads[3])
+    for key, value in got.items():
+        assert value.shape == want[key].shape and value.dtype == np.float32, key
+        np.testing.assert_allclose(value, want[key], rtol=0, atol=1e-6 * float(np.abs(want[key]).max()), err_msg=key)
+    if bf:
+        assert np.array_equal(got["d_unit_out"], want["d_unit_out"]) and np.array_equal(got["d_w_out"], want["d_w_out"])
+    if name == "cut_f32":   # a slot the budget cut: weight 0, candidate 0, no gradient into the unit's output
+        cut = ~z["valid"].reshape(-1)
+        assert cut.any() and not np.any(args[1][cut]) and not np.any(c[cut]) and not np.any(grads[0][cut])
