@@ -1,11 +1,13 @@
 // The end of the replay's cell pass over every slot of a window at once, and its backward:
 //   y = W_out(unit_out), pre = RMSNorm_g(y), c = tanh(alpha * pre)      (reference python/hsn/model/cell.py:719-721)
 // with autograd's gradients of unit_out, alpha, W_out.weight and the norm's gain. The slots are independent, so a
-// tile of 64 slots is one block's work: the tile and W_out sit in shared memory, a thread holds 4 slots x d/16
-// columns of the product, the norm's row sums are shuffles over the 16 lanes that share a slot. The pass is bound by
-// the tensors it reads and writes once (y and c are 2 x 4 d bytes a slot, the product 2 d^2 flops); the backward
-// keeps each block's share of d_W_out in registers over all of its tiles and a second kernel adds the blocks' shares
-// in block order, so the sums have the same bits every run.
+// tile of slots is one block's work with the tile and W_out in shared memory. The pass is bound by the tensors it
+// reads and writes once (y and c are 2 x 4 d bytes a slot against 2 d^2 flops), so the products only have to stay out
+// of the way: with bf16 products a warp takes 16 slots through warp-level tensor-core products (mma.sync m16n8k16,
+// fp32 accumulators in registers, where the norm's row sums and the tanh need them: 2 shuffles a row, no round trip
+// through tensor memory for a 64-wide row); in float32 a thread holds 4 slots x d/16 columns on the CUDA cores.
+// The backward keeps each block's share of d_W_out in registers over all of its tiles and a second kernel adds the
+// blocks' shares in a fixed order, so the sums have the same bits every run.
 #include "../../include/hsn_tail_b200.h"
 #include "../../include/hsn_window_b200.h"
 #include "common.cuh"
@@ -18,8 +20,7 @@ namespace {
 using namespace hsnw;
 
 constexpr int kThreads = 256;
-constexpr int kTile = 64;        // slots a tile: 16 thread rows x 4 slots
-constexpr int kSumLanes = 4;     // interleaved partial sums of the final reduction (a fixed order)
+constexpr int kTile = 64;        // slots a tile of the float32 kernels: 16 thread rows x 4 slots
 
 template <int D>
 struct Shape {
@@ -39,32 +40,22 @@ __device__ __forceinline__ float sum16(float v) {   // over the 16 lanes of a ha
 }
 
 // A tile of unit_out as float rows in shared memory; rows beyond the last slot are zero.
-template <int D, bool BF>
-__device__ __forceinline__ void load_tile(float* X, const void* src, int64_t first, int64_t slots, int tid) {
+template <int D>
+__device__ __forceinline__ void load_tile(float* X, const float* src, int64_t first, int64_t slots, int tid) {
     constexpr int XP = Shape<D>::XP, Q = D / 4;
     for (int e = tid; e < kTile * Q; e += kThreads) {
         const int p = e / Q, q = e - p * Q;
         float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        if (first + p < slots) {
-            if constexpr (BF) {
-                const uint2 raw = __ldg(reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(src) + (first + p) * D) + q);
-                v.x = bf16_value(static_cast<uint16_t>(raw.x & 0xffffu));
-                v.y = bf16_value(static_cast<uint16_t>(raw.x >> 16));
-                v.z = bf16_value(static_cast<uint16_t>(raw.y & 0xffffu));
-                v.w = bf16_value(static_cast<uint16_t>(raw.y >> 16));
-            } else {
-                v = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(src) + (first + p) * D) + q);
-            }
-        }
+        if (first + p < slots) v = __ldg(reinterpret_cast<const float4*>(src + (first + p) * D) + q);
         *reinterpret_cast<float4*>(X + p * XP + 4 * q) = v;
     }
 }
 
-template <int D, bool BF>
+template <int D>
 __device__ __forceinline__ void load_weights(float* W, float* G, const float* w_out, const float* gain, int tid) {
     for (int e = tid; e < D * D; e += kThreads) {
         const int j = e / D, k = e - j * D;
-        W[j * Shape<D>::WP + k] = maybe_bf16(__ldg(w_out + e), BF);
+        W[j * Shape<D>::WP + k] = __ldg(w_out + e);
     }
     for (int e = tid; e < D; e += kThreads) G[e] = __ldg(gain + e);
 }
@@ -97,9 +88,9 @@ __device__ __forceinline__ void tile_product(float (&acc)[4][Shape<D>::CPT], con
     }
 }
 
-template <int D, bool BF>
+template <int D>
 __global__ void __launch_bounds__(kThreads)
-k_tail_fwd(const float* __restrict__ w_out, const float* __restrict__ gain, float eps, const void* __restrict__ unit_out,
+k_tail_fwd(const float* __restrict__ w_out, const float* __restrict__ gain, float eps, const float* __restrict__ unit_out,
            const float* __restrict__ alpha, int64_t slots, float* __restrict__ y_out, float* __restrict__ c_out) {
     constexpr int CPT = Shape<D>::CPT, WP = Shape<D>::WP, XP = Shape<D>::XP;
     extern __shared__ __align__(16) float smem[];
@@ -108,8 +99,8 @@ k_tail_fwd(const float* __restrict__ w_out, const float* __restrict__ gain, floa
     float* G = W + D * WP;         // [D]
     const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
     const int64_t first = static_cast<int64_t>(blockIdx.x) * kTile;
-    load_weights<D, BF>(W, G, w_out, gain, tid);
-    load_tile<D, BF>(X, unit_out, first, slots, tid);
+    load_weights<D>(W, G, w_out, gain, tid);
+    load_tile<D>(X, unit_out, first, slots, tid);
     __syncthreads();
     float acc[4][CPT];
     tile_product<D>(acc, X, ty, [&](int k, int c) { return W[(tx + 16 * c) * WP + k]; });
@@ -119,7 +110,6 @@ k_tail_fwd(const float* __restrict__ w_out, const float* __restrict__ gain, floa
         float ss = 0.0f;
 #pragma unroll
         for (int c = 0; c < CPT; ++c) {
-            acc[i][c] = maybe_bf16(acc[i][c], BF);
             ss = fmaf(acc[i][c], acc[i][c], ss);
         }
         ss = sum16(ss);
@@ -137,11 +127,11 @@ k_tail_fwd(const float* __restrict__ w_out, const float* __restrict__ gain, floa
 }
 
 // `partial` [blocks][D D + D]: the block's share of d_W_out, then of the gain's gradient.
-template <int D, bool BF>
+template <int D>
 __global__ void __launch_bounds__(kThreads)
-k_tail_bwd(const float* __restrict__ w_out, const float* __restrict__ gain, float eps, const void* __restrict__ unit_out,
+k_tail_bwd(const float* __restrict__ w_out, const float* __restrict__ gain, float eps, const float* __restrict__ unit_out,
            const float* __restrict__ alpha, const float* __restrict__ y_in, const float* __restrict__ d_c, int64_t slots,
-           void* __restrict__ d_unit_out, float* __restrict__ d_alpha, float* __restrict__ partial) {
+           float* __restrict__ d_unit_out, float* __restrict__ d_alpha, float* __restrict__ partial) {
     constexpr int CPT = Shape<D>::CPT, WP = Shape<D>::WP, XP = Shape<D>::XP;
     extern __shared__ __align__(16) float smem[];
     float* X = smem;                // [kTile][XP] unit_out
@@ -150,7 +140,7 @@ k_tail_bwd(const float* __restrict__ w_out, const float* __restrict__ gain, floa
     float* G = W + D * WP;          // [D]
     float* GS = G + D;              // [16][D] the thread rows' shares of the gain's gradient
     const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
-    load_weights<D, BF>(W, G, w_out, gain, tid);
+    load_weights<D>(W, G, w_out, gain, tid);
     float dw[CPT][CPT];
     float dg[CPT];
 #pragma unroll
@@ -163,7 +153,7 @@ k_tail_bwd(const float* __restrict__ w_out, const float* __restrict__ gain, floa
     for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
         const int64_t first = tile * kTile;
         __syncthreads();   // the previous tile's reads are over; the weights are in place
-        load_tile<D, BF>(X, unit_out, first, slots, tid);
+        load_tile<D>(X, unit_out, first, slots, tid);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int64_t p = first + ty * 4 + i;
@@ -200,7 +190,7 @@ k_tail_bwd(const float* __restrict__ w_out, const float* __restrict__ gain, floa
 #pragma unroll
             for (int c = 0; c < CPT; ++c) {
                 const float dy = rho * scaled[c] - rho * rho * rho * yv[c] * mean;
-                DY[(ty * 4 + i) * XP + tx + 16 * c] = maybe_bf16(dy, BF);
+                DY[(ty * 4 + i) * XP + tx + 16 * c] = dy;
             }
             if (in && tx == 0) d_alpha[p] = da;
         }
@@ -213,11 +203,7 @@ k_tail_bwd(const float* __restrict__ w_out, const float* __restrict__ gain, floa
             const int64_t p = first + ty * 4 + i;
             if (p < slots) {
 #pragma unroll
-                for (int c = 0; c < CPT; ++c) {
-                    const int64_t at = p * D + tx + 16 * c;
-                    if constexpr (BF) static_cast<uint16_t*>(d_unit_out)[at] = bf16_bits(acc[i][c]);
-                    else static_cast<float*>(d_unit_out)[at] = acc[i][c];
-                }
+                for (int c = 0; c < CPT; ++c) d_unit_out[p * D + tx + 16 * c] = acc[i][c];
             }
         }
         // d_W_out[j][k] += sum_p d_y[p][j] unit_out[p][k], j = ty + 16 i, k = tx + 16 c
@@ -251,30 +237,308 @@ k_tail_bwd(const float* __restrict__ w_out, const float* __restrict__ gain, floa
     }
 }
 
-// The blocks' shares added in block order (kSumLanes interleaved sums, then those in order).
+// ---------------------------------------------------------------------------------------------------------------
+// bf16 products: a tile of 128 slots, a warp owns 16 of them.
+
+constexpr int kTileMma = 128;
+
+template <int D>
+struct MmaShape {
+    static constexpr int PB = D + 8;        // pitch of a row of bf16 values: rows 16-byte aligned, fragment loads hit 32 banks
+    static constexpr int PW = PB / 2;       // the same in 32-bit words
+    static constexpr int NT = D / 8;        // 8-column tiles of a row
+    static constexpr int KS = D / 16;       // 16-deep steps of a product over d
+    static constexpr int MT = D / 16;       // 16-row tiles of d_W_out
+    static constexpr int TILES = MT * NT;
+    static constexpr int TPW = (TILES + 7) / 8;   // d_W_out tiles a warp
+    static constexpr size_t fwd_bytes = sizeof(uint32_t) * (kTileMma * PW + D * PW) + sizeof(float) * D;
+    static constexpr size_t bwd_bytes = sizeof(uint32_t) * (2 * kTileMma * PW + D * PW) + sizeof(float) * (D + 8 * D);
+};
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    return static_cast<uint32_t>(bf16_bits(lo)) | (static_cast<uint32_t>(bf16_bits(hi)) << 16);
+}
+
+// c += a b for one 16 x 8 tile: a 16 x 16 (row major fragments), b 16 x 8 (column fragments), bf16 in, float32 sums.
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Four (two) 8 x 8 blocks of bf16 values, each handed out transposed: a lane ends up with the elements [2t][g] and
+// [2t + 1][g] of block i in r[i]. Lane l gives the address of row l % 8 of block l / 8.
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* row) {
+    const uint32_t at = static_cast<uint32_t>(__cvta_generic_to_shared(row));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(at));
+}
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t (&r)[2], const void* row) {
+    const uint32_t at = static_cast<uint32_t>(__cvta_generic_to_shared(row));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(at));
+}
+
+// A tile of unit_out (bf16) into shared memory rows of pitch PB; rows beyond the last slot are zero.
+template <int D>
+__device__ __forceinline__ void load_tile_bf16(uint32_t* Xs, const uint16_t* src, int64_t first, int64_t slots, int tid) {
+    constexpr int PW = MmaShape<D>::PW, Q = D / 8;
+    for (int e = tid; e < kTileMma * Q; e += kThreads) {
+        const int p = e / Q, q = e - p * Q;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (first + p < slots) v = __ldg(reinterpret_cast<const uint4*>(src + (first + p) * D) + q);
+        *reinterpret_cast<uint4*>(Xs + p * PW + 4 * q) = v;
+    }
+}
+
+// acc[nt] = the warp's 16 rows of A (rows r0.. of a tile in shared memory) times B, B(k, n) read as the packed pair
+// (k, k + 1) of row n of Bs: Bs holds the right-hand side with its summed index along a row.
+template <int D>
+__device__ __forceinline__ void warp_product(float (&acc)[MmaShape<D>::NT][4], const uint32_t* As, const uint32_t* Bs, int r0, int g, int t) {
+    constexpr int PW = MmaShape<D>::PW, NT = MmaShape<D>::NT, KS = MmaShape<D>::KS;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[nt][i] = 0.0f;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+        uint32_t a[4];
+        a[0] = As[(r0 + g) * PW + 8 * ks + t];
+        a[1] = As[(r0 + g + 8) * PW + 8 * ks + t];
+        a[2] = As[(r0 + g) * PW + 8 * ks + 4 + t];
+        a[3] = As[(r0 + g + 8) * PW + 8 * ks + 4 + t];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const uint32_t b0 = Bs[(8 * nt + g) * PW + 8 * ks + t];
+            const uint32_t b1 = Bs[(8 * nt + g) * PW + 8 * ks + 4 + t];
+            mma_bf16(acc[nt], a, b0, b1);
+        }
+    }
+}
+
+__device__ __forceinline__ float sum4_lanes(float v) {   // over the 4 lanes that share a row of a fragment
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    return v;
+}
+
+// A lane holds, of row g + 8 h of its warp's 16 rows, the columns 8 nt + 2 t and + 1 in acc[nt][2 h], [2 h + 1].
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+k_tail_fwd_mma(const float* __restrict__ w_out, const float* __restrict__ gain, float eps, const uint16_t* __restrict__ unit_out,
+               const float* __restrict__ alpha, int64_t slots, float* __restrict__ y_out, float* __restrict__ c_out) {
+    constexpr int PW = MmaShape<D>::PW, NT = MmaShape<D>::NT;
+    extern __shared__ __align__(16) uint32_t smem_w[];
+    uint32_t* Xs = smem_w;                  // [kTileMma][PW] unit_out
+    uint32_t* Ws = Xs + kTileMma * PW;      // [D][PW] W_out[j][k]
+    float* G = reinterpret_cast<float*>(Ws + D * PW);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int64_t first = static_cast<int64_t>(blockIdx.x) * kTileMma;
+    for (int e = tid; e < D * D / 2; e += kThreads) {
+        const int j = e / (D / 2), k2 = e - j * (D / 2);
+        const float2 v = __ldg(reinterpret_cast<const float2*>(w_out) + e);
+        Ws[j * PW + k2] = pack_bf16(v.x, v.y);
+    }
+    for (int e = tid; e < D; e += kThreads) G[e] = __ldg(gain + e);
+    load_tile_bf16<D>(Xs, unit_out, first, slots, tid);
+    __syncthreads();
+    float acc[NT][4];
+    warp_product<D>(acc, Xs, Ws, warp * 16, g, t);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int64_t p = first + warp * 16 + g + 8 * h;
+        float ss = 0.0f;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            acc[nt][2 * h] = bf16r(acc[nt][2 * h]);
+            acc[nt][2 * h + 1] = bf16r(acc[nt][2 * h + 1]);
+            ss = fmaf(acc[nt][2 * h], acc[nt][2 * h], ss);
+            ss = fmaf(acc[nt][2 * h + 1], acc[nt][2 * h + 1], ss);
+        }
+        ss = sum4_lanes(ss);
+        const float rho = 1.0f / sqrtf(ss / static_cast<float>(D) + eps);
+        if (p < slots) {
+            const float a = __ldg(alpha + p);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const int j = 8 * nt + 2 * t;
+                const float y0 = acc[nt][2 * h], y1 = acc[nt][2 * h + 1];
+                *reinterpret_cast<float2*>(y_out + p * D + j) = make_float2(y0, y1);
+                *reinterpret_cast<float2*>(c_out + p * D + j) = make_float2(tanhf(a * (y0 * rho * G[j])), tanhf(a * (y1 * rho * G[j + 1])));
+            }
+        }
+    }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+k_tail_bwd_mma(const float* __restrict__ w_out, const float* __restrict__ gain, float eps, const uint16_t* __restrict__ unit_out,
+               const float* __restrict__ alpha, const float* __restrict__ y_in, const float* __restrict__ d_c, int64_t slots,
+               uint16_t* __restrict__ d_unit_out, float* __restrict__ d_alpha, float* __restrict__ partial) {
+    using S = MmaShape<D>;
+    constexpr int PB = S::PB, PW = S::PW, NT = S::NT, MT = S::MT, TILES = S::TILES, TPW = S::TPW;
+    extern __shared__ __align__(16) uint32_t smem_w[];
+    uint32_t* Xs = smem_w;                   // [kTileMma][PW] unit_out
+    uint32_t* DYs = Xs + kTileMma * PW;      // [kTileMma][PW] d_y
+    uint32_t* Wt = DYs + kTileMma * PW;      // [D][PW] Wt[k][j] = W_out[j][k]
+    float* G = reinterpret_cast<float*>(Wt + D * PW);
+    float* GS = G + D;                       // [8][D] the warps' shares of the gain's gradient
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    for (int e = tid; e < D * D / 2; e += kThreads) {
+        const int k = e / (D / 2), j2 = e - k * (D / 2);
+        Wt[k * PW + j2] = pack_bf16(__ldg(w_out + (2 * j2) * D + k), __ldg(w_out + (2 * j2 + 1) * D + k));
+    }
+    for (int e = tid; e < D; e += kThreads) G[e] = __ldg(gain + e);
+    float dw[TPW][4];
+    float dg[NT][2];
+#pragma unroll
+    for (int i = 0; i < TPW; ++i)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) dw[i][c] = 0.0f;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) dg[nt][0] = dg[nt][1] = 0.0f;
+    const int r0 = warp * 16;
+    const int mt = warp % MT;
+    const int64_t tiles = (slots + kTileMma - 1) / kTileMma;
+    for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+        const int64_t first = tile * kTileMma;
+        __syncthreads();   // the previous tile's reads are over; the weights are in place
+        load_tile_bf16<D>(Xs, unit_out, first, slots, tid);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int row = r0 + g + 8 * h;
+            const int64_t p = first + row;
+            const bool in = p < slots;
+            float2 yv[NT], sc[NT];   // sc: the cotangent, then g d_pre
+            float ss = 0.0f;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const int j = 8 * nt + 2 * t;
+                yv[nt] = in ? __ldg(reinterpret_cast<const float2*>(y_in + p * D + j)) : make_float2(0.0f, 0.0f);
+                sc[nt] = in ? __ldg(reinterpret_cast<const float2*>(d_c + p * D + j)) : make_float2(0.0f, 0.0f);
+                ss = fmaf(yv[nt].x, yv[nt].x, ss);
+                ss = fmaf(yv[nt].y, yv[nt].y, ss);
+            }
+            const float a = in ? __ldg(alpha + p) : 0.0f;
+            ss = sum4_lanes(ss);
+            const float rho = 1.0f / sqrtf(ss / static_cast<float>(D) + eps);
+            float da = 0.0f, dot = 0.0f;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const float gj = G[8 * nt + 2 * t + c];
+                    const float yj = c ? yv[nt].y : yv[nt].x;
+                    const float dcj = c ? sc[nt].y : sc[nt].x;
+                    const float pre = yj * rho * gj;
+                    const float cv = tanhf(a * pre);
+                    const float dz = dcj * (1.0f - cv * cv);
+                    da = fmaf(dz, pre, da);
+                    const float dpre = a * dz;
+                    dg[nt][c] = fmaf(dpre * yj, rho, dg[nt][c]);
+                    const float scaled = dpre * gj;
+                    dot = fmaf(yj, scaled, dot);
+                    if (c) sc[nt].y = scaled;
+                    else sc[nt].x = scaled;
+                }
+            }
+            da = sum4_lanes(da);
+            dot = sum4_lanes(dot);
+            const float mean = dot / static_cast<float>(D);
+            const float rho3 = rho * rho * rho;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+                DYs[row * PW + 4 * nt + t] = pack_bf16(rho * sc[nt].x - rho3 * yv[nt].x * mean, rho * sc[nt].y - rho3 * yv[nt].y * mean);
+            if (in && t == 0) d_alpha[p] = da;
+        }
+        __syncthreads();   // the tile and every row of d_y are in place
+        {   // d_unit_out = d_y W_out on the warp's own rows
+            float acc[NT][4];
+            warp_product<D>(acc, DYs, Wt, r0, g, t);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int64_t p = first + r0 + g + 8 * h;
+                if (p < slots) {
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+                        *reinterpret_cast<uint32_t*>(d_unit_out + p * D + 8 * nt + 2 * t) = pack_bf16(acc[nt][2 * h], acc[nt][2 * h + 1]);
+                }
+            }
+        }
+        // d_W_out[j][k] += sum_p d_y[p][j] unit_out[p][k]: both operands are stored with p along the rows, so both
+        // fragments come transposed; the warp's tiles share the rows 16 mt.. of d_W_out
+        const uint16_t* dy16 = reinterpret_cast<const uint16_t*>(DYs);
+        const uint16_t* x16 = reinterpret_cast<const uint16_t*>(Xs);
+#pragma unroll 2
+        for (int ks = 0; ks < kTileMma / 16; ++ks) {
+            uint32_t a[4];
+            ldmatrix_x4_trans(a, dy16 + (16 * ks + (lane & 7) + 8 * (lane >> 4)) * PB + 16 * mt + 8 * ((lane >> 3) & 1));
+#pragma unroll
+            for (int i = 0; i < TPW; ++i) {
+                const int at = warp + 8 * i;
+                if (at < TILES) {
+                    uint32_t b[2];
+                    ldmatrix_x2_trans(b, x16 + (16 * ks + (lane & 7) + 8 * ((lane >> 3) & 1)) * PB + 8 * (at / MT));
+                    mma_bf16(dw[i], a, b[0], b[1]);
+                }
+            }
+        }
+    }
+    float* mine = partial + static_cast<int64_t>(blockIdx.x) * (D * D + D);
+#pragma unroll
+    for (int i = 0; i < TPW; ++i) {
+        const int at = warp + 8 * i;
+        if (at < TILES) {
+            const int m = 16 * mt + g, n = 8 * (at / MT) + 2 * t;
+            mine[m * D + n] = dw[i][0];
+            mine[m * D + n + 1] = dw[i][1];
+            mine[(m + 8) * D + n] = dw[i][2];
+            mine[(m + 8) * D + n + 1] = dw[i][3];
+        }
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            float v = dg[nt][c];
+            v += __shfl_xor_sync(0xffffffffu, v, 4);
+            v += __shfl_xor_sync(0xffffffffu, v, 8);
+            v += __shfl_xor_sync(0xffffffffu, v, 16);
+            if (g == 0) GS[warp * D + 8 * nt + 2 * t + c] = v;
+        }
+    }
+    __syncthreads();
+    for (int e = tid; e < D; e += kThreads) {
+        float s = 0.0f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) s += GS[r * D + e];
+        mine[D * D + e] = s;
+    }
+}
+
+// The blocks' shares added in a fixed order: eight threads an output take every eighth block, their sums meet in
+// shared memory and are added in order.
 template <bool BF>
 __global__ void __launch_bounds__(kThreads)
 k_tail_wgrad(const float* __restrict__ partial, int blocks, int d, float* __restrict__ d_w_out, float* __restrict__ d_gain) {
+    __shared__ float part[8][32];
     const int outputs = d * d + d;
-    const int e = static_cast<int>(blockIdx.x) * kThreads + static_cast<int>(threadIdx.x);
-    if (e >= outputs) return;
-    float s[kSumLanes];
-#pragma unroll
-    for (int l = 0; l < kSumLanes; ++l) s[l] = 0.0f;
-    int b = 0;
-    for (; b + kSumLanes <= blocks; b += kSumLanes) {
-#pragma unroll
-        for (int l = 0; l < kSumLanes; ++l) s[l] += __ldg(partial + static_cast<int64_t>(b + l) * outputs + e);
+    const int lane = static_cast<int>(threadIdx.x) & 31, w = static_cast<int>(threadIdx.x) >> 5;
+    const int e = static_cast<int>(blockIdx.x) * 32 + lane;
+    float s = 0.0f;
+    if (e < outputs) {
+#pragma unroll 4
+        for (int b = w; b < blocks; b += 8) s += __ldg(partial + static_cast<int64_t>(b) * outputs + e);
     }
-    for (int l = 0; b + l < blocks; ++l) s[l] += __ldg(partial + static_cast<int64_t>(b + l) * outputs + e);
-    float total = s[0];
+    part[w][lane] = s;
+    __syncthreads();
+    if (w == 0 && e < outputs) {
+        float total = part[0][lane];
 #pragma unroll
-    for (int l = 1; l < kSumLanes; ++l) total += s[l];
-    if (e < d * d) d_w_out[e] = maybe_bf16(total, BF);
-    else d_gain[e - d * d] = total;
+        for (int r = 1; r < 8; ++r) total += part[r][lane];
+        if (e < d * d) d_w_out[e] = maybe_bf16(total, BF);
+        else d_gain[e - d * d] = total;
+    }
 }
-
-int blocks_per_sm(int d) { return d <= 64 ? 2 : 1; }
 
 int check(const HsnwTail* t, int64_t slots, const char* what) {
     if (!t || slots < 0) return hsnw_fail(HSNW_E_ARG, what);
@@ -285,22 +549,41 @@ int check(const HsnwTail* t, int64_t slots, const char* what) {
     return HSNW_OK;
 }
 
-int64_t bwd_blocks(int d, int64_t slots, int sms) {
-    const int64_t tiles = (slots + kTile - 1) / kTile;
-    return std::max<int64_t>(1, std::min<int64_t>(tiles, static_cast<int64_t>(sms) * blocks_per_sm(d)));
+// The backward's blocks: at most two an SM (one at d = 128: registers and shared memory), every block the same number of tiles
+// where the tiles allow it.
+int64_t bwd_blocks(const HsnwTail* t, int64_t slots, int sms) {
+    const int tile = t->prod_bf16 ? kTileMma : kTile;
+    const int per_sm = t->d <= 64 ? 2 : 1;
+    const int64_t tiles = std::max<int64_t>(1, (slots + tile - 1) / tile);
+    const int64_t cap = static_cast<int64_t>(sms) * per_sm;
+    const int64_t rounds = (tiles + cap - 1) / cap;
+    return (tiles + rounds - 1) / rounds;
 }
 
-template <int D, bool BF>
+template <int D>
 void launch_fwd(const HsnwTail* t, const void* unit_out, const float* alpha, int64_t slots, float* y, float* c, cudaStream_t stream) {
-    const unsigned tiles = static_cast<unsigned>((slots + kTile - 1) / kTile);
-    k_tail_fwd<D, BF><<<tiles, kThreads, Shape<D>::fwd_bytes, stream>>>(t->w_out, t->norm_weight, t->norm_eps, unit_out, alpha, slots, y, c);
+    if (t->prod_bf16) {
+        const unsigned tiles = static_cast<unsigned>((slots + kTileMma - 1) / kTileMma);
+        k_tail_fwd_mma<D><<<tiles, kThreads, MmaShape<D>::fwd_bytes, stream>>>(t->w_out, t->norm_weight, t->norm_eps,
+                                                                             static_cast<const uint16_t*>(unit_out), alpha, slots, y, c);
+    } else {
+        const unsigned tiles = static_cast<unsigned>((slots + kTile - 1) / kTile);
+        k_tail_fwd<D><<<tiles, kThreads, Shape<D>::fwd_bytes, stream>>>(t->w_out, t->norm_weight, t->norm_eps,
+                                                                       static_cast<const float*>(unit_out), alpha, slots, y, c);
+    }
 }
 
-template <int D, bool BF>
+template <int D>
 void launch_bwd(const HsnwTail* t, const void* unit_out, const float* alpha, const float* y, const float* d_c, int64_t slots,
                 void* d_unit_out, float* d_alpha, float* partial, int blocks, cudaStream_t stream) {
-    k_tail_bwd<D, BF><<<static_cast<unsigned>(blocks), kThreads, Shape<D>::bwd_bytes, stream>>>(
-        t->w_out, t->norm_weight, t->norm_eps, unit_out, alpha, y, d_c, slots, d_unit_out, d_alpha, partial);
+    if (t->prod_bf16)
+        k_tail_bwd_mma<D><<<static_cast<unsigned>(blocks), kThreads, MmaShape<D>::bwd_bytes, stream>>>(
+            t->w_out, t->norm_weight, t->norm_eps, static_cast<const uint16_t*>(unit_out), alpha, y, d_c, slots,
+            static_cast<uint16_t*>(d_unit_out), d_alpha, partial);
+    else
+        k_tail_bwd<D><<<static_cast<unsigned>(blocks), kThreads, Shape<D>::bwd_bytes, stream>>>(
+            t->w_out, t->norm_weight, t->norm_eps, static_cast<const float*>(unit_out), alpha, y, d_c, slots,
+            static_cast<float*>(d_unit_out), d_alpha, partial);
 }
 
 }  // namespace
@@ -308,7 +591,7 @@ void launch_bwd(const HsnwTail* t, const void* unit_out, const float* alpha, con
 extern "C" int64_t hsnw_tail_scratch_bytes(const HsnwTail* tail, int64_t slots) {
     if (!tail || slots < 0 || tail->d < 16 || tail->d > 128) return 0;
     const int sms = std::max(148, hsnw_sm_count_current());
-    const int64_t bytes = bwd_blocks(tail->d, slots, sms) * (static_cast<int64_t>(tail->d) * tail->d + tail->d) * static_cast<int64_t>(sizeof(float));
+    const int64_t bytes = bwd_blocks(tail, slots, sms) * (static_cast<int64_t>(tail->d) * tail->d + tail->d) * static_cast<int64_t>(sizeof(float));
     return (bytes + 255) / 256 * 256;
 }
 
@@ -318,12 +601,13 @@ extern "C" int hsnw_tail_forward(const HsnwTail* tail, const void* unit_out, con
     if (int rc = check(tail, slots, "tail_forward: null or negative")) return rc;
     if (slots == 0) return HSNW_OK;
     if (!unit_out || !alpha || !y || !c) return hsnw_fail(HSNW_E_ARG, "tail_forward: null tensor");
+    if (reinterpret_cast<uintptr_t>(unit_out) % 16 || reinterpret_cast<uintptr_t>(y) % 8 || reinterpret_cast<uintptr_t>(c) % 8)
+        return hsnw_fail(HSNW_E_ARG, "tail_forward: unit_out must be 16-byte aligned, y and c 8-byte");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     hsnw_profile_mark(HSNW_K_TAIL_FWD, stream);
 #define HSNW_TAIL_FWD(D) \
     case D: \
-        if (tail->prod_bf16) launch_fwd<D, true>(tail, unit_out, alpha, slots, y, c, stream); \
-        else launch_fwd<D, false>(tail, unit_out, alpha, slots, y, c, stream); \
+        launch_fwd<D>(tail, unit_out, alpha, slots, y, c, stream); \
         break
     switch (tail->d) {
         HSNW_TAIL_FWD(16);
@@ -351,14 +635,15 @@ extern "C" int hsnw_tail_backward(const HsnwTail* tail, const void* unit_out, co
     }
     if (!unit_out || !alpha || !y || !d_c || !d_unit_out || !d_alpha) return hsnw_fail(HSNW_E_ARG, "tail_backward: null tensor");
     if (!scratch || scratch_bytes < hsnw_tail_scratch_bytes(tail, slots)) return hsnw_fail(HSNW_E_ARG, "tail_backward: scratch too small");
-    if (reinterpret_cast<uintptr_t>(scratch) % 16) return hsnw_fail(HSNW_E_ARG, "tail_backward: scratch not 16-byte aligned");
-    const int blocks = static_cast<int>(bwd_blocks(d, slots, std::max(1, hsnw_sm_count_current())));
+    if (reinterpret_cast<uintptr_t>(scratch) % 16 || reinterpret_cast<uintptr_t>(unit_out) % 16 || reinterpret_cast<uintptr_t>(y) % 8
+        || reinterpret_cast<uintptr_t>(d_c) % 8 || reinterpret_cast<uintptr_t>(d_unit_out) % 4 || reinterpret_cast<uintptr_t>(tail->w_out) % 8)
+        return hsnw_fail(HSNW_E_ARG, "tail_backward: scratch and unit_out must be 16-byte aligned, y, d_c and W_out 8-byte, d_unit_out 4-byte");
+    const int blocks = static_cast<int>(bwd_blocks(tail, slots, std::max(1, hsnw_sm_count_current())));
     float* partial = static_cast<float*>(scratch);
     hsnw_profile_mark(HSNW_K_TAIL_BWD, stream);
 #define HSNW_TAIL_BWD(D) \
     case D: \
-        if (tail->prod_bf16) launch_bwd<D, true>(tail, unit_out, alpha, y, d_c, slots, d_unit_out, d_alpha, partial, blocks, stream); \
-        else launch_bwd<D, false>(tail, unit_out, alpha, y, d_c, slots, d_unit_out, d_alpha, partial, blocks, stream); \
+        launch_bwd<D>(tail, unit_out, alpha, y, d_c, slots, d_unit_out, d_alpha, partial, blocks, stream); \
         break
     switch (d) {
         HSNW_TAIL_BWD(16);
@@ -367,7 +652,7 @@ extern "C" int hsnw_tail_backward(const HsnwTail* tail, const void* unit_out, co
         HSNW_TAIL_BWD(128);
     }
 #undef HSNW_TAIL_BWD
-    const unsigned out_blocks = static_cast<unsigned>((d * d + d + kThreads - 1) / kThreads);
+    const unsigned out_blocks = static_cast<unsigned>((d * d + d + 31) / 32);
     if (tail->prod_bf16) k_tail_wgrad<true><<<out_blocks, kThreads, 0, stream>>>(partial, blocks, d, d_w_out, d_norm_weight);
     else k_tail_wgrad<false><<<out_blocks, kThreads, 0, stream>>>(partial, blocks, d, d_w_out, d_norm_weight);
     return hsnw_check_launch("tail_backward");
@@ -376,10 +661,10 @@ extern "C" int hsnw_tail_backward(const HsnwTail* tail, const void* unit_out, co
 void hsnw_tail_set_attributes() {
     bool ok = true;
 #define HSNW_TAIL_OPT(D) \
-    ok = ok && hsnw_opt_in(reinterpret_cast<const void*>(k_tail_fwd<D, true>), "tail_fwd") \
-         && hsnw_opt_in(reinterpret_cast<const void*>(k_tail_fwd<D, false>), "tail_fwd") \
-         && hsnw_opt_in(reinterpret_cast<const void*>(k_tail_bwd<D, true>), "tail_bwd") \
-         && hsnw_opt_in(reinterpret_cast<const void*>(k_tail_bwd<D, false>), "tail_bwd")
+    ok = ok && hsnw_opt_in(reinterpret_cast<const void*>(k_tail_fwd<D>), "tail_fwd") \
+         && hsnw_opt_in(reinterpret_cast<const void*>(k_tail_fwd_mma<D>), "tail_fwd_mma") \
+         && hsnw_opt_in(reinterpret_cast<const void*>(k_tail_bwd<D>), "tail_bwd") \
+         && hsnw_opt_in(reinterpret_cast<const void*>(k_tail_bwd_mma<D>), "tail_bwd_mma")
     HSNW_TAIL_OPT(16);
     HSNW_TAIL_OPT(32);
     HSNW_TAIL_OPT(64);
