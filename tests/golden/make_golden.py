@@ -796,26 +796,40 @@ def make_replay(root: Path) -> None:
         def wrapper(u, eps, h_read, sel, *, record=None, real=real, cell=cell, out=out):
             leaves = [t.detach().clone().requires_grad_(True) for t in (u, eps, sel.alpha)]
             seen: dict[str, torch.Tensor] = {}
-            hook = cell.W_out.register_forward_hook(lambda mod, inp, res: seen.update(unit_out=inp[0]))
+            hooks = [cell.W_out.register_forward_hook(lambda mod, inp, res: seen.update(unit_out=inp[0])),
+                     cell.norm.register_forward_hook(lambda mod, inp, res: seen.update(v_raw=inp[0], v=res))]  # fmt: skip
+            grouped = cell.units.forward_grouped
+
+            def grouped_seen(v, idx, **kw):   # the view of v the unit pass reads: its gradient is the unit pass's alone
+                seen["v_units"] = v
+                return grouped(v, idx, **kw)
+
+            cell.units.forward_grouped = grouped_seen
             try:
                 rec: dict[str, torch.Tensor] = {}
                 c, b = real(leaves[0], leaves[1], h_read, dataclasses.replace(sel, alpha=leaves[2]), record=rec)
             finally:
-                hook.remove()
+                for hook in hooks:
+                    hook.remove()
+                del cell.units.forward_grouped
             gen = torch.Generator().manual_seed(51)
             d_c = torch.randn(c.shape, generator=gen).to(c.dtype)
             d_b = torch.randn(b.shape, generator=gen).to(b.dtype)
             params = dict(cell.named_parameters())
-            grads = torch.autograd.grad([c, b], [*leaves, seen["unit_out"], *params.values()], [d_c, d_b], allow_unused=True,
+            grads = torch.autograd.grad([c, b], [*leaves, seen["unit_out"], seen["v_raw"], seen["v_units"], *params.values()], [d_c, d_b], allow_unused=True,
                                         retain_graph=True)   # the window caches casts of the weights: the real call below shares them
             f32 = torch.float32
             out.update(u=_np(u), eps=_np(eps), h_read=_np(h_read), cells=sel.cell_idx.numpy(), units=sel.unit_idx.numpy(),
                        valid=sel.valid.numpy(), alpha=_np(sel.alpha), c=_np(c), b=_np(b), d_c=_np(d_c), d_b=_np(d_b),
                        unit_out=_np(seen["unit_out"].to(f32)), d_u=_np(grads[0]), d_eps=_np(grads[1]), d_alpha=_np(grads[2]),
-                       d_unit_out=_np(grads[3].to(f32)), cand_eps=np.array(float(cell.cand_norm.eps)))  # fmt: skip
+                       d_unit_out=_np(grads[3].to(f32)), cand_eps=np.array(float(cell.cand_norm.eps)),
+                       v_raw=_np(seen["v_raw"]), v=_np(seen["v"].to(f32)), d_v_raw=_np(grads[4]), d_v_units=_np(grads[5].to(f32)),
+                       norm_eps=np.array(float(cell.norm.eps if cell.norm.eps is not None else torch.finfo(torch.float32).eps)))  # fmt: skip
+            print("   dtypes: v_raw", seen["v_raw"].dtype, "v", seen["v"].dtype, "v_units", seen["v_units"].dtype, "d_v_units", grads[5].dtype,
+                  "gate_pre", rec["gate_pre"].dtype, "b", b.dtype)
             for key, value in rec.items():
                 out["rec_" + key] = _np(value.to(f32))
-            for (key, value), grad in zip(params.items(), grads[4:], strict=True):
+            for (key, value), grad in zip(params.items(), grads[6:], strict=True):
                 out["w_" + key] = _np(value)
                 if grad is not None:
                     out["g_" + key] = _np(grad.to(f32))
