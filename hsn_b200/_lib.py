@@ -131,6 +131,11 @@ class HsnwTail(Structure):
     _fields_ = [("d", c_int32), ("prod_bf16", c_int32), ("norm_eps", c_float), ("reserved", c_int32), ("w_out", c_void_p), ("norm_weight", c_void_p)]  # fmt: skip
 
 
+class HsnwGate(Structure):
+    _fields_ = [("d", c_int32), ("prod_bf16", c_int32), ("norm_eps", c_float), ("reserved", c_int32), ("norm_weight", c_void_p),
+                ("gate_w", c_void_p), ("gate_b", c_void_p)]  # fmt: skip
+
+
 class HsnwPrologue(Structure):
     _fields_ = (
         [(n, c_int32) for n in PROLOGUE_INTS]
@@ -176,6 +181,10 @@ SYMBOLS: dict[str, tuple[object, list[object]]] = {
                                    c_int64, c_void_p]),
     "hsnw_scorer_logits_backward": (c_int, [POINTER(HsnwScorer), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
                                             c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "hsnw_gate_scratch_bytes": (c_int64, [POINTER(HsnwGate), c_int64, c_int]),
+    "hsnw_gate_forward": (c_int, [POINTER(HsnwGate), c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "hsnw_gate_backward": (c_int, [POINTER(HsnwGate), c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_void_p, c_int64, c_void_p]),
     "hsnw_tail_scratch_bytes": (c_int64, [POINTER(HsnwTail), c_int64]),
     "hsnw_tail_forward": (c_int, [POINTER(HsnwTail), c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
     "hsnw_tail_backward": (c_int, [POINTER(HsnwTail), c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,

@@ -12,6 +12,7 @@
 #include "../../include/hsn_window_b200.h"
 #include "common.cuh"
 #include "host_util.h"
+#include "mma_tiles.cuh"
 
 #include <algorithm>
 #include <cstdint>
@@ -255,29 +256,6 @@ struct MmaShape {
     static constexpr size_t bwd_bytes = sizeof(uint32_t) * (2 * kTileMma * PW + D * PW) + sizeof(float) * (D + 8 * D);
 };
 
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    return static_cast<uint32_t>(bf16_bits(lo)) | (static_cast<uint32_t>(bf16_bits(hi)) << 16);
-}
-
-// c += a b for one 16 x 8 tile: a 16 x 16 (row major fragments), b 16 x 8 (column fragments), bf16 in, float32 sums.
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-// Four (two) 8 x 8 blocks of bf16 values, each handed out transposed: a lane ends up with the elements [2t][g] and
-// [2t + 1][g] of block i in r[i]. Lane l gives the address of row l % 8 of block l / 8.
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* row) {
-    const uint32_t at = static_cast<uint32_t>(__cvta_generic_to_shared(row));
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(at));
-}
-__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t (&r)[2], const void* row) {
-    const uint32_t at = static_cast<uint32_t>(__cvta_generic_to_shared(row));
-    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(at));
-}
-
 // A tile of unit_out (bf16) into shared memory rows of pitch PB; rows beyond the last slot are zero.
 template <int D>
 __device__ __forceinline__ void load_tile_bf16(uint32_t* Xs, const uint16_t* src, int64_t first, int64_t slots, int tid) {
@@ -313,12 +291,6 @@ __device__ __forceinline__ void warp_product(float (&acc)[MmaShape<D>::NT][4], c
             mma_bf16(acc[nt], a, b0, b1);
         }
     }
-}
-
-__device__ __forceinline__ float sum4_lanes(float v) {   // over the 4 lanes that share a row of a fragment
-    v += __shfl_xor_sync(0xffffffffu, v, 1);
-    v += __shfl_xor_sync(0xffffffffu, v, 2);
-    return v;
 }
 
 // A lane holds, of row g + 8 h of its warp's 16 rows, the columns 8 nt + 2 t and + 1 in acc[nt][2 h], [2 h + 1].

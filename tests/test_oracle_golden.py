@@ -443,3 +443,32 @@ def test_replay_tail_equals_the_reference(name: str) -> None:
     if name == "cut_f32":   # a slot the budget cut: weight 0, candidate 0, no gradient into the unit's output
         cut = ~z["valid"].reshape(-1)
         assert cut.any() and not np.any(args[1][cut]) and not np.any(c[cut]) and not np.any(grads[0][cut])
+
+
+@pytest.mark.parametrize("name", ["f32", "cut_f32", "bf16", "wide_bf16"])
+def test_replay_norm_and_gate_equal_the_reference(name: str) -> None:
+    """The cell norm, the gate and the sigmoid of ``replay_sparse`` with autograd's gradients, on the values the
+    reference's own replay held inside a split window (the norm's input and output taken by a forward hook, the unit
+    pass's own gradient of ``v`` by wrapping ``forward_grouped``): float32 to rounding; under bf16 autocast the
+    bfloat16-rounded results to one bfloat16 step."""
+    from oracle import gate_oracle as G
+
+    z = load_golden(f"replay_{name}")
+    bf = "bf16" in name
+    F = z["v_raw"].shape[-1]
+    d = F // 4
+    args = (z["v_raw"].reshape(-1, F), z["w_norm.weight"], z["w_gate.weight"], z["w_gate.bias"])
+    eps = float(z["norm_eps"])
+    v, rms, gate_pre, b = G.forward_norm_gate(*args, norm_eps=eps, bf16=bf)
+    grads = G.backward_norm_gate(*args, z["d_v_units"].reshape(-1, F), z["d_b"].reshape(-1, d), norm_eps=eps, bf16=bf)
+    step = 2.0**-7 if bf else 4e-6   # one bfloat16 step of the largest value, or float32 rounding of a sum
+    for got, want, tol, what in (
+        (v, z["v"].reshape(-1, F), 4e-6, "v"), (rms, z["rec_rms"].reshape(-1), 4e-6, "rms"),
+        (gate_pre, z["rec_gate_pre"].reshape(-1, d), step, "gate_pre"), (b, z["b"].reshape(-1, d), step, "b"),
+        (grads[0], z["d_v_raw"].reshape(-1, F), 1e-4 if bf else 4e-6, "d_v_raw"), (grads[1], z["g_norm.weight"], 4e-6, "d_norm_w"),
+        (grads[2], z["g_gate.weight"], step, "d_gate_w"), (grads[3], z["g_gate.bias"], step, "d_gate_b"),
+    ):  # fmt: skip
+        assert got.shape == want.shape and got.dtype == np.float32, what
+        np.testing.assert_allclose(got, want, rtol=0, atol=tol * float(np.abs(want).max()), err_msg=what)
+    if name == "bf16":   # here nothing falls on a rounding boundary: the bfloat16 parts equal the reference's to the bit
+        assert np.array_equal(gate_pre, z["rec_gate_pre"].reshape(-1, d)) and np.array_equal(grads[2], z["g_gate.weight"])
