@@ -57,7 +57,10 @@ CONFIGS["units"] = dict(pairs=32 * 256 * 8, M=8, d=64, H=512, units=True)
 CONFIGS["scorer"] = dict(R=32 * 256, N=256, d=64, M=8, S=9, scorer=True)
 # the end of the replay's cell pass (not the headline): every slot of the c2 window, forward and backward
 CONFIGS["tail"] = dict(slots=32 * 256 * 8, d=64, tail=True)
+# the cell norm and the gate of the replay's cell pass (not the headline): every slot of the c2 window, forward and backward
+CONFIGS["gate"] = dict(slots=32 * 256 * 8, d=64, gate=True)
 WORKLOADS = {
+    "gate": "the replay's cell norm + gate + sigmoid over a window's 65,536 slots (4d 256 -> d 64), bf16 products, forward + backward",
     "tail": "the replay's W_out + candidate norm + weighted tanh over a window's 65,536 slots (d 64), bf16 products, forward + backward",
     "scorer": "the replay's scorer logits over a window's 8192 positions x 256 cells (d 64, 8 units, 9 scalars), bf16 products, forward + weight gradients",
     "units": "the replay's grouped unit pass over a window's 65,536 pairs: 8 units 256 -> 512 -> 64, bf16 products, forward + backward",
@@ -287,7 +290,7 @@ def run_reference(args, c: dict, name: str) -> None:
 
 
 def run_side_reference(args, c: dict, name: str) -> None:
-    """`--impl reference` for the side configurations `units`, `scorer` and `tail`: the numpy restatement of the pass
+    """`--impl reference` for the side configurations `units`, `scorer`, `tail` and `gate`: the numpy restatement of the pass
     (forward + backward, bf16 rounding emulated) on a sample of the workload, on the host's cores."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
@@ -304,6 +307,18 @@ def run_side_reference(args, c: dict, name: str) -> None:
         def step():
             _, pre = U.forward_grouped(v, idx, *bank, bf16=True)
             U.backward_grouped(v, idx, *bank, pre, cot, bf16=True)
+            return n
+    elif name == "gate":
+        from oracle import gate_oracle as GO
+
+        n, d = 16384, c["d"]
+        gx, gnw, ggw, ggb = f(n, 4 * d, scale=0.8), 1.0 + f(4 * d, scale=0.2), f(d, 4 * d, scale=(4 * d) ** -0.5), f(d, scale=0.3)
+        gdv, gdb = f(n, 4 * d), f(n, d)
+        unit, sample = "slots/s", f"{n} of the window's slots per step"
+
+        def step():
+            GO.forward_norm_gate(gx, gnw, ggw, ggb, norm_eps=1e-6, bf16=True)
+            GO.backward_norm_gate(gx, gnw, ggw, ggb, gdv, gdb, norm_eps=1e-6, bf16=True)
             return n
     elif name == "tail":
         from oracle import tail_oracle as TO
@@ -335,7 +350,7 @@ def run_side_reference(args, c: dict, name: str) -> None:
     done = sum(step() for _ in range(args.steps))
     sec = time.perf_counter() - t0
     value = done / sec
-    metric = {"units": "grouped unit pass pairs/s (forward + backward)", "tail": TAIL_METRIC}.get(name, "scorer logits cells/s (forward + weight gradients)")
+    metric = {"units": "grouped unit pass pairs/s (forward + backward)", "tail": TAIL_METRIC, "gate": GATE_METRIC}.get(name, "scorer logits cells/s (forward + weight gradients)")
     print(json.dumps({
         "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": sec / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -1166,6 +1181,113 @@ def run_tail(args, c: dict, name: str) -> None:
         "cpu_baseline": cpu, "clocks": clocks_summary(clock_lines, 0)}))  # fmt: skip
 
 
+GATE_METRIC = "replay norm + gate slots/s (forward + backward)"
+
+
+def run_gate(args, c: dict, name: str) -> None:
+    """`--config gate`: `hsnw_gate_forward` + `hsnw_gate_backward` over the benchmark window's slots through the C ABI on
+    buffers made once; a step = both. Beside it the CPU restatement on a sample of the slots, and the reference's lines
+    in PyTorch on the same device."""
+    import ctypes
+
+    import torch
+
+    from hsn_b200 import _lib
+    from hsn_b200.kernels.gate import norm_gate_backward, norm_gate_forward
+    from hsn_b200.window import launch_profile
+
+    world, rank, local, dev = dist_setup()
+    P, d = c["slots"], c["d"]
+    F = 4 * d
+    gen = torch.Generator(device=dev).manual_seed(0)
+    f = lambda *shape, scale=1.0: torch.randn(*shape, generator=gen, device=dev) * scale  # noqa: E731
+    x, nw, gw, gb = f(P, F, scale=0.8), 1.0 + f(F, scale=0.2), f(d, F, scale=F**-0.5), f(d, scale=0.3)
+    d_v, d_b = f(P, F), f(P, d)
+    lib = _lib.library()
+    if not lib.hsnw_prepared(local):
+        _lib.check(lib.hsnw_prepare(local))
+    st = _lib.HsnwGate(d=d, prod_bf16=1, norm_eps=1e-6, reserved=0, norm_weight=nw.data_ptr(), gate_w=gw.data_ptr(), gate_b=gb.data_ptr())
+    v, rms, gp, b = torch.empty(P, F, device=dev), torch.empty(P, device=dev), torch.empty(P, d, device=dev), torch.empty(P, d, device=dev)
+    d_x, d_nw, d_gw, d_gb = torch.empty(P, F, device=dev), torch.empty(F, device=dev), torch.empty(d, F, device=dev), torch.empty(d, device=dev)
+    need_f = int(lib.hsnw_gate_scratch_bytes(ctypes.byref(st), P, 0))
+    need_b = int(lib.hsnw_gate_scratch_bytes(ctypes.byref(st), P, 1))
+    scr_f, scr_b = torch.empty(need_f, dtype=torch.uint8, device=dev), torch.empty(need_b, dtype=torch.uint8, device=dev)
+    stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+    def step(i):   # (the pass's tensors, 300 MB, are more than twice L2: nothing of one pass survives to the next)
+        _lib.check(lib.hsnw_gate_forward(ctypes.byref(st), x.data_ptr(), P, v.data_ptr(), rms.data_ptr(), gp.data_ptr(), b.data_ptr(),
+                                         scr_f.data_ptr(), need_f, stream))  # fmt: skip
+        _lib.check(lib.hsnw_gate_backward(ctypes.byref(st), x.data_ptr(), gp.data_ptr(), d_v.data_ptr(), d_b.data_ptr(), P, d_x.data_ptr(),
+                                          d_nw.data_ptr(), d_gw.data_ptr(), d_gb.data_ptr(), scr_b.data_ptr(), need_b, stream))  # fmt: skip
+
+    for i in range(max(3, args.warmup)):
+        step(i)
+    want = norm_gate_forward(x, nw, gw, gb)
+    wantb = norm_gate_backward(x, nw, gw, gb, want[2], d_v, d_b)
+    if not (all(torch.equal(a, w) for a, w in zip((v, rms, gp, b), want, strict=True))
+            and all(torch.equal(a, w) for a, w in zip((d_x, d_nw, d_gw, d_gb), wantb, strict=True))):
+        raise SystemExit("bench.py --config gate: the direct calls and the Python wrappers disagree")
+    clock_lines: list = []
+    stop = threading.Event()
+    threading.Thread(target=sample_clocks, args=(stop, clock_lines), daemon=True).start()
+    fwd_ms = bwd_ms = 0.0
+    for i in range(5):
+        with launch_profile() as prof:
+            step(i)
+        fwd_ms += prof.ms.get("gate_fwd", 0.0) / 5
+        bwd_ms += prof.ms.get("gate_bwd", 0.0) / 5
+    ms_total, each = timed_steps(step, args.steps, torch.cuda.synchronize)
+    stop.set()
+    norm = torch.nn.RMSNorm(F, eps=1e-6, device=dev)
+    gate = torch.nn.Linear(F, d, device=dev)
+
+    def torch_step(i):
+        xr = x.clone().requires_grad_(True)
+        vr = norm(xr)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            pre = gate(vr).to(torch.float32)
+        torch.autograd.backward([vr, torch.sigmoid(pre)], [d_v, d_b])
+        norm.weight.grad = gate.weight.grad = gate.bias.grad = None
+
+    for i in range(3):
+        torch_step(i)
+    torch_total, torch_each = timed_steps(torch_step, max(3, args.steps // 4), torch.cuda.synchronize)
+    cpu = None
+    if not args.no_cpu_baseline:
+        from oracle import gate_oracle as GO
+
+        n = 16384
+        hx, hnw, hgw, hgb, hdv, hdb = (t.cpu().numpy() for t in (x[:n], nw, gw, gb, d_v[:n], d_b[:n]))
+        t0 = time.perf_counter()
+        reps = 0
+        while time.perf_counter() - t0 < 10.0:
+            GO.forward_norm_gate(hx, hnw, hgw, hgb, norm_eps=1e-6, bf16=True)
+            GO.backward_norm_gate(hx, hnw, hgw, hgb, hdv, hdb, norm_eps=1e-6, bf16=True)
+            reps += 1
+        cpu = {"value": reps * n / (time.perf_counter() - t0), "unit": "slots/s", "cores": blas_threads(), "kind": "port",
+               "sample": f"{reps} passes of forward + backward over {n} of the window's slots (numpy restatement, bf16 rounding emulated)"}
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    fwd_bytes = float(P) * (16 * d + 16 * d + 4 + 8 * d)    # v_raw read; v, rms, gate_pre, b written
+    bwd_bytes = float(P) * (16 * d + 16 * d + 8 * d + 16 * d)   # v_raw, d_v_units, gate_pre and d_b read; d_v_raw written
+    kernel_ms = fwd_ms + bwd_ms
+    achieved = (fwd_bytes + bwd_bytes) / (kernel_ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": GATE_METRIC, "value": P / (kernel_ms * 1e-3), "unit": "slots/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": kernel_ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32 norm, bf16 products", "data": "synthetic",
+        "config": {"workload": WORKLOADS[name], "l2": "the pass's tensors (300 MB) are larger than L2",
+                   "forward_ms": fwd_ms, "backward_ms": bwd_ms, "step_ms": spread(each),
+                   "torch_rmsnorm_linear_sigmoid_autocast_autograd_ms": spread(torch_each)},
+        "gpu_launches": 5 * args.steps,
+        "roofline": {"bound": "hbm", "kernel": "k_gate_fwd + k_gate_bwd", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": None, "peak_source": "measured" if peaks else "fallback",
+                     "forward": {"achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9, "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak},
+                     "backward": {"achieved": bwd_bytes / (bwd_ms * 1e-3) / 1e9, "frac": bwd_bytes / (bwd_ms * 1e-3) / 1e9 / peak},
+                     "how": "per slot 40 d + 4 bytes forward (v_raw read; v, rms, gate_pre, b written) and 56 d backward (v_raw, the unit pass's gradient, gate_pre, d_b read; d_v_raw written) / the calls' event time, mean of five profiled steps"},
+        "cpu_baseline": cpu, "clocks": clocks_summary(clock_lines, 0)}))  # fmt: skip
+
+
 def run_trainer_sharded(args, c: dict, name: str, world: int, rank: int, dev) -> None:
     """`--config adamw --gpus N`: the same parameter vector replicated on N ranks, a step = the gradient exchange
     and the AdamW step as ONE kernel per rank over peer memory (`ShardedAdamW`: reduce-scatter, step, all-gather),
@@ -1256,7 +1378,7 @@ def main() -> None:
         if args.steps == 100:
             args.steps = 20
         run_decoder(args, c, args.config)
-    elif c.get("units") or c.get("scorer") or c.get("tail"):
+    elif c.get("units") or c.get("scorer") or c.get("tail") or c.get("gate"):
         if args.steps == 100:
             args.steps = 20
         if args.impl == "reference":
@@ -1265,6 +1387,8 @@ def main() -> None:
             run_units(args, c, args.config)
         elif c.get("tail"):
             run_tail(args, c, args.config)
+        elif c.get("gate"):
+            run_gate(args, c, args.config)
         else:
             run_scorer(args, c, args.config)
     elif c.get("trainer"):

@@ -8,7 +8,8 @@
 // A block takes tiles of 128 slots, a warp 16 of them. Everything row-wise (the norm and its backward, sigmoid) runs
 // with a warp on one row at a time and a lane on 4 consecutive features per 128, so global accesses are whole rows;
 // the products run on warp-level tensor-core tiles (mma_tiles.cuh) from bf16 copies of the tile in shared memory,
-// the gate's weight read as packed bf16 pairs from a 32 KB copy that stays in L1. Backward, per tile: v and
+// the gate's weight as packed bf16 pairs in shared memory too (read through L1 from global memory the products' B
+// fragments took a third of the forward's time). Backward, per tile: v and
 // d_gate_pre into shared memory; d_W_gate += d_gate_pre^T v (both read transposed, a warp keeps d * 4 d / 1024
 // accumulator tiles in registers over all of the block's tiles); d_gate_pre W_gate on the warp's own rows, written
 // as bf16 over the warp's rows of v (that sum IS a bf16 value in the reference); then the norm's backward row by row.
@@ -41,8 +42,8 @@ struct GateShape {
     static constexpr int TPW = (TILES + 7) / 8;        // d_W_gate tiles a warp
     static constexpr int LV = (F + 127) / 128;         // groups of 4 features a lane
     static constexpr int OUTPUTS = D * F + F + D;      // a block's shares: d_W_gate, the gain's gradient, d_b_gate
-    static constexpr size_t fwd_bytes = sizeof(uint32_t) * kTile * PWF + sizeof(float) * (F + D);
-    static constexpr size_t bwd_bytes = sizeof(uint32_t) * (kTile * PWF + kTile * PWD) + sizeof(float) * (F + kTile + 8 * (F + D));
+    static constexpr size_t fwd_bytes = sizeof(uint32_t) * (kTile * PWF + D * PWF) + sizeof(float) * (F + D);
+    static constexpr size_t bwd_bytes = sizeof(uint32_t) * (kTile * PWF + kTile * PWD + F * PWD) + sizeof(float) * (F + kTile + 8 * (F + D));
 };
 
 // wb [d][2 d] words: (W[j][2 w], W[j][2 w + 1]); wtb [4 d][d / 2] words: (W[2 w][f], W[2 w + 1][f]).
@@ -66,8 +67,10 @@ __device__ __forceinline__ float warp_total(float v) {
     return v;
 }
 
+// The slots' rows are read once: streaming loads and stores (evict first), so that the gate's packed weight, which
+// every product step reads through L1, stays there.
 __device__ __forceinline__ float4 ld4_or_zero(const float* base, bool on) {
-    return on ? __ldg(reinterpret_cast<const float4*>(base)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    return on ? __ldcs(reinterpret_cast<const float4*>(base)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 }
 
 template <int D>
@@ -79,10 +82,15 @@ k_gate_fwd(const uint32_t* __restrict__ wb, const float* __restrict__ norm_w, co
     constexpr int F = S::F, PWF = S::PWF, NT = S::NT, KSF = S::KSF, LV = S::LV;
     extern __shared__ __align__(16) uint32_t smem_w[];
     uint32_t* Vs = smem_w;                                          // [kTile][PWF] v as bf16
-    float* NW = reinterpret_cast<float*>(Vs + kTile * PWF);         // [F]
+    uint32_t* Ws = Vs + kTile * PWF;                                // [D][PWF] W_gate[j][f] as bf16
+    float* NW = reinterpret_cast<float*>(Ws + D * PWF);             // [F]
     float* GB = NW + F;                                             // [D] the bias as bf16 values
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int64_t first = static_cast<int64_t>(blockIdx.x) * kTile;
+    for (int e = tid; e < D * (F / 8); e += kThreads) {   // 16 bytes at a time
+        const int j = e / (F / 8), q = e - j * (F / 8);
+        *reinterpret_cast<uint4*>(Ws + j * PWF + 4 * q) = __ldg(reinterpret_cast<const uint4*>(wb) + e);
+    }
     for (int e = tid; e < F; e += kThreads) NW[e] = __ldg(norm_w + e);
     for (int e = tid; e < D; e += kThreads) GB[e] = bf16r(__ldg(gate_b + e));
     __syncthreads();
@@ -113,7 +121,7 @@ k_gate_fwd(const uint32_t* __restrict__ wb, const float* __restrict__ norm_w, co
                 if (f < F) {
                     const float4 nw = *reinterpret_cast<const float4*>(NW + f);
                     const float4 v = make_float4(x[q][i].x * rms * nw.x, x[q][i].y * rms * nw.y, x[q][i].z * rms * nw.z, x[q][i].w * rms * nw.w);
-                    if (p < slots) *reinterpret_cast<float4*>(v_out + p * F + f) = v;
+                    if (p < slots) __stcs(reinterpret_cast<float4*>(v_out + p * F + f), v);
                     *reinterpret_cast<uint2*>(Vs + row * PWF + f / 2) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
                 }
             }
@@ -136,8 +144,8 @@ k_gate_fwd(const uint32_t* __restrict__ wb, const float* __restrict__ norm_w, co
         a[3] = Vs[(r0 + g + 8) * PWF + 8 * ks + 4 + t];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            const uint32_t b0 = __ldg(wb + (8 * nt + g) * (F / 2) + 8 * ks + t);
-            const uint32_t b1 = __ldg(wb + (8 * nt + g) * (F / 2) + 8 * ks + 4 + t);
+            const uint32_t b0 = Ws[(8 * nt + g) * PWF + 8 * ks + t];
+            const uint32_t b1 = Ws[(8 * nt + g) * PWF + 8 * ks + 4 + t];
             mma_bf16(acc[nt], a, b0, b1);
         }
     }
@@ -168,10 +176,15 @@ k_gate_bwd(const uint32_t* __restrict__ wtb, const float* __restrict__ norm_w, f
     extern __shared__ __align__(16) uint32_t smem_w[];
     uint32_t* Vs = smem_w;                                          // [kTile][PWF] v as bf16, then d_gate_pre W_gate as bf16
     uint32_t* DGs = Vs + kTile * PWF;                               // [kTile][PWD] d_gate_pre as bf16
-    float* NW = reinterpret_cast<float*>(DGs + kTile * PWD);        // [F]
+    uint32_t* WT = DGs + kTile * PWD;                               // [F][PWD] WT[f][j] = W_gate[j][f] as bf16
+    float* NW = reinterpret_cast<float*>(WT + F * PWD);             // [F]
     float* RMS = NW + F;                                            // [kTile]
     float* RS = RMS + kTile;                                        // [8][F + D] the warps' shares at the end
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    for (int e = tid; e < F * (D / 8); e += kThreads) {   // 16 bytes at a time
+        const int f = e / (D / 8), q = e - f * (D / 8);
+        *reinterpret_cast<uint4*>(WT + f * PWD + 4 * q) = __ldg(reinterpret_cast<const uint4*>(wtb) + e);
+    }
     for (int e = tid; e < F; e += kThreads) NW[e] = __ldg(norm_w + e);
     float dw[TPW][4];
     float4 dnw[LV];
@@ -268,8 +281,8 @@ k_gate_bwd(const uint32_t* __restrict__ wtb, const float* __restrict__ norm_w, f
                 float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
                 for (int ks = 0; ks < KSD; ++ks) {
-                    const uint32_t b0 = __ldg(wtb + (8 * nt + g) * (D / 2) + 8 * ks + t);
-                    const uint32_t b1 = __ldg(wtb + (8 * nt + g) * (D / 2) + 8 * ks + 4 + t);
+                    const uint32_t b0 = WT[(8 * nt + g) * PWD + 8 * ks + t];
+                    const uint32_t b1 = WT[(8 * nt + g) * PWD + 8 * ks + 4 + t];
                     mma_bf16(acc, a[ks], b0, b1);
                 }
                 Vs[(r0 + g) * PWF + 4 * nt + t] = pack_bf16(acc[0], acc[1]);
@@ -325,9 +338,9 @@ k_gate_bwd(const uint32_t* __restrict__ wtb, const float* __restrict__ norm_w, f
                         const int f = 4 * lane + 128 * i;
                         if (f < F) {
                             const float4 xi = x[q][i], d = dv[q][i];
-                            *reinterpret_cast<float4*>(d_v_raw + p * F + f) =
-                                make_float4(rms * d.x - rms3 * xi.x * mean, rms * d.y - rms3 * xi.y * mean, rms * d.z - rms3 * xi.z * mean,
-                                            rms * d.w - rms3 * xi.w * mean);
+                            __stcs(reinterpret_cast<float4*>(d_v_raw + p * F + f),
+                                   make_float4(rms * d.x - rms3 * xi.x * mean, rms * d.y - rms3 * xi.y * mean, rms * d.z - rms3 * xi.z * mean,
+                                               rms * d.w - rms3 * xi.w * mean));
                         }
                     }
                 }
@@ -401,8 +414,8 @@ int check(const HsnwGate* s, int64_t slots, const char* what) {
 int64_t outputs_of(int d) { return static_cast<int64_t>(d) * 4 * d + 4 * d + d; }
 int64_t packed_bytes(int d) { return (static_cast<int64_t>(d) * 4 * d * 2 + 255) / 256 * 256; }
 
-// The backward's blocks: at most two an SM (one at d = 64: 203 registers a thread), every block the same number of
-// tiles where the tiles allow it.
+// The backward's blocks: two an SM up to d = 32, one at d = 64 (134 KB of shared memory, 203 registers a thread); every
+// block the same number of tiles where the tiles allow it.
 int64_t bwd_blocks(int d, int64_t slots, int sms) {
     const int64_t tiles = std::max<int64_t>(1, (slots + kTile - 1) / kTile);
     const int64_t cap = static_cast<int64_t>(sms) * (d >= 64 ? 1 : 2);
