@@ -5,7 +5,7 @@
 // pass's gradient, once more backward; v and d_v_raw are written once: the pass is bound by those four tensors
 // (forward 32 d + 8 d + 4 bytes a slot, backward 48 d + 8 d), the gate's product is 8 d^2 flops a slot.
 //
-// A block takes tiles of 128 slots, a warp 16 of them. Everything row-wise (the norm and its backward, sigmoid) runs
+// A block takes tiles of 128 slots forward (a warp 16 of them) and of 64 backward. Everything row-wise (the norm and its backward, sigmoid) runs
 // with a warp on one row at a time and a lane on 4 consecutive features per 128, so global accesses are whole rows;
 // the products run on warp-level tensor-core tiles (mma_tiles.cuh) from bf16 copies of the tile in shared memory,
 // the gate's weight as packed bf16 pairs in shared memory too (read through L1 from global memory the products' B
@@ -27,7 +27,8 @@ namespace {
 using namespace hsnw;
 
 constexpr int kThreads = 256;
-constexpr int kTile = 128;
+constexpr int kTile = 128;      // slots a tile of the forward: a warp 16 of them
+constexpr int kTileB = 64;      // of the backward: 8 rows a warp in the row-wise phases, 16 rows x half the columns in the product
 constexpr int kRowsAtOnce = 4;
 
 template <int D>
@@ -43,7 +44,7 @@ struct GateShape {
     static constexpr int LV = (F + 127) / 128;         // groups of 4 features a lane
     static constexpr int OUTPUTS = D * F + F + D;      // a block's shares: d_W_gate, the gain's gradient, d_b_gate
     static constexpr size_t fwd_bytes = sizeof(uint32_t) * (kTile * PWF + D * PWF) + sizeof(float) * (F + D);
-    static constexpr size_t bwd_bytes = sizeof(uint32_t) * (kTile * PWF + kTile * PWD + F * PWD) + sizeof(float) * (F + kTile + 8 * (F + D));
+    static constexpr size_t bwd_bytes = sizeof(uint32_t) * (kTileB * PWF + kTileB * PWD + F * PWD) + sizeof(float) * (F + kTileB + 8 * (F + D));
 };
 
 // wb [d][2 d] words: (W[j][2 w], W[j][2 w + 1]); wtb [4 d][d / 2] words: (W[2 w][f], W[2 w + 1][f]).
@@ -166,7 +167,7 @@ k_gate_fwd(const uint32_t* __restrict__ wb, const float* __restrict__ norm_w, co
 
 // `partial` [blocks][D F + F + D]: the block's shares of d_W_gate, of the gain's gradient and of d_b_gate.
 template <int D>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 2)   // two blocks an SM: the d_W_gate accumulators leave the registers between products
 k_gate_bwd(const uint32_t* __restrict__ wtb, const float* __restrict__ norm_w, float eps, const float* __restrict__ v_raw,
            const float* __restrict__ gate_pre, const float* __restrict__ d_v_units, const float* __restrict__ d_b, int64_t slots,
            float* __restrict__ d_v_raw, float* __restrict__ partial) {
@@ -174,12 +175,12 @@ k_gate_bwd(const uint32_t* __restrict__ wtb, const float* __restrict__ norm_w, f
     constexpr int F = S::F, PBF = S::PBF, PWF = S::PWF, PBD = S::PBD, PWD = S::PWD, NTF = S::NTF, KSD = S::KSD, MT = S::MT,
                   TILES = S::TILES, TPW = S::TPW, LV = S::LV;
     extern __shared__ __align__(16) uint32_t smem_w[];
-    uint32_t* Vs = smem_w;                                          // [kTile][PWF] v as bf16, then d_gate_pre W_gate as bf16
-    uint32_t* DGs = Vs + kTile * PWF;                               // [kTile][PWD] d_gate_pre as bf16
-    uint32_t* WT = DGs + kTile * PWD;                               // [F][PWD] WT[f][j] = W_gate[j][f] as bf16
+    uint32_t* Vs = smem_w;                                          // [kTileB][PWF] v as bf16, then d_gate_pre W_gate as bf16
+    uint32_t* DGs = Vs + kTileB * PWF;                              // [kTileB][PWD] d_gate_pre as bf16
+    uint32_t* WT = DGs + kTileB * PWD;                               // [F][PWD] WT[f][j] = W_gate[j][f] as bf16
     float* NW = reinterpret_cast<float*>(WT + F * PWD);             // [F]
-    float* RMS = NW + F;                                            // [kTile]
-    float* RS = RMS + kTile;                                        // [8][F + D] the warps' shares at the end
+    float* RMS = NW + F;                                            // [kTileB]
+    float* RS = RMS + kTileB;                                        // [8][F + D] the warps' shares at the end
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     for (int e = tid; e < F * (D / 8); e += kThreads) {   // 16 bytes at a time
         const int f = e / (D / 8), q = e - f * (D / 8);
@@ -195,15 +196,18 @@ k_gate_bwd(const uint32_t* __restrict__ wtb, const float* __restrict__ norm_w, f
         for (int c = 0; c < 4; ++c) dw[i][c] = 0.0f;
 #pragma unroll
     for (int i = 0; i < LV; ++i) dnw[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    const int r0 = warp * 16;
+    constexpr int RW = kTileB / 8;            // rows a warp in the row-wise phases
+    const int r0 = warp * RW;
+    const int rm = (warp & 3) * 16;           // the warp's 16 rows in the product of phase (c)
+    const int nt0 = (warp >> 2) * (NTF / 2);  // and its half of the columns
     const int mt = warp % MT;
     const bool has_j = 2 * lane < D;   // the lane's pair of gate columns
-    const int64_t tiles = (slots + kTile - 1) / kTile;
+    const int64_t tiles = (slots + kTileB - 1) / kTileB;
     for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-        const int64_t first = tile * kTile;
+        const int64_t first = tile * kTileB;
         __syncthreads();   // the previous tile's reads are over; the gain is in place
         // (a) v and d_gate_pre of the warp's rows, as bf16 in shared memory
-        for (int rr = 0; rr < 16; rr += kRowsAtOnce) {
+        for (int rr = 0; rr < RW; rr += kRowsAtOnce) {
             float4 x[kRowsAtOnce][LV];
             float2 gp[kRowsAtOnce], db[kRowsAtOnce];
 #pragma unroll
@@ -251,7 +255,7 @@ k_gate_bwd(const uint32_t* __restrict__ wtb, const float* __restrict__ norm_w, f
             const uint16_t* dg16 = reinterpret_cast<const uint16_t*>(DGs);
             const uint16_t* v16 = reinterpret_cast<const uint16_t*>(Vs);
 #pragma unroll 1
-            for (int ks = 0; ks < kTile / 16; ++ks) {
+            for (int ks = 0; ks < kTileB / 16; ++ks) {
                 uint32_t a[4];
                 ldmatrix_x4_trans(a, dg16 + (16 * ks + (lane & 7) + 8 * (lane >> 4)) * PBD + 16 * mt + 8 * ((lane >> 3) & 1));
 #pragma unroll
@@ -266,18 +270,18 @@ k_gate_bwd(const uint32_t* __restrict__ wtb, const float* __restrict__ norm_w, f
             }
         }
         __syncthreads();   // every warp has read every row of v: the rows can be overwritten
-        // (c) d_gate_pre W_gate on the warp's rows (K = d, N = 4 d), rounded to bf16 over the warp's rows of v
+        // (c) d_gate_pre W_gate (K = d, N = 4 d) on 16 rows x half the columns a warp, rounded to bf16 over those rows of v
         {
             uint32_t a[KSD][4];
 #pragma unroll
             for (int ks = 0; ks < KSD; ++ks) {
-                a[ks][0] = DGs[(r0 + g) * PWD + 8 * ks + t];
-                a[ks][1] = DGs[(r0 + g + 8) * PWD + 8 * ks + t];
-                a[ks][2] = DGs[(r0 + g) * PWD + 8 * ks + 4 + t];
-                a[ks][3] = DGs[(r0 + g + 8) * PWD + 8 * ks + 4 + t];
+                a[ks][0] = DGs[(rm + g) * PWD + 8 * ks + t];
+                a[ks][1] = DGs[(rm + g + 8) * PWD + 8 * ks + t];
+                a[ks][2] = DGs[(rm + g) * PWD + 8 * ks + 4 + t];
+                a[ks][3] = DGs[(rm + g + 8) * PWD + 8 * ks + 4 + t];
             }
 #pragma unroll 4
-            for (int nt = 0; nt < NTF; ++nt) {
+            for (int nt = nt0; nt < nt0 + NTF / 2; ++nt) {
                 float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
                 for (int ks = 0; ks < KSD; ++ks) {
@@ -285,13 +289,13 @@ k_gate_bwd(const uint32_t* __restrict__ wtb, const float* __restrict__ norm_w, f
                     const uint32_t b1 = WT[(8 * nt + g) * PWD + 8 * ks + 4 + t];
                     mma_bf16(acc, a[ks], b0, b1);
                 }
-                Vs[(r0 + g) * PWF + 4 * nt + t] = pack_bf16(acc[0], acc[1]);
-                Vs[(r0 + g + 8) * PWF + 4 * nt + t] = pack_bf16(acc[2], acc[3]);
+                Vs[(rm + g) * PWF + 4 * nt + t] = pack_bf16(acc[0], acc[1]);
+                Vs[(rm + g + 8) * PWF + 4 * nt + t] = pack_bf16(acc[2], acc[3]);
             }
         }
-        __syncwarp();
+        __syncthreads();   // a row's columns came from two warps
         // (d) the norm's backward, a row at a time
-        for (int rr = 0; rr < 16; rr += kRowsAtOnce) {
+        for (int rr = 0; rr < RW; rr += kRowsAtOnce) {
             float4 x[kRowsAtOnce][LV], dv[kRowsAtOnce][LV];
 #pragma unroll
             for (int q = 0; q < kRowsAtOnce; ++q) {
@@ -414,11 +418,11 @@ int check(const HsnwGate* s, int64_t slots, const char* what) {
 int64_t outputs_of(int d) { return static_cast<int64_t>(d) * 4 * d + 4 * d + d; }
 int64_t packed_bytes(int d) { return (static_cast<int64_t>(d) * 4 * d * 2 + 255) / 256 * 256; }
 
-// The backward's blocks: two an SM up to d = 32, one at d = 64 (134 KB of shared memory, 203 registers a thread); every
-// block the same number of tiles where the tiles allow it.
+// The backward's blocks: two an SM, every block the same number of tiles where the tiles allow it.
 int64_t bwd_blocks(int d, int64_t slots, int sms) {
-    const int64_t tiles = std::max<int64_t>(1, (slots + kTile - 1) / kTile);
-    const int64_t cap = static_cast<int64_t>(sms) * (d >= 64 ? 1 : 2);
+    const int64_t tiles = std::max<int64_t>(1, (slots + kTileB - 1) / kTileB);
+    const int64_t cap = static_cast<int64_t>(sms) * 2;
+    (void)d;
     const int64_t rounds = (tiles + cap - 1) / cap;
     return (tiles + rounds - 1) / rounds;
 }
