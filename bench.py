@@ -1279,7 +1279,7 @@ def run_gate(args, c: dict, name: str) -> None:
         "config": {"workload": WORKLOADS[name], "l2": "the pass's tensors (300 MB) are larger than L2",
                    "forward_ms": fwd_ms, "backward_ms": bwd_ms, "step_ms": spread(each),
                    "torch_rmsnorm_linear_sigmoid_autocast_autograd_ms": spread(torch_each)},
-        "gpu_launches": 5 * args.steps,
+        "gpu_launches": 3 * args.steps,
         "roofline": {"bound": "hbm", "kernel": "k_gate_fwd + k_gate_bwd", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": None, "peak_source": "measured" if peaks else "fallback",
                      "forward": {"achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9, "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak},

@@ -47,21 +47,6 @@ struct GateShape {
     static constexpr size_t bwd_bytes = sizeof(uint32_t) * (kTileB * PWF + kTileB * PWD + F * PWD) + sizeof(float) * (F + kTileB + 8 * (F + D));
 };
 
-// wb [d][2 d] words: (W[j][2 w], W[j][2 w + 1]); wtb [4 d][d / 2] words: (W[2 w][f], W[2 w + 1][f]).
-__global__ void k_gate_pack(const float* __restrict__ w, int d, uint32_t* __restrict__ wb, uint32_t* __restrict__ wtb) {
-    const int F = 4 * d;
-    const int e = static_cast<int>(blockIdx.x) * blockDim.x + static_cast<int>(threadIdx.x);
-    if (e >= d * F / 2) return;
-    if (wb) {
-        const float2 v = __ldg(reinterpret_cast<const float2*>(w) + e);
-        wb[e] = pack_bf16(v.x, v.y);
-    }
-    if (wtb) {
-        const int f = e / (d / 2), j2 = e - f * (d / 2);
-        wtb[e] = pack_bf16(__ldg(w + (2 * j2) * F + f), __ldg(w + (2 * j2 + 1) * F + f));
-    }
-}
-
 __device__ __forceinline__ float warp_total(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -76,7 +61,7 @@ __device__ __forceinline__ float4 ld4_or_zero(const float* base, bool on) {
 
 template <int D>
 __global__ void __launch_bounds__(kThreads)
-k_gate_fwd(const uint32_t* __restrict__ wb, const float* __restrict__ norm_w, const float* __restrict__ gate_b, float eps,
+k_gate_fwd(const float* __restrict__ gate_w, const float* __restrict__ norm_w, const float* __restrict__ gate_b, float eps,
            const float* __restrict__ v_raw, int64_t slots, float* __restrict__ v_out, float* __restrict__ rms_out,
            float* __restrict__ gp_out, float* __restrict__ b_out) {
     using S = GateShape<D>;
@@ -88,9 +73,10 @@ k_gate_fwd(const uint32_t* __restrict__ wb, const float* __restrict__ norm_w, co
     float* GB = NW + F;                                             // [D] the bias as bf16 values
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int64_t first = static_cast<int64_t>(blockIdx.x) * kTile;
-    for (int e = tid; e < D * (F / 8); e += kThreads) {   // 16 bytes at a time
-        const int j = e / (F / 8), q = e - j * (F / 8);
-        *reinterpret_cast<uint4*>(Ws + j * PWF + 4 * q) = __ldg(reinterpret_cast<const uint4*>(wb) + e);
+    for (int e = tid; e < D * (F / 4); e += kThreads) {   // four weights at a time
+        const int j = e / (F / 4), q = e - j * (F / 4);
+        const float4 w4 = __ldg(reinterpret_cast<const float4*>(gate_w) + e);
+        *reinterpret_cast<uint2*>(Ws + j * PWF + 2 * q) = make_uint2(pack_bf16(w4.x, w4.y), pack_bf16(w4.z, w4.w));
     }
     for (int e = tid; e < F; e += kThreads) NW[e] = __ldg(norm_w + e);
     for (int e = tid; e < D; e += kThreads) GB[e] = bf16r(__ldg(gate_b + e));
@@ -168,7 +154,7 @@ k_gate_fwd(const uint32_t* __restrict__ wb, const float* __restrict__ norm_w, co
 // `partial` [blocks][D F + F + D]: the block's shares of d_W_gate, of the gain's gradient and of d_b_gate.
 template <int D>
 __global__ void __launch_bounds__(kThreads, 2)   // two blocks an SM: the d_W_gate accumulators leave the registers between products
-k_gate_bwd(const uint32_t* __restrict__ wtb, const float* __restrict__ norm_w, float eps, const float* __restrict__ v_raw,
+k_gate_bwd(const float* __restrict__ gate_w, const float* __restrict__ norm_w, float eps, const float* __restrict__ v_raw,
            const float* __restrict__ gate_pre, const float* __restrict__ d_v_units, const float* __restrict__ d_b, int64_t slots,
            float* __restrict__ d_v_raw, float* __restrict__ partial) {
     using S = GateShape<D>;
@@ -182,9 +168,9 @@ k_gate_bwd(const uint32_t* __restrict__ wtb, const float* __restrict__ norm_w, f
     float* RMS = NW + F;                                            // [kTileB]
     float* RS = RMS + kTileB;                                        // [8][F + D] the warps' shares at the end
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    for (int e = tid; e < F * (D / 8); e += kThreads) {   // 16 bytes at a time
-        const int f = e / (D / 8), q = e - f * (D / 8);
-        *reinterpret_cast<uint4*>(WT + f * PWD + 4 * q) = __ldg(reinterpret_cast<const uint4*>(wtb) + e);
+    for (int e = tid; e < (D / 2) * F; e += kThreads) {   // a pair of the gate's rows at a time, f along the lanes
+        const int j2 = e / F, f = e - j2 * F;
+        WT[f * PWD + j2] = pack_bf16(__ldg(gate_w + (2 * j2) * F + f), __ldg(gate_w + (2 * j2 + 1) * F + f));
     }
     for (int e = tid; e < F; e += kThreads) NW[e] = __ldg(norm_w + e);
     float dw[TPW][4];
@@ -411,12 +397,11 @@ int check(const HsnwGate* s, int64_t slots, const char* what) {
     if (!s->prod_bf16) return hsnw_fail(HSNW_E_UNSUPPORTED, "gate: float32 products are not taken here");
     if (s->d != 16 && s->d != 32 && s->d != 64) return hsnw_fail(HSNW_E_UNSUPPORTED, "gate: d must be 16, 32 or 64");
     if (!(s->norm_eps >= 0.0f)) return hsnw_fail(HSNW_E_ARG, "gate: negative or NaN norm_eps");
-    if (reinterpret_cast<uintptr_t>(s->gate_w) % 8) return hsnw_fail(HSNW_E_ARG, "gate: the weight must be 8-byte aligned");
+    if (reinterpret_cast<uintptr_t>(s->gate_w) % 16) return hsnw_fail(HSNW_E_ARG, "gate: the weight must be 16-byte aligned");
     return HSNW_OK;
 }
 
 int64_t outputs_of(int d) { return static_cast<int64_t>(d) * 4 * d + 4 * d + d; }
-int64_t packed_bytes(int d) { return (static_cast<int64_t>(d) * 4 * d * 2 + 255) / 256 * 256; }
 
 // The backward's blocks: two an SM, every block the same number of tiles where the tiles allow it.
 int64_t bwd_blocks(int d, int64_t slots, int sms) {
@@ -433,12 +418,9 @@ bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0;
 
 extern "C" int64_t hsnw_gate_scratch_bytes(const HsnwGate* gate, int64_t slots, int backward) {
     if (!gate || slots < 0 || gate->d < 16 || gate->d > 64) return 0;
-    int64_t bytes = packed_bytes(gate->d);
-    if (backward) {
-        const int sms = std::max(148, hsnw_sm_count_current());
-        bytes += (bwd_blocks(gate->d, slots, sms) * outputs_of(gate->d) * static_cast<int64_t>(sizeof(float)) + 255) / 256 * 256;
-    }
-    return bytes;
+    if (!backward) return 256;   // the forward keeps nothing between its launches
+    const int sms = std::max(148, hsnw_sm_count_current());
+    return (bwd_blocks(gate->d, slots, sms) * outputs_of(gate->d) * static_cast<int64_t>(sizeof(float)) + 255) / 256 * 256;
 }
 
 extern "C" int hsnw_gate_forward(const HsnwGate* gate, const float* v_raw, int64_t slots, float* v, float* rms, float* gate_pre, float* b,
@@ -452,13 +434,11 @@ extern "C" int hsnw_gate_forward(const HsnwGate* gate, const float* v_raw, int64
         return hsnw_fail(HSNW_E_ARG, "gate_forward: v_raw, v and scratch must be 16-byte aligned, gate_pre and b 8-byte");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     const int d = gate->d;
-    uint32_t* wb = static_cast<uint32_t*>(scratch);
     hsnw_profile_mark(HSNW_K_GATE_FWD, stream);
-    k_gate_pack<<<(d * 2 * d + 255) / 256, 256, 0, stream>>>(gate->gate_w, d, wb, nullptr);
     const unsigned tiles = static_cast<unsigned>((slots + kTile - 1) / kTile);
 #define HSNW_GATE_FWD(D) \
     case D: \
-        k_gate_fwd<D><<<tiles, kThreads, GateShape<D>::fwd_bytes, stream>>>(wb, gate->norm_weight, gate->gate_b, gate->norm_eps, v_raw, slots, \
+        k_gate_fwd<D><<<tiles, kThreads, GateShape<D>::fwd_bytes, stream>>>(gate->gate_w, gate->norm_weight, gate->gate_b, gate->norm_eps, v_raw, slots, \
                                                                           v, rms, gate_pre, b); \
         break
     switch (d) {
@@ -490,15 +470,13 @@ extern "C" int hsnw_gate_backward(const HsnwGate* gate, const float* v_raw, cons
     if (!aligned16(v_raw) || !aligned16(d_v_units) || !aligned16(d_v_raw) || !aligned16(scratch) || reinterpret_cast<uintptr_t>(gate_pre) % 8
         || reinterpret_cast<uintptr_t>(d_b) % 8)
         return hsnw_fail(HSNW_E_ARG, "gate_backward: v_raw, d_v_units, d_v_raw and scratch must be 16-byte aligned, gate_pre and d_b 8-byte");
-    uint32_t* wtb = static_cast<uint32_t*>(scratch);
-    float* partial = reinterpret_cast<float*>(static_cast<char*>(scratch) + packed_bytes(d));
+    float* partial = static_cast<float*>(scratch);
     const int blocks = static_cast<int>(bwd_blocks(d, slots, std::max(1, hsnw_sm_count_current())));
     hsnw_profile_mark(HSNW_K_GATE_BWD, stream);
-    k_gate_pack<<<(d * 2 * d + 255) / 256, 256, 0, stream>>>(gate->gate_w, d, nullptr, wtb);
 #define HSNW_GATE_BWD(D) \
     case D: \
         k_gate_bwd<D><<<static_cast<unsigned>(blocks), kThreads, GateShape<D>::bwd_bytes, stream>>>( \
-            wtb, gate->norm_weight, gate->norm_eps, v_raw, gate_pre, d_v_units, d_b, slots, d_v_raw, partial); \
+            gate->gate_w, gate->norm_weight, gate->norm_eps, v_raw, gate_pre, d_v_units, d_b, slots, d_v_raw, partial); \
         break
     switch (d) {
         HSNW_GATE_BWD(16);
