@@ -5,15 +5,16 @@
 // pass's gradient, once more backward; v and d_v_raw are written once: the pass is bound by those four tensors
 // (forward 32 d + 8 d + 4 bytes a slot, backward 48 d + 8 d), the gate's product is 8 d^2 flops a slot.
 //
-// A block takes tiles of 128 slots forward (a warp 16 of them) and of 64 backward. Everything row-wise (the norm and its backward, sigmoid) runs
-// with a warp on one row at a time and a lane on 4 consecutive features per 128, so global accesses are whole rows;
-// the products run on warp-level tensor-core tiles (mma_tiles.cuh) from bf16 copies of the tile in shared memory,
-// the gate's weight as packed bf16 pairs in shared memory too (read through L1 from global memory the products' B
-// fragments took a third of the forward's time). Backward, per tile: v and
-// d_gate_pre into shared memory; d_W_gate += d_gate_pre^T v (both read transposed, a warp keeps d * 4 d / 1024
-// accumulator tiles in registers over all of the block's tiles); d_gate_pre W_gate on the warp's own rows, written
-// as bf16 over the warp's rows of v (that sum IS a bf16 value in the reference); then the norm's backward row by row.
-// Blocks write their shares of the three parameter gradients once, a last kernel adds them in a fixed order.
+// A block takes tiles of 128 slots forward (a warp 16 of them) and of 64 backward (two blocks an SM). Everything
+// row-wise (the norm and its backward, sigmoid) runs with a warp on one row at a time and a lane on 4 consecutive
+// features per 128, so global accesses are whole rows, streamed; the products run on warp-level tensor-core tiles
+// (mma_tiles.cuh) from bf16 copies in shared memory of the tile and of the gate's weight, which every block converts
+// as it stages it (read through L1 from global memory, the products' B fragments took a third of the forward's time).
+// Backward, per tile: v and d_gate_pre into shared memory; d_W_gate += d_gate_pre^T v (both read transposed, a warp
+// keeps d * 4 d / 1024 accumulator tiles over all of the block's tiles); d_gate_pre W_gate (a warp 16 rows x half the
+// columns), written as bf16 over those rows of v (that sum IS a bf16 value in the reference); then the norm's backward
+// row by row. Blocks write their shares of the three parameter gradients once, a last kernel adds them in a fixed
+// order.
 #include "../../include/hsn_gate_b200.h"
 #include "../../include/hsn_window_b200.h"
 #include "common.cuh"

@@ -35,7 +35,8 @@ typedef struct HsnwGate {
     const float *norm_weight, *gate_w, *gate_b;
 } HsnwGate;
 
-/* Bytes of device scratch for `slots` slots (256-byte aligned); backward != 0: the backward call's. */
+/* Bytes of device scratch for `slots` slots (256-byte aligned); backward != 0: the backward call's (the blocks'
+ * shares of the parameter gradients). The forward keeps nothing between launches: 256 bytes. */
 int64_t hsnw_gate_scratch_bytes(const HsnwGate* gate, int64_t slots, int backward);
 
 /* v_raw [slots, 4 d] -> v [slots, 4 d], rms [slots], gate_pre [slots, d], b [slots, d]. */
