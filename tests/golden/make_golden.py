@@ -816,7 +816,9 @@ def make_replay(root: Path) -> None:
             d_c = torch.randn(c.shape, generator=gen).to(c.dtype)
             d_b = torch.randn(b.shape, generator=gen).to(b.dtype)
             params = dict(cell.named_parameters())
-            grads = torch.autograd.grad([c, b], [*leaves, seen["unit_out"], seen["v_raw"], seen["v_units"], *params.values()], [d_c, d_b], allow_unused=True,
+            graph = cell.graph
+            padded = graph._padded_weights()   # [N, D_max] float32, the window's cached tensor: the one the call used
+            grads = torch.autograd.grad([c, b], [*leaves, seen["unit_out"], seen["v_raw"], seen["v_units"], padded, *params.values()], [d_c, d_b], allow_unused=True,
                                         retain_graph=True)   # the window caches casts of the weights: the real call below shares them
             f32 = torch.float32
             out.update(u=_np(u), eps=_np(eps), h_read=_np(h_read), cells=sel.cell_idx.numpy(), units=sel.unit_idx.numpy(),
@@ -824,12 +826,13 @@ def make_replay(root: Path) -> None:
                        unit_out=_np(seen["unit_out"].to(f32)), d_u=_np(grads[0]), d_eps=_np(grads[1]), d_alpha=_np(grads[2]),
                        d_unit_out=_np(grads[3].to(f32)), cand_eps=np.array(float(cell.cand_norm.eps)),
                        v_raw=_np(seen["v_raw"]), v=_np(seen["v"].to(f32)), d_v_raw=_np(grads[4]), d_v_units=_np(grads[5].to(f32)),
-                       norm_eps=np.array(float(cell.norm.eps if cell.norm.eps is not None else torch.finfo(torch.float32).eps)))  # fmt: skip
+                       norm_eps=np.array(float(cell.norm.eps if cell.norm.eps is not None else torch.finfo(torch.float32).eps)),
+                       pad_src=graph._pad_src.numpy(), edge_w=_np(padded), d_edge_w=_np(grads[6]))  # fmt: skip
             print("   dtypes: v_raw", seen["v_raw"].dtype, "v", seen["v"].dtype, "v_units", seen["v_units"].dtype, "d_v_units", grads[5].dtype,
                   "gate_pre", rec["gate_pre"].dtype, "b", b.dtype)
             for key, value in rec.items():
                 out["rec_" + key] = _np(value.to(f32))
-            for (key, value), grad in zip(params.items(), grads[6:], strict=True):
+            for (key, value), grad in zip(params.items(), grads[7:], strict=True):
                 out["w_" + key] = _np(value)
                 if grad is not None:
                     out["g_" + key] = _np(grad.to(f32))

@@ -472,3 +472,28 @@ def test_replay_norm_and_gate_equal_the_reference(name: str) -> None:
         np.testing.assert_allclose(got, want, rtol=0, atol=tol * float(np.abs(want).max()), err_msg=what)
     if name == "bf16":   # here nothing falls on a rounding boundary: the bfloat16 parts equal the reference's to the bit
         assert np.array_equal(gate_pre, z["rec_gate_pre"].reshape(-1, d)) and np.array_equal(grads[2], z["g_gate.weight"])
+
+
+@pytest.mark.parametrize("name", ["f32", "cut_f32", "bf16", "wide_bf16"])
+def test_replay_messages_equal_the_reference(name: str) -> None:
+    """The gathered inputs ``v_raw = [u; eps; h[cell]; m]`` of ``replay_sparse`` with the messages ``m`` over the cell's
+    in-neighbours, and autograd's gradients of ``u``, ``eps``, the padded edge weights and ``V``: under bf16 autocast to
+    the bit but for the edge weights' gradient, which the reference accumulates slot by slot in bfloat16 (within one
+    bfloat16 step); float32 to rounding."""
+    from oracle import messages_oracle as M
+
+    z = load_golden(f"replay_{name}")
+    bf = "bf16" in name
+    cells = np.where(z["valid"], z["cells"], 0)
+    tables = (cells, z["pad_src"], z["edge_w"], z["w_V.weight"])
+    v_raw = M.forward_messages(z["u"], z["eps"], z["h_read"], *tables, bf16=bf)
+    grads = M.backward_messages(z["h_read"], *tables, z["d_v_raw"], bf16=bf)
+    d = z["u"].shape[-1]
+    assert v_raw.dtype == np.float32 and np.array_equal(v_raw[..., : 3 * d], z["v_raw"][..., : 3 * d])
+    np.testing.assert_allclose(v_raw, z["v_raw"], rtol=0, atol=1e-6)
+    np.testing.assert_allclose(v_raw[..., 3 * d :], z["rec_m"], rtol=0, atol=1e-6)
+    for got, key, tol in zip(grads, ("d_u", "d_eps", "d_edge_w", "g_V.weight"), (1e-6, 1e-6, 2.0**-7 if bf else 1e-6, 1e-6), strict=True):
+        assert got.shape == z[key].shape and got.dtype == np.float32, key
+        np.testing.assert_allclose(got, z[key], rtol=0, atol=tol * float(np.abs(z[key]).max()), err_msg=key)
+    if bf:
+        assert np.array_equal(v_raw, z["v_raw"]) and np.array_equal(grads[3], z["g_V.weight"])
