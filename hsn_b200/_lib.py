@@ -136,6 +136,10 @@ class HsnwGate(Structure):
                 ("gate_w", c_void_p), ("gate_b", c_void_p)]  # fmt: skip
 
 
+class HsnwMessages(Structure):
+    _fields_ = [(n, c_int32) for n in ("d", "n_cells", "degree", "k", "prod_bf16", "reserved")] + [(n, c_void_p) for n in ("v_w", "edge_w", "pad_src")]
+
+
 class HsnwPrologue(Structure):
     _fields_ = (
         [(n, c_int32) for n in PROLOGUE_INTS]
@@ -181,6 +185,10 @@ SYMBOLS: dict[str, tuple[object, list[object]]] = {
                                    c_int64, c_void_p]),
     "hsnw_scorer_logits_backward": (c_int, [POINTER(HsnwScorer), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
                                             c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "hsnw_messages_scratch_bytes": (c_int64, [POINTER(HsnwMessages), c_int64]),
+    "hsnw_messages_forward": (c_int, [POINTER(HsnwMessages), c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+    "hsnw_messages_backward": (c_int, [POINTER(HsnwMessages), c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_int64, c_void_p]),
     "hsnw_gate_scratch_bytes": (c_int64, [POINTER(HsnwGate), c_int64, c_int]),
     "hsnw_gate_forward": (c_int, [POINTER(HsnwGate), c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "hsnw_gate_backward": (c_int, [POINTER(HsnwGate), c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,

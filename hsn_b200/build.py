@@ -23,7 +23,7 @@ CSRC = PACKAGE / "csrc"
 LIB_DIR = PACKAGE / "lib"
 LIBRARY = LIB_DIR / "libhsn_window_b200.so"
 MANIFEST = LIB_DIR / "window_build.json"
-SOURCES = ("api.cu", "ops_kernels.cu", "sweep_kernels.cu", "window_fwd.cu", "window_bwd.cu", "window_rows.cu", "window_rows_bwd.cu", "selftest.cu", "prologue.cu", "trainer.cu", "decode.cu", "units.cu", "scorer.cu", "tail.cu", "gate.cu")
+SOURCES = ("api.cu", "ops_kernels.cu", "sweep_kernels.cu", "window_fwd.cu", "window_bwd.cu", "window_rows.cu", "window_rows_bwd.cu", "selftest.cu", "prologue.cu", "trainer.cu", "decode.cu", "units.cu", "scorer.cu", "tail.cu", "gate.cu", "messages.cu")
 HEADERS = ("common.cuh", "select.cuh", "stage.cuh", "umma.cuh", "host_util.h", "rows.cuh", "mma_tiles.cuh")
 ARCH = ("-gencode", "arch=compute_100a,code=sm_100a")
 
@@ -40,7 +40,7 @@ def _sha(path: Path) -> str:
 
 
 def source_hashes() -> dict[str, str]:
-    files = [CSRC / n for n in (*SOURCES, *HEADERS)] + [ROOT / "include" / "hsn_window_b200.h", ROOT / "include" / "hsn_trainer_b200.h", ROOT / "include" / "hsn_units_b200.h", ROOT / "include" / "hsn_scorer_b200.h", ROOT / "include" / "hsn_tail_b200.h", ROOT / "include" / "hsn_gate_b200.h"]
+    files = [CSRC / n for n in (*SOURCES, *HEADERS)] + [ROOT / "include" / "hsn_window_b200.h", ROOT / "include" / "hsn_trainer_b200.h", ROOT / "include" / "hsn_units_b200.h", ROOT / "include" / "hsn_scorer_b200.h", ROOT / "include" / "hsn_tail_b200.h", ROOT / "include" / "hsn_gate_b200.h", ROOT / "include" / "hsn_messages_b200.h"]
     return {str(f.relative_to(ROOT)): _sha(f) for f in files}
 
 

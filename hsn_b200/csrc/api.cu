@@ -158,6 +158,7 @@ extern "C" int hsnw_prepare(int device) {
     hsnw_scorer_set_attributes();
     hsnw_tail_set_attributes();
     hsnw_gate_set_attributes();
+    hsnw_messages_set_attributes();
     const cudaError_t status = cudaGetLastError();
     if (previous >= 0 && previous != device) cudaSetDevice(previous);
     if (!attributes_ok) return HSNW_E_CUDA;  // the message names the kernel
@@ -258,7 +259,7 @@ namespace {
 struct ProfileMark { cudaEvent_t event; int kind; };
 std::vector<ProfileMark> profile_marks;
 cudaStream_t profile_stream = nullptr;
-const char* const kind_names[HSNW_K_KINDS] = {"init", "pre", "front", "row", "unit", "update", "head", "mid", "tail_head", "rows_fwd", "rows_bwd", "prologue", "decode", "units_fwd", "units_bwd", "scorer_fwd", "scorer_bwd", "tail_fwd", "tail_bwd", "gate_fwd", "gate_bwd"};
+const char* const kind_names[HSNW_K_KINDS] = {"init", "pre", "front", "row", "unit", "update", "head", "mid", "tail_head", "rows_fwd", "rows_bwd", "prologue", "decode", "units_fwd", "units_bwd", "scorer_fwd", "scorer_bwd", "tail_fwd", "tail_bwd", "gate_fwd", "gate_bwd", "msg_fwd", "msg_bwd"};
 }  // namespace
 
 void hsnw_profile_mark_slow(int kind, cudaStream_t stream) {

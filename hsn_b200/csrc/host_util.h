@@ -29,6 +29,7 @@ void hsnw_units_set_attributes();
 void hsnw_scorer_set_attributes();
 void hsnw_tail_set_attributes();
 void hsnw_gate_set_attributes();
+void hsnw_messages_set_attributes();
 struct HsnwBackward;
 struct HsnwModel;
 struct HsnwForward;
@@ -50,7 +51,7 @@ void hsnw_set_path(int path);
 enum HsnwKernelKind {
     HSNW_K_INIT = 0, HSNW_K_PRE, HSNW_K_FRONT, HSNW_K_ROW, HSNW_K_UNIT, HSNW_K_UPDATE,
     HSNW_K_HEAD, HSNW_K_MID, HSNW_K_TAIL_HEAD, HSNW_K_ROWS_FWD, HSNW_K_ROWS_BWD, HSNW_K_PROLOGUE, HSNW_K_DECODE, HSNW_K_UNITS_FWD, HSNW_K_UNITS_BWD,
-    HSNW_K_SCORER_FWD, HSNW_K_SCORER_BWD, HSNW_K_TAIL_FWD, HSNW_K_TAIL_BWD, HSNW_K_GATE_FWD, HSNW_K_GATE_BWD, HSNW_K_KINDS
+    HSNW_K_SCORER_FWD, HSNW_K_SCORER_BWD, HSNW_K_TAIL_FWD, HSNW_K_TAIL_BWD, HSNW_K_GATE_FWD, HSNW_K_GATE_BWD, HSNW_K_MSG_FWD, HSNW_K_MSG_BWD, HSNW_K_KINDS
 };
 extern bool g_hsnw_profile_on;
 void hsnw_profile_mark_slow(int kind, cudaStream_t stream);

@@ -33,6 +33,27 @@ __device__ __forceinline__ void ldmatrix_x2_trans(uint32_t (&r)[2], const void* 
     asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(at));
 }
 
+// acc[nt] = the warp's 16 rows r0.. of A (bf16 rows of pitch PWA words in shared memory, K = 16 KS along a row) times
+// B, with B(k, n) read as the packed pair (k, k + 1) of row n of Bs (pitch PWB words): Bs holds the right-hand side
+// with its summed index along a row.
+template <int NT, int KS, int PWA, int PWB>
+__device__ __forceinline__ void warp_rows_product(float (&acc)[NT][4], const uint32_t* As, const uint32_t* Bs, int r0, int g, int t) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[nt][i] = 0.0f;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+        uint32_t a[4];
+        a[0] = As[(r0 + g) * PWA + 8 * ks + t];
+        a[1] = As[(r0 + g + 8) * PWA + 8 * ks + t];
+        a[2] = As[(r0 + g) * PWA + 8 * ks + 4 + t];
+        a[3] = As[(r0 + g + 8) * PWA + 8 * ks + 4 + t];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) mma_bf16(acc[nt], a, Bs[(8 * nt + g) * PWB + 8 * ks + t], Bs[(8 * nt + g) * PWB + 8 * ks + 4 + t]);
+    }
+}
+
 __device__ __forceinline__ float sum4_lanes(float v) {   // over the 4 lanes that share a row of a fragment
     v += __shfl_xor_sync(0xffffffffu, v, 1);
     v += __shfl_xor_sync(0xffffffffu, v, 2);

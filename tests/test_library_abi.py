@@ -22,7 +22,7 @@ def lib() -> ctypes.CDLL:
 
 
 def test_every_declared_symbol_is_exported(lib: ctypes.CDLL) -> None:
-    text = "".join((HEADER.parent / name).read_text() for name in ("hsn_window_b200.h", "hsn_trainer_b200.h", "hsn_units_b200.h", "hsn_scorer_b200.h", "hsn_tail_b200.h", "hsn_gate_b200.h"))
+    text = "".join((HEADER.parent / name).read_text() for name in ("hsn_window_b200.h", "hsn_trainer_b200.h", "hsn_units_b200.h", "hsn_scorer_b200.h", "hsn_tail_b200.h", "hsn_gate_b200.h", "hsn_messages_b200.h"))
     declared = set(re.findall(r"\b(hsnw_[a-z_]+)\s*\(", text))
     assert declared, "no entry points found in the header"
     assert declared == set(_lib.SYMBOLS), declared ^ set(_lib.SYMBOLS)
@@ -41,6 +41,7 @@ def test_structures_match_the_header() -> None:
     assert ctypes.sizeof(_lib.HsnwScorer) == 6 * 4 + 2 * 8 and _lib.HsnwScorer.weight.offset == 24
     assert ctypes.sizeof(_lib.HsnwTail) == 4 * 4 + 2 * 8 and _lib.HsnwTail.w_out.offset == 16
     assert ctypes.sizeof(_lib.HsnwGate) == 4 * 4 + 3 * 8 and _lib.HsnwGate.norm_weight.offset == 16
+    assert ctypes.sizeof(_lib.HsnwMessages) == 6 * 4 + 3 * 8 and _lib.HsnwMessages.v_w.offset == 24
 
 
 def test_version_and_errors_without_a_device(lib: ctypes.CDLL) -> None:
