@@ -59,7 +59,10 @@ CONFIGS["scorer"] = dict(R=32 * 256, N=256, d=64, M=8, S=9, scorer=True)
 CONFIGS["tail"] = dict(slots=32 * 256 * 8, d=64, tail=True)
 # the cell norm and the gate of the replay's cell pass (not the headline): every slot of the c2 window, forward and backward
 CONFIGS["gate"] = dict(slots=32 * 256 * 8, d=64, gate=True)
+# the messages and the gathered inputs of the replay's cell pass (not the headline): every slot of the c2 window
+CONFIGS["messages"] = dict(R=32 * 256, N=256, d=64, K=8, D=4, messages=True)
 WORKLOADS = {
+    "messages": "the replay's messages + gathered inputs over a window's 8192 positions x 8 slots (N 256, d 64, 4 in-neighbours), bf16 products, forward + backward",
     "gate": "the replay's cell norm + gate + sigmoid over a window's 65,536 slots (4d 256 -> d 64), bf16 products, forward + backward",
     "tail": "the replay's W_out + candidate norm + weighted tanh over a window's 65,536 slots (d 64), bf16 products, forward + backward",
     "scorer": "the replay's scorer logits over a window's 8192 positions x 256 cells (d 64, 8 units, 9 scalars), bf16 products, forward + weight gradients",
@@ -290,7 +293,7 @@ def run_reference(args, c: dict, name: str) -> None:
 
 
 def run_side_reference(args, c: dict, name: str) -> None:
-    """`--impl reference` for the side configurations `units`, `scorer`, `tail` and `gate`: the numpy restatement of the pass
+    """`--impl reference` for the side configurations `units`, `scorer`, `tail`, `gate` and `messages`: the numpy restatement of the pass
     (forward + backward, bf16 rounding emulated) on a sample of the workload, on the host's cores."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
@@ -308,6 +311,19 @@ def run_side_reference(args, c: dict, name: str) -> None:
             _, pre = U.forward_grouped(v, idx, *bank, bf16=True)
             U.backward_grouped(v, idx, *bank, pre, cot, bf16=True)
             return n
+    elif name == "messages":
+        from oracle import messages_oracle as MO
+
+        n, N, d, K, D = 128, c["N"], c["d"], c["K"], c["D"]
+        mu, me, mh, mv, mdv = f(n, d), f(n, d), f(n, N, d, scale=0.5), f(d, d, scale=d**-0.5), f(n, K, 4 * d)
+        mcells = np.stack([rng.permutation(N)[:K] for _ in range(n)]).astype(np.int64)
+        msrc, mw = rng.integers(0, N, (N, D)).astype(np.int64), rng.random((N, D)).astype(np.float32)
+        unit, sample = "slots/s", f"{n} of the window's positions ({n * K} slots) per step"
+
+        def step():
+            MO.forward_messages(mu, me, mh, mcells, msrc, mw, mv, bf16=True)
+            MO.backward_messages(mh, mcells, msrc, mw, mv, mdv, bf16=True)
+            return n * K
     elif name == "gate":
         from oracle import gate_oracle as GO
 
@@ -350,7 +366,7 @@ def run_side_reference(args, c: dict, name: str) -> None:
     done = sum(step() for _ in range(args.steps))
     sec = time.perf_counter() - t0
     value = done / sec
-    metric = {"units": "grouped unit pass pairs/s (forward + backward)", "tail": TAIL_METRIC, "gate": GATE_METRIC}.get(name, "scorer logits cells/s (forward + weight gradients)")
+    metric = {"units": "grouped unit pass pairs/s (forward + backward)", "tail": TAIL_METRIC, "gate": GATE_METRIC, "messages": MSG_METRIC}.get(name, "scorer logits cells/s (forward + weight gradients)")
     print(json.dumps({
         "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": sec / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -1288,6 +1304,117 @@ def run_gate(args, c: dict, name: str) -> None:
         "cpu_baseline": cpu, "clocks": clocks_summary(clock_lines, 0)}))  # fmt: skip
 
 
+MSG_METRIC = "replay messages slots/s (forward + backward)"
+
+
+def run_messages(args, c: dict, name: str) -> None:
+    """`--config messages`: `hsnw_messages_forward` + `hsnw_messages_backward` over the benchmark window's slots through
+    the C ABI on buffers made once; a step = both. Beside it the CPU restatement on a sample of the positions, and the
+    reference's lines in PyTorch on the same device."""
+    import ctypes
+
+    import torch
+
+    from hsn_b200 import _lib
+    from hsn_b200.kernels.messages import messages_backward, messages_forward
+    from hsn_b200.window import launch_profile
+
+    world, rank, local, dev = dist_setup()
+    R, N, d, K, D = c["R"], c["N"], c["d"], c["K"], c["D"]
+    gen = torch.Generator(device=dev).manual_seed(0)
+    f = lambda *shape, scale=1.0: torch.randn(*shape, generator=gen, device=dev) * scale  # noqa: E731
+    u, eps, h = f(R, d, scale=0.7), f(R, d, scale=0.4), f(R, N, d, scale=0.5)
+    cells = torch.rand(R, N, generator=gen, device=dev).argsort(dim=1)[:, :K].contiguous()
+    pad_src = torch.randint(0, N, (N, D), generator=gen, device=dev)
+    edge_w = torch.softmax(f(N, D), dim=1)
+    v_w, d_v_raw = f(d, d, scale=d**-0.5), f(R, K, 4 * d)
+    lib = _lib.library()
+    if not lib.hsnw_prepared(local):
+        _lib.check(lib.hsnw_prepare(local))
+    st = _lib.HsnwMessages(d=d, n_cells=N, degree=D, k=K, prod_bf16=1, reserved=0, v_w=v_w.data_ptr(), edge_w=edge_w.data_ptr(),
+                           pad_src=pad_src.data_ptr())  # fmt: skip
+    v_raw = torch.empty(R, K, 4 * d, device=dev)
+    d_u, d_eps, d_ew, d_vw = torch.empty(R, d, device=dev), torch.empty(R, d, device=dev), torch.empty(N, D, device=dev), torch.empty(d, d, device=dev)
+    need = int(lib.hsnw_messages_scratch_bytes(ctypes.byref(st), R))
+    scratch = torch.empty(need, dtype=torch.uint8, device=dev)
+    stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+    def step(i):   # (the recorded state alone, 537 MB, is four times L2)
+        _lib.check(lib.hsnw_messages_forward(ctypes.byref(st), u.data_ptr(), eps.data_ptr(), h.data_ptr(), cells.data_ptr(), R, v_raw.data_ptr(), stream))
+        _lib.check(lib.hsnw_messages_backward(ctypes.byref(st), h.data_ptr(), cells.data_ptr(), d_v_raw.data_ptr(), R, d_u.data_ptr(), d_eps.data_ptr(),
+                                              d_ew.data_ptr(), d_vw.data_ptr(), scratch.data_ptr(), need, stream))  # fmt: skip
+
+    for i in range(max(3, args.warmup)):
+        step(i)
+    want = messages_forward(u, eps, h, cells, pad_src, edge_w, v_w)
+    wantb = messages_backward(h, cells, pad_src, edge_w, v_w, d_v_raw)
+    if not (torch.equal(v_raw, want) and all(torch.equal(a, w) for a, w in zip((d_u, d_eps, d_ew, d_vw), wantb, strict=True))):
+        raise SystemExit("bench.py --config messages: the direct calls and the Python wrappers disagree")
+    clock_lines: list = []
+    stop = threading.Event()
+    threading.Thread(target=sample_clocks, args=(stop, clock_lines), daemon=True).start()
+    fwd_ms = bwd_ms = 0.0
+    for i in range(5):
+        with launch_profile() as prof:
+            step(i)
+        fwd_ms += prof.ms.get("msg_fwd", 0.0) / 5
+        bwd_ms += prof.ms.get("msg_bwd", 0.0) / 5
+    ms_total, each = timed_steps(step, args.steps, torch.cuda.synchronize)
+    stop.set()
+    lin = torch.nn.Linear(d, d, bias=False, device=dev)
+    ew = edge_w.clone().requires_grad_(True)
+
+    def torch_step(i):
+        ur, er = u.clone().requires_grad_(True), eps.clone().requires_grad_(True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            index = pad_src[cells].reshape(R, K * D, 1).expand(R, K * D, d)
+            sources = lin(h.gather(1, index)).reshape(R, K, D, d)
+            m = (sources * ew.to(sources.dtype)[cells][..., None]).sum(dim=2)
+        h_sel = h.gather(1, cells[..., None].expand(R, K, d))
+        out = torch.cat([ur[:, None].expand(R, K, d), er[:, None].expand(R, K, d), h_sel, m.to(torch.float32)], dim=-1)
+        out.backward(d_v_raw)
+        lin.weight.grad = ew.grad = None
+
+    for i in range(3):
+        torch_step(i)
+    torch_total, torch_each = timed_steps(torch_step, max(3, args.steps // 4), torch.cuda.synchronize)
+    cpu = None
+    if not args.no_cpu_baseline:
+        from oracle import messages_oracle as MO
+
+        n = 128
+        hu, he, hh, hc, hs, hw, hv, hd = (t.cpu().numpy() for t in (u[:n], eps[:n], h[:n], cells[:n], pad_src, edge_w, v_w, d_v_raw[:n]))
+        t0 = time.perf_counter()
+        reps = 0
+        while time.perf_counter() - t0 < 10.0:
+            MO.forward_messages(hu, he, hh, hc, hs, hw, hv, bf16=True)
+            MO.backward_messages(hh, hc, hs, hw, hv, hd, bf16=True)
+            reps += 1
+        cpu = {"value": reps * n * K / (time.perf_counter() - t0), "unit": "slots/s", "cores": blas_threads(), "kind": "port",
+               "sample": f"{reps} passes of forward + backward over {n} of the window's positions (numpy restatement, bf16 rounding emulated)"}
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    P = float(R) * K
+    fwd_bytes = P * (4 * d * (D + 1) + 8 + 16 * d) + R * 8.0 * d     # D + 1 rows of the state and the cell index read, v_raw written; u, eps a row
+    bwd_bytes = P * (4 * d * D + 8 + 16 * d) + R * 8.0 * d           # D rows of the state, the cell index, d_v_raw read; d_u, d_eps written
+    kernel_ms = fwd_ms + bwd_ms
+    achieved = (fwd_bytes + bwd_bytes) / (kernel_ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": MSG_METRIC, "value": P / (kernel_ms * 1e-3), "unit": "slots/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": kernel_ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16 products, f32 tensors", "data": "synthetic",
+        "config": {"workload": WORKLOADS[name], "l2": "the recorded state (537 MB) is larger than L2",
+                   "forward_ms": fwd_ms, "backward_ms": bwd_ms, "step_ms": spread(each),
+                   "torch_gather_linear_sum_cat_autocast_autograd_ms": spread(torch_each)},
+        "gpu_launches": 5 * args.steps,
+        "roofline": {"bound": "hbm", "kernel": "k_msg_fwd + k_msg_bwd", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": None, "peak_source": "measured" if peaks else "fallback",
+                     "forward": {"achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9, "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak},
+                     "backward": {"achieved": bwd_bytes / (bwd_ms * 1e-3) / 1e9, "frac": bwd_bytes / (bwd_ms * 1e-3) / 1e9 / peak},
+                     "how": "per slot 4 d (D + 1) + 8 + 16 d bytes forward (the cell's and its D in-neighbours' rows of the state, the cell index; v_raw written) and 4 d D + 8 + 16 d backward (the in-neighbours' rows, the cell index, d_v_raw) / the calls' event time, mean of five profiled steps"},
+        "cpu_baseline": cpu, "clocks": clocks_summary(clock_lines, 0)}))  # fmt: skip
+
+
 def run_trainer_sharded(args, c: dict, name: str, world: int, rank: int, dev) -> None:
     """`--config adamw --gpus N`: the same parameter vector replicated on N ranks, a step = the gradient exchange
     and the AdamW step as ONE kernel per rank over peer memory (`ShardedAdamW`: reduce-scatter, step, all-gather),
@@ -1378,7 +1505,7 @@ def main() -> None:
         if args.steps == 100:
             args.steps = 20
         run_decoder(args, c, args.config)
-    elif c.get("units") or c.get("scorer") or c.get("tail") or c.get("gate"):
+    elif c.get("units") or c.get("scorer") or c.get("tail") or c.get("gate") or c.get("messages"):
         if args.steps == 100:
             args.steps = 20
         if args.impl == "reference":
@@ -1389,6 +1516,8 @@ def main() -> None:
             run_tail(args, c, args.config)
         elif c.get("gate"):
             run_gate(args, c, args.config)
+        elif c.get("messages"):
+            run_messages(args, c, args.config)
         else:
             run_scorer(args, c, args.config)
     elif c.get("trainer"):

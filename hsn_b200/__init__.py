@@ -7,10 +7,10 @@ C ABI, with the reference's Python interface on top.
   streaming step, decoder).
 * :mod:`hsn_b200.kernels.trainer` mirrors ``hsn.kernels.trainer``; :mod:`hsn_b200.parallel` holds the fused
   gradient exchange + AdamW; :mod:`hsn_b200.state` the carried state's snapshots and checkpoint payload.
-* :mod:`hsn_b200.kernels.units`, :mod:`hsn_b200.kernels.scorer`, :mod:`hsn_b200.kernels.tail` and
-  :mod:`hsn_b200.kernels.gate` are four pieces of the split window's replay: ``UnitBank.forward_grouped``,
-  ``_scorer_logits``, the end of ``replay_sparse`` (``W_out``, candidate norm, ``tanh``) and its cell norm and gate, as
-  autograd functions.
+* :mod:`hsn_b200.kernels.units`, :mod:`hsn_b200.kernels.scorer`, :mod:`hsn_b200.kernels.tail`,
+  :mod:`hsn_b200.kernels.gate` and :mod:`hsn_b200.kernels.messages` are five pieces of the split window's replay:
+  ``_scorer_logits``, and ``PDGCell.replay_sparse`` in four (messages and gathered inputs, cell norm and gate,
+  ``UnitBank.forward_grouped``, ``W_out`` + candidate norm + ``tanh``), as autograd functions.
 * :mod:`hsn_b200.build` compiles ``csrc`` into ``lib/libhsn_window_b200.so``.
 
 Importing the package neither initialises CUDA nor loads the library.
