@@ -3,7 +3,8 @@
 // (reference python/hsn/model/cell.py:698-705) with autograd's gradients of u, eps, V and the padded edge weights; the
 // state is a constant of the replay. A slot reads its cell's row and the rows of up to four in-neighbours from the
 // recorded state (256 bytes each at d = 64, wherever the router sent it) and writes 4 d floats: the pass is bound by
-// those rows and by v_raw (forward 16 d degree + 8 d... bytes a slot), V's product is 2 d^2 flops a neighbour.
+// those rows and by v_raw (forward 4 d (degree + 1) + 8 + 16 d bytes a slot, backward 4 d degree + 8 + 16 d), V's
+// product is 2 d^2 flops a neighbour.
 //
 // A block takes tiles of 32 slots = 128 (slot, neighbour) rows, gathered as bf16 into shared memory; a warp owns 16
 // rows = 4 slots, V's product is a warp-level tensor-core tile (mma_tiles.cuh) and the weighted sum over a slot's four
