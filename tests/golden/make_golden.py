@@ -32,8 +32,10 @@ inputs and outputs of every function on the window path as ``.npz`` files:
                         and the reference's digests.
 * ``replay_*.npz``      ``PDGCell.replay_sparse`` (``python/hsn/model/cell.py:655-734``) as the split window's replay
                         calls it (``python/hsn/train/split.py:657``), on that call's own arguments: inputs, results,
-                        the record, ``W_out``'s input and its gradient, and autograd's gradients of the inputs and of
-                        every cell parameter for seeded cotangents of ``(c, b)``.
+                        the record, the values at the cuts between its steps (the cell norm's input and output and
+                        ``W_out``'s input with their gradients, the unit pass's own gradient of its input), the
+                        graph's tables with the padded edge weights and their gradient, and autograd's gradients of
+                        the inputs and of every cell parameter for seeded cotangents of ``(c, b)``.
 * ``chain_*.npz``       two chained windows against the unsplit window of twice the length: the
                         carried state forward, the state cotangent ``(A, R)`` backward.
 
