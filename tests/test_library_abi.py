@@ -80,6 +80,20 @@ def test_no_gpu_means_a_loud_failure_not_a_fallback(lib: ctypes.CDLL) -> None:
     with pytest.raises(RuntimeError):   # the grouped unit pass has no CPU path either
         grouped_forward(torch.zeros(4, 32), torch.zeros(4, dtype=torch.int64), torch.zeros(2, 32, 16), torch.zeros(2, 16),
                         torch.zeros(2, 16, 8), torch.zeros(2, 8))
+    from hsn_b200.kernels.gate import norm_gate_forward
+    from hsn_b200.kernels.messages import messages_forward
+    from hsn_b200.kernels.scorer import scorer_logits_forward
+    from hsn_b200.kernels.tail import tail_forward
+
+    z = torch.zeros
+    with pytest.raises(RuntimeError):   # nor have the other pieces of the replay
+        tail_forward(z(4, 16), torch.ones(4), z(16, 16), torch.ones(16))
+    with pytest.raises(RuntimeError):
+        norm_gate_forward(z(4, 64), torch.ones(64), z(16, 64), z(16))
+    with pytest.raises(RuntimeError):
+        messages_forward(z(2, 16), z(2, 16), z(2, 8, 16), z(2, 1, dtype=torch.int64), z(8, 2, dtype=torch.int64), z(8, 2), z(16, 16))
+    with pytest.raises(RuntimeError):
+        scorer_logits_forward(z(2, 3 * 16 + 1 + 2), z(2), z(3, 16), z(3, 16), z(3, 5, 16), z(3, 5, dtype=torch.int64), z(3, 5, 2), age_max=10.0)
 
 
 def test_python_interface_keeps_the_reference_names() -> None:
