@@ -11,8 +11,9 @@
 // neighbours two shuffles between the lanes that hold them. Backward, per tile: the sources again (cheaper than a
 // record), each row's <d_m, sources_j> to a per-slot buffer, w_j d_m as a bf16 tile, and d_V += (w d_m)^T h[src] with
 // both operands read transposed, a warp keeping its tiles of d_V over all of the block's tiles. The edge weights'
-// gradient is a sum over the slots of each cell: a block a cell scans the window's slots in order (no atomics: the
-// same bits every run); d_u and d_eps are sums over a row's k slots.
+// gradient is a sum over the slots of each cell: every block keeps a table [n_cells][4] in shared memory that four
+// lanes fill in slot order, and the blocks' tables are added in block order (no atomics: the same bits every run; a
+// graph of more than 2048 cells takes a scan per cell instead); d_u and d_eps are sums over a row's k slots.
 #include "../../include/hsn_messages_b200.h"
 #include "../../include/hsn_window_b200.h"
 #include "common.cuh"
@@ -36,7 +37,8 @@ struct MsgShape {
     static constexpr int TILES = MT * NT;
     static constexpr int TPW = (TILES + 7) / 8;
     static constexpr size_t fwd_bytes = sizeof(uint32_t) * (kRows * PW + D * PW) + sizeof(float) * kRows + sizeof(int64_t) * kRows;
-    static constexpr size_t bwd_bytes = sizeof(uint32_t) * (2 * kRows * PW + D * PW) + sizeof(float) * (kRows + kSlots * D) + sizeof(int64_t) * kRows;
+    static constexpr size_t bwd_bytes = sizeof(uint32_t) * (2 * kRows * PW + D * PW) + sizeof(float) * (kRows + kSlots * D + kRows) + sizeof(int) * kSlots
+                                        + sizeof(int64_t) * kRows;   // (+ the table [n_cells][4] with FOLD)
 };
 
 struct Graph {
@@ -131,11 +133,14 @@ k_msg_fwd(const float* __restrict__ v_w, Graph gr, const float* __restrict__ u, 
     }
 }
 
-// `rowval` [slots][4]: <d_m, sources_j> of every slot and neighbour; `partial` [blocks][D D]: the block's share of d_V.
-template <int D>
+// `partial` [blocks][D D]: the block's share of d_V. The rows' <d_m, sources_j> go, with FOLD, into the block's own
+// table [n_cells][4] in shared memory (four lanes, one a neighbour, add a tile's 32 slots in slot order while the other
+// warps multiply) and from there to `edges` [blocks][n_cells][4]; without (a graph too large for the table) to `edges`
+// [slots][4], which a scan per cell sums.
+template <int D, bool FOLD>
 __global__ void __launch_bounds__(kThreads)
 k_msg_bwd(const float* __restrict__ v_w, Graph gr, const float* __restrict__ h, const int64_t* __restrict__ cells,
-          const float* __restrict__ d_v_raw, int64_t slots, float* __restrict__ rowval, float* __restrict__ partial) {
+          const float* __restrict__ d_v_raw, int64_t slots, float* __restrict__ edges, float* __restrict__ partial) {
     using S = MsgShape<D>;
     constexpr int PB = S::PB, PW = S::PW, NT = S::NT, KS = S::KS, MT = S::MT, TILES = S::TILES, TPW = S::TPW;
     extern __shared__ __align__(16) uint32_t smem_w[];
@@ -145,8 +150,13 @@ k_msg_bwd(const float* __restrict__ v_w, Graph gr, const float* __restrict__ h, 
     int64_t* SRC = reinterpret_cast<int64_t*>(Ws + D * PW);       // [kRows]
     float* WE = reinterpret_cast<float*>(SRC + kRows);            // [kRows]
     float* DM = WE + kRows;                                       // [kSlots][D] d_m as bf16 values
+    float* ROWV = DM + kSlots * D;                                // [kRows] <d_m, sources_j> of the tile's rows
+    int* CELL = reinterpret_cast<int*>(ROWV + kRows);             // [kSlots] the tile's cells, -1 beyond the last slot
+    float* ACC = reinterpret_cast<float*>(CELL + kSlots);         // [n_cells][4] (FOLD)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     stage_weight<D>(Ws, v_w, tid);
+    if constexpr (FOLD)
+        for (int e = tid; e < gr.n_cells * 4; e += kThreads) ACC[e] = 0.0f;
     float dv[TPW][4];
 #pragma unroll
     for (int i = 0; i < TPW; ++i)
@@ -158,6 +168,7 @@ k_msg_bwd(const float* __restrict__ v_w, Graph gr, const float* __restrict__ h, 
     for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
         const int64_t first = tile * kSlots;
         __syncthreads();   // the previous tile's reads are over
+        if (FOLD && tid < kSlots) CELL[tid] = first + tid < slots ? static_cast<int>(__ldg(cells + first + tid)) : -1;
         for (int e = tid; e < kSlots * (D / 4); e += kThreads) {
             const int s = e / (D / 4), q = e - s * (D / 4);
             const int64_t p = first + s;
@@ -179,7 +190,11 @@ k_msg_bwd(const float* __restrict__ v_w, Graph gr, const float* __restrict__ h, 
                     sum += bf16r(dm[8 * nt + 2 * t] * bf16r(acc[nt][2 * h2])) + bf16r(dm[8 * nt + 2 * t + 1] * bf16r(acc[nt][2 * h2 + 1]));
                 sum = sum4_lanes(sum);
                 const int64_t p = first + (row >> 2);
-                if (t == 0 && p < slots) rowval[p * 4 + (row & 3)] = bf16r(sum);
+                if constexpr (FOLD) {
+                    if (t == 0) ROWV[row] = bf16r(sum);
+                } else {
+                    if (t == 0 && p < slots) edges[p * 4 + (row & 3)] = bf16r(sum);
+                }
             }
         }
         for (int e = tid; e < kRows * (D / 2); e += kThreads) {
@@ -189,6 +204,12 @@ k_msg_bwd(const float* __restrict__ v_w, Graph gr, const float* __restrict__ h, 
             DS[row * PW + w2] = pack_bf16(dm[0] * w, dm[1] * w);
         }
         __syncthreads();
+        if (FOLD && tid < 4) {   // neighbour tid of every slot of the tile, in slot order
+            for (int s2 = 0; s2 < kSlots; ++s2) {
+                const int c = CELL[s2];
+                if (c >= 0) ACC[c * 4 + tid] += ROWV[4 * s2 + tid];
+            }
+        }
         // d_V[o][e] += sum_rows (w d_m)[row][o] h[src][row][e]: both operands hold the rows along their rows
         const uint16_t* ds16 = reinterpret_cast<const uint16_t*>(DS);
         const uint16_t* hs16 = reinterpret_cast<const uint16_t*>(Hs);
@@ -218,6 +239,34 @@ k_msg_bwd(const float* __restrict__ v_w, Graph gr, const float* __restrict__ h, 
             mine[(m + 8) * D + n] = dv[i][2];
             mine[(m + 8) * D + n + 1] = dv[i][3];
         }
+    }
+    if constexpr (FOLD) {
+        __syncthreads();
+        float* table = edges + static_cast<int64_t>(blockIdx.x) * gr.n_cells * 4;
+        for (int e = tid; e < gr.n_cells * 4; e += kThreads) table[e] = ACC[e];
+    }
+}
+
+// The blocks' tables of the edge weights' gradient added in block order (eight threads an output, then those eight in
+// order), as bf16 values; output e = 4 n + j goes to d_edge_w[n][j] for j < degree.
+__global__ void __launch_bounds__(kThreads)
+k_msg_etable(const float* __restrict__ tables, int blocks, int n_cells, int degree, float* __restrict__ d_edge_w) {
+    __shared__ float part[8][32];
+    const int outputs = n_cells * 4;
+    const int lane = static_cast<int>(threadIdx.x) & 31, w = static_cast<int>(threadIdx.x) >> 5;
+    const int e = static_cast<int>(blockIdx.x) * 32 + lane;
+    float s = 0.0f;
+    if (e < outputs) {
+#pragma unroll 4
+        for (int b = w; b < blocks; b += 8) s += __ldg(tables + static_cast<int64_t>(b) * outputs + e);
+    }
+    part[w][lane] = s;
+    __syncthreads();
+    if (w == 0 && e < outputs && (e & 3) < degree) {
+        float total = part[0][lane];
+#pragma unroll
+        for (int r = 1; r < 8; ++r) total += part[r][lane];
+        d_edge_w[(e >> 2) * degree + (e & 3)] = bf16r(total);
     }
 }
 
@@ -304,7 +353,12 @@ int64_t bwd_blocks(int64_t slots, int sms) {
     return (tiles + rounds - 1) / rounds;
 }
 
-int64_t rowval_bytes(int64_t slots) { return (slots * 4 * static_cast<int64_t>(sizeof(float)) + 255) / 256 * 256; }
+constexpr int kFoldCells = 2048;   // the largest graph whose table [n_cells][4] a block keeps in shared memory
+// The edge buffer: the blocks' tables, or a value per slot and neighbour.
+int64_t edges_bytes(const HsnwMessages* m, int64_t slots, int64_t blocks) {
+    const int64_t floats = m->n_cells <= kFoldCells ? blocks * m->n_cells * 4 : slots * 4;
+    return (floats * static_cast<int64_t>(sizeof(float)) + 255) / 256 * 256;
+}
 bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
 
 }  // namespace
@@ -313,7 +367,8 @@ extern "C" int64_t hsnw_messages_scratch_bytes(const HsnwMessages* msg, int64_t 
     if (!msg || rows < 0 || msg->k < 1 || msg->d < 16 || msg->d > 64) return 0;
     const int64_t slots = rows * msg->k;
     const int sms = std::max(148, hsnw_sm_count_current());
-    return rowval_bytes(slots) + (bwd_blocks(slots, sms) * msg->d * msg->d * static_cast<int64_t>(sizeof(float)) + 255) / 256 * 256;
+    const int64_t blocks = bwd_blocks(slots, sms);
+    return edges_bytes(msg, slots, blocks) + (blocks * msg->d * msg->d * static_cast<int64_t>(sizeof(float)) + 255) / 256 * 256;
 }
 
 extern "C" int hsnw_messages_forward(const HsnwMessages* msg, const float* u, const float* eps, const float* h, const int64_t* cells,
@@ -360,14 +415,19 @@ extern "C" int hsnw_messages_backward(const HsnwMessages* msg, const float* h, c
     if (!aligned16(h) || !aligned16(d_v_raw) || !aligned16(scratch)) return hsnw_fail(HSNW_E_ARG, "messages_backward: tensors and scratch must be 16-byte aligned");
     const int64_t slots = rows * msg->k;
     const Graph gr{msg->edge_w, msg->pad_src, msg->n_cells, msg->degree, msg->k};
-    float* rowval = static_cast<float*>(scratch);
-    float* partial = reinterpret_cast<float*>(static_cast<char*>(scratch) + rowval_bytes(slots));
     const int blocks = static_cast<int>(bwd_blocks(slots, std::max(1, hsnw_sm_count_current())));
+    const bool fold = msg->n_cells <= kFoldCells;
+    // (the scratch was sized for at least as many blocks: the partial sums start behind the larger edge buffer)
+    const int64_t edge_bytes = edges_bytes(msg, slots, bwd_blocks(slots, std::max(148, hsnw_sm_count_current())));
+    float* edges = static_cast<float*>(scratch);
+    float* partial = reinterpret_cast<float*>(static_cast<char*>(scratch) + edge_bytes);
+    const size_t table_bytes = fold ? sizeof(float) * 4 * static_cast<size_t>(msg->n_cells) : 0;
     hsnw_profile_mark(HSNW_K_MSG_BWD, stream);
-    if (cudaMemsetAsync(rowval, 0, static_cast<size_t>(rowval_bytes(slots)), stream) != cudaSuccess) return hsnw_check_launch("messages_backward");
+    if (!fold && cudaMemsetAsync(edges, 0, static_cast<size_t>(edge_bytes), stream) != cudaSuccess) return hsnw_check_launch("messages_backward");
 #define HSNW_MSG_BWD(D) \
     case D: \
-        k_msg_bwd<D><<<static_cast<unsigned>(blocks), kThreads, MsgShape<D>::bwd_bytes, stream>>>(msg->v_w, gr, h, cells, d_v_raw, slots, rowval, partial); \
+        if (fold) k_msg_bwd<D, true><<<static_cast<unsigned>(blocks), kThreads, MsgShape<D>::bwd_bytes + table_bytes, stream>>>(msg->v_w, gr, h, cells, d_v_raw, slots, edges, partial); \
+        else k_msg_bwd<D, false><<<static_cast<unsigned>(blocks), kThreads, MsgShape<D>::bwd_bytes, stream>>>(msg->v_w, gr, h, cells, d_v_raw, slots, edges, partial); \
         break
     switch (d) {
         HSNW_MSG_BWD(16);
@@ -376,7 +436,8 @@ extern "C" int hsnw_messages_backward(const HsnwMessages* msg, const float* h, c
     }
 #undef HSNW_MSG_BWD
     k_msg_vgrad<<<static_cast<unsigned>((d * d + 31) / 32), kThreads, 0, stream>>>(partial, blocks, d * d, d_v_w);
-    k_msg_egrad<<<static_cast<unsigned>(msg->n_cells), kThreads, 0, stream>>>(cells, rowval, slots, msg->degree, d_edge_w);
+    if (fold) k_msg_etable<<<static_cast<unsigned>((msg->n_cells * 4 + 31) / 32), kThreads, 0, stream>>>(edges, blocks, msg->n_cells, msg->degree, d_edge_w);
+    else k_msg_egrad<<<static_cast<unsigned>(msg->n_cells), kThreads, 0, stream>>>(cells, edges, slots, msg->degree, d_edge_w);
     const int64_t outs = rows * 2 * d;
     k_msg_ugrad<<<static_cast<unsigned>((outs + 255) / 256), 256, 0, stream>>>(d_v_raw, rows, msg->k, d, d_u, d_eps);
     return hsnw_check_launch("messages_backward");
@@ -385,7 +446,8 @@ extern "C" int hsnw_messages_backward(const HsnwMessages* msg, const float* h, c
 void hsnw_messages_set_attributes() {
     bool ok = true;
 #define HSNW_MSG_OPT(D) \
-    ok = ok && hsnw_opt_in(reinterpret_cast<const void*>(k_msg_fwd<D>), "msg_fwd") && hsnw_opt_in(reinterpret_cast<const void*>(k_msg_bwd<D>), "msg_bwd")
+    ok = ok && hsnw_opt_in(reinterpret_cast<const void*>(k_msg_fwd<D>), "msg_fwd") && hsnw_opt_in(reinterpret_cast<const void*>(k_msg_bwd<D, true>), "msg_bwd") \
+         && hsnw_opt_in(reinterpret_cast<const void*>(k_msg_bwd<D, false>), "msg_bwd")
     HSNW_MSG_OPT(16);
     HSNW_MSG_OPT(32);
     HSNW_MSG_OPT(64);

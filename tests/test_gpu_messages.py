@@ -53,10 +53,10 @@ def _case(rng, R, N, d, K, D):
     return f(R, d, scale=0.7), f(R, d, scale=0.4), f(R, N, d, scale=0.5), cells, pad_src, edge_w, f(d, d, scale=d**-0.5), f(R, K, 4 * d)
 
 
-@pytest.mark.parametrize("R,N,d,K,D", [(40, 256, 64, 8, 4), (3, 7, 16, 1, 1), (5, 33, 32, 3, 3), (300, 64, 64, 8, 2)])
+@pytest.mark.parametrize("R,N,d,K,D", [(40, 256, 64, 8, 4), (3, 7, 16, 1, 1), (5, 33, 32, 3, 3), (300, 64, 64, 8, 2), (3, 2100, 16, 6, 2)])
 def test_messages_equal_the_oracle(R: int, N: int, d: int, K: int, D: int) -> None:
     """The benchmark's model, one slot and one neighbour, a ragged tile with three neighbours, more tiles than
-    resident blocks."""
+    resident blocks, a graph too large for a block's table of edge sums (the scan per cell)."""
     from hsn_b200.kernels.messages import messages_backward, messages_forward
 
     u, eps, h, cells, pad_src, edge_w, v_w, d_v_raw = _case(np.random.default_rng(R + N + d), R, N, d, K, D)
