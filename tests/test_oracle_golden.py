@@ -497,3 +497,57 @@ def test_replay_messages_equal_the_reference(name: str) -> None:
         np.testing.assert_allclose(got, z[key], rtol=0, atol=tol * float(np.abs(z[key]).max()), err_msg=key)
     if bf:
         assert np.array_equal(v_raw, z["v_raw"]) and np.array_equal(grads[3], z["g_V.weight"])
+
+
+def _numeric(fn, x, eps=1e-6):
+    """Central differences of the scalar ``fn`` at ``x`` (float64), entry by entry."""
+    g = np.zeros_like(x)
+    it = np.nditer(x, flags=["multi_index"])
+    for _ in it:
+        i = it.multi_index
+        keep = x[i]
+        x[i] = keep + eps
+        hi = fn()
+        x[i] = keep - eps
+        lo = fn()
+        x[i] = keep
+        g[i] = (hi - lo) / (2 * eps)
+    return g
+
+
+def test_the_replay_oracles_backwards_are_the_gradients_of_their_forwards() -> None:
+    """Independent of the fixtures: in float64 the three restated backwards of ``replay_sparse``'s steps equal central
+    differences of the restated forwards."""
+    from oracle import gate_oracle as G
+    from oracle import messages_oracle as M
+    from oracle import tail_oracle as T
+
+    rng = np.random.default_rng(7)
+    f = lambda *s, scale=1.0: rng.standard_normal(s) * scale  # noqa: E731
+    # the tail
+    P, d = 5, 6
+    x, alpha, w, g, cot = f(P, d), 1.0 + 0.3 * f(P), f(d, d, scale=0.5), 1.0 + 0.2 * f(d), f(P, d)
+    loss = lambda: float((T.forward_tail(x, alpha, w, g)[0] * cot).sum())  # noqa: E731
+    _, y = T.forward_tail(x, alpha, w, g)
+    got = T.backward_tail(x, alpha, w, g, y, cot)
+    for a, wrt in zip(got, (x, alpha, w, g), strict=True):
+        np.testing.assert_allclose(a, _numeric(loss, wrt), rtol=1e-6, atol=1e-8)
+    # the norm and the gate
+    F = 4 * d
+    vr, nw, gw, gb, dv, db = f(P, F), 1.0 + 0.2 * f(F), f(d, F, scale=0.3), f(d, scale=0.3), f(P, F), f(P, d)
+
+    def loss2():
+        v, _, _, b = G.forward_norm_gate(vr, nw, gw, gb, norm_eps=1e-6)
+        return float((v * dv).sum() + (b * db).sum())
+
+    got = G.backward_norm_gate(vr, nw, gw, gb, dv, db, norm_eps=1e-6)
+    for a, wrt in zip(got, (vr, nw, gw, gb), strict=True):
+        np.testing.assert_allclose(a, _numeric(loss2, wrt), rtol=1e-6, atol=1e-8)
+    # the messages
+    R, N, K, D = 3, 7, 2, 3
+    u, e, h, vw, ew, cot3 = f(R, d), f(R, d), f(R, N, d), f(d, d, scale=0.5), rng.random((N, D)), f(R, K, 4 * d)
+    cells, src = rng.integers(0, N, (R, K)), rng.integers(0, N, (N, D))
+    loss3 = lambda: float((M.forward_messages(u, e, h, cells, src, ew, vw) * cot3).sum())  # noqa: E731
+    got = M.backward_messages(h, cells, src, ew, vw, cot3)
+    for a, wrt in zip(got, (u, e, ew, vw), strict=True):
+        np.testing.assert_allclose(a, _numeric(loss3, wrt), rtol=1e-6, atol=1e-8)
